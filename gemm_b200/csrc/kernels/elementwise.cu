@@ -1,0 +1,332 @@
+// Memory-bound token-wise kernels: embedding gather, RMSNorm (+residual add, + MXFP8 quantisation of
+// the normalised row), per-head QK-RMSNorm + NeoX RoPE + paged KV write, SiLU-gate, MXFP8 activation
+// quantiser with optional row gather, dtype casts.  All are one pass over HBM with 16-byte accesses.
+//
+// Replaces in the reference (cuda/llm/cuda_llm_runner.c): embed_f16:79 / batch_embed_f16:4422,
+// rmsnorm_f32:87 / batch_rmsnorm_f32:8291 / add_f32:465, qknorm_f32:151, rope_neox_f32:180 /
+// batch_rope_neox_f32:8056, kv_cache_store_f16:209 / batch_kv_store_f16:8206, silu_mul_f32:455,
+// quantize_to_fp8_e4m3 (cuda/cuda_fp8_mma_kernels.h).  Numerics follow common/transformer.h:593-637
+// (RMSNorm), :1281-1315 (QK-norm) and :1183-1219 (NeoX RoPE, inv_freq = base^(-2j/d)).
+#include "sm100.cuh"
+#include "host_common.h"
+
+namespace gb {
+
+__device__ __forceinline__ int e8m0_amax(float amax) {
+  const float s = amax * (1.0f / 448.0f);
+  const uint32_t bits = __float_as_uint(s);
+  int e = (int)((bits >> 23) & 0xff);
+  if (bits & 0x7fffffu) e += 1;
+  return max(1, min(e, 254));
+}
+__device__ __forceinline__ size_t sf_atom_offset(int row, int blk32, int k_atoms) {
+  return ((size_t)(row >> 7) * k_atoms + (blk32 >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (blk32 & 3);
+}
+
+struct alignas(16) bf16x8 { __nv_bfloat162 v[4]; };
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
+  bf16x8 r = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { float2 t = __bfloat1622float2(r.v[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
+  bf16x8 r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = r;
+}
+
+// ------------------------------------------------------------------------------------------ embed
+__global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
+                             int n_tok, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ------------------------------------------------------------------------------------------ rmsnorm
+// One CTA per row.  Optional: residual[row] += delta[row] first (the sum is written back and is the
+// normalised input); optional MXFP8 output (e4m3 bytes + scale atoms) beside / instead of bf16.
+template <int VPT>   // 8-element vectors per thread (hidden <= 256 * 8 * VPT)
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ x_in,
+               const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ out_q,
+               uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out) {
+  const int row = blockIdx.x;
+  const int nvec = hidden >> 3;
+  float v[VPT][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      if (residual != nullptr) {
+        float r[8], d[8];
+        load8(residual + (size_t)row * ld_in + vi * 8, r);
+        if (delta != nullptr) {
+          load8(delta + (size_t)row * ld_in + vi * 8, d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[j] = __bfloat162float(__float2bfloat16(r[j] + d[j]));
+          store8(residual + (size_t)row * ld_in + vi * 8, r);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = r[j];
+      } else {
+        load8(x_in + (size_t)row * ld_in + vi * 8, v[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  __shared__ float red[8];
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float scale = rsqrtf(tot / (float)hidden + eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    float w[8], y[8];
+    float amax = 0.f;
+    if (vi < nvec) {
+      load8(weight + vi * 8, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        y[j] = __bfloat162float(__float2bfloat16(v[i][j] * scale * w[j]));
+        amax = fmaxf(amax, fabsf(y[j]));
+      }
+      if (out != nullptr) store8(out + (size_t)row * ld_out + vi * 8, y);
+    }
+    if (out_q != nullptr) {
+      // 4 consecutive threads hold one 32-element block
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      if (vi < nvec) {
+        const int e = e8m0_amax(amax);
+        const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+        uint8_t q[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(y[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
+        *reinterpret_cast<uint2*>(out_q + (size_t)row * hidden + vi * 8) = *reinterpret_cast<uint2*>(q);
+        if ((vi & 3) == 0) out_sf[sf_atom_offset(row, vi >> 2, hidden >> 7)] = (uint8_t)e;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------ qk-norm + rope + kv write
+// One warp per (token, head) over the fused QKV row [Hq*D | Hkv*D | Hkv*D].  Q heads: RMSNorm over D
+// (weight q_w, skipped if null), NeoX rotation of the first 2*rope_pairs dims, written to q_out.
+// K heads: same with k_w, written into the paged cache slot of the token; V heads: copied to the cache.
+// Cache layout: [num_slots, Hkv, D] for K and for V, slot = block * block_size + offset.
+template <int D>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
+                    const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w, __nv_bfloat16* __restrict__ q_out,
+                    __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int n_tok, int hq, int hkv,
+                    int rope_pairs, float theta, float eps, int ld_qkv, float q_scale) {
+  constexpr int EPL = D / 32;            // elements per lane, index = lane + 32 * i
+  const int heads = hq + 2 * hkv;
+  const long gw = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (gw >= (long)n_tok * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int t = (int)(gw / heads), h = (int)(gw % heads);
+  const __nv_bfloat16* src = qkv + (size_t)t * ld_qkv + (size_t)h * D;
+  float x[EPL];
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) x[i] = __bfloat162float(src[lane + 32 * i]);
+  const bool is_q = h < hq, is_k = !is_q && h < hq + hkv;
+  if (is_q || is_k) {
+    const __nv_bfloat16* w = is_q ? q_w : k_w;
+    if (w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) ss += x[i] * x[i];
+      ss = warp_sum(ss);
+      const float sc = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) x[i] = x[i] * sc * __bfloat162float(w[lane + 32 * i]);
+    }
+    const float pos = (float)positions[t];
+    // pair (j, j + rope_pairs) for j < rope_pairs; with full rotary rope_pairs = D/2 = 32 * EPL/2
+    if (2 * rope_pairs == D) {
+#pragma unroll
+      for (int i = 0; i < EPL / 2; ++i) {
+        const int j = lane + 32 * i;
+        const float inv_freq = powf(theta, -2.0f * (float)j / (float)D);
+        float s, c;
+        sincosf(pos * inv_freq, &s, &c);
+        const float a = x[i], b = x[i + EPL / 2];
+        x[i] = a * c - b * s;
+        x[i + EPL / 2] = a * s + b * c;
+      }
+    } else {
+      // partial rotary: pairs may straddle lanes -> go through shuffles of the partner element
+      const float rd = 2.0f * (float)rope_pairs;
+      float xo[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) xo[i] = x[i];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int idx = lane + 32 * i;
+        const bool lo = idx < rope_pairs, hi = idx >= rope_pairs && idx < 2 * rope_pairs;
+        const int pidx = lo ? idx + rope_pairs : idx - rope_pairs;
+        float partner = 0.f;
+#pragma unroll
+        for (int ii = 0; ii < EPL; ++ii) {
+          const float cand = __shfl_sync(0xffffffffu, xo[ii], pidx & 31);
+          if ((pidx >> 5) == ii) partner = cand;
+        }
+        if (lo || hi) {
+          const int j = lo ? idx : idx - rope_pairs;
+          const float inv_freq = powf(theta, -2.0f * (float)j / rd);
+          float s, c;
+          sincosf(pos * inv_freq, &s, &c);
+          x[i] = lo ? (xo[i] * c - partner * s) : (partner * s + xo[i] * c);
+        }
+      }
+    }
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * hq + h) * D;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) x[i] *= q_scale;
+  } else {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int kh = is_k ? h - hq : h - hq - hkv;
+    dst = (is_k ? k_cache : v_cache) + ((size_t)slot * hkv + kh) * D;
+  }
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) dst[lane + 32 * i] = __float2bfloat16(x[i]);
+}
+
+// ------------------------------------------------------------------------------------------ silu * up
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, long rows, int inter, int ld) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vec_per_row = inter >> 3;
+  if (idx >= rows * vec_per_row) return;
+  const long r = idx / vec_per_row;
+  const int c = (int)(idx % vec_per_row) * 8;
+  float g[8], u[8], y[8];
+  load8(gate_up + r * ld + c, g);
+  load8(gate_up + r * ld + inter + c, u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) y[j] = g[j] / (1.0f + __expf(-g[j])) * u[j];
+  store8(out + r * inter + c, y);
+}
+
+// ------------------------------------------------------------------------------------------ mxfp8 quantiser
+// out row r <- in row (src_rows ? src_rows[r] : r); rows whose source is negative are zero-filled with
+// scale 1.  One warp per 256 elements: lane holds 8 elements, 4 lanes share a scale.
+__global__ void __launch_bounds__(256)
+mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src_rows, uint8_t* __restrict__ out_q,
+                uint8_t* __restrict__ out_sf, long out_rows, int k, int ld_in) {
+  const int vec_per_row = k >> 3;
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool act = idx < out_rows * vec_per_row;
+  const long r = act ? idx / vec_per_row : 0;
+  const int vi = act ? (int)(idx % vec_per_row) : 0;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  long src = r;
+  if (act && src_rows != nullptr) src = src_rows[r];
+  if (act && src >= 0) load8(in + src * ld_in + vi * 8, v);
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  if (!act) return;
+  const int e = (src >= 0) ? e8m0_amax(amax) : 127;
+  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+  uint8_t q[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(v[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
+  *reinterpret_cast<uint2*>(out_q + r * k + vi * 8) = *reinterpret_cast<uint2*>(q);
+  if ((vi & 3) == 0) out_sf[sf_atom_offset((int)r, vi >> 2, k >> 7)] = (uint8_t)e;
+}
+
+// ------------------------------------------------------------------------------------------ casts
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16(in[i]);
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+GB_API int gb_embed(const int* ids, const void* table, void* out, int n_tok, int hidden, int vocab, cudaStream_t stream) {
+  if (hidden % 8) return fail("embed: hidden %% 8 != 0%s");
+  if (n_tok <= 0) return 0;
+  embed_kernel<<<n_tok, 128, 0, stream>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, n_tok, hidden, vocab);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// residual (in/out, may be null) += delta (may be null); y = rmsnorm(residual or x_in) * weight.
+// out (bf16) and out_q/out_sf (MXFP8) are optional outputs.
+GB_API int gb_rmsnorm(void* residual, const void* delta, const void* x_in, const void* weight, void* out, void* out_q, void* out_sf,
+                      int rows, int hidden, float eps, int ld_in, int ld_out, cudaStream_t stream) {
+  if (hidden % 8 || hidden > 256 * 8 * 4) return fail("rmsnorm: hidden must be a multiple of 8 and <= 8192%s");
+  if (out_q != nullptr && hidden % 128) return fail("rmsnorm: MXFP8 output needs hidden %% 128 == 0%s");
+  if (rows <= 0) return 0;
+  const int nvec = hidden / 8;
+#define GB_RMS(V) rmsnorm_kernel<V><<<rows, 256, 0, stream>>>((__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, \
+    (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out)
+  if (nvec <= 256) GB_RMS(1); else if (nvec <= 512) GB_RMS(2); else if (nvec <= 768) GB_RMS(3); else GB_RMS(4);
+#undef GB_RMS
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_qk_norm_rope(const void* qkv, const int* positions, const int* slots, const void* q_w, const void* k_w, void* q_out,
+                           void* k_cache, void* v_cache, int n_tok, int hq, int hkv, int head_dim, int rope_pairs, float theta,
+                           float eps, int ld_qkv, float q_scale, cudaStream_t stream) {
+  if (n_tok <= 0) return 0;
+  const long warps = (long)n_tok * (hq + 2 * hkv);
+  const int blocks = (int)((warps + 7) / 8);
+#define GB_QK(DV) qk_norm_rope_kernel<DV><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)qkv, positions, slots, \
+    (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
+    n_tok, hq, hkv, rope_pairs, theta, eps, ld_qkv, q_scale)
+  if (head_dim == 64) GB_QK(64); else if (head_dim == 128) GB_QK(128); else if (head_dim == 256) GB_QK(256);
+  else return fail("qk_norm_rope: head_dim must be 64, 128 or 256%s");
+#undef GB_QK
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_silu_mul(const void* gate_up, void* out, long rows, int inter, int ld, cudaStream_t stream) {
+  if (inter % 8) return fail("silu_mul: inter %% 8 != 0%s");
+  const long n = rows * (inter / 8);
+  if (n <= 0) return 0;
+  silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inter, ld);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_mx_quant(const void* in, const int* src_rows, void* out_q, void* out_sf, long out_rows, int k, int ld_in, cudaStream_t stream) {
+  if (k % 128) return fail("mx_quant: k %% 128 != 0%s");
+  const long n = out_rows * (k / 8);
+  if (n <= 0) return 0;
+  mx_quant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_cast_f32_bf16(const float* in, void* out, long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  cast_f32_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(in, (__nv_bfloat16*)out, n);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,385 @@
+// Persistent tcgen05 GEMM for linear layers:  Out[token, n] = sum_k X[token, k] * W[n, k].
+//
+// Orientation: the WEIGHT matrix is the MMA "A" operand (128 weight rows per tile fill the 128 TMEM
+// lanes) and the TOKENS are the MMA "N" dimension (16..256 per tile).  Decode batches of 8..64
+// tokens therefore waste no tensor-core work, and the same kernel serves prefill with 128/256-token
+// tiles.  Both operands are K-major, staged by TMA into 128-byte-swizzled shared memory; accumulators
+// live in TMEM (double buffered when they fit) and are drained by four epilogue warps.
+//
+// Variants (template parameters):
+//   MODE 0  bf16 x bf16  (kind::f16)
+//   MODE 1  MXFP8: e4m3 x e4m3 with one E8M0 scale per 32 K-elements on both operands
+//           (kind::mxf8f6f4.block_scale; scale factors copied smem -> TMEM with tcgen05.cp)
+//   DUAL    two weight tiles (gate rows, up rows) share one token tile; epilogue = SiLU(gate) * up
+//   grouped (run time)  one weight matrix per group (expert); every group owns a row segment of X
+//           described by device arrays, so no host synchronisation is needed after routing.
+// Epilogues: bf16 / f32 store with optional bias, per-row scale and row scatter; or MXFP8
+// re-quantisation (fp8 bytes + E8M0 scales in the layout MODE 1 consumes) so that the next GEMM
+// reads what this one wrote.
+//
+// Replaces in the reference: the cuBLAS call sites of cuda/llm/cuda_llm_runner.c:15488-17418, the
+// mma.sync GEMMs of cuda/cuda_kernels_common.h, silu_mul_f32 (cuda_llm_runner.c:455), the grouped
+// expert GEMMs of mmq_*_grouped (cuda_llm_runner.c:5295-7329) and m3_gemm_mxfp8 (common/m3_impl.h:791-825).
+#include "sm100.cuh"
+#include "host_common.h"
+
+namespace gb {
+
+constexpr int kMaxGroups = 256;
+constexpr int kGemmThreads = 192;
+
+struct GemmArgs {
+  int n_out;            // output features per group (weight rows of the gate half when DUAL)
+  int k;                // reduction length in elements
+  int m_tok;            // rows of X that exist (plain) / capacity of the segment buffer (grouped)
+  int num_groups;       // 0 = plain GEMM
+  int w_rows_per_group; // weight rows between consecutive groups
+  int up_row_offset;    // DUAL: first "up" row inside a group
+  const int* seg_start; // [G] first X row of each group (multiple of min(TN,128); of 128 for MX), device
+  const int* seg_count; // [G] valid rows of each group, device
+  const uint8_t* sfa;   // MODE 1: weight scales, 512-byte atoms [w_row/128][k/128]
+  const uint8_t* sfb;   // MODE 1: activation scales, 512-byte atoms [x_row/128][k/128]
+  void* out;            // bf16 / f32 [rows, ldo]  or fp8 bytes [rows, ldo] for the quantising epilogue
+  int ldo;
+  int out_f32;
+  uint8_t* out_sf;      // quantising epilogue: scale atoms [x_row/128][n/128]
+  const float* bias;    // optional [n_out] (plain, per group not supported)
+  const int* row_map;   // optional: output row of X row r (negative = drop)
+  const float* row_scale; // optional: multiply row r of the result
+  int stages;
+  KernelStatus* status;
+};
+
+struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; };
+
+// Maps the linear tile index of the persistent loop to a tile.  Every warp role walks the same
+// sequence, so each keeps its own cursor.  n-blocks vary fastest: CTAs that run at the same time
+// share one token tile (L2 reuse) and stream different weight rows.
+template <int TN>
+struct TileCursor {
+  int g = 0, base = 0;
+  __device__ __forceinline__ bool get(const GemmArgs& a, const int* s_start, const int* s_count, int t, Tile& o) {
+    const int n_blocks = (a.n_out + 127) >> 7;
+    if (a.num_groups == 0) {
+      const int tok_blocks = (a.m_tok + TN - 1) / TN;
+      if (t >= n_blocks * tok_blocks) return false;
+      const int nb = t % n_blocks, tb = t / n_blocks;
+      o.n0 = nb * 128; o.w_row0 = o.n0; o.w_row1 = a.up_row_offset + o.n0;
+      o.x_row0 = tb * TN; o.valid = min(TN, a.m_tok - o.x_row0); o.out_row0 = o.x_row0;
+      return true;
+    }
+    while (g < a.num_groups) {
+      const int tiles_g = ((s_count[g] + TN - 1) / TN) * n_blocks;
+      if (t < base + tiles_g) {
+        const int lt = t - base;
+        const int nb = lt % n_blocks, tb = lt / n_blocks;
+        o.n0 = nb * 128;
+        o.w_row0 = g * a.w_rows_per_group + o.n0;
+        o.w_row1 = o.w_row0 + a.up_row_offset;
+        o.x_row0 = s_start[g] + tb * TN;
+        o.valid = min(TN, s_count[g] - tb * TN);
+        o.out_row0 = o.x_row0;
+        return true;
+      }
+      base += tiles_g; ++g;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+// E8M0 exponent for a block whose absolute maximum is `amax`: the smallest power of two s with
+// amax / s <= 448 (largest e4m3 magnitude), so quantisation never saturates.
+__device__ __forceinline__ int e8m0_from_amax(float amax) {
+  const float s = amax * (1.0f / 448.0f);
+  uint32_t bits = __float_as_uint(s);
+  int e = (int)((bits >> 23) & 0xff);
+  if (bits & 0x7fffffu) e += 1;
+  return max(1, min(e, 254));
+}
+
+template <int TN, int MODE, bool DUAL, bool QUANT_OUT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmArgs args) {
+  constexpr int NA = DUAL ? 2 : 1;
+  constexpr int A_BYTES = 128 * 128;                 // 128 rows x 128 bytes
+  constexpr int B_BYTES = TN * 128;
+  constexpr int SFB_ATOMS = (TN + 127) / 128;
+  constexpr int SF_BYTES = (MODE == 1) ? (((NA + SFB_ATOMS) * 512 + 1023) & ~1023) : 0;
+  constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + SF_BYTES;
+  constexpr int ACC_COLS = NA * TN;
+  constexpr int SF_COLS = (MODE == 1) ? (NA * 4 + SFB_ATOMS * 4) : 0;
+  constexpr int NACC = (2 * ACC_COLS + SF_COLS <= 512) ? 2 : 1;
+  constexpr int NEED_COLS = NACC * ACC_COLS + SF_COLS;
+  constexpr int TMEM_COLS = NEED_COLS <= 32 ? 32 : NEED_COLS <= 64 ? 64 : NEED_COLS <= 128 ? 128 : NEED_COLS <= 256 ? 256 : 512;
+  static_assert(NEED_COLS <= 512, "accumulators do not fit TMEM");
+  constexpr int KB_ELEMS = (MODE == 1) ? 128 : 64;   // K elements per 128-byte row
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const int S = args.stages;
+  uint8_t* tail = smem + (size_t)S * STAGE_BYTES;
+  uint64_t* full_bar = (uint64_t*)tail;              // [S]
+  uint64_t* empty_bar = full_bar + S;                // [S]
+  uint64_t* accf_bar = empty_bar + S;                // [2] accumulator full
+  uint64_t* acce_bar = accf_bar + 2;                 // [2] accumulator empty
+  uint32_t* tmem_slot = (uint32_t*)(acce_bar + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  int* s_start = (int*)(tmem_slot + 4);
+  int* s_count = s_start + kMaxGroups;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (args.k + KB_ELEMS - 1) / KB_ELEMS;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&accf_bar[i], 1); mbar_init(&acce_bar[i], 4); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX);
+  }
+  for (int i = threadIdx.x; i < args.num_groups; i += blockDim.x) { s_start[i] = args.seg_start[i]; s_count[i] = args.seg_count[i]; }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_sf = tmem_base + NACC * ACC_COLS;   // SFA0 [, SFA1], SFB columns
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (one lane)
+    if (lane == 0) {
+      TileCursor<TN> cur; Tile t;
+      int s = 0; uint32_t ph = 0;
+      bool ok = true;
+      for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 100, s)) { ok = false; break; }
+          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], NA * A_BYTES + B_BYTES + ((MODE == 1) ? (NA + SFB_ATOMS) * 512 : 0));
+          const int kx = kb * KB_ELEMS;
+          tma_load_2d(st, &tmW, &full_bar[s], kx, t.w_row0);
+          if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], kx, t.w_row1);
+          tma_load_2d(st + NA * A_BYTES, &tmX, &full_bar[s], kx, t.x_row0);
+          if (MODE == 1) {
+            uint8_t* sf = st + NA * A_BYTES + B_BYTES;
+            const size_t kbs = (size_t)num_kb;
+            bulk_load(sf, args.sfa + ((size_t)(t.w_row0 >> 7) * kbs + kb) * 512, 512, &full_bar[s]);
+            if (DUAL) bulk_load(sf + 512, args.sfa + ((size_t)(t.w_row1 >> 7) * kbs + kb) * 512, 512, &full_bar[s]);
+#pragma unroll
+            for (int i = 0; i < SFB_ATOMS; ++i)
+              bulk_load(sf + (NA + i) * 512, args.sfb + ((size_t)((t.x_row0 >> 7) + i) * kbs + kb) * 512, 512, &full_bar[s]);
+          }
+          if (++s == S) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (one lane)
+    if (lane == 0) {
+      TileCursor<TN> cur; Tile t;
+      int s = 0; uint32_t ph = 0;
+      int acc = 0; uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
+        if (!mbar_wait(&acce_bar[acc], acc_ph ^ 1, abort_flag, args.status, 200, acc)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + acc * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[s], ph, abort_flag, args.status, 201, s)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          uint32_t sfb_t = 0;
+          if (MODE == 1) {
+            const uint32_t sf = st + NA * A_BYTES + B_BYTES;
+            tc_cp_32x128b_warpx4(tmem_sf, make_sdesc_noswizzle(sf, 0, 128));
+            if (DUAL) tc_cp_32x128b_warpx4(tmem_sf + 4, make_sdesc_noswizzle(sf + 512, 0, 128));
+#pragma unroll
+            for (int i = 0; i < SFB_ATOMS; ++i)
+              tc_cp_32x128b_warpx4(tmem_sf + NA * 4 + i * 4, make_sdesc_noswizzle(sf + (NA + i) * 512, 0, 128));
+            sfb_t = tmem_sf + NA * 4;   // token tiles of MX GEMMs always start on a 128-row boundary
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t a0 = make_sdesc_sw128(st + j * 32);
+            const uint64_t b = make_sdesc_sw128(st + NA * A_BYTES + j * 32);
+            const uint32_t accum = (kb > 0 || j > 0) ? 1u : 0u;
+            if (MODE == 0) {
+              constexpr uint32_t idesc = make_idesc(128, TN, 1, 1);
+              mma_f16_ss(d0, a0, b, idesc, accum);
+              if (DUAL) mma_f16_ss(d0 + TN, make_sdesc_sw128(st + A_BYTES + j * 32), b, idesc, accum);
+            } else {
+              const uint32_t idesc = make_idesc_mx(128, TN, 0, 0, j, j);
+              mma_mxf8_ss(d0, a0, b, idesc, accum, tmem_sf, sfb_t);
+              if (DUAL) mma_mxf8_ss(d0 + TN, make_sdesc_sw128(st + A_BYTES + j * 32), b, idesc, accum, tmem_sf + 4, sfb_t);
+            }
+          }
+          tc_commit(&empty_bar[s]);
+          if (++s == S) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&accf_bar[acc]);
+        if (NACC == 2) { if (++acc == 2) { acc = 0; acc_ph ^= 1; } } else { acc_ph ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;                       // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;                // weight row inside the tile == output feature
+    TileCursor<TN> cur; Tile t;
+    int acc = 0; uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
+      if (!mbar_wait(&accf_bar[acc], acc_ph, abort_flag, args.status, 300, acc)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tacc = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      const int n = t.n0 + row;
+      const bool n_ok = n < args.n_out;
+      const float bias = (args.bias != nullptr && n_ok) ? args.bias[n] : 0.0f;
+#pragma unroll 1
+      for (int c = 0; c < TN; c += 16) {
+        uint32_t r0[16], r1[16];
+        tmem_ld_x16(tacc + c, r0);
+        if (DUAL) tmem_ld_x16(tacc + TN + c, r1);
+        tc_wait_ld();
+        if (c >= t.valid) continue;             // uniform across the CTA's epilogue warps
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int xr = c + j;
+          float v = __uint_as_float(r0[j]);
+          if (DUAL) v = silu_f(v) * __uint_as_float(r1[j]);
+          v += bias;
+          const bool live = xr < t.valid;
+          const int x_row = t.x_row0 + xr;
+          if (QUANT_OUT) {
+            // 32 lanes of this warp = one 32-wide block along n of one token: shared E8M0 scale.
+            float amax = warp_max(n_ok ? fabsf(v) : 0.0f);
+            const int e = e8m0_from_amax(amax);
+            const float inv = __uint_as_float((uint32_t)(254 - e) << 23);   // 2^(127-e)
+            if (live) {
+              if (n_ok) {
+                __nv_fp8_e4m3 f8(v * inv);
+                ((uint8_t*)args.out)[(size_t)x_row * args.ldo + n] = *(uint8_t*)&f8;
+              }
+              if (lane == 0) {
+                const size_t nkb = (size_t)((args.n_out + 127) >> 7);
+                args.out_sf[((size_t)(x_row >> 7) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + ((x_row >> 5) & 3) * 4 + q] = (uint8_t)e;
+              }
+            }
+          } else if (live && n_ok) {
+            int orow = x_row;
+            if (args.row_map != nullptr) orow = args.row_map[x_row];
+            if (orow >= 0) {
+              if (args.row_scale != nullptr) v *= args.row_scale[x_row];
+              if (args.out_f32) ((float*)args.out)[(size_t)orow * args.ldo + n] = v;
+              else ((__nv_bfloat16*)args.out)[(size_t)orow * args.ldo + n] = __float2bfloat16(v);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acce_bar[acc]);
+      if (NACC == 2) { if (++acc == 2) { acc = 0; acc_ph ^= 1; } } else { acc_ph ^= 1; }
+    }
+  }
+
+  // Teardown.  After an abort, copies may still be landing in shared memory: give them a bounded
+  // grace period before the CTA (and its shared memory) goes away.
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+template <int TN, int MODE, bool DUAL, bool QUANT_OUT>
+static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmArgs a, int max_tiles, cudaStream_t stream) {
+  constexpr int NA = DUAL ? 2 : 1;
+  constexpr int SFB_ATOMS = (TN + 127) / 128;
+  constexpr int STAGE_BYTES = NA * 16384 + TN * 128 + ((MODE == 1) ? (((NA + SFB_ATOMS) * 512 + 1023) & ~1023) : 0);
+  const int tail = 1024 + 2 * kMaxGroups * 4 + 256;
+  int stages = (int)((220 * 1024 - tail - 1024) / STAGE_BYTES);
+  if (stages > 8) stages = 8;
+  if (stages < 2) return fail("gemm: tile does not fit shared memory%s");
+  a.stages = stages;
+  const int smem = stages * STAGE_BYTES + tail + 1024;
+  auto kern = gemm_tc_kernel<TN, MODE, DUAL, QUANT_OUT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+    attr_set = true;
+  }
+  int grid = sm_count();
+  if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
+  kern<<<grid, kGemmThreads, smem, stream>>>(tmW, tmX, a);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+// Flags of gb_gemm.
+enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8 };
+
+// Linear layer on tensor cores.
+//   w        [w_rows, k] row-major (bf16, or e4m3 bytes when GEMM_MX), w_rows = groups * w_rows_per_group
+//   x        [x_rows, k] row-major, same element type as w
+//   out      [*, ldo]    bf16 (default), f32 (GEMM_OUT_F32) or e4m3 + out_sf (GEMM_QUANT_OUT)
+//   tn       token tile: 16, 32, 64, 128 or 256 (256: bf16 non-DUAL only)
+// Grouped mode (num_groups > 0): seg_start / seg_count are device arrays; seg_start[g] must be a
+// multiple of min(tn, 128); `max_rows` bounds the segment buffer (TMA extent).
+GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, int m_tok, int ldw, int ldx, int ldo,
+                   int flags, int tn, int num_groups, int w_rows_per_group, int up_row_offset, const int* seg_start,
+                   const int* seg_count, int x_rows, const void* sfa, const void* sfb, void* out_sf, const float* bias,
+                   const int* row_map, const float* row_scale, void* status, cudaStream_t stream) {
+  const bool mx = flags & GEMM_MX, dual = flags & GEMM_DUAL, qo = flags & GEMM_QUANT_OUT;
+  if (num_groups > kMaxGroups) return fail("gemm: too many groups%s");
+  if (mx && (k % 128 != 0)) return fail("gemm: MXFP8 needs k %% 128 == 0%s");
+  if (mx && tn < 32) return fail("gemm: MXFP8 needs a token tile of at least 32%s");
+  // The scale factors of a token tile must start at column 0 of their 4-column TMEM block (an MMA whose
+  // scale address pointed at column 1..3 raised "misaligned address"), so every MX token tile starts on a
+  // 128-row boundary: narrow tiles only for a single token block, grouped segments 128-aligned with tn = 128.
+  if (mx && num_groups == 0 && tn < 128 && m_tok > tn) return fail("gemm: MXFP8 with tn < 128 needs m_tok <= tn%s");
+  if (mx && num_groups > 0 && tn != 128) return fail("gemm: grouped MXFP8 needs tn == 128 (segments aligned to 128 rows)%s");
+  if (!mx && (k % 8 != 0)) return fail("gemm: bf16 needs k %% 8 == 0%s");
+  if ((mx || num_groups > 0 || dual) && (n_out % 128 != 0)) return fail("gemm: n_out must be a multiple of 128 for MX / grouped / dual%s");
+  const int esz = mx ? 1 : 2;
+  const long w_rows = (num_groups > 0) ? (long)num_groups * w_rows_per_group : (dual ? (long)up_row_offset + n_out : (long)n_out);
+  CUtensorMap tmW, tmX;
+  const TmapDtype dt = mx ? TM_U8 : TM_BF16;
+  const uint32_t box_k = mx ? 128 : 64;
+  if (make_tmap_2d(&tmW, w, dt, (uint64_t)k, (uint64_t)w_rows, (uint64_t)ldw * esz, box_k, 128, TM_SW_128)) return -1;
+  if (make_tmap_2d(&tmX, x, dt, (uint64_t)k, (uint64_t)x_rows, (uint64_t)ldx * esz, box_k, (uint32_t)tn, TM_SW_128)) return -1;
+  GemmArgs a;
+  memset(&a, 0, sizeof(a));
+  a.n_out = n_out; a.k = k; a.m_tok = m_tok; a.num_groups = num_groups; a.w_rows_per_group = w_rows_per_group;
+  a.up_row_offset = up_row_offset; a.seg_start = seg_start; a.seg_count = seg_count;
+  a.sfa = (const uint8_t*)sfa; a.sfb = (const uint8_t*)sfb; a.out = out; a.ldo = ldo; a.out_f32 = (flags & GEMM_OUT_F32) ? 1 : 0;
+  a.out_sf = (uint8_t*)out_sf; a.bias = bias; a.row_map = row_map; a.row_scale = row_scale; a.status = (KernelStatus*)status;
+  int max_tiles = 0;
+  if (num_groups == 0) max_tiles = ((n_out + 127) / 128) * ((m_tok + tn - 1) / tn);
+  if (num_groups == 0 && m_tok <= 0) return 0;
+
+#define GB_DISPATCH(TNV)                                                                                      \
+  if (tn == TNV) {                                                                                            \
+    if (!mx && !dual && !qo) return launch_gemm<TNV, 0, false, false>(tmW, tmX, a, max_tiles, stream);        \
+    if (!mx && dual && !qo) return launch_gemm<TNV, 0, true, false>(tmW, tmX, a, max_tiles, stream);          \
+    if (mx && !dual && !qo) return launch_gemm<TNV, 1, false, false>(tmW, tmX, a, max_tiles, stream);         \
+    if (mx && dual && qo) return launch_gemm<TNV, 1, true, true>(tmW, tmX, a, max_tiles, stream);             \
+    if (mx && dual && !qo) return launch_gemm<TNV, 1, true, false>(tmW, tmX, a, max_tiles, stream);           \
+    if (!mx && dual && qo) return launch_gemm<TNV, 0, true, true>(tmW, tmX, a, max_tiles, stream);            \
+  }
+  GB_DISPATCH(16)
+  GB_DISPATCH(32)
+  GB_DISPATCH(64)
+  GB_DISPATCH(128)
+  if (tn == 256 && !mx && !dual && !qo) return launch_gemm<256, 0, false, false>(tmW, tmX, a, max_tiles, stream);
+#undef GB_DISPATCH
+  return fail("gemm: unsupported variant%s (tn=%ld flags=%ld)", "", (long)tn, (long)flags);
+}

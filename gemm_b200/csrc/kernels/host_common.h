@@ -1,0 +1,49 @@
+// Host-side helpers shared by the kernel launchers: error strings, TMA descriptor encoding through
+// the driver entry point (no link-time dependency on libcuda), launch configuration.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#define GB_API extern "C" __attribute__((visibility("default")))
+
+namespace gb {
+
+// Last error message of this thread; returned by gb_last_error().
+char* last_error_buf();
+
+inline int fail(const char* fmt, const char* a = "", long b = 0, long c = 0) {
+  snprintf(last_error_buf(), 512, fmt, a, b, c);
+  return -1;
+}
+
+#define GB_CUDA_OK(expr)                                                                    \
+  do {                                                                                      \
+    cudaError_t _e = (expr);                                                                \
+    if (_e != cudaSuccess) {                                                                \
+      snprintf(gb::last_error_buf(), 512, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return -1;                                                                            \
+    }                                                                                       \
+  } while (0)
+
+enum TmapDtype { TM_U8 = 0, TM_BF16 = 1, TM_F16 = 2, TM_F32 = 3, TM_U32 = 4 };
+enum TmapSwizzle { TM_SW_NONE = 0, TM_SW_32 = 1, TM_SW_64 = 2, TM_SW_128 = 3 };
+
+// Encode a tiled tensor map of rank 2..4.  dims / box are in elements, innermost first; strides are in
+// bytes for dims 1.. (dim 0 is contiguous).  Returns 0 on success.
+int make_tmap(CUtensorMap* out, const void* base, TmapDtype dt, int rank, const uint64_t* dims,
+              const uint64_t* strides_bytes, const uint32_t* box, TmapSwizzle sw);
+
+inline int make_tmap_2d(CUtensorMap* out, const void* base, TmapDtype dt, uint64_t inner, uint64_t outer,
+                        uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, TmapSwizzle sw) {
+  uint64_t dims[2] = {inner, outer};
+  uint64_t strides[1] = {row_stride_bytes};
+  uint32_t box[2] = {box_inner, box_outer};
+  return make_tmap(out, base, dt, 2, dims, strides, box, sw);
+}
+
+int sm_count();   // SMs of the current device (cached per device)
+
+}  // namespace gb

@@ -1,0 +1,175 @@
+"""Linear layers on the tcgen05 GEMM kernel (csrc/kernels/gemm_tc.cu) and their PyTorch references.
+
+``linear`` / ``linear_mx`` / ``grouped_*`` run the CUDA kernel when the tensors live on a GPU and the
+fp32 PyTorch reference on CPU tensors (the CPU path exists for tests and for the CPU engine; there is
+no silent fallback on a GPU: a missing library raises).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _native
+from . import mxfp8
+from .mxfp8 import MxTensor
+
+GEMM_MX, GEMM_DUAL, GEMM_QUANT_OUT, GEMM_OUT_F32 = 1, 2, 4, 8
+
+_c = ctypes.c_void_p
+_i = ctypes.c_int
+
+
+def _p(t: Optional[torch.Tensor]):
+    return _c(t.data_ptr()) if t is not None else _c(0)
+
+
+def _stream():
+    return _c(torch.cuda.current_stream().cuda_stream)
+
+
+def pick_tn(m_tok: int, mx: bool = False, dual: bool = False) -> int:
+    """Token-tile width: the smallest supported tile that covers the batch, capped by TMEM capacity."""
+    lo = 32 if mx else 16
+    hi = 128 if (mx or dual) else 256
+    tn = lo
+    while tn < hi and tn < m_tok:
+        tn *= 2
+    return tn
+
+
+def _launch(w, x, out, n_out, k, m_tok, ldw, ldx, ldo, flags, tn, num_groups=0, w_rows_per_group=0, up_row_offset=0,
+            seg_start=None, seg_count=None, x_rows=None, sfa=None, sfb=None, out_sf=None, bias=None, row_map=None,
+            row_scale=None):
+    lib = _native.cuda()
+    rc = lib.gb_gemm(_p(w), _p(x), _p(out), _i(n_out), _i(k), _i(m_tok), _i(ldw), _i(ldx), _i(ldo), _i(flags), _i(tn),
+                     _i(num_groups), _i(w_rows_per_group), _i(up_row_offset), _p(seg_start), _p(seg_count),
+                     _i(x_rows if x_rows is not None else m_tok), _p(sfa), _p(sfb), _p(out_sf), _p(bias), _p(row_map),
+                     _p(row_scale), _c(_native.status_ptr()), _stream())
+    _native.check(rc, "gb_gemm")
+
+
+# --------------------------------------------------------------------------------------------- bf16
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+           out_dtype=torch.bfloat16, tn: Optional[int] = None) -> torch.Tensor:
+    """``x [M, K] @ w[N, K]^T`` (bf16 operands, fp32 accumulate)."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not x.is_cuda:
+        y = x.float() @ w.float().t()
+        if bias is not None:
+            y = y + bias.float()
+        return y.to(out_dtype)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=x.device)
+    flags = GEMM_OUT_F32 if out.dtype == torch.float32 else 0
+    _launch(w, x, out, n, k, m, w.stride(0), x.stride(0), out.stride(0), flags, tn or pick_tn(m), bias=bias)
+    return out
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None,
+                  tn: Optional[int] = None) -> torch.Tensor:
+    """``silu(x @ Wg^T) * (x @ Wu^T)`` with ``w_gate_up = [Wg; Wu]`` stacked along rows ([2I, K])."""
+    m, k = x.shape
+    inter = w_gate_up.shape[0] // 2
+    if not x.is_cuda:
+        y = x.float() @ w_gate_up.float().t()
+        return (torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]).to(torch.bfloat16)
+    if out is None:
+        out = torch.empty(m, inter, dtype=torch.bfloat16, device=x.device)
+    _launch(w_gate_up, x, out, inter, k, m, w_gate_up.stride(0), x.stride(0), out.stride(0), GEMM_DUAL,
+            tn or pick_tn(m, dual=True), up_row_offset=inter)
+    return out
+
+
+# --------------------------------------------------------------------------------------------- mxfp8
+def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+              tn: Optional[int] = None) -> torch.Tensor:
+    """Block-scaled fp8 linear: both operands MXFP8, bf16 (or f32) result [x.rows, w.rows]."""
+    if not x.data.is_cuda:
+        return (mxfp8.dequantize(x) @ mxfp8.dequantize(w).t()).to(out_dtype)
+    m, n, k = x.rows, w.rows, w.k
+    if out is None:
+        out = torch.empty(m, n, dtype=out_dtype, device=x.data.device)
+    flags = GEMM_MX | (GEMM_OUT_F32 if out.dtype == torch.float32 else 0)
+    _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn or pick_tn(m, mx=True), x_rows=x.data.shape[0],
+            sfa=w.sf, sfb=x.sf)
+    return out
+
+
+def linear_mx_swiglu_quant(x: MxTensor, w_gate_up: MxTensor, tn: Optional[int] = None) -> MxTensor:
+    """MXFP8 gate/up projection with SiLU(gate)*up and re-quantisation to MXFP8 in the epilogue."""
+    inter = w_gate_up.rows // 2
+    if not x.data.is_cuda:
+        y = mxfp8.dequantize(x) @ mxfp8.dequantize(w_gate_up).t()
+        h = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+        return mxfp8.quantize(h)
+    rows_p = x.data.shape[0]
+    out = torch.zeros(rows_p, inter, dtype=torch.uint8, device=x.data.device)
+    out_sf = torch.full((rows_p // 128, inter // 128, 512), 127, dtype=torch.uint8, device=x.data.device)
+    _launch(w_gate_up.data, x.data, out, inter, x.k, x.rows, x.k, x.k, inter, GEMM_MX | GEMM_DUAL | GEMM_QUANT_OUT,
+            tn or pick_tn(x.rows, mx=True, dual=True), up_row_offset=inter, x_rows=rows_p, sfa=w_gate_up.sf, sfb=x.sf,
+            out_sf=out_sf)
+    return MxTensor(out, out_sf, x.rows, inter)
+
+
+# --------------------------------------------------------------------------------------------- grouped
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, seg_count: torch.Tensor, tn: int,
+                   out: Optional[torch.Tensor] = None, dual: bool = False, row_map: Optional[torch.Tensor] = None,
+                   row_scale: Optional[torch.Tensor] = None, sfa=None, sfb=None, quant_out: bool = False,
+                   out_sf: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One GEMM per group over row segments of ``x``.
+
+    ``w`` is ``[G, R, K]`` (R = 2I stacked gate/up rows when ``dual``); group g multiplies the rows
+    ``seg_start[g] : seg_start[g] + seg_count[g]`` of ``x``.  ``seg_start`` entries must be multiples of
+    ``min(tn, 128)``.  With ``sfa``/``sfb`` the operands are e4m3 bytes with scale atoms (MXFP8); that mode
+    needs ``tn == 128`` and 128-aligned segments.
+    """
+    g, r, k = w.shape
+    n_out = r // 2 if dual else r
+    mx = sfa is not None
+    if not x.is_cuda:
+        return _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out)
+    flags = (GEMM_MX if mx else 0) | (GEMM_DUAL if dual else 0) | (GEMM_QUANT_OUT if quant_out else 0)
+    if out is None:
+        if quant_out:
+            out = torch.zeros(x.shape[0], n_out, dtype=torch.uint8, device=x.device)
+        else:
+            out = torch.empty(x.shape[0], n_out, dtype=torch.bfloat16, device=x.device)
+    if out.dtype == torch.float32:
+        flags |= GEMM_OUT_F32
+    _launch(w, x, out, n_out, k, x.shape[0], k, x.stride(0), out.stride(0), flags, tn, num_groups=g, w_rows_per_group=r,
+            up_row_offset=n_out if dual else 0, seg_start=seg_start, seg_count=seg_count, x_rows=x.shape[0], sfa=sfa,
+            sfb=sfb, out_sf=out_sf, row_map=row_map, row_scale=row_scale)
+    return out
+
+
+def _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out):
+    g, r, k = w.shape
+    n_out = r // 2 if dual else r
+    if sfa is not None:
+        wf = mxfp8.dequantize_rowmajor(w.reshape(g * r, k), mxfp8.unpack_sf_atoms(sfa, g * r, k // 32)).reshape(g, r, k)
+        xf = mxfp8.dequantize_rowmajor(x, mxfp8.unpack_sf_atoms(sfb, x.shape[0], k // 32))
+    else:
+        wf, xf = w.float(), x.float()
+    res = torch.zeros(x.shape[0], n_out, dtype=torch.float32)
+    for gi in range(g):
+        s, c = int(seg_start[gi]), int(seg_count[gi])
+        if c == 0:
+            continue
+        y = xf[s:s + c] @ wf[gi].t()
+        if dual:
+            y = torch.nn.functional.silu(y[:, :n_out]) * y[:, n_out:]
+        res[s:s + c] = y
+    if quant_out:
+        return res
+    if row_scale is not None:
+        res = res * row_scale.float().unsqueeze(-1)
+    if row_map is not None:
+        assert out is not None
+        keep = row_map >= 0
+        out[row_map[keep].long()] = res[keep].to(out.dtype)
+        return out
+    return res.to(torch.bfloat16)

@@ -1,0 +1,111 @@
+"""tcgen05 GEMM kernel vs a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+from gemm_b200 import _native
+from gemm_b200.ops import gemm, mxfp8
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 256, 512), (16, 128, 64), (37, 384, 1024), (64, 5120, 2048), (130, 200, 264),
+                                   (300, 1024, 4096), (1024, 2048, 2048)])
+def test_linear_bf16(m, n, k):
+    torch.manual_seed(0)
+    x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    y = gemm.linear(x, w)
+    ref = x.float() @ w.float().t()
+    _native.assert_status_ok()
+    assert _rel(y, ref) < 1e-2
+
+
+def test_linear_bias_f32_out():
+    torch.manual_seed(1)
+    x = torch.randn(20, 256, device="cuda").bfloat16()
+    w = torch.randn(130, 256, device="cuda").bfloat16()
+    b = torch.randn(130, device="cuda")
+    y = gemm.linear(x, w, bias=b, out_dtype=torch.float32)
+    ref = x.float() @ w.float().t() + b
+    _native.assert_status_ok()
+    assert _rel(y, ref) < 1e-3
+
+
+@pytest.mark.parametrize("m,inter,k", [(8, 128, 256), (100, 768, 2048), (512, 1536, 1024)])
+def test_linear_swiglu(m, inter, k):
+    torch.manual_seed(2)
+    x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(2 * inter, k, device="cuda") * 0.05).bfloat16()
+    y = gemm.linear_swiglu(x, w)
+    r = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(r[:, :inter]) * r[:, inter:]
+    _native.assert_status_ok()
+    assert _rel(y, ref) < 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 128, 128), (32, 256, 512), (70, 768, 2048), (256, 2048, 768), (1000, 512, 1024)])
+def test_linear_mxfp8(m, n, k):
+    torch.manual_seed(3)
+    x = torch.randn(m, k, device="cuda") * torch.rand(m, 1, device="cuda") * 4
+    w = torch.randn(n, k, device="cuda") * 0.05
+    xq, wq = mxfp8.quantize(x), mxfp8.quantize(w)
+    y = gemm.linear_mx(xq, wq, out_dtype=torch.float32)
+    ref = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t()
+    _native.assert_status_ok()
+    assert _rel(y, ref) < 2e-3
+
+
+@pytest.mark.parametrize("m,inter,k", [(8, 128, 256), (100, 768, 2048)])
+def test_mx_swiglu_quant_epilogue(m, inter, k):
+    torch.manual_seed(4)
+    x = torch.randn(m, k, device="cuda")
+    w = torch.randn(2 * inter, k, device="cuda") * 0.05
+    xq, wq = mxfp8.quantize(x), mxfp8.quantize(w)
+    hq = gemm.linear_mx_swiglu_quant(xq, wq)
+    r = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t()
+    ref = torch.nn.functional.silu(r[:, :inter]) * r[:, inter:]
+    _native.assert_status_ok()
+    got = mxfp8.dequantize(hq)
+    assert _rel(got, ref) < 5e-2          # e4m3 has 3 mantissa bits
+    # scales must be the ones the reference quantiser picks for (nearly) the same values
+    ref_q = mxfp8.quantize(ref)
+    e_ref = mxfp8.unpack_sf_atoms(ref_q.sf, m, inter // 32).int()
+    e_got = mxfp8.unpack_sf_atoms(hq.sf, m, inter // 32).int()
+    assert (e_ref - e_got).abs().max().item() <= 1
+
+
+@pytest.mark.parametrize("mx", [False, True])
+def test_grouped(mx):
+    torch.manual_seed(5)
+    g, inter, k = 6, 256, 512
+    tn = 128 if mx else 32
+    counts = torch.tensor([5, 0, 140, 32, 1, 17], dtype=torch.int32)
+    starts = torch.zeros(g, dtype=torch.int32)
+    pos = 0
+    for i in range(g):
+        starts[i] = pos
+        pos += (int(counts[i]) + tn - 1) // tn * tn
+    rows = (pos + 127) // 128 * 128
+    x = torch.randn(rows, k, device="cuda")
+    w = torch.randn(g, 2 * inter, k, device="cuda") * 0.05
+    sd, cd = starts.cuda(), counts.cuda()
+    if mx:
+        xq = mxfp8.quantize(x)
+        wq = mxfp8.quantize(w.reshape(g * 2 * inter, k))
+        y = gemm.grouped_linear(xq.data, wq.data.reshape(g, 2 * inter, k), sd, cd, tn, dual=True, sfa=wq.sf, sfb=xq.sf)
+        xf, wf = mxfp8.dequantize(xq), mxfp8.dequantize(wq).reshape(g, 2 * inter, k)
+    else:
+        y = gemm.grouped_linear(x.bfloat16(), w.bfloat16(), sd, cd, tn, dual=True)
+        xf, wf = x.bfloat16().float(), w.bfloat16().float()
+    _native.assert_status_ok()
+    for i in range(g):
+        s, c = int(starts[i]), int(counts[i])
+        if c == 0:
+            continue
+        r = xf[s:s + c] @ wf[i].t()
+        ref = torch.nn.functional.silu(r[:, :inter]) * r[:, inter:]
+        assert _rel(y[s:s + c], ref) < 1e-2, f"group {i}"
