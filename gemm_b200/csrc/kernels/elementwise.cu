@@ -17,7 +17,7 @@ __device__ __forceinline__ int e8m0_amax(float amax) {
   const uint32_t bits = __float_as_uint(s);
   int e = (int)((bits >> 23) & 0xff);
   if (bits & 0x7fffffu) e += 1;
-  return max(1, min(e, 254));
+  return amax == 0.0f ? 127 : max(1, min(e, 254));   // an all-zero block gets scale 1
 }
 __device__ __forceinline__ size_t sf_atom_offset(int row, int blk32, int k_atoms) {
   return ((size_t)(row >> 7) * k_atoms + (blk32 >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (blk32 & 3);
@@ -247,7 +247,7 @@ mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ sr
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   if (!act) return;
-  const int e = (src >= 0) ? e8m0_amax(amax) : 127;
+  const int e = e8m0_amax(amax);
   const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
   uint8_t q[8];
 #pragma unroll

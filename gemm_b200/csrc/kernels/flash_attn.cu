@@ -1,0 +1,376 @@
+// FlashAttention forward over a paged KV cache on tcgen05, one kernel for prefill and decode.
+//
+// A CTA owns one KV head of one sequence and a tile of 128 query ROWS, where a row is a
+// (token, query-head-in-group) pair: with G = Hq / Hkv query heads per KV head the tile covers
+// floor(128 / G) consecutive tokens.  Every K/V block is therefore fetched once for the whole GQA
+// group.  Decode is the same kernel with one token per sequence (G valid rows) and, when the batch is
+// small, the KV range split over several CTAs whose partial (O, log-sum-exp) results a second kernel
+// merges (the same merge rule serves context parallelism across GPUs).
+//
+// Pipeline per 128-position KV block j (S, P, O live in TMEM; P overwrites S in place as packed bf16):
+//   TMA warp   : K_j, V_j pages -> 128B-swizzled smem (2 stages each), page ids from the block table
+//   MMA thread : S_{j+1} = Q K_{j+1}^T   (issued before waiting for softmax j, so it overlaps)
+//                O     += P_j V_j        (A operand = P from TMEM, B = V MN-major from smem)
+//   softmax    : 128 threads, one per row: S row -> running max / sum, P = exp2(S - m) -> TMEM,
+//                rescale O in TMEM when the row max moved, final O / l -> global
+// Q arrives pre-multiplied by softmax_scale * log2(e) (done by the RoPE kernel) so exp2 is exact base.
+//
+// Replaces in the reference: fa2_attn_f (cuda/llm/fa2_kernels.cu:55), batch_attn_causal_f32
+// (cuda/llm/cuda_llm_runner.c:8340), attn_decode_f32 (:391, which keeps seq_len scores in shared
+// memory and so bounds the context), cuda/fa2/cuda_fa2_kernels.h.  Numerics: tf_attn_worker
+// (common/transformer.h:1333-1530).
+#include "sm100.cuh"
+#include "host_common.h"
+
+namespace gb {
+
+constexpr int kFaThreads = 192;
+constexpr int kBN = 128;            // KV positions per block
+constexpr int kD = 128;             // head dim
+
+struct FaArgs {
+  const int* work;          // [n_work, 4] = {seq, kv_head, q_tok0 (within the sequence's chunk), split}
+  const int* cu_q;          // [B+1] token offsets of each sequence's query chunk in Q / O
+  const int* kv_len;        // [B] KV length of each sequence INCLUDING the chunk being processed
+  const int* block_table;   // [B, max_pages]
+  int max_pages;
+  int page_size;            // positions per page (8..128, divides 128)
+  int hq, hkv;
+  int num_splits;
+  int causal;
+  int window;               // sliding window (0 = off): position p attends to (p - window, p]
+  __nv_bfloat16* out;       // [T, Hq, D]                 (num_splits == 1)
+  float* part_o;            // [splits, T, Hq, D] f32     (num_splits > 1)
+  float* part_lse;          // [splits, T, Hq] base-2 log-sum-exp
+  int total_tokens;
+  KernelStatus* status;
+};
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kFaThreads, 1)
+flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const FaArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                       // 2 x [128 rows x 128 B]  (d halves)
+  uint8_t* sK = smem + 32768;               // 2 stages x 32 KB
+  uint8_t* sV = smem + 32768 * 3;           // 2 stages x 32 KB
+  uint64_t* bars = (uint64_t*)(smem + 32768 * 5);
+  uint64_t* q_full = bars;                  // 1
+  uint64_t* k_full = bars + 1;              // 2
+  uint64_t* k_empty = bars + 3;             // 2
+  uint64_t* v_full = bars + 5;              // 2
+  uint64_t* v_empty = bars + 7;             // 2
+  uint64_t* s_full = bars + 9;              // 2
+  uint64_t* p_ready = bars + 11;            // 1 (128 arrivals)
+  uint64_t* o_ready = bars + 12;            // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = a.hq / a.hkv;
+  const int tpt = 128 / G;                  // tokens per tile
+  const int* wk = a.work + (size_t)blockIdx.x * 4;
+  const int seq = wk[0], kvh = wk[1], q_tok0 = wk[2], split = wk[3];
+  const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
+  const int kv_len = a.kv_len[seq];
+  const int n_tok = min(tpt, q_len - q_tok0);            // valid tokens of this tile
+  const int pos0 = kv_len - q_len + q_tok0;              // position of the tile's first token
+  // KV block range of this CTA
+  int last_pos = a.causal ? (pos0 + n_tok - 1) : (kv_len - 1);
+  int first_pos = 0;
+  if (a.window > 0) first_pos = max(0, pos0 - a.window + 1);
+  int blk_lo = first_pos / kBN, blk_hi = last_pos / kBN + 1;     // [lo, hi)
+  if (a.num_splits > 1) {
+    const int nb = blk_hi - blk_lo, per = (nb + a.num_splits - 1) / a.num_splits;
+    blk_lo = blk_lo + split * per;
+    blk_hi = min(blk_hi, blk_lo + per);
+  }
+  const int n_blk = max(0, blk_hi - blk_lo);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&s_full[i], 1); }
+    mbar_init(p_ready, 128); mbar_init(o_ready, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0 && n_blk > 0) {
+      // Q tile: box (64 d, G heads, tpt tokens), two d-halves
+      mbar_expect_tx(q_full, (uint32_t)(2 * 128 * G * tpt));
+      tma_load_3d(sQ, &tmQ, q_full, 0, kvh * G, q_begin + q_tok0);
+      tma_load_3d(sQ + 16384, &tmQ, q_full, 64, kvh * G, q_begin + q_tok0);
+      const int ppb = kBN / a.page_size;               // pages per KV block
+      const uint32_t page_bytes = (uint32_t)a.page_size * 128;
+      const int* bt = a.block_table + (size_t)seq * a.max_pages;
+      const int last_page = (kv_len + a.page_size - 1) / a.page_size - 1;
+      bool ok = true;
+      for (int j = 0; j < n_blk && ok; ++j) {
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        const int blk = blk_lo + j;
+        // Pages past the end of the sequence are replaced by its last page: the tile is always filled with
+        // finite cache contents (their scores are masked, and 0 * finite stays 0 in P V).
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, a.status, 400, j)) { ok = false; break; }
+        mbar_expect_tx(&k_full[s], 32768u);
+        for (int p = 0; p < ppb; ++p) {
+          const int page = bt[min(blk * ppb + p, last_page)];
+          uint8_t* dst = sK + s * 32768 + p * page_bytes;
+          tma_load_3d(dst, &tmK, &k_full[s], 0, kvh, page * a.page_size);
+          tma_load_3d(dst + 16384, &tmK, &k_full[s], 64, kvh, page * a.page_size);
+        }
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, a.status, 401, j)) { ok = false; break; }
+        mbar_expect_tx(&v_full[s], 32768u);
+        for (int p = 0; p < ppb; ++p) {
+          const int page = bt[min(blk * ppb + p, last_page)];
+          uint8_t* dst = sV + s * 32768 + p * page_bytes;
+          tma_load_3d(dst, &tmV, &v_full[s], 0, kvh, page * a.page_size);
+          tma_load_3d(dst + 16384, &tmV, &v_full[s], 64, kvh, page * a.page_size);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_blk > 0) {
+      constexpr uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc(128, 128, 1, 1, 0, 1);     // B (= V) is MN-major
+      const uint32_t q_addr = smem_u32(sQ);
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status, 500);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[s], ph, abort_flag, a.status, 501, j)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + s * 32768);
+        const uint32_t d = tmem_base + s * 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+          mma_f16_ss(d, make_sdesc_sw128(q_addr + off), make_sdesc_sw128(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(&s_full[s]);
+        tc_commit(&k_empty[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_blk && ok; ++j) {
+        if (j + 1 < n_blk) { if (!issue_s(j + 1)) { ok = false; break; } }
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(p_ready, j & 1, abort_flag, a.status, 502, j)) { ok = false; break; }
+        if (!mbar_wait(&v_full[s], ph, abort_flag, a.status, 503, j)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(sV + s * 32768);
+        const uint32_t p_t = tmem_base + s * 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_f16_ts(tmem_o, p_t + ks * 8, make_sdesc_sw128_mn(v_addr + ks * 2048, 16384), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(o_ready);
+        tc_commit(&v_empty[s]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax + epilogue, one row per thread
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const int t_local = r / G, h_local = r - t_local * G;
+    const bool row_valid = (t_local < n_tok) && (r < tpt * G);
+    const int qpos = pos0 + min(t_local, n_tok - 1);
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_blk && ok; ++j) {
+      const int s = j & 1;
+      if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, a.status, 600, j)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t s_t = tmem_base + s * 128 + lane_off;
+      float sv[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_x32(s_t + c * 32, reinterpret_cast<uint32_t*>(sv) + c * 32);
+      tc_wait_ld();
+      const int kv0 = (blk_lo + j) * kBN;
+      int hi = kv_len - 1;
+      if (a.causal) hi = min(hi, qpos);
+      int lo = 0;
+      if (a.window > 0) lo = max(0, qpos - a.window + 1);
+      if (kv0 + kBN - 1 > hi || kv0 < lo) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) { const int kp = kv0 + c; if (kp > hi || kp < lo) sv[c] = -INFINITY; }
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sv[c]);
+      const float m_new = fmaxf(m, mx);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = fast_exp2(m - m_use);      // m = -inf -> 0
+      float rs = 0.f;
+      uint32_t pk[64];
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        const float p0 = fast_exp2(sv[2 * c] - m_use), p1 = fast_exp2(sv[2 * c + 1] - m_use);
+        rs += p0 + p1;
+        pk[c] = pack_bf16x2(p0, p1);
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      tmem_st_x32(s_t, pk);
+      tmem_st_x32(s_t + 32, pk + 32);
+      if (j > 0) {
+        if (!mbar_wait(o_ready, (j - 1) & 1, abort_flag, a.status, 601, j)) { ok = false; break; }
+        tc_fence_after();
+        if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld_x32(tmem_o + lane_off + c * 32, o);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_x32(tmem_o + lane_off + c * 32, o);
+          }
+        }
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok && n_blk > 0) ok = mbar_wait(o_ready, (n_blk - 1) & 1, abort_flag, a.status, 602);
+    if (ok) {
+      tc_fence_after();
+      const int tok = q_begin + q_tok0 + t_local;
+      const int head = kvh * G + h_local;
+      const float inv_l = (l > 0.f) ? 1.0f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (n_blk > 0) { tmem_ld_x32(tmem_o + lane_off + c * 32, o); tc_wait_ld(); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (row_valid) {
+          if (a.num_splits == 1) {
+            uint4* dst = reinterpret_cast<uint4*>(a.out + ((size_t)tok * a.hq + head) * kD + c * 32);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[v * 8 + 0]) * inv_l, __uint_as_float(o[v * 8 + 1]) * inv_l);
+              w.y = pack_bf16x2(__uint_as_float(o[v * 8 + 2]) * inv_l, __uint_as_float(o[v * 8 + 3]) * inv_l);
+              w.z = pack_bf16x2(__uint_as_float(o[v * 8 + 4]) * inv_l, __uint_as_float(o[v * 8 + 5]) * inv_l);
+              w.w = pack_bf16x2(__uint_as_float(o[v * 8 + 6]) * inv_l, __uint_as_float(o[v * 8 + 7]) * inv_l);
+              dst[v] = w;
+            }
+          } else {
+            float4* dst = reinterpret_cast<float4*>(a.part_o + (((size_t)split * a.total_tokens + tok) * a.hq + head) * kD + c * 32);
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              dst[v] = make_float4(__uint_as_float(o[v * 4]) * inv_l, __uint_as_float(o[v * 4 + 1]) * inv_l,
+                                   __uint_as_float(o[v * 4 + 2]) * inv_l, __uint_as_float(o[v * 4 + 3]) * inv_l);
+          }
+        }
+      }
+      if (row_valid && a.num_splits > 1)
+        a.part_lse[((size_t)split * a.total_tokens + tok) * a.hq + head] = (l > 0.f) ? (m + log2f(l)) : -INFINITY;
+    }
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// Merge of split-KV partials: out = sum_s 2^(lse_s - lse_max) O_s / sum_s 2^(lse_s - lse_max).
+// One warp per (token, head); D = 128 -> 4 floats per lane.
+__global__ void fa_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, __nv_bfloat16* __restrict__ out,
+                                  float* __restrict__ out_lse, int splits, long rows) {
+  const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (w >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float mx = -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_lse[(size_t)s * rows + w]);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float den = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ls = part_lse[(size_t)s * rows + w];
+    if (ls == -INFINITY) continue;
+    const float wgt = exp2f(ls - mx);
+    const float4 v = *reinterpret_cast<const float4*>(part_o + ((size_t)s * rows + w) * kD + lane * 4);
+    acc[0] += wgt * v.x; acc[1] += wgt * v.y; acc[2] += wgt * v.z; acc[3] += wgt * v.w;
+    den += wgt;
+  }
+  const float inv = den > 0.f ? 1.0f / den : 0.f;
+  uint2 o;
+  o.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
+  o.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
+  *reinterpret_cast<uint2*>(out + (size_t)w * kD + lane * 4) = o;
+  if (out_lse != nullptr && lane == 0) out_lse[w] = den > 0.f ? mx + log2f(den) : -INFINITY;
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+// q [T, Hq, 128] bf16 (pre-scaled by softmax_scale * log2 e), k_cache / v_cache [num_slots, Hkv, 128] bf16,
+// out [T, Hq, 128] bf16.  `work` is a device int32 [n_work, 4] list {seq, kv_head, q_tok0, split}.
+// With num_splits > 1, part_o / part_lse receive the partials and gb_fa_combine finishes.
+GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
+                         const int* work, int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages,
+                         int page_size, long num_slots, int total_tokens, int hq, int hkv, int head_dim, int num_splits, int causal,
+                         int window, void* status, cudaStream_t stream) {
+  if (head_dim != 128) return fail("flash_attn: head_dim must be 128%s");
+  if (hq % hkv) return fail("flash_attn: Hq %% Hkv != 0%s");
+  const int G = hq / hkv;
+  if (G > 128) return fail("flash_attn: group size > 128%s");
+  if (page_size < 8 || page_size > 128 || (128 % page_size) || (page_size % 8)) return fail("flash_attn: page_size must be 8..128, a multiple of 8 dividing 128%s");
+  if (n_work <= 0) return 0;
+  const int tpt = 128 / G;
+  CUtensorMap tmQ, tmK, tmV;
+  {
+    uint64_t dims[3] = {128, (uint64_t)hq, (uint64_t)total_tokens};
+    uint64_t strides[2] = {256, (uint64_t)hq * 256};
+    uint32_t box[3] = {64, (uint32_t)G, (uint32_t)tpt};
+    if (make_tmap(&tmQ, q, TM_BF16, 3, dims, strides, box, TM_SW_128)) return -1;
+  }
+  {
+    uint64_t dims[3] = {128, (uint64_t)hkv, (uint64_t)num_slots};
+    uint64_t strides[2] = {256, (uint64_t)hkv * 256};
+    uint32_t box[3] = {64, 1, (uint32_t)page_size};
+    if (make_tmap(&tmK, k_cache, TM_BF16, 3, dims, strides, box, TM_SW_128)) return -1;
+    if (make_tmap(&tmV, v_cache, TM_BF16, 3, dims, strides, box, TM_SW_128)) return -1;
+  }
+  FaArgs a;
+  memset(&a, 0, sizeof(a));
+  a.work = work; a.cu_q = cu_q; a.kv_len = kv_len; a.block_table = block_table; a.max_pages = max_pages; a.page_size = page_size;
+  a.hq = hq; a.hkv = hkv; a.num_splits = num_splits; a.causal = causal; a.window = window; a.out = (__nv_bfloat16*)out;
+  a.part_o = part_o; a.part_lse = part_lse; a.total_tokens = total_tokens; a.status = (KernelStatus*)status;
+  const int smem = 32768 * 5 + 256 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    GB_CUDA_OK(cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    attr_set = true;
+  }
+  flash_attn_kernel<<<n_work, kFaThreads, smem, stream>>>(tmQ, tmK, tmV, a);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_fa_combine(const float* part_o, const float* part_lse, void* out, float* out_lse, int splits, long rows, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  fa_combine_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(part_o, part_lse, (__nv_bfloat16*)out, out_lse, splits, rows);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -96,7 +96,7 @@ __device__ __forceinline__ int e8m0_from_amax(float amax) {
   uint32_t bits = __float_as_uint(s);
   int e = (int)((bits >> 23) & 0xff);
   if (bits & 0x7fffffu) e += 1;
-  return max(1, min(e, 254));
+  return amax == 0.0f ? 127 : max(1, min(e, 254));   // an all-zero block gets scale 1
 }
 
 template <int TN, int MODE, bool DUAL, bool QUANT_OUT>

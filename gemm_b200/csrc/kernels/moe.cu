@@ -1,0 +1,242 @@
+// Mixture-of-experts routing on the device, with no host synchronisation anywhere:
+//   gb_moe_route   router logits -> (softmax | sigmoid+bias) -> top-k -> renormalised weights
+//   gb_moe_plan    top-k ids -> per-expert row segments (aligned for the grouped GEMM), the row of every
+//                  (token, k) pair in the expert-sorted buffer and the source token of every row;
+//                  ordering inside an expert is by (token, k), so results are run-to-run identical
+//   gb_moe_combine out[t] = sum_k w[t,k] * y[row(t,k)]   (fixed order -> deterministic)
+//
+// Router semantics follow common/transformer.h:4050-4091 (softmax over all experts, top-k, weights
+// renormalised to sum 1; ties go to the lower index, NaN counts as -FLT_MAX as in
+// cuda/llm/cuda_llm_runner.c:7958-8035) and common/m3_impl.h:692-698 for the sigmoid + bias variant.
+// Replaces moe_topk_kernel (cuda_llm_runner.c:7958), the host-side moe_topk_softmax (:13611, a
+// device->host sync per layer), gather_rows_f32 (:7931) and scatter_add_weighted_f32 (:7943).
+#include "sm100.cuh"
+#include "host_common.h"
+#include <float.h>
+
+namespace gb {
+
+constexpr int kMaxTopK = 16;
+
+// One warp per token.  E <= 512.
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
+                 int n_tok, int n_exp, int k, int mode, int renorm, float routed_scale, int ld) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (w >= n_tok) return;
+  const int lane = threadIdx.x & 31;
+  constexpr int MAXV = 16;
+  float p[MAXV], sel[MAXV];
+  float mx = -FLT_MAX;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int e = lane + 32 * i;
+    float v = -FLT_MAX;
+    if (e < n_exp) { v = logits[(size_t)w * ld + e]; if (!(v == v)) v = -FLT_MAX; }
+    p[i] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = warp_max(mx);
+  if (mode == 0) {
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) { const int e = lane + 32 * i; p[i] = (e < n_exp) ? expf(p[i] - mx) : 0.f; sum += p[i]; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) { p[i] *= inv; sel[i] = (lane + 32 * i < n_exp) ? p[i] : -FLT_MAX; }
+  } else {
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int e = lane + 32 * i;
+      p[i] = (e < n_exp) ? 1.0f / (1.0f + expf(-p[i])) : 0.f;
+      sel[i] = (e < n_exp) ? p[i] + (bias != nullptr ? bias[e] : 0.f) : -FLT_MAX;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f; int my_id = 0;      // lane j keeps the j-th pick
+  for (int j = 0; j < k; ++j) {
+    float best = -FLT_MAX; int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int e = lane + 32 * i;
+      if (e < n_exp && (sel[i] > best || (sel[i] == best && e < bi))) { best = sel[i]; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    // owner lane removes it and publishes its probability
+    float pv = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) if (lane + 32 * i == bi) { pv = p[i]; sel[i] = -FLT_MAX; }
+    pv = __shfl_sync(0xffffffffu, pv, bi & 31);
+    wsum += pv;
+    if (lane == j) { my_w = pv; my_id = bi; }
+  }
+  if (lane < k) {
+    float wv = my_w;
+    if (renorm) wv = wv / fmaxf(wsum, 1e-20f);
+    ids[(size_t)w * k + lane] = my_id;
+    weights[(size_t)w * k + lane] = wv * routed_scale;
+  }
+}
+
+constexpr int kPlanBlock = 256;
+
+// block_hist[b][e] = pairs of block b routed to expert e (pairs whose expert is outside [e_lo, e_hi) are dropped)
+__global__ void __launch_bounds__(kPlanBlock)
+moe_hist_kernel(const int* __restrict__ ids, int* __restrict__ block_hist, long n_pairs, int n_exp) {
+  extern __shared__ int sh[];
+  for (int e = threadIdx.x; e < n_exp; e += kPlanBlock) sh[e] = 0;
+  __syncthreads();
+  const long i = (long)blockIdx.x * kPlanBlock + threadIdx.x;
+  if (i < n_pairs) { const int e = ids[i]; if (e >= 0 && e < n_exp) atomicAdd(&sh[e], 1); }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_exp; e += kPlanBlock) block_hist[(size_t)blockIdx.x * n_exp + e] = sh[e];
+}
+
+// One block per expert: exclusive scan of block_hist[:, e] over the blocks (in place) and seg_count[e].
+__global__ void __launch_bounds__(256)
+moe_scan_kernel(int* __restrict__ block_hist, int* __restrict__ seg_count, int n_blocks, int n_exp) {
+  __shared__ int part[256];
+  const int e = blockIdx.x, t = threadIdx.x;
+  const int per = (n_blocks + 255) / 256;
+  const int b0 = t * per, b1 = min(n_blocks, b0 + per);
+  int sum = 0;
+  for (int b = b0; b < b1; ++b) sum += block_hist[(size_t)b * n_exp + e];
+  part[t] = sum;
+  __syncthreads();
+  // Hillis-Steele inclusive scan over 256 partial sums
+  for (int o = 1; o < 256; o <<= 1) {
+    int v = (t >= o) ? part[t - o] : 0;
+    __syncthreads();
+    part[t] += v;
+    __syncthreads();
+  }
+  int run = part[t] - sum;
+  for (int b = b0; b < b1; ++b) { const int c = block_hist[(size_t)b * n_exp + e]; block_hist[(size_t)b * n_exp + e] = run; run += c; }
+  if (t == 255) seg_count[e] = part[255];
+}
+
+// Experts are grouped into "regions" of experts_per_region consecutive experts (the experts of one
+// destination rank); region r starts at row r * region_rows, segments inside are aligned to `align`.
+__global__ void __launch_bounds__(512)
+moe_seg_kernel(const int* __restrict__ seg_count, int* __restrict__ seg_start, int* __restrict__ region_rows_used,
+               int n_exp, int experts_per_region, int region_rows, int align) {
+  const int r = threadIdx.x;
+  if (r < n_exp / experts_per_region) {
+    int pos = 0;
+    for (int i = 0; i < experts_per_region; ++i) {
+      const int ee = r * experts_per_region + i;
+      seg_start[ee] = r * region_rows + pos;
+      pos += (seg_count[ee] + align - 1) / align * align;
+    }
+    if (region_rows_used != nullptr) region_rows_used[r] = pos;
+  }
+}
+
+__global__ void __launch_bounds__(kPlanBlock)
+moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ block_hist, const int* __restrict__ seg_start,
+                   int* __restrict__ pair_row, int* __restrict__ row_token, long n_pairs, int n_exp, int k, long capacity) {
+  __shared__ int se[kPlanBlock];
+  const long i = (long)blockIdx.x * kPlanBlock + threadIdx.x;
+  int e = -1;
+  if (i < n_pairs) { e = ids[i]; if (e < 0 || e >= n_exp) e = -1; }
+  se[threadIdx.x] = e;
+  __syncthreads();
+  if (i >= n_pairs) return;
+  if (e < 0) { pair_row[i] = -1; return; }
+  int rank = 0;
+  for (int j = 0; j < (int)threadIdx.x; ++j) rank += (se[j] == e);
+  const long row = (long)seg_start[e] + block_hist[(size_t)blockIdx.x * n_exp + e] + rank;
+  if (row < capacity) { pair_row[i] = (int)row; row_token[row] = (int)(i / k); }
+  else pair_row[i] = -1;
+}
+
+// out[t, :] = sum_j w[t, j] * y[pair_row[t*k + j], :]   (bf16 in / out, fp32 accumulate, fixed order)
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ weights,
+                   __nv_bfloat16* __restrict__ out, int hidden, int k, int ld_y) {
+  const int t = blockIdx.x;
+  __shared__ int rows[kMaxTopK];
+  __shared__ float ws[kMaxTopK];
+  if (threadIdx.x < k) { rows[threadIdx.x] = pair_row[(size_t)t * k + threadIdx.x]; ws[threadIdx.x] = weights ? weights[(size_t)t * k + threadIdx.x] : 1.0f; }
+  __syncthreads();
+  for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int r = rows[j];
+      if (r < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)r * ld_y + v * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); acc[2 * i] += ws[j] * f.x; acc[2 * i + 1] += ws[j] * f.y; }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]); o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * hidden + v * 8) = o;
+  }
+}
+
+// Plain row gather (bf16): out[r] = in[src[r]] or zeros when src[r] < 0.
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src, __nv_bfloat16* __restrict__ out,
+                                   long rows, int hidden, int ld_in) {
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vpr = hidden >> 3;
+  if (idx >= rows * vpr) return;
+  const long r = idx / vpr; const int v = (int)(idx % vpr);
+  const int s = src[r];
+  uint4 val = make_uint4(0, 0, 0, 0);
+  if (s >= 0) val = *reinterpret_cast<const uint4*>(in + (size_t)s * ld_in + v * 8);
+  *reinterpret_cast<uint4*>(out + r * hidden + v * 8) = val;
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+GB_API int gb_moe_route(const float* logits, const float* bias, int* ids, float* weights, int n_tok, int n_exp, int k, int mode,
+                        int renorm, float routed_scale, int ld, cudaStream_t stream) {
+  if (n_exp > 512 || k > kMaxTopK || k > n_exp) return fail("moe_route: need n_exp <= 512 and k <= 16%s");
+  if (n_tok <= 0) return 0;
+  moe_route_kernel<<<(n_tok + 7) / 8, 256, 0, stream>>>(logits, bias, ids, weights, n_tok, n_exp, k, mode, renorm, routed_scale, ld);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// workspace: int32 [ceil(n_pairs / 256) * n_exp].  row_token must hold `capacity` ints (set to -1 here).
+GB_API int gb_moe_plan(const int* ids, int* workspace, int* seg_start, int* seg_count, int* region_rows_used, int* pair_row,
+                       int* row_token, long n_pairs, int n_exp, int k, int experts_per_region, int region_rows, int align,
+                       long capacity, cudaStream_t stream) {
+  if (n_exp > 512) return fail("moe_plan: n_exp > 512%s");
+  if (n_exp % experts_per_region) return fail("moe_plan: n_exp %% experts_per_region != 0%s");
+  const int nb = (int)((n_pairs + kPlanBlock - 1) / kPlanBlock);
+  GB_CUDA_OK(cudaMemsetAsync(row_token, 0xff, (size_t)capacity * sizeof(int), stream));
+  if (nb > 0) moe_hist_kernel<<<nb, kPlanBlock, n_exp * sizeof(int), stream>>>(ids, workspace, n_pairs, n_exp);
+  moe_scan_kernel<<<n_exp, 256, 0, stream>>>(workspace, seg_count, nb, n_exp);
+  moe_seg_kernel<<<1, 512, 0, stream>>>(seg_count, seg_start, region_rows_used, n_exp, experts_per_region, region_rows, align);
+  if (nb > 0) moe_scatter_kernel<<<nb, kPlanBlock, 0, stream>>>(ids, workspace, seg_start, pair_row, row_token, n_pairs, n_exp, k, capacity);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_moe_combine(const void* y, const int* pair_row, const float* weights, void* out, int n_tok, int hidden, int k, int ld_y,
+                          cudaStream_t stream) {
+  if (hidden % 8 || k > kMaxTopK) return fail("moe_combine: hidden %% 8 != 0 or k > 16%s");
+  if (n_tok <= 0) return 0;
+  moe_combine_kernel<<<n_tok, 256, 0, stream>>>((const __nv_bfloat16*)y, pair_row, weights, (__nv_bfloat16*)out, hidden, k, ld_y);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_gather_rows(const void* in, const int* src, void* out, long rows, int hidden, int ld_in, cudaStream_t stream) {
+  if (hidden % 8) return fail("gather_rows: hidden %% 8 != 0%s");
+  const long n = rows * (hidden / 8);
+  if (n <= 0) return 0;
+  gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, src, (__nv_bfloat16*)out, rows, hidden, ld_in);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

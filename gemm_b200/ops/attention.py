@@ -1,0 +1,128 @@
+"""Attention over the paged KV cache: wrapper of csrc/kernels/flash_attn.cu (prefill and decode share one
+tcgen05 kernel; small decode batches split the KV range and merge partials) and the PyTorch reference.
+
+Conventions: ``q [T, Hq, D]`` is already multiplied by ``softmax_scale * log2(e)`` (see
+``elementwise.softmax_scale_log2``); ``k_cache`` / ``v_cache`` are ``[num_slots, Hkv, D]`` with
+``slot = page * page_size + offset``; ``cu_q [B+1]`` gives each sequence's span of query tokens,
+``kv_len [B]`` the sequence length including those tokens; ``block_table [B, max_pages]`` lists pages.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import _native
+
+_c, _i, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+
+
+def _p(t):
+    return _c(t.data_ptr()) if t is not None else _c(0)
+
+
+def build_work(q_lens: Sequence[int], hq: int, hkv: int, num_splits: int = 1) -> torch.Tensor:
+    """Host-side work list ``[n, 4] = {seq, kv_head, q_tok0, split}``: longest tiles first within a sequence,
+    the heads of one tile adjacent (their K/V blocks hit in L2)."""
+    g = hq // hkv
+    tpt = 128 // g
+    items: List[List[int]] = []
+    for s, ql in enumerate(q_lens):
+        n_tiles = (ql + tpt - 1) // tpt
+        for ti in reversed(range(n_tiles)):
+            for sp in range(num_splits):
+                for h in range(hkv):
+                    items.append([s, h, ti * tpt, sp])
+    return torch.tensor(items, dtype=torch.int32).reshape(-1, 4)
+
+
+def pick_splits(n_seqs: int, hkv: int, max_kv: int, sm_count: int = 148) -> int:
+    """Number of KV splits for decode: enough CTAs to cover the SMs, at least 2 KV blocks per split."""
+    base = max(1, n_seqs * hkv)
+    blocks = max(1, (max_kv + 127) // 128)
+    splits = max(1, min(sm_count // base, blocks // 2 if blocks >= 2 else 1, 16))
+    return splits
+
+
+def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+              block_table: torch.Tensor, page_size: int, work: torch.Tensor, num_splits: int = 1, causal: bool = True,
+              window: int = 0, out: Optional[torch.Tensor] = None, scratch=None) -> torch.Tensor:
+    """Attention output ``[T, Hq, D]`` (bf16).  ``work`` comes from ``build_work`` (moved to the device)."""
+    t, hq, d = q.shape
+    hkv = k_cache.shape[1]
+    if not q.is_cuda:
+        return attention_ref(q, k_cache, v_cache, cu_q, kv_len, block_table, page_size, causal, window)
+    if out is None:
+        out = torch.empty(t, hq, d, dtype=torch.bfloat16, device=q.device)
+    lib = _native.cuda()
+    part_o = part_lse = None
+    if num_splits > 1:
+        if scratch is not None:
+            part_o, part_lse = scratch
+        else:
+            part_o = torch.empty(num_splits, t, hq, d, dtype=torch.float32, device=q.device)
+            part_lse = torch.empty(num_splits, t, hq, dtype=torch.float32, device=q.device)
+    stream = _c(torch.cuda.current_stream().cuda_stream)
+    rc = lib.gb_flash_attn(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
+                           _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
+                           _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(num_splits), _i(1 if causal else 0),
+                           _i(window), _c(_native.status_ptr()), stream)
+    _native.check(rc, "gb_flash_attn")
+    if num_splits > 1:
+        rc = lib.gb_fa_combine(_p(part_o), _p(part_lse), _p(out), _c(0), _i(num_splits), _l(t * hq), stream)
+        _native.check(rc, "gb_fa_combine")
+    return out
+
+
+def combine_partials(part_o: torch.Tensor, part_lse: torch.Tensor):
+    """Merge flash partials ``part_o [S, R, D]`` (each normalised by its own sum) and base-2 ``part_lse [S, R]``.
+    Returns ``(out bf16 [R, D], lse f32 [R])``.  Also the rule for context parallelism (KV sharded over GPUs)."""
+    s, r, d = part_o.shape
+    if not part_o.is_cuda:
+        mx = part_lse.max(dim=0).values
+        w = torch.exp2(part_lse - mx)
+        w = torch.where(torch.isinf(part_lse) & (part_lse < 0), torch.zeros_like(w), w)
+        den = w.sum(0)
+        out = (w.unsqueeze(-1) * part_o).sum(0) / den.clamp_min(1e-30).unsqueeze(-1)
+        return out.to(torch.bfloat16), mx + torch.log2(den)
+    out = torch.empty(r, d, dtype=torch.bfloat16, device=part_o.device)
+    lse = torch.empty(r, dtype=torch.float32, device=part_o.device)
+    rc = _native.cuda().gb_fa_combine(_p(part_o), _p(part_lse), _p(out), _p(lse), _i(s), _l(r),
+                                      _c(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "gb_fa_combine")
+    return out, lse
+
+
+def attention_ref(q, k_cache, v_cache, cu_q, kv_len, block_table, page_size, causal=True, window=0) -> torch.Tensor:
+    """fp32 reference: gathers each sequence's K/V through the block table and applies masked softmax."""
+    t, hq, d = q.shape
+    hkv = k_cache.shape[1]
+    g = hq // hkv
+    out = torch.zeros(t, hq, d, dtype=torch.float32, device=q.device)
+    cu = cu_q.tolist()
+    for s in range(len(cu) - 1):
+        q0, q1 = cu[s], cu[s + 1]
+        ql, kl = q1 - q0, int(kv_len[s])
+        if ql == 0:
+            continue
+        n_pages = (kl + page_size - 1) // page_size
+        slots = (block_table[s, :n_pages].long().unsqueeze(1) * page_size + torch.arange(page_size, device=q.device)).reshape(-1)[:kl]
+        k = k_cache[slots].float()          # [kl, hkv, d]
+        v = v_cache[slots].float()
+        qs = q[q0:q1].float()               # [ql, hq, d]  (already scaled, log2 domain)
+        k = k.repeat_interleave(g, dim=1)
+        v = v.repeat_interleave(g, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", qs, k) * math.log(2.0)
+        qpos = torch.arange(kl - ql, kl, device=q.device).unsqueeze(1)
+        kpos = torch.arange(kl, device=q.device).unsqueeze(0)
+        mask = torch.ones(ql, kl, dtype=torch.bool, device=q.device)
+        if causal:
+            mask &= kpos <= qpos
+        if window > 0:
+            mask &= kpos > qpos - window
+        sc = sc.masked_fill(~mask.unsqueeze(0), float("-inf"))
+        p = torch.softmax(sc, dim=-1)
+        out[q0:q1] = torch.einsum("hqk,khd->qhd", p, v)
+    return out.to(torch.bfloat16)

@@ -1,0 +1,176 @@
+"""Token-wise ops: embedding gather, RMSNorm (+residual add, +MXFP8 output), QK-norm + RoPE + paged KV
+write, SiLU-gate, MXFP8 activation quantiser.  CUDA kernels live in csrc/kernels/elementwise.cu; each
+function falls back to the fp32 PyTorch reference only for CPU tensors.
+
+Reference behaviour: common/transformer.h:593-637 (RMSNorm), :1281-1315 (per-head QK-norm),
+:1183-1219 (NeoX RoPE, pairs (j, j + d/2), inv_freq = theta^(-2j/d)).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native
+from . import mxfp8
+from .mxfp8 import MxTensor
+
+_c, _i, _f, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_long
+
+
+def _p(t):
+    return _c(t.data_ptr()) if t is not None else _c(0)
+
+
+def _s():
+    return _c(torch.cuda.current_stream().cuda_stream)
+
+
+# ------------------------------------------------------------------------------------------ embed
+def embed(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """Rows of a bf16 embedding table; ids int32 [T]."""
+    if not table.is_cuda:
+        return table[ids.long()].to(torch.bfloat16)
+    out = torch.empty(ids.numel(), table.shape[1], dtype=torch.bfloat16, device=table.device)
+    _native.check(_native.cuda().gb_embed(_p(ids), _p(table), _p(out), _i(ids.numel()), _i(table.shape[1]),
+                                          _i(table.shape[0]), _s()), "gb_embed")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ rmsnorm
+def rmsnorm_ref(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(torch.bfloat16)
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
+            quantize: bool = False, want_bf16: bool = True):
+    """RMSNorm of ``x`` (or of ``residual += x`` when ``residual`` is given; the sum is written back).
+
+    Returns the bf16 result, or ``(bf16 | None, MxTensor)`` when ``quantize`` asks for an MXFP8 copy that
+    feeds a block-scaled GEMM.
+    """
+    rows, hidden = x.shape
+    if not x.is_cuda:
+        if residual is not None:
+            residual.copy_((residual.float() + x.float()).to(torch.bfloat16))
+            src = residual
+        else:
+            src = x
+        y = rmsnorm_ref(src, w, eps)
+        if quantize:
+            return (y if want_bf16 else None), mxfp8.quantize(y.float())
+        return y
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
+    q = sf = None
+    if quantize:
+        rp = (rows + 127) // 128 * 128
+        q = torch.zeros(rp, hidden, dtype=torch.uint8, device=x.device)
+        sf = torch.full((rp // 128, hidden // 128, 512), 127, dtype=torch.uint8, device=x.device)
+    if residual is not None:
+        rc = _native.cuda().gb_rmsnorm(_p(residual), _p(x), _c(0), _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden),
+                                       _f(eps), _i(residual.stride(0)), _i(hidden), _s())
+    else:
+        rc = _native.cuda().gb_rmsnorm(_c(0), _c(0), _p(x), _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden), _f(eps),
+                                       _i(x.stride(0)), _i(hidden), _s())
+    _native.check(rc, "gb_rmsnorm")
+    if quantize:
+        return out, MxTensor(q, sf, rows, hidden)
+    return out
+
+
+# ------------------------------------------------------------------------------------------ qk norm + rope + kv write
+def rope_ref(x: torch.Tensor, positions: torch.Tensor, theta: float, rope_dim: Optional[int] = None) -> torch.Tensor:
+    """NeoX rotation of ``x [T, H, D]`` (fp32 math)."""
+    t, h, d = x.shape
+    rd = rope_dim or d
+    half = rd // 2
+    j = torch.arange(half, dtype=torch.float32, device=x.device)
+    inv = theta ** (-2.0 * j / rd)
+    ang = positions.to(torch.float32).unsqueeze(-1) * inv            # [T, half]
+    cos, sin = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
+    xf = x.float().clone()
+    a, b = xf[..., :half].clone(), xf[..., half:rd].clone()
+    xf[..., :half] = a * cos - b * sin
+    xf[..., half:rd] = a * sin + b * cos
+    return xf
+
+
+def qk_norm_rope_ref(qkv, positions, q_w, k_w, hq, hkv, d, theta, eps, q_scale, rope_dim=None):
+    t = qkv.shape[0]
+    q = qkv[:, : hq * d].float().reshape(t, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].float().reshape(t, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].reshape(t, hkv, d)
+    if q_w is not None:
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_w.float()
+    if k_w is not None:
+        k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_w.float()
+    q = rope_ref(q, positions, theta, rope_dim) * q_scale
+    k = rope_ref(k, positions, theta, rope_dim)
+    return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+
+
+def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, q_w, k_w, k_cache: torch.Tensor,
+                 v_cache: torch.Tensor, hq: int, hkv: int, d: int, theta: float, eps: float, q_scale: float,
+                 rope_dim: Optional[int] = None) -> torch.Tensor:
+    """Per-head RMSNorm (optional) + RoPE on the fused QKV rows; K / V go to cache slot ``slots[t]``.
+
+    ``k_cache`` / ``v_cache`` are ``[num_slots, Hkv, D]``.  Returns ``q [T, Hq, D]`` multiplied by ``q_scale``.
+    """
+    t = qkv.shape[0]
+    if not qkv.is_cuda:
+        q, k, v = qk_norm_rope_ref(qkv, positions, q_w, k_w, hq, hkv, d, theta, eps, q_scale, rope_dim)
+        ok = slots >= 0
+        k_cache[slots[ok].long()] = k[ok]
+        v_cache[slots[ok].long()] = v[ok]
+        return q
+    q_out = torch.empty(t, hq, d, dtype=torch.bfloat16, device=qkv.device)
+    pairs = (rope_dim or d) // 2
+    rc = _native.cuda().gb_qk_norm_rope(_p(qkv), _p(positions), _p(slots), _p(q_w), _p(k_w), _p(q_out), _p(k_cache),
+                                        _p(v_cache), _i(t), _i(hq), _i(hkv), _i(d), _i(pairs), _f(theta), _f(eps),
+                                        _i(qkv.stride(0)), _f(q_scale), _s())
+    _native.check(rc, "gb_qk_norm_rope")
+    return q_out
+
+
+# ------------------------------------------------------------------------------------------ misc
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` over ``[rows, 2I]`` rows laid out as [gate | up]."""
+    rows, two_i = gate_up.shape
+    inter = two_i // 2
+    if not gate_up.is_cuda:
+        g = gate_up.float()
+        return (torch.nn.functional.silu(g[:, :inter]) * g[:, inter:]).to(torch.bfloat16)
+    out = torch.empty(rows, inter, dtype=torch.bfloat16, device=gate_up.device)
+    _native.check(_native.cuda().gb_silu_mul(_p(gate_up), _p(out), _l(rows), _i(inter), _i(gate_up.stride(0)), _s()),
+                  "gb_silu_mul")
+    return out
+
+
+def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_rows: Optional[int] = None) -> MxTensor:
+    """bf16 ``[rows, K]`` -> MXFP8.  With ``src_rows`` (int32) output row r is input row ``src_rows[r]``
+    (negative = zero row): the gather of MoE dispatch fused with the quantiser."""
+    k = x.shape[1]
+    n = out_rows if out_rows is not None else (src_rows.numel() if src_rows is not None else x.shape[0])
+    if not x.is_cuda:
+        if src_rows is not None:
+            g = torch.zeros(n, k, dtype=torch.float32)
+            ok = src_rows[:n] >= 0
+            g[ok] = x.float()[src_rows[:n][ok].long()]
+        else:
+            g = x.float()
+        t = mxfp8.quantize(g)
+        return t
+    rp = (n + 127) // 128 * 128
+    q = torch.zeros(rp, k, dtype=torch.uint8, device=x.device)
+    sf = torch.full((rp // 128, k // 128, 512), 127, dtype=torch.uint8, device=x.device)
+    _native.check(_native.cuda().gb_mx_quant(_p(x), _p(src_rows), _p(q), _p(sf), _l(n), _i(k), _i(x.stride(0)), _s()),
+                  "gb_mx_quant")
+    return MxTensor(q, sf, n, k)
+
+
+def softmax_scale_log2(d: int) -> float:
+    """``q_scale`` that the attention kernel expects folded into Q: 1/sqrt(d) * log2(e)."""
+    return (1.0 / math.sqrt(d)) * math.log2(math.e)

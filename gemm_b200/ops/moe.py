@@ -1,0 +1,156 @@
+"""Mixture-of-experts routing ops (csrc/kernels/moe.cu) and their PyTorch references.
+
+``route``    router logits -> top-k ids and weights (softmax + renormalise, or sigmoid + bias)
+``plan``     expert-sorted row layout for the grouped GEMM, computed on the device
+``combine``  router-weighted sum of the k expert outputs of every token
+
+Reference semantics: common/transformer.h:4050-4130 (softmax over all experts, top-k, renormalise, weighted
+sum) and common/m3_impl.h:692-714 (sigmoid router with selection bias and routed scale).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _native
+
+_c, _i, _f, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_long
+
+
+def _p(t):
+    return _c(t.data_ptr()) if t is not None else _c(0)
+
+
+def _s():
+    return _c(torch.cuda.current_stream().cuda_stream)
+
+
+def route_ref(logits: torch.Tensor, k: int, mode: str = "softmax", bias: Optional[torch.Tensor] = None,
+              renorm: bool = True, routed_scale: float = 1.0):
+    lf = torch.nan_to_num(logits.float(), nan=-3.4e38)
+    if mode == "softmax":
+        p = torch.softmax(lf, dim=-1)
+        sel = p
+    else:
+        p = torch.sigmoid(lf)
+        sel = p + (bias.float() if bias is not None else 0.0)
+    # ties -> lower index: stable descending sort
+    order = torch.sort(sel, dim=-1, descending=True, stable=True).indices[:, :k]
+    w = torch.gather(p, 1, order)
+    if renorm:
+        w = w / w.sum(-1, keepdim=True).clamp_min(1e-20)
+    return order.to(torch.int32), (w * routed_scale).float()
+
+
+def route(logits: torch.Tensor, k: int, mode: str = "softmax", bias: Optional[torch.Tensor] = None, renorm: bool = True,
+          routed_scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``logits`` f32 [T, E] -> (ids int32 [T, k], weights f32 [T, k])."""
+    if not logits.is_cuda:
+        return route_ref(logits, k, mode, bias, renorm, routed_scale)
+    t, e = logits.shape
+    ids = torch.empty(t, k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(t, k, dtype=torch.float32, device=logits.device)
+    rc = _native.cuda().gb_moe_route(_p(logits), _p(bias), _p(ids), _p(w), _i(t), _i(e), _i(k), _i(0 if mode == "softmax" else 1),
+                                     _i(1 if renorm else 0), _f(routed_scale), _i(logits.stride(0)), _s())
+    _native.check(rc, "gb_moe_route")
+    return ids, w
+
+
+@dataclass
+class MoePlan:
+    seg_start: torch.Tensor      # int32 [E]   first row of each expert's segment
+    seg_count: torch.Tensor      # int32 [E]   valid rows per expert
+    pair_row: torch.Tensor       # int32 [T*k] row of every (token, k) pair (-1 = dropped)
+    row_token: torch.Tensor      # int32 [capacity] source token of every row (-1 = padding)
+    region_used: torch.Tensor    # int32 [regions] rows used (padded) in each region
+    capacity: int
+    region_rows: int
+
+
+def plan_capacity(n_pairs: int, n_exp: int, align: int, regions: int = 1, k: int = 8) -> Tuple[int, int]:
+    """(rows per region, total rows) that can never overflow, whatever the routing."""
+    epr = n_exp // regions
+    tokens = (n_pairs + k - 1) // k
+    per_region = tokens * min(k, epr) + epr * (align - 1)
+    per_region = (per_region + 127) // 128 * 128
+    return per_region, per_region * regions
+
+
+def plan_ref(ids: torch.Tensor, n_exp: int, k: int, align: int, regions: int = 1) -> MoePlan:
+    flat = ids.reshape(-1).long()
+    n_pairs = flat.numel()
+    region_rows, capacity = plan_capacity(n_pairs, n_exp, align, regions, k)
+    epr = n_exp // regions
+    counts = torch.bincount(flat, minlength=n_exp)[:n_exp]
+    seg_start = torch.zeros(n_exp, dtype=torch.int64)
+    region_used = torch.zeros(regions, dtype=torch.int64)
+    for r in range(regions):
+        pos = 0
+        for i in range(epr):
+            e = r * epr + i
+            seg_start[e] = r * region_rows + pos
+            pos += (int(counts[e]) + align - 1) // align * align
+        region_used[r] = pos
+    order = torch.sort(flat, stable=True).indices          # by expert, then (token, k)
+    rank = torch.zeros(n_pairs, dtype=torch.int64)
+    sorted_e = flat[order]
+    first = torch.zeros(n_exp + 1, dtype=torch.int64)
+    first[1:] = torch.cumsum(counts, 0)
+    rank[order] = torch.arange(n_pairs) - first[sorted_e]
+    pair_row = seg_start[flat] + rank
+    row_token = torch.full((capacity,), -1, dtype=torch.int32)
+    row_token[pair_row] = (torch.arange(n_pairs) // k).to(torch.int32)
+    return MoePlan(seg_start.to(torch.int32), counts.to(torch.int32), pair_row.to(torch.int32), row_token,
+                   region_used.to(torch.int32), capacity, region_rows)
+
+
+def plan(ids: torch.Tensor, n_exp: int, align: int, regions: int = 1, workspace=None) -> MoePlan:
+    """Device-side plan from ``ids int32 [T, k]``; no host synchronisation."""
+    t, k = ids.shape
+    if not ids.is_cuda:
+        return plan_ref(ids, n_exp, k, align, regions)
+    n_pairs = t * k
+    region_rows, capacity = plan_capacity(n_pairs, n_exp, align, regions, k)
+    dev = ids.device
+    nb = (n_pairs + 255) // 256
+    ws = torch.empty(max(1, nb * n_exp), dtype=torch.int32, device=dev)
+    seg_start = torch.empty(n_exp, dtype=torch.int32, device=dev)
+    seg_count = torch.empty(n_exp, dtype=torch.int32, device=dev)
+    region_used = torch.empty(regions, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(n_pairs, dtype=torch.int32, device=dev)
+    row_token = torch.empty(capacity, dtype=torch.int32, device=dev)
+    rc = _native.cuda().gb_moe_plan(_p(ids), _p(ws), _p(seg_start), _p(seg_count), _p(region_used), _p(pair_row), _p(row_token),
+                                    _l(n_pairs), _i(n_exp), _i(k), _i(n_exp // regions), _i(region_rows), _i(align),
+                                    _l(capacity), _s())
+    _native.check(rc, "gb_moe_plan")
+    return MoePlan(seg_start, seg_count, pair_row, row_token, region_used, capacity, region_rows)
+
+
+def combine(y: torch.Tensor, pair_row: torch.Tensor, weights: Optional[torch.Tensor], n_tok: int, k: int) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * y[pair_row[t*k + j]]`` (bf16, fp32 accumulation in fixed order)."""
+    hidden = y.shape[1]
+    if not y.is_cuda:
+        rows = pair_row.reshape(n_tok, k).long()
+        g = y.float()[rows.clamp_min(0)] * (rows >= 0).unsqueeze(-1)
+        w = weights.float().unsqueeze(-1) if weights is not None else 1.0
+        return (g * w).sum(1).to(torch.bfloat16)
+    out = torch.empty(n_tok, hidden, dtype=torch.bfloat16, device=y.device)
+    rc = _native.cuda().gb_moe_combine(_p(y), _p(pair_row), _p(weights), _p(out), _i(n_tok), _i(hidden), _i(k), _i(y.stride(0)), _s())
+    _native.check(rc, "gb_moe_combine")
+    return out
+
+
+def gather_rows(x: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """``out[r] = x[src[r]]`` (zeros where src < 0), bf16."""
+    if not x.is_cuda:
+        out = torch.zeros(src.numel(), x.shape[1], dtype=x.dtype)
+        ok = src >= 0
+        out[ok] = x[src[ok].long()]
+        return out
+    out = torch.empty(src.numel(), x.shape[1], dtype=torch.bfloat16, device=x.device)
+    rc = _native.cuda().gb_gather_rows(_p(x), _p(src), _p(out), _l(src.numel()), _i(x.shape[1]), _i(x.stride(0)), _s())
+    _native.check(rc, "gb_gather_rows")
+    return out

@@ -42,7 +42,8 @@ def e8m0_from_amax(amax: torch.Tensor) -> torch.Tensor:
     bits = s.view(torch.int32)
     e = (bits >> 23) & 0xFF
     e = e + ((bits & 0x7FFFFF) != 0).to(torch.int32)
-    return e.clamp(1, 254)
+    e = e.clamp(1, 254)
+    return torch.where(amax == 0, torch.full_like(e, 127), e)     # an all-zero block gets scale 1
 
 
 def quantize_rowmajor(x: torch.Tensor):

@@ -1,0 +1,135 @@
+"""Token-wise, MoE-routing and sampling kernels vs their PyTorch fp32 references."""
+import pytest
+import torch
+
+from gemm_b200 import _native
+from gemm_b200.ops import elementwise as ew
+from gemm_b200.ops import moe, mxfp8, sampling
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def test_embed():
+    table = torch.randn(1000, 256, device="cuda").bfloat16()
+    ids = torch.randint(0, 1000, (37,), device="cuda", dtype=torch.int32)
+    assert torch.equal(ew.embed(ids, table), table[ids.long()])
+
+
+@pytest.mark.parametrize("rows,hidden", [(5, 1024), (33, 2048), (7, 4096), (3, 5120), (2, 8192)])
+def test_rmsnorm(rows, hidden):
+    torch.manual_seed(0)
+    x = torch.randn(rows, hidden, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda")).bfloat16()
+    y = ew.rmsnorm(x, w, 1e-6)
+    assert _rel(y, ew.rmsnorm_ref(x, w, 1e-6)) < 4e-3
+
+
+def test_rmsnorm_residual_quant():
+    torch.manual_seed(1)
+    rows, hidden = 70, 2048
+    res = torch.randn(rows, hidden, device="cuda").bfloat16()
+    delta = torch.randn(rows, hidden, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(hidden, device="cuda")).bfloat16()
+    res_ref = (res.float() + delta.float()).bfloat16()
+    y_ref = ew.rmsnorm_ref(res_ref, w, 1e-6)
+    y, q = ew.rmsnorm(delta, w, 1e-6, residual=res, quantize=True)
+    assert torch.equal(res, res_ref)
+    assert _rel(y, y_ref) < 4e-3
+    # the quantised copy must be exactly what the reference quantiser makes of the kernel's bf16 output
+    q_ref = mxfp8.quantize(y.float())
+    assert torch.equal(q.data[:rows], q_ref.data[:rows])
+    assert torch.equal(mxfp8.unpack_sf_atoms(q.sf, rows, hidden // 32), mxfp8.unpack_sf_atoms(q_ref.sf, rows, hidden // 32))
+
+
+@pytest.mark.parametrize("d,rope_dim", [(128, None), (64, None), (256, 64)])
+def test_qk_norm_rope(d, rope_dim):
+    torch.manual_seed(2)
+    t, hq, hkv = 19, 8, 2
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+    pos = torch.randint(0, 5000, (t,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(64, device="cuda")[:t].to(torch.int32)
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    kc = torch.zeros(64, hkv, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros(64, hkv, d, device="cuda", dtype=torch.bfloat16)
+    q = ew.qk_norm_rope(qkv, pos, slots, qw, kw, kc, vc, hq, hkv, d, 1e6, 1e-6, 0.25, rope_dim)
+    qr, kr, vr = ew.qk_norm_rope_ref(qkv, pos, qw, kw, hq, hkv, d, 1e6, 1e-6, 0.25, rope_dim)
+    assert _rel(q, qr) < 6e-3
+    assert _rel(kc[slots.long()], kr) < 6e-3
+    assert torch.equal(vc[slots.long()], vr)
+
+
+def test_silu_mul_and_quant_gather():
+    torch.manual_seed(3)
+    gu = torch.randn(50, 512, device="cuda").bfloat16()
+    ref = torch.nn.functional.silu(gu.float()[:, :256]) * gu.float()[:, 256:]
+    assert _rel(ew.silu_mul(gu), ref) < 4e-3
+    x = torch.randn(40, 256, device="cuda").bfloat16()
+    src = torch.tensor([3, -1, 7, 7, 0, 39, -1, 12], device="cuda", dtype=torch.int32)
+    q = ew.mx_quantize(x, src)
+    g = torch.zeros(8, 256, device="cuda")
+    ok = src >= 0
+    g[ok] = x.float()[src[ok].long()]
+    q_ref = mxfp8.quantize(g)
+    assert torch.equal(q.data[:8], q_ref.data[:8])
+    assert torch.equal(mxfp8.unpack_sf_atoms(q.sf, 8, 8), mxfp8.unpack_sf_atoms(q_ref.sf, 8, 8))
+
+
+@pytest.mark.parametrize("mode", ["softmax", "sigmoid"])
+def test_moe_route(mode):
+    torch.manual_seed(4)
+    t, e, k = 300, 128, 8
+    logits = torch.randn(t, e, device="cuda")
+    logits[5, 7] = float("nan")
+    logits[6, :] = 0.0                      # all ties -> ids 0..7
+    bias = torch.randn(e, device="cuda") * 0.1 if mode == "sigmoid" else None
+    ids, w = moe.route(logits, k, mode, bias, True, 2.5 if mode == "sigmoid" else 1.0)
+    ids_r, w_r = moe.route_ref(logits.cpu(), k, mode, bias.cpu() if bias is not None else None, True, 2.5 if mode == "sigmoid" else 1.0)
+    assert torch.equal(ids.cpu(), ids_r)
+    assert torch.allclose(w.cpu(), w_r, rtol=1e-4, atol=1e-6)
+    if mode == "softmax":
+        assert ids[6].tolist() == list(range(8))
+
+
+@pytest.mark.parametrize("t,regions", [(1, 1), (64, 1), (1000, 1), (300, 8)])
+def test_moe_plan_and_combine(t, regions):
+    torch.manual_seed(5)
+    e, k, align, hidden = 128, 8, 128, 256
+    logits = torch.randn(t, e, device="cuda")
+    ids, w = moe.route(logits, k)
+    pl = moe.plan(ids, e, align, regions)
+    ref = moe.plan_ref(ids.cpu(), e, k, align, regions)
+    assert torch.equal(pl.seg_count.cpu(), ref.seg_count)
+    assert torch.equal(pl.seg_start.cpu(), ref.seg_start)
+    assert torch.equal(pl.pair_row.cpu(), ref.pair_row)
+    assert torch.equal(pl.row_token.cpu(), ref.row_token)
+    assert torch.equal(pl.region_used.cpu(), ref.region_used)
+    x = torch.randn(t, hidden, device="cuda").bfloat16()
+    xs = moe.gather_rows(x, pl.row_token)
+    ok = pl.row_token >= 0
+    assert torch.equal(xs[ok], x[pl.row_token[ok].long()])
+    out = moe.combine(xs, pl.pair_row, w, t, k)
+    assert _rel(out, x.float() * w.sum(-1, keepdim=True)) < 5e-3
+
+
+def test_argmax_and_sample():
+    torch.manual_seed(6)
+    b, v = 5, 151936
+    logits = torch.randn(b, v, device="cuda")
+    logits[2, 100] = logits[2, 50000] = 50.0         # tie -> lower id
+    assert sampling.argmax(logits).tolist() == torch.tensor([int(logits[i].argmax()) if i != 2 else 100 for i in range(b)]).tolist()
+    assert sampling.argmax(logits.bfloat16(), idx_offset=7)[2].item() == 107
+    # sampled tokens must come from the reference candidate set; frequencies roughly follow p
+    row = torch.randn(v, device="cuda") * 3
+    idx, p = sampling.candidate_set_ref(row.cpu(), 0.8, 20, 0.9)
+    draws = torch.stack([sampling.sample(row.unsqueeze(0), 0.8, 20, 0.9, seed=1, step=s) for s in range(400)]).flatten().cpu()
+    allowed = set(idx.tolist())
+    assert all(int(d) in allowed for d in draws)
+    top = int(idx[0])
+    freq = (draws == top).float().mean().item()
+    assert abs(freq - float(p[0])) < 0.12
+    _native.assert_status_ok()
