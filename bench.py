@@ -1,0 +1,250 @@
+#!/usr/bin/env python
+"""Headline benchmark: Qwen3-30B-A3B-shaped MoE, MXFP8, decode tokens/s (plus prefill tokens/s, TTFT, TPOT).
+
+    python bench.py --gpus N --steps K --warmup W            # N = 1; torchrun launches N > 1
+    python bench.py --impl reference ...                      # the reference arm (unavailable: see DESIGN.md)
+
+Workload (BASELINE.json config 3): 48 layers, hidden 2048, 32 Q / 4 KV heads of 128, 128 experts top-8 with
+expert FFN 768, vocab 151936; random-init N(0, 0.02) weights quantised to MXFP8 (1x32 E8M0 scales), MXFP8
+activations, bf16 outputs; 64 prompts of 2048 uniform-random token ids are prefilled, then decoded greedily.
+With N GPUs the 64 sequences are split N ways for attention (data parallel) and the 128 experts N ways
+(expert parallel), so the total work is fixed: strong scaling.
+
+A timed *step* is one decode step of the whole 64-sequence batch at context >= 2048: it streams every expert's
+weights (~29 GB over the job) and the KV cache (~13 GB) from HBM, far more than the 126 MB L2, so no L2 flush
+is needed between steps.  ``value`` = decoded tokens per second over the whole job, timed on the device with
+CUDA events, max over ranks.  The ``e2e`` figure drives the same steps through the public ``Engine`` API with
+the step's input token ids copied from pinned host memory and the sampled ids read back to the host each step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3-30b-a3b")
+    ap.add_argument("--fmt", default="mxfp8", choices=["mxfp8", "bf16"])
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: run fewer layers (the JSON line then says so and is not a valid bench number)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--moe-path", default="fused", choices=["fused", "nccl"], help="multi-GPU expert exchange: fused peer-memory kernels or the NCCL baseline")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, parts[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        busy = [c for c, p in zip(sm, power) if p > 300] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def reference_arm(args):
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "the reference is a C source tree without setup.py/pyproject.toml (pip: 'not installable'); its CUDA runner is "
+                      "single-GPU, batch 1 and does not load the qwen3moe architecture, so this metric/config has no reference code path"}))
+    return 0
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from gemm_b200 import _native
+    from gemm_b200.models.config import get_config
+    from gemm_b200.models.weights import synthetic_weights
+    from gemm_b200.serve.engine import Engine, SamplingParams
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    par = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        from gemm_b200.parallel.expert import ExpertParallel
+        par = ExpertParallel(dist.group.WORLD, device, fused=(args.moe_path == "fused"))
+    if args.gpus != world and rank == 0:
+        print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
+    n_gpus = world
+
+    cfg = get_config(args.model)
+    n_layers = args.layers if args.layers > 0 else cfg.n_layers
+    assert args.batch % n_gpus == 0
+    b_local = args.batch // n_gpus
+    t0 = time.time()
+    weights = synthetic_weights(cfg, args.fmt, device=device, seed=0, ep_rank=rank, ep_size=n_gpus, n_layers=n_layers)
+    torch.cuda.synchronize()
+    if rank == 0:
+        print(f"[bench] weights {weights.nbytes() / 2**30:.1f} GiB on rank 0 in {time.time() - t0:.1f}s", file=sys.stderr)
+    total_new = args.warmup + args.steps * (1 if args.no_e2e else 2) + 16
+    max_len = args.prompt_len + total_new + 8
+    engine = Engine(weights, max_batch=b_local, max_seq_len=max_len, page_size=128, par=par, max_prefill_tokens=16384)
+    if par is not None:
+        par.attach(engine, cfg, max_tokens=16384)
+
+    # synthetic prompts: uniform token ids from seed 0 (the same global batch whatever N is)
+    g = torch.Generator().manual_seed(0)
+    all_prompts = torch.randint(0, cfg.vocab, (args.batch, args.prompt_len), generator=g, dtype=torch.int32)
+    prompts = [all_prompts[rank * b_local + i] for i in range(b_local)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- prefill (TTFT, prefill tok/s)
+    # warm-up pass on a short prompt so that lazy initialisation is not timed
+    engine.prefill([prompts[0][:256]])
+    engine.reset()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    logits = engine.prefill(prompts, reserve=total_new)
+    first = engine._sample(logits, SamplingParams(), 0)
+    e1.record()
+    barrier()
+    prefill_ms = max_over_ranks(e0.elapsed_time(e1))
+    prefill_tok_s = args.batch * args.prompt_len / (prefill_ms / 1e3)
+
+    # ---------------------------------------------------------------- decode (device-timed steps)
+    engine.begin_decode(first, SamplingParams(), max_new_tokens=total_new, use_graph=True)
+    launches_before = _native.launch_count()
+    engine._decode_body_count = None
+    for _ in range(args.warmup):
+        engine.decode_step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    step_ms = []
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    evs[0].record()
+    for i in range(args.steps):
+        engine.decode_step()
+        evs[i + 1].record()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = max_over_ranks(evs[0].elapsed_time(evs[-1]))
+    per_step = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    tpot_p50 = max_over_ranks(statistics.median(per_step))
+    decode_tok_s = args.batch * args.steps / (total_ms / 1e3)
+    kernels_per_step = engine.kernels_per_step
+    st = _native.read_status()
+
+    # ---------------------------------------------------------------- end to end through the public API
+    e2e = None
+    if not args.no_e2e:
+        ids_host = torch.empty(b_local, dtype=torch.int32).pin_memory()
+        out_host = torch.empty(b_local, dtype=torch.int32).pin_memory()
+        ids_host.copy_(engine._static["tokens"].cpu())
+        for _ in range(3):
+            engine.set_next_tokens(ids_host); out_host.copy_(engine.decode_step(), non_blocking=True); torch.cuda.synchronize(); ids_host.copy_(out_host)
+        barrier()
+        w0 = torch.cuda.Event(enable_timing=True); w1 = torch.cuda.Event(enable_timing=True)
+        w0.record()
+        for _ in range(args.steps):
+            engine.set_next_tokens(ids_host)                       # H2D: this step's input ids from pinned memory
+            toks = engine.decode_step()
+            out_host.copy_(toks, non_blocking=True)                # D2H: the step's result
+            torch.cuda.synchronize()
+            ids_host.copy_(out_host)                               # the host owns the token stream
+        w1.record()
+        barrier()
+        e2e_ms = max_over_ranks(w0.elapsed_time(w1))
+        e2e = {"value": args.batch * args.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": b_local * 4 * n_gpus,
+               "d2h_bytes_per_step": b_local * 4 * n_gpus, "ms_per_step": e2e_ms / args.steps}
+
+    if rank == 0:
+        line = {
+            "metric": "decode_tokens_per_s", "value": decode_tok_s, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "mxfp8 weights+activations, bf16 outputs, fp32 accumulate" if args.fmt == "mxfp8" else "bf16",
+            "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
+            "config": {"model": args.model, "global_batch": args.batch, "seq_len": args.prompt_len, "decode_context": args.prompt_len + args.warmup,
+                       "parallelism": f"dp{n_gpus}-attention+ep{n_gpus}" if n_gpus > 1 else "single", "layers": n_layers,
+                       "l2": "no flush: each step streams ~29 GB of expert weights and ~13 GB of KV over the job, inputs >> 126 MB L2",
+                       "moe_path": args.moe_path if n_gpus > 1 else "local"},
+            "prefill_tokens_per_s": prefill_tok_s, "ttft_ms_p50": prefill_ms, "tpot_ms_p50": tpot_p50,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": kernels_per_step * args.steps,
+            "kernels_per_step": kernels_per_step, "kernel_status": st["what"], "native_libs": _native.loaded_libraries(),
+        }
+        if n_layers != cfg.n_layers:
+            line["invalid"] = f"debug run with {n_layers} of {cfg.n_layers} layers"
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        if par is not None:
+            par.close()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -58,11 +58,21 @@ def cuda_available() -> bool:
     return (_LIB_DIR / "libgb_cuda.so").exists()
 
 
-def check(rc: int, what: str = "kernel launch"):
-    """Raise with the library's message if a native call returned non-zero."""
+_launches = 0
+
+
+def check(rc: int, what: str = "kernel launch", n: int = 1):
+    """Raise with the library's message if a native call returned non-zero; count its ``n`` kernel launches."""
+    global _launches
     if rc != 0:
         msg = cuda().gb_last_error().decode(errors="replace")
         raise RuntimeError(f"{what} failed: {msg}")
+    _launches += n
+
+
+def launch_count() -> int:
+    """Kernels of this library launched (or captured into a graph) so far by this process."""
+    return _launches
 
 
 def loaded_libraries():

@@ -262,9 +262,31 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16
   if (i < n) out[i] = __float2bfloat16(in[i]);
 }
 
+// Decode bookkeeping kept on the device so that a captured step can be replayed without the host:
+// every live sequence advances by one position; its next slot comes from the block table.
+__global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ kv_len, int* __restrict__ slots,
+                                      const int* __restrict__ block_table, const int* __restrict__ live, int max_pages, int page_size, int n) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n) return;
+  if (live != nullptr && live[b] == 0) return;
+  const int p = positions[b] + 1;
+  positions[b] = p;
+  kv_len[b] = p + 1;
+  const int page = block_table[(size_t)b * max_pages + min(p / page_size, max_pages - 1)];
+  slots[b] = page * page_size + p % page_size;
+}
+
 }  // namespace gb
 
 using namespace gb;
+
+GB_API int gb_decode_advance(int* positions, int* kv_len, int* slots, const int* block_table, const int* live, int max_pages,
+                             int page_size, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, kv_len, slots, block_table, live, max_pages, page_size, n);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 GB_API int gb_embed(const int* ids, const void* table, void* out, int n_tok, int hidden, int vocab, cudaStream_t stream) {
   if (hidden % 8) return fail("embed: hidden %% 8 != 0%s");

@@ -1,0 +1,233 @@
+"""Decoder-only transformer (Qwen2 / Qwen3 dense and Qwen3-MoE) over a paged KV cache.
+
+One ``forward`` serves prefill chunks, decode steps and mixed batches: tokens of all sequences are packed
+into ``[T, hidden]`` rows, attention works from per-sequence metadata (``ForwardBatch``).  Every op is a
+hand-written sm_100a kernel from ``gemm_b200.ops`` when the tensors are on a GPU; on CPU tensors the same
+call sequence runs the PyTorch references, which is how the layer logic is tested without a GPU.
+
+Layer recipe (reference: common/transformer.h:3550-4174):
+  h = RMSNorm(x); qkv = h Wqkv^T (+bias); per-head QK-RMSNorm; NeoX RoPE; K/V -> paged cache;
+  a = causal GQA attention; x += a Wo^T  [tensor-parallel: all-reduce]
+  h = RMSNorm(x); dense: x += (SiLU(h Wg^T) * h Wu^T) Wd^T  [TP all-reduce]
+                  MoE  : softmax router -> top-k -> renormalise; x += sum_k w_k FFN_k(h)  [EP dispatch / combine]
+  logits = RMSNorm(x) Whead^T on the last token of every sequence.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..ops import attention as att
+from ..ops import elementwise as ew
+from ..ops import gemm, moe, sampling
+from ..ops.mxfp8 import MxTensor
+from .config import ModelConfig
+from .weights import LinearWeight, ModelWeights
+
+
+@dataclass
+class KvCache:
+    """Paged KV storage: per layer ``k`` and ``v`` of shape ``[num_pages * page_size, Hkv_local, D]`` (bf16)."""
+    k: List[torch.Tensor]
+    v: List[torch.Tensor]
+    page_size: int
+    num_pages: int
+
+    @staticmethod
+    def allocate(cfg: ModelConfig, num_pages: int, page_size: int, device, hkv_local: Optional[int] = None,
+                 n_layers: Optional[int] = None) -> "KvCache":
+        hkv = hkv_local if hkv_local is not None else cfg.n_kv_heads
+        nl = n_layers if n_layers is not None else cfg.n_layers
+        shape = (num_pages * page_size, hkv, cfg.head_dim)
+        return KvCache([torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(nl)],
+                       [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(nl)], page_size, num_pages)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * 2 for t in self.k) * 2
+
+
+@dataclass
+class ForwardBatch:
+    ids: torch.Tensor              # int32 [T]
+    positions: torch.Tensor        # int32 [T]
+    slots: torch.Tensor            # int32 [T] cache slot of every token (-1 = do not store)
+    cu_q: torch.Tensor             # int32 [B+1]
+    kv_len: torch.Tensor           # int32 [B] length including this step's tokens
+    block_table: torch.Tensor      # int32 [B, max_pages]
+    work: torch.Tensor             # int32 [n_work, 4] attention work list
+    logit_rows: torch.Tensor       # int32/int64 [B'] rows of T whose logits are wanted
+    num_splits: int = 1
+    embeds: Optional[torch.Tensor] = None   # bf16 [T, H]: injected embeddings instead of ids (vision tokens)
+    n_tokens: int = 0
+
+    @staticmethod
+    def build(q_lens: Sequence[int], ctx_lens: Sequence[int], ids, block_table: torch.Tensor, page_size: int, hq: int, hkv: int,
+              device, num_splits: int = 1, all_logits: bool = False) -> "ForwardBatch":
+        """Host-side assembly from per-sequence chunk lengths and the lengths already cached."""
+        b = len(q_lens)
+        pos, slots, cu = [], [], [0]
+        bt = block_table.cpu()
+        for s in range(b):
+            for i in range(q_lens[s]):
+                p = ctx_lens[s] + i
+                pos.append(p)
+                slots.append(int(bt[s, p // page_size]) * page_size + p % page_size)
+            cu.append(cu[-1] + q_lens[s])
+        t = cu[-1]
+        rows = list(range(t)) if all_logits else [cu[s + 1] - 1 for s in range(b) if q_lens[s] > 0]
+        i32 = dict(dtype=torch.int32, device=device)
+        ids_t = ids.to(device=device, dtype=torch.int32) if torch.is_tensor(ids) else torch.tensor(ids, **i32)
+        return ForwardBatch(ids=ids_t, positions=torch.tensor(pos, **i32), slots=torch.tensor(slots, **i32),
+                            cu_q=torch.tensor(cu, **i32), kv_len=torch.tensor([c + q for c, q in zip(ctx_lens, q_lens)], **i32),
+                            block_table=block_table.to(device=device, dtype=torch.int32),
+                            work=att.build_work(q_lens, hq, hkv, num_splits).to(device),
+                            logit_rows=torch.tensor(rows, dtype=torch.int64, device=device), num_splits=num_splits, n_tokens=t)
+
+
+class SingleProcess:
+    """Parallel context of an unsharded model: every collective is the identity."""
+    tp_size = 1
+    tp_rank = 0
+    ep_size = 1
+    ep_rank = 0
+
+    def tp_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def moe_ffn(self, model: "Transformer", lw, h: torch.Tensor) -> Optional[torch.Tensor]:
+        return None            # None -> the model runs its local MoE path
+
+
+def apply_linear(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``x W^T (+ bias)`` in the weight's format; ``x_mx`` is an already-quantised copy of ``x`` if the caller has one."""
+    if lw.fmt == "bf16":
+        return gemm.linear(x, lw.w, bias=lw.bias, out_dtype=out_dtype)
+    xm = x_mx if x_mx is not None else ew.mx_quantize(x)
+    y = gemm.linear_mx(xm, lw.mx, out_dtype=out_dtype, bias=lw.bias)
+    return y
+
+
+class Transformer:
+    def __init__(self, weights: ModelWeights, kv: KvCache, par=None):
+        self.w = weights
+        self.cfg = weights.cfg
+        self.kv = kv
+        self.par = par if par is not None else SingleProcess()
+        cfg = self.cfg
+        self.hq_local = cfg.n_heads // weights.tp_size
+        self.hkv_local = max(1, cfg.n_kv_heads // weights.tp_size)
+        self.q_scale = ew.softmax_scale_log2(cfg.head_dim)
+        self.mx = weights.fmt == "mxfp8"
+        self.snapshots = {}            # layer -> hidden rows captured after that layer (debug / DeepStack)
+        self.snapshot_layers: Sequence[int] = ()
+
+    # ------------------------------------------------------------------------------------------------
+    def attention_block(self, li: int, lw, h: torch.Tensor, h_mx: Optional[MxTensor], fb: ForwardBatch) -> torch.Tensor:
+        cfg = self.cfg
+        qkv = apply_linear(lw.wqkv, h, h_mx)
+        q = ew.qk_norm_rope(qkv, fb.positions, fb.slots, lw.q_norm, lw.k_norm, self.kv.k[li], self.kv.v[li], self.hq_local,
+                            self.hkv_local, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, cfg.rope_dim)
+        a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
+                          num_splits=fb.num_splits, causal=True, window=cfg.sliding_window)
+        a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
+        o = apply_linear(lw.wo, a2)
+        return self.par.tp_all_reduce(o)
+
+    def dense_ffn(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor]) -> torch.Tensor:
+        if lw.w_gate_up.fmt == "bf16":
+            act = gemm.linear_swiglu(h, lw.w_gate_up.w)
+            y = gemm.linear(act, lw.w_down.w)
+        else:
+            xm = h_mx if h_mx is not None else ew.mx_quantize(h)
+            act = gemm.linear_mx_swiglu_quant(xm, lw.w_gate_up.mx)
+            y = gemm.linear_mx(act, lw.w_down.mx)
+        return self.par.tp_all_reduce(y)
+
+    def moe_local(self, lw, h: torch.Tensor) -> torch.Tensor:
+        """All experts on this GPU: route -> plan -> (gather + quantise) -> grouped gate/up -> grouped down -> combine."""
+        cfg = self.cfg
+        t = h.shape[0]
+        e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
+        logits = gemm.linear(h, lw.router, out_dtype=torch.float32)
+        ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+        if self.mx:
+            pl = moe.plan(ids, e, 128)
+            xq = ew.mx_quantize(h, pl.row_token)
+            dev = h.device
+            hq = torch.zeros(pl.capacity, inter, dtype=torch.uint8, device=dev)
+            hsf = torch.full((pl.capacity // 128, inter // 128, 512), 127, dtype=torch.uint8, device=dev)
+            gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, 128, out=hq, dual=True,
+                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf)
+            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, 128, sfa=lw.w2.mx.sf, sfb=hsf)
+        else:
+            tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
+            pl = moe.plan(ids, e, tn)
+            xs = moe.gather_rows(h, pl.row_token)
+            act = gemm.grouped_linear(xs, lw.w13.w.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True)
+            y = gemm.grouped_linear(act, lw.w2.w.view(e, hid, inter), pl.seg_start, pl.seg_count, tn)
+        return moe.combine(y, pl.pair_row, wts, t, k)
+
+    # ------------------------------------------------------------------------------------------------
+    def forward_hidden(self, fb: ForwardBatch, first_layer: int = 0, last_layer: Optional[int] = None,
+                       x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Residual stream after layers ``[first_layer, last_layer)`` (pipeline stages pass ``x`` in)."""
+        cfg, w = self.cfg, self.w
+        last_layer = len(w.layers) if last_layer is None else last_layer
+        if x is None:
+            x = fb.embeds if fb.embeds is not None else ew.embed(fb.ids, w.embed)
+        delta = None
+        for li in range(first_layer, last_layer):
+            lw = w.layers[li]
+            if self.mx:
+                h, h_mx = ew.rmsnorm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps,
+                                     residual=x if delta is not None else None, quantize=True, want_bf16=False)
+            else:
+                h, h_mx = ew.rmsnorm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps,
+                                     residual=x if delta is not None else None), None
+            delta = self.attention_block(li, lw, h, h_mx, fb)
+            need_bf16 = (not self.mx) or cfg.is_moe
+            if self.mx:
+                h, h_mx = ew.rmsnorm(delta, lw.ffn_norm, cfg.rms_eps, residual=x, quantize=True, want_bf16=need_bf16)
+            else:
+                h, h_mx = ew.rmsnorm(delta, lw.ffn_norm, cfg.rms_eps, residual=x), None
+            if lw.w13 is not None:
+                delta = self.par.moe_ffn(self, lw, h)
+                if delta is None:
+                    delta = self.moe_local(lw, h)
+            else:
+                delta = self.dense_ffn(lw, h, h_mx)
+            if li in self.snapshot_layers:
+                self.snapshots[li] = (x.float() + delta.float())
+        if delta is not None:
+            # fold the last delta into the stream (the final norm kernel does it for the full model)
+            self._last_delta = delta
+        else:
+            self._last_delta = None
+        return x
+
+    def forward(self, fb: ForwardBatch) -> torch.Tensor:
+        """Logits ``f32 [len(logit_rows), V_local]``."""
+        x = self.forward_hidden(fb)
+        return self.head(x, fb)
+
+    def head(self, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        cfg, w = self.cfg, self.w
+        delta = self._last_delta
+        rows = fb.logit_rows
+        xr = x[rows]
+        if delta is not None:
+            xr = (xr.float() + delta[rows].float()).to(torch.bfloat16)
+        hn = ew.rmsnorm(xr.contiguous(), w.final_norm, cfg.rms_eps)
+        return gemm.linear(hn, w.lm_head.w, out_dtype=torch.float32)
+
+    def final_hidden(self, x: torch.Tensor) -> torch.Tensor:
+        """Residual stream with the pending delta folded in (what a pipeline stage hands to the next)."""
+        if self._last_delta is None:
+            return x
+        return (x.float() + self._last_delta.float()).to(torch.bfloat16)
+
+
+def greedy_tokens(logits: torch.Tensor, vocab_start: int = 0) -> torch.Tensor:
+    return sampling.argmax(logits, idx_offset=vocab_start)

@@ -1,0 +1,226 @@
+"""Weight containers and the synthetic (random-init) checkpoint generator.
+
+A ``LinearWeight`` keeps one projection in the format the kernels consume:
+
+* ``bf16``   row-major ``[N, K]``
+* ``mxfp8``  e4m3 bytes + E8M0 scale atoms (``ops.mxfp8.MxTensor``)
+
+Grouped (expert) weights use the same class with ``groups > 0`` and rows stacked expert after expert.
+Tensor-parallel and expert-parallel shards are cut when the weights are made or loaded, never at run
+time (the reference slices TP rows out of the full matrix on every call, common/transformer.h:4239-4272).
+
+Random init follows the benchmark recipe: N(0, 0.02) for matrices, ones for norms, seeded per tensor so
+that a sharded model is a slice of the unsharded one.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..ops import elementwise as ew
+from ..ops import mxfp8
+from ..ops.mxfp8 import MxTensor
+from .config import ModelConfig
+
+
+@dataclass
+class LinearWeight:
+    fmt: str                                  # "bf16" | "mxfp8"
+    n: int                                    # output features (per group)
+    k: int
+    w: Optional[torch.Tensor] = None          # bf16 [rows, K]
+    mx: Optional[MxTensor] = None
+    bias: Optional[torch.Tensor] = None       # f32 [n]
+    groups: int = 0                           # > 0: expert-stacked, rows = groups * rows_per_group
+    rows_per_group: int = 0
+
+    @property
+    def device(self):
+        return self.w.device if self.w is not None else self.mx.data.device
+
+    def dequantized(self) -> torch.Tensor:
+        """fp32 copy of the full matrix (tests and CPU reference paths)."""
+        if self.fmt == "bf16":
+            return self.w.float()
+        return mxfp8.dequantize(self.mx)
+
+    def nbytes(self) -> int:
+        if self.fmt == "bf16":
+            return self.w.numel() * 2
+        return self.mx.data.numel() + self.mx.sf.numel()
+
+    def to(self, device) -> "LinearWeight":
+        return LinearWeight(self.fmt, self.n, self.k, w=self.w.to(device) if self.w is not None else None,
+                            mx=self.mx.to(device) if self.mx is not None else None,
+                            bias=self.bias.to(device) if self.bias is not None else None, groups=self.groups,
+                            rows_per_group=self.rows_per_group)
+
+
+def make_linear(w_f: torch.Tensor, fmt: str, bias: Optional[torch.Tensor] = None, groups: int = 0) -> LinearWeight:
+    """Wrap a float / bf16 matrix ``[rows, K]`` (rows = groups * rows_per_group when grouped)."""
+    rows, k = w_f.shape
+    rpg = rows // groups if groups else 0
+    n = rpg if groups else rows
+    if fmt == "bf16":
+        return LinearWeight("bf16", n, k, w=w_f.to(torch.bfloat16).contiguous(), bias=bias, groups=groups, rows_per_group=rpg)
+    if fmt == "mxfp8":
+        if w_f.is_cuda:
+            mx = ew.mx_quantize(w_f.to(torch.bfloat16).contiguous())
+        else:
+            mx = mxfp8.quantize(w_f.to(torch.bfloat16).float())
+        return LinearWeight("mxfp8", n, k, mx=mx, bias=bias, groups=groups, rows_per_group=rpg)
+    raise ValueError(f"unknown weight format {fmt!r}")
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    wqkv: LinearWeight
+    wo: LinearWeight
+    ffn_norm: torch.Tensor
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    w_gate_up: Optional[LinearWeight] = None      # dense FFN, rows [gate ; up]
+    w_down: Optional[LinearWeight] = None
+    router: Optional[torch.Tensor] = None         # bf16 [E, H]
+    router_bias: Optional[torch.Tensor] = None    # f32 [E] (sigmoid router)
+    w13: Optional[LinearWeight] = None            # experts, rows per expert [gate ; up] = 2I
+    w2: Optional[LinearWeight] = None             # experts, rows per expert = H, K = I
+
+
+@dataclass
+class ModelWeights:
+    cfg: ModelConfig
+    embed: torch.Tensor                           # bf16 [V, H]
+    layers: List[LayerWeights]
+    final_norm: torch.Tensor
+    lm_head: LinearWeight                         # bf16 [V(/tp), H]
+    fmt: str = "bf16"
+    tp_rank: int = 0
+    tp_size: int = 1
+    ep_rank: int = 0
+    ep_size: int = 1
+    vocab_start: int = 0                          # first vocabulary id of the LM-head shard
+
+    def to(self, device) -> "ModelWeights":
+        def mv(x):
+            return x.to(device) if x is not None else None
+        layers = [LayerWeights(attn_norm=mv(l.attn_norm), wqkv=mv(l.wqkv), wo=mv(l.wo), ffn_norm=mv(l.ffn_norm), q_norm=mv(l.q_norm),
+                               k_norm=mv(l.k_norm), w_gate_up=mv(l.w_gate_up), w_down=mv(l.w_down), router=mv(l.router),
+                               router_bias=mv(l.router_bias), w13=mv(l.w13), w2=mv(l.w2)) for l in self.layers]
+        return ModelWeights(cfg=self.cfg, embed=mv(self.embed), layers=layers, final_norm=mv(self.final_norm), lm_head=mv(self.lm_head),
+                            fmt=self.fmt, tp_rank=self.tp_rank, tp_size=self.tp_size, ep_rank=self.ep_rank, ep_size=self.ep_size,
+                            vocab_start=self.vocab_start)
+
+    def nbytes(self) -> int:
+        tot = self.embed.numel() * 2 + self.lm_head.nbytes()
+        for l in self.layers:
+            for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.w13, l.w2):
+                if lw is not None:
+                    tot += lw.nbytes()
+        return tot
+
+
+def _randn(shape, seed: int, device, std: float = 0.02) -> torch.Tensor:
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return torch.randn(shape, generator=g, device=device, dtype=torch.float32).mul_(std).to(torch.bfloat16)
+
+
+def _seed(base: int, layer: int, tensor: int) -> int:
+    return (base * 1000003 + layer * 1009 + tensor) & 0x7FFFFFFF
+
+
+def shard_range(n: int, parts: int, idx: int):
+    """Even split with the remainder to the low ranks (the rule of common/glm5.h:178-202)."""
+    q, r = divmod(n, parts)
+    lo = idx * q + min(idx, r)
+    return lo, lo + q + (1 if idx < r else 0)
+
+
+def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
+                      ep_rank: int = 0, ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None) -> ModelWeights:
+    """Random-init weights of ``cfg`` in format ``fmt``; TP shards attention / dense FFN (Megatron style:
+    q/k/v/gate/up by rows, o/down by columns), EP keeps the experts ``e`` with ``e // (E / ep_size) == ep_rank``.
+    KV heads are replicated when ``n_kv_heads < tp_size``."""
+    h, d = cfg.hidden, cfg.head_dim
+    assert cfg.n_heads % tp_size == 0, "n_heads must divide by the TP size"
+    hq_l = cfg.n_heads // tp_size
+    if cfg.n_kv_heads >= tp_size:
+        assert cfg.n_kv_heads % tp_size == 0
+        hkv_l = cfg.n_kv_heads // tp_size
+        kv_lo = tp_rank * hkv_l
+    else:
+        assert tp_size % cfg.n_kv_heads == 0
+        hkv_l = 1
+        kv_lo = tp_rank // (tp_size // cfg.n_kv_heads)
+    layers: List[LayerWeights] = []
+    nl = n_layers if n_layers is not None else cfg.n_layers
+    for li in range(nl):
+        wq = _randn((cfg.q_dim, h), _seed(seed, li, 1), device)[tp_rank * hq_l * d:(tp_rank + 1) * hq_l * d]
+        wk = _randn((cfg.kv_dim, h), _seed(seed, li, 2), device)[kv_lo * d:(kv_lo + hkv_l) * d]
+        wv = _randn((cfg.kv_dim, h), _seed(seed, li, 3), device)[kv_lo * d:(kv_lo + hkv_l) * d]
+        wo = _randn((h, cfg.q_dim), _seed(seed, li, 4), device)[:, tp_rank * hq_l * d:(tp_rank + 1) * hq_l * d]
+        bias = None
+        if cfg.qkv_bias:
+            bq = _randn((cfg.q_dim,), _seed(seed, li, 20), device).float()[tp_rank * hq_l * d:(tp_rank + 1) * hq_l * d]
+            bk = _randn((cfg.kv_dim,), _seed(seed, li, 21), device).float()[kv_lo * d:(kv_lo + hkv_l) * d]
+            bv = _randn((cfg.kv_dim,), _seed(seed, li, 22), device).float()[kv_lo * d:(kv_lo + hkv_l) * d]
+            bias = torch.cat([bq, bk, bv]).contiguous()
+        lw = LayerWeights(
+            attn_norm=torch.ones(h, dtype=torch.bfloat16, device=device),
+            wqkv=make_linear(torch.cat([wq, wk, wv]), fmt, bias=bias),
+            wo=make_linear(wo.contiguous(), fmt),
+            ffn_norm=torch.ones(h, dtype=torch.bfloat16, device=device),
+            q_norm=torch.ones(d, dtype=torch.bfloat16, device=device) if cfg.qk_norm else None,
+            k_norm=torch.ones(d, dtype=torch.bfloat16, device=device) if cfg.qk_norm else None,
+        )
+        del wq, wk, wv, wo
+        if cfg.is_moe:
+            e, inter = cfg.n_experts, cfg.expert_ffn
+            assert e % ep_size == 0
+            e_l = e // ep_size
+            lw.router = _randn((e, h), _seed(seed, li, 5), device)
+            if cfg.router == "sigmoid":
+                lw.router_bias = torch.zeros(e, dtype=torch.float32, device=device)
+            # experts are generated one EP shard at a time so that the peak stays one shard
+            g13 = torch.Generator(device=device); g13.manual_seed(_seed(seed, li, 6))
+            g2 = torch.Generator(device=device); g2.manual_seed(_seed(seed, li, 7))
+            w13 = w2 = None
+            for r in range(ep_size):
+                a = torch.randn((e_l * 2 * inter, h), generator=g13, device=device, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
+                b = torch.randn((e_l * h, inter), generator=g2, device=device, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
+                if r == ep_rank:
+                    w13, w2 = a, b
+                    if ep_rank == ep_size - 1:
+                        break
+                else:
+                    del a, b
+            lw.w13 = make_linear(w13, fmt, groups=e_l)
+            lw.w2 = make_linear(w2, fmt, groups=e_l)
+            del w13, w2
+        else:
+            f = cfg.ffn
+            assert f % tp_size == 0
+            f_l = f // tp_size
+            wg = _randn((f, h), _seed(seed, li, 8), device)[tp_rank * f_l:(tp_rank + 1) * f_l]
+            wu = _randn((f, h), _seed(seed, li, 9), device)[tp_rank * f_l:(tp_rank + 1) * f_l]
+            wd = _randn((h, f), _seed(seed, li, 10), device)[:, tp_rank * f_l:(tp_rank + 1) * f_l]
+            lw.w_gate_up = make_linear(torch.cat([wg, wu]), fmt)
+            lw.w_down = make_linear(wd.contiguous(), fmt)
+            del wg, wu, wd
+        layers.append(lw)
+    embed = _randn((cfg.vocab, h), _seed(seed, 9999, 1), device)
+    if cfg.tie_embeddings:
+        head_full = embed
+    else:
+        head_full = _randn((cfg.vocab, h), _seed(seed, 9999, 2), device)
+    v0, v1 = (0, cfg.vocab)
+    if shard_vocab and tp_size > 1:
+        v0, v1 = shard_range(cfg.vocab, tp_size, tp_rank)
+    lm_head = make_linear(head_full[v0:v1].contiguous() if (v0, v1) != (0, cfg.vocab) else head_full, "bf16")
+    return ModelWeights(cfg=cfg, embed=embed, layers=layers, final_norm=torch.ones(h, dtype=torch.bfloat16, device=device),
+                        lm_head=lm_head, fmt=fmt, tp_rank=tp_rank, tp_size=tp_size, ep_rank=ep_rank, ep_size=ep_size,
+                        vocab_start=v0)

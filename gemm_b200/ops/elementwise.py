@@ -174,3 +174,19 @@ def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_ro
 def softmax_scale_log2(d: int) -> float:
     """``q_scale`` that the attention kernel expects folded into Q: 1/sqrt(d) * log2(e)."""
     return (1.0 / math.sqrt(d)) * math.log2(math.e)
+
+
+def decode_advance(positions: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                   live: Optional[torch.Tensor] = None) -> None:
+    """In place: position += 1, kv_len = position + 1, slot from the block table (per decode sequence)."""
+    n = positions.numel()
+    if not positions.is_cuda:
+        sel = torch.ones(n, dtype=torch.bool) if live is None else live.bool()
+        positions[sel] += 1
+        kv_len[sel] = positions[sel] + 1
+        idx = torch.arange(n)[sel]
+        pages = block_table[idx, (positions[sel] // page_size).long().clamp_max(block_table.shape[1] - 1)]
+        slots[sel] = pages * page_size + positions[sel] % page_size
+        return
+    _native.check(_native.cuda().gb_decode_advance(_p(positions), _p(kv_len), _p(slots), _p(block_table), _p(live),
+                                                   _i(block_table.shape[1]), _i(page_size), _i(n), _s()), "gb_decode_advance")

@@ -86,16 +86,19 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.
 
 # --------------------------------------------------------------------------------------------- mxfp8
 def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
-              tn: Optional[int] = None) -> torch.Tensor:
+              tn: Optional[int] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Block-scaled fp8 linear: both operands MXFP8, bf16 (or f32) result [x.rows, w.rows]."""
     if not x.data.is_cuda:
-        return (mxfp8.dequantize(x) @ mxfp8.dequantize(w).t()).to(out_dtype)
+        y = mxfp8.dequantize(x) @ mxfp8.dequantize(w).t()
+        if bias is not None:
+            y = y + bias.float()
+        return y.to(out_dtype)
     m, n, k = x.rows, w.rows, w.k
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=x.data.device)
     flags = GEMM_MX | (GEMM_OUT_F32 if out.dtype == torch.float32 else 0)
     _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn or pick_tn(m, mx=True), x_rows=x.data.shape[0],
-            sfa=w.sf, sfb=x.sf)
+            sfa=w.sf, sfb=x.sf, bias=bias)
     return out
 
 

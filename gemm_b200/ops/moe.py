@@ -125,7 +125,7 @@ def plan(ids: torch.Tensor, n_exp: int, align: int, regions: int = 1, workspace=
     rc = _native.cuda().gb_moe_plan(_p(ids), _p(ws), _p(seg_start), _p(seg_count), _p(region_used), _p(pair_row), _p(row_token),
                                     _l(n_pairs), _i(n_exp), _i(k), _i(n_exp // regions), _i(region_rows), _i(align),
                                     _l(capacity), _s())
-    _native.check(rc, "gb_moe_plan")
+    _native.check(rc, "gb_moe_plan", n=4)
     return MoePlan(seg_start, seg_count, pair_row, row_token, region_used, capacity, region_rows)
 
 
