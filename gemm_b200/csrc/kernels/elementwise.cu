@@ -19,7 +19,10 @@ __device__ __forceinline__ int e8m0_amax(float amax) {
   if (bits & 0x7fffffu) e += 1;
   return amax == 0.0f ? 127 : max(1, min(e, 254));   // an all-zero block gets scale 1
 }
-__device__ __forceinline__ size_t sf_atom_offset(int row, int blk32, int k_atoms) {
+// Byte offset of the scale of (row, 32-element block) in the two atom layouts: one 512-byte atom per
+// 128 rows (rows interleaved 32 x 4) or per 32 rows (bytes 0..3 of each 16-byte lane row).
+__device__ __forceinline__ size_t sf_atom_offset(long row, int blk32, int k_atoms, int layout32 = 0) {
+  if (layout32) return ((size_t)(row >> 5) * k_atoms + (blk32 >> 2)) * 512 + (row & 31) * 16 + (blk32 & 3);
   return ((size_t)(row >> 7) * k_atoms + (blk32 >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (blk32 & 3);
 }
 
@@ -55,7 +58,7 @@ template <int VPT>   // 8-element vectors per thread (hidden <= 256 * 8 * VPT)
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ x_in,
                const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ out_q,
-               uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out) {
+               uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out, int sf32) {
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;
   float v[VPT][8];
@@ -115,7 +118,7 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
 #pragma unroll
         for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(y[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
         *reinterpret_cast<uint2*>(out_q + (size_t)row * hidden + vi * 8) = *reinterpret_cast<uint2*>(q);
-        if ((vi & 3) == 0) out_sf[sf_atom_offset(row, vi >> 2, hidden >> 7)] = (uint8_t)e;
+        if ((vi & 3) == 0) out_sf[sf_atom_offset(row, vi >> 2, hidden >> 7, sf32)] = (uint8_t)e;
       }
     }
   }
@@ -229,7 +232,7 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_
 // scale 1.  One warp per 256 elements: lane holds 8 elements, 4 lanes share a scale.
 __global__ void __launch_bounds__(256)
 mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src_rows, uint8_t* __restrict__ out_q,
-                uint8_t* __restrict__ out_sf, long out_rows, int k, int ld_in) {
+                uint8_t* __restrict__ out_sf, long out_rows, int k, int ld_in, int sf32) {
   const int vec_per_row = k >> 3;
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const bool act = idx < out_rows * vec_per_row;
@@ -253,7 +256,7 @@ mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ sr
 #pragma unroll
   for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(v[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
   *reinterpret_cast<uint2*>(out_q + r * k + vi * 8) = *reinterpret_cast<uint2*>(q);
-  if ((vi & 3) == 0) out_sf[sf_atom_offset((int)r, vi >> 2, k >> 7)] = (uint8_t)e;
+  if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, k >> 7, sf32)] = (uint8_t)e;
 }
 
 // ------------------------------------------------------------------------------------------ casts
@@ -299,13 +302,13 @@ GB_API int gb_embed(const int* ids, const void* table, void* out, int n_tok, int
 // residual (in/out, may be null) += delta (may be null); y = rmsnorm(residual or x_in) * weight.
 // out (bf16) and out_q/out_sf (MXFP8) are optional outputs.
 GB_API int gb_rmsnorm(void* residual, const void* delta, const void* x_in, const void* weight, void* out, void* out_q, void* out_sf,
-                      int rows, int hidden, float eps, int ld_in, int ld_out, cudaStream_t stream) {
+                      int rows, int hidden, float eps, int ld_in, int ld_out, int sf32, cudaStream_t stream) {
   if (hidden % 8 || hidden > 256 * 8 * 4) return fail("rmsnorm: hidden must be a multiple of 8 and <= 8192%s");
   if (out_q != nullptr && hidden % 128) return fail("rmsnorm: MXFP8 output needs hidden %% 128 == 0%s");
   if (rows <= 0) return 0;
   const int nvec = hidden / 8;
 #define GB_RMS(V) rmsnorm_kernel<V><<<rows, 256, 0, stream>>>((__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, \
-    (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out)
+    (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out, sf32)
   if (nvec <= 256) GB_RMS(1); else if (nvec <= 512) GB_RMS(2); else if (nvec <= 768) GB_RMS(3); else GB_RMS(4);
 #undef GB_RMS
   GB_CUDA_OK(cudaGetLastError());
@@ -337,11 +340,11 @@ GB_API int gb_silu_mul(const void* gate_up, void* out, long rows, int inter, int
   return 0;
 }
 
-GB_API int gb_mx_quant(const void* in, const int* src_rows, void* out_q, void* out_sf, long out_rows, int k, int ld_in, cudaStream_t stream) {
+GB_API int gb_mx_quant(const void* in, const int* src_rows, void* out_q, void* out_sf, long out_rows, int k, int ld_in, int sf32, cudaStream_t stream) {
   if (k % 128) return fail("mx_quant: k %% 128 != 0%s");
   const long n = out_rows * (k / 8);
   if (n <= 0) return 0;
-  mx_quant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in);
+  mx_quant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

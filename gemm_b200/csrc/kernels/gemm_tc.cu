@@ -38,7 +38,7 @@ struct GemmArgs {
   const int* seg_start; // [G] first X row of each group (multiple of min(TN,128); of 128 for MX), device
   const int* seg_count; // [G] valid rows of each group, device
   const uint8_t* sfa;   // MODE 1: weight scales, 512-byte atoms [w_row/128][k/128]
-  const uint8_t* sfb;   // MODE 1: activation scales, 512-byte atoms [x_row/128][k/128]
+  const uint8_t* sfb;   // MODE 1: activation scales, 512-byte atoms [x_row/128][k/128] (TN >= 128) or [x_row/32][k/128] (TN = 32)
   void* out;            // bf16 / f32 [rows, ldo]  or fp8 bytes [rows, ldo] for the quantising epilogue
   int ldo;
   int out_f32;
@@ -167,9 +167,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             const size_t kbs = (size_t)num_kb;
             bulk_load(sf, args.sfa + ((size_t)(t.w_row0 >> 7) * kbs + kb) * 512, 512, &full_bar[s]);
             if (DUAL) bulk_load(sf + 512, args.sfa + ((size_t)(t.w_row1 >> 7) * kbs + kb) * 512, 512, &full_bar[s]);
+            if (TN == 32) {
+              // narrow tiles use one atom per 32 rows (bytes 0..3 of each 16-byte lane row), so that the tile's
+              // scales always land in column 0 of their TMEM block whatever 32-row boundary the tile starts on
+              bulk_load(sf + NA * 512, args.sfb + ((size_t)(t.x_row0 >> 5) * kbs + kb) * 512, 512, &full_bar[s]);
+            } else {
 #pragma unroll
-            for (int i = 0; i < SFB_ATOMS; ++i)
-              bulk_load(sf + (NA + i) * 512, args.sfb + ((size_t)((t.x_row0 >> 7) + i) * kbs + kb) * 512, 512, &full_bar[s]);
+              for (int i = 0; i < SFB_ATOMS; ++i)
+                bulk_load(sf + (NA + i) * 512, args.sfb + ((size_t)((t.x_row0 >> 7) + i) * kbs + kb) * 512, 512, &full_bar[s]);
+            }
           }
           if (++s == S) { s = 0; ph ^= 1; }
         }
@@ -254,7 +260,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           const int x_row = t.x_row0 + xr;
           if (QUANT_OUT) {
             // 32 lanes of this warp = one 32-wide block along n of one token: shared E8M0 scale.
-            float amax = warp_max(n_ok ? fabsf(v) : 0.0f);
+            const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(n_ok ? fabsf(v) : 0.0f)));
             const int e = e8m0_from_amax(amax);
             const float inv = __uint_as_float((uint32_t)(254 - e) << 23);   // 2^(127-e)
             if (live) {
@@ -264,7 +270,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               }
               if (lane == 0) {
                 const size_t nkb = (size_t)((args.n_out + 127) >> 7);
-                args.out_sf[((size_t)(x_row >> 7) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + ((x_row >> 5) & 3) * 4 + q] = (uint8_t)e;
+                if (TN == 32) args.out_sf[((size_t)(x_row >> 5) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + q] = (uint8_t)e;
+                else args.out_sf[((size_t)(x_row >> 7) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + ((x_row >> 5) & 3) * 4 + q] = (uint8_t)e;
               }
             }
           } else if (live && n_ok) {
@@ -345,8 +352,9 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   // The scale factors of a token tile must start at column 0 of their 4-column TMEM block (an MMA whose
   // scale address pointed at column 1..3 raised "misaligned address"), so every MX token tile starts on a
   // 128-row boundary: narrow tiles only for a single token block, grouped segments 128-aligned with tn = 128.
-  if (mx && num_groups == 0 && tn < 128 && m_tok > tn) return fail("gemm: MXFP8 with tn < 128 needs m_tok <= tn%s");
-  if (mx && num_groups > 0 && tn != 128) return fail("gemm: grouped MXFP8 needs tn == 128 (segments aligned to 128 rows)%s");
+  // tn = 32 reads activation scales in the one-atom-per-32-rows layout, tn = 128 in the 128-row layout; tn = 64
+  // (128-row layout, second half at column 2) is kept to a single token block.
+  if (mx && tn == 64 && (num_groups > 0 || m_tok > tn)) return fail("gemm: MXFP8 with tn = 64 needs a single token block%s");
   if (!mx && (k % 8 != 0)) return fail("gemm: bf16 needs k %% 8 == 0%s");
   if ((mx || num_groups > 0 || dual) && (n_out % 128 != 0)) return fail("gemm: n_out must be a multiple of 128 for MX / grouped / dual%s");
   const int esz = mx ? 1 : 2;

@@ -104,7 +104,7 @@ def apply_linear(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTensor] = N
     """``x W^T (+ bias)`` in the weight's format; ``x_mx`` is an already-quantised copy of ``x`` if the caller has one."""
     if lw.fmt == "bf16":
         return gemm.linear(x, lw.w, bias=lw.bias, out_dtype=out_dtype)
-    xm = x_mx if x_mx is not None else ew.mx_quantize(x)
+    xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if x.shape[0] <= 32 else 128)
     y = gemm.linear_mx(xm, lw.mx, out_dtype=out_dtype, bias=lw.bias)
     return y
 
@@ -140,7 +140,7 @@ class Transformer:
             act = gemm.linear_swiglu(h, lw.w_gate_up.w)
             y = gemm.linear(act, lw.w_down.w)
         else:
-            xm = h_mx if h_mx is not None else ew.mx_quantize(h)
+            xm = h_mx if h_mx is not None else ew.mx_quantize(h, sf_layout=32 if h.shape[0] <= 32 else 128)
             act = gemm.linear_mx_swiglu_quant(xm, lw.w_gate_up.mx)
             y = gemm.linear_mx(act, lw.w_down.mx)
         return self.par.tp_all_reduce(y)
@@ -153,14 +153,16 @@ class Transformer:
         logits = gemm.linear(h, lw.router, out_dtype=torch.float32)
         ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
         if self.mx:
-            pl = moe.plan(ids, e, 128)
-            xq = ew.mx_quantize(h, pl.row_token)
+            # token tile (= scale-atom layout) by the expected rows per expert: 32 for decode-sized batches
+            tn = 32 if (t * k) // e <= 24 else 128
+            pl = moe.plan(ids, e, tn)
+            xq = ew.mx_quantize(h, pl.row_token, sf_layout=tn)
             dev = h.device
             hq = torch.zeros(pl.capacity, inter, dtype=torch.uint8, device=dev)
-            hsf = torch.full((pl.capacity // 128, inter // 128, 512), 127, dtype=torch.uint8, device=dev)
-            gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, 128, out=hq, dual=True,
+            hsf = ew.sf_alloc(pl.capacity, inter, dev, tn)
+            gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, out=hq, dual=True,
                                 sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf)
-            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, 128, sfa=lw.w2.mx.sf, sfb=hsf)
+            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf)
         else:
             tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
             pl = moe.plan(ids, e, tn)
@@ -180,16 +182,17 @@ class Transformer:
         delta = None
         for li in range(first_layer, last_layer):
             lw = w.layers[li]
+            lay = 32 if x.shape[0] <= 32 else 128
             if self.mx:
                 h, h_mx = ew.rmsnorm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps,
-                                     residual=x if delta is not None else None, quantize=True, want_bf16=False)
+                                     residual=x if delta is not None else None, quantize=True, want_bf16=False, sf_layout=lay)
             else:
                 h, h_mx = ew.rmsnorm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps,
                                      residual=x if delta is not None else None), None
             delta = self.attention_block(li, lw, h, h_mx, fb)
             need_bf16 = (not self.mx) or cfg.is_moe
             if self.mx:
-                h, h_mx = ew.rmsnorm(delta, lw.ffn_norm, cfg.rms_eps, residual=x, quantize=True, want_bf16=need_bf16)
+                h, h_mx = ew.rmsnorm(delta, lw.ffn_norm, cfg.rms_eps, residual=x, quantize=True, want_bf16=need_bf16, sf_layout=lay)
             else:
                 h, h_mx = ew.rmsnorm(delta, lw.ffn_norm, cfg.rms_eps, residual=x), None
             if lw.w13 is not None:

@@ -45,8 +45,13 @@ def rmsnorm_ref(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(torch.bfloat16)
 
 
+def sf_alloc(rows_padded: int, k: int, device, layout: int = 128) -> torch.Tensor:
+    """Scale-atom buffer for ``rows_padded`` rows (a multiple of 128) initialised to scale 1."""
+    return torch.full((rows_padded // layout, k // 128, 512), 127, dtype=torch.uint8, device=device)
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
-            quantize: bool = False, want_bf16: bool = True):
+            quantize: bool = False, want_bf16: bool = True, sf_layout: int = 128):
     """RMSNorm of ``x`` (or of ``residual += x`` when ``residual`` is given; the sum is written back).
 
     Returns the bf16 result, or ``(bf16 | None, MxTensor)`` when ``quantize`` asks for an MXFP8 copy that
@@ -61,23 +66,23 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
             src = x
         y = rmsnorm_ref(src, w, eps)
         if quantize:
-            return (y if want_bf16 else None), mxfp8.quantize(y.float())
+            return (y if want_bf16 else None), mxfp8.quantize(y.float(), sf_layout=sf_layout)
         return y
     out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
     q = sf = None
     if quantize:
         rp = (rows + 127) // 128 * 128
         q = torch.zeros(rp, hidden, dtype=torch.uint8, device=x.device)
-        sf = torch.full((rp // 128, hidden // 128, 512), 127, dtype=torch.uint8, device=x.device)
+        sf = sf_alloc(rp, hidden, x.device, sf_layout)
     if residual is not None:
         rc = _native.cuda().gb_rmsnorm(_p(residual), _p(x), _c(0), _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden),
-                                       _f(eps), _i(residual.stride(0)), _i(hidden), _s())
+                                       _f(eps), _i(residual.stride(0)), _i(hidden), _i(1 if sf_layout == 32 else 0), _s())
     else:
         rc = _native.cuda().gb_rmsnorm(_c(0), _c(0), _p(x), _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden), _f(eps),
-                                       _i(x.stride(0)), _i(hidden), _s())
+                                       _i(x.stride(0)), _i(hidden), _i(1 if sf_layout == 32 else 0), _s())
     _native.check(rc, "gb_rmsnorm")
     if quantize:
-        return out, MxTensor(q, sf, rows, hidden)
+        return out, MxTensor(q, sf, rows, hidden, sf_layout)
     return out
 
 
@@ -149,7 +154,8 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_rows: Optional[int] = None) -> MxTensor:
+def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_rows: Optional[int] = None,
+                sf_layout: int = 128) -> MxTensor:
     """bf16 ``[rows, K]`` -> MXFP8.  With ``src_rows`` (int32) output row r is input row ``src_rows[r]``
     (negative = zero row): the gather of MoE dispatch fused with the quantiser."""
     k = x.shape[1]
@@ -161,14 +167,14 @@ def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_ro
             g[ok] = x.float()[src_rows[:n][ok].long()]
         else:
             g = x.float()
-        t = mxfp8.quantize(g)
+        t = mxfp8.quantize(g, sf_layout=sf_layout)
         return t
     rp = (n + 127) // 128 * 128
     q = torch.zeros(rp, k, dtype=torch.uint8, device=x.device)
-    sf = torch.full((rp // 128, k // 128, 512), 127, dtype=torch.uint8, device=x.device)
-    _native.check(_native.cuda().gb_mx_quant(_p(x), _p(src_rows), _p(q), _p(sf), _l(n), _i(k), _i(x.stride(0)), _s()),
-                  "gb_mx_quant")
-    return MxTensor(q, sf, n, k)
+    sf = sf_alloc(rp, k, x.device, sf_layout)
+    _native.check(_native.cuda().gb_mx_quant(_p(x), _p(src_rows), _p(q), _p(sf), _l(n), _i(k), _i(x.stride(0)),
+                                             _i(1 if sf_layout == 32 else 0), _s()), "gb_mx_quant")
+    return MxTensor(q, sf, n, k, sf_layout)
 
 
 def softmax_scale_log2(d: int) -> float:

@@ -30,7 +30,10 @@ def _stream():
 
 
 def pick_tn(m_tok: int, mx: bool = False, dual: bool = False) -> int:
-    """Token-tile width: the smallest supported tile that covers the batch, capped by TMEM capacity."""
+    """Token-tile width: the smallest supported tile that covers the batch, capped by TMEM capacity.
+    MXFP8 operands come in two scale layouts, so their tile is 32 (sf_layout 32) or 128 (sf_layout 128)."""
+    if mx:
+        return 32 if m_tok <= 32 else 128
     lo = 32 if mx else 16
     hi = 128 if (mx or dual) else 256
     tn = lo
@@ -97,7 +100,8 @@ def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=x.data.device)
     flags = GEMM_MX | (GEMM_OUT_F32 if out.dtype == torch.float32 else 0)
-    _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn or pick_tn(m, mx=True), x_rows=x.data.shape[0],
+    assert w.sf_layout == 128
+    _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn or x.sf_layout, x_rows=x.data.shape[0],
             sfa=w.sf, sfb=x.sf, bias=bias)
     return out
 
@@ -108,14 +112,13 @@ def linear_mx_swiglu_quant(x: MxTensor, w_gate_up: MxTensor, tn: Optional[int] =
     if not x.data.is_cuda:
         y = mxfp8.dequantize(x) @ mxfp8.dequantize(w_gate_up).t()
         h = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
-        return mxfp8.quantize(h)
+        return mxfp8.quantize(h, sf_layout=x.sf_layout)
     rows_p = x.data.shape[0]
     out = torch.zeros(rows_p, inter, dtype=torch.uint8, device=x.data.device)
-    out_sf = torch.full((rows_p // 128, inter // 128, 512), 127, dtype=torch.uint8, device=x.data.device)
+    out_sf = torch.full((rows_p // x.sf_layout, inter // 128, 512), 127, dtype=torch.uint8, device=x.data.device)
     _launch(w_gate_up.data, x.data, out, inter, x.k, x.rows, x.k, x.k, inter, GEMM_MX | GEMM_DUAL | GEMM_QUANT_OUT,
-            tn or pick_tn(x.rows, mx=True, dual=True), up_row_offset=inter, x_rows=rows_p, sfa=w_gate_up.sf, sfb=x.sf,
-            out_sf=out_sf)
-    return MxTensor(out, out_sf, x.rows, inter)
+            tn or x.sf_layout, up_row_offset=inter, x_rows=rows_p, sfa=w_gate_up.sf, sfb=x.sf, out_sf=out_sf)
+    return MxTensor(out, out_sf, x.rows, inter, x.sf_layout)
 
 
 # --------------------------------------------------------------------------------------------- grouped
@@ -128,13 +131,13 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
     ``w`` is ``[G, R, K]`` (R = 2I stacked gate/up rows when ``dual``); group g multiplies the rows
     ``seg_start[g] : seg_start[g] + seg_count[g]`` of ``x``.  ``seg_start`` entries must be multiples of
     ``min(tn, 128)``.  With ``sfa``/``sfb`` the operands are e4m3 bytes with scale atoms (MXFP8); that mode
-    needs ``tn == 128`` and 128-aligned segments.
+    needs ``tn`` 32 or 128, segments aligned to ``tn`` and activation scales in the matching atom layout.
     """
     g, r, k = w.shape
     n_out = r // 2 if dual else r
     mx = sfa is not None
     if not x.is_cuda:
-        return _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out)
+        return _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out, out_sf)
     flags = (GEMM_MX if mx else 0) | (GEMM_DUAL if dual else 0) | (GEMM_QUANT_OUT if quant_out else 0)
     if out is None:
         if quant_out:
@@ -149,12 +152,13 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
     return out
 
 
-def _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out):
+def _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out, out_sf=None):
     g, r, k = w.shape
     n_out = r // 2 if dual else r
     if sfa is not None:
+        lay = 32 if sfb.shape[0] * 32 == x.shape[0] else 128
         wf = mxfp8.dequantize_rowmajor(w.reshape(g * r, k), mxfp8.unpack_sf_atoms(sfa, g * r, k // 32)).reshape(g, r, k)
-        xf = mxfp8.dequantize_rowmajor(x, mxfp8.unpack_sf_atoms(sfb, x.shape[0], k // 32))
+        xf = mxfp8.dequantize_rowmajor(x, mxfp8.unpack_sf_atoms(sfb, x.shape[0], k // 32, lay))
     else:
         wf, xf = w.float(), x.float()
     res = torch.zeros(x.shape[0], n_out, dtype=torch.float32)
@@ -167,7 +171,12 @@ def _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa
             y = torch.nn.functional.silu(y[:, :n_out]) * y[:, n_out:]
         res[s:s + c] = y
     if quant_out:
-        return res
+        q = mxfp8.quantize(res, sf_layout=(32 if (out_sf is not None and out_sf.shape[0] * 32 == res.shape[0]) else 128))
+        if out is not None:
+            out.copy_(q.data[: out.shape[0]])
+            out_sf.copy_(q.sf)
+            return out
+        return q.data
     if row_scale is not None:
         res = res * row_scale.float().unsqueeze(-1)
     if row_map is not None:

@@ -28,12 +28,13 @@ _INV448 = torch.tensor(1.0 / 448.0, dtype=torch.float32)
 class MxTensor:
     """Row-major e4m3 bytes plus scales in atom layout.  ``rows`` counts valid rows (storage may be padded)."""
     data: torch.Tensor      # uint8 [rows_padded, k]
-    sf: torch.Tensor        # uint8 [ceil(rows_padded/128), k/128, 512]
+    sf: torch.Tensor        # uint8 [ceil(rows_padded/128), k/128, 512]  (or [rows_padded/32, k/128, 512] when sf_layout == 32)
     rows: int
     k: int
+    sf_layout: int = 128    # rows per scale atom: 128 (default) or 32 (token tiles of 32 rows)
 
     def to(self, device):
-        return MxTensor(self.data.to(device), self.sf.to(device), self.rows, self.k)
+        return MxTensor(self.data.to(device), self.sf.to(device), self.rows, self.k, self.sf_layout)
 
 
 def e8m0_from_amax(amax: torch.Tensor) -> torch.Tensor:
@@ -66,25 +67,35 @@ def dequantize_rowmajor(q: torch.Tensor, e: torch.Tensor) -> torch.Tensor:
     return (v * scale.unsqueeze(-1)).reshape(rows, k)
 
 
-def pack_sf_atoms(e: torch.Tensor) -> torch.Tensor:
-    """uint8 [rows, K/32] -> uint8 [ceil(rows/128), ceil(K/128), 512] (padding scales = 127 i.e. 1.0)."""
+def pack_sf_atoms(e: torch.Tensor, layout: int = 128) -> torch.Tensor:
+    """uint8 [rows, K/32] -> uint8 [ceil(rows/128), ceil(K/128), 512] (padding scales = 127 i.e. 1.0).
+
+    ``layout=32`` gives one atom per 32 rows, ``[ceil(rows/32), ceil(K/128), 512]``: the four scales of
+    (row, k-atom) sit in bytes 0..3 of the row's 16-byte lane slot, the other 12 bytes are unused."""
     rows, nb = e.shape
     rp, kp = (rows + 127) // 128 * 128, (nb + 3) // 4 * 4
     pad = torch.full((rp, kp), 127, dtype=torch.uint8, device=e.device)
     pad[:rows, :nb] = e
+    if layout == 32:
+        t = torch.full((rp // 32, kp // 4, 32, 16), 127, dtype=torch.uint8, device=e.device)
+        t[..., :4] = pad.reshape(rp // 32, 32, kp // 4, 4).permute(0, 2, 1, 3)
+        return t.reshape(rp // 32, kp // 4, 512)
     # [R/128, 4(row group), 32(lane), K/128, 4(sub-block)] -> [R/128, K/128, 32, 4, 4]
     t = pad.reshape(rp // 128, 4, 32, kp // 4, 4).permute(0, 3, 2, 1, 4).contiguous()
     return t.reshape(rp // 128, kp // 4, 512)
 
 
-def unpack_sf_atoms(sf: torch.Tensor, rows: int, nb: int) -> torch.Tensor:
+def unpack_sf_atoms(sf: torch.Tensor, rows: int, nb: int, layout: int = 128) -> torch.Tensor:
     """Inverse of pack_sf_atoms."""
     rb, kb, _ = sf.shape
+    if layout == 32:
+        t = sf.reshape(rb, kb, 32, 16)[..., :4].permute(0, 2, 1, 3).contiguous().reshape(rb * 32, kb * 4)
+        return t[:rows, :nb].contiguous()
     t = sf.reshape(rb, kb, 32, 4, 4).permute(0, 3, 2, 1, 4).contiguous().reshape(rb * 128, kb * 4)
     return t[:rows, :nb].contiguous()
 
 
-def quantize(x: torch.Tensor, pad_rows_to: int = 128) -> MxTensor:
+def quantize(x: torch.Tensor, pad_rows_to: int = 128, sf_layout: int = 128) -> MxTensor:
     """Quantise [rows, K] (K % 128 == 0) into an MxTensor whose storage rows are padded with zeros."""
     rows, k = x.shape
     assert k % 128 == 0, "MXFP8 GEMM operands need K % 128 == 0"
@@ -93,9 +104,9 @@ def quantize(x: torch.Tensor, pad_rows_to: int = 128) -> MxTensor:
     if rp != rows:
         q = torch.cat([q, torch.zeros(rp - rows, k, dtype=torch.uint8, device=q.device)])
         e = torch.cat([e, torch.full((rp - rows, k // 32), 127, dtype=torch.uint8, device=e.device)])
-    return MxTensor(q.contiguous(), pack_sf_atoms(e), rows, k)
+    return MxTensor(q.contiguous(), pack_sf_atoms(e, sf_layout), rows, k, sf_layout)
 
 
 def dequantize(t: MxTensor) -> torch.Tensor:
-    e = unpack_sf_atoms(t.sf, t.data.shape[0], t.k // 32)
+    e = unpack_sf_atoms(t.sf, t.data.shape[0], t.k // 32, t.sf_layout)
     return dequantize_rowmajor(t.data, e)[: t.rows]

@@ -47,24 +47,25 @@ def test_linear_swiglu(m, inter, k):
     assert _rel(y, ref) < 1e-2
 
 
-@pytest.mark.parametrize("m,n,k", [(8, 128, 128), (32, 256, 512), (70, 768, 2048), (256, 2048, 768), (1000, 512, 1024)])
-def test_linear_mxfp8(m, n, k):
+@pytest.mark.parametrize("m,n,k,lay", [(8, 128, 128, 128), (32, 256, 512, 128), (70, 768, 2048, 128), (256, 2048, 768, 128),
+                                       (1000, 512, 1024, 128), (8, 256, 512, 32), (32, 5120, 2048, 32)])
+def test_linear_mxfp8(m, n, k, lay):
     torch.manual_seed(3)
     x = torch.randn(m, k, device="cuda") * torch.rand(m, 1, device="cuda") * 4
     w = torch.randn(n, k, device="cuda") * 0.05
-    xq, wq = mxfp8.quantize(x), mxfp8.quantize(w)
+    xq, wq = mxfp8.quantize(x, sf_layout=lay), mxfp8.quantize(w)
     y = gemm.linear_mx(xq, wq, out_dtype=torch.float32)
     ref = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t()
     _native.assert_status_ok()
     assert _rel(y, ref) < 2e-3
 
 
-@pytest.mark.parametrize("m,inter,k", [(8, 128, 256), (100, 768, 2048)])
-def test_mx_swiglu_quant_epilogue(m, inter, k):
+@pytest.mark.parametrize("m,inter,k,lay", [(8, 128, 256, 128), (100, 768, 2048, 128), (20, 768, 2048, 32)])
+def test_mx_swiglu_quant_epilogue(m, inter, k, lay):
     torch.manual_seed(4)
     x = torch.randn(m, k, device="cuda")
     w = torch.randn(2 * inter, k, device="cuda") * 0.05
-    xq, wq = mxfp8.quantize(x), mxfp8.quantize(w)
+    xq, wq = mxfp8.quantize(x, sf_layout=lay), mxfp8.quantize(w)
     hq = gemm.linear_mx_swiglu_quant(xq, wq)
     r = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t()
     ref = torch.nn.functional.silu(r[:, :inter]) * r[:, inter:]
@@ -74,15 +75,14 @@ def test_mx_swiglu_quant_epilogue(m, inter, k):
     # scales must be the ones the reference quantiser picks for (nearly) the same values
     ref_q = mxfp8.quantize(ref)
     e_ref = mxfp8.unpack_sf_atoms(ref_q.sf, m, inter // 32).int()
-    e_got = mxfp8.unpack_sf_atoms(hq.sf, m, inter // 32).int()
+    e_got = mxfp8.unpack_sf_atoms(hq.sf, m, inter // 32, lay).int()
     assert (e_ref - e_got).abs().max().item() <= 1
 
 
-@pytest.mark.parametrize("mx", [False, True])
-def test_grouped(mx):
+@pytest.mark.parametrize("mx,tn", [(False, 32), (True, 128), (True, 32)])
+def test_grouped(mx, tn):
     torch.manual_seed(5)
     g, inter, k = 6, 256, 512
-    tn = 128 if mx else 32
     counts = torch.tensor([5, 0, 140, 32, 1, 17], dtype=torch.int32)
     starts = torch.zeros(g, dtype=torch.int32)
     pos = 0
@@ -94,7 +94,7 @@ def test_grouped(mx):
     w = torch.randn(g, 2 * inter, k, device="cuda") * 0.05
     sd, cd = starts.cuda(), counts.cuda()
     if mx:
-        xq = mxfp8.quantize(x)
+        xq = mxfp8.quantize(x, sf_layout=tn)
         wq = mxfp8.quantize(w.reshape(g * 2 * inter, k))
         y = gemm.grouped_linear(xq.data, wq.data.reshape(g, 2 * inter, k), sd, cd, tn, dual=True, sfa=wq.sf, sfb=xq.sf)
         xf, wf = mxfp8.dequantize(xq), mxfp8.dequantize(wq).reshape(g, 2 * inter, k)
