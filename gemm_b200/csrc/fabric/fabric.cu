@@ -240,31 +240,28 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(PeerTable pt, EpDispatchArgs a) {
   const uint32_t epoch = *a.epoch_ctr;          // the plan kernel advanced the epoch for this layer
   const int vec_per_row = a.hidden >> 3;
-  const long total = (long)pt.world * a.region_rows * vec_per_row;
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx - threadIdx.x < total; idx += (long)gridDim.x * blockDim.x) {
-    const bool act = idx < total;
-    const long r = act ? idx / vec_per_row : 0;
-    const int vi = act ? (int)(idx % vec_per_row) : 0;
-    const int tok = act ? a.row_token[r] : -1;
+  const long total_rows = (long)pt.world * a.region_rows;
+  const int lane = threadIdx.x & 31;
+  const long warp0 = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long n_warps = ((long)gridDim.x * blockDim.x) >> 5;
+  // one warp per plan row; padding rows (token < 0) cost one load
+  for (long r = warp0; r < total_rows; r += n_warps) {
+    const int tok = a.row_token[r];
+    if (tok < 0) continue;
     const int dst = (int)(r / a.region_rows);
     const long drow = (long)pt.rank * a.region_rows + (r % a.region_rows);
-    float v[8];
+    for (int vi = lane; vi < vec_per_row; vi += 32) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(a.h + (size_t)tok * a.ld_h + vi * 8);
+      if (a.mx) {
+        float v[8];
+        const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = 0.f;
-    uint4 raw = make_uint4(0, 0, 0, 0);
-    if (tok >= 0) {
-      raw = *reinterpret_cast<const uint4*>(a.h + (size_t)tok * a.ld_h + vi * 8);
-      const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(hh[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+        float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(hh[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
-    }
-    if (a.mx) {
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      if (tok >= 0) {
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
         const int e = ep_e8m0(amax);
         const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
         uint8_t q[8];
@@ -278,10 +275,10 @@ ep_dispatch_kernel(PeerTable pt, EpDispatchArgs a) {
           if (a.sf32) sfb[((size_t)(drow >> 5) * katoms + (blk >> 2)) * 512 + (drow & 31) * 16 + (blk & 3)] = (uint8_t)e;
           else sfb[((size_t)(drow >> 7) * katoms + (blk >> 2)) * 512 + (drow & 31) * 16 + ((drow >> 5) & 3) * 4 + (blk & 3)] = (uint8_t)e;
         }
+      } else {
+        __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>((char*)pt.base[dst] + a.x_off);
+        *reinterpret_cast<uint4*>(xb + (size_t)drow * a.hidden + vi * 8) = raw;
       }
-    } else if (tok >= 0) {
-      __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>((char*)pt.base[dst] + a.x_off);
-      *reinterpret_cast<uint4*>(xb + (size_t)drow * a.hidden + vi * 8) = raw;
     }
   }
   // segment table: entry (dst, e_local) lands at index rank * experts_per_rank + e_local on dst
@@ -403,8 +400,9 @@ GB_API int gb_ep_dispatch(void* const* bases, int world, int rank, const void* h
   a.h = (const __nv_bfloat16*)h; a.ld_h = ld_h; a.hidden = hidden; a.row_token = row_token; a.seg_start = seg_start; a.seg_count = seg_count;
   a.region_rows = region_rows; a.experts_per_rank = experts_per_rank; a.x_off = x_off; a.sf_off = sf_off; a.meta_off = meta_off;
   a.flags_off = flags_off; a.mx = mx; a.sf32 = sf32; a.epoch_ctr = (uint32_t*)epoch_ctr; a.done_ctr = (unsigned*)done_ctr; a.st = (KernelStatus*)status;
-  const long total = (long)world * region_rows * (hidden / 8);
-  int grid = (int)std::min<long>((total + 255) / 256, (long)sm_count() * 8);
+  if ((hidden / 8) % 32) return fail("ep_dispatch: hidden must be a multiple of 256%s");
+  const long total_rows = (long)world * region_rows;
+  int grid = (int)std::min<long>((total_rows + 7) / 8, (long)sm_count() * 8);
   if (grid < 1) grid = 1;
   ep_dispatch_kernel<<<grid, 256, 0, stream>>>(make_table(bases, world, rank), a);
   GB_CUDA_OK(cudaGetLastError());

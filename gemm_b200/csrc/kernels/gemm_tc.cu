@@ -22,6 +22,7 @@
 // expert GEMMs of mmq_*_grouped (cuda_llm_runner.c:5295-7329) and m3_gemm_mxfp8 (common/m3_impl.h:791-825).
 #include "sm100.cuh"
 #include "host_common.h"
+#include "../fabric/fabric.cuh"
 
 namespace gb {
 
@@ -48,6 +49,17 @@ struct GemmArgs {
   const float* row_scale; // optional: multiply row r of the result
   int stages;
   KernelStatus* status;
+  // ---- expert-parallel extras (all optional) ----
+  int w_group_mod;                 // > 0: the weights of group g are those of expert g % w_group_mod
+  const uint32_t* wait_flags;      // wait until wait_flags[i] >= *epoch_ptr for i < wait_n before touching X / segments
+  int wait_n;
+  const uint32_t* epoch_ptr;
+  void* peer_out[kMaxRanks];       // epilogue target per source rank: rows of region s go to peer_out[s]
+  int peer_region_rows;            // > 0 enables the peer epilogue: X row r belongs to source r / region_rows and lands
+  int peer_rank;                   //   at row peer_rank * region_rows + r % region_rows of that peer's buffer
+  uint32_t* signal_flags[kMaxRanks];  // after the last tile of the grid: *signal_flags[p] = *epoch_ptr (release, system scope)
+  int signal_n;
+  unsigned* done_ctr;
 };
 
 struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; };
@@ -74,7 +86,7 @@ struct TileCursor {
         const int lt = t - base;
         const int nb = lt % n_blocks, tb = lt / n_blocks;
         o.n0 = nb * 128;
-        o.w_row0 = g * a.w_rows_per_group + o.n0;
+        o.w_row0 = (a.w_group_mod > 0 ? g % a.w_group_mod : g) * a.w_rows_per_group + o.n0;
         o.w_row1 = o.w_row0 + a.up_row_offset;
         o.x_row0 = s_start[g] + tb * TN;
         o.valid = min(TN, s_count[g] - tb * TN);
@@ -139,15 +151,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     fence_barrier_init();
     tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX);
   }
-  for (int i = threadIdx.x; i < args.num_groups; i += blockDim.x) { s_start[i] = args.seg_start[i]; s_count[i] = args.seg_count[i]; }
+  if (args.wait_n > 0) {
+    // Rows and segment tables are written by peer GPUs: wait for every source's flag of this epoch, then make the
+    // observed data visible to the TMA (async proxy) reads that follow.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t want = *args.epoch_ptr;
+      for (int i = 0; i < args.wait_n; ++i)
+        if (!wait_flag_ge(args.wait_flags + i, want, args.status, 110, i)) { *abort_flag = 1; break; }
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+    }
+    __syncthreads();
+  }
+  if (!*abort_flag)
+    for (int i = threadIdx.x; i < args.num_groups; i += blockDim.x) { s_start[i] = args.seg_start[i]; s_count[i] = args.seg_count[i]; }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_sf = tmem_base + NACC * ACC_COLS;   // SFA0 [, SFA1], SFB columns
+  const bool run = (*abort_flag == 0);
 
-  if (warp == 0) {
+  if (!run) {
+    // a failed wait: nothing was issued, fall through to the teardown
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one lane)
     if (lane == 0) {
       TileCursor<TN> cur; Tile t;
@@ -276,11 +304,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
           } else if (live && n_ok) {
             int orow = x_row;
+            void* obase = args.out;
+            if (args.peer_region_rows > 0) {
+              const int src = x_row / args.peer_region_rows;
+              obase = args.peer_out[src];
+              orow = args.peer_rank * args.peer_region_rows + (x_row - src * args.peer_region_rows);
+            }
             if (args.row_map != nullptr) orow = args.row_map[x_row];
             if (orow >= 0) {
               if (args.row_scale != nullptr) v *= args.row_scale[x_row];
-              if (args.out_f32) ((float*)args.out)[(size_t)orow * args.ldo + n] = v;
-              else ((__nv_bfloat16*)args.out)[(size_t)orow * args.ldo + n] = __float2bfloat16(v);
+              if (args.out_f32) ((float*)obase)[(size_t)orow * args.ldo + n] = v;
+              else ((__nv_bfloat16*)obase)[(size_t)orow * args.ldo + n] = __float2bfloat16(v);
             }
           }
         }
@@ -301,6 +335,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  if (args.signal_n > 0 && threadIdx.x == 0) {
+    // every store of this CTA happened before the barrier above; publish once the whole grid is done
+    __threadfence_system();
+    if (atomicAdd(args.done_ctr, 1u) == gridDim.x - 1) {
+      *args.done_ctr = 0;
+      const uint32_t e = *args.epoch_ptr;
+      for (int p = 0; p < args.signal_n; ++p) st_release_sys(args.signal_flags[p], e);
+    }
+  }
 }
 
 template <int TN, int MODE, bool DUAL, bool QUANT_OUT>
@@ -331,6 +374,21 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmArgs 
 
 using namespace gb;
 
+// Optional expert-parallel arguments of gb_gemm (host struct, mirrored by ctypes in parallel/fabric.py).
+struct GemmExtras {
+  int w_group_mod;
+  int wait_n;
+  const uint32_t* wait_flags;
+  const uint32_t* epoch_ptr;
+  void* peer_out[kMaxRanks];
+  int peer_region_rows;
+  int peer_rank;
+  uint32_t* signal_flags[kMaxRanks];
+  int signal_n;
+  int pad;
+  unsigned* done_ctr;
+};
+
 // Flags of gb_gemm.
 enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8 };
 
@@ -344,7 +402,7 @@ enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8 };
 GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, int m_tok, int ldw, int ldx, int ldo,
                    int flags, int tn, int num_groups, int w_rows_per_group, int up_row_offset, const int* seg_start,
                    const int* seg_count, int x_rows, const void* sfa, const void* sfb, void* out_sf, const float* bias,
-                   const int* row_map, const float* row_scale, void* status, cudaStream_t stream) {
+                   const int* row_map, const float* row_scale, const GemmExtras* ex, void* status, cudaStream_t stream) {
   const bool mx = flags & GEMM_MX, dual = flags & GEMM_DUAL, qo = flags & GEMM_QUANT_OUT;
   if (num_groups > kMaxGroups) return fail("gemm: too many groups%s");
   if (mx && (k % 128 != 0)) return fail("gemm: MXFP8 needs k %% 128 == 0%s");
@@ -358,7 +416,8 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   if (!mx && (k % 8 != 0)) return fail("gemm: bf16 needs k %% 8 == 0%s");
   if ((mx || num_groups > 0 || dual) && (n_out % 128 != 0)) return fail("gemm: n_out must be a multiple of 128 for MX / grouped / dual%s");
   const int esz = mx ? 1 : 2;
-  const long w_rows = (num_groups > 0) ? (long)num_groups * w_rows_per_group : (dual ? (long)up_row_offset + n_out : (long)n_out);
+  const int w_groups = (ex != nullptr && ex->w_group_mod > 0) ? ex->w_group_mod : num_groups;
+  const long w_rows = (num_groups > 0) ? (long)w_groups * w_rows_per_group : (dual ? (long)up_row_offset + n_out : (long)n_out);
   CUtensorMap tmW, tmX;
   const TmapDtype dt = mx ? TM_U8 : TM_BF16;
   const uint32_t box_k = mx ? 128 : 64;
@@ -370,6 +429,14 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   a.up_row_offset = up_row_offset; a.seg_start = seg_start; a.seg_count = seg_count;
   a.sfa = (const uint8_t*)sfa; a.sfb = (const uint8_t*)sfb; a.out = out; a.ldo = ldo; a.out_f32 = (flags & GEMM_OUT_F32) ? 1 : 0;
   a.out_sf = (uint8_t*)out_sf; a.bias = bias; a.row_map = row_map; a.row_scale = row_scale; a.status = (KernelStatus*)status;
+  if (ex != nullptr) {
+    a.w_group_mod = ex->w_group_mod; a.wait_flags = ex->wait_flags; a.wait_n = ex->wait_n; a.epoch_ptr = ex->epoch_ptr;
+    for (int i = 0; i < kMaxRanks; ++i) { a.peer_out[i] = ex->peer_out[i]; a.signal_flags[i] = ex->signal_flags[i]; }
+    a.peer_region_rows = ex->peer_region_rows; a.peer_rank = ex->peer_rank; a.signal_n = ex->signal_n; a.done_ctr = ex->done_ctr;
+    if (a.w_group_mod > 0) {
+      // the tensor map of W must cover the experts only
+    }
+  }
   int max_tiles = 0;
   if (num_groups == 0) max_tiles = ((n_out + 127) / 128) * ((m_tok + tn - 1) / tn);
   if (num_groups == 0 && m_tok <= 0) return 0;

@@ -12,6 +12,7 @@
 // device->host sync per layer), gather_rows_f32 (:7931) and scatter_add_weighted_f32 (:7943).
 #include "sm100.cuh"
 #include "host_common.h"
+#include "../fabric/fabric.cuh"
 #include <float.h>
 
 namespace gb {
@@ -125,8 +126,9 @@ moe_scan_kernel(int* __restrict__ block_hist, int* __restrict__ seg_count, int n
 // destination rank); region r starts at row r * region_rows, segments inside are aligned to `align`.
 __global__ void __launch_bounds__(512)
 moe_seg_kernel(const int* __restrict__ seg_count, int* __restrict__ seg_start, int* __restrict__ region_rows_used,
-               int n_exp, int experts_per_region, int region_rows, int align) {
+               int n_exp, int experts_per_region, int region_rows, int align, unsigned* epoch_ctr) {
   const int r = threadIdx.x;
+  if (r == 0 && epoch_ctr != nullptr) *epoch_ctr = *epoch_ctr + 1;     // one tick per MoE layer call (expert-parallel epoch)
   if (r < n_exp / experts_per_region) {
     int pos = 0;
     for (int i = 0; i < experts_per_region; ++i) {
@@ -159,10 +161,22 @@ moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ block_hi
 // out[t, :] = sum_j w[t, j] * y[pair_row[t*k + j], :]   (bf16 in / out, fp32 accumulate, fixed order)
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ weights,
-                   __nv_bfloat16* __restrict__ out, int hidden, int k, int ld_y) {
+                   __nv_bfloat16* __restrict__ out, int hidden, int k, int ld_y, const uint32_t* wait_flags, int wait_n,
+                   const uint32_t* epoch_ptr, KernelStatus* st) {
   const int t = blockIdx.x;
   __shared__ int rows[kMaxTopK];
   __shared__ float ws[kMaxTopK];
+  __shared__ int failed;
+  if (wait_n > 0) {
+    // expert outputs are stored into `y` by the GPUs that own the experts: wait for each one's completion flag
+    if (threadIdx.x == 0) {
+      failed = 0;
+      const uint32_t want = *epoch_ptr;
+      for (int i = 0; i < wait_n; ++i) if (!wait_flag_ge(wait_flags + i, want, st, 800, i)) { failed = 1; break; }
+    }
+    __syncthreads();
+    if (failed) return;
+  }
   if (threadIdx.x < k) { rows[threadIdx.x] = pair_row[(size_t)t * k + threadIdx.x]; ws[threadIdx.x] = weights ? weights[(size_t)t * k + threadIdx.x] : 1.0f; }
   __syncthreads();
   for (int v = threadIdx.x; v < hidden / 8; v += blockDim.x) {
@@ -210,24 +224,25 @@ GB_API int gb_moe_route(const float* logits, const float* bias, int* ids, float*
 // workspace: int32 [ceil(n_pairs / 256) * n_exp].  row_token must hold `capacity` ints (set to -1 here).
 GB_API int gb_moe_plan(const int* ids, int* workspace, int* seg_start, int* seg_count, int* region_rows_used, int* pair_row,
                        int* row_token, long n_pairs, int n_exp, int k, int experts_per_region, int region_rows, int align,
-                       long capacity, cudaStream_t stream) {
+                       long capacity, void* epoch_ctr, cudaStream_t stream) {
   if (n_exp > 512) return fail("moe_plan: n_exp > 512%s");
   if (n_exp % experts_per_region) return fail("moe_plan: n_exp %% experts_per_region != 0%s");
   const int nb = (int)((n_pairs + kPlanBlock - 1) / kPlanBlock);
   GB_CUDA_OK(cudaMemsetAsync(row_token, 0xff, (size_t)capacity * sizeof(int), stream));
   if (nb > 0) moe_hist_kernel<<<nb, kPlanBlock, n_exp * sizeof(int), stream>>>(ids, workspace, n_pairs, n_exp);
   moe_scan_kernel<<<n_exp, 256, 0, stream>>>(workspace, seg_count, nb, n_exp);
-  moe_seg_kernel<<<1, 512, 0, stream>>>(seg_count, seg_start, region_rows_used, n_exp, experts_per_region, region_rows, align);
+  moe_seg_kernel<<<1, 512, 0, stream>>>(seg_count, seg_start, region_rows_used, n_exp, experts_per_region, region_rows, align, (unsigned*)epoch_ctr);
   if (nb > 0) moe_scatter_kernel<<<nb, kPlanBlock, 0, stream>>>(ids, workspace, seg_start, pair_row, row_token, n_pairs, n_exp, k, capacity);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 GB_API int gb_moe_combine(const void* y, const int* pair_row, const float* weights, void* out, int n_tok, int hidden, int k, int ld_y,
-                          cudaStream_t stream) {
+                          const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream) {
   if (hidden % 8 || k > kMaxTopK) return fail("moe_combine: hidden %% 8 != 0 or k > 16%s");
   if (n_tok <= 0) return 0;
-  moe_combine_kernel<<<n_tok, 256, 0, stream>>>((const __nv_bfloat16*)y, pair_row, weights, (__nv_bfloat16*)out, hidden, k, ld_y);
+  moe_combine_kernel<<<n_tok, 256, 0, stream>>>((const __nv_bfloat16*)y, pair_row, weights, (__nv_bfloat16*)out, hidden, k, ld_y,
+                                               (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

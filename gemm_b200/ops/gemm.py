@@ -17,6 +17,14 @@ from .mxfp8 import MxTensor
 
 GEMM_MX, GEMM_DUAL, GEMM_QUANT_OUT, GEMM_OUT_F32 = 1, 2, 4, 8
 
+
+class GemmExtras(ctypes.Structure):
+    """Expert-parallel arguments of ``gb_gemm`` (mirrors ``struct GemmExtras`` in csrc/kernels/gemm_tc.cu)."""
+    _fields_ = [("w_group_mod", ctypes.c_int), ("wait_n", ctypes.c_int), ("wait_flags", ctypes.c_void_p),
+                ("epoch_ptr", ctypes.c_void_p), ("peer_out", ctypes.c_void_p * 8), ("peer_region_rows", ctypes.c_int),
+                ("peer_rank", ctypes.c_int), ("signal_flags", ctypes.c_void_p * 8), ("signal_n", ctypes.c_int),
+                ("pad", ctypes.c_int), ("done_ctr", ctypes.c_void_p)]
+
 _c = ctypes.c_void_p
 _i = ctypes.c_int
 
@@ -44,12 +52,12 @@ def pick_tn(m_tok: int, mx: bool = False, dual: bool = False) -> int:
 
 def _launch(w, x, out, n_out, k, m_tok, ldw, ldx, ldo, flags, tn, num_groups=0, w_rows_per_group=0, up_row_offset=0,
             seg_start=None, seg_count=None, x_rows=None, sfa=None, sfb=None, out_sf=None, bias=None, row_map=None,
-            row_scale=None):
+            row_scale=None, extras=None):
     lib = _native.cuda()
     rc = lib.gb_gemm(_p(w), _p(x), _p(out), _i(n_out), _i(k), _i(m_tok), _i(ldw), _i(ldx), _i(ldo), _i(flags), _i(tn),
                      _i(num_groups), _i(w_rows_per_group), _i(up_row_offset), _p(seg_start), _p(seg_count),
                      _i(x_rows if x_rows is not None else m_tok), _p(sfa), _p(sfb), _p(out_sf), _p(bias), _p(row_map),
-                     _p(row_scale), _c(_native.status_ptr()), _stream())
+                     _p(row_scale), ctypes.byref(extras) if extras is not None else _c(0), _c(_native.status_ptr()), _stream())
     _native.check(rc, "gb_gemm")
 
 
@@ -125,7 +133,7 @@ def linear_mx_swiglu_quant(x: MxTensor, w_gate_up: MxTensor, tn: Optional[int] =
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, seg_count: torch.Tensor, tn: int,
                    out: Optional[torch.Tensor] = None, dual: bool = False, row_map: Optional[torch.Tensor] = None,
                    row_scale: Optional[torch.Tensor] = None, sfa=None, sfb=None, quant_out: bool = False,
-                   out_sf: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out_sf: Optional[torch.Tensor] = None, extras=None, w_groups: Optional[int] = None) -> torch.Tensor:
     """One GEMM per group over row segments of ``x``.
 
     ``w`` is ``[G, R, K]`` (R = 2I stacked gate/up rows when ``dual``); group g multiplies the rows
@@ -134,6 +142,8 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
     needs ``tn`` 32 or 128, segments aligned to ``tn`` and activation scales in the matching atom layout.
     """
     g, r, k = w.shape
+    if w_groups is not None:
+        g = w_groups                      # more row groups than weight groups (expert parallel: group = (source, expert))
     n_out = r // 2 if dual else r
     mx = sfa is not None
     if not x.is_cuda:
@@ -148,7 +158,7 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
         flags |= GEMM_OUT_F32
     _launch(w, x, out, n_out, k, x.shape[0], k, x.stride(0), out.stride(0), flags, tn, num_groups=g, w_rows_per_group=r,
             up_row_offset=n_out if dual else 0, seg_start=seg_start, seg_count=seg_count, x_rows=x.shape[0], sfa=sfa,
-            sfb=sfb, out_sf=out_sf, row_map=row_map, row_scale=row_scale)
+            sfb=sfb, out_sf=out_sf, row_map=row_map, row_scale=row_scale, extras=extras)
     return out
 
 

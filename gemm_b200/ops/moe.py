@@ -107,13 +107,20 @@ def plan_ref(ids: torch.Tensor, n_exp: int, k: int, align: int, regions: int = 1
                    region_used.to(torch.int32), capacity, region_rows)
 
 
-def plan(ids: torch.Tensor, n_exp: int, align: int, regions: int = 1, workspace=None) -> MoePlan:
-    """Device-side plan from ``ids int32 [T, k]``; no host synchronisation."""
+def plan(ids: torch.Tensor, n_exp: int, align: int, regions: int = 1, workspace=None, epoch_ctr: int = 0,
+         region_rows: Optional[int] = None) -> MoePlan:
+    """Device-side plan from ``ids int32 [T, k]``; no host synchronisation.  ``region_rows`` fixes the rows per
+    region (expert parallel: the same value on every rank); it must be at least ``plan_capacity``'s."""
     t, k = ids.shape
     if not ids.is_cuda:
         return plan_ref(ids, n_exp, k, align, regions)
     n_pairs = t * k
-    region_rows, capacity = plan_capacity(n_pairs, n_exp, align, regions, k)
+    need_rows, capacity = plan_capacity(n_pairs, n_exp, align, regions, k)
+    if region_rows is None:
+        region_rows = need_rows
+    else:
+        assert region_rows >= need_rows and region_rows % 128 == 0
+        capacity = region_rows * regions
     dev = ids.device
     nb = (n_pairs + 255) // 256
     ws = torch.empty(max(1, nb * n_exp), dtype=torch.int32, device=dev)
@@ -124,12 +131,13 @@ def plan(ids: torch.Tensor, n_exp: int, align: int, regions: int = 1, workspace=
     row_token = torch.empty(capacity, dtype=torch.int32, device=dev)
     rc = _native.cuda().gb_moe_plan(_p(ids), _p(ws), _p(seg_start), _p(seg_count), _p(region_used), _p(pair_row), _p(row_token),
                                     _l(n_pairs), _i(n_exp), _i(k), _i(n_exp // regions), _i(region_rows), _i(align),
-                                    _l(capacity), _s())
+                                    _l(capacity), _c(epoch_ctr), _s())
     _native.check(rc, "gb_moe_plan", n=4)
     return MoePlan(seg_start, seg_count, pair_row, row_token, region_used, capacity, region_rows)
 
 
-def combine(y: torch.Tensor, pair_row: torch.Tensor, weights: Optional[torch.Tensor], n_tok: int, k: int) -> torch.Tensor:
+def combine(y: torch.Tensor, pair_row: torch.Tensor, weights: Optional[torch.Tensor], n_tok: int, k: int,
+            wait_flags: int = 0, wait_n: int = 0, epoch_ptr: int = 0) -> torch.Tensor:
     """``out[t] = sum_j weights[t, j] * y[pair_row[t*k + j]]`` (bf16, fp32 accumulation in fixed order)."""
     hidden = y.shape[1]
     if not y.is_cuda:
@@ -138,7 +146,8 @@ def combine(y: torch.Tensor, pair_row: torch.Tensor, weights: Optional[torch.Ten
         w = weights.float().unsqueeze(-1) if weights is not None else 1.0
         return (g * w).sum(1).to(torch.bfloat16)
     out = torch.empty(n_tok, hidden, dtype=torch.bfloat16, device=y.device)
-    rc = _native.cuda().gb_moe_combine(_p(y), _p(pair_row), _p(weights), _p(out), _i(n_tok), _i(hidden), _i(k), _i(y.stride(0)), _s())
+    rc = _native.cuda().gb_moe_combine(_p(y), _p(pair_row), _p(weights), _p(out), _i(n_tok), _i(hidden), _i(k), _i(y.stride(0)),
+                                       _c(wait_flags), _i(wait_n), _c(epoch_ptr), _c(_native.status_ptr()), _s())
     _native.check(rc, "gb_moe_combine")
     return out
 

@@ -1,0 +1,186 @@
+"""Expert parallelism over the NVLink fabric: data-parallel attention + expert-parallel MoE.
+
+Rank ``r`` owns the experts ``[r * E/N, (r+1) * E/N)`` and attends to its own sequences.  A MoE layer is
+
+  route + plan (local)  ->  dispatch kernel: gather, MXFP8-quantise and STORE every (token, expert) row into the
+  owning GPU's expert buffer over NVLink, then raise a flag there  ->  grouped gate/up GEMM on the owner (waits
+  for the flags of all sources, groups = (source rank, local expert))  ->  grouped down GEMM whose epilogue STORES
+  the result rows straight back into the source GPU's combine buffer and raises its flag  ->  combine kernel on
+  the source (waits for the owners' flags, router-weighted sum in fixed order).
+
+No NCCL call and no host synchronisation is involved; the exchange is the prologue / epilogue of the compute
+kernels.  ``fused=False`` selects the baseline that only calls NCCL: all-gather the tokens, run the owned experts on
+all of them, reduce-scatter the partial sums — the reference's own expert-parallel formulation
+("replicate tokens, compute owned experts, all-reduce", common/m3_impl.h:699-714,924-950).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops import elementwise as ew
+from ..ops import gemm, moe
+from .fabric import Fabric
+
+_c, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+
+
+class ExpertParallel:
+    tp_size = 1
+    tp_rank = 0
+
+    def __init__(self, group, device: torch.device, fused: bool = True):
+        self.group = group
+        self.device = device
+        self.ep_size = dist.get_world_size(group)
+        self.ep_rank = dist.get_rank(group)
+        self.fused = fused
+        self.fab: Optional[Fabric] = None
+        self._buckets: Dict[int, dict] = {}
+
+    # ------------------------------------------------------------------------------------------ setup
+    def attach(self, engine, cfg, max_tokens: int) -> None:
+        """Size the symmetric buffers for at most ``max_tokens`` tokens per rank and forward pass."""
+        self.cfg = cfg
+        self.max_tokens = max_tokens
+        if not self.fused:
+            return
+        w, k, e, hid = self.ep_size, cfg.n_experts_used, cfg.n_experts, cfg.hidden
+        self.e_local = e // w
+        rows_big, _ = moe.plan_capacity(max_tokens * k, e, 128, w, k)
+        total_rows = rows_big * w
+        mx = engine.w.fmt == "mxfp8"
+        x_bytes = total_rows * hid * (1 if mx else 2)
+        sf_bytes = (total_rows // 32) * (hid // 128) * 512 if mx else 0
+        y_bytes = total_rows * hid * 2
+        heap = x_bytes + sf_bytes + y_bytes + (4 << 20)
+        self.fab = Fabric(self.group, self.device, heap)
+        f = self.fab
+        self.x_off = f.alloc(x_bytes)
+        self.sf_off = f.alloc(max(sf_bytes, 16))
+        self.y_off = f.alloc(y_bytes)
+        self.meta_off = f.alloc(2 * w * self.e_local * 4)
+        self.flags_d = f.alloc(8 * 4)
+        self.flags_c = f.alloc(8 * 4)
+        self.epoch = f.ctl_word()
+        self.done_d, self.done_g = f.ctl_word(), f.ctl_word()
+        self.mx = mx
+        self.total_rows_max = total_rows
+        self.meta = f.view(self.meta_off, (2, w * self.e_local), torch.int32)
+
+    def _bucket(self, t: int) -> dict:
+        """Buffer geometry for a forward pass of ``t`` tokens (rounded up so that all ranks agree)."""
+        for cap in (8, 64, 1024, self.max_tokens):
+            if t <= cap:
+                break
+        else:
+            raise ValueError(f"{t} tokens exceed the expert-parallel buffers ({self.max_tokens})")
+        if cap in self._buckets:
+            return self._buckets[cap]
+        cfg, w = self.cfg, self.ep_size
+        k, e, hid, inter = cfg.n_experts_used, cfg.n_experts, cfg.hidden, cfg.expert_ffn
+        tn = 32 if (cap * k) // e <= 24 else 128        # rows per (source, expert) group
+        rows, _ = moe.plan_capacity(cap * k, e, tn, w, k)
+        total = rows * w
+        f = self.fab
+        b = {"tn": tn, "region_rows": rows, "total": total}
+        b["x"] = f.view(self.x_off, (total, hid), torch.uint8 if self.mx else torch.bfloat16)
+        b["sf"] = f.view(self.sf_off, (total // tn, hid // 128, 512), torch.uint8) if self.mx else None
+        b["y"] = f.view(self.y_off, (total, hid), torch.bfloat16)
+        if self.mx:
+            b["hq"] = torch.zeros(total, inter, dtype=torch.uint8, device=self.device)
+            b["hsf"] = ew.sf_alloc(total, inter, self.device, tn)
+        else:
+            b["act"] = torch.zeros(total, inter, dtype=torch.bfloat16, device=self.device)
+        n_groups = w * self.e_local
+        ex1 = gemm.GemmExtras()
+        ex1.w_group_mod = self.e_local
+        ex1.wait_n = w
+        ex1.wait_flags = f.local_base + self.flags_d
+        ex1.epoch_ptr = self.epoch
+        ex2 = gemm.GemmExtras()
+        ex2.w_group_mod = self.e_local
+        ex2.epoch_ptr = self.epoch
+        for p in range(w):
+            ex2.peer_out[p] = f.peer_ptr(p, self.y_off)
+            ex2.signal_flags[p] = f.peer_ptr(p, self.flags_c) + 4 * self.ep_rank
+        ex2.peer_region_rows = rows
+        ex2.peer_rank = self.ep_rank
+        ex2.signal_n = w
+        ex2.done_ctr = self.done_g
+        b["ex1"], b["ex2"], b["groups"] = ex1, ex2, n_groups
+        self._buckets[cap] = b
+        return b
+
+    # ------------------------------------------------------------------------------------------ model hooks
+    def tp_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+    def moe_ffn(self, model, lw, h: torch.Tensor) -> torch.Tensor:
+        if not self.fused:
+            return self._moe_nccl(model, lw, h)
+        cfg, w, f = self.cfg, self.ep_size, self.fab
+        t = h.shape[0]
+        e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
+        b = self._bucket(t)
+        tn, rows = b["tn"], b["region_rows"]
+        logits = gemm.linear(h, lw.router, out_dtype=torch.float32)
+        ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+        pl = moe.plan(ids, e, tn, regions=w, epoch_ctr=self.epoch, region_rows=rows)
+        stream = _c(torch.cuda.current_stream().cuda_stream)
+        rc = f.lib.gb_ep_dispatch(f.bases_arr, _i(w), _i(self.ep_rank), _c(h.data_ptr()), _i(h.stride(0)), _i(hid), _c(pl.row_token.data_ptr()),
+                                  _c(pl.seg_start.data_ptr()), _c(pl.seg_count.data_ptr()), _i(rows), _i(self.e_local), _sz(self.x_off),
+                                  _sz(self.sf_off), _sz(self.meta_off), _sz(self.flags_d), _i(1 if self.mx else 0), _i(1 if tn == 32 else 0),
+                                  _c(self.epoch), _c(self.done_d), _c(_native.status_ptr()), stream)
+        _native.check(rc, "gb_ep_dispatch")
+        seg_start, seg_count = self.meta[0], self.meta[1]
+        if self.mx:
+            gemm.grouped_linear(b["x"], lw.w13.mx.data.view(self.e_local, 2 * inter, hid), seg_start, seg_count, tn, out=b["hq"], dual=True,
+                                sfa=lw.w13.mx.sf, sfb=b["sf"], quant_out=True, out_sf=b["hsf"], extras=b["ex1"], w_groups=b["groups"])
+            gemm.grouped_linear(b["hq"], lw.w2.mx.data.view(self.e_local, hid, inter), seg_start, seg_count, tn, out=b["y"],
+                                sfa=lw.w2.mx.sf, sfb=b["hsf"], extras=b["ex2"], w_groups=b["groups"])
+        else:
+            gemm.grouped_linear(b["x"], lw.w13.w.view(self.e_local, 2 * inter, hid), seg_start, seg_count, tn, out=b["act"], dual=True,
+                                extras=b["ex1"], w_groups=b["groups"])
+            gemm.grouped_linear(b["act"], lw.w2.w.view(self.e_local, hid, inter), seg_start, seg_count, tn, out=b["y"], extras=b["ex2"],
+                                w_groups=b["groups"])
+        return moe.combine(b["y"], pl.pair_row, wts, t, k, wait_flags=f.local_base + self.flags_c, wait_n=w, epoch_ptr=self.epoch)
+
+    # ------------------------------------------------------------------------------------------ NCCL-only baseline
+    def _moe_nccl(self, model, lw, h: torch.Tensor) -> torch.Tensor:
+        cfg, w = self.cfg, self.ep_size
+        t, hid = h.shape
+        k, e = cfg.n_experts_used, cfg.n_experts
+        e_local = e // w
+        allh = torch.empty(w * t, hid, dtype=h.dtype, device=h.device)
+        dist.all_gather_into_tensor(allh, h.contiguous(), group=self.group)
+        logits = gemm.linear(allh, lw.router, out_dtype=torch.float32)
+        ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+        local = ids - self.ep_rank * e_local
+        local = torch.where((local >= 0) & (local < e_local), local, torch.full_like(local, -1))
+        inter = cfg.expert_ffn
+        tn = 32 if (w * t * k) // e <= 24 else 128
+        pl = moe.plan(local, e_local, tn)
+        if model.mx:
+            xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
+            hq = torch.zeros(pl.capacity, inter, dtype=torch.uint8, device=h.device)
+            hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn)
+            gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, out=hq, dual=True,
+                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf)
+            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf)
+        else:
+            xs = moe.gather_rows(allh, pl.row_token)
+            act = gemm.grouped_linear(xs, lw.w13.w.view(e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True)
+            y = gemm.grouped_linear(act, lw.w2.w.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn)
+        part = moe.combine(y, pl.pair_row, wts, w * t, k).float()
+        out = torch.empty(t, hid, dtype=torch.float32, device=h.device)
+        dist.reduce_scatter_tensor(out, part, group=self.group)
+        return out.to(torch.bfloat16)
+
+    def close(self) -> None:
+        if self.fab is not None:
+            self.fab.close()

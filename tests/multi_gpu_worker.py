@@ -1,0 +1,139 @@
+"""Worker of tests/test_multi_gpu.py: one process per GPU, launched by ``torch.distributed.run``.
+Checks the fabric collectives against values computed from an NCCL all-gather in fixed rank order, and the
+expert-parallel engine (fused peer-memory path and NCCL baseline) against the single-GPU engine."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from gemm_b200 import _native  # noqa: E402
+from gemm_b200.models.config import get_config  # noqa: E402
+from gemm_b200.models.transformer import ForwardBatch, KvCache, Transformer  # noqa: E402
+from gemm_b200.models.weights import synthetic_weights  # noqa: E402
+from gemm_b200.parallel.expert import ExpertParallel  # noqa: E402
+from gemm_b200.parallel.fabric import Fabric  # noqa: E402
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def check_collectives(fab, rank, world, dev):
+    torch.manual_seed(100 + rank)
+    for dtype in (torch.float32, torch.bfloat16):
+        ar = fab.make_allreduce(4096, dtype, chunks=4)
+        for n in (8, 1000 if dtype == torch.float32 else 1000 // 8 * 8, 4096):
+            x = torch.randn(n, device=dev).to(dtype)
+            gathered = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(gathered, x)
+            ref = torch.zeros(n, device=dev)
+            for g in gathered:
+                ref += g.float()
+            for _ in range(3):                       # repeated calls exercise the epoch counters
+                y = ar(x)
+            assert torch.equal(y, ref.to(dtype)), f"one-shot all-reduce mismatch {dtype} n={n}"
+        big = fab.make_allreduce_large(1 << 18, dtype, chunks=16)
+        x = torch.randn(200000 // 64 * 64, device=dev).to(dtype)
+        gathered = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(gathered, x)
+        ref = torch.zeros(x.numel(), device=dev)
+        for g in gathered:
+            ref += g.float()
+        for _ in range(2):
+            y = big(x)
+        assert torch.equal(y, ref.to(dtype)), f"two-shot all-reduce mismatch {dtype}"
+    ex = fab.make_exchange(4096, chunks=2)
+    x = torch.full((1024,), float(rank), device=dev)
+    ag = ex.all_gather(x).view(torch.float32).view(world, 1024)
+    assert all(bool((ag[r] == r).all()) for r in range(world))
+    x2 = (torch.arange(world, device=dev, dtype=torch.float32).unsqueeze(1) * 10 + rank).repeat(1, 1024).contiguous()
+    a2a = ex.all_to_all(x2).view(torch.float32).view(world, 1024)
+    assert all(bool((a2a[r] == rank * 10 + r).all()) for r in range(world))
+    am = fab.make_argmax(16)
+    val = torch.tensor([1.0, 5.0, float(rank), 7.0], device=dev)
+    idx = torch.tensor([rank, 100 - rank, 3, 10 + rank], dtype=torch.int32, device=dev)
+    oi, ov = am(val, idx)
+    assert oi.tolist() == [0, 100 - (world - 1), 3, 10] and ov.tolist() == [1.0, 5.0, float(world - 1), 7.0], (oi, ov)
+    fab.barrier()
+    torch.cuda.synchronize()
+    _native.assert_status_ok()
+
+
+def run_model(model, cfg, toks, page, dev):
+    """Prefill (two chunks) + 2 decode steps; returns the list of logits tensors."""
+    lens = [t.numel() - 2 for t in toks]
+    b = len(toks)
+    pages_per = [(t.numel() + page - 1) // page for t in toks]
+    bt = torch.zeros(b, max(pages_per), dtype=torch.int32)
+    p0 = 0
+    for s in range(b):
+        bt[s, : pages_per[s]] = torch.arange(p0, p0 + pages_per[s])
+        p0 += pages_per[s]
+    ctx = [0] * b
+    outs = []
+    for chunk in ([l // 2 for l in lens], [l - l // 2 for l in lens]):
+        ids = torch.cat([toks[s][ctx[s]:ctx[s] + chunk[s]] for s in range(b)])
+        fb = ForwardBatch.build(chunk, ctx, ids, bt, page, cfg.n_heads, cfg.n_kv_heads, dev)
+        outs.append(model.forward(fb).float())
+        ctx = [c + q for c, q in zip(ctx, chunk)]
+    for step in range(2):
+        ids = torch.stack([toks[s][lens[s] + step] for s in range(b)])
+        fb = ForwardBatch.build([1] * b, ctx, ids, bt, page, cfg.n_heads, cfg.n_kv_heads, dev)
+        outs.append(model.forward(fb).float())
+        ctx = [c + 1 for c in ctx]
+    return outs
+
+
+def check_expert_parallel(rank, world, dev, fmt, fused):
+    cfg = get_config("tiny-moe")
+    page = 16
+    g = torch.Generator().manual_seed(7)
+    all_toks = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (40, 90, 33, 70, 52, 64, 48, 81)][: 2 * world]
+    mine = all_toks[rank * 2: rank * 2 + 2]
+    w_full = synthetic_weights(cfg, fmt, device=dev, seed=5)
+    w_ep = synthetic_weights(cfg, fmt, device=dev, seed=5, ep_rank=rank, ep_size=world)
+    ref_model = Transformer(w_full, KvCache.allocate(cfg, 64, page, dev))
+    ref = run_model(ref_model, cfg, mine, page, dev)
+    par = ExpertParallel(dist.group.WORLD, dev, fused=fused)
+
+    class _E:            # the slice of the Engine interface that attach() needs
+        w = w_ep
+    par.attach(_E, cfg, max_tokens=256)
+    model = Transformer(w_ep, KvCache.allocate(cfg, 64, page, dev), par)
+    got = run_model(model, cfg, mine, page, dev)
+    torch.cuda.synchronize()
+    _native.assert_status_ok()
+    tol = 2e-2 if fmt == "bf16" else 6e-2
+    for a, b in zip(got, ref):
+        r = rel(a, b)
+        assert r < tol, f"EP({fmt}, fused={fused}) differs from the single-GPU engine: rel {r}"
+    dist.barrier()
+    par.close()
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("all", "collectives"):
+        fab = Fabric(dist.group.WORLD, dev, 32 << 20)
+        check_collectives(fab, rank, world, dev)
+        dist.barrier()
+        fab.close()
+    if what in ("all", "ep"):
+        for fmt, fused in (("bf16", True), ("mxfp8", True), ("mxfp8", False)):
+            check_expert_parallel(rank, world, dev, fmt, fused)
+    dist.barrier()
+    if rank == 0:
+        print("MULTI_GPU_WORKER_OK", what, "world", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,33 @@
+"""Multi-GPU tests: fabric collectives and expert parallelism, run as child processes (one per GPU)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(what: str, nproc: int, port: int):
+    env = dict(os.environ)
+    env.setdefault("NCCL_NVLS_ENABLE", "0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "multi_gpu_worker.py"), what]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert r.returncode == 0 and "MULTI_GPU_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-6000:])
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_fabric_collectives():
+    _launch("collectives", min(_ngpu(), 4), 29611)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_expert_parallel_matches_single_gpu():
+    _launch("ep", min(_ngpu(), 4), 29612)
