@@ -185,19 +185,16 @@ def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: 
             lw.router = _randn((e, h), _seed(seed, li, 5), device)
             if cfg.router == "sigmoid":
                 lw.router_bias = torch.zeros(e, dtype=torch.float32, device=device)
-            # experts are generated one EP shard at a time so that the peak stays one shard
-            g13 = torch.Generator(device=device); g13.manual_seed(_seed(seed, li, 6))
-            g2 = torch.Generator(device=device); g2.manual_seed(_seed(seed, li, 7))
-            w13 = w2 = None
-            for r in range(ep_size):
-                a = torch.randn((e_l * 2 * inter, h), generator=g13, device=device, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
-                b = torch.randn((e_l * h, inter), generator=g2, device=device, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
-                if r == ep_rank:
-                    w13, w2 = a, b
-                    if ep_rank == ep_size - 1:
-                        break
-                else:
-                    del a, b
+            # every expert has its own seed, so an expert-parallel shard is bit-identical to a slice of the full model
+            w13 = torch.empty((e_l * 2 * inter, h), dtype=torch.bfloat16, device=device)
+            w2 = torch.empty((e_l * h, inter), dtype=torch.bfloat16, device=device)
+            gen = torch.Generator(device=device)
+            for j in range(e_l):
+                ge = ep_rank * e_l + j
+                gen.manual_seed(_seed(seed, li, 1000 + 2 * ge))
+                w13[j * 2 * inter:(j + 1) * 2 * inter] = torch.randn((2 * inter, h), generator=gen, device=device, dtype=torch.float32).mul_(0.02)
+                gen.manual_seed(_seed(seed, li, 1001 + 2 * ge))
+                w2[j * h:(j + 1) * h] = torch.randn((h, inter), generator=gen, device=device, dtype=torch.float32).mul_(0.02)
             lw.w13 = make_linear(w13, fmt, groups=e_l)
             lw.w2 = make_linear(w2, fmt, groups=e_l)
             del w13, w2

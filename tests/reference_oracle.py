@@ -1,0 +1,39 @@
+"""Builds the reference project's own CPU decoders / engine with gcc (when its source tree is present) so that
+tests can compare against them bit for bit.  Nothing of the reference is copied: it is compiled from its place
+and loaded through ctypes; tests that need it are skipped when the tree or gcc is missing."""
+import ctypes
+import os
+import shutil
+import subprocess
+import tempfile
+
+REF_ROOT = os.environ.get("GEMM_REFERENCE_ROOT", "/root/reference")
+_cache = {}
+
+
+def available() -> bool:
+    return os.path.isdir(os.path.join(REF_ROOT, "common")) and shutil.which("gcc") is not None
+
+
+def _build(name: str, source: str, extra=()):
+    if name in _cache:
+        return _cache[name]
+    d = tempfile.mkdtemp(prefix="gemm_ref_oracle_")
+    src = os.path.join(d, name + ".c")
+    with open(src, "w") as f:
+        f.write(source)
+    so = os.path.join(d, name + ".so")
+    cmd = ["gcc", "-O2", "-shared", "-fPIC", "-w", "-mavx2", "-mfma", "-mf16c", "-I", os.path.join(REF_ROOT, "common"), src, "-o", so, "-lm", "-lpthread", *extra]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("reference oracle build failed:\n" + r.stderr[-3000:])
+    _cache[name] = ctypes.CDLL(so)
+    return _cache[name]
+
+
+def dequant_lib():
+    """ctypes handle exposing the reference's ``dequant_row(type, src, dst, n)``."""
+    lib = _build("ref_dequant", '#define GGML_DEQUANT_IMPLEMENTATION\n#include "gguf_loader.h"\n#include "ggml_dequant.h"\n')
+    lib.dequant_row.argtypes = [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+    lib.dequant_row.restype = ctypes.c_int
+    return lib
