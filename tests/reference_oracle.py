@@ -37,3 +37,15 @@ def dequant_lib():
     lib.dequant_row.argtypes = [ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
     lib.dequant_row.restype = ctypes.c_int
     return lib
+
+
+def tokenizer_lib():
+    """ctypes handle exposing the reference's gguf_open / bpe_vocab_load / bpe_tokenize."""
+    lib = _build("ref_tok", '#define GGUF_LOADER_IMPLEMENTATION\n#include "gguf_loader.h"\n#define BPE_TOKENIZER_IMPLEMENTATION\n#include "bpe_tokenizer.h"\n')
+    lib.gguf_open.restype = ctypes.c_void_p
+    lib.gguf_open.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    lib.bpe_vocab_load.restype = ctypes.c_void_p
+    lib.bpe_vocab_load.argtypes = [ctypes.c_void_p]
+    lib.bpe_tokenize.restype = ctypes.c_int
+    lib.bpe_tokenize.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
+    return lib
