@@ -1,0 +1,365 @@
+"""Checkpoint loading and writing: GGUF (any ggml type, dequantised on load) and Hugging Face safetensors.
+
+Names follow the layouts the reference reads: GGUF ``token_embd / output_norm / output / blk.N.{attn_norm, attn_q, attn_k,
+attn_v, attn_q_norm, attn_k_norm, attn_output, ffn_norm, ffn_gate, ffn_up, ffn_down}.weight``, MoE ``blk.N.{ffn_gate_inp,
+ffn_gate_exps, ffn_up_exps, ffn_down_exps}.weight`` as 3-D tensors (common/transformer.h:1775-2010), and the HF Qwen3 names
+``model.layers.N.self_attn.{q,k,v,o}_proj``, ``mlp.{gate,up,down}_proj``, ``mlp.experts.E.*`` (cuda/llm/cuda_llm_runner.c:12293-12447).
+Hyper-parameters come from the GGUF key/values (``<arch>.*``) or, for safetensors, from ``config.json``.
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import _native
+from ..utils import gguf as G
+from .config import ARCHS, ModelConfig
+from .weights import ModelWeights, RandomSource, build_weights
+
+
+# ------------------------------------------------------------------------------------------ GGUF
+def config_from_gguf(f: G.GGUFFile) -> ModelConfig:
+    m = f.metadata
+    arch = m.get("general.architecture", "qwen3")
+    if arch not in ARCHS:
+        raise ValueError(f"unsupported architecture {arch!r} (supported: {ARCHS})")
+
+    def key(name, default=None):
+        return m.get(f"{arch}.{name}", default)
+
+    hidden = int(key("embedding_length"))
+    n_heads = int(key("attention.head_count"))
+    head_dim = int(key("attention.key_length", hidden // n_heads))
+    vocab = key("vocab_size")
+    if vocab is None:
+        vocab = f.tensors["token_embd.weight"].shape[0]
+    n_exp = int(key("expert_count", 0) or 0)
+    cfg = ModelConfig(
+        arch=arch, n_layers=int(key("block_count")), hidden=hidden, n_heads=n_heads,
+        n_kv_heads=int(key("attention.head_count_kv", n_heads)), head_dim=head_dim, ffn=int(key("feed_forward_length", 0) or 0),
+        vocab=int(vocab), rms_eps=float(key("attention.layer_norm_rms_epsilon", 1e-6)), rope_theta=float(key("rope.freq_base", 1e6)),
+        rope_dim=(int(key("rope.dimension_count")) if key("rope.dimension_count") not in (None, head_dim) else None),
+        qk_norm="blk.0.attn_q_norm.weight" in f.tensors, qkv_bias="blk.0.attn_q.bias" in f.tensors,
+        tie_embeddings="output.weight" not in f.tensors, max_seq_len=int(key("context_length", 4096)),
+        n_experts=n_exp, n_experts_used=int(key("expert_used_count", 0) or 0), expert_ffn=int(key("expert_feed_forward_length", 0) or 0),
+        shared_expert_ffn=int(key("expert_shared_feed_forward_length", 0) or 0),
+        full_attention_interval=int(key("attention.full_attention_interval", 0) or 0),
+        n_deepstack_layers=int(key("n_deepstack_layers", 0) or 0),
+    )
+    sections = key("rope.dimension_sections")
+    if sections is not None:
+        cfg.mrope_sections = [int(x) for x in sections]
+    return cfg
+
+
+class GGUFSource:
+    """Tensor source over an open GGUF file: every tensor is dequantised to float32 on request."""
+
+    def __init__(self, f: G.GGUFFile):
+        self.f = f
+        self._cache_name = None
+        self._cache = None
+
+    def has(self, name: str) -> bool:
+        return name in self.f.tensors
+
+    def get(self, name: str, shape) -> torch.Tensor:
+        t = self.f.tensors[name]
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"{name}: file has shape {t.shape}, model wants {tuple(shape)}")
+        return t.to_float()
+
+    def get_expert(self, name: str, e: int, shape) -> torch.Tensor:
+        t = self.f.tensors[name]
+        if tuple(t.shape[1:]) != tuple(shape):
+            raise ValueError(f"{name}: file has per-expert shape {t.shape[1:]}, model wants {tuple(shape)}")
+        per = int(np.prod(shape))
+        blk, nbytes = G.block_info(t.ggml_type)
+        off = e * per // blk * nbytes
+        raw = t.raw()[off: off + per // blk * nbytes]
+        return G.dequantize(raw, t.ggml_type, per).reshape(tuple(shape))
+
+
+def load_gguf(path: str, fmt: str = "bf16", device="cuda", tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0, ep_size: int = 1,
+              shard_vocab: bool = False) -> ModelWeights:
+    """Load a GGUF checkpoint into the run-time weight format ``fmt`` (``bf16`` or ``mxfp8``), sharded for this rank."""
+    with G.GGUFFile(path) as f:
+        cfg = config_from_gguf(f)
+        return build_weights(cfg, GGUFSource(f), fmt, device, tp_rank, tp_size, ep_rank, ep_size, shard_vocab)
+
+
+def save_gguf(cfg: ModelConfig, src, path: str, wtype: str = "F16", tokens=None, merges=None, token_types=None, pre: str = "qwen2") -> None:
+    """Write the tensors of ``src`` (any tensor source) as a GGUF file the reference engine can load.
+
+    Matrices are quantised to ``wtype`` (norms and biases stay F32).  The reference refuses files without a tokenizer
+    vocabulary (common/bpe_tokenizer.h:356-360), so a byte-level dummy vocabulary is written when none is given."""
+    w = G.GGUFWriter()
+    a = cfg.arch
+    w.add_string("general.architecture", a)
+    w.add_string("general.name", f"synthetic-{a}")
+    w.add_u32(f"{a}.block_count", cfg.n_layers)
+    w.add_u32(f"{a}.embedding_length", cfg.hidden)
+    w.add_u32(f"{a}.attention.head_count", cfg.n_heads)
+    w.add_u32(f"{a}.attention.head_count_kv", cfg.n_kv_heads)
+    w.add_u32(f"{a}.attention.key_length", cfg.head_dim)
+    w.add_u32(f"{a}.attention.value_length", cfg.head_dim)
+    w.add_u32(f"{a}.feed_forward_length", cfg.ffn)
+    w.add_u32(f"{a}.vocab_size", cfg.vocab)
+    w.add_u32(f"{a}.context_length", cfg.max_seq_len)
+    w.add_f32(f"{a}.attention.layer_norm_rms_epsilon", cfg.rms_eps)
+    w.add_f32(f"{a}.rope.freq_base", cfg.rope_theta)
+    if cfg.is_moe:
+        w.add_u32(f"{a}.expert_count", cfg.n_experts)
+        w.add_u32(f"{a}.expert_used_count", cfg.n_experts_used)
+        w.add_u32(f"{a}.expert_feed_forward_length", cfg.expert_ffn)
+    if tokens is None:
+        from ..utils.tokenizer import byte_alphabet
+        tokens = byte_alphabet() + [f"<extra_{i}>" for i in range(max(0, cfg.vocab - 256))]
+        tokens = tokens[: cfg.vocab]
+        merges, token_types = [], [1] * len(tokens)
+    w.add_string("tokenizer.ggml.model", "gpt2")
+    w.add_string("tokenizer.ggml.pre", pre)
+    w.add_string_array("tokenizer.ggml.tokens", tokens)
+    w.add_string_array("tokenizer.ggml.merges", merges or [])
+    if token_types is not None:
+        w.add_array("tokenizer.ggml.token_type", token_types)
+    w.add_u32("tokenizer.ggml.eos_token_id", max(0, len(tokens) - 1))
+    h, d = cfg.hidden, cfg.head_dim
+
+    def mat(name, shape):
+        w.add_tensor(name, src.get(name, shape).float(), wtype)
+
+    def vec(name, shape):
+        w.add_tensor(name, src.get(name, shape).float(), "F32")
+
+    mat("token_embd.weight", (cfg.vocab, h))
+    vec("output_norm.weight", (h,))
+    if not cfg.tie_embeddings:
+        mat("output.weight", (cfg.vocab, h))
+    for li in range(cfg.n_layers):
+        p = f"blk.{li}."
+        vec(p + "attn_norm.weight", (h,))
+        mat(p + "attn_q.weight", (cfg.q_dim, h)); mat(p + "attn_k.weight", (cfg.kv_dim, h)); mat(p + "attn_v.weight", (cfg.kv_dim, h))
+        mat(p + "attn_output.weight", (h, cfg.q_dim))
+        if cfg.qkv_bias:
+            vec(p + "attn_q.bias", (cfg.q_dim,)); vec(p + "attn_k.bias", (cfg.kv_dim,)); vec(p + "attn_v.bias", (cfg.kv_dim,))
+        if cfg.qk_norm:
+            vec(p + "attn_q_norm.weight", (d,)); vec(p + "attn_k_norm.weight", (d,))
+        vec(p + "ffn_norm.weight", (h,))
+        if cfg.is_moe:
+            e, inter = cfg.n_experts, cfg.expert_ffn
+            w.add_tensor(p + "ffn_gate_inp.weight", src.get(p + "ffn_gate_inp.weight", (e, h)).float(), "F32")
+            for nm, shp in (("ffn_gate_exps.weight", (inter, h)), ("ffn_up_exps.weight", (inter, h)), ("ffn_down_exps.weight", (h, inter))):
+                full = torch.stack([src.get_expert(p + nm, ei, shp).float() for ei in range(e)])
+                w.add_tensor(p + nm, full, wtype)
+        else:
+            mat(p + "ffn_gate.weight", (cfg.ffn, h)); mat(p + "ffn_up.weight", (cfg.ffn, h)); mat(p + "ffn_down.weight", (h, cfg.ffn))
+    w.write(path)
+
+
+# ------------------------------------------------------------------------------------------ safetensors
+_ST_DTYPES = {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "F8_E4M3": torch.float8_e4m3fn, "U8": torch.uint8,
+              "I8": torch.int8, "I32": torch.int32, "I64": torch.int64, "F64": torch.float64, "I16": torch.int16}
+
+
+def _st_lib():
+    lib = _native.host()
+    if not getattr(lib, "_st_ready", False):
+        lib.gbh_st_open.restype = ctypes.c_void_p
+        lib.gbh_st_data.restype = ctypes.c_void_p
+        lib.gbh_st_count.restype = ctypes.c_long
+        lib.gbh_st_metadata.restype = ctypes.c_char_p
+        lib._st_ready = True
+    return lib
+
+
+class SafetensorsFile:
+    """Memory-mapped safetensors file; ``tensors[name]`` gives a zero-copy torch view (CPU)."""
+
+    def __init__(self, path: str):
+        lib = _st_lib()
+        self._h = lib.gbh_st_open(path.encode())
+        if not self._h:
+            raise IOError(lib.gbh_last_error().decode())
+        self.info: Dict[str, tuple] = {}
+        name = ctypes.create_string_buffer(1024)
+        dt = ctypes.create_string_buffer(8)
+        for i in range(lib.gbh_st_count(ctypes.c_void_p(self._h))):
+            nd, nb = ctypes.c_int(), ctypes.c_uint64()
+            shape = (ctypes.c_int64 * 8)()
+            lib.gbh_st_info(ctypes.c_void_p(self._h), i, name, 1024, dt, ctypes.byref(nd), shape, ctypes.byref(nb))
+            self.info[name.value.decode()] = (i, dt.value.decode(), tuple(int(shape[d]) for d in range(nd.value)), nb.value)
+
+    def keys(self):
+        return self.info.keys()
+
+    def get(self, name: str) -> torch.Tensor:
+        i, dt, shape, nb = self.info[name]
+        p = _st_lib().gbh_st_data(ctypes.c_void_p(self._h), i)
+        if nb == 0:
+            return torch.empty(shape, dtype=_ST_DTYPES[dt])
+        buf = (ctypes.c_uint8 * nb).from_address(p)
+        return torch.frombuffer(buf, dtype=torch.uint8).view(_ST_DTYPES[dt]).reshape(shape)
+
+    def metadata(self, key: str) -> Optional[str]:
+        v = _st_lib().gbh_st_metadata(ctypes.c_void_p(self._h), key.encode())
+        return v.decode() if v else None
+
+    def close(self):
+        if self._h:
+            _st_lib().gbh_st_close(ctypes.c_void_p(self._h))
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def save_safetensors(tensors: Dict[str, torch.Tensor], path: str) -> None:
+    rev = {v: k for k, v in _ST_DTYPES.items()}
+    names = list(tensors)
+    ts = [tensors[n].contiguous().cpu() for n in names]
+    n = len(names)
+    c_names = (ctypes.c_char_p * n)(*[x.encode() for x in names])
+    c_dt = (ctypes.c_char_p * n)(*[rev[t.dtype].encode() for t in ts])
+    ranks = (ctypes.c_int * n)(*[t.dim() for t in ts])
+    flat = [int(s) for t in ts for s in t.shape]
+    shapes = (ctypes.c_int64 * max(1, len(flat)))(*flat)
+    ptrs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
+    nbytes = (ctypes.c_uint64 * n)(*[t.numel() * t.element_size() for t in ts])
+    if _st_lib().gbh_st_write(path.encode(), n, c_names, c_dt, ranks, shapes, ptrs, nbytes) != 0:
+        raise IOError(_st_lib().gbh_last_error().decode())
+
+
+_HF_MAP = {"attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj", "attn_v": "self_attn.v_proj", "attn_output": "self_attn.o_proj",
+           "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm", "attn_norm": "input_layernorm",
+           "ffn_norm": "post_attention_layernorm", "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj",
+           "ffn_gate_inp": "mlp.gate"}
+_HF_EXPERT = {"ffn_gate_exps": "gate_proj", "ffn_up_exps": "up_proj", "ffn_down_exps": "down_proj"}
+
+
+def hf_name(gguf_name: str, expert: Optional[int] = None) -> str:
+    """HF safetensors name of a GGUF tensor name (Qwen2 / Qwen3 / Qwen3-MoE layout)."""
+    if gguf_name == "token_embd.weight":
+        return "model.embed_tokens.weight"
+    if gguf_name == "output_norm.weight":
+        return "model.norm.weight"
+    if gguf_name == "output.weight":
+        return "lm_head.weight"
+    _, li, rest = gguf_name.split(".", 2)
+    base, kind = rest.rsplit(".", 1)
+    if base in _HF_EXPERT:
+        return f"model.layers.{li}.mlp.experts.{expert}.{_HF_EXPERT[base]}.{kind}"
+    return f"model.layers.{li}.{_HF_MAP[base]}.{kind}"
+
+
+class SafetensorsSource:
+    """Tensor source over a directory of HF safetensors shards (or one file).  MXFP8 checkpoints (``F8_E4M3`` weights with a
+    ``<name>_scale_inv`` E8M0 tensor of shape [rows, cols/32]) are dequantised exactly: e4m3 * 2^(s-127)."""
+
+    def __init__(self, path: str):
+        files = [path] if os.path.isfile(path) else sorted(os.path.join(path, x) for x in os.listdir(path) if x.endswith(".safetensors"))
+        if not files:
+            raise IOError(f"no .safetensors files under {path}")
+        self.files = [SafetensorsFile(p) for p in files]
+        self.where = {k: f for f in self.files for k in f.keys()}
+
+    def _raw(self, name: str) -> torch.Tensor:
+        t = self.where[name].get(name)
+        if t.dtype == torch.float8_e4m3fn:
+            s = self.where[name + "_scale_inv"].get(name + "_scale_inv")
+            scale = (s.to(torch.int32) << 23).view(torch.float32)
+            rows, cols = t.shape
+            return (t.to(torch.float32).reshape(rows, cols // 32, 32) * scale.unsqueeze(-1)).reshape(rows, cols)
+        return t.to(torch.float32)
+
+    def has(self, name: str) -> bool:
+        return hf_name(name) in self.where
+
+    def get(self, name: str, shape) -> torch.Tensor:
+        t = self._raw(hf_name(name))
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"{name}: checkpoint has shape {tuple(t.shape)}, model wants {tuple(shape)}")
+        return t
+
+    def get_expert(self, name: str, e: int, shape) -> torch.Tensor:
+        return self._raw(hf_name(name, e))
+
+
+def config_from_hf(path: str) -> ModelConfig:
+    with open(os.path.join(path, "config.json")) as fh:
+        c = json.load(fh)
+    mt = c.get("model_type", "qwen3")
+    arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3moe"}.get(mt, "qwen3")
+    hidden, heads = c["hidden_size"], c["num_attention_heads"]
+    return ModelConfig(arch=arch, n_layers=c["num_hidden_layers"], hidden=hidden, n_heads=heads, n_kv_heads=c.get("num_key_value_heads", heads),
+                       head_dim=c.get("head_dim", hidden // heads), ffn=c.get("intermediate_size", 0), vocab=c["vocab_size"],
+                       rms_eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e6), qk_norm=(mt != "qwen2"), qkv_bias=(mt == "qwen2"),
+                       tie_embeddings=c.get("tie_word_embeddings", False), max_seq_len=c.get("max_position_embeddings", 4096),
+                       n_experts=c.get("num_experts", 0), n_experts_used=c.get("num_experts_per_tok", 0),
+                       expert_ffn=c.get("moe_intermediate_size", 0), norm_topk=c.get("norm_topk_prob", True))
+
+
+def load_safetensors(path: str, fmt: str = "bf16", device="cuda", cfg: Optional[ModelConfig] = None, **shard) -> ModelWeights:
+    """Load an HF checkpoint directory (config.json + *.safetensors)."""
+    cfg = cfg or config_from_hf(path)
+    return build_weights(cfg, SafetensorsSource(path), fmt, device, **shard)
+
+
+def save_hf_checkpoint(cfg: ModelConfig, src, path: str, mxfp8: bool = False) -> None:
+    """Write ``src`` as an HF-layout directory (one safetensors file + config.json); ``mxfp8`` stores the projection matrices
+    as F8_E4M3 + ``_scale_inv`` E8M0 the way MXFP8 checkpoints do."""
+    from ..ops import mxfp8 as MX
+    os.makedirs(path, exist_ok=True)
+    out: Dict[str, torch.Tensor] = {}
+    h, d = cfg.hidden, cfg.head_dim
+
+    def put(name, t, quant, expert=None):
+        key = hf_name(name, expert)
+        if quant and mxfp8:
+            q, e = MX.quantize_rowmajor(t.float())
+            out[key] = q.view(torch.float8_e4m3fn)
+            out[key + "_scale_inv"] = e
+        else:
+            out[key] = t.to(torch.bfloat16)
+
+    put("token_embd.weight", src.get("token_embd.weight", (cfg.vocab, h)), False)
+    put("output_norm.weight", src.get("output_norm.weight", (h,)), False)
+    if not cfg.tie_embeddings:
+        put("output.weight", src.get("output.weight", (cfg.vocab, h)), False)
+    for li in range(cfg.n_layers):
+        p = f"blk.{li}."
+        for nm, shp, qn in (("attn_norm.weight", (h,), False), ("attn_q.weight", (cfg.q_dim, h), True), ("attn_k.weight", (cfg.kv_dim, h), True),
+                            ("attn_v.weight", (cfg.kv_dim, h), True), ("attn_output.weight", (h, cfg.q_dim), True), ("ffn_norm.weight", (h,), False)):
+            put(p + nm, src.get(p + nm, shp), qn)
+        if cfg.qk_norm:
+            put(p + "attn_q_norm.weight", src.get(p + "attn_q_norm.weight", (d,)), False)
+            put(p + "attn_k_norm.weight", src.get(p + "attn_k_norm.weight", (d,)), False)
+        if cfg.qkv_bias:
+            for nm, n in (("attn_q.bias", cfg.q_dim), ("attn_k.bias", cfg.kv_dim), ("attn_v.bias", cfg.kv_dim)):
+                put(p + nm, src.get(p + nm, (n,)), False)
+        if cfg.is_moe:
+            put(p + "ffn_gate_inp.weight", src.get(p + "ffn_gate_inp.weight", (cfg.n_experts, h)), False)
+            for e in range(cfg.n_experts):
+                put(p + "ffn_gate_exps.weight", src.get_expert(p + "ffn_gate_exps.weight", e, (cfg.expert_ffn, h)), True, e)
+                put(p + "ffn_up_exps.weight", src.get_expert(p + "ffn_up_exps.weight", e, (cfg.expert_ffn, h)), True, e)
+                put(p + "ffn_down_exps.weight", src.get_expert(p + "ffn_down_exps.weight", e, (h, cfg.expert_ffn)), True, e)
+        else:
+            put(p + "ffn_gate.weight", src.get(p + "ffn_gate.weight", (cfg.ffn, h)), True)
+            put(p + "ffn_up.weight", src.get(p + "ffn_up.weight", (cfg.ffn, h)), True)
+            put(p + "ffn_down.weight", src.get(p + "ffn_down.weight", (h, cfg.ffn)), True)
+    save_safetensors(out, os.path.join(path, "model.safetensors"))
+    mt = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3moe": "qwen3_moe"}.get(cfg.arch, "qwen3")
+    with open(os.path.join(path, "config.json"), "w") as fh:
+        json.dump({"model_type": mt, "hidden_size": h, "num_attention_heads": cfg.n_heads, "num_key_value_heads": cfg.n_kv_heads, "head_dim": d,
+                   "num_hidden_layers": cfg.n_layers, "intermediate_size": cfg.ffn, "vocab_size": cfg.vocab, "rms_norm_eps": cfg.rms_eps,
+                   "rope_theta": cfg.rope_theta, "tie_word_embeddings": cfg.tie_embeddings, "max_position_embeddings": cfg.max_seq_len,
+                   "num_experts": cfg.n_experts, "num_experts_per_tok": cfg.n_experts_used, "moe_intermediate_size": cfg.expert_ffn,
+                   "norm_topk_prob": cfg.norm_topk}, fh)

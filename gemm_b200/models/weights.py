@@ -14,6 +14,7 @@ that a sharded model is a slice of the unsharded one.
 """
 from __future__ import annotations
 
+import zlib
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -123,16 +124,6 @@ class ModelWeights:
         return tot
 
 
-def _randn(shape, seed: int, device, std: float = 0.02) -> torch.Tensor:
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    return torch.randn(shape, generator=g, device=device, dtype=torch.float32).mul_(std).to(torch.bfloat16)
-
-
-def _seed(base: int, layer: int, tensor: int) -> int:
-    return (base * 1000003 + layer * 1009 + tensor) & 0x7FFFFFFF
-
-
 def shard_range(n: int, parts: int, idx: int):
     """Even split with the remainder to the low ranks (the rule of common/glm5.h:178-202)."""
     q, r = divmod(n, parts)
@@ -140,12 +131,41 @@ def shard_range(n: int, parts: int, idx: int):
     return lo, lo + q + (1 if idx < r else 0)
 
 
-def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
-                      ep_rank: int = 0, ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None) -> ModelWeights:
-    """Random-init weights of ``cfg`` in format ``fmt``; TP shards attention / dense FFN (Megatron style:
-    q/k/v/gate/up by rows, o/down by columns), EP keeps the experts ``e`` with ``e // (E / ep_size) == ep_rank``.
-    KV heads are replicated when ``n_kv_heads < tp_size``."""
+class RandomSource:
+    """Tensor source of a random-init checkpoint: N(0, 0.02) matrices, unit norms, zero biases... every tensor
+    (and every expert) has its own seed derived from its GGUF name, so shards are slices of the same model."""
+
+    def __init__(self, cfg: ModelConfig, seed: int = 0, device="cpu", std: float = 0.02):
+        self.cfg, self.seed, self.device, self.std = cfg, seed, torch.device(device), std
+        self._gen = torch.Generator(device=self.device)
+
+    def _randn(self, key: str, shape) -> torch.Tensor:
+        self._gen.manual_seed((zlib.crc32(key.encode()) ^ (self.seed * 2654435761)) & 0x7FFFFFFF)
+        return torch.randn(tuple(shape), generator=self._gen, device=self.device, dtype=torch.float32).mul_(self.std).to(torch.bfloat16)
+
+    def has(self, name: str) -> bool:
+        return True
+
+    def get(self, name: str, shape) -> torch.Tensor:
+        if name.endswith("norm.weight"):
+            return torch.ones(tuple(shape), dtype=torch.bfloat16, device=self.device)
+        if name.endswith(".bias"):
+            return self._randn(name, shape)
+        return self._randn(name, shape)
+
+    def get_expert(self, name: str, e: int, shape) -> torch.Tensor:
+        return self._randn(f"{name}#{e}", shape)
+
+
+def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0,
+                  ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None) -> ModelWeights:
+    """Assemble ``ModelWeights`` in format ``fmt`` from a tensor source that answers GGUF tensor names
+    (``RandomSource``, ``loader.GGUFSource``, ``loader.SafetensorsSource``).
+
+    TP shards attention and the dense FFN Megatron style (q/k/v/gate/up by rows, o/down by columns; KV heads are
+    replicated when ``n_kv_heads < tp_size``), EP keeps the experts ``[ep_rank * E/ep_size, (ep_rank+1) * E/ep_size)``."""
     h, d = cfg.hidden, cfg.head_dim
+    dev = torch.device(device)
     assert cfg.n_heads % tp_size == 0, "n_heads must divide by the TP size"
     hq_l = cfg.n_heads // tp_size
     if cfg.n_kv_heads >= tp_size:
@@ -156,45 +176,48 @@ def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: 
         assert tp_size % cfg.n_kv_heads == 0
         hkv_l = 1
         kv_lo = tp_rank // (tp_size // cfg.n_kv_heads)
+    q0, q1 = tp_rank * hq_l * d, (tp_rank + 1) * hq_l * d
+    k0, k1 = kv_lo * d, (kv_lo + hkv_l) * d
+
+    def mv(t):
+        return t.to(dev)
+
     layers: List[LayerWeights] = []
     nl = n_layers if n_layers is not None else cfg.n_layers
     for li in range(nl):
-        wq = _randn((cfg.q_dim, h), _seed(seed, li, 1), device)[tp_rank * hq_l * d:(tp_rank + 1) * hq_l * d]
-        wk = _randn((cfg.kv_dim, h), _seed(seed, li, 2), device)[kv_lo * d:(kv_lo + hkv_l) * d]
-        wv = _randn((cfg.kv_dim, h), _seed(seed, li, 3), device)[kv_lo * d:(kv_lo + hkv_l) * d]
-        wo = _randn((h, cfg.q_dim), _seed(seed, li, 4), device)[:, tp_rank * hq_l * d:(tp_rank + 1) * hq_l * d]
+        pre = f"blk.{li}."
+        wq = src.get(pre + "attn_q.weight", (cfg.q_dim, h))[q0:q1]
+        wk = src.get(pre + "attn_k.weight", (cfg.kv_dim, h))[k0:k1]
+        wv = src.get(pre + "attn_v.weight", (cfg.kv_dim, h))[k0:k1]
+        wo = src.get(pre + "attn_output.weight", (h, cfg.q_dim))[:, q0:q1]
         bias = None
         if cfg.qkv_bias:
-            bq = _randn((cfg.q_dim,), _seed(seed, li, 20), device).float()[tp_rank * hq_l * d:(tp_rank + 1) * hq_l * d]
-            bk = _randn((cfg.kv_dim,), _seed(seed, li, 21), device).float()[kv_lo * d:(kv_lo + hkv_l) * d]
-            bv = _randn((cfg.kv_dim,), _seed(seed, li, 22), device).float()[kv_lo * d:(kv_lo + hkv_l) * d]
-            bias = torch.cat([bq, bk, bv]).contiguous()
+            bias = torch.cat([src.get(pre + "attn_q.bias", (cfg.q_dim,))[q0:q1].float(), src.get(pre + "attn_k.bias", (cfg.kv_dim,))[k0:k1].float(),
+                              src.get(pre + "attn_v.bias", (cfg.kv_dim,))[k0:k1].float()]).contiguous()
+            bias = mv(bias)
         lw = LayerWeights(
-            attn_norm=torch.ones(h, dtype=torch.bfloat16, device=device),
-            wqkv=make_linear(torch.cat([wq, wk, wv]), fmt, bias=bias),
-            wo=make_linear(wo.contiguous(), fmt),
-            ffn_norm=torch.ones(h, dtype=torch.bfloat16, device=device),
-            q_norm=torch.ones(d, dtype=torch.bfloat16, device=device) if cfg.qk_norm else None,
-            k_norm=torch.ones(d, dtype=torch.bfloat16, device=device) if cfg.qk_norm else None,
+            attn_norm=mv(src.get(pre + "attn_norm.weight", (h,)).to(torch.bfloat16)),
+            wqkv=make_linear(mv(torch.cat([wq, wk, wv])), fmt, bias=bias),
+            wo=make_linear(mv(wo.contiguous()), fmt),
+            ffn_norm=mv(src.get(pre + "ffn_norm.weight", (h,)).to(torch.bfloat16)),
+            q_norm=mv(src.get(pre + "attn_q_norm.weight", (d,)).to(torch.bfloat16)) if cfg.qk_norm else None,
+            k_norm=mv(src.get(pre + "attn_k_norm.weight", (d,)).to(torch.bfloat16)) if cfg.qk_norm else None,
         )
         del wq, wk, wv, wo
         if cfg.is_moe:
             e, inter = cfg.n_experts, cfg.expert_ffn
             assert e % ep_size == 0
             e_l = e // ep_size
-            lw.router = _randn((e, h), _seed(seed, li, 5), device)
+            lw.router = mv(src.get(pre + "ffn_gate_inp.weight", (e, h)).to(torch.bfloat16))
             if cfg.router == "sigmoid":
-                lw.router_bias = torch.zeros(e, dtype=torch.float32, device=device)
-            # every expert has its own seed, so an expert-parallel shard is bit-identical to a slice of the full model
-            w13 = torch.empty((e_l * 2 * inter, h), dtype=torch.bfloat16, device=device)
-            w2 = torch.empty((e_l * h, inter), dtype=torch.bfloat16, device=device)
-            gen = torch.Generator(device=device)
+                lw.router_bias = torch.zeros(e, dtype=torch.float32, device=dev)
+            w13 = torch.empty((e_l * 2 * inter, h), dtype=torch.bfloat16, device=dev)
+            w2 = torch.empty((e_l * h, inter), dtype=torch.bfloat16, device=dev)
             for j in range(e_l):
                 ge = ep_rank * e_l + j
-                gen.manual_seed(_seed(seed, li, 1000 + 2 * ge))
-                w13[j * 2 * inter:(j + 1) * 2 * inter] = torch.randn((2 * inter, h), generator=gen, device=device, dtype=torch.float32).mul_(0.02)
-                gen.manual_seed(_seed(seed, li, 1001 + 2 * ge))
-                w2[j * h:(j + 1) * h] = torch.randn((h, inter), generator=gen, device=device, dtype=torch.float32).mul_(0.02)
+                w13[j * 2 * inter: j * 2 * inter + inter] = mv(src.get_expert(pre + "ffn_gate_exps.weight", ge, (inter, h)))
+                w13[j * 2 * inter + inter:(j + 1) * 2 * inter] = mv(src.get_expert(pre + "ffn_up_exps.weight", ge, (inter, h)))
+                w2[j * h:(j + 1) * h] = mv(src.get_expert(pre + "ffn_down_exps.weight", ge, (h, inter)))
             lw.w13 = make_linear(w13, fmt, groups=e_l)
             lw.w2 = make_linear(w2, fmt, groups=e_l)
             del w13, w2
@@ -202,22 +225,28 @@ def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: 
             f = cfg.ffn
             assert f % tp_size == 0
             f_l = f // tp_size
-            wg = _randn((f, h), _seed(seed, li, 8), device)[tp_rank * f_l:(tp_rank + 1) * f_l]
-            wu = _randn((f, h), _seed(seed, li, 9), device)[tp_rank * f_l:(tp_rank + 1) * f_l]
-            wd = _randn((h, f), _seed(seed, li, 10), device)[:, tp_rank * f_l:(tp_rank + 1) * f_l]
-            lw.w_gate_up = make_linear(torch.cat([wg, wu]), fmt)
-            lw.w_down = make_linear(wd.contiguous(), fmt)
+            f0, f1 = tp_rank * f_l, (tp_rank + 1) * f_l
+            wg = src.get(pre + "ffn_gate.weight", (f, h))[f0:f1]
+            wu = src.get(pre + "ffn_up.weight", (f, h))[f0:f1]
+            wd = src.get(pre + "ffn_down.weight", (h, f))[:, f0:f1]
+            lw.w_gate_up = make_linear(mv(torch.cat([wg, wu])), fmt)
+            lw.w_down = make_linear(mv(wd.contiguous()), fmt)
             del wg, wu, wd
         layers.append(lw)
-    embed = _randn((cfg.vocab, h), _seed(seed, 9999, 1), device)
-    if cfg.tie_embeddings:
+    embed = mv(src.get("token_embd.weight", (cfg.vocab, h)).to(torch.bfloat16))
+    if cfg.tie_embeddings or not src.has("output.weight"):
         head_full = embed
     else:
-        head_full = _randn((cfg.vocab, h), _seed(seed, 9999, 2), device)
+        head_full = mv(src.get("output.weight", (cfg.vocab, h)).to(torch.bfloat16))
     v0, v1 = (0, cfg.vocab)
     if shard_vocab and tp_size > 1:
         v0, v1 = shard_range(cfg.vocab, tp_size, tp_rank)
     lm_head = make_linear(head_full[v0:v1].contiguous() if (v0, v1) != (0, cfg.vocab) else head_full, "bf16")
-    return ModelWeights(cfg=cfg, embed=embed, layers=layers, final_norm=torch.ones(h, dtype=torch.bfloat16, device=device),
-                        lm_head=lm_head, fmt=fmt, tp_rank=tp_rank, tp_size=tp_size, ep_rank=ep_rank, ep_size=ep_size,
-                        vocab_start=v0)
+    return ModelWeights(cfg=cfg, embed=embed, layers=layers, final_norm=mv(src.get("output_norm.weight", (h,)).to(torch.bfloat16)),
+                        lm_head=lm_head, fmt=fmt, tp_rank=tp_rank, tp_size=tp_size, ep_rank=ep_rank, ep_size=ep_size, vocab_start=v0)
+
+
+def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
+                      ep_rank: int = 0, ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None) -> ModelWeights:
+    """Random-init weights of ``cfg`` (generated on ``device``) in format ``fmt``."""
+    return build_weights(cfg, RandomSource(cfg, seed, device), fmt, device, tp_rank, tp_size, ep_rank, ep_size, shard_vocab, n_layers)

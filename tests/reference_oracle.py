@@ -49,3 +49,20 @@ def tokenizer_lib():
     lib.bpe_tokenize.restype = ctypes.c_int
     lib.bpe_tokenize.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int]
     return lib
+
+
+def engine_lib():
+    """ctypes handle exposing the reference CPU engine (gguf_open, transformer_load, transformer_forward_logits, ...)."""
+    src = ('#define GGUF_LOADER_IMPLEMENTATION\n#include "gguf_loader.h"\n#define GGML_DEQUANT_IMPLEMENTATION\n#include "ggml_dequant.h"\n'
+           '#define TRANSFORMER_IMPLEMENTATION\n#include "transformer.h"\n'
+           'int ref_n_vocab(transformer_model *m) { return m->n_vocab; }\n')
+    lib = _build("ref_engine", src)
+    lib.gguf_open.restype = ctypes.c_void_p
+    lib.gguf_open.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    lib.transformer_load.restype = ctypes.c_void_p
+    lib.transformer_load.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.transformer_forward_logits.restype = ctypes.POINTER(ctypes.c_float)
+    lib.transformer_forward_logits.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int]
+    lib.transformer_set_f64_accum.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.ref_n_vocab.argtypes = [ctypes.c_void_p]
+    return lib

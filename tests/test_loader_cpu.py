@@ -1,0 +1,88 @@
+"""Checkpoint round trips (GGUF in several ggml types, HF safetensors incl. MXFP8) and parity of our engine with the
+reference CPU engine on a GGUF file written by our writer."""
+import numpy as np
+import pytest
+import torch
+
+from gemm_b200.models import loader, reference
+from gemm_b200.models.config import get_config
+from gemm_b200.models.transformer import ForwardBatch, KvCache, Transformer
+from gemm_b200.models.weights import RandomSource, build_weights
+from tests import reference_oracle as oracle
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("name,wtype,tol", [("tiny-dense", "F16", 2e-3), ("tiny-moe", "Q8_0", 2e-2), ("tiny-qwen2", "Q4_K", 0.2), ("tiny-dense", "BF16", 1e-6)])
+def test_gguf_checkpoint_roundtrip(tmp_path, name, wtype, tol):
+    cfg = get_config(name)
+    src = RandomSource(cfg, seed=3)
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, src, path, wtype)
+    w = loader.load_gguf(path, "bf16", device="cpu")
+    w0 = build_weights(cfg, src, "bf16", device="cpu")
+    assert w.cfg.n_layers == cfg.n_layers and w.cfg.hidden == cfg.hidden and w.cfg.n_experts == cfg.n_experts and w.cfg.qk_norm == cfg.qk_norm
+    assert w.cfg.qkv_bias == cfg.qkv_bias and w.cfg.tie_embeddings == cfg.tie_embeddings
+    for a, b in zip(w.layers, w0.layers):
+        assert _rel(a.wqkv.w, b.wqkv.w) <= tol
+        if cfg.is_moe:
+            assert _rel(a.w13.w, b.w13.w) <= tol and _rel(a.w2.w, b.w2.w) <= tol and torch.equal(a.router, b.router)
+        else:
+            assert _rel(a.w_down.w, b.w_down.w) <= tol
+    toks = torch.randint(0, cfg.vocab, (12,))
+    assert _rel(reference.reference_logits(w, toks), reference.reference_logits(w0, toks)) <= max(10 * tol, 1e-5)
+
+
+@pytest.mark.parametrize("mx", [False, True])
+def test_hf_safetensors_roundtrip(tmp_path, mx):
+    cfg = get_config("tiny-moe")
+    src = RandomSource(cfg, seed=4)
+    d = str(tmp_path / "hf")
+    loader.save_hf_checkpoint(cfg, src, d, mxfp8=mx)
+    cfg2 = loader.config_from_hf(d)
+    assert cfg2.n_experts == cfg.n_experts and cfg2.arch == "qwen3moe" and cfg2.head_dim == cfg.head_dim
+    w = loader.load_safetensors(d, "bf16", device="cpu")
+    w0 = build_weights(cfg, src, "bf16", device="cpu")
+    tol = 0.05 if mx else 1e-6
+    assert _rel(w.layers[0].wqkv.w, w0.layers[0].wqkv.w) <= tol and _rel(w.layers[1].w13.w, w0.layers[1].w13.w) <= tol
+    assert torch.equal(w.embed, w0.embed)
+    if mx:
+        # an MXFP8 checkpoint loaded straight into the MXFP8 run-time format reproduces the stored values exactly
+        wm = loader.load_safetensors(d, "mxfp8", device="cpu")
+        assert _rel(wm.layers[0].wo.dequantized(), w.layers[0].wo.w.float()) < 1e-6
+
+
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not present")
+@pytest.mark.parametrize("name,wtype", [("tiny-dense", "Q8_0"), ("tiny-moe", "F16"), ("tiny-qwen2", "Q4_K")])
+def test_engine_matches_reference_cpu_engine(tmp_path, name, wtype):
+    """The reference's own transformer.h loads the GGUF our writer produced and runs it token by token; our engine
+    (loading the same file) must give the same logits up to bf16 rounding of activations."""
+    cfg = get_config(name)
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=5), path, wtype)
+    ref = oracle.engine_lib()
+    g = ref.gguf_open(path.encode(), 1)
+    assert g
+    m = ref.transformer_load(g, 256)
+    assert m, "the reference engine refused our GGUF file"
+    ref.transformer_set_f64_accum(m, 1)
+    assert ref.ref_n_vocab(m) == cfg.vocab
+    torch.manual_seed(0)
+    toks = torch.randint(0, cfg.vocab, (20,))
+    ref_logits = []
+    for pos, t in enumerate(toks.tolist()):
+        p = ref.transformer_forward_logits(m, t, pos)
+        ref_logits.append(torch.from_numpy(np.ctypeslib.as_array(p, shape=(cfg.vocab,)).copy()))
+    w = loader.load_gguf(path, "bf16", device="cpu")
+    # fp32 oracle on the loaded weights == the reference arithmetic
+    ours32 = reference.reference_logits(w, toks)
+    assert _rel(ours32[-1], ref_logits[-1]) < 5e-3 and _rel(ours32[5], ref_logits[5]) < 5e-3
+    # the paged engine (bf16 activations)
+    model = Transformer(w, KvCache.allocate(cfg, 8, 16, "cpu"))
+    bt = torch.tensor([[3, 1, 0, 2]], dtype=torch.int32)
+    fb = ForwardBatch.build([20], [0], toks, bt, 16, cfg.n_heads, cfg.n_kv_heads, "cpu", all_logits=True)
+    ours = model.forward(fb)
+    assert _rel(ours[-1], ref_logits[-1]) < 3e-2
+    assert int(ours[-1].argmax()) == int(ref_logits[-1].argmax()) or _rel(ours[-1], ref_logits[-1]) < 1e-2
