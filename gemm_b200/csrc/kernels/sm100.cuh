@@ -54,7 +54,7 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 // Default budgets.  An mbarrier inside one CTA should flip within microseconds; one second
 // means something is broken.  Waits on a peer GPU tolerate launch skew between ranks.
 constexpr uint64_t kMbarBudgetNs = 2ull * 1000 * 1000 * 1000;
-constexpr uint64_t kPeerBudgetNs = 4ull * 1000 * 1000 * 1000;
+constexpr uint64_t kPeerBudgetNs = 2ull * 1000 * 1000 * 1000;
 
 // ---------------------------------------------------------------------------------------------
 // Small helpers

@@ -74,7 +74,7 @@ class ExpertParallel:
 
     def _bucket(self, t: int) -> dict:
         """Buffer geometry for a forward pass of ``t`` tokens (rounded up so that all ranks agree)."""
-        for cap in (8, 64, 1024, self.max_tokens):
+        for cap in sorted({min(c, self.max_tokens) for c in (8, 64, 1024, self.max_tokens)}):
             if t <= cap:
                 break
         else:

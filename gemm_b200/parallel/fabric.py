@@ -83,6 +83,8 @@ class Fabric:
     def view(self, off: int, shape, dtype) -> torch.Tensor:
         """Tensor view of this rank's part of a symmetric sub-buffer."""
         n = int(torch.tensor(shape).prod().item()) * torch.empty(0, dtype=dtype).element_size()
+        if off < 0 or off + n > self.heap_bytes:
+            raise IndexError(f"view [{off}, {off + n}) leaves the symmetric heap of {self.heap_bytes} bytes")
         return self._heap_t[off:off + n].view(dtype).view(*shape)
 
     def peer_ptr(self, rank: int, off: int) -> int:

@@ -90,9 +90,9 @@ def run_model(model, cfg, toks, page, dev):
 def check_expert_parallel(rank, world, dev, fmt, fused):
     cfg = get_config("tiny-moe")
     page = 16
-    g = torch.Generator().manual_seed(7)
-    all_toks = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (40, 90, 33, 70, 52, 64, 48, 81)][: 2 * world]
-    mine = all_toks[rank * 2: rank * 2 + 2]
+    # every rank gets sequences of the same lengths (the NCCL baseline gathers equal token counts) with its own content
+    g = torch.Generator().manual_seed(7 + rank)
+    mine = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (40, 90)]
     w_full = synthetic_weights(cfg, fmt, device=dev, seed=5)
     w_ep = synthetic_weights(cfg, fmt, device=dev, seed=5, ep_rank=rank, ep_size=world)
     ref_model = Transformer(w_full, KvCache.allocate(cfg, 64, page, dev))

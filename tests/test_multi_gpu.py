@@ -15,7 +15,7 @@ def _launch(what: str, nproc: int, port: int):
     env.setdefault("NCCL_NVLS_ENABLE", "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(HERE, "multi_gpu_worker.py"), what]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     if r.returncode != 0:
         log_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")
         if os.path.isdir(log_dir):
