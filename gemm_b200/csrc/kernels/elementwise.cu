@@ -9,6 +9,7 @@
 // (RMSNorm), :1281-1315 (QK-norm) and :1183-1219 (NeoX RoPE, inv_freq = base^(-2j/d)).
 #include "sm100.cuh"
 #include "host_common.h"
+#include <algorithm>
 
 namespace gb {
 
@@ -259,6 +260,36 @@ mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ sr
   if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, k >> 7, sf32)] = (uint8_t)e;
 }
 
+// Gathering variant, one warp per output row: padding rows (source < 0) are skipped after one load, so a mostly
+// empty expert-sorted buffer costs almost nothing.  Needs k % 256 == 0; the output must be pre-zeroed.
+__global__ void __launch_bounds__(256)
+mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src_rows, uint8_t* __restrict__ out_q,
+                     uint8_t* __restrict__ out_sf, long out_rows, int k, int ld_in, int sf32) {
+  const int lane = threadIdx.x & 31;
+  const long warp0 = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, n_warps = ((long)gridDim.x * blockDim.x) >> 5;
+  const int vec_per_row = k >> 3;
+  for (long r = warp0; r < out_rows; r += n_warps) {
+    const int src = src_rows[r];
+    if (src < 0) continue;
+    for (int vi = lane; vi < vec_per_row; vi += 32) {
+      float v[8];
+      load8(in + (size_t)src * ld_in + vi * 8, v);
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      const int e = e8m0_amax(amax);
+      const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+      uint8_t q[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(v[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
+      *reinterpret_cast<uint2*>(out_q + r * k + vi * 8) = *reinterpret_cast<uint2*>(q);
+      if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, k >> 7, sf32)] = (uint8_t)e;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------ casts
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -344,6 +375,12 @@ GB_API int gb_mx_quant(const void* in, const int* src_rows, void* out_q, void* o
   if (k % 128) return fail("mx_quant: k %% 128 != 0%s");
   const long n = out_rows * (k / 8);
   if (n <= 0) return 0;
+  if (src_rows != nullptr && k % 256 == 0) {
+    const long blocks = std::min<long>((out_rows + 7) / 8, (long)sm_count() * 16);
+    mx_quant_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
+    GB_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   mx_quant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;

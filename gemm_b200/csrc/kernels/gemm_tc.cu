@@ -60,9 +60,19 @@ struct GemmArgs {
   uint32_t* signal_flags[kMaxRanks];  // after the last tile of the grid: *signal_flags[p] = *epoch_ptr (release, system scope)
   int signal_n;
   unsigned* done_ctr;
+  // ---- split-K (plain GEMMs with few tiles): `splits` CTAs share one output tile, each reduces a K range into a
+  // fp32 partial in sk_ws; the warp that arrives last at the tile's semaphore sums the partials in split order
+  // (deterministic) and runs the normal epilogue.
+  int splits;
+  float* sk_ws;                    // [tiles][splits][NA * TN][128] fp32
+  unsigned* sk_ctr;                // [tiles][4] self-resetting arrival counters (one per epilogue warp)
+  // ---- arg-max epilogue: instead of storing the result, every epilogue warp writes the maximum of its 32 output
+  // features and its feature index per token: amax_val / amax_idx [ceil(n_out/128) * 4][m_tok]
+  float* amax_val;
+  int* amax_idx;
 };
 
-struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; };
+struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; int ks; int tile_id; };
 
 // Maps the linear tile index of the persistent loop to a tile.  Every warp role walks the same
 // sequence, so each keeps its own cursor.  n-blocks vary fastest: CTAs that run at the same time
@@ -74,8 +84,10 @@ struct TileCursor {
     const int n_blocks = (a.n_out + 127) >> 7;
     if (a.num_groups == 0) {
       const int tok_blocks = (a.m_tok + TN - 1) / TN;
-      if (t >= n_blocks * tok_blocks) return false;
-      const int nb = t % n_blocks, tb = t / n_blocks;
+      const int sp = a.splits > 1 ? a.splits : 1;
+      if (t >= n_blocks * tok_blocks * sp) return false;
+      o.ks = t % sp; o.tile_id = t / sp;
+      const int nb = o.tile_id % n_blocks, tb = o.tile_id / n_blocks;
       o.n0 = nb * 128; o.w_row0 = o.n0; o.w_row1 = a.up_row_offset + o.n0;
       o.x_row0 = tb * TN; o.valid = min(TN, a.m_tok - o.x_row0); o.out_row0 = o.x_row0;
       return true;
@@ -90,7 +102,7 @@ struct TileCursor {
         o.w_row1 = o.w_row0 + a.up_row_offset;
         o.x_row0 = s_start[g] + tb * TN;
         o.valid = min(TN, s_count[g] - tb * TN);
-        o.out_row0 = o.x_row0;
+        o.out_row0 = o.x_row0; o.ks = 0; o.tile_id = t;
         return true;
       }
       base += tiles_g; ++g;
@@ -143,6 +155,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (args.k + KB_ELEMS - 1) / KB_ELEMS;
+  const int kb_per = (args.splits > 1) ? (num_kb + args.splits - 1) / args.splits : num_kb;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -182,7 +195,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0; uint32_t ph = 0;
       bool ok = true;
       for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = t.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 100, s)) { ok = false; break; }
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], NA * A_BYTES + B_BYTES + ((MODE == 1) ? (NA + SFB_ATOMS) * 512 : 0));
@@ -220,7 +234,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         if (!mbar_wait(&acce_bar[acc], acc_ph ^ 1, abort_flag, args.status, 200, acc)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + acc * ACC_COLS;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = t.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, args.status, 201, s)) { ok = false; break; }
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -238,7 +253,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           for (int j = 0; j < 4; ++j) {
             const uint64_t a0 = make_sdesc_sw128(st + j * 32);
             const uint64_t b = make_sdesc_sw128(st + NA * A_BYTES + j * 32);
-            const uint32_t accum = (kb > 0 || j > 0) ? 1u : 0u;
+            const uint32_t accum = (kb > kb0 || j > 0) ? 1u : 0u;
             if (MODE == 0) {
               constexpr uint32_t idesc = make_idesc(128, TN, 1, 1);
               mma_f16_ss(d0, a0, b, idesc, accum);
@@ -271,13 +286,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const int n = t.n0 + row;
       const bool n_ok = n < args.n_out;
       const float bias = (args.bias != nullptr && n_ok) ? args.bias[n] : 0.0f;
-#pragma unroll 1
-      for (int c = 0; c < TN; c += 16) {
-        uint32_t r0[16], r1[16];
-        tmem_ld_x16(tacc + c, r0);
-        if (DUAL) tmem_ld_x16(tacc + TN + c, r1);
-        tc_wait_ld();
-        if (c >= t.valid) continue;             // uniform across the CTA's epilogue warps
+      // Everything after the accumulators are in registers: activation, bias, then one of the store forms.
+      auto finish_chunk = [&](int c, const uint32_t* r0, const uint32_t* r1) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int xr = c + j;
@@ -302,6 +312,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 else args.out_sf[((size_t)(x_row >> 7) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + ((x_row >> 5) & 3) * 4 + q] = (uint8_t)e;
               }
             }
+          } else if (args.amax_val != nullptr) {
+            // order-preserving integer image of the float, so that one redux gives the warp maximum; ties -> lowest feature
+            float vv = (n_ok && v == v) ? v : -3.4e38f;
+            uint32_t key = __float_as_uint(vv);
+            key = (key & 0x80000000u) ? ~key : (key | 0x80000000u);
+            const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
+            const uint32_t who = __ballot_sync(0xffffffffu, key == kmax);
+            if (live && lane == (int)__ffs(who) - 1) {
+              const size_t slot = (size_t)((t.n0 >> 7) * 4 + q) * args.m_tok + x_row;
+              args.amax_val[slot] = vv; args.amax_idx[slot] = n;
+            }
           } else if (live && n_ok) {
             int orow = x_row;
             void* obase = args.out;
@@ -318,6 +339,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             }
           }
         }
+      };
+      if (args.splits > 1) {
+        // ---- split-K: park the partial, the last warp to arrive reduces
+        float* ws = args.sk_ws + ((size_t)t.tile_id * args.splits) * (size_t)(NA * TN * 128);
+        float* mine = ws + (size_t)t.ks * (NA * TN * 128);
+#pragma unroll 1
+        for (int c = 0; c < TN; c += 16) {
+          uint32_t r0[16], r1[16];
+          tmem_ld_x16(tacc + c, r0);
+          if (DUAL) tmem_ld_x16(tacc + TN + c, r1);
+          tc_wait_ld();
+          if (c >= t.valid) continue;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            mine[(size_t)(c + j) * 128 + row] = __uint_as_float(r0[j]);
+            if (DUAL) mine[(size_t)(TN + c + j) * 128 + row] = __uint_as_float(r1[j]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acce_bar[acc]);        // TMEM buffer is free again
+        __threadfence();
+        unsigned old = 0;
+        if (lane == 0) old = atomicAdd(&args.sk_ctr[(size_t)t.tile_id * 4 + q], 1u);
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old == (unsigned)args.splits - 1) {
+          if (lane == 0) args.sk_ctr[(size_t)t.tile_id * 4 + q] = 0;
+          __threadfence();
+#pragma unroll 1
+          for (int c = 0; c < TN && c < t.valid; c += 16) {
+            uint32_t r0[16], r1[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float a0 = 0.f, a1 = 0.f;
+              for (int sidx = 0; sidx < args.splits; ++sidx) {
+                const float* src = ws + (size_t)sidx * (NA * TN * 128);
+                a0 += __ldcg(src + (size_t)(c + j) * 128 + row);
+                if (DUAL) a1 += __ldcg(src + (size_t)(TN + c + j) * 128 + row);
+              }
+              r0[j] = __float_as_uint(a0); r1[j] = __float_as_uint(a1);
+            }
+            finish_chunk(c, r0, r1);
+          }
+        }
+        if (NACC == 2) { if (++acc == 2) { acc = 0; acc_ph ^= 1; } } else { acc_ph ^= 1; }
+        continue;
+      }
+#pragma unroll 1
+      for (int c = 0; c < TN; c += 16) {
+        uint32_t r0[16], r1[16];
+        tmem_ld_x16(tacc + c, r0);
+        if (DUAL) tmem_ld_x16(tacc + TN + c, r1);
+        tc_wait_ld();
+        if (c >= t.valid) continue;             // uniform across the CTA's epilogue warps
+        finish_chunk(c, r0, r1);
       }
       tc_fence_before();
       __syncwarp();
@@ -387,6 +463,14 @@ struct GemmExtras {
   int signal_n;
   int pad;
   unsigned* done_ctr;
+  int splits;
+  int pad2;
+  float* sk_ws;
+  unsigned* sk_ctr;
+  float* amax_val;
+  int* amax_idx;
+  long sk_ws_bytes;          // capacity of sk_ws
+  long sk_ctr_count;         // capacity of sk_ctr (entries)
 };
 
 // Flags of gb_gemm.
@@ -433,12 +517,22 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
     a.w_group_mod = ex->w_group_mod; a.wait_flags = ex->wait_flags; a.wait_n = ex->wait_n; a.epoch_ptr = ex->epoch_ptr;
     for (int i = 0; i < kMaxRanks; ++i) { a.peer_out[i] = ex->peer_out[i]; a.signal_flags[i] = ex->signal_flags[i]; }
     a.peer_region_rows = ex->peer_region_rows; a.peer_rank = ex->peer_rank; a.signal_n = ex->signal_n; a.done_ctr = ex->done_ctr;
-    if (a.w_group_mod > 0) {
-      // the tensor map of W must cover the experts only
+    a.amax_val = ex->amax_val; a.amax_idx = ex->amax_idx;
+    if (ex->splits > 1 && num_groups == 0) {
+      const int kb_elems = mx ? 128 : 64;
+      const int num_kb = (k + kb_elems - 1) / kb_elems;
+      int sp = ex->splits < num_kb ? ex->splits : num_kb;
+      const int kb_per = (num_kb + sp - 1) / sp;
+      sp = (num_kb + kb_per - 1) / kb_per;                    // no empty split
+      const long tiles = (long)((n_out + 127) / 128) * ((m_tok + tn - 1) / tn);
+      const long need = tiles * sp * (dual ? 2 : 1) * tn * 128 * 4;
+      if (sp > 1 && ex->sk_ws != nullptr && need <= ex->sk_ws_bytes && tiles * 4 <= ex->sk_ctr_count) {
+        a.splits = sp; a.sk_ws = ex->sk_ws; a.sk_ctr = ex->sk_ctr;
+      }
     }
   }
   int max_tiles = 0;
-  if (num_groups == 0) max_tiles = ((n_out + 127) / 128) * ((m_tok + tn - 1) / tn);
+  if (num_groups == 0) max_tiles = ((n_out + 127) / 128) * ((m_tok + tn - 1) / tn) * (a.splits > 1 ? a.splits : 1);
   if (num_groups == 0 && m_tok <= 0) return 0;
 
 #define GB_DISPATCH(TNV)                                                                                      \

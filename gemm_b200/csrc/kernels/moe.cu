@@ -128,16 +128,21 @@ __global__ void __launch_bounds__(512)
 moe_seg_kernel(const int* __restrict__ seg_count, int* __restrict__ seg_start, int* __restrict__ region_rows_used,
                int n_exp, int experts_per_region, int region_rows, int align, unsigned* epoch_ctr) {
   const int r = threadIdx.x;
+  __shared__ int cnt[512], start[512];
   if (r == 0 && epoch_ctr != nullptr) *epoch_ctr = *epoch_ctr + 1;     // one tick per MoE layer call (expert-parallel epoch)
+  if (r < n_exp) cnt[r] = seg_count[r];
+  __syncthreads();
   if (r < n_exp / experts_per_region) {
     int pos = 0;
     for (int i = 0; i < experts_per_region; ++i) {
       const int ee = r * experts_per_region + i;
-      seg_start[ee] = r * region_rows + pos;
-      pos += (seg_count[ee] + align - 1) / align * align;
+      start[ee] = r * region_rows + pos;
+      pos += (cnt[ee] + align - 1) / align * align;
     }
     if (region_rows_used != nullptr) region_rows_used[r] = pos;
   }
+  __syncthreads();
+  if (r < n_exp) seg_start[r] = start[r];
 }
 
 __global__ void __launch_bounds__(kPlanBlock)

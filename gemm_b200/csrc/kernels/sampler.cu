@@ -44,6 +44,46 @@ argmax_kernel(const T* __restrict__ logits, int* __restrict__ out_idx, float* __
   }
 }
 
+// Final step of the arg-max fused into the LM-head GEMM: reduce [parts][rows] (value, index) pairs per row.
+__global__ void __launch_bounds__(256)
+argmax_pairs_kernel(const float* __restrict__ val, const int* __restrict__ idx, int* __restrict__ out_idx, float* __restrict__ out_val,
+                    int parts, int rows, int idx_offset) {
+  const int r = blockIdx.x;
+  float bv = -FLT_MAX; int bi = 0x7fffffff;
+  for (int p = threadIdx.x; p < parts; p += blockDim.x) better(bv, bi, val[(size_t)p * rows + r], idx[(size_t)p * rows + r]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  __shared__ float sv[8]; __shared__ int si[8];
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) better(bv, bi, sv[w], si[w]);
+    out_idx[r] = bi + idx_offset;
+    if (out_val) out_val[r] = bv;
+  }
+}
+
+// Two-stage arg-max for wide rows: stage 1 covers a row with `chunks` CTAs.
+template <typename T>
+__global__ void __launch_bounds__(256)
+argmax_chunk_kernel(const T* __restrict__ logits, float* __restrict__ pval, int* __restrict__ pidx, int vocab, long ld, int rows) {
+  const int r = blockIdx.y, c = blockIdx.x, chunks = gridDim.x;
+  const int per = (vocab + chunks - 1) / chunks;
+  const int i0 = c * per, i1 = min(vocab, i0 + per);
+  const T* row = logits + (size_t)r * ld;
+  float bv = -FLT_MAX; int bi = 0x7fffffff;
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) { float v = ld_logit(row, i); if (!(v == v)) v = -FLT_MAX; better(bv, bi, v, i); }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  __shared__ float sv[8]; __shared__ int si[8];
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) better(bv, bi, sv[w], si[w]);
+    pval[(size_t)c * rows + r] = bv; pidx[(size_t)c * rows + r] = bi;
+  }
+}
+
 // Counter-based generator: 64-bit mix of (seed, step, row) -> uniform in [0, 1).
 __device__ __forceinline__ float uniform01(uint64_t seed, uint64_t step, uint64_t row) {
   uint64_t z = seed + 0x9E3779B97F4A7C15ull * (step + 1) + 0xBF58476D1CE4E5B9ull * (row + 1);
@@ -155,6 +195,25 @@ GB_API int gb_argmax(const void* logits, int* out_idx, float* out_val, int rows,
   if (rows <= 0) return 0;
   if (dtype == 0) argmax_kernel<float><<<rows, 1024, 0, stream>>>((const float*)logits, out_idx, out_val, vocab, ld, idx_offset);
   else argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, out_idx, out_val, vocab, ld, idx_offset);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_argmax_pairs(const float* val, const int* idx, int* out_idx, float* out_val, int parts, int rows, int idx_offset, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  argmax_pairs_kernel<<<rows, 256, 0, stream>>>(val, idx, out_idx, out_val, parts, rows, idx_offset);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Wide-row arg-max in two stages; pval / pidx are scratch of chunks * rows entries.
+GB_API int gb_argmax2(const void* logits, int* out_idx, float* out_val, float* pval, int* pidx, int rows, int vocab, long ld, int dtype,
+                      int idx_offset, int chunks, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  dim3 grid(chunks, rows);
+  if (dtype == 0) argmax_chunk_kernel<float><<<grid, 256, 0, stream>>>((const float*)logits, pval, pidx, vocab, ld, rows);
+  else argmax_chunk_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)logits, pval, pidx, vocab, ld, rows);
+  argmax_pairs_kernel<<<rows, 256, 0, stream>>>(pval, pidx, out_idx, out_val, chunks, rows, idx_offset);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

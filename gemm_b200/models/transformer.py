@@ -215,15 +215,22 @@ class Transformer:
         x = self.forward_hidden(fb)
         return self.head(x, fb)
 
-    def head(self, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+    def _head_input(self, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         delta = self._last_delta
         rows = fb.logit_rows
         xr = x[rows]
         if delta is not None:
             xr = (xr.float() + delta[rows].float()).to(torch.bfloat16)
-        hn = ew.rmsnorm(xr.contiguous(), w.final_norm, cfg.rms_eps)
-        return gemm.linear(hn, w.lm_head.w, out_dtype=torch.float32)
+        return ew.rmsnorm(xr.contiguous(), w.final_norm, cfg.rms_eps)
+
+    def head(self, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        return gemm.linear(self._head_input(x, fb), self.w.lm_head.w, out_dtype=torch.float32)
+
+    def forward_greedy(self, fb: ForwardBatch, want_value: bool = False):
+        """Greedy next tokens ``int32 [len(logit_rows)]``: the arg-max runs in the LM-head GEMM's epilogue, no logits are stored."""
+        x = self.forward_hidden(fb)
+        return gemm.linear_argmax(self._head_input(x, fb), self.w.lm_head.w, idx_offset=self.w.vocab_start, want_value=want_value)
 
     def final_hidden(self, x: torch.Tensor) -> torch.Tensor:
         """Residual stream with the pending delta folded in (what a pipeline stage hands to the next)."""

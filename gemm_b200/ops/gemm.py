@@ -23,7 +23,35 @@ class GemmExtras(ctypes.Structure):
     _fields_ = [("w_group_mod", ctypes.c_int), ("wait_n", ctypes.c_int), ("wait_flags", ctypes.c_void_p),
                 ("epoch_ptr", ctypes.c_void_p), ("peer_out", ctypes.c_void_p * 8), ("peer_region_rows", ctypes.c_int),
                 ("peer_rank", ctypes.c_int), ("signal_flags", ctypes.c_void_p * 8), ("signal_n", ctypes.c_int),
-                ("pad", ctypes.c_int), ("done_ctr", ctypes.c_void_p)]
+                ("pad", ctypes.c_int), ("done_ctr", ctypes.c_void_p), ("splits", ctypes.c_int), ("pad2", ctypes.c_int),
+                ("sk_ws", ctypes.c_void_p), ("sk_ctr", ctypes.c_void_p), ("amax_val", ctypes.c_void_p), ("amax_idx", ctypes.c_void_p),
+                ("sk_ws_bytes", ctypes.c_long), ("sk_ctr_count", ctypes.c_long)]
+
+
+_SK_WS_BYTES = 64 << 20
+_SK_CTR = 1 << 16
+_sk_state = {}
+
+
+def _splitk_extras(n_out: int, m_tok: int, k: int, tn: int, mx: bool, device) -> Optional["GemmExtras"]:
+    """Extras that turn on split-K when the plain tiling would leave most SMs idle (decode-sized GEMMs)."""
+    tiles = ((n_out + 127) // 128) * ((m_tok + tn - 1) // tn)
+    sms = 148
+    if tiles * 2 > sms:
+        return None
+    num_kb = (k + (127 if mx else 63)) // (128 if mx else 64)
+    splits = min(sms // tiles, num_kb // 2, 16)
+    if splits < 2:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    if key not in _sk_state:
+        _sk_state[key] = (torch.empty(_SK_WS_BYTES, dtype=torch.uint8, device=device), torch.zeros(_SK_CTR, dtype=torch.int32, device=device))
+    ws, ctr = _sk_state[key]
+    ex = GemmExtras()
+    ex.splits = splits
+    ex.sk_ws, ex.sk_ctr = ws.data_ptr(), ctr.data_ptr()
+    ex.sk_ws_bytes, ex.sk_ctr_count = _SK_WS_BYTES, _SK_CTR
+    return ex
 
 _c = ctypes.c_void_p
 _i = ctypes.c_int
@@ -76,8 +104,33 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=x.device)
     flags = GEMM_OUT_F32 if out.dtype == torch.float32 else 0
-    _launch(w, x, out, n, k, m, w.stride(0), x.stride(0), out.stride(0), flags, tn or pick_tn(m), bias=bias)
+    tn = tn or pick_tn(m)
+    _launch(w, x, out, n, k, m, w.stride(0), x.stride(0), out.stride(0), flags, tn, bias=bias,
+            extras=_splitk_extras(n, m, k, tn, False, x.device))
     return out
+
+
+def linear_argmax(x: torch.Tensor, w: torch.Tensor, idx_offset: int = 0, want_value: bool = False):
+    """Greedy sampling fused into the LM head: ``argmax_n (x W^T)[t, n]`` without ever writing the logits.  Returns int32 ``[M]``
+    (+ the winning values).  Ties resolve to the lower index."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not x.is_cuda:
+        y = torch.nan_to_num(x.float() @ w.float().t(), nan=-3.4e38)
+        val, idx = y.max(dim=-1)
+        idx = (idx + idx_offset).to(torch.int32)
+        return (idx, val) if want_value else idx
+    parts = ((n + 127) // 128) * 4
+    pv = torch.empty(parts, m, dtype=torch.float32, device=x.device)
+    pi = torch.empty(parts, m, dtype=torch.int32, device=x.device)
+    ex = GemmExtras()
+    ex.amax_val, ex.amax_idx = pv.data_ptr(), pi.data_ptr()
+    _launch(w, x, None, n, k, m, w.stride(0), x.stride(0), n, GEMM_OUT_F32, pick_tn(m), extras=ex)
+    out = torch.empty(m, dtype=torch.int32, device=x.device)
+    val = torch.empty(m, dtype=torch.float32, device=x.device) if want_value else None
+    rc = _native.cuda().gb_argmax_pairs(_p(pv), _p(pi), _p(out), _p(val), _i(parts), _i(m), _i(idx_offset), _stream())
+    _native.check(rc, "gb_argmax_pairs")
+    return (out, val) if want_value else out
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None,
@@ -109,8 +162,9 @@ def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_
         out = torch.empty(m, n, dtype=out_dtype, device=x.data.device)
     flags = GEMM_MX | (GEMM_OUT_F32 if out.dtype == torch.float32 else 0)
     assert w.sf_layout == 128
-    _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn or x.sf_layout, x_rows=x.data.shape[0],
-            sfa=w.sf, sfb=x.sf, bias=bias)
+    tn = tn or x.sf_layout
+    _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn, x_rows=x.data.shape[0],
+            sfa=w.sf, sfb=x.sf, bias=bias, extras=_splitk_extras(n, m, k, tn, True, x.data.device))
     return out
 
 

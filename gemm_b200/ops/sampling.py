@@ -31,9 +31,17 @@ def argmax(logits: torch.Tensor, idx_offset: int = 0, want_value: bool = False):
     out = torch.empty(b, dtype=torch.int32, device=logits.device)
     val = torch.empty(b, dtype=torch.float32, device=logits.device) if want_value else None
     dt = 0 if logits.dtype == torch.float32 else 1
-    rc = _native.cuda().gb_argmax(_p(logits), _p(out), _p(val), _i(b), _i(v), _l(logits.stride(0)), _i(dt), _i(idx_offset),
-                                  _c(torch.cuda.current_stream().cuda_stream))
-    _native.check(rc, "gb_argmax")
+    stream = _c(torch.cuda.current_stream().cuda_stream)
+    if v >= 16384:
+        chunks = max(1, min(64, 1184 // max(1, b)))
+        pv = torch.empty(chunks * b, dtype=torch.float32, device=logits.device)
+        pi = torch.empty(chunks * b, dtype=torch.int32, device=logits.device)
+        rc = _native.cuda().gb_argmax2(_p(logits), _p(out), _p(val), _p(pv), _p(pi), _i(b), _i(v), _l(logits.stride(0)), _i(dt),
+                                       _i(idx_offset), _i(chunks), stream)
+        _native.check(rc, "gb_argmax2", n=2)
+    else:
+        rc = _native.cuda().gb_argmax(_p(logits), _p(out), _p(val), _i(b), _i(v), _l(logits.stride(0)), _i(dt), _i(idx_offset), stream)
+        _native.check(rc, "gb_argmax")
     return (out, val) if want_value else out
 
 

@@ -190,8 +190,11 @@ class Engine:
         fb = ForwardBatch(ids=st["ids"], positions=st["positions"], slots=st["slots"], cu_q=st["cu_q"], kv_len=st["kv_len"],
                           block_table=st["block_table"], work=st["work"], logit_rows=st["rows"], num_splits=self._splits,
                           n_tokens=st["ids"].numel())
-        logits = self.model.forward(fb)
-        tok = self._sample(logits, self._sp, self.step_count)
+        if self._sp.temperature <= 0 and not hasattr(self.par, "merge_sampled"):
+            tok = self.model.forward_greedy(fb)
+        else:
+            logits = self.model.forward(fb)
+            tok = self._sample(logits, self._sp, self.step_count)
         st["tokens"].copy_(tok)
         st["ids"].copy_(tok)
         ew.decode_advance(st["positions"], st["kv_len"], st["slots"], st["block_table"], self.page_size)

@@ -109,3 +109,37 @@ def test_grouped(mx, tn):
         r = xf[s:s + c] @ wf[i].t()
         ref = torch.nn.functional.silu(r[:, :inter]) * r[:, inter:]
         assert _rel(y[s:s + c], ref) < 1e-2, f"group {i}"
+
+
+@pytest.mark.parametrize("m,n,k,mx", [(8, 5120, 2048, False), (64, 2048, 4096, False), (8, 5120, 2048, True), (64, 2048, 4096, True), (20, 128, 2048, False)])
+def test_split_k_small_batches(m, n, k, mx):
+    """Decode-sized GEMMs take the split-K path (few tiles, long K): same result, and bit-identical from run to run."""
+    torch.manual_seed(6)
+    x = torch.randn(m, k, device="cuda") * 0.5
+    w = torch.randn(n, k, device="cuda") * 0.05
+    if mx:
+        xq, wq = mxfp8.quantize(x, sf_layout=32 if m <= 32 else 128), mxfp8.quantize(w)
+        assert gemm._splitk_extras(n, m, k, xq.sf_layout, True, x.device) is not None
+        y1 = gemm.linear_mx(xq, wq, out_dtype=torch.float32)
+        y2 = gemm.linear_mx(xq, wq, out_dtype=torch.float32)
+        ref = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t()
+    else:
+        assert gemm._splitk_extras(n, m, k, gemm.pick_tn(m), False, x.device) is not None
+        y1 = gemm.linear(x.bfloat16(), w.bfloat16(), out_dtype=torch.float32)
+        y2 = gemm.linear(x.bfloat16(), w.bfloat16(), out_dtype=torch.float32)
+        ref = x.bfloat16().float() @ w.bfloat16().float().t()
+    _native.assert_status_ok()
+    assert torch.equal(y1, y2)
+    assert _rel(y1, ref) < 2e-3
+
+
+def test_linear_argmax_matches_logits_argmax():
+    torch.manual_seed(7)
+    m, n, k = 64, 151936, 256
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = torch.randn(n, k, device="cuda").bfloat16()
+    idx, val = gemm.linear_argmax(x, w, idx_offset=5, want_value=True)
+    logits = gemm.linear(x, w, out_dtype=torch.float32)
+    _native.assert_status_ok()
+    ref_val, ref_idx = logits.max(dim=-1)
+    assert torch.equal(idx.long() - 5, ref_idx) and torch.equal(val, ref_val)
