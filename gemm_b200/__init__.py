@@ -5,3 +5,16 @@ Layout:  ``ops`` (CUDA kernels + PyTorch references), ``models`` (Qwen2/3 dense,
 checkpoints), ``serve`` (engine, scheduler, HTTP front end).
 """
 __version__ = "0.1.0"
+
+
+def __getattr__(name):
+    if name == "LLM":
+        from .serve.llm import LLM
+        return LLM
+    if name == "SamplingParams":
+        from .serve.engine import SamplingParams
+        return SamplingParams
+    if name == "Engine":
+        from .serve.engine import Engine
+        return Engine
+    raise AttributeError(name)
