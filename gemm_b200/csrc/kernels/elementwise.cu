@@ -9,6 +9,7 @@
 // (RMSNorm), :1281-1315 (QK-norm) and :1183-1219 (NeoX RoPE, inv_freq = base^(-2j/d)).
 #include "sm100.cuh"
 #include "host_common.h"
+#include "../fabric/fabric.cuh"
 #include <algorithm>
 
 namespace gb {
@@ -59,9 +60,22 @@ template <int VPT>   // 8-element vectors per thread (hidden <= 256 * 8 * VPT)
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ delta, const __nv_bfloat16* __restrict__ x_in,
                const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ out_q,
-               uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out, int sf32) {
+               uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out, int sf32,
+               const float* __restrict__ partials, int n_partials, long partial_stride, const uint32_t* wait_flags, int wait_n,
+               const uint32_t* epoch_ptr, KernelStatus* st) {
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;
+  if (wait_n > 0) {
+    // the partial sums of a tensor-parallel projection are stored here by the peers: wait for every rank's flag
+    __shared__ int failed;
+    if (threadIdx.x == 0) {
+      failed = 0;
+      const uint32_t want = *epoch_ptr;
+      for (int i = 0; i < wait_n; ++i) if (!wait_flag_ge(wait_flags + i, want, st, 900, i)) { failed = 1; break; }
+    }
+    __syncthreads();
+    if (failed) return;
+  }
   float v[VPT][8];
   float ss = 0.f;
 #pragma unroll
@@ -71,7 +85,19 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
       if (residual != nullptr) {
         float r[8], d[8];
         load8(residual + (size_t)row * ld_in + vi * 8, r);
-        if (delta != nullptr) {
+        if (partials != nullptr) {
+          // all-reduce fused into its consumer: sum the ranks' fp32 partials in rank order (bit-identical everywhere)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) d[j] = 0.f;
+          for (int p = 0; p < n_partials; ++p) {
+            const float4* src = reinterpret_cast<const float4*>(partials + (size_t)p * partial_stride + (size_t)row * hidden + vi * 8);
+            const float4 a = src[0], b = src[1];
+            d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w; d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[j] = __bfloat162float(__float2bfloat16(r[j] + d[j]));
+          store8(residual + (size_t)row * ld_in + vi * 8, r);
+        } else if (delta != nullptr) {
           load8(delta + (size_t)row * ld_in + vi * 8, d);
 #pragma unroll
           for (int j = 0; j < 8; ++j) r[j] = __bfloat162float(__float2bfloat16(r[j] + d[j]));
@@ -332,18 +358,35 @@ GB_API int gb_embed(const int* ids, const void* table, void* out, int n_tok, int
 
 // residual (in/out, may be null) += delta (may be null); y = rmsnorm(residual or x_in) * weight.
 // out (bf16) and out_q/out_sf (MXFP8) are optional outputs.
-GB_API int gb_rmsnorm(void* residual, const void* delta, const void* x_in, const void* weight, void* out, void* out_q, void* out_sf,
-                      int rows, int hidden, float eps, int ld_in, int ld_out, int sf32, cudaStream_t stream) {
+static int rmsnorm_launch(void* residual, const void* delta, const void* x_in, const void* weight, void* out, void* out_q, void* out_sf,
+                          int rows, int hidden, float eps, int ld_in, int ld_out, int sf32, const float* partials, int n_partials,
+                          long partial_stride, const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream) {
   if (hidden % 8 || hidden > 256 * 8 * 4) return fail("rmsnorm: hidden must be a multiple of 8 and <= 8192%s");
   if (out_q != nullptr && hidden % 128) return fail("rmsnorm: MXFP8 output needs hidden %% 128 == 0%s");
   if (rows <= 0) return 0;
   const int nvec = hidden / 8;
 #define GB_RMS(V) rmsnorm_kernel<V><<<rows, 256, 0, stream>>>((__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, \
-    (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out, sf32)
+    (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out, sf32, \
+    partials, n_partials, partial_stride, (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status)
   if (nvec <= 256) GB_RMS(1); else if (nvec <= 512) GB_RMS(2); else if (nvec <= 768) GB_RMS(3); else GB_RMS(4);
 #undef GB_RMS
   GB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+GB_API int gb_rmsnorm(void* residual, const void* delta, const void* x_in, const void* weight, void* out, void* out_q, void* out_sf,
+                      int rows, int hidden, float eps, int ld_in, int ld_out, int sf32, cudaStream_t stream) {
+  return rmsnorm_launch(residual, delta, x_in, weight, out, out_q, out_sf, rows, hidden, eps, ld_in, ld_out, sf32, nullptr, 0, 0, nullptr, 0,
+                        nullptr, nullptr, stream);
+}
+
+// residual += sum over ranks of partials[p] (fp32, [n_partials][partial_stride] with rows * hidden used), then RMSNorm.
+// Waits (bounded) until wait_flags[i] >= *epoch_ptr for i < wait_n before reading the partials.
+GB_API int gb_rmsnorm_reduce(void* residual, const float* partials, int n_partials, long partial_stride, const void* weight, void* out,
+                             void* out_q, void* out_sf, int rows, int hidden, float eps, int sf32, const void* wait_flags, int wait_n,
+                             const void* epoch_ptr, void* status, cudaStream_t stream) {
+  return rmsnorm_launch(residual, nullptr, nullptr, weight, out, out_q, out_sf, rows, hidden, eps, hidden, hidden, sf32, partials, n_partials,
+                        partial_stride, wait_flags, wait_n, epoch_ptr, status, stream);
 }
 
 GB_API int gb_qk_norm_rope(const void* qkv, const int* positions, const int* slots, const void* q_w, const void* k_w, void* q_out,

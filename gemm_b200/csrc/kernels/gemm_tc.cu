@@ -60,6 +60,8 @@ struct GemmArgs {
   uint32_t* signal_flags[kMaxRanks];  // after the last tile of the grid: *signal_flags[p] = *epoch_ptr (release, system scope)
   int signal_n;
   unsigned* done_ctr;
+  int peer_bcast;                  // > 0: tensor-parallel partial: every result row is stored to peer_out[p] for all p < peer_bcast
+  int epoch_self_tick;             // != 0: signal *epoch_ptr + 1 and store it back (no separate tick kernel)
   // ---- split-K (plain GEMMs with few tiles): `splits` CTAs share one output tile, each reduces a K range into a
   // fp32 partial in sk_ws; the warp that arrives last at the tile's semaphore sums the partials in split order
   // (deterministic) and runs the normal epilogue.
@@ -70,6 +72,9 @@ struct GemmArgs {
   // features and its feature index per token: amax_val / amax_idx [ceil(n_out/128) * 4][m_tok]
   float* amax_val;
   int* amax_idx;
+  // ---- extents of the caller's buffers in bytes (0 = unknown): every global access of the kernel that is not a TMA
+  // tile is checked against them; a violation is recorded in the status word (ST_BAD_ARG) and the access is skipped.
+  size_t sfa_bytes, sfb_bytes, out_bytes, out_sf_bytes;
 };
 
 struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; int ks; int tile_id; };
@@ -207,16 +212,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           if (MODE == 1) {
             uint8_t* sf = st + NA * A_BYTES + B_BYTES;
             const size_t kbs = (size_t)num_kb;
-            bulk_load(sf, args.sfa + ((size_t)(t.w_row0 >> 7) * kbs + kb) * 512, 512, &full_bar[s]);
-            if (DUAL) bulk_load(sf + 512, args.sfa + ((size_t)(t.w_row1 >> 7) * kbs + kb) * 512, 512, &full_bar[s]);
+            // scale atoms: offsets are checked against the buffers' extents; a bad one is reported and replaced by atom 0
+            auto atom = [&](const uint8_t* base, size_t extent, size_t off, int where) -> const uint8_t* {
+              if (extent != 0 && off + 512 > extent) { report_status(args.status, ST_BAD_ARG, where, (int)(off >> 9), (int)(extent >> 9), ti); return base; }
+              return base + off;
+            };
+            bulk_load(sf, atom(args.sfa, args.sfa_bytes, ((size_t)(t.w_row0 >> 7) * kbs + kb) * 512, 120), 512, &full_bar[s]);
+            if (DUAL) bulk_load(sf + 512, atom(args.sfa, args.sfa_bytes, ((size_t)(t.w_row1 >> 7) * kbs + kb) * 512, 121), 512, &full_bar[s]);
             if (TN == 32) {
               // narrow tiles use one atom per 32 rows (bytes 0..3 of each 16-byte lane row), so that the tile's
               // scales always land in column 0 of their TMEM block whatever 32-row boundary the tile starts on
-              bulk_load(sf + NA * 512, args.sfb + ((size_t)(t.x_row0 >> 5) * kbs + kb) * 512, 512, &full_bar[s]);
+              bulk_load(sf + NA * 512, atom(args.sfb, args.sfb_bytes, ((size_t)(t.x_row0 >> 5) * kbs + kb) * 512, 122), 512, &full_bar[s]);
             } else {
 #pragma unroll
               for (int i = 0; i < SFB_ATOMS; ++i)
-                bulk_load(sf + (NA + i) * 512, args.sfb + ((size_t)((t.x_row0 >> 7) + i) * kbs + kb) * 512, 512, &full_bar[s]);
+                bulk_load(sf + (NA + i) * 512, atom(args.sfb, args.sfb_bytes, ((size_t)((t.x_row0 >> 7) + i) * kbs + kb) * 512, 123), 512, &full_bar[s]);
             }
           }
           if (++s == S) { s = 0; ph ^= 1; }
@@ -304,12 +314,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (live) {
               if (n_ok) {
                 __nv_fp8_e4m3 f8(v * inv);
-                ((uint8_t*)args.out)[(size_t)x_row * args.ldo + n] = *(uint8_t*)&f8;
+                const size_t off = (size_t)x_row * args.ldo + n;
+                if (args.out_bytes != 0 && off >= args.out_bytes) report_status(args.status, ST_BAD_ARG, 310, x_row, n, ti);
+                else ((uint8_t*)args.out)[off] = *(uint8_t*)&f8;
               }
               if (lane == 0) {
                 const size_t nkb = (size_t)((args.n_out + 127) >> 7);
-                if (TN == 32) args.out_sf[((size_t)(x_row >> 5) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + q] = (uint8_t)e;
-                else args.out_sf[((size_t)(x_row >> 7) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + ((x_row >> 5) & 3) * 4 + q] = (uint8_t)e;
+                const size_t off = (TN == 32) ? ((size_t)(x_row >> 5) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + q
+                                              : ((size_t)(x_row >> 7) * nkb + (size_t)(t.n0 >> 7)) * 512 + (x_row & 31) * 16 + ((x_row >> 5) & 3) * 4 + q;
+                if (args.out_sf_bytes != 0 && off >= args.out_sf_bytes) report_status(args.status, ST_BAD_ARG, 311, x_row, (int)(off >> 9), ti);
+                else args.out_sf[off] = (uint8_t)e;
               }
             }
           } else if (args.amax_val != nullptr) {
@@ -332,9 +346,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               orow = args.peer_rank * args.peer_region_rows + (x_row - src * args.peer_region_rows);
             }
             if (args.row_map != nullptr) orow = args.row_map[x_row];
-            if (orow >= 0) {
+            if (args.peer_bcast > 0) {
+              // row-parallel partial result: the same value goes into this rank's slot on every GPU of the group
+              for (int p = 0; p < args.peer_bcast; ++p) {
+                if (args.out_f32) ((float*)args.peer_out[p])[(size_t)orow * args.ldo + n] = v;
+                else ((__nv_bfloat16*)args.peer_out[p])[(size_t)orow * args.ldo + n] = __float2bfloat16(v);
+              }
+            } else if (orow >= 0) {
               if (args.row_scale != nullptr) v *= args.row_scale[x_row];
-              if (args.out_f32) ((float*)obase)[(size_t)orow * args.ldo + n] = v;
+              const size_t off = ((size_t)orow * args.ldo + n) * (args.out_f32 ? 4 : 2);
+              if (args.out_bytes != 0 && args.peer_region_rows == 0 && off >= args.out_bytes) report_status(args.status, ST_BAD_ARG, 312, orow, n, ti);
+              else if (args.out_f32) ((float*)obase)[(size_t)orow * args.ldo + n] = v;
               else ((__nv_bfloat16*)obase)[(size_t)orow * args.ldo + n] = __float2bfloat16(v);
             }
           }
@@ -416,7 +438,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __threadfence_system();
     if (atomicAdd(args.done_ctr, 1u) == gridDim.x - 1) {
       *args.done_ctr = 0;
-      const uint32_t e = *args.epoch_ptr;
+      uint32_t e = *args.epoch_ptr;
+      if (args.epoch_self_tick) { e += 1; *const_cast<uint32_t*>(args.epoch_ptr) = e; }
       for (int p = 0; p < args.signal_n; ++p) st_release_sys(args.signal_flags[p], e);
     }
   }
@@ -471,6 +494,9 @@ struct GemmExtras {
   int* amax_idx;
   long sk_ws_bytes;          // capacity of sk_ws
   long sk_ctr_count;         // capacity of sk_ctr (entries)
+  int peer_bcast;
+  int epoch_self_tick;
+  size_t sfa_bytes, sfb_bytes, out_bytes, out_sf_bytes;
 };
 
 // Flags of gb_gemm.
@@ -517,7 +543,8 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
     a.w_group_mod = ex->w_group_mod; a.wait_flags = ex->wait_flags; a.wait_n = ex->wait_n; a.epoch_ptr = ex->epoch_ptr;
     for (int i = 0; i < kMaxRanks; ++i) { a.peer_out[i] = ex->peer_out[i]; a.signal_flags[i] = ex->signal_flags[i]; }
     a.peer_region_rows = ex->peer_region_rows; a.peer_rank = ex->peer_rank; a.signal_n = ex->signal_n; a.done_ctr = ex->done_ctr;
-    a.amax_val = ex->amax_val; a.amax_idx = ex->amax_idx;
+    a.amax_val = ex->amax_val; a.amax_idx = ex->amax_idx; a.peer_bcast = ex->peer_bcast; a.epoch_self_tick = ex->epoch_self_tick;
+    a.sfa_bytes = ex->sfa_bytes; a.sfb_bytes = ex->sfb_bytes; a.out_bytes = ex->out_bytes; a.out_sf_bytes = ex->out_sf_bytes;
     if (ex->splits > 1 && num_groups == 0) {
       const int kb_elems = mx ? 128 : 64;
       const int num_kb = (k + kb_elems - 1) / kb_elems;

@@ -96,6 +96,18 @@ class SingleProcess:
     def tp_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         return x
 
+    def row_linear(self, lw: "LinearWeight", x: torch.Tensor, x_mx=None):
+        """Row-parallel projection (o_proj / down_proj).  Returns the residual update: a tensor, or an object that
+        ``add_norm`` / ``materialize`` know how to finish (a reduction still in flight)."""
+        return apply_linear(lw, x, x_mx)
+
+    def add_norm(self, delta, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor], **kw):
+        """``residual += delta`` (if a residual is given) followed by RMSNorm; see ``ops.elementwise.rmsnorm``."""
+        return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
+
+    def materialize(self, delta) -> torch.Tensor:
+        return delta
+
     def moe_ffn(self, model: "Transformer", lw, h: torch.Tensor) -> Optional[torch.Tensor]:
         return None            # None -> the model runs its local MoE path
 
@@ -132,18 +144,15 @@ class Transformer:
         a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
                           num_splits=fb.num_splits, causal=True, window=cfg.sliding_window)
         a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
-        o = apply_linear(lw.wo, a2)
-        return self.par.tp_all_reduce(o)
+        return self.par.row_linear(lw.wo, a2)
 
     def dense_ffn(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor]) -> torch.Tensor:
         if lw.w_gate_up.fmt == "bf16":
             act = gemm.linear_swiglu(h, lw.w_gate_up.w)
-            y = gemm.linear(act, lw.w_down.w)
-        else:
-            xm = h_mx if h_mx is not None else ew.mx_quantize(h, sf_layout=32 if h.shape[0] <= 32 else 128)
-            act = gemm.linear_mx_swiglu_quant(xm, lw.w_gate_up.mx)
-            y = gemm.linear_mx(act, lw.w_down.mx)
-        return self.par.tp_all_reduce(y)
+            return self.par.row_linear(lw.w_down, act)
+        xm = h_mx if h_mx is not None else ew.mx_quantize(h, sf_layout=32 if h.shape[0] <= 32 else 128)
+        act = gemm.linear_mx_swiglu_quant(xm, lw.w_gate_up.mx)
+        return self.par.row_linear(lw.w_down, None, act)
 
     def moe_local(self, lw, h: torch.Tensor) -> torch.Tensor:
         """All experts on this GPU: route -> plan -> (gather + quantise) -> grouped gate/up -> grouped down -> combine."""
@@ -183,18 +192,18 @@ class Transformer:
         for li in range(first_layer, last_layer):
             lw = w.layers[li]
             lay = 32 if x.shape[0] <= 32 else 128
+            par = self.par
             if self.mx:
-                h, h_mx = ew.rmsnorm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps,
-                                     residual=x if delta is not None else None, quantize=True, want_bf16=False, sf_layout=lay)
+                h, h_mx = par.add_norm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps, x if delta is not None else None,
+                                       quantize=True, want_bf16=False, sf_layout=lay)
             else:
-                h, h_mx = ew.rmsnorm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps,
-                                     residual=x if delta is not None else None), None
+                h, h_mx = par.add_norm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps, x if delta is not None else None), None
             delta = self.attention_block(li, lw, h, h_mx, fb)
             need_bf16 = (not self.mx) or cfg.is_moe
             if self.mx:
-                h, h_mx = ew.rmsnorm(delta, lw.ffn_norm, cfg.rms_eps, residual=x, quantize=True, want_bf16=need_bf16, sf_layout=lay)
+                h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, quantize=True, want_bf16=need_bf16, sf_layout=lay)
             else:
-                h, h_mx = ew.rmsnorm(delta, lw.ffn_norm, cfg.rms_eps, residual=x), None
+                h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x), None
             if lw.w13 is not None:
                 delta = self.par.moe_ffn(self, lw, h)
                 if delta is None:
@@ -202,12 +211,9 @@ class Transformer:
             else:
                 delta = self.dense_ffn(lw, h, h_mx)
             if li in self.snapshot_layers:
-                self.snapshots[li] = (x.float() + delta.float())
-        if delta is not None:
-            # fold the last delta into the stream (the final norm kernel does it for the full model)
-            self._last_delta = delta
-        else:
-            self._last_delta = None
+                self.snapshots[li] = (x.float() + self.par.materialize(delta).float())
+        # the last delta stays pending: the head (or the next pipeline stage) folds it into the stream
+        self._last_delta = self.par.materialize(delta) if delta is not None else None
         return x
 
     def forward(self, fb: ForwardBatch) -> torch.Tensor:

@@ -158,7 +158,7 @@ class RandomSource:
 
 
 def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0,
-                  ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None) -> ModelWeights:
+                  ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None, layer_range=None) -> ModelWeights:
     """Assemble ``ModelWeights`` in format ``fmt`` from a tensor source that answers GGUF tensor names
     (``RandomSource``, ``loader.GGUFSource``, ``loader.SafetensorsSource``).
 
@@ -184,7 +184,8 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
 
     layers: List[LayerWeights] = []
     nl = n_layers if n_layers is not None else cfg.n_layers
-    for li in range(nl):
+    lo, hi = layer_range if layer_range is not None else (0, nl)       # pipeline stages keep a contiguous slice of layers
+    for li in range(lo, hi):
         pre = f"blk.{li}."
         wq = src.get(pre + "attn_q.weight", (cfg.q_dim, h))[q0:q1]
         wk = src.get(pre + "attn_k.weight", (cfg.kv_dim, h))[k0:k1]
@@ -247,6 +248,8 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
 
 
 def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,
-                      ep_rank: int = 0, ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None) -> ModelWeights:
+                      ep_rank: int = 0, ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None,
+                      layer_range=None) -> ModelWeights:
     """Random-init weights of ``cfg`` (generated on ``device``) in format ``fmt``."""
-    return build_weights(cfg, RandomSource(cfg, seed, device), fmt, device, tp_rank, tp_size, ep_rank, ep_size, shard_vocab, n_layers)
+    return build_weights(cfg, RandomSource(cfg, seed, device), fmt, device, tp_rank, tp_size, ep_rank, ep_size, shard_vocab, n_layers,
+                         layer_range)

@@ -25,7 +25,8 @@ class GemmExtras(ctypes.Structure):
                 ("peer_rank", ctypes.c_int), ("signal_flags", ctypes.c_void_p * 8), ("signal_n", ctypes.c_int),
                 ("pad", ctypes.c_int), ("done_ctr", ctypes.c_void_p), ("splits", ctypes.c_int), ("pad2", ctypes.c_int),
                 ("sk_ws", ctypes.c_void_p), ("sk_ctr", ctypes.c_void_p), ("amax_val", ctypes.c_void_p), ("amax_idx", ctypes.c_void_p),
-                ("sk_ws_bytes", ctypes.c_long), ("sk_ctr_count", ctypes.c_long)]
+                ("sk_ws_bytes", ctypes.c_long), ("sk_ctr_count", ctypes.c_long), ("peer_bcast", ctypes.c_int), ("epoch_self_tick", ctypes.c_int),
+                ("sfa_bytes", ctypes.c_size_t), ("sfb_bytes", ctypes.c_size_t), ("out_bytes", ctypes.c_size_t), ("out_sf_bytes", ctypes.c_size_t)]
 
 
 _SK_WS_BYTES = 64 << 20
@@ -82,6 +83,11 @@ def _launch(w, x, out, n_out, k, m_tok, ldw, ldx, ldo, flags, tn, num_groups=0, 
             seg_start=None, seg_count=None, x_rows=None, sfa=None, sfb=None, out_sf=None, bias=None, row_map=None,
             row_scale=None, extras=None):
     lib = _native.cuda()
+    if extras is None:
+        extras = GemmExtras()
+    # extents of the caller's buffers: the kernel checks its scale-atom loads and its stores against them
+    nb = lambda t: t.numel() * t.element_size() if t is not None else 0
+    extras.sfa_bytes, extras.sfb_bytes, extras.out_bytes, extras.out_sf_bytes = nb(sfa), nb(sfb), nb(out), nb(out_sf)
     rc = lib.gb_gemm(_p(w), _p(x), _p(out), _i(n_out), _i(k), _i(m_tok), _i(ldw), _i(ldx), _i(ldo), _i(flags), _i(tn),
                      _i(num_groups), _i(w_rows_per_group), _i(up_row_offset), _p(seg_start), _p(seg_count),
                      _i(x_rows if x_rows is not None else m_tok), _p(sfa), _p(sfb), _p(out_sf), _p(bias), _p(row_map),

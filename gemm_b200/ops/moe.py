@@ -80,11 +80,13 @@ def plan_capacity(n_pairs: int, n_exp: int, align: int, regions: int = 1, k: int
 
 
 def plan_ref(ids: torch.Tensor, n_exp: int, k: int, align: int, regions: int = 1) -> MoePlan:
+    """CPU reference of the device plan.  Ids outside ``[0, n_exp)`` are dropped (their ``pair_row`` is -1)."""
     flat = ids.reshape(-1).long()
     n_pairs = flat.numel()
     region_rows, capacity = plan_capacity(n_pairs, n_exp, align, regions, k)
     epr = n_exp // regions
-    counts = torch.bincount(flat, minlength=n_exp)[:n_exp]
+    ok = (flat >= 0) & (flat < n_exp)
+    counts = torch.bincount(flat[ok], minlength=n_exp)[:n_exp]
     seg_start = torch.zeros(n_exp, dtype=torch.int64)
     region_used = torch.zeros(regions, dtype=torch.int64)
     for r in range(regions):
@@ -94,15 +96,17 @@ def plan_ref(ids: torch.Tensor, n_exp: int, k: int, align: int, regions: int = 1
             seg_start[e] = r * region_rows + pos
             pos += (int(counts[e]) + align - 1) // align * align
         region_used[r] = pos
-    order = torch.sort(flat, stable=True).indices          # by expert, then (token, k)
+    key = torch.where(ok, flat, torch.full_like(flat, n_exp))
+    order = torch.sort(key, stable=True).indices              # by expert, then (token, k)
+    sorted_e = key[order]
+    first = torch.zeros(n_exp + 2, dtype=torch.int64)
+    first[1:n_exp + 1] = torch.cumsum(counts, 0)
+    first[n_exp + 1] = n_pairs
     rank = torch.zeros(n_pairs, dtype=torch.int64)
-    sorted_e = flat[order]
-    first = torch.zeros(n_exp + 1, dtype=torch.int64)
-    first[1:] = torch.cumsum(counts, 0)
     rank[order] = torch.arange(n_pairs) - first[sorted_e]
-    pair_row = seg_start[flat] + rank
+    pair_row = torch.where(ok, seg_start[flat.clamp(0, n_exp - 1)] + rank, torch.full_like(flat, -1))
     row_token = torch.full((capacity,), -1, dtype=torch.int32)
-    row_token[pair_row] = (torch.arange(n_pairs) // k).to(torch.int32)
+    row_token[pair_row[ok]] = (torch.arange(n_pairs)[ok] // k).to(torch.int32)
     return MoePlan(seg_start.to(torch.int32), counts.to(torch.int32), pair_row.to(torch.int32), row_token,
                    region_used.to(torch.int32), capacity, region_rows)
 

@@ -47,6 +47,7 @@ class ExpertParallel:
         """Size the symmetric buffers for at most ``max_tokens`` tokens per rank and forward pass."""
         self.cfg = cfg
         self.max_tokens = max_tokens
+        self.mx = getattr(getattr(engine, "w", None), "fmt", "bf16") == "mxfp8"
         if not self.fused:
             return
         w, k, e, hid = self.ep_size, cfg.n_experts_used, cfg.n_experts, cfg.hidden
@@ -120,6 +121,16 @@ class ExpertParallel:
     def tp_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         return x
 
+    def row_linear(self, lw, x, x_mx=None):
+        from ..models.transformer import apply_linear
+        return apply_linear(lw, x, x_mx)
+
+    def add_norm(self, delta, weight, eps, residual, **kw):
+        return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
+
+    def materialize(self, delta):
+        return delta
+
     def moe_ffn(self, model, lw, h: torch.Tensor) -> torch.Tensor:
         if not self.fused:
             return self._moe_nccl(model, lw, h)
@@ -157,7 +168,12 @@ class ExpertParallel:
         k, e = cfg.n_experts_used, cfg.n_experts
         e_local = e // w
         allh = torch.empty(w * t, hid, dtype=h.dtype, device=h.device)
-        dist.all_gather_into_tensor(allh, h.contiguous(), group=self.group)
+        if h.is_cuda:
+            dist.all_gather_into_tensor(allh, h.contiguous(), group=self.group)
+        else:                                   # gloo (CPU ranks in the tests) has no tensor all-gather / reduce-scatter
+            parts = [torch.empty_like(h) for _ in range(w)]
+            dist.all_gather(parts, h.contiguous(), group=self.group)
+            allh = torch.cat(parts)
         logits = gemm.linear(allh, lw.router, out_dtype=torch.float32)
         ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
         local = ids - self.ep_rank * e_local
@@ -177,6 +193,9 @@ class ExpertParallel:
             act = gemm.grouped_linear(xs, lw.w13.w.view(e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True)
             y = gemm.grouped_linear(act, lw.w2.w.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn)
         part = moe.combine(y, pl.pair_row, wts, w * t, k).float()
+        if not h.is_cuda:
+            dist.all_reduce(part, group=self.group)
+            return part[self.ep_rank * t:(self.ep_rank + 1) * t].to(torch.bfloat16)
         out = torch.empty(t, hid, dtype=torch.float32, device=h.device)
         dist.reduce_scatter_tensor(out, part, group=self.group)
         return out.to(torch.bfloat16)

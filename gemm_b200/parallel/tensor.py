@@ -1,0 +1,168 @@
+"""Tensor parallelism (Megatron style) with the reduction fused into the kernels around it.
+
+Weights are cut at load time: q/k/v/gate/up by rows (column parallel), o_proj/down_proj by columns (row parallel); KV heads
+are sharded, or replicated when there are fewer KV heads than ranks.  The reference does this between CPU ranks with an
+all-reduce of ``n_embd`` floats after o_proj and after ffn_down (common/transformer.h:4178-4283,
+cpu/llm/test_transformer_parallel.c:431-525).  Here, for decode-sized batches, there is no all-reduce kernel at all:
+
+  row-parallel GEMM epilogue  --stores fp32 partial rows into this rank's slot on EVERY GPU, then raises a flag-->
+  next RMSNorm kernel         --waits for all ranks' flags, sums the slots in rank order, adds the residual, normalises
+                                (and quantises to MXFP8 for the next GEMM)
+
+so the collective costs one NVLink store per output element and no extra launch; sums are bit-identical on all ranks,
+which keeps greedy decoding in lock step without broadcasting tokens.  Large (prefill) batches use the two-shot
+reduce-scatter + all-gather kernel of the fabric.  ``fused=False`` is the NCCL baseline.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops import elementwise as ew
+from ..ops import gemm
+from ..ops.mxfp8 import MxTensor
+from .fabric import Fabric
+
+_c, _i, _f, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_long
+
+
+@dataclass
+class PendingReduce:
+    """Partial sums of a row-parallel projection sitting in the slots of channel ``chan``; finished by ``add_norm``."""
+    chan: int
+    rows: int
+    hidden: int
+
+
+class TensorParallel:
+    ep_size = 1
+    ep_rank = 0
+
+    def __init__(self, group, device: torch.device, fused: bool = True, max_fused_rows: int = 256):
+        self.group, self.device, self.fused = group, device, fused
+        self.tp_size = dist.get_world_size(group)
+        self.tp_rank = dist.get_rank(group)
+        self.max_fused_rows = max_fused_rows
+        self.fab: Optional[Fabric] = None
+        self._chan = 0
+
+    def attach(self, engine, cfg, max_tokens: int) -> None:
+        self.cfg = cfg
+        if not self.fused:
+            return
+        w, h = self.tp_size, cfg.hidden
+        slot = self.max_fused_rows * h * 4
+        big = max_tokens * h
+        heap = 2 * w * slot + 2 * big * 2 + (8 << 20)
+        self.fab = f = Fabric(self.group, self.device, heap)
+        self.slot_elems = self.max_fused_rows * h
+        self.slots_off = [f.alloc(w * slot), f.alloc(w * slot)]
+        self.flags_off = [f.alloc(32), f.alloc(32)]
+        self.epoch = [f.ctl_word(), f.ctl_word()]
+        self.done = [f.ctl_word(), f.ctl_word()]
+        self.big = f.make_allreduce_large(big, torch.bfloat16, chunks=64)
+        self.argmax = f.make_argmax(4096)
+        self._extras = []
+        for ch in range(2):
+            ex = gemm.GemmExtras()
+            ex.epoch_ptr = self.epoch[ch]
+            ex.epoch_self_tick = 1
+            ex.peer_bcast = w
+            for p in range(w):
+                ex.peer_out[p] = f.peer_ptr(p, self.slots_off[ch]) + self.tp_rank * slot
+                ex.signal_flags[p] = f.peer_ptr(p, self.flags_off[ch]) + 4 * self.tp_rank
+            ex.signal_n = w
+            ex.done_ctr = self.done[ch]
+            self._extras.append(ex)
+
+    # ------------------------------------------------------------------------------------------ model hooks
+    def tp_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_size == 1:
+            return x
+        if not self.fused:
+            dist.all_reduce(x, group=self.group)
+            return x
+        return self.big(x.contiguous())
+
+    def row_linear(self, lw, x, x_mx: Optional[MxTensor] = None):
+        from ..models.transformer import apply_linear
+        rows = x.shape[0] if x is not None else x_mx.rows
+        if not self.fused or self.tp_size == 1 or rows > self.max_fused_rows:
+            return self.tp_all_reduce(apply_linear(lw, x, x_mx))
+        ch = self._chan
+        self._chan ^= 1
+        n, k = lw.n, lw.k
+        ex = self._extras[ch]
+        if lw.fmt == "bf16":
+            tn = gemm.pick_tn(rows)
+            gemm._launch(lw.w, x, None, n, k, rows, lw.w.stride(0), x.stride(0), n, gemm.GEMM_OUT_F32, tn, bias=None, extras=ex)
+        else:
+            xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if rows <= 32 else 128)
+            gemm._launch(lw.mx.data, xm.data, None, n, k, rows, k, k, n, gemm.GEMM_MX | gemm.GEMM_OUT_F32, xm.sf_layout,
+                         x_rows=xm.data.shape[0], sfa=lw.mx.sf, sfb=xm.sf, extras=ex)
+        return PendingReduce(ch, rows, n)
+
+    def _reduce_norm(self, pr: PendingReduce, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128):
+        f = self.fab
+        rows, hidden = pr.rows, pr.hidden
+        out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device) if want_bf16 else None
+        q = sf = None
+        if quantize:
+            rp = (rows + 127) // 128 * 128
+            q = torch.zeros(rp, hidden, dtype=torch.uint8, device=self.device)
+            sf = ew.sf_alloc(rp, hidden, self.device, sf_layout)
+        p = lambda t: _c(t.data_ptr()) if t is not None else _c(0)
+        rc = f.lib.gb_rmsnorm_reduce(p(residual), _c(f.local_base + self.slots_off[pr.chan]), _i(self.tp_size), _l(self.slot_elems), p(weight),
+                                     p(out), p(q), p(sf), _i(rows), _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0),
+                                     _c(f.local_base + self.flags_off[pr.chan]), _i(self.tp_size), _c(self.epoch[pr.chan]),
+                                     _c(_native.status_ptr()), _c(torch.cuda.current_stream().cuda_stream))
+        _native.check(rc, "gb_rmsnorm_reduce")
+        if quantize:
+            return out, MxTensor(q, sf, rows, hidden, sf_layout)
+        return out
+
+    def add_norm(self, delta, weight, eps, residual, **kw):
+        if isinstance(delta, PendingReduce):
+            return self._reduce_norm(delta, weight, eps, residual, **kw)
+        return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
+
+    def materialize(self, delta):
+        """Finish a pending reduction into a plain tensor (sum of the ranks' partials, bf16)."""
+        if not isinstance(delta, PendingReduce):
+            return delta
+        f = self.fab
+        slots = f.view(self.slots_off[delta.chan], (self.tp_size, self.slot_elems), torch.float32)
+        # order the read after the peers' stores: a fabric barrier (device side) covers the flags of this channel
+        f.barrier()
+        return slots[:, : delta.rows * delta.hidden].sum(0).reshape(delta.rows, delta.hidden).to(torch.bfloat16)
+
+    def moe_ffn(self, model, lw, h):
+        return None
+
+    def merge_sampled(self, tok: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+        """Greedy merge for a vocabulary-sharded LM head: arg-max all-reduce of this shard's (value, index)."""
+        if self.tp_size == 1 or logits.shape[1] == self.cfg.vocab:
+            return tok
+        val = logits.gather(1, (tok.long() - self._vocab_start).clamp_min(0).unsqueeze(1)).squeeze(1).contiguous()
+        if self.fused:
+            idx, _ = self.argmax(val, tok.contiguous())
+            return idx
+        vals = [torch.empty_like(val) for _ in range(self.tp_size)]
+        toks = [torch.empty_like(tok) for _ in range(self.tp_size)]
+        dist.all_gather(vals, val, group=self.group)
+        dist.all_gather(toks, tok, group=self.group)
+        v, t = torch.stack(vals), torch.stack(toks)
+        best = v.max(0).values
+        cand = torch.where(v == best, t, torch.full_like(t, 2 ** 31 - 1))
+        return cand.min(0).values
+
+    _vocab_start = 0
+
+    def close(self) -> None:
+        if self.fab is not None:
+            self.fab.close()

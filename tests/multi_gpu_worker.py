@@ -114,6 +114,37 @@ def check_expert_parallel(rank, world, dev, fmt, fused):
     par.close()
 
 
+def check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-dense"):
+    """Every rank runs the same sequences on its weight shard; logits must equal the unsharded engine's, and be
+    bit-identical across ranks (lock-step greedy decoding needs that)."""
+    from gemm_b200.parallel.tensor import TensorParallel
+    cfg = get_config(name)
+    page = 16
+    g = torch.Generator().manual_seed(11)
+    toks = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (40, 90)]
+    w_full = synthetic_weights(cfg, fmt, device=dev, seed=5)
+    w_tp = synthetic_weights(cfg, fmt, device=dev, seed=5, tp_rank=rank, tp_size=world)
+    ref = run_model(Transformer(w_full, KvCache.allocate(cfg, 64, page, dev)), cfg, toks, page, dev)
+    par = TensorParallel(dist.group.WORLD, dev, fused=fused)
+    par.attach(None, cfg, max_tokens=256)
+    hkv_local = max(1, cfg.n_kv_heads // world)
+    model = Transformer(w_tp, KvCache.allocate(cfg, 64, page, dev, hkv_local), par)
+    got = run_model(model, cfg, toks, page, dev)
+    torch.cuda.synchronize()
+    _native.assert_status_ok()
+    tol = 2e-2 if fmt == "bf16" else 6e-2
+    for a, b in zip(got, ref):
+        r = rel(a, b)
+        assert r < tol, f"TP({fmt}, fused={fused}) differs from the single-GPU engine: rel {r}"
+    last = got[-1].contiguous()
+    gathered = [torch.empty_like(last) for _ in range(world)]
+    dist.all_gather(gathered, last)
+    if fused:
+        assert all(torch.equal(gathered[0], x) for x in gathered), "ranks disagree bitwise after the fused reduction"
+    dist.barrier()
+    par.close()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -129,6 +160,9 @@ def main():
     if what in ("all", "ep"):
         for fmt, fused in (("bf16", True), ("mxfp8", True), ("mxfp8", False)):
             check_expert_parallel(rank, world, dev, fmt, fused)
+    if what in ("all", "tp"):
+        for fmt, fused in (("bf16", True), ("mxfp8", True), ("bf16", False)):
+            check_tensor_parallel(rank, world, dev, fmt, fused)
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_WORKER_OK", what, "world", world)

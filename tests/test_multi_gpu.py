@@ -36,3 +36,8 @@ def test_fabric_collectives():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_expert_parallel_matches_single_gpu():
     _launch("ep", min(_ngpu(), 4), 29612)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_tensor_parallel_matches_single_gpu():
+    _launch("tp", 2, 29613)
