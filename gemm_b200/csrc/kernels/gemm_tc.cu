@@ -182,7 +182,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     __syncthreads();
   }
   if (!*abort_flag)
-    for (int i = threadIdx.x; i < args.num_groups; i += blockDim.x) { s_start[i] = args.seg_start[i]; s_count[i] = args.seg_count[i]; }
+    for (int i = threadIdx.x; i < args.num_groups; i += blockDim.x) {
+      // segment tables come from device memory: clamp them into the X buffer so that a corrupt table cannot walk off it
+      const int st0 = args.seg_start[i], cn = args.seg_count[i];
+      const bool sane = st0 >= 0 && cn >= 0 && st0 <= args.m_tok && cn <= args.m_tok - st0;
+      if (!sane) report_status(args.status, ST_BAD_ARG, 130, i, st0, cn);
+      s_start[i] = sane ? st0 : 0; s_count[i] = sane ? cn : 0;
+    }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();

@@ -94,18 +94,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           KernelStatus* st, int where, int aux = 0) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
-  for (uint32_t it = 1;; ++it) {
+  // A failed try_wait has already blocked for the hardware's own time limit, so the clock is read on every retry.
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0x3ffu) == 0) {
-      if (*abort_flag) return false;
-      uint64_t now = globaltimer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kMbarBudgetNs) {
-        *abort_flag = 1;
-        report_status(st, ST_TIMEOUT_MBAR, where, aux, (int)parity, 0);
-        return false;
-      }
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > kMbarBudgetNs) {
+      *abort_flag = 1;
+      report_status(st, ST_TIMEOUT_MBAR, where, aux, (int)parity, 0);
+      return false;
     }
   }
 }

@@ -1,0 +1,207 @@
+"""OpenAI-compatible HTTP front end over ``LLM`` (continuous batching).
+
+Endpoints (the set the reference serves in server/server.c:2094-2270 for its LLM):
+  POST /v1/chat/completions   messages -> ChatML prompt -> completion (``stream: true`` gives server-sent events)
+  POST /v1/completions        raw prompt completion
+  GET  /v1/models             the loaded model
+  GET  /v1/progress           queue / running counts and tokens produced so far (server.c:1632)
+  GET  /health
+
+Unlike the reference (one global model, one request at a time, token-by-token prefill: server/server_llm.c:422-632),
+requests from all connections are queued into one engine thread that steps the scheduler, so concurrent
+requests share every forward pass.  Standard library only.
+"""
+from __future__ import annotations
+
+import json
+import queue
+import threading
+import time
+import uuid
+from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
+from typing import Dict, List, Optional
+
+from .engine import SamplingParams
+from .llm import LLM
+
+
+def build_chat_prompt(messages: List[dict]) -> str:
+    """OpenAI ``messages`` -> ChatML text (the template Qwen models are trained with; server_llm.c:298)."""
+    parts = []
+    for m in messages:
+        content = m.get("content", "")
+        if isinstance(content, list):                       # multimodal content parts: keep the text parts
+            content = "".join(p.get("text", "") for p in content if isinstance(p, dict))
+        parts.append(f"<|im_start|>{m.get('role', 'user')}\n{content}<|im_end|>\n")
+    parts.append("<|im_start|>assistant\n")
+    return "".join(parts)
+
+
+class EngineThread(threading.Thread):
+    """Owns the ``LLM``; HTTP handlers submit requests and read tokens from per-request queues."""
+
+    def __init__(self, llm: LLM):
+        super().__init__(daemon=True)
+        self.llm = llm
+        self.inbox: "queue.Queue" = queue.Queue()
+        self.streams: Dict[int, "queue.Queue"] = {}
+        self.tokens_total = 0
+        self.stop_flag = False
+
+    def submit(self, ids: List[int], sp: SamplingParams) -> "queue.Queue":
+        q: "queue.Queue" = queue.Queue()
+        self.inbox.put((ids, sp, q))
+        return q
+
+    def run(self):
+        while not self.stop_flag:
+            try:
+                while True:
+                    ids, sp, q = self.inbox.get(block=not self.llm.has_work(), timeout=0.05)
+                    rid = self.llm.add_request(ids, sp)
+                    self.streams[rid] = q
+            except queue.Empty:
+                pass
+            if not self.llm.has_work():
+                continue
+            produced = self.llm.step()
+            self.tokens_total += len(produced)
+            for rid, tok in produced.items():
+                q = self.streams.get(rid)
+                if q is None:
+                    continue
+                q.put(tok)
+                if self.llm._reqs[rid].done:
+                    q.put(None)
+                    del self.streams[rid]
+                    self.llm._reqs.pop(rid, None)
+
+
+def make_handler(engine: EngineThread, model_name: str):
+    llm = engine.llm
+
+    class Handler(BaseHTTPRequestHandler):
+        protocol_version = "HTTP/1.1"
+
+        def log_message(self, fmt, *args):            # quiet
+            pass
+
+        def _json(self, code: int, obj) -> None:
+            body = json.dumps(obj).encode()
+            self.send_response(code)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(body)))
+            self.end_headers()
+            self.wfile.write(body)
+
+        def do_GET(self):
+            if self.path == "/health":
+                return self._json(200, {"status": "ok"})
+            if self.path == "/v1/models":
+                return self._json(200, {"object": "list", "data": [{"id": model_name, "object": "model"}]})
+            if self.path == "/v1/progress":
+                return self._json(200, {"waiting": llm.sched.num_waiting, "running": llm.sched.num_running,
+                                        "tokens_generated": engine.tokens_total, "steps": llm.steps})
+            self._json(404, {"error": "not found"})
+
+        def do_POST(self):
+            n = int(self.headers.get("Content-Length", "0"))
+            try:
+                req = json.loads(self.rfile.read(n) or b"{}")
+            except json.JSONDecodeError:
+                return self._json(400, {"error": "invalid JSON"})
+            chat = self.path == "/v1/chat/completions"
+            if not chat and self.path != "/v1/completions":
+                return self._json(404, {"error": "not found"})
+            if chat:
+                prompt = build_chat_prompt(req.get("messages", []))
+            else:
+                prompt = req.get("prompt", "")
+            if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+                ids = prompt                                   # pre-tokenised prompt
+            else:
+                if llm.tokenizer is None:
+                    return self._json(400, {"error": "no tokenizer loaded: send the prompt as a list of token ids"})
+                ids = llm.tokenizer.encode(prompt)
+            stops = []
+            if llm.tokenizer is not None:
+                stops = [i for i in (llm.tokenizer.eos_id, llm.tokenizer.eot_id) if i >= 0]
+            sp = SamplingParams(max_new_tokens=int(req.get("max_tokens", 128)), temperature=float(req.get("temperature", 0.0)),
+                                top_k=int(req.get("top_k", 0)), top_p=float(req.get("top_p", 1.0)), seed=int(req.get("seed", 0)),
+                                stop_token_ids=tuple(stops))
+            stop_strings = req.get("stop") or []
+            if isinstance(stop_strings, str):
+                stop_strings = [stop_strings]
+            q = engine.submit(ids, sp)
+            rid = "cmpl-" + uuid.uuid4().hex[:24]
+            created = int(time.time())
+            obj = "chat.completion" if chat else "text_completion"
+
+            def text_of(toks: List[int]) -> str:
+                return llm.tokenizer.decode(toks) if llm.tokenizer is not None else " ".join(str(t) for t in toks)
+
+            toks: List[int] = []
+            if req.get("stream"):
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Transfer-Encoding", "chunked")
+                self.end_headers()
+
+                def chunk(payload: dict):
+                    data = ("data: " + json.dumps(payload) + "\n\n").encode()
+                    self.wfile.write(f"{len(data):X}\r\n".encode() + data + b"\r\n")
+                    self.wfile.flush()
+
+                sent = ""
+                while True:
+                    t = q.get()
+                    if t is None:
+                        break
+                    toks.append(t)
+                    full = text_of(toks)
+                    delta, sent = full[len(sent):], full
+                    piece = {"delta": {"content": delta}} if chat else {"text": delta}
+                    chunk({"id": rid, "object": obj + ".chunk", "created": created, "model": model_name,
+                           "choices": [dict(index=0, finish_reason=None, **piece)]})
+                    if any(s and s in full for s in stop_strings):
+                        break
+                chunk({"id": rid, "object": obj + ".chunk", "created": created, "model": model_name,
+                       "choices": [dict(index=0, finish_reason="stop", **({"delta": {}} if chat else {"text": ""}))]})
+                done = b"data: [DONE]\n\n"
+                self.wfile.write(f"{len(done):X}\r\n".encode() + done + b"\r\n0\r\n\r\n")
+                return
+            while True:
+                t = q.get()
+                if t is None:
+                    break
+                toks.append(t)
+            text = text_of(toks)
+            for s in stop_strings:
+                if s and s in text:
+                    text = text[: text.index(s)]
+            finish = "length" if len(toks) >= sp.max_new_tokens else "stop"
+            choice = {"index": 0, "finish_reason": finish}
+            if chat:
+                choice["message"] = {"role": "assistant", "content": text}
+            else:
+                choice["text"] = text
+            self._json(200, {"id": rid, "object": obj, "created": created, "model": model_name, "choices": [choice], "token_ids": toks,
+                             "usage": {"prompt_tokens": len(ids), "completion_tokens": len(toks), "total_tokens": len(ids) + len(toks)}})
+
+    return Handler
+
+
+def serve(llm: LLM, host: str = "127.0.0.1", port: int = 8080, model_name: str = "gemm_b200", block: bool = True):
+    """Start the engine thread and the HTTP server.  Returns ``(server, engine_thread)``; with ``block`` it serves for ever."""
+    engine = EngineThread(llm)
+    engine.start()
+    httpd = ThreadingHTTPServer((host, port), make_handler(engine, model_name))
+    if block:
+        try:
+            httpd.serve_forever()
+        finally:
+            engine.stop_flag = True
+    else:
+        threading.Thread(target=httpd.serve_forever, daemon=True).start()
+    return httpd, engine
