@@ -1,0 +1,86 @@
+"""Inference-state checkpoints: save the KV cache of the live sequences (plus positions and pending tokens) and resume
+later — e.g. to skip a long prefill when sweeping decode settings.
+
+Counterpart of the reference's 'TPCP' files (a64fx/llm/tp_runner.c:155-563: magic + version, model and TP geometry,
+cache position, next token, then per-layer K / V buffers; every header field is validated on load,
+tp_cache_matches_model :356-387).  Our file: magic ``GBKV1\\n``, a JSON header line (geometry, sequences), then for every layer
+the K and V rows of the used cache slots in sequence order (bf16).  A truncated or mismatching file is rejected.
+"""
+from __future__ import annotations
+
+import json
+import struct
+from typing import Dict, List
+
+import torch
+
+MAGIC = b"GBKV1\n"
+
+
+def _geometry(engine) -> Dict:
+    cfg = engine.cfg
+    return {"arch": cfg.arch, "n_layers": len(engine.w.layers), "hidden": cfg.hidden, "n_kv_heads_local": engine.kv.k[0].shape[1],
+            "head_dim": cfg.head_dim, "vocab": cfg.vocab, "tp_size": engine.w.tp_size, "tp_rank": engine.w.tp_rank,
+            "ep_size": engine.w.ep_size, "ep_rank": engine.w.ep_rank, "fmt": engine.w.fmt}
+
+
+def save_state(engine, path: str, next_tokens=None) -> None:
+    """Write the cached K/V of all sequences of ``engine`` (a ``serve.engine.Engine``)."""
+    ps = engine.page_size
+    header = {"geometry": _geometry(engine), "seq_len": list(engine.seq_len), "page_size": ps,
+              "next_tokens": [int(t) for t in (next_tokens.tolist() if next_tokens is not None else [])]}
+    slots = []
+    for s, n in enumerate(engine.seq_len):
+        pages = engine.seq_pages[s]
+        for p in range(n):
+            slots.append(pages[p // ps] * ps + p % ps)
+    idx = torch.tensor(slots, dtype=torch.long, device=engine.device)
+    with open(path, "wb") as f:
+        f.write(MAGIC)
+        hb = json.dumps(header).encode()
+        f.write(struct.pack("<Q", len(hb)))
+        f.write(hb)
+        for li in range(len(engine.kv.k)):
+            for t in (engine.kv.k[li], engine.kv.v[li]):
+                f.write(t[idx].contiguous().cpu().view(torch.uint8).numpy().tobytes())
+
+
+def load_state(engine, path: str) -> torch.Tensor:
+    """Restore sequences into an empty ``engine``; returns the saved pending tokens (int32).  Raises on any mismatch."""
+    with open(path, "rb") as f:
+        if f.read(len(MAGIC)) != MAGIC:
+            raise ValueError("not a KV state file (bad magic)")
+        raw = f.read(8)
+        if len(raw) != 8:
+            raise ValueError("truncated KV state file")
+        (hl,) = struct.unpack("<Q", raw)
+        if hl > (1 << 26):
+            raise ValueError("implausible header length")
+        header = json.loads(f.read(hl))
+        geo, mine = header["geometry"], _geometry(engine)
+        for k, v in mine.items():
+            if geo.get(k) != v:
+                raise ValueError(f"KV state file does not match the model: {k} is {geo.get(k)!r} in the file, {v!r} here")
+        if header["page_size"] <= 0:
+            raise ValueError("bad page size")
+        engine.reset()
+        ps = engine.page_size
+        slots = []
+        for n in header["seq_len"]:
+            engine.seq_pages.append([])
+            engine.seq_len.append(0)
+            s = len(engine.seq_pages) - 1
+            engine._ensure_pages(s, n)
+            engine.seq_len[s] = n
+            pages = engine.seq_pages[s]
+            slots.extend(pages[p // ps] * ps + p % ps for p in range(n))
+        idx = torch.tensor(slots, dtype=torch.long, device=engine.device)
+        row = engine.kv.k[0].shape[1] * engine.kv.k[0].shape[2] * 2
+        for li in range(len(engine.kv.k)):
+            for t in (engine.kv.k[li], engine.kv.v[li]):
+                buf = f.read(len(slots) * row)
+                if len(buf) != len(slots) * row:
+                    raise ValueError("truncated KV state file")
+                vals = torch.frombuffer(bytearray(buf), dtype=torch.uint8).view(torch.bfloat16).reshape(len(slots), t.shape[1], t.shape[2])
+                t[idx] = vals.to(engine.device)
+    return torch.tensor(header["next_tokens"], dtype=torch.int32)

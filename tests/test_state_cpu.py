@@ -1,0 +1,55 @@
+"""Inference-state checkpoints and the weight stager (CPU)."""
+import json
+
+import pytest
+import torch
+
+from gemm_b200.models.config import get_config
+from gemm_b200.models.weights import RandomSource, build_weights, synthetic_weights
+from gemm_b200.serve.engine import Engine, SamplingParams
+from gemm_b200.utils import checkpoint, stage
+
+
+def test_kv_state_roundtrip_and_validation(tmp_path):
+    torch.manual_seed(0)
+    cfg = get_config("tiny-dense")
+    w = synthetic_weights(cfg, "bf16", device="cpu", seed=1)
+    prompts = [torch.randint(0, cfg.vocab, (n,), dtype=torch.int32) for n in (19, 7)]
+    a = Engine(w, max_batch=2, max_seq_len=64, page_size=16)
+    first = a._sample(a.prefill(prompts, reserve=8), SamplingParams(), 0)
+    path = str(tmp_path / "state.gbkv")
+    checkpoint.save_state(a, path, first)
+    a.begin_decode(first, SamplingParams(), 6, use_graph=False)
+    ref = [a.decode_step().clone() for _ in range(4)]
+    b = Engine(w, max_batch=2, max_seq_len=64, page_size=16, num_pages=20)      # different page pool -> different page ids
+    b.pages.alloc(3)
+    nxt = checkpoint.load_state(b, path)
+    assert torch.equal(nxt, first.cpu().to(torch.int32)) and b.seq_len == [19, 7]
+    b.begin_decode(nxt, SamplingParams(), 6, use_graph=False)
+    got = [b.decode_step().clone() for _ in range(4)]
+    assert all(torch.equal(x, y) for x, y in zip(ref, got))
+    # mismatching model and truncated file are rejected
+    other = Engine(synthetic_weights(get_config("tiny-moe"), "bf16", device="cpu"), max_batch=2, max_seq_len=64, page_size=16)
+    with pytest.raises(ValueError):
+        checkpoint.load_state(other, path)
+    data = open(path, "rb").read()
+    open(path, "wb").write(data[: len(data) // 2])
+    with pytest.raises(ValueError):
+        checkpoint.load_state(b, path)
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "mxfp8"])
+def test_stage_per_rank_blobs(tmp_path, fmt):
+    cfg = get_config("tiny-moe")
+    src = RandomSource(cfg, seed=2)
+    d = str(tmp_path / "staged")
+    stage.stage(cfg, src, d, fmt, ep_size=2)
+    man = json.load(open(d + "/manifest.json"))
+    assert man["files"] == ["rank00.safetensors", "rank01.safetensors"]
+    for r in range(2):
+        w = stage.load_staged(d, r, device="cpu")
+        ref = build_weights(cfg, src, fmt, "cpu", ep_rank=r, ep_size=2)
+        assert w.ep_rank == r and w.layers[0].w13.groups == cfg.n_experts // 2
+        assert torch.equal(w.layers[1].w13.dequantized(), ref.layers[1].w13.dequantized())
+        assert torch.equal(w.layers[0].wqkv.dequantized(), ref.layers[0].wqkv.dequantized())
+        assert torch.equal(w.embed, ref.embed)
