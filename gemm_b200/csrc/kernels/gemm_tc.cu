@@ -169,10 +169,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     fence_barrier_init();
     tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX);
   }
+  __syncthreads();                                   // barriers and the abort flag are initialised for everyone
   if (args.wait_n > 0) {
     // Rows and segment tables are written by peer GPUs: wait for every source's flag of this epoch, then make the
     // observed data visible to the TMA (async proxy) reads that follow.
-    __syncthreads();
     if (threadIdx.x == 0) {
       const uint32_t want = *args.epoch_ptr;
       for (int i = 0; i < args.wait_n; ++i)
