@@ -93,16 +93,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // of the CTA returns false within ~1k polls.  Returns true when the phase completed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           KernelStatus* st, int where, int aux = 0) {
-  if (mbar_try_wait(bar, parity)) return true;
-  // A failed try_wait has already blocked for the hardware's own time limit, so the clock is read on every retry.
-  const uint64_t t0 = globaltimer_ns();
-  for (;;) {
+  // Fast path: plain polling.  A failed try_wait blocks for a hardware time limit of unknown length, so after a
+  // short burst the clock (and the CTA's abort flag) is consulted every 16 polls.
+#pragma unroll 1
+  for (int it = 0; it < 256; ++it)
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kMbarBudgetNs) {
-      *abort_flag = 1;
-      report_status(st, ST_TIMEOUT_MBAR, where, aux, (int)parity, 0);
-      return false;
+  const uint64_t t0 = globaltimer_ns();
+#pragma unroll 1
+  for (uint32_t it = 0;; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 15u) == 15u) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kMbarBudgetNs) {
+        *abort_flag = 1;
+        report_status(st, ST_TIMEOUT_MBAR, where, aux, (int)parity, 0);
+        return false;
+      }
     }
   }
 }
