@@ -28,6 +28,8 @@ __device__ __forceinline__ float4 bf16x4_to_f4(uint2 v) {
 // ------------------------------------------------------------------------------------------ barrier
 // flags: uint32 [world] in every heap at flags_off.  One thread per peer.
 __global__ void fabric_barrier_kernel(PeerTable pt, size_t flags_off, uint32_t* epoch_ctr, KernelStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   const uint32_t epoch = *epoch_ctr + 1;
   const int p = threadIdx.x;
   if (p < pt.world) {
@@ -47,6 +49,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 allreduce_oneshot_kernel(PeerTable pt, size_t data_off, size_t flags_off, const T* __restrict__ in, T* __restrict__ out,
                          long n, long max_elems, uint32_t* epoch_ctr, unsigned* done_ctr, KernelStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int EPV = 16 / sizeof(T);
   const uint32_t epoch = *epoch_ctr + 1;
   const int chunks = gridDim.x, c = blockIdx.x;
@@ -99,6 +103,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 allreduce_twoshot_kernel(PeerTable pt, size_t in_off, size_t out_off, size_t flags_off, long n, uint32_t* epoch_ctr,
                          unsigned* done_ctr, KernelStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int EPV = 16 / sizeof(T);
   const uint32_t epoch = *epoch_ctr + 1;
   const int chunks = gridDim.x, c = blockIdx.x, W = pt.world;
@@ -152,6 +158,8 @@ allreduce_twoshot_kernel(PeerTable pt, size_t in_off, size_t out_off, size_t fla
 __global__ void __launch_bounds__(256)
 push_exchange_kernel(PeerTable pt, size_t out_off, size_t flags_off, const char* __restrict__ in, size_t bytes_per_dst,
                      size_t dst_stride_in, uint32_t* epoch_ctr, unsigned* done_ctr, KernelStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   const uint32_t epoch = *epoch_ctr + 1;
   const int chunks = gridDim.x, c = blockIdx.x;
   const size_t nvec = bytes_per_dst / 16, per = (nvec + chunks - 1) / chunks;
@@ -180,6 +188,8 @@ push_exchange_kernel(PeerTable pt, size_t out_off, size_t flags_off, const char*
 __global__ void __launch_bounds__(256)
 argmax_allreduce_kernel(PeerTable pt, size_t data_off, size_t flags_off, const float* __restrict__ val, const int* __restrict__ idx,
                         int* __restrict__ out_idx, float* __restrict__ out_val, int rows, int max_rows, uint32_t* epoch_ctr, KernelStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   const uint32_t epoch = *epoch_ctr + 1;
   for (int p = 0; p < pt.world; ++p) {
     int2* dst = reinterpret_cast<int2*>((char*)pt.base[p] + data_off) + (size_t)pt.rank * max_rows;
@@ -238,6 +248,8 @@ __device__ __forceinline__ int ep_e8m0(float amax) {
 
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(PeerTable pt, EpDispatchArgs a) {
+  pdl_wait();
+  pdl_trigger();
   const uint32_t epoch = *a.epoch_ctr;          // the plan kernel advanced the epoch for this layer
   const int vec_per_row = a.hidden >> 3;
   const long total_rows = (long)pt.world * a.region_rows;
@@ -302,7 +314,9 @@ ep_dispatch_kernel(PeerTable pt, EpDispatchArgs a) {
 }
 
 // Advances a device-resident epoch counter (one thread); used where no other kernel can carry the tick.
-__global__ void epoch_tick_kernel(uint32_t* ctr) { *ctr = *ctr + 1; }
+__global__ void epoch_tick_kernel(uint32_t* ctr) {
+  pdl_wait();
+  pdl_trigger(); *ctr = *ctr + 1; }
 
 }  // namespace gb
 
@@ -340,7 +354,7 @@ static PeerTable make_table(void* const* bases, int world, int rank) {
 
 GB_API int gb_fabric_barrier(void* const* bases, int world, int rank, size_t flags_off, void* epoch_ctr, void* status, cudaStream_t stream) {
   if (world > kMaxRanks) return fail("fabric: world > 8%s");
-  fabric_barrier_kernel<<<1, 32, 0, stream>>>(make_table(bases, world, rank), flags_off, (uint32_t*)epoch_ctr, (KernelStatus*)status);
+  launch_k(fabric_barrier_kernel, 1, 32, 0, stream, make_table(bases, world, rank), flags_off, (uint32_t*)epoch_ctr, (KernelStatus*)status);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -352,8 +366,8 @@ GB_API int gb_allreduce_oneshot(void* const* bases, int world, int rank, size_t 
   const int esz = dtype == 0 ? 4 : 2;
   if ((n * esz) % 16 || n > max_elems || (max_elems * esz) % 16) return fail("allreduce_oneshot: size must be a multiple of 16 bytes and fit the slot%s");
   PeerTable pt = make_table(bases, world, rank);
-  if (dtype == 0) allreduce_oneshot_kernel<float><<<chunks, 256, 0, stream>>>(pt, data_off, flags_off, (const float*)in, (float*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
-  else allreduce_oneshot_kernel<__nv_bfloat16><<<chunks, 256, 0, stream>>>(pt, data_off, flags_off, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
+  if (dtype == 0) launch_k(allreduce_oneshot_kernel<float>, chunks, 256, 0, stream, pt, data_off, flags_off, (const float*)in, (float*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
+  else launch_k(allreduce_oneshot_kernel<__nv_bfloat16>, chunks, 256, 0, stream, pt, data_off, flags_off, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -364,8 +378,8 @@ GB_API int gb_allreduce_twoshot(void* const* bases, int world, int rank, size_t 
   const int esz = dtype == 0 ? 4 : 2;
   if ((n * esz) % (16 * world)) return fail("allreduce_twoshot: bytes must be a multiple of 16 * world%s");
   PeerTable pt = make_table(bases, world, rank);
-  if (dtype == 0) allreduce_twoshot_kernel<float><<<chunks, 256, 0, stream>>>(pt, in_off, out_off, flags_off, n, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
-  else allreduce_twoshot_kernel<__nv_bfloat16><<<chunks, 256, 0, stream>>>(pt, in_off, out_off, flags_off, n, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
+  if (dtype == 0) launch_k(allreduce_twoshot_kernel<float>, chunks, 256, 0, stream, pt, in_off, out_off, flags_off, n, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
+  else launch_k(allreduce_twoshot_kernel<__nv_bfloat16>, chunks, 256, 0, stream, pt, in_off, out_off, flags_off, n, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -374,7 +388,7 @@ GB_API int gb_push_exchange(void* const* bases, int world, int rank, size_t out_
                             size_t dst_stride_in, int chunks, void* epoch_ctr, void* done_ctr, void* status, cudaStream_t stream) {
   if (world > kMaxRanks) return fail("fabric: world > 8%s");
   if (bytes_per_dst % 16 || dst_stride_in % 16) return fail("push_exchange: sizes must be multiples of 16 bytes%s");
-  push_exchange_kernel<<<chunks, 256, 0, stream>>>(make_table(bases, world, rank), out_off, flags_off, (const char*)in, bytes_per_dst,
+  launch_k(push_exchange_kernel, chunks, 256, 0, stream, make_table(bases, world, rank), out_off, flags_off, (const char*)in, bytes_per_dst,
                                                    dst_stride_in, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -384,7 +398,7 @@ GB_API int gb_argmax_allreduce(void* const* bases, int world, int rank, size_t d
                                int* out_idx, float* out_val, int rows, int max_rows, void* epoch_ctr, void* status, cudaStream_t stream) {
   if (world > kMaxRanks) return fail("fabric: world > 8%s");
   if (rows > max_rows) return fail("argmax_allreduce: too many rows%s");
-  argmax_allreduce_kernel<<<1, 256, 0, stream>>>(make_table(bases, world, rank), data_off, flags_off, val, idx, out_idx, out_val, rows, max_rows,
+  launch_k(argmax_allreduce_kernel, 1, 256, 0, stream, make_table(bases, world, rank), data_off, flags_off, val, idx, out_idx, out_val, rows, max_rows,
                                                  (uint32_t*)epoch_ctr, (KernelStatus*)status);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -404,13 +418,13 @@ GB_API int gb_ep_dispatch(void* const* bases, int world, int rank, const void* h
   const long total_rows = (long)world * region_rows;
   int grid = (int)std::min<long>((total_rows + 7) / 8, (long)sm_count() * 8);
   if (grid < 1) grid = 1;
-  ep_dispatch_kernel<<<grid, 256, 0, stream>>>(make_table(bases, world, rank), a);
+  launch_k(ep_dispatch_kernel, grid, 256, 0, stream, make_table(bases, world, rank), a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 GB_API int gb_epoch_tick(void* ctr, cudaStream_t stream) {
-  epoch_tick_kernel<<<1, 1, 0, stream>>>((uint32_t*)ctr);
+  launch_k(epoch_tick_kernel, 1, 1, 0, stream, (uint32_t*)ctr);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

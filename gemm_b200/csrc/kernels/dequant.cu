@@ -198,6 +198,8 @@ __device__ float block_elem(int type, const uint8_t* b, int i) {
 // Whole tensor -> bf16, one thread per element (coalesced writes; reads hit the same block within a warp).
 __global__ void __launch_bounds__(256)
 dequant_bf16_kernel(const uint8_t* __restrict__ src, __nv_bfloat16* __restrict__ dst, long n, int type, int blk, int bytes) {
+  pdl_wait();
+  pdl_trigger();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const long bi = i / blk;
@@ -211,6 +213,8 @@ template <int M>
 __global__ void __launch_bounds__(256)
 gemv_quant_kernel(const uint8_t* __restrict__ w, const __nv_bfloat16* __restrict__ x, float* __restrict__ y, int rows, int k, int type, int blk,
                   int bytes, long row_bytes, int ldx, int ldy) {
+  pdl_wait();
+  pdl_trigger();
   const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -256,7 +260,7 @@ GB_API int gb_dequant_bf16(const void* src, void* dst, long n, int type, cudaStr
   if (blk == 0) return fail("dequant: unsupported ggml type%s %ld", "", (long)type);
   if (n % blk) return fail("dequant: element count is not a multiple of the block size%s");
   if (n <= 0) return 0;
-  dequant_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const uint8_t*)src, (__nv_bfloat16*)dst, n, type, blk, bytes);
+  launch_k(dequant_bf16_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const uint8_t*)src, (__nv_bfloat16*)dst, n, type, blk, bytes);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -271,7 +275,7 @@ GB_API int gb_gemv_quant(const void* w, const void* x, float* y, int rows, int k
   if (rows <= 0) return 0;
   const long row_bytes = (long)(k / blk) * bytes;
   const int blocks = (rows + 7) / 8;
-#define GB_GEMV(MV) gemv_quant_kernel<MV><<<blocks, 256, 0, stream>>>((const uint8_t*)w, (const __nv_bfloat16*)x, y, rows, k, type, blk, bytes, row_bytes, ldx, ldy)
+#define GB_GEMV(MV) launch_k(gemv_quant_kernel<MV>, blocks, 256, 0, stream, (const uint8_t*)w, (const __nv_bfloat16*)x, y, rows, k, type, blk, bytes, row_bytes, ldx, ldy)
   switch (m) { case 1: GB_GEMV(1); break; case 2: GB_GEMV(2); break; case 3: GB_GEMV(3); break; case 4: GB_GEMV(4); break;
                case 5: GB_GEMV(5); break; case 6: GB_GEMV(6); break; case 7: GB_GEMV(7); break; default: GB_GEMV(8); }
 #undef GB_GEMV

@@ -45,6 +45,8 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
 // ------------------------------------------------------------------------------------------ embed
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
                              int n_tok, int hidden, int vocab) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -62,9 +64,21 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
                const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ out_q,
                uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out, int sf32,
                const float* __restrict__ partials, int n_partials, long partial_stride, const uint32_t* wait_flags, int wait_n,
-               const uint32_t* epoch_ptr, KernelStatus* st) {
+               const uint32_t* epoch_ptr, KernelStatus* st, const __nv_bfloat16* __restrict__ comb_y, const int* __restrict__ comb_rows,
+               const float* __restrict__ comb_w, int comb_k, int comb_ld) {
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x;
   const int nvec = hidden >> 3;
+  __shared__ int c_rows[16];
+  __shared__ float c_w[16];
+  if (comb_y != nullptr) {
+    // MoE combine fused into its consumer: delta[row] = sum_j w[row, j] * y[pair_row[row, j]]
+    if (threadIdx.x < comb_k) {
+      c_rows[threadIdx.x] = comb_rows[(size_t)row * comb_k + threadIdx.x];
+      c_w[threadIdx.x] = comb_w != nullptr ? comb_w[(size_t)row * comb_k + threadIdx.x] : 1.0f;
+    }
+  }
   if (wait_n > 0) {
     // the partial sums of a tensor-parallel projection are stored here by the peers: wait for every rank's flag
     __shared__ int failed;
@@ -76,6 +90,7 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
     __syncthreads();
     if (failed) return;
   }
+  if (comb_y != nullptr) __syncthreads();
   float v[VPT][8];
   float ss = 0.f;
 #pragma unroll
@@ -96,6 +111,21 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) r[j] = __bfloat162float(__float2bfloat16(r[j] + d[j]));
+          store8(residual + (size_t)row * ld_in + vi * 8, r);
+        } else if (comb_y != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) d[j] = 0.f;
+          for (int c = 0; c < comb_k; ++c) {
+            const int cr = c_rows[c];
+            if (cr < 0) continue;
+            float yv[8];
+            load8(comb_y + (size_t)cr * comb_ld + vi * 8, yv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) d[j] += c_w[c] * yv[j];
+          }
+          // same roundings as the unfused pair of kernels: the combined row is bf16, then the residual sum is bf16
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[j] = __bfloat162float(__float2bfloat16(r[j] + __bfloat162float(__float2bfloat16(d[j]))));
           store8(residual + (size_t)row * ld_in + vi * 8, r);
         } else if (delta != nullptr) {
           load8(delta + (size_t)row * ld_in + vi * 8, d);
@@ -162,6 +192,8 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict
                     const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int n_tok, int hq, int hkv,
                     int rope_pairs, float theta, float eps, int ld_qkv, float q_scale) {
+  pdl_wait();
+  pdl_trigger();
   constexpr int EPL = D / 32;            // elements per lane, index = lane + 32 * i
   const int heads = hq + 2 * hkv;
   const long gw = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -241,6 +273,8 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict
 
 // ------------------------------------------------------------------------------------------ silu * up
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, long rows, int inter, int ld) {
+  pdl_wait();
+  pdl_trigger();
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const int vec_per_row = inter >> 3;
   if (idx >= rows * vec_per_row) return;
@@ -260,6 +294,8 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_
 __global__ void __launch_bounds__(256)
 mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src_rows, uint8_t* __restrict__ out_q,
                 uint8_t* __restrict__ out_sf, long out_rows, int k, int ld_in, int sf32) {
+  pdl_wait();
+  pdl_trigger();
   const int vec_per_row = k >> 3;
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const bool act = idx < out_rows * vec_per_row;
@@ -291,6 +327,8 @@ mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ sr
 __global__ void __launch_bounds__(256)
 mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src_rows, uint8_t* __restrict__ out_q,
                      uint8_t* __restrict__ out_sf, long out_rows, int k, int ld_in, int sf32) {
+  pdl_wait();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const long warp0 = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, n_warps = ((long)gridDim.x * blockDim.x) >> 5;
   const int vec_per_row = k >> 3;
@@ -318,6 +356,8 @@ mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict
 
 // ------------------------------------------------------------------------------------------ casts
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
+  pdl_wait();
+  pdl_trigger();
   const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = __float2bfloat16(in[i]);
 }
@@ -326,6 +366,8 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16
 // every live sequence advances by one position; its next slot comes from the block table.
 __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ kv_len, int* __restrict__ slots,
                                       const int* __restrict__ block_table, const int* __restrict__ live, int max_pages, int page_size, int n) {
+  pdl_wait();
+  pdl_trigger();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= n) return;
   if (live != nullptr && live[b] == 0) return;
@@ -343,7 +385,7 @@ using namespace gb;
 GB_API int gb_decode_advance(int* positions, int* kv_len, int* slots, const int* block_table, const int* live, int max_pages,
                              int page_size, int n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  decode_advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, kv_len, slots, block_table, live, max_pages, page_size, n);
+  launch_k(decode_advance_kernel, (n + 127) / 128, 128, 0, stream, positions, kv_len, slots, block_table, live, max_pages, page_size, n);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -351,7 +393,7 @@ GB_API int gb_decode_advance(int* positions, int* kv_len, int* slots, const int*
 GB_API int gb_embed(const int* ids, const void* table, void* out, int n_tok, int hidden, int vocab, cudaStream_t stream) {
   if (hidden % 8) return fail("embed: hidden %% 8 != 0%s");
   if (n_tok <= 0) return 0;
-  embed_kernel<<<n_tok, 128, 0, stream>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, n_tok, hidden, vocab);
+  launch_k(embed_kernel, n_tok, 128, 0, stream, ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, n_tok, hidden, vocab);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -360,14 +402,18 @@ GB_API int gb_embed(const int* ids, const void* table, void* out, int n_tok, int
 // out (bf16) and out_q/out_sf (MXFP8) are optional outputs.
 static int rmsnorm_launch(void* residual, const void* delta, const void* x_in, const void* weight, void* out, void* out_q, void* out_sf,
                           int rows, int hidden, float eps, int ld_in, int ld_out, int sf32, const float* partials, int n_partials,
-                          long partial_stride, const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream) {
+                          long partial_stride, const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream,
+                          const void* comb_y = nullptr, const int* comb_rows = nullptr, const float* comb_w = nullptr, int comb_k = 0,
+                          int comb_ld = 0) {
+  if (comb_k > 16) return fail("rmsnorm: combine of more than 16 rows%s");
   if (hidden % 8 || hidden > 256 * 8 * 4) return fail("rmsnorm: hidden must be a multiple of 8 and <= 8192%s");
   if (out_q != nullptr && hidden % 128) return fail("rmsnorm: MXFP8 output needs hidden %% 128 == 0%s");
   if (rows <= 0) return 0;
   const int nvec = hidden / 8;
-#define GB_RMS(V) rmsnorm_kernel<V><<<rows, 256, 0, stream>>>((__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, \
+#define GB_RMS(V) launch_k(rmsnorm_kernel<V>, rows, 256, 0, stream, (__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, \
     (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out, sf32, \
-    partials, n_partials, partial_stride, (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status)
+    partials, n_partials, partial_stride, (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status, \
+    (const __nv_bfloat16*)comb_y, comb_rows, comb_w, comb_k, comb_ld)
   if (nvec <= 256) GB_RMS(1); else if (nvec <= 512) GB_RMS(2); else if (nvec <= 768) GB_RMS(3); else GB_RMS(4);
 #undef GB_RMS
   GB_CUDA_OK(cudaGetLastError());
@@ -389,13 +435,22 @@ GB_API int gb_rmsnorm_reduce(void* residual, const float* partials, int n_partia
                         partial_stride, wait_flags, wait_n, epoch_ptr, status, stream);
 }
 
+// residual[t] += sum_j w[t, j] * y[pair_row[t * k + j]] (the MoE combine), then RMSNorm: the combine never makes a round trip
+// through memory.  Optional bounded wait on wait_flags (expert-parallel: the rows of y are stored by the experts' GPUs).
+GB_API int gb_rmsnorm_combine(void* residual, const void* y, const int* pair_row, const float* weights, int k, int ld_y, const void* weight,
+                              void* out, void* out_q, void* out_sf, int rows, int hidden, float eps, int sf32, const void* wait_flags,
+                              int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream) {
+  return rmsnorm_launch(residual, nullptr, nullptr, weight, out, out_q, out_sf, rows, hidden, eps, hidden, hidden, sf32, nullptr, 0, 0,
+                        wait_flags, wait_n, epoch_ptr, status, stream, y, pair_row, weights, k, ld_y);
+}
+
 GB_API int gb_qk_norm_rope(const void* qkv, const int* positions, const int* slots, const void* q_w, const void* k_w, void* q_out,
                            void* k_cache, void* v_cache, int n_tok, int hq, int hkv, int head_dim, int rope_pairs, float theta,
                            float eps, int ld_qkv, float q_scale, cudaStream_t stream) {
   if (n_tok <= 0) return 0;
   const long warps = (long)n_tok * (hq + 2 * hkv);
   const int blocks = (int)((warps + 7) / 8);
-#define GB_QK(DV) qk_norm_rope_kernel<DV><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)qkv, positions, slots, \
+#define GB_QK(DV) launch_k(qk_norm_rope_kernel<DV>, blocks, 256, 0, stream, (const __nv_bfloat16*)qkv, positions, slots, \
     (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
     n_tok, hq, hkv, rope_pairs, theta, eps, ld_qkv, q_scale)
   if (head_dim == 64) GB_QK(64); else if (head_dim == 128) GB_QK(128); else if (head_dim == 256) GB_QK(256);
@@ -409,7 +464,7 @@ GB_API int gb_silu_mul(const void* gate_up, void* out, long rows, int inter, int
   if (inter % 8) return fail("silu_mul: inter %% 8 != 0%s");
   const long n = rows * (inter / 8);
   if (n <= 0) return 0;
-  silu_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inter, ld);
+  launch_k(silu_mul_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inter, ld);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -420,18 +475,18 @@ GB_API int gb_mx_quant(const void* in, const int* src_rows, void* out_q, void* o
   if (n <= 0) return 0;
   if (src_rows != nullptr && k % 256 == 0) {
     const long blocks = std::min<long>((out_rows + 7) / 8, (long)sm_count() * 16);
-    mx_quant_rows_kernel<<<(unsigned)blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
+    launch_k(mx_quant_rows_kernel, (unsigned)blocks, 256, 0, stream, (const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
     GB_CUDA_OK(cudaGetLastError());
     return 0;
   }
-  mx_quant_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
+  launch_k(mx_quant_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 GB_API int gb_cast_f32_bf16(const float* in, void* out, long n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  cast_f32_bf16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(in, (__nv_bfloat16*)out, n);
+  launch_k(cast_f32_bf16_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, in, (__nv_bfloat16*)out, n);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -73,6 +73,24 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Prologue that touches no global memory: it overlaps the tail of the previous kernel of the stream.
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&s_full[i], 1); }
+    mbar_init(p_ready, 128); mbar_init(o_ready, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256;
+  pdl_wait();
+  pdl_trigger();
+
   const int G = a.hq / a.hkv;
   const int tpt = 128 / G;                  // tokens per tile
   const int* wk = a.work + (size_t)blockIdx.x * 4;
@@ -93,20 +111,6 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   }
   const int n_blk = max(0, blk_hi - blk_lo);
 
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&s_full[i], 1); }
-    mbar_init(p_ready, 128); mbar_init(o_ready, 1);
-    *abort_flag = 0;
-    fence_barrier_init();
-    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-  }
-  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
 
   if (warp == 0) {
     if (lane == 0 && n_blk > 0) {
@@ -297,6 +301,8 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 // One warp per (token, head); D = 128 -> 4 floats per lane.
 __global__ void fa_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, __nv_bfloat16* __restrict__ out,
                                   float* __restrict__ out_lse, int splits, long rows) {
+  pdl_wait();
+  pdl_trigger();
   const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (w >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -363,14 +369,14 @@ GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache
     GB_CUDA_OK(cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  flash_attn_kernel<<<n_work, kFaThreads, smem, stream>>>(tmQ, tmK, tmV, a);
+  launch_k(flash_attn_kernel, n_work, kFaThreads, smem, stream, tmQ, tmK, tmV, a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 GB_API int gb_fa_combine(const float* part_o, const float* part_lse, void* out, float* out_lse, int splits, long rows, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  fa_combine_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(part_o, part_lse, (__nv_bfloat16*)out, out_lse, splits, rows);
+  launch_k(fa_combine_kernel, (unsigned)((rows * 32 + 255) / 256), 256, 0, stream, part_o, part_lse, (__nv_bfloat16*)out, out_lse, splits, rows);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -75,6 +75,9 @@ struct GemmArgs {
   // ---- extents of the caller's buffers in bytes (0 = unknown): every global access of the kernel that is not a TMA
   // tile is checked against them; a violation is recorded in the status word (ST_BAD_ARG) and the access is skipped.
   size_t sfa_bytes, sfb_bytes, out_bytes, out_sf_bytes;
+  // ---- weight layout: 0 = row-major [rows, k]; 1 = tiled [rows/128][k-blocks][128 rows][128 bytes], every 16 KB operand
+  // tile of the main loop is one contiguous block of memory (one DRAM burst sequence instead of 128 strided lines)
+  int w_tiled;
 };
 
 struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; int ks; int tile_id; };
@@ -169,7 +172,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     fence_barrier_init();
     tma_prefetch_desc(&tmW); tma_prefetch_desc(&tmX);
   }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   __syncthreads();                                   // barriers and the abort flag are initialised for everyone
+  pdl_wait();                                        // everything above overlapped the previous kernel's tail
+  pdl_trigger();                                     // at most one dependent grid is resident ahead of its turn
   if (args.wait_n > 0) {
     // Rows and segment tables are written by peer GPUs: wait for every source's flag of this epoch, then make the
     // observed data visible to the TMA (async proxy) reads that follow.
@@ -189,7 +195,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       if (!sane) report_status(args.status, ST_BAD_ARG, 130, i, st0, cn);
       s_start[i] = sane ? st0 : 0; s_count[i] = sane ? cn : 0;
     }
-  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -212,8 +217,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], NA * A_BYTES + B_BYTES + ((MODE == 1) ? (NA + SFB_ATOMS) * 512 : 0));
           const int kx = kb * KB_ELEMS;
-          tma_load_2d(st, &tmW, &full_bar[s], kx, t.w_row0);
-          if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], kx, t.w_row1);
+          if (args.w_tiled) {
+            tma_load_2d(st, &tmW, &full_bar[s], 0, ((t.w_row0 >> 7) * num_kb + kb) << 7);
+            if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], 0, ((t.w_row1 >> 7) * num_kb + kb) << 7);
+          } else {
+            tma_load_2d(st, &tmW, &full_bar[s], kx, t.w_row0);
+            if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], kx, t.w_row1);
+          }
           tma_load_2d(st + NA * A_BYTES, &tmX, &full_bar[s], kx, t.x_row0);
           if (MODE == 1) {
             uint8_t* sf = st + NA * A_BYTES + B_BYTES;
@@ -295,6 +305,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     TileCursor<TN> cur; Tile t;
     int acc = 0; uint32_t acc_ph = 0;
     bool ok = true;
+    const bool simple_store = !QUANT_OUT && args.amax_val == nullptr && args.peer_region_rows == 0 && args.row_map == nullptr &&
+                              args.peer_bcast == 0 && args.row_scale == nullptr && args.splits <= 1;
     for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
       if (!mbar_wait(&accf_bar[acc], acc_ph, abort_flag, args.status, 300, acc)) { ok = false; break; }
       tc_fence_after();
@@ -398,30 +410,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll 1
           for (int c = 0; c < TN && c < t.valid; c += 16) {
             uint32_t r0[16], r1[16];
+            float a0[16], a1[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              float a0 = 0.f, a1 = 0.f;
-              for (int sidx = 0; sidx < args.splits; ++sidx) {
-                const float* src = ws + (size_t)sidx * (NA * TN * 128);
-                a0 += __ldcg(src + (size_t)(c + j) * 128 + row);
-                if (DUAL) a1 += __ldcg(src + (size_t)(TN + c + j) * 128 + row);
+            for (int j = 0; j < 16; ++j) { a0[j] = 0.f; a1[j] = 0.f; }
+            // split order is fixed (deterministic sum); the 16 (32) loads of one split are independent of each other
+            for (int sidx = 0; sidx < args.splits; ++sidx) {
+              const float* src = ws + (size_t)sidx * (NA * TN * 128);
+              float l0[16], l1[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                l0[j] = __ldcg(src + (size_t)(c + j) * 128 + row);
+                if (DUAL) l1[j] = __ldcg(src + (size_t)(TN + c + j) * 128 + row);
               }
-              r0[j] = __float_as_uint(a0); r1[j] = __float_as_uint(a1);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) { a0[j] += l0[j]; if (DUAL) a1[j] += l1[j]; }
             }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { r0[j] = __float_as_uint(a0[j]); r1[j] = __float_as_uint(a1[j]); }
             finish_chunk(c, r0, r1);
           }
         }
         if (NACC == 2) { if (++acc == 2) { acc = 0; acc_ph ^= 1; } } else { acc_ph ^= 1; }
         continue;
       }
+      if (simple_store) {
+        // Common case (plain row-major bf16 / f32 result): every decision is made once per tile, the inner loop is
+        // convert + store.  The tile's last element is checked against the buffer's extent.
+        const size_t esz = args.out_f32 ? 4 : 2;
+        const size_t last = ((size_t)(t.x_row0 + t.valid - 1) * args.ldo + n) * esz;
+        bool store_ok = n_ok;
+        if (store_ok && args.out_bytes != 0 && last >= args.out_bytes) {
+          report_status(args.status, ST_BAD_ARG, 312, t.x_row0 + t.valid - 1, n, ti);
+          store_ok = false;
+        }
+        __nv_bfloat16* o16 = (__nv_bfloat16*)args.out + (size_t)t.x_row0 * args.ldo + n;
+        float* o32 = (float*)args.out + (size_t)t.x_row0 * args.ldo + n;
 #pragma unroll 1
-      for (int c = 0; c < TN; c += 16) {
-        uint32_t r0[16], r1[16];
-        tmem_ld_x16(tacc + c, r0);
-        if (DUAL) tmem_ld_x16(tacc + TN + c, r1);
-        tc_wait_ld();
-        if (c >= t.valid) continue;             // uniform across the CTA's epilogue warps
-        finish_chunk(c, r0, r1);
+        for (int c = 0; c < TN; c += 16) {
+          uint32_t r0[16], r1[16];
+          tmem_ld_x16(tacc + c, r0);
+          if (DUAL) tmem_ld_x16(tacc + TN + c, r1);
+          tc_wait_ld();
+          if (c >= t.valid) continue;
+          if (!store_ok) continue;
+          if (c + 16 <= t.valid) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = __uint_as_float(r0[j]);
+              if (DUAL) v = silu_f(v) * __uint_as_float(r1[j]);
+              v += bias;
+              if (args.out_f32) o32[(size_t)(c + j) * args.ldo] = v;
+              else o16[(size_t)(c + j) * args.ldo] = __float2bfloat16(v);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = __uint_as_float(r0[j]);
+              if (DUAL) v = silu_f(v) * __uint_as_float(r1[j]);
+              v += bias;
+              if (c + j < t.valid) {
+                if (args.out_f32) o32[(size_t)(c + j) * args.ldo] = v;
+                else o16[(size_t)(c + j) * args.ldo] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < TN; c += 16) {
+          uint32_t r0[16], r1[16];
+          tmem_ld_x16(tacc + c, r0);
+          if (DUAL) tmem_ld_x16(tacc + TN + c, r1);
+          tc_wait_ld();
+          if (c >= t.valid) continue;             // uniform across the CTA's epilogue warps
+          finish_chunk(c, r0, r1);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -470,7 +533,7 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmArgs 
   }
   int grid = sm_count();
   if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
-  kern<<<grid, kGemmThreads, smem, stream>>>(tmW, tmX, a);
+  launch_k(kern, grid, kGemmThreads, smem, stream, tmW, tmX, a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -506,7 +569,7 @@ struct GemmExtras {
 };
 
 // Flags of gb_gemm.
-enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8 };
+enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8, GEMM_W_TILED = 16 };
 
 // Linear layer on tensor cores.
 //   w        [w_rows, k] row-major (bf16, or e4m3 bytes when GEMM_MX), w_rows = groups * w_rows_per_group
@@ -537,13 +600,23 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   CUtensorMap tmW, tmX;
   const TmapDtype dt = mx ? TM_U8 : TM_BF16;
   const uint32_t box_k = mx ? 128 : 64;
-  if (make_tmap_2d(&tmW, w, dt, (uint64_t)k, (uint64_t)w_rows, (uint64_t)ldw * esz, box_k, 128, TM_SW_128)) return -1;
+  const bool w_tiled = flags & GEMM_W_TILED;
+  if (w_tiled) {
+    // tiled weights: [ceil(rows / 128)][ceil(k / box_k)][128][box_k]; a 2-D map whose rows are the 128-byte tile rows
+    if (num_groups > 0 && (w_rows_per_group % 128 != 0 || up_row_offset % 128 != 0)) return fail("gemm: tiled weights need 128-row aligned groups%s");
+    if (dual && up_row_offset % 128 != 0) return fail("gemm: tiled weights need a 128-row aligned up offset%s");
+    const uint64_t kbs = ((uint64_t)k + box_k - 1) / box_k;
+    const uint64_t rb = ((uint64_t)w_rows + 127) / 128;
+    if (rb * kbs * 128 >= (1ull << 31)) return fail("gemm: tiled weight too large for 32-bit tile coordinates%s");
+    if (make_tmap_2d(&tmW, w, dt, box_k, rb * kbs * 128, 128, box_k, 128, TM_SW_128)) return -1;
+  } else if (make_tmap_2d(&tmW, w, dt, (uint64_t)k, (uint64_t)w_rows, (uint64_t)ldw * esz, box_k, 128, TM_SW_128)) return -1;
   if (make_tmap_2d(&tmX, x, dt, (uint64_t)k, (uint64_t)x_rows, (uint64_t)ldx * esz, box_k, (uint32_t)tn, TM_SW_128)) return -1;
   GemmArgs a;
   memset(&a, 0, sizeof(a));
   a.n_out = n_out; a.k = k; a.m_tok = m_tok; a.num_groups = num_groups; a.w_rows_per_group = w_rows_per_group;
   a.up_row_offset = up_row_offset; a.seg_start = seg_start; a.seg_count = seg_count;
   a.sfa = (const uint8_t*)sfa; a.sfb = (const uint8_t*)sfb; a.out = out; a.ldo = ldo; a.out_f32 = (flags & GEMM_OUT_F32) ? 1 : 0;
+  a.w_tiled = w_tiled ? 1 : 0;
   a.out_sf = (uint8_t*)out_sf; a.bias = bias; a.row_map = row_map; a.row_scale = row_scale; a.status = (KernelStatus*)status;
   if (ex != nullptr) {
     a.w_group_mod = ex->w_group_mod; a.wait_flags = ex->wait_flags; a.wait_n = ex->wait_n; a.epoch_ptr = ex->epoch_ptr;

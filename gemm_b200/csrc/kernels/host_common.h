@@ -46,4 +46,24 @@ inline int make_tmap_2d(CUtensorMap* out, const void* base, TmapDtype dt, uint64
 
 int sm_count();   // SMs of the current device (cached per device)
 
+// Programmatic dependent launch: when on (default; gb_set_pdl(0) or GB_PDL=0 turns it off), every kernel of this library
+// is launched with the "programmatic stream serialization" attribute.  Each kernel signals
+// griddepcontrol.launch_dependents as soon as it starts and executes griddepcontrol.wait before its first access to
+// global memory, so the launch latency and the prologue (barrier init, TMEM allocation, descriptor prefetch) of kernel
+// N+1 overlap the tail of kernel N while all memory dependencies stay those of a plain stream.
+bool pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<Args&&>(args)...);
+}
+
 }  // namespace gb

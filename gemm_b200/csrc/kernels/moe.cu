@@ -23,6 +23,8 @@ constexpr int kMaxTopK = 16;
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
                  int n_tok, int n_exp, int k, int mode, int renorm, float routed_scale, int ld) {
+  pdl_wait();
+  pdl_trigger();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (w >= n_tok) return;
   const int lane = threadIdx.x & 31;
@@ -90,6 +92,8 @@ constexpr int kPlanBlock = 256;
 // block_hist[b][e] = pairs of block b routed to expert e (pairs whose expert is outside [e_lo, e_hi) are dropped)
 __global__ void __launch_bounds__(kPlanBlock)
 moe_hist_kernel(const int* __restrict__ ids, int* __restrict__ block_hist, long n_pairs, int n_exp) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ int sh[];
   for (int e = threadIdx.x; e < n_exp; e += kPlanBlock) sh[e] = 0;
   __syncthreads();
@@ -102,6 +106,8 @@ moe_hist_kernel(const int* __restrict__ ids, int* __restrict__ block_hist, long 
 // One block per expert: exclusive scan of block_hist[:, e] over the blocks (in place) and seg_count[e].
 __global__ void __launch_bounds__(256)
 moe_scan_kernel(int* __restrict__ block_hist, int* __restrict__ seg_count, int n_blocks, int n_exp) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int part[256];
   const int e = blockIdx.x, t = threadIdx.x;
   const int per = (n_blocks + 255) / 256;
@@ -127,6 +133,8 @@ moe_scan_kernel(int* __restrict__ block_hist, int* __restrict__ seg_count, int n
 __global__ void __launch_bounds__(512)
 moe_seg_kernel(const int* __restrict__ seg_count, int* __restrict__ seg_start, int* __restrict__ region_rows_used,
                int n_exp, int experts_per_region, int region_rows, int align, unsigned* epoch_ctr) {
+  pdl_wait();
+  pdl_trigger();
   const int r = threadIdx.x;
   __shared__ int cnt[512], start[512];
   if (r == 0 && epoch_ctr != nullptr) *epoch_ctr = *epoch_ctr + 1;     // one tick per MoE layer call (expert-parallel epoch)
@@ -148,6 +156,8 @@ moe_seg_kernel(const int* __restrict__ seg_count, int* __restrict__ seg_start, i
 __global__ void __launch_bounds__(kPlanBlock)
 moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ block_hist, const int* __restrict__ seg_start,
                    int* __restrict__ pair_row, int* __restrict__ row_token, long n_pairs, int n_exp, int k, long capacity) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int se[kPlanBlock];
   const long i = (long)blockIdx.x * kPlanBlock + threadIdx.x;
   int e = -1;
@@ -163,11 +173,59 @@ moe_scatter_kernel(const int* __restrict__ ids, const int* __restrict__ block_hi
   else pair_row[i] = -1;
 }
 
+// The whole plan in one CTA for decode-sized batches (n_pairs <= kSmallPairs): histogram, aligned segment starts,
+// rank of every pair inside its expert (by pair index, so the order is the one of the multi-kernel path) and the
+// scatter, all from shared memory.  Replaces one memset and four launches.
+constexpr int kSmallPairs = 2048;
+__global__ void __launch_bounds__(1024)
+moe_plan_small_kernel(const int* __restrict__ ids, int* __restrict__ seg_start, int* __restrict__ seg_count,
+                      int* __restrict__ region_rows_used, int* __restrict__ pair_row, int* __restrict__ row_token, int n_pairs,
+                      int n_exp, int k, int experts_per_region, int region_rows, int align, int capacity, unsigned* epoch_ctr) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ int se[kSmallPairs];
+  __shared__ int cnt[512], start[512];
+  const int t = threadIdx.x;
+  if (t == 0 && epoch_ctr != nullptr) *epoch_ctr = *epoch_ctr + 1;
+  for (int e = t; e < n_exp; e += blockDim.x) cnt[e] = 0;
+  for (int r = t; r < capacity; r += blockDim.x) row_token[r] = -1;
+  __syncthreads();
+  for (int i = t; i < n_pairs; i += blockDim.x) {
+    int e = ids[i];
+    if (e < 0 || e >= n_exp) e = -1;
+    se[i] = e;
+    if (e >= 0) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (t < n_exp / experts_per_region) {
+    int pos = 0;
+    for (int i = 0; i < experts_per_region; ++i) {
+      const int ee = t * experts_per_region + i;
+      start[ee] = t * region_rows + pos;
+      pos += (cnt[ee] + align - 1) / align * align;
+    }
+    if (region_rows_used != nullptr) region_rows_used[t] = pos;
+  }
+  __syncthreads();
+  for (int e = t; e < n_exp; e += blockDim.x) { seg_start[e] = start[e]; seg_count[e] = cnt[e]; }
+  for (int i = t; i < n_pairs; i += blockDim.x) {
+    const int e = se[i];
+    if (e < 0) { pair_row[i] = -1; continue; }
+    int rank = 0;
+    for (int j = 0; j < i; ++j) rank += (se[j] == e);
+    const int row = start[e] + rank;
+    if (row < capacity) { pair_row[i] = row; row_token[row] = i / k; }
+    else pair_row[i] = -1;
+  }
+}
+
 // out[t, :] = sum_j w[t, j] * y[pair_row[t*k + j], :]   (bf16 in / out, fp32 accumulate, fixed order)
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pair_row, const float* __restrict__ weights,
                    __nv_bfloat16* __restrict__ out, int hidden, int k, int ld_y, const uint32_t* wait_flags, int wait_n,
                    const uint32_t* epoch_ptr, KernelStatus* st) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   __shared__ int rows[kMaxTopK];
   __shared__ float ws[kMaxTopK];
@@ -203,6 +261,8 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
 // Plain row gather (bf16): out[r] = in[src[r]] or zeros when src[r] < 0.
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src, __nv_bfloat16* __restrict__ out,
                                    long rows, int hidden, int ld_in) {
+  pdl_wait();
+  pdl_trigger();
   const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const int vpr = hidden >> 3;
   if (idx >= rows * vpr) return;
@@ -221,7 +281,7 @@ GB_API int gb_moe_route(const float* logits, const float* bias, int* ids, float*
                         int renorm, float routed_scale, int ld, cudaStream_t stream) {
   if (n_exp > 512 || k > kMaxTopK || k > n_exp) return fail("moe_route: need n_exp <= 512 and k <= 16%s");
   if (n_tok <= 0) return 0;
-  moe_route_kernel<<<(n_tok + 7) / 8, 256, 0, stream>>>(logits, bias, ids, weights, n_tok, n_exp, k, mode, renorm, routed_scale, ld);
+  launch_k(moe_route_kernel, (n_tok + 7) / 8, 256, 0, stream, logits, bias, ids, weights, n_tok, n_exp, k, mode, renorm, routed_scale, ld);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -232,12 +292,18 @@ GB_API int gb_moe_plan(const int* ids, int* workspace, int* seg_start, int* seg_
                        long capacity, void* epoch_ctr, cudaStream_t stream) {
   if (n_exp > 512) return fail("moe_plan: n_exp > 512%s");
   if (n_exp % experts_per_region) return fail("moe_plan: n_exp %% experts_per_region != 0%s");
+  if (n_pairs <= kSmallPairs && capacity < (1l << 30)) {
+    launch_k(moe_plan_small_kernel, 1, 1024, 0, stream, ids, seg_start, seg_count, region_rows_used, pair_row, row_token, (int)n_pairs,
+             n_exp, k, experts_per_region, region_rows, align, (int)capacity, (unsigned*)epoch_ctr);
+    GB_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   const int nb = (int)((n_pairs + kPlanBlock - 1) / kPlanBlock);
   GB_CUDA_OK(cudaMemsetAsync(row_token, 0xff, (size_t)capacity * sizeof(int), stream));
-  if (nb > 0) moe_hist_kernel<<<nb, kPlanBlock, n_exp * sizeof(int), stream>>>(ids, workspace, n_pairs, n_exp);
-  moe_scan_kernel<<<n_exp, 256, 0, stream>>>(workspace, seg_count, nb, n_exp);
-  moe_seg_kernel<<<1, 512, 0, stream>>>(seg_count, seg_start, region_rows_used, n_exp, experts_per_region, region_rows, align, (unsigned*)epoch_ctr);
-  if (nb > 0) moe_scatter_kernel<<<nb, kPlanBlock, 0, stream>>>(ids, workspace, seg_start, pair_row, row_token, n_pairs, n_exp, k, capacity);
+  if (nb > 0) launch_k(moe_hist_kernel, nb, kPlanBlock, n_exp * sizeof(int), stream, ids, workspace, n_pairs, n_exp);
+  launch_k(moe_scan_kernel, n_exp, 256, 0, stream, workspace, seg_count, nb, n_exp);
+  launch_k(moe_seg_kernel, 1, 512, 0, stream, seg_count, seg_start, region_rows_used, n_exp, experts_per_region, region_rows, align, (unsigned*)epoch_ctr);
+  if (nb > 0) launch_k(moe_scatter_kernel, nb, kPlanBlock, 0, stream, ids, workspace, seg_start, pair_row, row_token, n_pairs, n_exp, k, capacity);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -246,7 +312,7 @@ GB_API int gb_moe_combine(const void* y, const int* pair_row, const float* weigh
                           const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream) {
   if (hidden % 8 || k > kMaxTopK) return fail("moe_combine: hidden %% 8 != 0 or k > 16%s");
   if (n_tok <= 0) return 0;
-  moe_combine_kernel<<<n_tok, 256, 0, stream>>>((const __nv_bfloat16*)y, pair_row, weights, (__nv_bfloat16*)out, hidden, k, ld_y,
+  launch_k(moe_combine_kernel, n_tok, 256, 0, stream, (const __nv_bfloat16*)y, pair_row, weights, (__nv_bfloat16*)out, hidden, k, ld_y,
                                                (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -256,7 +322,7 @@ GB_API int gb_gather_rows(const void* in, const int* src, void* out, long rows, 
   if (hidden % 8) return fail("gather_rows: hidden %% 8 != 0%s");
   const long n = rows * (hidden / 8);
   if (n <= 0) return 0;
-  gather_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, src, (__nv_bfloat16*)out, rows, hidden, ld_in);
+  launch_k(gather_rows_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)in, src, (__nv_bfloat16*)out, rows, hidden, ld_in);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

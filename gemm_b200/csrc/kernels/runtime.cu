@@ -1,6 +1,7 @@
 // Process-wide runtime pieces of the kernel library: last-error string, the status word that
 // bounded waits report into, TMA descriptor encoding, device properties.
 #include "host_common.h"
+#include <stdlib.h>
 #include "sm100.cuh"
 #include <cudaTypedefs.h>
 #include <mutex>
@@ -58,6 +59,15 @@ int sm_count() {
   return cached[dev];
 }
 
+static int g_pdl = -1;
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("GB_PDL");
+    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
+}
+
 static __device__ KernelStatus g_status;
 
 }  // namespace gb
@@ -84,3 +94,10 @@ GB_API int gb_status_read(int* out16, int clear) {
 }
 
 GB_API int gb_sm_count() { return gb::sm_count(); }
+
+// Turn programmatic dependent launch on (1) or off (0) for every later launch of this library; returns the old setting.
+GB_API int gb_set_pdl(int on) {
+  const int old = gb::pdl_enabled() ? 1 : 0;
+  gb::g_pdl = on ? 1 : 0;
+  return old;
+}

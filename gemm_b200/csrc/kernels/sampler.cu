@@ -23,6 +23,8 @@ __device__ __forceinline__ void better(float& v, int& i, float ov, int oi) {
 template <typename T>
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const T* __restrict__ logits, int* __restrict__ out_idx, float* __restrict__ out_val, int vocab, long ld, int idx_offset) {
+  pdl_wait();
+  pdl_trigger();
   const T* row = logits + (size_t)blockIdx.x * ld;
   float bv = -FLT_MAX; int bi = 0x7fffffff;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -48,6 +50,8 @@ argmax_kernel(const T* __restrict__ logits, int* __restrict__ out_idx, float* __
 __global__ void __launch_bounds__(256)
 argmax_pairs_kernel(const float* __restrict__ val, const int* __restrict__ idx, int* __restrict__ out_idx, float* __restrict__ out_val,
                     int parts, int rows, int idx_offset) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   float bv = -FLT_MAX; int bi = 0x7fffffff;
   for (int p = threadIdx.x; p < parts; p += blockDim.x) better(bv, bi, val[(size_t)p * rows + r], idx[(size_t)p * rows + r]);
@@ -67,6 +71,8 @@ argmax_pairs_kernel(const float* __restrict__ val, const int* __restrict__ idx, 
 template <typename T>
 __global__ void __launch_bounds__(256)
 argmax_chunk_kernel(const T* __restrict__ logits, float* __restrict__ pval, int* __restrict__ pidx, int vocab, long ld, int rows) {
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.y, c = blockIdx.x, chunks = gridDim.x;
   const int per = (vocab + chunks - 1) / chunks;
   const int i0 = c * per, i1 = min(vocab, i0 + per);
@@ -103,6 +109,8 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 sample_kernel(const T* __restrict__ logits, int* __restrict__ out_idx, int vocab, long ld, float temperature, int top_k, float top_p,
               uint64_t seed, uint64_t step) {
+  pdl_wait();
+  pdl_trigger();
   const T* row = logits + (size_t)blockIdx.x * ld;
   __shared__ unsigned hist[256];
   __shared__ unsigned s_prefix, s_remaining;
@@ -193,15 +201,15 @@ using namespace gb;
 // dtype: 0 = f32, 1 = bf16.  idx_offset is added to the winning index (first vocabulary id of a shard).
 GB_API int gb_argmax(const void* logits, int* out_idx, float* out_val, int rows, int vocab, long ld, int dtype, int idx_offset, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (dtype == 0) argmax_kernel<float><<<rows, 1024, 0, stream>>>((const float*)logits, out_idx, out_val, vocab, ld, idx_offset);
-  else argmax_kernel<__nv_bfloat16><<<rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, out_idx, out_val, vocab, ld, idx_offset);
+  if (dtype == 0) launch_k(argmax_kernel<float>, rows, 1024, 0, stream, (const float*)logits, out_idx, out_val, vocab, ld, idx_offset);
+  else launch_k(argmax_kernel<__nv_bfloat16>, rows, 1024, 0, stream, (const __nv_bfloat16*)logits, out_idx, out_val, vocab, ld, idx_offset);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 GB_API int gb_argmax_pairs(const float* val, const int* idx, int* out_idx, float* out_val, int parts, int rows, int idx_offset, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_pairs_kernel<<<rows, 256, 0, stream>>>(val, idx, out_idx, out_val, parts, rows, idx_offset);
+  launch_k(argmax_pairs_kernel, rows, 256, 0, stream, val, idx, out_idx, out_val, parts, rows, idx_offset);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -211,9 +219,9 @@ GB_API int gb_argmax2(const void* logits, int* out_idx, float* out_val, float* p
                       int idx_offset, int chunks, cudaStream_t stream) {
   if (rows <= 0) return 0;
   dim3 grid(chunks, rows);
-  if (dtype == 0) argmax_chunk_kernel<float><<<grid, 256, 0, stream>>>((const float*)logits, pval, pidx, vocab, ld, rows);
-  else argmax_chunk_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)logits, pval, pidx, vocab, ld, rows);
-  argmax_pairs_kernel<<<rows, 256, 0, stream>>>(pval, pidx, out_idx, out_val, chunks, rows, idx_offset);
+  if (dtype == 0) launch_k(argmax_chunk_kernel<float>, grid, 256, 0, stream, (const float*)logits, pval, pidx, vocab, ld, rows);
+  else launch_k(argmax_chunk_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)logits, pval, pidx, vocab, ld, rows);
+  launch_k(argmax_pairs_kernel, rows, 256, 0, stream, pval, pidx, out_idx, out_val, chunks, rows, idx_offset);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -221,8 +229,8 @@ GB_API int gb_argmax2(const void* logits, int* out_idx, float* out_val, float* p
 GB_API int gb_sample(const void* logits, int* out_idx, int rows, int vocab, long ld, int dtype, float temperature, int top_k, float top_p,
                      unsigned long long seed, unsigned long long step, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (dtype == 0) sample_kernel<float><<<rows, 1024, 0, stream>>>((const float*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step);
-  else sample_kernel<__nv_bfloat16><<<rows, 1024, 0, stream>>>((const __nv_bfloat16*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step);
+  if (dtype == 0) launch_k(sample_kernel<float>, rows, 1024, 0, stream, (const float*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step);
+  else launch_k(sample_kernel<__nv_bfloat16>, rows, 1024, 0, stream, (const __nv_bfloat16*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -47,6 +47,15 @@ __device__ __forceinline__ void report_status(KernelStatus* st, int code, int wh
   }
 }
 
+// Programmatic dependent launch.  pdl_trigger(): the next kernel of the stream may be scheduled (it still blocks in its
+// own pdl_wait() until this grid has completed and its writes are visible).  pdl_wait(): returns once every kernel this
+// one depends on has completed; nothing before it may touch global memory that an earlier kernel writes or reads.
+// Both are no-ops for a kernel launched without the attribute.  Kernels here trigger right AFTER their own wait: a trigger
+// at kernel entry let whole chains of not-yet-runnable grids become resident at once and measured slower than plain
+// stream order on the decode step.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t;
 }

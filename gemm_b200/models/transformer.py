@@ -106,7 +106,7 @@ class SingleProcess:
         return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
 
     def materialize(self, delta) -> torch.Tensor:
-        return delta
+        return delta.materialize() if hasattr(delta, "materialize") else delta
 
     def moe_ffn(self, model: "Transformer", lw, h: torch.Tensor) -> Optional[torch.Tensor]:
         return None            # None -> the model runs its local MoE path
@@ -115,7 +115,7 @@ class SingleProcess:
 def apply_linear(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
     """``x W^T (+ bias)`` in the weight's format; ``x_mx`` is an already-quantised copy of ``x`` if the caller has one."""
     if lw.fmt == "bf16":
-        return gemm.linear(x, lw.w, bias=lw.bias, out_dtype=out_dtype)
+        return gemm.linear(x, lw.w, bias=lw.bias, out_dtype=out_dtype, w_tiled=lw.tiled)
     xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if x.shape[0] <= 32 else 128)
     y = gemm.linear_mx(xm, lw.mx, out_dtype=out_dtype, bias=lw.bias)
     return y
@@ -148,7 +148,7 @@ class Transformer:
 
     def dense_ffn(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor]) -> torch.Tensor:
         if lw.w_gate_up.fmt == "bf16":
-            act = gemm.linear_swiglu(h, lw.w_gate_up.w)
+            act = gemm.linear_swiglu(h, lw.w_gate_up.w, w_tiled=lw.w_gate_up.tiled)
             return self.par.row_linear(lw.w_down, act)
         xm = h_mx if h_mx is not None else ew.mx_quantize(h, sf_layout=32 if h.shape[0] <= 32 else 128)
         act = gemm.linear_mx_swiglu_quant(xm, lw.w_gate_up.mx)
@@ -167,18 +167,19 @@ class Transformer:
             pl = moe.plan(ids, e, tn)
             xq = ew.mx_quantize(h, pl.row_token, sf_layout=tn)
             dev = h.device
-            hq = torch.zeros(pl.capacity, inter, dtype=torch.uint8, device=dev)
-            hsf = ew.sf_alloc(pl.capacity, inter, dev, tn)
+            hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=dev)
+            hsf = ew.sf_alloc(pl.capacity, inter, dev, tn, init=False)
             gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, out=hq, dual=True,
-                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf)
-            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf)
+                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf, w_tiled=lw.w13.mx.tiled)
+            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
+                                    w_tiled=lw.w2.mx.tiled)
         else:
             tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
             pl = moe.plan(ids, e, tn)
             xs = moe.gather_rows(h, pl.row_token)
-            act = gemm.grouped_linear(xs, lw.w13.w.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True)
-            y = gemm.grouped_linear(act, lw.w2.w.view(e, hid, inter), pl.seg_start, pl.seg_count, tn)
-        return moe.combine(y, pl.pair_row, wts, t, k)
+            act = gemm.grouped_linear(xs, lw.w13.w.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
+            y = gemm.grouped_linear(act, lw.w2.w.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)
+        return moe.PendingCombine(y, pl.pair_row, wts, t, k)
 
     # ------------------------------------------------------------------------------------------------
     def forward_hidden(self, fb: ForwardBatch, first_layer: int = 0, last_layer: Optional[int] = None,
@@ -231,12 +232,13 @@ class Transformer:
         return ew.rmsnorm(xr.contiguous(), w.final_norm, cfg.rms_eps)
 
     def head(self, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
-        return gemm.linear(self._head_input(x, fb), self.w.lm_head.w, out_dtype=torch.float32)
+        return gemm.linear(self._head_input(x, fb), self.w.lm_head.w, out_dtype=torch.float32, w_tiled=self.w.lm_head.tiled)
 
     def forward_greedy(self, fb: ForwardBatch, want_value: bool = False):
         """Greedy next tokens ``int32 [len(logit_rows)]``: the arg-max runs in the LM-head GEMM's epilogue, no logits are stored."""
         x = self.forward_hidden(fb)
-        return gemm.linear_argmax(self._head_input(x, fb), self.w.lm_head.w, idx_offset=self.w.vocab_start, want_value=want_value)
+        return gemm.linear_argmax(self._head_input(x, fb), self.w.lm_head.w, idx_offset=self.w.vocab_start, want_value=want_value,
+                                  w_tiled=self.w.lm_head.tiled)
 
     def final_hidden(self, x: torch.Tensor) -> torch.Tensor:
         """Residual stream with the pending delta folded in (what a pipeline stage hands to the next)."""

@@ -36,6 +36,28 @@ class LinearWeight:
     bias: Optional[torch.Tensor] = None       # f32 [n]
     groups: int = 0                           # > 0: expert-stacked, rows = groups * rows_per_group
     rows_per_group: int = 0
+    tiled: bool = False                       # bf16 ``w`` is in the tiled layout (``mx.tiled`` for MXFP8)
+
+    @property
+    def is_tiled(self) -> bool:
+        return self.tiled if self.fmt == "bf16" else self.mx.tiled
+
+    def tile_(self) -> "LinearWeight":
+        """Re-lay the matrix in place into the GEMM kernel's tiled weight layout (``ops.mxfp8.tile_weight``)."""
+        t = self.w if self.fmt == "bf16" else self.mx.data
+        if self.is_tiled or not mxfp8.can_tile(t) or (self.groups and self.rows_per_group % 128):
+            return self
+        t.copy_(mxfp8.tile_weight(t))
+        if self.fmt == "bf16":
+            self.tiled = True
+        else:
+            self.mx.tiled = True
+        return self
+
+    def untiled_data(self) -> torch.Tensor:
+        """Row-major copy of the stored matrix (bf16 values or e4m3 bytes)."""
+        t = self.w if self.fmt == "bf16" else self.mx.data
+        return mxfp8.untile_weight(t) if self.is_tiled else t
 
     @property
     def device(self):
@@ -44,7 +66,7 @@ class LinearWeight:
     def dequantized(self) -> torch.Tensor:
         """fp32 copy of the full matrix (tests and CPU reference paths)."""
         if self.fmt == "bf16":
-            return self.w.float()
+            return self.untiled_data().float()
         return mxfp8.dequantize(self.mx)
 
     def nbytes(self) -> int:
@@ -56,7 +78,7 @@ class LinearWeight:
         return LinearWeight(self.fmt, self.n, self.k, w=self.w.to(device) if self.w is not None else None,
                             mx=self.mx.to(device) if self.mx is not None else None,
                             bias=self.bias.to(device) if self.bias is not None else None, groups=self.groups,
-                            rows_per_group=self.rows_per_group)
+                            rows_per_group=self.rows_per_group, tiled=self.tiled)
 
 
 def make_linear(w_f: torch.Tensor, fmt: str, bias: Optional[torch.Tensor] = None, groups: int = 0) -> LinearWeight:
@@ -115,6 +137,17 @@ class ModelWeights:
                             fmt=self.fmt, tp_rank=self.tp_rank, tp_size=self.tp_size, ep_rank=self.ep_rank, ep_size=self.ep_size,
                             vocab_start=self.vocab_start)
 
+    def tile_(self) -> "ModelWeights":
+        """Put every projection matrix into the tiled weight layout (in place).  An LM head that shares its storage with
+        the embedding table (tied embeddings) stays row-major: the embedding lookup reads rows."""
+        for l in self.layers:
+            for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.w13, l.w2):
+                if lw is not None:
+                    lw.tile_()
+        if self.lm_head.w is not None and self.lm_head.w.data_ptr() != self.embed.data_ptr():
+            self.lm_head.tile_()
+        return self
+
     def nbytes(self) -> int:
         tot = self.embed.numel() * 2 + self.lm_head.nbytes()
         for l in self.layers:
@@ -158,9 +191,11 @@ class RandomSource:
 
 
 def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0,
-                  ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None, layer_range=None) -> ModelWeights:
+                  ep_size: int = 1, shard_vocab: bool = False, n_layers: Optional[int] = None, layer_range=None,
+                  tile: Optional[bool] = None) -> ModelWeights:
     """Assemble ``ModelWeights`` in format ``fmt`` from a tensor source that answers GGUF tensor names
-    (``RandomSource``, ``loader.GGUFSource``, ``loader.SafetensorsSource``).
+    (``RandomSource``, ``loader.GGUFSource``, ``loader.SafetensorsSource``).  ``tile`` (default: on for CUDA devices) stores
+    the projection matrices in the GEMM kernel's tiled layout.
 
     TP shards attention and the dense FFN Megatron style (q/k/v/gate/up by rows, o/down by columns; KV heads are
     replicated when ``n_kv_heads < tp_size``), EP keeps the experts ``[ep_rank * E/ep_size, (ep_rank+1) * E/ep_size)``."""
@@ -243,8 +278,11 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
     if shard_vocab and tp_size > 1:
         v0, v1 = shard_range(cfg.vocab, tp_size, tp_rank)
     lm_head = make_linear(head_full[v0:v1].contiguous() if (v0, v1) != (0, cfg.vocab) else head_full, "bf16")
-    return ModelWeights(cfg=cfg, embed=embed, layers=layers, final_norm=mv(src.get("output_norm.weight", (h,)).to(torch.bfloat16)),
-                        lm_head=lm_head, fmt=fmt, tp_rank=tp_rank, tp_size=tp_size, ep_rank=ep_rank, ep_size=ep_size, vocab_start=v0)
+    mw = ModelWeights(cfg=cfg, embed=embed, layers=layers, final_norm=mv(src.get("output_norm.weight", (h,)).to(torch.bfloat16)),
+                      lm_head=lm_head, fmt=fmt, tp_rank=tp_rank, tp_size=tp_size, ep_rank=ep_rank, ep_size=ep_size, vocab_start=v0)
+    if tile if tile is not None else dev.type == "cuda":
+        mw.tile_()
+    return mw
 
 
 def synthetic_weights(cfg: ModelConfig, fmt: str = "bf16", device="cuda", seed: int = 0, tp_rank: int = 0, tp_size: int = 1,

@@ -45,9 +45,14 @@ def rmsnorm_ref(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(torch.bfloat16)
 
 
-def sf_alloc(rows_padded: int, k: int, device, layout: int = 128) -> torch.Tensor:
-    """Scale-atom buffer for ``rows_padded`` rows (a multiple of 128) initialised to scale 1."""
-    return torch.full((rows_padded // layout, k // 128, 512), 127, dtype=torch.uint8, device=device)
+def sf_alloc(rows_padded: int, k: int, device, layout: int = 128, init: bool = True) -> torch.Tensor:
+    """Scale-atom buffer for ``rows_padded`` rows (a multiple of 128).  ``init`` fills it with scale 1; the hot paths
+    skip the fill: rows that no kernel writes only ever feed accumulator columns that the GEMM epilogue drops
+    (every token is its own MMA column, so their contents cannot reach a valid row)."""
+    shape = (rows_padded // layout, k // 128, 512)
+    if not init:
+        return torch.empty(shape, dtype=torch.uint8, device=device)
+    return torch.full(shape, 127, dtype=torch.uint8, device=device)
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
@@ -57,7 +62,14 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
     Returns the bf16 result, or ``(bf16 | None, MxTensor)`` when ``quantize`` asks for an MXFP8 copy that
     feeds a block-scaled GEMM.
     """
-    rows, hidden = x.shape
+    pend = None
+    if hasattr(x, "materialize"):                    # ops.moe.PendingCombine: the MoE combine is done by this kernel
+        if residual is None or not x.y.is_cuda:
+            x = x.materialize()
+        else:
+            pend = x
+            x = pend.y
+    rows, hidden = (pend.n_tok, pend.y.shape[1]) if pend is not None else x.shape
     if not x.is_cuda:
         if residual is not None:
             residual.copy_((residual.float() + x.float()).to(torch.bfloat16))
@@ -72,9 +84,14 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
     q = sf = None
     if quantize:
         rp = (rows + 127) // 128 * 128
-        q = torch.zeros(rp, hidden, dtype=torch.uint8, device=x.device)
-        sf = sf_alloc(rp, hidden, x.device, sf_layout)
-    if residual is not None:
+        q = torch.empty(rp, hidden, dtype=torch.uint8, device=x.device)
+        sf = sf_alloc(rp, hidden, x.device, sf_layout, init=False)
+    if pend is not None:
+        assert residual.stride(0) == hidden
+        rc = _native.cuda().gb_rmsnorm_combine(_p(residual), _p(pend.y), _p(pend.pair_row), _p(pend.weights), _i(pend.k), _i(pend.y.stride(0)),
+                                               _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0),
+                                               _c(pend.wait_flags), _i(pend.wait_n), _c(pend.epoch_ptr), _c(_native.status_ptr()), _s())
+    elif residual is not None:
         rc = _native.cuda().gb_rmsnorm(_p(residual), _p(x), _c(0), _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden),
                                        _f(eps), _i(residual.stride(0)), _i(hidden), _i(1 if sf_layout == 32 else 0), _s())
     else:
@@ -157,7 +174,8 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_rows: Optional[int] = None,
                 sf_layout: int = 128) -> MxTensor:
     """bf16 ``[rows, K]`` -> MXFP8.  With ``src_rows`` (int32) output row r is input row ``src_rows[r]``
-    (negative = zero row): the gather of MoE dispatch fused with the quantiser."""
+    (negative = padding row, left unwritten on the GPU and zero on the CPU): the gather of MoE dispatch fused with the
+    quantiser."""
     k = x.shape[1]
     n = out_rows if out_rows is not None else (src_rows.numel() if src_rows is not None else x.shape[0])
     if not x.is_cuda:
@@ -170,8 +188,8 @@ def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_ro
         t = mxfp8.quantize(g, sf_layout=sf_layout)
         return t
     rp = (n + 127) // 128 * 128
-    q = torch.zeros(rp, k, dtype=torch.uint8, device=x.device)
-    sf = sf_alloc(rp, k, x.device, sf_layout)
+    q = torch.empty(rp, k, dtype=torch.uint8, device=x.device)
+    sf = sf_alloc(rp, k, x.device, sf_layout, init=False)
     _native.check(_native.cuda().gb_mx_quant(_p(x), _p(src_rows), _p(q), _p(sf), _l(n), _i(k), _i(x.stride(0)),
                                              _i(1 if sf_layout == 32 else 0), _s()), "gb_mx_quant")
     return MxTensor(q, sf, n, k, sf_layout)

@@ -7,6 +7,7 @@ no silent fallback on a GPU: a missing library raises).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -15,7 +16,7 @@ from .. import _native
 from . import mxfp8
 from .mxfp8 import MxTensor
 
-GEMM_MX, GEMM_DUAL, GEMM_QUANT_OUT, GEMM_OUT_F32 = 1, 2, 4, 8
+GEMM_MX, GEMM_DUAL, GEMM_QUANT_OUT, GEMM_OUT_F32, GEMM_W_TILED = 1, 2, 4, 8, 16
 
 
 class GemmExtras(ctypes.Structure):
@@ -34,14 +35,22 @@ _SK_CTR = 1 << 16
 _sk_state = {}
 
 
-def _splitk_extras(n_out: int, m_tok: int, k: int, tn: int, mx: bool, device) -> Optional["GemmExtras"]:
-    """Extras that turn on split-K when the plain tiling would leave most SMs idle (decode-sized GEMMs)."""
+SPLIT_K = os.environ.get("GB_SPLITK", "0") == "1"
+
+
+def _splitk_extras(n_out: int, m_tok: int, k: int, tn: int, mx: bool, device, force: bool = False) -> Optional["GemmExtras"]:
+    """Extras that turn on split-K when the plain tiling would leave most SMs idle (decode-sized GEMMs).
+
+    Off unless asked for (``force`` / ``GB_SPLITK=1``): on B200 the decode projections measured faster without it
+    (one CTA streams a 128-row weight panel in a few microseconds; the partial-sum round trip costs more)."""
+    if not (force or SPLIT_K):
+        return None
     tiles = ((n_out + 127) // 128) * ((m_tok + tn - 1) // tn)
     sms = 148
-    if tiles * 2 > sms:
+    if tiles * 4 > sms:
         return None
     num_kb = (k + (127 if mx else 63)) // (128 if mx else 64)
-    splits = min(sms // tiles, num_kb // 2, 16)
+    splits = min(sms // tiles, num_kb // 4, 8)
     if splits < 2:
         return None
     key = (device.index if device.index is not None else torch.cuda.current_device())
@@ -97,32 +106,32 @@ def _launch(w, x, out, n_out, k, m_tok, ldw, ldx, ldo, flags, tn, num_groups=0, 
 
 # --------------------------------------------------------------------------------------------- bf16
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-           out_dtype=torch.bfloat16, tn: Optional[int] = None) -> torch.Tensor:
-    """``x [M, K] @ w[N, K]^T`` (bf16 operands, fp32 accumulate)."""
+           out_dtype=torch.bfloat16, tn: Optional[int] = None, split_k: bool = False, w_tiled: bool = False) -> torch.Tensor:
+    """``x [M, K] @ w[N, K]^T`` (bf16 operands, fp32 accumulate).  ``w_tiled``: ``w`` is in ``mxfp8.tile_weight`` layout."""
     m, k = x.shape
     n = w.shape[0]
     if not x.is_cuda:
-        y = x.float() @ w.float().t()
+        y = x.float() @ (mxfp8.untile_weight(w) if w_tiled else w).float().t()
         if bias is not None:
             y = y + bias.float()
         return y.to(out_dtype)
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=x.device)
-    flags = GEMM_OUT_F32 if out.dtype == torch.float32 else 0
+    flags = (GEMM_OUT_F32 if out.dtype == torch.float32 else 0) | (GEMM_W_TILED if w_tiled else 0)
     tn = tn or pick_tn(m)
     _launch(w, x, out, n, k, m, w.stride(0), x.stride(0), out.stride(0), flags, tn, bias=bias,
-            extras=_splitk_extras(n, m, k, tn, False, x.device))
+            extras=_splitk_extras(n, m, k, tn, False, x.device, split_k))
     return out
 
 
-def linear_argmax(x: torch.Tensor, w: torch.Tensor, idx_offset: int = 0, want_value: bool = False):
+def linear_argmax(x: torch.Tensor, w: torch.Tensor, idx_offset: int = 0, want_value: bool = False, w_tiled: bool = False):
     """Greedy sampling fused into the LM head: ``argmax_n (x W^T)[t, n]`` without ever writing the logits.  Returns int32 ``[M]``
     (+ the winning values).  Ties resolve to the lower index."""
     m, k = x.shape
     n = w.shape[0]
     if not x.is_cuda:
-        y = torch.nan_to_num(x.float() @ w.float().t(), nan=-3.4e38)
+        y = torch.nan_to_num(x.float() @ (mxfp8.untile_weight(w) if w_tiled else w).float().t(), nan=-3.4e38)
         val, idx = y.max(dim=-1)
         idx = (idx + idx_offset).to(torch.int32)
         return (idx, val) if want_value else idx
@@ -131,7 +140,7 @@ def linear_argmax(x: torch.Tensor, w: torch.Tensor, idx_offset: int = 0, want_va
     pi = torch.empty(parts, m, dtype=torch.int32, device=x.device)
     ex = GemmExtras()
     ex.amax_val, ex.amax_idx = pv.data_ptr(), pi.data_ptr()
-    _launch(w, x, None, n, k, m, w.stride(0), x.stride(0), n, GEMM_OUT_F32, pick_tn(m), extras=ex)
+    _launch(w, x, None, n, k, m, w.stride(0), x.stride(0), n, GEMM_OUT_F32 | (GEMM_W_TILED if w_tiled else 0), pick_tn(m), extras=ex)
     out = torch.empty(m, dtype=torch.int32, device=x.device)
     val = torch.empty(m, dtype=torch.float32, device=x.device) if want_value else None
     rc = _native.cuda().gb_argmax_pairs(_p(pv), _p(pi), _p(out), _p(val), _i(parts), _i(m), _i(idx_offset), _stream())
@@ -140,23 +149,23 @@ def linear_argmax(x: torch.Tensor, w: torch.Tensor, idx_offset: int = 0, want_va
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch.Tensor] = None,
-                  tn: Optional[int] = None) -> torch.Tensor:
+                  tn: Optional[int] = None, w_tiled: bool = False) -> torch.Tensor:
     """``silu(x @ Wg^T) * (x @ Wu^T)`` with ``w_gate_up = [Wg; Wu]`` stacked along rows ([2I, K])."""
     m, k = x.shape
     inter = w_gate_up.shape[0] // 2
     if not x.is_cuda:
-        y = x.float() @ w_gate_up.float().t()
+        y = x.float() @ (mxfp8.untile_weight(w_gate_up) if w_tiled else w_gate_up).float().t()
         return (torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]).to(torch.bfloat16)
     if out is None:
         out = torch.empty(m, inter, dtype=torch.bfloat16, device=x.device)
-    _launch(w_gate_up, x, out, inter, k, m, w_gate_up.stride(0), x.stride(0), out.stride(0), GEMM_DUAL,
+    _launch(w_gate_up, x, out, inter, k, m, w_gate_up.stride(0), x.stride(0), out.stride(0), GEMM_DUAL | (GEMM_W_TILED if w_tiled else 0),
             tn or pick_tn(m, dual=True), up_row_offset=inter)
     return out
 
 
 # --------------------------------------------------------------------------------------------- mxfp8
 def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
-              tn: Optional[int] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+              tn: Optional[int] = None, bias: Optional[torch.Tensor] = None, split_k: bool = False) -> torch.Tensor:
     """Block-scaled fp8 linear: both operands MXFP8, bf16 (or f32) result [x.rows, w.rows]."""
     if not x.data.is_cuda:
         y = mxfp8.dequantize(x) @ mxfp8.dequantize(w).t()
@@ -166,11 +175,12 @@ def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_
     m, n, k = x.rows, w.rows, w.k
     if out is None:
         out = torch.empty(m, n, dtype=out_dtype, device=x.data.device)
-    flags = GEMM_MX | (GEMM_OUT_F32 if out.dtype == torch.float32 else 0)
+    flags = GEMM_MX | (GEMM_OUT_F32 if out.dtype == torch.float32 else 0) | (GEMM_W_TILED if w.tiled else 0)
     assert w.sf_layout == 128
-    tn = tn or x.sf_layout
+    if tn is None:
+        tn = 64 if (x.sf_layout == 128 and m <= 64) else x.sf_layout      # a single token block may use the 64-wide tile
     _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn, x_rows=x.data.shape[0],
-            sfa=w.sf, sfb=x.sf, bias=bias, extras=_splitk_extras(n, m, k, tn, True, x.data.device))
+            sfa=w.sf, sfb=x.sf, bias=bias, extras=_splitk_extras(n, m, k, tn, True, x.data.device, split_k))
     return out
 
 
@@ -182,9 +192,10 @@ def linear_mx_swiglu_quant(x: MxTensor, w_gate_up: MxTensor, tn: Optional[int] =
         h = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
         return mxfp8.quantize(h, sf_layout=x.sf_layout)
     rows_p = x.data.shape[0]
-    out = torch.zeros(rows_p, inter, dtype=torch.uint8, device=x.data.device)
-    out_sf = torch.full((rows_p // x.sf_layout, inter // 128, 512), 127, dtype=torch.uint8, device=x.data.device)
-    _launch(w_gate_up.data, x.data, out, inter, x.k, x.rows, x.k, x.k, inter, GEMM_MX | GEMM_DUAL | GEMM_QUANT_OUT,
+    out = torch.empty(rows_p, inter, dtype=torch.uint8, device=x.data.device)
+    out_sf = torch.empty((rows_p // x.sf_layout, inter // 128, 512), dtype=torch.uint8, device=x.data.device)
+    _launch(w_gate_up.data, x.data, out, inter, x.k, x.rows, x.k, x.k, inter,
+            GEMM_MX | GEMM_DUAL | GEMM_QUANT_OUT | (GEMM_W_TILED if w_gate_up.tiled else 0),
             tn or x.sf_layout, up_row_offset=inter, x_rows=rows_p, sfa=w_gate_up.sf, sfb=x.sf, out_sf=out_sf)
     return MxTensor(out, out_sf, x.rows, inter, x.sf_layout)
 
@@ -193,7 +204,8 @@ def linear_mx_swiglu_quant(x: MxTensor, w_gate_up: MxTensor, tn: Optional[int] =
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, seg_count: torch.Tensor, tn: int,
                    out: Optional[torch.Tensor] = None, dual: bool = False, row_map: Optional[torch.Tensor] = None,
                    row_scale: Optional[torch.Tensor] = None, sfa=None, sfb=None, quant_out: bool = False,
-                   out_sf: Optional[torch.Tensor] = None, extras=None, w_groups: Optional[int] = None) -> torch.Tensor:
+                   out_sf: Optional[torch.Tensor] = None, extras=None, w_groups: Optional[int] = None,
+                   w_tiled: bool = False) -> torch.Tensor:
     """One GEMM per group over row segments of ``x``.
 
     ``w`` is ``[G, R, K]`` (R = 2I stacked gate/up rows when ``dual``); group g multiplies the rows
@@ -207,11 +219,13 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
     n_out = r // 2 if dual else r
     mx = sfa is not None
     if not x.is_cuda:
+        if w_tiled:
+            w = mxfp8.untile_weight(w.reshape(-1, k)).reshape(w.shape)
         return _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out, out_sf)
-    flags = (GEMM_MX if mx else 0) | (GEMM_DUAL if dual else 0) | (GEMM_QUANT_OUT if quant_out else 0)
+    flags = (GEMM_MX if mx else 0) | (GEMM_DUAL if dual else 0) | (GEMM_QUANT_OUT if quant_out else 0) | (GEMM_W_TILED if w_tiled else 0)
     if out is None:
         if quant_out:
-            out = torch.zeros(x.shape[0], n_out, dtype=torch.uint8, device=x.device)
+            out = torch.empty(x.shape[0], n_out, dtype=torch.uint8, device=x.device)
         else:
             out = torch.empty(x.shape[0], n_out, dtype=torch.bfloat16, device=x.device)
     if out.dtype == torch.float32:

@@ -136,7 +136,7 @@ def plan(ids: torch.Tensor, n_exp: int, align: int, regions: int = 1, workspace=
     rc = _native.cuda().gb_moe_plan(_p(ids), _p(ws), _p(seg_start), _p(seg_count), _p(region_used), _p(pair_row), _p(row_token),
                                     _l(n_pairs), _i(n_exp), _i(k), _i(n_exp // regions), _i(region_rows), _i(align),
                                     _l(capacity), _c(epoch_ctr), _s())
-    _native.check(rc, "gb_moe_plan", n=4)
+    _native.check(rc, "gb_moe_plan", n=1 if n_pairs <= 2048 else 4)
     return MoePlan(seg_start, seg_count, pair_row, row_token, region_used, capacity, region_rows)
 
 
@@ -154,6 +154,28 @@ def combine(y: torch.Tensor, pair_row: torch.Tensor, weights: Optional[torch.Ten
                                        _c(wait_flags), _i(wait_n), _c(epoch_ptr), _c(_native.status_ptr()), _s())
     _native.check(rc, "gb_moe_combine")
     return out
+
+
+@dataclass
+class PendingCombine:
+    """Expert outputs whose router-weighted sum has not been formed yet.  ``ops.elementwise.rmsnorm`` accepts it as the
+    residual update and does the combine inside the normalisation kernel (one launch and one round trip through memory
+    less per MoE layer); ``materialize`` forms the plain tensor."""
+    y: torch.Tensor
+    pair_row: torch.Tensor
+    weights: Optional[torch.Tensor]
+    n_tok: int
+    k: int
+    wait_flags: int = 0
+    wait_n: int = 0
+    epoch_ptr: int = 0
+
+    @property
+    def shape(self):
+        return (self.n_tok, self.y.shape[1])
+
+    def materialize(self) -> torch.Tensor:
+        return combine(self.y, self.pair_row, self.weights, self.n_tok, self.k, self.wait_flags, self.wait_n, self.epoch_ptr)
 
 
 def gather_rows(x: torch.Tensor, src: torch.Tensor) -> torch.Tensor:

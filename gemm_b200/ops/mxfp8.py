@@ -32,9 +32,32 @@ class MxTensor:
     rows: int
     k: int
     sf_layout: int = 128    # rows per scale atom: 128 (default) or 32 (token tiles of 32 rows)
+    tiled: bool = False     # ``data`` holds the tiled weight layout (see ``tile_weight``); same shape, permuted memory
 
     def to(self, device):
-        return MxTensor(self.data.to(device), self.sf.to(device), self.rows, self.k, self.sf_layout)
+        return MxTensor(self.data.to(device), self.sf.to(device), self.rows, self.k, self.sf_layout, self.tiled)
+
+
+def tile_weight(w: torch.Tensor) -> torch.Tensor:
+    """Row-major ``[rows, K]`` -> the tiled weight layout of the GEMM kernel, returned with the same shape.
+
+    Memory order becomes ``[rows/128][K/box][128 rows][box]`` with ``box`` = 128 bytes of elements (128 fp8 / 64 bf16):
+    every 16 KB operand tile that the kernel's TMA fetches is one contiguous block, so a decode step streams the weights
+    as long DRAM bursts instead of 128-byte lines that are a row pitch apart."""
+    rows, k = w.shape
+    box = 128 // w.element_size()
+    assert rows % 128 == 0 and k % box == 0, "tiled weights need rows % 128 == 0 and K a multiple of 128 bytes"
+    return w.reshape(rows // 128, 128, k // box, box).permute(0, 2, 1, 3).contiguous().view(rows, k)
+
+
+def untile_weight(t: torch.Tensor) -> torch.Tensor:
+    rows, k = t.shape
+    box = 128 // t.element_size()
+    return t.reshape(rows // 128, k // box, 128, box).permute(0, 2, 1, 3).contiguous().view(rows, k)
+
+
+def can_tile(w: torch.Tensor) -> bool:
+    return w.dim() == 2 and w.shape[0] % 128 == 0 and (w.shape[1] * w.element_size()) % 128 == 0
 
 
 def e8m0_from_amax(amax: torch.Tensor) -> torch.Tensor:
@@ -109,4 +132,4 @@ def quantize(x: torch.Tensor, pad_rows_to: int = 128, sf_layout: int = 128) -> M
 
 def dequantize(t: MxTensor) -> torch.Tensor:
     e = unpack_sf_atoms(t.sf, t.data.shape[0], t.k // 32, t.sf_layout)
-    return dequantize_rowmajor(t.data, e)[: t.rows]
+    return dequantize_rowmajor(untile_weight(t.data) if t.tiled else t.data, e)[: t.rows]

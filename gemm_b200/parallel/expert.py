@@ -129,7 +129,7 @@ class ExpertParallel:
         return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
 
     def materialize(self, delta):
-        return delta
+        return delta.materialize() if hasattr(delta, "materialize") else delta
 
     def moe_ffn(self, model, lw, h: torch.Tensor) -> torch.Tensor:
         if not self.fused:
@@ -151,15 +151,16 @@ class ExpertParallel:
         seg_start, seg_count = self.meta[0], self.meta[1]
         if self.mx:
             gemm.grouped_linear(b["x"], lw.w13.mx.data.view(self.e_local, 2 * inter, hid), seg_start, seg_count, tn, out=b["hq"], dual=True,
-                                sfa=lw.w13.mx.sf, sfb=b["sf"], quant_out=True, out_sf=b["hsf"], extras=b["ex1"], w_groups=b["groups"])
+                                sfa=lw.w13.mx.sf, sfb=b["sf"], quant_out=True, out_sf=b["hsf"], extras=b["ex1"], w_groups=b["groups"],
+                                w_tiled=lw.w13.mx.tiled)
             gemm.grouped_linear(b["hq"], lw.w2.mx.data.view(self.e_local, hid, inter), seg_start, seg_count, tn, out=b["y"],
-                                sfa=lw.w2.mx.sf, sfb=b["hsf"], extras=b["ex2"], w_groups=b["groups"])
+                                sfa=lw.w2.mx.sf, sfb=b["hsf"], extras=b["ex2"], w_groups=b["groups"], w_tiled=lw.w2.mx.tiled)
         else:
             gemm.grouped_linear(b["x"], lw.w13.w.view(self.e_local, 2 * inter, hid), seg_start, seg_count, tn, out=b["act"], dual=True,
-                                extras=b["ex1"], w_groups=b["groups"])
+                                extras=b["ex1"], w_groups=b["groups"], w_tiled=lw.w13.tiled)
             gemm.grouped_linear(b["act"], lw.w2.w.view(self.e_local, hid, inter), seg_start, seg_count, tn, out=b["y"], extras=b["ex2"],
-                                w_groups=b["groups"])
-        return moe.combine(b["y"], pl.pair_row, wts, t, k, wait_flags=f.local_base + self.flags_c, wait_n=w, epoch_ptr=self.epoch)
+                                w_groups=b["groups"], w_tiled=lw.w2.tiled)
+        return moe.PendingCombine(b["y"], pl.pair_row, wts, t, k, wait_flags=f.local_base + self.flags_c, wait_n=w, epoch_ptr=self.epoch)
 
     # ------------------------------------------------------------------------------------------ NCCL-only baseline
     def _moe_nccl(self, model, lw, h: torch.Tensor) -> torch.Tensor:
@@ -183,15 +184,16 @@ class ExpertParallel:
         pl = moe.plan(local, e_local, tn)
         if model.mx:
             xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
-            hq = torch.zeros(pl.capacity, inter, dtype=torch.uint8, device=h.device)
-            hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn)
+            hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
+            hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)
             gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, out=hq, dual=True,
-                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf)
-            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf)
+                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf, w_tiled=lw.w13.mx.tiled)
+            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
+                                    w_tiled=lw.w2.mx.tiled)
         else:
             xs = moe.gather_rows(allh, pl.row_token)
-            act = gemm.grouped_linear(xs, lw.w13.w.view(e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True)
-            y = gemm.grouped_linear(act, lw.w2.w.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn)
+            act = gemm.grouped_linear(xs, lw.w13.w.view(e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
+            y = gemm.grouped_linear(act, lw.w2.w.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)
         part = moe.combine(y, pl.pair_row, wts, w * t, k).float()
         if not h.is_cuda:
             dist.all_reduce(part, group=self.group)

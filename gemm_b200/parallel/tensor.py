@@ -100,10 +100,11 @@ class TensorParallel:
         ex = self._extras[ch]
         if lw.fmt == "bf16":
             tn = gemm.pick_tn(rows)
-            gemm._launch(lw.w, x, None, n, k, rows, lw.w.stride(0), x.stride(0), n, gemm.GEMM_OUT_F32, tn, bias=None, extras=ex)
+            gemm._launch(lw.w, x, None, n, k, rows, lw.w.stride(0), x.stride(0), n, gemm.GEMM_OUT_F32 | (gemm.GEMM_W_TILED if lw.tiled else 0), tn, bias=None,
+                         extras=ex)
         else:
             xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if rows <= 32 else 128)
-            gemm._launch(lw.mx.data, xm.data, None, n, k, rows, k, k, n, gemm.GEMM_MX | gemm.GEMM_OUT_F32, xm.sf_layout,
+            gemm._launch(lw.mx.data, xm.data, None, n, k, rows, k, k, n, gemm.GEMM_MX | gemm.GEMM_OUT_F32 | (gemm.GEMM_W_TILED if lw.mx.tiled else 0), xm.sf_layout,
                          x_rows=xm.data.shape[0], sfa=lw.mx.sf, sfb=xm.sf, extras=ex)
         return PendingReduce(ch, rows, n)
 
@@ -134,7 +135,7 @@ class TensorParallel:
     def materialize(self, delta):
         """Finish a pending reduction into a plain tensor (sum of the ranks' partials, bf16)."""
         if not isinstance(delta, PendingReduce):
-            return delta
+            return delta.materialize() if hasattr(delta, "materialize") else delta
         f = self.fab
         slots = f.view(self.slots_off[delta.chan], (self.tp_size, self.slot_elems), torch.float32)
         # order the read after the peers' stores: a fabric barrier (device side) covers the flags of this channel

@@ -1,0 +1,177 @@
+"""Kernel micro-benchmarks: ``python -m gemm_b200.utils.microbench --case <name> [--iters N]``.
+
+Every case times one op of the library on shapes of the Qwen3-30B-A3B benchmark configuration with CUDA events on the
+launching stream, after warm-up, with the L2 flushed (a 256 MiB buffer is rewritten) before every timed launch, and
+prints one JSON line per measurement: achieved TFLOP/s and GB/s of the bytes that must come from HBM.  ``--once`` runs
+each op a single time without timing (the form to put under a profiler).
+
+Cases
+  gemm         dense projections: decode (64 tokens) and prefill (16384 tokens), bf16 and MXFP8
+  moe_decode   grouped expert GEMMs (gate/up with SwiGLU + re-quantisation, down) for 64 tokens x top-8 of 128 experts
+  moe_prefill  the same for 16384 tokens
+  attn_decode  paged flash-decode, 64 sequences x 2048 cached tokens, 32 query / 4 KV heads
+  attn_prefill causal prefill, 8 sequences x 2048 tokens
+  lm_head      64 x 151936 x 2048 with the arg-max epilogue
+
+Counterpart in the reference: cuda/gemm/bench_log.md and cuda/fa2/bench_log.md are produced by stand-alone bench
+programs of the same kind.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from .. import _native
+from ..ops import attention as att
+from ..ops import elementwise as ew
+from ..ops import gemm, moe, mxfp8
+
+_flush = None
+
+
+def _timeit(fn, iters: int, warm: int = 3) -> float:
+    """Median milliseconds of ``fn`` (L2 flushed before each timed call)."""
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def _emit(name: str, ms: float, flops: float, hbm_bytes: float, **kw) -> None:
+    print(json.dumps(dict(case=name, ms=round(ms, 5), tflops=round(flops / ms / 1e9, 1), hbm_gbs=round(hbm_bytes / ms / 1e6, 1), **kw)),
+          flush=True)
+
+
+def _run(name, fn, flops, hbm_bytes, args, **kw):
+    if args.once:
+        fn()
+        torch.cuda.synchronize()
+        print(json.dumps(dict(case=name, ran="once")), flush=True)
+        return
+    _emit(name, _timeit(fn, args.iters), flops, hbm_bytes, **kw)
+
+
+def case_gemm(args):
+    for (m, n, k) in [(64, 5120, 2048), (64, 2048, 4096), (16384, 5120, 2048), (16384, 2048, 4096), (8192, 8192, 8192)]:
+        x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+        wt = mxfp8.tile_weight(w)
+        _run(f"gemm_bf16_{m}x{n}x{k}", lambda: gemm.linear(x, wt, w_tiled=True), 2.0 * m * n * k, n * k * 2 + m * k * 2 + m * n * 2, args)
+        if not args.once:
+            _emit(f"torch_matmul_{m}x{n}x{k}", _timeit(lambda: torch.matmul(x, w.t()), args.iters), 2.0 * m * n * k, n * k * 2 + m * k * 2 + m * n * 2)
+        xq = mxfp8.quantize(x.float(), sf_layout=32 if m <= 32 else 128)
+        wq = mxfp8.quantize(w.float())
+        wq = mxfp8.MxTensor(mxfp8.tile_weight(wq.data), wq.sf, wq.rows, wq.k, 128, tiled=True)
+        _run(f"gemm_mxfp8_{m}x{n}x{k}", lambda: gemm.linear_mx(xq, wq), 2.0 * m * n * k, n * k + m * k + m * n * 2, args)
+
+
+def _moe(args, t: int, name: str):
+    e, kk, h, inter = 128, 8, 2048, 768
+    tn = 32 if (t * kk) // e <= 24 else 128
+    ids, _ = moe.route(torch.randn(t, e, device="cuda"), kk)
+    pl = moe.plan(ids, e, tn)
+    x = torch.randn(t, h, device="cuda").bfloat16()
+    xq = ew.mx_quantize(x, pl.row_token, sf_layout=tn)
+    w1 = mxfp8.quantize(torch.randn(e * 2 * inter, h, device="cuda") * 0.05)
+    w2 = mxfp8.quantize(torch.randn(e * h, inter, device="cuda") * 0.05)
+    d1, d2 = mxfp8.tile_weight(w1.data), mxfp8.tile_weight(w2.data)
+    hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device="cuda")
+    hsf = ew.sf_alloc(pl.capacity, inter, "cuda", tn, init=False)
+
+    def gate_up():
+        gemm.grouped_linear(xq.data, d1.view(e, 2 * inter, h), pl.seg_start, pl.seg_count, tn, out=hq, dual=True, sfa=w1.sf, sfb=xq.sf,
+                            quant_out=True, out_sf=hsf, w_tiled=True)
+
+    def down():
+        gemm.grouped_linear(hq, d2.view(e, h, inter), pl.seg_start, pl.seg_count, tn, sfa=w2.sf, sfb=hsf, w_tiled=True)
+
+    gate_up()
+    touched = int((pl.seg_count > 0).sum())
+    fl = 2.0 * t * kk * h * inter
+    _run(f"{name}_gate_up", gate_up, 2 * fl, touched * 2 * h * inter + t * kk * h, args, tn=tn, experts_touched=touched)
+    _run(f"{name}_down", down, fl, touched * h * inter + t * kk * inter + t * kk * h * 2, args, tn=tn, experts_touched=touched)
+
+
+def case_moe_decode(args):
+    _moe(args, 64, "moe_decode")
+
+
+def case_moe_prefill(args):
+    _moe(args, 16384, "moe_prefill")
+
+
+def _attn(args, b: int, q_len: int, ctx: int, name: str):
+    hq, hkv, d, page = 32, 4, 128, 64
+    pages_per = (ctx + q_len + page - 1) // page
+    n_pages = b * pages_per + 1
+    k = (torch.randn(n_pages * page, hkv, d, device="cuda") * 0.5).bfloat16()
+    v = (torch.randn(n_pages * page, hkv, d, device="cuda") * 0.5).bfloat16()
+    bt = (torch.arange(b * pages_per, device="cuda", dtype=torch.int32) + 1).reshape(b, pages_per)
+    q = (torch.randn(b * q_len, hq, d, device="cuda") * 0.5 * ew.softmax_scale_log2(d)).bfloat16()
+    q_lens = [q_len] * b
+    cu = torch.tensor([i * q_len for i in range(b + 1)], device="cuda", dtype=torch.int32)
+    kv_len = torch.full((b,), ctx + q_len, device="cuda", dtype=torch.int32)
+    splits = att.pick_splits(b, hkv, ctx + q_len) if q_len == 1 else 1
+    if args.splits > 0:
+        splits = args.splits
+    work = att.build_work(q_lens, hq, hkv, splits).to("cuda")
+
+    def run():
+        att.attention(q, k, v, cu, kv_len, bt, page, work, num_splits=splits, causal=True)
+
+    kv_bytes = b * (ctx + q_len) * hkv * d * 2 * 2
+    if q_len == 1:
+        flops = 4.0 * b * hq * (ctx + 1) * d
+    else:
+        flops = 4.0 * b * hq * d * (q_len * ctx + q_len * (q_len + 1) / 2)
+    _run(name, run, flops, kv_bytes + b * q_len * hq * d * 4, args, splits=splits)
+
+
+def case_attn_decode(args):
+    _attn(args, 64, 1, 2048, "attn_decode")
+
+
+def case_attn_prefill(args):
+    _attn(args, 8, 2048, 0, "attn_prefill")
+
+
+def case_lm_head(args):
+    m, n, k = 64, 151936, 2048
+    x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    w = mxfp8.tile_weight((torch.randn(n, k, device="cuda") * 0.05).bfloat16())
+    _run("lm_head_argmax", lambda: gemm.linear_argmax(x, w, w_tiled=True), 2.0 * m * n * k, n * k * 2, args)
+
+
+CASES = {"gemm": case_gemm, "moe_decode": case_moe_decode, "moe_prefill": case_moe_prefill, "attn_decode": case_attn_decode,
+         "attn_prefill": case_attn_prefill, "lm_head": case_lm_head}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES))
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--splits", type=int, default=0, help="attention cases: force the number of KV splits")
+    ap.add_argument("--once", action="store_true", help="run each op once, untimed (for use under a profiler)")
+    args = ap.parse_args(argv)
+    torch.manual_seed(0)
+    for name in (sorted(CASES) if args.case == "all" else [args.case]):
+        CASES[name](args)
+    print(json.dumps(dict(kernel_status=_native.read_status()["what"])), flush=True)
+
+
+if __name__ == "__main__":
+    main()

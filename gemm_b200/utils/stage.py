@@ -23,9 +23,9 @@ def _put_linear(out: Dict[str, torch.Tensor], key: str, lw: Optional[LinearWeigh
     if lw is None:
         return
     if lw.fmt == "bf16":
-        out[key + ".w"] = lw.w
+        out[key + ".w"] = lw.untiled_data()
     else:
-        out[key + ".q"] = lw.mx.data
+        out[key + ".q"] = lw.untiled_data()
         out[key + ".sf"] = lw.mx.sf
     if lw.bias is not None:
         out[key + ".bias"] = lw.bias

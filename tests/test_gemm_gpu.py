@@ -111,22 +111,22 @@ def test_grouped(mx, tn):
         assert _rel(y[s:s + c], ref) < 1e-2, f"group {i}"
 
 
-@pytest.mark.parametrize("m,n,k,mx", [(8, 5120, 2048, False), (64, 2048, 4096, False), (8, 5120, 2048, True), (64, 2048, 4096, True), (20, 128, 2048, False)])
+@pytest.mark.parametrize("m,n,k,mx", [(8, 2048, 2048, False), (64, 2048, 4096, False), (8, 2048, 2048, True), (64, 2048, 4096, True), (20, 128, 2048, False)])
 def test_split_k_small_batches(m, n, k, mx):
-    """Decode-sized GEMMs take the split-K path (few tiles, long K): same result, and bit-identical from run to run."""
+    """The optional split-K path (few tiles, long K): same result, and bit-identical from run to run."""
     torch.manual_seed(6)
     x = torch.randn(m, k, device="cuda") * 0.5
     w = torch.randn(n, k, device="cuda") * 0.05
     if mx:
         xq, wq = mxfp8.quantize(x, sf_layout=32 if m <= 32 else 128), mxfp8.quantize(w)
-        assert gemm._splitk_extras(n, m, k, xq.sf_layout, True, x.device) is not None
-        y1 = gemm.linear_mx(xq, wq, out_dtype=torch.float32)
-        y2 = gemm.linear_mx(xq, wq, out_dtype=torch.float32)
+        assert gemm._splitk_extras(n, m, k, xq.sf_layout, True, x.device, True) is not None
+        y1 = gemm.linear_mx(xq, wq, out_dtype=torch.float32, tn=xq.sf_layout, split_k=True)
+        y2 = gemm.linear_mx(xq, wq, out_dtype=torch.float32, tn=xq.sf_layout, split_k=True)
         ref = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t()
     else:
-        assert gemm._splitk_extras(n, m, k, gemm.pick_tn(m), False, x.device) is not None
-        y1 = gemm.linear(x.bfloat16(), w.bfloat16(), out_dtype=torch.float32)
-        y2 = gemm.linear(x.bfloat16(), w.bfloat16(), out_dtype=torch.float32)
+        assert gemm._splitk_extras(n, m, k, gemm.pick_tn(m), False, x.device, True) is not None
+        y1 = gemm.linear(x.bfloat16(), w.bfloat16(), out_dtype=torch.float32, split_k=True)
+        y2 = gemm.linear(x.bfloat16(), w.bfloat16(), out_dtype=torch.float32, split_k=True)
         ref = x.bfloat16().float() @ w.bfloat16().float().t()
     _native.assert_status_ok()
     assert torch.equal(y1, y2)
@@ -143,3 +143,46 @@ def test_linear_argmax_matches_logits_argmax():
     _native.assert_status_ok()
     ref_val, ref_idx = logits.max(dim=-1)
     assert torch.equal(idx.long() - 5, ref_idx) and torch.equal(val, ref_val)
+
+
+@pytest.mark.parametrize("m", [8, 64, 300])
+def test_tiled_weight_layout_is_bit_identical(m):
+    """The tiled weight layout changes where the bytes live, not what is computed."""
+    torch.manual_seed(12)
+    n, k = 1024, 2048
+    x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    wt = mxfp8.tile_weight(w)
+    assert torch.equal(mxfp8.untile_weight(wt), w)
+    assert torch.equal(gemm.linear(x, w), gemm.linear(x, wt, w_tiled=True))
+    assert torch.equal(gemm.linear_swiglu(x, w), gemm.linear_swiglu(x, wt, w_tiled=True))
+    lay = 32 if m <= 32 else 128
+    xq, wq = mxfp8.quantize(x.float(), sf_layout=lay), mxfp8.quantize(w.float())
+    wqt = mxfp8.MxTensor(mxfp8.tile_weight(wq.data), wq.sf, wq.rows, wq.k, 128, tiled=True)
+    assert torch.equal(mxfp8.dequantize(wqt), mxfp8.dequantize(wq))
+    assert torch.equal(gemm.linear_mx(xq, wq), gemm.linear_mx(xq, wqt))
+    a, b = gemm.linear_mx_swiglu_quant(xq, wq), gemm.linear_mx_swiglu_quant(xq, wqt)
+    assert torch.equal(a.data[:m], b.data[:m])
+    _native.assert_status_ok()
+
+
+def test_tiled_grouped_weights():
+    torch.manual_seed(13)
+    g, inter, k, tn = 8, 256, 512, 32
+    counts = torch.tensor([3, 0, 32, 17, 1, 40, 5, 9])
+    starts = torch.zeros(g, dtype=torch.int64)
+    pos = 0
+    for i in range(g):
+        starts[i] = pos
+        pos += (int(counts[i]) + tn - 1) // tn * tn
+    cap = (pos + 127) // 128 * 128
+    x = torch.randn(cap, k, device="cuda") * 0.5
+    w = torch.randn(g * 2 * inter, k, device="cuda") * 0.05
+    sd, cd = starts.to("cuda", torch.int32), counts.to("cuda", torch.int32)
+    xq, wq = mxfp8.quantize(x, sf_layout=32), mxfp8.quantize(w)
+    y0 = gemm.grouped_linear(xq.data, wq.data.view(g, 2 * inter, k), sd, cd, tn, dual=True, sfa=wq.sf, sfb=xq.sf)
+    y1 = gemm.grouped_linear(xq.data, mxfp8.tile_weight(wq.data).view(g, 2 * inter, k), sd, cd, tn, dual=True, sfa=wq.sf, sfb=xq.sf, w_tiled=True)
+    for i in range(g):
+        s, c = int(starts[i]), int(counts[i])
+        assert torch.equal(y0[s:s + c], y1[s:s + c])
+    _native.assert_status_ok()
