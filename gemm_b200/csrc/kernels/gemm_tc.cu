@@ -22,6 +22,7 @@
 // expert GEMMs of mmq_*_grouped (cuda_llm_runner.c:5295-7329) and m3_gemm_mxfp8 (common/m3_impl.h:791-825).
 #include "sm100.cuh"
 #include "host_common.h"
+#include <stdlib.h>
 #include "../fabric/fabric.cuh"
 
 namespace gb {
@@ -78,6 +79,7 @@ struct GemmArgs {
   // ---- weight layout: 0 = row-major [rows, k]; 1 = tiled [rows/128][k-blocks][128 rows][128 bytes], every 16 KB operand
   // tile of the main loop is one contiguous block of memory (one DRAM burst sequence instead of 128 strided lines)
   int w_tiled;
+  int debug;     // experiment knob (GB_GEMM_DEBUG): bit 0 = issue no MMA (pure load stream), bit 1 = load no weight tiles (pure MMA issue)
 };
 
 struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; int ks; int tile_id; };
@@ -210,14 +212,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       TileCursor<TN> cur; Tile t;
       int s = 0; uint32_t ph = 0;
       bool ok = true;
+      int dbg_i = 0;
       for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
         const int kb0 = t.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 100, s)) { ok = false; break; }
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-          mbar_expect_tx(&full_bar[s], NA * A_BYTES + B_BYTES + ((MODE == 1) ? (NA + SFB_ATOMS) * 512 : 0));
+          const bool load_w = !(args.debug & 2);
+          mbar_expect_tx(&full_bar[s], (load_w ? NA * A_BYTES : 0) + B_BYTES + ((MODE == 1) ? (NA + SFB_ATOMS) * 512 : 0));
           const int kx = kb * KB_ELEMS;
-          if (args.w_tiled) {
+          if (!load_w) {
+          } else if (args.w_tiled) {
             tma_load_2d(st, &tmW, &full_bar[s], 0, ((t.w_row0 >> 7) * num_kb + kb) << 7);
             if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], 0, ((t.w_row1 >> 7) * num_kb + kb) << 7);
           } else {
@@ -245,6 +250,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 bulk_load(sf + (NA + i) * 512, atom(args.sfb, args.sfb_bytes, ((size_t)((t.x_row0 >> 7) + i) * kbs + kb) * 512, 123), 512, &full_bar[s]);
             }
           }
+          if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[dbg_i++] = clock64();
           if (++s == S) { s = 0; ph ^= 1; }
         }
       }
@@ -256,6 +262,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0; uint32_t ph = 0;
       int acc = 0; uint32_t acc_ph = 0;
       bool ok = true;
+      int dbg_i = 0;
       for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
         if (!mbar_wait(&acce_bar[acc], acc_ph ^ 1, abort_flag, args.status, 200, acc)) { ok = false; break; }
         tc_fence_after();
@@ -263,9 +270,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int kb0 = t.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, args.status, 201, s)) { ok = false; break; }
+          if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[2048 + dbg_i++] = clock64();
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
           uint32_t sfb_t = 0;
+          if (args.debug & 1) { tc_commit(&empty_bar[s]); if (++s == S) { s = 0; ph ^= 1; } continue; }
           if (MODE == 1) {
             const uint32_t sf = st + NA * A_BYTES + B_BYTES;
             tc_cp_32x128b_warpx4(tmem_sf, make_sdesc_noswizzle(sf, 0, 128));
@@ -305,10 +314,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     TileCursor<TN> cur; Tile t;
     int acc = 0; uint32_t acc_ph = 0;
     bool ok = true;
+    int dbg_t = 0;
     const bool simple_store = !QUANT_OUT && args.amax_val == nullptr && args.peer_region_rows == 0 && args.row_map == nullptr &&
                               args.peer_bcast == 0 && args.row_scale == nullptr && args.splits <= 1;
     for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
       if (!mbar_wait(&accf_bar[acc], acc_ph, abort_flag, args.status, 300, acc)) { ok = false; break; }
+      if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4096 + dbg_t] = clock64();
       tc_fence_after();
       const uint32_t tacc = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
       const int n = t.n0 + row;
@@ -489,6 +500,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acce_bar[acc]);
+      if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4608 + dbg_t++] = clock64();
       if (NACC == 2) { if (++acc == 2) { acc = 0; acc_ph ^= 1; } } else { acc_ph ^= 1; }
     }
   }
@@ -522,6 +534,12 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmArgs 
   const int tail = 1024 + 2 * kMaxGroups * 4 + 256;
   int stages = (int)((220 * 1024 - tail - 1024) / STAGE_BYTES);
   if (stages > 8) stages = 8;
+  {
+    // GB_GEMM_STAGES caps the pipeline depth (an experiment knob: how latency-bound is a shape?)
+    static int cap = -1;
+    if (cap < 0) { const char* e = getenv("GB_GEMM_STAGES"); cap = (e != nullptr && atoi(e) >= 2) ? atoi(e) : 0; }
+    if (cap > 0 && stages > cap) stages = cap;
+  }
   if (stages < 2) return fail("gemm: tile does not fit shared memory%s");
   a.stages = stages;
   const int smem = stages * STAGE_BYTES + tail + 1024;
@@ -617,6 +635,13 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   a.up_row_offset = up_row_offset; a.seg_start = seg_start; a.seg_count = seg_count;
   a.sfa = (const uint8_t*)sfa; a.sfb = (const uint8_t*)sfb; a.out = out; a.ldo = ldo; a.out_f32 = (flags & GEMM_OUT_F32) ? 1 : 0;
   a.w_tiled = w_tiled ? 1 : 0;
+  {
+    static int dbg = -1;
+    if (dbg < 0) { const char* e = getenv("GB_GEMM_DEBUG"); dbg = e != nullptr ? atoi(e) : 0; }
+    a.debug = dbg;
+    if ((dbg & 4) && ex != nullptr && ex->sk_ws != nullptr && ex->sk_ws_bytes >= 5120 * 8) a.sk_ws = ex->sk_ws;
+    else a.debug &= ~4;
+  }
   a.out_sf = (uint8_t*)out_sf; a.bias = bias; a.row_map = row_map; a.row_scale = row_scale; a.status = (KernelStatus*)status;
   if (ex != nullptr) {
     a.w_group_mod = ex->w_group_mod; a.wait_flags = ex->wait_flags; a.wait_n = ex->wait_n; a.epoch_ptr = ex->epoch_ptr;
