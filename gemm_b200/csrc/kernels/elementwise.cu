@@ -288,6 +288,41 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_
   store8(out + r * inter + c, y);
 }
 
+// SiLU(gate) * up followed by MXFP8 quantisation: gate_up [rows, 2 * inter] bf16 -> e4m3 bytes [rows, inter] + scale atoms.
+// Used after a plain (single-accumulator) gate/up GEMM for prefill-sized expert batches, where the two-accumulator GEMM
+// with this math in its epilogue cannot double-buffer its accumulators in TMEM.  Rows whose row_valid entry is negative
+// (padding of the expert-sorted buffer) are skipped.  8 elements per thread, 4 threads share a scale.
+__global__ void __launch_bounds__(256)
+silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const int* __restrict__ row_valid, uint8_t* __restrict__ out_q,
+                      uint8_t* __restrict__ out_sf, long rows, int inter, int ld, int sf32) {
+  pdl_wait();
+  pdl_trigger();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vec_per_row = inter >> 3;
+  const long r = idx / vec_per_row;
+  const int vi = (int)(idx % vec_per_row);
+  const bool live = r < rows && (row_valid == nullptr || row_valid[r] >= 0);
+  float y[8];
+  float amax = 0.f;
+  if (live) {
+    float g[8], u[8];
+    load8(gate_up + r * ld + vi * 8, g);
+    load8(gate_up + r * ld + inter + vi * 8, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { y[j] = g[j] / (1.0f + __expf(-g[j])) * u[j]; amax = fmaxf(amax, fabsf(y[j])); }
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  if (!live) return;
+  const int e = e8m0_amax(amax);
+  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+  uint8_t q[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(y[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
+  *reinterpret_cast<uint2*>(out_q + r * inter + vi * 8) = *reinterpret_cast<uint2*>(q);
+  if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, inter >> 7, sf32)] = (uint8_t)e;
+}
+
 // ------------------------------------------------------------------------------------------ mxfp8 quantiser
 // out row r <- in row (src_rows ? src_rows[r] : r); rows whose source is negative are zero-filled with
 // scale 1.  One warp per 256 elements: lane holds 8 elements, 4 lanes share a scale.
@@ -465,6 +500,17 @@ GB_API int gb_silu_mul(const void* gate_up, void* out, long rows, int inter, int
   const long n = rows * (inter / 8);
   if (n <= 0) return 0;
   launch_k(silu_mul_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inter, ld);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_silu_mul_quant(const void* gate_up, const int* row_valid, void* out_q, void* out_sf, long rows, int inter, int ld, int sf32,
+                             cudaStream_t stream) {
+  if (inter % 128) return fail("silu_mul_quant: inter %% 128 != 0%s");
+  const long n = rows * (inter / 8);
+  if (n <= 0) return 0;
+  launch_k(silu_mul_quant_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)gate_up, row_valid, (uint8_t*)out_q,
+           (uint8_t*)out_sf, rows, inter, ld, sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

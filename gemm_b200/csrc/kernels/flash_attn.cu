@@ -109,7 +109,14 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     blk_lo = blk_lo + split * per;
     blk_hi = min(blk_hi, blk_lo + per);
   }
-  const int n_blk = max(0, blk_hi - blk_lo);
+  int n_blk = max(0, blk_hi - blk_lo);
+  // a work item that names a KV head this cache does not have (a work list built for other head counts): nothing of it is
+  // touched, the tile is written as "no keys" and the status word says why
+  const bool bad_item = kvh < 0 || kvh >= a.hkv || q_tok0 < 0 || q_len < 0;
+  if (bad_item) {
+    if (threadIdx.x == 0) report_status(a.status, ST_BAD_ARG, 640, kvh, a.hkv, q_tok0);
+    n_blk = 0;
+  }
 
 
   if (warp == 0) {
@@ -188,7 +195,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const int t_local = r / G, h_local = r - t_local * G;
-    const bool row_valid = (t_local < n_tok) && (r < tpt * G);
+    const bool row_valid = (t_local < n_tok) && (r < tpt * G) && !bad_item;
     const int qpos = pos0 + min(t_local, n_tok - 1);
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     float m = -INFINITY, l = 0.f;

@@ -315,8 +315,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     int acc = 0; uint32_t acc_ph = 0;
     bool ok = true;
     int dbg_t = 0;
-    const bool simple_store = !QUANT_OUT && args.amax_val == nullptr && args.peer_region_rows == 0 && args.row_map == nullptr &&
-                              args.peer_bcast == 0 && args.row_scale == nullptr && args.splits <= 1;
+    const bool simple_store = !QUANT_OUT && args.amax_val == nullptr && args.row_map == nullptr && args.peer_bcast == 0 &&
+                              args.row_scale == nullptr && args.splits <= 1;
     for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
       if (!mbar_wait(&accf_bar[acc], acc_ph, abort_flag, args.status, 300, acc)) { ok = false; break; }
       if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4096 + dbg_t] = clock64();
@@ -450,12 +450,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const size_t esz = args.out_f32 ? 4 : 2;
         const size_t last = ((size_t)(t.x_row0 + t.valid - 1) * args.ldo + n) * esz;
         bool store_ok = n_ok;
-        if (store_ok && args.out_bytes != 0 && last >= args.out_bytes) {
+        if (store_ok && args.out_bytes != 0 && args.peer_region_rows == 0 && last >= args.out_bytes) {
           report_status(args.status, ST_BAD_ARG, 312, t.x_row0 + t.valid - 1, n, ti);
           store_ok = false;
         }
-        __nv_bfloat16* o16 = (__nv_bfloat16*)args.out + (size_t)t.x_row0 * args.ldo + n;
-        float* o32 = (float*)args.out + (size_t)t.x_row0 * args.ldo + n;
+        void* obase = args.out;
+        size_t orow0 = (size_t)t.x_row0;
+        if (args.peer_region_rows > 0) {
+          // expert-parallel result rows go back to the GPU they came from; a tile never straddles two source regions
+          const int src = t.x_row0 / args.peer_region_rows;
+          obase = args.peer_out[src];
+          orow0 = (size_t)args.peer_rank * args.peer_region_rows + (size_t)(t.x_row0 - src * args.peer_region_rows);
+        }
+        __nv_bfloat16* o16 = (__nv_bfloat16*)obase + orow0 * args.ldo + n;
+        float* o32 = (float*)obase + orow0 * args.ldo + n;
 #pragma unroll 1
         for (int c = 0; c < TN; c += 16) {
           uint32_t r0[16], r1[16];

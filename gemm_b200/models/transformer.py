@@ -121,6 +121,27 @@ def apply_linear(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTensor] = N
     return y
 
 
+def expert_gate_up_mx(x_q: torch.Tensor, x_sf: torch.Tensor, w13: LinearWeight, n_w_groups: int, seg_start: torch.Tensor,
+                      seg_count: torch.Tensor, tn: int, hq: torch.Tensor, hsf: torch.Tensor, row_valid: Optional[torch.Tensor] = None,
+                      extras=None, w_groups: Optional[int] = None, scratch: Optional[torch.Tensor] = None) -> None:
+    """MXFP8 expert gate/up projection + SiLU(gate) * up + re-quantisation into ``hq`` / ``hsf`` (the down projection's input).
+
+    Decode-sized batches (token tile 32) run the two-accumulator GEMM with the activation and the quantiser in its epilogue.
+    Prefill-sized batches (token tile 128) run one plain GEMM over the stacked [gate; up] rows and a fused SiLU*up+quantise
+    kernel: two 128-token accumulators cannot be double-buffered in TMEM, so the fused epilogue would serialise with the
+    tensor-core work there (measured 2.1 ms against 0.8 ms for 16384 tokens x top-8)."""
+    two_i, hid = w13.rows_per_group, w13.k
+    wv = w13.mx.data.view(n_w_groups, two_i, hid)
+    if tn == 32 or not x_q.is_cuda:
+        gemm.grouped_linear(x_q, wv, seg_start, seg_count, tn, out=hq, dual=True, sfa=w13.mx.sf, sfb=x_sf, quant_out=True, out_sf=hsf,
+                            extras=extras, w_groups=w_groups, w_tiled=w13.mx.tiled)
+        return
+    gu = scratch if scratch is not None else torch.empty(x_q.shape[0], two_i, dtype=torch.bfloat16, device=x_q.device)
+    gemm.grouped_linear(x_q, wv, seg_start, seg_count, tn, out=gu, sfa=w13.mx.sf, sfb=x_sf, extras=extras, w_groups=w_groups,
+                        w_tiled=w13.mx.tiled)
+    ew.silu_mul_quant(gu, hq, hsf, row_valid, sf_layout=tn)
+
+
 class Transformer:
     def __init__(self, weights: ModelWeights, kv: KvCache, par=None):
         self.w = weights
@@ -169,8 +190,7 @@ class Transformer:
             dev = h.device
             hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=dev)
             hsf = ew.sf_alloc(pl.capacity, inter, dev, tn, init=False)
-            gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, out=hq, dual=True,
-                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf, w_tiled=lw.w13.mx.tiled)
+            expert_gate_up_mx(xq.data, xq.sf, lw.w13, e, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
             y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
                                     w_tiled=lw.w2.mx.tiled)
         else:

@@ -171,6 +171,23 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def silu_mul_quant(gate_up: torch.Tensor, out_q: torch.Tensor, out_sf: torch.Tensor, row_valid: Optional[torch.Tensor] = None,
+                   sf_layout: int = 128) -> None:
+    """``SiLU(gate) * up`` of ``gate_up [rows, 2I]`` (bf16) quantised to MXFP8 into ``out_q [rows, I]`` / ``out_sf`` (scale atoms of
+    layout ``sf_layout``).  Rows with ``row_valid < 0`` are left untouched."""
+    rows, two_i = gate_up.shape
+    inter = two_i // 2
+    if not gate_up.is_cuda:
+        g = gate_up.float()
+        h = torch.nn.functional.silu(g[:, :inter]) * g[:, inter:]
+        t = mxfp8.quantize(h, sf_layout=sf_layout)
+        out_q[:rows].copy_(t.data[:rows])
+        out_sf.copy_(t.sf[: out_sf.shape[0]])
+        return
+    _native.check(_native.cuda().gb_silu_mul_quant(_p(gate_up), _p(row_valid), _p(out_q), _p(out_sf), _l(rows), _i(inter),
+                                                   _i(gate_up.stride(0)), _i(1 if sf_layout == 32 else 0), _s()), "gb_silu_mul_quant")
+
+
 def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_rows: Optional[int] = None,
                 sf_layout: int = 128) -> MxTensor:
     """bf16 ``[rows, K]`` -> MXFP8.  With ``src_rows`` (int32) output row r is input row ``src_rows[r]``

@@ -150,9 +150,11 @@ class ExpertParallel:
         _native.check(rc, "gb_ep_dispatch")
         seg_start, seg_count = self.meta[0], self.meta[1]
         if self.mx:
-            gemm.grouped_linear(b["x"], lw.w13.mx.data.view(self.e_local, 2 * inter, hid), seg_start, seg_count, tn, out=b["hq"], dual=True,
-                                sfa=lw.w13.mx.sf, sfb=b["sf"], quant_out=True, out_sf=b["hsf"], extras=b["ex1"], w_groups=b["groups"],
-                                w_tiled=lw.w13.mx.tiled)
+            from ..models.transformer import expert_gate_up_mx
+            if tn != 32 and "gu" not in b:
+                b["gu"] = torch.empty(b["total"], 2 * inter, dtype=torch.bfloat16, device=self.device)
+            expert_gate_up_mx(b["x"], b["sf"], lw.w13, self.e_local, seg_start, seg_count, tn, b["hq"], b["hsf"], None, extras=b["ex1"],
+                              w_groups=b["groups"], scratch=b.get("gu"))
             gemm.grouped_linear(b["hq"], lw.w2.mx.data.view(self.e_local, hid, inter), seg_start, seg_count, tn, out=b["y"],
                                 sfa=lw.w2.mx.sf, sfb=b["hsf"], extras=b["ex2"], w_groups=b["groups"], w_tiled=lw.w2.mx.tiled)
         else:
@@ -186,8 +188,8 @@ class ExpertParallel:
             xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
             hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
             hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)
-            gemm.grouped_linear(xq.data, lw.w13.mx.data.view(e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, out=hq, dual=True,
-                                sfa=lw.w13.mx.sf, sfb=xq.sf, quant_out=True, out_sf=hsf, w_tiled=lw.w13.mx.tiled)
+            from ..models.transformer import expert_gate_up_mx
+            expert_gate_up_mx(xq.data, xq.sf, lw.w13, e_local, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
             y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e_local, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
                                     w_tiled=lw.w2.mx.tiled)
         else:

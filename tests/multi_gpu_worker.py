@@ -76,12 +76,12 @@ def run_model(model, cfg, toks, page, dev):
     outs = []
     for chunk in ([l // 2 for l in lens], [l - l // 2 for l in lens]):
         ids = torch.cat([toks[s][ctx[s]:ctx[s] + chunk[s]] for s in range(b)])
-        fb = ForwardBatch.build(chunk, ctx, ids, bt, page, cfg.n_heads, cfg.n_kv_heads, dev)
+        fb = ForwardBatch.build(chunk, ctx, ids, bt, page, model.hq_local, model.hkv_local, dev)
         outs.append(model.forward(fb).float())
         ctx = [c + q for c, q in zip(ctx, chunk)]
     for step in range(2):
         ids = torch.stack([toks[s][lens[s] + step] for s in range(b)])
-        fb = ForwardBatch.build([1] * b, ctx, ids, bt, page, cfg.n_heads, cfg.n_kv_heads, dev)
+        fb = ForwardBatch.build([1] * b, ctx, ids, bt, page, model.hq_local, model.hkv_local, dev)
         outs.append(model.forward(fb).float())
         ctx = [c + 1 for c in ctx]
     return outs

@@ -156,3 +156,23 @@ def test_argmax_and_sample():
     freq = (draws == top).float().mean().item()
     assert abs(freq - float(p[0])) < 0.12
     _native.assert_status_ok()
+
+
+@pytest.mark.parametrize("lay", [32, 128])
+def test_silu_mul_quant(lay):
+    torch.manual_seed(21)
+    rows, inter = 200, 768
+    gu = torch.randn(rows, 2 * inter, device="cuda").bfloat16()
+    valid = torch.arange(rows, device="cuda", dtype=torch.int32)
+    valid[5] = -1
+    rp = (rows + 127) // 128 * 128
+    q = torch.zeros(rp, inter, dtype=torch.uint8, device="cuda")
+    sf = ew.sf_alloc(rp, inter, "cuda", lay)
+    ew.silu_mul_quant(gu, q, sf, valid, sf_layout=lay)
+    g = gu.float()
+    ref = mxfp8.quantize(torch.nn.functional.silu(g[:, :inter]) * g[:, inter:], sf_layout=lay)
+    ok = valid >= 0
+    # __expf in the kernel against torch's exp: allow one fp8 code of difference on a few elements
+    a, b = mxfp8.dequantize(mxfp8.MxTensor(q, sf, rows, inter, lay)), mxfp8.dequantize(ref)
+    assert _rel(a[ok], b[ok]) < 2e-2
+    assert (q[5] == 0).all()
