@@ -22,7 +22,7 @@ constexpr int kMaxTopK = 16;
 // One warp per token.  E <= 512.
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
-                 int n_tok, int n_exp, int k, int mode, int renorm, float routed_scale, int ld) {
+                 int n_tok, int n_exp, int k, int mode, int renorm, float routed_scale, int ld, int id_shift, int n_local) {
   pdl_wait();
   pdl_trigger();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -82,7 +82,9 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bia
   if (lane < k) {
     float wv = my_w;
     if (renorm) wv = wv / fmaxf(wsum, 1e-20f);
-    ids[(size_t)w * k + lane] = my_id;
+    // expert-parallel ranks that see every token keep only their own experts: ids become local, the others -1
+    const int lid = my_id - id_shift;
+    ids[(size_t)w * k + lane] = (n_local > 0 && (lid < 0 || lid >= n_local)) ? -1 : lid;
     weights[(size_t)w * k + lane] = wv * routed_scale;
   }
 }
@@ -258,6 +260,57 @@ moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ 
   }
 }
 
+// Expert-parallel combine for decode-sized batches where every rank sees all tokens: this rank's experts contribute
+//   partial[t, :] = sum_{j : expert of (t, j) is local} w[t, j] * y[pair_row[t * k + j], :]        (fp32, fixed order)
+// and the row goes straight into slot `rank` of the token's home GPU (tokens_per_rank consecutive tokens per rank), where the
+// next RMSNorm sums the ranks' slots.  The last CTA advances the epoch and raises this rank's flag on every GPU.
+struct CombineScatterArgs {
+  const __nv_bfloat16* y; const int* pair_row; const float* weights;
+  int hidden, k, ld_y, tokens_per_rank;
+  float* slot[kMaxRanks];          // slot[p] = start of this rank's slot in rank p's heap ([tokens_per_rank, hidden] fp32)
+  uint32_t* flag[kMaxRanks];       // this rank's flag in rank p's heap
+  int world;
+  uint32_t* epoch_ctr; unsigned* done_ctr;
+};
+__global__ void __launch_bounds__(256)
+moe_combine_scatter_kernel(const CombineScatterArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  __shared__ int rows[kMaxTopK];
+  __shared__ float ws[kMaxTopK];
+  if (threadIdx.x < a.k) {
+    rows[threadIdx.x] = a.pair_row[(size_t)t * a.k + threadIdx.x];
+    ws[threadIdx.x] = a.weights ? a.weights[(size_t)t * a.k + threadIdx.x] : 1.0f;
+  }
+  __syncthreads();
+  const int home = t / a.tokens_per_rank, lr = t - home * a.tokens_per_rank;
+  float* dst = a.slot[home] + (size_t)lr * a.hidden;
+  for (int v = threadIdx.x; v < a.hidden / 8; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < a.k; ++j) {
+      const int r = rows[j];
+      if (r < 0) continue;
+      const uint4 raw = *reinterpret_cast<const uint4*>(a.y + (size_t)r * a.ld_y + v * 8);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); acc[2 * i] += ws[j] * f.x; acc[2 * i + 1] += ws[j] * f.y; }
+    }
+    reinterpret_cast<float4*>(dst + v * 8)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    reinterpret_cast<float4*>(dst + v * 8)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(a.done_ctr, 1u) == gridDim.x - 1) {
+      *a.done_ctr = 0;
+      const uint32_t e = *a.epoch_ctr + 1;
+      *a.epoch_ctr = e;
+      for (int p = 0; p < a.world; ++p) st_release_sys(a.flag[p], e);
+    }
+  }
+}
+
 // Plain row gather (bf16): out[r] = in[src[r]] or zeros when src[r] < 0.
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src, __nv_bfloat16* __restrict__ out,
                                    long rows, int hidden, int ld_in) {
@@ -278,10 +331,10 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ in, const i
 using namespace gb;
 
 GB_API int gb_moe_route(const float* logits, const float* bias, int* ids, float* weights, int n_tok, int n_exp, int k, int mode,
-                        int renorm, float routed_scale, int ld, cudaStream_t stream) {
+                        int renorm, float routed_scale, int ld, int id_shift, int n_local, cudaStream_t stream) {
   if (n_exp > 512 || k > kMaxTopK || k > n_exp) return fail("moe_route: need n_exp <= 512 and k <= 16%s");
   if (n_tok <= 0) return 0;
-  launch_k(moe_route_kernel, (n_tok + 7) / 8, 256, 0, stream, logits, bias, ids, weights, n_tok, n_exp, k, mode, renorm, routed_scale, ld);
+  launch_k(moe_route_kernel, (n_tok + 7) / 8, 256, 0, stream, logits, bias, ids, weights, n_tok, n_exp, k, mode, renorm, routed_scale, ld, id_shift, n_local);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -314,6 +367,22 @@ GB_API int gb_moe_combine(const void* y, const int* pair_row, const float* weigh
   if (n_tok <= 0) return 0;
   launch_k(moe_combine_kernel, n_tok, 256, 0, stream, (const __nv_bfloat16*)y, pair_row, weights, (__nv_bfloat16*)out, hidden, k, ld_y,
                                                (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// slots[p] / flags[p]: device pointers (as mapped in this process) of this rank's slot and flag on rank p.
+GB_API int gb_moe_combine_scatter(const void* y, const int* pair_row, const float* weights, int n_tok, int hidden, int k, int ld_y,
+                                  int tokens_per_rank, void* const* slots, void* const* flags, int world, void* epoch_ctr, void* done_ctr,
+                                  cudaStream_t stream) {
+  if (hidden % 8 || k > kMaxTopK || world > kMaxRanks) return fail("moe_combine_scatter: hidden %% 8 != 0, k > 16 or world > 8%s");
+  if (n_tok <= 0 || n_tok != tokens_per_rank * world) return fail("moe_combine_scatter: n_tok must be tokens_per_rank * world%s");
+  CombineScatterArgs a;
+  memset(&a, 0, sizeof(a));
+  a.y = (const __nv_bfloat16*)y; a.pair_row = pair_row; a.weights = weights; a.hidden = hidden; a.k = k; a.ld_y = ld_y;
+  a.tokens_per_rank = tokens_per_rank; a.world = world; a.epoch_ctr = (uint32_t*)epoch_ctr; a.done_ctr = (unsigned*)done_ctr;
+  for (int p = 0; p < world; ++p) { a.slot[p] = (float*)slots[p]; a.flag[p] = (uint32_t*)flags[p]; }
+  launch_k(moe_combine_scatter_kernel, n_tok, 256, 0, stream, a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -46,15 +46,22 @@ def route_ref(logits: torch.Tensor, k: int, mode: str = "softmax", bias: Optiona
 
 
 def route(logits: torch.Tensor, k: int, mode: str = "softmax", bias: Optional[torch.Tensor] = None, renorm: bool = True,
-          routed_scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``logits`` f32 [T, E] -> (ids int32 [T, k], weights f32 [T, k])."""
+          routed_scale: float = 1.0, local_range: Optional[Tuple[int, int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``logits`` f32 [T, E] -> (ids int32 [T, k], weights f32 [T, k]).  ``local_range = (first, count)`` turns the ids into
+    indices of this rank's experts (``id - first``) and marks the picks that belong to other ranks with -1; the weights are
+    still those of the full top-k."""
     if not logits.is_cuda:
-        return route_ref(logits, k, mode, bias, renorm, routed_scale)
+        ids, w = route_ref(logits, k, mode, bias, renorm, routed_scale)
+        if local_range is not None:
+            lid = ids - local_range[0]
+            ids = torch.where((lid >= 0) & (lid < local_range[1]), lid, torch.full_like(lid, -1))
+        return ids, w
     t, e = logits.shape
     ids = torch.empty(t, k, dtype=torch.int32, device=logits.device)
     w = torch.empty(t, k, dtype=torch.float32, device=logits.device)
     rc = _native.cuda().gb_moe_route(_p(logits), _p(bias), _p(ids), _p(w), _i(t), _i(e), _i(k), _i(0 if mode == "softmax" else 1),
-                                     _i(1 if renorm else 0), _f(routed_scale), _i(logits.stride(0)), _s())
+                                     _i(1 if renorm else 0), _f(routed_scale), _i(logits.stride(0)),
+                                     _i(local_range[0] if local_range else 0), _i(local_range[1] if local_range else 0), _s())
     _native.check(rc, "gb_moe_route")
     return ids, w
 

@@ -8,6 +8,12 @@ Rank ``r`` owns the experts ``[r * E/N, (r+1) * E/N)`` and attends to its own se
   the result rows straight back into the source GPU's combine buffer and raises its flag  ->  combine kernel on
   the source (waits for the owners' flags, router-weighted sum in fixed order).
 
+Decode-sized batches (at most ``gather_max`` tokens per rank) take a second route, because there the step is bound by
+the expert weights every GPU has to stream, and per-source row groups would make each GPU stream its experts once per
+source: the ranks all-gather their few token rows (peer stores), every rank routes ALL tokens and runs its own experts
+over one merged token tile per expert, and the combine kernel sums this rank's experts per token in fp32 and stores the
+row into its slot on the token's home GPU, where the next RMSNorm kernel adds the ranks' slots to the residual.
+
 No NCCL call and no host synchronisation is involved; the exchange is the prologue / epilogue of the compute
 kernels.  ``fused=False`` selects the baseline that only calls NCCL: all-gather the tokens, run the owned experts on
 all of them, reduce-scatter the partial sums — the reference's own expert-parallel formulation
@@ -29,9 +35,19 @@ from .fabric import Fabric
 _c, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 
 
+class PendingSlots:
+    """fp32 partial sums of a MoE layer sitting in the per-rank slots of this GPU; finished by the next RMSNorm."""
+
+    def __init__(self, g: dict, rows: int):
+        self.g, self.rows = g, rows
+
+
 class ExpertParallel:
+    use_gather = True        # False forces the dispatch route for every batch size (tests)
     tp_size = 1
     tp_rank = 0
+
+    gather_max = 64          # tokens per rank up to which the all-gather route is taken
 
     def __init__(self, group, device: torch.device, fused: bool = True):
         self.group = group
@@ -58,7 +74,8 @@ class ExpertParallel:
         x_bytes = total_rows * hid * (1 if mx else 2)
         sf_bytes = (total_rows // 32) * (hid // 128) * 512 if mx else 0
         y_bytes = total_rows * hid * 2
-        heap = x_bytes + sf_bytes + y_bytes + (4 << 20)
+        g_caps = sorted({min(c, max_tokens) for c in (8, self.gather_max)})
+        heap = x_bytes + sf_bytes + y_bytes + (4 << 20) + sum(w * c * hid * (2 + 4) + 4096 for c in g_caps)
         self.fab = Fabric(self.group, self.device, heap)
         f = self.fab
         self.x_off = f.alloc(x_bytes)
@@ -72,6 +89,17 @@ class ExpertParallel:
         self.mx = mx
         self.total_rows_max = total_rows
         self.meta = f.view(self.meta_off, (2, w * self.e_local), torch.int32)
+        # all-gather route: per capacity a gather buffer, the fp32 partial slots and one flag per source rank
+        self._gather = {}
+        for cap in g_caps:
+            g = {"cap": cap, "ag": f.make_exchange(cap * hid * 2, chunks=max(1, min(8, cap // 8)))}
+            g["stage"] = torch.zeros(cap, hid, dtype=torch.bfloat16, device=self.device)
+            g["slots_off"] = f.alloc(w * cap * hid * 4)
+            g["flags_off"] = f.alloc(32)
+            g["epoch"], g["done"] = f.ctl_word(), f.ctl_word()
+            g["slot_ptrs"] = (ctypes.c_void_p * 8)(*[f.peer_ptr(p, g["slots_off"]) + self.ep_rank * cap * hid * 4 for p in range(w)])
+            g["flag_ptrs"] = (ctypes.c_void_p * 8)(*[f.peer_ptr(p, g["flags_off"]) + 4 * self.ep_rank for p in range(w)])
+            self._gather[cap] = g
 
     def _bucket(self, t: int) -> dict:
         """Buffer geometry for a forward pass of ``t`` tokens (rounded up so that all ranks agree)."""
@@ -125,15 +153,76 @@ class ExpertParallel:
         from ..models.transformer import apply_linear
         return apply_linear(lw, x, x_mx)
 
-    def add_norm(self, delta, weight, eps, residual, **kw):
-        return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
+    def add_norm(self, delta, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128):
+        if not isinstance(delta, PendingSlots):
+            kw = dict(quantize=quantize, want_bf16=want_bf16, sf_layout=sf_layout) if quantize else {}
+            return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
+        f, g = self.fab, delta.g
+        rows, hidden, cap = delta.rows, self.cfg.hidden, g["cap"]
+        out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device) if want_bf16 or not quantize else None
+        q = sf = None
+        if quantize:
+            rp = (rows + 127) // 128 * 128
+            q = torch.empty(rp, hidden, dtype=torch.uint8, device=self.device)
+            sf = ew.sf_alloc(rp, hidden, self.device, sf_layout, init=False)
+        p = lambda t: _c(t.data_ptr()) if t is not None else _c(0)
+        rc = f.lib.gb_rmsnorm_reduce(p(residual), _c(f.local_base + g["slots_off"]), _i(self.ep_size), ctypes.c_long(cap * hidden), p(weight),
+                                     p(out), p(q), p(sf), _i(rows), _i(hidden), ctypes.c_float(eps), _i(1 if sf_layout == 32 else 0),
+                                     _c(f.local_base + g["flags_off"]), _i(self.ep_size), _c(g["epoch"]), _c(_native.status_ptr()),
+                                     _c(torch.cuda.current_stream().cuda_stream))
+        _native.check(rc, "gb_rmsnorm_reduce")
+        if quantize:
+            from ..ops.mxfp8 import MxTensor
+            return out, MxTensor(q, sf, rows, hidden, sf_layout)
+        return out
 
     def materialize(self, delta):
+        if isinstance(delta, PendingSlots):
+            f, g = self.fab, delta.g
+            slots = f.view(g["slots_off"], (self.ep_size, g["cap"], self.cfg.hidden), torch.float32)
+            f.barrier()          # every rank's combine kernel (and its stores) precede its arrival at the barrier
+            return slots[:, : delta.rows].sum(0).to(torch.bfloat16)
         return delta.materialize() if hasattr(delta, "materialize") else delta
+
+    def _moe_gather(self, model, lw, h: torch.Tensor):
+        """Decode-sized batches: all-gather the token rows, run the local experts over all of them, scatter fp32 partial sums."""
+        cfg, w, f = self.cfg, self.ep_size, self.fab
+        t = h.shape[0]
+        k, inter, hid = cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
+        g = self._gather[min(c for c in self._gather if t <= c)]
+        cap = g["cap"]
+        g["stage"][:t].copy_(h)
+        allh = g["ag"].all_gather(g["stage"]).view(torch.bfloat16).view(w * cap, hid)
+        logits = gemm.linear(allh, lw.router, out_dtype=torch.float32)
+        ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale,
+                             local_range=(self.ep_rank * self.e_local, self.e_local))
+        if self.mx:
+            from ..models.transformer import expert_gate_up_mx
+            tn = 32
+            pl = moe.plan(ids, self.e_local, tn)
+            xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
+            hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
+            hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)
+            expert_gate_up_mx(xq.data, xq.sf, lw.w13, self.e_local, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
+            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(self.e_local, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
+                                    w_tiled=lw.w2.mx.tiled)
+        else:
+            tn = gemm.pick_tn(max(1, (w * cap * k + cfg.n_experts - 1) // cfg.n_experts), dual=True)
+            pl = moe.plan(ids, self.e_local, tn)
+            xs = moe.gather_rows(allh, pl.row_token)
+            act = gemm.grouped_linear(xs, lw.w13.w.view(self.e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
+            y = gemm.grouped_linear(act, lw.w2.w.view(self.e_local, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)
+        rc = f.lib.gb_moe_combine_scatter(_c(y.data_ptr()), _c(pl.pair_row.data_ptr()), _c(wts.data_ptr()), _i(w * cap), _i(hid), _i(k),
+                                          _i(y.stride(0)), _i(cap), g["slot_ptrs"], g["flag_ptrs"], _i(w), _c(g["epoch"]), _c(g["done"]),
+                                          _c(torch.cuda.current_stream().cuda_stream))
+        _native.check(rc, "gb_moe_combine_scatter")
+        return PendingSlots(g, t)
 
     def moe_ffn(self, model, lw, h: torch.Tensor) -> torch.Tensor:
         if not self.fused:
             return self._moe_nccl(model, lw, h)
+        if h.shape[0] <= min(self.gather_max, self.max_tokens) and self.use_gather:
+            return self._moe_gather(model, lw, h)
         cfg, w, f = self.cfg, self.ep_size, self.fab
         t = h.shape[0]
         e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden

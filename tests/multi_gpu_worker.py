@@ -87,7 +87,7 @@ def run_model(model, cfg, toks, page, dev):
     return outs
 
 
-def check_expert_parallel(rank, world, dev, fmt, fused):
+def check_expert_parallel(rank, world, dev, fmt, fused, gather=True):
     cfg = get_config("tiny-moe")
     page = 16
     # every rank gets sequences of the same lengths (the NCCL baseline gathers equal token counts) with its own content
@@ -98,6 +98,7 @@ def check_expert_parallel(rank, world, dev, fmt, fused):
     ref_model = Transformer(w_full, KvCache.allocate(cfg, 64, page, dev))
     ref = run_model(ref_model, cfg, mine, page, dev)
     par = ExpertParallel(dist.group.WORLD, dev, fused=fused)
+    par.use_gather = gather          # True: small batches all-gather their tokens; False: every batch is dispatched row by row
 
     class _E:            # the slice of the Engine interface that attach() needs
         w = w_ep
@@ -109,7 +110,7 @@ def check_expert_parallel(rank, world, dev, fmt, fused):
     tol = 2e-2 if fmt == "bf16" else 6e-2
     for a, b in zip(got, ref):
         r = rel(a, b)
-        assert r < tol, f"EP({fmt}, fused={fused}) differs from the single-GPU engine: rel {r}"
+        assert r < tol, f"EP({fmt}, fused={fused}, gather={gather}) differs from the single-GPU engine: rel {r}"
     dist.barrier()
     par.close()
 
@@ -158,8 +159,8 @@ def main():
         dist.barrier()
         fab.close()
     if what in ("all", "ep"):
-        for fmt, fused in (("bf16", True), ("mxfp8", True), ("mxfp8", False)):
-            check_expert_parallel(rank, world, dev, fmt, fused)
+        for fmt, fused, gather in (("bf16", True, True), ("mxfp8", True, True), ("bf16", True, False), ("mxfp8", True, False), ("mxfp8", False, True)):
+            check_expert_parallel(rank, world, dev, fmt, fused, gather)
     if what in ("all", "tp"):
         for fmt, fused in (("bf16", True), ("mxfp8", True), ("bf16", False)):
             check_tensor_parallel(rank, world, dev, fmt, fused)
