@@ -48,18 +48,51 @@ def parse_args():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks, power and throttle reasons of one GPU while the timed region runs (read-only NVML queries from a
+    thread, every 20 ms; ``nvidia-smi -lms`` as the fallback when the NVML binding is missing)."""
     FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
+    def __init__(self, gpu_index: int, uuid: str = ""):
+        self.gpu, self.uuid = gpu_index, uuid
         self.proc = None
         self.lines = []
+        self.samples = []          # (sm_mhz, max_mhz, power_w, set(reasons))
+        self.stop_flag = False
+        self.thread = None
+        self.mode = None
+
+    def _nvml_loop(self, nv, h):
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        while not self.stop_flag:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((float(sm), float(mx), pw, {n for n, b in bits.items() if r & b}))
+            except Exception:
+                pass
+            time.sleep(0.02)
 
     def start(self):
         try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByUUID(self.uuid) if self.uuid else nv.nvmlDeviceGetHandleByIndex(self.gpu)
+            self.mode = "nvml"
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.mode = None
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.mode = "smi"
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -70,29 +103,32 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            pass
-        sm, mx, reasons, power = [], [], set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
-            parts = [p.strip() for p in ln.split(",")]
-            if len(parts) < 8:
-                continue
+        if self.mode is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML binding and no nvidia-smi"], "samples": 0}
+        if self.mode == "nvml":
+            self.stop_flag = True
+            self.thread.join(timeout=1)
+        else:
+            self.proc.terminate()
             try:
-                sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
-            except ValueError:
-                continue
-            for nm, v in zip(names, parts[4:8]):
-                if v.lower().startswith("active"):
-                    reasons.add(nm)
+                self.proc.wait(timeout=2)
+            except Exception:
+                pass
+            for ln in self.lines:
+                parts = [p.strip() for p in ln.split(",")]
+                if len(parts) < 8:
+                    continue
+                try:
+                    self.samples.append((float(parts[1]), float(parts[2]), float(parts[3]),
+                                         {nm for nm, v in zip(self.NAMES, parts[4:8]) if v.lower().startswith("active")}))
+                except ValueError:
+                    continue
+        sm = [x[0] for x in self.samples]
+        power = [x[2] for x in self.samples]
+        reasons = set().union(*[x[3] for x in self.samples]) if self.samples else set()
         busy = [c for c, p in zip(sm, power) if p > 300] or sm
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(x[1] for x in self.samples) if self.samples else None,
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None, "source": self.mode}
 
 
 def reference_arm(args):
@@ -164,6 +200,8 @@ def main():
     # warm-up pass on a short prompt so that lazy initialisation is not timed
     engine.prefill([prompts[0][:256]])
     engine.reset()
+    engine.prefill(prompts[: min(8, b_local)])        # one full-size chunk: the prefill-sized kernel variants are loaded too
+    engine.reset()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -181,7 +219,11 @@ def main():
     for _ in range(args.warmup):
         engine.decode_step()
     barrier()
-    sampler = ClockSampler(local_rank)
+    try:
+        _uuid = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
+    except Exception:
+        _uuid = ""
+    sampler = ClockSampler(local_rank, _uuid)
     sampler.start()
     step_ms = []
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]

@@ -89,6 +89,53 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bia
   }
 }
 
+// Router logits for decode-sized batches on the CUDA cores: out[m, n] = sum_k x[m, k] * w[n, k] (bf16 in, fp32 out).
+// A 128 x 2048 router matrix is one tensor-core tile, i.e. one CTA walking 32 k-steps (about 20 us); here 64 CTAs each take
+// 8 tokens (staged in shared memory) x 16 experts and finish in a few microseconds.  k % 256 == 0, k <= 8192.
+constexpr int kSlTok = 8, kSlRows = 16;
+__global__ void __launch_bounds__(256)
+small_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, float* __restrict__ out, int m, int n, int k,
+                    int ldx, int ldw, int ldo) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ uint4 sx[];                     // [kSlTok][k / 8] vectors of 8 bf16
+  const int n0 = blockIdx.x * kSlRows, m0 = blockIdx.y * kSlTok;
+  const int kv = k >> 3;
+  for (int i = threadIdx.x; i < kSlTok * kv; i += blockDim.x) {
+    const int tk = i / kv, v = i - tk * kv;
+    sx[i] = (m0 + tk < m) ? *reinterpret_cast<const uint4*>(x + (size_t)(m0 + tk) * ldx + v * 8) : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll 1
+  for (int rr = 0; rr < kSlRows / 8; ++rr) {
+    const int row = n0 + warp * (kSlRows / 8) + rr;
+    if (row >= n) continue;
+    float acc[kSlTok];
+#pragma unroll
+    for (int i = 0; i < kSlTok; ++i) acc[i] = 0.f;
+    for (int v = lane; v < kv; v += 32) {
+      const uint4 wr = *reinterpret_cast<const uint4*>(w + (size_t)row * ldw + v * 8);
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wr);
+      float wf[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(wh[i]); wf[2 * i] = f.x; wf[2 * i + 1] = f.y; }
+#pragma unroll
+      for (int tk = 0; tk < kSlTok; ++tk) {
+        const uint4 xr = sx[tk * kv + v];
+        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xr);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(xh[i]); acc[tk] += wf[2 * i] * f.x + wf[2 * i + 1] * f.y; }
+      }
+    }
+#pragma unroll
+    for (int tk = 0; tk < kSlTok; ++tk) {
+      const float s = warp_sum(acc[tk]);
+      if (lane == 0 && m0 + tk < m) out[(size_t)(m0 + tk) * ldo + row] = s;
+    }
+  }
+}
+
 constexpr int kPlanBlock = 256;
 
 // block_hist[b][e] = pairs of block b routed to expert e (pairs whose expert is outside [e_lo, e_hi) are dropped)
@@ -199,14 +246,13 @@ moe_plan_small_kernel(const int* __restrict__ ids, int* __restrict__ seg_start, 
     if (e >= 0) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();
-  if (t < n_exp / experts_per_region) {
+  // aligned segment starts: every expert sums the padded counts of the experts before it in its region (parallel, E <= 512)
+  for (int e = t; e < n_exp; e += blockDim.x) {
+    const int r = e / experts_per_region, e0 = r * experts_per_region;
     int pos = 0;
-    for (int i = 0; i < experts_per_region; ++i) {
-      const int ee = t * experts_per_region + i;
-      start[ee] = t * region_rows + pos;
-      pos += (cnt[ee] + align - 1) / align * align;
-    }
-    if (region_rows_used != nullptr) region_rows_used[t] = pos;
+    for (int i = e0; i < e; ++i) pos += (cnt[i] + align - 1) / align * align;
+    start[e] = r * region_rows + pos;
+    if (region_rows_used != nullptr && e == e0 + experts_per_region - 1) region_rows_used[r] = pos + (cnt[e] + align - 1) / align * align;
   }
   __syncthreads();
   for (int e = t; e < n_exp; e += blockDim.x) { seg_start[e] = start[e]; seg_count[e] = cnt[e]; }
@@ -329,6 +375,18 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ in, const i
 }  // namespace gb
 
 using namespace gb;
+
+GB_API int gb_small_linear(const void* x, const void* w, float* out, int m, int n, int k, int ldx, int ldw, int ldo, cudaStream_t stream) {
+  if (k % 256 || k > 8192) return fail("small_linear: k must be a multiple of 256 and <= 8192%s");
+  if (m <= 0 || n <= 0) return 0;
+  const size_t smem = (size_t)kSlTok * k * 2;
+  static bool attr_set = false;
+  if (!attr_set) { GB_CUDA_OK(cudaFuncSetAttribute(small_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 8192 * 2)); attr_set = true; }
+  launch_k(small_linear_kernel, dim3((n + kSlRows - 1) / kSlRows, (m + kSlTok - 1) / kSlTok), 256, smem, stream, (const __nv_bfloat16*)x,
+           (const __nv_bfloat16*)w, out, m, n, k, ldx, ldw, ldo);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 GB_API int gb_moe_route(const float* logits, const float* bias, int* ids, float* weights, int n_tok, int n_exp, int k, int mode,
                         int renorm, float routed_scale, int ld, int id_shift, int n_local, cudaStream_t stream) {

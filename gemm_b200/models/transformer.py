@@ -180,7 +180,7 @@ class Transformer:
         cfg = self.cfg
         t = h.shape[0]
         e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
-        logits = gemm.linear(h, lw.router, out_dtype=torch.float32)
+        logits = moe.router_logits(h, lw.router)
         ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
         if self.mx:
             # token tile (= scale-atom layout) by the expected rows per expert: 32 for decode-sized batches

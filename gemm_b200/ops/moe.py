@@ -28,6 +28,20 @@ def _s():
     return _c(torch.cuda.current_stream().cuda_stream)
 
 
+def router_logits(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Router logits ``f32 [T, E] = h [T, H] @ w [E, H]^T`` (bf16 operands).  Up to 256 tokens run on a CUDA-core kernel that spreads
+    the small matrix over many CTAs; larger batches use the tensor-core GEMM."""
+    from . import gemm
+    t, k = h.shape
+    if h.is_cuda and t <= 256 and k % 256 == 0 and k <= 8192 and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        out = torch.empty(t, w.shape[0], dtype=torch.float32, device=h.device)
+        rc = _native.cuda().gb_small_linear(_p(h), _p(w), _p(out), _i(t), _i(w.shape[0]), _i(k), _i(h.stride(0)), _i(w.stride(0)),
+                                            _i(out.stride(0)), _s())
+        _native.check(rc, "gb_small_linear")
+        return out
+    return gemm.linear(h, w, out_dtype=torch.float32)
+
+
 def route_ref(logits: torch.Tensor, k: int, mode: str = "softmax", bias: Optional[torch.Tensor] = None,
               renorm: bool = True, routed_scale: float = 1.0):
     lf = torch.nan_to_num(logits.float(), nan=-3.4e38)

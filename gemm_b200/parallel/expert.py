@@ -74,7 +74,7 @@ class ExpertParallel:
         x_bytes = total_rows * hid * (1 if mx else 2)
         sf_bytes = (total_rows // 32) * (hid // 128) * 512 if mx else 0
         y_bytes = total_rows * hid * 2
-        g_caps = sorted({min(c, max_tokens) for c in (8, self.gather_max)})
+        g_caps = sorted({min(c, max_tokens) for c in (8, 16, 32, self.gather_max)})
         heap = x_bytes + sf_bytes + y_bytes + (4 << 20) + sum(w * c * hid * (2 + 4) + 4096 for c in g_caps)
         self.fab = Fabric(self.group, self.device, heap)
         f = self.fab
@@ -193,7 +193,7 @@ class ExpertParallel:
         cap = g["cap"]
         g["stage"][:t].copy_(h)
         allh = g["ag"].all_gather(g["stage"]).view(torch.bfloat16).view(w * cap, hid)
-        logits = gemm.linear(allh, lw.router, out_dtype=torch.float32)
+        logits = moe.router_logits(allh, lw.router)
         ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale,
                              local_range=(self.ep_rank * self.e_local, self.e_local))
         if self.mx:
@@ -228,7 +228,7 @@ class ExpertParallel:
         e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
         b = self._bucket(t)
         tn, rows = b["tn"], b["region_rows"]
-        logits = gemm.linear(h, lw.router, out_dtype=torch.float32)
+        logits = moe.router_logits(h, lw.router)
         ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
         pl = moe.plan(ids, e, tn, regions=w, epoch_ctr=self.epoch, region_rows=rows)
         stream = _c(torch.cuda.current_stream().cuda_stream)
@@ -266,7 +266,7 @@ class ExpertParallel:
             parts = [torch.empty_like(h) for _ in range(w)]
             dist.all_gather(parts, h.contiguous(), group=self.group)
             allh = torch.cat(parts)
-        logits = gemm.linear(allh, lw.router, out_dtype=torch.float32)
+        logits = moe.router_logits(allh, lw.router)
         ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
         local = ids - self.ep_rank * e_local
         local = torch.where((local >= 0) & (local < e_local), local, torch.full_like(local, -1))

@@ -176,3 +176,13 @@ def test_silu_mul_quant(lay):
     a, b = mxfp8.dequantize(mxfp8.MxTensor(q, sf, rows, inter, lay)), mxfp8.dequantize(ref)
     assert _rel(a[ok], b[ok]) < 2e-2
     assert (q[5] == 0).all()
+
+
+@pytest.mark.parametrize("t,e,k", [(1, 128, 2048), (64, 128, 2048), (77, 60, 1024), (256, 256, 4096)])
+def test_router_logits_small_batch(t, e, k):
+    torch.manual_seed(22)
+    h = torch.randn(t, k, device="cuda").bfloat16()
+    w = (torch.randn(e, k, device="cuda") * 0.05).bfloat16()
+    got = moe.router_logits(h, w)
+    ref = h.float() @ w.float().t()
+    assert got.dtype == torch.float32 and _rel(got, ref) < 1e-5
