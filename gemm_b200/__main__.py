@@ -1,0 +1,164 @@
+"""Command line of the framework: ``python -m gemm_b200 <command> ...``.
+
+  generate   load a checkpoint (GGUF / HF safetensors directory / synthetic preset) and complete one or more prompts
+  serve      OpenAI-compatible HTTP server over the continuous-batching engine
+  inspect    dump the metadata and tensor table of a GGUF file
+  tokenize   print the token ids (and pieces) of a text with the tokenizer stored in a GGUF file
+  stage      cut a checkpoint into per-rank blobs in the run-time weight format
+  microbench kernel micro-benchmarks (same as ``python -m gemm_b200.utils.microbench``)
+  build      compile the native libraries in-tree
+
+The reference spreads these over separate programs: cpu/llm/test_transformer.c (generate: ``<model> [prompt] [max_gen]
+[n_threads]``), server/server.c (``--model --host --port``), tests/test_gguf_loader.c, tests/test_bpe_tokenizer.c and
+common/m3_stage.c.  Environment variables of the reference (LLM_THREADS, M3_PREFILL, ...) become flags here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+
+def _load_llm(args):
+    import os
+    from .serve.llm import LLM
+    kw = dict(max_running=args.max_running, num_pages=args.pages, page_size=args.page_size)
+    if args.model.startswith("synthetic:"):
+        return LLM.from_synthetic(args.model.split(":", 1)[1], fmt=args.format, device=args.device, **kw)
+    if os.path.isdir(args.model):
+        tok = None
+        if args.tokenizer:
+            from .utils import gguf as G
+            from .utils.tokenizer import Tokenizer
+            with G.GGUFFile(args.tokenizer) as f:
+                tok = Tokenizer.from_gguf(f)
+        return LLM.from_safetensors(args.model, fmt=args.format, device=args.device, tokenizer=tok, **kw)
+    return LLM.from_gguf(args.model, fmt=args.format, device=args.device, **kw)
+
+
+def _add_model_args(p):
+    p.add_argument("--model", required=True, help="GGUF file, HF safetensors directory, or synthetic:<preset>")
+    p.add_argument("--format", default="bf16", choices=["bf16", "mxfp8"], help="run-time weight format")
+    p.add_argument("--device", default="cuda")
+    p.add_argument("--tokenizer", default="", help="GGUF file to take the tokenizer from (safetensors checkpoints)")
+    p.add_argument("--max-running", type=int, default=64)
+    p.add_argument("--pages", type=int, default=512, help="KV cache pages")
+    p.add_argument("--page-size", type=int, default=128)
+
+
+def cmd_generate(args):
+    from .serve.engine import SamplingParams
+    llm = _load_llm(args)
+    prompts = args.prompt or ["Hello"]
+    sp = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, seed=args.seed)
+    enc = []
+    for p in prompts:
+        if args.ids:
+            enc.append([int(x) for x in p.replace(",", " ").split()])
+        elif llm.tokenizer is None:
+            sys.exit("this checkpoint carries no tokenizer: pass --ids and prompts as token ids, or --tokenizer <gguf>")
+        else:
+            enc.append(llm.tokenizer.encode(p))
+    t0 = time.time()
+    outs = llm.generate(enc, sp)
+    dt = time.time() - t0
+    n_new = sum(len(o) for o in outs)
+    for p, o in zip(prompts, outs):
+        text = llm.decode(o) if llm.tokenizer is not None else " ".join(map(str, o))
+        print(json.dumps({"prompt": p, "completion": text, "token_ids": o}))
+    print(json.dumps({"new_tokens": n_new, "seconds": round(dt, 3), "tokens_per_s": round(n_new / max(dt, 1e-9), 1)}), file=sys.stderr)
+
+
+def cmd_serve(args):
+    from .serve.server import serve
+    llm = _load_llm(args)
+    print(f"serving {args.model} on http://{args.host}:{args.port}", file=sys.stderr)
+    serve(llm, host=args.host, port=args.port, model_name=args.name or args.model, block=True)
+
+
+def cmd_inspect(args):
+    from .utils import gguf as G
+    with G.GGUFFile(args.file) as f:
+        print(f"version {f.version}  alignment {f.alignment}  tensors {len(f.tensors)}  kv {len(f.metadata)}")
+        for k, v in f.metadata.items():
+            s = repr(v)
+            print(f"  {k} = {s if len(s) < 100 else s[:97] + '...'}")
+        if args.tensors:
+            for t in f.tensors.values():
+                print(f"  {t.name:48s} {str(tuple(t.shape)):28s} {t.type_name:8s} bytes {t.nbytes}")
+
+
+def cmd_tokenize(args):
+    from .utils import gguf as G
+    from .utils.tokenizer import Tokenizer
+    with G.GGUFFile(args.file) as f:
+        tok = Tokenizer.from_gguf(f)
+    ids = tok.encode(args.text)
+    print(json.dumps({"ids": ids, "pieces": [tok.decode([i]) for i in ids], "roundtrip": tok.decode(ids)}, ensure_ascii=False))
+
+
+def cmd_stage(args):
+    import os
+    from .models import loader
+    from .utils import gguf as G
+    from .utils import stage
+    if os.path.isdir(args.model):
+        cfg, src = loader.config_from_hf(args.model), loader.SafetensorsSource(args.model)
+    else:
+        f = G.GGUFFile(args.model)
+        cfg, src = loader.config_from_gguf(f), loader.GGUFSource(f)
+    stage.stage(cfg, src, args.out, args.format, tp_size=args.tp, ep_size=args.ep)
+    print(json.dumps({"ranks": max(args.tp, args.ep), "out": args.out}))
+
+
+def cmd_build(args):
+    from . import build
+    build.build_all(verbose=True)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="python -m gemm_b200", description=__doc__.split("\n")[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("generate", help="complete prompts")
+    _add_model_args(g)
+    g.add_argument("--prompt", action="append", help="prompt text (repeatable); with --ids, space separated token ids")
+    g.add_argument("--ids", action="store_true")
+    g.add_argument("--max-new-tokens", type=int, default=64)
+    g.add_argument("--temperature", type=float, default=0.0)
+    g.add_argument("--top-k", type=int, default=0)
+    g.add_argument("--top-p", type=float, default=1.0)
+    g.add_argument("--seed", type=int, default=0)
+    g.set_defaults(fn=cmd_generate)
+    s = sub.add_parser("serve", help="HTTP server")
+    _add_model_args(s)
+    s.add_argument("--host", default="127.0.0.1")
+    s.add_argument("--port", type=int, default=8080)
+    s.add_argument("--name", default="")
+    s.set_defaults(fn=cmd_serve)
+    i = sub.add_parser("inspect", help="dump a GGUF file")
+    i.add_argument("file")
+    i.add_argument("--tensors", action="store_true")
+    i.set_defaults(fn=cmd_inspect)
+    t = sub.add_parser("tokenize", help="tokenize a text")
+    t.add_argument("file")
+    t.add_argument("text")
+    t.set_defaults(fn=cmd_tokenize)
+    st = sub.add_parser("stage", help="per-rank weight blobs")
+    st.add_argument("--model", required=True)
+    st.add_argument("--out", required=True)
+    st.add_argument("--format", default="mxfp8", choices=["bf16", "mxfp8"])
+    st.add_argument("--tp", type=int, default=1)
+    st.add_argument("--ep", type=int, default=1)
+    st.set_defaults(fn=cmd_stage)
+    mb = sub.add_parser("microbench", help="kernel micro-benchmarks")
+    mb.add_argument("rest", nargs=argparse.REMAINDER)
+    mb.set_defaults(fn=lambda a: __import__("gemm_b200.utils.microbench", fromlist=["main"]).main(a.rest))
+    b = sub.add_parser("build", help="compile the native libraries")
+    b.set_defaults(fn=cmd_build)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

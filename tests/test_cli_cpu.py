@@ -1,0 +1,31 @@
+"""Command line: generate from a synthetic preset on CPU, inspect / tokenize / stage a GGUF written by the library itself."""
+import json
+import os
+
+import pytest
+import torch
+
+from gemm_b200.__main__ import main
+from gemm_b200.models import loader
+from gemm_b200.models.config import get_config
+from gemm_b200.models.weights import RandomSource
+
+
+def test_generate_synthetic_cpu(capsys):
+    main(["generate", "--model", "synthetic:tiny-dense", "--device", "cpu", "--ids", "--prompt", "1 2 3 4 5", "--prompt", "9 8 7",
+          "--max-new-tokens", "4", "--pages", "16", "--page-size", "16"])
+    out = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert len(out) == 2 and all(len(o["token_ids"]) == 4 for o in out)
+
+
+def test_inspect_and_stage(tmp_path, capsys):
+    cfg = get_config("tiny-dense")
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, 1, "cpu"), path, wtype="F16")
+    main(["inspect", path, "--tensors"])
+    txt = capsys.readouterr().out
+    assert "general.architecture" in txt and "blk.0.attn_q.weight" in txt
+    out_dir = str(tmp_path / "staged")
+    main(["stage", "--model", path, "--out", out_dir, "--format", "bf16", "--tp", "2"])
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["ranks"] == 2
+    assert os.path.exists(os.path.join(out_dir, "manifest.json"))
