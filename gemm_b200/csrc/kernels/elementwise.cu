@@ -191,10 +191,30 @@ __global__ void __launch_bounds__(256)
 qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
                     const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int n_tok, int hq, int hkv,
-                    int rope_pairs, float theta, float eps, int ld_qkv, float q_scale) {
+                    int rope_pairs, float theta, float eps, int ld_qkv, float q_scale, const float2* __restrict__ rope_tab, int tab_len,
+                    const int* __restrict__ pos3, int sec_h3, int sec_w3) {
   pdl_wait();
   pdl_trigger();
   constexpr int EPL = D / 32;            // elements per lane, index = lane + 32 * i
+  // (cos, sin) of pair j at this token: from the precomputed table [position][pair] when there is one (exact range reduction,
+  // no powf / sincosf in the hot path), else computed.  With M-RoPE (pos3 = [3][n_tok] temporal / height / width positions)
+  // pair j takes the position of section j % 3 while j is inside that section's interleaved range, else the temporal one
+  // (common/transformer.h:1227-1251).
+  auto cos_sin = [&](int tok, int j, float denom, float& c, float& s) {
+    int p = positions[tok];
+    if (pos3 != nullptr) {
+      const int m3 = j % 3;
+      const int which = (m3 == 1 && j < sec_h3) ? 1 : (m3 == 2 && j < sec_w3) ? 2 : 0;
+      p = pos3[(size_t)which * n_tok + tok];
+    }
+    if (rope_tab != nullptr && p >= 0 && p < tab_len) {
+      const float2 cs = rope_tab[(size_t)p * rope_pairs + j];
+      c = cs.x; s = cs.y;
+    } else {
+      const float inv_freq = powf(theta, -2.0f * (float)j / denom);
+      sincosf((float)p * inv_freq, &s, &c);
+    }
+  };
   const int heads = hq + 2 * hkv;
   const long gw = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (gw >= (long)n_tok * heads) return;
@@ -216,15 +236,13 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict
 #pragma unroll
       for (int i = 0; i < EPL; ++i) x[i] = x[i] * sc * __bfloat162float(w[lane + 32 * i]);
     }
-    const float pos = (float)positions[t];
     // pair (j, j + rope_pairs) for j < rope_pairs; with full rotary rope_pairs = D/2 = 32 * EPL/2
     if (2 * rope_pairs == D) {
 #pragma unroll
       for (int i = 0; i < EPL / 2; ++i) {
         const int j = lane + 32 * i;
-        const float inv_freq = powf(theta, -2.0f * (float)j / (float)D);
         float s, c;
-        sincosf(pos * inv_freq, &s, &c);
+        cos_sin(t, j, (float)D, c, s);
         const float a = x[i], b = x[i + EPL / 2];
         x[i] = a * c - b * s;
         x[i + EPL / 2] = a * s + b * c;
@@ -248,9 +266,8 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict
         }
         if (lo || hi) {
           const int j = lo ? idx : idx - rope_pairs;
-          const float inv_freq = powf(theta, -2.0f * (float)j / rd);
           float s, c;
-          sincosf(pos * inv_freq, &s, &c);
+          cos_sin(t, j, rd, c, s);
           x[i] = lo ? (xo[i] * c - partner * s) : (partner * s + xo[i] * c);
         }
       }
@@ -481,13 +498,14 @@ GB_API int gb_rmsnorm_combine(void* residual, const void* y, const int* pair_row
 
 GB_API int gb_qk_norm_rope(const void* qkv, const int* positions, const int* slots, const void* q_w, const void* k_w, void* q_out,
                            void* k_cache, void* v_cache, int n_tok, int hq, int hkv, int head_dim, int rope_pairs, float theta,
-                           float eps, int ld_qkv, float q_scale, cudaStream_t stream) {
+                           float eps, int ld_qkv, float q_scale, const void* rope_tab, int tab_len, const int* pos3, int sec_h3, int sec_w3,
+                           cudaStream_t stream) {
   if (n_tok <= 0) return 0;
   const long warps = (long)n_tok * (hq + 2 * hkv);
   const int blocks = (int)((warps + 7) / 8);
 #define GB_QK(DV) launch_k(qk_norm_rope_kernel<DV>, blocks, 256, 0, stream, (const __nv_bfloat16*)qkv, positions, slots, \
     (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
-    n_tok, hq, hkv, rope_pairs, theta, eps, ld_qkv, q_scale)
+    n_tok, hq, hkv, rope_pairs, theta, eps, ld_qkv, q_scale, (const float2*)rope_tab, tab_len, pos3, sec_h3, sec_w3)
   if (head_dim == 64) GB_QK(64); else if (head_dim == 128) GB_QK(128); else if (head_dim == 256) GB_QK(256);
   else return fail("qk_norm_rope: head_dim must be 64, 128 or 256%s");
 #undef GB_QK

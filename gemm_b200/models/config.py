@@ -64,6 +64,18 @@ class ModelConfig:
     def kv_dim(self) -> int:
         return self.n_kv_heads * self.head_dim
 
+    @property
+    def is_hybrid(self) -> bool:
+        return self.full_attention_interval > 0
+
+    @property
+    def ssm_d_inner(self) -> int:
+        return self.ssm_n_heads_v * self.ssm_head_dim
+
+    @property
+    def ssm_qkv_dim(self) -> int:
+        return 2 * self.ssm_n_heads_k * self.ssm_head_dim + self.ssm_d_inner
+
     def is_ssm_layer(self, layer: int) -> bool:
         if self.full_attention_interval <= 0:
             return False
@@ -102,6 +114,13 @@ PRESETS: Dict[str, ModelConfig] = {
     "tiny-dense": ModelConfig(arch="qwen3", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=512),
     "tiny-moe": ModelConfig(arch="qwen3moe", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=512,
                             n_experts=16, n_experts_used=4, expert_ffn=128),
+    # hybrid: layers 0 and 2 are Delta-Net layers, 1 and 3 gated full attention; the MoE variant adds a shared expert
+    "tiny-qwen35": ModelConfig(arch="qwen35", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=512,
+                               rope_dim=64, full_attention_interval=2, ssm_d_conv=4, ssm_n_heads_k=2, ssm_n_heads_v=4, ssm_head_dim=64,
+                               attn_output_gate=True, mrope_sections=[11, 11, 10, 0]),
+    "tiny-qwen35moe": ModelConfig(arch="qwen35moe", n_layers=4, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=512,
+                                  rope_dim=64, full_attention_interval=2, ssm_d_conv=4, ssm_n_heads_k=2, ssm_n_heads_v=4, ssm_head_dim=64,
+                                  attn_output_gate=True, mrope_sections=[11, 11, 10, 0], n_experts=16, n_experts_used=4, expert_ffn=128, shared_expert_ffn=128),
     "tiny-qwen2": ModelConfig(arch="qwen2", n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=128, ffn=512, vocab=512,
                               qk_norm=False, qkv_bias=True, tie_embeddings=True),
 }

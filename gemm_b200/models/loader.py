@@ -51,9 +51,16 @@ def config_from_gguf(f: G.GGUFFile) -> ModelConfig:
         full_attention_interval=int(key("attention.full_attention_interval", 0) or 0),
         n_deepstack_layers=int(key("n_deepstack_layers", 0) or 0),
     )
+    if cfg.full_attention_interval > 0:            # Qwen3.5 hybrid: the ssm.* family (defaults of common/transformer.h:1699-1704)
+        cfg.ssm_d_conv = int(key("ssm.conv_kernel", 4))
+        cfg.ssm_head_dim = int(key("ssm.state_size", 128))
+        cfg.ssm_n_heads_k = int(key("ssm.group_count", 16))
+        cfg.ssm_n_heads_v = int(key("ssm.time_step_rank", 48))
+        cfg.attn_output_gate = True
     sections = key("rope.dimension_sections")
-    if sections is not None:
+    if sections is not None and sum(int(x) for x in sections) > 0:
         cfg.mrope_sections = [int(x) for x in sections]
+        cfg.rope_dim = 2 * sum(cfg.mrope_sections)
     return cfg
 
 
@@ -117,6 +124,19 @@ def save_gguf(cfg: ModelConfig, src, path: str, wtype: str = "F16", tokens=None,
         w.add_u32(f"{a}.expert_count", cfg.n_experts)
         w.add_u32(f"{a}.expert_used_count", cfg.n_experts_used)
         w.add_u32(f"{a}.expert_feed_forward_length", cfg.expert_ffn)
+    if cfg.is_moe and cfg.shared_expert_ffn:
+        w.add_u32(f"{a}.expert_shared_feed_forward_length", cfg.shared_expert_ffn)
+    if cfg.mrope_sections:
+        w.add_array(f"{a}.rope.dimension_sections", [int(x) for x in cfg.mrope_sections])
+    elif cfg.rope_dim:
+        w.add_u32(f"{a}.rope.dimension_count", cfg.rope_dim)
+    if cfg.is_hybrid:
+        w.add_u32(f"{a}.attention.full_attention_interval", cfg.full_attention_interval)
+        w.add_u32(f"{a}.ssm.conv_kernel", cfg.ssm_d_conv)
+        w.add_u32(f"{a}.ssm.state_size", cfg.ssm_head_dim)
+        w.add_u32(f"{a}.ssm.group_count", cfg.ssm_n_heads_k)
+        w.add_u32(f"{a}.ssm.time_step_rank", cfg.ssm_n_heads_v)
+        w.add_u32(f"{a}.ssm.inner_size", cfg.ssm_d_inner)
     if tokens is None:
         from ..utils.tokenizer import byte_alphabet
         tokens = byte_alphabet() + [f"<extra_{i}>" for i in range(max(0, cfg.vocab - 256))]
@@ -144,22 +164,44 @@ def save_gguf(cfg: ModelConfig, src, path: str, wtype: str = "F16", tokens=None,
     for li in range(cfg.n_layers):
         p = f"blk.{li}."
         vec(p + "attn_norm.weight", (h,))
-        mat(p + "attn_q.weight", (cfg.q_dim, h)); mat(p + "attn_k.weight", (cfg.kv_dim, h)); mat(p + "attn_v.weight", (cfg.kv_dim, h))
+        if cfg.is_ssm_layer(li):
+            qd, di, hv = cfg.ssm_qkv_dim, cfg.ssm_d_inner, cfg.ssm_n_heads_v
+            mat(p + "attn_qkv.weight", (qd, h)); mat(p + "attn_gate.weight", (di, h))
+            mat(p + "ssm_alpha.weight", (hv, h)); mat(p + "ssm_beta.weight", (hv, h)); mat(p + "ssm_out.weight", (h, di))
+            vec(p + "ssm_conv1d.weight", (qd, cfg.ssm_d_conv)); vec(p + "ssm_norm.weight", (cfg.ssm_head_dim,))
+            vec(p + "ssm_a", (hv,)); vec(p + "ssm_dt.bias", (hv,))
+            w.add_tensor(p + "post_attention_norm.weight", src.get(p + "ffn_norm.weight", (h,)).float(), "F32")
+            _save_ffn(cfg, src, w, p, wtype, mat)
+            continue
+        mat(p + "attn_q.weight", ((2 if cfg.attn_output_gate else 1) * cfg.q_dim, h))
+        mat(p + "attn_k.weight", (cfg.kv_dim, h)); mat(p + "attn_v.weight", (cfg.kv_dim, h))
         mat(p + "attn_output.weight", (h, cfg.q_dim))
         if cfg.qkv_bias:
             vec(p + "attn_q.bias", (cfg.q_dim,)); vec(p + "attn_k.bias", (cfg.kv_dim,)); vec(p + "attn_v.bias", (cfg.kv_dim,))
         if cfg.qk_norm:
             vec(p + "attn_q_norm.weight", (d,)); vec(p + "attn_k_norm.weight", (d,))
-        vec(p + "ffn_norm.weight", (h,))
-        if cfg.is_moe:
-            e, inter = cfg.n_experts, cfg.expert_ffn
-            w.add_tensor(p + "ffn_gate_inp.weight", src.get(p + "ffn_gate_inp.weight", (e, h)).float(), "F32")
-            for nm, shp in (("ffn_gate_exps.weight", (inter, h)), ("ffn_up_exps.weight", (inter, h)), ("ffn_down_exps.weight", (h, inter))):
-                full = torch.stack([src.get_expert(p + nm, ei, shp).float() for ei in range(e)])
-                w.add_tensor(p + nm, full, wtype)
+        if cfg.is_hybrid:
+            w.add_tensor(p + "post_attention_norm.weight", src.get(p + "ffn_norm.weight", (h,)).float(), "F32")
         else:
-            mat(p + "ffn_gate.weight", (cfg.ffn, h)); mat(p + "ffn_up.weight", (cfg.ffn, h)); mat(p + "ffn_down.weight", (h, cfg.ffn))
+            vec(p + "ffn_norm.weight", (h,))
+        _save_ffn(cfg, src, w, p, wtype, mat)
     w.write(path)
+
+
+def _save_ffn(cfg, src, w, p, wtype, mat) -> None:
+    h = cfg.hidden
+    if cfg.is_moe:
+        e, inter = cfg.n_experts, cfg.expert_ffn
+        w.add_tensor(p + "ffn_gate_inp.weight", src.get(p + "ffn_gate_inp.weight", (e, h)).float(), "F32")
+        for nm, shp in (("ffn_gate_exps.weight", (inter, h)), ("ffn_up_exps.weight", (inter, h)), ("ffn_down_exps.weight", (h, inter))):
+            full = torch.stack([src.get_expert(p + nm, ei, shp).float() for ei in range(e)])
+            w.add_tensor(p + nm, full, wtype)
+        if cfg.shared_expert_ffn:
+            fs = cfg.shared_expert_ffn
+            mat(p + "ffn_gate_shexp.weight", (fs, h)); mat(p + "ffn_up_shexp.weight", (fs, h)); mat(p + "ffn_down_shexp.weight", (h, fs))
+            w.add_tensor(p + "ffn_gate_inp_shexp.weight", src.get(p + "ffn_gate_inp_shexp.weight", (h,)).float(), "F32")
+    else:
+        mat(p + "ffn_gate.weight", (cfg.ffn, h)); mat(p + "ffn_up.weight", (cfg.ffn, h)); mat(p + "ffn_down.weight", (h, cfg.ffn))
 
 
 # ------------------------------------------------------------------------------------------ safetensors

@@ -34,17 +34,23 @@ def reference_logits(weights: ModelWeights, tokens: torch.Tensor, n_layers: Opti
     layers = weights.layers if n_layers is None else weights.layers[:n_layers]
     for lw in layers:
         h = _rms(x, lw.attn_norm, cfg.rms_eps)
+        if lw.ssm is not None:
+            x = x + _deltanet_layer(cfg, lw.ssm, h)
+            x = x + _ffn(cfg, lw, _rms(x, lw.ffn_norm, cfg.rms_eps))
+            continue
         qkv = h @ lw.wqkv.dequantized().t()
         if lw.wqkv.bias is not None:
             qkv = qkv + lw.wqkv.bias.float()
         q = qkv[:, : hq * d].reshape(s, hq, d)
         k = qkv[:, hq * d:(hq + hkv) * d].reshape(s, hkv, d)
-        v = qkv[:, (hq + hkv) * d:].reshape(s, hkv, d)
+        v = qkv[:, (hq + hkv) * d:(hq + 2 * hkv) * d].reshape(s, hkv, d)
+        gate = qkv[:, (hq + 2 * hkv) * d:] if cfg.attn_output_gate else None
         if lw.q_norm is not None:
             q = _rms(q, lw.q_norm, cfg.rms_eps)
             k = _rms(k, lw.k_norm, cfg.rms_eps)
-        q = rope_ref(q, pos, cfg.rope_theta, cfg.rope_dim)
-        k = rope_ref(k, pos, cfg.rope_theta, cfg.rope_dim)
+        rd = 2 * sum(cfg.mrope_sections) if (cfg.mrope_sections and sum(cfg.mrope_sections) > 0) else cfg.rope_dim
+        q = rope_ref(q, pos, cfg.rope_theta, rd)
+        k = rope_ref(k, pos, cfg.rope_theta, rd)
         k = k.repeat_interleave(g, dim=1)
         v = v.repeat_interleave(g, dim=1)
         sc = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(d)
@@ -53,8 +59,54 @@ def reference_logits(weights: ModelWeights, tokens: torch.Tensor, n_layers: Opti
             mask &= ~torch.ones(s, s, dtype=torch.bool, device=dev).tril(-cfg.sliding_window)
         sc = sc.masked_fill(~mask, float("-inf"))
         a = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v).reshape(s, hq * d)
+        if gate is not None:
+            a = a * torch.sigmoid(gate)
         x = x + a @ lw.wo.dequantized().t()
-        h = _rms(x, lw.ffn_norm, cfg.rms_eps)
+        x = x + _ffn(cfg, lw, _rms(x, lw.ffn_norm, cfg.rms_eps))
+    if return_hidden:
+        return x
+    hn = _rms(x, weights.final_norm, cfg.rms_eps)
+    return hn @ weights.lm_head.dequantized().t()
+
+
+def _deltanet_layer(cfg, ssm, h: torch.Tensor) -> torch.Tensor:
+    """One gated Delta-Net layer over a whole sequence from an all-zero state (common/transformer.h:2861-3113)."""
+    s = h.shape[0]
+    ng, hv, ds, ck = cfg.ssm_n_heads_k, cfg.ssm_n_heads_v, cfg.ssm_head_dim, cfg.ssm_d_conv
+    qd = cfg.ssm_qkv_dim
+    proj = h @ ssm.w_in.dequantized().t()
+    qkv, z = proj[:, :qd], proj[:, qd:]
+    ab = h @ ssm.w_ab.float().t()
+    sp = torch.nn.functional.softplus(ab[:, :hv] + ssm.dt_bias.float(), threshold=20.0)
+    decay = torch.exp(sp * ssm.a.float())                                    # [S, hv]
+    beta = torch.sigmoid(ab[:, hv:])
+    pad = torch.cat([torch.zeros(ck - 1, qd, device=h.device), qkv], 0)      # causal window, zero history
+    conv = sum(pad[f:f + s] * ssm.conv_w.float()[:, f] for f in range(ck))
+    conv = conv * torch.sigmoid(conv)
+    q = conv[:, : ng * ds].reshape(s, ng, ds)
+    k = conv[:, ng * ds: 2 * ng * ds].reshape(s, ng, ds)
+    v = conv[:, 2 * ng * ds:].reshape(s, hv, ds)
+    q = q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + cfg.rms_eps) * ds ** -0.5
+    k = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + cfg.rms_eps)
+    grp = torch.arange(hv, device=h.device) % ng
+    state = torch.zeros(hv, ds, ds, device=h.device)
+    outs = []
+    for t in range(s):
+        qt, kt = q[t, grp], k[t, grp]
+        state = state * decay[t, :, None, None]
+        delta = (v[t] - torch.einsum("hrc,hc->hr", state, kt)) * beta[t, :, None]
+        state = state + delta[:, :, None] * kt[:, None, :]
+        outs.append(torch.einsum("hrc,hc->hr", state, qt))
+    o = torch.stack(outs)                                                    # [S, hv, ds]
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + cfg.rms_eps) * ssm.norm.float()
+    zz = z.reshape(s, hv, ds)
+    return (o * zz * torch.sigmoid(zz)).reshape(s, hv * ds) @ ssm.w_out.dequantized().t()
+
+
+def _ffn(cfg, lw, h: torch.Tensor) -> torch.Tensor:
+    """Dense SwiGLU or top-k MoE (+ sigmoid-gated shared expert) output for normalised input ``h``."""
+    x = h
+    if True:
         if lw.w13 is not None:
             e, kk, inter = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn
             logits = h @ lw.router.float().t()
@@ -79,12 +131,14 @@ def reference_logits(weights: ModelWeights, tokens: torch.Tensor, n_layers: Opti
                 r = h[tok] @ w13[ei].t()
                 act = torch.nn.functional.silu(r[:, :inter]) * r[:, inter:]
                 y.index_add_(0, tok, (act @ w2[ei].t()) * wts[tok, slot].unsqueeze(-1))
-            x = x + y
-        else:
-            f = lw.w_gate_up.n // 2
-            r = h @ lw.w_gate_up.dequantized().t()
-            x = x + (torch.nn.functional.silu(r[:, :f]) * r[:, f:]) @ lw.w_down.dequantized().t()
-    if return_hidden:
-        return x
-    hn = _rms(x, weights.final_norm, cfg.rms_eps)
-    return hn @ weights.lm_head.dequantized().t()
+            if lw.sh_gate_up is not None:
+                fs = lw.sh_gate_up.n // 2
+                r = h @ lw.sh_gate_up.dequantized().t()
+                sh = (torch.nn.functional.silu(r[:, :fs]) * r[:, fs:]) @ lw.sh_down.dequantized().t()
+                if lw.sh_gate is not None:
+                    sh = sh * torch.sigmoid(h @ lw.sh_gate.float().t())
+                y = y + sh
+            return y
+        f = lw.w_gate_up.n // 2
+        r = h @ lw.w_gate_up.dequantized().t()
+        return (torch.nn.functional.silu(r[:, :f]) * r[:, f:]) @ lw.w_down.dequantized().t()

@@ -21,6 +21,7 @@ import torch
 
 from ..ops import attention as att
 from ..ops import elementwise as ew
+from ..ops import deltanet as dn
 from ..ops import gemm, moe, sampling
 from ..ops.mxfp8 import MxTensor
 from .config import ModelConfig
@@ -34,18 +35,43 @@ class KvCache:
     v: List[torch.Tensor]
     page_size: int
     num_pages: int
+    # Delta-Net layers of the hybrid models keep a fixed-size state per sequence slot instead of K/V pages:
+    # conv[l] f32 [slots, conv_k - 1, qkv_dim], rec[l] f32 [slots, heads_v, d, d] (None for attention layers)
+    conv: Optional[List[Optional[torch.Tensor]]] = None
+    rec: Optional[List[Optional[torch.Tensor]]] = None
 
     @staticmethod
     def allocate(cfg: ModelConfig, num_pages: int, page_size: int, device, hkv_local: Optional[int] = None,
-                 n_layers: Optional[int] = None) -> "KvCache":
+                 n_layers: Optional[int] = None, n_seq_slots: int = 64, first_layer: int = 0) -> "KvCache":
         hkv = hkv_local if hkv_local is not None else cfg.n_kv_heads
         nl = n_layers if n_layers is not None else cfg.n_layers
         shape = (num_pages * page_size, hkv, cfg.head_dim)
-        return KvCache([torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(nl)],
-                       [torch.zeros(shape, dtype=torch.bfloat16, device=device) for _ in range(nl)], page_size, num_pages)
+        ssm = [cfg.is_ssm_layer(first_layer + i) for i in range(nl)]
+        none = (0, hkv, cfg.head_dim)
+        kv = KvCache([torch.zeros(none if ssm[i] else shape, dtype=torch.bfloat16, device=device) for i in range(nl)],
+                     [torch.zeros(none if ssm[i] else shape, dtype=torch.bfloat16, device=device) for i in range(nl)], page_size, num_pages)
+        if any(ssm):
+            kv.conv = [torch.zeros(n_seq_slots, cfg.ssm_d_conv - 1, cfg.ssm_qkv_dim, dtype=torch.float32, device=device) if ssm[i] else None
+                       for i in range(nl)]
+            kv.rec = [torch.zeros(n_seq_slots, cfg.ssm_n_heads_v, cfg.ssm_head_dim, cfg.ssm_head_dim, dtype=torch.float32, device=device)
+                      if ssm[i] else None for i in range(nl)]
+        return kv
+
+    def reset_slots(self, slots) -> None:
+        """Zero the recurrent state of the given sequence slots (a new sequence starts from an empty state)."""
+        if self.conv is None:
+            return
+        idx = torch.as_tensor(list(slots), dtype=torch.long, device=self.k[0].device)
+        for c, r in zip(self.conv, self.rec):
+            if c is not None:
+                c[idx] = 0
+                r[idx] = 0
 
     def nbytes(self) -> int:
-        return sum(t.numel() * 2 for t in self.k) * 2
+        tot = sum(t.numel() * 2 for t in self.k) * 2
+        if self.conv is not None:
+            tot += sum(c.numel() * 4 + r.numel() * 4 for c, r in zip(self.conv, self.rec) if c is not None)
+        return tot
 
 
 @dataclass
@@ -61,10 +87,13 @@ class ForwardBatch:
     num_splits: int = 1
     embeds: Optional[torch.Tensor] = None   # bf16 [T, H]: injected embeddings instead of ids (vision tokens)
     n_tokens: int = 0
+    seq_slots: Optional[torch.Tensor] = None   # int32 [B] state slot of every sequence (Delta-Net layers); default 0..B-1
+    positions3: Optional[torch.Tensor] = None  # int32 [3, T] (t, h, w) positions for M-RoPE; default: all three = positions
+    deepstack: Optional[torch.Tensor] = None   # bf16 [n_deepstack, T, H] added to the stream after the first layers (Qwen3-VL)
 
     @staticmethod
     def build(q_lens: Sequence[int], ctx_lens: Sequence[int], ids, block_table: torch.Tensor, page_size: int, hq: int, hkv: int,
-              device, num_splits: int = 1, all_logits: bool = False) -> "ForwardBatch":
+              device, num_splits: int = 1, all_logits: bool = False, seq_slots: Optional[Sequence[int]] = None) -> "ForwardBatch":
         """Host-side assembly from per-sequence chunk lengths and the lengths already cached."""
         b = len(q_lens)
         pos, slots, cu = [], [], [0]
@@ -83,7 +112,8 @@ class ForwardBatch:
                             cu_q=torch.tensor(cu, **i32), kv_len=torch.tensor([c + q for c, q in zip(ctx_lens, q_lens)], **i32),
                             block_table=block_table.to(device=device, dtype=torch.int32),
                             work=att.build_work(q_lens, hq, hkv, num_splits).to(device),
-                            logit_rows=torch.tensor(rows, dtype=torch.int64, device=device), num_splits=num_splits, n_tokens=t)
+                            logit_rows=torch.tensor(rows, dtype=torch.int64, device=device), num_splits=num_splits, n_tokens=t,
+                            seq_slots=torch.tensor(list(seq_slots) if seq_slots is not None else list(range(b)), **i32))
 
 
 class SingleProcess:
@@ -153,6 +183,12 @@ class Transformer:
         self.hkv_local = max(1, cfg.n_kv_heads // weights.tp_size)
         self.q_scale = ew.softmax_scale_log2(cfg.head_dim)
         self.mx = weights.fmt == "mxfp8"
+        rd = cfg.rope_dim or cfg.head_dim
+        if cfg.mrope_sections and sum(cfg.mrope_sections) > 0:
+            rd = 2 * sum(cfg.mrope_sections)           # the rotary width under M-RoPE (common/transformer.h:1229-1232)
+        self.rope_dim = rd
+        self.rope_table = ew.rope_table(min(max(cfg.max_seq_len, 4096), 65536), rd, cfg.rope_theta, weights.embed.device) \
+            if weights.embed.is_cuda else None
         self.snapshots = {}            # layer -> hidden rows captured after that layer (debug / DeepStack)
         self.snapshot_layers: Sequence[int] = ()
 
@@ -161,11 +197,40 @@ class Transformer:
         cfg = self.cfg
         qkv = apply_linear(lw.wqkv, h, h_mx)
         q = ew.qk_norm_rope(qkv, fb.positions, fb.slots, lw.q_norm, lw.k_norm, self.kv.k[li], self.kv.v[li], self.hq_local,
-                            self.hkv_local, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, cfg.rope_dim)
+                            self.hkv_local, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
+                            positions3=fb.positions3, sections=cfg.mrope_sections)
         a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
                           num_splits=fb.num_splits, causal=True, window=cfg.sliding_window)
         a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
+        if cfg.attn_output_gate:
+            g0 = (self.hq_local + 2 * self.hkv_local) * cfg.head_dim
+            dn.gate_mul(a2, qkv[:, g0: g0 + self.hq_local * cfg.head_dim])
         return self.par.row_linear(lw.wo, a2)
+
+    def ssm_block(self, li: int, lw, h: torch.Tensor, h_mx: Optional[MxTensor], fb: ForwardBatch) -> torch.Tensor:
+        """Gated Delta-Net layer: projections -> causal conv + SiLU -> recurrence + gated norm -> output projection."""
+        cfg, ssm = self.cfg, lw.ssm
+        qd = cfg.ssm_qkv_dim
+        proj = apply_linear(ssm.w_in, h, h_mx)                        # [T, qkv_dim + d_inner]
+        ab = moe.router_logits(h, ssm.w_ab)                           # f32 [T, 2 * heads_v]
+        slots = fb.seq_slots if fb.seq_slots is not None else torch.arange(fb.cu_q.numel() - 1, dtype=torch.int32, device=h.device)
+        conv = dn.conv_silu(proj[:, :qd], ssm.conv_w, self.kv.conv[li], fb.cu_q, slots)
+        out = dn.deltanet(conv, proj[:, qd:], ab, ssm.a, ssm.dt_bias, ssm.norm, self.kv.rec[li], fb.cu_q, slots, cfg.ssm_n_heads_k,
+                          cfg.ssm_n_heads_v, cfg.ssm_head_dim, cfg.rms_eps)
+        return self.par.row_linear(ssm.w_out, out)
+
+    def shared_expert(self, lw, h: torch.Tensor) -> torch.Tensor:
+        """Always-on expert of the qwen35moe layers, scaled by sigmoid(h . g) (cuda/llm/cuda_llm_runner.c:11879-11897)."""
+        if lw.sh_gate_up.fmt == "bf16":
+            act = gemm.linear_swiglu(h, lw.sh_gate_up.w, w_tiled=lw.sh_gate_up.tiled)
+            y = apply_linear(lw.sh_down, act)
+        else:
+            xm = ew.mx_quantize(h, sf_layout=32 if h.shape[0] <= 32 else 128)
+            y = apply_linear(lw.sh_down, None, gemm.linear_mx_swiglu_quant(xm, lw.sh_gate_up.mx))
+        if lw.sh_gate is not None:
+            g = torch.sigmoid(moe.router_logits(h, lw.sh_gate) if h.is_cuda and h.shape[1] % 256 == 0 else h.float() @ lw.sh_gate.float().t())
+            y = (y.float() * g).to(torch.bfloat16)
+        return y
 
     def dense_ffn(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor]) -> torch.Tensor:
         if lw.w_gate_up.fmt == "bf16":
@@ -214,12 +279,13 @@ class Transformer:
             lw = w.layers[li]
             lay = 32 if x.shape[0] <= 32 else 128
             par = self.par
+            is_ssm = lw.ssm is not None
             if self.mx:
                 h, h_mx = par.add_norm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps, x if delta is not None else None,
-                                       quantize=True, want_bf16=False, sf_layout=lay)
+                                       quantize=True, want_bf16=is_ssm, sf_layout=lay)
             else:
                 h, h_mx = par.add_norm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps, x if delta is not None else None), None
-            delta = self.attention_block(li, lw, h, h_mx, fb)
+            delta = self.ssm_block(li, lw, h, h_mx, fb) if is_ssm else self.attention_block(li, lw, h, h_mx, fb)
             need_bf16 = (not self.mx) or cfg.is_moe
             if self.mx:
                 h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, quantize=True, want_bf16=need_bf16, sf_layout=lay)
@@ -229,8 +295,13 @@ class Transformer:
                 delta = self.par.moe_ffn(self, lw, h)
                 if delta is None:
                     delta = self.moe_local(lw, h)
+                if lw.sh_gate_up is not None:
+                    delta = (self.par.materialize(delta).float() + self.shared_expert(lw, h).float()).to(torch.bfloat16)
             else:
                 delta = self.dense_ffn(lw, h, h_mx)
+            if fb.deepstack is not None and li < fb.deepstack.shape[0]:
+                # DeepStack (Qwen3-VL): vision features of deeper encoder layers join the stream after the first decoder layers
+                delta = (self.par.materialize(delta).float() + fb.deepstack[li].float()).to(torch.bfloat16)
             if li in self.snapshot_layers:
                 self.snapshots[li] = (x.float() + self.par.materialize(delta).float())
         # the last delta stays pending: the head (or the next pipeline stage) folds it into the stream

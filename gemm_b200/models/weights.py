@@ -98,10 +98,26 @@ def make_linear(w_f: torch.Tensor, fmt: str, bias: Optional[torch.Tensor] = None
 
 
 @dataclass
+class SsmWeights:
+    """A Delta-Net layer (GGUF names: attn_qkv, attn_gate, ssm_alpha, ssm_beta, ssm_conv1d, ssm_a, ssm_dt.bias, ssm_norm, ssm_out)."""
+    w_in: LinearWeight            # rows [qkv (Q | K | V channels) ; z (d_inner)]
+    w_ab: torch.Tensor            # bf16 [2 * n_heads_v, H]: alpha rows then beta rows
+    conv_w: torch.Tensor          # f32 [qkv_dim, conv_k]
+    a: torch.Tensor               # f32 [n_heads_v]
+    dt_bias: torch.Tensor         # f32 [n_heads_v]
+    norm: torch.Tensor            # f32 [head_dim]
+    w_out: LinearWeight           # [H, d_inner]
+
+    def to(self, device) -> "SsmWeights":
+        return SsmWeights(self.w_in.to(device), self.w_ab.to(device), self.conv_w.to(device), self.a.to(device), self.dt_bias.to(device),
+                          self.norm.to(device), self.w_out.to(device))
+
+
+@dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
-    wqkv: LinearWeight
-    wo: LinearWeight
+    wqkv: Optional[LinearWeight]                  # rows [Q ; K ; V] (+ [gate] after V when the attention output is gated); None in SSM layers
+    wo: Optional[LinearWeight]
     ffn_norm: torch.Tensor
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
@@ -111,6 +127,10 @@ class LayerWeights:
     router_bias: Optional[torch.Tensor] = None    # f32 [E] (sigmoid router)
     w13: Optional[LinearWeight] = None            # experts, rows per expert [gate ; up] = 2I
     w2: Optional[LinearWeight] = None             # experts, rows per expert = H, K = I
+    ssm: Optional[SsmWeights] = None              # Delta-Net layer (then wqkv / wo are None)
+    sh_gate_up: Optional[LinearWeight] = None     # shared expert [gate ; up]
+    sh_down: Optional[LinearWeight] = None
+    sh_gate: Optional[torch.Tensor] = None        # bf16 [1, H]: sigmoid gate of the shared expert (absent = ungated)
 
 
 @dataclass
@@ -132,7 +152,8 @@ class ModelWeights:
             return x.to(device) if x is not None else None
         layers = [LayerWeights(attn_norm=mv(l.attn_norm), wqkv=mv(l.wqkv), wo=mv(l.wo), ffn_norm=mv(l.ffn_norm), q_norm=mv(l.q_norm),
                                k_norm=mv(l.k_norm), w_gate_up=mv(l.w_gate_up), w_down=mv(l.w_down), router=mv(l.router),
-                               router_bias=mv(l.router_bias), w13=mv(l.w13), w2=mv(l.w2)) for l in self.layers]
+                               router_bias=mv(l.router_bias), w13=mv(l.w13), w2=mv(l.w2), ssm=mv(l.ssm), sh_gate_up=mv(l.sh_gate_up),
+                               sh_down=mv(l.sh_down), sh_gate=mv(l.sh_gate)) for l in self.layers]
         return ModelWeights(cfg=self.cfg, embed=mv(self.embed), layers=layers, final_norm=mv(self.final_norm), lm_head=mv(self.lm_head),
                             fmt=self.fmt, tp_rank=self.tp_rank, tp_size=self.tp_size, ep_rank=self.ep_rank, ep_size=self.ep_size,
                             vocab_start=self.vocab_start)
@@ -141,7 +162,7 @@ class ModelWeights:
         """Put every projection matrix into the tiled weight layout (in place).  An LM head that shares its storage with
         the embedding table (tied embeddings) stays row-major: the embedding lookup reads rows."""
         for l in self.layers:
-            for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.w13, l.w2):
+            for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.w13, l.w2, l.sh_gate_up, l.sh_down) + ((l.ssm.w_in, l.ssm.w_out) if l.ssm else ()):
                 if lw is not None:
                     lw.tile_()
         if self.lm_head.w is not None and self.lm_head.w.data_ptr() != self.embed.data_ptr():
@@ -151,7 +172,7 @@ class ModelWeights:
     def nbytes(self) -> int:
         tot = self.embed.numel() * 2 + self.lm_head.nbytes()
         for l in self.layers:
-            for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.w13, l.w2):
+            for lw in (l.wqkv, l.wo, l.w_gate_up, l.w_down, l.w13, l.w2, l.sh_gate_up, l.sh_down) + ((l.ssm.w_in, l.ssm.w_out) if l.ssm else ()):
                 if lw is not None:
                     tot += lw.nbytes()
         return tot
@@ -182,12 +203,62 @@ class RandomSource:
     def get(self, name: str, shape) -> torch.Tensor:
         if name.endswith("norm.weight"):
             return torch.ones(tuple(shape), dtype=torch.bfloat16, device=self.device)
+        if name.endswith("ssm_a"):                       # fixed decay constants are negative
+            return -(self._randn(name, shape).float().abs() * 20 + 0.5).to(torch.bfloat16)
+        if name.endswith("ssm_conv1d.weight") or name.endswith("ssm_alpha.weight") or name.endswith("ssm_beta.weight"):
+            return (self._randn(name, shape).float() * 10).to(torch.bfloat16)
         if name.endswith(".bias"):
             return self._randn(name, shape)
         return self._randn(name, shape)
 
     def get_expert(self, name: str, e: int, shape) -> torch.Tensor:
         return self._randn(f"{name}#{e}", shape)
+
+
+def _post_attn_norm_name(src, pre: str) -> str:
+    """The norm before the FFN: ``ffn_norm`` (Qwen2/3) or ``post_attention_norm`` (Qwen3.5 GGUFs)."""
+    if hasattr(src, "has") and not isinstance(src, RandomSource) and not src.has(pre + "ffn_norm.weight") and src.has(pre + "post_attention_norm.weight"):
+        return "post_attention_norm.weight"
+    return "ffn_norm.weight"
+
+
+def _build_ffn(cfg, src, pre, lw, fmt, mv, dev, tp_rank, tp_size, ep_rank, ep_size) -> None:
+    """Dense FFN or MoE (+ optional shared expert) of one layer into ``lw``."""
+    h = cfg.hidden
+    if cfg.is_moe:
+        e, inter = cfg.n_experts, cfg.expert_ffn
+        assert e % ep_size == 0
+        e_l = e // ep_size
+        lw.router = mv(src.get(pre + "ffn_gate_inp.weight", (e, h)).to(torch.bfloat16))
+        if cfg.router == "sigmoid":
+            lw.router_bias = torch.zeros(e, dtype=torch.float32, device=dev)
+        w13 = torch.empty((e_l * 2 * inter, h), dtype=torch.bfloat16, device=dev)
+        w2 = torch.empty((e_l * h, inter), dtype=torch.bfloat16, device=dev)
+        for j in range(e_l):
+            ge = ep_rank * e_l + j
+            w13[j * 2 * inter: j * 2 * inter + inter] = mv(src.get_expert(pre + "ffn_gate_exps.weight", ge, (inter, h)))
+            w13[j * 2 * inter + inter:(j + 1) * 2 * inter] = mv(src.get_expert(pre + "ffn_up_exps.weight", ge, (inter, h)))
+            w2[j * h:(j + 1) * h] = mv(src.get_expert(pre + "ffn_down_exps.weight", ge, (h, inter)))
+        lw.w13 = make_linear(w13, fmt, groups=e_l)
+        lw.w2 = make_linear(w2, fmt, groups=e_l)
+        del w13, w2
+    else:
+        f = cfg.ffn
+        assert f % tp_size == 0
+        f_l = f // tp_size
+        f0, f1 = tp_rank * f_l, (tp_rank + 1) * f_l
+        wg = src.get(pre + "ffn_gate.weight", (f, h))[f0:f1]
+        wu = src.get(pre + "ffn_up.weight", (f, h))[f0:f1]
+        wd = src.get(pre + "ffn_down.weight", (h, f))[:, f0:f1]
+        lw.w_gate_up = make_linear(mv(torch.cat([wg, wu])), fmt)
+        lw.w_down = make_linear(mv(wd.contiguous()), fmt)
+        del wg, wu, wd
+    if cfg.is_moe and cfg.shared_expert_ffn > 0:
+        fs = cfg.shared_expert_ffn
+        lw.sh_gate_up = make_linear(mv(torch.cat([src.get(pre + "ffn_gate_shexp.weight", (fs, h)), src.get(pre + "ffn_up_shexp.weight", (fs, h))])), fmt)
+        lw.sh_down = make_linear(mv(src.get(pre + "ffn_down_shexp.weight", (h, fs)).contiguous()), fmt)
+        if not hasattr(src, "has") or src.has(pre + "ffn_gate_inp_shexp.weight"):
+            lw.sh_gate = mv(src.get(pre + "ffn_gate_inp_shexp.weight", (h,)).to(torch.bfloat16).reshape(1, h).contiguous())
 
 
 def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0,
@@ -222,7 +293,31 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
     lo, hi = layer_range if layer_range is not None else (0, nl)       # pipeline stages keep a contiguous slice of layers
     for li in range(lo, hi):
         pre = f"blk.{li}."
-        wq = src.get(pre + "attn_q.weight", (cfg.q_dim, h))[q0:q1]
+        if cfg.is_ssm_layer(li):
+            assert tp_size == 1, "Delta-Net layers are not tensor-parallel (the reference replicates them, test_transformer_parallel.c:351-364)"
+            qd, di, hv = cfg.ssm_qkv_dim, cfg.ssm_d_inner, cfg.ssm_n_heads_v
+            w_in = torch.cat([src.get(pre + "attn_qkv.weight", (qd, h)), src.get(pre + "attn_gate.weight", (di, h))])
+            ssm = SsmWeights(
+                w_in=make_linear(mv(w_in), fmt),
+                w_ab=mv(torch.cat([src.get(pre + "ssm_alpha.weight", (hv, h)), src.get(pre + "ssm_beta.weight", (hv, h))]).to(torch.bfloat16).contiguous()),
+                conv_w=mv(src.get(pre + "ssm_conv1d.weight", (qd, cfg.ssm_d_conv)).float().contiguous()),
+                a=mv(src.get(pre + "ssm_a", (hv,)).float().contiguous()), dt_bias=mv(src.get(pre + "ssm_dt.bias", (hv,)).float().contiguous()),
+                norm=mv(src.get(pre + "ssm_norm.weight", (cfg.ssm_head_dim,)).float().contiguous()),
+                w_out=make_linear(mv(src.get(pre + "ssm_out.weight", (h, di)).contiguous()), fmt))
+            del w_in
+            lw = LayerWeights(attn_norm=mv(src.get(pre + "attn_norm.weight", (h,)).to(torch.bfloat16)), wqkv=None, wo=None,
+                              ffn_norm=mv(src.get(pre + _post_attn_norm_name(src, pre), (h,)).to(torch.bfloat16)), ssm=ssm)
+            _build_ffn(cfg, src, pre, lw, fmt, mv, dev, tp_rank, tp_size, ep_rank, ep_size)
+            layers.append(lw)
+            continue
+        if cfg.attn_output_gate:
+            # attn_q emits [Q_h | gate_h] per head (common/transformer.h:3857-3868): de-interleave, the gate rows go after V
+            wqg = src.get(pre + "attn_q.weight", (2 * cfg.q_dim, h)).reshape(cfg.n_heads, 2, d, h)
+            wq = wqg[:, 0].reshape(cfg.q_dim, h)[q0:q1]
+            wgate = wqg[:, 1].reshape(cfg.q_dim, h)[q0:q1]
+        else:
+            wq = src.get(pre + "attn_q.weight", (cfg.q_dim, h))[q0:q1]
+            wgate = None
         wk = src.get(pre + "attn_k.weight", (cfg.kv_dim, h))[k0:k1]
         wv = src.get(pre + "attn_v.weight", (cfg.kv_dim, h))[k0:k1]
         wo = src.get(pre + "attn_output.weight", (h, cfg.q_dim))[:, q0:q1]
@@ -233,41 +328,14 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
             bias = mv(bias)
         lw = LayerWeights(
             attn_norm=mv(src.get(pre + "attn_norm.weight", (h,)).to(torch.bfloat16)),
-            wqkv=make_linear(mv(torch.cat([wq, wk, wv])), fmt, bias=bias),
+            wqkv=make_linear(mv(torch.cat([wq, wk, wv] + ([wgate] if wgate is not None else []))), fmt, bias=bias),
             wo=make_linear(mv(wo.contiguous()), fmt),
-            ffn_norm=mv(src.get(pre + "ffn_norm.weight", (h,)).to(torch.bfloat16)),
+            ffn_norm=mv(src.get(pre + _post_attn_norm_name(src, pre), (h,)).to(torch.bfloat16)),
             q_norm=mv(src.get(pre + "attn_q_norm.weight", (d,)).to(torch.bfloat16)) if cfg.qk_norm else None,
             k_norm=mv(src.get(pre + "attn_k_norm.weight", (d,)).to(torch.bfloat16)) if cfg.qk_norm else None,
         )
         del wq, wk, wv, wo
-        if cfg.is_moe:
-            e, inter = cfg.n_experts, cfg.expert_ffn
-            assert e % ep_size == 0
-            e_l = e // ep_size
-            lw.router = mv(src.get(pre + "ffn_gate_inp.weight", (e, h)).to(torch.bfloat16))
-            if cfg.router == "sigmoid":
-                lw.router_bias = torch.zeros(e, dtype=torch.float32, device=dev)
-            w13 = torch.empty((e_l * 2 * inter, h), dtype=torch.bfloat16, device=dev)
-            w2 = torch.empty((e_l * h, inter), dtype=torch.bfloat16, device=dev)
-            for j in range(e_l):
-                ge = ep_rank * e_l + j
-                w13[j * 2 * inter: j * 2 * inter + inter] = mv(src.get_expert(pre + "ffn_gate_exps.weight", ge, (inter, h)))
-                w13[j * 2 * inter + inter:(j + 1) * 2 * inter] = mv(src.get_expert(pre + "ffn_up_exps.weight", ge, (inter, h)))
-                w2[j * h:(j + 1) * h] = mv(src.get_expert(pre + "ffn_down_exps.weight", ge, (h, inter)))
-            lw.w13 = make_linear(w13, fmt, groups=e_l)
-            lw.w2 = make_linear(w2, fmt, groups=e_l)
-            del w13, w2
-        else:
-            f = cfg.ffn
-            assert f % tp_size == 0
-            f_l = f // tp_size
-            f0, f1 = tp_rank * f_l, (tp_rank + 1) * f_l
-            wg = src.get(pre + "ffn_gate.weight", (f, h))[f0:f1]
-            wu = src.get(pre + "ffn_up.weight", (f, h))[f0:f1]
-            wd = src.get(pre + "ffn_down.weight", (h, f))[:, f0:f1]
-            lw.w_gate_up = make_linear(mv(torch.cat([wg, wu])), fmt)
-            lw.w_down = make_linear(mv(wd.contiguous()), fmt)
-            del wg, wu, wd
+        _build_ffn(cfg, src, pre, lw, fmt, mv, dev, tp_rank, tp_size, ep_rank, ep_size)
         layers.append(lw)
     embed = mv(src.get("token_embd.weight", (cfg.vocab, h)).to(torch.bfloat16))
     if cfg.tie_embeddings or not src.has("output.weight"):

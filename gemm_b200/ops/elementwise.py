@@ -120,30 +120,70 @@ def rope_ref(x: torch.Tensor, positions: torch.Tensor, theta: float, rope_dim: O
     return xf
 
 
-def qk_norm_rope_ref(qkv, positions, q_w, k_w, hq, hkv, d, theta, eps, q_scale, rope_dim=None):
+def rope_table(max_pos: int, rope_dim: int, theta: float, device) -> torch.Tensor:
+    """(cos, sin) of every (position, rotary pair): f32 ``[max_pos, rope_dim / 2, 2]``, computed in float64."""
+    j = torch.arange(rope_dim // 2, dtype=torch.float64)
+    inv = theta ** (-2.0 * j / rope_dim)
+    ang = torch.arange(max_pos, dtype=torch.float64).unsqueeze(-1) * inv
+    return torch.stack([ang.cos(), ang.sin()], -1).to(torch.float32).to(device).contiguous()
+
+
+def mrope_positions(positions3: torch.Tensor, sections, pairs: int) -> torch.Tensor:
+    """Position used by every rotary pair under M-RoPE: ``[T, pairs]`` from ``positions3 [3, T]`` (t, h, w) and the
+    section sizes: pair j belongs to section j % 3 while j < 3 * size of that section, otherwise to the temporal one."""
+    j = torch.arange(pairs, device=positions3.device)
+    which = torch.zeros(pairs, dtype=torch.long, device=positions3.device)
+    which[(j % 3 == 1) & (j < 3 * sections[1])] = 1
+    which[(j % 3 == 2) & (j < 3 * sections[2])] = 2
+    return positions3.long().t()[:, which]                     # [T, pairs]
+
+
+def _rope_pairs_ref(x: torch.Tensor, pos_pairs: torch.Tensor, theta: float, rope_dim: int) -> torch.Tensor:
+    """NeoX rotation with an own position per (token, pair)."""
+    half = rope_dim // 2
+    j = torch.arange(half, dtype=torch.float32, device=x.device)
+    ang = pos_pairs.to(torch.float32) * theta ** (-2.0 * j / rope_dim)
+    cos, sin = ang.cos().unsqueeze(1), ang.sin().unsqueeze(1)
+    xf = x.float().clone()
+    a, b = xf[..., :half].clone(), xf[..., half:rope_dim].clone()
+    xf[..., :half] = a * cos - b * sin
+    xf[..., half:rope_dim] = a * sin + b * cos
+    return xf
+
+
+def qk_norm_rope_ref(qkv, positions, q_w, k_w, hq, hkv, d, theta, eps, q_scale, rope_dim=None, positions3=None, sections=None):
     t = qkv.shape[0]
     q = qkv[:, : hq * d].float().reshape(t, hq, d)
     k = qkv[:, hq * d:(hq + hkv) * d].float().reshape(t, hkv, d)
-    v = qkv[:, (hq + hkv) * d:].reshape(t, hkv, d)
+    v = qkv[:, (hq + hkv) * d:(hq + 2 * hkv) * d].reshape(t, hkv, d)
     if q_w is not None:
         q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_w.float()
     if k_w is not None:
         k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_w.float()
-    q = rope_ref(q, positions, theta, rope_dim) * q_scale
-    k = rope_ref(k, positions, theta, rope_dim)
+    if positions3 is not None and sections:
+        rd = rope_dim or d
+        pp = mrope_positions(positions3, sections, rd // 2)
+        q = _rope_pairs_ref(q, pp, theta, rd) * q_scale
+        k = _rope_pairs_ref(k, pp, theta, rd)
+    else:
+        q = rope_ref(q, positions, theta, rope_dim) * q_scale
+        k = rope_ref(k, positions, theta, rope_dim)
     return q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
 
 
 def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, q_w, k_w, k_cache: torch.Tensor,
                  v_cache: torch.Tensor, hq: int, hkv: int, d: int, theta: float, eps: float, q_scale: float,
-                 rope_dim: Optional[int] = None) -> torch.Tensor:
+                 rope_dim: Optional[int] = None, table: Optional[torch.Tensor] = None, positions3: Optional[torch.Tensor] = None,
+                 sections=None) -> torch.Tensor:
     """Per-head RMSNorm (optional) + RoPE on the fused QKV rows; K / V go to cache slot ``slots[t]``.
 
     ``k_cache`` / ``v_cache`` are ``[num_slots, Hkv, D]``.  Returns ``q [T, Hq, D]`` multiplied by ``q_scale``.
+    ``table`` (from ``rope_table``) replaces the in-kernel powf / sincosf; ``positions3`` int32 ``[3, T]`` + ``sections`` select
+    M-RoPE.
     """
     t = qkv.shape[0]
     if not qkv.is_cuda:
-        q, k, v = qk_norm_rope_ref(qkv, positions, q_w, k_w, hq, hkv, d, theta, eps, q_scale, rope_dim)
+        q, k, v = qk_norm_rope_ref(qkv, positions, q_w, k_w, hq, hkv, d, theta, eps, q_scale, rope_dim, positions3, sections)
         ok = slots >= 0
         k_cache[slots[ok].long()] = k[ok]
         v_cache[slots[ok].long()] = v[ok]
@@ -152,7 +192,9 @@ def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor
     pairs = (rope_dim or d) // 2
     rc = _native.cuda().gb_qk_norm_rope(_p(qkv), _p(positions), _p(slots), _p(q_w), _p(k_w), _p(q_out), _p(k_cache),
                                         _p(v_cache), _i(t), _i(hq), _i(hkv), _i(d), _i(pairs), _f(theta), _f(eps),
-                                        _i(qkv.stride(0)), _f(q_scale), _s())
+                                        _i(qkv.stride(0)), _f(q_scale), _p(table), _i(table.shape[0] if table is not None else 0),
+                                        _p(positions3 if (positions3 is not None and sections) else None),
+                                        _i(3 * sections[1] if sections else 0), _i(3 * sections[2] if sections else 0), _s())
     _native.check(rc, "gb_qk_norm_rope")
     return q_out
 

@@ -59,7 +59,8 @@ class Engine:
         self.max_pages_per_seq = (max_seq_len + page_size - 1) // page_size
         n_pages = num_pages if num_pages is not None else max_batch * self.max_pages_per_seq
         hkv_local = max(1, self.cfg.n_kv_heads // weights.tp_size)
-        self.kv = KvCache.allocate(self.cfg, n_pages, page_size, self.device, hkv_local, n_layers=len(weights.layers))
+        # one recurrent-state slot per sequence plus a scratch slot (hybrid models; used by the warm-up run before graph capture)
+        self.kv = KvCache.allocate(self.cfg, n_pages, page_size, self.device, hkv_local, n_layers=len(weights.layers), n_seq_slots=max_batch + 1)
         self.pages = PageAllocator(n_pages)
         self.model = Transformer(weights, self.kv, par)
         self.par = self.model.par
@@ -100,6 +101,9 @@ class Engine:
         """Batched, chunked prefill of new sequences (token id tensors, host or device).  Returns the logits of
         the last prompt token of every sequence, ``f32 [B, V_local]``.  ``reserve`` extra positions are paged in."""
         base = len(self.seq_pages)
+        if base + len(prompts) > self.max_batch:
+            raise ValueError(f"{base + len(prompts)} sequences exceed max_batch = {self.max_batch}")
+        self.kv.reset_slots(range(base, base + len(prompts)))
         for pr in prompts:
             self.seq_pages.append([])
             self.seq_len.append(0)
@@ -120,7 +124,7 @@ class Engine:
                 ids.append(prompts[i][done[i]:done[i] + take])
                 room -= take
             fb = ForwardBatch.build(q_lens, ctx, torch.cat([x.to(self.device) for x in ids]), self._block_table([base + i for i in seqs]),
-                                    self.page_size, self.hq_local, self.hkv_local, self.device)
+                                    self.page_size, self.hq_local, self.hkv_local, self.device, seq_slots=[base + i for i in seqs])
             logits = self.model.forward(fb)
             for j, i in enumerate(seqs):
                 done[i] += q_lens[j]
@@ -161,6 +165,7 @@ class Engine:
         st["work"] = att.build_work([1] * b, self.hq_local, self.hkv_local, splits).to(self.device)
         st["rows"] = torch.arange(b, dtype=torch.int64, device=self.device)
         st["tokens"] = torch.zeros(b, dtype=torch.int32, device=self.device)
+        st["seq_slots"] = torch.arange(b, dtype=torch.int32, device=self.device)
         self._splits = splits
         self._graph = None
         self.step_count = 0
@@ -171,6 +176,7 @@ class Engine:
             side.wait_stream(torch.cuda.current_stream())
             from .. import _native
             n0 = _native.launch_count()
+            st["seq_slots"].fill_(self.max_batch)          # the warm-up run must not advance any sequence's recurrent state
             with torch.cuda.stream(side):
                 self._decode_body()
             self.kernels_per_step = _native.launch_count() - n0
@@ -178,6 +184,7 @@ class Engine:
             torch.cuda.synchronize()
             for k, v in saved.items():
                 st[k].copy_(v)
+            st["seq_slots"].copy_(torch.arange(b, dtype=torch.int32, device=self.device))
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
                 self._decode_body()
@@ -189,7 +196,7 @@ class Engine:
         st = self._static
         fb = ForwardBatch(ids=st["ids"], positions=st["positions"], slots=st["slots"], cu_q=st["cu_q"], kv_len=st["kv_len"],
                           block_table=st["block_table"], work=st["work"], logit_rows=st["rows"], num_splits=self._splits,
-                          n_tokens=st["ids"].numel())
+                          n_tokens=st["ids"].numel(), seq_slots=st["seq_slots"])
         if self._sp.temperature <= 0 and not hasattr(self.par, "merge_sampled"):
             tok = self.model.forward_greedy(fb)
         else:

@@ -42,7 +42,9 @@ class LLM:
         self.device = weights.embed.device
         self.page_size = page_size
         hkv_local = max(1, self.cfg.n_kv_heads // weights.tp_size)
-        self.kv = KvCache.allocate(self.cfg, num_pages, page_size, self.device, hkv_local, n_layers=len(weights.layers))
+        self.kv = KvCache.allocate(self.cfg, num_pages, page_size, self.device, hkv_local, n_layers=len(weights.layers), n_seq_slots=max_running)
+        self._free_slots = list(range(max_running))       # recurrent-state slots of the hybrid models, one per running request
+        self._slot_of: Dict[int, int] = {}
         self.blocks = KvBlockManager(num_pages, page_size)
         self.sched = Scheduler(self.blocks, max_running, max_batch_tokens)
         self.model = Transformer(weights, self.kv, par)
@@ -94,7 +96,11 @@ class LLM:
             q_lens.append(it.q_len)
             ctx.append(it.ctx_len)
             ids.extend(r.tokens[it.ctx_len: it.ctx_len + it.q_len])
-        fb = ForwardBatch.build(q_lens, ctx, ids, bt, self.page_size, self.model.hq_local, self.model.hkv_local, self.device)
+            if it.req_id not in self._slot_of:              # first chunk of this request: take a state slot and clear it
+                self._slot_of[it.req_id] = self._free_slots.pop()
+                self.kv.reset_slots([self._slot_of[it.req_id]])
+        fb = ForwardBatch.build(q_lens, ctx, ids, bt, self.page_size, self.model.hq_local, self.model.hkv_local, self.device,
+                                seq_slots=[self._slot_of[it.req_id] for it in plan])
         logits = self.model.forward(fb)                     # one row per plan item (its last token)
         produced: Dict[int, int] = {}
         finished = []
@@ -110,6 +116,8 @@ class LLM:
                 fin = tok in sp.stop_token_ids or len(r.out) >= sp.max_new_tokens
                 r.done = fin
             finished.append(fin)
+            if fin and it.req_id in self._slot_of:
+                self._free_slots.append(self._slot_of.pop(it.req_id))
         self.sched.commit(finished)
         self.steps += 1
         return produced

@@ -14,7 +14,7 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("name,fmt", [("tiny-dense", "bf16"), ("tiny-moe", "bf16"), ("tiny-qwen2", "bf16"), ("tiny-moe", "mxfp8"),
-                                      ("tiny-dense", "mxfp8")])
+                                      ("tiny-dense", "mxfp8"), ("tiny-qwen35", "bf16"), ("tiny-qwen35moe", "bf16"), ("tiny-qwen35", "mxfp8")])
 def test_prefill_then_decode_matches_oracle(name, fmt):
     torch.manual_seed(0)
     cfg = get_config(name)
@@ -34,6 +34,10 @@ def test_prefill_then_decode_matches_oracle(name, fmt):
         outs = model.forward(fb)
         ctx = [c + q for c, q in zip(ctx, chunk)]
     tol = 3e-2 if fmt == "bf16" else 0.2      # e4m3 activations: ~4% noise per GEMM operand
+    if "qwen35" in name and fmt == "bf16":
+        # four layers; in the MoE variant a bf16-sized perturbation can flip a near-tied expert choice (random router weights),
+        # which moves single logits rows by ~10 %: every component alone agrees with the oracle to 0.3 %
+        tol = 0.15 if "moe" in name else 6e-2
     for s in range(2):
         ref = reference.reference_logits(w, toks[s][: lens[s]])[-1]
         assert _rel(outs[s], ref) < tol

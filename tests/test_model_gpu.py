@@ -32,7 +32,7 @@ def _run(model, cfg, toks, lens, bt, page, device, chunks, decode_steps):
 
 
 @pytest.mark.parametrize("name,fmt", [("tiny-dense", "bf16"), ("tiny-moe", "bf16"), ("tiny-qwen2", "bf16"), ("tiny-dense", "mxfp8"),
-                                      ("tiny-moe", "mxfp8")])
+                                      ("tiny-moe", "mxfp8"), ("tiny-qwen35", "bf16"), ("tiny-qwen35moe", "bf16"), ("tiny-qwen35", "mxfp8")])
 def test_gpu_engine_matches_cpu_engine_and_oracle(name, fmt):
     torch.manual_seed(0)
     cfg = get_config(name)
@@ -56,6 +56,8 @@ def test_gpu_engine_matches_cpu_engine_and_oracle(name, fmt):
     o_gpu = _run(m_gpu, cfg, toks, lens, bt, page, "cuda", chunks, 3)
     _native.assert_status_ok()
     tol = 2e-2 if fmt == "bf16" else 6e-2
+    if "qwen35" in name:
+        tol = 0.15 if "moe" in name else (4e-2 if fmt == "bf16" else 0.1)     # 4 layers; near-tied expert choices can flip (CPU test)
     for a, b in zip(o_gpu, o_cpu):
         assert _rel(a, b) < tol
     # oracle on the last prefill chunk (logits of the last token of sequences 0 and 2)
