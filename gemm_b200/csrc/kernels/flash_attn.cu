@@ -39,8 +39,8 @@ struct FaArgs {
   int num_splits;
   int causal;
   int window;               // sliding window (0 = off): position p attends to (p - window, p]
-  __nv_bfloat16* out;       // [T, Hq, D]                 (num_splits == 1)
-  float* part_o;            // [splits, T, Hq, D] f32     (num_splits > 1)
+  __nv_bfloat16* out;       // [T, Hq, D]                 (used when part_o is null)
+  float* part_o;            // [splits, T, Hq, D] f32     (num_splits > 1, or 1 split whose partial a caller merges itself)
   float* part_lse;          // [splits, T, Hq] base-2 log-sum-exp
   int total_tokens;
   KernelStatus* status;
@@ -270,7 +270,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
         if (row_valid) {
-          if (a.num_splits == 1) {
+          if (a.part_o == nullptr) {
             uint4* dst = reinterpret_cast<uint4*>(a.out + ((size_t)tok * a.hq + head) * kD + c * 32);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -290,7 +290,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           }
         }
       }
-      if (row_valid && a.num_splits > 1)
+      if (row_valid && a.part_o != nullptr)
         a.part_lse[((size_t)split * a.total_tokens + tok) * a.hq + head] = (l > 0.f) ? (m + log2f(l)) : -INFINITY;
     }
   }
@@ -350,6 +350,9 @@ GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache
   if (G > 128) return fail("flash_attn: group size > 128%s");
   if (page_size < 8 || page_size > 128 || (128 % page_size) || (page_size % 8)) return fail("flash_attn: page_size must be 8..128, a multiple of 8 dividing 128%s");
   if (n_work <= 0) return 0;
+  if (num_splits > 1 && part_o == nullptr) return fail("flash_attn: num_splits > 1 needs partial buffers%s");
+  if (part_o == nullptr && out == nullptr) return fail("flash_attn: no output buffer%s");
+  if (part_o != nullptr && part_lse == nullptr) return fail("flash_attn: partial output needs part_lse%s");
   const int tpt = 128 / G;
   CUtensorMap tmQ, tmK, tmV;
   {

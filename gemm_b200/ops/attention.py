@@ -76,6 +76,53 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_
     return out
 
 
+def attention_partial(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                      block_table: torch.Tensor, page_size: int, work: torch.Tensor, num_splits: int = 1, causal: bool = False,
+                      window: int = 0):
+    """Flash partials of the attention over THIS cache only: ``(part_o f32 [S, T, Hq, D]`` normalised by its own sum,
+    ``part_lse f32 [S, T, Hq]`` base 2; -inf where a row saw no key).  The caller merges them with partials of other KV
+    shards (``combine_partials``): the building block of context parallelism."""
+    t, hq, d = q.shape
+    if not q.is_cuda:
+        return _attention_partial_ref(q, k_cache, v_cache, cu_q, kv_len, block_table, page_size, causal, window)
+    part_o = torch.empty(num_splits, t, hq, d, dtype=torch.float32, device=q.device)
+    part_lse = torch.empty(num_splits, t, hq, dtype=torch.float32, device=q.device)
+    rc = _native.cuda().gb_flash_attn(_p(q), _p(k_cache), _p(v_cache), _c(0), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
+                                      _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
+                                      _l(k_cache.shape[0]), _i(t), _i(hq), _i(k_cache.shape[1]), _i(d), _i(num_splits), _i(1 if causal else 0),
+                                      _i(window), _c(_native.status_ptr()), _c(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "gb_flash_attn")
+    return part_o, part_lse
+
+
+def _attention_partial_ref(q, k_cache, v_cache, cu_q, kv_len, block_table, page_size, causal, window):
+    """CPU reference of ``attention_partial`` (one split).  ``q`` carries softmax_scale * log2(e), scores are base 2."""
+    t, hq, d = q.shape
+    hkv = k_cache.shape[1]
+    g = hq // hkv
+    out = torch.zeros(1, t, hq, d, dtype=torch.float32)
+    lse = torch.full((1, t, hq), float("-inf"), dtype=torch.float32)
+    cu = cu_q.tolist()
+    for s in range(len(cu) - 1):
+        q0, q1 = cu[s], cu[s + 1]
+        ql, kl = q1 - q0, int(kv_len[s])
+        if ql == 0 or kl == 0:
+            continue
+        n_pages = (kl + page_size - 1) // page_size
+        idx = (block_table[s, :n_pages].long().unsqueeze(1) * page_size + torch.arange(page_size)).reshape(-1)[:kl]
+        k = k_cache[idx].float().repeat_interleave(g, dim=1)
+        v = v_cache[idx].float().repeat_interleave(g, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", q[q0:q1].float(), k)
+        if causal:
+            qpos = torch.arange(kl - ql, kl).unsqueeze(1)
+            sc = sc.masked_fill(~(torch.arange(kl).unsqueeze(0) <= qpos), float("-inf"))
+        l2 = torch.logsumexp(sc * math.log(2.0), dim=-1) / math.log(2.0)
+        p = torch.exp2(sc - l2.unsqueeze(-1))
+        out[0, q0:q1] = torch.einsum("hqk,khd->qhd", p, v)
+        lse[0, q0:q1] = l2.t()
+    return out, lse
+
+
 def combine_partials(part_o: torch.Tensor, part_lse: torch.Tensor):
     """Merge flash partials ``part_o [S, R, D]`` (each normalised by its own sum) and base-2 ``part_lse [S, R]``.
     Returns ``(out bf16 [R, D], lse f32 [R])``.  Also the rule for context parallelism (KV sharded over GPUs)."""

@@ -47,6 +47,10 @@ def main():
     rank, world = dist.get_rank(), dist.get_world_size()
     what = sys.argv[1]
     g = torch.Generator().manual_seed(3)
+    if what == "cp":
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from cp_check import check_context_parallel
+        check_context_parallel(rank, world, "cpu", False)
     if what == "groups":
         lay = ParallelLayout(tp=2, pp=2, dp=world // 4)
         grp = init_parallel(lay)

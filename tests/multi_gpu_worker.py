@@ -161,6 +161,10 @@ def main():
     if what in ("all", "ep"):
         for fmt, fused, gather in (("bf16", True, True), ("mxfp8", True, True), ("bf16", True, False), ("mxfp8", True, False), ("mxfp8", False, True)):
             check_expert_parallel(rank, world, dev, fmt, fused, gather)
+    if what in ("all", "cp"):
+        from cp_check import check_context_parallel
+        for fused in (True, False):
+            check_context_parallel(rank, world, dev, fused)
     if what in ("all", "tp"):
         for fmt, fused in (("bf16", True), ("mxfp8", True), ("bf16", False)):
             check_tensor_parallel(rank, world, dev, fmt, fused)

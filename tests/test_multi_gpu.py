@@ -41,3 +41,8 @@ def test_expert_parallel_matches_single_gpu():
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_tensor_parallel_matches_single_gpu():
     _launch("tp", 2, 29613)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_context_parallel_decode_attention():
+    _launch("cp", min(_ngpu(), 4), 29614)
