@@ -302,9 +302,40 @@ def hf_name(gguf_name: str, expert: Optional[int] = None) -> str:
     return f"model.layers.{li}.{_HF_MAP[base]}.{kind}"
 
 
+E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def mxfp4_dequant(packed: torch.Tensor, scale_e8m0: torch.Tensor) -> torch.Tensor:
+    """MXFP4: ``packed`` uint8 [rows, cols / 2] (two e2m1 codes per byte, low nibble = even column), one E8M0 scale per 32
+    columns ``[rows, cols / 32]`` -> f32 [rows, cols].  The expert format of DeepSeek-V4-Flash (common/ds4f.h:1-34)."""
+    rows, half = packed.shape
+    lut = torch.tensor(E2M1_VALUES + tuple(-v for v in E2M1_VALUES), dtype=torch.float32, device=packed.device)
+    codes = torch.stack([packed & 0xF, packed >> 4], dim=-1).reshape(rows, half * 2).long()
+    scale = (scale_e8m0.to(torch.int32) << 23).view(torch.float32)
+    return (lut[codes].reshape(rows, half * 2 // 32, 32) * scale.unsqueeze(-1)).reshape(rows, half * 2)
+
+
+def mxfp4_quant(w: torch.Tensor):
+    """Inverse of ``mxfp4_dequant`` (round to nearest e2m1 after scaling each 32-block so that its maximum is <= 6)."""
+    rows, cols = w.shape
+    blk = w.float().reshape(rows, cols // 32, 32)
+    amax = blk.abs().amax(-1)
+    e = torch.where(amax > 0, torch.ceil(torch.log2(amax / 6.0)), torch.zeros_like(amax)).clamp(-126, 127)
+    scaled = blk / torch.exp2(e).unsqueeze(-1)
+    grid = torch.tensor(E2M1_VALUES, dtype=torch.float32)
+    mag = (scaled.abs().unsqueeze(-1) - grid).abs().argmin(-1)
+    codes = (mag | ((scaled < 0).long() << 3)).reshape(rows, cols).to(torch.uint8)
+    return (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous(), (e + 127).to(torch.uint8)
+
+
 class SafetensorsSource:
-    """Tensor source over a directory of HF safetensors shards (or one file).  MXFP8 checkpoints (``F8_E4M3`` weights with a
-    ``<name>_scale_inv`` E8M0 tensor of shape [rows, cols/32]) are dequantised exactly: e4m3 * 2^(s-127)."""
+    """Tensor source over a directory of HF safetensors shards (or one file).  Quantised checkpoints are dequantised exactly:
+
+    * MXFP8: ``F8_E4M3`` weight + ``<name>_scale_inv`` E8M0 (uint8) [rows, cols / 32]            -> e4m3 * 2^(s - 127)
+    * FP8 with 128 x 128 block scales: ``F8_E4M3`` weight + ``<name>_scale_inv`` F32 / BF16 [rows / 128, cols / 128]
+      (the dense format of GLM-5 and DeepSeek-V4-Flash: common/glm5_impl.h:399-471, common/ds4f.h:1-34)
+    * MXFP4: ``U8`` weight [rows, cols / 2] + ``<name>_scale`` E8M0 [rows, cols / 32] (DeepSeek-V4-Flash experts)
+    """
 
     def __init__(self, path: str):
         files = [path] if os.path.isfile(path) else sorted(os.path.join(path, x) for x in os.listdir(path) if x.endswith(".safetensors"))
@@ -317,9 +348,14 @@ class SafetensorsSource:
         t = self.where[name].get(name)
         if t.dtype == torch.float8_e4m3fn:
             s = self.where[name + "_scale_inv"].get(name + "_scale_inv")
-            scale = (s.to(torch.int32) << 23).view(torch.float32)
             rows, cols = t.shape
-            return (t.to(torch.float32).reshape(rows, cols // 32, 32) * scale.unsqueeze(-1)).reshape(rows, cols)
+            if s.dtype == torch.uint8:                                  # MXFP8: E8M0 per 1 x 32
+                scale = (s.to(torch.int32) << 23).view(torch.float32)
+                return (t.to(torch.float32).reshape(rows, cols // 32, 32) * scale.unsqueeze(-1)).reshape(rows, cols)
+            sc = s.to(torch.float32).repeat_interleave(128, 0)[:rows].repeat_interleave(128, 1)[:, :cols]   # f32 per 128 x 128
+            return t.to(torch.float32) * sc
+        if t.dtype == torch.uint8 and (name + "_scale") in self.where:  # MXFP4
+            return mxfp4_dequant(t, self.where[name + "_scale"].get(name + "_scale"))
         return t.to(torch.float32)
 
     def has(self, name: str) -> bool:

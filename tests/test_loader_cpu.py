@@ -94,3 +94,25 @@ def test_engine_matches_reference_cpu_engine(tmp_path, name, wtype):
     ours = model.forward(fb)
     assert _rel(ours[-1], ref_logits[-1]) < 3e-2
     assert int(ours[-1].argmax()) == int(ref_logits[-1].argmax()) or _rel(ours[-1], ref_logits[-1]) < 1e-2
+
+
+def test_fp8_block_scaled_and_mxfp4_checkpoints(tmp_path):
+    """Dense FP8 weights with 128 x 128 f32 block scales (GLM-5 / DeepSeek-V4-Flash layout) and MXFP4 weights are read back as
+    the values they encode."""
+    torch.manual_seed(9)
+    w = torch.randn(256, 384) * 0.05
+    sc = w.reshape(2, 128, 3, 128).abs().amax(dim=(1, 3)) / 448.0
+    q = (w / sc.repeat_interleave(128, 0).repeat_interleave(128, 1)).to(torch.float8_e4m3fn)
+    w4 = torch.randn(64, 128) * 0.3
+    p4, s4 = loader.mxfp4_quant(w4)
+    path = str(tmp_path / "q.safetensors")
+    loader.save_safetensors({"model.embed_tokens.weight": q, "model.embed_tokens.weight_scale_inv": sc.float(),
+                             "model.norm.weight": p4, "model.norm.weight_scale": s4}, path)
+    src = loader.SafetensorsSource(path)
+    got = src.get("token_embd.weight", (256, 384))
+    assert torch.equal(got, q.float() * sc.repeat_interleave(128, 0).repeat_interleave(128, 1))
+    assert _rel(got, w) < 0.05
+    got4 = src._raw("model.norm.weight")
+    assert got4.shape == (64, 128) and _rel(got4, w4) < 0.15
+    again = loader.mxfp4_dequant(*loader.mxfp4_quant(got4))      # representable values survive another encode / decode
+    assert torch.equal(again, got4)
