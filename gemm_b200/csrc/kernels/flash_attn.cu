@@ -304,6 +304,290 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Decode-specialised flash kernel: one new token per sequence, so a GQA group has only G (<= 16) query rows.  Here the KV
+// POSITIONS are the MMA M dimension and the query heads the N dimension (the same trick as the GEMM's "weights are M"):
+//   S^T[128 pos x 16 heads] = K_j[128 x 128] Q^T          (A = K tile, K-major;  B = Q, 16 rows, K-major)
+//   O^T[128 d   x 16 heads] += V_j^T[128 d x 128 pos] P_j  (A = V tile, MN-major; B = P^T written to smem as [head][pos])
+// A softmax thread owns one KV position (S^T) or one output feature (O^T) and touches 16 values per block instead of the
+// 128 of the prefill layout, where the 8 live rows of a decode tile sat in one warp that did all the exponentials.  Max and
+// sum over the 128 positions of a block are warp shuffles plus a 4-entry shared-memory exchange.  Shared memory per CTA is
+// about 107 KB (K and V tiles alternate through one ring of three 32 KB slots), so two CTAs share an SM: with 64 sequences x 4 KV heads all 256 work
+// items are resident at once and there is no second, partly filled wave.
+constexpr int kFdN = 16;                 // MMA N: query heads of one KV head, zero padded
+constexpr int kFdThreads = 192;
+constexpr int kFdSmem = 4096 + 3 * 32768 + 8192 + 2048 + 1024;   // Q, tile ring, P x2, barriers + reductions, alignment
+
+// Reduce 16 per-lane values over the 32 lanes of a warp with 16 shuffles (a reduce-scatter: 8 + 4 + 2 + 1 exchanges, then one
+// more between neighbours): lane L returns the result for index L >> 1.
+#define GB_RS_STEP(IN, OUT, N, BIT, OP)                                                       \
+  _Pragma("unroll") for (int i = 0; i < N; ++i) {                                            \
+    const bool up = (lane & BIT) != 0;                                                       \
+    const float send = up ? IN[i] : IN[N + i], keep = up ? IN[N + i] : IN[i];                 \
+    OUT[i] = OP(keep, __shfl_xor_sync(0xffffffffu, send, BIT));                               \
+  }
+__device__ __forceinline__ float rs_max(float a, float b) { return fmaxf(a, b); }
+__device__ __forceinline__ float rs_add(float a, float b) { return a + b; }
+__device__ __forceinline__ float warp_reduce16_max(const float* v, int lane) {
+  float a[8], b[4], c[2], d[1];
+  GB_RS_STEP(v, a, 8, 16, rs_max) GB_RS_STEP(a, b, 4, 8, rs_max) GB_RS_STEP(b, c, 2, 4, rs_max) GB_RS_STEP(c, d, 1, 2, rs_max)
+  return fmaxf(d[0], __shfl_xor_sync(0xffffffffu, d[0], 1));
+}
+__device__ __forceinline__ float warp_reduce16_sum(const float* v, int lane) {
+  float a[8], b[4], c[2], d[1];
+  GB_RS_STEP(v, a, 8, 16, rs_add) GB_RS_STEP(a, b, 4, 8, rs_add) GB_RS_STEP(b, c, 2, 4, rs_add) GB_RS_STEP(c, d, 1, 2, rs_add)
+  return d[0] + __shfl_xor_sync(0xffffffffu, d[0], 1);
+}
+
+// Barrier over the 128 softmax threads (named barrier 1) that also ANDs a predicate: every thread learns whether all of them
+// got through their bounded wait, so they leave the loop together and nobody is left standing at a barrier.
+__device__ __forceinline__ bool softmax_bar_and(bool pred) {
+  uint32_t r;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(r) : "r"((uint32_t)pred) : "memory");
+  return r != 0;
+}
+
+__global__ void __launch_bounds__(kFdThreads, 2)
+flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const FaArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;                          // 2 d-halves x [16 heads x 128 B]
+  uint8_t* ring = smem + 4096;                 // 3 slots x 32 KB; tile t = 2j is K of block j, t = 2j + 1 is V of block j, slot = t % 3
+  uint8_t* sP = ring + 3 * 32768;              // 2 buffers x 2 position-halves x [16 heads x 128 B] (bf16, 128B swizzle)
+  uint64_t* bars = (uint64_t*)(sP + 8192);
+  uint64_t* q_full = bars;                     // 1
+  uint64_t* t_full = bars + 1;                 // 3
+  uint64_t* t_empty = bars + 4;                // 3
+  uint64_t* s_full = bars + 7;                 // 2
+  uint64_t* p_ready = bars + 9;                // 1 (128 arrivals)
+  uint64_t* o_ready = bars + 10;               // 2: block j commits to o_ready[j & 1]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  float* red_max = (float*)(bars + 16);        // [2 (block parity)][4 warps][16 heads]
+  float* red_sum = red_max + 2 * 4 * kFdN;     // [2][4][16]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
+    mbar_init(p_ready, 128); mbar_init(&o_ready[0], 1); mbar_init(&o_ready[1], 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+  }
+  // rows of Q beyond the group size are never loaded: keep them finite (their columns of S and O are never stored)
+  for (int i = threadIdx.x; i < 4096 / 16; i += kFdThreads) reinterpret_cast<uint4*>(sQ)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  if (warp == 1) { tmem_alloc(tmem_slot, 64); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 2 * kFdN;
+  pdl_wait();
+  pdl_trigger();
+
+  const int G = a.hq / a.hkv;
+  const int* wk = a.work + (size_t)blockIdx.x * 4;
+  const int seq = wk[0], kvh = wk[1], split = wk[3];
+  const int tok = a.cu_q[seq];
+  const int kv_len = a.kv_len[seq];
+  const int qpos = kv_len - 1;
+  int first_pos = 0;
+  if (a.window > 0) first_pos = max(0, qpos - a.window + 1);
+  int blk_lo = first_pos / kBN, blk_hi = (kv_len > 0) ? (kv_len - 1) / kBN + 1 : 0;
+  if (a.num_splits > 1) {
+    const int nb = blk_hi - blk_lo, per = (nb + a.num_splits - 1) / a.num_splits;
+    blk_lo = blk_lo + split * per;
+    blk_hi = min(blk_hi, blk_lo + per);
+  }
+  int n_blk = max(0, blk_hi - blk_lo);
+  const bool bad_item = kvh < 0 || kvh >= a.hkv || G > kFdN || (a.cu_q[seq + 1] - tok) != 1;
+  if (bad_item) {
+    if (threadIdx.x == 0) report_status(a.status, ST_BAD_ARG, 650, kvh, a.hkv, G);
+    n_blk = 0;
+  }
+
+  if (warp == 0) {
+    if (lane == 0 && n_blk > 0) {
+      mbar_expect_tx(q_full, (uint32_t)(2 * 128 * G));
+      tma_load_3d(sQ, &tmQ, q_full, 0, kvh * G, tok);
+      tma_load_3d(sQ + 2048, &tmQ, q_full, 64, kvh * G, tok);
+      const int ppb = kBN / a.page_size;
+      const uint32_t page_bytes = (uint32_t)a.page_size * 128;
+      const int* bt = a.block_table + (size_t)seq * a.max_pages;
+      const int last_page = (kv_len + a.page_size - 1) / a.page_size - 1;
+      bool ok = true;
+      for (int t = 0; t < 2 * n_blk && ok; ++t) {
+        const int slot = t % 3; const uint32_t ph = (uint32_t)(t / 3) & 1;
+        const int blk = blk_lo + (t >> 1);
+        const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
+        if (!mbar_wait(&t_empty[slot], ph ^ 1, abort_flag, a.status, 410, t)) { ok = false; break; }
+        mbar_expect_tx(&t_full[slot], 32768u);
+        for (int p = 0; p < ppb; ++p) {
+          const int page = bt[min(blk * ppb + p, last_page)];
+          uint8_t* dst = ring + slot * 32768 + p * page_bytes;
+          tma_load_3d(dst, tm, &t_full[slot], 0, kvh, page * a.page_size);
+          tma_load_3d(dst + 16384, tm, &t_full[slot], 64, kvh, page * a.page_size);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n_blk > 0) {
+      constexpr uint32_t idesc_s = make_idesc(128, kFdN, 1, 1, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc(128, kFdN, 1, 1, 1, 0);      // A (= V^T) is MN-major
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status, 510);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const int t = 2 * j, slot = t % 3; const uint32_t ph = (uint32_t)(t / 3) & 1;
+        if (!mbar_wait(&t_full[slot], ph, abort_flag, a.status, 511, j)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(ring + slot * 32768);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_f16_ss(tmem_base + s * kFdN, make_sdesc_sw128(k_addr + (ks >> 2) * 16384 + (ks & 3) * 32),
+                     make_sdesc_sw128(q_addr + (ks >> 2) * 2048 + (ks & 3) * 32), idesc_s, ks > 0 ? 1u : 0u);
+        tc_commit(&s_full[s]);
+        tc_commit(&t_empty[slot]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_blk && ok; ++j) {
+        if (j + 1 < n_blk) { if (!issue_s(j + 1)) { ok = false; break; } }
+        const int tv = 2 * j + 1, vslot = tv % 3;
+        if (!mbar_wait(p_ready, j & 1, abort_flag, a.status, 512, j)) { ok = false; break; }
+        if (!mbar_wait(&t_full[vslot], (uint32_t)(tv / 3) & 1, abort_flag, a.status, 513, j)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(ring + vslot * 32768);
+        const uint32_t pj = p_addr + (j & 1) * 4096;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_f16_ss(tmem_o, make_sdesc_sw128_mn(v_addr + ks * 2048, 16384), make_sdesc_sw128(pj + (ks >> 2) * 2048 + (ks & 3) * 32),
+                     idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(&o_ready[j & 1]);
+        tc_commit(&t_empty[vslot]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax: thread r = KV position r of the block / feature r of O
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    float m[kFdN], l[kFdN];          // m: the reference maximum the exponentials are taken against (may lag the true maximum by <= kTau)
+#pragma unroll
+    for (int h = 0; h < kFdN; ++h) { m[h] = -INFINITY; l[h] = 0.f; }
+    constexpr float kTau = 8.0f;     // O and l are only rescaled when a block raises a maximum by more than 2^kTau
+    bool ok = true;
+    for (int j = 0; j < n_blk && ok; ++j) {
+      const int s = j & 1;
+      const bool got_s = mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, a.status, 610, j);
+      tc_fence_after();
+      float sv[kFdN];
+      tmem_ld_x16(tmem_base + s * kFdN + lane_off, reinterpret_cast<uint32_t*>(sv));
+      tc_wait_ld();
+      const int kp = (blk_lo + j) * kBN + r;
+      const bool live = kp <= qpos && kp >= first_pos;
+      float* rm = red_max + (j & 1) * 4 * kFdN;
+      float* rs = red_sum + (j & 1) * 4 * kFdN;
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) if (!live || h >= G) sv[h] = -INFINITY;
+      {
+        const float v = warp_reduce16_max(sv, lane);            // lane L ends with head L >> 1
+        if ((lane & 1) == 0) rm[q * kFdN + (lane >> 1)] = v;
+      }
+      if (!softmax_bar_and(got_s)) { ok = false; break; }          // maxima of all four warps are in rm
+      float bm[kFdN];
+      bool need = false;
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) {
+        bm[h] = fmaxf(fmaxf(rm[h], rm[kFdN + h]), fmaxf(rm[2 * kFdN + h], rm[3 * kFdN + h]));
+        need |= (h < G) && (bm[h] > m[h] + kTau);                  // also true for the first finite maximum (m = -inf)
+      }
+      float alpha[kFdN], pv[kFdN];
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) {
+        const float m_new = need ? fmaxf(m[h], bm[h]) : m[h];
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[h] = need ? fast_exp2(m[h] - m_use) : 1.0f;
+        m[h] = m_new;
+        pv[h] = fast_exp2(sv[h] - m_use);
+      }
+      {
+        const float v = warp_reduce16_sum(pv, lane);
+        if ((lane & 1) == 0) rs[q * kFdN + (lane >> 1)] = v;
+      }
+      bool got_o = true;
+      if (j >= 2) {
+        // the P buffer of this parity was read by the second MMA of block j - 2
+        got_o = mbar_wait(&o_ready[s], (uint32_t)((j - 2) >> 1) & 1, abort_flag, a.status, 611, j);
+      }
+      if (got_o && need && j > 0) {
+        // rare: a maximum moved by more than 2^kTau.  All earlier P V products must have landed in O before it is rescaled.
+        got_o = mbar_wait(&o_ready[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1, abort_flag, a.status, 613, j);
+        tc_fence_after();
+        if (got_o) {
+          uint32_t o[kFdN];
+          tmem_ld_x16(tmem_o + lane_off, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int h = 0; h < kFdN; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * alpha[h]);
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                       :: "r"(tmem_o + lane_off), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
+                          "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+          tc_wait_st();
+        }
+      }
+      if (got_o) {
+        // P^T into shared memory as [head][position] bf16, the K-major B operand of the second MMA (128-byte swizzle)
+        uint8_t* pb = sP + s * 4096;
+        const int half = r >> 6, chunk = (r & 63) >> 3;
+#pragma unroll
+        for (int h = 0; h < kFdN; ++h)
+          *reinterpret_cast<__nv_bfloat16*>(pb + half * 2048 + h * 128 + ((chunk ^ (h & 7)) << 4) + (r & 7) * 2) = __float2bfloat16(pv[h]);
+        fence_proxy_async_smem();                // P in shared memory -> visible to the tensor core's reads
+        tc_fence_before();
+        mbar_arrive(p_ready);
+      }
+      if (!softmax_bar_and(got_o)) { ok = false; break; }          // also: the sums of all four warps are in rs
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) l[h] = l[h] * alpha[h] + (rs[h] + rs[kFdN + h] + rs[2 * kFdN + h] + rs[3 * kFdN + h]);
+    }
+    if (ok && n_blk > 0) ok = mbar_wait(&o_ready[(n_blk - 1) & 1], (uint32_t)((n_blk - 1) >> 1) & 1, abort_flag, a.status, 612);
+    if (ok && !bad_item) {
+      tc_fence_after();
+      uint32_t o[kFdN];
+      if (n_blk > 0) { tmem_ld_x16(tmem_o + lane_off, o); tc_wait_ld(); }
+      else {
+#pragma unroll
+        for (int h = 0; h < kFdN; ++h) o[h] = 0u;
+      }
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) {
+        if (h >= G) continue;
+        const float inv_l = (l[h] > 0.f) ? 1.0f / l[h] : 0.f;
+        const int head = kvh * G + h;
+        const float val = __uint_as_float(o[h]) * inv_l;
+        if (a.part_o == nullptr) a.out[((size_t)tok * a.hq + head) * kD + r] = __float2bfloat16(val);
+        else a.part_o[(((size_t)split * a.total_tokens + tok) * a.hq + head) * kD + r] = val;
+        if (a.part_o != nullptr && r == 0)
+          a.part_lse[((size_t)split * a.total_tokens + tok) * a.hq + head] = (l[h] > 0.f) ? (m[h] + log2f(l[h])) : -INFINITY;
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 64); }
+}
+
 // Merge of split-KV partials: out = sum_s 2^(lse_s - lse_max) O_s / sum_s 2^(lse_s - lse_max).
 // One warp per (token, head); D = 128 -> 4 floats per lane.
 __global__ void fa_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, __nv_bfloat16* __restrict__ out,
@@ -380,6 +664,48 @@ GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache
     attr_set = true;
   }
   launch_k(flash_attn_kernel, n_work, kFaThreads, smem, stream, tmQ, tmK, tmV, a);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Decode form of gb_flash_attn: every sequence contributes exactly one query token (cu_q = 0, 1, 2, ...), Hq / Hkv <= 16.
+// Same arguments and outputs; work items are {seq, kv_head, 0, split}.
+GB_API int gb_flash_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
+                           const int* work, int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages,
+                           int page_size, long num_slots, int total_tokens, int hq, int hkv, int head_dim, int num_splits, int window,
+                           void* status, cudaStream_t stream) {
+  if (head_dim != 128) return fail("flash_decode: head_dim must be 128%s");
+  if (hq % hkv || hq / hkv > kFdN) return fail("flash_decode: needs Hq %% Hkv == 0 and a group of at most 16 heads%s");
+  if (page_size < 8 || page_size > 128 || (128 % page_size) || (page_size % 8)) return fail("flash_decode: page_size must be 8..128, a multiple of 8 dividing 128%s");
+  if (n_work <= 0) return 0;
+  if (num_splits > 1 && part_o == nullptr) return fail("flash_decode: num_splits > 1 needs partial buffers%s");
+  if (part_o == nullptr && out == nullptr) return fail("flash_decode: no output buffer%s");
+  const int G = hq / hkv;
+  CUtensorMap tmQ, tmK, tmV;
+  {
+    uint64_t dims[3] = {128, (uint64_t)hq, (uint64_t)total_tokens};
+    uint64_t strides[2] = {256, (uint64_t)hq * 256};
+    uint32_t box[3] = {64, (uint32_t)G, 1};
+    if (make_tmap(&tmQ, q, TM_BF16, 3, dims, strides, box, TM_SW_128)) return -1;
+  }
+  {
+    uint64_t dims[3] = {128, (uint64_t)hkv, (uint64_t)num_slots};
+    uint64_t strides[2] = {256, (uint64_t)hkv * 256};
+    uint32_t box[3] = {64, 1, (uint32_t)page_size};
+    if (make_tmap(&tmK, k_cache, TM_BF16, 3, dims, strides, box, TM_SW_128)) return -1;
+    if (make_tmap(&tmV, v_cache, TM_BF16, 3, dims, strides, box, TM_SW_128)) return -1;
+  }
+  FaArgs a;
+  memset(&a, 0, sizeof(a));
+  a.work = work; a.cu_q = cu_q; a.kv_len = kv_len; a.block_table = block_table; a.max_pages = max_pages; a.page_size = page_size;
+  a.hq = hq; a.hkv = hkv; a.num_splits = num_splits; a.causal = 1; a.window = window; a.out = (__nv_bfloat16*)out;
+  a.part_o = part_o; a.part_lse = part_lse; a.total_tokens = total_tokens; a.status = (KernelStatus*)status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    GB_CUDA_OK(cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmem));
+    attr_set = true;
+  }
+  launch_k(flash_decode_kernel, n_work, kFdThreads, kFdSmem, stream, tmQ, tmK, tmV, a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -89,6 +89,7 @@ class ForwardBatch:
     n_tokens: int = 0
     seq_slots: Optional[torch.Tensor] = None   # int32 [B] state slot of every sequence (Delta-Net layers); default 0..B-1
     positions3: Optional[torch.Tensor] = None  # int32 [3, T] (t, h, w) positions for M-RoPE; default: all three = positions
+    is_decode: bool = False                    # every sequence contributes exactly one token (selects the decode attention kernel)
     deepstack: Optional[torch.Tensor] = None   # bf16 [n_deepstack, T, H] added to the stream after the first layers (Qwen3-VL)
 
     @staticmethod
@@ -113,7 +114,8 @@ class ForwardBatch:
                             block_table=block_table.to(device=device, dtype=torch.int32),
                             work=att.build_work(q_lens, hq, hkv, num_splits).to(device),
                             logit_rows=torch.tensor(rows, dtype=torch.int64, device=device), num_splits=num_splits, n_tokens=t,
-                            seq_slots=torch.tensor(list(seq_slots) if seq_slots is not None else list(range(b)), **i32))
+                            seq_slots=torch.tensor(list(seq_slots) if seq_slots is not None else list(range(b)), **i32),
+                            is_decode=(b > 0 and all(q == 1 for q in q_lens)))
 
 
 class SingleProcess:
@@ -200,7 +202,7 @@ class Transformer:
                             self.hkv_local, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
                             positions3=fb.positions3, sections=cfg.mrope_sections)
         a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
-                          num_splits=fb.num_splits, causal=True, window=cfg.sliding_window)
+                          num_splits=fb.num_splits, causal=True, window=cfg.sliding_window, decode=fb.is_decode)
         a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
         if cfg.attn_output_gate:
             g0 = (self.hq_local + 2 * self.hkv_local) * cfg.head_dim

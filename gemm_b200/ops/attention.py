@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import List, Optional, Sequence
 
 import torch
@@ -21,6 +22,9 @@ _c, _i, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
 
 def _p(t):
     return _c(t.data_ptr()) if t is not None else _c(0)
+
+
+USE_DECODE_KERNEL = os.environ.get("GB_DECODE_ATTN", "1") != "0"      # 0: decode steps use the general kernel (A/B measurements)
 
 
 def build_work(q_lens: Sequence[int], hq: int, hkv: int, num_splits: int = 1) -> torch.Tensor:
@@ -48,8 +52,9 @@ def pick_splits(n_seqs: int, hkv: int, max_kv: int, sm_count: int = 148) -> int:
 
 def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
               block_table: torch.Tensor, page_size: int, work: torch.Tensor, num_splits: int = 1, causal: bool = True,
-              window: int = 0, out: Optional[torch.Tensor] = None, scratch=None) -> torch.Tensor:
-    """Attention output ``[T, Hq, D]`` (bf16).  ``work`` comes from ``build_work`` (moved to the device)."""
+              window: int = 0, out: Optional[torch.Tensor] = None, scratch=None, decode: bool = False) -> torch.Tensor:
+    """Attention output ``[T, Hq, D]`` (bf16).  ``work`` comes from ``build_work`` (moved to the device).  ``decode`` (every
+    sequence has exactly one query token, at most 16 query heads per KV head) selects the decode-specialised kernel."""
     t, hq, d = q.shape
     hkv = k_cache.shape[1]
     if not q.is_cuda:
@@ -65,11 +70,18 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_
             part_o = torch.empty(num_splits, t, hq, d, dtype=torch.float32, device=q.device)
             part_lse = torch.empty(num_splits, t, hq, dtype=torch.float32, device=q.device)
     stream = _c(torch.cuda.current_stream().cuda_stream)
-    rc = lib.gb_flash_attn(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
-                           _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
-                           _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(num_splits), _i(1 if causal else 0),
-                           _i(window), _c(_native.status_ptr()), stream)
-    _native.check(rc, "gb_flash_attn")
+    if decode and USE_DECODE_KERNEL and hq // hkv <= 16:
+        rc = lib.gb_flash_decode(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
+                                 _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
+                                 _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(num_splits), _i(window),
+                                 _c(_native.status_ptr()), stream)
+        _native.check(rc, "gb_flash_decode")
+    else:
+        rc = lib.gb_flash_attn(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
+                               _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
+                               _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(num_splits), _i(1 if causal else 0),
+                               _i(window), _c(_native.status_ptr()), stream)
+        _native.check(rc, "gb_flash_attn")
     if num_splits > 1:
         rc = lib.gb_fa_combine(_p(part_o), _p(part_lse), _p(out), _c(0), _i(num_splits), _l(t * hq), stream)
         _native.check(rc, "gb_fa_combine")

@@ -196,7 +196,7 @@ class Engine:
         st = self._static
         fb = ForwardBatch(ids=st["ids"], positions=st["positions"], slots=st["slots"], cu_q=st["cu_q"], kv_len=st["kv_len"],
                           block_table=st["block_table"], work=st["work"], logit_rows=st["rows"], num_splits=self._splits,
-                          n_tokens=st["ids"].numel(), seq_slots=st["seq_slots"])
+                          n_tokens=st["ids"].numel(), seq_slots=st["seq_slots"], is_decode=True)
         if self._sp.temperature <= 0 and not hasattr(self.par, "merge_sampled"):
             tok = self.model.forward_greedy(fb)
         else:

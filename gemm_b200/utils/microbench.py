@@ -115,7 +115,9 @@ def case_moe_prefill(args):
 
 
 def _attn(args, b: int, q_len: int, ctx: int, name: str):
-    hq, hkv, d, page = 32, 4, 128, 64
+    hq, hkv, d, page = args.hq, args.hkv, 128, args.page
+    b = args.batch if args.batch > 0 else b
+    ctx = args.ctx if args.ctx >= 0 else ctx
     pages_per = (ctx + q_len + page - 1) // page
     n_pages = b * pages_per + 1
     k = (torch.randn(n_pages * page, hkv, d, device="cuda") * 0.5).bfloat16()
@@ -131,14 +133,14 @@ def _attn(args, b: int, q_len: int, ctx: int, name: str):
     work = att.build_work(q_lens, hq, hkv, splits).to("cuda")
 
     def run():
-        att.attention(q, k, v, cu, kv_len, bt, page, work, num_splits=splits, causal=True)
+        att.attention(q, k, v, cu, kv_len, bt, page, work, num_splits=splits, causal=True, decode=(q_len == 1))
 
     kv_bytes = b * (ctx + q_len) * hkv * d * 2 * 2
     if q_len == 1:
         flops = 4.0 * b * hq * (ctx + 1) * d
     else:
         flops = 4.0 * b * hq * d * (q_len * ctx + q_len * (q_len + 1) / 2)
-    _run(name, run, flops, kv_bytes + b * q_len * hq * d * 4, args, splits=splits)
+    _run(name, run, flops, kv_bytes + b * q_len * hq * d * 4, args, splits=splits, batch=b, ctx=ctx, hq=hq, hkv=hkv, page=page)
 
 
 def case_attn_decode(args):
@@ -165,6 +167,11 @@ def main(argv=None):
     ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES))
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--splits", type=int, default=0, help="attention cases: force the number of KV splits")
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=4)
+    ap.add_argument("--page", type=int, default=128, help="attention cases: KV page size")
+    ap.add_argument("--batch", type=int, default=0, help="attention cases: number of sequences (0 = the case's default)")
+    ap.add_argument("--ctx", type=int, default=-1, help="attention cases: cached tokens per sequence (-1 = the case's default)")
     ap.add_argument("--once", action="store_true", help="run each op once, untimed (for use under a profiler)")
     args = ap.parse_args(argv)
     torch.manual_seed(0)

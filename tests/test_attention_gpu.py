@@ -79,3 +79,30 @@ def test_sliding_window_and_noncausal():
     ref = att.attention_ref(q, kc, vc, cu, kvl, bt, 128, causal=False)
     _native.assert_status_ok()
     assert _rel(out, ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("hq,hkv,page", [(32, 4, 128), (8, 2, 16), (16, 1, 64), (4, 4, 128)])
+def test_decode_kernel(hq, hkv, page, splits):
+    """The decode-specialised kernel (KV positions on the MMA M axis) against the fp32 reference and the general kernel."""
+    b = 7
+    q_lens, ctx = [1] * b, [0, 5, 127, 128, 1000, 2047, 300]
+    q, kc, vc, cu, kvl, bt = _setup(q_lens, ctx, hq, hkv, page, seed=3)
+    work = att.build_work(q_lens, hq, hkv, splits).cuda()
+    out = att.attention(q, kc, vc, cu, kvl, bt, page, work, num_splits=splits, decode=True)
+    ref = att.attention_ref(q, kc, vc, cu, kvl, bt, page)
+    _native.assert_status_ok()
+    assert _rel(out, ref) < 1.5e-2
+    gen = att.attention(q, kc, vc, cu, kvl, bt, page, work, num_splits=splits)
+    assert _rel(out, gen) < 1.5e-2
+
+
+def test_decode_kernel_sliding_window():
+    b = 3
+    q_lens, ctx = [1] * b, [700, 90, 300]
+    q, kc, vc, cu, kvl, bt = _setup(q_lens, ctx, 8, 2, 128, seed=4)
+    work = att.build_work(q_lens, 8, 2).cuda()
+    out = att.attention(q, kc, vc, cu, kvl, bt, 128, work, window=200, decode=True)
+    ref = att.attention_ref(q, kc, vc, cu, kvl, bt, 128, window=200)
+    _native.assert_status_ok()
+    assert _rel(out, ref) < 1.5e-2
