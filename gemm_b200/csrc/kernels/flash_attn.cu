@@ -478,10 +478,11 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int r = q * 32 + lane;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     float m[kFdN], l[kFdN];          // m: the reference maximum the exponentials are taken against (may lag the true maximum by <= kTau)
+                                     // l: THIS thread's share of the row sums (its positions only); the threads' shares are added once, at the end
 #pragma unroll
     for (int h = 0; h < kFdN; ++h) { m[h] = -INFINITY; l[h] = 0.f; }
     constexpr float kTau = 8.0f;     // O and l are only rescaled when a block raises a maximum by more than 2^kTau
-    bool ok = true;
+    bool ok = true, fail_o = false;  // fail_o: a wait for the second MMA ran out; it is put to the vote at the next barrier
     for (int j = 0; j < n_blk && ok; ++j) {
       const int s = j & 1;
       const bool got_s = mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, a.status, 610, j);
@@ -492,14 +493,13 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int kp = (blk_lo + j) * kBN + r;
       const bool live = kp <= qpos && kp >= first_pos;
       float* rm = red_max + (j & 1) * 4 * kFdN;
-      float* rs = red_sum + (j & 1) * 4 * kFdN;
 #pragma unroll
       for (int h = 0; h < kFdN; ++h) if (!live || h >= G) sv[h] = -INFINITY;
       {
         const float v = warp_reduce16_max(sv, lane);            // lane L ends with head L >> 1
         if ((lane & 1) == 0) rm[q * kFdN + (lane >> 1)] = v;
       }
-      if (!softmax_bar_and(got_s)) { ok = false; break; }          // maxima of all four warps are in rm
+      if (!softmax_bar_and(got_s && !fail_o)) { ok = false; break; }   // maxima of all four warps are in rm; all 128 threads leave together
       float bm[kFdN];
       bool need = false;
 #pragma unroll
@@ -515,10 +515,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         alpha[h] = need ? fast_exp2(m[h] - m_use) : 1.0f;
         m[h] = m_new;
         pv[h] = fast_exp2(sv[h] - m_use);
-      }
-      {
-        const float v = warp_reduce16_sum(pv, lane);
-        if ((lane & 1) == 0) rs[q * kFdN + (lane >> 1)] = v;
+        l[h] = l[h] * alpha[h] + pv[h];
       }
       bool got_o = true;
       if (j >= 2) {
@@ -552,11 +549,17 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_before();
         mbar_arrive(p_ready);
       }
-      if (!softmax_bar_and(got_o)) { ok = false; break; }          // also: the sums of all four warps are in rs
-#pragma unroll
-      for (int h = 0; h < kFdN; ++h) l[h] = l[h] * alpha[h] + (rs[h] + rs[kFdN + h] + rs[2 * kFdN + h] + rs[3 * kFdN + h]);
+      fail_o |= !got_o;
     }
-    if (ok && n_blk > 0) ok = mbar_wait(&o_ready[(n_blk - 1) & 1], (uint32_t)((n_blk - 1) >> 1) & 1, abort_flag, a.status, 612);
+    if (ok && !fail_o && n_blk > 0) ok = mbar_wait(&o_ready[(n_blk - 1) & 1], (uint32_t)((n_blk - 1) >> 1) & 1, abort_flag, a.status, 612);
+    // row sums: add the 128 threads' shares (one reduce-scatter per warp, then the four warps through shared memory)
+    {
+      const float v = warp_reduce16_sum(l, lane);
+      if ((lane & 1) == 0) red_sum[q * kFdN + (lane >> 1)] = v;
+      ok = softmax_bar_and(ok && !fail_o);       // every softmax thread gets here exactly once, whatever happened in the loop
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) l[h] = red_sum[h] + red_sum[kFdN + h] + red_sum[2 * kFdN + h] + red_sum[3 * kFdN + h];
+    }
     if (ok && !bad_item) {
       tc_fence_after();
       uint32_t o[kFdN];
