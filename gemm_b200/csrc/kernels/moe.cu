@@ -19,16 +19,11 @@ namespace gb {
 
 constexpr int kMaxTopK = 16;
 
-// One warp per token.  E <= 512.
-__global__ void __launch_bounds__(256)
-moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
-                 int n_tok, int n_exp, int k, int mode, int renorm, float routed_scale, int ld, int id_shift, int n_local) {
-  pdl_wait();
-  pdl_trigger();
-  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (w >= n_tok) return;
-  const int lane = threadIdx.x & 31;
-  constexpr int MAXV = 16;
+// Routing of token `w` by one warp (E <= 512): lane j < k ends with the j-th pick.  Returns the (possibly local) expert id.
+template <int MAXV>
+__device__ __forceinline__ int route_token_n(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                                           float* __restrict__ weights, int w, int lane, int n_exp, int k, int mode, int renorm,
+                                           float routed_scale, int ld, int id_shift, int n_local) {
   float p[MAXV], sel[MAXV];
   float mx = -FLT_MAX;
 #pragma unroll
@@ -79,14 +74,37 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bia
     wsum += pv;
     if (lane == j) { my_w = pv; my_id = bi; }
   }
+  int out_id = -1;
   if (lane < k) {
     float wv = my_w;
     if (renorm) wv = wv / fmaxf(wsum, 1e-20f);
     // expert-parallel ranks that see every token keep only their own experts: ids become local, the others -1
     const int lid = my_id - id_shift;
-    ids[(size_t)w * k + lane] = (n_local > 0 && (lid < 0 || lid >= n_local)) ? -1 : lid;
+    out_id = (n_local > 0 && (lid < 0 || lid >= n_local)) ? -1 : lid;
+    ids[(size_t)w * k + lane] = out_id;
     weights[(size_t)w * k + lane] = wv * routed_scale;
   }
+  return out_id;
+}
+
+// The per-lane expert slots are sized to the expert count, so a 128-expert router runs a quarter of the 512-expert code.
+__device__ __forceinline__ int route_token(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                                           float* __restrict__ weights, int w, int lane, int n_exp, int k, int mode, int renorm,
+                                           float routed_scale, int ld, int id_shift, int n_local) {
+  if (n_exp <= 128) return route_token_n<4>(logits, bias, ids, weights, w, lane, n_exp, k, mode, renorm, routed_scale, ld, id_shift, n_local);
+  if (n_exp <= 256) return route_token_n<8>(logits, bias, ids, weights, w, lane, n_exp, k, mode, renorm, routed_scale, ld, id_shift, n_local);
+  return route_token_n<16>(logits, bias, ids, weights, w, lane, n_exp, k, mode, renorm, routed_scale, ld, id_shift, n_local);
+}
+
+// One warp per token.
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights,
+                 int n_tok, int n_exp, int k, int mode, int renorm, float routed_scale, int ld, int id_shift, int n_local) {
+  pdl_wait();
+  pdl_trigger();
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (w >= n_tok) return;
+  route_token(logits, bias, ids, weights, w, threadIdx.x & 31, n_exp, k, mode, renorm, routed_scale, ld, id_shift, n_local);
 }
 
 // Router logits for decode-sized batches on the CUDA cores: out[m, n] = sum_k x[m, k] * w[n, k] (bf16 in, fp32 out).
@@ -101,22 +119,34 @@ small_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
   extern __shared__ uint4 sx[];                     // [kSlTok][k / 8] vectors of 8 bf16
   const int n0 = blockIdx.x * kSlRows, m0 = blockIdx.y * kSlTok;
   const int kv = k >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int RPW = kSlRows / 8;                  // rows per warp
+  constexpr int MAXV = 8;                           // weight vectors per lane and row held in registers (k <= 2048); longer rows loop
+  // the weight rows of this warp are requested first, so that their latency overlaps the staging of the token rows
+  uint4 wr[RPW][MAXV];
+#pragma unroll
+  for (int rr = 0; rr < RPW; ++rr) {
+    const int row = n0 + warp * RPW + rr;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      wr[rr][i] = (row < n && v < kv) ? *reinterpret_cast<const uint4*>(w + (size_t)row * ldw + v * 8) : make_uint4(0, 0, 0, 0);
+    }
+  }
   for (int i = threadIdx.x; i < kSlTok * kv; i += blockDim.x) {
     const int tk = i / kv, v = i - tk * kv;
     sx[i] = (m0 + tk < m) ? *reinterpret_cast<const uint4*>(x + (size_t)(m0 + tk) * ldx + v * 8) : make_uint4(0, 0, 0, 0);
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#pragma unroll 1
-  for (int rr = 0; rr < kSlRows / 8; ++rr) {
-    const int row = n0 + warp * (kSlRows / 8) + rr;
+#pragma unroll
+  for (int rr = 0; rr < RPW; ++rr) {
+    const int row = n0 + warp * RPW + rr;
     if (row >= n) continue;
     float acc[kSlTok];
 #pragma unroll
     for (int i = 0; i < kSlTok; ++i) acc[i] = 0.f;
-    for (int v = lane; v < kv; v += 32) {
-      const uint4 wr = *reinterpret_cast<const uint4*>(w + (size_t)row * ldw + v * 8);
-      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wr);
+    auto fma_vec = [&](const uint4& wv, int v) {
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
       float wf[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(wh[i]); wf[2 * i] = f.x; wf[2 * i + 1] = f.y; }
@@ -127,7 +157,10 @@ small_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 #pragma unroll
         for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(xh[i]); acc[tk] += wf[2 * i] * f.x + wf[2 * i + 1] * f.y; }
       }
-    }
+    };
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) if (lane + 32 * i < kv) fma_vec(wr[rr][i], lane + 32 * i);
+    for (int v = lane + 32 * MAXV; v < kv; v += 32) fma_vec(*reinterpret_cast<const uint4*>(w + (size_t)row * ldw + v * 8), v);
 #pragma unroll
     for (int tk = 0; tk < kSlTok; ++tk) {
       const float s = warp_sum(acc[tk]);
@@ -229,7 +262,10 @@ constexpr int kSmallPairs = 2048;
 __global__ void __launch_bounds__(1024)
 moe_plan_small_kernel(const int* __restrict__ ids, int* __restrict__ seg_start, int* __restrict__ seg_count,
                       int* __restrict__ region_rows_used, int* __restrict__ pair_row, int* __restrict__ row_token, int n_pairs,
-                      int n_exp, int k, int experts_per_region, int region_rows, int align, int capacity, unsigned* epoch_ctr) {
+                      int n_exp, int k, int experts_per_region, int region_rows, int align, int capacity, unsigned* epoch_ctr,
+                      const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids_out,
+                      float* __restrict__ weights_out, int n_route_exp, int mode, int renorm, float routed_scale, int ld, int id_shift,
+                      int n_local) {
   pdl_wait();
   pdl_trigger();
   __shared__ int se[kSmallPairs];
@@ -239,11 +275,24 @@ moe_plan_small_kernel(const int* __restrict__ ids, int* __restrict__ seg_start, 
   for (int e = t; e < n_exp; e += blockDim.x) cnt[e] = 0;
   for (int r = t; r < capacity; r += blockDim.x) row_token[r] = -1;
   __syncthreads();
-  for (int i = t; i < n_pairs; i += blockDim.x) {
-    int e = ids[i];
-    if (e < 0 || e >= n_exp) e = -1;
-    se[i] = e;
-    if (e >= 0) atomicAdd(&cnt[e], 1);
+  if (logits != nullptr) {
+    // routing fused in: a warp per token picks the top-k and leaves the ids in shared memory for the plan
+    const int lane = t & 31, n_tok = n_pairs / k;
+    for (int w = t >> 5; w < n_tok; w += (int)(blockDim.x >> 5)) {
+      int e = route_token(logits, bias, ids_out, weights_out, w, lane, n_route_exp, k, mode, renorm, routed_scale, ld, id_shift, n_local);
+      if (lane < k) {
+        if (e < 0 || e >= n_exp) e = -1;
+        se[w * k + lane] = e;
+        if (e >= 0) atomicAdd(&cnt[e], 1);
+      }
+    }
+  } else {
+    for (int i = t; i < n_pairs; i += blockDim.x) {
+      int e = ids[i];
+      if (e < 0 || e >= n_exp) e = -1;
+      se[i] = e;
+      if (e >= 0) atomicAdd(&cnt[e], 1);
+    }
   }
   __syncthreads();
   // aligned segment starts: every expert sums the padded counts of the experts before it in its region (parallel, E <= 512)
@@ -405,7 +454,8 @@ GB_API int gb_moe_plan(const int* ids, int* workspace, int* seg_start, int* seg_
   if (n_exp % experts_per_region) return fail("moe_plan: n_exp %% experts_per_region != 0%s");
   if (n_pairs <= kSmallPairs && capacity < (1l << 30)) {
     launch_k(moe_plan_small_kernel, 1, 1024, 0, stream, ids, seg_start, seg_count, region_rows_used, pair_row, row_token, (int)n_pairs,
-             n_exp, k, experts_per_region, region_rows, align, (int)capacity, (unsigned*)epoch_ctr);
+             n_exp, k, experts_per_region, region_rows, align, (int)capacity, (unsigned*)epoch_ctr, (const float*)nullptr,
+             (const float*)nullptr, (int*)nullptr, (float*)nullptr, 0, 0, 0, 1.0f, 0, 0, 0);
     GB_CUDA_OK(cudaGetLastError());
     return 0;
   }
@@ -415,6 +465,22 @@ GB_API int gb_moe_plan(const int* ids, int* workspace, int* seg_start, int* seg_
   launch_k(moe_scan_kernel, n_exp, 256, 0, stream, workspace, seg_count, nb, n_exp);
   launch_k(moe_seg_kernel, 1, 512, 0, stream, seg_count, seg_start, region_rows_used, n_exp, experts_per_region, region_rows, align, (unsigned*)epoch_ctr);
   if (nb > 0) launch_k(moe_scatter_kernel, nb, kPlanBlock, 0, stream, ids, workspace, seg_start, pair_row, row_token, n_pairs, n_exp, k, capacity);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Routing and plan in one launch for decode-sized batches (n_tok * k <= 2048): logits f32 [n_tok, n_route_exp] -> ids / weights
+// [n_tok, k] plus every output of gb_moe_plan over `n_exp` plan experts (= n_local when the ids are made local, else n_route_exp).
+GB_API int gb_moe_route_plan(const float* logits, const float* bias, int* ids, float* weights, int n_tok, int n_route_exp, int k, int mode,
+                             int renorm, float routed_scale, int ld, int id_shift, int n_local, int* seg_start, int* seg_count,
+                             int* region_rows_used, int* pair_row, int* row_token, int n_exp, int experts_per_region, int region_rows,
+                             int align, long capacity, void* epoch_ctr, cudaStream_t stream) {
+  if (n_route_exp > 512 || n_exp > 512 || k > kMaxTopK || k > n_route_exp) return fail("moe_route_plan: need n_exp <= 512 and k <= 16%s");
+  if ((long)n_tok * k > kSmallPairs || n_tok <= 0) return fail("moe_route_plan: batch too large for the single-kernel path%s");
+  if (n_exp % experts_per_region) return fail("moe_route_plan: n_exp %% experts_per_region != 0%s");
+  launch_k(moe_plan_small_kernel, 1, 1024, 0, stream, (const int*)nullptr, seg_start, seg_count, region_rows_used, pair_row, row_token,
+           n_tok * k, n_exp, k, experts_per_region, region_rows, align, (int)capacity, (unsigned*)epoch_ctr, logits, bias, ids, weights,
+           n_route_exp, mode, renorm, routed_scale, ld, id_shift, n_local);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

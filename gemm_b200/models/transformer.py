@@ -248,11 +248,10 @@ class Transformer:
         t = h.shape[0]
         e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
         logits = moe.router_logits(h, lw.router)
-        ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
         if self.mx:
             # token tile (= scale-atom layout) by the expected rows per expert: 32 for decode-sized batches
             tn = 32 if (t * k) // e <= 24 else 128
-            pl = moe.plan(ids, e, tn)
+            ids, wts, pl = moe.route_plan(logits, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
             xq = ew.mx_quantize(h, pl.row_token, sf_layout=tn)
             dev = h.device
             hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=dev)
@@ -262,7 +261,7 @@ class Transformer:
                                     w_tiled=lw.w2.mx.tiled)
         else:
             tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
-            pl = moe.plan(ids, e, tn)
+            ids, wts, pl = moe.route_plan(logits, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
             xs = moe.gather_rows(h, pl.row_token)
             act = gemm.grouped_linear(xs, lw.w13.w.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
             y = gemm.grouped_linear(act, lw.w2.w.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)

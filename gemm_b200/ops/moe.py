@@ -161,6 +161,39 @@ def plan(ids: torch.Tensor, n_exp: int, align: int, regions: int = 1, workspace=
     return MoePlan(seg_start, seg_count, pair_row, row_token, region_used, capacity, region_rows)
 
 
+def route_plan(logits: torch.Tensor, k: int, n_exp: int, align: int, mode: str = "softmax", bias: Optional[torch.Tensor] = None,
+               renorm: bool = True, routed_scale: float = 1.0, local_range: Optional[Tuple[int, int]] = None, regions: int = 1,
+               epoch_ctr: int = 0, region_rows: Optional[int] = None):
+    """``route`` followed by ``plan``; decode-sized batches (T * k <= 2048) do both in ONE kernel.  ``n_exp`` is the number of
+    experts the plan is built over (the local count when ``local_range`` is given).  Returns ``(ids, weights, MoePlan)``."""
+    t, e_all = logits.shape
+    if not logits.is_cuda or t * k > 2048:
+        ids, w = route(logits, k, mode, bias, renorm, routed_scale, local_range)
+        return ids, w, plan(ids, n_exp, align, regions, epoch_ctr=epoch_ctr, region_rows=region_rows)
+    dev = logits.device
+    n_pairs = t * k
+    need_rows, capacity = plan_capacity(n_pairs, n_exp, align, regions, k)
+    if region_rows is None:
+        region_rows = need_rows
+    else:
+        assert region_rows >= need_rows and region_rows % 128 == 0
+        capacity = region_rows * regions
+    ids = torch.empty(t, k, dtype=torch.int32, device=dev)
+    w = torch.empty(t, k, dtype=torch.float32, device=dev)
+    seg_start = torch.empty(n_exp, dtype=torch.int32, device=dev)
+    seg_count = torch.empty(n_exp, dtype=torch.int32, device=dev)
+    region_used = torch.empty(regions, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(n_pairs, dtype=torch.int32, device=dev)
+    row_token = torch.empty(capacity, dtype=torch.int32, device=dev)
+    rc = _native.cuda().gb_moe_route_plan(_p(logits), _p(bias), _p(ids), _p(w), _i(t), _i(e_all), _i(k), _i(0 if mode == "softmax" else 1),
+                                          _i(1 if renorm else 0), _f(routed_scale), _i(logits.stride(0)),
+                                          _i(local_range[0] if local_range else 0), _i(local_range[1] if local_range else 0),
+                                          _p(seg_start), _p(seg_count), _p(region_used), _p(pair_row), _p(row_token), _i(n_exp),
+                                          _i(n_exp // regions), _i(region_rows), _i(align), _l(capacity), _c(epoch_ctr), _s())
+    _native.check(rc, "gb_moe_route_plan")
+    return ids, w, MoePlan(seg_start, seg_count, pair_row, row_token, region_used, capacity, region_rows)
+
+
 def combine(y: torch.Tensor, pair_row: torch.Tensor, weights: Optional[torch.Tensor], n_tok: int, k: int,
             wait_flags: int = 0, wait_n: int = 0, epoch_ptr: int = 0) -> torch.Tensor:
     """``out[t] = sum_j weights[t, j] * y[pair_row[t*k + j]]`` (bf16, fp32 accumulation in fixed order)."""

@@ -186,3 +186,18 @@ def test_router_logits_small_batch(t, e, k):
     got = moe.router_logits(h, w)
     ref = h.float() @ w.float().t()
     assert got.dtype == torch.float32 and _rel(got, ref) < 1e-5
+
+
+@pytest.mark.parametrize("t,local", [(1, None), (64, None), (256, None), (64, (32, 16)), (200, (0, 64))])
+def test_route_plan_single_kernel(t, local):
+    """Routing + plan in one launch equals the two separate ops."""
+    torch.manual_seed(23)
+    e, k, align = 128, 8, 32
+    logits = torch.randn(t, e, device="cuda")
+    n_plan = local[1] if local else e
+    ids, w, pl = moe.route_plan(logits, k, n_plan, align, local_range=local)
+    ids2, w2 = moe.route(logits, k, local_range=local)
+    pl2 = moe.plan(ids2, n_plan, align)
+    assert torch.equal(ids, ids2) and torch.equal(w, w2)
+    for a, b in ((pl.seg_start, pl2.seg_start), (pl.seg_count, pl2.seg_count), (pl.pair_row, pl2.pair_row), (pl.row_token, pl2.row_token)):
+        assert torch.equal(a, b)
