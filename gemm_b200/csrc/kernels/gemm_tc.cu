@@ -79,8 +79,11 @@ struct GemmArgs {
   // ---- weight layout: 0 = row-major [rows, k]; 1 = tiled [rows/128][k-blocks][128 rows][128 bytes], every 16 KB operand
   // tile of the main loop is one contiguous block of memory (one DRAM burst sequence instead of 128 strided lines)
   int w_tiled;
-  int debug;     // experiment knob (GB_GEMM_DEBUG): bit 0 = issue no MMA (pure load stream), bit 1 = load no weight tiles (pure MMA issue)
+  int debug;     // experiment knob (GB_GEMM_DEBUG): bit 0 = issue no MMA (pure load stream), bit 1 = load no weight tiles, bit 4 = load nothing (pure MMA issue)
 };
+
+// k-steps whose MXFP8 scale atoms are fetched by one bulk copy (2 for the widest tile, whose stages are short of room)
+__host__ __device__ constexpr int sf_group(int tn) { return tn >= 256 ? 2 : 4; }
 
 struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; int ks; int tile_id; };
 
@@ -140,10 +143,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   constexpr int A_BYTES = 128 * 128;                 // 128 rows x 128 bytes
   constexpr int B_BYTES = TN * 128;
   constexpr int SFB_ATOMS = (TN + 127) / 128;
-  constexpr int SF_BYTES = (MODE == 1) ? (((NA + SFB_ATOMS) * 512 + 1023) & ~1023) : 0;
+  // Scale atoms travel and are copied to TMEM in groups of SFG k-steps: the atoms of consecutive k-steps are contiguous in
+  // memory, so one bulk copy per operand and group replaces SFG copies of 512 bytes (which cost the producer thread
+  // more issue time than the 16 KB operand tiles).  The group sits in the stage of its first k-step.
+  constexpr int SFG = sf_group(TN);
+  constexpr int SF_BYTES = (MODE == 1) ? (((NA + SFB_ATOMS) * 512 * SFG + 1023) & ~1023) : 0;
   constexpr int STAGE_BYTES = NA * A_BYTES + B_BYTES + SF_BYTES;
   constexpr int ACC_COLS = NA * TN;
-  constexpr int SF_COLS = (MODE == 1) ? (NA * 4 + SFB_ATOMS * 4) : 0;
+  constexpr int SF_COLS = (MODE == 1) ? (NA * 4 + SFB_ATOMS * 4) * SFG : 0;
   constexpr int NACC = (2 * ACC_COLS + SF_COLS <= 512) ? 2 : 1;
   constexpr int NEED_COLS = NACC * ACC_COLS + SF_COLS;
   constexpr int TMEM_COLS = NEED_COLS <= 32 ? 32 : NEED_COLS <= 64 ? 64 : NEED_COLS <= 128 ? 128 : NEED_COLS <= 256 ? 256 : 512;
@@ -218,8 +225,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 100, s)) { ok = false; break; }
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          if (args.debug & 16) {           // no loads at all: the MMA thread runs on whatever shared memory holds
+            mbar_arrive(&full_bar[s]);
+            if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[dbg_i++] = clock64();
+            if (++s == S) { s = 0; ph ^= 1; }
+            continue;
+          }
           const bool load_w = !(args.debug & 2);
-          mbar_expect_tx(&full_bar[s], (load_w ? NA * A_BYTES : 0) + B_BYTES + ((MODE == 1) ? (NA + SFB_ATOMS) * 512 : 0));
+          const int kbi = kb - kb0;
+          const int glen = (MODE == 1 && kbi % SFG == 0) ? min(SFG, kb1 - kb) : 0;     // scale group starting at this k-step
+          mbar_expect_tx(&full_bar[s], (load_w ? NA * A_BYTES : 0) + B_BYTES + (NA + SFB_ATOMS) * 512 * glen);
           const int kx = kb * KB_ELEMS;
           if (!load_w) {
           } else if (args.w_tiled) {
@@ -230,24 +245,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], kx, t.w_row1);
           }
           tma_load_2d(st + NA * A_BYTES, &tmX, &full_bar[s], kx, t.x_row0);
-          if (MODE == 1) {
+          if (MODE == 1 && glen > 0) {
             uint8_t* sf = st + NA * A_BYTES + B_BYTES;
             const size_t kbs = (size_t)num_kb;
-            // scale atoms: offsets are checked against the buffers' extents; a bad one is reported and replaced by atom 0
-            auto atom = [&](const uint8_t* base, size_t extent, size_t off, int where) -> const uint8_t* {
-              if (extent != 0 && off + 512 > extent) { report_status(args.status, ST_BAD_ARG, where, (int)(off >> 9), (int)(extent >> 9), ti); return base; }
+            const uint32_t gbytes = (uint32_t)glen * 512;
+            // scale atoms: offsets are checked against the buffers' extents; a bad one is reported and replaced by the first atoms
+            auto atoms = [&](const uint8_t* base, size_t extent, size_t off, int where) -> const uint8_t* {
+              if (extent != 0 && off + gbytes > extent) { report_status(args.status, ST_BAD_ARG, where, (int)(off >> 9), (int)(extent >> 9), ti); return base; }
               return base + off;
             };
-            bulk_load(sf, atom(args.sfa, args.sfa_bytes, ((size_t)(t.w_row0 >> 7) * kbs + kb) * 512, 120), 512, &full_bar[s]);
-            if (DUAL) bulk_load(sf + 512, atom(args.sfa, args.sfa_bytes, ((size_t)(t.w_row1 >> 7) * kbs + kb) * 512, 121), 512, &full_bar[s]);
+            bulk_load(sf, atoms(args.sfa, args.sfa_bytes, ((size_t)(t.w_row0 >> 7) * kbs + kb) * 512, 120), gbytes, &full_bar[s]);
+            if (DUAL) bulk_load(sf + SFG * 512, atoms(args.sfa, args.sfa_bytes, ((size_t)(t.w_row1 >> 7) * kbs + kb) * 512, 121), gbytes, &full_bar[s]);
             if (TN == 32) {
               // narrow tiles use one atom per 32 rows (bytes 0..3 of each 16-byte lane row), so that the tile's
               // scales always land in column 0 of their TMEM block whatever 32-row boundary the tile starts on
-              bulk_load(sf + NA * 512, atom(args.sfb, args.sfb_bytes, ((size_t)(t.x_row0 >> 5) * kbs + kb) * 512, 122), 512, &full_bar[s]);
+              bulk_load(sf + NA * SFG * 512, atoms(args.sfb, args.sfb_bytes, ((size_t)(t.x_row0 >> 5) * kbs + kb) * 512, 122), gbytes, &full_bar[s]);
             } else {
 #pragma unroll
-              for (int i = 0; i < SFB_ATOMS; ++i)
-                bulk_load(sf + (NA + i) * 512, atom(args.sfb, args.sfb_bytes, ((size_t)((t.x_row0 >> 7) + i) * kbs + kb) * 512, 123), 512, &full_bar[s]);
+              for (int i = 0; i < SFB_ATOMS; ++i) {
+                // a 256-token tile whose valid rows end in its first half has no second atom to fetch (it may lie past the
+                // end of the scale buffer): the first one is fetched again so that the byte count of the stage stays fixed
+                const int ai = (i * 128 < t.valid) ? i : 0;
+                bulk_load(sf + (NA + i) * SFG * 512, atoms(args.sfb, args.sfb_bytes, ((size_t)((t.x_row0 >> 7) + ai) * kbs + kb) * 512, 123), gbytes, &full_bar[s]);
+              }
             }
           }
           if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[dbg_i++] = clock64();
@@ -275,14 +295,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
           uint32_t sfb_t = 0;
           if (args.debug & 1) { tc_commit(&empty_bar[s]); if (++s == S) { s = 0; ph ^= 1; } continue; }
+          uint32_t sfa_t = 0;
           if (MODE == 1) {
-            const uint32_t sf = st + NA * A_BYTES + B_BYTES;
-            tc_cp_32x128b_warpx4(tmem_sf, make_sdesc_noswizzle(sf, 0, 128));
-            if (DUAL) tc_cp_32x128b_warpx4(tmem_sf + 4, make_sdesc_noswizzle(sf + 512, 0, 128));
+            const int kbi = kb - kb0, gj = kbi % SFG;
+            if (gj == 0) {
+              // the scale atoms of the next SFG k-steps came with this stage: copy them all into their TMEM columns
+              const uint32_t sf = st + NA * A_BYTES + B_BYTES;
+              const int glen = min(SFG, kb1 - kb);
+              for (int g = 0; g < glen; ++g) {
+                tc_cp_32x128b_warpx4(tmem_sf + g * 4, make_sdesc_noswizzle(sf + g * 512, 0, 128));
+                if (DUAL) tc_cp_32x128b_warpx4(tmem_sf + (SFG + g) * 4, make_sdesc_noswizzle(sf + (SFG + g) * 512, 0, 128));
 #pragma unroll
-            for (int i = 0; i < SFB_ATOMS; ++i)
-              tc_cp_32x128b_warpx4(tmem_sf + NA * 4 + i * 4, make_sdesc_noswizzle(sf + (NA + i) * 512, 0, 128));
-            sfb_t = tmem_sf + NA * 4;   // token tiles of MX GEMMs always start on a 128-row boundary
+                for (int i = 0; i < SFB_ATOMS; ++i)
+                  tc_cp_32x128b_warpx4(tmem_sf + (NA * SFG + g * SFB_ATOMS + i) * 4, make_sdesc_noswizzle(sf + ((NA + i) * SFG + g) * 512, 0, 128));
+              }
+            }
+            sfa_t = tmem_sf + gj * 4;
+            // token tiles of MX GEMMs always start on a 128-row boundary; the atoms of a 256-token tile sit side by side
+            sfb_t = tmem_sf + (NA * SFG + gj * SFB_ATOMS) * 4;
           }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -295,8 +325,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
               if (DUAL) mma_f16_ss(d0 + TN, make_sdesc_sw128(st + A_BYTES + j * 32), b, idesc, accum);
             } else {
               const uint32_t idesc = make_idesc_mx(128, TN, 0, 0, j, j);
-              mma_mxf8_ss(d0, a0, b, idesc, accum, tmem_sf, sfb_t);
-              if (DUAL) mma_mxf8_ss(d0 + TN, make_sdesc_sw128(st + A_BYTES + j * 32), b, idesc, accum, tmem_sf + 4, sfb_t);
+              mma_mxf8_ss(d0, a0, b, idesc, accum, sfa_t, sfb_t);
+              if (DUAL) mma_mxf8_ss(d0 + TN, make_sdesc_sw128(st + A_BYTES + j * 32), b, idesc, accum, sfa_t + SFG * 4, sfb_t);
             }
           }
           tc_commit(&empty_bar[s]);
@@ -464,6 +494,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
         __nv_bfloat16* o16 = (__nv_bfloat16*)obase + orow0 * args.ldo + n;
         float* o32 = (float*)obase + orow0 * args.ldo + n;
+        if constexpr (NACC == 1 && !DUAL) {
+          if (!args.out_f32) {
+            // One accumulator buffer (the widest tile with its scale columns fills TMEM): pull the whole row into registers
+            // as packed bf16, hand the buffer back to the MMA thread, and only then store, so that the stores overlap the
+            // next tile's MMAs.
+            uint32_t pk[TN / 2];
+#pragma unroll
+            for (int c = 0; c < TN; c += 16) {
+              uint32_t r[16];
+              tmem_ld_x16(tacc + c, r);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) pk[c / 2 + j] = pack_bf16x2(__uint_as_float(r[2 * j]) + bias, __uint_as_float(r[2 * j + 1]) + bias);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acce_bar[acc]);
+            if (store_ok) {
+#pragma unroll
+              for (int i = 0; i < TN / 2; ++i) {
+                const int xr = 2 * i;
+                if (xr < t.valid) ((unsigned short*)o16)[(size_t)xr * args.ldo] = (unsigned short)(pk[i] & 0xffffu);
+                if (xr + 1 < t.valid) ((unsigned short*)o16)[(size_t)(xr + 1) * args.ldo] = (unsigned short)(pk[i] >> 16);
+              }
+            }
+            if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4608 + dbg_t++] = clock64();
+            acc_ph ^= 1;
+            continue;
+          }
+        }
 #pragma unroll 1
         for (int c = 0; c < TN; c += 16) {
           uint32_t r0[16], r1[16];
@@ -538,7 +598,7 @@ template <int TN, int MODE, bool DUAL, bool QUANT_OUT>
 static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmArgs a, int max_tiles, cudaStream_t stream) {
   constexpr int NA = DUAL ? 2 : 1;
   constexpr int SFB_ATOMS = (TN + 127) / 128;
-  constexpr int STAGE_BYTES = NA * 16384 + TN * 128 + ((MODE == 1) ? (((NA + SFB_ATOMS) * 512 + 1023) & ~1023) : 0);
+  constexpr int STAGE_BYTES = NA * 16384 + TN * 128 + ((MODE == 1) ? (((NA + SFB_ATOMS) * 512 * sf_group(TN) + 1023) & ~1023) : 0);
   const int tail = 1024 + 2 * kMaxGroups * 4 + 256;
   int stages = (int)((220 * 1024 - tail - 1024) / STAGE_BYTES);
   if (stages > 8) stages = 8;
@@ -601,7 +661,7 @@ enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8, GEMM_W_
 //   w        [w_rows, k] row-major (bf16, or e4m3 bytes when GEMM_MX), w_rows = groups * w_rows_per_group
 //   x        [x_rows, k] row-major, same element type as w
 //   out      [*, ldo]    bf16 (default), f32 (GEMM_OUT_F32) or e4m3 + out_sf (GEMM_QUANT_OUT)
-//   tn       token tile: 16, 32, 64, 128 or 256 (256: bf16 non-DUAL only)
+//   tn       token tile: 16, 32, 64, 128 or 256 (256: non-DUAL without quantised output only)
 // Grouped mode (num_groups > 0): seg_start / seg_count are device arrays; seg_start[g] must be a
 // multiple of min(tn, 128); `max_rows` bounds the segment buffer (TMA extent).
 GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, int m_tok, int ldw, int ldx, int ldo,
@@ -688,6 +748,7 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   GB_DISPATCH(64)
   GB_DISPATCH(128)
   if (tn == 256 && !mx && !dual && !qo) return launch_gemm<256, 0, false, false>(tmW, tmX, a, max_tiles, stream);
+  if (tn == 256 && mx && !dual && !qo) return launch_gemm<256, 1, false, false>(tmW, tmX, a, max_tiles, stream);
 #undef GB_DISPATCH
   return fail("gemm: unsupported variant%s (tn=%ld flags=%ld)", "", (long)tn, (long)flags);
 }

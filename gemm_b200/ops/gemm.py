@@ -47,6 +47,9 @@ _sk_state = {}
 
 
 SPLIT_K = os.environ.get("GB_SPLITK", "0") == "1"
+# MXFP8 GEMMs over 256 or more tokens use 256-token tiles: one block-scaled tcgen05.mma costs the issuing thread about 160
+# cycles whether it is 128 or 256 columns wide, so the wide tile nearly doubles the tensor throughput of the prefill GEMMs.
+WIDE_TILE = os.environ.get("GB_WIDE_TILE", "1") != "0"
 
 
 def _splitk_extras(n_out: int, m_tok: int, k: int, tn: int, mx: bool, device, force: bool = False) -> Optional["GemmExtras"]:
@@ -197,6 +200,8 @@ def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_
     assert w.sf_layout == 128
     if tn is None:
         tn = 64 if (x.sf_layout == 128 and m <= 64) else x.sf_layout      # a single token block may use the 64-wide tile
+        if WIDE_TILE and tn == 128 and m >= 256 and out.dtype == torch.bfloat16 and not split_k:
+            tn = 256
     _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn, x_rows=x.data.shape[0],
             sfa=w.sf, sfb=x.sf, bias=bias, extras=_splitk_extras(n, m, k, tn, True, x.data.device, split_k))
     return out
@@ -248,6 +253,9 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
             out = torch.empty(x.shape[0], n_out, dtype=torch.bfloat16, device=x.device)
     if out.dtype == torch.float32:
         flags |= GEMM_OUT_F32
+    if (WIDE_TILE and mx and tn == 128 and not dual and not quant_out and row_map is None and row_scale is None
+            and out.dtype == torch.bfloat16 and x.shape[0] >= 256 * g):
+        tn = 256                          # prefill-sized segments (the scale atoms keep the 128-row layout)
     _launch(w, x, out, n_out, k, x.shape[0], k, x.stride(0), out.stride(0), flags, tn, num_groups=g, w_rows_per_group=r,
             up_row_offset=n_out if dual else 0, seg_start=seg_start, seg_count=seg_count, x_rows=x.shape[0], sfa=sfa,
             sfb=sfb, out_sf=out_sf, row_map=row_map, row_scale=row_scale, extras=extras)

@@ -60,6 +60,48 @@ def test_linear_mxfp8(m, n, k, lay):
     assert _rel(y, ref) < 2e-3
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 256, 256), (300, 384, 768), (700, 512, 2048), (1024, 2048, 4096)])
+def test_linear_mxfp8_wide_tile(m, n, k):
+    """bf16 results of 256 or more tokens take the 256-token tile (one accumulator buffer, registers staged epilogue); the
+    last tile may end in its first or its second half."""
+    torch.manual_seed(31)
+    x = torch.randn(m, k, device="cuda") * torch.rand(m, 1, device="cuda") * 4
+    w = torch.randn(n, k, device="cuda") * 0.05
+    bias = torch.randn(n, device="cuda")
+    xq, wq = mxfp8.quantize(x, sf_layout=128), mxfp8.quantize(w)
+    assert gemm.WIDE_TILE
+    y = gemm.linear_mx(xq, wq, bias=bias)
+    y128 = gemm.linear_mx(xq, wq, bias=bias, tn=128)
+    ref = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t() + bias
+    _native.assert_status_ok()
+    assert y.dtype == torch.bfloat16 and _rel(y, ref) < 4e-3
+    assert torch.equal(y, y128)
+
+
+def test_grouped_mxfp8_wide_tile():
+    torch.manual_seed(32)
+    g, n, k = 5, 384, 512
+    counts = torch.tensor([300, 0, 129, 512, 90], dtype=torch.int32)       # the last segment ends the buffer in a tile's first half
+    starts = torch.zeros(g, dtype=torch.int32)
+    pos = 0
+    for i in range(g):
+        starts[i] = pos
+        pos += (int(counts[i]) + 127) // 128 * 128
+    rows = max(pos, 256 * g)
+    x = torch.randn(rows, k, device="cuda")
+    w = torch.randn(g, n, k, device="cuda") * 0.05
+    xq = mxfp8.quantize(x, sf_layout=128)
+    wq = mxfp8.quantize(w.reshape(g * n, k))
+    sd, cd = starts.cuda(), counts.cuda()
+    y = gemm.grouped_linear(xq.data, wq.data.reshape(g, n, k), sd, cd, 128, sfa=wq.sf, sfb=xq.sf)
+    _native.assert_status_ok()
+    xf, wf = mxfp8.dequantize(xq), mxfp8.dequantize(wq).reshape(g, n, k)
+    for i in range(g):
+        s0, c = int(starts[i]), int(counts[i])
+        if c:
+            assert _rel(y[s0:s0 + c], xf[s0:s0 + c] @ wf[i].t()) < 4e-3, f"group {i}"
+
+
 @pytest.mark.parametrize("m,inter,k,lay", [(8, 128, 256, 128), (100, 768, 2048, 128), (20, 768, 2048, 32)])
 def test_mx_swiglu_quant_epilogue(m, inter, k, lay):
     torch.manual_seed(4)
