@@ -288,6 +288,96 @@ qk_norm_rope_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict
   for (int i = 0; i < EPL; ++i) dst[lane + 32 * i] = __float2bfloat16(x[i]);
 }
 
+// The same for head_dim 128 with full rotary (the Qwen3 shape), 16 lanes per (token, head): lane l holds elements 4l..4l+3 and
+// 64+4l..64+4l+3, i.e. both halves of four NeoX pairs, so that every access is an 8-byte vector and a warp moves 256
+// contiguous bytes per instruction (the generic kernel moves 2 bytes per lane).
+__global__ void __launch_bounds__(256)
+qk_norm_rope128_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ slots,
+                       const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w, __nv_bfloat16* __restrict__ q_out,
+                       __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int n_tok, int hq, int hkv,
+                       float theta, float eps, int ld_qkv, float q_scale, const float2* __restrict__ rope_tab, int tab_len,
+                       const int* __restrict__ pos3, int sec_h3, int sec_w3) {
+  pdl_wait();
+  pdl_trigger();
+  constexpr int D = 128, PAIRS = 64;
+  const int heads = hq + 2 * hkv;
+  const long total = (long)n_tok * heads;
+  long gh = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const bool active = gh < total;
+  if (!active) gh = total - 1;                 // the idle half of the last warp computes along (shuffles use the full mask)
+  const int l = threadIdx.x & 15;
+  const int t = (int)(gh / heads), h = (int)(gh % heads);
+  const __nv_bfloat16* src = qkv + (size_t)t * ld_qkv + (size_t)h * D;
+  auto unpack4 = [](uint2 v, float* f) {
+    const __nv_bfloat162* hp = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const float2 a = __bfloat1622float2(hp[0]), b = __bfloat1622float2(hp[1]);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+  };
+  float xa[4], xb[4];
+  unpack4(*reinterpret_cast<const uint2*>(src + 4 * l), xa);
+  unpack4(*reinterpret_cast<const uint2*>(src + PAIRS + 4 * l), xb);
+  const bool is_q = h < hq, is_k = !is_q && h < hq + hkv;
+  if (is_q || is_k) {
+    const __nv_bfloat16* w = is_q ? q_w : k_w;
+    if (w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ss += xa[i] * xa[i] + xb[i] * xb[i];
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float sc = rsqrtf(ss / (float)D + eps);
+      float wa[4], wb[4];
+      unpack4(*reinterpret_cast<const uint2*>(w + 4 * l), wa);
+      unpack4(*reinterpret_cast<const uint2*>(w + PAIRS + 4 * l), wb);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { xa[i] = xa[i] * sc * wa[i]; xb[i] = xb[i] * sc * wb[i]; }
+    }
+    float c[4], sn[4];
+    const int p0 = positions[t];
+    if (pos3 == nullptr && rope_tab != nullptr && p0 >= 0 && p0 < tab_len) {
+      const float4* tp = reinterpret_cast<const float4*>(rope_tab + (size_t)p0 * PAIRS + 4 * l);
+      const float4 u = tp[0], v = tp[1];
+      c[0] = u.x; sn[0] = u.y; c[1] = u.z; sn[1] = u.w; c[2] = v.x; sn[2] = v.y; c[3] = v.z; sn[3] = v.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int j = 4 * l + i;
+        int p = p0;
+        if (pos3 != nullptr) {
+          const int m3 = j % 3;
+          const int which = (m3 == 1 && j < sec_h3) ? 1 : (m3 == 2 && j < sec_w3) ? 2 : 0;
+          p = pos3[(size_t)which * n_tok + t];
+        }
+        if (rope_tab != nullptr && p >= 0 && p < tab_len) { const float2 cs = rope_tab[(size_t)p * PAIRS + j]; c[i] = cs.x; sn[i] = cs.y; }
+        else { const float inv_freq = powf(theta, -2.0f * (float)j / (float)D); sincosf((float)p * inv_freq, &sn[i], &c[i]); }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = xa[i], b = xb[i];
+      xa[i] = a * c[i] - b * sn[i];
+      xb[i] = a * sn[i] + b * c[i];
+    }
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)t * hq + h) * D;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { xa[i] *= q_scale; xb[i] *= q_scale; }
+  } else {
+    const int slot = slots[t];
+    if (slot < 0) return;
+    const int kh = is_k ? h - hq : h - hq - hkv;
+    dst = (is_k ? k_cache : v_cache) + ((size_t)slot * hkv + kh) * D;
+  }
+  if (!active) return;
+  uint2 oa, ob;
+  oa.x = pack_bf16x2(xa[0], xa[1]); oa.y = pack_bf16x2(xa[2], xa[3]);
+  ob.x = pack_bf16x2(xb[0], xb[1]); ob.y = pack_bf16x2(xb[2], xb[3]);
+  *reinterpret_cast<uint2*>(dst + 4 * l) = oa;
+  *reinterpret_cast<uint2*>(dst + PAIRS + 4 * l) = ob;
+}
+
 // ------------------------------------------------------------------------------------------ silu * up
 __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, long rows, int inter, int ld) {
   pdl_wait();
@@ -406,6 +496,30 @@ mx_quant_rows_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict
   }
 }
 
+// Gather of rows that are already MXFP8: output row r <- input row src_rows[r] (bytes and scales; the scale layouts of the
+// two sides may differ), negative sources are skipped.  The MoE dispatch of a layer whose RMSNorm already produced the
+// quantised tokens: every token is quantised once instead of once per selected expert.  One warp per output row, k % 128 == 0.
+__global__ void __launch_bounds__(256)
+mx_gather_rows_kernel(const uint8_t* __restrict__ in_q, const uint8_t* __restrict__ in_sf, const int* __restrict__ src_rows,
+                      uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf, long out_rows, int k, int in_sf32, int out_sf32) {
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const long warp0 = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, n_warps = ((long)gridDim.x * blockDim.x) >> 5;
+  const int vecs = k >> 4, k_atoms = k >> 7;
+  for (long r = warp0; r < out_rows; r += n_warps) {
+    const int src = src_rows[r];
+    if (src < 0) continue;
+    const uint4* ip = reinterpret_cast<const uint4*>(in_q + (size_t)src * k);
+    uint4* op = reinterpret_cast<uint4*>(out_q + (size_t)r * k);
+    for (int vi = lane; vi < vecs; vi += 32) op[vi] = ip[vi];
+    // the four scales of one 128-element block are four consecutive bytes in either layout
+    for (int a = lane; a < k_atoms; a += 32)
+      *reinterpret_cast<uint32_t*>(out_sf + sf_atom_offset(r, a * 4, k_atoms, out_sf32)) =
+          *reinterpret_cast<const uint32_t*>(in_sf + sf_atom_offset(src, a * 4, k_atoms, in_sf32));
+  }
+}
+
 // ------------------------------------------------------------------------------------------ casts
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
   pdl_wait();
@@ -502,6 +616,15 @@ GB_API int gb_qk_norm_rope(const void* qkv, const int* positions, const int* slo
                            cudaStream_t stream) {
   if (n_tok <= 0) return 0;
   const long warps = (long)n_tok * (hq + 2 * hkv);
+  const auto al8 = [](const void* p) { return ((uintptr_t)p & 7) == 0; };
+  if (head_dim == 128 && rope_pairs == 64 && ld_qkv % 4 == 0 && al8(qkv) && al8(q_w) && al8(k_w) && al8(q_out) && al8(k_cache) &&
+      al8(v_cache) && ((uintptr_t)rope_tab & 15) == 0) {
+    launch_k(qk_norm_rope128_kernel, (unsigned)((warps + 15) / 16), 256, 0, stream, (const __nv_bfloat16*)qkv, positions, slots,
+             (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+             n_tok, hq, hkv, theta, eps, ld_qkv, q_scale, (const float2*)rope_tab, tab_len, pos3, sec_h3, sec_w3);
+    GB_CUDA_OK(cudaGetLastError());
+    return 0;
+  }
   const int blocks = (int)((warps + 7) / 8);
 #define GB_QK(DV) launch_k(qk_norm_rope_kernel<DV>, blocks, 256, 0, stream, (const __nv_bfloat16*)qkv, positions, slots, \
     (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
@@ -544,6 +667,17 @@ GB_API int gb_mx_quant(const void* in, const int* src_rows, void* out_q, void* o
     return 0;
   }
   launch_k(mx_quant_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_mx_gather_rows(const void* in_q, const void* in_sf, const int* src_rows, void* out_q, void* out_sf, long out_rows, int k,
+                             int in_sf32, int out_sf32, cudaStream_t stream) {
+  if (out_rows <= 0) return 0;
+  if (k % 128 != 0) return fail("mx_gather_rows: k %% 128 != 0%s");
+  const long blocks = std::min<long>((out_rows + 7) / 8, (long)sm_count() * 16);
+  launch_k(mx_gather_rows_kernel, (unsigned)blocks, 256, 0, stream, (const uint8_t*)in_q, (const uint8_t*)in_sf, src_rows, (uint8_t*)out_q,
+           (uint8_t*)out_sf, out_rows, k, in_sf32, out_sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

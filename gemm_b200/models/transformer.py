@@ -242,7 +242,7 @@ class Transformer:
         act = gemm.linear_mx_swiglu_quant(xm, lw.w_gate_up.mx)
         return self.par.row_linear(lw.w_down, None, act)
 
-    def moe_local(self, lw, h: torch.Tensor) -> torch.Tensor:
+    def moe_local(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor] = None) -> torch.Tensor:
         """All experts on this GPU: route -> plan -> (gather + quantise) -> grouped gate/up -> grouped down -> combine."""
         cfg = self.cfg
         t = h.shape[0]
@@ -252,7 +252,9 @@ class Transformer:
             # token tile (= scale-atom layout) by the expected rows per expert: 32 for decode-sized batches
             tn = 32 if (t * k) // e <= 24 else 128
             ids, wts, pl = moe.route_plan(logits, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
-            xq = ew.mx_quantize(h, pl.row_token, sf_layout=tn)
+            # the RMSNorm before this block already quantised the tokens: gather bytes and scales (every token is quantised
+            # once, not once per selected expert)
+            xq = ew.mx_gather_rows(h_mx, pl.row_token, sf_layout=tn) if h_mx is not None else ew.mx_quantize(h, pl.row_token, sf_layout=tn)
             dev = h.device
             hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=dev)
             hsf = ew.sf_alloc(pl.capacity, inter, dev, tn, init=False)
@@ -295,7 +297,7 @@ class Transformer:
             if lw.w13 is not None:
                 delta = self.par.moe_ffn(self, lw, h)
                 if delta is None:
-                    delta = self.moe_local(lw, h)
+                    delta = self.moe_local(lw, h, h_mx)
                 if lw.sh_gate_up is not None:
                     delta = (self.par.materialize(delta).float() + self.shared_expert(lw, h).float()).to(torch.bfloat16)
             else:

@@ -254,6 +254,23 @@ def mx_quantize(x: torch.Tensor, src_rows: Optional[torch.Tensor] = None, out_ro
     return MxTensor(q, sf, n, k, sf_layout)
 
 
+def mx_gather_rows(x: MxTensor, src_rows: torch.Tensor, sf_layout: int = 128) -> MxTensor:
+    """Rows of an MXFP8 tensor in the order of ``src_rows`` (int32; negative = padding row, left unwritten on the GPU and zero
+    on the CPU), scales re-laid for ``sf_layout``: the MoE gather when the tokens are already quantised."""
+    n, k = src_rows.numel(), x.k
+    if not x.data.is_cuda:
+        g = torch.zeros(n, k, dtype=torch.float32)
+        ok = src_rows >= 0
+        g[ok] = mxfp8.dequantize(x)[src_rows[ok].long()]
+        return mxfp8.quantize(g, sf_layout=sf_layout)
+    rp = (n + 127) // 128 * 128
+    q = torch.empty(rp, k, dtype=torch.uint8, device=x.data.device)
+    sf = sf_alloc(rp, k, x.data.device, sf_layout, init=False)
+    _native.check(_native.cuda().gb_mx_gather_rows(_p(x.data), _p(x.sf), _p(src_rows), _p(q), _p(sf), _l(n), _i(k),
+                                                   _i(1 if x.sf_layout == 32 else 0), _i(1 if sf_layout == 32 else 0), _s()), "gb_mx_gather_rows")
+    return MxTensor(q, sf, n, k, sf_layout)
+
+
 def softmax_scale_log2(d: int) -> float:
     """``q_scale`` that the attention kernel expects folded into Q: 1/sqrt(d) * log2(e)."""
     return (1.0 / math.sqrt(d)) * math.log2(math.e)

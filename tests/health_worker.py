@@ -39,6 +39,8 @@ def main():
         return 0
     except PeerLost as e:
         print(f"rank {rank} PEERLOST {e.ranks} at step {hb.step}", flush=True)
+        if rank == 0:
+            time.sleep(2.0)      # this rank hosts the store: stay until the other survivors have read the heartbeats too
         return 3
     except RuntimeError as e:
         print(f"rank {rank} FAILED {e}", flush=True)

@@ -63,6 +63,46 @@ def test_qk_norm_rope(d, rope_dim):
     assert torch.equal(vc[slots.long()], vr)
 
 
+@pytest.mark.parametrize("mrope", [False, True])
+def test_qk_norm_rope_head128_table_and_mrope(mrope):
+    """The vectorised head_dim-128 kernel with the (cos, sin) table, and with per-section positions."""
+    torch.manual_seed(22)
+    t, hq, hkv, d = 37, 4, 2, 128
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+    pos = torch.randint(0, 3000, (t,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(64, device="cuda")[:t].to(torch.int32)
+    slots[3] = -1
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    kc = torch.zeros(64, hkv, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros(64, hkv, d, device="cuda", dtype=torch.bfloat16)
+    tab = ew.rope_table(3000, d, 1e6, "cuda")
+    p3 = torch.stack([pos, pos + 5, pos + 9]).contiguous().clamp_max(2999) if mrope else None
+    sec = [24, 20, 20] if mrope else None
+    q = ew.qk_norm_rope(qkv, pos, slots, qw, kw, kc, vc, hq, hkv, d, 1e6, 1e-6, 0.25, None, table=tab, positions3=p3, sections=sec)
+    qr, kr, vr = ew.qk_norm_rope_ref(qkv, pos, qw, kw, hq, hkv, d, 1e6, 1e-6, 0.25, None, p3, sec)
+    live = slots >= 0
+    assert _rel(q, qr) < 6e-3
+    assert _rel(kc[slots[live].long()], kr[live]) < 6e-3
+    assert torch.equal(vc[slots[live].long()], vr[live])
+
+
+@pytest.mark.parametrize("lay_in,lay_out", [(128, 128), (128, 32), (32, 32)])
+def test_mx_gather_rows_equals_quantising_gathered_rows(lay_in, lay_out):
+    torch.manual_seed(23)
+    t, k = 50, 512
+    x = (torch.randn(t, k, device="cuda") * torch.rand(t, 1, device="cuda") * 8).bfloat16()
+    src = torch.randint(-1, t, (300,), device="cuda", dtype=torch.int32)
+    xq = ew.mx_quantize(x, sf_layout=lay_in)
+    got = ew.mx_gather_rows(xq, src, sf_layout=lay_out)
+    want = ew.mx_quantize(x, src, sf_layout=lay_out)
+    ok = (src >= 0).cpu()
+    assert torch.equal(got.data[:300].cpu()[ok], want.data[:300].cpu()[ok])
+    sg = mxfp8.unpack_sf_atoms(got.sf, 300, k // 32, lay_out).cpu()[ok]
+    sw = mxfp8.unpack_sf_atoms(want.sf, 300, k // 32, lay_out).cpu()[ok]
+    assert torch.equal(sg, sw)
+
+
 def test_silu_mul_and_quant_gather():
     torch.manual_seed(3)
     gu = torch.randn(50, 512, device="cuda").bfloat16()
