@@ -79,11 +79,11 @@ struct GemmArgs {
   // ---- weight layout: 0 = row-major [rows, k]; 1 = tiled [rows/128][k-blocks][128 rows][128 bytes], every 16 KB operand
   // tile of the main loop is one contiguous block of memory (one DRAM burst sequence instead of 128 strided lines)
   int w_tiled;
-  int debug;     // experiment knob (GB_GEMM_DEBUG): bit 0 = issue no MMA (pure load stream), bit 1 = load no weight tiles, bit 4 = load nothing (pure MMA issue)
+  int debug;     // experiment knob (GB_GEMM_DEBUG): bit 0 = issue no MMA (pure load stream), bit 1 = load no weight tiles
 };
 
 // k-steps whose MXFP8 scale atoms are fetched by one bulk copy (2 for the widest tile, whose stages are short of room)
-__host__ __device__ constexpr int sf_group(int tn) { return tn >= 256 ? 2 : 4; }
+__host__ __device__ constexpr int sf_group(int tn) { return tn >= 256 ? 2 : tn >= 128 ? 4 : 1; }
 
 struct Tile { int w_row0; int w_row1; int x_row0; int valid; int n0; int out_row0; int ks; int tile_id; };
 
@@ -222,24 +222,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int dbg_i = 0;
       for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
         const int kb0 = t.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        // Per tile: the row coordinate of the (tiled) weight blocks and the start of each scale-atom stream.  The atoms of one
+        // 128-row block are contiguous over k, so a stream is checked against its buffer's extent once, for the whole k range;
+        // a bad one is reported and replaced by the buffer's first atoms.
+        const int wy0 = ((t.w_row0 >> 7) * num_kb) << 7, wy1 = ((t.w_row1 >> 7) * num_kb) << 7;
+        const uint8_t* sfa0 = nullptr; const uint8_t* sfa1 = nullptr; const uint8_t* sfbp[SFB_ATOMS];
+        if (MODE == 1) {
+          const size_t row_bytes = (size_t)num_kb * 512;
+          auto stream_of = [&](const uint8_t* base, size_t extent, size_t atom_row, int where) -> const uint8_t* {
+            const size_t off = atom_row * row_bytes;
+            if (extent != 0 && off + row_bytes > extent) { report_status(args.status, ST_BAD_ARG, where, (int)atom_row, (int)(extent >> 9), ti); return base; }
+            return base + off;
+          };
+          sfa0 = stream_of(args.sfa, args.sfa_bytes, (size_t)(t.w_row0 >> 7), 120);
+          if (DUAL) sfa1 = stream_of(args.sfa, args.sfa_bytes, (size_t)(t.w_row1 >> 7), 121);
+          if (TN == 32) {
+            // narrow tiles use one atom per 32 rows (bytes 0..3 of each 16-byte lane row), so that the tile's
+            // scales always land in column 0 of their TMEM block whatever 32-row boundary the tile starts on
+            sfbp[0] = stream_of(args.sfb, args.sfb_bytes, (size_t)(t.x_row0 >> 5), 122);
+          } else {
+#pragma unroll
+            for (int i = 0; i < SFB_ATOMS; ++i) {
+              // a 256-token tile whose valid rows end in its first half has no second atom to fetch (it may lie past the
+              // end of the scale buffer): the first one is fetched again so that the byte count of a stage stays fixed
+              const int ai = (i * 128 < t.valid) ? i : 0;
+              sfbp[i] = stream_of(args.sfb, args.sfb_bytes, (size_t)((t.x_row0 >> 7) + ai), 123);
+            }
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 100, s)) { ok = false; break; }
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-          if (args.debug & 16) {           // no loads at all: the MMA thread runs on whatever shared memory holds
-            mbar_arrive(&full_bar[s]);
-            if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[dbg_i++] = clock64();
-            if (++s == S) { s = 0; ph ^= 1; }
-            continue;
-          }
           const bool load_w = !(args.debug & 2);
-          const int kbi = kb - kb0;
-          const int glen = (MODE == 1 && kbi % SFG == 0) ? min(SFG, kb1 - kb) : 0;     // scale group starting at this k-step
+          // length of the scale group that starts at this k-step (0 = none starts here)
+          const int glen = (MODE != 1) ? 0 : (SFG == 1) ? 1 : ((kb - kb0) % SFG == 0) ? min(SFG, kb1 - kb) : 0;
           mbar_expect_tx(&full_bar[s], (load_w ? NA * A_BYTES : 0) + B_BYTES + (NA + SFB_ATOMS) * 512 * glen);
           const int kx = kb * KB_ELEMS;
           if (!load_w) {
           } else if (args.w_tiled) {
-            tma_load_2d(st, &tmW, &full_bar[s], 0, ((t.w_row0 >> 7) * num_kb + kb) << 7);
-            if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], 0, ((t.w_row1 >> 7) * num_kb + kb) << 7);
+            tma_load_2d(st, &tmW, &full_bar[s], 0, wy0 + (kb << 7));
+            if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], 0, wy1 + (kb << 7));
           } else {
             tma_load_2d(st, &tmW, &full_bar[s], kx, t.w_row0);
             if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], kx, t.w_row1);
@@ -247,28 +269,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tma_load_2d(st + NA * A_BYTES, &tmX, &full_bar[s], kx, t.x_row0);
           if (MODE == 1 && glen > 0) {
             uint8_t* sf = st + NA * A_BYTES + B_BYTES;
-            const size_t kbs = (size_t)num_kb;
             const uint32_t gbytes = (uint32_t)glen * 512;
-            // scale atoms: offsets are checked against the buffers' extents; a bad one is reported and replaced by the first atoms
-            auto atoms = [&](const uint8_t* base, size_t extent, size_t off, int where) -> const uint8_t* {
-              if (extent != 0 && off + gbytes > extent) { report_status(args.status, ST_BAD_ARG, where, (int)(off >> 9), (int)(extent >> 9), ti); return base; }
-              return base + off;
-            };
-            bulk_load(sf, atoms(args.sfa, args.sfa_bytes, ((size_t)(t.w_row0 >> 7) * kbs + kb) * 512, 120), gbytes, &full_bar[s]);
-            if (DUAL) bulk_load(sf + SFG * 512, atoms(args.sfa, args.sfa_bytes, ((size_t)(t.w_row1 >> 7) * kbs + kb) * 512, 121), gbytes, &full_bar[s]);
-            if (TN == 32) {
-              // narrow tiles use one atom per 32 rows (bytes 0..3 of each 16-byte lane row), so that the tile's
-              // scales always land in column 0 of their TMEM block whatever 32-row boundary the tile starts on
-              bulk_load(sf + NA * SFG * 512, atoms(args.sfb, args.sfb_bytes, ((size_t)(t.x_row0 >> 5) * kbs + kb) * 512, 122), gbytes, &full_bar[s]);
-            } else {
+            const size_t koff = (size_t)kb * 512;
+            bulk_load(sf, sfa0 + koff, gbytes, &full_bar[s]);
+            if (DUAL) bulk_load(sf + SFG * 512, sfa1 + koff, gbytes, &full_bar[s]);
 #pragma unroll
-              for (int i = 0; i < SFB_ATOMS; ++i) {
-                // a 256-token tile whose valid rows end in its first half has no second atom to fetch (it may lie past the
-                // end of the scale buffer): the first one is fetched again so that the byte count of the stage stays fixed
-                const int ai = (i * 128 < t.valid) ? i : 0;
-                bulk_load(sf + (NA + i) * SFG * 512, atoms(args.sfb, args.sfb_bytes, ((size_t)((t.x_row0 >> 7) + ai) * kbs + kb) * 512, 123), gbytes, &full_bar[s]);
-              }
-            }
+            for (int i = 0; i < SFB_ATOMS; ++i) bulk_load(sf + (NA + i) * SFG * 512, sfbp[i] + koff, gbytes, &full_bar[s]);
           }
           if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[dbg_i++] = clock64();
           if (++s == S) { s = 0; ph ^= 1; }
@@ -301,8 +307,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (gj == 0) {
               // the scale atoms of the next SFG k-steps came with this stage: copy them all into their TMEM columns
               const uint32_t sf = st + NA * A_BYTES + B_BYTES;
-              const int glen = min(SFG, kb1 - kb);
-              for (int g = 0; g < glen; ++g) {
+              const int glen = (SFG == 1) ? 1 : min(SFG, kb1 - kb);
+#pragma unroll
+              for (int g = 0; g < SFG; ++g) {
+                if (g >= glen) break;
                 tc_cp_32x128b_warpx4(tmem_sf + g * 4, make_sdesc_noswizzle(sf + g * 512, 0, 128));
                 if (DUAL) tc_cp_32x128b_warpx4(tmem_sf + (SFG + g) * 4, make_sdesc_noswizzle(sf + (SFG + g) * 512, 0, 128));
 #pragma unroll

@@ -229,12 +229,13 @@ def test_router_logits_small_batch(t, e, k):
 
 
 @pytest.mark.parametrize("t,local", [(1, None), (64, None), (256, None), (64, (32, 16)), (200, (0, 64))])
-def test_route_plan_single_kernel(t, local):
+def test_route_plan_single_kernel(t, local, monkeypatch):
     """Routing + plan in one launch equals the two separate ops."""
     torch.manual_seed(23)
     e, k, align = 128, 8, 32
     logits = torch.randn(t, e, device="cuda")
     n_plan = local[1] if local else e
+    monkeypatch.setattr(moe, "FUSED_ROUTE_PAIRS", 2048)      # force the fused kernel also above its default threshold
     ids, w, pl = moe.route_plan(logits, k, n_plan, align, local_range=local)
     ids2, w2 = moe.route(logits, k, local_range=local)
     pl2 = moe.plan(ids2, n_plan, align)
