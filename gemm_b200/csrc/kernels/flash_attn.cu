@@ -7,12 +7,13 @@
 // small, the KV range split over several CTAs whose partial (O, log-sum-exp) results a second kernel
 // merges (the same merge rule serves context parallelism across GPUs).
 //
-// Pipeline per 128-position KV block j (S, P, O live in TMEM; P overwrites S in place as packed bf16):
-//   TMA warp   : K_j, V_j pages -> 128B-swizzled smem (2 stages each), page ids from the block table
-//   MMA thread : S_{j+1} = Q K_{j+1}^T   (issued before waiting for softmax j, so it overlaps)
-//                O     += P_j V_j        (A operand = P from TMEM, B = V MN-major from smem)
-//   softmax    : 128 threads, one per row: S row -> running max / sum, P = exp2(S - m) -> TMEM,
-//                rescale O in TMEM when the row max moved, final O / l -> global
+// Pipeline per 128-position KV block j (S, P, O live in TMEM; P overwrites S in place as packed bf16).  A CTA uses half of
+// TMEM and 96 KB of shared memory, so two CTAs share an SM and one's tensor work runs under the other's softmax:
+//   TMA warp   : K_j, V_j pages -> 128B-swizzled smem (one block each; K_{j+1} lands while softmax j runs), page ids from
+//                the block table
+//   MMA thread : S_j = Q K_j^T, then O += P_j V_j  (A operand = P from TMEM, B = V MN-major from smem)
+//   softmax    : 128 threads, one per row: S row -> reference max / sum, P = exp2(S - m) -> TMEM; O is rescaled only when
+//                a row's maximum has grown by more than 2^8; final O / l -> global
 // Q arrives pre-multiplied by softmax_scale * log2(e) (done by the RoPE kernel) so exp2 is exact base.
 //
 // Replaces in the reference: fa2_attn_f (cuda/llm/fa2_kernels.cu:55), batch_attn_causal_f32
@@ -52,42 +53,45 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-__global__ void __launch_bounds__(kFaThreads, 1)
+constexpr int kFaSmem = 32768 * 3 + 256 + 1024;
+
+__global__ void __launch_bounds__(kFaThreads, 2)
 flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FaArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;                       // 2 x [128 rows x 128 B]  (d halves)
-  uint8_t* sK = smem + 32768;               // 2 stages x 32 KB
-  uint8_t* sV = smem + 32768 * 3;           // 2 stages x 32 KB
-  uint64_t* bars = (uint64_t*)(smem + 32768 * 5);
-  uint64_t* q_full = bars;                  // 1
-  uint64_t* k_full = bars + 1;              // 2
-  uint64_t* k_empty = bars + 3;             // 2
-  uint64_t* v_full = bars + 5;              // 2
-  uint64_t* v_empty = bars + 7;             // 2
-  uint64_t* s_full = bars + 9;              // 2
-  uint64_t* p_ready = bars + 11;            // 1 (128 arrivals)
-  uint64_t* o_ready = bars + 12;            // 1
-  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
+  uint8_t* sK = smem + 32768;               // one block: 2 x [128 positions x 128 B]
+  uint8_t* sV = smem + 32768 * 2;           // one block
+  uint64_t* bars = (uint64_t*)(smem + 32768 * 3);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 2;
+  uint64_t* v_full = bars + 3;
+  uint64_t* v_empty = bars + 4;
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;             // 128 arrivals
+  uint64_t* o_ready = bars + 7;
+  uint32_t* tmem_slot = (uint32_t*)(bars + 8);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Prologue that touches no global memory: it overlaps the tail of the previous kernel of the stream.
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); mbar_init(&s_full[i], 1); }
-    mbar_init(p_ready, 128); mbar_init(o_ready, 1);
+    mbar_init(q_full, 1); mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    mbar_init(s_full, 1); mbar_init(p_ready, 128); mbar_init(o_ready, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+  // Half of TMEM: S / P (128 columns, P overwrites S in place) and O (128 columns).  Two CTAs share an SM, so one CTA's MMAs
+  // run under the other's softmax; inside a CTA the block loop is a plain chain S -> softmax -> P V.
+  if (warp == 1) { tmem_alloc(tmem_slot, 256); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
+  const uint32_t tmem_o = tmem_base + 128;
   pdl_wait();
   pdl_trigger();
 
@@ -118,7 +122,6 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     n_blk = 0;
   }
 
-
   if (warp == 0) {
     if (lane == 0 && n_blk > 0) {
       // Q tile: box (64 d, G heads, tpt tokens), two d-halves
@@ -131,25 +134,26 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int last_page = (kv_len + a.page_size - 1) / a.page_size - 1;
       bool ok = true;
       for (int j = 0; j < n_blk && ok; ++j) {
-        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        const uint32_t ph = j & 1;
         const int blk = blk_lo + j;
         // Pages past the end of the sequence are replaced by its last page: the tile is always filled with
         // finite cache contents (their scores are masked, and 0 * finite stays 0 in P V).
-        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, a.status, 400, j)) { ok = false; break; }
-        mbar_expect_tx(&k_full[s], 32768u);
+        // K_j may land as soon as S_{j-1} has been computed, V_j as soon as P_{j-1} V_{j-1} has: both long before they are needed.
+        if (!mbar_wait(k_empty, ph ^ 1, abort_flag, a.status, 400, j)) { ok = false; break; }
+        mbar_expect_tx(k_full, 32768u);
         for (int p = 0; p < ppb; ++p) {
           const int page = bt[min(blk * ppb + p, last_page)];
-          uint8_t* dst = sK + s * 32768 + p * page_bytes;
-          tma_load_3d(dst, &tmK, &k_full[s], 0, kvh, page * a.page_size);
-          tma_load_3d(dst + 16384, &tmK, &k_full[s], 64, kvh, page * a.page_size);
+          uint8_t* dst = sK + p * page_bytes;
+          tma_load_3d(dst, &tmK, k_full, 0, kvh, page * a.page_size);
+          tma_load_3d(dst + 16384, &tmK, k_full, 64, kvh, page * a.page_size);
         }
-        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, a.status, 401, j)) { ok = false; break; }
-        mbar_expect_tx(&v_full[s], 32768u);
+        if (!mbar_wait(v_empty, ph ^ 1, abort_flag, a.status, 401, j)) { ok = false; break; }
+        mbar_expect_tx(v_full, 32768u);
         for (int p = 0; p < ppb; ++p) {
           const int page = bt[min(blk * ppb + p, last_page)];
-          uint8_t* dst = sV + s * 32768 + p * page_bytes;
-          tma_load_3d(dst, &tmV, &v_full[s], 0, kvh, page * a.page_size);
-          tma_load_3d(dst + 16384, &tmV, &v_full[s], 64, kvh, page * a.page_size);
+          uint8_t* dst = sV + p * page_bytes;
+          tma_load_3d(dst, &tmV, v_full, 0, kvh, page * a.page_size);
+          tma_load_3d(dst + 16384, &tmV, v_full, 64, kvh, page * a.page_size);
         }
       }
     }
@@ -157,37 +161,29 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (lane == 0 && n_blk > 0) {
       constexpr uint32_t idesc_s = make_idesc(128, 128, 1, 1, 0, 0);
       constexpr uint32_t idesc_o = make_idesc(128, 128, 1, 1, 0, 1);     // B (= V) is MN-major
-      const uint32_t q_addr = smem_u32(sQ);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
       bool ok = mbar_wait(q_full, 0, abort_flag, a.status, 500);
-      auto issue_s = [&](int j) -> bool {
-        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[s], ph, abort_flag, a.status, 501, j)) return false;
+      for (int j = 0; j < n_blk && ok; ++j) {
+        const uint32_t ph = j & 1;
+        // S_j = Q K_j^T.  The tensor pipe runs this thread's MMAs in order, so S_j overwrites P_{j-1} only after
+        // P_{j-1} V_{j-1} has read it, and a completed S_j implies that O holds every earlier product.
+        if (!mbar_wait(k_full, ph, abort_flag, a.status, 501, j)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sK + s * 32768);
-        const uint32_t d = tmem_base + s * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-          mma_f16_ss(d, make_sdesc_sw128(q_addr + off), make_sdesc_sw128(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
+          mma_f16_ss(tmem_base, make_sdesc_sw128(q_addr + off), make_sdesc_sw128(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
         }
-        tc_commit(&s_full[s]);
-        tc_commit(&k_empty[s]);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_blk && ok; ++j) {
-        if (j + 1 < n_blk) { if (!issue_s(j + 1)) { ok = false; break; } }
-        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(p_ready, j & 1, abort_flag, a.status, 502, j)) { ok = false; break; }
-        if (!mbar_wait(&v_full[s], ph, abort_flag, a.status, 503, j)) { ok = false; break; }
+        tc_commit(s_full);
+        tc_commit(k_empty);
+        if (!mbar_wait(p_ready, ph, abort_flag, a.status, 502, j)) { ok = false; break; }
+        if (!mbar_wait(v_full, ph, abort_flag, a.status, 503, j)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t v_addr = smem_u32(sV + s * 32768);
-        const uint32_t p_t = tmem_base + s * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          mma_f16_ts(tmem_o, p_t + ks * 8, make_sdesc_sw128_mn(v_addr + ks * 2048, 16384), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
-        tc_commit(o_ready);
-        tc_commit(&v_empty[s]);
+          mma_f16_ts(tmem_o, tmem_base + ks * 8, make_sdesc_sw128_mn(v_addr + ks * 2048, 16384), idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(v_empty);
+        if (j == n_blk - 1) tc_commit(o_ready);
       }
     }
   } else {
@@ -198,64 +194,78 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const bool row_valid = (t_local < n_tok) && (r < tpt * G) && !bad_item;
     const int qpos = pos0 + min(t_local, n_tok - 1);
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const uint32_t s_t = tmem_base + lane_off;
+    // m is the maximum the exponents refer to; it follows the true running maximum only when that has moved by more
+    // than 2^kTau, so that O and l are rarely rescaled (P stays below 2^kTau, harmless in bf16 with fp32 sums).
+    constexpr float kTau = 8.0f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blk && ok; ++j) {
-      const int s = j & 1;
-      if (!mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, a.status, 600, j)) { ok = false; break; }
+      if (!mbar_wait(s_full, j & 1, abort_flag, a.status, 600, j)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_t = tmem_base + s * 128 + lane_off;
-      float sv[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_x32(s_t + c * 32, reinterpret_cast<uint32_t*>(sv) + c * 32);
-      tc_wait_ld();
       const int kv0 = (blk_lo + j) * kBN;
       int hi = kv_len - 1;
       if (a.causal) hi = min(hi, qpos);
       int lo = 0;
       if (a.window > 0) lo = max(0, qpos - a.window + 1);
-      if (kv0 + kBN - 1 > hi || kv0 < lo) {
+      const bool edge = (kv0 + kBN - 1 > hi || kv0 < lo);
+      // pass 1: row maximum (the scores are read again in pass 2 instead of being kept in 128 registers)
+      float mx = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) { const int kp = kv0 + c; if (kp > hi || kp < lo) sv[c] = -INFINITY; }
+      for (int c = 0; c < 4; ++c) {
+        float sv[32];
+        tmem_ld_x32(s_t + c * 32, reinterpret_cast<uint32_t*>(sv));
+        tc_wait_ld();
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { const int kp = kv0 + c * 32 + i; if (kp > hi || kp < lo) sv[i] = -INFINITY; }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, sv[i]);
       }
-      float mx = sv[0];
+      float alpha = 1.0f;
+      const bool grow = mx > m + kTau || (m == -INFINITY && mx > -INFINITY);
+      if (grow) { alpha = fast_exp2(m - mx); m = mx; }          // m = -inf -> alpha 0 (l and O are 0 then anyway)
+      const float m_use = (m == -INFINITY) ? 0.f : m;
+      // O holds all products up to block j - 1 (see the MMA thread): rescale it now if some row of this warp moved its reference
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll
-      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sv[c]);
-      const float m_new = fmaxf(m, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = fast_exp2(m - m_use);      // m = -inf -> 0
-      float rs = 0.f;
-      uint32_t pk[64];
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld_x32(tmem_o + lane_off + c * 32, o);
+          tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const float p0 = fast_exp2(sv[2 * c] - m_use), p1 = fast_exp2(sv[2 * c + 1] - m_use);
-        rs += p0 + p1;
-        pk[c] = pack_bf16x2(p0, p1);
-      }
-      l = l * alpha + rs;
-      m = m_new;
-      tmem_st_x32(s_t, pk);
-      tmem_st_x32(s_t + 32, pk + 32);
-      if (j > 0) {
-        if (!mbar_wait(o_ready, (j - 1) & 1, abort_flag, a.status, 601, j)) { ok = false; break; }
-        tc_fence_after();
-        if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld_x32(tmem_o + lane_off + c * 32, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_x32(tmem_o + lane_off + c * 32, o);
-          }
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_x32(tmem_o + lane_off + c * 32, o);
         }
       }
+      // pass 2: P = exp2(S - m) as packed bf16 over the first half of the S columns (chunk c lands on columns that
+      // chunks <= c have already been read from)
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float sv[32];
+        tmem_ld_x32(s_t + c * 32, reinterpret_cast<uint32_t*>(sv));
+        tc_wait_ld();
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { const int kp = kv0 + c * 32 + i; if (kp > hi || kp < lo) sv[i] = -INFINITY; }
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = fast_exp2(sv[2 * i] - m_use), p1 = fast_exp2(sv[2 * i + 1] - m_use);
+          rs += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_x16(s_t + c * 16, pk);
+      }
+      l = l * alpha + rs;
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(p_ready);
     }
-    if (ok && n_blk > 0) ok = mbar_wait(o_ready, (n_blk - 1) & 1, abort_flag, a.status, 602);
+    if (ok && n_blk > 0) ok = mbar_wait(o_ready, 0, abort_flag, a.status, 602);
     if (ok) {
       tc_fence_after();
       const int tok = q_begin + q_tok0 + t_local;
@@ -301,7 +311,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 256); }
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -660,7 +670,7 @@ GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache
   a.work = work; a.cu_q = cu_q; a.kv_len = kv_len; a.block_table = block_table; a.max_pages = max_pages; a.page_size = page_size;
   a.hq = hq; a.hkv = hkv; a.num_splits = num_splits; a.causal = causal; a.window = window; a.out = (__nv_bfloat16*)out;
   a.part_o = part_o; a.part_lse = part_lse; a.total_tokens = total_tokens; a.status = (KernelStatus*)status;
-  const int smem = 32768 * 5 + 256 + 1024;
+  const int smem = kFaSmem;
   static bool attr_set = false;
   if (!attr_set) {
     GB_CUDA_OK(cudaFuncSetAttribute(flash_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

@@ -92,9 +92,15 @@ def _moe(args, t: int, name: str):
     hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device="cuda")
     hsf = ew.sf_alloc(pl.capacity, inter, "cuda", tn, init=False)
 
+    gu = torch.empty(pl.capacity, 2 * inter, dtype=torch.bfloat16, device="cuda") if tn == 128 else None
+
     def gate_up():
-        gemm.grouped_linear(xq.data, d1.view(e, 2 * inter, h), pl.seg_start, pl.seg_count, tn, out=hq, dual=True, sfa=w1.sf, sfb=xq.sf,
-                            quant_out=True, out_sf=hsf, w_tiled=True)
+        if tn == 32:        # decode: SiLU(gate) * up and the re-quantisation run in the GEMM epilogue
+            gemm.grouped_linear(xq.data, d1.view(e, 2 * inter, h), pl.seg_start, pl.seg_count, tn, out=hq, dual=True, sfa=w1.sf, sfb=xq.sf,
+                                quant_out=True, out_sf=hsf, w_tiled=True)
+        else:               # prefill: plain GEMM over the stacked rows (256-token tiles) + one fused activation / quantise pass
+            gemm.grouped_linear(xq.data, d1.view(e, 2 * inter, h), pl.seg_start, pl.seg_count, tn, out=gu, sfa=w1.sf, sfb=xq.sf, w_tiled=True)
+            ew.silu_mul_quant(gu, hq, hsf, pl.row_token, sf_layout=tn)
 
     def down():
         gemm.grouped_linear(hq, d2.view(e, h, inter), pl.seg_start, pl.seg_count, tn, sfa=w2.sf, sfb=hsf, w_tiled=True)
