@@ -416,17 +416,20 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const int* __re
     load8(gate_up + r * ld + vi * 8, g);
     load8(gate_up + r * ld + inter + vi * 8, u);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { y[j] = g[j] / (1.0f + __expf(-g[j])) * u[j]; amax = fmaxf(amax, fabsf(y[j])); }
+    for (int j = 0; j < 8; ++j) { y[j] = __fdividef(g[j], 1.0f + __expf(-g[j])) * u[j]; amax = fmaxf(amax, fabsf(y[j])); }
   }
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   if (!live) return;
   const int e = e8m0_amax(amax);
   const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
-  uint8_t q[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(y[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
-  *reinterpret_cast<uint2*>(out_q + r * inter + vi * 8) = *reinterpret_cast<uint2*>(q);
+  // two values per conversion instruction
+  uint2 q;
+  q.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[0] * inv, y[1] * inv), __NV_SATFINITE, __NV_E4M3) |
+        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[2] * inv, y[3] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+  q.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[4] * inv, y[5] * inv), __NV_SATFINITE, __NV_E4M3) |
+        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[6] * inv, y[7] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+  *reinterpret_cast<uint2*>(out_q + r * inter + vi * 8) = q;
   if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, inter >> 7, sf32)] = (uint8_t)e;
 }
 

@@ -67,6 +67,7 @@ struct GemmArgs {
   // fp32 partial in sk_ws; the warp that arrives last at the tile's semaphore sums the partials in split order
   // (deterministic) and runs the normal epilogue.
   int splits;
+  long partial_stride;             // > 0: no in-kernel reduction, split ks stores its fp32 partial at out + ks * partial_stride (elements)
   float* sk_ws;                    // [tiles][splits][NA * TN][128] fp32
   unsigned* sk_ctr;                // [tiles][4] self-resetting arrival counters (one per epilogue warp)
   // ---- arg-max epilogue: instead of storing the result, every epilogue warp writes the maximum of its 32 output
@@ -354,7 +355,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     bool ok = true;
     int dbg_t = 0;
     const bool simple_store = !QUANT_OUT && args.amax_val == nullptr && args.row_map == nullptr && args.peer_bcast == 0 &&
-                              args.row_scale == nullptr && args.splits <= 1;
+                              args.row_scale == nullptr && (args.splits <= 1 || args.partial_stride > 0);
     for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
       if (!mbar_wait(&accf_bar[acc], acc_ph, abort_flag, args.status, 300, acc)) { ok = false; break; }
       if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4096 + dbg_t] = clock64();
@@ -362,7 +363,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const uint32_t tacc = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
       const int n = t.n0 + row;
       const bool n_ok = n < args.n_out;
-      const float bias = (args.bias != nullptr && n_ok) ? args.bias[n] : 0.0f;
+      const float bias = (args.bias != nullptr && n_ok && (args.partial_stride == 0 || t.ks == 0)) ? args.bias[n] : 0.0f;
       // Everything after the accumulators are in registers: activation, bias, then one of the store forms.
       auto finish_chunk = [&](int c, const uint32_t* r0, const uint32_t* r1) {
 #pragma unroll
@@ -429,7 +430,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           }
         }
       };
-      if (args.splits > 1) {
+      if (args.splits > 1 && args.partial_stride == 0) {
         // ---- split-K: park the partial, the last warp to arrive reduces
         float* ws = args.sk_ws + ((size_t)t.tile_id * args.splits) * (size_t)(NA * TN * 128);
         float* mine = ws + (size_t)t.ks * (NA * TN * 128);
@@ -486,7 +487,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         // Common case (plain row-major bf16 / f32 result): every decision is made once per tile, the inner loop is
         // convert + store.  The tile's last element is checked against the buffer's extent.
         const size_t esz = args.out_f32 ? 4 : 2;
-        const size_t last = ((size_t)(t.x_row0 + t.valid - 1) * args.ldo + n) * esz;
+        const size_t part_off = (size_t)t.ks * (size_t)args.partial_stride;     // split-K partials: one output slab per split
+        const size_t last = (part_off + (size_t)(t.x_row0 + t.valid - 1) * args.ldo + n) * esz;
         bool store_ok = n_ok;
         if (store_ok && args.out_bytes != 0 && args.peer_region_rows == 0 && last >= args.out_bytes) {
           report_status(args.status, ST_BAD_ARG, 312, t.x_row0 + t.valid - 1, n, ti);
@@ -500,8 +502,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           obase = args.peer_out[src];
           orow0 = (size_t)args.peer_rank * args.peer_region_rows + (size_t)(t.x_row0 - src * args.peer_region_rows);
         }
-        __nv_bfloat16* o16 = (__nv_bfloat16*)obase + orow0 * args.ldo + n;
-        float* o32 = (float*)obase + orow0 * args.ldo + n;
+        __nv_bfloat16* o16 = (__nv_bfloat16*)obase + part_off + orow0 * args.ldo + n;
+        float* o32 = (float*)obase + part_off + orow0 * args.ldo + n;
         if constexpr (NACC == 1 && !DUAL) {
           if (!args.out_f32) {
             // One accumulator buffer (the widest tile with its scale columns fills TMEM): pull the whole row into registers
@@ -509,12 +511,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             // next tile's MMAs.
             uint32_t pk[TN / 2];
 #pragma unroll
-            for (int c = 0; c < TN; c += 16) {
-              uint32_t r[16];
-              tmem_ld_x16(tacc + c, r);
+            for (int c = 0; c < TN; c += 64) {
+              uint32_t r[64];                      // two loads in flight per wait: the readout is latency-bound
+              tmem_ld_x32(tacc + c, r);
+              tmem_ld_x32(tacc + c + 32, r + 32);
               tc_wait_ld();
 #pragma unroll
-              for (int j = 0; j < 8; ++j) pk[c / 2 + j] = pack_bf16x2(__uint_as_float(r[2 * j]) + bias, __uint_as_float(r[2 * j + 1]) + bias);
+              for (int j = 0; j < 32; ++j) pk[c / 2 + j] = pack_bf16x2(__uint_as_float(r[2 * j]) + bias, __uint_as_float(r[2 * j + 1]) + bias);
             }
             tc_fence_before();
             __syncwarp();
@@ -660,6 +663,7 @@ struct GemmExtras {
   int peer_bcast;
   int epoch_self_tick;
   size_t sfa_bytes, sfb_bytes, out_bytes, out_sf_bytes;
+  long partial_stride;       // > 0 with splits > 1: every K split stores its fp32 partial into its own slab of `out` (the consumer sums them)
 };
 
 // Flags of gb_gemm.
@@ -725,7 +729,14 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
     a.peer_region_rows = ex->peer_region_rows; a.peer_rank = ex->peer_rank; a.signal_n = ex->signal_n; a.done_ctr = ex->done_ctr;
     a.amax_val = ex->amax_val; a.amax_idx = ex->amax_idx; a.peer_bcast = ex->peer_bcast; a.epoch_self_tick = ex->epoch_self_tick;
     a.sfa_bytes = ex->sfa_bytes; a.sfb_bytes = ex->sfb_bytes; a.out_bytes = ex->out_bytes; a.out_sf_bytes = ex->out_sf_bytes;
-    if (ex->splits > 1 && num_groups == 0) {
+    if (ex->splits > 1 && num_groups == 0 && ex->partial_stride > 0) {
+      if (!(flags & GEMM_OUT_F32) || dual || qo) return fail("gemm: split-K partials need a plain fp32 output%s");
+      const int kb_elems = mx ? 128 : 64;
+      const int num_kb = (k + kb_elems - 1) / kb_elems;
+      const int kb_per = (num_kb + ex->splits - 1) / ex->splits;
+      if ((num_kb + kb_per - 1) / kb_per != ex->splits) return fail("gemm: split-K partials: a split would be empty%s");
+      a.splits = ex->splits; a.partial_stride = ex->partial_stride;
+    } else if (ex->splits > 1 && num_groups == 0) {
       const int kb_elems = mx ? 128 : 64;
       const int num_kb = (k + kb_elems - 1) / kb_elems;
       int sp = ex->splits < num_kb ? ex->splits : num_kb;

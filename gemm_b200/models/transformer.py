@@ -14,6 +14,7 @@ Layer recipe (reference: common/transformer.h:3550-4174):
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
@@ -118,6 +119,10 @@ class ForwardBatch:
                             is_decode=(b > 0 and all(q == 1 for q in q_lens)))
 
 
+# K-split partial sums for decode-sized row projections (GB_SPLIT_PROJ=0 switches them off)
+SPLIT_PROJ = os.environ.get("GB_SPLIT_PROJ", "1") != "0"
+
+
 class SingleProcess:
     """Parallel context of an unsharded model: every collective is the identity."""
     tp_size = 1
@@ -131,7 +136,7 @@ class SingleProcess:
     def row_linear(self, lw: "LinearWeight", x: torch.Tensor, x_mx=None):
         """Row-parallel projection (o_proj / down_proj).  Returns the residual update: a tensor, or an object that
         ``add_norm`` / ``materialize`` know how to finish (a reduction still in flight)."""
-        return apply_linear(lw, x, x_mx)
+        return apply_linear_split(lw, x, x_mx)
 
     def add_norm(self, delta, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor], **kw):
         """``residual += delta`` (if a residual is given) followed by RMSNorm; see ``ops.elementwise.rmsnorm``."""
@@ -151,6 +156,20 @@ def apply_linear(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTensor] = N
     xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if x.shape[0] <= 32 else 128)
     y = gemm.linear_mx(xm, lw.mx, out_dtype=out_dtype, bias=lw.bias)
     return y
+
+
+def apply_linear_split(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTensor] = None):
+    """``apply_linear`` for a projection whose result goes into the residual stream: a decode-sized MXFP8 projection with few
+    output tiles (o_proj: 16 tiles of 128 rows, 32 k-steps each) is cut along K so that it fills the GPU, and the partial sums
+    are left for the residual add + RMSNorm kernel that follows."""
+    if lw.fmt != "bf16" and SPLIT_PROJ:
+        xm = x_mx if x_mx is not None else (ew.mx_quantize(x, sf_layout=32 if x.shape[0] <= 32 else 128) if x.is_cuda else None)
+        if xm is not None and xm.data.is_cuda:
+            sp = gemm.pick_partials(lw.mx.rows, xm.rows, lw.mx.k, True)
+            if sp > 1:
+                return gemm.linear_mx_partials(xm, lw.mx, sp, bias=lw.bias)
+            return gemm.linear_mx(xm, lw.mx, bias=lw.bias)
+    return apply_linear(lw, x, x_mx)
 
 
 def expert_gate_up_mx(x_q: torch.Tensor, x_sf: torch.Tensor, w13: LinearWeight, n_w_groups: int, seg_start: torch.Tensor,

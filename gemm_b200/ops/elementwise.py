@@ -63,6 +63,22 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
     feeds a block-scaled GEMM.
     """
     pend = None
+    if hasattr(x, "buf") and hasattr(x, "materialize"):          # ops.gemm.PendingPartials: K-split partial sums, summed by this kernel
+        if residual is None or not x.buf.is_cuda or residual.stride(0) != x.hidden:
+            x = x.materialize()
+        else:
+            rows, hidden = x.rows, x.hidden
+            out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=residual.device) if want_bf16 else None
+            q = sf = None
+            if quantize:
+                rp = (rows + 127) // 128 * 128
+                q = torch.empty(rp, hidden, dtype=torch.uint8, device=residual.device)
+                sf = sf_alloc(rp, hidden, residual.device, sf_layout, init=False)
+            rc = _native.cuda().gb_rmsnorm_reduce(_p(residual), _p(x.buf), _i(x.n), _l(rows * hidden), _p(w), _p(out), _p(q), _p(sf), _i(rows),
+                                                  _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0), _c(0), _i(0), _c(0),
+                                                  _c(_native.status_ptr()), _s())
+            _native.check(rc, "gb_rmsnorm_reduce")
+            return (out, MxTensor(q, sf, rows, hidden, sf_layout)) if quantize else out
     if hasattr(x, "materialize"):                    # ops.moe.PendingCombine: the MoE combine is done by this kernel
         if residual is None or not x.y.is_cuda:
             x = x.materialize()

@@ -27,7 +27,8 @@ class GemmExtras(ctypes.Structure):
                 ("pad", ctypes.c_int), ("done_ctr", ctypes.c_void_p), ("splits", ctypes.c_int), ("pad2", ctypes.c_int),
                 ("sk_ws", ctypes.c_void_p), ("sk_ctr", ctypes.c_void_p), ("amax_val", ctypes.c_void_p), ("amax_idx", ctypes.c_void_p),
                 ("sk_ws_bytes", ctypes.c_long), ("sk_ctr_count", ctypes.c_long), ("peer_bcast", ctypes.c_int), ("epoch_self_tick", ctypes.c_int),
-                ("sfa_bytes", ctypes.c_size_t), ("sfb_bytes", ctypes.c_size_t), ("out_bytes", ctypes.c_size_t), ("out_sf_bytes", ctypes.c_size_t)]
+                ("sfa_bytes", ctypes.c_size_t), ("sfb_bytes", ctypes.c_size_t), ("out_bytes", ctypes.c_size_t), ("out_sf_bytes", ctypes.c_size_t),
+                ("partial_stride", ctypes.c_long)]
 
 
 _DEBUG = int(os.environ.get("GB_GEMM_DEBUG", "0"))
@@ -205,6 +206,47 @@ def linear_mx(x: MxTensor, w: MxTensor, out: Optional[torch.Tensor] = None, out_
     _launch(w.data, x.data, out, n, k, m, k, k, out.stride(0), flags, tn, x_rows=x.data.shape[0],
             sfa=w.sf, sfb=x.sf, bias=bias, extras=_splitk_extras(n, m, k, tn, True, x.data.device, split_k))
     return out
+
+
+class PendingPartials:
+    """K-split partial sums of a projection, ``buf`` f32 ``[n, rows, hidden]``: the consumer (the next residual add + RMSNorm,
+    ``ops.elementwise.rmsnorm``) sums them in split order, so a decode-sized GEMM can spread over the whole GPU without a
+    reduction pass of its own."""
+
+    def __init__(self, buf: torch.Tensor):
+        self.buf = buf
+        self.n, self.rows, self.hidden = buf.shape
+
+    def materialize(self) -> torch.Tensor:
+        return self.buf.sum(0).to(torch.bfloat16)
+
+
+def pick_partials(n_out: int, m_tok: int, k: int, mx: bool) -> int:
+    """Number of K splits for ``linear_mx_partials``: enough to give every SM a tile, at least 4 k-steps per split."""
+    if m_tok > 64:
+        return 1
+    tiles = (n_out + 127) // 128
+    num_kb = k // (128 if mx else 64)
+    want = min(8, 148 // max(tiles, 1), num_kb // 4)
+    while want > 1:
+        kb_per = -(-num_kb // want)
+        if -(-num_kb // kb_per) == want:
+            return want
+        want -= 1
+    return 1
+
+
+def linear_mx_partials(x: MxTensor, w: MxTensor, splits: int, bias: Optional[torch.Tensor] = None) -> PendingPartials:
+    """``linear_mx`` with the K range cut into ``splits`` CTAs per output tile; every split stores its fp32 partial (the bias
+    goes into split 0).  GPU only."""
+    m, n, k = x.rows, w.rows, w.k
+    out = torch.empty(splits, m, n, dtype=torch.float32, device=x.data.device)
+    tn = 64 if (x.sf_layout == 128 and m <= 64) else x.sf_layout
+    ex = GemmExtras()
+    ex.splits, ex.partial_stride = splits, m * n
+    _launch(w.data, x.data, out, n, k, m, k, k, n, GEMM_MX | GEMM_OUT_F32 | (GEMM_W_TILED if w.tiled else 0), tn, x_rows=x.data.shape[0],
+            sfa=w.sf, sfb=x.sf, bias=bias, extras=ex)
+    return PendingPartials(out)
 
 
 def linear_mx_swiglu_quant(x: MxTensor, w_gate_up: MxTensor, tn: Optional[int] = None) -> MxTensor:

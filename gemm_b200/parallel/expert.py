@@ -150,8 +150,8 @@ class ExpertParallel:
         return x
 
     def row_linear(self, lw, x, x_mx=None):
-        from ..models.transformer import apply_linear
-        return apply_linear(lw, x, x_mx)
+        from ..models.transformer import apply_linear_split
+        return apply_linear_split(lw, x, x_mx)
 
     def add_norm(self, delta, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128):
         if not isinstance(delta, PendingSlots):

@@ -258,3 +258,27 @@ def test_expert_gate_up_prefill_path_matches_fused_epilogue():
         if c:
             assert _rel(a[s:s + c], b[s:s + c]) < 3e-2, f"group {i}"
     _native.assert_status_ok()
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 2048, 4096), (8, 2048, 4096), (33, 256, 1024)])
+def test_linear_mx_partials_feed_the_norm(m, n, k):
+    """K-split partial sums (one fp32 slab per split) summed by the residual add + RMSNorm kernel."""
+    from gemm_b200.ops import elementwise as ew
+    torch.manual_seed(41)
+    x = torch.randn(m, k, device="cuda")
+    w = torch.randn(n, k, device="cuda") * 0.05
+    bias = torch.randn(n, device="cuda")
+    lay = 32 if m <= 32 else 128
+    xq, wq = mxfp8.quantize(x, sf_layout=lay), mxfp8.quantize(w)
+    sp = gemm.pick_partials(n, m, k, True)
+    assert sp > 1
+    pend = gemm.linear_mx_partials(xq, wq, sp, bias=bias)
+    ref = mxfp8.dequantize(xq) @ mxfp8.dequantize(wq).t() + bias
+    _native.assert_status_ok()
+    assert _rel(pend.buf.sum(0), ref) < 2e-3
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    nw = (1 + 0.1 * torch.randn(n, device="cuda")).bfloat16()
+    res2 = res.clone()
+    got = ew.rmsnorm(pend, nw, 1e-6, residual=res)
+    want = ew.rmsnorm(pend.materialize(), nw, 1e-6, residual=res2)
+    assert _rel(got, want) < 1e-2 and _rel(res, res2) < 1e-2
