@@ -6,6 +6,8 @@
   tokenize   print the token ids (and pieces) of a text with the tokenizer stored in a GGUF file
   stage      cut a checkpoint into per-rank blobs in the run-time weight format
   microbench kernel micro-benchmarks (same as ``python -m gemm_b200.utils.microbench``)
+  estimate   roofline estimate of decode / prefill throughput for a model preset (tools/decode_estimate.py of the reference)
+  compare    run the same prompt through the CPU reference path and the GPU kernels and report the agreement token by token
   build      compile the native libraries in-tree
 
 The reference spreads these over separate programs: cpu/llm/test_transformer.c (generate: ``<model> [prompt] [max_gen]
@@ -112,12 +114,70 @@ def cmd_stage(args):
     print(json.dumps({"ranks": max(args.tp, args.ep), "out": args.out}))
 
 
+def cmd_compare(args):
+    """CPU-vs-GPU comparison token by token (cuda/llm/test_cuda_llm.c prints the same: per-token arg-max of both sides and the
+    logit difference), plus the token agreement and edit distance of the two greedy continuations (ref/llm/llm_server.py)."""
+    import os
+    import torch
+    from .models import loader, reference
+    from .models.config import get_config
+    from .models.transformer import ForwardBatch, KvCache, Transformer
+    from .models.weights import synthetic_weights
+    if args.model.startswith("synthetic:"):
+        w_cpu = synthetic_weights(get_config(args.model.split(":", 1)[1]), args.format, device="cpu", seed=args.seed)
+    elif os.path.isdir(args.model):
+        w_cpu = loader.load_safetensors(args.model, args.format, "cpu")
+    else:
+        w_cpu = loader.load_gguf(args.model, args.format, "cpu")
+    cfg = w_cpu.cfg
+    g = torch.Generator().manual_seed(args.seed)
+    prompt = [int(x) for x in args.ids.replace(",", " ").split()] if args.ids else torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist()
+    page = 16
+    n_pages = (len(prompt) + args.steps + page) // page + 1
+    bt = torch.arange(n_pages, dtype=torch.int32).unsqueeze(0)
+    sides = {"cpu": Transformer(w_cpu, KvCache.allocate(cfg, n_pages, page, "cpu"))}
+    if torch.cuda.is_available():
+        sides["gpu"] = Transformer(w_cpu.to("cuda"), KvCache.allocate(cfg, n_pages, page, "cuda"))
+    outs = {}
+    for name, m in sides.items():
+        dev = "cpu" if name == "cpu" else "cuda"
+        toks, rows = list(prompt), []
+        fb = ForwardBatch.build([len(toks)], [0], torch.tensor(toks), bt, page, cfg.n_heads, cfg.n_kv_heads, dev)
+        logits = m.forward(fb).float().cpu()[0]
+        for _ in range(args.steps):
+            rows.append(logits)
+            toks.append(int(logits.argmax()))
+            fb = ForwardBatch.build([1], [len(toks) - 1], torch.tensor(toks[-1:]), bt, page, cfg.n_heads, cfg.n_kv_heads, dev)
+            logits = m.forward(fb).float().cpu()[0]
+        outs[name] = (toks[len(prompt):], rows)
+    report = {"prompt_len": len(prompt), "steps": args.steps, "cpu_tokens": outs["cpu"][0]}
+    if args.oracle:
+        ref = reference.reference_logits(w_cpu, torch.tensor(prompt))[-1]
+        report["cpu_vs_fp32_oracle_rel"] = float((outs["cpu"][1][0] - ref).norm() / ref.norm())
+    if "gpu" in outs:
+        a, b = outs["cpu"], outs["gpu"]
+        rel = [float((x - y).norm() / (x.norm() + 1e-12)) for x, y in zip(a[1], b[1])]
+        agree = sum(int(x == y) for x, y in zip(a[0], b[0]))
+        # Levenshtein distance of the two continuations
+        d = list(range(len(b[0]) + 1))
+        for i, x in enumerate(a[0], 1):
+            prev, d[0] = d[0], i
+            for j, y in enumerate(b[0], 1):
+                prev, d[j] = d[j], min(d[j] + 1, d[j - 1] + 1, prev + (x != y))
+        report.update(gpu_tokens=b[0], logit_rel_per_step=[round(r, 5) for r in rel], token_agreement=agree / max(1, args.steps), edit_distance=d[-1])
+    print(json.dumps(report))
+
+
 def cmd_build(args):
     from . import build
     build.build_all(verbose=True)
 
 
 def main(argv=None):
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] in ("microbench", "estimate"):          # these take their own flags: hand the rest over untouched
+        mod = __import__(f"gemm_b200.utils.{argv[0]}", fromlist=["main"])
+        return mod.main(argv[1:])
     ap = argparse.ArgumentParser(prog="python -m gemm_b200", description=__doc__.split("\n")[0])
     sub = ap.add_subparsers(dest="cmd", required=True)
     g = sub.add_parser("generate", help="complete prompts")
@@ -154,6 +214,18 @@ def main(argv=None):
     mb = sub.add_parser("microbench", help="kernel micro-benchmarks")
     mb.add_argument("rest", nargs=argparse.REMAINDER)
     mb.set_defaults(fn=lambda a: __import__("gemm_b200.utils.microbench", fromlist=["main"]).main(a.rest))
+    es = sub.add_parser("estimate", help="roofline estimate")
+    es.add_argument("rest", nargs=argparse.REMAINDER)
+    es.set_defaults(fn=lambda a: __import__("gemm_b200.utils.estimate", fromlist=["main"]).main(a.rest))
+    cp = sub.add_parser("compare", help="CPU path against GPU kernels, token by token")
+    cp.add_argument("--model", required=True, help="GGUF file, HF safetensors directory, or synthetic:<preset>")
+    cp.add_argument("--format", default="bf16", choices=["bf16", "mxfp8"])
+    cp.add_argument("--ids", default="", help="prompt as token ids (default: random ids)")
+    cp.add_argument("--prompt-len", type=int, default=32)
+    cp.add_argument("--steps", type=int, default=8)
+    cp.add_argument("--seed", type=int, default=0)
+    cp.add_argument("--oracle", action="store_true", help="also compare the CPU path with the fp32 oracle")
+    cp.set_defaults(fn=cmd_compare)
     b = sub.add_parser("build", help="compile the native libraries")
     b.set_defaults(fn=cmd_build)
     args = ap.parse_args(argv)

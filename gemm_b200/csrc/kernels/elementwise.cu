@@ -296,7 +296,8 @@ qk_norm_rope128_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restr
                        const __nv_bfloat16* __restrict__ q_w, const __nv_bfloat16* __restrict__ k_w, __nv_bfloat16* __restrict__ q_out,
                        __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int n_tok, int hq, int hkv,
                        float theta, float eps, int ld_qkv, float q_scale, const float2* __restrict__ rope_tab, int tab_len,
-                       const int* __restrict__ pos3, int sec_h3, int sec_w3) {
+                       const int* __restrict__ pos3, int sec_h3, int sec_w3, const float* __restrict__ part, int n_part,
+                       long part_stride) {
   pdl_wait();
   pdl_trigger();
   constexpr int D = 128, PAIRS = 64;
@@ -314,8 +315,19 @@ qk_norm_rope128_kernel(const __nv_bfloat16* __restrict__ qkv, const int* __restr
     f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
   };
   float xa[4], xb[4];
-  unpack4(*reinterpret_cast<const uint2*>(src + 4 * l), xa);
-  unpack4(*reinterpret_cast<const uint2*>(src + PAIRS + 4 * l), xb);
+  if (part != nullptr) {
+    // the projection arrives as K-split fp32 partial sums [n_part][n_tok][ld_qkv]: summed here in split order
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { xa[i] = 0.f; xb[i] = 0.f; }
+    const float* pp = part + (size_t)t * ld_qkv + (size_t)h * D + 4 * l;
+    for (int p = 0; p < n_part; ++p, pp += part_stride) {
+      const float4 a = *reinterpret_cast<const float4*>(pp), b = *reinterpret_cast<const float4*>(pp + PAIRS);
+      xa[0] += a.x; xa[1] += a.y; xa[2] += a.z; xa[3] += a.w; xb[0] += b.x; xb[1] += b.y; xb[2] += b.z; xb[3] += b.w;
+    }
+  } else {
+    unpack4(*reinterpret_cast<const uint2*>(src + 4 * l), xa);
+    unpack4(*reinterpret_cast<const uint2*>(src + PAIRS + 4 * l), xb);
+  }
   const bool is_q = h < hq, is_k = !is_q && h < hq + hkv;
   if (is_q || is_k) {
     const __nv_bfloat16* w = is_q ? q_w : k_w;
@@ -523,6 +535,20 @@ mx_gather_rows_kernel(const uint8_t* __restrict__ in_q, const uint8_t* __restric
   }
 }
 
+// ------------------------------------------------------------------------------------------ KV page copy
+// cache page dst[i] <- cache page src[i] (16-byte vectors): the copy-on-write of a forked sequence's tail page
+// (the reference's per-sequence KV arrays are copied whole on a clone: common/glm5.h:640).
+__global__ void __launch_bounds__(256)
+kv_copy_pages_kernel(uint4* __restrict__ cache, const int* __restrict__ src, const int* __restrict__ dst, int n_pages, long vec_per_page) {
+  pdl_wait();
+  pdl_trigger();
+  const int s = src[blockIdx.x], d = dst[blockIdx.x];
+  if (s < 0 || d < 0 || s >= n_pages || d >= n_pages || s == d) return;
+  const uint4* sp = cache + (size_t)s * vec_per_page;
+  uint4* dp = cache + (size_t)d * vec_per_page;
+  for (long i = (long)blockIdx.y * blockDim.x + threadIdx.x; i < vec_per_page; i += (long)gridDim.y * blockDim.x) dp[i] = sp[i];
+}
+
 // ------------------------------------------------------------------------------------------ casts
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
   pdl_wait();
@@ -613,6 +639,24 @@ GB_API int gb_rmsnorm_combine(void* residual, const void* y, const int* pair_row
                         wait_flags, wait_n, epoch_ptr, status, stream, y, pair_row, weights, k, ld_y);
 }
 
+// Same with the fused QKV rows given as K-split fp32 partial sums `part` [n_part][n_tok][ld_qkv] (head_dim 128, full rotary only).
+GB_API int gb_qk_norm_rope_partials(const float* part, int n_part, long part_stride, const int* positions, const int* slots, const void* q_w,
+                                    const void* k_w, void* q_out, void* k_cache, void* v_cache, int n_tok, int hq, int hkv, float theta,
+                                    float eps, int ld_qkv, float q_scale, const void* rope_tab, int tab_len, const int* pos3, int sec_h3,
+                                    int sec_w3, cudaStream_t stream) {
+  if (n_tok <= 0) return 0;
+  const auto al = [](const void* p, int a) { return ((uintptr_t)p & (uintptr_t)(a - 1)) == 0; };
+  if (n_part < 1 || ld_qkv % 4 != 0 || part_stride % 4 != 0 || !al(part, 16) || !al(q_w, 8) || !al(k_w, 8) || !al(q_out, 8) ||
+      !al(k_cache, 8) || !al(v_cache, 8) || !al(rope_tab, 16))
+    return fail("qk_norm_rope_partials: misaligned argument%s");
+  const long warps = (long)n_tok * (hq + 2 * hkv);
+  launch_k(qk_norm_rope128_kernel, (unsigned)((warps + 15) / 16), 256, 0, stream, (const __nv_bfloat16*)nullptr, positions, slots,
+           (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+           n_tok, hq, hkv, theta, eps, ld_qkv, q_scale, (const float2*)rope_tab, tab_len, pos3, sec_h3, sec_w3, part, n_part, part_stride);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 GB_API int gb_qk_norm_rope(const void* qkv, const int* positions, const int* slots, const void* q_w, const void* k_w, void* q_out,
                            void* k_cache, void* v_cache, int n_tok, int hq, int hkv, int head_dim, int rope_pairs, float theta,
                            float eps, int ld_qkv, float q_scale, const void* rope_tab, int tab_len, const int* pos3, int sec_h3, int sec_w3,
@@ -624,7 +668,7 @@ GB_API int gb_qk_norm_rope(const void* qkv, const int* positions, const int* slo
       al8(v_cache) && ((uintptr_t)rope_tab & 15) == 0) {
     launch_k(qk_norm_rope128_kernel, (unsigned)((warps + 15) / 16), 256, 0, stream, (const __nv_bfloat16*)qkv, positions, slots,
              (const __nv_bfloat16*)q_w, (const __nv_bfloat16*)k_w, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
-             n_tok, hq, hkv, theta, eps, ld_qkv, q_scale, (const float2*)rope_tab, tab_len, pos3, sec_h3, sec_w3);
+             n_tok, hq, hkv, theta, eps, ld_qkv, q_scale, (const float2*)rope_tab, tab_len, pos3, sec_h3, sec_w3, (const float*)nullptr, 0, 0L);
     GB_CUDA_OK(cudaGetLastError());
     return 0;
   }
@@ -681,6 +725,17 @@ GB_API int gb_mx_gather_rows(const void* in_q, const void* in_sf, const int* src
   const long blocks = std::min<long>((out_rows + 7) / 8, (long)sm_count() * 16);
   launch_k(mx_gather_rows_kernel, (unsigned)blocks, 256, 0, stream, (const uint8_t*)in_q, (const uint8_t*)in_sf, src_rows, (uint8_t*)out_q,
            (uint8_t*)out_sf, out_rows, k, in_sf32, out_sf32);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// Copies `n` pages of `page_bytes` bytes inside one cache tensor; src / dst are device arrays of page indices.
+GB_API int gb_kv_copy_pages(void* cache, const int* src, const int* dst, int n, int n_pages, long page_bytes, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (page_bytes % 16 != 0 || ((uintptr_t)cache & 15) != 0) return fail("kv_copy_pages: pages must be 16-byte aligned%s");
+  const long vecs = page_bytes / 16;
+  const unsigned by = (unsigned)std::min<long>((vecs + 255) / 256, 64);
+  launch_k(kv_copy_pages_kernel, dim3((unsigned)n, by), 256, 0, stream, (uint4*)cache, src, dst, n_pages, vecs);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

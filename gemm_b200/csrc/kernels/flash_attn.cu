@@ -45,6 +45,10 @@ struct FaArgs {
   float* part_lse;          // [splits, T, Hq] base-2 log-sum-exp
   int total_tokens;
   KernelStatus* status;
+  // decode kernel only: MXFP8 copy of the output rows [T, Hq * 128] (e4m3 bytes + E8M0 scale atoms), the o_proj operand
+  uint8_t* out_q;
+  uint8_t* out_sf;
+  int out_sf32;             // scale-atom layout: one atom per 32 rows (1) or per 128 rows (0)
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -584,7 +588,23 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float inv_l = (l[h] > 0.f) ? 1.0f / l[h] : 0.f;
         const int head = kvh * G + h;
         const float val = __uint_as_float(o[h]) * inv_l;
-        if (a.part_o == nullptr) a.out[((size_t)tok * a.hq + head) * kD + r] = __float2bfloat16(val);
+        if (a.out_q != nullptr) {
+          // the 32 features of this warp are one scale block of the row: quantise here instead of in a kernel of its own
+          const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(val))));
+          const float sc = amax * (1.0f / 448.0f);
+          const uint32_t bits = __float_as_uint(sc);
+          int e = (int)((bits >> 23) & 0xff) + ((bits & 0x7fffffu) ? 1 : 0);
+          e = amax == 0.0f ? 127 : max(1, min(e, 254));
+          const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+          __nv_fp8_e4m3 f8(val * inv);
+          a.out_q[(size_t)tok * a.hq * kD + (size_t)head * kD + r] = *reinterpret_cast<uint8_t*>(&f8);
+          if (lane == 0) {
+            const int blk = head * 4 + q, k_atoms = a.hq;       // 128 features per head = one atom column block per head
+            const size_t off = a.out_sf32 ? ((size_t)(tok >> 5) * k_atoms + (blk >> 2)) * 512 + (tok & 31) * 16 + (blk & 3)
+                                          : ((size_t)(tok >> 7) * k_atoms + (blk >> 2)) * 512 + (tok & 31) * 16 + ((tok >> 5) & 3) * 4 + (blk & 3);
+            a.out_sf[off] = (uint8_t)e;
+          }
+        } else if (a.part_o == nullptr) a.out[((size_t)tok * a.hq + head) * kD + r] = __float2bfloat16(val);
         else a.part_o[(((size_t)split * a.total_tokens + tok) * a.hq + head) * kD + r] = val;
         if (a.part_o != nullptr && r == 0)
           a.part_lse[((size_t)split * a.total_tokens + tok) * a.hq + head] = (l[h] > 0.f) ? (m[h] + log2f(l[h])) : -INFINITY;
@@ -683,10 +703,10 @@ GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache
 
 // Decode form of gb_flash_attn: every sequence contributes exactly one query token (cu_q = 0, 1, 2, ...), Hq / Hkv <= 16.
 // Same arguments and outputs; work items are {seq, kv_head, 0, split}.
-GB_API int gb_flash_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
+static int flash_decode_impl(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
                            const int* work, int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages,
                            int page_size, long num_slots, int total_tokens, int hq, int hkv, int head_dim, int num_splits, int window,
-                           void* status, cudaStream_t stream) {
+                           void* status, cudaStream_t stream, uint8_t* out_q, uint8_t* out_sf, int out_sf32) {
   if (head_dim != 128) return fail("flash_decode: head_dim must be 128%s");
   if (hq % hkv || hq / hkv > kFdN) return fail("flash_decode: needs Hq %% Hkv == 0 and a group of at most 16 heads%s");
   if (page_size < 8 || page_size > 128 || (128 % page_size) || (page_size % 8)) return fail("flash_decode: page_size must be 8..128, a multiple of 8 dividing 128%s");
@@ -713,6 +733,7 @@ GB_API int gb_flash_decode(const void* q, const void* k_cache, const void* v_cac
   a.work = work; a.cu_q = cu_q; a.kv_len = kv_len; a.block_table = block_table; a.max_pages = max_pages; a.page_size = page_size;
   a.hq = hq; a.hkv = hkv; a.num_splits = num_splits; a.causal = 1; a.window = window; a.out = (__nv_bfloat16*)out;
   a.part_o = part_o; a.part_lse = part_lse; a.total_tokens = total_tokens; a.status = (KernelStatus*)status;
+  a.out_q = out_q; a.out_sf = out_sf; a.out_sf32 = out_sf32;
   static bool attr_set = false;
   if (!attr_set) {
     GB_CUDA_OK(cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmem));
@@ -721,6 +742,23 @@ GB_API int gb_flash_decode(const void* q, const void* k_cache, const void* v_cac
   launch_k(flash_decode_kernel, n_work, kFdThreads, kFdSmem, stream, tmQ, tmK, tmV, a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+GB_API int gb_flash_decode(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
+                           const int* work, int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages,
+                           int page_size, long num_slots, int total_tokens, int hq, int hkv, int head_dim, int num_splits, int window,
+                           void* status, cudaStream_t stream) {
+  return flash_decode_impl(q, k_cache, v_cache, out, part_o, part_lse, work, n_work, cu_q, kv_len, block_table, max_pages, page_size, num_slots, total_tokens, hq, hkv, head_dim, num_splits, window, status, stream, nullptr, nullptr, 0);
+}
+
+// gb_flash_decode with the output written as MXFP8 rows [T, Hq * 128] (single split only): out_q e4m3 bytes, out_sf scale atoms in
+// the 32-row (sf32 = 1) or 128-row layout.
+GB_API int gb_flash_decode_mx(const void* q, const void* k_cache, const void* v_cache, void* out_q, void* out_sf, int sf32, const int* work,
+                              int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages, int page_size,
+                              long num_slots, int total_tokens, int hq, int hkv, int head_dim, int window, void* status, cudaStream_t stream) {
+  if (out_q == nullptr || out_sf == nullptr) return fail("flash_decode_mx: no output buffer%s");
+  return flash_decode_impl(q, k_cache, v_cache, out_q, nullptr, nullptr, work, n_work, cu_q, kv_len, block_table, max_pages, page_size,
+                           num_slots, total_tokens, hq, hkv, head_dim, 1, window, status, stream, (uint8_t*)out_q, (uint8_t*)out_sf, sf32);
 }
 
 GB_API int gb_fa_combine(const float* part_o, const float* part_lse, void* out, float* out_lse, int splits, long rows, cudaStream_t stream) {

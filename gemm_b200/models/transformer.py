@@ -14,12 +14,14 @@ Layer recipe (reference: common/transformer.h:3550-4174):
 """
 from __future__ import annotations
 
+import ctypes
 import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
 import torch
 
+from .. import _native
 from ..ops import attention as att
 from ..ops import elementwise as ew
 from ..ops import deltanet as dn
@@ -67,6 +69,28 @@ class KvCache:
             if c is not None:
                 c[idx] = 0
                 r[idx] = 0
+
+    def copy_pages(self, pairs) -> None:
+        """``page dst <- page src`` for every ``(src, dst)`` of ``pairs`` in every layer's K and V: the copy-on-write step of a
+        forked sequence (``serve.scheduler.KvBlockManager.fork`` names the tail page to copy)."""
+        pairs = [p for p in pairs if p is not None]
+        if not pairs:
+            return
+        dev = self.k[0].device
+        src = torch.tensor([p[0] for p in pairs], dtype=torch.int32, device=dev)
+        dst = torch.tensor([p[1] for p in pairs], dtype=torch.int32, device=dev)
+        for t in list(self.k) + list(self.v):
+            if t.shape[0] == 0:
+                continue
+            if not t.is_cuda:
+                pg = t.view(self.num_pages, self.page_size, *t.shape[1:])
+                pg[dst.long()] = pg[src.long()]
+                continue
+            page_bytes = self.page_size * t.shape[1] * t.shape[2] * t.element_size()
+            rc = _native.cuda().gb_kv_copy_pages(ctypes.c_void_p(t.data_ptr()), ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()),
+                                                 ctypes.c_int(len(pairs)), ctypes.c_int(self.num_pages), ctypes.c_long(page_bytes),
+                                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            _native.check(rc, "gb_kv_copy_pages")
 
     def nbytes(self) -> int:
         tot = sum(t.numel() * 2 for t in self.k) * 2
@@ -121,6 +145,9 @@ class ForwardBatch:
 
 # K-split partial sums for decode-sized row projections (GB_SPLIT_PROJ=0 switches them off)
 SPLIT_PROJ = os.environ.get("GB_SPLIT_PROJ", "1") != "0"
+
+
+FUSE_ATTN_QUANT = os.environ.get("GB_FUSE_ATTN_QUANT", "1") != "0"
 
 
 class SingleProcess:
@@ -216,10 +243,18 @@ class Transformer:
     # ------------------------------------------------------------------------------------------------
     def attention_block(self, li: int, lw, h: torch.Tensor, h_mx: Optional[MxTensor], fb: ForwardBatch) -> torch.Tensor:
         cfg = self.cfg
-        qkv = apply_linear(lw.wqkv, h, h_mx)
+        # decode-sized batches: the projection is cut along K and the rope kernel sums the partials (not with an output gate,
+        # whose columns are read again below)
+        qkv = apply_linear(lw.wqkv, h, h_mx) if cfg.attn_output_gate else apply_linear_split(lw.wqkv, h, h_mx)
         q = ew.qk_norm_rope(qkv, fb.positions, fb.slots, lw.q_norm, lw.k_norm, self.kv.k[li], self.kv.v[li], self.hq_local,
                             self.hkv_local, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
                             positions3=fb.positions3, sections=cfg.mrope_sections)
+        if (self.mx and lw.wo.fmt != "bf16" and not cfg.attn_output_gate and FUSE_ATTN_QUANT
+                and att.can_decode_mx(q, self.hkv_local, fb.num_splits, fb.is_decode)):
+            # decode: the attention kernel emits the MXFP8 operand of the output projection itself
+            a_mx = att.attention_decode_mx(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
+                                           window=cfg.sliding_window, sf_layout=32 if q.shape[0] <= 32 else 128)
+            return self.par.row_linear(lw.wo, None, a_mx)
         a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
                           num_splits=fb.num_splits, causal=True, window=cfg.sliding_window, decode=fb.is_decode)
         a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)

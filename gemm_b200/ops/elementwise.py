@@ -197,6 +197,20 @@ def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor
     ``table`` (from ``rope_table``) replaces the in-kernel powf / sincosf; ``positions3`` int32 ``[3, T]`` + ``sections`` select
     M-RoPE.
     """
+    if hasattr(qkv, "buf"):                  # ops.gemm.PendingPartials: K-split partial sums of the QKV projection
+        pend = qkv
+        pairs = (rope_dim or d) // 2
+        if pend.buf.is_cuda and d == 128 and pairs == 64 and pend.hidden % 4 == 0:
+            t = pend.rows
+            q_out = torch.empty(t, hq, d, dtype=torch.bfloat16, device=pend.buf.device)
+            rc = _native.cuda().gb_qk_norm_rope_partials(_p(pend.buf), _i(pend.n), _l(pend.rows * pend.hidden), _p(positions), _p(slots), _p(q_w),
+                                                         _p(k_w), _p(q_out), _p(k_cache), _p(v_cache), _i(t), _i(hq), _i(hkv), _f(theta), _f(eps),
+                                                         _i(pend.hidden), _f(q_scale), _p(table), _i(table.shape[0] if table is not None else 0),
+                                                         _p(positions3 if (positions3 is not None and sections) else None),
+                                                         _i(3 * sections[1] if sections else 0), _i(3 * sections[2] if sections else 0), _s())
+            _native.check(rc, "gb_qk_norm_rope_partials")
+            return q_out
+        qkv = pend.materialize()
     t = qkv.shape[0]
     if not qkv.is_cuda:
         q, k, v = qk_norm_rope_ref(qkv, positions, q_w, k_w, hq, hkv, d, theta, eps, q_scale, rope_dim, positions3, sections)

@@ -1,0 +1,125 @@
+"""Roofline estimate of decode and prefill throughput of a model configuration on B200s.
+
+``python -m gemm_b200 estimate --model qwen3-30b-a3b --batch 64 --ctx 2048 --gpus 8 --format mxfp8``
+
+Per decode step the time is the larger of the memory-bound part (bytes every GPU must read from HBM: the weights it
+touches once per step, the KV cache of its sequences) and the communication-bound part (bytes it must move over NVLink),
+plus a fixed cost per kernel launch; prefill adds the tensor-core time.  Weights amortise over the batch, KV does not;
+an MoE layer touches only the experts some token selected: E * (1 - (1 - k/E)^B) of them in expectation.  The numbers
+are ceilings (routing, softmax and launch gaps beyond the fixed term are not modelled); ``--derate`` applies an
+efficiency factor.  Also reports whether weights + KV fit in HBM.
+
+Counterpart in the reference: tools/decode_estimate.py (per-step time = max(memory, communication), fit check, the same
+treatment of batch and context), with the platform constants replaced by this machine's measured ones.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from dataclasses import dataclass
+
+from ..models.config import ModelConfig, get_config
+
+
+@dataclass
+class Platform:
+    hbm_gbs: float = 6535.0          # measured copy bandwidth
+    hbm_gib: float = 180.0
+    nvlink_gbs: float = 770.0        # measured peer copy, per direction per GPU
+    tensor_tflops: float = 1667.5    # measured cuBLAS bf16 burst
+    fp8_speedup: float = 1.15        # measured: block-scaled e4m3 GEMM against the bf16 figure above
+    launch_us: float = 4.0           # fixed cost per kernel in a programmatic-dependent-launch chain
+    kernels_per_layer: int = 13
+
+
+def _bytes_per_weight(fmt: str) -> float:
+    return {"bf16": 2.0, "mxfp8": 1.0 + 1.0 / 32.0}[fmt]
+
+
+def layer_params(cfg: ModelConfig):
+    """(attention, dense-or-shared FFN, one expert, router) parameter counts of one layer."""
+    d = cfg.head_dim
+    attn = cfg.hidden * (cfg.n_heads + 2 * cfg.n_kv_heads) * d + cfg.n_heads * d * cfg.hidden
+    if cfg.n_experts > 0:
+        expert = 3 * cfg.hidden * cfg.expert_ffn
+        dense = 3 * cfg.hidden * cfg.shared_expert_ffn
+        router = cfg.hidden * cfg.n_experts
+    else:
+        expert, router = 0, 0
+        dense = 3 * cfg.hidden * cfg.ffn
+    return attn, dense, expert, router
+
+
+def experts_touched(n_experts: int, k: int, tokens: int) -> float:
+    """Expected number of distinct experts chosen by ``tokens`` tokens routing uniformly to ``k`` of ``n_experts``."""
+    if n_experts == 0:
+        return 0.0
+    return n_experts * (1.0 - (1.0 - k / n_experts) ** tokens)
+
+
+def estimate(cfg: ModelConfig, batch: int, ctx: int, gpus: int = 1, fmt: str = "mxfp8", mode: str = "ep", plat: Platform = Platform(),
+             derate: float = 1.0, prefill_chunk: int = 16384) -> dict:
+    """``mode`` "ep": experts sharded over the GPUs, attention replicated, the batch split by GPU (data-parallel attention);
+    "tp": every projection sharded, batch replicated."""
+    bw = _bytes_per_weight(fmt)
+    attn, dense, expert, router = layer_params(cfg)
+    n_layers = cfg.n_layers
+    kv_tok = 2 * cfg.n_kv_heads * cfg.head_dim * 2                      # bytes per token per layer (bf16 K and V)
+    head = cfg.vocab * cfg.hidden * 2                                   # LM head stays bf16
+    local_batch = batch if mode == "tp" else -(-batch // gpus)
+    # ---- decode: bytes one GPU reads per step
+    touched = experts_touched(cfg.n_experts, cfg.n_experts_used, batch)
+    if mode == "tp":
+        w_layer = (attn + dense + touched * expert) * bw / gpus + router * 2
+        kv_layer = batch * ctx * kv_tok / min(gpus, cfg.n_kv_heads)
+        comm_layer = 2 * batch * cfg.hidden * 4 * (gpus - 1) / gpus * (2 if gpus > 1 else 0)      # two all-reduces of fp32 rows
+    else:
+        w_layer = (attn + dense) * bw + touched * expert * bw / gpus + router * 2
+        kv_layer = local_batch * ctx * kv_tok
+        # all-gather of the token rows (bf16) in, fp32 partial rows back to the tokens' home GPUs
+        comm_layer = (batch - local_batch) * cfg.hidden * 2 + local_batch * cfg.hidden * 4 * (gpus - 1) if gpus > 1 else 0
+    mem_s = n_layers * (w_layer + kv_layer) / (plat.hbm_gbs * 1e9) + head / (1 if mode == "ep" else gpus) / (plat.hbm_gbs * 1e9)
+    comm_s = n_layers * comm_layer / (plat.nvlink_gbs * 1e9)
+    launch_s = n_layers * plat.kernels_per_layer * plat.launch_us * 1e-6
+    step_s = (max(mem_s, comm_s) + launch_s) / derate
+    # ---- prefill: FLOPs of one chunk
+    tokens = min(prefill_chunk, batch * ctx)
+    act = (attn + dense + cfg.n_experts_used * expert + router) * 2.0 * tokens
+    attn_flops = 4.0 * tokens * cfg.n_heads * cfg.head_dim * (ctx / 2)
+    peak = plat.tensor_tflops * 1e12 * (plat.fp8_speedup if fmt == "mxfp8" else 1.0)
+    chunk_s = n_layers * (act / peak + attn_flops / (plat.tensor_tflops * 1e12)) / gpus / derate
+    # ---- fit
+    w_total = n_layers * ((attn + dense) * bw * (1 if mode == "ep" else 1 / gpus) + cfg.n_experts * expert * bw / gpus) + 2 * head
+    kv_total = n_layers * (local_batch if mode == "ep" else batch / min(gpus, cfg.n_kv_heads)) * ctx * kv_tok
+    return {
+        "decode_ms_per_step": step_s * 1e3, "decode_tokens_per_s": batch / step_s,
+        "decode_memory_ms": mem_s * 1e3, "decode_comm_ms": comm_s * 1e3, "decode_launch_ms": launch_s * 1e3,
+        "decode_bound": "memory" if mem_s >= comm_s else "communication",
+        "experts_touched_per_layer": touched,
+        "prefill_tokens_per_s": tokens / chunk_s,
+        "weights_gib_per_gpu": w_total / 2 ** 30, "kv_gib_per_gpu": kv_total / 2 ** 30,
+        "fits": (w_total + kv_total) / 2 ** 30 < plat.hbm_gib * 0.95,
+    }
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--model", default="qwen3-30b-a3b")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--gpus", default="1", help="comma separated GPU counts")
+    ap.add_argument("--format", default="mxfp8", choices=["bf16", "mxfp8"])
+    ap.add_argument("--mode", default="ep", choices=["ep", "tp"])
+    ap.add_argument("--derate", type=float, default=1.0)
+    ap.add_argument("--hbm-gbs", type=float, default=Platform.hbm_gbs)
+    ap.add_argument("--nvlink-gbs", type=float, default=Platform.nvlink_gbs)
+    args = ap.parse_args(argv)
+    cfg = get_config(args.model)
+    plat = Platform(hbm_gbs=args.hbm_gbs, nvlink_gbs=args.nvlink_gbs)
+    for g in [int(x) for x in args.gpus.split(",")]:
+        r = estimate(cfg, args.batch, args.ctx, g, args.format, args.mode, plat, args.derate)
+        print(json.dumps({"gpus": g, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}}))
+
+
+if __name__ == "__main__":
+    main()

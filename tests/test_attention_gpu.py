@@ -106,3 +106,27 @@ def test_decode_kernel_sliding_window():
     ref = att.attention_ref(q, kc, vc, cu, kvl, bt, 128, window=200)
     _native.assert_status_ok()
     assert _rel(out, ref) < 1.5e-2
+
+
+@pytest.mark.parametrize("b,lay", [(7, 32), (40, 128)])
+def test_decode_kernel_mxfp8_output(b, lay):
+    """The decode kernel's MXFP8 output (the o_proj operand) equals quantising its bf16 output."""
+    from gemm_b200.ops import elementwise as ew
+    from gemm_b200.ops import mxfp8
+    hq, hkv, page = 32, 4, 128
+    q_lens = [1] * b
+    ctx = [(37 * i) % 900 for i in range(b)]
+    q, kc, vc, cu, kvl, bt = _setup(q_lens, ctx, hq, hkv, page, seed=6)
+    work = att.build_work(q_lens, hq, hkv, 1).cuda()
+    out = att.attention(q, kc, vc, cu, kvl, bt, page, work, decode=True)
+    assert att.can_decode_mx(q, hkv, 1, True)
+    om = att.attention_decode_mx(q, kc, vc, cu, kvl, bt, page, work, sf_layout=lay)
+    _native.assert_status_ok()
+    want = ew.mx_quantize(out.reshape(b, hq * 128), sf_layout=lay)
+    got_f, want_f = mxfp8.dequantize(om), mxfp8.dequantize(want)
+    assert _rel(got_f, out.reshape(b, hq * 128)) < 4e-2                 # e4m3 rounding
+    # the kernel quantises the fp32 value, the reference path a bf16-rounded one: scales agree, bytes differ by at most one step rarely
+    sg = mxfp8.unpack_sf_atoms(om.sf, b, hq * 4, lay).int()
+    sw = mxfp8.unpack_sf_atoms(want.sf, b, hq * 4, lay).int()
+    assert (sg - sw).abs().max().item() <= 1
+    assert _rel(got_f, want_f) < 2e-2

@@ -29,3 +29,24 @@ def test_inspect_and_stage(tmp_path, capsys):
     main(["stage", "--model", path, "--out", out_dir, "--format", "bf16", "--tp", "2"])
     assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["ranks"] == 2
     assert os.path.exists(os.path.join(out_dir, "manifest.json"))
+
+
+def test_estimate_roofline():
+    from gemm_b200.models.config import get_config
+    from gemm_b200.utils import estimate as est
+    cfg = get_config("qwen3-30b-a3b")
+    assert abs(est.experts_touched(128, 8, 64) - 126.0) < 1.0
+    r1 = est.estimate(cfg, 64, 2048, 1, "mxfp8")
+    r8 = est.estimate(cfg, 64, 2048, 8, "mxfp8")
+    assert r1["fits"] and r8["fits"]
+    assert 5.0 < r1["decode_ms_per_step"] < 14.0                # measured 13.3 ms on one B200: the estimate is a ceiling
+    assert r8["decode_ms_per_step"] < r1["decode_ms_per_step"]
+    assert r1["decode_bound"] == "memory"
+    assert est.estimate(cfg, 64, 2048, 1, "bf16")["decode_memory_ms"] > r1["decode_memory_ms"]
+
+
+def test_compare_command_cpu_side(capsys):
+    from gemm_b200.__main__ import main
+    main(["compare", "--model", "synthetic:tiny-dense", "--steps", "3", "--prompt-len", "12", "--oracle"])
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert len(rep["cpu_tokens"]) == 3 and rep["cpu_vs_fp32_oracle_rel"] < 3e-2

@@ -68,3 +68,35 @@ def test_gpu_engine_matches_cpu_engine_and_oracle(name, fmt):
             lim = 0.15 if fmt == "bf16" else 0.3          # twice the layers of the other test models
         assert _rel(o_gpu[1][row], ref) < lim
     assert any("libgb_cuda" in p for p in _native.loaded_libraries())
+
+
+def test_forked_sequence_continues_like_its_parent():
+    """KV fork: full pages are shared, the tail page is copied on the device; the fork then decodes exactly like the parent."""
+    from gemm_b200.serve.scheduler import KvBlockManager
+    torch.manual_seed(5)
+    cfg = get_config("tiny-dense")
+    w = synthetic_weights(cfg, "bf16", device="cuda", seed=2)
+    page, n_pages, n_prompt = 16, 32, 40
+    kv = KvCache.allocate(cfg, n_pages, page, "cuda")
+    model = Transformer(w, kv)
+    blocks = KvBlockManager(n_pages, page)
+    a = blocks.new_sequence()
+    blocks.reserve(a, n_prompt + 1)
+    toks = torch.randint(0, cfg.vocab, (n_prompt + 1,))
+
+    def table(seq):
+        pg = blocks.pages(seq)
+        return torch.tensor([pg], dtype=torch.int32)
+
+    fb = ForwardBatch.build([n_prompt], [0], toks[:n_prompt], table(a), page, cfg.n_heads, cfg.n_kv_heads, "cuda")
+    model.forward(fb)
+    b, copy = blocks.fork(a, n_prompt)                      # 2 shared pages + an 8-token tail page to copy
+    assert copy is not None
+    kv.copy_pages([copy])
+    blocks.reserve(b, n_prompt + 1)
+    outs = []
+    for seq in (a, b):
+        fbd = ForwardBatch.build([1], [n_prompt], toks[n_prompt:], table(seq), page, cfg.n_heads, cfg.n_kv_heads, "cuda")
+        outs.append(model.forward(fbd).float().cpu())
+    _native.assert_status_ok()
+    assert torch.equal(outs[0], outs[1])

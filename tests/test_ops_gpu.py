@@ -87,6 +87,26 @@ def test_qk_norm_rope_head128_table_and_mrope(mrope):
     assert torch.equal(vc[slots[live].long()], vr[live])
 
 
+def test_qk_norm_rope_from_split_k_partials():
+    from gemm_b200.ops import gemm
+    torch.manual_seed(24)
+    t, hq, hkv, d = 21, 4, 2, 128
+    width = (hq + 2 * hkv) * d
+    parts = torch.randn(3, t, width, device="cuda") * 0.6
+    pend = gemm.PendingPartials(parts)
+    qkv = parts.sum(0).bfloat16()
+    pos = torch.randint(0, 3000, (t,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(64, device="cuda")[:t].to(torch.int32)
+    qw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    kw = (1 + 0.1 * torch.randn(d, device="cuda")).bfloat16()
+    kc, vc = (torch.zeros(64, hkv, d, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(vc)
+    tab = ew.rope_table(3000, d, 1e6, "cuda")
+    q = ew.qk_norm_rope(pend, pos, slots, qw, kw, kc, vc, hq, hkv, d, 1e6, 1e-6, 0.25, None, table=tab)
+    q2 = ew.qk_norm_rope(qkv, pos, slots, qw, kw, kc2, vc2, hq, hkv, d, 1e6, 1e-6, 0.25, None, table=tab)
+    assert _rel(q, q2) < 6e-3 and _rel(kc, kc2) < 6e-3 and _rel(vc, vc2) < 6e-3
+
+
 @pytest.mark.parametrize("lay_in,lay_out", [(128, 128), (128, 32), (32, 32)])
 def test_mx_gather_rows_equals_quantising_gathered_rows(lay_in, lay_out):
     torch.manual_seed(23)
