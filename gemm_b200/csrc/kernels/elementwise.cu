@@ -411,72 +411,108 @@ __global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_
 // Used after a plain (single-accumulator) gate/up GEMM for prefill-sized expert batches, where the two-accumulator GEMM
 // with this math in its epilogue cannot double-buffer its accumulators in TMEM.  Rows whose row_valid entry is negative
 // (padding of the expert-sorted buffer) are skipped.  8 elements per thread, 4 threads share a scale.
+constexpr int kSiluU = 2;        // items per thread: the gate and up vectors of both are requested before the first use
 __global__ void __launch_bounds__(256)
 silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const int* __restrict__ row_valid, uint8_t* __restrict__ out_q,
                       uint8_t* __restrict__ out_sf, long rows, int inter, int ld, int sf32) {
   pdl_wait();
   pdl_trigger();
-  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const int vec_per_row = inter >> 3;
-  const long r = idx / vec_per_row;
-  const int vi = (int)(idx % vec_per_row);
-  const bool live = r < rows && (row_valid == nullptr || row_valid[r] >= 0);
-  float y[8];
-  float amax = 0.f;
-  if (live) {
-    float g[8], u[8];
-    load8(gate_up + r * ld + vi * 8, g);
-    load8(gate_up + r * ld + inter + vi * 8, u);
+  const long base = (long)blockIdx.x * (256 * kSiluU) + threadIdx.x;
+  bf16x8 gr[kSiluU], ur[kSiluU];
+  long rr[kSiluU];
+  int vv[kSiluU];
+  bool live[kSiluU];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { y[j] = __fdividef(g[j], 1.0f + __expf(-g[j])) * u[j]; amax = fmaxf(amax, fabsf(y[j])); }
+  for (int u = 0; u < kSiluU; ++u) {
+    const long idx = base + u * 256;
+    rr[u] = idx / vec_per_row;
+    vv[u] = (int)(idx - rr[u] * vec_per_row);
+    live[u] = rr[u] < rows && (row_valid == nullptr || row_valid[rr[u]] >= 0);
+    if (live[u]) {
+      gr[u] = *reinterpret_cast<const bf16x8*>(gate_up + rr[u] * ld + vv[u] * 8);
+      ur[u] = *reinterpret_cast<const bf16x8*>(gate_up + rr[u] * ld + inter + vv[u] * 8);
+    }
   }
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  if (!live) return;
-  const int e = e8m0_amax(amax);
-  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
-  // two values per conversion instruction
-  uint2 q;
-  q.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[0] * inv, y[1] * inv), __NV_SATFINITE, __NV_E4M3) |
-        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[2] * inv, y[3] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
-  q.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[4] * inv, y[5] * inv), __NV_SATFINITE, __NV_E4M3) |
-        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[6] * inv, y[7] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
-  *reinterpret_cast<uint2*>(out_q + r * inter + vi * 8) = q;
-  if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, inter >> 7, sf32)] = (uint8_t)e;
+#pragma unroll
+  for (int u = 0; u < kSiluU; ++u) {
+    float y[8];
+    float amax = 0.f;
+    if (live[u]) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(gr[u].v[j]), up = __bfloat1622float2(ur[u].v[j]);
+        y[2 * j] = __fdividef(g.x, 1.0f + __expf(-g.x)) * up.x;
+        y[2 * j + 1] = __fdividef(g.y, 1.0f + __expf(-g.y)) * up.y;
+        amax = fmaxf(amax, fmaxf(fabsf(y[2 * j]), fabsf(y[2 * j + 1])));
+      }
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!live[u]) continue;
+    const int e = e8m0_amax(amax);
+    const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+    uint2 q;            // two values per conversion instruction
+    q.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[0] * inv, y[1] * inv), __NV_SATFINITE, __NV_E4M3) |
+          ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[2] * inv, y[3] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+    q.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[4] * inv, y[5] * inv), __NV_SATFINITE, __NV_E4M3) |
+          ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(y[6] * inv, y[7] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+    *reinterpret_cast<uint2*>(out_q + rr[u] * inter + vv[u] * 8) = q;
+    if ((vv[u] & 3) == 0) out_sf[sf_atom_offset(rr[u], vv[u] >> 2, inter >> 7, sf32)] = (uint8_t)e;
+  }
 }
 
 // ------------------------------------------------------------------------------------------ mxfp8 quantiser
 // out row r <- in row (src_rows ? src_rows[r] : r); rows whose source is negative are zero-filled with
 // scale 1.  One warp per 256 elements: lane holds 8 elements, 4 lanes share a scale.
+constexpr int kMxQuantU = 4;     // vectors per thread: all loads of a thread are issued before the first use
 __global__ void __launch_bounds__(256)
 mx_quant_kernel(const __nv_bfloat16* __restrict__ in, const int* __restrict__ src_rows, uint8_t* __restrict__ out_q,
                 uint8_t* __restrict__ out_sf, long out_rows, int k, int ld_in, int sf32) {
   pdl_wait();
   pdl_trigger();
   const int vec_per_row = k >> 3;
-  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-  const bool act = idx < out_rows * vec_per_row;
-  const long r = act ? idx / vec_per_row : 0;
-  const int vi = act ? (int)(idx % vec_per_row) : 0;
-  float v[8];
+  const long total = out_rows * vec_per_row;
+  const long base = (long)blockIdx.x * (256 * kMxQuantU) + threadIdx.x;
+  bf16x8 raw[kMxQuantU];
+  long rr[kMxQuantU];
+  int vv[kMxQuantU];
+  bool act[kMxQuantU], have[kMxQuantU];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) v[j] = 0.f;
-  long src = r;
-  if (act && src_rows != nullptr) src = src_rows[r];
-  if (act && src >= 0) load8(in + src * ld_in + vi * 8, v);
-  float amax = 0.f;
+  for (int u = 0; u < kMxQuantU; ++u) {
+    const long idx = base + u * 256;
+    act[u] = idx < total;
+    rr[u] = act[u] ? idx / vec_per_row : 0;
+    vv[u] = act[u] ? (int)(idx - rr[u] * vec_per_row) : 0;
+    long src = rr[u];
+    if (act[u] && src_rows != nullptr) src = src_rows[rr[u]];
+    have[u] = act[u] && src >= 0;
+    if (have[u]) raw[u] = *reinterpret_cast<const bf16x8*>(in + src * ld_in + vv[u] * 8);
+  }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  if (!act) return;
-  const int e = e8m0_amax(amax);
-  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
-  uint8_t q[8];
+  for (int u = 0; u < kMxQuantU; ++u) {
+    float v[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(v[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
-  *reinterpret_cast<uint2*>(out_q + r * k + vi * 8) = *reinterpret_cast<uint2*>(q);
-  if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, k >> 7, sf32)] = (uint8_t)e;
+    for (int j = 0; j < 4; ++j) {
+      const float2 t2 = have[u] ? __bfloat1622float2(raw[u].v[j]) : make_float2(0.f, 0.f);
+      v[2 * j] = t2.x; v[2 * j + 1] = t2.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    if (!act[u]) continue;
+    const int e = e8m0_amax(amax);
+    const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+    uint2 q;
+    q.x = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3) |
+          ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+    q.y = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v[4] * inv, v[5] * inv), __NV_SATFINITE, __NV_E4M3) |
+          ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(v[6] * inv, v[7] * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+    *reinterpret_cast<uint2*>(out_q + rr[u] * k + vv[u] * 8) = q;
+    if ((vv[u] & 3) == 0) out_sf[sf_atom_offset(rr[u], vv[u] >> 2, k >> 7, sf32)] = (uint8_t)e;
+  }
 }
 
 // Gathering variant, one warp per output row: padding rows (source < 0) are skipped after one load, so a mostly
@@ -522,16 +558,36 @@ mx_gather_rows_kernel(const uint8_t* __restrict__ in_q, const uint8_t* __restric
   const int lane = threadIdx.x & 31;
   const long warp0 = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5, n_warps = ((long)gridDim.x * blockDim.x) >> 5;
   const int vecs = k >> 4, k_atoms = k >> 7;
-  for (long r = warp0; r < out_rows; r += n_warps) {
-    const int src = src_rows[r];
-    if (src < 0) continue;
-    const uint4* ip = reinterpret_cast<const uint4*>(in_q + (size_t)src * k);
-    uint4* op = reinterpret_cast<uint4*>(out_q + (size_t)r * k);
-    for (int vi = lane; vi < vecs; vi += 32) op[vi] = ip[vi];
+  // two rows per warp and step; the loads of both rows (4 vectors per lane and row at a time) are issued before the stores
+  for (long r0 = warp0 * 2; r0 < out_rows; r0 += n_warps * 2) {
+    int src[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) src[u] = (r0 + u < out_rows) ? src_rows[r0 + u] : -1;
+    for (int v0 = 0; v0 < vecs; v0 += 128) {
+      uint4 buf[2][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int vi = v0 + lane + 32 * i;
+          if (src[u] >= 0 && vi < vecs) buf[u][i] = reinterpret_cast<const uint4*>(in_q + (size_t)src[u] * k)[vi];
+        }
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int vi = v0 + lane + 32 * i;
+          if (src[u] >= 0 && vi < vecs) reinterpret_cast<uint4*>(out_q + (size_t)(r0 + u) * k)[vi] = buf[u][i];
+        }
+    }
     // the four scales of one 128-element block are four consecutive bytes in either layout
-    for (int a = lane; a < k_atoms; a += 32)
-      *reinterpret_cast<uint32_t*>(out_sf + sf_atom_offset(r, a * 4, k_atoms, out_sf32)) =
-          *reinterpret_cast<const uint32_t*>(in_sf + sf_atom_offset(src, a * 4, k_atoms, in_sf32));
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (src[u] < 0) continue;
+      for (int a = lane; a < k_atoms; a += 32)
+        *reinterpret_cast<uint32_t*>(out_sf + sf_atom_offset(r0 + u, a * 4, k_atoms, out_sf32)) =
+            *reinterpret_cast<const uint32_t*>(in_sf + sf_atom_offset(src[u], a * 4, k_atoms, in_sf32));
+    }
   }
 }
 
@@ -697,7 +753,7 @@ GB_API int gb_silu_mul_quant(const void* gate_up, const int* row_valid, void* ou
   if (inter % 128) return fail("silu_mul_quant: inter %% 128 != 0%s");
   const long n = rows * (inter / 8);
   if (n <= 0) return 0;
-  launch_k(silu_mul_quant_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)gate_up, row_valid, (uint8_t*)out_q,
+  launch_k(silu_mul_quant_kernel, (unsigned)((n + 256 * kSiluU - 1) / (256 * kSiluU)), 256, 0, stream, (const __nv_bfloat16*)gate_up, row_valid, (uint8_t*)out_q,
            (uint8_t*)out_sf, rows, inter, ld, sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -713,7 +769,7 @@ GB_API int gb_mx_quant(const void* in, const int* src_rows, void* out_q, void* o
     GB_CUDA_OK(cudaGetLastError());
     return 0;
   }
-  launch_k(mx_quant_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
+  launch_k(mx_quant_kernel, (unsigned)((n + 256 * kMxQuantU - 1) / (256 * kMxQuantU)), 256, 0, stream, (const __nv_bfloat16*)in, src_rows, (uint8_t*)out_q, (uint8_t*)out_sf, out_rows, k, ld_in, sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -275,6 +275,7 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int tok = q_begin + q_tok0 + t_local;
       const int head = kvh * G + h_local;
       const float inv_l = (l > 0.f) ? 1.0f / l : 0.f;
+      uint32_t sf_word = 0;                  // the row's four E8M0 scales (MXFP8 output)
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -284,7 +285,30 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
         if (row_valid) {
-          if (a.part_o == nullptr) {
+          if (a.out_q != nullptr) {
+            // this thread holds a whole (token, head) row: its 32-feature scale blocks are thread-local
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(__uint_as_float(o[i]) * inv_l));
+            const float sc = amax * (1.0f / 448.0f);
+            const uint32_t bits = __float_as_uint(sc);
+            int e = (int)((bits >> 23) & 0xff) + ((bits & 0x7fffffu) ? 1 : 0);
+            e = amax == 0.0f ? 127 : max(1, min(e, 254));
+            const float inv = __uint_as_float((uint32_t)(254 - e) << 23) * inv_l;
+            sf_word |= (uint32_t)e << (8 * c);
+            uint4* dst = reinterpret_cast<uint4*>(a.out_q + ((size_t)tok * a.hq + head) * kD + c * 32);
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              uint32_t w4[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int b0 = v * 16 + i * 4;
+                w4[i] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(o[b0]) * inv, __uint_as_float(o[b0 + 1]) * inv), __NV_SATFINITE, __NV_E4M3) |
+                        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__uint_as_float(o[b0 + 2]) * inv, __uint_as_float(o[b0 + 3]) * inv), __NV_SATFINITE, __NV_E4M3) << 16);
+              }
+              dst[v] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+          } else if (a.part_o == nullptr) {
             uint4* dst = reinterpret_cast<uint4*>(a.out + ((size_t)tok * a.hq + head) * kD + c * 32);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -303,6 +327,13 @@ flash_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                                    __uint_as_float(o[v * 4 + 2]) * inv_l, __uint_as_float(o[v * 4 + 3]) * inv_l);
           }
         }
+      }
+      if (row_valid && a.out_q != nullptr) {
+        // blocks head*4 .. head*4+3 of the row [Hq * 128] share one atom column block: four consecutive bytes
+        const int k_atoms = a.hq;
+        const size_t off = a.out_sf32 ? ((size_t)(tok >> 5) * k_atoms + head) * 512 + (tok & 31) * 16
+                                      : ((size_t)(tok >> 7) * k_atoms + head) * 512 + (tok & 31) * 16 + ((tok >> 5) & 3) * 4;
+        *reinterpret_cast<uint32_t*>(a.out_sf + off) = sf_word;
       }
       if (row_valid && a.part_o != nullptr)
         a.part_lse[((size_t)split * a.total_tokens + tok) * a.hq + head] = (l > 0.f) ? (m + log2f(l)) : -INFINITY;
@@ -657,10 +688,10 @@ using namespace gb;
 // q [T, Hq, 128] bf16 (pre-scaled by softmax_scale * log2 e), k_cache / v_cache [num_slots, Hkv, 128] bf16,
 // out [T, Hq, 128] bf16.  `work` is a device int32 [n_work, 4] list {seq, kv_head, q_tok0, split}.
 // With num_splits > 1, part_o / part_lse receive the partials and gb_fa_combine finishes.
-GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
+static int flash_attn_impl(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
                          const int* work, int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages,
                          int page_size, long num_slots, int total_tokens, int hq, int hkv, int head_dim, int num_splits, int causal,
-                         int window, void* status, cudaStream_t stream) {
+                         int window, void* status, cudaStream_t stream, uint8_t* out_q, uint8_t* out_sf, int out_sf32) {
   if (head_dim != 128) return fail("flash_attn: head_dim must be 128%s");
   if (hq % hkv) return fail("flash_attn: Hq %% Hkv != 0%s");
   const int G = hq / hkv;
@@ -690,6 +721,7 @@ GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache
   a.work = work; a.cu_q = cu_q; a.kv_len = kv_len; a.block_table = block_table; a.max_pages = max_pages; a.page_size = page_size;
   a.hq = hq; a.hkv = hkv; a.num_splits = num_splits; a.causal = causal; a.window = window; a.out = (__nv_bfloat16*)out;
   a.part_o = part_o; a.part_lse = part_lse; a.total_tokens = total_tokens; a.status = (KernelStatus*)status;
+  a.out_q = out_q; a.out_sf = out_sf; a.out_sf32 = out_sf32;
   const int smem = kFaSmem;
   static bool attr_set = false;
   if (!attr_set) {
@@ -699,6 +731,23 @@ GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache
   launch_k(flash_attn_kernel, n_work, kFaThreads, smem, stream, tmQ, tmK, tmV, a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
+}
+
+GB_API int gb_flash_attn(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
+                         const int* work, int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages,
+                         int page_size, long num_slots, int total_tokens, int hq, int hkv, int head_dim, int num_splits, int causal,
+                         int window, void* status, cudaStream_t stream) {
+  return flash_attn_impl(q, k_cache, v_cache, out, part_o, part_lse, work, n_work, cu_q, kv_len, block_table, max_pages, page_size, num_slots, total_tokens, hq, hkv, head_dim, num_splits, causal, window, status, stream, nullptr, nullptr, 0);
+}
+
+// gb_flash_attn with the output written as MXFP8 rows [T, Hq * 128] (one KV split): the operand of the output projection.
+GB_API int gb_flash_attn_mx(const void* q, const void* k_cache, const void* v_cache, void* out_q, void* out_sf, int sf32, const int* work,
+                            int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages, int page_size,
+                            long num_slots, int total_tokens, int hq, int hkv, int head_dim, int causal, int window, void* status,
+                            cudaStream_t stream) {
+  if (out_q == nullptr || out_sf == nullptr) return fail("flash_attn_mx: no output buffer%s");
+  return flash_attn_impl(q, k_cache, v_cache, out_q, nullptr, nullptr, work, n_work, cu_q, kv_len, block_table, max_pages, page_size, num_slots,
+                         total_tokens, hq, hkv, head_dim, 1, causal, window, status, stream, (uint8_t*)out_q, (uint8_t*)out_sf, sf32);
 }
 
 // Decode form of gb_flash_attn: every sequence contributes exactly one query token (cu_q = 0, 1, 2, ...), Hq / Hkv <= 16.

@@ -21,16 +21,16 @@ constexpr int kMaxTopK = 16;
 
 // Routing of token `w` by one warp (E <= 512): lane j < k ends with the j-th pick.  Returns the (possibly local) expert id.
 template <int MAXV>
-__device__ __forceinline__ int route_token_n(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
-                                           float* __restrict__ weights, int w, int lane, int n_exp, int k, int mode, int renorm,
-                                           float routed_scale, int ld, int id_shift, int n_local) {
+__device__ __forceinline__ int route_row(const float* row, const float* __restrict__ bias, int* __restrict__ ids_row,
+                                         float* __restrict__ weights_row, int lane, int n_exp, int k, int mode, int renorm,
+                                         float routed_scale, int id_shift, int n_local) {
   float p[MAXV], sel[MAXV];
   float mx = -FLT_MAX;
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
     const int e = lane + 32 * i;
     float v = -FLT_MAX;
-    if (e < n_exp) { v = logits[(size_t)w * ld + e]; if (!(v == v)) v = -FLT_MAX; }
+    if (e < n_exp) { v = row[e]; if (!(v == v)) v = -FLT_MAX; }
     p[i] = v;
     mx = fmaxf(mx, v);
   }
@@ -81,10 +81,18 @@ __device__ __forceinline__ int route_token_n(const float* __restrict__ logits, c
     // expert-parallel ranks that see every token keep only their own experts: ids become local, the others -1
     const int lid = my_id - id_shift;
     out_id = (n_local > 0 && (lid < 0 || lid >= n_local)) ? -1 : lid;
-    ids[(size_t)w * k + lane] = out_id;
-    weights[(size_t)w * k + lane] = wv * routed_scale;
+    ids_row[lane] = out_id;
+    weights_row[lane] = wv * routed_scale;
   }
   return out_id;
+}
+
+template <int MAXV>
+__device__ __forceinline__ int route_token_n(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ ids,
+                                           float* __restrict__ weights, int w, int lane, int n_exp, int k, int mode, int renorm,
+                                           float routed_scale, int ld, int id_shift, int n_local) {
+  return route_row<MAXV>(logits + (size_t)w * ld, bias, ids + (size_t)w * k, weights + (size_t)w * k, lane, n_exp, k, mode, renorm,
+                         routed_scale, id_shift, n_local);
 }
 
 // The per-lane expert slots are sized to the expert count, so a 128-expert router runs a quarter of the 512-expert code.
@@ -167,6 +175,82 @@ small_linear_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
       if (lane == 0 && m0 + tk < m) out[(size_t)(m0 + tk) * ldo + row] = s;
     }
   }
+}
+
+// Router projection and routing in one launch for decode-sized batches and up to 128 experts: the CTAs of `small_linear_kernel`
+// that share a token group (one per 16 experts) form a thread-block cluster, leave their logits in the shared memory of the
+// cluster's first CTA (distributed shared memory), and after the cluster barrier that CTA routes its 8 tokens, one warp each.
+// The logits never go to global memory and the routing kernel's launch disappears.
+__global__ void __launch_bounds__(256)
+router_route_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, int m, int n, int k, int ldx, int ldw,
+                    const float* __restrict__ bias, int* __restrict__ ids, float* __restrict__ weights, int topk, int mode, int renorm,
+                    float routed_scale, int id_shift, int n_local) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ uint4 sx[];                     // [kSlTok][k / 8] vectors of 8 bf16
+  __shared__ float lg[kSlTok][128];                 // used in the cluster's first CTA: logits of its 8 tokens
+  const int n0 = blockIdx.x * kSlRows, m0 = blockIdx.y * kSlTok;
+  const int kv = k >> 3;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int RPW = kSlRows / 8;
+  constexpr int MAXV = 8;
+  uint4 wr[RPW][MAXV];
+#pragma unroll
+  for (int rr = 0; rr < RPW; ++rr) {
+    const int row = n0 + warp * RPW + rr;
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int v = lane + 32 * i;
+      wr[rr][i] = (row < n && v < kv) ? *reinterpret_cast<const uint4*>(w + (size_t)row * ldw + v * 8) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  for (int i = threadIdx.x; i < kSlTok * kv; i += blockDim.x) {
+    const int tk = i / kv, v = i - tk * kv;
+    sx[i] = (m0 + tk < m) ? *reinterpret_cast<const uint4*>(x + (size_t)(m0 + tk) * ldx + v * 8) : make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  // address of lg in the cluster's CTA 0 (the cluster spans blockIdx.x)
+  uint32_t lg0;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(lg0) : "r"(smem_u32(&lg[0][0])), "r"(0));
+#pragma unroll
+  for (int rr = 0; rr < RPW; ++rr) {
+    const int row = n0 + warp * RPW + rr;
+    float acc[kSlTok];
+#pragma unroll
+    for (int i = 0; i < kSlTok; ++i) acc[i] = 0.f;
+    auto fma_vec = [&](const uint4& wv, int v) {
+      const __nv_bfloat162* wh = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      float wf[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(wh[i]); wf[2 * i] = f.x; wf[2 * i + 1] = f.y; }
+#pragma unroll
+      for (int tk = 0; tk < kSlTok; ++tk) {
+        const uint4 xr = sx[tk * kv + v];
+        const __nv_bfloat162* xh = reinterpret_cast<const __nv_bfloat162*>(&xr);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(xh[i]); acc[tk] += wf[2 * i] * f.x + wf[2 * i + 1] * f.y; }
+      }
+    };
+    if (row < n) {
+#pragma unroll
+      for (int i = 0; i < MAXV; ++i) if (lane + 32 * i < kv) fma_vec(wr[rr][i], lane + 32 * i);
+      for (int v = lane + 32 * MAXV; v < kv; v += 32) fma_vec(*reinterpret_cast<const uint4*>(w + (size_t)row * ldw + v * 8), v);
+    }
+#pragma unroll
+    for (int tk = 0; tk < kSlTok; ++tk) {
+      const float s = warp_sum(acc[tk]);
+      if (lane == 0 && row < n)
+        asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(lg0 + (uint32_t)(tk * 128 + row) * 4u), "f"(s) : "memory");
+    }
+  }
+  // every CTA of the cluster arrives (no early exit above), so the barrier completes; release / acquire orders the remote stores
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (blockIdx.x != 0) return;
+  const int tok = m0 + warp;                         // 8 warps, 8 tokens
+  if (tok >= m) return;
+  route_row<4>(&lg[warp][0], bias, ids + (size_t)tok * topk, weights + (size_t)tok * topk, lane, n, topk, mode, renorm, routed_scale,
+               id_shift, n_local);
 }
 
 constexpr int kPlanBlock = 256;
@@ -424,6 +508,27 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ in, const i
 }  // namespace gb
 
 using namespace gb;
+
+// Router projection + routing for m <= 64 tokens and n_exp <= 128 experts (n_exp % 16 == 0): ids / weights [m, topk] as gb_moe_route
+// writes them.  x bf16 [m, k], w bf16 [n_exp, k]; k % 256 == 0, k <= 8192.
+GB_API int gb_router_route(const void* x, const void* w, int m, int n_exp, int k, int ldx, int ldw, const float* bias, int* ids, float* weights,
+                           int topk, int mode, int renorm, float routed_scale, int id_shift, int n_local, cudaStream_t stream) {
+  if (m <= 0) return 0;
+  if (n_exp > 128 || n_exp % kSlRows != 0 || k % 256 != 0 || k > 8192 || topk > kMaxTopK || topk > 32 || ldx % 8 != 0 || ldw % 8 != 0)
+    return fail("router_route: unsupported shape%s");
+  const size_t smem = (size_t)kSlTok * (k / 8) * sizeof(uint4);
+  static bool attr_set = false;
+  if (!attr_set) {
+    GB_CUDA_OK(cudaFuncSetAttribute(router_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSlTok * (8192 / 8) * (int)sizeof(uint4)));
+    attr_set = true;
+  }
+  const unsigned cx = (unsigned)(n_exp / kSlRows);
+  GB_CUDA_OK(launch_k_cluster(router_route_kernel, dim3(cx, (unsigned)((m + kSlTok - 1) / kSlTok)), 256, smem, stream, cx,
+                              (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, m, n_exp, k, ldx, ldw, bias, ids, weights, topk, mode, renorm,
+                              routed_scale, id_shift, n_local));
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 GB_API int gb_small_linear(const void* x, const void* w, float* out, int m, int n, int k, int ldx, int ldw, int ldo, cudaStream_t stream) {
   if (k % 256 || k > 8192) return fail("small_linear: k must be a multiple of 256 and <= 8192%s");

@@ -255,6 +255,10 @@ class Transformer:
             a_mx = att.attention_decode_mx(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
                                            window=cfg.sliding_window, sf_layout=32 if q.shape[0] <= 32 else 128)
             return self.par.row_linear(lw.wo, None, a_mx)
+        if self.mx and lw.wo.fmt != "bf16" and not cfg.attn_output_gate and FUSE_ATTN_QUANT and att.can_attention_mx(q, fb.num_splits):
+            a_mx = att.attention_mx(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
+                                    causal=True, window=cfg.sliding_window, sf_layout=32 if q.shape[0] <= 32 else 128)
+            return self.par.row_linear(lw.wo, None, a_mx)
         a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
                           num_splits=fb.num_splits, causal=True, window=cfg.sliding_window, decode=fb.is_decode)
         a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
@@ -301,11 +305,10 @@ class Transformer:
         cfg = self.cfg
         t = h.shape[0]
         e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
-        logits = moe.router_logits(h, lw.router)
         if self.mx:
             # token tile (= scale-atom layout) by the expected rows per expert: 32 for decode-sized batches
             tn = 32 if (t * k) // e <= 24 else 128
-            ids, wts, pl = moe.route_plan(logits, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+            ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
             # the RMSNorm before this block already quantised the tokens: gather bytes and scales (every token is quantised
             # once, not once per selected expert)
             xq = ew.mx_gather_rows(h_mx, pl.row_token, sf_layout=tn) if h_mx is not None else ew.mx_quantize(h, pl.row_token, sf_layout=tn)
@@ -317,7 +320,7 @@ class Transformer:
                                     w_tiled=lw.w2.mx.tiled)
         else:
             tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
-            ids, wts, pl = moe.route_plan(logits, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+            ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
             xs = moe.gather_rows(h, pl.row_token)
             act = gemm.grouped_linear(xs, lw.w13.w.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
             y = gemm.grouped_linear(act, lw.w2.w.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)

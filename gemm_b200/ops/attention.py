@@ -107,6 +107,29 @@ def attention_decode_mx(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     return MxTensor(oq, sf, t, hq * d, sf_layout)
 
 
+def attention_mx(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                 block_table: torch.Tensor, page_size: int, work: torch.Tensor, causal: bool = True, window: int = 0, sf_layout: int = 128):
+    """The general (prefill / mixed batch) kernel with the output leaving as the MXFP8 operand of the output projection
+    (``MxTensor`` of ``[T, Hq * D]``): a softmax thread owns a whole (token, head) row, so its scale blocks are thread-local."""
+    from . import elementwise as ew
+    from .mxfp8 import MxTensor
+    t, hq, d = q.shape
+    hkv = k_cache.shape[1]
+    rp = (t + 127) // 128 * 128
+    oq = torch.empty(rp, hq * d, dtype=torch.uint8, device=q.device)
+    sf = ew.sf_alloc(rp, hq * d, q.device, sf_layout, init=False)
+    rc = _native.cuda().gb_flash_attn_mx(_p(q), _p(k_cache), _p(v_cache), _p(oq), _p(sf), _i(1 if sf_layout == 32 else 0), _p(work),
+                                         _i(work.shape[0]), _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
+                                         _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(1 if causal else 0), _i(window),
+                                         _c(_native.status_ptr()), _c(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "gb_flash_attn_mx")
+    return MxTensor(oq, sf, t, hq * d, sf_layout)
+
+
+def can_attention_mx(q: torch.Tensor, num_splits: int) -> bool:
+    return bool(q.is_cuda and num_splits == 1 and q.shape[2] == 128)
+
+
 def can_decode_mx(q: torch.Tensor, hkv: int, num_splits: int, decode: bool) -> bool:
     return bool(decode and USE_DECODE_KERNEL and q.is_cuda and num_splits == 1 and q.shape[2] == 128 and q.shape[1] // hkv <= 16)
 

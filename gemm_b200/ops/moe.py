@@ -81,6 +81,45 @@ def route(logits: torch.Tensor, k: int, mode: str = "softmax", bias: Optional[to
     return ids, w
 
 
+# Off by default: on the 48-layer benchmark model (64 tokens x top-8 of 128 experts per step) the cluster kernel measured 13.55 ms per
+# decode step against 13.45 ms for the projection kernel followed by the routing kernel (8 co-scheduled CTAs and a cluster
+# barrier cost more than the launch they save).  GB_FUSED_ROUTER=1 switches it on.
+FUSED_ROUTER = os.environ.get("GB_FUSED_ROUTER", "0") == "1"
+
+
+def can_route_hidden(h: torch.Tensor, w: torch.Tensor, k: int) -> bool:
+    """Shapes the fused router projection + routing kernel takes: decode-sized batches, at most 128 experts."""
+    e, hid = w.shape
+    return bool(FUSED_ROUTER and h.is_cuda and h.shape[0] <= 64 and e <= 128 and e % 16 == 0 and hid % 256 == 0 and hid <= 8192 and k <= 16
+                and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and h.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
+
+
+def route_hidden(h: torch.Tensor, w: torch.Tensor, k: int, mode: str = "softmax", bias: Optional[torch.Tensor] = None, renorm: bool = True,
+                 routed_scale: float = 1.0, local_range: Optional[Tuple[int, int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``route(router_logits(h, w), ...)`` in one launch (a thread-block cluster per 8 tokens keeps the logits in shared memory).
+    Falls back to the two ops for shapes ``can_route_hidden`` refuses."""
+    if not can_route_hidden(h, w, k):
+        return route(router_logits(h, w), k, mode, bias, renorm, routed_scale, local_range)
+    t, e = h.shape[0], w.shape[0]
+    ids = torch.empty(t, k, dtype=torch.int32, device=h.device)
+    wt = torch.empty(t, k, dtype=torch.float32, device=h.device)
+    rc = _native.cuda().gb_router_route(_p(h), _p(w), _i(t), _i(e), _i(h.shape[1]), _i(h.stride(0)), _i(w.stride(0)), _p(bias), _p(ids), _p(wt),
+                                        _i(k), _i(0 if mode == "softmax" else 1), _i(1 if renorm else 0), _f(routed_scale),
+                                        _i(local_range[0] if local_range else 0), _i(local_range[1] if local_range else 0), _s())
+    _native.check(rc, "gb_router_route")
+    return ids, wt
+
+
+def route_plan_hidden(h: torch.Tensor, w: torch.Tensor, k: int, n_exp: int, align: int, mode: str = "softmax",
+                      bias: Optional[torch.Tensor] = None, renorm: bool = True, routed_scale: float = 1.0,
+                      local_range: Optional[Tuple[int, int]] = None, regions: int = 1, epoch_ctr: int = 0, region_rows: Optional[int] = None):
+    """Router projection, routing and plan from the hidden rows: ``(ids, weights, MoePlan)`` (see ``route_plan``)."""
+    if can_route_hidden(h, w, k) and h.shape[0] * k > FUSED_ROUTE_PAIRS:
+        ids, wt = route_hidden(h, w, k, mode, bias, renorm, routed_scale, local_range)
+        return ids, wt, plan(ids, n_exp, align, regions, epoch_ctr=epoch_ctr, region_rows=region_rows)
+    return route_plan(router_logits(h, w), k, n_exp, align, mode, bias, renorm, routed_scale, local_range, regions, epoch_ctr, region_rows)
+
+
 @dataclass
 class MoePlan:
     seg_start: torch.Tensor      # int32 [E]   first row of each expert's segment

@@ -193,13 +193,12 @@ class ExpertParallel:
         cap = g["cap"]
         g["stage"][:t].copy_(h)
         allh = g["ag"].all_gather(g["stage"]).view(torch.bfloat16).view(w * cap, hid)
-        logits = moe.router_logits(allh, lw.router)
         rt = dict(mode=cfg.router, bias=lw.router_bias, renorm=cfg.norm_topk, routed_scale=cfg.routed_scale,
                   local_range=(self.ep_rank * self.e_local, self.e_local))
         if self.mx:
             from ..models.transformer import expert_gate_up_mx
             tn = 32
-            ids, wts, pl = moe.route_plan(logits, k, self.e_local, tn, **rt)
+            ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
             xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
             hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
             hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)
@@ -208,7 +207,7 @@ class ExpertParallel:
                                     w_tiled=lw.w2.mx.tiled)
         else:
             tn = gemm.pick_tn(max(1, (w * cap * k + cfg.n_experts - 1) // cfg.n_experts), dual=True)
-            ids, wts, pl = moe.route_plan(logits, k, self.e_local, tn, **rt)
+            ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
             xs = moe.gather_rows(allh, pl.row_token)
             act = gemm.grouped_linear(xs, lw.w13.w.view(self.e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
             y = gemm.grouped_linear(act, lw.w2.w.view(self.e_local, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)

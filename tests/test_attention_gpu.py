@@ -130,3 +130,23 @@ def test_decode_kernel_mxfp8_output(b, lay):
     sw = mxfp8.unpack_sf_atoms(want.sf, b, hq * 4, lay).int()
     assert (sg - sw).abs().max().item() <= 1
     assert _rel(got_f, want_f) < 2e-2
+
+
+def test_prefill_kernel_mxfp8_output():
+    """The general kernel's MXFP8 output equals quantising its bf16 output (mixed batch: prefill chunks and a decode row)."""
+    from gemm_b200.ops import elementwise as ew
+    from gemm_b200.ops import mxfp8
+    hq, hkv, page = 32, 4, 16
+    q_lens, ctx = [150, 1, 40], [0, 77, 200]
+    q, kc, vc, cu, kvl, bt = _setup(q_lens, ctx, hq, hkv, page, seed=8)
+    work = att.build_work(q_lens, hq, hkv, 1).cuda()
+    out = att.attention(q, kc, vc, cu, kvl, bt, page, work)
+    t = sum(q_lens)
+    om = att.attention_mx(q, kc, vc, cu, kvl, bt, page, work, sf_layout=128)
+    _native.assert_status_ok()
+    want = ew.mx_quantize(out.reshape(t, hq * 128), sf_layout=128)
+    sg = mxfp8.unpack_sf_atoms(om.sf, t, hq * 4, 128).int()
+    sw = mxfp8.unpack_sf_atoms(want.sf, t, hq * 4, 128).int()
+    assert (sg - sw).abs().max().item() <= 1
+    assert _rel(mxfp8.dequantize(om), mxfp8.dequantize(want)) < 2e-2
+    assert _rel(mxfp8.dequantize(om), out.reshape(t, hq * 128)) < 4e-2

@@ -262,3 +262,18 @@ def test_route_plan_single_kernel(t, local, monkeypatch):
     assert torch.equal(ids, ids2) and torch.equal(w, w2)
     for a, b in ((pl.seg_start, pl2.seg_start), (pl.seg_count, pl2.seg_count), (pl.pair_row, pl2.pair_row), (pl.row_token, pl2.row_token)):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("t,e,local,mode", [(64, 128, None, "softmax"), (5, 128, (32, 16), "softmax"), (33, 64, None, "sigmoid"), (8, 16, None, "softmax")])
+def test_route_hidden_cluster_kernel(t, e, local, mode, monkeypatch):
+    """Router projection + routing in one cluster launch equals the projection kernel followed by the routing kernel."""
+    torch.manual_seed(31)
+    hid, k = 2048, 8
+    h = torch.randn(t, hid, device="cuda").bfloat16()
+    w = (torch.randn(e, hid, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(e, device="cuda") * 0.1 if mode == "sigmoid" else None
+    monkeypatch.setattr(moe, "FUSED_ROUTER", True)
+    assert moe.can_route_hidden(h, w, k)
+    ids, wt = moe.route_hidden(h, w, k, mode, bias, True, 1.5, local)
+    ids2, wt2 = moe.route(moe.router_logits(h, w), k, mode, bias, True, 1.5, local)
+    assert torch.equal(ids, ids2) and torch.equal(wt, wt2)
