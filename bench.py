@@ -43,6 +43,9 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: run fewer layers (the JSON line then says so and is not a valid bench number)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "ep", "tp"],
+                    help="multi-GPU layout: ep = experts sharded, attention data-parallel (MoE models); tp = every projection sharded, "
+                         "batch replicated (dense models); auto picks by model")
     ap.add_argument("--moe-path", default="fused", choices=["fused", "nccl"], help="multi-GPU expert exchange: fused peer-memory kernels or the NCCL baseline")
     return ap.parse_args()
 
@@ -156,20 +159,30 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     par = None
+    cfg0 = get_config(args.model)
+    layout = args.parallel if args.parallel != "auto" else ("ep" if cfg0.n_experts > 0 else "tp")
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-        from gemm_b200.parallel.expert import ExpertParallel
-        par = ExpertParallel(dist.group.WORLD, device, fused=(args.moe_path == "fused"))
+        if layout == "ep":
+            from gemm_b200.parallel.expert import ExpertParallel
+            par = ExpertParallel(dist.group.WORLD, device, fused=(args.moe_path == "fused"))
+        else:
+            from gemm_b200.parallel.tensor import TensorParallel
+            par = TensorParallel(dist.group.WORLD, device, fused=(args.moe_path == "fused"))
     if args.gpus != world and rank == 0:
         print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
     n_gpus = world
 
     cfg = get_config(args.model)
     n_layers = args.layers if args.layers > 0 else cfg.n_layers
-    assert args.batch % n_gpus == 0
-    b_local = args.batch // n_gpus
+    tp = layout == "tp" and n_gpus > 1
+    assert tp or args.batch % n_gpus == 0
+    b_local = args.batch if tp else args.batch // n_gpus          # tensor parallelism replicates the batch on every rank
     t0 = time.time()
-    weights = synthetic_weights(cfg, args.fmt, device=device, seed=0, ep_rank=rank, ep_size=n_gpus, n_layers=n_layers)
+    if tp:
+        weights = synthetic_weights(cfg, args.fmt, device=device, seed=0, tp_rank=rank, tp_size=n_gpus, n_layers=n_layers)
+    else:
+        weights = synthetic_weights(cfg, args.fmt, device=device, seed=0, ep_rank=rank, ep_size=n_gpus, n_layers=n_layers)
     torch.cuda.synchronize()
     if rank == 0:
         print(f"[bench] weights {weights.nbytes() / 2**30:.1f} GiB on rank 0 in {time.time() - t0:.1f}s", file=sys.stderr)
@@ -182,7 +195,7 @@ def main():
     # synthetic prompts: uniform token ids from seed 0 (the same global batch whatever N is)
     g = torch.Generator().manual_seed(0)
     all_prompts = torch.randint(0, cfg.vocab, (args.batch, args.prompt_len), generator=g, dtype=torch.int32)
-    prompts = [all_prompts[rank * b_local + i] for i in range(b_local)]
+    prompts = [all_prompts[(0 if tp else rank * b_local) + i] for i in range(b_local)]
 
     def barrier():
         if world > 1:
@@ -270,7 +283,7 @@ def main():
             "vs_baseline": None, "dtype": "mxfp8 weights+activations, bf16 outputs, fp32 accumulate" if args.fmt == "mxfp8" else "bf16",
             "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "config": {"model": args.model, "global_batch": args.batch, "seq_len": args.prompt_len, "decode_context": args.prompt_len + args.warmup,
-                       "parallelism": f"dp{n_gpus}-attention+ep{n_gpus}" if n_gpus > 1 else "single", "layers": n_layers,
+                       "parallelism": (f"tp{n_gpus}" if tp else f"dp{n_gpus}-attention+ep{n_gpus}") if n_gpus > 1 else "single", "layers": n_layers,
                        "l2": "no flush: each step streams ~29 GB of expert weights and ~13 GB of KV over the job, inputs >> 126 MB L2",
                        "moe_path": args.moe_path if n_gpus > 1 else "local"},
             "prefill_tokens_per_s": prefill_tok_s, "ttft_ms_p50": prefill_ms, "tpot_ms_p50": tpot_p50,

@@ -189,6 +189,11 @@ def apply_linear_split(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTenso
     """``apply_linear`` for a projection whose result goes into the residual stream: a decode-sized MXFP8 projection with few
     output tiles (o_proj: 16 tiles of 128 rows, 32 k-steps each) is cut along K so that it fills the GPU, and the partial sums
     are left for the residual add + RMSNorm kernel that follows."""
+    if lw.fmt == "bf16" and SPLIT_PROJ and x is not None and x.is_cuda and lw.n % 128 == 0:
+        sp = gemm.pick_partials(lw.n, x.shape[0], lw.k, False)
+        if sp > 1:
+            return gemm.linear_partials(x, lw.w, sp, bias=lw.bias, w_tiled=lw.tiled)
+        return apply_linear(lw, x, x_mx)
     if lw.fmt != "bf16" and SPLIT_PROJ:
         xm = x_mx if x_mx is not None else (ew.mx_quantize(x, sf_layout=32 if x.shape[0] <= 32 else 128) if x.is_cuda else None)
         if xm is not None and xm.data.is_cuda:

@@ -236,6 +236,18 @@ def pick_partials(n_out: int, m_tok: int, k: int, mx: bool) -> int:
     return 1
 
 
+def linear_partials(x: torch.Tensor, w: torch.Tensor, splits: int, bias: Optional[torch.Tensor] = None, w_tiled: bool = False) -> PendingPartials:
+    """bf16 ``linear`` with the K range cut into ``splits`` CTAs per output tile, one fp32 partial slab per split (GPU only)."""
+    m, k = x.shape
+    n = w.shape[0]
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    out = torch.empty(splits, m, n, dtype=torch.float32, device=x.device)
+    ex = GemmExtras()
+    ex.splits, ex.partial_stride = splits, m * n
+    _launch(w, x, out, n, k, m, w.stride(0), x.stride(0), n, GEMM_OUT_F32 | (GEMM_W_TILED if w_tiled else 0), pick_tn(m), bias=bias, extras=ex)
+    return PendingPartials(out)
+
+
 def linear_mx_partials(x: MxTensor, w: MxTensor, splits: int, bias: Optional[torch.Tensor] = None) -> PendingPartials:
     """``linear_mx`` with the K range cut into ``splits`` CTAs per output tile; every split stores its fp32 partial (the bias
     goes into split 0).  GPU only."""

@@ -282,3 +282,18 @@ def test_linear_mx_partials_feed_the_norm(m, n, k):
     got = ew.rmsnorm(pend, nw, 1e-6, residual=res)
     want = ew.rmsnorm(pend.materialize(), nw, 1e-6, residual=res2)
     assert _rel(got, want) < 1e-2 and _rel(res, res2) < 1e-2
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 4096, 12288), (8, 1024, 4096)])
+def test_linear_bf16_partials(m, n, k):
+    torch.manual_seed(42)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(n, device="cuda")
+    sp = gemm.pick_partials(n, m, k, False)
+    assert sp > 1
+    pend = gemm.linear_partials(x, w, sp, bias=bias)
+    _native.assert_status_ok()
+    ref = x.float() @ w.float().t() + bias
+    assert _rel(pend.buf.sum(0), ref) < 2e-3
+    assert _rel(pend.materialize(), gemm.linear(x, w, bias=bias)) < 1e-2
