@@ -462,6 +462,48 @@ silu_mul_quant_kernel(const __nv_bfloat16* __restrict__ gate_up, const int* __re
   }
 }
 
+// SiLU(gate) * up from K-split partial sums: part f32 [n_part][rows][2 * inter] (gate columns first).  The slabs are added in
+// split order; the result goes out as bf16 and / or as MXFP8 with scale atoms.  8 elements per thread, 4 threads share a scale.
+__global__ void __launch_bounds__(256)
+silu_mul_partials_kernel(const float* __restrict__ part, int n_part, long part_stride, __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ out_q,
+                         uint8_t* __restrict__ out_sf, long rows, int inter, int sf32) {
+  pdl_wait();
+  pdl_trigger();
+  const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int vec_per_row = inter >> 3;
+  const long r = idx / vec_per_row;
+  const int vi = (int)(idx - r * vec_per_row);
+  const bool live = r < rows;
+  float y[8];
+  float amax = 0.f;
+  if (live) {
+    float g[8], u[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { g[j] = 0.f; u[j] = 0.f; }
+    const float* pp = part + r * (2L * inter) + vi * 8;
+    for (int p = 0; p < n_part; ++p, pp += part_stride) {
+      const float4 g0 = *reinterpret_cast<const float4*>(pp), g1 = *reinterpret_cast<const float4*>(pp + 4);
+      const float4 u0 = *reinterpret_cast<const float4*>(pp + inter), u1 = *reinterpret_cast<const float4*>(pp + inter + 4);
+      g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
+      u[0] += u0.x; u[1] += u0.y; u[2] += u0.z; u[3] += u0.w; u[4] += u1.x; u[5] += u1.y; u[6] += u1.z; u[7] += u1.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { y[j] = g[j] / (1.0f + __expf(-g[j])) * u[j]; amax = fmaxf(amax, fabsf(y[j])); }
+    if (out != nullptr) store8(out + r * inter + vi * 8, y);
+  }
+  if (out_q == nullptr) return;
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  if (!live) return;
+  const int e = e8m0_amax(amax);
+  const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+  uint8_t q[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(y[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
+  *reinterpret_cast<uint2*>(out_q + r * inter + vi * 8) = *reinterpret_cast<uint2*>(q);
+  if ((vi & 3) == 0) out_sf[sf_atom_offset(r, vi >> 2, inter >> 7, sf32)] = (uint8_t)e;
+}
+
 // ------------------------------------------------------------------------------------------ mxfp8 quantiser
 // out row r <- in row (src_rows ? src_rows[r] : r); rows whose source is negative are zero-filled with
 // scale 1.  One warp per 256 elements: lane holds 8 elements, 4 lanes share a scale.
@@ -755,6 +797,18 @@ GB_API int gb_silu_mul_quant(const void* gate_up, const int* row_valid, void* ou
   if (n <= 0) return 0;
   launch_k(silu_mul_quant_kernel, (unsigned)((n + 256 * kSiluU - 1) / (256 * kSiluU)), 256, 0, stream, (const __nv_bfloat16*)gate_up, row_valid, (uint8_t*)out_q,
            (uint8_t*)out_sf, rows, inter, ld, sf32);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_silu_mul_partials(const float* part, int n_part, long part_stride, void* out, void* out_q, void* out_sf, long rows, int inter,
+                                int sf32, cudaStream_t stream) {
+  if (inter % 8 || (out_q != nullptr && inter % 128)) return fail("silu_mul_partials: inter must be a multiple of 8 (128 with MXFP8 output)%s");
+  if (part_stride % 4 != 0 || ((uintptr_t)part & 15) != 0) return fail("silu_mul_partials: misaligned partials%s");
+  const long n = rows * (inter / 8);
+  if (n <= 0) return 0;
+  launch_k(silu_mul_partials_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, part, n_part, part_stride, (__nv_bfloat16*)out, (uint8_t*)out_q,
+           (uint8_t*)out_sf, rows, inter, sf32);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -543,6 +543,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tc_wait_ld();
           if (c >= t.valid) continue;
           if (!store_ok) continue;
+          if (DUAL && args.partial_stride > 0) {
+            // K-split partials of a gate/up pair: both raw sums are stored (gate at column n, up at n_out + n of a 2 * n_out wide
+            // slab); the activation needs the full sums and is applied by the kernel that adds the slabs
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c + j < t.valid) {
+                o32[(size_t)(c + j) * args.ldo] = __uint_as_float(r0[j]);
+                o32[(size_t)(c + j) * args.ldo + args.n_out] = __uint_as_float(r1[j]);
+              }
+            continue;
+          }
           if (c + 16 <= t.valid) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -730,7 +741,7 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
     a.amax_val = ex->amax_val; a.amax_idx = ex->amax_idx; a.peer_bcast = ex->peer_bcast; a.epoch_self_tick = ex->epoch_self_tick;
     a.sfa_bytes = ex->sfa_bytes; a.sfb_bytes = ex->sfb_bytes; a.out_bytes = ex->out_bytes; a.out_sf_bytes = ex->out_sf_bytes;
     if (ex->splits > 1 && num_groups == 0 && ex->partial_stride > 0) {
-      if (!(flags & GEMM_OUT_F32) || dual || qo) return fail("gemm: split-K partials need a plain fp32 output%s");
+      if (!(flags & GEMM_OUT_F32) || qo) return fail("gemm: split-K partials need a plain fp32 output%s");
       const int kb_elems = mx ? 128 : 64;
       const int num_kb = (k + kb_elems - 1) / kb_elems;
       const int kb_per = (num_kb + ex->splits - 1) / ex->splits;

@@ -298,11 +298,21 @@ class Transformer:
         return y
 
     def dense_ffn(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor]) -> torch.Tensor:
-        if lw.w_gate_up.fmt == "bf16":
-            act = gemm.linear_swiglu(h, lw.w_gate_up.w, w_tiled=lw.w_gate_up.tiled)
+        gu = lw.w_gate_up
+        inter = gu.n // 2
+        if gu.fmt == "bf16":
+            sp = gemm.pick_partials_dual(inter, h.shape[0], gu.k, False) if (SPLIT_PROJ and h.is_cuda and inter % 128 == 0) else 1
+            if sp > 1:      # decode-sized batch: the projection is cut along K to fill the GPU, the activation kernel adds the partials
+                act = ew.silu_mul_partials(gemm.swiglu_partials(h, gu.w, sp, w_tiled=gu.tiled))
+            else:
+                act = gemm.linear_swiglu(h, gu.w, w_tiled=gu.tiled)
             return self.par.row_linear(lw.w_down, act)
         xm = h_mx if h_mx is not None else ew.mx_quantize(h, sf_layout=32 if h.shape[0] <= 32 else 128)
-        act = gemm.linear_mx_swiglu_quant(xm, lw.w_gate_up.mx)
+        sp = gemm.pick_partials_dual(inter, xm.rows, gu.k, True) if (SPLIT_PROJ and xm.data.is_cuda and inter % 128 == 0) else 1
+        if sp > 1:
+            act = ew.silu_mul_partials(gemm.swiglu_partials(xm, gu.mx, sp), quantize=True, sf_layout=xm.sf_layout)
+        else:
+            act = gemm.linear_mx_swiglu_quant(xm, gu.mx)
         return self.par.row_linear(lw.w_down, None, act)
 
     def moe_local(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor] = None) -> torch.Tensor:

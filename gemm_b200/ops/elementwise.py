@@ -243,6 +243,29 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def silu_mul_partials(pend, quantize: bool = False, sf_layout: int = 128):
+    """SiLU(gate) * up from the K-split partial sums of ``ops.gemm.swiglu_partials`` (``pend.buf`` f32 ``[S, M, 2I]``): bf16 ``[M, I]``, or
+    an ``MxTensor`` when ``quantize``."""
+    s_, m, two_i = pend.buf.shape
+    inter = two_i // 2
+    if not pend.buf.is_cuda:
+        y = pend.buf.sum(0)
+        h = torch.nn.functional.silu(y[:, :inter]) * y[:, inter:]
+        return mxfp8.quantize(h, sf_layout=sf_layout) if quantize else h.to(torch.bfloat16)
+    dev = pend.buf.device
+    out = q = sf = None
+    if quantize:
+        rp = (m + 127) // 128 * 128
+        q = torch.empty(rp, inter, dtype=torch.uint8, device=dev)
+        sf = sf_alloc(rp, inter, dev, sf_layout, init=False)
+    else:
+        out = torch.empty(m, inter, dtype=torch.bfloat16, device=dev)
+    rc = _native.cuda().gb_silu_mul_partials(_p(pend.buf), _i(s_), _l(m * two_i), _p(out), _p(q), _p(sf), _l(m), _i(inter),
+                                             _i(1 if sf_layout == 32 else 0), _s())
+    _native.check(rc, "gb_silu_mul_partials")
+    return MxTensor(q, sf, m, inter, sf_layout) if quantize else out
+
+
 def silu_mul_quant(gate_up: torch.Tensor, out_q: torch.Tensor, out_sf: torch.Tensor, row_valid: Optional[torch.Tensor] = None,
                    sf_layout: int = 128) -> None:
     """``SiLU(gate) * up`` of ``gate_up [rows, 2I]`` (bf16) quantised to MXFP8 into ``out_q [rows, I]`` / ``out_sf`` (scale atoms of

@@ -221,19 +221,25 @@ class PendingPartials:
         return self.buf.sum(0).to(torch.bfloat16)
 
 
-def pick_partials(n_out: int, m_tok: int, k: int, mx: bool) -> int:
-    """Number of K splits for ``linear_mx_partials``: enough to give every SM a tile, at least 4 k-steps per split."""
+def pick_partials(n_out: int, m_tok: int, k: int, mx: bool, sms: int = 148) -> int:
+    """Number of K splits for a decode-sized projection: the split count (at most 8, at least 4 k-steps per split, no empty split)
+    that fills the last wave of CTAs best; ties go to fewer splits.  96 tiles -> 3 splits (288 CTAs = 1.95 waves), 16 tiles -> 8."""
     if m_tok > 64:
         return 1
     tiles = (n_out + 127) // 128
     num_kb = k // (128 if mx else 64)
-    want = min(8, 148 // max(tiles, 1), num_kb // 4)
-    while want > 1:
-        kb_per = -(-num_kb // want)
-        if -(-num_kb // kb_per) == want:
-            return want
-        want -= 1
-    return 1
+    best, best_eff = 1, 0.0
+    for sp in range(1, 9):
+        if sp > 1 and num_kb // sp < 4:
+            break
+        kb_per = -(-num_kb // sp)
+        if -(-num_kb // kb_per) != sp:
+            continue
+        units = tiles * sp
+        eff = units / (-(-units // sms) * sms)
+        if eff > best_eff * 1.05:
+            best, best_eff = sp, eff
+    return best
 
 
 def linear_partials(x: torch.Tensor, w: torch.Tensor, splits: int, bias: Optional[torch.Tensor] = None, w_tiled: bool = False) -> PendingPartials:
@@ -245,6 +251,38 @@ def linear_partials(x: torch.Tensor, w: torch.Tensor, splits: int, bias: Optiona
     ex = GemmExtras()
     ex.splits, ex.partial_stride = splits, m * n
     _launch(w, x, out, n, k, m, w.stride(0), x.stride(0), n, GEMM_OUT_F32 | (GEMM_W_TILED if w_tiled else 0), pick_tn(m), bias=bias, extras=ex)
+    return PendingPartials(out)
+
+
+def pick_partials_dual(inter: int, m_tok: int, k: int, mx: bool) -> int:
+    """K splits for a decode-sized gate/up projection (a tile = 128 gate rows + 128 up rows)."""
+    return pick_partials(inter, m_tok, k, mx)
+
+
+def swiglu_partials(x, w_gate_up, splits: int, w_tiled: bool = False) -> PendingPartials:
+    """Gate/up projection cut along K: raw fp32 partial sums ``[splits, M, 2I]`` (gate columns first); ``ops.elementwise.silu_mul_partials``
+    adds the slabs and applies SiLU(gate) * up.  ``x`` / ``w_gate_up`` are bf16 tensors or ``MxTensor`` operands.  GPU only."""
+    mx = isinstance(x, MxTensor)
+    if mx:
+        m, k, two_i = x.rows, x.k, w_gate_up.rows
+        xd, wd, dev = x.data, w_gate_up.data, x.data.device
+        tn = 64 if (x.sf_layout == 128 and m <= 64) else x.sf_layout
+        flags = GEMM_MX | GEMM_DUAL | GEMM_OUT_F32 | (GEMM_W_TILED if w_gate_up.tiled else 0)
+        kw = dict(x_rows=xd.shape[0], sfa=w_gate_up.sf, sfb=x.sf)
+        ldw = ldx = k
+    else:
+        m, k = x.shape
+        two_i = w_gate_up.shape[0]
+        xd, wd, dev = x, w_gate_up, x.device
+        tn = pick_tn(m, dual=True)
+        flags = GEMM_DUAL | GEMM_OUT_F32 | (GEMM_W_TILED if w_tiled else 0)
+        kw = {}
+        ldw, ldx = w_gate_up.stride(0), x.stride(0)
+    inter = two_i // 2
+    out = torch.empty(splits, m, two_i, dtype=torch.float32, device=dev)
+    ex = GemmExtras()
+    ex.splits, ex.partial_stride = splits, m * two_i
+    _launch(wd, xd, out, inter, k, m, ldw, ldx, two_i, flags, tn, up_row_offset=inter, extras=ex, **kw)
     return PendingPartials(out)
 
 

@@ -297,3 +297,25 @@ def test_linear_bf16_partials(m, n, k):
     ref = x.float() @ w.float().t() + bias
     assert _rel(pend.buf.sum(0), ref) < 2e-3
     assert _rel(pend.materialize(), gemm.linear(x, w, bias=bias)) < 1e-2
+
+
+@pytest.mark.parametrize("mx", [False, True])
+def test_swiglu_from_k_split_partials(mx):
+    from gemm_b200.ops import elementwise as ew
+    torch.manual_seed(43)
+    m, inter, k = 32, 1536, 4096
+    x = torch.randn(m, k, device="cuda")
+    w = torch.randn(2 * inter, k, device="cuda") * 0.03
+    sp = gemm.pick_partials_dual(inter, m, k, mx)
+    assert sp > 1
+    if mx:
+        xq, wq = mxfp8.quantize(x, sf_layout=32), mxfp8.quantize(w)
+        got = ew.silu_mul_partials(gemm.swiglu_partials(xq, wq, sp), quantize=True, sf_layout=32)
+        want = gemm.linear_mx_swiglu_quant(xq, wq)
+        _native.assert_status_ok()
+        assert _rel(mxfp8.dequantize(got), mxfp8.dequantize(want)) < 2e-2
+    else:
+        got = ew.silu_mul_partials(gemm.swiglu_partials(x.bfloat16(), w.bfloat16(), sp))
+        want = gemm.linear_swiglu(x.bfloat16(), w.bfloat16())
+        _native.assert_status_ok()
+        assert _rel(got, want) < 1e-2
