@@ -65,7 +65,7 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
                uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out, int sf32,
                const float* __restrict__ partials, int n_partials, long partial_stride, const uint32_t* wait_flags, int wait_n,
                const uint32_t* epoch_ptr, KernelStatus* st, const __nv_bfloat16* __restrict__ comb_y, const int* __restrict__ comb_rows,
-               const float* __restrict__ comb_w, int comb_k, int comb_ld) {
+               const float* __restrict__ comb_w, int comb_k, int comb_ld, int part_inner, long part_inner_stride) {
   pdl_wait();
   pdl_trigger();
   const int row = blockIdx.x;
@@ -104,8 +104,11 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
           // all-reduce fused into its consumer: sum the ranks' fp32 partials in rank order (bit-identical everywhere)
 #pragma unroll
           for (int j = 0; j < 8; ++j) d[j] = 0.f;
+          // partial p = (rank, K split): ranks are partial_stride apart, the splits of one rank part_inner_stride
           for (int p = 0; p < n_partials; ++p) {
-            const float4* src = reinterpret_cast<const float4*>(partials + (size_t)p * partial_stride + (size_t)row * hidden + vi * 8);
+            const int po = p / part_inner, pi = p - po * part_inner;
+            const float4* src = reinterpret_cast<const float4*>(partials + (size_t)po * partial_stride + (size_t)pi * part_inner_stride +
+                                                                (size_t)row * hidden + vi * 8);
             const float4 a = src[0], b = src[1];
             d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w; d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
           }
@@ -697,7 +700,8 @@ static int rmsnorm_launch(void* residual, const void* delta, const void* x_in, c
                           int rows, int hidden, float eps, int ld_in, int ld_out, int sf32, const float* partials, int n_partials,
                           long partial_stride, const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream,
                           const void* comb_y = nullptr, const int* comb_rows = nullptr, const float* comb_w = nullptr, int comb_k = 0,
-                          int comb_ld = 0) {
+                          int comb_ld = 0, int part_inner = 1, long part_inner_stride = 0) {
+  if (part_inner < 1) part_inner = 1;
   if (comb_k > 16) return fail("rmsnorm: combine of more than 16 rows%s");
   if (hidden % 8 || hidden > 256 * 8 * 4) return fail("rmsnorm: hidden must be a multiple of 8 and <= 8192%s");
   if (out_q != nullptr && hidden % 128) return fail("rmsnorm: MXFP8 output needs hidden %% 128 == 0%s");
@@ -706,7 +710,7 @@ static int rmsnorm_launch(void* residual, const void* delta, const void* x_in, c
 #define GB_RMS(V) launch_k(rmsnorm_kernel<V>, rows, 256, 0, stream, (__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, \
     (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out, sf32, \
     partials, n_partials, partial_stride, (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status, \
-    (const __nv_bfloat16*)comb_y, comb_rows, comb_w, comb_k, comb_ld)
+    (const __nv_bfloat16*)comb_y, comb_rows, comb_w, comb_k, comb_ld, part_inner, part_inner_stride)
   if (nvec <= 256) GB_RMS(1); else if (nvec <= 512) GB_RMS(2); else if (nvec <= 768) GB_RMS(3); else GB_RMS(4);
 #undef GB_RMS
   GB_CUDA_OK(cudaGetLastError());
@@ -726,6 +730,16 @@ GB_API int gb_rmsnorm_reduce(void* residual, const float* partials, int n_partia
                              const void* epoch_ptr, void* status, cudaStream_t stream) {
   return rmsnorm_launch(residual, nullptr, nullptr, weight, out, out_q, out_sf, rows, hidden, eps, hidden, hidden, sf32, partials, n_partials,
                         partial_stride, wait_flags, wait_n, epoch_ptr, status, stream);
+}
+
+// The same when every rank's slot holds `n_inner` K-split partials, `inner_stride` elements apart: n_ranks * n_inner slabs are summed
+// (rank-major, split-minor order).
+GB_API int gb_rmsnorm_reduce2(void* residual, const float* partials, int n_ranks, long rank_stride, int n_inner, long inner_stride,
+                              const void* weight, void* out, void* out_q, void* out_sf, int rows, int hidden, float eps, int sf32,
+                              const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream) {
+  return rmsnorm_launch(residual, nullptr, nullptr, weight, out, out_q, out_sf, rows, hidden, eps, hidden, hidden, sf32, partials,
+                        n_ranks * (n_inner < 1 ? 1 : n_inner), rank_stride, wait_flags, wait_n, epoch_ptr, status, stream, nullptr, nullptr, nullptr, 0,
+                        0, n_inner, inner_stride);
 }
 
 // residual[t] += sum_j w[t, j] * y[pair_row[t * k + j]] (the MoE combine), then RMSNorm: the combine never makes a round trip

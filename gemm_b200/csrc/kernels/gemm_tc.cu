@@ -416,8 +416,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             if (args.row_map != nullptr) orow = args.row_map[x_row];
             if (args.peer_bcast > 0) {
               // row-parallel partial result: the same value goes into this rank's slot on every GPU of the group
+              const size_t po = (size_t)t.ks * (size_t)args.partial_stride;      // K-split partials: one slab per split inside the slot
               for (int p = 0; p < args.peer_bcast; ++p) {
-                if (args.out_f32) ((float*)args.peer_out[p])[(size_t)orow * args.ldo + n] = v;
+                if (args.out_f32) ((float*)args.peer_out[p])[po + (size_t)orow * args.ldo + n] = v;
                 else ((__nv_bfloat16*)args.peer_out[p])[(size_t)orow * args.ldo + n] = __float2bfloat16(v);
               }
             } else if (orow >= 0) {

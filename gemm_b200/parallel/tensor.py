@@ -37,6 +37,7 @@ class PendingReduce:
     chan: int
     rows: int
     hidden: int
+    splits: int = 1          # K-split slabs per rank inside its slot
 
 
 class TensorParallel:
@@ -98,6 +99,14 @@ class TensorParallel:
         self._chan ^= 1
         n, k = lw.n, lw.k
         ex = self._extras[ch]
+        # decode-sized batches: the shard's K range is cut further, every split stores its own slab inside this rank's slot
+        sp = gemm.pick_partials(n, rows, k, lw.fmt != "bf16") if n % 128 == 0 else 1
+        while sp > 1 and sp * rows * n > self.slot_elems:
+            sp -= 1
+        kb = k // (64 if lw.fmt == "bf16" else 128)
+        if sp > 1 and -(-kb // -(-kb // sp)) != sp:
+            sp = 1
+        ex.splits, ex.partial_stride = (sp, rows * n) if sp > 1 else (0, 0)
         if lw.fmt == "bf16":
             tn = gemm.pick_tn(rows)
             gemm._launch(lw.w, x, None, n, k, rows, lw.w.stride(0), x.stride(0), n, gemm.GEMM_OUT_F32 | (gemm.GEMM_W_TILED if lw.tiled else 0), tn, bias=None,
@@ -106,7 +115,7 @@ class TensorParallel:
             xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if rows <= 32 else 128)
             gemm._launch(lw.mx.data, xm.data, None, n, k, rows, k, k, n, gemm.GEMM_MX | gemm.GEMM_OUT_F32 | (gemm.GEMM_W_TILED if lw.mx.tiled else 0), xm.sf_layout,
                          x_rows=xm.data.shape[0], sfa=lw.mx.sf, sfb=xm.sf, extras=ex)
-        return PendingReduce(ch, rows, n)
+        return PendingReduce(ch, rows, n, max(sp, 1))
 
     def _reduce_norm(self, pr: PendingReduce, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128):
         f = self.fab
@@ -115,14 +124,15 @@ class TensorParallel:
         q = sf = None
         if quantize:
             rp = (rows + 127) // 128 * 128
-            q = torch.zeros(rp, hidden, dtype=torch.uint8, device=self.device)
-            sf = ew.sf_alloc(rp, hidden, self.device, sf_layout)
+            q = torch.empty(rp, hidden, dtype=torch.uint8, device=self.device)
+            sf = ew.sf_alloc(rp, hidden, self.device, sf_layout, init=False)
         p = lambda t: _c(t.data_ptr()) if t is not None else _c(0)
-        rc = f.lib.gb_rmsnorm_reduce(p(residual), _c(f.local_base + self.slots_off[pr.chan]), _i(self.tp_size), _l(self.slot_elems), p(weight),
-                                     p(out), p(q), p(sf), _i(rows), _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0),
-                                     _c(f.local_base + self.flags_off[pr.chan]), _i(self.tp_size), _c(self.epoch[pr.chan]),
-                                     _c(_native.status_ptr()), _c(torch.cuda.current_stream().cuda_stream))
-        _native.check(rc, "gb_rmsnorm_reduce")
+        rc = f.lib.gb_rmsnorm_reduce2(p(residual), _c(f.local_base + self.slots_off[pr.chan]), _i(self.tp_size), _l(self.slot_elems),
+                                      _i(pr.splits), _l(rows * hidden), p(weight),
+                                      p(out), p(q), p(sf), _i(rows), _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0),
+                                      _c(f.local_base + self.flags_off[pr.chan]), _i(self.tp_size), _c(self.epoch[pr.chan]),
+                                      _c(_native.status_ptr()), _c(torch.cuda.current_stream().cuda_stream))
+        _native.check(rc, "gb_rmsnorm_reduce2")
         if quantize:
             return out, MxTensor(q, sf, rows, hidden, sf_layout)
         return out
@@ -140,7 +150,8 @@ class TensorParallel:
         slots = f.view(self.slots_off[delta.chan], (self.tp_size, self.slot_elems), torch.float32)
         # order the read after the peers' stores: a fabric barrier (device side) covers the flags of this channel
         f.barrier()
-        return slots[:, : delta.rows * delta.hidden].sum(0).reshape(delta.rows, delta.hidden).to(torch.bfloat16)
+        n = delta.rows * delta.hidden
+        return slots[:, : delta.splits * n].reshape(self.tp_size * delta.splits, n).sum(0).reshape(delta.rows, delta.hidden).to(torch.bfloat16)
 
     def moe_ffn(self, model, lw, h):
         return None

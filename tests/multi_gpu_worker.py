@@ -146,6 +146,32 @@ def check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-dense"):
     dist.all_gather(gathered, last)
     if fused:
         assert all(torch.equal(gathered[0], x) for x in gathered), "ranks disagree bitwise after the fused reduction"
+        # a decode-sized row-parallel projection whose shard is long enough to be cut along K as well (several slabs per rank in
+        # the slot): the fused reduction + RMSNorm against all-reduce + norm in PyTorch
+        from gemm_b200.models.weights import make_linear
+        from gemm_b200.ops import elementwise as ew
+        hidden, k_shard, rows = cfg.hidden, 2048, 24
+        gg = torch.Generator(device="cpu").manual_seed(100 + rank)
+        w_sh = (torch.randn(hidden, k_shard, generator=gg) * 0.05).to(dev)
+        x_sh = torch.randn(rows, k_shard, generator=gg).to(dev).bfloat16()
+        lw = make_linear(w_sh, fmt)
+        resid = torch.randn(rows, hidden, generator=torch.Generator().manual_seed(3)).to(dev).bfloat16()
+        nw = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+        pend = par.row_linear(lw, x_sh)
+        assert getattr(pend, "splits", 1) > 1, "the projection was expected to take the K-split path"
+        r1 = resid.clone()
+        out = par.add_norm(pend, nw, 1e-6, r1)
+        full = (x_sh.float() @ lw.dequantized().t()) if fmt == "bf16" else None
+        if full is None:
+            xq = ew.mx_quantize(x_sh, sf_layout=32)
+            from gemm_b200.ops import mxfp8 as _mx
+            full = _mx.dequantize(xq) @ lw.dequantized().t()
+        dist.all_reduce(full)
+        r2 = (resid.float() + full).bfloat16()
+        want = ew.rmsnorm_ref(r2, nw, 1e-6)
+        torch.cuda.synchronize()
+        _native.assert_status_ok()
+        assert rel(r1, r2) < 1e-2 and rel(out, want) < 1e-2, f"K-split row-parallel projection: {rel(r1, r2)} {rel(out, want)}"
     dist.barrier()
     par.close()
 
