@@ -99,7 +99,7 @@ allreduce_oneshot_kernel(PeerTable pt, size_t data_off, size_t flags_off, const 
 // inputs through NVLink once their "ready" flag of the chunk is up), pushes the reduced slice into every
 // peer's output and raises "done"; every CTA leaves after the done flags of its chunk arrived from all ranks.
 //   flags: uint32 [2][world][chunks]  (0 = ready, 1 = done)
-template <typename T>
+template <typename T, int MW>      // MW: upper bound of the world size this instance is compiled for (sizes its register arrays)
 __global__ void __launch_bounds__(256)
 allreduce_twoshot_kernel(PeerTable pt, size_t in_off, size_t out_off, size_t flags_off, long n, uint32_t* epoch_ctr,
                          unsigned* done_ctr, KernelStatus* st) {
@@ -121,23 +121,40 @@ allreduce_twoshot_kernel(PeerTable pt, size_t in_off, size_t out_off, size_t fla
   }
   __syncthreads();
   const long s0 = (long)pt.rank * slice + c * per, s1 = min((long)(pt.rank + 1) * slice, s0 + per);
-  for (long v = s0 + threadIdx.x; v < s1; v += blockDim.x) {
-    float acc[8];
+  // Four vectors per thread and step: all their peer loads (W each) are requested before the first sum, so that a CTA keeps
+  // U * W * 256 * 16 bytes in flight over the links (one vector per thread left NVLink at a quarter of its bandwidth).
+  constexpr int U = MW <= 4 ? 4 : 2;
+  for (long vb = s0; vb < s1; vb += (long)U * blockDim.x) {
+    Vec16 x[U][MW];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int p = 0; p < W; ++p) {
-      const Vec16 x = reinterpret_cast<const Vec16*>((char*)pt.base[p] + in_off)[v];
-      if (sizeof(T) == 4) {
-        acc[0] += __uint_as_float(x.x); acc[1] += __uint_as_float(x.y); acc[2] += __uint_as_float(x.z); acc[3] += __uint_as_float(x.w);
-      } else {
-        const float4 a = bf16x4_to_f4(make_uint2(x.x, x.y)), b = bf16x4_to_f4(make_uint2(x.z, x.w));
-        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
-      }
+    for (int u = 0; u < U; ++u) {
+      const long v = vb + (long)u * blockDim.x + threadIdx.x;
+#pragma unroll
+      for (int p = 0; p < MW; ++p)
+        if (p < W && v < s1) x[u][p] = reinterpret_cast<const Vec16*>((char*)pt.base[p] + in_off)[v];
     }
-    Vec16 o;
-    if (sizeof(T) == 4) { o.x = __float_as_uint(acc[0]); o.y = __float_as_uint(acc[1]); o.z = __float_as_uint(acc[2]); o.w = __float_as_uint(acc[3]); }
-    else { o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]); o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]); }
-    for (int p = 0; p < W; ++p) reinterpret_cast<Vec16*>((char*)pt.base[p] + out_off)[v] = o;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long v = vb + (long)u * blockDim.x + threadIdx.x;
+      if (v >= s1) continue;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int p = 0; p < MW; ++p) {
+        if (p >= W) continue;
+        if (sizeof(T) == 4) {
+          acc[0] += __uint_as_float(x[u][p].x); acc[1] += __uint_as_float(x[u][p].y); acc[2] += __uint_as_float(x[u][p].z); acc[3] += __uint_as_float(x[u][p].w);
+        } else {
+          const float4 a = bf16x4_to_f4(make_uint2(x[u][p].x, x[u][p].y)), b = bf16x4_to_f4(make_uint2(x[u][p].z, x[u][p].w));
+          acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w; acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
+      }
+      Vec16 o;
+      if (sizeof(T) == 4) { o.x = __float_as_uint(acc[0]); o.y = __float_as_uint(acc[1]); o.z = __float_as_uint(acc[2]); o.w = __float_as_uint(acc[3]); }
+      else { o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]); o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]); }
+      for (int p = 0; p < W; ++p) reinterpret_cast<Vec16*>((char*)pt.base[p] + out_off)[v] = o;
+    }
   }
   __syncthreads();
   if ((int)threadIdx.x < W) {
@@ -378,8 +395,11 @@ GB_API int gb_allreduce_twoshot(void* const* bases, int world, int rank, size_t 
   const int esz = dtype == 0 ? 4 : 2;
   if ((n * esz) % (16 * world)) return fail("allreduce_twoshot: bytes must be a multiple of 16 * world%s");
   PeerTable pt = make_table(bases, world, rank);
-  if (dtype == 0) launch_k(allreduce_twoshot_kernel<float>, chunks, 256, 0, stream, pt, in_off, out_off, flags_off, n, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
-  else launch_k(allreduce_twoshot_kernel<__nv_bfloat16>, chunks, 256, 0, stream, pt, in_off, out_off, flags_off, n, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
+#define GB_TWOSHOT(TT, MWV) launch_k(allreduce_twoshot_kernel<TT, MWV>, chunks, 256, 0, stream, pt, in_off, out_off, flags_off, n, \
+                                      (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status)
+  if (dtype == 0) { if (world <= 2) GB_TWOSHOT(float, 2); else if (world <= 4) GB_TWOSHOT(float, 4); else GB_TWOSHOT(float, 8); }
+  else { if (world <= 2) GB_TWOSHOT(__nv_bfloat16, 2); else if (world <= 4) GB_TWOSHOT(__nv_bfloat16, 4); else GB_TWOSHOT(__nv_bfloat16, 8); }
+#undef GB_TWOSHOT
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -16,6 +16,7 @@ reduce-scatter + all-gather kernel of the fabric.  ``fused=False`` is the NCCL b
 from __future__ import annotations
 
 import ctypes
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -29,6 +30,9 @@ from ..ops.mxfp8 import MxTensor
 from .fabric import Fabric
 
 _c, _i, _f, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_long
+
+
+TP_DIRECT = os.environ.get("GB_TP_DIRECT", "1") != "0"
 
 
 @dataclass
@@ -66,7 +70,7 @@ class TensorParallel:
         self.flags_off = [f.alloc(32), f.alloc(32)]
         self.epoch = [f.ctl_word(), f.ctl_word()]
         self.done = [f.ctl_word(), f.ctl_word()]
-        self.big = f.make_allreduce_large(big, torch.bfloat16, chunks=64)
+        self.big = f.make_allreduce_large(big, torch.bfloat16)
         self.argmax = f.make_argmax(4096)
         self._extras = []
         for ch in range(2):
@@ -94,6 +98,15 @@ class TensorParallel:
         from ..models.transformer import apply_linear
         rows = x.shape[0] if x is not None else x_mx.rows
         if not self.fused or self.tp_size == 1 or rows > self.max_fused_rows:
+            if TP_DIRECT and self.fused and self.tp_size > 1 and rows * lw.n <= self.big.n and (x if x is not None else x_mx.data).is_cuda:
+                # prefill-sized: the GEMM writes its partial result straight into the all-reduce's input buffer in the fabric heap
+                out = self.big.input_view[: rows * lw.n].view(rows, lw.n)
+                if lw.fmt == "bf16":
+                    gemm.linear(x, lw.w, bias=lw.bias, out=out, w_tiled=lw.tiled)
+                else:
+                    xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if rows <= 32 else 128)
+                    gemm.linear_mx(xm, lw.mx, out=out, bias=lw.bias)
+                return self.big(out)
             return self.tp_all_reduce(apply_linear(lw, x, x_mx))
         ch = self._chan
         self._chan ^= 1
