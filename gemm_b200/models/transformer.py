@@ -362,10 +362,13 @@ class Transformer:
                 h, h_mx = par.add_norm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps, x if delta is not None else None), None
             delta = self.ssm_block(li, lw, h, h_mx, fb) if is_ssm else self.attention_block(li, lw, h, h_mx, fb)
             need_bf16 = (not self.mx) or cfg.is_moe
+            # a parallel context may name the buffer the normalised rows should land in (the staging buffer of its exchange)
+            ob = par.ffn_in_buffer(x.shape[0], lw) if (hasattr(par, "ffn_in_buffer") and x.is_cuda) else None
+            okw = {"out_buf": ob} if ob is not None else {}
             if self.mx:
-                h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, quantize=True, want_bf16=need_bf16, sf_layout=lay)
+                h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, quantize=True, want_bf16=need_bf16, sf_layout=lay, **okw)
             else:
-                h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x), None
+                h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, **okw), None
             if lw.w13 is not None:
                 delta = self.par.moe_ffn(self, lw, h)
                 if delta is None:

@@ -56,7 +56,7 @@ def sf_alloc(rows_padded: int, k: int, device, layout: int = 128, init: bool = T
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
-            quantize: bool = False, want_bf16: bool = True, sf_layout: int = 128):
+            quantize: bool = False, want_bf16: bool = True, sf_layout: int = 128, out_buf: Optional[torch.Tensor] = None):
     """RMSNorm of ``x`` (or of ``residual += x`` when ``residual`` is given; the sum is written back).
 
     Returns the bf16 result, or ``(bf16 | None, MxTensor)`` when ``quantize`` asks for an MXFP8 copy that
@@ -68,7 +68,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
             x = x.materialize()
         else:
             rows, hidden = x.rows, x.hidden
-            out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=residual.device) if want_bf16 else None
+            out = (out_buf[:rows] if out_buf is not None else torch.empty(rows, hidden, dtype=torch.bfloat16, device=residual.device)) if want_bf16 else None
             q = sf = None
             if quantize:
                 rp = (rows + 127) // 128 * 128
@@ -96,7 +96,8 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
         if quantize:
             return (y if want_bf16 else None), mxfp8.quantize(y.float(), sf_layout=sf_layout)
         return y
-    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=x.device) if want_bf16 else None
+    # ``out_buf``: a caller-owned bf16 buffer (at least ``rows`` contiguous rows) that receives the result instead of a fresh tensor
+    out = (out_buf[:rows] if out_buf is not None else torch.empty(rows, hidden, dtype=torch.bfloat16, device=x.device)) if want_bf16 else None
     q = sf = None
     if quantize:
         rp = (rows + 127) // 128 * 128

@@ -153,13 +153,24 @@ class ExpertParallel:
         from ..models.transformer import apply_linear_split
         return apply_linear_split(lw, x, x_mx)
 
-    def add_norm(self, delta, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128):
+    def ffn_in_buffer(self, rows: int, lw):
+        """Where the RMSNorm in front of an MoE block should leave its bf16 rows: the staging buffer of the decode all-gather, so that
+        no copy kernel runs between the norm and the exchange (None = no preference)."""
+        if not (self.fused and self.use_gather and lw.w13 is not None and getattr(self, "_gather", None)) or rows > self.gather_max:
+            return None
+        caps = [c for c in self._gather if rows <= c]
+        return self._gather[min(caps)]["stage"] if caps else None
+
+    def add_norm(self, delta, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128, out_buf=None):
         if not isinstance(delta, PendingSlots):
             kw = dict(quantize=quantize, want_bf16=want_bf16, sf_layout=sf_layout) if quantize else {}
+            if out_buf is not None:
+                kw["out_buf"] = out_buf
             return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
         f, g = self.fab, delta.g
         rows, hidden, cap = delta.rows, self.cfg.hidden, g["cap"]
-        out = torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device) if want_bf16 or not quantize else None
+        out = (out_buf[:rows] if out_buf is not None else torch.empty(rows, hidden, dtype=torch.bfloat16, device=self.device)) \
+            if want_bf16 or not quantize else None
         q = sf = None
         if quantize:
             rp = (rows + 127) // 128 * 128
@@ -191,7 +202,8 @@ class ExpertParallel:
         k, inter, hid = cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
         g = self._gather[min(c for c in self._gather if t <= c)]
         cap = g["cap"]
-        g["stage"][:t].copy_(h)
+        if h.data_ptr() != g["stage"].data_ptr():          # the norm in front of this block usually wrote straight into the staging buffer
+            g["stage"][:t].copy_(h)
         allh = g["ag"].all_gather(g["stage"]).view(torch.bfloat16).view(w * cap, hid)
         rt = dict(mode=cfg.router, bias=lw.router_bias, renorm=cfg.norm_topk, routed_scale=cfg.routed_scale,
                   local_range=(self.ep_rank * self.e_local, self.e_local))
