@@ -52,7 +52,7 @@ def parse_args():
 
 class ClockSampler:
     """Samples SM clocks, power and throttle reasons of one GPU while the timed region runs (read-only NVML queries from a
-    thread, every 20 ms; ``nvidia-smi -lms`` as the fallback when the NVML binding is missing)."""
+    thread, every 50 ms; ``nvidia-smi -lms`` as the fallback when the NVML binding is missing)."""
     FIELDS = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
@@ -79,7 +79,7 @@ class ClockSampler:
                 self.samples.append((float(sm), float(mx), pw, {n for n, b in bits.items() if r & b}))
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.05)
 
     def start(self):
         try:
@@ -241,9 +241,11 @@ def main():
     step_ms = []
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     evs[0].record()
+    t_host0 = time.perf_counter()
     for i in range(args.steps):
         engine.decode_step()
         evs[i + 1].record()
+    host_enqueue_ms = (time.perf_counter() - t_host0) * 1e3 / args.steps      # host time to enqueue one step (diagnostic)
     barrier()
     clocks = sampler.stop()
     total_ms = max_over_ranks(evs[0].elapsed_time(evs[-1]))
@@ -288,7 +290,8 @@ def main():
                        "moe_path": args.moe_path if n_gpus > 1 else "local"},
             "prefill_tokens_per_s": prefill_tok_s, "ttft_ms_p50": prefill_ms, "tpot_ms_p50": tpot_p50,
             "clocks": clocks, "e2e": e2e, "gpu_launches": kernels_per_step * args.steps,
-            "kernels_per_step": kernels_per_step, "kernel_status": st["what"], "native_libs": _native.loaded_libraries(),
+            "kernels_per_step": kernels_per_step, "kernel_status": st["what"], "host_enqueue_ms_per_step": round(host_enqueue_ms, 3),
+            "step_ms_min_max": [round(min(per_step), 3), round(max(per_step), 3)], "native_libs": _native.loaded_libraries(),
         }
         if n_layers != cfg.n_layers:
             line["invalid"] = f"debug run with {n_layers} of {cfg.n_layers} layers"

@@ -67,6 +67,7 @@ struct GemmArgs {
   // fp32 partial in sk_ws; the warp that arrives last at the tile's semaphore sums the partials in split order
   // (deterministic) and runs the normal epilogue.
   int splits;
+  int tile_hint, m_tok_hint;       // host only: expected number of tiles and tokens per tile row (grid sizing of memory-bound launches)
   long partial_stride;             // > 0: no in-kernel reduction, split ks stores its fp32 partial at out + ks * partial_stride (elements)
   float* sk_ws;                    // [tiles][splits][NA * TN][128] fp32
   unsigned* sk_ctr;                // [tiles][4] self-resetting arrival counters (one per epilogue warp)
@@ -642,6 +643,20 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmArgs 
   }
   int grid = sm_count();
   if (max_tiles > 0 && max_tiles < grid) grid = max_tiles;
+  // Memory-bound (decode-sized) launches: all CTAs share the HBM stream, so a round of g tiles takes time proportional to g and the
+  // kernel time goes with ceil(tiles / g) * g.  Take the g in [3/4 SMs, SMs] that wastes the fewest tile slots (768 equal tiles:
+  // 128 CTAs x 6 rounds instead of 148 CTAs with a sixth round for 28 of them); ties go to more CTAs.
+  static int even_waves = -1;
+  if (even_waves < 0) { const char* e = getenv("GB_GEMM_EVEN_WAVES"); even_waves = (e != nullptr && atoi(e) == 0) ? 0 : 1; }
+  if (even_waves && a.tile_hint > grid && a.m_tok_hint <= 64) {
+    const int sms = grid;
+    const long base = (long)((a.tile_hint + sms - 1) / sms) * sms;
+    long best = base;
+    for (int g = sms - 1; g >= sms * 3 / 4; --g) {
+      const long slots = (long)((a.tile_hint + g - 1) / g) * g;
+      if (slots < best && slots * 100 < base * 97) { best = slots; grid = g; }      // worth it from 3 % fewer slots on
+    }
+  }
   launch_k(kern, grid, kGemmThreads, smem, stream, tmW, tmX, a);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -763,6 +778,10 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   }
   int max_tiles = 0;
   if (num_groups == 0) max_tiles = ((n_out + 127) / 128) * ((m_tok + tn - 1) / tn) * (a.splits > 1 ? a.splits : 1);
+  // grouped launches do not know their tile count on the host; a decode-sized one (narrow token tile) has about one token tile
+  // per group
+  a.tile_hint = num_groups == 0 ? max_tiles : num_groups * ((n_out + 127) / 128);
+  a.m_tok_hint = num_groups == 0 ? m_tok : (tn <= 32 ? tn : 1 << 20);
   if (num_groups == 0 && m_tok <= 0) return 0;
 
 #define GB_DISPATCH(TNV)                                                                                      \
