@@ -655,7 +655,8 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // Merge of split-KV partials: out = sum_s 2^(lse_s - lse_max) O_s / sum_s 2^(lse_s - lse_max).
 // One warp per (token, head); D = 128 -> 4 floats per lane.
 __global__ void fa_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, __nv_bfloat16* __restrict__ out,
-                                  float* __restrict__ out_lse, int splits, long rows) {
+                                  float* __restrict__ out_lse, int splits, long rows, uint8_t* __restrict__ out_q, uint8_t* __restrict__ out_sf,
+                                  int out_sf32, int hq) {
   pdl_wait();
   pdl_trigger();
   const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -674,6 +675,29 @@ __global__ void fa_combine_kernel(const float* __restrict__ part_o, const float*
     den += wgt;
   }
   const float inv = den > 0.f ? 1.0f / den : 0.f;
+  if (out_q != nullptr) {
+    // MXFP8 row of the output projection's operand [T, Hq * 128]: eight lanes (32 features) share a scale
+    float amax = fmaxf(fmaxf(fabsf(acc[0]), fabsf(acc[1])), fmaxf(fabsf(acc[2]), fabsf(acc[3]))) * inv;
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const uint32_t bits = __float_as_uint(amax * (1.0f / 448.0f));
+    int e = (int)((bits >> 23) & 0xff) + ((bits & 0x7fffffu) ? 1 : 0);
+    e = amax == 0.0f ? 127 : max(1, min(e, 254));
+    const float sc = __uint_as_float((uint32_t)(254 - e) << 23) * inv;
+    const uint32_t q4 = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(acc[0] * sc, acc[1] * sc), __NV_SATFINITE, __NV_E4M3) |
+                        ((uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(acc[2] * sc, acc[3] * sc), __NV_SATFINITE, __NV_E4M3) << 16);
+    *reinterpret_cast<uint32_t*>(out_q + (size_t)w * kD + lane * 4) = q4;
+    if ((lane & 7) == 0) {
+      const long tok = w / hq;
+      const int head = (int)(w - tok * hq), sub = lane >> 3;
+      const size_t off = out_sf32 ? ((size_t)(tok >> 5) * hq + head) * 512 + (tok & 31) * 16 + sub
+                                  : ((size_t)(tok >> 7) * hq + head) * 512 + (tok & 31) * 16 + ((tok >> 5) & 3) * 4 + sub;
+      out_sf[off] = (uint8_t)e;
+    }
+    if (out_lse != nullptr && lane == 0) out_lse[w] = den > 0.f ? mx + log2f(den) : -INFINITY;
+    return;
+  }
   uint2 o;
   o.x = pack_bf16x2(acc[0] * inv, acc[1] * inv);
   o.y = pack_bf16x2(acc[2] * inv, acc[3] * inv);
@@ -812,7 +836,19 @@ GB_API int gb_flash_decode_mx(const void* q, const void* k_cache, const void* v_
 
 GB_API int gb_fa_combine(const float* part_o, const float* part_lse, void* out, float* out_lse, int splits, long rows, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  launch_k(fa_combine_kernel, (unsigned)((rows * 32 + 255) / 256), 256, 0, stream, part_o, part_lse, (__nv_bfloat16*)out, out_lse, splits, rows);
+  launch_k(fa_combine_kernel, (unsigned)((rows * 32 + 255) / 256), 256, 0, stream, part_o, part_lse, (__nv_bfloat16*)out, out_lse, splits, rows,
+           (uint8_t*)nullptr, (uint8_t*)nullptr, 0, 1);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// The same merge with the result written as MXFP8 rows [T, hq * 128] (rows = T * hq): the operand of the output projection.
+GB_API int gb_fa_combine_mx(const float* part_o, const float* part_lse, void* out_q, void* out_sf, int sf32, int hq, int splits, long rows,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (hq < 1 || rows % hq) return fail("fa_combine_mx: rows must be tokens * heads%s");
+  launch_k(fa_combine_kernel, (unsigned)((rows * 32 + 255) / 256), 256, 0, stream, part_o, part_lse, (__nv_bfloat16*)nullptr, (float*)nullptr, splits,
+           rows, (uint8_t*)out_q, (uint8_t*)out_sf, sf32, hq);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -258,7 +258,7 @@ class Transformer:
                 and att.can_decode_mx(q, self.hkv_local, fb.num_splits, fb.is_decode)):
             # decode: the attention kernel emits the MXFP8 operand of the output projection itself
             a_mx = att.attention_decode_mx(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
-                                           window=cfg.sliding_window, sf_layout=32 if q.shape[0] <= 32 else 128)
+                                           window=cfg.sliding_window, sf_layout=32 if q.shape[0] <= 32 else 128, num_splits=fb.num_splits)
             return self.par.row_linear(lw.wo, None, a_mx)
         if self.mx and lw.wo.fmt != "bf16" and not cfg.attn_output_gate and FUSE_ATTN_QUANT and att.can_attention_mx(q, fb.num_splits):
             a_mx = att.attention_mx(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,

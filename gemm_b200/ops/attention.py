@@ -89,7 +89,8 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_
 
 
 def attention_decode_mx(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
-                        block_table: torch.Tensor, page_size: int, work: torch.Tensor, window: int = 0, sf_layout: int = 128):
+                        block_table: torch.Tensor, page_size: int, work: torch.Tensor, window: int = 0, sf_layout: int = 128,
+                        num_splits: int = 1):
     """Decode attention (one token per sequence, one KV split) whose output leaves the kernel as the MXFP8 operand of the output
     projection: ``MxTensor`` of ``[T, Hq * D]``.  GPU only; the caller checks ``can_decode_mx``."""
     from . import elementwise as ew
@@ -99,6 +100,19 @@ def attention_decode_mx(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     rp = (t + 127) // 128 * 128
     oq = torch.empty(rp, hq * d, dtype=torch.uint8, device=q.device)
     sf = ew.sf_alloc(rp, hq * d, q.device, sf_layout, init=False)
+    if num_splits > 1:
+        # split KV ranges: fp32 partials from the decode kernel, merged (and quantised) by the combine kernel
+        lib, stream = _native.cuda(), _c(torch.cuda.current_stream().cuda_stream)
+        part_o = torch.empty(num_splits, t, hq, d, dtype=torch.float32, device=q.device)
+        part_lse = torch.empty(num_splits, t, hq, dtype=torch.float32, device=q.device)
+        rc = lib.gb_flash_decode(_p(q), _p(k_cache), _p(v_cache), _c(0), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
+                                 _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
+                                 _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(num_splits), _i(window),
+                                 _c(_native.status_ptr()), stream)
+        _native.check(rc, "gb_flash_decode")
+        rc = lib.gb_fa_combine_mx(_p(part_o), _p(part_lse), _p(oq), _p(sf), _i(1 if sf_layout == 32 else 0), _i(hq), _i(num_splits), _l(t * hq), stream)
+        _native.check(rc, "gb_fa_combine_mx")
+        return MxTensor(oq, sf, t, hq * d, sf_layout)
     rc = _native.cuda().gb_flash_decode_mx(_p(q), _p(k_cache), _p(v_cache), _p(oq), _p(sf), _i(1 if sf_layout == 32 else 0), _p(work),
                                            _i(work.shape[0]), _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
                                            _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(window), _c(_native.status_ptr()),
@@ -131,7 +145,7 @@ def can_attention_mx(q: torch.Tensor, num_splits: int) -> bool:
 
 
 def can_decode_mx(q: torch.Tensor, hkv: int, num_splits: int, decode: bool) -> bool:
-    return bool(decode and USE_DECODE_KERNEL and q.is_cuda and num_splits == 1 and q.shape[2] == 128 and q.shape[1] // hkv <= 16)
+    return bool(decode and USE_DECODE_KERNEL and q.is_cuda and num_splits >= 1 and q.shape[2] == 128 and q.shape[1] // hkv <= 16)
 
 
 def attention_partial(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,

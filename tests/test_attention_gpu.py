@@ -108,8 +108,8 @@ def test_decode_kernel_sliding_window():
     assert _rel(out, ref) < 1.5e-2
 
 
-@pytest.mark.parametrize("b,lay", [(7, 32), (40, 128)])
-def test_decode_kernel_mxfp8_output(b, lay):
+@pytest.mark.parametrize("b,lay,splits", [(7, 32, 1), (40, 128, 1), (5, 32, 3)])
+def test_decode_kernel_mxfp8_output(b, lay, splits):
     """The decode kernel's MXFP8 output (the o_proj operand) equals quantising its bf16 output."""
     from gemm_b200.ops import elementwise as ew
     from gemm_b200.ops import mxfp8
@@ -117,10 +117,10 @@ def test_decode_kernel_mxfp8_output(b, lay):
     q_lens = [1] * b
     ctx = [(37 * i) % 900 for i in range(b)]
     q, kc, vc, cu, kvl, bt = _setup(q_lens, ctx, hq, hkv, page, seed=6)
-    work = att.build_work(q_lens, hq, hkv, 1).cuda()
-    out = att.attention(q, kc, vc, cu, kvl, bt, page, work, decode=True)
-    assert att.can_decode_mx(q, hkv, 1, True)
-    om = att.attention_decode_mx(q, kc, vc, cu, kvl, bt, page, work, sf_layout=lay)
+    work = att.build_work(q_lens, hq, hkv, splits).cuda()
+    out = att.attention(q, kc, vc, cu, kvl, bt, page, work, decode=True, num_splits=splits)
+    assert att.can_decode_mx(q, hkv, splits, True)
+    om = att.attention_decode_mx(q, kc, vc, cu, kvl, bt, page, work, sf_layout=lay, num_splits=splits)
     _native.assert_status_ok()
     want = ew.mx_quantize(out.reshape(b, hq * 128), sf_layout=lay)
     got_f, want_f = mxfp8.dequantize(om), mxfp8.dequantize(want)
