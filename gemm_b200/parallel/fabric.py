@@ -114,7 +114,10 @@ class Fabric:
     def make_allreduce_large(self, n_elems: int, dtype: torch.dtype, chunks: int = 296) -> "TwoShotAllReduce":
         return TwoShotAllReduce(self, n_elems, dtype, chunks)
 
-    def make_exchange(self, bytes_per_dst: int, chunks: int = 8) -> "PushExchange":
+    def make_exchange(self, bytes_per_dst: int, chunks: int = 0) -> "PushExchange":
+        """``chunks`` = CTAs of the push kernel (0: by size, one per 32 KB per destination, between 8 and 296)."""
+        if chunks <= 0:
+            chunks = max(8, min(296, bytes_per_dst // (32 << 10)))
         return PushExchange(self, bytes_per_dst, chunks)
 
     def make_argmax(self, max_rows: int) -> "ArgmaxAllReduce":

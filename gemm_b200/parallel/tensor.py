@@ -114,7 +114,9 @@ class TensorParallel:
         ex = self._extras[ch]
         # decode-sized batches: the shard's K range is cut further, every split stores its own slab inside this rank's slot
         sp = gemm.pick_partials(n, rows, k, lw.fmt != "bf16") if n % 128 == 0 else 1
-        while sp > 1 and sp * rows * n > self.slot_elems:
+        # every slab goes to every GPU (fp32): keep what one rank sends per projection near 4 MB, or the K splits cost more link
+        # time than they save in the GEMM (8 GPUs, 32 rows x 4096: 0.5 MB per peer and slab)
+        while sp > 1 and (sp * rows * n > self.slot_elems or sp * rows * n * 4 * (self.tp_size - 1) > (4 << 20)):
             sp -= 1
         kb = k // (64 if lw.fmt == "bf16" else 128)
         if sp > 1 and -(-kb // -(-kb // sp)) != sp:
