@@ -480,8 +480,11 @@ moe_combine_scatter_kernel(const CombineScatterArgs a) {
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    // Every CTA orders its rows before its arrival at GPU scope; the last one to arrive has thereby observed all of them and
+    // publishes with one system-scope fence + release stores (release is cumulative), instead of a system fence per CTA.
+    __threadfence();
     if (atomicAdd(a.done_ctr, 1u) == gridDim.x - 1) {
+      __threadfence_system();
       *a.done_ctr = 0;
       const uint32_t e = *a.epoch_ctr + 1;
       *a.epoch_ctr = e;
