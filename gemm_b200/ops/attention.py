@@ -42,11 +42,12 @@ def build_work(q_lens: Sequence[int], hq: int, hkv: int, num_splits: int = 1) ->
     return torch.tensor(items, dtype=torch.int32).reshape(-1, 4)
 
 
-def pick_splits(n_seqs: int, hkv: int, max_kv: int, sm_count: int = 148) -> int:
-    """Number of KV splits for decode: enough CTAs to cover the SMs, at least 2 KV blocks per split."""
+def pick_splits(n_seqs: int, hkv: int, max_kv: int, sm_count: int = 148, ctas_per_sm: int = 2) -> int:
+    """Number of KV splits for decode: enough CTAs to fill the GPU (the decode kernel runs two CTAs per SM, and one CTA streams
+    its KV range at a fraction of an SM's share of the memory bandwidth), at least 2 KV blocks per split."""
     base = max(1, n_seqs * hkv)
     blocks = max(1, (max_kv + 127) // 128)
-    splits = max(1, min(sm_count // base, blocks // 2 if blocks >= 2 else 1, 16))
+    splits = max(1, min((sm_count * ctas_per_sm) // base, blocks // 2 if blocks >= 2 else 1, 16))
     return splits
 
 
