@@ -253,6 +253,9 @@ struct EpDispatchArgs {
   size_t flags_off;            // uint32 [world]
   int mx; int sf32;
   uint32_t* epoch_ctr; unsigned* done_ctr; KernelStatus* st;
+  // tokens that are already MXFP8 (the RMSNorm in front of the MoE block quantised them): rows and scale words are copied as
+  // 16-byte / 4-byte stores instead of being quantised again per (token, expert) pair
+  const uint8_t* hq; const uint8_t* hsf; int in_sf32;
 };
 
 __device__ __forceinline__ int ep_e8m0(float amax) {
@@ -279,6 +282,27 @@ ep_dispatch_kernel(PeerTable pt, EpDispatchArgs a) {
     if (tok < 0) continue;
     const int dst = (int)(r / a.region_rows);
     const long drow = (long)pt.rank * a.region_rows + (r % a.region_rows);
+    if (a.hq != nullptr) {
+      const int katoms = a.hidden >> 7;
+      const uint4* ip = reinterpret_cast<const uint4*>(a.hq + (size_t)tok * a.hidden);
+      uint4* op = reinterpret_cast<uint4*>((uint8_t*)pt.base[dst] + a.x_off + (size_t)drow * a.hidden);
+      for (int v0 = 0; v0 < (a.hidden >> 4); v0 += 128) {
+        uint4 buf[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const int vi = v0 + lane + 32 * i; if (vi < (a.hidden >> 4)) buf[i] = ip[vi]; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const int vi = v0 + lane + 32 * i; if (vi < (a.hidden >> 4)) op[vi] = buf[i]; }
+      }
+      uint8_t* sfb = (uint8_t*)pt.base[dst] + a.sf_off;
+      for (int ka = lane; ka < katoms; ka += 32) {
+        const size_t si = a.in_sf32 ? ((size_t)(tok >> 5) * katoms + ka) * 512 + (tok & 31) * 16
+                                    : ((size_t)(tok >> 7) * katoms + ka) * 512 + (tok & 31) * 16 + ((tok >> 5) & 3) * 4;
+        const size_t so = a.sf32 ? ((size_t)(drow >> 5) * katoms + ka) * 512 + (drow & 31) * 16
+                                 : ((size_t)(drow >> 7) * katoms + ka) * 512 + (drow & 31) * 16 + ((drow >> 5) & 3) * 4;
+        *reinterpret_cast<uint32_t*>(sfb + so) = *reinterpret_cast<const uint32_t*>(a.hsf + si);
+      }
+      continue;
+    }
     for (int vi = lane; vi < vec_per_row; vi += 32) {
       const uint4 raw = *reinterpret_cast<const uint4*>(a.h + (size_t)tok * a.ld_h + vi * 8);
       if (a.mx) {
@@ -435,6 +459,27 @@ GB_API int gb_ep_dispatch(void* const* bases, int world, int rank, const void* h
   a.region_rows = region_rows; a.experts_per_rank = experts_per_rank; a.x_off = x_off; a.sf_off = sf_off; a.meta_off = meta_off;
   a.flags_off = flags_off; a.mx = mx; a.sf32 = sf32; a.epoch_ctr = (uint32_t*)epoch_ctr; a.done_ctr = (unsigned*)done_ctr; a.st = (KernelStatus*)status;
   if ((hidden / 8) % 32) return fail("ep_dispatch: hidden must be a multiple of 256%s");
+  const long total_rows = (long)world * region_rows;
+  int grid = (int)std::min<long>((total_rows + 7) / 8, (long)sm_count() * 8);
+  if (grid < 1) grid = 1;
+  launch_k(ep_dispatch_kernel, grid, 256, 0, stream, make_table(bases, world, rank), a);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// gb_ep_dispatch for tokens that are already MXFP8: hq e4m3 bytes [T, hidden], hsf their scale atoms (in_sf32: 32-row layout).
+GB_API int gb_ep_dispatch_mx(void* const* bases, int world, int rank, const void* hq, const void* hsf, int in_sf32, int hidden,
+                             const int* row_token, const int* seg_start, const int* seg_count, int region_rows, int experts_per_rank,
+                             size_t x_off, size_t sf_off, size_t meta_off, size_t flags_off, int sf32, void* epoch_ctr, void* done_ctr,
+                             void* status, cudaStream_t stream) {
+  if (world > kMaxRanks) return fail("fabric: world > 8%s");
+  if (hidden % 128 || region_rows % 128 || ((uintptr_t)hq & 15) || ((uintptr_t)hsf & 3)) return fail("ep_dispatch_mx: bad shape or alignment%s");
+  EpDispatchArgs a;
+  memset(&a, 0, sizeof(a));
+  a.hidden = hidden; a.row_token = row_token; a.seg_start = seg_start; a.seg_count = seg_count;
+  a.region_rows = region_rows; a.experts_per_rank = experts_per_rank; a.x_off = x_off; a.sf_off = sf_off; a.meta_off = meta_off;
+  a.flags_off = flags_off; a.mx = 1; a.sf32 = sf32; a.epoch_ctr = (uint32_t*)epoch_ctr; a.done_ctr = (unsigned*)done_ctr; a.st = (KernelStatus*)status;
+  a.hq = (const uint8_t*)hq; a.hsf = (const uint8_t*)hsf; a.in_sf32 = in_sf32;
   const long total_rows = (long)world * region_rows;
   int grid = (int)std::min<long>((total_rows + 7) / 8, (long)sm_count() * 8);
   if (grid < 1) grid = 1;

@@ -172,7 +172,7 @@ class SingleProcess:
     def materialize(self, delta) -> torch.Tensor:
         return delta.materialize() if hasattr(delta, "materialize") else delta
 
-    def moe_ffn(self, model: "Transformer", lw, h: torch.Tensor) -> Optional[torch.Tensor]:
+    def moe_ffn(self, model: "Transformer", lw, h: torch.Tensor, h_mx=None) -> Optional[torch.Tensor]:
         return None            # None -> the model runs its local MoE path
 
 
@@ -370,7 +370,7 @@ class Transformer:
             else:
                 h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, **okw), None
             if lw.w13 is not None:
-                delta = self.par.moe_ffn(self, lw, h)
+                delta = self.par.moe_ffn(self, lw, h, h_mx)
                 if delta is None:
                     delta = self.moe_local(lw, h, h_mx)
                 if lw.sh_gate_up is not None:

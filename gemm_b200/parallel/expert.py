@@ -22,6 +22,7 @@ all of them, reduce-scatter the partial sums — the reference's own expert-para
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -40,6 +41,10 @@ class PendingSlots:
 
     def __init__(self, g: dict, rows: int):
         self.g, self.rows = g, rows
+
+
+# GB_EP_DISPATCH_MX=0: the dispatch quantises the bf16 rows itself instead of copying the rows the RMSNorm already quantised
+DISPATCH_MX = os.environ.get("GB_EP_DISPATCH_MX", "1") != "0"
 
 
 class ExpertParallel:
@@ -229,7 +234,7 @@ class ExpertParallel:
         _native.check(rc, "gb_moe_combine_scatter")
         return PendingSlots(g, t)
 
-    def moe_ffn(self, model, lw, h: torch.Tensor) -> torch.Tensor:
+    def moe_ffn(self, model, lw, h: torch.Tensor, h_mx=None) -> torch.Tensor:
         if not self.fused:
             return self._moe_nccl(model, lw, h)
         if h.shape[0] <= min(self.gather_max, self.max_tokens) and self.use_gather:
@@ -243,11 +248,20 @@ class ExpertParallel:
         ids, wts = moe.route(logits, k, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
         pl = moe.plan(ids, e, tn, regions=w, epoch_ctr=self.epoch, region_rows=rows)
         stream = _c(torch.cuda.current_stream().cuda_stream)
-        rc = f.lib.gb_ep_dispatch(f.bases_arr, _i(w), _i(self.ep_rank), _c(h.data_ptr()), _i(h.stride(0)), _i(hid), _c(pl.row_token.data_ptr()),
-                                  _c(pl.seg_start.data_ptr()), _c(pl.seg_count.data_ptr()), _i(rows), _i(self.e_local), _sz(self.x_off),
-                                  _sz(self.sf_off), _sz(self.meta_off), _sz(self.flags_d), _i(1 if self.mx else 0), _i(1 if tn == 32 else 0),
-                                  _c(self.epoch), _c(self.done_d), _c(_native.status_ptr()), stream)
-        _native.check(rc, "gb_ep_dispatch")
+        if self.mx and h_mx is not None and h_mx.data.is_cuda and DISPATCH_MX:
+            # the tokens are already MXFP8 (quantised by the RMSNorm in front of this block): the dispatch copies bytes and scales
+            rc = f.lib.gb_ep_dispatch_mx(f.bases_arr, _i(w), _i(self.ep_rank), _c(h_mx.data.data_ptr()), _c(h_mx.sf.data_ptr()),
+                                         _i(1 if h_mx.sf_layout == 32 else 0), _i(hid), _c(pl.row_token.data_ptr()), _c(pl.seg_start.data_ptr()),
+                                         _c(pl.seg_count.data_ptr()), _i(rows), _i(self.e_local), _sz(self.x_off), _sz(self.sf_off),
+                                         _sz(self.meta_off), _sz(self.flags_d), _i(1 if tn == 32 else 0), _c(self.epoch), _c(self.done_d),
+                                         _c(_native.status_ptr()), stream)
+            _native.check(rc, "gb_ep_dispatch_mx")
+        else:
+            rc = f.lib.gb_ep_dispatch(f.bases_arr, _i(w), _i(self.ep_rank), _c(h.data_ptr()), _i(h.stride(0)), _i(hid), _c(pl.row_token.data_ptr()),
+                                      _c(pl.seg_start.data_ptr()), _c(pl.seg_count.data_ptr()), _i(rows), _i(self.e_local), _sz(self.x_off),
+                                      _sz(self.sf_off), _sz(self.meta_off), _sz(self.flags_d), _i(1 if self.mx else 0), _i(1 if tn == 32 else 0),
+                                      _c(self.epoch), _c(self.done_d), _c(_native.status_ptr()), stream)
+            _native.check(rc, "gb_ep_dispatch")
         seg_start, seg_count = self.meta[0], self.meta[1]
         if self.mx:
             from ..models.transformer import expert_gate_up_mx

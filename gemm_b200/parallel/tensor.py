@@ -168,7 +168,7 @@ class TensorParallel:
         n = delta.rows * delta.hidden
         return slots[:, : delta.splits * n].reshape(self.tp_size * delta.splits, n).sum(0).reshape(delta.rows, delta.hidden).to(torch.bfloat16)
 
-    def moe_ffn(self, model, lw, h):
+    def moe_ffn(self, model, lw, h, h_mx=None):
         return None
 
     def merge_sampled(self, tok: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
