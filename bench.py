@@ -290,7 +290,8 @@ def main():
                        "moe_path": args.moe_path if n_gpus > 1 else "local"},
             "prefill_tokens_per_s": prefill_tok_s, "ttft_ms_p50": prefill_ms, "tpot_ms_p50": tpot_p50,
             "clocks": clocks, "e2e": e2e, "gpu_launches": kernels_per_step * args.steps,
-            "kernels_per_step": kernels_per_step, "kernel_status": st["what"], "host_enqueue_ms_per_step": round(host_enqueue_ms, 3),
+            "kernels_per_step": kernels_per_step, "kernel_status": st["what"], "kernel_status_detail": {k: (list(v) if isinstance(v, tuple) else v) for k, v in st.items()},
+            "host_enqueue_ms_per_step": round(host_enqueue_ms, 3),
             "step_ms_min_max": [round(min(per_step), 3), round(max(per_step), 3)], "native_libs": _native.loaded_libraries(),
         }
         if n_layers != cfg.n_layers:

@@ -80,6 +80,7 @@ struct GemmArgs {
   size_t sfa_bytes, sfb_bytes, out_bytes, out_sf_bytes;
   // ---- weight layout: 0 = row-major [rows, k]; 1 = tiled [rows/128][k-blocks][128 rows][128 bytes], every 16 KB operand
   // tile of the main loop is one contiguous block of memory (one DRAM burst sequence instead of 128 strided lines)
+  int dual_raw;  // DUAL without the activation: the second accumulator is the row block up_row_offset further down the same matrix
   int w_tiled;
   int debug;     // experiment knob (GB_GEMM_DEBUG): bit 0 = issue no MMA (pure load stream), bit 1 = load no weight tiles
 };
@@ -545,6 +546,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           tc_wait_ld();
           if (c >= t.valid) continue;
           if (!store_ok) continue;
+          if (DUAL && args.dual_raw && args.partial_stride == 0) {
+            // two row blocks of ONE projection share a token tile (rows n and up_row_offset + n): both plain results are stored.
+            // Halves the tiles, the token-tile loads and the per-tile overhead of projections with a short K (expert down_proj).
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (c + j < t.valid) {
+                if (args.out_f32) {
+                  o32[(size_t)(c + j) * args.ldo] = __uint_as_float(r0[j]);
+                  o32[(size_t)(c + j) * args.ldo + args.up_row_offset] = __uint_as_float(r1[j]);
+                } else {
+                  o16[(size_t)(c + j) * args.ldo] = __float2bfloat16(__uint_as_float(r0[j]));
+                  o16[(size_t)(c + j) * args.ldo + args.up_row_offset] = __float2bfloat16(__uint_as_float(r1[j]));
+                }
+              }
+            continue;
+          }
           if (DUAL && args.partial_stride > 0) {
             // K-split partials of a gate/up pair: both raw sums are stored (gate at column n, up at n_out + n of a 2 * n_out wide
             // slab); the activation needs the full sums and is applied by the kernel that adds the slabs
@@ -694,7 +711,7 @@ struct GemmExtras {
 };
 
 // Flags of gb_gemm.
-enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8, GEMM_W_TILED = 16 };
+enum { GEMM_MX = 1, GEMM_DUAL = 2, GEMM_QUANT_OUT = 4, GEMM_OUT_F32 = 8, GEMM_W_TILED = 16, GEMM_DUAL_RAW = 32 };
 
 // Linear layer on tensor cores.
 //   w        [w_rows, k] row-major (bf16, or e4m3 bytes when GEMM_MX), w_rows = groups * w_rows_per_group
@@ -742,6 +759,8 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   a.up_row_offset = up_row_offset; a.seg_start = seg_start; a.seg_count = seg_count;
   a.sfa = (const uint8_t*)sfa; a.sfb = (const uint8_t*)sfb; a.out = out; a.ldo = ldo; a.out_f32 = (flags & GEMM_OUT_F32) ? 1 : 0;
   a.w_tiled = w_tiled ? 1 : 0;
+  a.dual_raw = (flags & GEMM_DUAL_RAW) ? 1 : 0;
+  if (a.dual_raw && (!dual || qo)) return fail("gemm: GEMM_DUAL_RAW needs GEMM_DUAL without GEMM_QUANT_OUT%s");
   {
     static int dbg = -1;
     if (dbg < 0) { const char* e = getenv("GB_GEMM_DEBUG"); dbg = e != nullptr ? atoi(e) : 0; }

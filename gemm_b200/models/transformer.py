@@ -150,6 +150,9 @@ SPLIT_PROJ = os.environ.get("GB_SPLIT_PROJ", "1") != "0"
 FUSE_ATTN_QUANT = os.environ.get("GB_FUSE_ATTN_QUANT", "1") != "0"
 
 
+PAIR_DOWN = os.environ.get("GB_PAIR_DOWN", "1") != "0"
+
+
 class SingleProcess:
     """Parallel context of an unsharded model: every collective is the identity."""
     tp_size = 1
@@ -332,7 +335,7 @@ class Transformer:
             hsf = ew.sf_alloc(pl.capacity, inter, dev, tn, init=False)
             expert_gate_up_mx(xq.data, xq.sf, lw.w13, e, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
             y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
-                                    w_tiled=lw.w2.mx.tiled)
+                                    w_tiled=lw.w2.mx.tiled, pair_rows=(tn == 32 and PAIR_DOWN))
         else:
             tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
             ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)

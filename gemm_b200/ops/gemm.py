@@ -16,7 +16,7 @@ from .. import _native
 from . import mxfp8
 from .mxfp8 import MxTensor
 
-GEMM_MX, GEMM_DUAL, GEMM_QUANT_OUT, GEMM_OUT_F32, GEMM_W_TILED = 1, 2, 4, 8, 16
+GEMM_MX, GEMM_DUAL, GEMM_QUANT_OUT, GEMM_OUT_F32, GEMM_W_TILED, GEMM_DUAL_RAW = 1, 2, 4, 8, 16, 32
 
 
 class GemmExtras(ctypes.Structure):
@@ -320,7 +320,7 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
                    out: Optional[torch.Tensor] = None, dual: bool = False, row_map: Optional[torch.Tensor] = None,
                    row_scale: Optional[torch.Tensor] = None, sfa=None, sfb=None, quant_out: bool = False,
                    out_sf: Optional[torch.Tensor] = None, extras=None, w_groups: Optional[int] = None,
-                   w_tiled: bool = False) -> torch.Tensor:
+                   w_tiled: bool = False, pair_rows: bool = False) -> torch.Tensor:
     """One GEMM per group over row segments of ``x``.
 
     ``w`` is ``[G, R, K]`` (R = 2I stacked gate/up rows when ``dual``); group g multiplies the rows
@@ -331,25 +331,30 @@ def grouped_linear(x: torch.Tensor, w: torch.Tensor, seg_start: torch.Tensor, se
     g, r, k = w.shape
     if w_groups is not None:
         g = w_groups                      # more row groups than weight groups (expert parallel: group = (source, expert))
-    n_out = r // 2 if dual else r
+    # ``pair_rows``: a tile takes row blocks n and R/2 + n of the SAME projection (two accumulators, plain stores): half the tiles
+    # and token-tile loads for projections with a short K, such as the expert down projection of a decode step
+    pair = bool(pair_rows and not dual and not quant_out and row_map is None and row_scale is None and x.is_cuda and r % 256 == 0)
+    n_out = r // 2 if (dual or pair) else r
     mx = sfa is not None
     if not x.is_cuda:
         if w_tiled:
             w = mxfp8.untile_weight(w.reshape(-1, k)).reshape(w.shape)
         return _grouped_reference(x, w, seg_start, seg_count, dual, row_map, row_scale, sfa, sfb, quant_out, out, out_sf)
     flags = (GEMM_MX if mx else 0) | (GEMM_DUAL if dual else 0) | (GEMM_QUANT_OUT if quant_out else 0) | (GEMM_W_TILED if w_tiled else 0)
+    if pair:
+        flags |= GEMM_DUAL | GEMM_DUAL_RAW
     if out is None:
         if quant_out:
             out = torch.empty(x.shape[0], n_out, dtype=torch.uint8, device=x.device)
         else:
-            out = torch.empty(x.shape[0], n_out, dtype=torch.bfloat16, device=x.device)
+            out = torch.empty(x.shape[0], r if pair else n_out, dtype=torch.bfloat16, device=x.device)
     if out.dtype == torch.float32:
         flags |= GEMM_OUT_F32
-    if (WIDE_TILE and mx and tn == 128 and not dual and not quant_out and row_map is None and row_scale is None
+    if (WIDE_TILE and mx and tn == 128 and not dual and not pair and not quant_out and row_map is None and row_scale is None
             and out.dtype == torch.bfloat16 and x.shape[0] >= 256 * g):
         tn = 256                          # prefill-sized segments (the scale atoms keep the 128-row layout)
     _launch(w, x, out, n_out, k, x.shape[0], k, x.stride(0), out.stride(0), flags, tn, num_groups=g, w_rows_per_group=r,
-            up_row_offset=n_out if dual else 0, seg_start=seg_start, seg_count=seg_count, x_rows=x.shape[0], sfa=sfa,
+            up_row_offset=n_out if (dual or pair) else 0, seg_start=seg_start, seg_count=seg_count, x_rows=x.shape[0], sfa=sfa,
             sfb=sfb, out_sf=out_sf, row_map=row_map, row_scale=row_scale, extras=extras)
     return out
 

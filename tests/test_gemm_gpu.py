@@ -319,3 +319,33 @@ def test_swiglu_from_k_split_partials(mx):
         want = gemm.linear_swiglu(x.bfloat16(), w.bfloat16())
         _native.assert_status_ok()
         assert _rel(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("mx", [True, False])
+def test_grouped_pair_rows_equals_plain(mx):
+    """Two row blocks of one projection per tile (two accumulators, plain stores) give the plain grouped GEMM's result."""
+    torch.manual_seed(44)
+    g, n, k, tn = 5, 512, 768, 32
+    counts = torch.tensor([5, 0, 32, 17, 1], dtype=torch.int32)
+    starts = torch.zeros(g, dtype=torch.int32)
+    pos = 0
+    for i in range(g):
+        starts[i] = pos
+        pos += (int(counts[i]) + tn - 1) // tn * tn
+    rows = (pos + 127) // 128 * 128
+    x = torch.randn(rows, k, device="cuda")
+    w = torch.randn(g, n, k, device="cuda") * 0.05
+    sd, cd = starts.cuda(), counts.cuda()
+    if mx:
+        xq = mxfp8.quantize(x, sf_layout=tn)
+        wq = mxfp8.quantize(w.reshape(g * n, k))
+        a = gemm.grouped_linear(xq.data, wq.data.reshape(g, n, k), sd, cd, tn, sfa=wq.sf, sfb=xq.sf, pair_rows=True)
+        b = gemm.grouped_linear(xq.data, wq.data.reshape(g, n, k), sd, cd, tn, sfa=wq.sf, sfb=xq.sf)
+    else:
+        a = gemm.grouped_linear(x.bfloat16(), w.bfloat16(), sd, cd, tn, pair_rows=True)
+        b = gemm.grouped_linear(x.bfloat16(), w.bfloat16(), sd, cd, tn)
+    _native.assert_status_ok()
+    for i in range(g):
+        s0, c = int(starts[i]), int(counts[i])
+        if c:
+            assert torch.equal(a[s0:s0 + c], b[s0:s0 + c]), f"group {i}"
