@@ -64,11 +64,14 @@ class ClockSampler:
         self.stop_flag = False
         self.thread = None
         self.mode = None
+        self.t_mark = None         # set by mark(): the timed region starts here
+        self.max_query_ms = 0.0
 
     def _nvml_loop(self, nv, h):
         bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
         mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
         while not self.stop_flag:
+            t_q = time.perf_counter()
             try:
                 sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
                 pw = nv.nvmlDeviceGetPowerUsage(h) / 1000.0
@@ -76,9 +79,11 @@ class ClockSampler:
                     r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
                 except Exception:
                     r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                self.samples.append((float(sm), float(mx), pw, {n for n, b in bits.items() if r & b}))
+                if self.t_mark is not None:          # queries before mark() only warm the NVML paths up
+                    self.samples.append((float(sm), float(mx), pw, {n for n, b in bits.items() if r & b}))
             except Exception:
                 pass
+            self.max_query_ms = max(self.max_query_ms, (time.perf_counter() - t_q) * 1e3)     # slowest round of queries (diagnostic)
             time.sleep(0.05)
 
     def start(self):
@@ -100,6 +105,11 @@ class ClockSampler:
             self.thread.start()
         except Exception:
             self.proc = None
+
+    def mark(self):
+        """The timed region starts now; everything sampled before (first-call costs of the NVML queries included) is dropped."""
+        self.t_mark = time.perf_counter()
+        self.lines = []
 
     def _read(self):
         for line in self.proc.stdout:
@@ -131,7 +141,8 @@ class ClockSampler:
         reasons = set().union(*[x[3] for x in self.samples]) if self.samples else set()
         busy = [c for c, p in zip(sm, power) if p > 300] or sm
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(x[1] for x in self.samples) if self.samples else None,
-                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None, "source": self.mode}
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None, "source": self.mode,
+                "max_query_ms": round(self.max_query_ms, 1)}
 
 
 def reference_arm(args):
@@ -229,15 +240,19 @@ def main():
     engine.begin_decode(first, SamplingParams(), max_new_tokens=total_new, use_graph=True)
     launches_before = _native.launch_count()
     engine._decode_body_count = None
-    for _ in range(args.warmup):
-        engine.decode_step()
-    barrier()
+    # The clock sampler starts BEFORE the warm-up steps: the first NVML queries of a process can take seconds and were seen to
+    # stall the GPU's work submission for about 2 s once per process; they now land in the warm-up, not in the timed region.
     try:
         _uuid = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
     except Exception:
         _uuid = ""
     sampler = ClockSampler(local_rank, _uuid)
     sampler.start()
+    time.sleep(0.3)
+    for _ in range(args.warmup):
+        engine.decode_step()
+    barrier()
+    sampler.mark()
     step_ms = []
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     evs[0].record()
