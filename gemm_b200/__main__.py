@@ -8,6 +8,7 @@
   microbench kernel micro-benchmarks (same as ``python -m gemm_b200.utils.microbench``)
   estimate   roofline estimate of decode / prefill throughput for a model preset (tools/decode_estimate.py of the reference)
   compare    run the same prompt through the CPU reference path and the GPU kernels and report the agreement token by token
+  dump       run a prompt and write the hidden state after every layer (and the logits) as .npy files for layer-by-layer comparison
   build      compile the native libraries in-tree
 
 The reference spreads these over separate programs: cpu/llm/test_transformer.c (generate: ``<model> [prompt] [max_gen]
@@ -168,6 +169,40 @@ def cmd_compare(args):
     print(json.dumps(report))
 
 
+def cmd_dump(args):
+    """Hidden state after every layer + final logits of one prompt as ``.npy`` files (f32): the layer-by-layer debugging aid the
+    reference gets from its npy writer (common/npy_io.h) and safetensors_writer.h dumps."""
+    import os
+    import numpy as np
+    import torch
+    from .models import loader
+    from .models.config import get_config
+    from .models.transformer import ForwardBatch, KvCache, Transformer
+    from .models.weights import synthetic_weights
+    dev = args.device if (args.device != "cuda" or torch.cuda.is_available()) else "cpu"
+    if args.model.startswith("synthetic:"):
+        w = synthetic_weights(get_config(args.model.split(":", 1)[1]), args.format, device=dev, seed=args.seed)
+    elif os.path.isdir(args.model):
+        w = loader.load_safetensors(args.model, args.format, dev)
+    else:
+        w = loader.load_gguf(args.model, args.format, dev)
+    cfg = w.cfg
+    ids = [int(x) for x in args.ids.replace(",", " ").split()]
+    page = 16
+    n_pages = len(ids) // page + 2
+    m = Transformer(w, KvCache.allocate(cfg, n_pages, page, dev))
+    m.snapshot_layers = tuple(range(len(w.layers)))
+    bt = torch.arange(n_pages, dtype=torch.int32).unsqueeze(0)
+    fb = ForwardBatch.build([len(ids)], [0], torch.tensor(ids), bt, page, cfg.n_heads, cfg.n_kv_heads, dev)
+    fb.logit_rows = torch.arange(len(ids), device=fb.ids.device)
+    logits = m.forward(fb).float().cpu()
+    os.makedirs(args.out, exist_ok=True)
+    for li, h in sorted(m.snapshots.items()):
+        np.save(os.path.join(args.out, f"layer_{li:03d}.npy"), h.float().cpu().numpy())
+    np.save(os.path.join(args.out, "logits.npy"), logits.numpy())
+    print(json.dumps({"layers": len(m.snapshots), "tokens": len(ids), "out": args.out, "argmax_last": int(logits[-1].argmax())}))
+
+
 def cmd_build(args):
     from . import build
     build.build_all(verbose=True)
@@ -226,6 +261,14 @@ def main(argv=None):
     cp.add_argument("--seed", type=int, default=0)
     cp.add_argument("--oracle", action="store_true", help="also compare the CPU path with the fp32 oracle")
     cp.set_defaults(fn=cmd_compare)
+    dp = sub.add_parser("dump", help="per-layer hidden states as .npy")
+    dp.add_argument("--model", required=True, help="GGUF file, HF safetensors directory, or synthetic:<preset>")
+    dp.add_argument("--format", default="bf16", choices=["bf16", "mxfp8"])
+    dp.add_argument("--device", default="cuda")
+    dp.add_argument("--ids", required=True, help="prompt as token ids")
+    dp.add_argument("--out", required=True)
+    dp.add_argument("--seed", type=int, default=0)
+    dp.set_defaults(fn=cmd_dump)
     b = sub.add_parser("build", help="compile the native libraries")
     b.set_defaults(fn=cmd_build)
     args = ap.parse_args(argv)

@@ -50,3 +50,14 @@ def test_compare_command_cpu_side(capsys):
     main(["compare", "--model", "synthetic:tiny-dense", "--steps", "3", "--prompt-len", "12", "--oracle"])
     rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert len(rep["cpu_tokens"]) == 3 and rep["cpu_vs_fp32_oracle_rel"] < 3e-2
+
+
+def test_dump_command_writes_layer_states(tmp_path, capsys):
+    import numpy as np
+    from gemm_b200.__main__ import main
+    main(["dump", "--model", "synthetic:tiny-dense", "--device", "cpu", "--ids", "1 2 3 4 5", "--out", str(tmp_path)])
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["layers"] == 2 and rep["tokens"] == 5
+    h = np.load(tmp_path / "layer_001.npy")
+    lg = np.load(tmp_path / "logits.npy")
+    assert h.shape == (5, 256) and lg.shape[0] == 5 and np.isfinite(h).all()
