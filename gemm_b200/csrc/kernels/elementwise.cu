@@ -650,6 +650,35 @@ kv_copy_pages_kernel(uint4* __restrict__ cache, const int* __restrict__ src, con
   for (long i = (long)blockIdx.y * blockDim.x + threadIdx.x; i < vec_per_page; i += (long)gridDim.y * blockDim.x) dp[i] = sp[i];
 }
 
+// ------------------------------------------------------------------------------------------ INT8 KV codec
+// rows of head_dim bf16 values (one per cache slot and KV head) <-> int8 with one f32 scale per row: scale = amax / 127,
+// q = round(x / scale) clamped to [-127, 127] (the rule of kv_cache_store_q8, cuda/llm/cuda_llm_runner.c:220-241, with the maximum
+// taken over the whole head; the reference's reduction only spans a warp).  One warp per row, head_dim % 32 == 0, <= 256.
+__global__ void __launch_bounds__(256)
+kv_quant_q8_kernel(const __nv_bfloat16* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, long rows, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const long r = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (r >= rows) return;
+  const int lane = threadIdx.x & 31, per = d >> 5;
+  float v[8];
+  float amax = 0.f;
+  for (int i = 0; i < per; ++i) { v[i] = __bfloat162float(x[r * d + lane * per + i]); amax = fmaxf(amax, fabsf(v[i])); }
+  amax = warp_max(amax);
+  const float inv = amax > 0.f ? 127.0f / amax : 0.f;
+  if (lane == 0) scale[r] = amax / 127.0f;
+  for (int i = 0; i < per; ++i) q[r * d + lane * per + i] = (int8_t)max(-127, min(127, __float2int_rn(v[i] * inv)));
+}
+
+__global__ void __launch_bounds__(256)
+kv_dequant_q8_kernel(const int8_t* __restrict__ q, const float* __restrict__ scale, __nv_bfloat16* __restrict__ x, long rows, int d) {
+  pdl_wait();
+  pdl_trigger();
+  const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * d) return;
+  x[i] = __float2bfloat16((float)q[i] * scale[i / d]);
+}
+
 // ------------------------------------------------------------------------------------------ casts
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
   pdl_wait();
@@ -860,6 +889,21 @@ GB_API int gb_kv_copy_pages(void* cache, const int* src, const int* dst, int n, 
   const long vecs = page_bytes / 16;
   const unsigned by = (unsigned)std::min<long>((vecs + 255) / 256, 64);
   launch_k(kv_copy_pages_kernel, dim3((unsigned)n, by), 256, 0, stream, (uint4*)cache, src, dst, n_pages, vecs);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_kv_quant_q8(const void* x, void* q, float* scale, long rows, int d, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (d % 32 || d > 256) return fail("kv_quant_q8: head_dim must be a multiple of 32, at most 256%s");
+  launch_k(kv_quant_q8_kernel, (unsigned)((rows * 32 + 255) / 256), 256, 0, stream, (const __nv_bfloat16*)x, (int8_t*)q, scale, rows, d);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+GB_API int gb_kv_dequant_q8(const void* q, const float* scale, void* x, long rows, int d, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  launch_k(kv_dequant_q8_kernel, (unsigned)((rows * d + 255) / 256), 256, 0, stream, (const int8_t*)q, scale, (__nv_bfloat16*)x, rows, d);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

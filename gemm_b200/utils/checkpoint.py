@@ -4,7 +4,8 @@ later — e.g. to skip a long prefill when sweeping decode settings.
 Counterpart of the reference's 'TPCP' files (a64fx/llm/tp_runner.c:155-563: magic + version, model and TP geometry,
 cache position, next token, then per-layer K / V buffers; every header field is validated on load,
 tp_cache_matches_model :356-387).  Our file: magic ``GBKV1\\n``, a JSON header line (geometry, sequences), then for every layer
-the K and V rows of the used cache slots in sequence order (bf16).  A truncated or mismatching file is rejected.
+the K and V rows of the used cache slots in sequence order: bf16, or with ``kv_format="q8"`` int8 rows followed by one f32 scale per
+(slot, KV head) (``ops.kvquant``: about half the size, the reference's INT8 KV rule).  A truncated or mismatching file is rejected.
 """
 from __future__ import annotations
 
@@ -24,10 +25,13 @@ def _geometry(engine) -> Dict:
             "ep_size": engine.w.ep_size, "ep_rank": engine.w.ep_rank, "fmt": engine.w.fmt}
 
 
-def save_state(engine, path: str, next_tokens=None) -> None:
-    """Write the cached K/V of all sequences of ``engine`` (a ``serve.engine.Engine``)."""
+def save_state(engine, path: str, next_tokens=None, kv_format: str = "bf16") -> None:
+    """Write the cached K/V of all sequences of ``engine`` (a ``serve.engine.Engine``); ``kv_format`` "bf16" or "q8"."""
+    if kv_format not in ("bf16", "q8"):
+        raise ValueError(f"unknown KV format {kv_format!r}")
+    from ..ops import kvquant
     ps = engine.page_size
-    header = {"geometry": _geometry(engine), "seq_len": list(engine.seq_len), "page_size": ps,
+    header = {"geometry": _geometry(engine), "seq_len": list(engine.seq_len), "page_size": ps, "kv_format": kv_format,
               "next_tokens": [int(t) for t in (next_tokens.tolist() if next_tokens is not None else [])]}
     slots = []
     for s, n in enumerate(engine.seq_len):
@@ -42,7 +46,13 @@ def save_state(engine, path: str, next_tokens=None) -> None:
         f.write(hb)
         for li in range(len(engine.kv.k)):
             for t in (engine.kv.k[li], engine.kv.v[li]):
-                f.write(t[idx].contiguous().cpu().view(torch.uint8).numpy().tobytes())
+                rows = t[idx].contiguous()
+                if kv_format == "q8":
+                    q, sc = kvquant.quantize_q8(rows)
+                    f.write(q.cpu().view(torch.uint8).numpy().tobytes())
+                    f.write(sc.cpu().numpy().tobytes())
+                else:
+                    f.write(rows.cpu().view(torch.uint8).numpy().tobytes())
 
 
 def load_state(engine, path: str) -> torch.Tensor:
@@ -63,6 +73,10 @@ def load_state(engine, path: str) -> torch.Tensor:
                 raise ValueError(f"KV state file does not match the model: {k} is {geo.get(k)!r} in the file, {v!r} here")
         if header["page_size"] <= 0:
             raise ValueError("bad page size")
+        kv_format = header.get("kv_format", "bf16")
+        if kv_format not in ("bf16", "q8"):
+            raise ValueError(f"unknown KV format {kv_format!r} in the file")
+        from ..ops import kvquant
         engine.reset()
         ps = engine.page_size
         slots = []
@@ -78,6 +92,15 @@ def load_state(engine, path: str) -> torch.Tensor:
         row = engine.kv.k[0].shape[1] * engine.kv.k[0].shape[2] * 2
         for li in range(len(engine.kv.k)):
             for t in (engine.kv.k[li], engine.kv.v[li]):
+                if kv_format == "q8":
+                    nq, ns = len(slots) * (row // 2), len(slots) * t.shape[1] * 4
+                    buf, sbuf = f.read(nq), f.read(ns)
+                    if len(buf) != nq or len(sbuf) != ns:
+                        raise ValueError("truncated KV state file")
+                    q = torch.frombuffer(bytearray(buf), dtype=torch.int8).reshape(len(slots), t.shape[1], t.shape[2])
+                    sc = torch.frombuffer(bytearray(sbuf), dtype=torch.float32).reshape(len(slots), t.shape[1])
+                    t[idx] = kvquant.dequantize_q8(q.to(engine.device), sc.to(engine.device))
+                    continue
                 buf = f.read(len(slots) * row)
                 if len(buf) != len(slots) * row:
                     raise ValueError("truncated KV state file")

@@ -277,3 +277,16 @@ def test_route_hidden_cluster_kernel(t, e, local, mode, monkeypatch):
     ids, wt = moe.route_hidden(h, w, k, mode, bias, True, 1.5, local)
     ids2, wt2 = moe.route(moe.router_logits(h, w), k, mode, bias, True, 1.5, local)
     assert torch.equal(ids, ids2) and torch.equal(wt, wt2)
+
+
+def test_kv_int8_codec_matches_reference():
+    from gemm_b200.ops import kvquant
+    torch.manual_seed(41)
+    x = (torch.randn(300, 4, 128, device="cuda") * torch.rand(300, 4, 1, device="cuda") * 5).bfloat16()
+    x[7, 1] = 0
+    q, sc = kvquant.quantize_q8(x)
+    q_ref, sc_ref = kvquant.quantize_q8_ref(x.cpu())
+    assert torch.equal(sc.cpu(), sc_ref)
+    assert (q.cpu().int() - q_ref.int()).abs().max().item() <= 1          # rounding of ties / fma differences
+    back = kvquant.dequantize_q8(q, sc)
+    assert _rel(back, x) < 1e-2
