@@ -2,9 +2,9 @@
 """Headline benchmark: Qwen3-30B-A3B-shaped MoE, MXFP8, decode tokens/s (plus prefill tokens/s, TTFT, TPOT).
 
     python bench.py --gpus N --steps K --warmup W            # N = 1; torchrun launches N > 1
-    python bench.py --impl reference ...                      # the reference arm (unavailable: see DESIGN.md)
+    python bench.py --impl reference ...                      # the reference arm (prints why it is unavailable)
 
-Workload (BASELINE.json config 3): 48 layers, hidden 2048, 32 Q / 4 KV heads of 128, 128 experts top-8 with
+Workload (the MoE expert-parallel benchmark configuration): 48 layers, hidden 2048, 32 Q / 4 KV heads of 128, 128 experts top-8 with
 expert FFN 768, vocab 151936; random-init N(0, 0.02) weights quantised to MXFP8 (1x32 E8M0 scales), MXFP8
 activations, bf16 outputs; 64 prompts of 2048 uniform-random token ids are prefilled, then decoded greedily.
 With N GPUs the 64 sequences are split N ways for attention (data parallel) and the 128 experts N ways

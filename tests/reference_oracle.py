@@ -7,7 +7,9 @@ import shutil
 import subprocess
 import tempfile
 
-REF_ROOT = os.environ.get("GEMM_REFERENCE_ROOT", "/root/reference")
+# the reference checkout: GEMM_REFERENCE_ROOT, or a directory "reference" beside this repository
+REF_ROOT = os.environ.get("GEMM_REFERENCE_ROOT",
+                          os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 _cache = {}
 
 

@@ -17,8 +17,8 @@ def _launch(what: str, nproc: int, port: int):
            "--master-port", str(port), os.path.join(HERE, "multi_gpu_worker.py"), what]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     if r.returncode != 0:
-        log_dir = os.path.join(os.path.dirname(HERE), "gpurun_out")
-        if os.path.isdir(log_dir):
+        log_dir = os.environ.get("GB_TEST_LOG_DIR", "")        # where to leave the workers' output of a failed run
+        if log_dir and os.path.isdir(log_dir):
             with open(os.path.join(log_dir, f"multi_gpu_{what}.log"), "w") as f:
                 f.write(r.stdout + "\n---- stderr ----\n" + r.stderr)
     assert r.returncode == 0 and "MULTI_GPU_WORKER_OK" in r.stdout, (r.stdout[-3000:], r.stderr[-6000:])
