@@ -7,7 +7,8 @@ touches once per step, the KV cache of its sequences) and the communication-boun
 plus a fixed cost per kernel launch; prefill adds the tensor-core time.  Weights amortise over the batch, KV does not;
 an MoE layer touches only the experts some token selected: E * (1 - (1 - k/E)^B) of them in expectation.  The numbers
 are ceilings (routing, softmax and launch gaps beyond the fixed term are not modelled); ``--derate`` applies an
-efficiency factor.  Also reports whether weights + KV fit in HBM.
+efficiency factor.  Also reports whether weights + KV fit in HBM.  ``--cp 1,2,4,8`` prints the cost model of context-parallel
+decode attention instead (KV shard read time, size of the flash partial, all-gather / ring / tree merge times).
 
 Counterpart in the reference: tools/decode_estimate.py (per-step time = max(memory, communication), fit check, the same
 treatment of batch and context), with the platform constants replaced by this machine's measured ones.
@@ -102,6 +103,30 @@ def estimate(cfg: ModelConfig, batch: int, ctx: int, gpus: int = 1, fmt: str = "
     }
 
 
+def context_parallel_decode(cfg: ModelConfig, batch: int, ctx: int, cp: int, plat: Platform = Platform(), hop_us: float = 5.0) -> dict:
+    """Cost model of context-parallel decode attention (KV positions sharded block-cyclically over ``cp`` GPUs, every GPU computes
+    flash partials on its shard, the partials are merged).  Per layer and step a GPU reads 1/cp of the KV and owns a partial of
+    ``n_heads * (head_dim + 1)`` f32 per sequence (O normalised + log-sum-exp; 16 640 bytes for 32 heads of 128 plus the maximum,
+    the figure of the reference's ring-attention study).  Two ways to merge: the all-gather by peer stores that
+    ``parallel/context.py`` uses (one exchange: a launch-and-flag latency plus (cp-1) partials over the link), and a ring relay of
+    the running (m, l, o) state (cp-1 dependent hops, each a latency plus one partial): a64fx/utofu-tests/ring_attn_bench.c,
+    summary.md:71-118.  ``hop_us`` is the one-way latency of a peer store becoming visible (flag round included)."""
+    partial = batch * cfg.n_heads * (cfg.head_dim + 1) * 4
+    kv_layer = batch * ctx * 2 * cfg.n_kv_heads * cfg.head_dim * 2
+    link = plat.nvlink_gbs * 1e9
+    attn_us = kv_layer / cp / (plat.hbm_gbs * 1e9) * 1e6
+    gather_us = hop_us + (cp - 1) * partial / link * 1e6 if cp > 1 else 0.0
+    ring_us = (cp - 1) * (hop_us + partial / link * 1e6) if cp > 1 else 0.0
+    tree_us = 0.0
+    n = 1
+    while n < cp:                       # recursive doubling: log2(cp) exchanges of one partial
+        tree_us += hop_us + partial / link * 1e6
+        n *= 2
+    return {"kv_read_us_per_layer": attn_us, "partial_bytes": partial, "merge_allgather_us": gather_us, "merge_ring_us": ring_us,
+            "merge_tree_us": tree_us, "kv_gib_per_gpu": cfg.n_layers * kv_layer / cp / 2 ** 30,
+            "attention_us_per_layer": attn_us + min(gather_us, ring_us, tree_us) if cp > 1 else attn_us}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--model", default="qwen3-30b-a3b")
@@ -113,9 +138,15 @@ def main(argv=None):
     ap.add_argument("--derate", type=float, default=1.0)
     ap.add_argument("--hbm-gbs", type=float, default=Platform.hbm_gbs)
     ap.add_argument("--nvlink-gbs", type=float, default=Platform.nvlink_gbs)
+    ap.add_argument("--cp", default="", help="comma separated context-parallel degrees: print the long-context decode attention cost model instead")
     args = ap.parse_args(argv)
     cfg = get_config(args.model)
     plat = Platform(hbm_gbs=args.hbm_gbs, nvlink_gbs=args.nvlink_gbs)
+    if args.cp:
+        for c in [int(x) for x in args.cp.split(",")]:
+            r = context_parallel_decode(cfg, args.batch, args.ctx, c, plat)
+            print(json.dumps({"cp": c, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}}))
+        return
     for g in [int(x) for x in args.gpus.split(",")]:
         r = estimate(cfg, args.batch, args.ctx, g, args.format, args.mode, plat, args.derate)
         print(json.dumps({"gpus": g, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}}))

@@ -61,3 +61,15 @@ def test_dump_command_writes_layer_states(tmp_path, capsys):
     h = np.load(tmp_path / "layer_001.npy")
     lg = np.load(tmp_path / "logits.npy")
     assert h.shape == (5, 256) and lg.shape[0] == 5 and np.isfinite(h).all()
+
+
+def test_context_parallel_cost_model():
+    from gemm_b200.models.config import get_config
+    from gemm_b200.utils import estimate as est
+    cfg = get_config("qwen3-30b-a3b")
+    one = est.context_parallel_decode(cfg, 1, 1 << 20, 1)
+    eight = est.context_parallel_decode(cfg, 1, 1 << 20, 8)
+    assert one["partial_bytes"] == 32 * 129 * 4                       # 16 512 bytes of (O, lse) for 32 heads of 128
+    assert abs(eight["kv_read_us_per_layer"] * 8 - one["kv_read_us_per_layer"]) < 1e-6
+    assert eight["merge_allgather_us"] < eight["merge_tree_us"] < eight["merge_ring_us"]      # one exchange beats dependent hops on a switch
+    assert eight["attention_us_per_layer"] < one["attention_us_per_layer"]
