@@ -103,7 +103,7 @@ def _moe(args, t: int, name: str):
             ew.silu_mul_quant(gu, hq, hsf, pl.row_token, sf_layout=tn)
 
     def down():
-        gemm.grouped_linear(hq, d2.view(e, h, inter), pl.seg_start, pl.seg_count, tn, sfa=w2.sf, sfb=hsf, w_tiled=True)
+        gemm.grouped_linear(hq, d2.view(e, h, inter), pl.seg_start, pl.seg_count, tn, sfa=w2.sf, sfb=hsf, w_tiled=True, pair_rows=(tn == 32))
 
     gate_up()
     touched = int((pl.seg_count > 0).sum())
