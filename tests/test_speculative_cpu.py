@@ -1,0 +1,94 @@
+"""Speculative greedy decoding: the output equals plain greedy decoding whatever the drafts are (engine on CPU tensors)."""
+import torch
+
+from gemm_b200.models.config import get_config
+from gemm_b200.models.transformer import KvCache, Transformer
+from gemm_b200.models.weights import synthetic_weights
+from gemm_b200.serve.speculative import CallableDrafter, NgramDrafter, SpeculativeDecoder, accept_greedy
+
+
+def test_accept_rule():
+    assert accept_greedy([], [7]) == (0, 7)
+    assert accept_greedy([1, 2, 3], [1, 2, 3, 4]) == (3, 4)
+    assert accept_greedy([1, 9, 3], [1, 2, 3, 4]) == (1, 2)
+    assert accept_greedy([9, 2, 3], [1, 2, 3, 4]) == (0, 1)
+
+
+def test_ngram_drafter():
+    d = NgramDrafter(gamma=3, max_ngram=2)
+    assert d.propose([5, 6, 7, 8, 9, 5, 6]) == [7, 8, 9]
+    assert d.propose([1, 2, 3]) == []
+    assert d.propose([4, 4, 4, 4]) == [4]                     # latest earlier occurrence of (4, 4) is followed by one token
+    assert NgramDrafter(gamma=2, max_ngram=3).propose([1, 2, 3, 9, 1, 2, 3]) == [9, 1]
+
+
+def _decoder(name, drafter, page=16, n_pages=64):
+    cfg = get_config(name)
+    w = synthetic_weights(cfg, "bf16", device="cpu", seed=3)
+    kv = KvCache.allocate(cfg, n_pages, page, "cpu")
+    return cfg, SpeculativeDecoder(Transformer(w, kv), kv, page, n_pages, drafter)
+
+
+def test_speculative_equals_plain_greedy_for_any_draft():
+    torch.manual_seed(1)
+    cfg, plain = _decoder("tiny-dense", None)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (21, 9, 40)]
+    n_new = 14
+    ref = plain.generate(prompts, n_new)
+    assert all(len(o) == n_new for o in ref)
+    assert plain.stats.verify_steps == n_new - 1 and plain.stats.drafted == 0
+
+    # an oracle that knows the continuation: every draft is accepted, gamma + 1 tokens per step
+    full = [p + o for p, o in zip(prompts, ref)]
+
+    def oracle(tokens):
+        for f in full:
+            if list(tokens) == f[: len(tokens)]:
+                return f[len(tokens): len(tokens) + 4]
+        return []
+    _, dec = _decoder("tiny-dense", CallableDrafter(oracle, gamma=4))
+    assert dec.generate(prompts, n_new) == ref
+    assert dec.stats.acceptance == 1.0 and dec.stats.verify_steps == 3          # 1 + 5 + 5 + 3 tokens
+    assert dec.stats.produced == 3 * (n_new - 1)
+
+    # drafts that are right for two tokens and then wrong: the wrong tail is dropped, its K/V overwritten later
+    def half_right(tokens):
+        good = oracle(tokens)[:2]
+        return good + [(good[-1] + 1) % cfg.vocab if good else 0, 1]
+    _, dec = _decoder("tiny-dense", CallableDrafter(half_right, gamma=4))
+    assert dec.generate(prompts, n_new) == ref
+    assert 0.0 < dec.stats.acceptance < 1.0
+
+    # always wrong: one token per step, like plain decoding
+    _, dec = _decoder("tiny-dense", CallableDrafter(lambda t: [(t[-1] + 1) % 7, 3, 3], gamma=3))
+    out = dec.generate(prompts, n_new)
+    assert out == ref
+
+    # prompt lookup (whatever it finds) and a stop token
+    _, dec = _decoder("tiny-dense", NgramDrafter(gamma=3))
+    assert dec.generate(prompts, n_new) == ref
+    stop = ref[0][5]
+    _, dec = _decoder("tiny-dense", CallableDrafter(oracle, gamma=4))
+    got = dec.generate(prompts, n_new, stop_token_ids=[stop])
+    for g, r in zip(got, ref):
+        cut = r.index(stop) + 1 if stop in r else len(r)
+        assert g == r[:cut]
+
+
+def test_moe_model_and_hybrid_refusal():
+    torch.manual_seed(2)
+    cfg, plain = _decoder("tiny-moe", None)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (12, 30)]
+    ref = plain.generate(prompts, 8)
+    full = [p + o for p, o in zip(prompts, ref)]
+
+    def oracle(tokens):
+        for f in full:
+            if list(tokens) == f[: len(tokens)]:
+                return f[len(tokens): len(tokens) + 3]
+        return []
+    _, dec = _decoder("tiny-moe", CallableDrafter(oracle, gamma=3))
+    assert dec.generate(prompts, 8) == ref
+    import pytest
+    with pytest.raises(ValueError):
+        _decoder("tiny-qwen35", None)
