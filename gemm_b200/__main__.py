@@ -64,13 +64,22 @@ def cmd_generate(args):
         else:
             enc.append(llm.tokenizer.encode(p))
     t0 = time.time()
-    outs = llm.generate(enc, sp)
+    stats = None
+    if args.speculative > 0:
+        if args.temperature != 0.0:
+            sys.exit("--speculative verifies drafts against greedy choices: use it with --temperature 0")
+        outs, stats = llm.generate_speculative(enc, args.max_new_tokens, gamma=args.speculative)
+    else:
+        outs = llm.generate(enc, sp)
     dt = time.time() - t0
     n_new = sum(len(o) for o in outs)
     for p, o in zip(prompts, outs):
         text = llm.decode(o) if llm.tokenizer is not None else " ".join(map(str, o))
         print(json.dumps({"prompt": p, "completion": text, "token_ids": o}))
-    print(json.dumps({"new_tokens": n_new, "seconds": round(dt, 3), "tokens_per_s": round(n_new / max(dt, 1e-9), 1)}), file=sys.stderr)
+    summary = {"new_tokens": n_new, "seconds": round(dt, 3), "tokens_per_s": round(n_new / max(dt, 1e-9), 1)}
+    if stats is not None:
+        summary.update(verify_steps=stats.verify_steps, draft_acceptance=round(stats.acceptance, 3), tokens_per_step=round(stats.tokens_per_step, 2))
+    print(json.dumps(summary), file=sys.stderr)
 
 
 def cmd_serve(args):
@@ -224,6 +233,8 @@ def main(argv=None):
     g.add_argument("--top-k", type=int, default=0)
     g.add_argument("--top-p", type=float, default=1.0)
     g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--speculative", type=int, default=0, metavar="GAMMA",
+                   help="greedy speculative decoding with prompt-lookup drafts of up to GAMMA tokens, verified in one batched step")
     g.set_defaults(fn=cmd_generate)
     s = sub.add_parser("serve", help="HTTP server")
     _add_model_args(s)

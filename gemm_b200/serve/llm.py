@@ -41,6 +41,7 @@ class LLM:
         self.tokenizer = tokenizer
         self.device = weights.embed.device
         self.page_size = page_size
+        self.num_pages = num_pages
         hkv_local = max(1, self.cfg.n_kv_heads // weights.tp_size)
         self.kv = KvCache.allocate(self.cfg, num_pages, page_size, self.device, hkv_local, n_layers=len(weights.layers), n_seq_slots=max_running)
         self._free_slots = list(range(max_running))       # recurrent-state slots of the hybrid models, one per running request
@@ -132,6 +133,19 @@ class LLM:
         while self.has_work():
             self.step()
         return [self._reqs.pop(r).out for r in rids]
+
+    def generate_speculative(self, prompts: Sequence, max_new_tokens: int = 64, gamma: int = 4, drafter=None,
+                             stop_token_ids: Sequence[int] = ()):
+        """Greedy generation with speculative decoding (``serve/speculative.py``): same tokens as greedy ``generate``, fewer
+        model steps when the drafts hit.  Uses the whole cache, so no request may be in flight.  Returns (outputs, statistics)."""
+        from .speculative import NgramDrafter, SpeculativeDecoder
+        if self.has_work():
+            raise RuntimeError("speculative generation needs an idle engine")
+        if self.blocks.num_free != self.num_pages:
+            raise RuntimeError("speculative generation needs an empty cache")
+        dec = SpeculativeDecoder(self.model, self.kv, self.page_size, self.num_pages, drafter or NgramDrafter(gamma=gamma))
+        enc = [self.tokenizer.encode(p) if isinstance(p, str) else list(p) for p in prompts]
+        return dec.generate(enc, max_new_tokens, stop_token_ids), dec.stats
 
     def stream(self, prompt, sp: Optional[SamplingParams] = None) -> Iterator[int]:
         """Yield the tokens of one request as they are produced (other queued requests keep being served)."""

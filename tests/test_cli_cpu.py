@@ -73,3 +73,16 @@ def test_context_parallel_cost_model():
     assert abs(eight["kv_read_us_per_layer"] * 8 - one["kv_read_us_per_layer"]) < 1e-6
     assert eight["merge_allgather_us"] < eight["merge_tree_us"] < eight["merge_ring_us"]      # one exchange beats dependent hops on a switch
     assert eight["attention_us_per_layer"] < one["attention_us_per_layer"]
+
+
+def test_generate_speculative_flag_gives_the_greedy_tokens(capsys):
+    base = ["generate", "--model", "synthetic:tiny-dense", "--device", "cpu", "--ids", "--prompt", "1 2 3 1 2 3 1 2", "--prompt", "7 7 7 7",
+            "--max-new-tokens", "10", "--pages", "16", "--page-size", "16"]
+    main(base)
+    plain = [json.loads(l)["token_ids"] for l in capsys.readouterr().out.strip().splitlines()]
+    main(base + ["--speculative", "3"])
+    cap = capsys.readouterr()
+    spec = [json.loads(l)["token_ids"] for l in cap.out.strip().splitlines()]
+    assert spec == plain
+    summary = json.loads(cap.err.strip().splitlines()[-1])
+    assert summary["verify_steps"] <= 9 and "draft_acceptance" in summary
