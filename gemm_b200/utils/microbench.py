@@ -12,6 +12,8 @@ Cases
   attn_decode  paged flash-decode, 64 sequences x 2048 cached tokens, 32 query / 4 KV heads
   attn_prefill causal prefill, 8 sequences x 2048 tokens
   lm_head      64 x 151936 x 2048 with the arg-max epilogue
+  spec_verify  whole-model step over 1, 2, 3 and 5 positions per sequence (speculative verification against plain decode);
+               builds the full Qwen3-30B-A3B shape, not part of ``all``
 
 Counterpart in the reference: cuda/gemm/bench_log.md and cuda/fa2/bench_log.md are produced by stand-alone bench
 programs of the same kind.
@@ -164,13 +166,71 @@ def case_lm_head(args):
     _run("lm_head_argmax", lambda: gemm.linear_argmax(x, w, w_tiled=True), 2.0 * m * n * k, n * k * 2, args)
 
 
+def case_spec_verify(args):
+    """Cost of a speculative-decoding verify step (1 + gamma query positions per sequence through the chunked-prefill path)
+    against a plain decode step, on the benchmark model: 64 sequences x 2048 cached tokens, MXFP8."""
+    from ..models.config import get_config
+    from ..models.transformer import ForwardBatch
+    from ..models.weights import synthetic_weights
+    from ..serve.engine import Engine
+    name, b, ctx = "qwen3-30b-a3b", (args.batch or 64), (args.ctx if args.ctx >= 0 else 2048)
+    cfg = get_config(name)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    w = synthetic_weights(cfg, "mxfp8", device=dev, seed=0)
+    eng = Engine(w, max_batch=b, max_seq_len=ctx + 16, page_size=128, max_prefill_tokens=16384)
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab, (b, ctx), generator=g, dtype=torch.int32)
+    eng.prefill([prompts[i] for i in range(b)], reserve=8)
+    bt = eng._block_table(range(b))
+    variants = {}
+    for q in (1, 2, 3, 5):
+        ids = torch.randint(0, cfg.vocab, (b * q,), generator=g, dtype=torch.int32)
+        splits = att.pick_splits(b, eng.hkv_local, ctx + 8) if q == 1 else 1
+        variants[q] = ForwardBatch.build([q] * b, [ctx] * b, ids, bt, 128, eng.hq_local, eng.hkv_local, dev, num_splits=splits, all_logits=True)
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(max(3, args.iters // 2)):
+            a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(e))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    with torch.no_grad():
+        base = None
+        for q, fb in variants.items():
+            ms = timed(lambda: eng.model.forward_greedy(fb))
+            base = base or ms
+            print(json.dumps(dict(case="spec_verify_eager", positions_per_seq=q, tokens=b * q, ms=round(ms, 3), vs_one=round(ms / base, 3))), flush=True)
+        base = None
+        for q, fb in variants.items():             # the same steps replayed from a CUDA graph (no host time between launches)
+            try:
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    eng.model.forward_greedy(fb)
+                ms = timed(gr.replay)
+            except Exception as exc:               # a host read inside the step cannot be captured: the eager figure stands
+                print(json.dumps(dict(case="spec_verify_graph", positions_per_seq=q, error=str(exc)[:120])), flush=True)
+                break
+            base = base or ms
+            print(json.dumps(dict(case="spec_verify_graph", positions_per_seq=q, tokens=b * q, ms=round(ms, 3), vs_one=round(ms / base, 3))), flush=True)
+
+
+MODEL_CASES = {"spec_verify": case_spec_verify}      # build the whole benchmark model: not part of --case all
 CASES = {"gemm": case_gemm, "moe_decode": case_moe_decode, "moe_prefill": case_moe_prefill, "attn_decode": case_attn_decode,
          "attn_prefill": case_attn_prefill, "lm_head": case_lm_head}
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES))
+    ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES) + sorted(MODEL_CASES))
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--splits", type=int, default=0, help="attention cases: force the number of KV splits")
     ap.add_argument("--hq", type=int, default=32)
@@ -182,7 +242,7 @@ def main(argv=None):
     args = ap.parse_args(argv)
     torch.manual_seed(0)
     for name in (sorted(CASES) if args.case == "all" else [args.case]):
-        CASES[name](args)
+        (CASES.get(name) or MODEL_CASES[name])(args)
     print(json.dumps(dict(kernel_status=_native.read_status()["what"])), flush=True)
 
 
