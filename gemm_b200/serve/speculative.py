@@ -8,8 +8,9 @@ decoding token for token.  Rejected positions need no cache roll-back: their K/V
 length, attention never reads past ``kv_len``, and the next step overwrites them (slots are a function of the position).
 That holds for attention layers only: recurrent (Delta-Net) state cannot be rewound, so hybrid models are refused.
 
-Two drafters are provided: ``NgramDrafter`` (prompt lookup: continue the most recent earlier occurrence of the current
-suffix; needs no second model) and ``CallableDrafter`` (wraps any function, e.g. a small draft model's greedy decode).
+Three drafters are provided: ``NgramDrafter`` (prompt lookup: continue the most recent earlier occurrence of the current
+suffix; needs no second model), ``ModelDrafter`` (a smaller model of the same vocabulary with its own paged cache, batched
+over the live sequences) and ``CallableDrafter`` (wraps any function).
 
 Counterpart in the reference: the multi-token-prediction draft of depth 1 with batched verification of the DeepSeek engine
 (a64fx/ds4f/DS4P_DECODE_PERF_FINDINGS.md:43-61), generalised to any draft source and depth.
@@ -50,6 +51,75 @@ class CallableDrafter:
 
     def propose(self, tokens: Sequence[int]) -> List[int]:
         return list(self.fn(tokens))[: self.gamma]
+
+
+class ModelDrafter:
+    """Drafts from a (smaller) model of the same vocabulary, decoded greedily with its own paged cache, for all live sequences
+    at once: one catch-up step over the tokens the draft cache does not hold yet (the tokens the target accepted or produced
+    since the last call), then ``gamma - 1`` single-token steps.  The draft cache follows the target's decisions the same way
+    the target's does: positions beyond the common prefix of what it was fed and what was kept are overwritten."""
+
+    def __init__(self, model: Transformer, kv: KvCache, page_size: int, num_pages: int, gamma: int = 4):
+        if model.cfg.is_hybrid:
+            raise ValueError("a draft model with recurrent layers cannot drop rejected positions")
+        self.model, self.kv, self.page, self.gamma = model, kv, page_size, gamma
+        self.blocks = KvBlockManager(num_pages, page_size)
+        self.device = model.w.embed.device
+        self._seq = {}                # key -> sequence handle of the block manager
+        self._held = {}               # key -> tokens whose K/V the draft cache holds, in position order
+        self.steps = 0
+
+    def _step(self, keys, q_lens, ctx, ids) -> List[int]:
+        pages = [self.blocks.pages(self._seq[k]) for k in keys]
+        bt = torch.zeros(len(keys), max(len(p) for p in pages), dtype=torch.int32)
+        for i, p in enumerate(pages):
+            bt[i, : len(p)] = torch.tensor(p, dtype=torch.int32)
+        m = self.model
+        fb = ForwardBatch.build(q_lens, ctx, ids, bt, self.page, m.hq_local, m.hkv_local, self.device)
+        self.steps += 1
+        return [int(t) for t in m.forward_greedy(fb).cpu()]
+
+    @torch.no_grad()
+    def propose_batch(self, keys: Sequence[int], tokens: Sequence[Sequence[int]], limits: Sequence[int]) -> List[List[int]]:
+        drafts: List[List[int]] = [[] for _ in keys]
+        act = [i for i in range(len(keys)) if limits[i] > 0]
+        if not act:
+            return drafts
+        q_lens, ctx, ids = [], [], []
+        for i in act:
+            k, t = keys[i], list(tokens[i])
+            if k not in self._seq:
+                self._seq[k], self._held[k] = self.blocks.new_sequence(), []
+            self.blocks.reserve(self._seq[k], len(t) + self.gamma + 1)
+            held = self._held[k]
+            c = 0
+            while c < len(held) and c < len(t) - 1 and held[c] == t[c]:
+                c += 1
+            q_lens.append(len(t) - c)
+            ctx.append(c)
+            ids.extend(t[c:])
+            self._held[k] = t
+        nxt = self._step([keys[i] for i in act], q_lens, ctx, ids)
+        for i, d in zip(act, nxt):
+            drafts[i].append(d)
+        for j in range(1, self.gamma):
+            act = [i for i in act if limits[i] > j]
+            if not act:
+                break
+            ctx = [len(tokens[i]) + j - 1 for i in act]
+            ids = [drafts[i][-1] for i in act]
+            for i in act:
+                self._held[keys[i]] = self._held[keys[i]] + [drafts[i][-1]]
+            nxt = self._step([keys[i] for i in act], [1] * len(act), ctx, ids)
+            for i, d in zip(act, nxt):
+                drafts[i].append(d)
+        return drafts
+
+    def finish(self, keys: Sequence[int]) -> None:
+        for k in keys:
+            if k in self._seq:
+                self.blocks.release(self._seq.pop(k))
+                self._held.pop(k, None)
 
 
 def accept_greedy(draft: Sequence[int], target: Sequence[int]) -> Tuple[int, int]:
@@ -121,11 +191,12 @@ class SpeculativeDecoder:
         done = [len(o) >= max_new_tokens or o[-1] in stop for o in out]
         while not all(done):
             live = [i for i in range(n_seq) if not done[i]]
-            drafts = []
-            for i in live:
-                room = max_new_tokens - len(out[i]) - 1           # tokens that may still follow the guaranteed one
-                d = self.drafter.propose(toks[i])[: max(0, min(gamma, room))] if self.drafter is not None else []
-                drafts.append([int(t) for t in d])
+            rooms = [max(0, min(gamma, max_new_tokens - len(out[i]) - 1)) for i in live]   # drafts that may follow the sure token
+            if hasattr(self.drafter, "propose_batch"):
+                drafts = [[int(t) for t in d][:r] for d, r in zip(self.drafter.propose_batch(live, [toks[i] for i in live], rooms), rooms)]
+            else:
+                drafts = [[int(t) for t in self.drafter.propose(toks[i])][:r] if self.drafter is not None and r > 0 else []
+                          for i, r in zip(live, rooms)]
             q_lens = [1 + len(d) for d in drafts]
             ids = []
             for i, d in zip(live, drafts):
@@ -152,4 +223,6 @@ class SpeculativeDecoder:
             self.stats.per_step.append(step_tokens)
         for s in seqs:
             self.blocks.release(s)
+        if hasattr(self.drafter, "finish"):
+            self.drafter.finish(range(n_seq))
         return out

@@ -92,3 +92,30 @@ def test_moe_model_and_hybrid_refusal():
     import pytest
     with pytest.raises(ValueError):
         _decoder("tiny-qwen35", None)
+
+
+def test_draft_model():
+    """A draft model equal to the target gets every draft accepted; a different one changes the step count, never the tokens."""
+    from gemm_b200.serve.speculative import ModelDrafter
+    torch.manual_seed(6)
+    cfg, plain = _decoder("tiny-dense", None)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (18, 35, 7)]
+    n_new = 13
+    ref = plain.generate(prompts, n_new)
+
+    def drafter(seed, gamma=3):
+        w = synthetic_weights(cfg, "bf16", device="cpu", seed=seed)
+        kv = KvCache.allocate(cfg, 64, 16, "cpu")
+        return ModelDrafter(Transformer(w, kv), kv, 16, 64, gamma=gamma)
+
+    same = drafter(3)                                       # the weights of the target
+    _, dec = _decoder("tiny-dense", same)
+    assert dec.generate(prompts, n_new) == ref
+    assert dec.stats.acceptance == 1.0 and dec.stats.verify_steps == 3          # 1 + 4 + 4 + 4 tokens
+    assert same.blocks.num_free == 64                       # the draft cache is returned
+    other = drafter(11)
+    _, dec = _decoder("tiny-dense", other)
+    assert dec.generate(prompts, n_new) == ref
+    assert dec.stats.acceptance < 1.0 and dec.stats.drafted > 0
+    # a second group on the same drafter starts from clean sequences
+    assert dec.generate(prompts[:2], 6) == [r[:6] for r in ref[:2]]
