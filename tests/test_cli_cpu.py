@@ -86,3 +86,13 @@ def test_generate_speculative_flag_gives_the_greedy_tokens(capsys):
     assert spec == plain
     summary = json.loads(cap.err.strip().splitlines()[-1])
     assert summary["verify_steps"] <= 9 and "draft_acceptance" in summary
+
+
+def test_speculative_speedup_model():
+    from gemm_b200.utils.estimate import speculative_speedup
+    r = speculative_speedup(1.0, 4, 1.38)
+    assert r["tokens_per_step"] == 5.0 and abs(r["speedup"] - 5 / 1.38) < 1e-9
+    r = speculative_speedup(0.0, 4, 1.38)
+    assert r["tokens_per_step"] == 1.0 and r["speedup"] < 1.0
+    r = speculative_speedup(0.5, 2, 1.26)
+    assert abs(r["tokens_per_step"] - 1.75) < 1e-9
