@@ -94,6 +94,7 @@ struct Scheduler {
   std::vector<Request> running;
   std::vector<PlanItem> last_plan;
   long clock = 0; long n_preempted = 0;
+  int lookahead = 0;       // speculative decoding: extra positions a decode item may fill with draft tokens
 
   // One engine step: every running sequence that finished its prompt decodes one token; what is left of the token
   // budget goes to prompt chunks, oldest request first; new requests are admitted while slots and pages allow.
@@ -105,7 +106,7 @@ struct Scheduler {
     for (size_t i = 0; i < running.size();) {
       Request& r = running[i];
       if (r.computed < r.prompt_len) { ++i; continue; }
-      const int total = r.prompt_len + r.generated + 1;
+      const int total = r.prompt_len + r.generated + 1 + lookahead;
       bool ok = kv->reserve(r.seq, total) == 0;
       while (!ok && running.size() > 1) {
         // recompute-preemption of the youngest other request
@@ -125,7 +126,7 @@ struct Scheduler {
       Request& rr = running[i];
       out.push_back({rr.id, rr.seq, 1, rr.prompt_len + rr.generated - 1 + 0, 0, 1});
       out.back().ctx_len = rr.prompt_len + rr.generated - 1;     // positions already cached before this token
-      --budget; ++i;
+      budget -= 1 + lookahead; ++i;
     }
     // prompt chunks of running requests
     for (Request& r : running) {
@@ -154,14 +155,15 @@ struct Scheduler {
   }
 
   // After the step ran: advance the requests; `finished[i] != 0` marks items whose sequence hit a stop condition.
-  void commit(const int* finished, int n) {
+  // `advance[i]` (optional) is the number of tokens a decode item produced: 1, or more after accepted draft tokens.
+  void commit(const int* finished, int n, const int* advance = nullptr) {
     for (int i = 0; i < n && i < (int)last_plan.size(); ++i) {
       const PlanItem& it = last_plan[i];
       for (size_t j = 0; j < running.size(); ++j) {
         Request& r = running[j];
         if (r.id != it.req_id) continue;
         if (it.is_prefill) { r.computed += it.q_len; if (it.emits_token) r.generated += 1; }
-        else r.generated += 1;
+        else r.generated += (advance && advance[i] > 1) ? advance[i] : 1;
         const bool done = (finished && finished[i]) || r.generated >= r.max_new;
         if (done && r.computed >= r.prompt_len) { kv->release(r.seq); running.erase(running.begin() + (long)j); }
         break;
@@ -260,6 +262,8 @@ GBH_API int gbh_sched_plan(void* h, long* req_id, int* seq, int* q_len, int* ctx
   return (int)items.size();
 }
 GBH_API void gbh_sched_commit(void* h, const int* finished, int n) { ((Scheduler*)h)->commit(finished, n); }
+GBH_API void gbh_sched_commit_n(void* h, const int* finished, const int* advance, int n) { ((Scheduler*)h)->commit(finished, n, advance); }
+GBH_API void gbh_sched_set_lookahead(void* h, int extra) { ((Scheduler*)h)->lookahead = extra < 0 ? 0 : extra; }
 GBH_API int gbh_sched_num_waiting(void* h) { return (int)((Scheduler*)h)->waiting.size(); }
 GBH_API int gbh_sched_num_running(void* h) { return (int)((Scheduler*)h)->running.size(); }
 GBH_API long gbh_sched_num_preempted(void* h) { return ((Scheduler*)h)->n_preempted; }

@@ -52,6 +52,10 @@ class LLM:
         self._reqs: Dict[int, _Req] = {}
         self._next_id = 0
         self.steps = 0
+        self.drafter = None                                 # speculative decoding of greedy requests inside the batching loop
+        self.produced_all: Dict[int, List[int]] = {}        # every token of the last step, per request (several after accepted drafts)
+        self.spec_drafted = 0
+        self.spec_accepted = 0
 
     # ------------------------------------------------------------------------------------------ constructors
     @classmethod
@@ -78,6 +82,15 @@ class LLM:
         self.sched.add(rid, len(prompt_ids), sp.max_new_tokens)
         return rid
 
+    def set_drafter(self, drafter) -> None:
+        """Speculative decoding inside continuous batching: decode items of greedy requests carry up to ``drafter.gamma`` draft
+        tokens (``drafter.propose(tokens)``, e.g. ``serve.speculative.NgramDrafter``), verified in the same step; the scheduler
+        reserves the extra positions and counts them against the token budget.  ``None`` switches it off."""
+        if drafter is not None and self.cfg.is_hybrid:
+            raise ValueError("speculative decoding needs a cache that can drop rejected positions: recurrent layers cannot")
+        self.drafter = drafter
+        self.sched.set_lookahead(drafter.gamma if drafter is not None else 0)
+
     def has_work(self) -> bool:
         return self.sched.num_waiting > 0 or self.sched.num_running > 0
 
@@ -87,39 +100,72 @@ class LLM:
         plan = self.sched.plan()
         if not plan:
             return {}
-        q_lens, ctx, ids, emit_rows = [], [], [], []
+        q_lens, ctx, ids, drafts = [], [], [], []
         max_pages = max(len(self.blocks.pages(it.seq)) for it in plan)
         bt = torch.zeros(len(plan), max_pages, dtype=torch.int32)
         for i, it in enumerate(plan):
             r = self._reqs[it.req_id]
             pages = self.blocks.pages(it.seq)
             bt[i, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
-            q_lens.append(it.q_len)
+            draft: List[int] = []
+            if self.drafter is not None and not it.is_prefill and r.sp.temperature <= 0:
+                room = min(self.drafter.gamma, r.sp.max_new_tokens - len(r.out) - 1)
+                if room > 0:
+                    draft = [int(t) for t in self.drafter.propose(r.tokens)][:room]
+            drafts.append(draft)
+            q_lens.append(it.q_len + len(draft))
             ctx.append(it.ctx_len)
-            ids.extend(r.tokens[it.ctx_len: it.ctx_len + it.q_len])
+            ids.extend(r.tokens[it.ctx_len: it.ctx_len + it.q_len] + draft)
             if it.req_id not in self._slot_of:              # first chunk of this request: take a state slot and clear it
                 self._slot_of[it.req_id] = self._free_slots.pop()
                 self.kv.reset_slots([self._slot_of[it.req_id]])
         fb = ForwardBatch.build(q_lens, ctx, ids, bt, self.page_size, self.model.hq_local, self.model.hkv_local, self.device,
                                 seq_slots=[self._slot_of[it.req_id] for it in plan])
-        logits = self.model.forward(fb)                     # one row per plan item (its last token)
+        # logits: one row per plan item (its last token); an item with draft tokens gets a row for each of its positions
+        row0, rows, p0 = [], [], 0
+        for q, d in zip(q_lens, drafts):
+            row0.append(len(rows))
+            rows.extend(range(p0 + q - 1 - len(d), p0 + q))
+            p0 += q
+        if any(drafts):
+            fb.logit_rows = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        logits = self.model.forward(fb)
         produced: Dict[int, int] = {}
-        finished = []
+        self.produced_all = {}
+        finished, advance = [], []
         for i, it in enumerate(plan):
             r = self._reqs[it.req_id]
             fin = False
+            new: List[int] = []
             if it.emits_token:
                 sp = r.sp
-                tok = int(sampling.sample(logits[i:i + 1], sp.temperature, sp.top_k, sp.top_p, sp.seed + it.req_id, len(r.out))[0])
-                r.tokens.append(tok)
-                r.out.append(tok)
-                produced[it.req_id] = tok
-                fin = tok in sp.stop_token_ids or len(r.out) >= sp.max_new_tokens
+                if drafts[i]:
+                    from .speculative import accept_greedy
+                    target = sampling.argmax(logits[row0[i]: row0[i] + len(drafts[i]) + 1]).cpu().tolist()
+                    n_keep, nxt = accept_greedy(drafts[i], target)
+                    new = drafts[i][:n_keep] + [nxt]
+                    self.spec_drafted += len(drafts[i])
+                    self.spec_accepted += n_keep
+                else:
+                    j = row0[i]
+                    new = [int(sampling.sample(logits[j:j + 1], sp.temperature, sp.top_k, sp.top_p, sp.seed + it.req_id, len(r.out))[0])]
+                kept = []
+                for tok in new:
+                    r.tokens.append(tok)
+                    r.out.append(tok)
+                    kept.append(tok)
+                    if tok in sp.stop_token_ids or len(r.out) >= sp.max_new_tokens:
+                        fin = True
+                        break
+                new = kept
+                produced[it.req_id] = new[-1]
+                self.produced_all[it.req_id] = new
                 r.done = fin
             finished.append(fin)
+            advance.append(max(1, len(new)))
             if fin and it.req_id in self._slot_of:
                 self._free_slots.append(self._slot_of.pop(it.req_id))
-        self.sched.commit(finished)
+        self.sched.commit(finished, advance if any(a > 1 for a in advance) else None)
         self.steps += 1
         return produced
 
@@ -152,9 +198,9 @@ class LLM:
         ids = self.tokenizer.encode(prompt) if isinstance(prompt, str) else list(prompt)
         rid = self.add_request(ids, sp)
         while not self._reqs[rid].done and self.has_work():
-            out = self.step()
-            if rid in out:
-                yield out[rid]
+            self.step()
+            for tok in self.produced_all.get(rid, ()):
+                yield tok
         self._reqs.pop(rid, None)
 
     def decode(self, ids: Sequence[int]) -> str:

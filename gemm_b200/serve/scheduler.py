@@ -95,9 +95,18 @@ class Scheduler:
         n = _lib().gbh_sched_plan(ctypes.c_void_p(self._h), rid, *arrs, c)
         return [PlanItem(rid[i], arrs[0][i], arrs[1][i], arrs[2][i], bool(arrs[3][i]), bool(arrs[4][i])) for i in range(min(n, c))]
 
-    def commit(self, finished: Sequence[bool]) -> None:
+    def commit(self, finished: Sequence[bool], advance: Optional[Sequence[int]] = None) -> None:
+        """``advance[i]``: tokens a decode item produced this step (more than one after accepted draft tokens)."""
         arr = (ctypes.c_int * max(1, len(finished)))(*[1 if f else 0 for f in finished])
-        _lib().gbh_sched_commit(ctypes.c_void_p(self._h), arr, len(finished))
+        if advance is None:
+            _lib().gbh_sched_commit(ctypes.c_void_p(self._h), arr, len(finished))
+        else:
+            adv = (ctypes.c_int * max(1, len(finished)))(*[int(a) for a in advance])
+            _lib().gbh_sched_commit_n(ctypes.c_void_p(self._h), arr, adv, len(finished))
+
+    def set_lookahead(self, extra: int) -> None:
+        """Decode items reserve (and are budgeted for) ``extra`` more positions: room for draft tokens of speculative decoding."""
+        _lib().gbh_sched_set_lookahead(ctypes.c_void_p(self._h), int(extra))
 
     @property
     def num_waiting(self) -> int:

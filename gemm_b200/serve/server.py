@@ -64,13 +64,14 @@ class EngineThread(threading.Thread):
                 pass
             if not self.llm.has_work():
                 continue
-            produced = self.llm.step()
-            self.tokens_total += len(produced)
-            for rid, tok in produced.items():
+            self.llm.step()
+            for rid, toks in self.llm.produced_all.items():
+                self.tokens_total += len(toks)
                 q = self.streams.get(rid)
                 if q is None:
                     continue
-                q.put(tok)
+                for tok in toks:
+                    q.put(tok)
                 if self.llm._reqs[rid].done:
                     q.put(None)
                     del self.streams[rid]

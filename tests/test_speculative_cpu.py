@@ -119,3 +119,50 @@ def test_draft_model():
     assert dec.stats.acceptance < 1.0 and dec.stats.drafted > 0
     # a second group on the same drafter starts from clean sequences
     assert dec.generate(prompts[:2], 6) == [r[:6] for r in ref[:2]]
+
+
+def test_drafts_inside_continuous_batching():
+    """``LLM.set_drafter``: decode items carry draft tokens through the scheduler (reserved look-ahead positions, several
+    tokens committed per step); outputs equal those of the plain engine, with fewer steps when the drafts hit."""
+    from gemm_b200.serve.engine import SamplingParams
+    from gemm_b200.serve.llm import LLM
+    torch.manual_seed(8)
+    cfg = get_config("tiny-dense")
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (19, 5, 33, 12, 27)]
+    sp = SamplingParams(max_new_tokens=11)
+
+    def make():
+        return LLM.from_synthetic("tiny-dense", device="cpu", seed=3, max_running=3, max_batch_tokens=48, num_pages=32, page_size=16)
+    plain = make()
+    ref = plain.generate(prompts, sp)
+    full = [p + o for p, o in zip(prompts, ref)]
+
+    def oracle(tokens):
+        for f in full:
+            if list(tokens) == f[: len(tokens)]:
+                return f[len(tokens): len(tokens) + 3]
+        return []
+    llm = make()
+    llm.set_drafter(CallableDrafter(oracle, gamma=3))
+    assert llm.generate(prompts, sp) == ref
+    assert llm.spec_accepted == llm.spec_drafted > 0 and llm.steps < plain.steps
+    assert llm.blocks.num_free == 32
+
+    wrong = make()
+    wrong.set_drafter(CallableDrafter(lambda t: [(t[-1] + 1) % 5, 2, 2], gamma=3))
+    assert wrong.generate(prompts, sp) == ref
+    assert wrong.spec_accepted < wrong.spec_drafted
+
+    # sampled requests take no drafts; greedy ones beside them still do; streaming yields every accepted token
+    mixed = make()
+    mixed.set_drafter(CallableDrafter(oracle, gamma=3))
+    a = mixed.add_request(prompts[0], sp)
+    b = mixed.add_request(prompts[1], SamplingParams(max_new_tokens=6, temperature=0.8, top_k=20, seed=1))
+    while mixed.has_work():
+        mixed.step()
+    assert mixed._reqs[a].out == ref[0] and len(mixed._reqs[b].out) == 6
+    st = make()
+    st.set_drafter(CallableDrafter(oracle, gamma=3))
+    assert list(st.stream(prompts[2], sp)) == ref[2]
+    st.set_drafter(None)
+    assert st.generate([prompts[3]], sp) == [ref[3]]
