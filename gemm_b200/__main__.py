@@ -85,6 +85,9 @@ def cmd_generate(args):
 def cmd_serve(args):
     from .serve.server import serve
     llm = _load_llm(args)
+    if args.speculative > 0:
+        from .serve.speculative import NgramDrafter
+        llm.set_drafter(NgramDrafter(gamma=args.speculative))
     print(f"serving {args.model} on http://{args.host}:{args.port}", file=sys.stderr)
     serve(llm, host=args.host, port=args.port, model_name=args.name or args.model, block=True)
 
@@ -240,6 +243,8 @@ def main(argv=None):
     _add_model_args(s)
     s.add_argument("--host", default="127.0.0.1")
     s.add_argument("--port", type=int, default=8080)
+    s.add_argument("--speculative", type=int, default=0, metavar="GAMMA",
+                   help="greedy requests decode speculatively with prompt-lookup drafts of up to GAMMA tokens")
     s.add_argument("--name", default="")
     s.set_defaults(fn=cmd_serve)
     i = sub.add_parser("inspect", help="dump a GGUF file")

@@ -51,6 +51,14 @@ def test_server_endpoints():
         assert all(r == out["token_ids"] for r in results)
         prog = json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/progress", timeout=10).read())
         assert prog["tokens_generated"] > 0 and prog["running"] == 0
+        # speculative decoding behind the same endpoints: same tokens, every accepted token is delivered
+        from gemm_b200.serve.speculative import NgramDrafter
+        long_plain = json.loads(_post(port, "/v1/completions", {"prompt": "the quick brown fox the quick", "max_tokens": 12}))["token_ids"]
+        llm.set_drafter(NgramDrafter(gamma=3))
+        long_spec = json.loads(_post(port, "/v1/completions", {"prompt": "the quick brown fox the quick", "max_tokens": 12}))["token_ids"]
+        assert long_spec == long_plain
+        raw = _post(port, "/v1/completions", {"prompt": "the quick brown fox the quick", "max_tokens": 12, "stream": True}).decode()
+        assert len([l for l in raw.splitlines() if l.startswith("data: ") and l != "data: [DONE]"]) >= len(long_plain)
     finally:
         httpd.shutdown()
         eng.stop_flag = True
