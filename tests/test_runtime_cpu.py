@@ -54,6 +54,30 @@ def test_scheduler_chunked_prefill_and_decode_first():
     assert s.num_running == 0 and kv.num_free == 64
 
 
+def test_scheduler_lookahead_and_multi_token_commit():
+    """Speculative decoding: decode items reserve and are budgeted for the look-ahead positions; a commit may advance a
+    request by several tokens."""
+    kv = KvBlockManager(8, 16)
+    s = Scheduler(kv, max_running=4, max_batch_tokens=16)
+    s.set_lookahead(3)
+    s.add(0, 14, 12)
+    s.add(1, 6, 9)
+    p = s.plan()
+    assert [(i.req_id, i.q_len) for i in p] == [(0, 14), (1, 2)]
+    s.commit([False, False])
+    p = s.plan()                              # request 0 decodes (budget 1 + 3), the rest of request 1's prompt follows
+    assert [(i.req_id, i.q_len, i.ctx_len, i.is_prefill) for i in p] == [(0, 1, 14, False), (1, 4, 2, True)]
+    assert len(kv.pages(p[0].seq)) == 2       # 14 + 1 generated + 1 new + 3 look-ahead = 19 positions -> two pages
+    s.commit([False, False], [4, 1])          # three drafts accepted + the model's own token; request 1 emitted its first token
+    p = s.plan()
+    assert [(i.req_id, i.ctx_len) for i in p] == [(0, 18), (1, 6)]
+    s.commit([False, False], [4, 2])
+    p = s.plan()
+    assert [(i.req_id, i.ctx_len) for i in p] == [(0, 22), (1, 8)]
+    s.commit([True, True], [1, 1])            # both hit a stop token
+    assert s.num_running == 0 and kv.num_free == 8
+
+
 def test_scheduler_preempts_youngest_when_out_of_pages():
     kv = KvBlockManager(5, 16)
     s = Scheduler(kv, max_running=4, max_batch_tokens=64)
