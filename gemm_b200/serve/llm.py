@@ -103,15 +103,21 @@ class LLM:
         q_lens, ctx, ids, drafts = [], [], [], []
         max_pages = max(len(self.blocks.pages(it.seq)) for it in plan)
         bt = torch.zeros(len(plan), max_pages, dtype=torch.int32)
+        draft_of: Dict[int, List[int]] = {}
+        if self.drafter is not None:                        # drafts for the decode items of greedy requests, batched if the drafter can
+            cand = [(it, self._reqs[it.req_id]) for it in plan if not it.is_prefill and self._reqs[it.req_id].sp.temperature <= 0]
+            rooms = [max(0, min(self.drafter.gamma, r.sp.max_new_tokens - len(r.out) - 1)) for _, r in cand]
+            if hasattr(self.drafter, "propose_batch"):
+                ds = self.drafter.propose_batch([it.req_id for it, _ in cand], [r.tokens for _, r in cand], rooms) if cand else []
+            else:
+                ds = [self.drafter.propose(r.tokens) if room > 0 else [] for (_, r), room in zip(cand, rooms)]
+            for (it, _), d, room in zip(cand, ds, rooms):
+                draft_of[it.req_id] = [int(t) for t in d][:room]
         for i, it in enumerate(plan):
             r = self._reqs[it.req_id]
             pages = self.blocks.pages(it.seq)
             bt[i, : len(pages)] = torch.tensor(pages, dtype=torch.int32)
-            draft: List[int] = []
-            if self.drafter is not None and not it.is_prefill and r.sp.temperature <= 0:
-                room = min(self.drafter.gamma, r.sp.max_new_tokens - len(r.out) - 1)
-                if room > 0:
-                    draft = [int(t) for t in self.drafter.propose(r.tokens)][:room]
+            draft = draft_of.get(it.req_id, [])
             drafts.append(draft)
             q_lens.append(it.q_len + len(draft))
             ctx.append(it.ctx_len)
@@ -165,6 +171,8 @@ class LLM:
             advance.append(max(1, len(new)))
             if fin and it.req_id in self._slot_of:
                 self._free_slots.append(self._slot_of.pop(it.req_id))
+            if fin and hasattr(self.drafter, "finish"):
+                self.drafter.finish([it.req_id])
         self.sched.commit(finished, advance if any(a > 1 for a in advance) else None)
         self.steps += 1
         return produced

@@ -166,3 +166,14 @@ def test_drafts_inside_continuous_batching():
     assert list(st.stream(prompts[2], sp)) == ref[2]
     st.set_drafter(None)
     assert st.generate([prompts[3]], sp) == [ref[3]]
+
+    # a draft model (here: the target's own weights, so every draft is right), batched over the step's decode items
+    from gemm_b200.serve.speculative import ModelDrafter
+    wd = synthetic_weights(cfg, "bf16", device="cpu", seed=3)
+    kvd = KvCache.allocate(cfg, 48, 16, "cpu")
+    md = ModelDrafter(Transformer(wd, kvd), kvd, 16, 48, gamma=3)
+    dm = make()
+    dm.set_drafter(md)
+    assert dm.generate(prompts, sp) == ref
+    assert dm.spec_accepted == dm.spec_drafted > 0 and dm.steps < plain.steps
+    assert md.blocks.num_free == 48                         # finished requests return their draft cache
