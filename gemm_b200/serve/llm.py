@@ -136,6 +136,7 @@ class LLM:
         if any(drafts):
             fb.logit_rows = torch.tensor(rows, dtype=torch.int64, device=self.device)
         logits = self.model.forward(fb)
+        greedy_rows = sampling.argmax(logits).cpu().tolist() if any(drafts) else None     # one device read for all drafted items
         produced: Dict[int, int] = {}
         self.produced_all = {}
         finished, advance = [], []
@@ -147,7 +148,7 @@ class LLM:
                 sp = r.sp
                 if drafts[i]:
                     from .speculative import accept_greedy
-                    target = sampling.argmax(logits[row0[i]: row0[i] + len(drafts[i]) + 1]).cpu().tolist()
+                    target = greedy_rows[row0[i]: row0[i] + len(drafts[i]) + 1]
                     n_keep, nxt = accept_greedy(drafts[i], target)
                     new = drafts[i][:n_keep] + [nxt]
                     self.spec_drafted += len(drafts[i])
