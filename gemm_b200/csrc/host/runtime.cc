@@ -93,63 +93,100 @@ struct Scheduler {
   std::deque<Request> waiting;
   std::vector<Request> running;
   std::vector<PlanItem> last_plan;
+  std::vector<long> aborted;   // requests dropped because they can never be served (read and cleared by take_aborted)
   long clock = 0; long n_preempted = 0;
   int lookahead = 0;       // speculative decoding: extra positions a decode item may fill with draft tokens
 
+  // A request whose prompt plus generation (plus look-ahead) exceeds the whole cache can never finish: refuse it up front.
+  bool fits(int prompt_len, int max_new) const {
+    return (long)prompt_len + std::max(max_new, 1) + lookahead <= (long)kv->num_pages * kv->page_size;
+  }
+
+  // Recompute-preemption of running[idx]: its pages go back, it restarts from position 0 at the head of the queue.
+  void preempt(size_t idx, std::vector<long>& preempted_now) {
+    Request v = running[idx];
+    kv->release(v.seq);
+    v.seq = -1; v.computed = 0; v.prompt_len += v.generated; v.max_new -= v.generated; v.generated = 0;
+    preempted_now.push_back(v.id);
+    waiting.push_front(v);
+    running.erase(running.begin() + (long)idx);
+    ++n_preempted;
+  }
+
   // One engine step: every running sequence that finished its prompt decodes one token; what is left of the token
   // budget goes to prompt chunks, oldest request first; new requests are admitted while slots and pages allow.
+  // Requests are visited oldest first, and a victim of preemption is always YOUNGER than the request that needs the page
+  // (or that request itself), so no request that already owns an item of this plan is ever preempted.  A request preempted
+  // in this call is not re-admitted in the same call: its sequence id could be reused inside one plan otherwise.
   int plan(std::vector<PlanItem>& out) {
     out.clear();
     int budget = max_batch_tokens;
-    // decode tokens (need one more position each); preempt the youngest when pages run out
+    std::vector<long> preempted_now;
     std::sort(running.begin(), running.end(), [](const Request& a, const Request& b) { return a.arrival < b.arrival; });
     for (size_t i = 0; i < running.size();) {
-      Request& r = running[i];
-      if (r.computed < r.prompt_len) { ++i; continue; }
-      const int total = r.prompt_len + r.generated + 1 + lookahead;
-      bool ok = kv->reserve(r.seq, total) == 0;
-      while (!ok && running.size() > 1) {
-        // recompute-preemption of the youngest other request
-        size_t victim = running.size() - 1;
-        if (victim == i) { if (i == 0) break; victim = i - 1; }
-        Request v = running[victim];
-        kv->release(v.seq);
-        v.seq = -1; v.computed = 0; v.prompt_len += v.generated; v.max_new -= v.generated; v.generated = 0;
-        waiting.push_front(v);
-        running.erase(running.begin() + (long)victim);
-        if (victim < i) --i;
-        ++n_preempted;
+      if (running[i].computed < running[i].prompt_len) { ++i; continue; }
+      if (budget <= 0) break;
+      const int total = running[i].prompt_len + running[i].generated + 1 + lookahead;
+      bool ok = kv->reserve(running[i].seq, total) == 0;
+      while (!ok && running.size() - 1 > i) {          // the youngest request behind this one gives up its pages
+        preempt(running.size() - 1, preempted_now);
         ok = kv->reserve(running[i].seq, total) == 0;
       }
-      if (!ok) { ++i; continue; }
-      if (budget <= 0) break;
-      Request& rr = running[i];
-      out.push_back({rr.id, rr.seq, 1, rr.prompt_len + rr.generated - 1 + 0, 0, 1});
-      out.back().ctx_len = rr.prompt_len + rr.generated - 1;     // positions already cached before this token
+      if (!ok) {
+        // this request is the youngest.  If older ones hold the pages it waits its turn from the queue; alone it has
+        // outgrown the whole cache and can never continue.
+        if (running.size() > 1) preempt(i, preempted_now);
+        else { aborted.push_back(running[i].id); kv->release(running[i].seq); running.erase(running.begin() + (long)i); }
+        continue;                                        // running[i] is now the next request (or the end)
+      }
+      const Request& rr = running[i];
+      out.push_back({rr.id, rr.seq, 1, rr.prompt_len + rr.generated - 1, 0, 1});   // ctx = positions cached before this token
       budget -= 1 + lookahead; ++i;
     }
     // prompt chunks of running requests
-    for (Request& r : running) {
+    for (size_t i = 0; i < running.size(); ++i) {
+      Request& r = running[i];
       if (budget <= 0) break;
       if (r.computed >= r.prompt_len) continue;
       const int take = std::min(budget, r.prompt_len - r.computed);
-      if (kv->reserve(r.seq, r.computed + take) != 0) continue;
+      if (kv->reserve(r.seq, r.computed + take) != 0) {
+        // no page for the next chunk.  Other requests will free pages as they finish; a lone request never gets more.
+        if (running.size() == 1 && out.empty()) { aborted.push_back(r.id); kv->release(r.seq); running.erase(running.begin() + (long)i); --i; }
+        continue;
+      }
       out.push_back({r.id, r.seq, take, r.computed, 1, (r.computed + take == r.prompt_len) ? 1 : 0});
       budget -= take;
     }
     // admissions
     while (budget > 0 && !waiting.empty() && (int)running.size() < max_running) {
       Request r = waiting.front();
+      if (std::find(preempted_now.begin(), preempted_now.end(), r.id) != preempted_now.end()) break;
+      if (!fits(r.prompt_len, r.max_new)) { aborted.push_back(r.id); waiting.pop_front(); continue; }
       const int take = std::min(budget, r.prompt_len);
       const int seq = kv->seq_new();
-      if (kv->reserve(seq, take) != 0) { kv->release(seq); break; }
+      if (kv->reserve(seq, take) != 0) {
+        kv->release(seq);
+        // nothing is running, so nothing will ever free a page for this chunk: shrink it to what is free, or give up
+        if (running.empty() && out.empty()) {
+          const int room = (int)kv->free_list.size() * kv->page_size;
+          if (room <= 0) { aborted.push_back(r.id); waiting.pop_front(); continue; }
+          const int seq2 = kv->seq_new();
+          const int take2 = std::min(take, room);
+          if (kv->reserve(seq2, take2) != 0) { kv->release(seq2); aborted.push_back(r.id); waiting.pop_front(); continue; }
+          waiting.pop_front();
+          r.seq = seq2; running.push_back(r);
+          out.push_back({r.id, seq2, take2, 0, 1, take2 == r.prompt_len ? 1 : 0});
+          budget -= take2;
+          continue;
+        }
+        break;
+      }
       waiting.pop_front();
       r.seq = seq;
       running.push_back(r);
       out.push_back({r.id, seq, take, 0, 1, take == r.prompt_len ? 1 : 0});
       budget -= take;
     }
-    // decode items were created with ctx = tokens before the new one: fix the convention (see commit())
     last_plan = out;
     return (int)out.size();
   }
@@ -247,8 +284,23 @@ GBH_API void* gbh_sched_create(void* kv, int max_running, int max_batch_tokens) 
   auto* s = new Scheduler(); s->kv = (KvManager*)kv; s->max_running = max_running; s->max_batch_tokens = max_batch_tokens; return s;
 }
 GBH_API void gbh_sched_destroy(void* h) { delete (Scheduler*)h; }
-GBH_API void gbh_sched_add(void* h, long req_id, int prompt_len, int max_new) {
-  auto* s = (Scheduler*)h; Request r; r.id = req_id; r.prompt_len = prompt_len; r.max_new = max_new; r.arrival = s->clock++; s->waiting.push_back(r);
+// Returns 0, or -1 (with the error text set) when the request could never fit the cache and was not queued.
+GBH_API int gbh_sched_add(void* h, long req_id, int prompt_len, int max_new) {
+  auto* s = (Scheduler*)h;
+  if (prompt_len <= 0) return fail("scheduler: empty prompt (request %ld)", req_id);
+  if (!s->fits(prompt_len, max_new))
+    return fail("scheduler: request %ld needs %d positions, the cache holds %d", req_id, prompt_len + std::max(max_new, 1) + s->lookahead,
+                s->kv->num_pages * s->kv->page_size);
+  Request r; r.id = req_id; r.prompt_len = prompt_len; r.max_new = max_new; r.arrival = s->clock++; s->waiting.push_back(r);
+  return 0;
+}
+// Requests the scheduler gave up on since the last call (they can never be served: the cache is too small for them).
+GBH_API int gbh_sched_take_aborted(void* h, long* out, int cap) {
+  auto* s = (Scheduler*)h;
+  int n = 0;
+  for (long id : s->aborted) if (n < cap) out[n++] = id;
+  s->aborted.clear();
+  return n;
 }
 // Fills parallel arrays (capacity cap) and returns the number of plan items.
 GBH_API int gbh_sched_plan(void* h, long* req_id, int* seq, int* q_len, int* ctx_len, int* is_prefill, int* emits, int cap) {

@@ -690,10 +690,12 @@ __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16
 // Decode bookkeeping kept on the device so that a captured step can be replayed without the host:
 // every live sequence advances by one position; its next slot comes from the block table.
 __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restrict__ kv_len, int* __restrict__ slots,
-                                      const int* __restrict__ block_table, const int* __restrict__ live, int max_pages, int page_size, int n) {
+                                      const int* __restrict__ block_table, const int* __restrict__ live, int max_pages, int page_size, int n,
+                                      unsigned long long* __restrict__ step_ctr) {
   pdl_wait();
   pdl_trigger();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b == 0 && step_ctr != nullptr) *step_ctr += 1;       // the step number the sampler of the NEXT step reads
   if (b >= n) return;
   if (live != nullptr && live[b] == 0) return;
   const int p = positions[b] + 1;
@@ -708,9 +710,10 @@ __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restri
 using namespace gb;
 
 GB_API int gb_decode_advance(int* positions, int* kv_len, int* slots, const int* block_table, const int* live, int max_pages,
-                             int page_size, int n, cudaStream_t stream) {
+                             int page_size, int n, void* step_ctr, cudaStream_t stream) {
   if (n <= 0) return 0;
-  launch_k(decode_advance_kernel, (n + 127) / 128, 128, 0, stream, positions, kv_len, slots, block_table, live, max_pages, page_size, n);
+  launch_k(decode_advance_kernel, (n + 127) / 128, 128, 0, stream, positions, kv_len, slots, block_table, live, max_pages, page_size, n,
+           (unsigned long long*)step_ctr);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

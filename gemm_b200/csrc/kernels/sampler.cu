@@ -108,9 +108,12 @@ constexpr int kMaxCand = 1024;
 template <typename T>
 __global__ void __launch_bounds__(1024)
 sample_kernel(const T* __restrict__ logits, int* __restrict__ out_idx, int vocab, long ld, float temperature, int top_k, float top_p,
-              uint64_t seed, uint64_t step) {
+              uint64_t seed, uint64_t step, const unsigned long long* __restrict__ step_ctr) {
   pdl_wait();
   pdl_trigger();
+  // A decode step replayed from a CUDA graph carries the same kernel arguments every time: the part of the step number that
+  // changes lives in device memory (advanced once per step by the decode bookkeeping kernel).
+  if (step_ctr != nullptr) step += *step_ctr;
   const T* row = logits + (size_t)blockIdx.x * ld;
   __shared__ unsigned hist[256];
   __shared__ unsigned s_prefix, s_remaining;
@@ -226,11 +229,13 @@ GB_API int gb_argmax2(const void* logits, int* out_idx, float* out_val, float* p
   return 0;
 }
 
+// `step_ctr` (optional, device): a 64-bit counter added to `step`, so that a captured launch draws fresh numbers at every replay.
 GB_API int gb_sample(const void* logits, int* out_idx, int rows, int vocab, long ld, int dtype, float temperature, int top_k, float top_p,
-                     unsigned long long seed, unsigned long long step, cudaStream_t stream) {
+                     unsigned long long seed, unsigned long long step, const void* step_ctr, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (dtype == 0) launch_k(sample_kernel<float>, rows, 1024, 0, stream, (const float*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step);
-  else launch_k(sample_kernel<__nv_bfloat16>, rows, 1024, 0, stream, (const __nv_bfloat16*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step);
+  const unsigned long long* sc = (const unsigned long long*)step_ctr;
+  if (dtype == 0) launch_k(sample_kernel<float>, rows, 1024, 0, stream, (const float*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step, sc);
+  else launch_k(sample_kernel<__nv_bfloat16>, rows, 1024, 0, stream, (const __nv_bfloat16*)logits, out_idx, vocab, ld, temperature, top_k, top_p, seed, step, sc);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

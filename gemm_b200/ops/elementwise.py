@@ -331,10 +331,13 @@ def softmax_scale_log2(d: int) -> float:
 
 
 def decode_advance(positions: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, page_size: int,
-                   live: Optional[torch.Tensor] = None) -> None:
-    """In place: position += 1, kv_len = position + 1, slot from the block table (per decode sequence)."""
+                   live: Optional[torch.Tensor] = None, step_ctr: Optional[torch.Tensor] = None) -> None:
+    """In place: position += 1, kv_len = position + 1, slot from the block table (per decode sequence).  ``step_ctr`` (int64 [1]):
+    the step counter of the sampler, advanced by one (``ops.sampling.sample`` reads it on the device)."""
     n = positions.numel()
     if not positions.is_cuda:
+        if step_ctr is not None:
+            step_ctr += 1
         sel = torch.ones(n, dtype=torch.bool) if live is None else live.bool()
         positions[sel] += 1
         kv_len[sel] = positions[sel] + 1
@@ -343,4 +346,4 @@ def decode_advance(positions: torch.Tensor, kv_len: torch.Tensor, slots: torch.T
         slots[sel] = pages * page_size + positions[sel] % page_size
         return
     _native.check(_native.cuda().gb_decode_advance(_p(positions), _p(kv_len), _p(slots), _p(block_table), _p(live),
-                                                   _i(block_table.shape[1]), _i(page_size), _i(n), _s()), "gb_decode_advance")
+                                                   _i(block_table.shape[1]), _i(page_size), _i(n), _p(step_ctr), _s()), "gb_decode_advance")

@@ -46,17 +46,19 @@ def argmax(logits: torch.Tensor, idx_offset: int = 0, want_value: bool = False):
 
 
 def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0,
-           step: int = 0) -> torch.Tensor:
-    """Draw one token per row.  ``temperature <= 0`` means greedy.  At most 1024 candidates are kept."""
+           step: int = 0, step_ctr: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Draw one token per row.  ``temperature <= 0`` means greedy.  At most 1024 candidates are kept.  The random numbers are a
+    function of ``(seed, step + step_ctr[0], row)``; ``step_ctr`` (int64 [1], on the logits' device) is read by the kernel, so a
+    launch captured in a CUDA graph draws from a new step at every replay."""
     if temperature <= 0.0:
         return argmax(logits)
     b, v = logits.shape
     if not logits.is_cuda:
-        return sample_ref(logits, temperature, top_k, top_p, seed, step)
+        return sample_ref(logits, temperature, top_k, top_p, seed, step + (int(step_ctr[0]) if step_ctr is not None else 0))
     out = torch.empty(b, dtype=torch.int32, device=logits.device)
     dt = 0 if logits.dtype == torch.float32 else 1
     rc = _native.cuda().gb_sample(_p(logits), _p(out), _i(b), _i(v), _l(logits.stride(0)), _i(dt), _f(temperature), _i(top_k),
-                                  _f(top_p), _u64(seed), _u64(step), _c(torch.cuda.current_stream().cuda_stream))
+                                  _f(top_p), _u64(seed), _u64(step), _p(step_ctr), _c(torch.cuda.current_stream().cuda_stream))
     _native.check(rc, "gb_sample")
     return out
 

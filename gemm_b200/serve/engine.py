@@ -135,8 +135,8 @@ class Engine:
         return torch.stack(last_logits)
 
     # ------------------------------------------------------------------------------------------ decode
-    def _sample(self, logits: torch.Tensor, sp: SamplingParams, step: int) -> torch.Tensor:
-        tok = sampling.sample(logits, sp.temperature, sp.top_k, sp.top_p, sp.seed, step) if sp.temperature > 0 else \
+    def _sample(self, logits: torch.Tensor, sp: SamplingParams, step: int, step_ctr: Optional[torch.Tensor] = None) -> torch.Tensor:
+        tok = sampling.sample(logits, sp.temperature, sp.top_k, sp.top_p, sp.seed, step, step_ctr) if sp.temperature > 0 else \
             sampling.argmax(logits, idx_offset=self.w.vocab_start)
         return self.par.merge_sampled(tok, logits) if hasattr(self.par, "merge_sampled") else tok
 
@@ -166,12 +166,15 @@ class Engine:
         st["rows"] = torch.arange(b, dtype=torch.int64, device=self.device)
         st["tokens"] = torch.zeros(b, dtype=torch.int32, device=self.device)
         st["seq_slots"] = torch.arange(b, dtype=torch.int32, device=self.device)
+        # decode step number on the device: the sampler reads it and the bookkeeping kernel advances it, so graph replays and
+        # eager steps draw the same random numbers
+        st["step"] = torch.ones(1, dtype=torch.int64, device=self.device)       # step 0 sampled the first token after the prefill
         self._splits = splits
         self._graph = None
         self.step_count = 0
         if use_graph and self.device.type == "cuda":
             # warm up on a side stream (lazy initialisations must not happen during capture), restoring state after
-            saved = {k: st[k].clone() for k in ("ids", "positions", "slots", "kv_len")}
+            saved = {k: st[k].clone() for k in ("ids", "positions", "slots", "kv_len", "step")}
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
             from .. import _native
@@ -201,10 +204,10 @@ class Engine:
             tok = self.model.forward_greedy(fb)
         else:
             logits = self.model.forward(fb)
-            tok = self._sample(logits, self._sp, self.step_count)
+            tok = self._sample(logits, self._sp, 0, st["step"])
         st["tokens"].copy_(tok)
         st["ids"].copy_(tok)
-        ew.decode_advance(st["positions"], st["kv_len"], st["slots"], st["block_table"], self.page_size)
+        ew.decode_advance(st["positions"], st["kv_len"], st["slots"], st["block_table"], self.page_size, step_ctr=st["step"])
 
     @torch.no_grad()
     def decode_step(self) -> torch.Tensor:

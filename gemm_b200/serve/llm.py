@@ -31,6 +31,7 @@ class _Req:
     sp: SamplingParams
     out: List[int] = field(default_factory=list)
     done: bool = False
+    error: Optional[str] = None      # set when the scheduler had to drop the request (the cache can never hold it)
 
 
 class LLM:
@@ -78,8 +79,8 @@ class LLM:
         sp = sp or SamplingParams()
         rid = self._next_id
         self._next_id += 1
+        self.sched.add(rid, len(prompt_ids), sp.max_new_tokens)      # raises ValueError for a request the cache can never hold
         self._reqs[rid] = _Req(list(prompt_ids), len(prompt_ids), sp)
-        self.sched.add(rid, len(prompt_ids), sp.max_new_tokens)
         return rid
 
     def set_drafter(self, drafter) -> None:
@@ -98,8 +99,19 @@ class LLM:
     def step(self) -> Dict[int, int]:
         """One engine step.  Returns ``{request id: new token}`` for the requests that produced a token."""
         plan = self.sched.plan()
+        for rid in self.sched.take_aborted():               # dropped by the scheduler: finish them with an error instead of spinning
+            r = self._reqs.get(rid)
+            if r is not None:
+                r.done, r.error = True, "request dropped: the KV cache cannot hold it"
+            if rid in self._slot_of:
+                self._free_slots.append(self._slot_of.pop(rid))
         if not plan:
+            if self.has_work():
+                self._idle_steps = getattr(self, "_idle_steps", 0) + 1
+                if self._idle_steps > 2:
+                    raise RuntimeError("scheduler made no progress: requests are queued but no step can be planned")
             return {}
+        self._idle_steps = 0
         q_lens, ctx, ids, drafts = [], [], [], []
         max_pages = max(len(self.blocks.pages(it.seq)) for it in plan)
         bt = torch.zeros(len(plan), max_pages, dtype=torch.int32)
@@ -122,8 +134,11 @@ class LLM:
             q_lens.append(it.q_len + len(draft))
             ctx.append(it.ctx_len)
             ids.extend(r.tokens[it.ctx_len: it.ctx_len + it.q_len] + draft)
-            if it.req_id not in self._slot_of:              # first chunk of this request: take a state slot and clear it
+            if it.req_id not in self._slot_of:              # first chunk of this request: take a state slot
                 self._slot_of[it.req_id] = self._free_slots.pop()
+            if it.is_prefill and it.ctx_len == 0:
+                # a sequence starts (or restarts after a recompute-preemption) from an empty recurrent state: unlike K/V, which the
+                # re-prefill overwrites, the conv / Delta-Net state of the first pass would otherwise leak into the second
                 self.kv.reset_slots([self._slot_of[it.req_id]])
         fb = ForwardBatch.build(q_lens, ctx, ids, bt, self.page_size, self.model.hq_local, self.model.hkv_local, self.device,
                                 seq_slots=[self._slot_of[it.req_id] for it in plan])
@@ -187,7 +202,11 @@ class LLM:
             rids.append(self.add_request(ids, sp))
         while self.has_work():
             self.step()
-        return [self._reqs.pop(r).out for r in rids]
+        reqs = [self._reqs.pop(r) for r in rids]
+        bad = [q.error for q in reqs if q.error]
+        if bad:
+            raise RuntimeError(bad[0])
+        return [q.out for q in reqs]
 
     def generate_speculative(self, prompts: Sequence, max_new_tokens: int = 64, gamma: int = 4, drafter=None,
                              stop_token_ids: Sequence[int] = ()):
@@ -210,7 +229,9 @@ class LLM:
             self.step()
             for tok in self.produced_all.get(rid, ()):
                 yield tok
-        self._reqs.pop(rid, None)
+        r = self._reqs.pop(rid, None)
+        if r is not None and r.error:
+            raise RuntimeError(r.error)
 
     def decode(self, ids: Sequence[int]) -> str:
         if self.tokenizer is None:

@@ -86,7 +86,15 @@ class Scheduler:
         self._cap = max_running + 64
 
     def add(self, req_id: int, prompt_len: int, max_new_tokens: int) -> None:
-        _lib().gbh_sched_add(ctypes.c_void_p(self._h), ctypes.c_long(req_id), prompt_len, max_new_tokens)
+        """Queue a request.  Raises ``ValueError`` when prompt + generation (+ look-ahead) can never fit the cache."""
+        if _lib().gbh_sched_add(ctypes.c_void_p(self._h), ctypes.c_long(req_id), prompt_len, max_new_tokens) != 0:
+            raise ValueError(_lib().gbh_last_error().decode())
+
+    def take_aborted(self) -> List[int]:
+        """Requests the scheduler dropped since the last call because the cache can never hold them."""
+        buf = (ctypes.c_long * 256)()
+        n = _lib().gbh_sched_take_aborted(ctypes.c_void_p(self._h), buf, 256)
+        return list(buf[:n])
 
     def plan(self) -> List[PlanItem]:
         c = self._cap

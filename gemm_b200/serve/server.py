@@ -58,13 +58,33 @@ class EngineThread(threading.Thread):
             try:
                 while True:
                     ids, sp, q = self.inbox.get(block=not self.llm.has_work(), timeout=0.05)
-                    rid = self.llm.add_request(ids, sp)
+                    try:
+                        rid = self.llm.add_request(ids, sp)
+                    except ValueError:                   # the cache can never hold this request: end its stream at once
+                        q.put(None)
+                        continue
                     self.streams[rid] = q
             except queue.Empty:
                 pass
             if not self.llm.has_work():
                 continue
-            self.llm.step()
+            try:
+                self.llm.step()
+            except Exception:
+                # a failed step must not leave clients blocked on their queues: end every open stream, drop the requests
+                import traceback
+                traceback.print_exc()
+                for q in self.streams.values():
+                    q.put(None)
+                self.streams.clear()
+                self.stop_flag = True
+                break
+            for rid, q in list(self.streams.items()):    # requests the scheduler dropped produce no token: close their streams
+                r = self.llm._reqs.get(rid)
+                if r is not None and r.error:
+                    q.put(None)
+                    del self.streams[rid]
+                    self.llm._reqs.pop(rid, None)
             for rid, toks in self.llm.produced_all.items():
                 self.tokens_total += len(toks)
                 q = self.streams.get(rid)

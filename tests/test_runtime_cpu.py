@@ -119,3 +119,79 @@ def test_profiler_tables():
     text = profiler.summary()
     profiler.enable(False)
     assert "per op" in text and "qkv" in text and "per component" in text and "attention" in text
+
+
+def _drive(s, kv, n_req, max_steps=400):
+    """Run a scheduler to completion, checking after every plan that its items name live, distinct sequences."""
+    steps = 0
+    while (s.num_running or s.num_waiting) and steps < max_steps:
+        p = s.plan()
+        s.take_aborted()
+        seqs = [i.seq for i in p]
+        assert len(set(seqs)) == len(seqs), f"a sequence appears twice in one plan: {p}"
+        for i in p:
+            pages = kv.pages(i.seq)                          # raises KeyError for a released sequence
+            assert len(pages) * kv.page_size >= i.ctx_len + i.q_len, (i, pages)
+        if not p:
+            break
+        s.commit([False] * len(p))
+        steps += 1
+    return steps
+
+
+def test_scheduler_never_preempts_a_planned_request():
+    """4 pages of 4 tokens, prompts of 6 and 8 tokens: the younger request runs out of pages while the older one already
+    has a decode item in the plan; the victim must be the younger one itself."""
+    kv = KvBlockManager(4, 4)
+    s = Scheduler(kv, max_running=4, max_batch_tokens=64)
+    s.add(0, 6, 6)
+    s.add(1, 8, 4)
+    steps = _drive(s, kv, 2)
+    assert steps < 400 and s.num_running == 0 and s.num_waiting == 0
+    assert kv.num_free == 4 and s.num_preempted >= 1
+
+
+def test_scheduler_rejects_and_aborts_what_can_never_fit():
+    kv = KvBlockManager(4, 4)
+    s = Scheduler(kv, max_running=4, max_batch_tokens=64)
+    try:
+        s.add(0, 20, 4)                                      # prompt alone exceeds the 16-position cache
+        assert False, "must be refused"
+    except ValueError:
+        pass
+    assert s.num_waiting == 0
+    # with look-ahead switched on later, a queued request may stop fitting: the plan drops it and reports it
+    s.add(1, 10, 5)
+    s.set_lookahead(4)
+    p = s.plan()
+    assert p == [] and s.take_aborted() == [1] and s.num_waiting == 0 and s.num_running == 0 and kv.num_free == 4
+
+
+def test_llm_reports_requests_that_cannot_fit():
+    cfg = get_config("tiny-dense")
+    w = synthetic_weights(cfg, "bf16", device="cpu", seed=2)
+    llm = LLM(w, max_running=2, max_batch_tokens=32, num_pages=4, page_size=4)
+    try:
+        llm.generate([list(range(1, 30))], SamplingParams(max_new_tokens=4))
+        assert False
+    except ValueError:
+        pass
+    assert not llm.has_work()
+    out = llm.generate([[1, 2, 3]], SamplingParams(max_new_tokens=3))
+    assert len(out[0]) == 3 and llm.blocks.num_free == 4
+
+
+def test_hybrid_preemption_restarts_from_an_empty_state():
+    """A preempted request of a Delta-Net model re-prefills from position 0: its recurrent slot must be cleared, or the state of
+    the first pass leaks into the second.  Tokens with a cache tight enough to preempt equal those of a roomy cache."""
+    torch.manual_seed(0)
+    cfg = get_config("tiny-qwen35")
+    w = synthetic_weights(cfg, "bf16", device="cpu", seed=3)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (9, 11)]
+    sp = SamplingParams(max_new_tokens=8)
+    roomy = LLM(w, max_running=2, max_batch_tokens=32, num_pages=32, page_size=4)
+    ref = roomy.generate(prompts, sp)
+    tight = LLM(w, max_running=2, max_batch_tokens=32, num_pages=8, page_size=4)
+    out = tight.generate(prompts, sp)
+    assert tight.sched.num_preempted >= 1, "the cache was meant to be too small for both requests"
+    assert out == ref
