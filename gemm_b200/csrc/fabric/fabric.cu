@@ -12,6 +12,14 @@
 // Protocol: every collective call has an epoch (a device-resident counter, so a captured CUDA graph can be
 // replayed).  Data is stored into the peers' heaps, then a flag word per (source rank[, chunk]) is set to the
 // epoch with release semantics at system scope; consumers poll with acquire loads under a time budget.
+//
+// Reuse of receive slots.  A flag proves that a peer has PUSHED call e, not that it has finished READING what it received
+// in call e.  The collectives whose result leaves the slots inside the same kernel (one-shot all-reduce, arg-max all-reduce)
+// therefore alternate between two slot sets by epoch parity: a rank can only start call e + 2 (the next writer of the
+// parity-e set) after its own call e + 1 completed, which needed every peer's flag of call e + 1, which a peer raises only
+// after its kernel of call e (and all its reads) ended.  The push exchange hands its receive buffer to later kernels of the
+// caller, so its parity cannot alternate; its optional entry handshake (`ack`) makes every rank wait until all peers have
+// ENTERED the same call (stream order puts their readers of the previous call before that) before the first store.
 #include "fabric.cuh"
 #include "../kernels/host_common.h"
 
@@ -48,11 +56,12 @@ __global__ void fabric_barrier_kernel(PeerTable pt, size_t flags_off, uint32_t* 
 template <typename T>
 __global__ void __launch_bounds__(256)
 allreduce_oneshot_kernel(PeerTable pt, size_t data_off, size_t flags_off, const T* __restrict__ in, T* __restrict__ out,
-                         long n, long max_elems, uint32_t* epoch_ctr, unsigned* done_ctr, KernelStatus* st) {
+                         long n, long max_elems, uint32_t* epoch_ctr, unsigned* done_ctr, KernelStatus* st, size_t parity_stride) {
   pdl_wait();
   pdl_trigger();
   constexpr int EPV = 16 / sizeof(T);
   const uint32_t epoch = *epoch_ctr + 1;
+  data_off += (size_t)(epoch & 1u) * parity_stride;          // two slot sets, alternating by call
   const int chunks = gridDim.x, c = blockIdx.x;
   const long nvec = (n + EPV - 1) / EPV;
   const long per = (nvec + chunks - 1) / chunks;
@@ -174,11 +183,21 @@ allreduce_twoshot_kernel(PeerTable pt, size_t in_off, size_t out_off, size_t fla
 // out_off + rank * bytes_per_dst.  dst_stride_in = 0 gives an all-gather, = bytes_per_dst an all-to-all.
 __global__ void __launch_bounds__(256)
 push_exchange_kernel(PeerTable pt, size_t out_off, size_t flags_off, const char* __restrict__ in, size_t bytes_per_dst,
-                     size_t dst_stride_in, uint32_t* epoch_ctr, unsigned* done_ctr, KernelStatus* st) {
+                     size_t dst_stride_in, uint32_t* epoch_ctr, unsigned* done_ctr, KernelStatus* st, size_t ack_off) {
   pdl_wait();
   pdl_trigger();
   const uint32_t epoch = *epoch_ctr + 1;
   const int chunks = gridDim.x, c = blockIdx.x;
+  if (ack_off != 0) {
+    // entry handshake: nobody stores into a peer before that peer has entered this call (its readers of the previous call's
+    // buffer precede this kernel in its stream).  CTA 0 announces, every CTA waits on the local copies.
+    if ((int)threadIdx.x < pt.world) {
+      const int p = threadIdx.x;
+      if (c == 0) st_release_sys(reinterpret_cast<uint32_t*>((char*)pt.base[p] + ack_off) + pt.rank, epoch);
+      wait_flag_ge(reinterpret_cast<uint32_t*>((char*)pt.base[pt.rank] + ack_off) + p, epoch, st, 731, p);
+    }
+    __syncthreads();
+  }
   const size_t nvec = bytes_per_dst / 16, per = (nvec + chunks - 1) / chunks;
   const size_t v0 = c * per, v1 = min(nvec, v0 + per);
   for (int p = 0; p < pt.world; ++p) {
@@ -204,10 +223,12 @@ push_exchange_kernel(PeerTable pt, size_t out_off, size_t flags_off, const char*
 // slots: [world][rows] of {float, int} at data_off.  One CTA.
 __global__ void __launch_bounds__(256)
 argmax_allreduce_kernel(PeerTable pt, size_t data_off, size_t flags_off, const float* __restrict__ val, const int* __restrict__ idx,
-                        int* __restrict__ out_idx, float* __restrict__ out_val, int rows, int max_rows, uint32_t* epoch_ctr, KernelStatus* st) {
+                        int* __restrict__ out_idx, float* __restrict__ out_val, int rows, int max_rows, uint32_t* epoch_ctr, KernelStatus* st,
+                        size_t parity_stride) {
   pdl_wait();
   pdl_trigger();
   const uint32_t epoch = *epoch_ctr + 1;
+  data_off += (size_t)(epoch & 1u) * parity_stride;
   for (int p = 0; p < pt.world; ++p) {
     int2* dst = reinterpret_cast<int2*>((char*)pt.base[p] + data_off) + (size_t)pt.rank * max_rows;
     for (int r = threadIdx.x; r < rows; r += blockDim.x) dst[r] = make_int2(__float_as_int(val[r]), idx[r]);
@@ -401,14 +422,17 @@ GB_API int gb_fabric_barrier(void* const* bases, int world, int rank, size_t fla
 }
 
 // dtype: 0 = f32, 1 = bf16.  n elements (multiple of 16 bytes), slots hold max_elems each, flags [world][chunks].
+// The slot area holds two sets of [world][max_elems] elements, `parity_stride` bytes apart (0 = a single set: the caller then has
+// to keep consecutive calls apart itself).
 GB_API int gb_allreduce_oneshot(void* const* bases, int world, int rank, size_t data_off, size_t flags_off, const void* in, void* out,
-                                long n, long max_elems, int dtype, int chunks, void* epoch_ctr, void* done_ctr, void* status, cudaStream_t stream) {
+                                long n, long max_elems, int dtype, int chunks, void* epoch_ctr, void* done_ctr, void* status,
+                                size_t parity_stride, cudaStream_t stream) {
   if (world > kMaxRanks) return fail("fabric: world > 8%s");
   const int esz = dtype == 0 ? 4 : 2;
   if ((n * esz) % 16 || n > max_elems || (max_elems * esz) % 16) return fail("allreduce_oneshot: size must be a multiple of 16 bytes and fit the slot%s");
   PeerTable pt = make_table(bases, world, rank);
-  if (dtype == 0) launch_k(allreduce_oneshot_kernel<float>, chunks, 256, 0, stream, pt, data_off, flags_off, (const float*)in, (float*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
-  else launch_k(allreduce_oneshot_kernel<__nv_bfloat16>, chunks, 256, 0, stream, pt, data_off, flags_off, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
+  if (dtype == 0) launch_k(allreduce_oneshot_kernel<float>, chunks, 256, 0, stream, pt, data_off, flags_off, (const float*)in, (float*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status, parity_stride);
+  else launch_k(allreduce_oneshot_kernel<__nv_bfloat16>, chunks, 256, 0, stream, pt, data_off, flags_off, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, n, max_elems, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status, parity_stride);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -429,21 +453,25 @@ GB_API int gb_allreduce_twoshot(void* const* bases, int world, int rank, size_t 
 }
 
 GB_API int gb_push_exchange(void* const* bases, int world, int rank, size_t out_off, size_t flags_off, const void* in, size_t bytes_per_dst,
-                            size_t dst_stride_in, int chunks, void* epoch_ctr, void* done_ctr, void* status, cudaStream_t stream) {
+                            size_t dst_stride_in, int chunks, void* epoch_ctr, void* done_ctr, void* status, size_t ack_off,
+                            cudaStream_t stream) {
+  // ack_off: offset of uint32 [world] handshake flags in every heap, or 0 when the caller's own ordering keeps a rank from
+  // overwriting a receive buffer that a peer still reads
   if (world > kMaxRanks) return fail("fabric: world > 8%s");
   if (bytes_per_dst % 16 || dst_stride_in % 16) return fail("push_exchange: sizes must be multiples of 16 bytes%s");
   launch_k(push_exchange_kernel, chunks, 256, 0, stream, make_table(bases, world, rank), out_off, flags_off, (const char*)in, bytes_per_dst,
-                                                   dst_stride_in, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status);
+                                                   dst_stride_in, (uint32_t*)epoch_ctr, (unsigned*)done_ctr, (KernelStatus*)status, ack_off);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 GB_API int gb_argmax_allreduce(void* const* bases, int world, int rank, size_t data_off, size_t flags_off, const float* val, const int* idx,
-                               int* out_idx, float* out_val, int rows, int max_rows, void* epoch_ctr, void* status, cudaStream_t stream) {
+                               int* out_idx, float* out_val, int rows, int max_rows, void* epoch_ctr, void* status, size_t parity_stride,
+                               cudaStream_t stream) {
   if (world > kMaxRanks) return fail("fabric: world > 8%s");
   if (rows > max_rows) return fail("argmax_allreduce: too many rows%s");
   launch_k(argmax_allreduce_kernel, 1, 256, 0, stream, make_table(bases, world, rank), data_off, flags_off, val, idx, out_idx, out_val, rows, max_rows,
-                                                 (uint32_t*)epoch_ctr, (KernelStatus*)status);
+                                                 (uint32_t*)epoch_ctr, (KernelStatus*)status, parity_stride);
   GB_CUDA_OK(cudaGetLastError());
   return 0;
 }

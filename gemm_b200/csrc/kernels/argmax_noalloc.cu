@@ -30,7 +30,7 @@ stage_one(const T* __restrict__ logits, Partial* __restrict__ part, int vocab, l
   const int i0 = c * per, i1 = min(vocab, i0 + per);
   const T* row = logits + (size_t)r * ld;
   float bv = -FLT_MAX; int bi = 0x7fffffff;
-  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) { float v = load_logit(row, i); if (!(v == v)) v = -FLT_MAX; take_better(bv, bi, v, i); }
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) { float v = load_logit(row, i); v = (v == v) ? fmaxf(v, -FLT_MAX) : -FLT_MAX; /* NaN and -inf count as the lowest finite value */ take_better(bv, bi, v, i); }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) take_better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
   __shared__ float sv[8]; __shared__ int si[8];

@@ -82,7 +82,6 @@ struct GemmArgs {
   // tile of the main loop is one contiguous block of memory (one DRAM burst sequence instead of 128 strided lines)
   int dual_raw;  // DUAL without the activation: the second accumulator is the row block up_row_offset further down the same matrix
   int w_tiled;
-  int debug;     // experiment knob (GB_GEMM_DEBUG): bit 0 = issue no MMA (pure load stream), bit 1 = load no weight tiles
 };
 
 // k-steps whose MXFP8 scale atoms are fetched by one bulk copy (2 for the widest tile, whose stages are short of room)
@@ -222,7 +221,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       TileCursor<TN> cur; Tile t;
       int s = 0; uint32_t ph = 0;
       bool ok = true;
-      int dbg_i = 0;
       for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
         const int kb0 = t.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         // Per tile: the row coordinate of the (tiled) weight blocks and the start of each scale-atom stream.  The atoms of one
@@ -256,13 +254,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag, args.status, 100, s)) { ok = false; break; }
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-          const bool load_w = !(args.debug & 2);
           // length of the scale group that starts at this k-step (0 = none starts here)
           const int glen = (MODE != 1) ? 0 : (SFG == 1) ? 1 : ((kb - kb0) % SFG == 0) ? min(SFG, kb1 - kb) : 0;
-          mbar_expect_tx(&full_bar[s], (load_w ? NA * A_BYTES : 0) + B_BYTES + (NA + SFB_ATOMS) * 512 * glen);
+          mbar_expect_tx(&full_bar[s], NA * A_BYTES + B_BYTES + (NA + SFB_ATOMS) * 512 * glen);
           const int kx = kb * KB_ELEMS;
-          if (!load_w) {
-          } else if (args.w_tiled) {
+          if (args.w_tiled) {
             tma_load_2d(st, &tmW, &full_bar[s], 0, wy0 + (kb << 7));
             if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], 0, wy1 + (kb << 7));
           } else {
@@ -279,7 +275,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < SFB_ATOMS; ++i) bulk_load(sf + (NA + i) * SFG * 512, sfbp[i] + koff, gbytes, &full_bar[s]);
           }
-          if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[dbg_i++] = clock64();
           if (++s == S) { s = 0; ph ^= 1; }
         }
       }
@@ -291,7 +286,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       int s = 0; uint32_t ph = 0;
       int acc = 0; uint32_t acc_ph = 0;
       bool ok = true;
-      int dbg_i = 0;
       for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
         if (!mbar_wait(&acce_bar[acc], acc_ph ^ 1, abort_flag, args.status, 200, acc)) { ok = false; break; }
         tc_fence_after();
@@ -299,11 +293,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         const int kb0 = t.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[s], ph, abort_flag, args.status, 201, s)) { ok = false; break; }
-          if ((args.debug & 4) && blockIdx.x == 0 && dbg_i < 2048) ((long long*)args.sk_ws)[2048 + dbg_i++] = clock64();
           tc_fence_after();
           const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
           uint32_t sfb_t = 0;
-          if (args.debug & 1) { tc_commit(&empty_bar[s]); if (++s == S) { s = 0; ph ^= 1; } continue; }
           uint32_t sfa_t = 0;
           if (MODE == 1) {
             const int kbi = kb - kb0, gj = kbi % SFG;
@@ -355,12 +347,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     TileCursor<TN> cur; Tile t;
     int acc = 0; uint32_t acc_ph = 0;
     bool ok = true;
-    int dbg_t = 0;
     const bool simple_store = !QUANT_OUT && args.amax_val == nullptr && args.row_map == nullptr && args.peer_bcast == 0 &&
                               args.row_scale == nullptr && (args.splits <= 1 || args.partial_stride > 0);
     for (int ti = blockIdx.x; ok && cur.get(args, s_start, s_count, ti, t); ti += gridDim.x) {
       if (!mbar_wait(&accf_bar[acc], acc_ph, abort_flag, args.status, 300, acc)) { ok = false; break; }
-      if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4096 + dbg_t] = clock64();
       tc_fence_after();
       const uint32_t tacc = tmem_base + acc * ACC_COLS + ((uint32_t)(q * 32) << 16);
       const int n = t.n0 + row;
@@ -533,7 +523,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 if (xr + 1 < t.valid) ((unsigned short*)o16)[(size_t)(xr + 1) * args.ldo] = (unsigned short)(pk[i] >> 16);
               }
             }
-            if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4608 + dbg_t++] = clock64();
             acc_ph ^= 1;
             continue;
           }
@@ -609,7 +598,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acce_bar[acc]);
-      if ((args.debug & 4) && blockIdx.x == 0 && threadIdx.x == 64 && dbg_t < 512) ((long long*)args.sk_ws)[4608 + dbg_t++] = clock64();
       if (NACC == 2) { if (++acc == 2) { acc = 0; acc_ph ^= 1; } } else { acc_ph ^= 1; }
     }
   }
@@ -643,12 +631,6 @@ static int launch_gemm(const CUtensorMap& tmW, const CUtensorMap& tmX, GemmArgs 
   const int tail = 1024 + 2 * kMaxGroups * 4 + 256;
   int stages = (int)((220 * 1024 - tail - 1024) / STAGE_BYTES);
   if (stages > 8) stages = 8;
-  {
-    // GB_GEMM_STAGES caps the pipeline depth (an experiment knob: how latency-bound is a shape?)
-    static int cap = -1;
-    if (cap < 0) { const char* e = getenv("GB_GEMM_STAGES"); cap = (e != nullptr && atoi(e) >= 2) ? atoi(e) : 0; }
-    if (cap > 0 && stages > cap) stages = cap;
-  }
   if (stages < 2) return fail("gemm: tile does not fit shared memory%s");
   a.stages = stages;
   const int smem = stages * STAGE_BYTES + tail + 1024;
@@ -761,13 +743,6 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   a.w_tiled = w_tiled ? 1 : 0;
   a.dual_raw = (flags & GEMM_DUAL_RAW) ? 1 : 0;
   if (a.dual_raw && (!dual || qo)) return fail("gemm: GEMM_DUAL_RAW needs GEMM_DUAL without GEMM_QUANT_OUT%s");
-  {
-    static int dbg = -1;
-    if (dbg < 0) { const char* e = getenv("GB_GEMM_DEBUG"); dbg = e != nullptr ? atoi(e) : 0; }
-    a.debug = dbg;
-    if ((dbg & 4) && ex != nullptr && ex->sk_ws != nullptr && ex->sk_ws_bytes >= 5120 * 8) a.sk_ws = ex->sk_ws;
-    else a.debug &= ~4;
-  }
   a.out_sf = (uint8_t*)out_sf; a.bias = bias; a.row_map = row_map; a.row_scale = row_scale; a.status = (KernelStatus*)status;
   if (ex != nullptr) {
     a.w_group_mod = ex->w_group_mod; a.wait_flags = ex->wait_flags; a.wait_n = ex->wait_n; a.epoch_ptr = ex->epoch_ptr;

@@ -29,7 +29,7 @@ argmax_kernel(const T* __restrict__ logits, int* __restrict__ out_idx, float* __
   float bv = -FLT_MAX; int bi = 0x7fffffff;
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
     float v = ld_logit(row, i);
-    if (!(v == v)) v = -FLT_MAX;
+    v = (v == v) ? fmaxf(v, -FLT_MAX) : -FLT_MAX; /* NaN and -inf count as the lowest finite value */
     better(bv, bi, v, i);
   }
 #pragma unroll
@@ -78,7 +78,7 @@ argmax_chunk_kernel(const T* __restrict__ logits, float* __restrict__ pval, int*
   const int i0 = c * per, i1 = min(vocab, i0 + per);
   const T* row = logits + (size_t)r * ld;
   float bv = -FLT_MAX; int bi = 0x7fffffff;
-  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) { float v = ld_logit(row, i); if (!(v == v)) v = -FLT_MAX; better(bv, bi, v, i); }
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) { float v = ld_logit(row, i); v = (v == v) ? fmaxf(v, -FLT_MAX) : -FLT_MAX; /* NaN and -inf count as the lowest finite value */ better(bv, bi, v, i); }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
   __shared__ float sv[8]; __shared__ int si[8];
@@ -122,7 +122,7 @@ sample_kernel(const T* __restrict__ logits, int* __restrict__ out_idx, int vocab
   __shared__ int s_count;
   const int kk = (top_k <= 0 || top_k > kMaxCand) ? min(kMaxCand, vocab) : min(top_k, vocab);
   auto key_of = [](float v) -> unsigned {
-    if (!(v == v)) v = -FLT_MAX;
+    v = (v == v) ? fmaxf(v, -FLT_MAX) : -FLT_MAX; /* NaN and -inf count as the lowest finite value */
     unsigned u = __float_as_uint(v);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);        // larger float -> larger key
   };

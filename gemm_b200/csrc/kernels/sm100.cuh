@@ -61,9 +61,11 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 
 // Default budgets.  An mbarrier inside one CTA should flip within microseconds; one second
-// means something is broken.  Waits on a peer GPU tolerate launch skew between ranks.
-constexpr uint64_t kMbarBudgetNs = 2ull * 1000 * 1000 * 1000;
-constexpr uint64_t kPeerBudgetNs = 2ull * 1000 * 1000 * 1000;
+// means something is broken.  Waits on a peer GPU tolerate launch skew between ranks.  The two budgets differ on purpose,
+// and neither is a round number a host-side stall is likely to hit: a stall of unknown origin can then be told from an expired
+// wait by its length alone (an expired wait also leaves its site in the status word).
+constexpr uint64_t kMbarBudgetNs = 1100ull * 1000 * 1000;
+constexpr uint64_t kPeerBudgetNs = 3300ull * 1000 * 1000;
 
 // ---------------------------------------------------------------------------------------------
 // Small helpers

@@ -31,17 +31,6 @@ class GemmExtras(ctypes.Structure):
                 ("partial_stride", ctypes.c_long)]
 
 
-_DEBUG = int(os.environ.get("GB_GEMM_DEBUG", "0"))
-_dbg_buf = None
-
-
-def debug_timeline():
-    """With ``GB_GEMM_DEBUG=4``: clock64 stamps of CTA 0 of the last GEMM launch: (loads issued per k-step, operands seen per
-    k-step, epilogue start per tile, epilogue end per tile)."""
-    b = _dbg_buf.cpu()
-    return b[:2048], b[2048:4096], b[4096:4608], b[4608:5120]
-
-
 _SK_WS_BYTES = 64 << 20
 _SK_CTR = 1 << 16
 _sk_state = {}
@@ -112,13 +101,6 @@ def _launch(w, x, out, n_out, k, m_tok, ldw, ldx, ldo, flags, tn, num_groups=0, 
     # extents of the caller's buffers: the kernel checks its scale-atom loads and its stores against them
     nb = lambda t: t.numel() * t.element_size() if t is not None else 0
     extras.sfa_bytes, extras.sfb_bytes, extras.out_bytes, extras.out_sf_bytes = nb(sfa), nb(sfb), nb(out), nb(out_sf)
-    if _DEBUG & 4:                      # pipeline timeline of CTA 0 (clock64 stamps), read back with debug_timeline()
-        global _dbg_buf
-        if _dbg_buf is None:
-            _dbg_buf = torch.zeros(5120, dtype=torch.int64, device=w.device)
-        if not extras.sk_ws:
-            _dbg_buf.zero_()
-            extras.sk_ws, extras.sk_ws_bytes = _dbg_buf.data_ptr(), 5120 * 8
     rc = lib.gb_gemm(_p(w), _p(x), _p(out), _i(n_out), _i(k), _i(m_tok), _i(ldw), _i(ldx), _i(ldo), _i(flags), _i(tn),
                      _i(num_groups), _i(w_rows_per_group), _i(up_row_offset), _p(seg_start), _p(seg_count),
                      _i(x_rows if x_rows is not None else m_tok), _p(sfa), _p(sfb), _p(out_sf), _p(bias), _p(row_map),

@@ -97,7 +97,7 @@ class ExpertParallel:
         # all-gather route: per capacity a gather buffer, the fp32 partial slots and one flag per source rank
         self._gather = {}
         for cap in g_caps:
-            g = {"cap": cap, "ag": f.make_exchange(cap * hid * 2, chunks=max(1, min(8, cap // 8)))}
+            g = {"cap": cap, "ag": f.make_exchange(cap * hid * 2, chunks=max(1, min(8, cap // 8)), handshake=False)}   # the combine exchange of every layer orders the ranks between two gathers
             g["stage"] = torch.zeros(cap, hid, dtype=torch.bfloat16, device=self.device)
             g["slots_off"] = f.alloc(w * cap * hid * 4)
             g["flags_off"] = f.alloc(32)

@@ -114,11 +114,13 @@ class Fabric:
     def make_allreduce_large(self, n_elems: int, dtype: torch.dtype, chunks: int = 296) -> "TwoShotAllReduce":
         return TwoShotAllReduce(self, n_elems, dtype, chunks)
 
-    def make_exchange(self, bytes_per_dst: int, chunks: int = 0) -> "PushExchange":
-        """``chunks`` = CTAs of the push kernel (0: by size, one per 32 KB per destination, between 8 and 296)."""
+    def make_exchange(self, bytes_per_dst: int, chunks: int = 0, handshake: bool = True) -> "PushExchange":
+        """``chunks`` = CTAs of the push kernel (0: by size, one per 32 KB per destination, between 8 and 296).  ``handshake``: every
+        call first waits until all peers have entered it, so back-to-back calls cannot overwrite a receive buffer that a peer
+        still reads; switch it off only where another exchange between two calls already orders the ranks."""
         if chunks <= 0:
             chunks = max(8, min(296, bytes_per_dst // (32 << 10)))
-        return PushExchange(self, bytes_per_dst, chunks)
+        return PushExchange(self, bytes_per_dst, chunks, handshake)
 
     def make_argmax(self, max_rows: int) -> "ArgmaxAllReduce":
         return ArgmaxAllReduce(self, max_rows)
@@ -138,7 +140,9 @@ class OneShotAllReduce:
         self.fab, self.dtype, self.chunks = fab, dtype, chunks
         esz = 4 if dtype == torch.float32 else 2
         self.max_elems = (max_elems * esz + 15) // 16 * 16 // esz
-        self.data_off = fab.alloc(fab.world * self.max_elems * esz)
+        # two slot sets used alternately (by call parity): a rank that is one call ahead never overwrites what a peer still sums
+        self.parity_stride = (fab.world * self.max_elems * esz + 1023) // 1024 * 1024
+        self.data_off = fab.alloc(2 * self.parity_stride)
         self.flags_off = fab.alloc(fab.world * chunks * 4)
         self.epoch, self.done = fab.ctl_word(), fab.ctl_word()
 
@@ -148,7 +152,8 @@ class OneShotAllReduce:
         f = self.fab
         rc = f.lib.gb_allreduce_oneshot(f.bases_arr, _i(f.world), _i(f.rank), _sz(self.data_off), _sz(self.flags_off), _c(x.data_ptr()),
                                         _c(out.data_ptr()), _l(x.numel()), _l(self.max_elems), _i(0 if self.dtype == torch.float32 else 1),
-                                        _i(self.chunks), _c(self.epoch), _c(self.done), _c(_native.status_ptr()), f._stream())
+                                        _i(self.chunks), _c(self.epoch), _c(self.done), _c(_native.status_ptr()), _sz(self.parity_stride),
+                                        f._stream())
         _native.check(rc, "gb_allreduce_oneshot")
         return out
 
@@ -187,11 +192,12 @@ class TwoShotAllReduce:
 class PushExchange:
     """All-gather (``stride = 0``) or all-to-all (``stride = bytes_per_dst``) by peer stores."""
 
-    def __init__(self, fab: Fabric, bytes_per_dst: int, chunks: int):
+    def __init__(self, fab: Fabric, bytes_per_dst: int, chunks: int, handshake: bool = True):
         self.fab, self.chunks = fab, chunks
         self.bytes_per_dst = (bytes_per_dst + 15) // 16 * 16
         self.out_off = fab.alloc(fab.world * self.bytes_per_dst)
         self.flags_off = fab.alloc(fab.world * chunks * 4)
+        self.ack_off = fab.alloc(8 * 4) if handshake else 0
         self.epoch, self.done = fab.ctl_word(), fab.ctl_word()
         self.out_view = fab.view(self.out_off, (fab.world, self.bytes_per_dst), torch.uint8)
 
@@ -199,7 +205,7 @@ class PushExchange:
         f = self.fab
         rc = f.lib.gb_push_exchange(f.bases_arr, _i(f.world), _i(f.rank), _sz(self.out_off), _sz(self.flags_off), _c(x.data_ptr()),
                                     _sz(self.bytes_per_dst), _sz(stride), _i(self.chunks), _c(self.epoch), _c(self.done),
-                                    _c(_native.status_ptr()), f._stream())
+                                    _c(_native.status_ptr()), _sz(self.ack_off), f._stream())
         _native.check(rc, "gb_push_exchange")
         return self.out_view
 
@@ -220,7 +226,8 @@ class ArgmaxAllReduce:
 
     def __init__(self, fab: Fabric, max_rows: int):
         self.fab, self.max_rows = fab, max_rows
-        self.data_off = fab.alloc(fab.world * max_rows * 8)
+        self.parity_stride = (fab.world * max_rows * 8 + 1023) // 1024 * 1024      # two slot sets, alternating by call
+        self.data_off = fab.alloc(2 * self.parity_stride)
         self.flags_off = fab.alloc(fab.world * 4)
         self.epoch = fab.ctl_word()
 
@@ -231,6 +238,6 @@ class ArgmaxAllReduce:
         f = self.fab
         rc = f.lib.gb_argmax_allreduce(f.bases_arr, _i(f.world), _i(f.rank), _sz(self.data_off), _sz(self.flags_off), _c(val.data_ptr()),
                                        _c(idx.data_ptr()), _c(out_i.data_ptr()), _c(out_v.data_ptr()), _i(rows), _i(self.max_rows),
-                                       _c(self.epoch), _c(_native.status_ptr()), f._stream())
+                                       _c(self.epoch), _c(_native.status_ptr()), _sz(self.parity_stride), f._stream())
         _native.check(rc, "gb_argmax_allreduce")
         return out_i, out_v

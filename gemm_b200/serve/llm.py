@@ -50,6 +50,11 @@ class LLM:
         self.blocks = KvBlockManager(num_pages, page_size)
         self.sched = Scheduler(self.blocks, max_running, max_batch_tokens)
         self.model = Transformer(weights, self.kv, par)
+        if weights.lm_head.w.shape[0] != self.cfg.vocab and weights.tp_size > 1:
+            # this loop samples from the local logits; with a vocabulary-sharded head every rank would pick a different token.
+            # serve.engine.Engine merges the shards (arg-max all-reduce); here the head must be whole.
+            raise ValueError("LLM (continuous batching) needs an unsharded LM head: build the weights with shard_vocab=False, "
+                             "or use serve.engine.Engine, which merges the vocabulary shards")
         self._reqs: Dict[int, _Req] = {}
         self._next_id = 0
         self.steps = 0

@@ -155,6 +155,8 @@ class SpeculativeDecoder:
     def __init__(self, model: Transformer, kv: KvCache, page_size: int, num_pages: int, drafter=None):
         if model.cfg.is_hybrid:
             raise ValueError("speculative decoding needs a cache that can drop rejected positions: recurrent layers cannot")
+        if model.w.tp_size > 1 and model.w.lm_head.w.shape[0] != model.cfg.vocab:
+            raise ValueError("speculative decoding takes the arg-max of the local logits: it needs an unsharded LM head")
         self.model, self.kv, self.page = model, kv, page_size
         self.blocks = KvBlockManager(num_pages, page_size)
         self.drafter = drafter

@@ -5,7 +5,10 @@ Counterpart of the reference's 'TPCP' files (a64fx/llm/tp_runner.c:155-563: magi
 cache position, next token, then per-layer K / V buffers; every header field is validated on load,
 tp_cache_matches_model :356-387).  Our file: magic ``GBKV1\\n``, a JSON header line (geometry, sequences), then for every layer
 the K and V rows of the used cache slots in sequence order: bf16, or with ``kv_format="q8"`` int8 rows followed by one f32 scale per
-(slot, KV head) (``ops.kvquant``: about half the size, the reference's INT8 KV rule).  A truncated or mismatching file is rejected.
+(slot, KV head) (``ops.kvquant``: about half the size, the reference's INT8 KV rule).  Layers of the hybrid models that keep a recurrent state
+instead of K/V (gated Delta-Net) write, per live sequence, the f32 conv history and the f32 recurrent matrix of its state slot
+(the reference stores conv state and recurrent state per layer as well, tp_runner.c:155-563).  A truncated or mismatching file
+is rejected.
 """
 from __future__ import annotations
 
@@ -20,9 +23,18 @@ MAGIC = b"GBKV1\n"
 
 def _geometry(engine) -> Dict:
     cfg = engine.cfg
-    return {"arch": cfg.arch, "n_layers": len(engine.w.layers), "hidden": cfg.hidden, "n_kv_heads_local": engine.kv.k[0].shape[1],
+    return {"arch": cfg.arch, "n_layers": len(engine.w.layers), "hidden": cfg.hidden, "n_kv_heads_local": _kv_rows(engine)[0],
             "head_dim": cfg.head_dim, "vocab": cfg.vocab, "tp_size": engine.w.tp_size, "tp_rank": engine.w.tp_rank,
-            "ep_size": engine.w.ep_size, "ep_rank": engine.w.ep_rank, "fmt": engine.w.fmt}
+            "ep_size": engine.w.ep_size, "ep_rank": engine.w.ep_rank, "fmt": engine.w.fmt,
+            "ssm_layers": [i for i in range(len(engine.kv.k)) if engine.kv.k[i].shape[0] == 0]}
+
+
+def _kv_rows(engine):
+    """(kv heads, head dim) of the attention layers' cache rows (the recurrent layers hold 0-row tensors)."""
+    for t in engine.kv.k:
+        if t.shape[0] > 0:
+            return t.shape[1], t.shape[2]
+    return engine.kv.k[0].shape[1], engine.kv.k[0].shape[2]
 
 
 def save_state(engine, path: str, next_tokens=None, kv_format: str = "bf16") -> None:
@@ -44,7 +56,13 @@ def save_state(engine, path: str, next_tokens=None, kv_format: str = "bf16") -> 
         hb = json.dumps(header).encode()
         f.write(struct.pack("<Q", len(hb)))
         f.write(hb)
+        n_seq = len(engine.seq_len)
         for li in range(len(engine.kv.k)):
+            if engine.kv.k[li].shape[0] == 0:
+                # recurrent layer: the state slots of the live sequences (slot s belongs to sequence s in a static-batch engine)
+                for t in (engine.kv.conv[li], engine.kv.rec[li]):
+                    f.write(t[:n_seq].contiguous().cpu().numpy().tobytes())
+                continue
             for t in (engine.kv.k[li], engine.kv.v[li]):
                 rows = t[idx].contiguous()
                 if kv_format == "q8":
@@ -89,8 +107,18 @@ def load_state(engine, path: str) -> torch.Tensor:
             pages = engine.seq_pages[s]
             slots.extend(pages[p // ps] * ps + p % ps for p in range(n))
         idx = torch.tensor(slots, dtype=torch.long, device=engine.device)
-        row = engine.kv.k[0].shape[1] * engine.kv.k[0].shape[2] * 2
+        hk, hd = _kv_rows(engine)
+        row = hk * hd * 2
+        n_seq = len(header["seq_len"])
         for li in range(len(engine.kv.k)):
+            if engine.kv.k[li].shape[0] == 0:
+                for t in (engine.kv.conv[li], engine.kv.rec[li]):
+                    nb = n_seq * t[0].numel() * 4
+                    buf = f.read(nb)
+                    if len(buf) != nb:
+                        raise ValueError("truncated KV state file")
+                    t[:n_seq] = torch.frombuffer(bytearray(buf), dtype=torch.float32).reshape(n_seq, *t.shape[1:]).to(engine.device)
+                continue
             for t in (engine.kv.k[li], engine.kv.v[li]):
                 if kv_format == "q8":
                     nq, ns = len(slots) * (row // 2), len(slots) * t.shape[1] * 4

@@ -85,3 +85,22 @@ def test_stage_per_rank_blobs(tmp_path, fmt):
         assert torch.equal(w.layers[1].w13.dequantized(), ref.layers[1].w13.dequantized())
         assert torch.equal(w.layers[0].wqkv.dequantized(), ref.layers[0].wqkv.dequantized())
         assert torch.equal(w.embed, ref.embed)
+
+
+def test_kv_state_of_a_hybrid_model_carries_the_recurrent_state(tmp_path):
+    """Delta-Net layers have no K/V rows; their conv history and recurrent matrix per sequence go into the file instead."""
+    torch.manual_seed(0)
+    cfg = get_config("tiny-qwen35")
+    w = synthetic_weights(cfg, "bf16", device="cpu", seed=5)
+    prompts = [torch.randint(0, cfg.vocab, (n,), dtype=torch.int32) for n in (13, 6)]
+    a = Engine(w, max_batch=2, max_seq_len=64, page_size=16)
+    first = a._sample(a.prefill(prompts, reserve=8), SamplingParams(), 0)
+    path = str(tmp_path / "hybrid.gbkv")
+    checkpoint.save_state(a, path, first)
+    a.begin_decode(first, SamplingParams(), 6, use_graph=False)
+    ref = [a.decode_step().clone() for _ in range(4)]
+    b = Engine(w, max_batch=2, max_seq_len=64, page_size=16)
+    nxt = checkpoint.load_state(b, path)
+    b.begin_decode(nxt, SamplingParams(), 6, use_graph=False)
+    got = [b.decode_step().clone() for _ in range(4)]
+    assert all(torch.equal(x, y) for x, y in zip(ref, got))

@@ -45,6 +45,17 @@ def test_no_alloc_argmax_matches_regular_entry_point_twice():
     assert int(_call(a)[1][3]) == 10
 
 
+def test_no_alloc_argmax_row_of_minus_infinity():
+    """A row that is -inf everywhere (a fully masked vocabulary) yields column 0 + offset, like the regular entry point."""
+    x = torch.full((3, 70000), float("-inf"), device="cuda")
+    x[1, 4242] = -5.0
+    rc, out, _ = _call(x, 7)
+    assert rc == 0
+    ref = sampling.argmax(x, idx_offset=7)
+    torch.cuda.synchronize()
+    assert out.tolist() == [7, 4249, 7] and torch.equal(out, ref)
+
+
 def test_no_alloc_argmax_rejects_oversized_batches():
     x = torch.zeros(1025, 8, device="cuda")
     rc, _, _ = _call(x)
