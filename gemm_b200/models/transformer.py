@@ -326,10 +326,14 @@ class Transformer:
         if self.mx:
             # token tile (= scale-atom layout) by the expected rows per expert: 32 for decode-sized batches
             tn = 32 if (t * k) // e <= 24 else 128
-            ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
-            # the RMSNorm before this block already quantised the tokens: gather bytes and scales (every token is quantised
-            # once, not once per selected expert)
-            xq = ew.mx_gather_rows(h_mx, pl.row_token, sf_layout=tn) if h_mx is not None else ew.mx_quantize(h, pl.row_token, sf_layout=tn)
+            if tn == 32 and moe.can_prep(h, lw.router, k):
+                # decode-sized batch: router projection, routing, plan and the quantised gather are one launch
+                ids, wts, pl, xq = moe.prep_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+            else:
+                ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+                # the RMSNorm before this block already quantised the tokens: gather bytes and scales (every token is quantised
+                # once, not once per selected expert)
+                xq = ew.mx_gather_rows(h_mx, pl.row_token, sf_layout=tn) if h_mx is not None else ew.mx_quantize(h, pl.row_token, sf_layout=tn)
             dev = h.device
             hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=dev)
             hsf = ew.sf_alloc(pl.capacity, inter, dev, tn, init=False)
@@ -338,8 +342,11 @@ class Transformer:
                                     w_tiled=lw.w2.mx.tiled, pair_rows=(tn == 32 and PAIR_DOWN))
         else:
             tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
-            ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
-            xs = moe.gather_rows(h, pl.row_token)
+            if moe.can_prep(h, lw.router, k):
+                ids, wts, pl, xs = moe.prep_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale, quantize=False)
+            else:
+                ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+                xs = moe.gather_rows(h, pl.row_token)
             act = gemm.grouped_linear(xs, lw.w13.w.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
             y = gemm.grouped_linear(act, lw.w2.w.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)
         return moe.PendingCombine(y, pl.pair_row, wts, t, k)

@@ -120,6 +120,60 @@ def route_plan_hidden(h: torch.Tensor, w: torch.Tensor, k: int, n_exp: int, alig
     return route_plan(router_logits(h, w), k, n_exp, align, mode, bias, renorm, routed_scale, local_range, regions, epoch_ctr, region_rows)
 
 
+# One-launch router + routing + plan + gather for decode-sized batches (csrc/kernels/moe_prep.cu); GB_MOE_PREP=0 keeps the
+# separate kernels.
+MOE_PREP = os.environ.get("GB_MOE_PREP", "1") != "0"
+
+
+def can_prep(h: torch.Tensor, w: torch.Tensor, k: int) -> bool:
+    """Shapes ``prep_hidden`` takes: up to 64 tokens, up to 128 experts, hidden a multiple of 256 (256 .. 4096 in powers of two)."""
+    if not (MOE_PREP and h.is_cuda and h.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and h.stride(1) == 1 and w.stride(1) == 1):
+        return False
+    if h.stride(0) % 8 or w.stride(0) % 8 or h.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    return bool(_native.cuda().gb_moe_prep_supported(_i(h.shape[0]), _i(h.shape[1]), _i(w.shape[0]), _i(k)))
+
+
+def prep_hidden(h: torch.Tensor, w: torch.Tensor, k: int, n_exp: int, align: int, mode: str = "softmax", bias: Optional[torch.Tensor] = None,
+                renorm: bool = True, routed_scale: float = 1.0, local_range: Optional[Tuple[int, int]] = None, quantize: bool = True,
+                wait_flags: int = 0, wait_n: int = 0, epoch_ptr: int = 0):
+    """Router projection, routing, plan AND the gather of the token rows into expert order in one launch.
+
+    Returns ``(ids, weights, MoePlan, rows)``; ``rows`` is an ``MxTensor`` (MXFP8 with scale atoms in the ``align``-row layout,
+    ``align`` 32 or 128) when ``quantize`` else a bf16 tensor ``[capacity, hidden]``.  Rows of the buffer that no (token, expert)
+    pair maps to are left unwritten: the grouped GEMM computes them and drops them.  ``n_exp`` is the number of experts the plan
+    covers (the local count with ``local_range``).  ``wait_*``: flags of peer GPUs to wait for before the tokens are read."""
+    from . import elementwise as ew
+    from .mxfp8 import MxTensor
+    t, hid = h.shape
+    dev = h.device
+    n_pairs = t * k
+    _, capacity = plan_capacity(n_pairs, n_exp, align, 1, k)
+    ids = torch.empty(t, k, dtype=torch.int32, device=dev)
+    wt = torch.empty(t, k, dtype=torch.float32, device=dev)
+    seg_start = torch.empty(n_exp, dtype=torch.int32, device=dev)
+    seg_count = torch.empty(n_exp, dtype=torch.int32, device=dev)
+    pair_row = torch.empty(n_pairs, dtype=torch.int32, device=dev)
+    row_token = torch.empty(capacity, dtype=torch.int32, device=dev)
+    xq = xsf = xs = None
+    if quantize:
+        assert align in (32, 128) and hid % 128 == 0
+        xq = torch.empty(capacity, hid, dtype=torch.uint8, device=dev)
+        xsf = ew.sf_alloc(capacity, hid, dev, align, init=False)
+    else:
+        xs = torch.empty(capacity, hid, dtype=torch.bfloat16, device=dev)
+    rc = _native.cuda().gb_moe_prep(_p(h), _i(h.stride(0)), _i(t), _i(hid), _p(w), _i(w.stride(0)), _i(w.shape[0]), _p(bias), _i(k),
+                                    _i(0 if mode == "softmax" else 1), _i(1 if renorm else 0), _f(routed_scale),
+                                    _i(local_range[0] if local_range else 0), _i(local_range[1] if local_range else 0), _i(align),
+                                    _i(capacity), _p(ids), _p(wt), _p(seg_start), _p(seg_count), _p(pair_row), _p(row_token), _p(xq), _p(xsf),
+                                    _i(1 if align == 32 else 0), _p(xs), _c(wait_flags), _i(wait_n), _c(epoch_ptr),
+                                    _c(_native.status_ptr()), _s())
+    _native.check(rc, "gb_moe_prep")
+    pl = MoePlan(seg_start, seg_count, pair_row, row_token, torch.empty(0, dtype=torch.int32, device=dev), capacity, capacity)
+    rows = MxTensor(xq, xsf, capacity, hid, align) if quantize else xs
+    return ids, wt, pl, rows
+
+
 @dataclass
 class MoePlan:
     seg_start: torch.Tensor      # int32 [E]   first row of each expert's segment

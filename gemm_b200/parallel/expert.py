@@ -215,8 +215,11 @@ class ExpertParallel:
         if self.mx:
             from ..models.transformer import expert_gate_up_mx
             tn = 32
-            ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
-            xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
+            if moe.can_prep(allh, lw.router, k):
+                ids, wts, pl, xq = moe.prep_hidden(allh, lw.router, k, self.e_local, tn, **rt)
+            else:
+                ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
+                xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
             hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
             hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)
             expert_gate_up_mx(xq.data, xq.sf, lw.w13, self.e_local, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
@@ -225,8 +228,11 @@ class ExpertParallel:
                                     w_tiled=lw.w2.mx.tiled, pair_rows=PAIR_DOWN)
         else:
             tn = gemm.pick_tn(max(1, (w * cap * k + cfg.n_experts - 1) // cfg.n_experts), dual=True)
-            ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
-            xs = moe.gather_rows(allh, pl.row_token)
+            if moe.can_prep(allh, lw.router, k):
+                ids, wts, pl, xs = moe.prep_hidden(allh, lw.router, k, self.e_local, tn, quantize=False, **rt)
+            else:
+                ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
+                xs = moe.gather_rows(allh, pl.row_token)
             act = gemm.grouped_linear(xs, lw.w13.w.view(self.e_local, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
             y = gemm.grouped_linear(act, lw.w2.w.view(self.e_local, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)
         rc = f.lib.gb_moe_combine_scatter(_c(y.data_ptr()), _c(pl.pair_row.data_ptr()), _c(wts.data_ptr()), _i(w * cap), _i(hid), _i(k),
