@@ -38,7 +38,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="qwen3-30b-a3b")
-    ap.add_argument("--fmt", default="mxfp8", choices=["mxfp8", "bf16"])
+    ap.add_argument("--fmt", default="mxfp8", choices=["mxfp8", "bf16", "q4_k", "q8_0"],
+                    help="weight format; q4_k / q8_0 keep ggml blocks in HBM (fused dequant-GEMV / GEMM)")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: run fewer layers (the JSON line then says so and is not a valid bench number)")
@@ -307,11 +308,13 @@ def main():
         line = {
             "metric": "decode_tokens_per_s", "value": decode_tok_s, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "mxfp8 weights+activations, bf16 outputs, fp32 accumulate" if args.fmt == "mxfp8" else "bf16",
+            "vs_baseline": None, "dtype": {"mxfp8": "mxfp8 weights+activations, bf16 outputs, fp32 accumulate", "bf16": "bf16",
+                                          "q4_k": "ggml Q4_K weights (kept quantised), bf16 activations / int8 in the GEMV, fp32 accumulate",
+                                          "q8_0": "ggml Q8_0 weights (kept quantised), bf16 activations / int8 in the GEMV, fp32 accumulate"}[args.fmt],
             "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "config": {"model": args.model, "global_batch": args.batch, "seq_len": args.prompt_len, "decode_context": args.prompt_len + args.warmup,
                        "parallelism": (f"tp{n_gpus}" if tp else f"dp{n_gpus}-attention+ep{n_gpus}") if n_gpus > 1 else "single", "layers": n_layers,
-                       "l2": "no flush: each step streams ~29 GB of expert weights and ~13 GB of KV over the job, inputs >> 126 MB L2",
+                       "l2": f"no flush: each step streams the {weights.nbytes() / 2**30:.1f} GiB of weights of a rank plus its KV cache, far more than the 126 MB L2",
                        "moe_path": args.moe_path if n_gpus > 1 else "local"},
             "prefill_tokens_per_s": prefill_tok_s, "ttft_ms_p50": prefill_ms, "tpot_ms_p50": tpot_p50,
             "clocks": clocks, "e2e": e2e, "gpu_launches": kernels_per_step * args.steps,

@@ -1,0 +1,337 @@
+// Fused dequant-GEMV for ggml-quantised weights that stay quantised in HBM: out[m, n] = sum_k W[n, k] * x[m, k] for one to
+// four tokens (latency-bound decode), W in Q4_K or Q8_0 blocks in the tiled layout of ops/ggml_torch.py (tiles of 128 rows x
+// 256 columns, each one contiguous piece of memory).
+//
+// How the bytes become arithmetic.  The activations are quantised to int8 per 32 values inside the kernel (fp32 scale d8 and
+// the block sum s8 = d8 * sum(q8) kept beside them in shared memory), so that a 32-bit word of weight nibbles / bytes meets a
+// word of activations in one dp4a:
+//   Q8_0:  acc += d * d8 * sum_i dp4a(q, q8)
+//   Q4_K:  acc += (d * sc) * d8 * sum_i dp4a(nibbles, q8)  -  (dmin * m) * s8      per 32-wide sub-block
+// (d * sc and dmin * m are applied once per sub-block, after the integer sum).  A weight word is unpacked once and used for every
+// token and both rows of a thread; a CTA never reads a weight byte twice, and every 16-byte load of a warp falls into one
+// contiguous stretch of its tile.
+//
+// Work split.  A CTA owns one row tile (128 output features) and a range of the K tiles (split-K: a projection with few rows still
+// fills the GPU; every split writes its fp32 partial into its own slab and the consumer adds the slabs in split order, as the
+// tensor-core GEMM's K-split does).  Warp w takes the 64-value chunk j = w % 4 of every 256-column tile for the row pairs
+// (r, r + 64), r = 32 * (w / 4) + lane: j is uniform in a warp, so the 6-bit scale unpacking is branch-free and the activation
+// words are a shared-memory broadcast.
+//
+// With tensor parallelism the result rows can go straight into this rank's slot on every GPU (peer stores) and the last CTA
+// raises the arrival flags: the one-shot all-reduce of a row-parallel projection is the tail of the GEMV, its sum happens in the
+// RMSNorm that follows (gb_rmsnorm_reduce2).
+//
+// Replaces in the reference: matvec_q4_K_q8_1_dp4a (cuda/llm/cuda_llm_runner.c:1307), quantize_f32_to_q8_1 (:1039),
+// matvec_q8_0_dp4a / matvec_q8_0_f16act (:611, :711), the fused gate/up pair matvec_q8_0_dp4a_fused2 (:752) and the dispatcher
+// launch_matvec_auto (:13363-13506); CPU counterpart tf_qmatvec_worker (common/transformer.h:648-738).
+#include "sm100.cuh"
+#include "host_common.h"
+#include "../fabric/fabric.cuh"
+
+namespace gb {
+
+constexpr int kQvThreads = 256;
+constexpr int kQ4KTileBytes = 128 * 144;
+constexpr int kQ80TileBytes = 128 * 256 + 128 * 16;
+constexpr int kQ80ScaleOff = 128 * 256;
+
+struct QGemvArgs {
+  const uint8_t* w;                 // tiled weights [row_tiles][num_kb][tile bytes]
+  const __nv_bfloat16* x; int ldx;  // activations [m, k]
+  float* out; int ldo;              // fp32 [splits][m][ldo]
+  long partial_stride;              // elements between the slabs of two K splits
+  const float* bias;                // optional [n_out], added by split 0
+  int n_out, row_tiles, num_kb, kb_per, splits;
+  void* peer_out[kMaxRanks];        // peer_bcast > 0: the slab goes to peer_out[p] for every p < peer_bcast instead of `out`
+  int peer_bcast;
+  uint32_t* signal_flags[kMaxRanks];
+  int signal_n;
+  unsigned* done_ctr;
+  uint32_t* epoch_ptr;
+  int epoch_self_tick;
+  int stages;
+  KernelStatus* status;
+};
+
+__device__ __forceinline__ int dp4a_s(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
+__device__ __forceinline__ uint32_t byte_of(uint32_t w, int i) { return (w >> (8 * i)) & 0xffu; }
+
+// TYPE: 0 = Q4_K, 1 = Q8_0.  M tokens.  Weight tiles travel through a ring of `stages` shared-memory slots filled by bulk copies
+// (one elected thread issues them, an mbarrier per slot counts the bytes): the bytes in flight per SM are what bounds a
+// memory-bound GEMV, and registers alone cannot hold enough of them.
+template <int TYPE, int M>
+__global__ void __launch_bounds__(kQvThreads, 2)
+qgemv_kernel(const QGemvArgs a) {
+  extern __shared__ uint8_t qv_smem_raw[];
+  uint8_t* qv_smem = (uint8_t*)(((uintptr_t)qv_smem_raw + 127) & ~(uintptr_t)127);
+  constexpr int TILE = TYPE == 0 ? kQ4KTileBytes : kQ80TileBytes;
+  const int S = a.stages;
+  const int tile_id = blockIdx.x / a.splits, ks = blockIdx.x - tile_id * a.splits;
+  const int kb0 = ks * a.kb_per, kb1 = min(a.num_kb, kb0 + a.kb_per);
+  const int nkb = kb1 - kb0;
+  uint8_t* ring = qv_smem;                                                       // [S][TILE]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + (size_t)S * TILE);     // [S]
+  uint64_t* empty_bar = full_bar + S;                                            // [S] 8 arrivals (one per warp)
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
+  int8_t* aq = reinterpret_cast<int8_t*>(ring + (size_t)S * TILE + 128);         // [nkb][M][256]
+  float* ad = reinterpret_cast<float*>(aq + (size_t)a.kb_per * M * 256);         // [nkb][M][8] block scales
+  float* as = ad + (size_t)a.kb_per * M * 8;                                     // [nkb][M][8] block sums (d8 * sum q8)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint8_t* wt = a.w + ((size_t)tile_id * a.num_kb + kb0) * TILE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kQvThreads / 32); }
+    *abort_flag = 0;
+    fence_barrier_init();
+    // weights do not depend on the kernel in front of this one: the first tiles are requested before the dependency wait
+    for (int s = 0; s < S && s < nkb; ++s) { mbar_expect_tx(&full_bar[s], TILE); bulk_load(ring + (size_t)s * TILE, wt + (size_t)s * TILE, TILE, &full_bar[s]); }
+  }
+  pdl_wait();
+  pdl_trigger();
+
+  // ---- activations of this CTA's K range -> int8 + scale + sum per 32 values (4 lanes x 8 values hold one block)
+  for (int it = threadIdx.x; it < nkb * M * 32; it += kQvThreads) {
+    const int v = it & 31, m = (it >> 5) % M, kbi = (it >> 5) / M;
+    const uint4 raw = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + (size_t)(kb0 + kbi) * 256 + v * 8);
+    const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float f[8];
+    float amax = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float2 t = __bfloat1622float2(hv[u]);
+      f[2 * u] = t.x; f[2 * u + 1] = t.y;
+      amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const float d = amax * (1.0f / 127.0f);
+    const float inv = d > 0.f ? 1.0f / d : 0.f;
+    int q[8], qsum = 0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { q[u] = max(-127, min(127, __float2int_rn(f[u] * inv))); qsum += q[u]; }
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+    uint2 pk;
+    pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+    pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+    *reinterpret_cast<uint2*>(aq + ((size_t)(kbi * M + m) * 256 + v * 8)) = pk;
+    if ((v & 3) == 0) { ad[(kbi * M + m) * 8 + (v >> 2)] = d; as[(kbi * M + m) * 8 + (v >> 2)] = d * (float)qsum; }
+  }
+  __syncthreads();                                         // also publishes the barrier initialisation to every thread
+
+  // ---- main loop: chunk j of every K tile for the rows (rp, rp + 64)
+  const int j = warp & 3, rp = (warp >> 2) * 32 + lane;
+  float acc[2][M];
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+
+  int st = 0; uint32_t ph = 0;
+  bool ok = true;
+  for (int kbi = 0; kbi < nkb; ++kbi) {
+    if (!mbar_wait(&full_bar[st], ph, abort_flag, a.status, 1300, st)) { ok = false; break; }
+    const uint8_t* t = ring + (size_t)st * TILE;
+    uint4 chd[2], cqw[2][4];             // per row: header (Q4_K) / scale word in .x (Q8_0), weight words (Q4_K uses 2 vectors, Q8_0 four)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int row = rp + 64 * r;
+      if (TYPE == 0) {
+        const uint8_t* b = t + row * 144;
+        chd[r] = *reinterpret_cast<const uint4*>(b);
+        cqw[r][0] = *reinterpret_cast<const uint4*>(b + 16 + 32 * j);
+        cqw[r][1] = *reinterpret_cast<const uint4*>(b + 32 + 32 * j);
+      } else {
+        const uint8_t* b = t + row * 256 + 64 * j;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cqw[r][u] = *reinterpret_cast<const uint4*>(b + 16 * u);
+        chd[r].x = *reinterpret_cast<const uint32_t*>(t + kQ80ScaleOff + (row * 8 + 2 * j) * 2);
+      }
+    }
+    // the slot's bytes are in registers: hand it back, and let the elected thread refill it with the tile S steps ahead
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[st]);
+    if (threadIdx.x == 0 && kbi + S < nkb) {
+      if (mbar_wait(&empty_bar[st], ph, abort_flag, a.status, 1301, st)) {
+        mbar_expect_tx(&full_bar[st], TILE);
+        bulk_load(ring + (size_t)st * TILE, wt + (size_t)(kbi + S) * TILE, TILE, &full_bar[st]);
+      } else ok = false;
+    }
+    if (++st == S) { st = 0; ph ^= 1; }
+
+    // per row: the two scale factors (and offsets) of this chunk's sub-blocks, and the unpacked words
+    float s_lo[2], s_hi[2], o_lo[2], o_hi[2];
+    uint32_t wlo[2][8], whi[2][8];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (TYPE == 0) {
+        const __half2 dd = *reinterpret_cast<const __half2*>(&chd[r].x);
+        const float d = __low2float(dd), dmin = __high2float(dd);
+        const uint32_t s0 = chd[r].y, s1 = chd[r].z, s2 = chd[r].w;
+        uint32_t sc0, sc1, mn0, mn1;
+        if (j < 2) {
+          sc0 = byte_of(s0, 2 * j) & 63u; sc1 = byte_of(s0, 2 * j + 1) & 63u;
+          mn0 = byte_of(s1, 2 * j) & 63u; mn1 = byte_of(s1, 2 * j + 1) & 63u;
+        } else {
+          const int b0 = 2 * j - 4, b1 = 2 * j - 3;
+          sc0 = (byte_of(s2, b0) & 15u) | ((byte_of(s0, b0) >> 6) << 4); sc1 = (byte_of(s2, b1) & 15u) | ((byte_of(s0, b1) >> 6) << 4);
+          mn0 = (byte_of(s2, b0) >> 4) | ((byte_of(s1, b0) >> 6) << 4); mn1 = (byte_of(s2, b1) >> 4) | ((byte_of(s1, b1) >> 6) << 4);
+        }
+        s_lo[r] = d * (float)sc0; s_hi[r] = d * (float)sc1; o_lo[r] = dmin * (float)mn0; o_hi[r] = dmin * (float)mn1;
+        const uint32_t* qq = reinterpret_cast<const uint32_t*>(&cqw[r][0]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { wlo[r][i] = qq[i] & 0x0f0f0f0fu; whi[r][i] = (qq[i] >> 4) & 0x0f0f0f0fu; }
+      } else {
+        const __half2 dd = *reinterpret_cast<const __half2*>(&chd[r].x);
+        s_lo[r] = __low2float(dd); s_hi[r] = __high2float(dd); o_lo[r] = 0.f; o_hi[r] = 0.f;
+        const uint32_t* qq = reinterpret_cast<const uint32_t*>(&cqw[r][0]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { wlo[r][i] = qq[i]; whi[r][i] = qq[8 + i]; }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const uint4* ap = reinterpret_cast<const uint4*>(aq + ((size_t)(kbi * M + m) * 256 + 64 * j));
+      const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+      const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+      const float d_lo = ad[(kbi * M + m) * 8 + 2 * j], d_hi = ad[(kbi * M + m) * 8 + 2 * j + 1];
+      const float t_lo = as[(kbi * M + m) * 8 + 2 * j], t_hi = as[(kbi * M + m) * 8 + 2 * j + 1];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        int sl = 0, sh = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { sl = dp4a_s(wlo[r][i], al[i], sl); sh = dp4a_s(whi[r][i], ah[i], sh); }
+        float v = s_lo[r] * d_lo * (float)sl + s_hi[r] * d_hi * (float)sh;
+        if (TYPE == 0) v -= o_lo[r] * t_lo + o_hi[r] * t_hi;
+        acc[r][m] += v;
+      }
+    }
+  }
+  (void)ok;
+  if (*abort_flag) {                                       // a wait gave up: copies may still be landing, bounded grace period
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+
+  // ---- the four chunk warps of a row group add up, one of them stores
+  __syncthreads();                                        // the activation tables are dead: reuse them (the ring may still receive nothing: every issued tile was consumed)
+  float* red = reinterpret_cast<float*>(aq);               // [8 warps][2 * M][32 lanes]
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) red[(warp * 2 * M + r * M + m) * 32 + lane] = acc[r][m];
+  __syncthreads();
+  if (j == 0) {
+    const size_t slab = (size_t)ks * (size_t)a.partial_stride;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int n = tile_id * 128 + rp + 64 * r;
+      if (n >= a.n_out) continue;
+      const float bias = (a.bias != nullptr && ks == 0) ? a.bias[n] : 0.f;
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float v = bias;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) v += red[((warp + jj) * 2 * M + r * M + m) * 32 + lane];     // chunks in fixed order
+        const size_t off = slab + (size_t)m * a.ldo + n;
+        if (a.peer_bcast > 0) { for (int p = 0; p < a.peer_bcast; ++p) reinterpret_cast<float*>(a.peer_out[p])[off] = v; }
+        else a.out[off] = v;
+      }
+    }
+  }
+  if (a.signal_n > 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      if (atomicAdd(a.done_ctr, 1u) == gridDim.x - 1) {
+        *a.done_ctr = 0;
+        uint32_t e = *a.epoch_ptr;
+        if (a.epoch_self_tick) { e += 1; *a.epoch_ptr = e; }
+        for (int p = 0; p < a.signal_n; ++p) st_release_sys(a.signal_flags[p], e);
+      }
+    }
+  }
+}
+
+}  // namespace gb
+
+using namespace gb;
+
+// Peer-store tail of gb_qgemv (all optional; mirrors the tensor-parallel fields of the GEMM's extras).
+struct QGemvPeer {
+  void* peer_out[kMaxRanks];
+  uint32_t* signal_flags[kMaxRanks];
+  int peer_bcast, signal_n;
+  unsigned* done_ctr;
+  uint32_t* epoch_ptr;
+  int epoch_self_tick, pad;
+};
+
+// Shared memory of one CTA: a ring of weight tiles + the quantised activations of its K range.  Two CTAs share an SM.
+constexpr int kQvSmemBudget = 110 * 1024;
+static int qgemv_stages(int type) { return type == 12 ? 4 : 2; }                 // 4 x 18 KB (Q4_K) / 2 x 34 KB (Q8_0)
+static int qgemv_tile_bytes(int type) { return type == 12 ? kQ4KTileBytes : kQ80TileBytes; }
+// Largest K range (in 256-column tiles) whose quantised activations fit beside the ring for `m` tokens.
+static int qgemv_max_kb(int m, int type) {
+  const int left = kQvSmemBudget - 1024 - qgemv_stages(type) * qgemv_tile_bytes(type);
+  const int by_act = left / (m * (256 + 64));
+  return by_act;
+}
+
+GB_API int gb_qgemv_supported(int ggml_type, int n_out, int k, int m) {
+  return ((ggml_type == 12 || ggml_type == 8) && m >= 1 && m <= 4 && k > 0 && k % 256 == 0 && n_out > 0) ? 1 : 0;
+}
+
+// Smallest split count (>= want) whose K range fits shared memory and leaves no split empty; 0 if none.
+GB_API int gb_qgemv_splits(int ggml_type, int k, int m, int want) {
+  const int num_kb = k / 256;
+  if (m < 1 || m > 4 || num_kb < 1 || (ggml_type != 12 && ggml_type != 8)) return 0;
+  for (int sp = want < 1 ? 1 : want; sp <= num_kb; ++sp) {
+    const int per = (num_kb + sp - 1) / sp;
+    if ((num_kb + per - 1) / per != sp) continue;
+    if (per <= qgemv_max_kb(m, ggml_type)) return sp;
+  }
+  return 0;
+}
+
+// w: tiled Q4_K (ggml_type 12) or Q8_0 (8) weights for ceil(n_out / 128) row tiles x k / 256 K tiles.  x bf16 [m, ldx], m <= 4.
+// out fp32: slab s (s < splits) at out + s * partial_stride holds [m][ldo] partial sums over the K range of split s.
+GB_API int gb_qgemv(const void* w, int ggml_type, const void* x, int ldx, float* out, int ldo, long partial_stride, const float* bias,
+                    int n_out, int k, int m, int splits, const QGemvPeer* peer, void* status, cudaStream_t stream) {
+  if (!gb_qgemv_supported(ggml_type, n_out, k, m)) return fail("qgemv: unsupported type / shape%s (type %ld, m %ld)", "", ggml_type, m);
+  if (ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail("qgemv: operands must be 16-byte aligned%s");
+  const int num_kb = k / 256;
+  if (splits < 1) splits = 1;
+  const int kb_per = (num_kb + splits - 1) / splits;
+  if ((num_kb + kb_per - 1) / kb_per != splits) return fail("qgemv: a K split would be empty%s");
+  if (kb_per > qgemv_max_kb(m, ggml_type)) return fail("qgemv: K range per split too long for shared memory%s (%ld tiles)", "", kb_per);
+  if (splits > 1 && partial_stride < (long)m * ldo) return fail("qgemv: partial slabs overlap%s");
+  QGemvArgs a;
+  memset(&a, 0, sizeof(a));
+  a.w = (const uint8_t*)w; a.x = (const __nv_bfloat16*)x; a.ldx = ldx; a.out = out; a.ldo = ldo; a.partial_stride = partial_stride; a.bias = bias;
+  a.n_out = n_out; a.row_tiles = (n_out + 127) / 128; a.num_kb = num_kb; a.kb_per = kb_per; a.splits = splits;
+  if (peer != nullptr) {
+    for (int i = 0; i < kMaxRanks; ++i) { a.peer_out[i] = peer->peer_out[i]; a.signal_flags[i] = peer->signal_flags[i]; }
+    a.peer_bcast = peer->peer_bcast; a.signal_n = peer->signal_n; a.done_ctr = peer->done_ctr; a.epoch_ptr = peer->epoch_ptr;
+    a.epoch_self_tick = peer->epoch_self_tick;
+  }
+  a.stages = qgemv_stages(ggml_type); a.status = (KernelStatus*)status;
+  size_t act = (size_t)kb_per * m * (256 + 64);
+  const size_t red = (size_t)8 * 2 * m * 32 * 4;
+  if (act < red) act = red;                                // the reduction scratch overlays the activation tables
+  const size_t smem = 128 + (size_t)a.stages * qgemv_tile_bytes(ggml_type) + 128 + act;
+  const int grid = a.row_tiles * splits;
+  const int t = ggml_type == 12 ? 0 : 1;
+#define GB_QV(TV, MV)                                                                                              \
+  {                                                                                                                 \
+    static bool attr = false;                                                                                       \
+    if (!attr) { GB_CUDA_OK(cudaFuncSetAttribute(qgemv_kernel<TV, MV>, cudaFuncAttributeMaxDynamicSharedMemorySize, kQvSmemBudget)); attr = true; } \
+    launch_k(qgemv_kernel<TV, MV>, grid, kQvThreads, smem, stream, a);                                              \
+  }
+  if (t == 0) { if (m == 1) GB_QV(0, 1) else if (m == 2) GB_QV(0, 2) else if (m == 3) GB_QV(0, 3) else GB_QV(0, 4) }
+  else { if (m == 1) GB_QV(1, 1) else if (m == 2) GB_QV(1, 2) else if (m == 3) GB_QV(1, 3) else GB_QV(1, 4) }
+#undef GB_QV
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

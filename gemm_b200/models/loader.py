@@ -67,10 +67,23 @@ def config_from_gguf(f: G.GGUFFile) -> ModelConfig:
 class GGUFSource:
     """Tensor source over an open GGUF file: every tensor is dequantised to float32 on request."""
 
-    def __init__(self, f: G.GGUFFile):
+    def __init__(self, f: G.GGUFFile, keep_blocks: bool = False):
         self.f = f
+        self.keep_blocks = keep_blocks       # hand out Q4_K / Q8_0 matrices as their raw blocks (no conversion at load)
         self._cache_name = None
         self._cache = None
+
+    def get_mat(self, name: str, shape):
+        """A 2-D projection matrix: its raw ggml blocks (``models.weights.QBlocks``) when ``keep_blocks`` and the type has a fused
+        dequant kernel (Q4_K, Q8_0), else float32 as ``get``."""
+        from .weights import QBlocks, QUANT_FMTS
+        t = self.f.tensors[name]
+        if self.keep_blocks and len(shape) == 2 and int(t.ggml_type) in QUANT_FMTS.values() and tuple(t.shape) == tuple(shape):
+            blk, nb = G.block_info(t.ggml_type)
+            rows, k = shape
+            raw = torch.from_numpy(np.array(t.raw(), copy=True)).reshape(rows, k // blk * nb)
+            return QBlocks(raw, int(t.ggml_type), k)
+        return self.get(name, shape)
 
     def has(self, name: str) -> bool:
         return name in self.f.tensors
@@ -94,10 +107,15 @@ class GGUFSource:
 
 def load_gguf(path: str, fmt: str = "bf16", device="cuda", tp_rank: int = 0, tp_size: int = 1, ep_rank: int = 0, ep_size: int = 1,
               shard_vocab: bool = False) -> ModelWeights:
-    """Load a GGUF checkpoint into the run-time weight format ``fmt`` (``bf16`` or ``mxfp8``), sharded for this rank."""
+    """Load a GGUF checkpoint into the run-time weight format ``fmt``, sharded for this rank.
+
+    ``bf16`` / ``mxfp8`` convert every matrix at load.  ``ggml`` converts nothing it has a kernel for: Q4_K and Q8_0 matrices keep
+    the file's blocks (re-ordered into tiles, bit for bit) and are multiplied by the fused dequant-GEMV / dequant-GEMM; tensors
+    of other types become bf16.  ``q4_k`` / ``q8_0`` additionally re-quantise the remaining matrices to that format."""
     with G.GGUFFile(path) as f:
         cfg = config_from_gguf(f)
-        return build_weights(cfg, GGUFSource(f), fmt, device, tp_rank, tp_size, ep_rank, ep_size, shard_vocab)
+        src = GGUFSource(f, keep_blocks=fmt in ("ggml", "q4_k", "q8_0"))
+        return build_weights(cfg, src, fmt, device, tp_rank, tp_size, ep_rank, ep_size, shard_vocab)
 
 
 def save_gguf(cfg: ModelConfig, src, path: str, wtype: str = "F16", tokens=None, merges=None, token_types=None, pre: str = "qwen2") -> None:

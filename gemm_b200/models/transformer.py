@@ -25,7 +25,7 @@ from .. import _native
 from ..ops import attention as att
 from ..ops import elementwise as ew
 from ..ops import deltanet as dn
-from ..ops import gemm, moe, sampling
+from ..ops import gemm, moe, qlinear, sampling
 from ..ops.mxfp8 import MxTensor
 from .config import ModelConfig
 from .weights import LinearWeight, ModelWeights
@@ -181,6 +181,8 @@ class SingleProcess:
 
 def apply_linear(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
     """``x W^T (+ bias)`` in the weight's format; ``x_mx`` is an already-quantised copy of ``x`` if the caller has one."""
+    if lw.is_quant:                       # ggml blocks in HBM: fused dequant-GEMV (<= 4 tokens) or dequant-GEMM
+        return qlinear.linear(x, lw.q, bias=lw.bias, out_dtype=out_dtype)
     if lw.fmt == "bf16":
         return gemm.linear(x, lw.w, bias=lw.bias, out_dtype=out_dtype, w_tiled=lw.tiled)
     xm = x_mx if x_mx is not None else ew.mx_quantize(x, sf_layout=32 if x.shape[0] <= 32 else 128)
@@ -192,6 +194,10 @@ def apply_linear_split(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTenso
     """``apply_linear`` for a projection whose result goes into the residual stream: a decode-sized MXFP8 projection with few
     output tiles (o_proj: 16 tiles of 128 rows, 32 k-steps each) is cut along K so that it fills the GPU, and the partial sums
     are left for the residual add + RMSNorm kernel that follows."""
+    if lw.is_quant:
+        if x.is_cuda and x.shape[0] <= qlinear.GEMV_MAX_TOKENS:
+            return qlinear.gemv_partials(x, lw.q, bias=lw.bias)      # K-split partial sums, added by the consumer
+        return apply_linear(lw, x, x_mx)
     if lw.fmt == "bf16" and SPLIT_PROJ and x is not None and x.is_cuda and lw.n % 128 == 0:
         sp = gemm.pick_partials(lw.n, x.shape[0], lw.k, False)
         if sp > 1:
@@ -303,6 +309,8 @@ class Transformer:
     def dense_ffn(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor]) -> torch.Tensor:
         gu = lw.w_gate_up
         inter = gu.n // 2
+        if gu.is_quant:
+            return self.par.row_linear(lw.w_down, qlinear.linear_swiglu(h, gu.q))
         if gu.fmt == "bf16":
             sp = gemm.pick_partials_dual(inter, h.shape[0], gu.k, False) if (SPLIT_PROJ and h.is_cuda and inter % 128 == 0) else 1
             if sp > 1:      # decode-sized batch: the projection is cut along K to fill the GPU, the activation kernel adds the partials
@@ -411,11 +419,16 @@ class Transformer:
         return ew.rmsnorm(xr.contiguous(), w.final_norm, cfg.rms_eps)
 
     def head(self, x: torch.Tensor, fb: ForwardBatch) -> torch.Tensor:
+        if self.w.lm_head.is_quant:
+            return qlinear.linear(self._head_input(x, fb), self.w.lm_head.q, out_dtype=torch.float32)
         return gemm.linear(self._head_input(x, fb), self.w.lm_head.w, out_dtype=torch.float32, w_tiled=self.w.lm_head.tiled)
 
     def forward_greedy(self, fb: ForwardBatch, want_value: bool = False):
         """Greedy next tokens ``int32 [len(logit_rows)]``: the arg-max runs in the LM-head GEMM's epilogue, no logits are stored."""
         x = self.forward_hidden(fb)
+        if self.w.lm_head.is_quant:
+            logits = qlinear.linear(self._head_input(x, fb), self.w.lm_head.q, out_dtype=torch.float32)
+            return sampling.argmax(logits, idx_offset=self.w.vocab_start, want_value=want_value)
         return gemm.linear_argmax(self._head_input(x, fb), self.w.lm_head.w, idx_offset=self.w.vocab_start, want_value=want_value,
                                   w_tiled=self.w.lm_head.tiled)
 

@@ -28,22 +28,31 @@ from .config import ModelConfig
 
 @dataclass
 class LinearWeight:
-    fmt: str                                  # "bf16" | "mxfp8"
+    fmt: str                                  # "bf16" | "mxfp8" | "q4_k" | "q8_0" (ggml blocks kept quantised in HBM)
     n: int                                    # output features (per group)
     k: int
     w: Optional[torch.Tensor] = None          # bf16 [rows, K]
     mx: Optional[MxTensor] = None
+    q: Optional["QTensor"] = None             # tiled ggml blocks (``ops.qlinear.QTensor``)
     bias: Optional[torch.Tensor] = None       # f32 [n]
     groups: int = 0                           # > 0: expert-stacked, rows = groups * rows_per_group
     rows_per_group: int = 0
     tiled: bool = False                       # bf16 ``w`` is in the tiled layout (``mx.tiled`` for MXFP8)
 
     @property
+    def is_quant(self) -> bool:
+        return self.q is not None
+
+    @property
     def is_tiled(self) -> bool:
+        if self.is_quant:
+            return True
         return self.tiled if self.fmt == "bf16" else self.mx.tiled
 
     def tile_(self) -> "LinearWeight":
         """Re-lay the matrix in place into the GEMM kernel's tiled weight layout (``ops.mxfp8.tile_weight``)."""
+        if self.is_quant:
+            return self                       # ggml blocks are stored in their own tile order from the start
         t = self.w if self.fmt == "bf16" else self.mx.data
         if self.is_tiled or not mxfp8.can_tile(t) or (self.groups and self.rows_per_group % 128):
             return self
@@ -61,28 +70,113 @@ class LinearWeight:
 
     @property
     def device(self):
+        if self.is_quant:
+            return self.q.data.device
         return self.w.device if self.w is not None else self.mx.data.device
 
     def dequantized(self) -> torch.Tensor:
         """fp32 copy of the full matrix (tests and CPU reference paths)."""
+        if self.is_quant:
+            return self.q.dequantize()
         if self.fmt == "bf16":
             return self.untiled_data().float()
         return mxfp8.dequantize(self.mx)
 
     def nbytes(self) -> int:
+        if self.is_quant:
+            return self.q.nbytes()
         if self.fmt == "bf16":
             return self.w.numel() * 2
         return self.mx.data.numel() + self.mx.sf.numel()
 
     def to(self, device) -> "LinearWeight":
         return LinearWeight(self.fmt, self.n, self.k, w=self.w.to(device) if self.w is not None else None,
-                            mx=self.mx.to(device) if self.mx is not None else None,
+                            mx=self.mx.to(device) if self.mx is not None else None, q=self.q.to(device) if self.q is not None else None,
                             bias=self.bias.to(device) if self.bias is not None else None, groups=self.groups,
                             rows_per_group=self.rows_per_group, tiled=self.tiled)
 
 
-def make_linear(w_f: torch.Tensor, fmt: str, bias: Optional[torch.Tensor] = None, groups: int = 0) -> LinearWeight:
-    """Wrap a float / bf16 matrix ``[rows, K]`` (rows = groups * rows_per_group when grouped)."""
+QUANT_FMTS = {"q4_k": 12, "q8_0": 8}          # run-time formats that keep ggml blocks: name -> ggml type id
+
+
+@dataclass
+class QBlocks:
+    """A matrix as row-major ggml blocks (the order of a GGUF file): ``raw`` uint8 ``[rows, row_bytes]``.  Supports what weight
+    assembly needs without decoding: row ranges, column ranges on block boundaries, stacking along rows."""
+    raw: torch.Tensor
+    ggml_type: int
+    k: int
+
+    @property
+    def shape(self):
+        return (self.raw.shape[0], self.k)
+
+    def _geom(self):
+        from ..ops import ggml_torch as gt
+        return gt.BLOCK[self.ggml_type]
+
+    def rows(self, a: int, b: int) -> "QBlocks":
+        return QBlocks(self.raw[a:b], self.ggml_type, self.k)
+
+    def cols(self, a: int, b: int) -> "QBlocks":
+        blk, nb = self._geom()
+        if a % blk or b % blk:
+            raise ValueError(f"column range [{a}, {b}) does not fall on {blk}-element block boundaries")
+        return QBlocks(self.raw[:, a // blk * nb: b // blk * nb], self.ggml_type, b - a)
+
+    def to(self, device) -> "QBlocks":
+        return QBlocks(self.raw.to(device), self.ggml_type, self.k)
+
+    def contiguous(self) -> "QBlocks":
+        return QBlocks(self.raw.contiguous(), self.ggml_type, self.k)
+
+
+def _mat(src, name: str, shape):
+    """A projection matrix from a tensor source: its ggml blocks when the source can hand them out (``get_mat``), else floats."""
+    return src.get_mat(name, shape) if hasattr(src, "get_mat") else src.get(name, shape)
+
+
+def _rows(t, a: int, b: int):
+    return t.rows(a, b) if isinstance(t, QBlocks) else t[a:b]
+
+
+def _cols(t, a: int, b: int):
+    return t.cols(a, b) if isinstance(t, QBlocks) else t[:, a:b]
+
+
+def _cat(parts):
+    """Stack matrices along rows; quantised parts must share type and width (a mixed list is decoded to float first)."""
+    if all(isinstance(p, QBlocks) for p in parts) and len({(p.ggml_type, p.k) for p in parts}) == 1:
+        return QBlocks(torch.cat([p.raw for p in parts]), parts[0].ggml_type, parts[0].k)
+    return torch.cat([_to_float(p) for p in parts])
+
+
+def _to_float(t):
+    if isinstance(t, QBlocks):
+        from ..ops import ggml_torch as gt
+        return gt.dequantize(t.raw.contiguous(), t.ggml_type, t.raw.shape[0], t.k).to(torch.bfloat16)
+    return t
+
+
+def make_linear(w_f, fmt: str, bias: Optional[torch.Tensor] = None, groups: int = 0) -> LinearWeight:
+    """Wrap a float / bf16 matrix ``[rows, K]`` (rows = groups * rows_per_group when grouped), or ggml blocks (``QBlocks``).
+
+    ``fmt`` "q4_k" / "q8_0" keeps (or makes) ggml blocks and stores them tiled for the fused dequant kernels; blocks of a type
+    without such a kernel, or with a width that is not a multiple of 256, are decoded to bf16.  Expert-stacked matrices have no
+    quantised path and are stored as bf16 under these formats."""
+    from ..ops.qlinear import QTensor
+    if fmt in QUANT_FMTS or fmt == "ggml" or isinstance(w_f, QBlocks):
+        rows, k = w_f.shape
+        want = QUANT_FMTS.get(fmt)
+        if groups == 0 and k % 256 == 0 and (want is not None or fmt == "ggml"):
+            if isinstance(w_f, QBlocks) and w_f.ggml_type in QUANT_FMTS.values() and (fmt == "ggml" or w_f.ggml_type == want):
+                name = {v: n for n, v in QUANT_FMTS.items()}[w_f.ggml_type]       # the file's own blocks, untouched
+                return LinearWeight(name, rows, k, q=QTensor.from_blocks(w_f.raw.contiguous(), w_f.ggml_type, rows, k), bias=bias)
+            if want is not None:
+                return LinearWeight(fmt, rows, k, q=QTensor.from_float(_to_float(w_f).float(), want), bias=bias)
+        w_f = _to_float(w_f)
+        if fmt in QUANT_FMTS or fmt == "ggml":
+            fmt = "bf16"
     rows, k = w_f.shape
     rpg = rows // groups if groups else 0
     n = rpg if groups else rows
@@ -178,6 +272,18 @@ class ModelWeights:
         return tot
 
 
+def ffn_shard(f: int, tp_size: int, tp_rank: int, fmt: str):
+    """Column range of the FFN width owned by a tensor-parallel rank.  Formats that keep ggml blocks cut on 256-column boundaries
+    (a K-quant super-block cannot be split), with the remainder going to the low ranks as in common/glm5.h:178-202 (its
+    block-aligned variant); the others split evenly."""
+    if (fmt in QUANT_FMTS or fmt == "ggml") and tp_size > 1 and f % 256 == 0:
+        lo, hi = shard_range(f // 256, tp_size, tp_rank)
+        return lo * 256, hi * 256
+    assert f % tp_size == 0
+    f_l = f // tp_size
+    return tp_rank * f_l, (tp_rank + 1) * f_l
+
+
 def shard_range(n: int, parts: int, idx: int):
     """Even split with the remainder to the low ranks (the rule of common/glm5.h:178-202)."""
     q, r = divmod(n, parts)
@@ -244,13 +350,11 @@ def _build_ffn(cfg, src, pre, lw, fmt, mv, dev, tp_rank, tp_size, ep_rank, ep_si
         del w13, w2
     else:
         f = cfg.ffn
-        assert f % tp_size == 0
-        f_l = f // tp_size
-        f0, f1 = tp_rank * f_l, (tp_rank + 1) * f_l
-        wg = src.get(pre + "ffn_gate.weight", (f, h))[f0:f1]
-        wu = src.get(pre + "ffn_up.weight", (f, h))[f0:f1]
-        wd = src.get(pre + "ffn_down.weight", (h, f))[:, f0:f1]
-        lw.w_gate_up = make_linear(mv(torch.cat([wg, wu])), fmt)
+        f0, f1 = ffn_shard(f, tp_size, tp_rank, fmt)
+        wg = _rows(_mat(src, pre + "ffn_gate.weight", (f, h)), f0, f1)
+        wu = _rows(_mat(src, pre + "ffn_up.weight", (f, h)), f0, f1)
+        wd = _cols(_mat(src, pre + "ffn_down.weight", (h, f)), f0, f1)
+        lw.w_gate_up = make_linear(mv(_cat([wg, wu])), fmt)
         lw.w_down = make_linear(mv(wd.contiguous()), fmt)
         del wg, wu, wd
     if cfg.is_moe and cfg.shared_expert_ffn > 0:
@@ -316,11 +420,11 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
             wq = wqg[:, 0].reshape(cfg.q_dim, h)[q0:q1]
             wgate = wqg[:, 1].reshape(cfg.q_dim, h)[q0:q1]
         else:
-            wq = src.get(pre + "attn_q.weight", (cfg.q_dim, h))[q0:q1]
+            wq = _rows(_mat(src, pre + "attn_q.weight", (cfg.q_dim, h)), q0, q1)
             wgate = None
-        wk = src.get(pre + "attn_k.weight", (cfg.kv_dim, h))[k0:k1]
-        wv = src.get(pre + "attn_v.weight", (cfg.kv_dim, h))[k0:k1]
-        wo = src.get(pre + "attn_output.weight", (h, cfg.q_dim))[:, q0:q1]
+        wk = _rows(_mat(src, pre + "attn_k.weight", (cfg.kv_dim, h)), k0, k1)
+        wv = _rows(_mat(src, pre + "attn_v.weight", (cfg.kv_dim, h)), k0, k1)
+        wo = _cols(_mat(src, pre + "attn_output.weight", (h, cfg.q_dim)), q0, q1)
         bias = None
         if cfg.qkv_bias:
             bias = torch.cat([src.get(pre + "attn_q.bias", (cfg.q_dim,))[q0:q1].float(), src.get(pre + "attn_k.bias", (cfg.kv_dim,))[k0:k1].float(),
@@ -328,7 +432,7 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
             bias = mv(bias)
         lw = LayerWeights(
             attn_norm=mv(src.get(pre + "attn_norm.weight", (h,)).to(torch.bfloat16)),
-            wqkv=make_linear(mv(torch.cat([wq, wk, wv] + ([wgate] if wgate is not None else []))), fmt, bias=bias),
+            wqkv=make_linear(mv(_cat([wq, wk, wv] + ([wgate] if wgate is not None else []))), fmt, bias=bias),
             wo=make_linear(mv(wo.contiguous()), fmt),
             ffn_norm=mv(src.get(pre + _post_attn_norm_name(src, pre), (h,)).to(torch.bfloat16)),
             q_norm=mv(src.get(pre + "attn_q_norm.weight", (d,)).to(torch.bfloat16)) if cfg.qk_norm else None,
@@ -337,15 +441,20 @@ def build_weights(cfg: ModelConfig, src, fmt: str = "bf16", device="cuda", tp_ra
         del wq, wk, wv, wo
         _build_ffn(cfg, src, pre, lw, fmt, mv, dev, tp_rank, tp_size, ep_rank, ep_size)
         layers.append(lw)
-    embed = mv(src.get("token_embd.weight", (cfg.vocab, h)).to(torch.bfloat16))
+    embed_src = _mat(src, "token_embd.weight", (cfg.vocab, h))
+    embed = mv(_to_float(embed_src).to(torch.bfloat16))          # the embedding lookup reads bf16 rows
+    quant_head = fmt in QUANT_FMTS or fmt == "ggml"
     if cfg.tie_embeddings or not src.has("output.weight"):
-        head_full = embed
+        head_full = embed_src if (quant_head and isinstance(embed_src, QBlocks)) else embed
     else:
-        head_full = mv(src.get("output.weight", (cfg.vocab, h)).to(torch.bfloat16))
+        head_src = _mat(src, "output.weight", (cfg.vocab, h))
+        head_full = head_src if (quant_head and isinstance(head_src, QBlocks)) else mv(_to_float(head_src).to(torch.bfloat16))
     v0, v1 = (0, cfg.vocab)
     if shard_vocab and tp_size > 1:
         v0, v1 = shard_range(cfg.vocab, tp_size, tp_rank)
-    lm_head = make_linear(head_full[v0:v1].contiguous() if (v0, v1) != (0, cfg.vocab) else head_full, "bf16")
+    head_rows = _rows(head_full, v0, v1).contiguous() if (v0, v1) != (0, cfg.vocab) else head_full
+    # the LM head streams the largest matrix of a decode step: under the block formats it stays quantised too
+    lm_head = make_linear(mv(head_rows), fmt if quant_head else "bf16")
     mw = ModelWeights(cfg=cfg, embed=embed, layers=layers, final_norm=mv(src.get("output_norm.weight", (h,)).to(torch.bfloat16)),
                       lm_head=lm_head, fmt=fmt, tp_rank=tp_rank, tp_size=tp_size, ep_rank=ep_rank, ep_size=ep_size, vocab_start=v0)
     if tile if tile is not None else dev.type == "cuda":

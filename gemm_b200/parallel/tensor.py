@@ -97,6 +97,8 @@ class TensorParallel:
     def row_linear(self, lw, x, x_mx: Optional[MxTensor] = None):
         from ..models.transformer import apply_linear
         rows = x.shape[0] if x is not None else x_mx.rows
+        if lw.is_quant:
+            return self._row_linear_quant(lw, x, rows)
         if not self.fused or self.tp_size == 1 or rows > self.max_fused_rows:
             if TP_DIRECT and self.fused and self.tp_size > 1 and rows * lw.n <= self.big.n and (x if x is not None else x_mx.data).is_cuda:
                 # prefill-sized: the GEMM writes its partial result straight into the all-reduce's input buffer in the fabric heap
@@ -131,6 +133,33 @@ class TensorParallel:
             gemm._launch(lw.mx.data, xm.data, None, n, k, rows, k, k, n, gemm.GEMM_MX | gemm.GEMM_OUT_F32 | (gemm.GEMM_W_TILED if lw.mx.tiled else 0), xm.sf_layout,
                          x_rows=xm.data.shape[0], sfa=lw.mx.sf, sfb=xm.sf, extras=ex)
         return PendingReduce(ch, rows, n, max(sp, 1))
+
+    def _row_linear_quant(self, lw, x: torch.Tensor, rows: int):
+        """Row-parallel projection over ggml blocks.  Up to four tokens: the fused dequant-GEMV stores its fp32 partial sums
+        straight into this rank's slot on every GPU and raises the arrival flags (the one-shot all-reduce is the GEMV's tail,
+        the sum happens in the RMSNorm that follows).  Larger batches: dequant-GEMM, then the stand-alone all-reduce."""
+        from ..ops import qlinear
+        if not self.fused or self.tp_size == 1 or rows > qlinear.GEMV_MAX_TOKENS or not x.is_cuda:
+            return self.tp_all_reduce(qlinear.linear(x, lw.q, bias=lw.bias if self.tp_rank == 0 else None))
+        ch = self._chan
+        self._chan ^= 1
+        ex = self._extras[ch]
+        n, k = lw.n, lw.k
+        sp = qlinear.pick_splits(n, k, rows, lw.q.ggml_type)
+        while sp > 1 and sp * rows * n > self.slot_elems:
+            sp -= 1
+        sp = max(1, _native.cuda().gb_qgemv_splits(_i(lw.q.ggml_type), _i(k), _i(rows), _i(sp)))
+        if sp * rows * n > self.slot_elems:
+            return self.tp_all_reduce(qlinear.linear(x, lw.q, bias=lw.bias if self.tp_rank == 0 else None))
+        peer = qlinear.QGemvPeer()
+        for p in range(self.tp_size):
+            peer.peer_out[p] = ex.peer_out[p]
+            peer.signal_flags[p] = ex.signal_flags[p]
+        peer.peer_bcast, peer.signal_n = self.tp_size, self.tp_size
+        peer.done_ctr, peer.epoch_ptr, peer.epoch_self_tick = ex.done_ctr, ex.epoch_ptr, 1
+        qlinear.gemv_partials(x, lw.q, splits=sp, bias=lw.bias if self.tp_rank == 0 else None, peer=peer,
+                              out=torch.empty(sp, 0, 0, dtype=torch.float32, device=x.device))
+        return PendingReduce(ch, rows, n, sp)
 
     def _reduce_norm(self, pr: PendingReduce, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128):
         f = self.fab

@@ -12,6 +12,8 @@ Cases
   attn_decode  paged flash-decode, 64 sequences x 2048 cached tokens, 32 query / 4 KV heads
   attn_prefill causal prefill, 8 sequences x 2048 tokens
   lm_head      64 x 151936 x 2048 with the arg-max epilogue
+  quant        ggml-quantised projections of the Qwen3-32B shape (Q4_K and Q8_0 blocks kept in HBM): fused dequant-GEMV for
+               1 and 4 tokens, fused dequant-GEMM for 8, 64 and 4096 tokens
   spec_verify  whole-model step over 1, 2, 3 and 5 positions per sequence (speculative verification against plain decode);
                builds the full Qwen3-30B-A3B shape, not part of ``all``
 
@@ -223,9 +225,34 @@ def case_spec_verify(args):
             print(json.dumps(dict(case="spec_verify_graph", positions_per_seq=q, tokens=b * q, ms=round(ms, 3), vs_one=round(ms / base, 3))), flush=True)
 
 
+def case_quant(args):
+    from ..ops import ggml_torch as gt
+    from ..ops import qlinear
+    shapes = [("qkv", 10240, 5120), ("gate_up", 51200, 5120), ("down", 5120, 25600)]
+    if args.once:
+        shapes = shapes[1:2]
+    for tname, t in (("q4_k", gt.Q4_K), ("q8_0", gt.Q8_0)):
+        blk, nb = gt.BLOCK[t]
+        for (pname, n, k) in shapes:
+            w = qlinear.QTensor.from_float(torch.randn(n, k, device="cuda") * 0.02, t)
+            wbytes = n * (k // blk) * nb
+            for m in ((1,) if args.once else (1, 4)):
+                x = torch.randn(m, k, device="cuda").bfloat16()
+                sp = qlinear.pick_splits(n, k, m, t)
+                out = torch.empty(sp, m, n, dtype=torch.float32, device="cuda")
+                _run(f"qgemv_{tname}_{pname}_{m}x{n}x{k}", lambda: qlinear.gemv_partials(x, w, splits=sp, out=out), 2.0 * m * n * k, wbytes, args, splits=sp)
+            for m in ((64,) if args.once else (8, 64, 4096)):
+                if m == 4096 and pname != "qkv":
+                    continue
+                x = torch.randn(m, k, device="cuda").bfloat16()
+                out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+                _run(f"qgemm_{tname}_{pname}_{m}x{n}x{k}", lambda: qlinear.gemm(x, w, out=out), 2.0 * m * n * k, wbytes + m * k * 2 + m * n * 2, args)
+            del w
+
+
 MODEL_CASES = {"spec_verify": case_spec_verify}      # build the whole benchmark model: not part of --case all
 CASES = {"gemm": case_gemm, "moe_decode": case_moe_decode, "moe_prefill": case_moe_prefill, "attn_decode": case_attn_decode,
-         "attn_prefill": case_attn_prefill, "lm_head": case_lm_head}
+         "attn_prefill": case_attn_prefill, "lm_head": case_lm_head, "quant": case_quant}
 
 
 def main(argv=None):

@@ -116,3 +116,31 @@ def test_fp8_block_scaled_and_mxfp4_checkpoints(tmp_path):
     assert got4.shape == (64, 128) and _rel(got4, w4) < 0.15
     again = loader.mxfp4_dequant(*loader.mxfp4_quant(got4))      # representable values survive another encode / decode
     assert torch.equal(again, got4)
+
+
+@pytest.mark.parametrize("wtype", ["Q4_K", "Q8_0"])
+def test_gguf_blocks_are_kept_without_conversion(tmp_path, wtype):
+    """``load_gguf(fmt="ggml")``: Q4_K / Q8_0 matrices stay the file's blocks (only re-ordered into tiles), tensor-parallel shards
+    are cut on block boundaries, and the engine over the kept blocks equals the engine over the decoded matrices."""
+    from gemm_b200.utils import gguf as G
+    cfg = get_config("tiny-dense")
+    src = RandomSource(cfg, seed=4)
+    path = str(tmp_path / "q.gguf")
+    loader.save_gguf(cfg, src, path, wtype)
+    w = loader.load_gguf(path, "ggml", device="cpu")
+    with G.GGUFFile(path) as f:
+        for li, lw in enumerate(w.layers):
+            assert lw.wqkv.is_quant and lw.wo.is_quant and lw.w_gate_up.is_quant and lw.w_down.is_quant
+            file_rows = np.concatenate([np.array(f.tensors[f"blk.{li}.attn_{n}.weight"].raw()) for n in "qkv"])
+            assert np.array_equal(lw.wqkv.q.blocks().reshape(-1).numpy(), file_rows)              # bit for bit the file's blocks
+            down = f.tensors[f"blk.{li}.ffn_down.weight"]
+            assert np.array_equal(lw.w_down.q.blocks().reshape(-1).numpy(), np.array(down.raw()))
+    wf = loader.load_gguf(path, "bf16", device="cpu")
+    toks = torch.randint(0, cfg.vocab, (10,))
+    assert _rel(reference.reference_logits(w, toks), reference.reference_logits(wf, toks)) < 2e-2
+    # two tensor-parallel shards: K ranges of the row-parallel projections fall on 256-column boundaries and add up to the matrix
+    parts = [loader.load_gguf(path, "ggml", device="cpu", tp_rank=r, tp_size=2) for r in range(2)]
+    for li in range(cfg.n_layers):
+        full = w.layers[li].w_down.dequantized()
+        got = torch.cat([p.layers[li].w_down.dequantized() for p in parts], dim=1)
+        assert all(p.layers[li].w_down.k % 256 == 0 for p in parts) and torch.equal(got, full)

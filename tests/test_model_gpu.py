@@ -32,7 +32,8 @@ def _run(model, cfg, toks, lens, bt, page, device, chunks, decode_steps):
 
 
 @pytest.mark.parametrize("name,fmt", [("tiny-dense", "bf16"), ("tiny-moe", "bf16"), ("tiny-qwen2", "bf16"), ("tiny-dense", "mxfp8"),
-                                      ("tiny-moe", "mxfp8"), ("tiny-qwen35", "bf16"), ("tiny-qwen35moe", "bf16"), ("tiny-qwen35", "mxfp8")])
+                                      ("tiny-moe", "mxfp8"), ("tiny-qwen35", "bf16"), ("tiny-qwen35moe", "bf16"), ("tiny-qwen35", "mxfp8"),
+                                      ("tiny-dense", "q8_0"), ("tiny-dense", "q4_k"), ("tiny-qwen2", "q4_k")])
 def test_gpu_engine_matches_cpu_engine_and_oracle(name, fmt):
     torch.manual_seed(0)
     cfg = get_config(name)
