@@ -2,14 +2,14 @@
 //   out[token, n] = sum_k W[n, k] * x[token, k],  five tokens and more (prefill, batched decode).
 //
 // The quantised blocks never become a bf16 matrix in memory.  Per 128-row x 256-column tile of W (one contiguous piece of the
-// tiled layout of ops/ggml_torch.py) a bulk copy brings the raw blocks into shared memory; eight warps unpack them in registers
+// tiled layout of ops/ggml_torch.py) a bulk copy brings the raw blocks into shared memory; sixteen warps unpack them in registers
 // (nibbles -> bf16 pairs with byte permutes, d * sc and dmin * m applied per 32-wide sub-block in packed bf16 arithmetic; int8 ->
 // fp32 -> bf16 for Q8_0) and write the result straight into the 128-byte-swizzled K-major operand tile that tcgen05.mma reads;
 // the tokens come in by TMA; the accumulator lives in TMEM.  Orientation as in the dense GEMM: W is the MMA A operand (128 rows
 // = 128 TMEM lanes), the tokens are N (16 .. 128 per tile).
 //
-// Warp roles of a CTA (448 threads): warp 0 producer (bulk copies of raw tiles, TMA loads of token tiles), warp 1 MMA issuer,
-// warps 2-5 epilogue (TMEM -> registers -> global), warps 6-13 unpack.  Rings: raw tiles (2-4, what shared memory leaves), bf16 operand tiles of 128 x 128
+// Warp roles of a CTA (704 threads): warp 0 producer (bulk copies of raw tiles, TMA loads of token tiles), warp 1 MMA issuer,
+// warps 2-5 epilogue (TMEM -> registers -> global), warps 6-21 unpack (a thread per 32-value sub-block and row).  Rings: raw tiles (2-4, what shared memory leaves), bf16 operand tiles of 128 x 128
 // (2), token tiles (2-3), accumulators (2); all waits are bounded and report into the status word.
 //
 // A raw Q4_K tile is 18 KB for 64 KB of bf16 operand: at decode sizes the kernel is bound by the HBM stream of the quantised
@@ -24,9 +24,9 @@
 
 namespace gb {
 
-constexpr int kQgThreads = 448;
+constexpr int kQgThreads = 704;
 constexpr int kQgUnpackWarp0 = 6;          // first unpack warp
-constexpr int kQgUnpackThreads = 256;
+constexpr int kQgUnpackThreads = 512;   // 16 warps: a thread unpacks one 32-value sub-block of one row
 constexpr int kQgA = 128 * 256;            // bytes of one bf16 operand stage: 2 atoms of [128 rows][64 k]
 
 struct QGemmArgs {
@@ -40,61 +40,47 @@ struct QGemmArgs {
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) { return __byte_perm(a, b, sel); }
 
-// 64 values of one Q4_K chunk (32 bytes of nibbles `qs`, scales a = d * sc and offsets b = dmin * m of its two sub-blocks)
-// -> eight 16-byte chunks of bf16 in the swizzled operand row `dst_row` (row index `row` gives the swizzle phase).
-__device__ __forceinline__ void unpack_q4k_chunk(const uint4 q0, const uint4 q1, float a_lo, float b_lo, float a_hi, float b_hi,
-                                                 uint8_t* dst_row, int row) {
+// One 32-value sub-block of a Q4_K chunk: the low (nib = 0) or high (nib = 1) nibbles of the 32 bytes `q0 q1`, scale a = d * sc
+// and offset b = dmin * m  ->  four 16-byte chunks of bf16 (values 32 * nib + 8c .. + 7, c < 4) in the swizzled operand row.
+__device__ __forceinline__ void unpack_q4k_sub(const uint4 q0, const uint4 q1, int nib, float a, float b, uint8_t* dst_row, int row) {
   const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
   const __nv_bfloat162 sixteen = __float2bfloat162_rn(16.0f);
-  const __nv_bfloat162 al = __float2bfloat162_rn(a_lo), ah = __float2bfloat162_rn(a_hi);
-  const __nv_bfloat162 bl = __float2bfloat162_rn(-b_lo), bh = __float2bfloat162_rn(-b_hi);
+  const __nv_bfloat162 a2 = __float2bfloat162_rn(a), b2 = __float2bfloat162_rn(-b);
+  const int sh = nib ? 1 : 0;
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    uint32_t lo[4], hi[4];
+    uint4 o;
+    uint32_t* po = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       // bf16(16 + q) = 0x4180 | (q << 3): exact for q < 16; the low byte carries 0x80 | q << 3, the high byte is 0x41
       const uint32_t x = w[2 * c + u];
-      const uint32_t l3 = ((x << 3) & 0x78787878u) | 0x80808080u;
-      const uint32_t h3 = ((x >> 1) & 0x78787878u) | 0x80808080u;
-      lo[2 * u] = prmt(l3, 0x41414141u, 0x4140); lo[2 * u + 1] = prmt(l3, 0x41414141u, 0x4342);
-      hi[2 * u] = prmt(h3, 0x41414141u, 0x4140); hi[2 * u + 1] = prmt(h3, 0x41414141u, 0x4342);
+      const uint32_t n3 = ((sh ? (x >> 1) : (x << 3)) & 0x78787878u) | 0x80808080u;
+      uint32_t p0 = prmt(n3, 0x41414141u, 0x4140), p1 = prmt(n3, 0x41414141u, 0x4342);
+      __nv_bfloat162 x0 = *reinterpret_cast<__nv_bfloat162*>(&p0), x1 = *reinterpret_cast<__nv_bfloat162*>(&p1);
+      x0 = __hfma2(__hsub2(x0, sixteen), a2, b2);            // q * a - b, one rounding
+      x1 = __hfma2(__hsub2(x1, sixteen), a2, b2);
+      po[2 * u] = *reinterpret_cast<uint32_t*>(&x0); po[2 * u + 1] = *reinterpret_cast<uint32_t*>(&x1);
     }
-    uint4 ol, oh;
-    uint32_t* pl = reinterpret_cast<uint32_t*>(&ol);
-    uint32_t* ph = reinterpret_cast<uint32_t*>(&oh);
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      __nv_bfloat162 xl = *reinterpret_cast<__nv_bfloat162*>(&lo[u]), xh = *reinterpret_cast<__nv_bfloat162*>(&hi[u]);
-      xl = __hfma2(__hsub2(xl, sixteen), al, bl);            // (q * a - b), one rounding
-      xh = __hfma2(__hsub2(xh, sixteen), ah, bh);
-      pl[u] = *reinterpret_cast<uint32_t*>(&xl); ph[u] = *reinterpret_cast<uint32_t*>(&xh);
-    }
-    *reinterpret_cast<uint4*>(dst_row + ((c ^ (row & 7)) << 4)) = ol;              // values 8c .. 8c+7 (low nibbles)
-    *reinterpret_cast<uint4*>(dst_row + (((4 + c) ^ (row & 7)) << 4)) = oh;        // values 32+8c .. (high nibbles)
+    *reinterpret_cast<uint4*>(dst_row + (((4 * nib + c) ^ (row & 7)) << 4)) = o;
   }
 }
 
-// 64 int8 values (four 16-byte vectors), scales d0 (first 32) and d1 -> eight swizzled 16-byte chunks of bf16.
-__device__ __forceinline__ void unpack_q80_chunk(const uint4* q, float d0, float d1, uint8_t* dst_row, int row) {
+// One Q8_0 block (32 int8 in two 16-byte vectors, scale d) -> four swizzled 16-byte chunks of bf16 (chunk index 4 * nib + c).
+__device__ __forceinline__ void unpack_q80_sub(const uint4 qa, const uint4 qb, int nib, float d, uint8_t* dst_row, int row) {
+  const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
-  for (int v = 0; v < 4; ++v) {
-    const float d = v < 2 ? d0 : d1;
-    const uint32_t w[4] = {q[v].x, q[v].y, q[v].z, q[v].w};
+  for (int c = 0; c < 4; ++c) {
+    uint4 o;
+    uint32_t* po = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint4 o;
-      uint32_t* po = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const uint32_t x = w[2 * half + u];
-        const float f0 = (float)(int)(int8_t)(x & 0xff), f1 = (float)(int)(int8_t)((x >> 8) & 0xff);
-        const float f2 = (float)(int)(int8_t)((x >> 16) & 0xff), f3 = (float)(int)(int8_t)(x >> 24);
-        po[2 * u] = pack_bf16x2(f0 * d, f1 * d); po[2 * u + 1] = pack_bf16x2(f2 * d, f3 * d);
-      }
-      const int c = 2 * v + half;                            // values 8c .. 8c+7
-      *reinterpret_cast<uint4*>(dst_row + ((c ^ (row & 7)) << 4)) = o;
+    for (int u = 0; u < 2; ++u) {
+      const uint32_t x = w[2 * c + u];
+      const float f0 = (float)(int)(int8_t)(x & 0xff), f1 = (float)(int)(int8_t)((x >> 8) & 0xff);
+      const float f2 = (float)(int)(int8_t)((x >> 16) & 0xff), f3 = (float)(int)(int8_t)(x >> 24);
+      po[2 * u] = pack_bf16x2(f0 * d, f1 * d); po[2 * u + 1] = pack_bf16x2(f2 * d, f3 * d);
     }
+    *reinterpret_cast<uint4*>(dst_row + (((4 * nib + c) ^ (row & 7)) << 4)) = o;
   }
 }
 
@@ -128,8 +114,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
   const int n_tiles = args.row_tiles * args.tok_tiles;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) { mbar_init(&a_full[i], 8); mbar_init(&a_empty[i], 1); mbar_init(&accf[i], 1); mbar_init(&acce[i], 4); }
-    for (int i = 0; i < 4; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 8); mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&a_full[i], kQgUnpackThreads / 32); mbar_init(&a_empty[i], 1); mbar_init(&accf[i], 1); mbar_init(&acce[i], 4); }
+    for (int i = 0; i < 4; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], kQgUnpackThreads / 32); mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmX);
@@ -235,9 +221,9 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
       if (++acc == 2) { acc = 0; acc_ph ^= 1; }
     }
   } else {
-    // ------------------------------------------------------------------ unpack (warps 6..13): raw blocks -> swizzled bf16 operand
-    const int ut = threadIdx.x - kQgUnpackWarp0 * 32;     // 0..255
-    const int row = ut >> 1, cpar = ut & 1;               // item: (row, atom cpar) of every operand stage
+    // ------------------------------------------------------------------ unpack (warps 6..21): raw blocks -> swizzled bf16 operand
+    const int ut = threadIdx.x - kQgUnpackWarp0 * 32;     // 0..511
+    const int row = ut >> 2, cpar = (ut >> 1) & 1, nib = ut & 1;       // item: sub-block (2j + nib) of row `row`, atom cpar of every stage
     int rs = 0; uint32_t rph = 0; int as = 0; uint32_t aph = 0;
     bool ok = true;
     for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
@@ -254,23 +240,19 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
             const uint4 q0 = *reinterpret_cast<const uint4*>(b + 16 + 32 * j), q1 = *reinterpret_cast<const uint4*>(b + 32 + 32 * j);
             const __half2 dd = *reinterpret_cast<const __half2*>(&hd.x);
             const float d = __low2float(dd), dmin = __high2float(dd);
-            uint32_t sc0, sc1, mn0, mn1;
-            if (h == 0) {
-              sc0 = (hd.y >> (16 * cpar)) & 63u; sc1 = (hd.y >> (16 * cpar + 8)) & 63u;
-              mn0 = (hd.z >> (16 * cpar)) & 63u; mn1 = (hd.z >> (16 * cpar + 8)) & 63u;
-            } else {
-              const uint32_t x0 = (hd.w >> (16 * cpar)) & 0xffu, x1 = (hd.w >> (16 * cpar + 8)) & 0xffu;
-              const uint32_t y0 = (hd.y >> (16 * cpar)) & 0xffu, y1 = (hd.y >> (16 * cpar + 8)) & 0xffu;
-              const uint32_t z0 = (hd.z >> (16 * cpar)) & 0xffu, z1 = (hd.z >> (16 * cpar + 8)) & 0xffu;
-              sc0 = (x0 & 15u) | ((y0 >> 6) << 4); sc1 = (x1 & 15u) | ((y1 >> 6) << 4);
-              mn0 = (x0 >> 4) | ((z0 >> 6) << 4); mn1 = (x1 >> 4) | ((z1 >> 6) << 4);
+            const int bsh = 16 * cpar + 8 * nib;           // byte (2 * cpar + nib) of the scale words
+            uint32_t sc, mn;
+            if (h == 0) {                                  // sub-blocks 0..3: 6 bits straight from bytes 0..3 / 4..7
+              sc = (hd.y >> bsh) & 63u; mn = (hd.z >> bsh) & 63u;
+            } else {                                       // sub-blocks 4..7: low 4 bits in bytes 8..11, high 2 bits in the top of bytes 0..7
+              const uint32_t x = (hd.w >> bsh) & 0xffu, y = (hd.y >> bsh) & 0xffu, z = (hd.z >> bsh) & 0xffu;
+              sc = (x & 15u) | ((y >> 6) << 4); mn = (x >> 4) | ((z >> 6) << 4);
             }
-            unpack_q4k_chunk(q0, q1, d * (float)sc0, dmin * (float)mn0, d * (float)sc1, dmin * (float)mn1, dst_row, row);
+            unpack_q4k_sub(q0, q1, nib, d * (float)sc, dmin * (float)mn, dst_row, row);
           } else {
-            const uint4* qp = reinterpret_cast<const uint4*>(rb + row * 256 + 64 * j);
-            const uint4 qv[4] = {qp[0], qp[1], qp[2], qp[3]};
-            const __half2 dd = *reinterpret_cast<const __half2*>(rb + 128 * 256 + (row * 8 + 2 * j) * 2);
-            unpack_q80_chunk(qv, __low2float(dd), __high2float(dd), dst_row, row);
+            const uint4* qp = reinterpret_cast<const uint4*>(rb + row * 256 + 64 * j + 32 * nib);
+            const __half dh = *reinterpret_cast<const __half*>(rb + 128 * 256 + (row * 8 + 2 * j + nib) * 2);
+            unpack_q80_sub(qp[0], qp[1], nib, __half2float(dh), dst_row, row);
           }
           fence_proxy_async_smem();                        // this thread's operand bytes -> visible to the tensor core
           __syncwarp();

@@ -13,9 +13,8 @@
 //
 // Work split.  A CTA owns one row tile (128 output features) and a range of the K tiles (split-K: a projection with few rows still
 // fills the GPU; every split writes its fp32 partial into its own slab and the consumer adds the slabs in split order, as the
-// tensor-core GEMM's K-split does).  Warp w takes the 64-value chunk j = w % 4 of every 256-column tile for the row pairs
-// (r, r + 64), r = 32 * (w / 4) + lane: j is uniform in a warp, so the 6-bit scale unpacking is branch-free and the activation
-// words are a shared-memory broadcast.
+// tensor-core GEMM's K-split does).  Inside a tile a lane owns one row and two of its four 64-value chunks; the activation words
+// it needs are the same for all lanes of a half warp (a shared-memory broadcast).
 //
 // With tensor parallelism the result rows can go straight into this rank's slot on every GPU (peer stores) and the last CTA
 // raises the arrival flags: the one-shot all-reduce of a row-parallel projection is the tail of the GEMV, its sum happens in the
@@ -56,9 +55,13 @@ struct QGemvArgs {
 __device__ __forceinline__ int dp4a_s(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
 __device__ __forceinline__ uint32_t byte_of(uint32_t w, int i) { return (w >> (8 * i)) & 0xffu; }
 
-// TYPE: 0 = Q4_K, 1 = Q8_0.  M tokens.  Weight tiles travel through a ring of `stages` shared-memory slots filled by bulk copies
-// (one elected thread issues them, an mbarrier per slot counts the bytes): the bytes in flight per SM are what bounds a
-// memory-bound GEMV, and registers alone cannot hold enough of them.
+// TYPE: 0 = Q4_K, 1 = Q8_0.  M tokens.  Persistent: CTA b walks a contiguous range of the work items (K split, row tile), which are
+// ordered split-major, so its items mostly share their K range and the quantised activations are rebuilt only when the split
+// changes.  Weight tiles travel through a ring of `stages` shared-memory slots filled by bulk copies (one elected thread issues
+// them, an mbarrier per slot counts the bytes) that runs ahead across item boundaries: the bytes in flight per SM are what
+// bounds a memory-bound GEMV, and registers alone cannot hold enough of them.
+// Thread mapping inside a 128 x 256 tile: warp w owns rows 16 w .. 16 w + 15; lane l works on row 16 w + (l & 15) and on the two
+// 64-value chunks 2 (l >> 4) and 2 (l >> 4) + 1, so a row's sum is one shuffle away and an item needs no block-wide step.
 template <int TYPE, int M>
 __global__ void __launch_bounds__(kQvThreads, 2)
 qgemv_kernel(const QGemvArgs a) {
@@ -66,179 +69,181 @@ qgemv_kernel(const QGemvArgs a) {
   uint8_t* qv_smem = (uint8_t*)(((uintptr_t)qv_smem_raw + 127) & ~(uintptr_t)127);
   constexpr int TILE = TYPE == 0 ? kQ4KTileBytes : kQ80TileBytes;
   const int S = a.stages;
-  const int tile_id = blockIdx.x / a.splits, ks = blockIdx.x - tile_id * a.splits;
-  const int kb0 = ks * a.kb_per, kb1 = min(a.num_kb, kb0 + a.kb_per);
-  const int nkb = kb1 - kb0;
+  const int n_items = a.row_tiles * a.splits;
+  const int it0 = (int)((long)blockIdx.x * n_items / gridDim.x), it1 = (int)((long)(blockIdx.x + 1) * n_items / gridDim.x);
   uint8_t* ring = qv_smem;                                                       // [S][TILE]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(ring + (size_t)S * TILE);     // [S]
   uint64_t* empty_bar = full_bar + S;                                            // [S] 8 arrivals (one per warp)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
-  int8_t* aq = reinterpret_cast<int8_t*>(ring + (size_t)S * TILE + 128);         // [nkb][M][256]
-  float* ad = reinterpret_cast<float*>(aq + (size_t)a.kb_per * M * 256);         // [nkb][M][8] block scales
-  float* as = ad + (size_t)a.kb_per * M * 8;                                     // [nkb][M][8] block sums (d8 * sum q8)
+  int8_t* aq = reinterpret_cast<int8_t*>(ring + (size_t)S * TILE + 128);         // [kb_per][M][256]
+  float* ad = reinterpret_cast<float*>(aq + (size_t)a.kb_per * M * 256);         // [kb_per][M][8] block scales
+  float* as = ad + (size_t)a.kb_per * M * 8;                                     // [kb_per][M][8] block sums (d8 * sum q8)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint8_t* wt = a.w + ((size_t)tile_id * a.num_kb + kb0) * TILE;
 
+  // producer cursor (thread 0 only): next tile to request = K tile p_kb of item p_it
+  int p_it = it0, p_kb = 0, p_st = 0;
+  auto item_range = [&](int it, int& tile_id, int& kb0, int& nkb) {
+    const int ks = it / a.row_tiles;
+    tile_id = it - ks * a.row_tiles;
+    kb0 = ks * a.kb_per;
+    nkb = min(a.num_kb, kb0 + a.kb_per) - kb0;
+  };
+  auto issue_next = [&]() {                                  // the slot p_st must be free
+    int tile_id, kb0, nkb;
+    item_range(p_it, tile_id, kb0, nkb);
+    mbar_expect_tx(&full_bar[p_st], TILE);
+    bulk_load(ring + (size_t)p_st * TILE, a.w + ((size_t)tile_id * a.num_kb + kb0 + p_kb) * TILE, TILE, &full_bar[p_st]);
+    if (++p_kb == nkb) { p_kb = 0; ++p_it; }
+    if (++p_st == S) p_st = 0;
+  };
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kQvThreads / 32); }
     *abort_flag = 0;
     fence_barrier_init();
     // weights do not depend on the kernel in front of this one: the first tiles are requested before the dependency wait
-    for (int s = 0; s < S && s < nkb; ++s) { mbar_expect_tx(&full_bar[s], TILE); bulk_load(ring + (size_t)s * TILE, wt + (size_t)s * TILE, TILE, &full_bar[s]); }
+    for (int s = 0; s < S && p_it < it1; ++s) issue_next();
   }
   pdl_wait();
   pdl_trigger();
 
-  // ---- activations of this CTA's K range -> int8 + scale + sum per 32 values (4 lanes x 8 values hold one block)
-  for (int it = threadIdx.x; it < nkb * M * 32; it += kQvThreads) {
-    const int v = it & 31, m = (it >> 5) % M, kbi = (it >> 5) / M;
-    const uint4 raw = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + (size_t)(kb0 + kbi) * 256 + v * 8);
-    const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    float f[8];
-    float amax = 0.f;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float2 t = __bfloat1622float2(hv[u]);
-      f[2 * u] = t.x; f[2 * u + 1] = t.y;
-      amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
-    }
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-    const float d = amax * (1.0f / 127.0f);
-    const float inv = d > 0.f ? 1.0f / d : 0.f;
-    int q[8], qsum = 0;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) { q[u] = max(-127, min(127, __float2int_rn(f[u] * inv))); qsum += q[u]; }
-    qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
-    qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
-    uint2 pk;
-    pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
-    pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
-    *reinterpret_cast<uint2*>(aq + ((size_t)(kbi * M + m) * 256 + v * 8)) = pk;
-    if ((v & 3) == 0) { ad[(kbi * M + m) * 8 + (v >> 2)] = d; as[(kbi * M + m) * 8 + (v >> 2)] = d * (float)qsum; }
-  }
-  __syncthreads();                                         // also publishes the barrier initialisation to every thread
-
-  // ---- main loop: chunk j of every K tile for the rows (rp, rp + 64)
-  const int j = warp & 3, rp = (warp >> 2) * 32 + lane;
-  float acc[2][M];
-#pragma unroll
-  for (int r = 0; r < 2; ++r)
-#pragma unroll
-    for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
-
+  const int row = warp * 16 + (lane & 15), jh = lane >> 4;   // row inside the tile; chunks 2 jh and 2 jh + 1
   int st = 0; uint32_t ph = 0;
+  int cur_ks = -1;
   bool ok = true;
-  for (int kbi = 0; kbi < nkb; ++kbi) {
-    if (!mbar_wait(&full_bar[st], ph, abort_flag, a.status, 1300, st)) { ok = false; break; }
-    const uint8_t* t = ring + (size_t)st * TILE;
-    uint4 chd[2], cqw[2][4];             // per row: header (Q4_K) / scale word in .x (Q8_0), weight words (Q4_K uses 2 vectors, Q8_0 four)
+  for (int it = it0; it < it1; ++it) {       // no early exit: every warp takes the same block-wide steps even after a failed wait
+    int tile_id, kb0, nkb;
+    item_range(it, tile_id, kb0, nkb);
+    const int ks = it / a.row_tiles;
+    if (ks != cur_ks) {
+      // ---- activations of this K range -> int8 + scale + sum per 32 values (4 lanes x 8 values hold one block)
+      cur_ks = ks;
+      __syncthreads();                                       // every warp is done with the old tables (and sees the barrier initialisation)
+      for (int q_it = threadIdx.x; q_it < nkb * M * 32; q_it += kQvThreads) {
+        const int v = q_it & 31, m = (q_it >> 5) % M, kbi = (q_it >> 5) / M;
+        const uint4 raw = *reinterpret_cast<const uint4*>(a.x + (size_t)m * a.ldx + (size_t)(kb0 + kbi) * 256 + v * 8);
+        const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float f[8];
+        float amax = 0.f;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const int row = rp + 64 * r;
+        for (int u = 0; u < 4; ++u) {
+          const float2 t = __bfloat1622float2(hv[u]);
+          f[2 * u] = t.x; f[2 * u + 1] = t.y;
+          amax = fmaxf(amax, fmaxf(fabsf(t.x), fabsf(t.y)));
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float d = amax * (1.0f / 127.0f);
+        const float inv = d > 0.f ? 1.0f / d : 0.f;
+        int q[8], qsum = 0;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) { q[u] = max(-127, min(127, __float2int_rn(f[u] * inv))); qsum += q[u]; }
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+        uint2 pk;
+        pk.x = (uint32_t)(q[0] & 0xff) | ((uint32_t)(q[1] & 0xff) << 8) | ((uint32_t)(q[2] & 0xff) << 16) | ((uint32_t)(q[3] & 0xff) << 24);
+        pk.y = (uint32_t)(q[4] & 0xff) | ((uint32_t)(q[5] & 0xff) << 8) | ((uint32_t)(q[6] & 0xff) << 16) | ((uint32_t)(q[7] & 0xff) << 24);
+        *reinterpret_cast<uint2*>(aq + ((size_t)(kbi * M + m) * 256 + v * 8)) = pk;
+        if ((v & 3) == 0) { ad[(kbi * M + m) * 8 + (v >> 2)] = d; as[(kbi * M + m) * 8 + (v >> 2)] = d * (float)qsum; }
+      }
+      __syncthreads();
+    }
+
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.f;
+    for (int kbi = 0; kbi < nkb; ++kbi) {
+      if (ok && !mbar_wait(&full_bar[st], ph, abort_flag, a.status, 1300, st)) ok = false;
+      ok = __all_sync(0xffffffffu, ok);                      // warp-uniform
+      if (!ok) continue;
+      const uint8_t* t = ring + (size_t)st * TILE;
+      // this lane's bytes of the tile: header + two 32-byte nibble chunks (Q4_K) / four 32-byte blocks + their four scales (Q8_0)
+      uint4 hd, qw[8];
       if (TYPE == 0) {
         const uint8_t* b = t + row * 144;
-        chd[r] = *reinterpret_cast<const uint4*>(b);
-        cqw[r][0] = *reinterpret_cast<const uint4*>(b + 16 + 32 * j);
-        cqw[r][1] = *reinterpret_cast<const uint4*>(b + 32 + 32 * j);
+        hd = *reinterpret_cast<const uint4*>(b);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) qw[u] = *reinterpret_cast<const uint4*>(b + 16 + 64 * jh + 16 * u);
       } else {
-        const uint8_t* b = t + row * 256 + 64 * j;
+        const uint8_t* b = t + row * 256 + 128 * jh;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) cqw[r][u] = *reinterpret_cast<const uint4*>(b + 16 * u);
-        chd[r].x = *reinterpret_cast<const uint32_t*>(t + kQ80ScaleOff + (row * 8 + 2 * j) * 2);
+        for (int u = 0; u < 8; ++u) qw[u] = *reinterpret_cast<const uint4*>(b + 16 * u);
+        const uint2 sc = *reinterpret_cast<const uint2*>(t + kQ80ScaleOff + (row * 8 + 4 * jh) * 2);
+        hd.x = sc.x; hd.y = sc.y;
       }
-    }
-    // the slot's bytes are in registers: hand it back, and let the elected thread refill it with the tile S steps ahead
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[st]);
-    if (threadIdx.x == 0 && kbi + S < nkb) {
-      if (mbar_wait(&empty_bar[st], ph, abort_flag, a.status, 1301, st)) {
-        mbar_expect_tx(&full_bar[st], TILE);
-        bulk_load(ring + (size_t)st * TILE, wt + (size_t)(kbi + S) * TILE, TILE, &full_bar[st]);
-      } else ok = false;
-    }
-    if (++st == S) { st = 0; ph ^= 1; }
-
-    // per row: the two scale factors (and offsets) of this chunk's sub-blocks, and the unpacked words
-    float s_lo[2], s_hi[2], o_lo[2], o_hi[2];
-    uint32_t wlo[2][8], whi[2][8];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      if (TYPE == 0) {
-        const __half2 dd = *reinterpret_cast<const __half2*>(&chd[r].x);
-        const float d = __low2float(dd), dmin = __high2float(dd);
-        const uint32_t s0 = chd[r].y, s1 = chd[r].z, s2 = chd[r].w;
-        uint32_t sc0, sc1, mn0, mn1;
-        if (j < 2) {
-          sc0 = byte_of(s0, 2 * j) & 63u; sc1 = byte_of(s0, 2 * j + 1) & 63u;
-          mn0 = byte_of(s1, 2 * j) & 63u; mn1 = byte_of(s1, 2 * j + 1) & 63u;
+      for (int c = 0; c < 2; ++c) {                          // the two chunks of this lane
+        const int j = 2 * jh + c;
+        float s_lo, s_hi, o_lo = 0.f, o_hi = 0.f;
+        uint32_t wlo[8], whi[8];
+        if (TYPE == 0) {
+          const __half2 dd = *reinterpret_cast<const __half2*>(&hd.x);
+          const float d = __low2float(dd), dmin = __high2float(dd);
+          const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
+          uint32_t sc0, sc1, mn0, mn1;
+          if (jh == 0) {                                     // sub-blocks 0..3: six bits straight from bytes 0..3 / 4..7
+            sc0 = byte_of(s0, 2 * c) & 63u; sc1 = byte_of(s0, 2 * c + 1) & 63u;
+            mn0 = byte_of(s1, 2 * c) & 63u; mn1 = byte_of(s1, 2 * c + 1) & 63u;
+          } else {                                           // sub-blocks 4..7: low 4 bits in bytes 8..11, high 2 bits on top of bytes 0..7
+            sc0 = (byte_of(s2, 2 * c) & 15u) | ((byte_of(s0, 2 * c) >> 6) << 4); sc1 = (byte_of(s2, 2 * c + 1) & 15u) | ((byte_of(s0, 2 * c + 1) >> 6) << 4);
+            mn0 = (byte_of(s2, 2 * c) >> 4) | ((byte_of(s1, 2 * c) >> 6) << 4); mn1 = (byte_of(s2, 2 * c + 1) >> 4) | ((byte_of(s1, 2 * c + 1) >> 6) << 4);
+          }
+          s_lo = d * (float)sc0; s_hi = d * (float)sc1; o_lo = dmin * (float)mn0; o_hi = dmin * (float)mn1;
+          const uint32_t* qq = reinterpret_cast<const uint32_t*>(&qw[2 * c]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { wlo[i] = qq[i] & 0x0f0f0f0fu; whi[i] = (qq[i] >> 4) & 0x0f0f0f0fu; }
         } else {
-          const int b0 = 2 * j - 4, b1 = 2 * j - 3;
-          sc0 = (byte_of(s2, b0) & 15u) | ((byte_of(s0, b0) >> 6) << 4); sc1 = (byte_of(s2, b1) & 15u) | ((byte_of(s0, b1) >> 6) << 4);
-          mn0 = (byte_of(s2, b0) >> 4) | ((byte_of(s1, b0) >> 6) << 4); mn1 = (byte_of(s2, b1) >> 4) | ((byte_of(s1, b1) >> 6) << 4);
+          const uint32_t sw = c == 0 ? hd.x : hd.y;
+          const __half2 dd = *reinterpret_cast<const __half2*>(&sw);
+          s_lo = __low2float(dd); s_hi = __high2float(dd);
+          const uint32_t* qq = reinterpret_cast<const uint32_t*>(&qw[4 * c]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) { wlo[i] = qq[i]; whi[i] = qq[8 + i]; }
         }
-        s_lo[r] = d * (float)sc0; s_hi[r] = d * (float)sc1; o_lo[r] = dmin * (float)mn0; o_hi[r] = dmin * (float)mn1;
-        const uint32_t* qq = reinterpret_cast<const uint32_t*>(&cqw[r][0]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { wlo[r][i] = qq[i] & 0x0f0f0f0fu; whi[r][i] = (qq[i] >> 4) & 0x0f0f0f0fu; }
-      } else {
-        const __half2 dd = *reinterpret_cast<const __half2*>(&chd[r].x);
-        s_lo[r] = __low2float(dd); s_hi[r] = __high2float(dd); o_lo[r] = 0.f; o_hi[r] = 0.f;
-        const uint32_t* qq = reinterpret_cast<const uint32_t*>(&cqw[r][0]);
+        for (int m = 0; m < M; ++m) {
+          const uint4* ap = reinterpret_cast<const uint4*>(aq + ((size_t)(kbi * M + m) * 256 + 64 * j));
+          const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+          const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+          const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+          const float d_lo = ad[(kbi * M + m) * 8 + 2 * j], d_hi = ad[(kbi * M + m) * 8 + 2 * j + 1];
+          int sl = 0, sh = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) { wlo[r][i] = qq[i]; whi[r][i] = qq[8 + i]; }
+          for (int i = 0; i < 8; ++i) { sl = dp4a_s(wlo[i], al[i], sl); sh = dp4a_s(whi[i], ah[i], sh); }
+          float v = s_lo * d_lo * (float)sl + s_hi * d_hi * (float)sh;
+          if (TYPE == 0) v -= o_lo * as[(kbi * M + m) * 8 + 2 * j] + o_hi * as[(kbi * M + m) * 8 + 2 * j + 1];
+          acc[m] += v;
+        }
       }
+      // Every word loaded from the slot has now been an operand of a dp4a, i.e. the shared-memory reads of this lane have returned.
+      // (A release issued right behind the load instructions let the refill land under reads still in flight: seen as wrong
+      // sums in a few lanes.)  Hand the slot back, and let the elected thread refill it with the next tile of the stream.
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[st]);
+      if (threadIdx.x == 0 && p_it < it1) {
+        if (mbar_wait(&empty_bar[st], ph, abort_flag, a.status, 1301, st)) issue_next();
+        else ok = false;
+      }
+      if (++st == S) { st = 0; ph ^= 1; }
     }
+    if (!ok) continue;
+
+    // ---- a row's two half sums meet in lanes l and l + 16; lanes 0..15 store 16 consecutive output features
+    const size_t slab = (size_t)ks * (size_t)a.partial_stride;
+    const int n = tile_id * 128 + row;
 #pragma unroll
     for (int m = 0; m < M; ++m) {
-      const uint4* ap = reinterpret_cast<const uint4*>(aq + ((size_t)(kbi * M + m) * 256 + 64 * j));
-      const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
-      const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-      const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
-      const float d_lo = ad[(kbi * M + m) * 8 + 2 * j], d_hi = ad[(kbi * M + m) * 8 + 2 * j + 1];
-      const float t_lo = as[(kbi * M + m) * 8 + 2 * j], t_hi = as[(kbi * M + m) * 8 + 2 * j + 1];
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        int sl = 0, sh = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) { sl = dp4a_s(wlo[r][i], al[i], sl); sh = dp4a_s(whi[r][i], ah[i], sh); }
-        float v = s_lo[r] * d_lo * (float)sl + s_hi[r] * d_hi * (float)sh;
-        if (TYPE == 0) v -= o_lo[r] * t_lo + o_hi[r] * t_hi;
-        acc[r][m] += v;
-      }
-    }
-  }
-  (void)ok;
-  if (*abort_flag) {                                       // a wait gave up: copies may still be landing, bounded grace period
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
-  }
-
-  // ---- the four chunk warps of a row group add up, one of them stores
-  __syncthreads();                                        // the activation tables are dead: reuse them (the ring may still receive nothing: every issued tile was consumed)
-  float* red = reinterpret_cast<float*>(aq);               // [8 warps][2 * M][32 lanes]
-#pragma unroll
-  for (int r = 0; r < 2; ++r)
-#pragma unroll
-    for (int m = 0; m < M; ++m) red[(warp * 2 * M + r * M + m) * 32 + lane] = acc[r][m];
-  __syncthreads();
-  if (j == 0) {
-    const size_t slab = (size_t)ks * (size_t)a.partial_stride;
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const int n = tile_id * 128 + rp + 64 * r;
-      if (n >= a.n_out) continue;
-      const float bias = (a.bias != nullptr && ks == 0) ? a.bias[n] : 0.f;
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        float v = bias;
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) v += red[((warp + jj) * 2 * M + r * M + m) * 32 + lane];     // chunks in fixed order
+      float v = acc[m] + __shfl_xor_sync(0xffffffffu, acc[m], 16);
+      if (jh == 0 && n < a.n_out) {
+        if (a.bias != nullptr && ks == 0) v += a.bias[n];
         const size_t off = slab + (size_t)m * a.ldo + n;
         if (a.peer_bcast > 0) { for (int p = 0; p < a.peer_bcast; ++p) reinterpret_cast<float*>(a.peer_out[p])[off] = v; }
         else a.out[off] = v;
       }
     }
+  }
+  if (*abort_flag) {                                       // copies may still be landing: bounded grace period
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
   if (a.signal_n > 0) {
     __syncthreads();
@@ -317,11 +322,10 @@ GB_API int gb_qgemv(const void* w, int ggml_type, const void* x, int ldx, float*
     a.epoch_self_tick = peer->epoch_self_tick;
   }
   a.stages = qgemv_stages(ggml_type); a.status = (KernelStatus*)status;
-  size_t act = (size_t)kb_per * m * (256 + 64);
-  const size_t red = (size_t)8 * 2 * m * 32 * 4;
-  if (act < red) act = red;                                // the reduction scratch overlays the activation tables
+  const size_t act = (size_t)kb_per * m * (256 + 64);
   const size_t smem = 128 + (size_t)a.stages * qgemv_tile_bytes(ggml_type) + 128 + act;
-  const int grid = a.row_tiles * splits;
+  int grid = a.row_tiles * splits;
+  if (grid > 2 * sm_count()) grid = 2 * sm_count();        // persistent: two CTAs per SM walk the items
   const int t = ggml_type == 12 ? 0 : 1;
 #define GB_QV(TV, MV)                                                                                              \
   {                                                                                                                 \

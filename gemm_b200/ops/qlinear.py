@@ -82,12 +82,23 @@ def _stream():
 
 
 def pick_splits(rows: int, k: int, m: int, ggml_type: int = gt.Q4_K, sms: int = 148) -> int:
-    """K splits of a decode-sized GEMV: enough CTAs for two per SM, at least two K tiles per split, and a K range whose quantised
-    activations fit shared memory."""
+    """K splits of a decode-sized GEMV.  The kernel is persistent (two CTAs per SM walk the (row tile, split) items in a fixed
+    stride), so the split count is the one that spreads the items most evenly over the CTAs, with at least two K tiles per item
+    and a K range whose quantised activations fit shared memory; ties go to fewer splits (fewer partial slabs)."""
     tiles = (rows + 127) // 128
     num_kb = k // 256
-    want = max(1, min(num_kb // 2 if num_kb >= 2 else 1, -(-2 * sms // tiles)))
-    sp = _native.cuda().gb_qgemv_splits(_i(ggml_type), _i(k), _i(m), _i(want))
+    ctas = 2 * sms
+    best, best_eff = 1, -1.0
+    for sp in range(1, max(1, num_kb // 2) + 1):
+        per = -(-num_kb // sp)
+        if -(-num_kb // per) != sp:
+            continue
+        items = tiles * sp
+        g = min(items, ctas)
+        eff = items / (g * -(-items // g)) * min(1.0, items / ctas)
+        if eff > best_eff + 0.02:
+            best, best_eff = sp, eff
+    sp = _native.cuda().gb_qgemv_splits(_i(ggml_type), _i(k), _i(m), _i(best))
     return max(1, sp)
 
 

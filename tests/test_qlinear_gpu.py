@@ -25,7 +25,8 @@ def _case(t, rows, k, m, seed=0):
 
 @pytest.mark.parametrize("t", [gt.Q4_K, gt.Q8_0])
 @pytest.mark.parametrize("rows,k,m,splits", [(256, 512, 1, 1), (384, 1024, 3, 2), (5120, 5120, 1, None), (1280, 5120, 4, None),
-                                             (200, 768, 2, 3), (5120, 3328, 2, None)])
+                                             (200, 768, 2, 3), (5120, 3328, 2, None), (2560, 5120, 3, 1), (1280, 5120, 2, 2),
+                                             (51200, 1024, 1, None)])      # the last three: K ranges longer than the tile ring (slots are refilled), many items per CTA
 def test_gemv_matches_fp32_reference(t, rows, k, m, splits):
     qw, x, ref = _case(t, rows, k, m, seed=rows + m)
     p = qlinear.gemv_partials(x, qw, splits=splits)
