@@ -36,7 +36,8 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"],
+                    help="ours = this framework; reference = the unmodified reference code; baseline = plain PyTorch + NCCL (baseline/torch_nccl.py)")
     ap.add_argument("--model", default="qwen3-30b-a3b")
     ap.add_argument("--fmt", default="mxfp8", choices=["mxfp8", "bf16", "q4_k", "q8_0"],
                     help="weight format; q4_k / q8_0 keep ggml blocks in HBM (fused dequant-GEMV / GEMM)")
@@ -153,10 +154,120 @@ def reference_arm(args):
     return 0
 
 
+def baseline_table():
+    """Measured decode tokens/s of the plain PyTorch + NCCL baseline (``bench.py --impl baseline``), keyed by
+    ``model|batch|prompt_len|n_gpus``; the file is written from runs on the same kind of box and sits beside the baseline code."""
+    try:
+        with open(os.path.join(ROOT, "baseline", "measured.json")) as f:
+            return json.load(f)
+    except Exception:
+        return {}
+
+
+def baseline_arm(args):
+    """The same metric and config through baseline/torch_nccl.py: torch.matmul / bmm, SDPA, NCCL collectives, a CUDA graph for
+    the decode step.  bf16 weights (PyTorch has no block-scaled fp8 grouped GEMM to call)."""
+    import torch
+    import torch.distributed as dist
+    from baseline.torch_nccl import BaselineModel
+    from gemm_b200.models.config import get_config
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    cfg = get_config(args.model)
+    layout = "single"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        layout = args.parallel if args.parallel != "auto" else ("ep" if cfg.n_experts > 0 else "tp")
+    n_layers = args.layers if args.layers > 0 else cfg.n_layers
+    tp = layout == "tp"
+    b_local = args.batch if (tp or world == 1) else args.batch // world
+    model = BaselineModel(cfg, device, seed=0, n_layers=n_layers, group=dist.group.WORLD if world > 1 else None, layout=layout)
+    total_new = args.warmup + args.steps + 8
+    model.alloc_kv(b_local, args.prompt_len + total_new)
+    g = torch.Generator().manual_seed(0)
+    all_prompts = torch.randint(0, cfg.vocab, (args.batch, args.prompt_len), generator=g, dtype=torch.int32)
+    prompts = all_prompts[(0 if (tp or world == 1) else rank * b_local): (0 if (tp or world == 1) else rank * b_local) + b_local]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    model.prefill(prompts[:1, :256])                      # lazy initialisation outside the timed region
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    first = model.prefill(prompts).argmax(-1)
+    e1.record()
+    barrier()
+    prefill_ms = max_over_ranks(e0.elapsed_time(e1))
+    model.begin_decode(first, use_graph=True)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(args.warmup):
+        model.decode_step()
+    barrier()
+    sampler.mark()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        model.decode_step()
+    b.record()
+    barrier()
+    total_ms = max_over_ranks(a.elapsed_time(b))
+    clocks = sampler.stop()
+    # end to end: the step's ids come from pinned host memory, the result goes back to the host
+    ids_host = torch.empty(b_local, dtype=model._ids.dtype).pin_memory()
+    out_host = torch.empty(b_local, dtype=model._ids.dtype).pin_memory()
+    ids_host.copy_(model._ids.cpu())
+    barrier()
+    w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0.record()
+    for _ in range(args.steps):
+        model._ids.copy_(ids_host, non_blocking=True)
+        out_host.copy_(model.decode_step(), non_blocking=True)
+        torch.cuda.synchronize()
+        ids_host.copy_(out_host)
+    w1.record()
+    barrier()
+    e2e_ms = max_over_ranks(w0.elapsed_time(w1))
+    if rank == 0:
+        esz = ids_host.element_size()
+        line = {"impl": "baseline", "metric": "decode_tokens_per_s", "value": args.batch * args.steps / (total_ms / 1e3), "unit": "tokens/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (torch.matmul / bmm, SDPA, NCCL)",
+                "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
+                "config": {"model": args.model, "global_batch": args.batch, "seq_len": args.prompt_len, "parallelism": f"{layout}{world}" if world > 1 else "single",
+                           "layers": n_layers, "l2": "no flush: every step streams all weights and the KV cache, far more than the 126 MB L2"},
+                "prefill_tokens_per_s": args.batch * args.prompt_len / (prefill_ms / 1e3), "ttft_ms_p50": prefill_ms, "clocks": clocks,
+                "e2e": {"value": args.batch * args.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": b_local * esz * world,
+                        "d2h_bytes_per_step": b_local * esz * world, "ms_per_step": e2e_ms / args.steps},
+                "gpu_launches": 0}
+        if n_layers != cfg.n_layers:
+            line["invalid"] = f"debug run with {n_layers} of {cfg.n_layers} layers"
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "baseline":
+        return baseline_arm(args)
 
     import torch
     import torch.distributed as dist
@@ -305,10 +416,13 @@ def main():
                "d2h_bytes_per_step": b_local * 4 * n_gpus, "ms_per_step": e2e_ms / args.steps}
 
     if rank == 0:
+        # the comparison number: the plain PyTorch + NCCL implementation of the same config on the same number of GPUs
+        base_val = baseline_table().get(f"{args.model}|{args.batch}|{args.prompt_len}|{n_gpus}")
+        vs_base = (decode_tok_s / base_val) if (base_val and n_layers == cfg.n_layers) else None
         line = {
             "metric": "decode_tokens_per_s", "value": decode_tok_s, "unit": "tokens/s", "n_gpus": n_gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": {"mxfp8": "mxfp8 weights+activations, bf16 outputs, fp32 accumulate", "bf16": "bf16",
+            "vs_baseline": vs_base, "baseline_tokens_per_s": base_val, "dtype": {"mxfp8": "mxfp8 weights+activations, bf16 outputs, fp32 accumulate", "bf16": "bf16",
                                           "q4_k": "ggml Q4_K weights (kept quantised), bf16 activations / int8 in the GEMV, fp32 accumulate",
                                           "q8_0": "ggml Q8_0 weights (kept quantised), bf16 activations / int8 in the GEMV, fp32 accumulate"}[args.fmt],
             "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",

@@ -268,6 +268,9 @@ def main(argv=None):
     es = sub.add_parser("estimate", help="roofline estimate")
     es.add_argument("rest", nargs=argparse.REMAINDER)
     es.set_defaults(fn=lambda a: __import__("gemm_b200.utils.estimate", fromlist=["main"]).main(a.rest))
+    cb = sub.add_parser("cpubench", help="native CPU engine against the reference CPU engine (Qwen3-0.6B shape, Q8_0)")
+    cb.add_argument("rest", nargs=argparse.REMAINDER)
+    cb.set_defaults(fn=lambda a: __import__("gemm_b200.utils.cpubench", fromlist=["main"]).main(a.rest))
     cp = sub.add_parser("compare", help="CPU path against GPU kernels, token by token")
     cp.add_argument("--model", required=True, help="GGUF file, HF safetensors directory, or synthetic:<preset>")
     cp.add_argument("--format", default="bf16", choices=["bf16", "mxfp8"])

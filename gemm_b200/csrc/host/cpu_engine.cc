@@ -1,0 +1,499 @@
+// Native CPU engine for dense Qwen2 / Qwen3 checkpoints in GGUF: the model runs straight from the file's (memory-mapped) ggml
+// blocks, single process, a pool of worker threads.  It is the counterpart of the reference's CPU engine
+// (common/transformer.h: transformer_load :1598, transformer_forward_pos :3499-3548, layer loop :3550-4174, Q8_0 dot
+// tf_qmatvec_worker :648-738, sampler :5415-5467) for the configuration that has no GPU in it: Qwen3-0.6B, Q8_0, batch 1.
+//
+// Numerics follow the reference's fp32 path so that greedy decoding picks the same tokens: fp32 activations, weights decoded
+// block by block (Q8_0: d * q), RMSNorm x * rsqrt(mean(x^2) + eps) * w, per-head QK-RMSNorm, NeoX RoPE with
+// inv_freq[j] = theta^(-2j / d), fp32 softmax, SiLU(gate) * up, arg-max with ties to the lower id.
+//
+// What differs is the schedule.  The reference prefills a prompt as n sequential single-token forwards, i.e. it streams every
+// weight n times; here the prompt is one batched pass: every weight row is decoded once into registers / L1 and multiplied with
+// all prompt tokens, attention is causal over the batch, and only the last token goes through the LM head.  Decode steps are
+// GEMVs over the raw blocks (AVX2: int8 -> fp32 in registers, FMA against the activations) split over the threads by rows.
+#include "common.h"
+#include "ggml_types.h"
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <algorithm>
+#include <chrono>
+#include <string>
+#include <vector>
+#if defined(__AVX2__)
+#include <immintrin.h>
+#endif
+#include <atomic>
+#include <condition_variable>
+#include <functional>
+#include <mutex>
+#include <thread>
+
+extern "C" {
+void* gbh_gguf_open(const char* path);
+void gbh_gguf_close(void* h);
+int gbh_gguf_find_tensor(void* h, const char* name);
+int gbh_gguf_tensor_info(void* h, int i, char* name, int name_cap, int* n_dims, uint64_t* dims4, int* type, uint64_t* nbytes);
+const void* gbh_gguf_tensor_data(void* h, int i);
+int gbh_gguf_find_key(void* h, const char* key);
+int gbh_gguf_kv_scalar(void* h, int i, double* out);
+const char* gbh_gguf_kv_string(void* h, int i, long j, uint64_t* len);
+}
+
+namespace gbh {
+
+int dequant_row(int type, const void* src, float* dst, long n);
+
+namespace {
+
+// Persistent workers: run(n, fn) calls fn(begin, end) on contiguous slices of [0, n), one per thread (the caller takes a slice too),
+// and returns when all are done.  Workers spin for a short while between jobs (a decode step issues hundreds of small jobs), then
+// sleep on a condition variable.  Counterpart of the reference's thread pool (common/transformer.h:2259-2344).
+inline void cpu_relax() {
+#if defined(__x86_64__)
+  __builtin_ia32_pause();
+#endif
+}
+
+class Pool {
+ public:
+  explicit Pool(int n) : n_(std::max(1, n)) {
+    for (int i = 1; i < n_; ++i) workers_.emplace_back([this, i] { loop(i); });
+  }
+  ~Pool() {
+    { std::lock_guard<std::mutex> g(mu_); stop_ = true; ++gen_; }
+    cv_.notify_all();
+    for (auto& t : workers_) t.join();
+  }
+  int size() const { return n_; }
+  void run(int n, const std::function<void(int, int)>& fn) {
+    if (n_ == 1 || n <= 1) { fn(0, n); return; }
+    { std::lock_guard<std::mutex> g(mu_); fn_ = &fn; total_ = n; pending_.store(n_ - 1); ++gen_; }
+    cv_.notify_all();
+    slice(0);
+    while (pending_.load(std::memory_order_acquire) != 0) cpu_relax();       // the slices are equal, the others finish about now
+  }
+ private:
+  void slice(int i) {
+    const int b = (int)((long)total_ * i / n_), e = (int)((long)total_ * (i + 1) / n_);
+    if (e > b) (*fn_)(b, e);
+  }
+  void loop(int i) {
+    unsigned long seen = 0;
+    for (;;) {
+      // a decode step issues a job every few tens of microseconds: keep spinning for about a millisecond before going to sleep
+      for (int spin = 0; spin < 60000 && gen_.load(std::memory_order_acquire) == seen; ++spin) cpu_relax();
+      if (gen_.load(std::memory_order_acquire) == seen) {
+        std::unique_lock<std::mutex> lk(mu_);
+        cv_.wait(lk, [&] { return gen_.load() != seen; });
+      }
+      seen = gen_.load(std::memory_order_acquire);
+      if (stop_) return;
+      slice(i);
+      pending_.fetch_sub(1, std::memory_order_release);
+    }
+  }
+  int n_;
+  std::vector<std::thread> workers_;
+  std::mutex mu_;
+  std::condition_variable cv_;
+  std::atomic<unsigned long> gen_{0};
+  std::atomic<int> pending_{0};
+  const std::function<void(int, int)>* fn_ = nullptr;
+  int total_ = 0;
+  bool stop_ = false;
+};
+
+struct QMat {                      // a [rows, k] matrix as it sits in the file
+  const uint8_t* data = nullptr;
+  int type = 0, rows = 0, k = 0;
+  long row_bytes = 0;
+};
+
+struct Layer {
+  std::vector<float> attn_norm, ffn_norm, q_norm, k_norm, bq, bk, bv;
+  QMat wq, wk, wv, wo, wgate, wup, wdown;
+};
+
+struct CpuEngine {
+  void* gguf = nullptr;
+  int n_layers = 0, hidden = 0, n_heads = 0, n_kv = 0, head_dim = 0, ffn = 0, vocab = 0, max_seq = 0, threads = 1;
+  float eps = 1e-6f, theta = 1e6f;
+  bool qk_norm = false, has_bias = false;
+  std::vector<Layer> layers;
+  std::vector<float> final_norm, inv_freq;
+  QMat embed, head;
+  std::vector<float> kc, vc;       // [layer][pos][n_kv * head_dim]
+  double t_prefill = 0, t_decode = 0;
+  Pool* pool = nullptr;
+  ~CpuEngine() { delete pool; }
+};
+
+float dot_f32(const float* a, const float* b, int n) {
+#if defined(__AVX2__)
+  __m256 s0 = _mm256_setzero_ps(), s1 = _mm256_setzero_ps();
+  int i = 0;
+  for (; i + 16 <= n; i += 16) {
+    s0 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i), _mm256_loadu_ps(b + i), s0);
+    s1 = _mm256_fmadd_ps(_mm256_loadu_ps(a + i + 8), _mm256_loadu_ps(b + i + 8), s1);
+  }
+  s0 = _mm256_add_ps(s0, s1);
+  __m128 lo = _mm_add_ps(_mm256_castps256_ps128(s0), _mm256_extractf128_ps(s0, 1));
+  lo = _mm_add_ps(lo, _mm_movehl_ps(lo, lo));
+  lo = _mm_add_ss(lo, _mm_shuffle_ps(lo, lo, 1));
+  float s = _mm_cvtss_f32(lo);
+  for (; i < n; ++i) s += a[i] * b[i];
+  return s;
+#else
+  float s = 0.f;
+  for (int i = 0; i < n; ++i) s += a[i] * b[i];
+  return s;
+#endif
+}
+
+// Four rows against one vector: every load of x feeds four FMA chains (the batched prefill is bound by re-reading the tokens).
+void dot4_f32(const float* r0, const float* r1, const float* r2, const float* r3, const float* x, int n, float* out) {
+#if defined(__AVX2__)
+  __m256 a0 = _mm256_setzero_ps(), a1 = a0, a2 = a0, a3 = a0;
+  int i = 0;
+  for (; i + 8 <= n; i += 8) {
+    const __m256 xv = _mm256_loadu_ps(x + i);
+    a0 = _mm256_fmadd_ps(_mm256_loadu_ps(r0 + i), xv, a0);
+    a1 = _mm256_fmadd_ps(_mm256_loadu_ps(r1 + i), xv, a1);
+    a2 = _mm256_fmadd_ps(_mm256_loadu_ps(r2 + i), xv, a2);
+    a3 = _mm256_fmadd_ps(_mm256_loadu_ps(r3 + i), xv, a3);
+  }
+  const __m256 acc[4] = {a0, a1, a2, a3};
+  const float* rows[4] = {r0, r1, r2, r3};
+  for (int r = 0; r < 4; ++r) {
+    __m128 lo = _mm_add_ps(_mm256_castps256_ps128(acc[r]), _mm256_extractf128_ps(acc[r], 1));
+    lo = _mm_add_ps(lo, _mm_movehl_ps(lo, lo));
+    lo = _mm_add_ss(lo, _mm_shuffle_ps(lo, lo, 1));
+    float s = _mm_cvtss_f32(lo);
+    for (int k2 = i; k2 < n; ++k2) s += rows[r][k2] * x[k2];
+    out[r] = s;
+  }
+#else
+  out[0] = dot_f32(r0, x, n); out[1] = dot_f32(r1, x, n); out[2] = dot_f32(r2, x, n); out[3] = dot_f32(r3, x, n);
+#endif
+}
+
+// One row of a Q8_0 matrix times an fp32 vector: per 32-block  d * sum(q * x).  Two blocks per iteration (independent FMA
+// chains), the fp16 scales converted by the F16C unit.
+float dot_q8_0(const uint8_t* row, const float* x, int k) {
+  float total = 0.f;
+  const int nb = k / 32;
+#if defined(__AVX2__) && defined(__F16C__)
+  __m256 acc0 = _mm256_setzero_ps(), acc1 = _mm256_setzero_ps();
+  auto block = [&](const uint8_t* blk, const float* xb, __m256& acc) {
+    uint16_t dh; memcpy(&dh, blk, 2);
+    const __m256 d = _mm256_set1_ps(_cvtsh_ss(dh));
+    __m256 s0 = _mm256_mul_ps(_mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(_mm_loadl_epi64((const __m128i*)(blk + 2)))), _mm256_loadu_ps(xb));
+    __m256 s1 = _mm256_mul_ps(_mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(_mm_loadl_epi64((const __m128i*)(blk + 10)))), _mm256_loadu_ps(xb + 8));
+    s0 = _mm256_fmadd_ps(_mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(_mm_loadl_epi64((const __m128i*)(blk + 18)))), _mm256_loadu_ps(xb + 16), s0);
+    s1 = _mm256_fmadd_ps(_mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(_mm_loadl_epi64((const __m128i*)(blk + 26)))), _mm256_loadu_ps(xb + 24), s1);
+    acc = _mm256_fmadd_ps(d, _mm256_add_ps(s0, s1), acc);
+  };
+  int b = 0;
+  for (; b + 2 <= nb; b += 2) {
+    block(row + (size_t)b * 34, x + b * 32, acc0);
+    block(row + (size_t)(b + 1) * 34, x + (b + 1) * 32, acc1);
+  }
+  if (b < nb) block(row + (size_t)b * 34, x + b * 32, acc0);
+  acc0 = _mm256_add_ps(acc0, acc1);
+  __m128 lo = _mm_add_ps(_mm256_castps256_ps128(acc0), _mm256_extractf128_ps(acc0, 1));
+  lo = _mm_add_ps(lo, _mm_movehl_ps(lo, lo));
+  lo = _mm_add_ss(lo, _mm_shuffle_ps(lo, lo, 1));
+  total = _mm_cvtss_f32(lo);
+#else
+  for (int b = 0; b < nb; ++b) {
+    const uint8_t* blk = row + (size_t)b * 34;
+    uint16_t dh; memcpy(&dh, blk, 2);
+    float s = 0.f;
+    for (int j = 0; j < 32; ++j) s += (float)(int8_t)blk[2 + j] * x[b * 32 + j];
+    total += fp16_to_f32(dh) * s;
+  }
+#endif
+  return total;
+}
+
+// y[t, n] = sum_k W[n, k] x[t, k] for t < T.  Rows are split over the threads; a row is decoded once (into `scratch`, one slice
+// per thread) when there are several tokens or its type has no direct kernel, and streamed straight from its blocks otherwise.
+void matmul(const CpuEngine& e, const QMat& w, const float* x, int ldx, int T, float* y, int ldy, const float* bias = nullptr) {
+  e.pool->run(w.rows, [&](int n0, int n1) {
+    std::vector<float> row((size_t)w.k * 4);
+    int n = n0;
+    if (T > 1)
+      for (; n + 4 <= n1; n += 4) {                          // four decoded rows share every token load
+        for (int r = 0; r < 4; ++r) dequant_row(w.type, w.data + (size_t)(n + r) * w.row_bytes, row.data() + (size_t)r * w.k, w.k);
+        for (int t = 0; t < T; ++t) {
+          float o4[4];
+          dot4_f32(row.data(), row.data() + w.k, row.data() + 2 * (size_t)w.k, row.data() + 3 * (size_t)w.k, x + (size_t)t * ldx, w.k, o4);
+          for (int r = 0; r < 4; ++r) y[(size_t)t * ldy + n + r] = o4[r] + (bias ? bias[n + r] : 0.f);
+        }
+      }
+    for (; n < n1; ++n) {
+      const uint8_t* src = w.data + (size_t)n * w.row_bytes;
+      const float b = bias ? bias[n] : 0.f;
+      if (T == 1 && w.type == T_Q8_0) { y[n] = dot_q8_0(src, x, w.k) + b; continue; }
+      dequant_row(w.type, src, row.data(), w.k);
+      for (int t = 0; t < T; ++t) y[(size_t)t * ldy + n] = dot_f32(row.data(), x + (size_t)t * ldx, w.k) + b;
+    }
+  });
+}
+
+void rmsnorm(const float* x, const float* w, float* y, int n, float eps) {
+  float ss = 0.f;
+  for (int i = 0; i < n; ++i) ss += x[i] * x[i];
+  const float s = 1.0f / sqrtf(ss / (float)n + eps);
+  for (int i = 0; i < n; ++i) y[i] = x[i] * s * w[i];
+}
+
+void rope_neox(float* v, int d, int pos, const float* inv_freq) {
+  const int half = d / 2;
+  for (int j = 0; j < half; ++j) {
+    const float a = (float)pos * inv_freq[j], c = cosf(a), s = sinf(a);
+    const float x0 = v[j], x1 = v[j + half];
+    v[j] = x0 * c - x1 * s;
+    v[j + half] = x0 * s + x1 * c;
+  }
+}
+
+int get_mat(void* g, const std::string& name, QMat* m, int want_rows, int want_k) {
+  const int i = gbh_gguf_find_tensor(g, name.c_str());
+  if (i < 0) return fail("cpu engine: tensor %s is missing", name.c_str());
+  int nd, type; uint64_t dims[4], nbytes; char nm[8];
+  gbh_gguf_tensor_info(g, i, nm, 8, &nd, dims, &type, &nbytes);
+  if (nd != 2 || (int)dims[0] != want_k || (int)dims[1] != want_rows)
+    return fail("cpu engine: %s has shape [%d, %d], wanted [%d, %d]", name.c_str(), (int)dims[1], (int)dims[0], want_rows, want_k);
+  const TypeInfo* ti = type_info(type);
+  if (ti == nullptr || want_k % ti->block) return fail("cpu engine: %s: unsupported tensor type %d", name.c_str(), type);
+  m->data = (const uint8_t*)gbh_gguf_tensor_data(g, i); m->type = type; m->rows = want_rows; m->k = want_k;
+  m->row_bytes = (long)(want_k / ti->block) * ti->bytes;
+  return 0;
+}
+
+int get_vec(void* g, const std::string& name, std::vector<float>* v, int n, bool optional = false) {
+  const int i = gbh_gguf_find_tensor(g, name.c_str());
+  if (i < 0) return optional ? 1 : fail("cpu engine: tensor %s is missing", name.c_str());
+  int nd, type; uint64_t dims[4], nbytes; char nm[8];
+  gbh_gguf_tensor_info(g, i, nm, 8, &nd, dims, &type, &nbytes);
+  if ((int)dims[0] != n) return fail("cpu engine: %s has %d elements, wanted %d", name.c_str(), (int)dims[0], n);
+  v->resize((size_t)n);
+  return dequant_row(type, gbh_gguf_tensor_data(g, i), v->data(), n);
+}
+
+double kv_num(void* g, const std::string& key, double dflt) {
+  const int i = gbh_gguf_find_key(g, key.c_str());
+  double v = dflt;
+  if (i >= 0) gbh_gguf_kv_scalar(g, i, &v);
+  return v;
+}
+
+// Layers + final norm over T tokens at positions pos0 .. pos0 + T - 1 (rows of x, [T, hidden], updated in place).
+void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
+  const int H = e.hidden, D = e.head_dim, QD = e.n_heads * D, KD = e.n_kv * D, F = e.ffn;
+  std::vector<float> h((size_t)T * H), q((size_t)T * QD), k((size_t)T * KD), v((size_t)T * KD), att((size_t)T * QD), o((size_t)T * H);
+  std::vector<float> g((size_t)T * F), u((size_t)T * F);
+  const float scale = 1.0f / sqrtf((float)D);
+  const int group = e.n_heads / e.n_kv;
+  for (int li = 0; li < e.n_layers; ++li) {
+    const Layer& L = e.layers[li];
+    float* kc = e.kc.data() + (size_t)li * e.max_seq * KD;
+    float* vc = e.vc.data() + (size_t)li * e.max_seq * KD;
+    e.pool->run(T, [&](int t0, int t1) {
+      for (int t = t0; t < t1; ++t) rmsnorm(x + (size_t)t * H, L.attn_norm.data(), h.data() + (size_t)t * H, H, e.eps);
+    });
+    matmul(e, L.wq, h.data(), H, T, q.data(), QD, e.has_bias ? L.bq.data() : nullptr);
+    matmul(e, L.wk, h.data(), H, T, k.data(), KD, e.has_bias ? L.bk.data() : nullptr);
+    matmul(e, L.wv, h.data(), H, T, v.data(), KD, e.has_bias ? L.bv.data() : nullptr);
+    e.pool->run(T, [&](int t0, int t1) {
+    for (int t = t0; t < t1; ++t) {
+      const int pos = pos0 + t;
+      for (int hq = 0; hq < e.n_heads; ++hq) {
+        float* qh = q.data() + (size_t)t * QD + hq * D;
+        if (e.qk_norm) rmsnorm(qh, L.q_norm.data(), qh, D, e.eps);
+        rope_neox(qh, D, pos, e.inv_freq.data());
+      }
+      for (int hk = 0; hk < e.n_kv; ++hk) {
+        float* kh = k.data() + (size_t)t * KD + hk * D;
+        if (e.qk_norm) rmsnorm(kh, L.k_norm.data(), kh, D, e.eps);
+        rope_neox(kh, D, pos, e.inv_freq.data());
+      }
+      memcpy(kc + (size_t)pos * KD, k.data() + (size_t)t * KD, sizeof(float) * KD);
+      memcpy(vc + (size_t)pos * KD, v.data() + (size_t)t * KD, sizeof(float) * KD);
+    }
+    });
+    // causal attention: token t sees positions 0 .. pos0 + t
+    e.pool->run(T * e.n_heads, [&](int i0, int i1) {
+      std::vector<float> sc((size_t)pos0 + T);
+      for (int idx = i0; idx < i1; ++idx) {
+        // interleave long and short contexts over the threads: item idx -> token (idx % T), head (idx / T)
+        const int t = idx % T, hq = idx / T;
+        const int n_ctx = pos0 + t + 1, hk = hq / group;
+        const float* qh = q.data() + (size_t)t * QD + hq * D;
+        float mx = -INFINITY;
+        for (int p = 0; p < n_ctx; ++p) { sc[p] = dot_f32(qh, kc + (size_t)p * KD + hk * D, D) * scale; mx = std::max(mx, sc[p]); }
+        float sum = 0.f;
+        for (int p = 0; p < n_ctx; ++p) { sc[p] = expf(sc[p] - mx); sum += sc[p]; }
+        const float inv = 1.0f / sum;
+        float* out = att.data() + (size_t)t * QD + hq * D;
+        for (int d = 0; d < D; ++d) out[d] = 0.f;
+        for (int p = 0; p < n_ctx; ++p) {
+          const float w = sc[p] * inv;
+          const float* vh = vc + (size_t)p * KD + hk * D;
+          for (int d = 0; d < D; ++d) out[d] += w * vh[d];
+        }
+      }
+    });
+    matmul(e, L.wo, att.data(), QD, T, o.data(), H);
+    e.pool->run(T, [&](int t0, int t1) {
+      for (int t = t0; t < t1; ++t) {
+        float* xr = x + (size_t)t * H;
+        const float* orow = o.data() + (size_t)t * H;
+        for (int i = 0; i < H; ++i) xr[i] += orow[i];
+        rmsnorm(xr, L.ffn_norm.data(), h.data() + (size_t)t * H, H, e.eps);
+      }
+    });
+    matmul(e, L.wgate, h.data(), H, T, g.data(), F);
+    matmul(e, L.wup, h.data(), H, T, u.data(), F);
+    e.pool->run(T * 8, [&](int c0, int c1) {               // (token, eighth of the FFN width) items: a single token still spreads
+      for (int c = c0; c < c1; ++c) {
+        const int t = c / 8, part = c % 8;
+        float* gr = g.data() + (size_t)t * F;
+        const float* ur = u.data() + (size_t)t * F;
+        for (int i = (int)((long)F * part / 8); i < (int)((long)F * (part + 1) / 8); ++i) gr[i] = gr[i] / (1.0f + expf(-gr[i])) * ur[i];
+      }
+    });
+    matmul(e, L.wdown, g.data(), F, T, o.data(), H);
+    for (int t = 0; t < T; ++t) {
+      float* xr = x + (size_t)t * H;
+      const float* orow = o.data() + (size_t)t * H;
+      for (int i = 0; i < H; ++i) xr[i] += orow[i];
+    }
+  }
+}
+
+void embed_rows(const CpuEngine& e, const int* tokens, int T, float* x) {
+  for (int t = 0; t < T; ++t) {
+    int id = tokens[t];
+    if (id < 0 || id >= e.vocab) id = 0;
+    dequant_row(e.embed.type, e.embed.data + (size_t)id * e.embed.row_bytes, x + (size_t)t * e.hidden, e.hidden);
+  }
+}
+
+void logits_of(CpuEngine& e, const float* xrow, float* logits) {
+  std::vector<float> hn((size_t)e.hidden);
+  rmsnorm(xrow, e.final_norm.data(), hn.data(), e.hidden, e.eps);
+  matmul(e, e.head, hn.data(), e.hidden, 1, logits, e.vocab);
+}
+
+int argmax(const float* v, int n) {
+  int bi = 0; float bv = -INFINITY;
+  for (int i = 0; i < n; ++i) { const float x = v[i] == v[i] ? v[i] : -3.4e38f; if (x > bv) { bv = x; bi = i; } }
+  return bi;
+}
+
+}  // namespace
+}  // namespace gbh
+
+using namespace gbh;
+
+// Open a GGUF checkpoint of a dense qwen2 / qwen3 model for CPU inference.  threads <= 0: all cores.  NULL on error.
+GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
+  void* g = gbh_gguf_open(path);
+  if (g == nullptr) return nullptr;
+  auto* e = new CpuEngine();
+  e->gguf = g;
+  std::string arch = "qwen3";
+  const int ai = gbh_gguf_find_key(g, "general.architecture");
+  if (ai >= 0) { uint64_t len = 0; const char* s = gbh_gguf_kv_string(g, ai, -1, &len); if (s) arch.assign(s, (size_t)len); }
+  if (arch != "qwen2" && arch != "qwen3") { fail("cpu engine: architecture %s is not a dense qwen2 / qwen3 model", arch.c_str()); delete e; gbh_gguf_close(g); return nullptr; }
+  const std::string p = arch + ".";
+  e->n_layers = (int)kv_num(g, p + "block_count", 0); e->hidden = (int)kv_num(g, p + "embedding_length", 0);
+  e->n_heads = (int)kv_num(g, p + "attention.head_count", 0); e->n_kv = (int)kv_num(g, p + "attention.head_count_kv", e->n_heads);
+  e->head_dim = (int)kv_num(g, p + "attention.key_length", e->n_heads ? e->hidden / e->n_heads : 0);
+  e->ffn = (int)kv_num(g, p + "feed_forward_length", 0);
+  e->eps = (float)kv_num(g, p + "attention.layer_norm_rms_epsilon", 1e-6); e->theta = (float)kv_num(g, p + "rope.freq_base", 1e6);
+  e->max_seq = max_seq > 0 ? max_seq : 4096;
+  e->threads = threads > 0 ? threads : (int)std::max(1u, std::thread::hardware_concurrency());
+  e->pool = new Pool(e->threads);
+  bool ok = e->n_layers > 0 && e->hidden > 0 && e->n_heads > 0 && e->n_kv > 0 && e->head_dim > 0 && e->ffn > 0 && e->n_heads % e->n_kv == 0;
+  if (!ok) fail("cpu engine: incomplete hyper-parameters in %s", path);
+  const int H = e->hidden, D = e->head_dim;
+  if (ok) {
+    const int ei = gbh_gguf_find_tensor(g, "token_embd.weight");
+    int nd = 0, type = 0; uint64_t dims[4] = {0, 0, 0, 0}, nbytes = 0; char nm[8];
+    if (ei < 0) { fail("cpu engine: token_embd.weight is missing"); ok = false; }
+    else { gbh_gguf_tensor_info(g, ei, nm, 8, &nd, dims, &type, &nbytes); e->vocab = (int)dims[1]; }
+  }
+  ok = ok && get_mat(g, "token_embd.weight", &e->embed, e->vocab, H) == 0;
+  if (ok) { if (gbh_gguf_find_tensor(g, "output.weight") >= 0) ok = get_mat(g, "output.weight", &e->head, e->vocab, H) == 0; else e->head = e->embed; }
+  ok = ok && get_vec(g, "output_norm.weight", &e->final_norm, H) == 0;
+  e->layers.resize((size_t)std::max(e->n_layers, 0));
+  for (int li = 0; ok && li < e->n_layers; ++li) {
+    Layer& L = e->layers[li];
+    const std::string b = "blk." + std::to_string(li) + ".";
+    ok = get_vec(g, b + "attn_norm.weight", &L.attn_norm, H) == 0 && get_vec(g, b + "ffn_norm.weight", &L.ffn_norm, H) == 0 &&
+         get_mat(g, b + "attn_q.weight", &L.wq, e->n_heads * D, H) == 0 && get_mat(g, b + "attn_k.weight", &L.wk, e->n_kv * D, H) == 0 &&
+         get_mat(g, b + "attn_v.weight", &L.wv, e->n_kv * D, H) == 0 && get_mat(g, b + "attn_output.weight", &L.wo, H, e->n_heads * D) == 0 &&
+         get_mat(g, b + "ffn_gate.weight", &L.wgate, e->ffn, H) == 0 && get_mat(g, b + "ffn_up.weight", &L.wup, e->ffn, H) == 0 &&
+         get_mat(g, b + "ffn_down.weight", &L.wdown, H, e->ffn) == 0;
+    if (!ok) break;
+    const int qn = get_vec(g, b + "attn_q_norm.weight", &L.q_norm, D, true);
+    if (qn == 0) { e->qk_norm = true; ok = get_vec(g, b + "attn_k_norm.weight", &L.k_norm, D) == 0; } else if (qn < 0) ok = false;
+    const int bq = get_vec(g, b + "attn_q.bias", &L.bq, e->n_heads * D, true);
+    if (bq == 0) { e->has_bias = true; ok = ok && get_vec(g, b + "attn_k.bias", &L.bk, e->n_kv * D) == 0 && get_vec(g, b + "attn_v.bias", &L.bv, e->n_kv * D) == 0; }
+    else if (bq < 0) ok = false;
+  }
+  if (!ok) { gbh_gguf_close(g); delete e; return nullptr; }
+  e->inv_freq.resize((size_t)D / 2);
+  for (int j = 0; j < D / 2; ++j) e->inv_freq[j] = powf(e->theta, -2.0f * (float)j / (float)D);
+  const size_t kvn = (size_t)e->n_layers * e->max_seq * e->n_kv * D;
+  e->kc.assign(kvn, 0.f); e->vc.assign(kvn, 0.f);
+  return e;
+}
+
+GBH_API void gbh_cpu_engine_free(void* h) {
+  auto* e = (CpuEngine*)h;
+  if (e == nullptr) return;
+  gbh_gguf_close(e->gguf);
+  delete e;
+}
+
+GBH_API int gbh_cpu_engine_vocab(void* h) { return ((CpuEngine*)h)->vocab; }
+GBH_API int gbh_cpu_engine_threads(void* h) { return ((CpuEngine*)h)->threads; }
+
+// Batched pass over `n` tokens at positions pos0 .. pos0 + n - 1 (fills the KV cache); logits [vocab] of the last one.
+GBH_API int gbh_cpu_engine_forward(void* h, const int* tokens, int n, int pos0, float* logits) {
+  auto* e = (CpuEngine*)h;
+  if (n <= 0 || pos0 < 0 || pos0 + n > e->max_seq) return fail("cpu engine: positions %d .. %d leave the cache of %d", pos0, pos0 + n, e->max_seq);
+  std::vector<float> x((size_t)n * e->hidden);
+  embed_rows(*e, tokens, n, x.data());
+  forward_hidden(*e, x.data(), n, pos0);
+  if (logits != nullptr) logits_of(*e, x.data() + (size_t)(n - 1) * e->hidden, logits);
+  return 0;
+}
+
+// Greedy generation: batched prefill of the prompt, then max_new - 1 single-token steps.  Writes max_new token ids and the
+// seconds spent in the two phases.
+GBH_API int gbh_cpu_engine_generate(void* h, const int* prompt, int n_prompt, int max_new, int* out_tokens, double* prefill_s, double* decode_s) {
+  auto* e = (CpuEngine*)h;
+  if (max_new <= 0) return 0;
+  if (n_prompt + max_new > e->max_seq) return fail("cpu engine: %d + %d tokens exceed the cache of %d", n_prompt, max_new, e->max_seq);
+  std::vector<float> logits((size_t)e->vocab);
+  auto t0 = std::chrono::steady_clock::now();
+  if (gbh_cpu_engine_forward(h, prompt, n_prompt, 0, logits.data()) != 0) return -1;
+  auto t1 = std::chrono::steady_clock::now();
+  int tok = argmax(logits.data(), e->vocab);
+  out_tokens[0] = tok;
+  for (int i = 1; i < max_new; ++i) {
+    if (gbh_cpu_engine_forward(h, &tok, 1, n_prompt + i - 1, logits.data()) != 0) return -1;
+    tok = argmax(logits.data(), e->vocab);
+    out_tokens[i] = tok;
+  }
+  auto t2 = std::chrono::steady_clock::now();
+  if (prefill_s) *prefill_s = std::chrono::duration<double>(t1 - t0).count();
+  if (decode_s) *decode_s = std::chrono::duration<double>(t2 - t1).count();
+  return 0;
+}

@@ -1,0 +1,146 @@
+"""CPU benchmark of the smallest benchmark configuration: Qwen3-0.6B shape, Q8_0 GGUF, batch 1, a prompt of random token ids,
+greedy decode — our native CPU engine against the reference project's CPU engine on the same file and the same ids.
+
+``python -m gemm_b200 cpubench [--prompt-len 128 --new 32 --threads 8 --reference-root DIR]``
+
+The reference arm compiles the reference's own ``common/transformer.h`` with gcc from its source tree (nothing of it lives in
+this repository) and drives it through the calls its command-line program makes (cpu/llm/test_transformer.c:284-345:
+``transformer_forward`` for every prompt token but the last, ``transformer_forward_logits`` after that, arg-max in between)."""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import shutil
+import subprocess
+import tempfile
+import time
+from typing import List, Optional, Tuple
+
+import torch
+
+_SHIM = r'''
+#define GGUF_LOADER_IMPLEMENTATION
+#include "gguf_loader.h"
+#define GGML_DEQUANT_IMPLEMENTATION
+#include "ggml_dequant.h"
+#define TRANSFORMER_IMPLEMENTATION
+#include "transformer.h"
+#include <time.h>
+static double now_s(void) { struct timespec t; clock_gettime(CLOCK_MONOTONIC, &t); return t.tv_sec + 1e-9 * t.tv_nsec; }
+/* the loop of cpu/llm/test_transformer.c: sequential prefill, then greedy decode */
+int ref_generate(const char *path, int max_seq, int n_threads, const int *prompt, int n_prompt, int max_new, int *out, double *prefill_s, double *decode_s) {
+    gguf_context *g = gguf_open(path, 1);
+    if (!g) return -1;
+    transformer_model *m = transformer_load(g, max_seq);
+    if (!m) return -2;
+    if (n_threads > 1) transformer_set_threads(m, n_threads);
+    double t0 = now_s();
+    float *logits = NULL;
+    for (int i = 0; i < n_prompt; i++) {
+        if (i == n_prompt - 1) logits = transformer_forward_logits(m, prompt[i], i);
+        else transformer_forward(m, prompt[i], i);
+    }
+    double t1 = now_s();
+    int pos = n_prompt, next = 0;
+    for (int s = 0; s < max_new; s++) {
+        if (s > 0) { logits = transformer_forward_logits(m, next, pos); pos++; }
+        if (!logits) return -3;
+        next = 0;
+        for (int j = 1; j < m->n_vocab; j++) if (logits[j] > logits[next]) next = j;
+        out[s] = next;
+    }
+    double t2 = now_s();
+    *prefill_s = t1 - t0; *decode_s = t2 - t1;
+    return 0;
+}
+'''
+
+
+def make_checkpoint(path: str, model: str = "qwen3-0.6b", wtype: str = "Q8_0", seed: int = 0) -> None:
+    """Write the random-init checkpoint (N(0, 0.02) matrices, unit norms) of ``model`` as a GGUF file in ggml type ``wtype``."""
+    from ..models import loader
+    from ..models.config import get_config
+    from ..models.weights import RandomSource
+    cfg = get_config(model)
+    loader.save_gguf(cfg, RandomSource(cfg, seed, "cpu"), path, wtype)
+
+
+def run_ours(path: str, prompt: List[int], max_new: int, threads: int) -> Tuple[List[int], float, float]:
+    from ..serve.cpu_engine import CpuEngine
+    eng = CpuEngine(path, max_seq_len=len(prompt) + max_new + 8, threads=threads)
+    try:
+        return eng.generate(prompt, max_new)
+    finally:
+        eng.close()
+
+
+def run_reference(ref_root: str, path: str, prompt: List[int], max_new: int, threads: int) -> Optional[Tuple[List[int], float, float]]:
+    """The reference CPU engine on the same file (None when its tree or gcc is missing)."""
+    if not os.path.isdir(os.path.join(ref_root, "common")) or shutil.which("gcc") is None:
+        return None
+    d = tempfile.mkdtemp(prefix="gemm_ref_cpubench_")
+    src, so = os.path.join(d, "shim.c"), os.path.join(d, "shim.so")
+    with open(src, "w") as f:
+        f.write(_SHIM)
+    cmd = ["gcc", "-O3", "-march=native", "-mavx2", "-mfma", "-mf16c", "-shared", "-fPIC", "-w", "-I", os.path.join(ref_root, "common"), src, "-o", so,
+           "-lm", "-lpthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("building the reference engine failed:\n" + r.stderr[-2000:])
+    lib = ctypes.CDLL(so)
+    ids = (ctypes.c_int * len(prompt))(*prompt)
+    out = (ctypes.c_int * max_new)()
+    tp, td = ctypes.c_double(), ctypes.c_double()
+    rc = lib.ref_generate(path.encode(), len(prompt) + max_new + 8, threads, ids, len(prompt), max_new, out, ctypes.byref(tp), ctypes.byref(td))
+    if rc != 0:
+        raise RuntimeError(f"the reference engine failed with code {rc}")
+    return list(out), tp.value, td.value
+
+
+def main(argv=None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser(description="CPU benchmark: native CPU engine vs the reference CPU engine (Qwen3-0.6B shape, Q8_0)")
+    ap.add_argument("--model", default="qwen3-0.6b")
+    ap.add_argument("--wtype", default="Q8_0")
+    ap.add_argument("--prompt-len", type=int, default=128)
+    ap.add_argument("--new", type=int, default=32)
+    ap.add_argument("--threads", type=int, default=os.cpu_count() or 1)
+    ap.add_argument("--gguf", default="", help="checkpoint to use (default: write the synthetic one to a temporary file)")
+    ap.add_argument("--reference-root", default=os.environ.get("GEMM_REFERENCE_ROOT", ""), help="source tree of the reference project (optional)")
+    args = ap.parse_args(argv)
+    from ..models.config import get_config
+    cfg = get_config(args.model)
+    path = args.gguf
+    tmp = None
+    if not path:
+        tmp = tempfile.mkdtemp(prefix="gemm_b200_cpubench_")
+        path = os.path.join(tmp, "model.gguf")
+        t0 = time.time()
+        make_checkpoint(path, args.model, args.wtype)
+        print(f"[cpubench] wrote {path} ({os.path.getsize(path) / 2**20:.0f} MiB) in {time.time() - t0:.1f}s")
+    g = torch.Generator().manual_seed(0)
+    prompt = torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist()
+    toks, tp, td = run_ours(path, prompt, args.new, args.threads)
+    n_tok = args.prompt_len + args.new
+    line = {"config": {"model": args.model, "wtype": args.wtype, "prompt_len": args.prompt_len, "new_tokens": args.new, "threads": args.threads},
+            "ours": {"prefill_s": round(tp, 4), "decode_s": round(td, 4), "total_s": round(tp + td, 4), "prefill_tok_s": round(args.prompt_len / tp, 2),
+                     "decode_tok_s": round((args.new - 1) / td, 2) if td > 0 else None, "tok_s_overall": round(n_tok / (tp + td), 2)}}
+    if args.reference_root:
+        ref = run_reference(args.reference_root, path, prompt, args.new, args.threads)
+        if ref is not None:
+            rt, rp, rd = ref
+            line["reference"] = {"prefill_s": round(rp, 4), "decode_s": round(rd, 4), "total_s": round(rp + rd, 4), "prefill_tok_s": round(args.prompt_len / rp, 2),
+                                 "decode_tok_s": round((args.new - 1) / rd, 2) if rd > 0 else None, "tok_s_overall": round(n_tok / (rp + rd), 2)}
+            line["tokens_identical"] = rt == toks
+            line["speedup_total"] = round((rp + rd) / (tp + td), 2)
+            line["speedup_decode"] = round(rd / td, 2) if td > 0 else None
+    print(json.dumps(line))
+    if tmp is not None:
+        shutil.rmtree(tmp, ignore_errors=True)
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main())

@@ -1,0 +1,62 @@
+"""Native CPU engine (csrc/host/cpu_engine.cc): logits against the fp32 PyTorch oracle and, when the reference tree is present,
+greedy tokens against the reference CPU engine on the same GGUF file."""
+import numpy as np
+import pytest
+import torch
+
+from gemm_b200.models import loader, reference
+from gemm_b200.models.config import get_config
+from gemm_b200.models.weights import RandomSource
+from gemm_b200.serve.cpu_engine import CpuEngine
+from gemm_b200.utils import cpubench
+from tests import reference_oracle as oracle
+
+
+def _rel(a, b):
+    a, b = torch.as_tensor(a).float(), torch.as_tensor(b).float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("name,wtype", [("tiny-dense", "Q8_0"), ("tiny-qwen2", "Q8_0"), ("tiny-dense", "Q4_K"), ("tiny-dense", "F16")])
+def test_logits_match_the_fp32_oracle(tmp_path, name, wtype):
+    cfg = get_config(name)
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=7), path, wtype)
+    w = loader.load_gguf(path, "bf16", device="cpu")          # the file's (quantised) weights, decoded: what the engine multiplies with
+    toks = torch.randint(0, cfg.vocab, (21,), generator=torch.Generator().manual_seed(1)).tolist()
+    want = reference.reference_logits(w, torch.tensor(toks))
+    eng = CpuEngine(path, max_seq_len=64, threads=3)
+    got_batched = eng.forward(toks, 0)                          # one batched pass
+    assert _rel(got_batched, want[-1]) < 2e-2                   # the oracle holds bf16 copies of the decoded weights
+    eng2 = CpuEngine(path, max_seq_len=64, threads=1)
+    for i, t in enumerate(toks):                                # token by token on one thread: same cache, same logits
+        got_seq = eng2.forward([t], i)
+    assert np.abs(got_seq - got_batched).max() < 1e-3 * max(1.0, np.abs(got_batched).max())
+    out, _, _ = eng.generate(toks, 5)
+    out1, _, _ = eng2.generate(toks, 5)
+    assert out == out1 and len(out) == 5
+
+
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not available")
+def test_greedy_tokens_equal_the_reference_engine(tmp_path):
+    cfg = get_config("tiny-dense")
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=9), path, "Q8_0")
+    prompt = torch.randint(0, cfg.vocab, (24,), generator=torch.Generator().manual_seed(2)).tolist()
+    ref = cpubench.run_reference(oracle.REF_ROOT, path, prompt, 12, threads=1)
+    ours = cpubench.run_ours(path, prompt, 12, threads=4)
+    assert ref is not None and ours[0] == ref[0]
+
+
+def test_load_errors_are_reported(tmp_path):
+    cfg = get_config("tiny-moe")
+    path = str(tmp_path / "moe.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=1), path, "Q8_0")
+    with pytest.raises(RuntimeError, match="dense"):
+        CpuEngine(path)
+    eng_path = str(tmp_path / "d.gguf")
+    cfg2 = get_config("tiny-dense")
+    loader.save_gguf(cfg2, RandomSource(cfg2, seed=1), eng_path, "Q8_0")
+    eng = CpuEngine(eng_path, max_seq_len=8)
+    with pytest.raises(RuntimeError, match="cache"):
+        eng.forward(list(range(9)), 0)
