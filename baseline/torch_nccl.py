@@ -194,6 +194,7 @@ class BaselineModel:
             last = x.reshape(nb, s, -1)[:, -1]
             outs.append(_rmsnorm(last, self.final_norm, cfg.rms_eps) @ self.head.t())
         self.pos = torch.full((b,), s, dtype=torch.long, device=self.device)
+        self._prompt_len, self._steps_done = s, 0
         return torch.cat(outs).float()
 
     def _ffn_prefill(self, L, h: torch.Tensor) -> torch.Tensor:
@@ -280,6 +281,9 @@ class BaselineModel:
             self._graph = g
 
     def decode_step(self) -> torch.Tensor:
+        self._steps_done = getattr(self, "_steps_done", 0) + 1
+        if self._prompt_len + self._steps_done >= self.max_len:      # checked on the host: the cache write must never leave the buffer
+            raise RuntimeError(f"KV cache of {self.max_len} positions is full")
         if self._graph is not None:
             self._graph.replay()
         else:

@@ -185,7 +185,7 @@ def baseline_arm(args):
     tp = layout == "tp"
     b_local = args.batch if (tp or world == 1) else args.batch // world
     model = BaselineModel(cfg, device, seed=0, n_layers=n_layers, group=dist.group.WORLD if world > 1 else None, layout=layout)
-    total_new = args.warmup + args.steps + 8
+    total_new = args.warmup + 2 * args.steps + 8             # device-timed steps + the end-to-end steps + slack
     model.alloc_kv(b_local, args.prompt_len + total_new)
     g = torch.Generator().manual_seed(0)
     all_prompts = torch.randint(0, cfg.vocab, (args.batch, args.prompt_len), generator=g, dtype=torch.int32)

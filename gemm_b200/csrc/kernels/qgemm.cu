@@ -88,7 +88,7 @@ __device__ __forceinline__ void unpack_q80_sub(const uint4 qa, const uint4 qb, i
 template <int TYPE, int TN>
 __global__ void __launch_bounds__(kQgThreads, 1)
 qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
-  constexpr int RAW = TYPE == 0 ? 128 * 144 : 128 * 256 + 128 * 16;      // bytes of a raw tile
+  constexpr int RAW = TYPE == 0 ? 128 * 144 : 128 * 272;                 // bytes of a raw tile (Q8_0 row: 256 values + 8 f16 scales)
   constexpr int RAW_PAD = (RAW + 1023) & ~1023;
   constexpr int B_BYTES = TN * 256;                                      // token stage: 2 atoms of [TN rows][64 k]
   constexpr int TMEM_COLS = 2 * TN < 32 ? 32 : 2 * TN;
@@ -250,8 +250,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
             }
             unpack_q4k_sub(q0, q1, nib, d * (float)sc, dmin * (float)mn, dst_row, row);
           } else {
-            const uint4* qp = reinterpret_cast<const uint4*>(rb + row * 256 + 64 * j + 32 * nib);
-            const __half dh = *reinterpret_cast<const __half*>(rb + 128 * 256 + (row * 8 + 2 * j + nib) * 2);
+            const uint4* qp = reinterpret_cast<const uint4*>(rb + row * 272 + 64 * j + 32 * nib);
+            const __half dh = *reinterpret_cast<const __half*>(rb + row * 272 + 256 + (2 * j + nib) * 2);
             unpack_q80_sub(qp[0], qp[1], nib, __half2float(dh), dst_row, row);
           }
           fence_proxy_async_smem();                        // this thread's operand bytes -> visible to the tensor core
@@ -278,7 +278,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
 
 template <int TYPE, int TN>
 static int launch_qgemm(const CUtensorMap& tmX, QGemmArgs a, cudaStream_t stream) {
-  constexpr int RAW = TYPE == 0 ? 128 * 144 : 128 * 256 + 128 * 16;
+  constexpr int RAW = TYPE == 0 ? 128 * 144 : 128 * 272;
   constexpr int RAW_PAD = (RAW + 1023) & ~1023;
   constexpr int B_BYTES = TN * 256;
   // token ring first (2 stages at least, 3 for wide tiles if they fit), the rest of shared memory buys depth for the raw-tile ring:

@@ -31,8 +31,8 @@ namespace gb {
 
 constexpr int kQvThreads = 256;
 constexpr int kQ4KTileBytes = 128 * 144;
-constexpr int kQ80TileBytes = 128 * 256 + 128 * 16;
-constexpr int kQ80ScaleOff = 128 * 256;
+constexpr int kQ80RowBytes = 256 + 16;            // a row of a Q8_0 tile: 256 int8 values, then its eight f16 scales
+constexpr int kQ80TileBytes = 128 * kQ80RowBytes;
 
 struct QGemvArgs {
   const uint8_t* w;                 // tiled weights [row_tiles][num_kb][tile bytes]
@@ -164,11 +164,24 @@ qgemv_kernel(const QGemvArgs a) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) qw[u] = *reinterpret_cast<const uint4*>(b + 16 + 64 * jh + 16 * u);
       } else {
-        const uint8_t* b = t + row * 256 + 128 * jh;
+        const uint8_t* b = t + row * kQ80RowBytes + 128 * jh;
 #pragma unroll
         for (int u = 0; u < 8; ++u) qw[u] = *reinterpret_cast<const uint4*>(b + 16 * u);
-        const uint2 sc = *reinterpret_cast<const uint2*>(t + kQ80ScaleOff + (row * 8 + 4 * jh) * 2);
+        const uint2 sc = *reinterpret_cast<const uint2*>(t + row * kQ80RowBytes + 256 + 8 * jh);
         hd.x = sc.x; hd.y = sc.y;
+      }
+      // Q4_K: the 6-bit scales / offsets of this lane's four sub-blocks (4 jh .. 4 jh + 3) as bytes of two words, unpacked with
+      // word-wide masks (sub-blocks 0..3: six bits straight from bytes 0..3 / 4..7; 4..7: low 4 bits in bytes 8..11, high 2 bits
+      // on top of bytes 0..7), both forms computed and one selected: no divergence between the two half warps.
+      uint32_t scw = 0, mnw = 0;
+      float dq = 0.f, dminq = 0.f;
+      if (TYPE == 0) {
+        const __half2 dd = *reinterpret_cast<const __half2*>(&hd.x);
+        dq = __low2float(dd); dminq = __high2float(dd);
+        const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
+        const uint32_t sc_lo = s0 & 0x3f3f3f3fu, mn_lo = s1 & 0x3f3f3f3fu;
+        const uint32_t sc_hi = (s2 & 0x0f0f0f0fu) | ((s0 >> 2) & 0x30303030u), mn_hi = ((s2 >> 4) & 0x0f0f0f0fu) | ((s1 >> 2) & 0x30303030u);
+        scw = jh ? sc_hi : sc_lo; mnw = jh ? mn_hi : mn_lo;
       }
 #pragma unroll
       for (int c = 0; c < 2; ++c) {                          // the two chunks of this lane
@@ -176,18 +189,8 @@ qgemv_kernel(const QGemvArgs a) {
         float s_lo, s_hi, o_lo = 0.f, o_hi = 0.f;
         uint32_t wlo[8], whi[8];
         if (TYPE == 0) {
-          const __half2 dd = *reinterpret_cast<const __half2*>(&hd.x);
-          const float d = __low2float(dd), dmin = __high2float(dd);
-          const uint32_t s0 = hd.y, s1 = hd.z, s2 = hd.w;
-          uint32_t sc0, sc1, mn0, mn1;
-          if (jh == 0) {                                     // sub-blocks 0..3: six bits straight from bytes 0..3 / 4..7
-            sc0 = byte_of(s0, 2 * c) & 63u; sc1 = byte_of(s0, 2 * c + 1) & 63u;
-            mn0 = byte_of(s1, 2 * c) & 63u; mn1 = byte_of(s1, 2 * c + 1) & 63u;
-          } else {                                           // sub-blocks 4..7: low 4 bits in bytes 8..11, high 2 bits on top of bytes 0..7
-            sc0 = (byte_of(s2, 2 * c) & 15u) | ((byte_of(s0, 2 * c) >> 6) << 4); sc1 = (byte_of(s2, 2 * c + 1) & 15u) | ((byte_of(s0, 2 * c + 1) >> 6) << 4);
-            mn0 = (byte_of(s2, 2 * c) >> 4) | ((byte_of(s1, 2 * c) >> 6) << 4); mn1 = (byte_of(s2, 2 * c + 1) >> 4) | ((byte_of(s1, 2 * c + 1) >> 6) << 4);
-          }
-          s_lo = d * (float)sc0; s_hi = d * (float)sc1; o_lo = dmin * (float)mn0; o_hi = dmin * (float)mn1;
+          s_lo = dq * (float)byte_of(scw, 2 * c); s_hi = dq * (float)byte_of(scw, 2 * c + 1);
+          o_lo = dminq * (float)byte_of(mnw, 2 * c); o_hi = dminq * (float)byte_of(mnw, 2 * c + 1);
           const uint32_t* qq = reinterpret_cast<const uint32_t*>(&qw[2 * c]);
 #pragma unroll
           for (int i = 0; i < 8; ++i) { wlo[i] = qq[i] & 0x0f0f0f0fu; whi[i] = (qq[i] >> 4) & 0x0f0f0f0fu; }
@@ -205,12 +208,15 @@ qgemv_kernel(const QGemvArgs a) {
           const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
           const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
           const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
-          const float d_lo = ad[(kbi * M + m) * 8 + 2 * j], d_hi = ad[(kbi * M + m) * 8 + 2 * j + 1];
+          const float2 d8 = *reinterpret_cast<const float2*>(ad + (kbi * M + m) * 8 + 2 * j);      // block scales of the two sub-blocks
           int sl = 0, sh = 0;
 #pragma unroll
           for (int i = 0; i < 8; ++i) { sl = dp4a_s(wlo[i], al[i], sl); sh = dp4a_s(whi[i], ah[i], sh); }
-          float v = s_lo * d_lo * (float)sl + s_hi * d_hi * (float)sh;
-          if (TYPE == 0) v -= o_lo * as[(kbi * M + m) * 8 + 2 * j] + o_hi * as[(kbi * M + m) * 8 + 2 * j + 1];
+          float v = s_lo * d8.x * (float)sl + s_hi * d8.y * (float)sh;
+          if (TYPE == 0) {
+            const float2 t8 = *reinterpret_cast<const float2*>(as + (kbi * M + m) * 8 + 2 * j);    // block sums
+            v -= o_lo * t8.x + o_hi * t8.y;
+          }
           acc[m] += v;
         }
       }
@@ -274,7 +280,7 @@ struct QGemvPeer {
 };
 
 // Shared memory of one CTA: a ring of weight tiles + the quantised activations of its K range.  Two CTAs share an SM.
-constexpr int kQvSmemBudget = 110 * 1024;
+constexpr int kQvSmemBudget = 110 * 1024;         // two CTAs per SM (three measured no faster: the kernel is not short of warps)
 static int qgemv_stages(int type) { return type == 12 ? 4 : 2; }                 // 4 x 18 KB (Q4_K) / 2 x 34 KB (Q8_0)
 static int qgemv_tile_bytes(int type) { return type == 12 ? kQ4KTileBytes : kQ80TileBytes; }
 // Largest K range (in 256-column tiles) whose quantised activations fit beside the ring for `m` tokens.
@@ -325,7 +331,8 @@ GB_API int gb_qgemv(const void* w, int ggml_type, const void* x, int ldx, float*
   const size_t act = (size_t)kb_per * m * (256 + 64);
   const size_t smem = 128 + (size_t)a.stages * qgemv_tile_bytes(ggml_type) + 128 + act;
   int grid = a.row_tiles * splits;
-  if (grid > 2 * sm_count()) grid = 2 * sm_count();        // persistent: two CTAs per SM walk the items
+  const int per_sm = 2;
+  if (grid > per_sm * sm_count()) grid = per_sm * sm_count();      // persistent: the resident CTAs walk the items
   const int t = ggml_type == 12 ? 0 : 1;
 #define GB_QV(TV, MV)                                                                                              \
   {                                                                                                                 \

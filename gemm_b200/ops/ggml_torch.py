@@ -16,8 +16,8 @@ Tiled layout.  A quantised matrix ``[rows, k]`` (rows a multiple of 128, k a mul
 row tile streams whole tiles:
 
 * Q4_K tile: 128 super-blocks of 144 bytes, row after row (18 432 bytes).
-* Q8_0 tile: the int8 values ``[128][256]`` (32 768 bytes) followed by the f16 scales ``[128][8]`` (2 048 bytes): the same
-  34 bytes per block as in the file, with the values 16-byte aligned.
+* Q8_0 tile: 128 rows of 272 bytes, a row being its 256 int8 values followed by its eight f16 scales: the same 34 bytes per
+  block as in the file, with the values 16-byte aligned (and a row stride that spreads the rows over the shared-memory banks).
 """
 from __future__ import annotations
 
@@ -134,10 +134,10 @@ def tile(raw: torch.Tensor, t: int, rows: int, k: int) -> torch.Tensor:
     if t == Q4_K:
         return raw.reshape(rt, TILE_ROWS, kt, 144).permute(0, 2, 1, 3).reshape(rt, kt, TILE_ROWS * 144).contiguous()
     b = raw.reshape(rt, TILE_ROWS, kt, 8, 34).permute(0, 2, 1, 3, 4)                     # [rt, kt, 128, 8, 34]
-    out = torch.empty(rt, kt, tile_bytes(Q8_0), dtype=torch.uint8, device=raw.device)
-    out[..., : TILE_ROWS * 256] = b[..., 2:].reshape(rt, kt, TILE_ROWS * 256)
-    out[..., TILE_ROWS * 256:] = b[..., :2].reshape(rt, kt, TILE_ROWS * 16)
-    return out
+    out = torch.empty(rt, kt, TILE_ROWS, 272, dtype=torch.uint8, device=raw.device)
+    out[..., :256] = b[..., 2:].reshape(rt, kt, TILE_ROWS, 256)
+    out[..., 256:] = b[..., :2].reshape(rt, kt, TILE_ROWS, 16)
+    return out.reshape(rt, kt, tile_bytes(Q8_0))
 
 
 def untile(tiled: torch.Tensor, t: int, rows: int, k: int) -> torch.Tensor:
@@ -145,6 +145,7 @@ def untile(tiled: torch.Tensor, t: int, rows: int, k: int) -> torch.Tensor:
     rt, kt = rows // TILE_ROWS, k // TILE_K
     if t == Q4_K:
         return tiled.reshape(rt, kt, TILE_ROWS, 144).permute(0, 2, 1, 3).reshape(rows, kt * 144).contiguous()
-    q = tiled[..., : TILE_ROWS * 256].reshape(rt, kt, TILE_ROWS, 8, 32)
-    d = tiled[..., TILE_ROWS * 256:].reshape(rt, kt, TILE_ROWS, 8, 2)
+    t4 = tiled.reshape(rt, kt, TILE_ROWS, 272)
+    q = t4[..., :256].reshape(rt, kt, TILE_ROWS, 8, 32)
+    d = t4[..., 256:].reshape(rt, kt, TILE_ROWS, 8, 2)
     return torch.cat([d, q], dim=-1).permute(0, 2, 1, 3, 4).reshape(rows, kt * 8 * 34).contiguous()
