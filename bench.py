@@ -415,6 +415,30 @@ def main():
         e2e = {"value": args.batch * args.steps / (e2e_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": b_local * 4 * n_gpus,
                "d2h_bytes_per_step": b_local * 4 * n_gpus, "ms_per_step": e2e_ms / args.steps}
 
+    # ---------------------------------------------------------------- multi-GPU correctness: fused peer-memory path against the NCCL path
+    check = None
+    if world > 1 and par is not None and len(engine.pages.free) >= b_local:
+        from gemm_b200.models.transformer import ForwardBatch
+        n_tok = 4
+        scratch = engine.pages.alloc(b_local)                          # one fresh page per sequence, given back below
+        bt = torch.tensor([[p] for p in scratch], dtype=torch.int32)
+        gchk = torch.Generator().manual_seed(1234 + (0 if tp else rank))
+        ids = torch.randint(0, cfg.vocab, (b_local * n_tok,), generator=gchk, dtype=torch.int32)
+        fbc = ForwardBatch.build([n_tok] * b_local, [0] * b_local, ids, bt, engine.page_size, engine.hq_local, engine.hkv_local, device)
+        outs = []
+        for fused_flag in (True, False):                               # same weights, same state, the two exchange implementations
+            par.fused = fused_flag and (args.moe_path == "fused")
+            outs.append(engine.model.forward(fbc).float())
+        par.fused = args.moe_path == "fused"
+        torch.cuda.synchronize()
+        engine.pages.release(scratch)
+        rel = ((outs[0] - outs[1]).norm() / (outs[1].norm() + 1e-12)).item()
+        same = float((outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean().item())
+        st_chk = _native.read_status()
+        check = {"tokens_equal": bool(-max_over_ranks(-same) >= 1.0), "token_agreement_min": -max_over_ranks(-same), "rel_l2_max": max_over_ranks(rel),
+                 "kernel_status": st_chk["what"], "compared": "fused peer-memory exchange vs torch.distributed (NCCL) exchange, one forward of "
+                 f"{n_tok} fresh tokens per sequence on every rank"}
+
     if rank == 0:
         # the comparison number: the plain PyTorch + NCCL implementation of the same config on the same number of GPUs
         base_val = baseline_table().get(f"{args.model}|{args.batch}|{args.prompt_len}|{n_gpus}")
@@ -431,7 +455,7 @@ def main():
                        "l2": f"no flush: each step streams the {weights.nbytes() / 2**30:.1f} GiB of weights of a rank plus its KV cache, far more than the 126 MB L2",
                        "moe_path": args.moe_path if n_gpus > 1 else "local"},
             "prefill_tokens_per_s": prefill_tok_s, "ttft_ms_p50": prefill_ms, "tpot_ms_p50": tpot_p50,
-            "clocks": clocks, "e2e": e2e, "gpu_launches": kernels_per_step * args.steps,
+            "clocks": clocks, "e2e": e2e, "check": check, "gpu_launches": kernels_per_step * args.steps,
             "kernels_per_step": kernels_per_step, "kernel_status": st["what"], "kernel_status_detail": {k: (list(v) if isinstance(v, tuple) else v) for k, v in st.items()},
             "rejected_region": rejected, "host_enqueue_ms_per_step": round(host_enqueue_ms, 3),
             "step_ms_min_max": [round(min(per_step), 3), round(max(per_step), 3)], "native_libs": _native.loaded_libraries(),

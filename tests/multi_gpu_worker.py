@@ -57,6 +57,34 @@ def check_collectives(fab, rank, world, dev):
     idx = torch.tensor([rank, 100 - rank, 3, 10 + rank], dtype=torch.int32, device=dev)
     oi, ov = am(val, idx)
     assert oi.tolist() == [0, 100 - (world - 1), 3, 10] and ov.tolist() == [1.0, 5.0, float(world - 1), 7.0], (oi, ov)
+    # back-to-back calls with fresh data every time and no host synchronisation in between: a rank may be a whole call ahead of a
+    # peer, which the alternating slot sets (one-shot, arg-max) and the entry handshake (exchange) have to absorb
+    ar = fab.make_allreduce(2048, torch.float32, chunks=2)
+    xs = [torch.randn(2048, device=dev) for _ in range(24)]
+    refs = []
+    for x in xs:
+        gathered = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(gathered, x)
+        r = torch.zeros_like(x)
+        for gx in gathered:
+            r += gx
+        refs.append(r)
+    torch.cuda.synchronize()
+    ys = [ar(x) for x in xs]
+    for y, r in zip(ys, refs):
+        assert torch.equal(y, r), "back-to-back one-shot all-reduce calls interfered"
+    ex2 = fab.make_exchange(2048, chunks=1)
+    outs = []
+    for i in range(16):
+        xi = torch.full((512,), float(rank * 100 + i), device=dev)
+        outs.append(ex2.all_gather(xi).view(torch.float32).view(world, 512).clone())
+    for i, o in enumerate(outs):
+        assert all(bool((o[r] == r * 100 + i).all()) for r in range(world)), "back-to-back exchanges interfered"
+    vals = [torch.tensor([float((rank * 7 + i) % world), 1.0], device=dev) for i in range(16)]
+    got = [am(v, torch.tensor([rank, 50 + rank], dtype=torch.int32, device=dev)) for v in vals]
+    for i, (oi, ov) in enumerate(got):
+        win = max(range(world), key=lambda r: ((r * 7 + i) % world, -r))
+        assert int(oi[0]) == win and float(ov[0]) == float((win * 7 + i) % world) and int(oi[1]) == 50, (i, oi, ov)
     fab.barrier()
     torch.cuda.synchronize()
     _native.assert_status_ok()
@@ -146,6 +174,27 @@ def check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-dense"):
     dist.all_gather(gathered, last)
     if fused:
         assert all(torch.equal(gathered[0], x) for x in gathered), "ranks disagree bitwise after the fused reduction"
+    if fused and fmt in ("q4_k", "q8_0"):
+        # decode-sized row-parallel projection over ggml blocks: the GEMV's tail stores the partial sums into every GPU's slot
+        from gemm_b200.models.weights import make_linear
+        from gemm_b200.ops import elementwise as ew
+        hidden, k_shard, rows = cfg.hidden, 2048, 2
+        gg = torch.Generator(device="cpu").manual_seed(100 + rank)
+        lw = make_linear((torch.randn(hidden, k_shard, generator=gg) * 0.05).to(dev), fmt)
+        x_sh = torch.randn(rows, k_shard, generator=gg).to(dev).bfloat16()
+        resid = torch.randn(rows, hidden, generator=torch.Generator().manual_seed(3)).to(dev).bfloat16()
+        nw = torch.ones(hidden, device=dev, dtype=torch.bfloat16)
+        pend = par.row_linear(lw, x_sh)
+        assert hasattr(pend, "chan"), "the projection was expected to take the fused GEMV path"
+        r1 = resid.clone()
+        out = par.add_norm(pend, nw, 1e-6, r1)
+        full = x_sh.float() @ lw.dequantized().t()
+        dist.all_reduce(full)
+        r2 = (resid.float() + full).bfloat16()
+        torch.cuda.synchronize()
+        _native.assert_status_ok()
+        assert rel(r1, r2) < 2e-2 and rel(out, ew.rmsnorm_ref(r2, nw, 1e-6)) < 2e-2, f"quantised row-parallel GEMV: {rel(r1, r2)}"
+    if fused and fmt in ("bf16", "mxfp8"):
         # a decode-sized row-parallel projection whose shard is long enough to be cut along K as well (several slabs per rank in
         # the slot): the fused reduction + RMSNorm against all-reduce + norm in PyTorch
         from gemm_b200.models.weights import make_linear
@@ -196,7 +245,10 @@ def main():
         for fused in (True, False):
             check_context_parallel(rank, world, dev, fused)
     if what in ("all", "tp"):
-        for fmt, fused in (("bf16", True), ("mxfp8", True), ("bf16", False)):
+        for fmt, fused in (("bf16", True), ("mxfp8", True), ("bf16", False), ("q4_k", True), ("q8_0", True)):
+            check_tensor_parallel(rank, world, dev, fmt, fused)
+    if what == "tp4":
+        for fmt, fused in (("bf16", True), ("mxfp8", True)):
             check_tensor_parallel(rank, world, dev, fmt, fused)
     dist.barrier()
     if rank == 0:

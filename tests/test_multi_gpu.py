@@ -30,12 +30,12 @@ def _ngpu():
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_fabric_collectives():
-    _launch("collectives", min(_ngpu(), 4), 29611)
+    _launch("collectives", min(_ngpu(), 8), 29611)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_expert_parallel_matches_single_gpu():
-    _launch("ep", min(_ngpu(), 4), 29612)
+    _launch("ep", min(_ngpu(), 8), 29612)
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
@@ -43,6 +43,11 @@ def test_tensor_parallel_matches_single_gpu():
     _launch("tp", 2, 29613)
 
 
+@pytest.mark.skipif(_ngpu() < 4, reason="needs at least 4 GPUs")
+def test_tensor_parallel_four_ranks_replicated_kv_heads():
+    _launch("tp4", 4, 29615)
+
+
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_context_parallel_decode_attention():
-    _launch("cp", min(_ngpu(), 4), 29614)
+    _launch("cp", min(_ngpu(), 8), 29614)
