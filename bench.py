@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: run fewer layers (the JSON line then says so and is not a valid bench number)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--baseline-eager", action="store_true", help="--impl baseline: run the decode step without a CUDA graph")
     ap.add_argument("--parallel", default="auto", choices=["auto", "ep", "tp"],
                     help="multi-GPU layout: ep = experts sharded, attention data-parallel (MoE models); tp = every projection sharded, "
                          "batch replicated (dense models); auto picks by model")
@@ -203,15 +204,23 @@ def baseline_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def note(msg):
+        if rank == 0:
+            print(f"[bench baseline] {msg}", file=sys.stderr, flush=True)
+
+    note("weights built")
     model.prefill(prompts[:1, :256])                      # lazy initialisation outside the timed region
     barrier()
+    note("first prefill done")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     first = model.prefill(prompts).argmax(-1)
     e1.record()
     barrier()
     prefill_ms = max_over_ranks(e0.elapsed_time(e1))
-    model.begin_decode(first, use_graph=True)
+    note(f"prefill {prefill_ms:.0f} ms")
+    model.begin_decode(first, use_graph=not args.baseline_eager)
+    note("decode graph captured" if not args.baseline_eager else "decode runs eagerly")
     sampler = ClockSampler(local_rank)
     sampler.start()
     for _ in range(args.warmup):
@@ -311,7 +320,10 @@ def main():
         print(f"[bench] weights {weights.nbytes() / 2**30:.1f} GiB on rank 0 in {time.time() - t0:.1f}s", file=sys.stderr)
     total_new = args.warmup + args.steps * (2 if args.no_e2e else 3) + 16        # room for one re-measured timed region
     max_len = args.prompt_len + total_new + 8
-    engine = Engine(weights, max_batch=b_local, max_seq_len=max_len, page_size=128, par=par, max_prefill_tokens=16384)
+    pages_per_seq = (max_len + 127) // 128
+    # one spare page per sequence at N > 1: the fused-vs-NCCL check below writes its scratch tokens there
+    engine = Engine(weights, max_batch=b_local, max_seq_len=max_len, page_size=128, par=par, max_prefill_tokens=16384,
+                    num_pages=b_local * pages_per_seq + (b_local if n_gpus > 1 else 0))
     if par is not None:
         par.attach(engine, cfg, max_tokens=16384)
 

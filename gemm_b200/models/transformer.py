@@ -343,11 +343,14 @@ class Transformer:
                 # once, not once per selected expert)
                 xq = ew.mx_gather_rows(h_mx, pl.row_token, sf_layout=tn) if h_mx is not None else ew.mx_quantize(h, pl.row_token, sf_layout=tn)
             dev = h.device
-            hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=dev)
-            hsf = ew.sf_alloc(pl.capacity, inter, dev, tn, init=False)
-            expert_gate_up_mx(xq.data, xq.sf, lw.w13, e, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
-            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
-                                    w_tiled=lw.w2.mx.tiled, pair_rows=(tn == 32 and PAIR_DOWN))
+            if tn == 32 and moe.can_fuse_ffn(xq, lw.w13, lw.w2, e, pl.capacity):
+                y = moe.expert_ffn_fused(xq, lw.w13, lw.w2, e, pl)          # gate/up, activation and down as one persistent launch
+            else:
+                hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=dev)
+                hsf = ew.sf_alloc(pl.capacity, inter, dev, tn, init=False)
+                expert_gate_up_mx(xq.data, xq.sf, lw.w13, e, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
+                y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
+                                        w_tiled=lw.w2.mx.tiled, pair_rows=(tn == 32 and PAIR_DOWN))
         else:
             tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
             if moe.can_prep(h, lw.router, k):

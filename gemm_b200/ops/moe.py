@@ -174,6 +174,42 @@ def prep_hidden(h: torch.Tensor, w: torch.Tensor, k: int, n_exp: int, align: int
     return ids, wt, pl, rows
 
 
+# gate/up + activation + down of a decode-sized batch as one persistent launch (GB_MOE_FFN_FUSED=0: two grouped GEMMs)
+MOE_FFN_FUSED = os.environ.get("GB_MOE_FFN_FUSED", "1") != "0"
+_ffn_ctr = {}
+
+
+def can_fuse_ffn(xq, w13, w2, n_groups: int, capacity: int) -> bool:
+    """Shapes ``expert_ffn_fused`` takes: MXFP8 rows with one scale atom per 32 rows, tiled MXFP8 expert weights."""
+    if not (MOE_FFN_FUSED and xq.data.is_cuda and xq.sf_layout == 32 and w13.mx is not None and w2.mx is not None and w13.mx.tiled and w2.mx.tiled):
+        return False
+    return bool(_native.cuda().gb_moe_ffn_supported(_i(w13.k), _i(w2.k), _i(n_groups), _i(capacity)))
+
+
+def expert_ffn_fused(xq, w13, w2, n_groups: int, pl: "MoePlan") -> torch.Tensor:
+    """``y [capacity, hidden]`` bf16: rows of ``xq`` (an ``MxTensor`` in expert order, 32-row scale atoms) through
+    ``down(SiLU(gate(x)) * up(x))`` of their expert.  Rows beyond a segment's count are not written."""
+    from . import elementwise as ew
+    lib = _native.cuda()
+    dev = xq.data.device
+    hid, inter, cap = w13.k, w2.k, pl.capacity
+    key = (dev.index, torch.cuda.current_stream().cuda_stream)
+    ctr = _ffn_ctr.get(key)
+    if ctr is None:
+        # one counter block per stream: launches on one stream run one after the other, the kernel leaves the block zeroed
+        ctr = _ffn_ctr[key] = torch.zeros(int(lib.gb_moe_ffn_ctr_count()), dtype=torch.int32, device=dev)
+    hq = torch.empty(cap, inter, dtype=torch.uint8, device=dev)
+    hsf = ew.sf_alloc(cap, inter, dev, 32, init=False)
+    y = torch.empty(cap, hid, dtype=torch.bfloat16, device=dev)
+    nb = lambda t: _l(t.numel() * t.element_size())
+    rc = lib.gb_moe_ffn(_p(w13.mx.data), _p(w13.mx.sf), nb(w13.mx.sf), _p(w2.mx.data), _p(w2.mx.sf), nb(w2.mx.sf),
+                        _p(xq.data), _i(xq.data.stride(0)), _p(xq.sf), nb(xq.sf), _p(hq), _i(hq.stride(0)), _p(hsf), nb(hsf),
+                        _p(y), _i(y.stride(0)), nb(y), _i(hid), _i(inter), _i(n_groups), _p(pl.seg_start), _p(pl.seg_count), _i(cap),
+                        _p(ctr), _i(ctr.numel()), _c(_native.status_ptr()), _s())
+    _native.check(rc, "gb_moe_ffn")
+    return y
+
+
 @dataclass
 class MoePlan:
     seg_start: torch.Tensor      # int32 [E]   first row of each expert's segment

@@ -220,12 +220,15 @@ class ExpertParallel:
             else:
                 ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
                 xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
-            hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
-            hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)
-            expert_gate_up_mx(xq.data, xq.sf, lw.w13, self.e_local, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
-            from ..models.transformer import PAIR_DOWN
-            y = gemm.grouped_linear(hq, lw.w2.mx.data.view(self.e_local, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
-                                    w_tiled=lw.w2.mx.tiled, pair_rows=PAIR_DOWN)
+            if moe.can_fuse_ffn(xq, lw.w13, lw.w2, self.e_local, pl.capacity):
+                y = moe.expert_ffn_fused(xq, lw.w13, lw.w2, self.e_local, pl)
+            else:
+                hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
+                hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)
+                expert_gate_up_mx(xq.data, xq.sf, lw.w13, self.e_local, pl.seg_start, pl.seg_count, tn, hq, hsf, pl.row_token)
+                from ..models.transformer import PAIR_DOWN
+                y = gemm.grouped_linear(hq, lw.w2.mx.data.view(self.e_local, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf,
+                                        sfb=hsf, w_tiled=lw.w2.mx.tiled, pair_rows=PAIR_DOWN)
         else:
             tn = gemm.pick_tn(max(1, (w * cap * k + cfg.n_experts - 1) // cfg.n_experts), dual=True)
             if moe.can_prep(allh, lw.router, k):

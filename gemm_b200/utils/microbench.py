@@ -114,6 +114,14 @@ def _moe(args, t: int, name: str):
     fl = 2.0 * t * kk * h * inter
     _run(f"{name}_gate_up", gate_up, 2 * fl, touched * 2 * h * inter + t * kk * h, args, tn=tn, experts_touched=touched)
     _run(f"{name}_down", down, fl, touched * h * inter + t * kk * inter + t * kk * h * 2, args, tn=tn, experts_touched=touched)
+    if tn == 32:
+        # the same two projections as one persistent launch
+        from ..models.weights import LinearWeight
+        lw1 = LinearWeight("mxfp8", 2 * inter, h, mx=mxfp8.MxTensor(d1, w1.sf, e * 2 * inter, h, 128, tiled=True), groups=e, rows_per_group=2 * inter)
+        lw2 = LinearWeight("mxfp8", h, inter, mx=mxfp8.MxTensor(d2, w2.sf, e * h, inter, 128, tiled=True), groups=e, rows_per_group=h)
+        if moe.can_fuse_ffn(xq, lw1, lw2, e, pl.capacity):
+            _run(f"{name}_ffn_fused", lambda: moe.expert_ffn_fused(xq, lw1, lw2, e, pl), 3 * fl,
+                 touched * 3 * h * inter + t * kk * h + t * kk * h * 2, args, tn=tn, experts_touched=touched)
 
 
 def case_moe_decode(args):
