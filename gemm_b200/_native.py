@@ -48,7 +48,8 @@ def host():
     """The host-side C++ library (loaded once)."""
     global _host
     if _host is None:
-        lib = _load("libgb_host.so")
+        # GEMM_B200_HOST_LIB names another build of the same sources inside _lib/ (the sanitizer build, build.build_host_sanitized)
+        lib = _load(os.environ.get("GEMM_B200_HOST_LIB", "libgb_host.so"))
         lib.gbh_last_error.restype = ctypes.c_char_p
         _host = lib
     return _host

@@ -8,7 +8,8 @@
 The libraries stay inside the package directory so that a copy of the source tree carries them.
 A source is recompiled only when it (or any header) is newer than its object file.
 
-Usage:  ``python -m gemm_b200.build [--force] [--verbose] [--host-only]``
+Usage:  ``python -m gemm_b200.build [--force] [--verbose] [--host-only] [--sanitize]``
+(``--sanitize`` builds ``_lib/libgb_host_san.so``, the host library under ASan + UBSan, instead).
 """
 from __future__ import annotations
 
@@ -60,11 +61,11 @@ def _compile(cmd, src, obj, verbose):
     return src
 
 
-def _build_lib(name, sources, compiler_cmd, link_cmd, hdr_time, force, verbose):
+def _build_lib(name, sources, compiler_cmd, link_cmd, hdr_time, force, verbose, tag=""):
     OBJ.mkdir(parents=True, exist_ok=True)
     jobs, objs = [], []
     for src in sources:
-        obj = OBJ / (src.stem + ("_cu.o" if src.suffix == ".cu" else "_cc.o"))
+        obj = OBJ / (src.stem + tag + ("_cu.o" if src.suffix == ".cu" else "_cc.o"))
         objs.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr_time):
             jobs.append((compiler_cmd + ["-c", str(src), "-o", str(obj)], src, obj))
@@ -89,6 +90,46 @@ def build_host(force=False, verbose=False) -> Path:
                       [cxx, "-shared", "-pthread"], hdr, force, verbose)
 
 
+SAN_FLAGS = ["-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer"]
+
+
+def build_host_sanitized(force=False, verbose=False) -> Path:
+    """``_lib/libgb_host_san.so``: the host library under AddressSanitizer + UndefinedBehaviorSanitizer.  A process uses it with
+    ``GEMM_B200_HOST_LIB=libgb_host_san.so`` and the ASan runtime preloaded (``sanitizer_runtime()``); tests/test_host_sanitizers.py
+    runs the host-side unit tests that way."""
+    srcs = sorted((CSRC / "host").glob("*.cc"))
+    hdr = _newest_header([CSRC / "host"])
+    cxx = _sanitizer_compiler()
+    if cxx is None:
+        raise RuntimeError("no C++ compiler with an AddressSanitizer runtime found")
+    flags = [f for f in CXX_FLAGS if f != "-O3"] + SAN_FLAGS
+    return _build_lib("libgb_host_san.so", srcs, [cxx] + flags + ["-I", str(CSRC / "host")],
+                      [cxx, "-shared", "-pthread", "-fsanitize=address,undefined"], hdr, force, verbose, tag="_san")
+
+
+def _asan_of(cxx: str) -> str:
+    try:
+        r = subprocess.run([cxx, "-print-file-name=libasan.so"], capture_output=True, text=True)
+    except OSError:
+        return ""
+    p = r.stdout.strip()
+    return os.path.realpath(p) if r.returncode == 0 and os.path.isabs(p) and os.path.exists(p) else ""
+
+
+def _sanitizer_compiler() -> str | None:
+    """The first of $CXX, g++ on PATH and /usr/bin/g++ that ships an ASan runtime (a toolchain without one cannot link the build)."""
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), "/usr/bin/g++"):
+        if cand and _asan_of(cand):
+            return cand
+    return None
+
+
+def sanitizer_runtime() -> str:
+    """Path of the ASan runtime that must be loaded before the interpreter (``LD_PRELOAD``); empty if no compiler has one."""
+    cxx = _sanitizer_compiler()
+    return _asan_of(cxx) if cxx else ""
+
+
 def build_cuda(force=False, verbose=False) -> Path:
     nvcc = _nvcc()
     if nvcc is None:
@@ -108,4 +149,7 @@ def build_all(force=False, verbose=False, host_only=False):
 
 
 if __name__ == "__main__":
+    if "--sanitize" in sys.argv:
+        print(build_host_sanitized(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+        sys.exit(0)
     build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv, host_only="--host-only" in sys.argv)

@@ -29,6 +29,7 @@ from ..ops import gemm, moe, qlinear, sampling
 from ..ops.mxfp8 import MxTensor
 from .config import ModelConfig
 from .weights import LinearWeight, ModelWeights
+from ..utils import profiler
 
 
 @dataclass
@@ -381,7 +382,8 @@ class Transformer:
                                        quantize=True, want_bf16=is_ssm, sf_layout=lay)
             else:
                 h, h_mx = par.add_norm(delta if delta is not None else x, lw.attn_norm, cfg.rms_eps, x if delta is not None else None), None
-            delta = self.ssm_block(li, lw, h, h_mx, fb) if is_ssm else self.attention_block(li, lw, h, h_mx, fb)
+            with profiler.region("ssm" if is_ssm else "attention", "block", "attention", li):
+                delta = self.ssm_block(li, lw, h, h_mx, fb) if is_ssm else self.attention_block(li, lw, h, h_mx, fb)
             need_bf16 = (not self.mx) or cfg.is_moe
             # a parallel context may name the buffer the normalised rows should land in (the staging buffer of its exchange)
             ob = par.ffn_in_buffer(x.shape[0], lw) if (hasattr(par, "ffn_in_buffer") and x.is_cuda) else None
@@ -390,14 +392,15 @@ class Transformer:
                 h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, quantize=True, want_bf16=need_bf16, sf_layout=lay, **okw)
             else:
                 h, h_mx = par.add_norm(delta, lw.ffn_norm, cfg.rms_eps, x, **okw), None
-            if lw.w13 is not None:
-                delta = self.par.moe_ffn(self, lw, h, h_mx)
-                if delta is None:
-                    delta = self.moe_local(lw, h, h_mx)
-                if lw.sh_gate_up is not None:
-                    delta = (self.par.materialize(delta).float() + self.shared_expert(lw, h).float()).to(torch.bfloat16)
-            else:
-                delta = self.dense_ffn(lw, h, h_mx)
+            with profiler.region("moe" if lw.w13 is not None else "ffn", "block", "ffn", li):
+                if lw.w13 is not None:
+                    delta = self.par.moe_ffn(self, lw, h, h_mx)
+                    if delta is None:
+                        delta = self.moe_local(lw, h, h_mx)
+                    if lw.sh_gate_up is not None:
+                        delta = (self.par.materialize(delta).float() + self.shared_expert(lw, h).float()).to(torch.bfloat16)
+                else:
+                    delta = self.dense_ffn(lw, h, h_mx)
             if fb.deepstack is not None and li < fb.deepstack.shape[0]:
                 # DeepStack (Qwen3-VL): vision features of deeper encoder layers join the stream after the first decoder layers
                 delta = (self.par.materialize(delta).float() + fb.deepstack[li].float()).to(torch.bfloat16)

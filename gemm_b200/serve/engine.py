@@ -14,6 +14,8 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+from ..utils import profiler
+
 from ..models.config import ModelConfig
 from ..models.transformer import ForwardBatch, KvCache, Transformer
 from ..models.weights import ModelWeights
@@ -125,7 +127,8 @@ class Engine:
                 room -= take
             fb = ForwardBatch.build(q_lens, ctx, torch.cat([x.to(self.device) for x in ids]), self._block_table([base + i for i in seqs]),
                                     self.page_size, self.hq_local, self.hkv_local, self.device, seq_slots=[base + i for i in seqs])
-            logits = self.model.forward(fb)
+            with profiler.region("prefill_chunk", "step", "engine"):
+                logits = self.model.forward(fb)
             for j, i in enumerate(seqs):
                 done[i] += q_lens[j]
                 if done[i] == prompts[i].numel():
@@ -212,10 +215,11 @@ class Engine:
     @torch.no_grad()
     def decode_step(self) -> torch.Tensor:
         """One token for every sequence; returns the device tensor of sampled ids (valid until the next step)."""
-        if self._graph is not None:
-            self._graph.replay()
-        else:
-            self._decode_body()
+        with profiler.region("decode_step", "step", "engine"):
+            if self._graph is not None:
+                self._graph.replay()
+            else:
+                self._decode_body()
         self.step_count += 1
         for s in range(len(self.seq_len)):
             self.seq_len[s] += 1

@@ -5,7 +5,9 @@ reference's common/profiler.h:44-77,110-249), fed by CUDA events on the GPU and 
         ...
     print(profiler.summary())
 
-Profiling is off unless ``GEMM_B200_PROFILE=1`` or ``profiler.enable()``; when off, ``region`` costs one branch."""
+Profiling is off unless ``GEMM_B200_PROFILE=1`` or ``profiler.enable()``; when off, ``region`` costs one branch.
+``GEMM_B200_NVTX=1`` (or ``enable_nvtx()``) makes every region an NVTX range as well (``name[layer]``), whether or not the
+timers are on, so that a timeline tool shows the model's structure above the kernels."""
 from __future__ import annotations
 
 import contextlib
@@ -19,7 +21,13 @@ import torch
 from .. import _native
 
 _enabled = os.environ.get("GEMM_B200_PROFILE", "0") == "1"
+_nvtx = os.environ.get("GEMM_B200_NVTX", "0") == "1"
 _pending: List[tuple] = []
+
+
+def enable_nvtx(on: bool = True) -> None:
+    global _nvtx
+    _nvtx = on
 
 
 def enable(on: bool = True) -> None:
@@ -33,6 +41,20 @@ def enabled() -> bool:
 
 @contextlib.contextmanager
 def region(name: str, op_type: str = "op", component: str = "model", layer: int = -1, flops: float = 0.0, nbytes: float = 0.0):
+    if _nvtx and torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name if layer < 0 else f"{name}[{layer}]")
+        try:
+            with _timed(name, op_type, component, layer, flops, nbytes):
+                yield
+        finally:
+            torch.cuda.nvtx.range_pop()
+        return
+    with _timed(name, op_type, component, layer, flops, nbytes):
+        yield
+
+
+@contextlib.contextmanager
+def _timed(name, op_type, component, layer, flops, nbytes):
     if not _enabled:
         yield
         return
