@@ -46,9 +46,10 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="debug only: run fewer layers (the JSON line then says so and is not a valid bench number)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--baseline-eager", action="store_true", help="--impl baseline: run the decode step without a CUDA graph")
-    ap.add_argument("--parallel", default="auto", choices=["auto", "ep", "tp"],
+    ap.add_argument("--parallel", default="auto", choices=["auto", "ep", "tp", "tp+ep"],
                     help="multi-GPU layout: ep = experts sharded, attention data-parallel (MoE models); tp = every projection sharded, "
-                         "batch replicated (dense models); auto picks by model")
+                         "batch replicated (dense models); tp+ep = attention sharded by heads and experts spread over the same ranks, "
+                         "batch replicated (the layout of the largest MoE models, e.g. --model qwen3-235b-a22b); auto picks by model")
     ap.add_argument("--moe-path", default="fused", choices=["fused", "nccl"], help="multi-GPU expert exchange: fused peer-memory kernels or the NCCL baseline")
     return ap.parse_args()
 
@@ -182,6 +183,7 @@ def baseline_arm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
         layout = args.parallel if args.parallel != "auto" else ("ep" if cfg.n_experts > 0 else "tp")
+        layout = "ep" if layout == "tp+ep" else layout             # the baseline has no hybrid layout: experts sharded, attention data-parallel
     n_layers = args.layers if args.layers > 0 else cfg.n_layers
     tp = layout == "tp"
     b_local = args.batch if (tp or world == 1) else args.batch // world
@@ -300,19 +302,21 @@ def main():
             par = ExpertParallel(dist.group.WORLD, device, fused=(args.moe_path == "fused"))
         else:
             from gemm_b200.parallel.tensor import TensorParallel
-            par = TensorParallel(dist.group.WORLD, device, fused=(args.moe_path == "fused"))
+            par = TensorParallel(dist.group.WORLD, device, fused=(args.moe_path == "fused"), ep_experts=(layout == "tp+ep"))
     if args.gpus != world and rank == 0:
         print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE {world}; using {world}", file=sys.stderr)
     n_gpus = world
 
     cfg = get_config(args.model)
     n_layers = args.layers if args.layers > 0 else cfg.n_layers
-    tp = layout == "tp" and n_gpus > 1
+    tp = layout in ("tp", "tp+ep") and n_gpus > 1
+    hybrid = layout == "tp+ep" and n_gpus > 1
     assert tp or args.batch % n_gpus == 0
     b_local = args.batch if tp else args.batch // n_gpus          # tensor parallelism replicates the batch on every rank
     t0 = time.time()
     if tp:
-        weights = synthetic_weights(cfg, args.fmt, device=device, seed=0, tp_rank=rank, tp_size=n_gpus, n_layers=n_layers)
+        weights = synthetic_weights(cfg, args.fmt, device=device, seed=0, tp_rank=rank, tp_size=n_gpus, n_layers=n_layers,
+                                    ep_rank=rank if hybrid else 0, ep_size=n_gpus if hybrid else 1)
     else:
         weights = synthetic_weights(cfg, args.fmt, device=device, seed=0, ep_rank=rank, ep_size=n_gpus, n_layers=n_layers)
     torch.cuda.synchronize()
@@ -463,7 +467,7 @@ def main():
                                           "q8_0": "ggml Q8_0 weights (kept quantised), bf16 activations / int8 in the GEMV, fp32 accumulate"}[args.fmt],
             "data": "synthetic (uniform random token ids, random-init N(0,0.02) weights)",
             "config": {"model": args.model, "global_batch": args.batch, "seq_len": args.prompt_len, "decode_context": args.prompt_len + args.warmup,
-                       "parallelism": (f"tp{n_gpus}" if tp else f"dp{n_gpus}-attention+ep{n_gpus}") if n_gpus > 1 else "single", "layers": n_layers,
+                       "parallelism": (f"tp{n_gpus}-attention+ep{n_gpus}" if hybrid else f"tp{n_gpus}" if tp else f"dp{n_gpus}-attention+ep{n_gpus}") if n_gpus > 1 else "single", "layers": n_layers,
                        "l2": f"no flush: each step streams the {weights.nbytes() / 2**30:.1f} GiB of weights of a rank plus its KV cache, far more than the 126 MB L2",
                        "moe_path": args.moe_path if n_gpus > 1 else "local"},
             "prefill_tokens_per_s": prefill_tok_s, "ttft_ms_p50": prefill_ms, "tpot_ms_p50": tpot_p50,

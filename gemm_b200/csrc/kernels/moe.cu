@@ -394,7 +394,10 @@ moe_combine_scatter_kernel(const CombineScatterArgs a) {
     ws[threadIdx.x] = a.weights ? a.weights[(size_t)t * a.k + threadIdx.x] : 1.0f;
   }
   __syncthreads();
-  const int home = t / a.tokens_per_rank, lr = t - home * a.tokens_per_rank;
+  // tokens_per_rank == 0: every rank holds every token (tensor-parallel attention in front of expert-parallel experts), the row
+  // goes into this rank's slot on ALL GPUs
+  const bool bcast = a.tokens_per_rank == 0;
+  const int home = bcast ? 0 : t / a.tokens_per_rank, lr = bcast ? t : t - home * a.tokens_per_rank;
   float* dst = a.slot[home] + (size_t)lr * a.hidden;
   for (int v = threadIdx.x; v < a.hidden / 8; v += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -408,6 +411,12 @@ moe_combine_scatter_kernel(const CombineScatterArgs a) {
     }
     reinterpret_cast<float4*>(dst + v * 8)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
     reinterpret_cast<float4*>(dst + v * 8)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (bcast)
+      for (int p = 1; p < a.world; ++p) {
+        float* d2 = a.slot[p] + (size_t)lr * a.hidden + v * 8;
+        reinterpret_cast<float4*>(d2)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        reinterpret_cast<float4*>(d2)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -539,7 +548,8 @@ GB_API int gb_moe_combine_scatter(const void* y, const int* pair_row, const floa
                                   int tokens_per_rank, void* const* slots, void* const* flags, int world, void* epoch_ctr, void* done_ctr,
                                   cudaStream_t stream) {
   if (hidden % 8 || k > kMaxTopK || world > kMaxRanks) return fail("moe_combine_scatter: hidden %% 8 != 0, k > 16 or world > 8%s");
-  if (n_tok <= 0 || n_tok != tokens_per_rank * world) return fail("moe_combine_scatter: n_tok must be tokens_per_rank * world%s");
+  // tokens_per_rank == 0: broadcast mode (every token row goes to every rank)
+  if (n_tok <= 0 || (tokens_per_rank != 0 && n_tok != tokens_per_rank * world)) return fail("moe_combine_scatter: n_tok must be tokens_per_rank * world%s");
   CombineScatterArgs a;
   memset(&a, 0, sizeof(a));
   a.y = (const __nv_bfloat16*)y; a.pair_row = pair_row; a.weights = weights; a.hidden = hidden; a.k = k; a.ld_y = ld_y;

@@ -327,19 +327,22 @@ class Transformer:
             act = gemm.linear_mx_swiglu_quant(xm, gu.mx)
         return self.par.row_linear(lw.w_down, None, act)
 
-    def moe_local(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor] = None) -> torch.Tensor:
-        """All experts on this GPU: route -> plan -> (gather + quantise) -> grouped gate/up -> grouped down -> combine."""
+    def moe_local(self, lw, h: torch.Tensor, h_mx: Optional[MxTensor] = None, local_range=None) -> torch.Tensor:
+        """The experts held by this GPU over the rows ``h``: route -> plan -> (gather + quantise) -> gate/up -> down -> combine.
+        ``local_range = (first expert, count)``: the weights are that slice of the experts; (token, expert) pairs routed
+        elsewhere are dropped from the plan and contribute nothing to the pending sum (the caller adds the ranks' sums)."""
         cfg = self.cfg
         t = h.shape[0]
-        e, k, inter, hid = cfg.n_experts, cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
+        e, k, inter, hid = (local_range[1] if local_range else cfg.n_experts), cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
+        rt = dict(mode=cfg.router, bias=lw.router_bias, renorm=cfg.norm_topk, routed_scale=cfg.routed_scale, local_range=local_range)
         if self.mx:
             # token tile (= scale-atom layout) by the expected rows per expert: 32 for decode-sized batches
-            tn = 32 if (t * k) // e <= 24 else 128
+            tn = 32 if (t * k) // cfg.n_experts <= 24 else 128
             if tn == 32 and moe.can_prep(h, lw.router, k):
                 # decode-sized batch: router projection, routing, plan and the quantised gather are one launch
-                ids, wts, pl, xq = moe.prep_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+                ids, wts, pl, xq = moe.prep_hidden(h, lw.router, k, e, tn, **rt)
             else:
-                ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+                ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, **rt)
                 # the RMSNorm before this block already quantised the tokens: gather bytes and scales (every token is quantised
                 # once, not once per selected expert)
                 xq = ew.mx_gather_rows(h_mx, pl.row_token, sf_layout=tn) if h_mx is not None else ew.mx_quantize(h, pl.row_token, sf_layout=tn)
@@ -353,11 +356,11 @@ class Transformer:
                 y = gemm.grouped_linear(hq, lw.w2.mx.data.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, sfa=lw.w2.mx.sf, sfb=hsf,
                                         w_tiled=lw.w2.mx.tiled, pair_rows=(tn == 32 and PAIR_DOWN))
         else:
-            tn = gemm.pick_tn(max(1, (t * k + e - 1) // e), dual=True)
+            tn = gemm.pick_tn(max(1, (t * k + cfg.n_experts - 1) // cfg.n_experts), dual=True)
             if moe.can_prep(h, lw.router, k):
-                ids, wts, pl, xs = moe.prep_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale, quantize=False)
+                ids, wts, pl, xs = moe.prep_hidden(h, lw.router, k, e, tn, quantize=False, **rt)
             else:
-                ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, cfg.router, lw.router_bias, cfg.norm_topk, cfg.routed_scale)
+                ids, wts, pl = moe.route_plan_hidden(h, lw.router, k, e, tn, **rt)
                 xs = moe.gather_rows(h, pl.row_token)
             act = gemm.grouped_linear(xs, lw.w13.w.view(e, 2 * inter, hid), pl.seg_start, pl.seg_count, tn, dual=True, w_tiled=lw.w13.tiled)
             y = gemm.grouped_linear(act, lw.w2.w.view(e, hid, inter), pl.seg_start, pl.seg_count, tn, w_tiled=lw.w2.tiled)

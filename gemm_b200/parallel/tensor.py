@@ -45,13 +45,22 @@ class PendingReduce:
 
 
 class TensorParallel:
+    """``ep_experts=True`` is the hybrid layout of the large MoE models (the reference runs the same N ranks as a tensor-parallel
+    group for attention and as an expert-parallel group for the experts: common/glm5.h:178-202, common/m3_impl.h:653-660,
+    716-722): attention and the dense projections are cut as above and every rank sees every token, each rank holds
+    ``E / N`` whole experts, evaluates them on the rows routed to them, and the ranks' router-weighted sums are added by the
+    same slot reduction that finishes a row-parallel projection.  No token exchange is needed in front of the experts.
+    Build the weights with ``tp_rank / tp_size`` AND ``ep_rank = tp_rank, ep_size = tp_size``."""
     ep_size = 1
     ep_rank = 0
 
-    def __init__(self, group, device: torch.device, fused: bool = True, max_fused_rows: int = 256):
+    def __init__(self, group, device: torch.device, fused: bool = True, max_fused_rows: int = 256, ep_experts: bool = False):
         self.group, self.device, self.fused = group, device, fused
         self.tp_size = dist.get_world_size(group)
         self.tp_rank = dist.get_rank(group)
+        self.ep_experts = ep_experts
+        if ep_experts:
+            self.ep_size, self.ep_rank = self.tp_size, self.tp_rank
         self.max_fused_rows = max_fused_rows
         self.fab: Optional[Fabric] = None
         self._chan = 0
@@ -198,7 +207,24 @@ class TensorParallel:
         return slots[:, : delta.splits * n].reshape(self.tp_size * delta.splits, n).sum(0).reshape(delta.rows, delta.hidden).to(torch.bfloat16)
 
     def moe_ffn(self, model, lw, h, h_mx=None):
-        return None
+        if not self.ep_experts or self.tp_size == 1:
+            return None                  # experts replicated: the model evaluates all of them locally
+        e_l = self.cfg.n_experts // self.ep_size
+        pc = model.moe_local(lw, h, h_mx, local_range=(self.ep_rank * e_l, e_l))
+        rows, hid = h.shape[0], self.cfg.hidden
+        if not (self.fused and h.is_cuda and rows <= self.max_fused_rows):
+            return self.tp_all_reduce(pc.materialize())
+        # decode-sized: this rank's router-weighted partial sums go into its slot on every GPU; the next RMSNorm adds the slots
+        ch = self._chan
+        self._chan ^= 1
+        ex, w = self._extras[ch], self.tp_size
+        slots = (ctypes.c_void_p * w)(*[ex.peer_out[p] for p in range(w)])
+        flags = (ctypes.c_void_p * w)(*[ex.signal_flags[p] for p in range(w)])
+        rc = self.fab.lib.gb_moe_combine_scatter(_c(pc.y.data_ptr()), _c(pc.pair_row.data_ptr()), _c(pc.weights.data_ptr()), _i(rows), _i(hid),
+                                                 _i(pc.k), _i(pc.y.stride(0)), _i(0), slots, flags, _i(w), _c(self.epoch[ch]), _c(self.done[ch]),
+                                                 _c(torch.cuda.current_stream().cuda_stream))
+        _native.check(rc, "gb_moe_combine_scatter")
+        return PendingReduce(ch, rows, hid, 1)
 
     def merge_sampled(self, tok: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """Greedy merge for a vocabulary-sharded LM head: arg-max all-reduce of this shard's (value, index)."""

@@ -61,16 +61,21 @@ def experts_touched(n_experts: int, k: int, tokens: int) -> float:
 def estimate(cfg: ModelConfig, batch: int, ctx: int, gpus: int = 1, fmt: str = "mxfp8", mode: str = "ep", plat: Platform = Platform(),
              derate: float = 1.0, prefill_chunk: int = 16384) -> dict:
     """``mode`` "ep": experts sharded over the GPUs, attention replicated, the batch split by GPU (data-parallel attention);
-    "tp": every projection sharded, batch replicated."""
+    "tp": every projection sharded, batch replicated; "tp+ep": attention sharded by heads with the batch replicated, whole
+    experts spread over the same GPUs (``parallel.tensor.TensorParallel(ep_experts=True)``): per layer one slot reduction
+    after o_proj and one after the experts, no token exchange."""
     bw = _bytes_per_weight(fmt)
     attn, dense, expert, router = layer_params(cfg)
     n_layers = cfg.n_layers
     kv_tok = 2 * cfg.n_kv_heads * cfg.head_dim * 2                      # bytes per token per layer (bf16 K and V)
     head = cfg.vocab * cfg.hidden * 2                                   # LM head stays bf16
+    hybrid = mode == "tp+ep"
+    mode = "tp" if hybrid else mode
     local_batch = batch if mode == "tp" else -(-batch // gpus)
     # ---- decode: bytes one GPU reads per step
     touched = experts_touched(cfg.n_experts, cfg.n_experts_used, batch)
     if mode == "tp":
+        # whole experts per GPU (hybrid) or every expert cut by columns (plain TP): the same bytes per GPU either way
         w_layer = (attn + dense + touched * expert) * bw / gpus + router * 2
         kv_layer = batch * ctx * kv_tok / min(gpus, cfg.n_kv_heads)
         comm_layer = 2 * batch * cfg.hidden * 4 * (gpus - 1) / gpus * (2 if gpus > 1 else 0)      # two all-reduces of fp32 rows
@@ -143,7 +148,7 @@ def main(argv=None):
     ap.add_argument("--ctx", type=int, default=2048)
     ap.add_argument("--gpus", default="1", help="comma separated GPU counts")
     ap.add_argument("--format", default="mxfp8", choices=["bf16", "mxfp8"])
-    ap.add_argument("--mode", default="ep", choices=["ep", "tp"])
+    ap.add_argument("--mode", default="ep", choices=["ep", "tp", "tp+ep"])
     ap.add_argument("--derate", type=float, default=1.0)
     ap.add_argument("--hbm-gbs", type=float, default=Platform.hbm_gbs)
     ap.add_argument("--nvlink-gbs", type=float, default=Platform.nvlink_gbs)

@@ -83,6 +83,19 @@ def main():
         got = run(Transformer(w, KvCache.allocate(cfg, 16, 16, "cpu"), par), cfg, toks)
         for a, b in zip(got, ref):
             assert rel(a, b) < 2e-2, rel(a, b)
+    elif what == "hybrid":
+        # tensor-parallel attention in front of expert-parallel experts on the same ranks: every rank sees every token
+        cfg = get_config("tiny-moe")
+        toks = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (20, 33)]
+        ref = run(Transformer(synthetic_weights(cfg, "bf16", "cpu", 5), KvCache.allocate(cfg, 16, 16, "cpu")), cfg, toks)
+        par = TensorParallel(dist.group.WORLD, torch.device("cpu"), fused=False, ep_experts=True)
+        par.attach(None, cfg, 64)
+        w = synthetic_weights(cfg, "bf16", "cpu", 5, tp_rank=rank, tp_size=world, ep_rank=rank, ep_size=world)
+        assert w.layers[0].w13.groups == cfg.n_experts // world
+        model = Transformer(w, KvCache.allocate(cfg, 16, 16, "cpu", max(1, cfg.n_kv_heads // world)), par)
+        got = run(model, cfg, toks)
+        for a, b in zip(got, ref):
+            assert rel(a, b) < 2e-2, rel(a, b)
     elif what == "pp":
         cfg = get_config("tiny-dense").with_(n_layers=5)
         toks = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (20, 33)]

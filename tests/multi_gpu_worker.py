@@ -147,18 +147,20 @@ def check_expert_parallel(rank, world, dev, fmt, fused, gather=True):
     par.close()
 
 
-def check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-dense"):
+def check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-dense", ep_experts=False):
     """Every rank runs the same sequences on its weight shard; logits must equal the unsharded engine's, and be
-    bit-identical across ranks (lock-step greedy decoding needs that)."""
+    bit-identical across ranks (lock-step greedy decoding needs that).  ``ep_experts``: an MoE model whose experts are
+    spread over the same ranks (tensor-parallel attention in front of expert-parallel experts)."""
     from gemm_b200.parallel.tensor import TensorParallel
     cfg = get_config(name)
     page = 16
     g = torch.Generator().manual_seed(11)
     toks = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (40, 90)]
     w_full = synthetic_weights(cfg, fmt, device=dev, seed=5)
-    w_tp = synthetic_weights(cfg, fmt, device=dev, seed=5, tp_rank=rank, tp_size=world)
+    w_tp = synthetic_weights(cfg, fmt, device=dev, seed=5, tp_rank=rank, tp_size=world, ep_rank=rank if ep_experts else 0,
+                             ep_size=world if ep_experts else 1)
     ref = run_model(Transformer(w_full, KvCache.allocate(cfg, 64, page, dev)), cfg, toks, page, dev)
-    par = TensorParallel(dist.group.WORLD, dev, fused=fused)
+    par = TensorParallel(dist.group.WORLD, dev, fused=fused, ep_experts=ep_experts)
     par.attach(None, cfg, max_tokens=256)
     hkv_local = max(1, cfg.n_kv_heads // world)
     model = Transformer(w_tp, KvCache.allocate(cfg, 64, page, dev, hkv_local), par)
@@ -194,7 +196,7 @@ def check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-dense"):
         torch.cuda.synchronize()
         _native.assert_status_ok()
         assert rel(r1, r2) < 2e-2 and rel(out, ew.rmsnorm_ref(r2, nw, 1e-6)) < 2e-2, f"quantised row-parallel GEMV: {rel(r1, r2)}"
-    if fused and fmt in ("bf16", "mxfp8"):
+    if fused and fmt in ("bf16", "mxfp8") and not ep_experts:
         # a decode-sized row-parallel projection whose shard is long enough to be cut along K as well (several slabs per rank in
         # the slot): the fused reduction + RMSNorm against all-reduce + norm in PyTorch
         from gemm_b200.models.weights import make_linear
@@ -247,6 +249,9 @@ def main():
     if what in ("all", "tp"):
         for fmt, fused in (("bf16", True), ("mxfp8", True), ("bf16", False), ("q4_k", True), ("q8_0", True)):
             check_tensor_parallel(rank, world, dev, fmt, fused)
+    if what in ("all", "hybrid"):
+        for fmt, fused in (("bf16", True), ("mxfp8", True), ("mxfp8", False)):
+            check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-moe", ep_experts=True)
     if what == "tp4":
         for fmt, fused in (("bf16", True), ("mxfp8", True)):
             check_tensor_parallel(rank, world, dev, fmt, fused)

@@ -49,5 +49,10 @@ def test_tensor_parallel_four_ranks_replicated_kv_heads():
 
 
 @pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
+def test_tensor_parallel_attention_with_expert_parallel_experts():
+    _launch("hybrid", 2, 29616)
+
+
+@pytest.mark.skipif(_ngpu() < 2, reason="needs at least 2 GPUs")
 def test_context_parallel_decode_attention():
     _launch("cp", min(_ngpu(), 8), 29614)
