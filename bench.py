@@ -268,8 +268,15 @@ def baseline_arm(args):
             line["invalid"] = f"debug run with {n_layers} of {cfg.n_layers} layers"
         print(json.dumps(line))
     if world > 1:
+        # The decode graph holds captured NCCL work: tearing the process group down under it did not return (the ranks sat in
+        # destroy_process_group until the launcher's limit).  Drop the graph, meet once more, and leave without the teardown.
+        torch.cuda.synchronize()
+        model._graph = None
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 
@@ -442,18 +449,25 @@ def main():
         ids = torch.randint(0, cfg.vocab, (b_local * n_tok,), generator=gchk, dtype=torch.int32)
         fbc = ForwardBatch.build([n_tok] * b_local, [0] * b_local, ids, bt, engine.page_size, engine.hq_local, engine.hkv_local, device)
         outs = []
+        outs, hid1 = [], []
         for fused_flag in (True, False):                               # same weights, same state, the two exchange implementations
             par.fused = fused_flag and (args.moe_path == "fused")
+            x1 = engine.model.forward_hidden(fbc, 0, 1)                # the residual stream after one layer (one attention + one FFN / MoE block)
+            hid1.append(x1.float() + engine.model._last_delta.float())
             outs.append(engine.model.forward(fbc).float())
         par.fused = args.moe_path == "fused"
         torch.cuda.synchronize()
         engine.pages.release(scratch)
-        rel = ((outs[0] - outs[1]).norm() / (outs[1].norm() + 1e-12)).item()
+        rel_of = lambda a, b: ((a - b).norm() / (b.norm() + 1e-12)).item()
         same = float((outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean().item())
         st_chk = _native.read_status()
-        check = {"tokens_equal": bool(-max_over_ranks(-same) >= 1.0), "token_agreement_min": -max_over_ranks(-same), "rel_l2_max": max_over_ranks(rel),
-                 "kernel_status": st_chk["what"], "compared": "fused peer-memory exchange vs torch.distributed (NCCL) exchange, one forward of "
-                 f"{n_tok} fresh tokens per sequence on every rank"}
+        check = {"tokens_equal": bool(-max_over_ranks(-same) >= 1.0), "token_agreement_min": -max_over_ranks(-same),
+                 "rel_l2_after_layer_1_max": max_over_ranks(rel_of(hid1[0], hid1[1])), "rel_l2_logits_max": max_over_ranks(rel_of(outs[0], outs[1])),
+                 "kernel_status": st_chk["what"],
+                 "compared": "fused peer-memory exchange vs torch.distributed (NCCL) exchange on the same weights and cache: one forward of "
+                             f"{n_tok} fresh tokens per sequence on every rank.  The two paths round the partial sums differently (fp32 slots vs "
+                             "bf16 rows); with random-init routers near-tied experts swap under that rounding, which is what moves the "
+                             "logits of the deep model while one layer agrees closely"}
 
     if rank == 0:
         # the comparison number: the plain PyTorch + NCCL implementation of the same config on the same number of GPUs
