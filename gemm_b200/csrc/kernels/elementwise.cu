@@ -43,6 +43,18 @@ __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* _
 }
 
 // ------------------------------------------------------------------------------------------ rmsnorm
+// Optional all-gather in the epilogue (expert-parallel decode): the normalised bf16 row also goes to `out[p]` on every GPU p (this
+// rank's region of p's gather buffer), and the CTA that finishes last advances the epoch and raises this rank's flag on
+// every GPU, so the kernel that consumes the gathered rows waits on flags instead of on an exchange kernel of its own.
+struct RmsBcast {
+  __nv_bfloat16* out[8];
+  uint32_t* flag[8];
+  int world;               // 0 = off
+  int pad;
+  uint32_t* epoch_ctr;
+  unsigned* done_ctr;
+};
+
 // One CTA per row.  Optional: residual[row] += delta[row] first (the sum is written back and is the
 // normalised input); optional MXFP8 output (e4m3 bytes + scale atoms) beside / instead of bf16.
 template <int VPT>   // 8-element vectors per thread (hidden <= 256 * 8 * VPT)
@@ -52,7 +64,7 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
                uint8_t* __restrict__ out_sf, int hidden, float eps, int ld_in, int ld_out, int sf32,
                const float* __restrict__ partials, int n_partials, long partial_stride, const uint32_t* wait_flags, int wait_n,
                const uint32_t* epoch_ptr, KernelStatus* st, const __nv_bfloat16* __restrict__ comb_y, const int* __restrict__ comb_rows,
-               const float* __restrict__ comb_w, int comb_k, int comb_ld, int part_inner, long part_inner_stride) {
+               const float* __restrict__ comb_w, int comb_k, int comb_ld, int part_inner, long part_inner_stride, const RmsBcast bc) {
   pdl_wait();
   pdl_trigger();
   const int row = blockIdx.x;
@@ -75,7 +87,11 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
       for (int i = 0; i < wait_n; ++i) if (!wait_flag_ge(wait_flags + i, want, st, 900, i)) { failed = 1; break; }
     }
     __syncthreads();
-    if (failed) return;
+    if (failed) {
+      // nothing is published (the consumers' own waits run out), but the arrival counter is left at zero for the next launch
+      if (bc.world > 0 && threadIdx.x == 0 && atomicAdd(bc.done_ctr, 1u) == gridDim.x - 1) *bc.done_ctr = 0;
+      return;
+    }
   }
   if (comb_y != nullptr) __syncthreads();
   float v[VPT][8];
@@ -153,6 +169,7 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
         amax = fmaxf(amax, fabsf(y[j]));
       }
       if (out != nullptr) store8(out + (size_t)row * ld_out + vi * 8, y);
+      for (int p = 0; p < bc.world; ++p) store8(bc.out[p] + (size_t)row * hidden + vi * 8, y);
     }
     if (out_q != nullptr) {
       // 4 consecutive threads hold one 32-element block
@@ -166,6 +183,20 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
         for (int j = 0; j < 8; ++j) { __nv_fp8_e4m3 f(y[j] * inv); q[j] = *reinterpret_cast<uint8_t*>(&f); }
         *reinterpret_cast<uint2*>(out_q + (size_t)row * hidden + vi * 8) = *reinterpret_cast<uint2*>(q);
         if ((vi & 3) == 0) out_sf[sf_atom_offset(row, vi >> 2, hidden >> 7, sf32)] = (uint8_t)e;
+      }
+    }
+  }
+  if (bc.world > 0) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // every CTA orders its rows before its arrival; the last one publishes with one system fence + release stores
+      __threadfence();
+      if (atomicAdd(bc.done_ctr, 1u) == gridDim.x - 1) {
+        __threadfence_system();
+        *bc.done_ctr = 0;
+        const uint32_t e = *bc.epoch_ctr + 1;
+        *bc.epoch_ctr = e;
+        for (int p = 0; p < bc.world; ++p) st_release_sys(bc.flag[p], e);
       }
     }
   }
@@ -719,8 +750,14 @@ static int rmsnorm_launch(void* residual, const void* delta, const void* x_in, c
                           int rows, int hidden, float eps, int ld_in, int ld_out, int sf32, const float* partials, int n_partials,
                           long partial_stride, const void* wait_flags, int wait_n, const void* epoch_ptr, void* status, cudaStream_t stream,
                           const void* comb_y = nullptr, const int* comb_rows = nullptr, const float* comb_w = nullptr, int comb_k = 0,
-                          int comb_ld = 0, int part_inner = 1, long part_inner_stride = 0) {
+                          int comb_ld = 0, int part_inner = 1, long part_inner_stride = 0, const RmsBcast* bcast = nullptr) {
   if (part_inner < 1) part_inner = 1;
+  RmsBcast bc;
+  memset(&bc, 0, sizeof(bc));
+  if (bcast != nullptr) {
+    bc = *bcast;
+    if (bc.world < 0 || bc.world > 8 || bc.epoch_ctr == nullptr || bc.done_ctr == nullptr) return fail("rmsnorm: bad gather arguments%s");
+  }
   if (comb_k > 16) return fail("rmsnorm: combine of more than 16 rows%s");
   if (hidden % 8 || hidden > 256 * 8 * 4) return fail("rmsnorm: hidden must be a multiple of 8 and <= 8192%s");
   if (out_q != nullptr && hidden % 128) return fail("rmsnorm: MXFP8 output needs hidden %% 128 == 0%s");
@@ -729,7 +766,7 @@ static int rmsnorm_launch(void* residual, const void* delta, const void* x_in, c
 #define GB_RMS(V) launch_k(rmsnorm_kernel<V>, rows, 256, 0, stream, (__nv_bfloat16*)residual, (const __nv_bfloat16*)delta, \
     (const __nv_bfloat16*)x_in, (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)out_q, (uint8_t*)out_sf, hidden, eps, ld_in, ld_out, sf32, \
     partials, n_partials, partial_stride, (const uint32_t*)wait_flags, wait_n, (const uint32_t*)epoch_ptr, (KernelStatus*)status, \
-    (const __nv_bfloat16*)comb_y, comb_rows, comb_w, comb_k, comb_ld, part_inner, part_inner_stride)
+    (const __nv_bfloat16*)comb_y, comb_rows, comb_w, comb_k, comb_ld, part_inner, part_inner_stride, bc)
   if (nvec <= 256) GB_RMS(1); else if (nvec <= 512) GB_RMS(2); else if (nvec <= 768) GB_RMS(3); else GB_RMS(4);
 #undef GB_RMS
   GB_CUDA_OK(cudaGetLastError());
@@ -749,6 +786,22 @@ GB_API int gb_rmsnorm_reduce(void* residual, const float* partials, int n_partia
                              const void* epoch_ptr, void* status, cudaStream_t stream) {
   return rmsnorm_launch(residual, nullptr, nullptr, weight, out, out_q, out_sf, rows, hidden, eps, hidden, hidden, sf32, partials, n_partials,
                         partial_stride, wait_flags, wait_n, epoch_ptr, status, stream);
+}
+
+// gb_rmsnorm_reduce whose bf16 result is also all-gathered: row r goes to bcast->out[p] + r * hidden on every GPU p and the flags
+// bcast->flag[p] are raised with the advanced epoch once all rows are stored (see RmsBcast).  `out` may be null.
+GB_API int gb_rmsnorm_reduce_bcast(void* residual, const float* partials, int n_partials, long partial_stride, const void* weight, void* out,
+                                   void* out_q, void* out_sf, int rows, int hidden, float eps, int sf32, const void* wait_flags, int wait_n,
+                                   const void* epoch_ptr, void* status, const RmsBcast* bcast, cudaStream_t stream) {
+  return rmsnorm_launch(residual, nullptr, nullptr, weight, out, out_q, out_sf, rows, hidden, eps, hidden, hidden, sf32, partials, n_partials,
+                        partial_stride, wait_flags, wait_n, epoch_ptr, status, stream, nullptr, nullptr, nullptr, 0, 0, 1, 0, bcast);
+}
+
+// residual += delta, RMSNorm, MXFP8 copy (optional) and the all-gather of the bf16 rows (see RmsBcast).
+GB_API int gb_rmsnorm_bcast(void* residual, const void* delta, const void* weight, void* out_q, void* out_sf, int rows, int hidden, float eps,
+                            int ld_in, int sf32, const RmsBcast* bcast, cudaStream_t stream) {
+  return rmsnorm_launch(residual, delta, nullptr, weight, nullptr, out_q, out_sf, rows, hidden, eps, ld_in, hidden, sf32, nullptr, 0, 0, nullptr, 0,
+                        nullptr, nullptr, stream, nullptr, nullptr, nullptr, 0, 0, 1, 0, bcast);
 }
 
 // The same when every rank's slot holds `n_inner` K-split partials, `inner_stride` elements apart: n_ranks * n_inner slabs are summed

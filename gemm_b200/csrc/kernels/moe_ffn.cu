@@ -23,6 +23,12 @@
 // one phase-0 tile more than the others skip the first rounds of phase 1 (about the cost of that tile), which keeps the
 // finish times level.  The CTA that finishes last zeroes the counters for the next launch.
 //
+// Optional last phase (expert parallelism where every rank holds all tokens of the step): the router-weighted sum of a token's
+// local expert rows, stored as an fp32 row into this rank's slot on the token's home GPU.  Token t is taken by CTA t % grid
+// after its tiles; its epilogue warps wait (bounded) on per-block counters of the phase-1 tiles that produced the rows.  The last
+// CTA advances the epoch and raises this rank's flag on every GPU, which is what the next RMSNorm (the consumer of the
+// slots) waits for.  With it a layer's expert block is one launch and one flag round.
+//
 // Replaces in the reference: the per-expert loops over mmq_*_grouped + silu_mul + down GEMV of the MoE decode path
 // (cuda/llm/cuda_llm_runner.c:5295-7329, 455).
 #include "sm100.cuh"
@@ -51,9 +57,16 @@ struct FfnArgs {
   int hidden, inter, num_groups, capacity;
   const int* seg_start;  // [G] first row of each expert's segment (multiple of 32; segments are packed in expert order)
   const int* seg_count;  // [G]
-  unsigned* ctr;         // [capacity / 32] epilogue warps done per block, then [kFfnMaxBlocks] = CTAs done, [+1] = grid-wide abort
+  unsigned* ctr;         // [kFfnMaxBlocks] phase-0 epilogue warps done per block, [kFfnMaxBlocks] the same for phase 1, then CTAs done, grid-wide abort
   int stages;
   KernelStatus* status;
+  // ---- optional combine + scatter phase (world > 0)
+  const int* pair_row;   // [n_tok * topk] row of y holding (token, j), negative = not computed here
+  const float* pair_w;   // [n_tok * topk] router weights
+  int n_tok, topk, tokens_per_rank, world;
+  float* slot[8];        // this rank's slot on GPU p: fp32 [tokens_per_rank, hidden]
+  uint32_t* flag[8];     // this rank's flag on GPU p
+  uint32_t* epoch_ctr;
 };
 
 struct FfnTile { int phase, b, nb; };
@@ -106,7 +119,8 @@ moe_ffn_kernel(const __grid_constant__ CUtensorMap tmW13, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k1 = a.hidden >> 7, k2 = a.inter >> 7;   // k-steps of the two phases
   const int nb1 = a.inter >> 7, nb2 = a.hidden >> 8; // tiles per token block
-  unsigned* done_ctr = a.ctr + kFfnMaxBlocks;
+  unsigned* ctr2 = a.ctr + kFfnMaxBlocks;
+  unsigned* done_ctr = a.ctr + 2 * kFfnMaxBlocks;
   unsigned* grid_abort = done_ctr + 1;
 
   if (threadIdx.x == 0) {
@@ -288,8 +302,62 @@ moe_ffn_kernel(const __grid_constant__ CUtensorMap tmW13, const __grid_constant_
             o[(size_t)j * a.ldy] = __float2bfloat16(__uint_as_float(r0[j]));
             o[(size_t)j * a.ldy + half] = __float2bfloat16(__uint_as_float(r1[j]));
           }
+        if (a.world > 0) {
+          __threadfence();
+          __syncwarp();
+          if (lane == 0) atomicAdd(ctr2 + t.b, 1u);
+        }
       }
       if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+    }
+    // ---------------------------------------------------------------- combine + scatter (the 128 epilogue threads, token by token)
+    if (a.world > 0) {
+      __shared__ int c_rows[16];
+      __shared__ float c_w[16];
+      __shared__ int c_fail[2];                     // by iteration parity: the reset of one iteration cannot overtake the readers of the one before
+      const int te = threadIdx.x - 64;               // 0..127
+      const unsigned want = (unsigned)nb2 * 4u;
+      int par = 0;
+      for (int tok = blockIdx.x; tok < a.n_tok; tok += gridDim.x, par ^= 1) {
+        if (te == 0) c_fail[par] = *abort_flag ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (te < a.topk) {
+          const int r = a.pair_row[(size_t)tok * a.topk + te];
+          c_rows[te] = r;
+          c_w[te] = a.pair_w[(size_t)tok * a.topk + te];
+          if (r >= 0) {
+            // the row exists once every phase-1 tile of its token block has stored
+            const unsigned* c = ctr2 + (r >> 5);
+            const uint64_t t0 = globaltimer_ns();
+            for (uint32_t it = 0; ld_acquire_gpu(c) < want; ++it) {
+              if ((it & 63u) == 63u) {
+                if (*abort_flag || ld_acquire_gpu(grid_abort) != 0) { c_fail[par] = 1; break; }
+                if (globaltimer_ns() - t0 > kMbarBudgetNs) {
+                  report_status(a.status, ST_TIMEOUT_FLAG, 620, r >> 5, (int)want, (int)ld_acquire_gpu(c));
+                  *abort_flag = 1; atomicExch(grid_abort, 1u); c_fail[par] = 1; break;
+                }
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (c_fail[par]) break;                       // uniform: every thread reads the same shared word after the barrier
+        const int home = tok / a.tokens_per_rank, lr = tok - home * a.tokens_per_rank;
+        float* dst = a.slot[home] + (size_t)lr * a.hidden;
+        for (int v = te; v < (a.hidden >> 3); v += 128) {
+          float accv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int j = 0; j < a.topk; ++j) {
+            const int r = c_rows[j];
+            if (r < 0) continue;
+            const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(a.y + (size_t)r * a.ldy + v * 8));
+            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(hh[i]); accv[2 * i] += c_w[j] * f.x; accv[2 * i + 1] += c_w[j] * f.y; }
+          }
+          reinterpret_cast<float4*>(dst + v * 8)[0] = make_float4(accv[0], accv[1], accv[2], accv[3]);
+          reinterpret_cast<float4*>(dst + v * 8)[1] = make_float4(accv[4], accv[5], accv[6], accv[7]);
+        }
+      }
     }
   }
 
@@ -308,9 +376,18 @@ moe_ffn_kernel(const __grid_constant__ CUtensorMap tmW13, const __grid_constant_
     if (atomicAdd(done_ctr, 1u) == gridDim.x - 1) {
       __threadfence();
       const int nclr = min(kFfnMaxBlocks, (a.capacity + 31) >> 5);
-      for (int i = 0; i < nclr; ++i) a.ctr[i] = 0;
+      for (int i = 0; i < nclr; ++i) { a.ctr[i] = 0; ctr2[i] = 0; }
       *grid_abort = 0;
       *done_ctr = 0;
+      if (a.world > 0) {
+        // every CTA ordered its slot rows before its arrival (fence + atomic): publish them with one system-scope fence
+        __threadfence_system();
+        const uint32_t e = *a.epoch_ctr + 1;
+        *a.epoch_ctr = e;
+        for (int p = 0; p < a.world; ++p) {
+          asm volatile("st.release.sys.global.u32 [%0], %1;" :: "l"(a.flag[p]), "r"(e) : "memory");
+        }
+      }
     }
   }
 }
@@ -324,7 +401,7 @@ GB_API int gb_moe_ffn_supported(int hidden, int inter, int num_groups, int capac
          capacity > 0 && capacity % 32 == 0 && capacity / 32 <= kFfnMaxBlocks;
 }
 // Number of 32-bit counters `ctr` must hold (zeroed once by the caller; the kernel leaves them zeroed).
-GB_API int gb_moe_ffn_ctr_count() { return kFfnMaxBlocks + 2; }
+GB_API int gb_moe_ffn_ctr_count() { return 2 * kFfnMaxBlocks + 2; }
 
 // The tile sequence of CTA `cta` of a grid of `grid` CTAs, as the kernel walks it: out[3 * i + 0..2] = (phase, block, n-block).
 // Returns the number of tiles (which may exceed `cap`; only `cap` are written).  Host-side: lets a test check that the
@@ -345,10 +422,14 @@ GB_API int gb_moe_ffn_schedule(int blocks, int hidden, int inter, int grid, int 
 //   xq / xsf    token rows [capacity, ldx] e4m3 + scale atoms in the one-atom-per-32-rows layout
 //   hq / hsf    scratch for the activations (written and read inside the launch)
 //   y           bf16 [capacity, ldy] result rows; rows of a segment beyond seg_count are not written
+//   world > 0   adds the combine + scatter phase: pair_row / pair_w [n_tok * topk], n_tok = tokens_per_rank * world tokens, slots[p] /
+//               flags[p] this rank's fp32 slot and flag on GPU p (as mapped here), epoch_ctr the exchange's epoch counter
 GB_API int gb_moe_ffn(const void* w13, const void* sf13, long sf13_bytes, const void* w2, const void* sf2, long sf2_bytes,
                       const void* xq, int ldx, const void* xsf, long xsf_bytes, void* hq, int ldh, void* hsf, long hsf_bytes,
                       void* y, int ldy, long y_bytes, int hidden, int inter, int num_groups, const int* seg_start,
-                      const int* seg_count, int capacity, unsigned* ctr, int ctr_count, void* status, cudaStream_t stream) {
+                      const int* seg_count, int capacity, unsigned* ctr, int ctr_count, const int* pair_row, const float* pair_w,
+                      int n_tok, int topk, int tokens_per_rank, void* const* slots, void* const* flags, int world, void* epoch_ctr,
+                      void* status, cudaStream_t stream) {
   if (!gb_moe_ffn_supported(hidden, inter, num_groups, capacity)) return fail("moe_ffn: unsupported shape%s (hidden=%ld inter=%ld)", "", hidden, inter);
   if (ctr == nullptr || ctr_count < gb_moe_ffn_ctr_count()) return fail("moe_ffn: counter buffer too small%s");
   const long k1 = hidden / 128, k2 = inter / 128, blocks = capacity / 32;
@@ -373,6 +454,14 @@ GB_API int gb_moe_ffn(const void* w13, const void* sf13, long sf13_bytes, const 
   a.hq = (uint8_t*)hq; a.y = (__nv_bfloat16*)y; a.ldh = ldh; a.ldy = ldy;
   a.hidden = hidden; a.inter = inter; a.num_groups = num_groups; a.capacity = capacity;
   a.seg_start = seg_start; a.seg_count = seg_count; a.ctr = ctr; a.status = (KernelStatus*)status;
+  if (world > 0) {
+    if (world > 8 || pair_row == nullptr || pair_w == nullptr || slots == nullptr || flags == nullptr || epoch_ctr == nullptr || topk < 1 ||
+        topk > 16 || tokens_per_rank < 1 || n_tok != tokens_per_rank * world || hidden % 8)
+      return fail("moe_ffn: bad combine arguments%s");
+    a.pair_row = pair_row; a.pair_w = pair_w; a.n_tok = n_tok; a.topk = topk; a.tokens_per_rank = tokens_per_rank; a.world = world;
+    a.epoch_ctr = (uint32_t*)epoch_ctr;
+    for (int p = 0; p < world; ++p) { a.slot[p] = (float*)slots[p]; a.flag[p] = (uint32_t*)flags[p]; }
+  }
   const int tail = 1024 + kFfnMaxBlocks * 3 + 256;
   int stages = (220 * 1024 - tail - 1024) / kFfnStage;
   if (stages > 8) stages = 8;

@@ -55,12 +55,21 @@ def sf_alloc(rows_padded: int, k: int, device, layout: int = 128, init: bool = T
     return torch.full(shape, 127, dtype=torch.uint8, device=device)
 
 
+class RmsBcast(ctypes.Structure):
+    """All-gather in the RMSNorm's epilogue (mirrors ``RmsBcast`` in csrc/kernels/elementwise.cu): where the bf16 rows go on every
+    GPU, the flags raised afterwards, the epoch and arrival counters."""
+    _fields_ = [("out", ctypes.c_void_p * 8), ("flag", ctypes.c_void_p * 8), ("world", ctypes.c_int), ("pad", ctypes.c_int),
+                ("epoch_ctr", ctypes.c_void_p), ("done_ctr", ctypes.c_void_p)]
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None,
-            quantize: bool = False, want_bf16: bool = True, sf_layout: int = 128, out_buf: Optional[torch.Tensor] = None):
+            quantize: bool = False, want_bf16: bool = True, sf_layout: int = 128, out_buf: Optional[torch.Tensor] = None,
+            bcast: Optional[RmsBcast] = None):
     """RMSNorm of ``x`` (or of ``residual += x`` when ``residual`` is given; the sum is written back).
 
     Returns the bf16 result, or ``(bf16 | None, MxTensor)`` when ``quantize`` asks for an MXFP8 copy that
-    feeds a block-scaled GEMM.
+    feeds a block-scaled GEMM.  ``bcast`` (only with K-split partial sums as ``x``): the kernel also stores the bf16 rows on
+    every GPU and raises the arrival flags; ``out_buf`` must then be the local destination among ``bcast.out``.
     """
     pend = None
     if hasattr(x, "buf") and hasattr(x, "materialize"):          # ops.gemm.PendingPartials: K-split partial sums, summed by this kernel
@@ -74,6 +83,14 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
                 rp = (rows + 127) // 128 * 128
                 q = torch.empty(rp, hidden, dtype=torch.uint8, device=residual.device)
                 sf = sf_alloc(rp, hidden, residual.device, sf_layout, init=False)
+            if bcast is not None:
+                # the local copy is one of the kernel's gather destinations: no separate bf16 store
+                rc = _native.cuda().gb_rmsnorm_reduce_bcast(_p(residual), _p(x.buf), _i(x.n), _l(rows * hidden), _p(w), _c(0), _p(q), _p(sf),
+                                                            _i(rows), _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0), _c(0), _i(0), _c(0),
+                                                            _c(_native.status_ptr()), ctypes.byref(bcast), _s())
+                _native.check(rc, "gb_rmsnorm_reduce_bcast")
+                out = out_buf[:rows]
+                return (out, MxTensor(q, sf, rows, hidden, sf_layout)) if quantize else out
             rc = _native.cuda().gb_rmsnorm_reduce(_p(residual), _p(x.buf), _i(x.n), _l(rows * hidden), _p(w), _p(out), _p(q), _p(sf), _i(rows),
                                                   _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0), _c(0), _i(0), _c(0),
                                                   _c(_native.status_ptr()), _s())
@@ -108,6 +125,11 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: Optional[tor
         rc = _native.cuda().gb_rmsnorm_combine(_p(residual), _p(pend.y), _p(pend.pair_row), _p(pend.weights), _i(pend.k), _i(pend.y.stride(0)),
                                                _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden), _f(eps), _i(1 if sf_layout == 32 else 0),
                                                _c(pend.wait_flags), _i(pend.wait_n), _c(pend.epoch_ptr), _c(_native.status_ptr()), _s())
+    elif residual is not None and bcast is not None:
+        assert x.stride(0) == residual.stride(0)
+        rc = _native.cuda().gb_rmsnorm_bcast(_p(residual), _p(x), _p(w), _p(q), _p(sf), _i(rows), _i(hidden), _f(eps), _i(residual.stride(0)),
+                                             _i(1 if sf_layout == 32 else 0), ctypes.byref(bcast), _s())
+        out = out_buf[:rows]
     elif residual is not None:
         rc = _native.cuda().gb_rmsnorm(_p(residual), _p(x), _c(0), _p(w), _p(out), _p(q), _p(sf), _i(rows), _i(hidden),
                                        _f(eps), _i(residual.stride(0)), _i(hidden), _i(1 if sf_layout == 32 else 0), _s())

@@ -186,9 +186,13 @@ def can_fuse_ffn(xq, w13, w2, n_groups: int, capacity: int) -> bool:
     return bool(_native.cuda().gb_moe_ffn_supported(_i(w13.k), _i(w2.k), _i(n_groups), _i(capacity)))
 
 
-def expert_ffn_fused(xq, w13, w2, n_groups: int, pl: "MoePlan") -> torch.Tensor:
+def expert_ffn_fused(xq, w13, w2, n_groups: int, pl: "MoePlan", scatter: Optional[dict] = None) -> torch.Tensor:
     """``y [capacity, hidden]`` bf16: rows of ``xq`` (an ``MxTensor`` in expert order, 32-row scale atoms) through
-    ``down(SiLU(gate(x)) * up(x))`` of their expert.  Rows beyond a segment's count are not written."""
+    ``down(SiLU(gate(x)) * up(x))`` of their expert.  Rows beyond a segment's count are not written.
+
+    ``scatter`` (expert parallelism, every rank holds all tokens): ``dict(weights, n_tok, k, tokens_per_rank, slots, flags, world,
+    epoch)``; the launch then also forms every token's router-weighted sum of its local rows and stores it (fp32) into this
+    rank's slot on the token's home GPU, and raises the flags (what ``gb_moe_combine_scatter`` does as a launch of its own)."""
     from . import elementwise as ew
     lib = _native.cuda()
     dev = xq.data.device
@@ -205,7 +209,12 @@ def expert_ffn_fused(xq, w13, w2, n_groups: int, pl: "MoePlan") -> torch.Tensor:
     rc = lib.gb_moe_ffn(_p(w13.mx.data), _p(w13.mx.sf), nb(w13.mx.sf), _p(w2.mx.data), _p(w2.mx.sf), nb(w2.mx.sf),
                         _p(xq.data), _i(xq.data.stride(0)), _p(xq.sf), nb(xq.sf), _p(hq), _i(hq.stride(0)), _p(hsf), nb(hsf),
                         _p(y), _i(y.stride(0)), nb(y), _i(hid), _i(inter), _i(n_groups), _p(pl.seg_start), _p(pl.seg_count), _i(cap),
-                        _p(ctr), _i(ctr.numel()), _c(_native.status_ptr()), _s())
+                        _p(ctr), _i(ctr.numel()),
+                        _p(pl.pair_row) if scatter else _c(0), _p(scatter["weights"]) if scatter else _c(0),
+                        _i(scatter["n_tok"] if scatter else 0), _i(scatter["k"] if scatter else 0),
+                        _i(scatter["tokens_per_rank"] if scatter else 0), scatter["slots"] if scatter else _c(0),
+                        scatter["flags"] if scatter else _c(0), _i(scatter["world"] if scatter else 0),
+                        _c(scatter["epoch"]) if scatter else _c(0), _c(_native.status_ptr()), _s())
     _native.check(rc, "gb_moe_ffn")
     return y
 

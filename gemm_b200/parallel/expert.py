@@ -36,6 +36,12 @@ from .fabric import Fabric
 _c, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 
 
+# token all-gather of the decode route as the epilogue of the RMSNorm in front of the MoE block (GB_FOLD_GATHER=0: exchange kernel)
+FOLD_GATHER = os.environ.get("GB_FOLD_GATHER", "1") != "0"
+# router-weighted sums + scatter of the decode route as the last phase of the fused expert kernel (GB_FOLD_COMBINE=0: own launch)
+FOLD_COMBINE = os.environ.get("GB_FOLD_COMBINE", "1") != "0"
+
+
 class PendingSlots:
     """fp32 partial sums of a MoE layer sitting in the per-rank slots of this GPU; finished by the next RMSNorm."""
 
@@ -104,7 +110,25 @@ class ExpertParallel:
             g["epoch"], g["done"] = f.ctl_word(), f.ctl_word()
             g["slot_ptrs"] = (ctypes.c_void_p * 8)(*[f.peer_ptr(p, g["slots_off"]) + self.ep_rank * cap * hid * 4 for p in range(w)])
             g["flag_ptrs"] = (ctypes.c_void_p * 8)(*[f.peer_ptr(p, g["flags_off"]) + 4 * self.ep_rank for p in range(w)])
+            # The token all-gather as the epilogue of the RMSNorm in front of the MoE block: the norm stores its rows into this rank's
+            # region of every GPU's gather buffer and raises flags the MoE front-end kernel waits on (no exchange launch).  Only
+            # where that front-end kernel takes the gathered batch; reuse of the buffer is ordered by the layer's combine round.
+            g["fold"] = bool(FOLD_GATHER and moe.MOE_PREP and _native.cuda().gb_moe_prep_supported(_i(w * cap), _i(hid), _i(e), _i(k)))
+            if g["fold"]:
+                ag = g["ag"]
+                g["gflags_off"] = f.alloc(32)
+                g["gepoch"], g["gdone"] = f.ctl_word(), f.ctl_word()
+                g["recv_local"] = f.view(ag.out_off + self.ep_rank * ag.bytes_per_dst, (cap, hid), torch.bfloat16)
+                bc = ew.RmsBcast()
+                for p in range(w):
+                    bc.out[p] = f.peer_ptr(p, ag.out_off) + self.ep_rank * ag.bytes_per_dst
+                    bc.flag[p] = f.peer_ptr(p, g["gflags_off"]) + 4 * self.ep_rank
+                bc.world, bc.epoch_ctr, bc.done_ctr = w, g["gepoch"], g["gdone"]
+                g["bc"] = bc
+                ag.out_view.zero_()          # rows of a region beyond a rank's token count are read (and dropped) by the front end: keep them finite
             self._gather[cap] = g
+        self._bcast_done = None
+        self.stats = {"fold_gather": 0, "fold_combine": 0}      # how often the folded forms ran (tests assert on them)
 
     def _bucket(self, t: int) -> dict:
         """Buffer geometry for a forward pass of ``t`` tokens (rounded up so that all ranks agree)."""
@@ -164,13 +188,25 @@ class ExpertParallel:
         if not (self.fused and self.use_gather and lw.w13 is not None and getattr(self, "_gather", None)) or rows > self.gather_max:
             return None
         caps = [c for c in self._gather if rows <= c]
-        return self._gather[min(caps)]["stage"] if caps else None
+        if not caps:
+            return None
+        g = self._gather[min(caps)]
+        return g["recv_local"] if g["fold"] else g["stage"]
 
     def add_norm(self, delta, weight, eps, residual, quantize=False, want_bf16=True, sf_layout=128, out_buf=None):
         if not isinstance(delta, PendingSlots):
             kw = dict(quantize=quantize, want_bf16=want_bf16, sf_layout=sf_layout) if quantize else {}
             if out_buf is not None:
                 kw["out_buf"] = out_buf
+                g = next((x for x in self._gather.values() if x["fold"] and x["recv_local"].data_ptr() == out_buf.data_ptr()), None) \
+                    if getattr(self, "_gather", None) else None
+                partial_sums = hasattr(delta, "buf") and delta.buf.is_cuda and residual is not None and residual.stride(0) == self.cfg.hidden
+                plain = torch.is_tensor(delta) and delta.is_cuda and residual is not None and delta.stride(0) == residual.stride(0)
+                if g is not None and (partial_sums or plain):
+                    # o_proj's result (K-split partial sums, or plain rows): added, normalised and all-gathered by one kernel
+                    kw["bcast"] = g["bc"]
+                    self._bcast_done = g
+                    self.stats["fold_gather"] += 1
             return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
         f, g = self.fab, delta.g
         rows, hidden, cap = delta.rows, self.cfg.hidden, g["cap"]
@@ -207,11 +243,21 @@ class ExpertParallel:
         k, inter, hid = cfg.n_experts_used, cfg.expert_ffn, cfg.hidden
         g = self._gather[min(c for c in self._gather if t <= c)]
         cap = g["cap"]
-        if h.data_ptr() != g["stage"].data_ptr():          # the norm in front of this block usually wrote straight into the staging buffer
-            g["stage"][:t].copy_(h)
-        allh = g["ag"].all_gather(g["stage"]).view(torch.bfloat16).view(w * cap, hid)
+        folded = self._bcast_done is g and h.data_ptr() == g["recv_local"].data_ptr()
+        self._bcast_done = None
         rt = dict(mode=cfg.router, bias=lw.router_bias, renorm=cfg.norm_topk, routed_scale=cfg.routed_scale,
                   local_range=(self.ep_rank * self.e_local, self.e_local))
+        if folded:
+            # the norm in front of this block has already stored the rows on every GPU: the front-end kernel waits for the flags
+            allh = g["ag"].out_view.view(torch.bfloat16).view(w * cap, hid)
+            if not moe.can_prep(allh, lw.router, k):
+                raise RuntimeError("expert parallel: the gathered batch does not fit the MoE front-end kernel the folded all-gather relies on "
+                                   "(set GB_FOLD_GATHER=0)")
+            rt.update(wait_flags=f.local_base + g["gflags_off"], wait_n=w, epoch_ptr=g["gepoch"])
+        else:
+            if h.data_ptr() != g["stage"].data_ptr():      # a norm that could not gather wrote somewhere else: stage, then exchange
+                g["stage"][:t].copy_(h)
+            allh = g["ag"].all_gather(g["stage"]).view(torch.bfloat16).view(w * cap, hid)
         if self.mx:
             from ..models.transformer import expert_gate_up_mx
             tn = 32
@@ -221,7 +267,13 @@ class ExpertParallel:
                 ids, wts, pl = moe.route_plan_hidden(allh, lw.router, k, self.e_local, tn, **rt)
                 xq = ew.mx_quantize(allh, pl.row_token, sf_layout=tn)
             if moe.can_fuse_ffn(xq, lw.w13, lw.w2, self.e_local, pl.capacity):
-                y = moe.expert_ffn_fused(xq, lw.w13, lw.w2, self.e_local, pl)
+                # gate/up, down, the router-weighted sums and their scatter to the tokens' home GPUs: one launch, one flag round
+                sc = dict(weights=wts, n_tok=w * cap, k=k, tokens_per_rank=cap, slots=g["slot_ptrs"], flags=g["flag_ptrs"], world=w,
+                          epoch=g["epoch"]) if FOLD_COMBINE else None
+                y = moe.expert_ffn_fused(xq, lw.w13, lw.w2, self.e_local, pl, scatter=sc)
+                if sc is not None:
+                    self.stats["fold_combine"] += 1
+                    return PendingSlots(g, t)
             else:
                 hq = torch.empty(pl.capacity, inter, dtype=torch.uint8, device=h.device)
                 hsf = ew.sf_alloc(pl.capacity, inter, h.device, tn, init=False)

@@ -143,6 +143,13 @@ def check_expert_parallel(rank, world, dev, fmt, fused, gather=True):
         print(f"EP({fmt}, fused={fused}, gather={gather}) rel per step: {[round(r, 4) for r in rels]}", flush=True)
     for r in rels:
         assert r < tol, f"EP({fmt}, fused={fused}, gather={gather}) differs from the single-GPU engine: rel {r}"
+    if fused and gather:
+        # the decode steps took the folded forms: all-gather in the RMSNorm's epilogue, combine + scatter inside the expert kernel
+        if rank == 0:
+            print(f"EP({fmt}) folded launches: {par.stats}", flush=True)
+        assert par.stats["fold_gather"] > 0, par.stats
+        if fmt == "mxfp8":
+            assert par.stats["fold_combine"] > 0, par.stats
     dist.barrier()
     par.close()
 
