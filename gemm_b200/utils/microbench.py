@@ -7,13 +7,16 @@ each op a single time without timing (the form to put under a profiler).
 
 Cases
   gemm         dense projections: decode (64 tokens) and prefill (16384 tokens), bf16 and MXFP8
-  moe_decode   grouped expert GEMMs (gate/up with SwiGLU + re-quantisation, down) for 64 tokens x top-8 of 128 experts
+  moe_decode   grouped expert GEMMs (gate/up with SwiGLU + re-quantisation, down) for 64 tokens x top-8 of 128 experts, as two
+               launches and as the one persistent launch
   moe_prefill  the same for 16384 tokens
   attn_decode  paged flash-decode, 64 sequences x 2048 cached tokens, 32 query / 4 KV heads
   attn_prefill causal prefill, 8 sequences x 2048 tokens
   lm_head      64 x 151936 x 2048 with the arg-max epilogue
   quant        ggml-quantised projections of the Qwen3-32B shape (Q4_K and Q8_0 blocks kept in HBM): fused dequant-GEMV for
                1 and 4 tokens, fused dequant-GEMM for 8, 64 and 4096 tokens
+  small        the kernels around them: RMSNorm + residual + MXFP8 copy, QK-norm + RoPE + cache write (64 and 16384 tokens), the
+               one-launch MoE front end, sampler and arg-max over 64 x 151936 logits, the Delta-Net recurrence (decode, prefill)
   spec_verify  whole-model step over 1, 2, 3 and 5 positions per sequence (speculative verification against plain decode);
                builds the full Qwen3-30B-A3B shape, not part of ``all``
 
@@ -258,9 +261,54 @@ def case_quant(args):
             del w
 
 
+def case_small(args):
+    """The kernels around the GEMMs and attention at the benchmark's shapes: RMSNorm (+ residual + MXFP8 copy), QK-norm + RoPE +
+    cache write, the one-launch MoE front end, the sampler, the Delta-Net recurrence; decode size (64 tokens) and, for the
+    bandwidth-bound ones, a prefill chunk (16384 tokens, more than L2)."""
+    from ..ops import deltanet as dn, sampling
+    h, hq, hkv, d = 2048, 32, 4, 128
+    nw = torch.ones(h, device="cuda", dtype=torch.bfloat16)
+    for t in (64, 16384):
+        x = torch.randn(t, h, device="cuda").bfloat16()
+        res = torch.randn(t, h, device="cuda").bfloat16()
+        _run(f"rmsnorm_add_quant_{t}x{h}", lambda: ew.rmsnorm(x, nw, 1e-6, residual=res, quantize=True, sf_layout=128), 0.0,
+             t * h * (2 + 2 + 2 + 2 + 1), args)
+        qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda").bfloat16()
+        pos = torch.arange(t, device="cuda", dtype=torch.int32) % 4096
+        slots = torch.randperm(t, device="cuda").to(torch.int32)
+        kc = torch.empty(t, hkv, d, device="cuda", dtype=torch.bfloat16)
+        vc = torch.empty_like(kc)
+        qw = torch.ones(d, device="cuda", dtype=torch.bfloat16)
+        tab = ew.rope_table(4096, d, 1e6, "cuda")
+        _run(f"qk_norm_rope_{t}", lambda: ew.qk_norm_rope(qkv, pos, slots, qw, qw, kc, vc, hq, hkv, d, 1e6, 1e-6, 1.0, table=tab), 0.0,
+             2 * t * (hq + 2 * hkv) * d * 2, args)
+    x = torch.randn(64, h, device="cuda").bfloat16()
+    router = (torch.randn(128, h, device="cuda") * 0.05).bfloat16()
+    if moe.can_prep(x, router, 8):
+        _run("moe_prep_64x2048_top8of128", lambda: moe.prep_hidden(x, router, 8, 128, 32), 2.0 * 64 * 128 * h, 128 * h * 2 + 64 * h * 2 + 512 * h, args)
+    logits = torch.randn(64, 151936, device="cuda")
+    _run("sampler_top_p_64x151936", lambda: sampling.sample(logits, 0.8, 40, 0.95, seed=1, step=3), 0.0, logits.numel() * 4, args)
+    _run("argmax_64x151936", lambda: sampling.argmax(logits), 0.0, logits.numel() * 4, args)
+    # Delta-Net layer of the Qwen3.5 shape: 16 key / 32 value heads of 128, one state matrix per value head and sequence
+    ng, hv, ds = 16, 32, 128
+    for name, lens in (("decode_64", [1] * 64), ("prefill_8x512", [512] * 8)):
+        t = sum(lens)
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        sl = torch.arange(len(lens), dtype=torch.int32, device="cuda")
+        qkv = (torch.randn(t, (2 * ng + hv) * ds, device="cuda") * 0.5).bfloat16()
+        z = torch.randn(t, hv * ds, device="cuda").bfloat16()
+        ab = torch.randn(t, 2 * hv, device="cuda")
+        a = -(torch.rand(hv, device="cuda") * 2 + 0.1)
+        bias = torch.randn(hv, device="cuda") * 0.5
+        nwd = torch.rand(ds, device="cuda") + 0.5
+        st = torch.randn(len(lens), hv, ds, ds, device="cuda") * 0.1
+        _run(f"deltanet_{name}", lambda: dn.deltanet(qkv, z, ab, a, bias, nwd, st, cu, sl, ng, hv, ds, 1e-6), 4.0 * t * hv * ds * ds,
+             2 * st.numel() * 4 + qkv.numel() * 2 + 2 * z.numel() * 2, args)
+
+
 MODEL_CASES = {"spec_verify": case_spec_verify}      # build the whole benchmark model: not part of --case all
 CASES = {"gemm": case_gemm, "moe_decode": case_moe_decode, "moe_prefill": case_moe_prefill, "attn_decode": case_attn_decode,
-         "attn_prefill": case_attn_prefill, "lm_head": case_lm_head, "quant": case_quant}
+         "attn_prefill": case_attn_prefill, "lm_head": case_lm_head, "quant": case_quant, "small": case_small}
 
 
 def main(argv=None):
