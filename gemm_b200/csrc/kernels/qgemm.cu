@@ -34,6 +34,8 @@ struct QGemmArgs {
   void* out; int ldo; int out_f32;
   const float* bias;
   int n_out, m_tok, num_kb, row_tiles, tok_tiles;
+  int splits, kb_per;            // K splits per output tile (>= 1) and 256-column blocks per split
+  long partial_stride;           // splits > 1: split ks stores its fp32 partial at out + ks * partial_stride (elements)
   int b_stages, raw_stages;
   KernelStatus* status;
 };
@@ -111,7 +113,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles = args.row_tiles * args.tok_tiles;
+  const int n_tiles = args.row_tiles * args.tok_tiles * args.splits;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) { mbar_init(&a_full[i], kQgUnpackThreads / 32); mbar_init(&a_empty[i], 1); mbar_init(&accf[i], 1); mbar_init(&acce[i], 4); }
@@ -135,9 +137,11 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
       int rs = 0; uint32_t rph = 0; int bs = 0; uint32_t bph = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
-        const int rt = t % args.row_tiles, tb = t / args.row_tiles;
+        const int ksp = t % args.splits, tt = t / args.splits;
+        const int rt = tt % args.row_tiles, tb = tt / args.row_tiles;
         const uint8_t* wt = args.w + (size_t)rt * args.num_kb * RAW;
-        for (int kb = 0; ok && kb < args.num_kb; ++kb) {
+        const int kb0 = ksp * args.kb_per, kb1 = min(args.num_kb, kb0 + args.kb_per);
+        for (int kb = kb0; ok && kb < kb1; ++kb) {
           if (!mbar_wait(&raw_empty[rs], rph ^ 1, abort_flag, args.status, 1200, rs)) { ok = false; break; }
           mbar_expect_tx(&raw_full[rs], RAW);
           bulk_load(rawb + (size_t)rs * RAW_PAD, wt + (size_t)kb * RAW, RAW, &raw_full[rs]);
@@ -164,7 +168,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
         if (!mbar_wait(&acce[acc], acc_ph ^ 1, abort_flag, args.status, 1210, acc)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d0 = tmem_base + acc * TN;
-        for (int ks = 0; ok && ks < 2 * args.num_kb; ++ks) {
+        const int kb0 = (t % args.splits) * args.kb_per, nkb = min(args.num_kb, kb0 + args.kb_per) - kb0;
+        for (int ks = 0; ok && ks < 2 * nkb; ++ks) {
           if (!mbar_wait(&a_full[as], aph, abort_flag, args.status, 1211, as)) { ok = false; break; }
           if (!mbar_wait(&b_full[bs], bph, abort_flag, args.status, 1212, bs)) { ok = false; break; }
           tc_fence_after();
@@ -192,14 +197,16 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
     int acc = 0; uint32_t acc_ph = 0;
     bool ok = true;
     for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
-      const int rt = t % args.row_tiles, tb = t / args.row_tiles;
+      const int ksp = t % args.splits, tt = t / args.splits;
+      const int rt = tt % args.row_tiles, tb = tt / args.row_tiles;
       if (!mbar_wait(&accf[acc], acc_ph, abort_flag, args.status, 1220, acc)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tacc = tmem_base + acc * TN + ((uint32_t)(q * 32) << 16);
       const int n = rt * 128 + row;
       const bool n_ok = n < args.n_out;
-      const float bias = (args.bias != nullptr && n_ok) ? args.bias[n] : 0.f;
+      const float bias = (args.bias != nullptr && n_ok && ksp == 0) ? args.bias[n] : 0.f;
       const int tok0 = tb * TN, valid = min(TN, args.m_tok - tok0);
+      const size_t part = (size_t)ksp * (size_t)args.partial_stride;
 #pragma unroll 1
       for (int c = 0; c < TN; c += 16) {
         uint32_t r[16];
@@ -210,7 +217,7 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
         for (int j = 0; j < 16; ++j) {
           if (c + j >= valid) break;
           const float v = __uint_as_float(r[j]) + bias;
-          const size_t off = (size_t)(tok0 + c + j) * args.ldo + n;
+          const size_t off = part + (size_t)(tok0 + c + j) * args.ldo + n;
           if (args.out_f32) reinterpret_cast<float*>(args.out)[off] = v;
           else reinterpret_cast<__nv_bfloat16*>(args.out)[off] = __float2bfloat16(v);
         }
@@ -227,7 +234,8 @@ qgemm_kernel(const __grid_constant__ CUtensorMap tmX, const QGemmArgs args) {
     int rs = 0; uint32_t rph = 0; int as = 0; uint32_t aph = 0;
     bool ok = true;
     for (int t = blockIdx.x; ok && t < n_tiles; t += gridDim.x) {
-      for (int kb = 0; ok && kb < args.num_kb; ++kb) {
+      const int kb0 = (t % args.splits) * args.kb_per, kb1 = min(args.num_kb, kb0 + args.kb_per);
+      for (int kb = kb0; ok && kb < kb1; ++kb) {
         if (!mbar_wait(&raw_full[rs], rph, abort_flag, args.status, 1230, rs)) { ok = false; break; }
         const uint8_t* rb = rawb + (size_t)rs * RAW_PAD;
         for (int h = 0; h < 2; ++h) {
@@ -295,7 +303,7 @@ static int launch_qgemm(const CUtensorMap& tmX, QGemmArgs a, cudaStream_t stream
   static bool attr_set = false;
   if (!attr_set) { GB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024)); attr_set = true; }
   int grid = sm_count();
-  const int tiles = a.row_tiles * a.tok_tiles;
+  const int tiles = a.row_tiles * a.tok_tiles * a.splits;
   if (tiles < grid) grid = tiles;
   launch_k(kern, grid, kQgThreads, smem, stream, tmX, a);
   GB_CUDA_OK(cudaGetLastError());
@@ -307,10 +315,10 @@ static int launch_qgemm(const CUtensorMap& tmX, QGemmArgs a, cudaStream_t stream
 using namespace gb;
 
 // w: tiled Q4_K (ggml type 12) or Q8_0 (8) weights, ceil(n_out / 128) row tiles x k / 256 K tiles.  x bf16 [m, ldx].
-// out bf16 (or f32) [m, ldo].  tn: token tile 16, 32, 64 or 128.
+// out bf16 (or f32) [m, ldo].  tn: token tile 16, 32, 64 or 128.  splits > 1 cuts K: `out` is then f32 [splits][m, ldo] (slabs
+// m * ldo apart), one partial sum per split for the consumer to add; no split may be empty.
 GB_API int gb_qgemm(const void* w, int ggml_type, const void* x, int ldx, void* out, int ldo, int out_f32, const float* bias, int n_out,
-                    int k, int m, int tn, int reserved, void* status, cudaStream_t stream) {
-  (void)reserved;
+                    int k, int m, int tn, int splits, void* status, cudaStream_t stream) {
   if (ggml_type != 12 && ggml_type != 8) return fail("qgemm: only Q4_K and Q8_0 have a fused tensor-core path%s");
   if (k <= 0 || k % 256 || n_out <= 0) return fail("qgemm: k must be a positive multiple of 256%s");
   if (m <= 0) return 0;
@@ -321,6 +329,13 @@ GB_API int gb_qgemm(const void* w, int ggml_type, const void* x, int ldx, void* 
   memset(&a, 0, sizeof(a));
   a.w = (const uint8_t*)w; a.out = out; a.ldo = ldo; a.out_f32 = out_f32; a.bias = bias; a.n_out = n_out; a.m_tok = m; a.num_kb = k / 256;
   a.row_tiles = (n_out + 127) / 128; a.tok_tiles = (m + tn - 1) / tn; a.status = (KernelStatus*)status;
+  a.splits = splits > 1 ? splits : 1;
+  a.kb_per = (a.num_kb + a.splits - 1) / a.splits;
+  if (a.splits > 1) {
+    if (!out_f32) return fail("qgemm: K-split partials need an fp32 output%s");
+    if ((a.num_kb + a.kb_per - 1) / a.kb_per != a.splits) return fail("qgemm: a K split would be empty%s");
+    a.partial_stride = (long)m * ldo;
+  }
   const int t = ggml_type == 12 ? 0 : 1;
 #define GB_QG(TNV)                                                             \
   if (tn == TNV) return t == 0 ? launch_qgemm<0, TNV>(tmX, a, stream) : launch_qgemm<1, TNV>(tmX, a, stream);

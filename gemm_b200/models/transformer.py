@@ -198,6 +198,10 @@ def apply_linear_split(lw: LinearWeight, x: torch.Tensor, x_mx: Optional[MxTenso
     if lw.is_quant:
         if x.is_cuda and x.shape[0] <= qlinear.GEMV_MAX_TOKENS:
             return qlinear.gemv_partials(x, lw.q, bias=lw.bias)      # K-split partial sums, added by the consumer
+        if x.is_cuda:
+            sp = qlinear.pick_gemm_splits(lw.q.rows, lw.q.k, x.shape[0])
+            if sp > 1:
+                return qlinear.gemm_partials(x, lw.q, sp, bias=lw.bias)
         return apply_linear(lw, x, x_mx)
     if lw.fmt == "bf16" and SPLIT_PROJ and x is not None and x.is_cuda and lw.n % 128 == 0:
         sp = gemm.pick_partials(lw.n, x.shape[0], lw.k, False)

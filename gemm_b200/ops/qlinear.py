@@ -140,6 +140,38 @@ def gemm(x: torch.Tensor, w: QTensor, bias: Optional[torch.Tensor] = None, out: 
     return out
 
 
+def pick_gemm_splits(rows: int, k: int, m: int, sms: int = 148) -> int:
+    """K splits of the dequant-GEMM for a decode-sized projection with few row tiles (Qwen3-32B down projection: 40 tiles over
+    100 K blocks): the split count (at most 8, at least 8 K blocks per split, none empty) that fills the last round of CTAs best."""
+    if m > 64:
+        return 1
+    tiles, num_kb = (rows + 127) // 128, k // 256
+    best, best_eff = 1, 0.0
+    for sp in range(1, 9):
+        if sp > 1 and num_kb // sp < 8:
+            break
+        per = -(-num_kb // sp)
+        if -(-num_kb // per) != sp:
+            continue
+        units = tiles * sp
+        eff = units / (-(-units // sms) * sms)
+        if eff > best_eff * 1.05:
+            best, best_eff = sp, eff
+    return best
+
+
+def gemm_partials(x: torch.Tensor, w: QTensor, splits: int, bias: Optional[torch.Tensor] = None) -> PendingPartials:
+    """The dequant-GEMM cut along K: fp32 partial sums ``[splits, m, rows]`` for the consumer to add (as ``gemv_partials``)."""
+    m, k = x.shape
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.stride(1) == 1 and k == w.k and splits >= 1
+    out = torch.empty(splits, m, w.rows, dtype=torch.float32, device=x.device)
+    rc = _native.cuda().gb_qgemm(_c(w.data.data_ptr()), _i(w.ggml_type), _c(x.data_ptr()), _i(x.stride(0)), _c(out.data_ptr()), _i(w.rows),
+                                 _i(1), _c(bias.data_ptr()) if bias is not None else _c(0), _i(w.rows), _i(k), _i(m), _i(_pick_tn(m)),
+                                 _i(splits), _c(_native.status_ptr()), _stream())
+    _native.check(rc, "gb_qgemm")
+    return PendingPartials(out)
+
+
 def linear(x: torch.Tensor, w: QTensor, bias: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16) -> torch.Tensor:
     """``x @ w^T (+ bias)``: GEMV up to four tokens, tensor-core GEMM above; fp32 reference on CPU tensors."""
     if not x.is_cuda:
@@ -149,6 +181,9 @@ def linear(x: torch.Tensor, w: QTensor, bias: Optional[torch.Tensor] = None, out
         return y.to(out_dtype)
     if x.shape[0] <= GEMV_MAX_TOKENS:
         return gemv_partials(x, w, bias=bias).buf.sum(0).to(out_dtype)
+    sp = pick_gemm_splits(w.rows, w.k, x.shape[0])
+    if sp > 1:
+        return gemm_partials(x, w, sp, bias=bias).buf.sum(0).to(out_dtype)
     return gemm(x, w, bias=bias, out_dtype=out_dtype)
 
 

@@ -47,6 +47,23 @@ def test_gemm_matches_fp32_reference(t, rows, k, m):
     assert y.shape == ref.shape and _rel(y, ref) < 6e-3          # weights reach the tensor core rounded to bf16
 
 
+@pytest.mark.parametrize("t", [gt.Q4_K, gt.Q8_0])
+@pytest.mark.parametrize("rows,k,m,splits", [(256, 4096, 8, 2), (640, 8192, 24, 3), (128, 2048, 64, 8), (384, 2560, 5, 4)])
+def test_gemm_k_split_partials_add_up(t, rows, k, m, splits):
+    """The K-split form: every split writes its own fp32 slab (bias in the first only); their sum is the plain result."""
+    qw, x, ref = _case(t, rows, k, m, seed=rows + m + splits)
+    bias = torch.randn(rows, device="cuda")
+    pend = qlinear.gemm_partials(x, qw, splits, bias=bias)
+    torch.cuda.synchronize()
+    _native.assert_status_ok()
+    assert pend.buf.shape == (splits, m, rows)
+    assert _rel(pend.buf.sum(0), ref + bias) < 6e-3
+    # no slab is empty and none holds the whole sum
+    norms = pend.buf.float().flatten(1).norm(dim=1)
+    assert bool((norms > 0).all()) and float(norms.max()) < float((ref + bias).norm()) * 1.01
+    assert qlinear.pick_gemm_splits(5120, 25600, 8) > 1 and qlinear.pick_gemm_splits(51200, 5120, 8) == 1
+
+
 def test_gemm_bias_bf16_output_and_linear_dispatch():
     qw, x, ref = _case(gt.Q4_K, 640, 1024, 20, seed=5)
     bias = torch.randn(640, device="cuda")
