@@ -21,7 +21,7 @@
 // it issues the first TMA load of that block's activations, followed by a proxy fence (generic writes -> async-proxy reads).  A
 // phase-0 tile never waits, and every CTA finishes its phase-0 tiles before it can wait, so the waits always end.  CTAs that got
 // one phase-0 tile more than the others skip the first rounds of phase 1 (about the cost of that tile), which keeps the
-// finish times level.  The CTA that finishes last zeroes the counters for the next launch.
+// finish times level (not when phase 0 is less than one round: then every CTA takes its share of phase 1).  The CTA that finishes last zeroes the counters for the next launch.
 //
 // Optional last phase (expert parallelism where every rank holds all tokens of the step): the router-weighted sum of a token's
 // local expert rows, stored as an fp32 row into this rank's slot on the token's home GPU.  Token t is taken by CTA t % grid
@@ -77,7 +77,11 @@ struct FfnCursor {
   __host__ __device__ __forceinline__ FfnCursor(int blocks, int nb1_, int nb2_, int k1, int k2_steps, int grid, int cta)
       : t1(blocks * nb1_), t2(blocks * nb2_), nb1(nb1_), nb2(nb2_), p(grid), c(cta), i1(0) {
     r = t1 % p;
-    skip = r ? (k1 + k2_steps / 2) / k2_steps : 0;      // one phase-0 tile costs about k1 / k2 phase-1 tiles
+    // One phase-0 tile costs about k1 / k2 phase-1 tiles: the CTAs without the extra tile run that many rounds of phase 1
+    // ahead.  Only worth it when there is at least one full round of phase 0: the early phase-1 tiles then belong to token
+    // blocks whose phase-0 tiles are finished.  With fewer phase-0 tiles than CTAs every phase-1 tile has to wait for
+    // them anyway, and handing them all to the CTAs without a phase-0 tile would serialise them there.
+    skip = (r && t1 >= p) ? (k1 + k2_steps / 2) / k2_steps : 0;
     k2 = (c < r) ? skip : 0;
   }
   __host__ __device__ __forceinline__ bool next(FfnTile& t) {

@@ -39,3 +39,16 @@ def test_schedule_covers_every_tile_once(blocks, hidden, inter, grid):
     cost = [sum(hidden // 128 if t[0] == 0 else inter // 128 for t in seq) for seq in seqs]
     mean = sum(cost) / len(cost)
     assert max(cost) <= mean + hidden // 128 + inter // 128
+
+
+def test_less_than_one_round_of_phase_0_spreads_phase_1_over_all_ctas():
+    """One expert-parallel rank of eight: 16 token blocks give 96 gate/up tiles for 148 CTAs.  Every down tile has to wait for
+    them anyway, so the down tiles go round-robin over ALL CTAs (one each), not only to the 52 CTAs without a gate/up tile."""
+    seqs = _sequences(16, 2048, 768, 148)
+    per_cta = [sum(1 for t in seq if t[0] == 1) for seq in seqs]
+    assert max(per_cta) == 1 and sum(per_cta) == 16 * 8
+    # with at least one full round of phase 0 the CTAs without the extra tile do run ahead
+    seqs = _sequences(32, 2048, 768, 148)                     # 192 gate/up tiles: 44 CTAs take two
+    heavy = [sum(1 for t in seq if t[0] == 1) for seq in seqs[:44]]
+    light = [sum(1 for t in seq if t[0] == 1) for seq in seqs[44:]]
+    assert max(heavy) < min(light)
