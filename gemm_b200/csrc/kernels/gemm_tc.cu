@@ -185,6 +185,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   }
   if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   __syncthreads();                                   // barriers and the abort flag are initialised for everyone
+  // Weights do not depend on the kernel in front of this one.  For a plain decode-sized GEMM (static tile sequence, one scale
+  // group per k-step) the producer thread requests the weight tiles and weight scales of its first tile's first k-steps NOW,
+  // before the dependency wait: the DRAM latency of the first loads and the fill of the ring overlap the previous kernel's
+  // tail.  The stage's barrier gets the byte count of this part without an arrival; the token tile (and its arrival) follow
+  // in the producer loop below.
+  int pre_stages = 0;
+  if (threadIdx.x == 0 && args.num_groups == 0 && args.wait_n == 0 && SFG == 1) {
+    TileCursor<TN> cur0; Tile t0;
+    if (cur0.get(args, s_start, s_count, blockIdx.x, t0)) {
+      const int kb0 = t0.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+      const size_t row_bytes = (size_t)num_kb * 512;
+      const size_t o0 = (size_t)(t0.w_row0 >> 7) * row_bytes, o1 = (size_t)(t0.w_row1 >> 7) * row_bytes;
+      const bool sf_ok = MODE != 1 || args.sfa_bytes == 0 || (o0 + row_bytes <= args.sfa_bytes && (!DUAL || o1 + row_bytes <= args.sfa_bytes));
+      if (sf_ok) {
+        const int wy0 = ((t0.w_row0 >> 7) * num_kb) << 7, wy1 = ((t0.w_row1 >> 7) * num_kb) << 7;
+        for (int kb = kb0; kb < kb1 && pre_stages < S; ++kb, ++pre_stages) {
+          uint8_t* st = smem + (size_t)pre_stages * STAGE_BYTES;
+          mbar_expect_tx_only(&full_bar[pre_stages], NA * A_BYTES + (MODE == 1 ? NA * 512 : 0));
+          if (args.w_tiled) {
+            tma_load_2d(st, &tmW, &full_bar[pre_stages], 0, wy0 + (kb << 7));
+            if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[pre_stages], 0, wy1 + (kb << 7));
+          } else {
+            tma_load_2d(st, &tmW, &full_bar[pre_stages], kb * KB_ELEMS, t0.w_row0);
+            if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[pre_stages], kb * KB_ELEMS, t0.w_row1);
+          }
+          if (MODE == 1) {
+            uint8_t* sf = st + NA * A_BYTES + B_BYTES;
+            bulk_load(sf, args.sfa + o0 + (size_t)kb * 512, 512, &full_bar[pre_stages]);
+            if (DUAL) bulk_load(sf + SFG * 512, args.sfa + o1 + (size_t)kb * 512, 512, &full_bar[pre_stages]);
+          }
+        }
+      }
+    }
+  }
   pdl_wait();                                        // everything above overlapped the previous kernel's tail
   pdl_trigger();                                     // at most one dependent grid is resident ahead of its turn
   if (args.wait_n > 0) {
@@ -256,9 +290,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           uint8_t* st = smem + (size_t)s * STAGE_BYTES;
           // length of the scale group that starts at this k-step (0 = none starts here)
           const int glen = (MODE != 1) ? 0 : (SFG == 1) ? 1 : ((kb - kb0) % SFG == 0) ? min(SFG, kb1 - kb) : 0;
-          mbar_expect_tx(&full_bar[s], NA * A_BYTES + B_BYTES + (NA + SFB_ATOMS) * 512 * glen);
+          // the weight part of this CTA's first k-steps was requested before the dependency wait (see above)
+          const bool pre = ti == (int)blockIdx.x && kb - kb0 < pre_stages;
+          mbar_expect_tx(&full_bar[s], pre ? B_BYTES + SFB_ATOMS * 512 * glen : NA * A_BYTES + B_BYTES + (NA + SFB_ATOMS) * 512 * glen);
           const int kx = kb * KB_ELEMS;
-          if (args.w_tiled) {
+          if (pre) {
+          } else if (args.w_tiled) {
             tma_load_2d(st, &tmW, &full_bar[s], 0, wy0 + (kb << 7));
             if (DUAL) tma_load_2d(st + A_BYTES, &tmW, &full_bar[s], 0, wy1 + (kb << 7));
           } else {
@@ -270,8 +307,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             uint8_t* sf = st + NA * A_BYTES + B_BYTES;
             const uint32_t gbytes = (uint32_t)glen * 512;
             const size_t koff = (size_t)kb * 512;
-            bulk_load(sf, sfa0 + koff, gbytes, &full_bar[s]);
-            if (DUAL) bulk_load(sf + SFG * 512, sfa1 + koff, gbytes, &full_bar[s]);
+            if (!pre) bulk_load(sf, sfa0 + koff, gbytes, &full_bar[s]);
+            if (DUAL && !pre) bulk_load(sf + SFG * 512, sfa1 + koff, gbytes, &full_bar[s]);
 #pragma unroll
             for (int i = 0; i < SFB_ATOMS; ++i) bulk_load(sf + (NA + i) * SFG * 512, sfbp[i] + koff, gbytes, &full_bar[s]);
           }
