@@ -44,6 +44,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=0, help="debug only: run fewer layers (the JSON line then says so and is not a valid bench number)")
+    ap.add_argument("--kv", default="bf16", choices=["bf16", "int8"], help="KV cache pages: bf16, or int8 + scales read directly by the decode "
+                    "attention kernel (a reduced-precision mode: the JSON line is then marked as not the headline configuration)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--baseline-eager", action="store_true", help="--impl baseline: run the decode step without a CUDA graph")
     ap.add_argument("--parallel", default="auto", choices=["auto", "ep", "tp", "tp+ep"],
@@ -334,7 +336,7 @@ def main():
     pages_per_seq = (max_len + 127) // 128
     # one spare page per sequence at N > 1: the fused-vs-NCCL check below writes its scratch tokens there
     engine = Engine(weights, max_batch=b_local, max_seq_len=max_len, page_size=128, par=par, max_prefill_tokens=16384,
-                    num_pages=b_local * pages_per_seq + (b_local if n_gpus > 1 else 0))
+                    num_pages=b_local * pages_per_seq + (b_local if n_gpus > 1 else 0), kv_dtype=args.kv)
     if par is not None:
         par.attach(engine, cfg, max_tokens=16384)
 
@@ -447,7 +449,8 @@ def main():
         bt = torch.tensor([[p] for p in scratch], dtype=torch.int32)
         gchk = torch.Generator().manual_seed(1234 + (0 if tp else rank))
         ids = torch.randint(0, cfg.vocab, (b_local * n_tok,), generator=gchk, dtype=torch.int32)
-        fbc = ForwardBatch.build([n_tok] * b_local, [0] * b_local, ids, bt, engine.page_size, engine.hq_local, engine.hkv_local, device)
+        fbc = ForwardBatch.build([n_tok] * b_local, [0] * b_local, ids, bt, engine.page_size, engine.hq_local, engine.hkv_local, device,
+                                 stage=engine.kv.quantized)
         outs = []
         outs, hid1 = [], []
         for fused_flag in (True, False):                               # same weights, same state, the two exchange implementations
@@ -492,6 +495,9 @@ def main():
         }
         if n_layers != cfg.n_layers:
             line["invalid"] = f"debug run with {n_layers} of {cfg.n_layers} layers"
+        if args.kv != "bf16":
+            line["invalid"] = (line.get("invalid", "") + "; " if line.get("invalid") else "") + f"KV cache kept as {args.kv}: reduced precision, not the headline configuration"
+            line["config"]["kv_cache"] = args.kv
         print(json.dumps(line))
     if world > 1:
         dist.barrier()

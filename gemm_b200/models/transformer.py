@@ -43,15 +43,44 @@ class KvCache:
     # conv[l] f32 [slots, conv_k - 1, qkv_dim], rec[l] f32 [slots, heads_v, d, d] (None for attention layers)
     conv: Optional[List[Optional[torch.Tensor]]] = None
     rec: Optional[List[Optional[torch.Tensor]]] = None
+    # INT8 mode (``kv_dtype="int8"``): the pages live in ``kq`` / ``vq`` (int8 ``[slots, Hkv, D]``) with one f32 scale per slot and
+    # head in ``ks`` / ``vs`` (the format of ops.attention.kv_store_q8), read directly by the INT8 decode attention kernel.  ``k`` /
+    # ``v`` then name ONE bf16 staging buffer shared by all layers: the QK-norm + RoPE kernel writes a step's new rows there, the
+    # prefill attention of a layer reads them there, and the store kernel quantises them into the layer's pages.
+    kq: Optional[List[torch.Tensor]] = None
+    vq: Optional[List[torch.Tensor]] = None
+    ks: Optional[List[torch.Tensor]] = None
+    vs: Optional[List[torch.Tensor]] = None
+
+    @property
+    def quantized(self) -> bool:
+        return self.kq is not None
 
     @staticmethod
     def allocate(cfg: ModelConfig, num_pages: int, page_size: int, device, hkv_local: Optional[int] = None,
-                 n_layers: Optional[int] = None, n_seq_slots: int = 64, first_layer: int = 0) -> "KvCache":
+                 n_layers: Optional[int] = None, n_seq_slots: int = 64, first_layer: int = 0, kv_dtype: str = "bf16",
+                 stage_pages: int = 0) -> "KvCache":
+        """``kv_dtype="int8"`` keeps the pages as int8 + scales; ``stage_pages`` pages of bf16 staging (enough for the tokens of one
+        forward pass, every sequence starting on a page boundary) are shared by all layers."""
         hkv = hkv_local if hkv_local is not None else cfg.n_kv_heads
         nl = n_layers if n_layers is not None else cfg.n_layers
         shape = (num_pages * page_size, hkv, cfg.head_dim)
         ssm = [cfg.is_ssm_layer(first_layer + i) for i in range(nl)]
         none = (0, hkv, cfg.head_dim)
+        if kv_dtype == "int8":
+            if any(ssm) or cfg.head_dim != 128:
+                raise ValueError("the INT8 KV cache is built for attention-only models with head_dim 128")
+            stage = (max(stage_pages, 1) * page_size, hkv, cfg.head_dim)
+            sk = torch.zeros(stage, dtype=torch.bfloat16, device=device)
+            sv = torch.zeros(stage, dtype=torch.bfloat16, device=device)
+            kv = KvCache([sk] * nl, [sv] * nl, page_size, num_pages)
+            kv.kq = [torch.zeros(shape, dtype=torch.int8, device=device) for _ in range(nl)]
+            kv.vq = [torch.zeros(shape, dtype=torch.int8, device=device) for _ in range(nl)]
+            kv.ks = [torch.zeros(shape[:2], dtype=torch.float32, device=device) for _ in range(nl)]
+            kv.vs = [torch.zeros(shape[:2], dtype=torch.float32, device=device) for _ in range(nl)]
+            return kv
+        if kv_dtype != "bf16":
+            raise ValueError(f"unknown kv_dtype {kv_dtype!r}")
         kv = KvCache([torch.zeros(none if ssm[i] else shape, dtype=torch.bfloat16, device=device) for i in range(nl)],
                      [torch.zeros(none if ssm[i] else shape, dtype=torch.bfloat16, device=device) for i in range(nl)], page_size, num_pages)
         if any(ssm):
@@ -80,6 +109,11 @@ class KvCache:
         dev = self.k[0].device
         src = torch.tensor([p[0] for p in pairs], dtype=torch.int32, device=dev)
         dst = torch.tensor([p[1] for p in pairs], dtype=torch.int32, device=dev)
+        if self.quantized:
+            for t in list(self.kq) + list(self.vq) + list(self.ks) + list(self.vs):
+                pg = t.view(self.num_pages, self.page_size, *t.shape[1:])
+                pg[dst.long()] = pg[src.long()]
+            return
         for t in list(self.k) + list(self.v):
             if t.shape[0] == 0:
                 continue
@@ -94,6 +128,9 @@ class KvCache:
             _native.check(rc, "gb_kv_copy_pages")
 
     def nbytes(self) -> int:
+        if self.quantized:
+            return sum(t.numel() * t.element_size() for t in list(self.kq) + list(self.vq) + list(self.ks) + list(self.vs)) + \
+                2 * self.k[0].numel() * 2
         tot = sum(t.numel() * 2 for t in self.k) * 2
         if self.conv is not None:
             tot += sum(c.numel() * 4 + r.numel() * 4 for c, r in zip(self.conv, self.rec) if c is not None)
@@ -117,11 +154,16 @@ class ForwardBatch:
     positions3: Optional[torch.Tensor] = None  # int32 [3, T] (t, h, w) positions for M-RoPE; default: all three = positions
     is_decode: bool = False                    # every sequence contributes exactly one token (selects the decode attention kernel)
     deepstack: Optional[torch.Tensor] = None   # bf16 [n_deepstack, T, H] added to the stream after the first layers (Qwen3-VL)
+    # INT8 KV cache: where a step's new K / V rows sit in the bf16 staging buffer, and (prefill) the block table of the staged sequences
+    stage_slots: Optional[torch.Tensor] = None # int32 [T]
+    stage_bt: Optional[torch.Tensor] = None    # int32 [B, pages]
 
     @staticmethod
     def build(q_lens: Sequence[int], ctx_lens: Sequence[int], ids, block_table: torch.Tensor, page_size: int, hq: int, hkv: int,
-              device, num_splits: int = 1, all_logits: bool = False, seq_slots: Optional[Sequence[int]] = None) -> "ForwardBatch":
-        """Host-side assembly from per-sequence chunk lengths and the lengths already cached."""
+              device, num_splits: int = 1, all_logits: bool = False, seq_slots: Optional[Sequence[int]] = None,
+              stage: bool = False) -> "ForwardBatch":
+        """Host-side assembly from per-sequence chunk lengths and the lengths already cached.  ``stage`` (INT8 KV cache) also lays the
+        step's tokens out in the staging buffer: a decode step row by row, a prefill step with every sequence on a page boundary."""
         b = len(q_lens)
         pos, slots, cu = [], [], [0]
         bt = block_table.cpu()
@@ -135,7 +177,26 @@ class ForwardBatch:
         rows = list(range(t)) if all_logits else [cu[s + 1] - 1 for s in range(b) if q_lens[s] > 0]
         i32 = dict(dtype=torch.int32, device=device)
         ids_t = ids.to(device=device, dtype=torch.int32) if torch.is_tensor(ids) else torch.tensor(ids, **i32)
-        return ForwardBatch(ids=ids_t, positions=torch.tensor(pos, **i32), slots=torch.tensor(slots, **i32),
+        st_slots = st_bt = None
+        if stage:
+            if all(q == 1 for q in q_lens):
+                st_slots = torch.arange(t, **i32)
+            else:
+                if any(c != 0 for c in ctx_lens):
+                    raise NotImplementedError("INT8 KV cache: a prefill chunk must start its sequence (the attention of a later chunk "
+                                              "would have to read the quantised history; raise max_prefill_tokens or use the bf16 cache)")
+                pages = [(q + page_size - 1) // page_size for q in q_lens]
+                first, ss = [0], []
+                for s in range(b):
+                    ss.extend(first[s] * page_size + i for i in range(q_lens[s]))
+                    first.append(first[s] + pages[s])
+                st_slots = torch.tensor(ss, **i32)
+                st_bt = torch.zeros(b, max(max(pages), 1), dtype=torch.int32)
+                for s in range(b):
+                    st_bt[s, : pages[s]] = torch.arange(first[s], first[s] + pages[s], dtype=torch.int32)
+                st_bt = st_bt.to(device)
+        return ForwardBatch(stage_slots=st_slots, stage_bt=st_bt,
+                            ids=ids_t, positions=torch.tensor(pos, **i32), slots=torch.tensor(slots, **i32),
                             cu_q=torch.tensor(cu, **i32), kv_len=torch.tensor([c + q for c, q in zip(ctx_lens, q_lens)], **i32),
                             block_table=block_table.to(device=device, dtype=torch.int32),
                             work=att.build_work(q_lens, hq, hkv, num_splits).to(device),
@@ -265,6 +326,8 @@ class Transformer:
         # decode-sized batches: the projection is cut along K and the rope kernel sums the partials (not with an output gate,
         # whose columns are read again below)
         qkv = apply_linear(lw.wqkv, h, h_mx) if cfg.attn_output_gate else apply_linear_split(lw.wqkv, h, h_mx)
+        if self.kv.quantized:
+            return self._attention_q8(li, lw, qkv, fb)
         q = ew.qk_norm_rope(qkv, fb.positions, fb.slots, lw.q_norm, lw.k_norm, self.kv.k[li], self.kv.v[li], self.hq_local,
                             self.hkv_local, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
                             positions3=fb.positions3, sections=cfg.mrope_sections)
@@ -280,6 +343,34 @@ class Transformer:
             return self.par.row_linear(lw.wo, None, a_mx)
         a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
                           num_splits=fb.num_splits, causal=True, window=cfg.sliding_window, decode=fb.is_decode)
+        a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
+        if cfg.attn_output_gate:
+            g0 = (self.hq_local + 2 * self.hkv_local) * cfg.head_dim
+            dn.gate_mul(a2, qkv[:, g0: g0 + self.hq_local * cfg.head_dim])
+        return self.par.row_linear(lw.wo, a2)
+
+    def _attention_q8(self, li: int, lw, qkv, fb: ForwardBatch) -> torch.Tensor:
+        """Attention with the INT8 KV cache: the new K / V rows go through the bf16 staging buffer (QK-norm + RoPE write them
+        there), are quantised into the layer's pages, and a decode step reads the INT8 pages directly; a prefill step attends over
+        the staged bf16 rows of its own tokens."""
+        cfg, kv = self.cfg, self.kv
+        if fb.stage_slots is None:
+            raise ValueError("the INT8 KV cache needs a ForwardBatch built with stage=True")
+        if fb.stage_slots.numel() > kv.k[li].shape[0] or (fb.stage_bt is not None and int(fb.stage_bt.shape[1]) * kv.page_size > kv.k[li].shape[0]):
+            raise ValueError("the forward pass has more tokens than the KV staging buffer holds")
+        q = ew.qk_norm_rope(qkv, fb.positions, fb.stage_slots, lw.q_norm, lw.k_norm, kv.k[li], kv.v[li], self.hq_local, self.hkv_local,
+                            cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
+                            positions3=fb.positions3, sections=cfg.mrope_sections)
+        att.kv_store_q8(kv.k[li], kv.v[li], fb.stage_slots, fb.slots, kv.kq[li], kv.vq[li], kv.ks[li], kv.vs[li])
+        if fb.is_decode:
+            a = att.attention_decode_q8(q, kv.kq[li], kv.vq[li], kv.ks[li], kv.vs[li], fb.kv_len, fb.block_table, kv.page_size,
+                                        num_splits=fb.num_splits, window=cfg.sliding_window)
+        else:
+            if fb.stage_bt is None:
+                raise NotImplementedError("INT8 KV cache: steps of several tokens per sequence on top of cached history (speculative "
+                                          "verification, later prefill chunks) are not built")
+            a = att.attention(q, kv.k[li], kv.v[li], fb.cu_q, fb.kv_len, fb.stage_bt, kv.page_size, fb.work, num_splits=1, causal=True,
+                              window=cfg.sliding_window)
         a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
         if cfg.attn_output_gate:
             g0 = (self.hq_local + 2 * self.hkv_local) * cfg.head_dim

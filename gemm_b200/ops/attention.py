@@ -89,6 +89,55 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_
     return out
 
 
+def kv_store_q8(k_src: torch.Tensor, v_src: torch.Tensor, src_slots: Optional[torch.Tensor], dst_slots: torch.Tensor, kq: torch.Tensor,
+                vq: torch.Tensor, ks: torch.Tensor, vs: torch.Tensor) -> None:
+    """Quantise the bf16 K / V rows ``k_src[src_slots[t]]`` (``[rows, Hkv, 128]``; row ``t`` when ``src_slots`` is None) of the
+    new tokens into the INT8 cache at ``dst_slots[t]`` (negative: skipped): int8 ``kq`` / ``vq`` ``[slots, Hkv, 128]`` and one f32
+    scale per slot and head in ``ks`` / ``vs`` ``[slots, Hkv]`` (``x = scale * q``, ``scale = amax / 127``)."""
+    from .kvquant import quantize_q8_ref
+    n = dst_slots.numel()
+    if not k_src.is_cuda:
+        src = src_slots.long() if src_slots is not None else torch.arange(n)
+        ok = dst_slots >= 0
+        for cache, sc, rows in ((kq, ks, k_src), (vq, vs, v_src)):
+            q, scale = quantize_q8_ref(rows[src[ok]])
+            cache[dst_slots[ok].long()] = q
+            sc[dst_slots[ok].long()] = scale
+        return
+    rc = _native.cuda().gb_kv_store_q8(_p(k_src), _p(v_src), _p(src_slots), _p(dst_slots), _p(kq), _p(vq), _p(ks), _p(vs), _i(n),
+                                       _i(kq.shape[1]), _i(kq.shape[2]), _l(k_src.shape[0]), _l(kq.shape[0]),
+                                       _c(torch.cuda.current_stream().cuda_stream))
+    _native.check(rc, "gb_kv_store_q8")
+
+
+def attention_decode_q8(q: torch.Tensor, kq: torch.Tensor, vq: torch.Tensor, ks: torch.Tensor, vs: torch.Tensor, kv_len: torch.Tensor,
+                        block_table: torch.Tensor, page_size: int, num_splits: int = 1, window: int = 0) -> torch.Tensor:
+    """Decode attention (one query token per sequence) over the INT8 cache of ``kv_store_q8``; ``q`` as for ``attention``.
+    Returns bf16 ``[B, Hq, 128]``.  (Reference: attn_decode_q8, cuda/llm/cuda_llm_runner.c:244-330.)"""
+    b, hq, d = q.shape
+    hkv = kq.shape[1]
+    if not q.is_cuda:
+        k = (kq.float() * ks.unsqueeze(-1)).to(torch.bfloat16)
+        v = (vq.float() * vs.unsqueeze(-1)).to(torch.bfloat16)
+        cu = torch.arange(b + 1, dtype=torch.int32)
+        return attention_ref(q, k, v, cu, kv_len, block_table, page_size, True, window)
+    out = torch.empty(b, hq, d, dtype=torch.bfloat16, device=q.device)
+    part_o = part_lse = None
+    if num_splits > 1:
+        part_o = torch.empty(num_splits, b, hq, d, dtype=torch.float32, device=q.device)
+        part_lse = torch.empty(num_splits, b, hq, dtype=torch.float32, device=q.device)
+    lib = _native.cuda()
+    stream = _c(torch.cuda.current_stream().cuda_stream)
+    rc = lib.gb_attn_decode_q8(_p(q), _p(kq), _p(vq), _p(ks), _p(vs), _p(out), _p(part_o), _p(part_lse), _p(kv_len), _p(block_table),
+                               _i(block_table.shape[1]), _i(page_size), _l(kq.shape[0]), _i(b), _i(hq), _i(hkv), _i(d), _i(num_splits),
+                               _i(window), _c(_native.status_ptr()), stream)
+    _native.check(rc, "gb_attn_decode_q8")
+    if num_splits > 1:
+        rc = lib.gb_fa_combine(_p(part_o), _p(part_lse), _p(out), _c(0), _i(num_splits), _l(b * hq), stream)
+        _native.check(rc, "gb_fa_combine")
+    return out
+
+
 def attention_decode_mx(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                         block_table: torch.Tensor, page_size: int, work: torch.Tensor, window: int = 0, sf_layout: int = 128,
                         num_splits: int = 1):

@@ -52,7 +52,7 @@ class PageAllocator:
 
 class Engine:
     def __init__(self, weights: ModelWeights, max_batch: int, max_seq_len: int, page_size: int = 128, par=None,
-                 max_prefill_tokens: int = 16384, num_pages: Optional[int] = None):
+                 max_prefill_tokens: int = 16384, num_pages: Optional[int] = None, kv_dtype: str = "bf16"):
         self.w = weights
         self.cfg: ModelConfig = weights.cfg
         self.device = weights.embed.device
@@ -62,7 +62,10 @@ class Engine:
         n_pages = num_pages if num_pages is not None else max_batch * self.max_pages_per_seq
         hkv_local = max(1, self.cfg.n_kv_heads // weights.tp_size)
         # one recurrent-state slot per sequence plus a scratch slot (hybrid models; used by the warm-up run before graph capture)
-        self.kv = KvCache.allocate(self.cfg, n_pages, page_size, self.device, hkv_local, n_layers=len(weights.layers), n_seq_slots=max_batch + 1)
+        # kv_dtype "int8": pages of int8 + scales read directly by the decode attention kernel (half the bytes per step and per
+        # sequence); a prompt must then fit one prefill chunk (max_prefill_tokens)
+        self.kv = KvCache.allocate(self.cfg, n_pages, page_size, self.device, hkv_local, n_layers=len(weights.layers), n_seq_slots=max_batch + 1,
+                                   kv_dtype=kv_dtype, stage_pages=(max_prefill_tokens + page_size - 1) // page_size + max_batch)
         self.pages = PageAllocator(n_pages)
         self.model = Transformer(weights, self.kv, par)
         self.par = self.model.par
@@ -126,7 +129,8 @@ class Engine:
                 ids.append(prompts[i][done[i]:done[i] + take])
                 room -= take
             fb = ForwardBatch.build(q_lens, ctx, torch.cat([x.to(self.device) for x in ids]), self._block_table([base + i for i in seqs]),
-                                    self.page_size, self.hq_local, self.hkv_local, self.device, seq_slots=[base + i for i in seqs])
+                                    self.page_size, self.hq_local, self.hkv_local, self.device, seq_slots=[base + i for i in seqs],
+                                    stage=self.kv.quantized)
             with profiler.region("prefill_chunk", "step", "engine"):
                 logits = self.model.forward(fb)
             for j, i in enumerate(seqs):
@@ -169,6 +173,7 @@ class Engine:
         st["rows"] = torch.arange(b, dtype=torch.int64, device=self.device)
         st["tokens"] = torch.zeros(b, dtype=torch.int32, device=self.device)
         st["seq_slots"] = torch.arange(b, dtype=torch.int32, device=self.device)
+        st["stage_slots"] = torch.arange(b, dtype=torch.int32, device=self.device) if self.kv.quantized else None
         # decode step number on the device: the sampler reads it and the bookkeeping kernel advances it, so graph replays and
         # eager steps draw the same random numbers
         st["step"] = torch.ones(1, dtype=torch.int64, device=self.device)       # step 0 sampled the first token after the prefill
@@ -202,7 +207,7 @@ class Engine:
         st = self._static
         fb = ForwardBatch(ids=st["ids"], positions=st["positions"], slots=st["slots"], cu_q=st["cu_q"], kv_len=st["kv_len"],
                           block_table=st["block_table"], work=st["work"], logit_rows=st["rows"], num_splits=self._splits,
-                          n_tokens=st["ids"].numel(), seq_slots=st["seq_slots"], is_decode=True)
+                          n_tokens=st["ids"].numel(), seq_slots=st["seq_slots"], is_decode=True, stage_slots=st["stage_slots"])
         if self._sp.temperature <= 0 and not hasattr(self.par, "merge_sampled"):
             tok = self.model.forward_greedy(fb)
         else:
