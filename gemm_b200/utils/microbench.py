@@ -162,6 +162,14 @@ def _attn(args, b: int, q_len: int, ctx: int, name: str):
     else:
         flops = 4.0 * b * hq * d * (q_len * ctx + q_len * (q_len + 1) / 2)
     _run(name, run, flops, kv_bytes + b * q_len * hq * d * 4, args, splits=splits, batch=b, ctx=ctx, hq=hq, hkv=hkv, page=page)
+    if q_len == 1:
+        # the same pages as int8 + one scale per slot and head, read directly by the INT8 decode attention kernel
+        kq, vq = torch.empty(k.shape, dtype=torch.int8, device="cuda"), torch.empty(v.shape, dtype=torch.int8, device="cuda")
+        ks, vs = torch.empty(k.shape[:2], device="cuda"), torch.empty(v.shape[:2], device="cuda")
+        att.kv_store_q8(k, v, None, torch.arange(k.shape[0], dtype=torch.int32, device="cuda"), kq, vq, ks, vs)
+        sp8 = args.splits if args.splits > 0 else max(1, min(8, (148 * 4) // max(1, b * hkv)))
+        _run(name + "_int8_kv", lambda: att.attention_decode_q8(q, kq, vq, ks, vs, kv_len, bt, page, num_splits=sp8), flops,
+             kv_bytes // 2 + b * (ctx + 1) * hkv * 8 + b * hq * d * 4, args, splits=sp8, batch=b, ctx=ctx, hq=hq, hkv=hkv, page=page)
 
 
 def case_attn_decode(args):
