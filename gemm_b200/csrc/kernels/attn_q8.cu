@@ -123,7 +123,7 @@ attn_decode_q8_kernel(const AttnQ8Args a) {
     // stays below 127 and a block sum below 4096 whatever the magnitude of V; the block sum is multiplied back in fp32
     const float vmax = warp_max(vsc);
     const float vrel = vmax > 0.f ? vsc / vmax : 0.f;
-    float p[G];
+    uint32_t p[G];                                           // this position's probability x value scale per head, as a half2 pair
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       int dot = 0;
@@ -143,7 +143,8 @@ attn_decode_q8_kernel(const AttnQ8Args a) {
       l[g] = l[g] * alpha + warp_sum(e);
       m[g] = m_new;
       o[g][0] *= alpha; o[g][1] *= alpha; o[g][2] *= alpha; o[g][3] *= alpha;
-      p[g] = e * vrel;
+      const __half2 ph = __float2half2_rn(e * vrel);
+      p[g] = *reinterpret_cast<const uint32_t*>(&ph);
     }
     // ---- values: lane = features 4 lane .. 4 lane + 3; the block's 32 positions one after the other, summed in half2
     __half2 acc01[G], acc23[G];
@@ -161,7 +162,8 @@ attn_decode_q8_kernel(const AttnQ8Args a) {
       const __half2 v01 = __hsub2(*reinterpret_cast<const __half2*>(&lo), bias), v23 = __hsub2(*reinterpret_cast<const __half2*>(&hi), bias);
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        const __half2 ph = __float2half2_rn(__shfl_sync(0xffffffffu, p[g], j));
+        const uint32_t pw = __shfl_sync(0xffffffffu, p[g], j);
+        const __half2 ph = *reinterpret_cast<const __half2*>(&pw);
         acc01[g] = __hfma2(ph, v01, acc01[g]);
         acc23[g] = __hfma2(ph, v23, acc23[g]);
       }
