@@ -265,7 +265,12 @@ def case_quant(args):
                     continue
                 x = torch.randn(m, k, device="cuda").bfloat16()
                 out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
-                _run(f"qgemm_{tname}_{pname}_{m}x{n}x{k}", lambda: qlinear.gemm(x, w, out=out), 2.0 * m * n * k, wbytes + m * k * 2 + m * n * 2, args)
+                sp = qlinear.pick_gemm_splits(n, k, m)
+                if sp > 1:      # few row tiles: K is cut and the consumer adds the slabs (here: a sum, which the model folds into its next kernel)
+                    _run(f"qgemm_{tname}_{pname}_{m}x{n}x{k}", lambda: qlinear.gemm_partials(x, w, sp), 2.0 * m * n * k,
+                         wbytes + m * k * 2 + sp * m * n * 4, args, splits=sp)
+                else:
+                    _run(f"qgemm_{tname}_{pname}_{m}x{n}x{k}", lambda: qlinear.gemm(x, w, out=out), 2.0 * m * n * k, wbytes + m * k * 2 + m * n * 2, args)
             del w
 
 
