@@ -797,6 +797,23 @@ GB_API int gb_rmsnorm_reduce_bcast(void* residual, const float* partials, int n_
                         partial_stride, wait_flags, wait_n, epoch_ptr, status, stream, nullptr, nullptr, nullptr, 0, 0, 1, 0, bcast);
 }
 
+// A rank with no rows to contribute still has to advance the epoch and raise its flags (the others wait for every rank).
+__global__ void bcast_signal_kernel(const RmsBcast bc) {
+  pdl_wait();
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    const uint32_t e = *bc.epoch_ctr + 1;
+    *bc.epoch_ctr = e;
+    for (int p = 0; p < bc.world; ++p) st_release_sys(bc.flag[p], e);
+  }
+}
+GB_API int gb_bcast_signal(const RmsBcast* bcast, cudaStream_t stream) {
+  if (bcast == nullptr || bcast->world < 1 || bcast->world > 8 || bcast->epoch_ctr == nullptr) return fail("bcast_signal: bad arguments%s");
+  launch_k(bcast_signal_kernel, 1, 32, 0, stream, *bcast);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 // residual += delta, RMSNorm, MXFP8 copy (optional) and the all-gather of the bf16 rows (see RmsBcast).
 GB_API int gb_rmsnorm_bcast(void* residual, const void* delta, const void* weight, void* out_q, void* out_sf, int rows, int hidden, float eps,
                             int ld_in, int sf32, const RmsBcast* bcast, cudaStream_t stream) {

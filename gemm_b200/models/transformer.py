@@ -470,6 +470,11 @@ class Transformer:
         if x is None:
             x = fb.embeds if fb.embeds is not None else ew.embed(fb.ids, w.embed)
         delta = None
+        if hasattr(self.par, "_sp_ok"):
+            # the fused tensor-parallel prefill path keeps the residual stream sharded by rows between the layers' GEMMs: only for
+            # plain dense stacks (nothing reads the whole stream or the normalised rows outside a GEMM in between)
+            self.par._sp_ok = not (cfg.is_moe or cfg.attn_output_gate or fb.deepstack is not None or self.snapshot_layers or
+                                   any(l.ssm is not None for l in w.layers[first_layer:last_layer]))
         for li in range(first_layer, last_layer):
             lw = w.layers[li]
             lay = 32 if x.shape[0] <= 32 else 128
@@ -505,6 +510,8 @@ class Transformer:
             if li in self.snapshot_layers:
                 self.snapshots[li] = (x.float() + self.par.materialize(delta).float())
         # the last delta stays pending: the head (or the next pipeline stage) folds it into the stream
+        if hasattr(self.par, "finish_residual"):
+            self.par.finish_residual(x, delta)
         self._last_delta = self.par.materialize(delta) if delta is not None else None
         return x
 

@@ -92,12 +92,31 @@ def pick_tn(m_tok: int, mx: bool = False, dual: bool = False) -> int:
     return tn
 
 
+_next_wait = None
+
+
+def wait_before_next_launch(flags_ptr: int, n: int, epoch_ptr: int) -> None:
+    """The NEXT GEMM launched through this module waits (bounded, on the device) until ``flags[i] >= *epoch_ptr`` for ``i < n`` before
+    it reads its token rows: the consumer side of an all-gather whose rows the peers store into this GPU's memory (the kernel
+    that produced them raised the flags)."""
+    global _next_wait
+    _next_wait = (flags_ptr, n, epoch_ptr)
+
+
 def _launch(w, x, out, n_out, k, m_tok, ldw, ldx, ldo, flags, tn, num_groups=0, w_rows_per_group=0, up_row_offset=0,
             seg_start=None, seg_count=None, x_rows=None, sfa=None, sfb=None, out_sf=None, bias=None, row_map=None,
             row_scale=None, extras=None):
+    global _next_wait
     lib = _native.cuda()
     if extras is None:
         extras = GemmExtras()
+    restore = None
+    if _next_wait is not None:
+        if extras.signal_n or extras.wait_n:
+            raise RuntimeError("gemm: a pending all-gather wait met a launch that has its own flag protocol")
+        restore = (extras.wait_flags, extras.wait_n, extras.epoch_ptr)
+        extras.wait_flags, extras.wait_n, extras.epoch_ptr = _next_wait
+        _next_wait = None
     # extents of the caller's buffers: the kernel checks its scale-atom loads and its stores against them
     nb = lambda t: t.numel() * t.element_size() if t is not None else 0
     extras.sfa_bytes, extras.sfb_bytes, extras.out_bytes, extras.out_sf_bytes = nb(sfa), nb(sfb), nb(out), nb(out_sf)
@@ -105,6 +124,8 @@ def _launch(w, x, out, n_out, k, m_tok, ldw, ldx, ldo, flags, tn, num_groups=0, 
                      _i(num_groups), _i(w_rows_per_group), _i(up_row_offset), _p(seg_start), _p(seg_count),
                      _i(x_rows if x_rows is not None else m_tok), _p(sfa), _p(sfb), _p(out_sf), _p(bias), _p(row_map),
                      _p(row_scale), ctypes.byref(extras) if extras is not None else _c(0), _c(_native.status_ptr()), _stream())
+    if restore is not None:
+        extras.wait_flags, extras.wait_n, extras.epoch_ptr = restore
     _native.check(rc, "gb_gemm")
 
 

@@ -33,6 +33,8 @@ _c, _i, _f, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_long
 
 
 TP_DIRECT = os.environ.get("GB_TP_DIRECT", "1") != "0"
+# prefill-sized row-parallel projections: GEMM -> reduce-scatter in the epilogue, all-gather -> GEMM in the consumer's prologue
+SEQ_PAR = os.environ.get("GB_TP_SEQ_PAR", "1") != "0"
 
 
 @dataclass
@@ -42,6 +44,16 @@ class PendingReduce:
     rows: int
     hidden: int
     splits: int = 1          # K-split slabs per rank inside its slot
+
+
+@dataclass
+class PendingScatter:
+    """Partial sums of a prefill-sized row-parallel projection, reduce-scattered by the GEMM's epilogue: rows ``[p * region, (p + 1) *
+    region)`` of every rank's partial result sit in GPU p's slots of channel ``chan``; finished by ``add_norm`` on the owner."""
+    chan: int
+    rows: int
+    hidden: int
+    region: int
 
 
 class TensorParallel:
@@ -64,6 +76,11 @@ class TensorParallel:
         self.max_fused_rows = max_fused_rows
         self.fab: Optional[Fabric] = None
         self._chan = 0
+        self._sp_chan = 0
+        self._x_sharded, self._x_region = False, 0
+        self.sp = None
+        self.sp_launches = 0        # row-parallel GEMMs that took the fused reduce-scatter path (tests assert on it)
+        self._sp_ok = True          # cleared by the model for forward passes that read the whole residual stream between layers
 
     def attach(self, engine, cfg, max_tokens: int) -> None:
         self.cfg = cfg
@@ -73,6 +90,8 @@ class TensorParallel:
         slot = self.max_fused_rows * h * 4
         big = max_tokens * h
         heap = 2 * w * slot + 2 * big * 2 + (8 << 20)
+        if SEQ_PAR and w > 1 and max_tokens >= w * 256:
+            heap += self.seq_par_heap_bytes(w, h, max_tokens)
         self.fab = f = Fabric(self.group, self.device, heap)
         self.slot_elems = self.max_fused_rows * h
         self.slots_off = [f.alloc(w * slot), f.alloc(w * slot)]
@@ -81,6 +100,7 @@ class TensorParallel:
         self.done = [f.ctl_word(), f.ctl_word()]
         self.big = f.make_allreduce_large(big, torch.bfloat16)
         self.argmax = f.make_argmax(4096)
+        self._attach_seq_par(f, cfg, max_tokens)
         self._extras = []
         for ch in range(2):
             ex = gemm.GemmExtras()
@@ -93,6 +113,94 @@ class TensorParallel:
             ex.signal_n = w
             ex.done_ctr = self.done[ch]
             self._extras.append(ex)
+
+    # ------------------------------------------------------------------------------------------ prefill: GEMM -> reduce-scatter, all-gather -> GEMM
+    def _attach_seq_par(self, f: Fabric, cfg, max_tokens: int) -> None:
+        """Buffers of the fused prefill path.  A row-parallel GEMM (o_proj, down_proj) stores the rows of region p of its fp32 partial
+        result straight into slot [this rank] on GPU p (its epilogue is the reduce-scatter, tile by tile under the math) and raises a
+        flag there; GPU p's residual-add + RMSNorm kernel waits for all flags, sums the slots in rank order, updates ITS rows of
+        the residual stream, and stores the normalised bf16 rows into the gather buffer of every GPU (its epilogue is the
+        all-gather); the next column-parallel GEMM (QKV, gate/up) waits for all ranks' gather flags before it loads its token
+        tiles.  Between the two GEMMs the residual stream is sharded by rows (sequence parallelism): per layer two exchanges of
+        rows / W rows instead of two all-reduces of all rows, no all-reduce launch, and the norm is computed once, not W times."""
+        self.sp = None
+        w, h = self.tp_size, cfg.hidden
+        if not (SEQ_PAR and w > 1 and max_tokens >= w * 256):
+            return
+        region_max = -(-max_tokens // (w * 256)) * 256
+        sp = {"region_max": region_max}
+        sp["slots_off"] = [f.alloc(w * region_max * h * 4) for _ in range(2)]
+        sp["gather_off"] = [f.alloc(w * region_max * h * 2) for _ in range(2)]
+        sp["rs_flags"] = [f.alloc(32) for _ in range(2)]
+        sp["ag_flags"] = [f.alloc(32) for _ in range(2)]
+        sp["rs_epoch"], sp["rs_done"] = [f.ctl_word(), f.ctl_word()], [f.ctl_word(), f.ctl_word()]
+        sp["ag_epoch"], sp["ag_done"] = [f.ctl_word(), f.ctl_word()], [f.ctl_word(), f.ctl_word()]
+        self.sp = sp
+
+    @staticmethod
+    def seq_par_heap_bytes(world: int, hidden: int, max_tokens: int) -> int:
+        region_max = -(-max_tokens // (world * 256)) * 256
+        return 2 * world * region_max * hidden * (4 + 2) + (1 << 20)
+
+    def _scatter_linear(self, lw, x: torch.Tensor, rows: int):
+        """Row-parallel bf16 projection whose epilogue reduce-scatters (see ``_attach_seq_par``)."""
+        sp, f, w = self.sp, self.fab, self.tp_size
+        ch = self._sp_chan
+        self._sp_chan ^= 1
+        self.sp_launches += 1
+        n = lw.n
+        region = -(-rows // (w * 256)) * 256
+        ex = gemm.GemmExtras()
+        for p in range(w):
+            ex.peer_out[p] = f.peer_ptr(p, sp["slots_off"][ch])
+            ex.signal_flags[p] = f.peer_ptr(p, sp["rs_flags"][ch]) + 4 * self.tp_rank
+        ex.peer_region_rows, ex.peer_rank, ex.signal_n = region, self.tp_rank, w
+        ex.done_ctr, ex.epoch_ptr, ex.epoch_self_tick = sp["rs_done"][ch], sp["rs_epoch"][ch], 1
+        tn = gemm.pick_tn(rows)
+        gemm._launch(lw.w, x, None, n, lw.k, rows, lw.w.stride(0), x.stride(0), n, gemm.GEMM_OUT_F32 | (gemm.GEMM_W_TILED if lw.tiled else 0), tn,
+                     bias=lw.bias if self.tp_rank == 0 else None, extras=ex)
+        return PendingScatter(ch, rows, n, region)
+
+    def _scatter_norm(self, ps: PendingScatter, weight, eps, residual: torch.Tensor):
+        """Owner side of the reduce-scatter + the all-gather of the normalised rows; returns the gathered rows (a view of the heap).
+        The consumer GEMM that follows waits for the gather flags (``gemm.wait_before_next_launch``)."""
+        sp, f, w, ch = self.sp, self.fab, self.tp_size, ps.chan
+        h, region = ps.hidden, ps.region
+        r0 = self.tp_rank * region
+        mine = max(0, min(ps.rows, r0 + region) - r0)
+        bc = ew.RmsBcast()
+        for p in range(w):
+            bc.out[p] = f.peer_ptr(p, sp["gather_off"][ch]) + r0 * h * 2
+            bc.flag[p] = f.peer_ptr(p, sp["ag_flags"][ch]) + 4 * self.tp_rank
+        bc.world, bc.epoch_ctr, bc.done_ctr = w, sp["ag_epoch"][ch], sp["ag_done"][ch]
+        stream = _c(torch.cuda.current_stream().cuda_stream)
+        if mine > 0:
+            res = residual[r0: r0 + mine]
+            assert res.is_contiguous() and residual.stride(0) == h
+            rc = f.lib.gb_rmsnorm_reduce_bcast(_c(res.data_ptr()), _c(f.local_base + sp["slots_off"][ch]), _i(w), _l(region * h), _c(weight.data_ptr()),
+                                               _c(0), _c(0), _c(0), _i(mine), _i(h), _f(eps), _i(0), _c(f.local_base + sp["rs_flags"][ch]), _i(w),
+                                               _c(sp["rs_epoch"][ch]), _c(_native.status_ptr()), ctypes.byref(bc), stream)
+            _native.check(rc, "gb_rmsnorm_reduce_bcast")
+        else:
+            _native.check(f.lib.gb_bcast_signal(ctypes.byref(bc), stream), "gb_bcast_signal")
+        gemm.wait_before_next_launch(f.local_base + sp["ag_flags"][ch], w, sp["ag_epoch"][ch])
+        return f.view(sp["gather_off"][ch], (ps.rows, h), torch.bfloat16)
+
+    def finish_residual(self, x: torch.Tensor, delta) -> None:
+        """Before the residual stream is read as a whole (final norm, snapshots): while the fused prefill path is in use every rank
+        keeps only its own rows of ``x`` current; gather the others (once per forward pass, NCCL)."""
+        if not isinstance(delta, PendingScatter) and not self._x_sharded:
+            return
+        region = self._x_region
+        w, rows = self.tp_size, x.shape[0]
+        pad = torch.zeros(w * region, x.shape[1], dtype=x.dtype, device=x.device)
+        r0 = self.tp_rank * region
+        mine = max(0, min(rows, r0 + region) - r0)
+        part = torch.zeros(region, x.shape[1], dtype=x.dtype, device=x.device)
+        part[:mine] = x[r0: r0 + mine]
+        dist.all_gather_into_tensor(pad, part, group=self.group)
+        x.copy_(pad[:rows])
+        self._x_sharded = False
 
     # ------------------------------------------------------------------------------------------ model hooks
     def tp_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -109,6 +217,9 @@ class TensorParallel:
         if lw.is_quant:
             return self._row_linear_quant(lw, x, rows)
         if not self.fused or self.tp_size == 1 or rows > self.max_fused_rows:
+            if (self.fused and self.tp_size > 1 and self.sp is not None and lw.fmt == "bf16" and x is not None and x.is_cuda and lw.n == self.cfg.hidden
+                    and rows >= self.tp_size * 256 and -(-rows // (self.tp_size * 256)) * 256 <= self.sp["region_max"] and self._sp_ok):
+                return self._scatter_linear(lw, x, rows)
             if TP_DIRECT and self.fused and self.tp_size > 1 and rows * lw.n <= self.big.n and (x if x is not None else x_mx.data).is_cuda:
                 # prefill-sized: the GEMM writes its partial result straight into the all-reduce's input buffer in the fabric heap
                 out = self.big.input_view[: rows * lw.n].view(rows, lw.n)
@@ -193,10 +304,24 @@ class TensorParallel:
     def add_norm(self, delta, weight, eps, residual, **kw):
         if isinstance(delta, PendingReduce):
             return self._reduce_norm(delta, weight, eps, residual, **kw)
+        if isinstance(delta, PendingScatter):
+            if kw.get("quantize") or residual is None:
+                raise RuntimeError("the fused prefill path serves bf16 models with a residual stream")
+            self._x_sharded, self._x_region = True, delta.region
+            return self._scatter_norm(delta, weight, eps, residual)
         return ew.rmsnorm(delta, weight, eps, residual=residual, **kw)
 
     def materialize(self, delta):
         """Finish a pending reduction into a plain tensor (sum of the ranks' partials, bf16)."""
+        if isinstance(delta, PendingScatter):
+            # every rank sums its own region of the slots, the regions are gathered (end of a forward pass: once, NCCL)
+            f, sp, w, h = self.fab, self.sp, self.tp_size, delta.hidden
+            f.barrier()          # every rank's GEMM (and its stores) precede its arrival at the barrier
+            slots = f.view(sp["slots_off"][delta.chan], (w, delta.region * h), torch.float32)
+            part = slots.sum(0).to(torch.bfloat16).view(delta.region, h)
+            full = torch.empty(w * delta.region, h, dtype=torch.bfloat16, device=self.device)
+            dist.all_gather_into_tensor(full, part.contiguous(), group=self.group)
+            return full[: delta.rows]
         if not isinstance(delta, PendingReduce):
             return delta.materialize() if hasattr(delta, "materialize") else delta
         f = self.fab

@@ -234,6 +234,41 @@ def check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-dense", ep_ex
     par.close()
 
 
+def check_tp_prefill_fused(rank, world, dev):
+    """Prefill-sized tensor parallelism with the GEMM -> reduce-scatter / all-gather -> GEMM path: the row-parallel projections
+    scatter their partial rows to the rows' owners from the epilogue, the owners' norm kernels gather the normalised rows to
+    every rank, the residual stream is sharded in between.  Logits against the unsharded engine, bitwise agreement of the ranks,
+    and a rank that owns no rows (4 ranks)."""
+    from gemm_b200.parallel.tensor import TensorParallel
+    cfg = get_config("tiny-dense")
+    page = 16
+    g = torch.Generator().manual_seed(21)
+    lens = (1203, 1002) if world >= 4 else (603, 802)      # halves: 1100 rows on 4 ranks -> regions of 512: the last rank owns none
+    toks = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in lens]
+    n_pages = sum((n + page - 1) // page for n in lens) + 2
+    w_full = synthetic_weights(cfg, "bf16", device=dev, seed=5)
+    w_tp = synthetic_weights(cfg, "bf16", device=dev, seed=5, tp_rank=rank, tp_size=world)
+    ref = run_model(Transformer(w_full, KvCache.allocate(cfg, n_pages, page, dev)), cfg, toks, page, dev)
+    par = TensorParallel(dist.group.WORLD, dev, fused=True)
+    par.attach(None, cfg, max_tokens=4096)
+    assert par.sp is not None
+    model = Transformer(w_tp, KvCache.allocate(cfg, n_pages, page, dev, max(1, cfg.n_kv_heads // world)), par)
+    got = run_model(model, cfg, toks, page, dev)
+    torch.cuda.synchronize()
+    _native.assert_status_ok()
+    assert par.sp_launches >= 2 * 2 * cfg.n_layers, par.sp_launches        # o_proj and down_proj of both prefill chunks
+    for a, b in zip(got, ref):
+        r = rel(a, b)
+        assert r < 2e-2, f"fused TP prefill differs from the single-GPU engine: rel {r}"
+    for t in got[:2]:
+        t = t.contiguous()
+        gathered = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        assert all(torch.equal(gathered[0], x) for x in gathered), "ranks disagree bitwise after the fused prefill path"
+    dist.barrier()
+    par.close()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -259,6 +294,8 @@ def main():
     if what in ("all", "hybrid"):
         for fmt, fused in (("bf16", True), ("mxfp8", True), ("mxfp8", False)):
             check_tensor_parallel(rank, world, dev, fmt, fused, name="tiny-moe", ep_experts=True)
+    if what in ("all", "tp", "tp4"):
+        check_tp_prefill_fused(rank, world, dev)
     if what == "tp4":
         for fmt, fused in (("bf16", True), ("mxfp8", True)):
             check_tensor_parallel(rank, world, dev, fmt, fused)
