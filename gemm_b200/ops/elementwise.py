@@ -58,7 +58,7 @@ def sf_alloc(rows_padded: int, k: int, device, layout: int = 128, init: bool = T
 class RmsBcast(ctypes.Structure):
     """All-gather in the RMSNorm's epilogue (mirrors ``RmsBcast`` in csrc/kernels/elementwise.cu): where the bf16 rows go on every
     GPU, the flags raised afterwards, the epoch and arrival counters."""
-    _fields_ = [("out", ctypes.c_void_p * 8), ("flag", ctypes.c_void_p * 8), ("world", ctypes.c_int), ("pad", ctypes.c_int),
+    _fields_ = [("out", ctypes.c_void_p * 8), ("flag", ctypes.c_void_p * 8), ("world", ctypes.c_int), ("partials_bf16", ctypes.c_int),
                 ("epoch_ctr", ctypes.c_void_p), ("done_ctr", ctypes.c_void_p)]
 
 

@@ -116,8 +116,8 @@ class TensorParallel:
 
     # ------------------------------------------------------------------------------------------ prefill: GEMM -> reduce-scatter, all-gather -> GEMM
     def _attach_seq_par(self, f: Fabric, cfg, max_tokens: int) -> None:
-        """Buffers of the fused prefill path.  A row-parallel GEMM (o_proj, down_proj) stores the rows of region p of its fp32 partial
-        result straight into slot [this rank] on GPU p (its epilogue is the reduce-scatter, tile by tile under the math) and raises a
+        """Buffers of the fused prefill path.  A row-parallel GEMM (o_proj, down_proj) stores the rows of region p of its partial
+        result (as bf16) straight into slot [this rank] on GPU p (its epilogue is the reduce-scatter, tile by tile under the math) and raises a
         flag there; GPU p's residual-add + RMSNorm kernel waits for all flags, sums the slots in rank order, updates ITS rows of
         the residual stream, and stores the normalised bf16 rows into the gather buffer of every GPU (its epilogue is the
         all-gather); the next column-parallel GEMM (QKV, gate/up) waits for all ranks' gather flags before it loads its token
@@ -129,7 +129,7 @@ class TensorParallel:
             return
         region_max = -(-max_tokens // (w * 256)) * 256
         sp = {"region_max": region_max}
-        sp["slots_off"] = [f.alloc(w * region_max * h * 4) for _ in range(2)]
+        sp["slots_off"] = [f.alloc(w * region_max * h * 2) for _ in range(2)]
         sp["gather_off"] = [f.alloc(w * region_max * h * 2) for _ in range(2)]
         sp["rs_flags"] = [f.alloc(32) for _ in range(2)]
         sp["ag_flags"] = [f.alloc(32) for _ in range(2)]
@@ -140,7 +140,7 @@ class TensorParallel:
     @staticmethod
     def seq_par_heap_bytes(world: int, hidden: int, max_tokens: int) -> int:
         region_max = -(-max_tokens // (world * 256)) * 256
-        return 2 * world * region_max * hidden * (4 + 2) + (1 << 20)
+        return 2 * world * region_max * hidden * (2 + 2) + (1 << 20)
 
     def _scatter_linear(self, lw, x: torch.Tensor, rows: int):
         """Row-parallel bf16 projection whose epilogue reduce-scatters (see ``_attach_seq_par``)."""
@@ -157,7 +157,8 @@ class TensorParallel:
         ex.peer_region_rows, ex.peer_rank, ex.signal_n = region, self.tp_rank, w
         ex.done_ctr, ex.epoch_ptr, ex.epoch_self_tick = sp["rs_done"][ch], sp["rs_epoch"][ch], 1
         tn = gemm.pick_tn(rows)
-        gemm._launch(lw.w, x, None, n, lw.k, rows, lw.w.stride(0), x.stride(0), n, gemm.GEMM_OUT_F32 | (gemm.GEMM_W_TILED if lw.tiled else 0), tn,
+        # the partial rows travel as bf16 (the precision of the all-reduce they replace, half the link bytes of fp32)
+        gemm._launch(lw.w, x, None, n, lw.k, rows, lw.w.stride(0), x.stride(0), n, gemm.GEMM_W_TILED if lw.tiled else 0, tn,
                      bias=lw.bias if self.tp_rank == 0 else None, extras=ex)
         return PendingScatter(ch, rows, n, region)
 
@@ -172,7 +173,7 @@ class TensorParallel:
         for p in range(w):
             bc.out[p] = f.peer_ptr(p, sp["gather_off"][ch]) + r0 * h * 2
             bc.flag[p] = f.peer_ptr(p, sp["ag_flags"][ch]) + 4 * self.tp_rank
-        bc.world, bc.epoch_ctr, bc.done_ctr = w, sp["ag_epoch"][ch], sp["ag_done"][ch]
+        bc.world, bc.epoch_ctr, bc.done_ctr, bc.partials_bf16 = w, sp["ag_epoch"][ch], sp["ag_done"][ch], 1
         stream = _c(torch.cuda.current_stream().cuda_stream)
         if mine > 0:
             res = residual[r0: r0 + mine]
@@ -317,8 +318,8 @@ class TensorParallel:
             # every rank sums its own region of the slots, the regions are gathered (end of a forward pass: once, NCCL)
             f, sp, w, h = self.fab, self.sp, self.tp_size, delta.hidden
             f.barrier()          # every rank's GEMM (and its stores) precede its arrival at the barrier
-            slots = f.view(sp["slots_off"][delta.chan], (w, delta.region * h), torch.float32)
-            part = slots.sum(0).to(torch.bfloat16).view(delta.region, h)
+            slots = f.view(sp["slots_off"][delta.chan], (w, delta.region * h), torch.bfloat16)
+            part = slots.float().sum(0).to(torch.bfloat16).view(delta.region, h)
             full = torch.empty(w * delta.region, h, dtype=torch.bfloat16, device=self.device)
             dist.all_gather_into_tensor(full, part.contiguous(), group=self.group)
             return full[: delta.rows]
