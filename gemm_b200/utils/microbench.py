@@ -129,6 +129,26 @@ def _moe(args, t: int, name: str):
 
 def case_moe_decode(args):
     _moe(args, 64, "moe_decode")
+    # what ONE rank of an 8-way expert-parallel group runs per layer: all 64 gathered tokens against its 16 local experts
+    from ..models.weights import LinearWeight
+    e_all, e_loc, kk, h, inter = 128, 16, 8, 2048, 768
+    x = torch.randn(64, h, device="cuda").bfloat16()
+    router = (torch.randn(e_all, h, device="cuda") * 0.05).bfloat16()
+    w1 = mxfp8.quantize(torch.randn(e_loc * 2 * inter, h, device="cuda") * 0.05)
+    w2 = mxfp8.quantize(torch.randn(e_loc * h, inter, device="cuda") * 0.05)
+    lw1 = LinearWeight("mxfp8", 2 * inter, h, mx=mxfp8.MxTensor(mxfp8.tile_weight(w1.data), w1.sf, e_loc * 2 * inter, h, 128, tiled=True),
+                       groups=e_loc, rows_per_group=2 * inter)
+    lw2 = LinearWeight("mxfp8", h, inter, mx=mxfp8.MxTensor(mxfp8.tile_weight(w2.data), w2.sf, e_loc * h, inter, 128, tiled=True),
+                       groups=e_loc, rows_per_group=h)
+    if moe.can_prep(x, router, kk):
+        ids, wts, pl, xq = moe.prep_hidden(x, router, kk, e_loc, 32, local_range=(32, e_loc))
+        touched = int((pl.seg_count > 0).sum())
+        pairs = int(pl.seg_count.sum())
+        _run("moe_prep_ep8_rank", lambda: moe.prep_hidden(x, router, kk, e_loc, 32, local_range=(32, e_loc)), 0.0, e_all * h * 2 + 64 * h * 2, args,
+             local_pairs=pairs)
+        if moe.can_fuse_ffn(xq, lw1, lw2, e_loc, pl.capacity):
+            _run("moe_ffn_fused_ep8_rank", lambda: moe.expert_ffn_fused(xq, lw1, lw2, e_loc, pl), 6.0 * pairs * h * inter,
+                 touched * 3 * h * inter + pairs * h * 3, args, experts_touched=touched, local_pairs=pairs)
 
 
 def case_moe_prefill(args):
