@@ -163,13 +163,19 @@ class Engine:
                               for s in range(b)], dtype=torch.int32, device=self.device)
         max_kv = max(self.seq_len) + max_new_tokens + 1
         splits = att.pick_splits(b, self.hkv_local, max_kv) if self.device.type == "cuda" else 1
+        # decode attention as one equal piece of the KV stream per resident CTA (the cuts follow the sequences as they grow)
+        sk = att.build_work_streamk([n + 1 for n in self.seq_len], self.hkv_local) \
+            if (self.device.type == "cuda" and att.DECODE_STREAMK and not self.kv.quantized and self.hq_local // self.hkv_local <= 16) else None
         st = self._static
         st["ids"] = first_tokens.to(device=self.device, dtype=torch.int32).clone()
         st["positions"], st["slots"] = pos, slots
         st["kv_len"] = pos + 1
         st["block_table"] = bt
         st["cu_q"] = torch.arange(b + 1, dtype=torch.int32, device=self.device)
-        st["work"] = att.build_work([1] * b, self.hq_local, self.hkv_local, splits).to(self.device)
+        if sk is not None:
+            st["work"], splits = sk[0].to(self.device), sk[1]
+        else:
+            st["work"] = att.build_work([1] * b, self.hq_local, self.hkv_local, splits).to(self.device)
         st["rows"] = torch.arange(b, dtype=torch.int64, device=self.device)
         st["tokens"] = torch.zeros(b, dtype=torch.int32, device=self.device)
         st["seq_slots"] = torch.arange(b, dtype=torch.int32, device=self.device)
