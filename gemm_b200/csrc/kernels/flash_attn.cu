@@ -502,10 +502,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       bool ok = true;
       for (int f = 0; ok && fd_fragment(a, f, fr); ++f) {
         if (fr.n_blk == 0) continue;
-        if (fc > 0 && !mbar_wait(q_empty, (uint32_t)(fc - 1) & 1, abort_flag, a.status, 409, f)) { ok = false; break; }
-        mbar_expect_tx(q_full, (uint32_t)(2 * 128 * G));
-        tma_load_3d(sQ, &tmQ, q_full, 0, fr.kvh * G, fr.tok);
-        tma_load_3d(sQ + 2048, &tmQ, q_full, 64, fr.kvh * G, fr.tok);
         const int ppb = kBN / a.page_size;
         const uint32_t page_bytes = (uint32_t)a.page_size * 128;
         const int* bt = a.block_table + (size_t)fr.seq * a.max_pages;
@@ -522,6 +518,14 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             uint8_t* dst = ring + slot * 32768 + p * page_bytes;
             tma_load_3d(dst, tm, &t_full[slot], 0, fr.kvh, page * a.page_size);
             tma_load_3d(dst + 16384, tm, &t_full[slot], 64, fr.kvh, page * a.page_size);
+          }
+          if (lt == 0) {
+            // the queries follow the fragment's first K tile: that tile is already on its way while this thread waits for the
+            // previous fragment's S products to release the Q buffer
+            if (fc > 0 && !mbar_wait(q_empty, (uint32_t)(fc - 1) & 1, abort_flag, a.status, 409, f)) { ok = false; break; }
+            mbar_expect_tx(q_full, (uint32_t)(2 * 128 * G));
+            tma_load_3d(sQ, &tmQ, q_full, 0, fr.kvh * G, fr.tok);
+            tma_load_3d(sQ + 2048, &tmQ, q_full, 64, fr.kvh * G, fr.tok);
           }
         }
         t_base += 2 * fr.n_blk; ++fc;
@@ -717,6 +721,34 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
       }
       if (!direct && !merge) continue;
+      float mg[kFdN];
+      if (!direct) {
+        // out = sum_s 2^(lse_s - lse_max) O_s / sum_s 2^(lse_s - lse_max) over the item's partials, in slot order.  One slot at a
+        // time for all heads: its 2 G loads are independent of each other (a load after a load per head and slot cost 30 us).
+        float mx[kFdN], acc[kFdN], den[kFdN];
+#pragma unroll
+        for (int h = 0; h < kFdN; ++h) { mx[h] = -INFINITY; acc[h] = 0.f; den[h] = 0.f; }
+        for (int sidx = 0; sidx < fr.nfrag; ++sidx) {
+          const size_t row0 = ((size_t)sidx * a.total_tokens + tok) * a.hq + (size_t)fr.kvh * G;
+          float ls[kFdN], pv[kFdN];
+#pragma unroll
+          for (int h = 0; h < kFdN; ++h) {
+            ls[h] = (h < G) ? __ldcg(a.part_lse + row0 + h) : -INFINITY;
+            pv[h] = (h < G) ? __ldcg(a.part_o + (row0 + h) * kD + r) : 0.f;
+          }
+#pragma unroll
+          for (int h = 0; h < kFdN; ++h) {
+            if (ls[h] == -INFINITY) continue;
+            const float m_new = fmaxf(mx[h], ls[h]);
+            const float so = exp2f(mx[h] - m_new), wn = exp2f(ls[h] - m_new);    // exp2(-inf) = 0 for the first finite slot
+            acc[h] = acc[h] * so + wn * pv[h];
+            den[h] = den[h] * so + wn;
+            mx[h] = m_new;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < kFdN; ++h) mg[h] = den[h] > 0.f ? acc[h] / den[h] : 0.f;
+      }
 #pragma unroll
       for (int h = 0; h < kFdN; ++h) {
         if (h >= G) continue;
@@ -726,20 +758,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const float inv_l = (l[h] > 0.f) ? 1.0f / l[h] : 0.f;
           val = __uint_as_float(o[h]) * inv_l;
         } else {
-          // out = sum_s 2^(lse_s - lse_max) O_s / sum_s 2^(lse_s - lse_max) over the item's partials, in slot order
-          float mx = -INFINITY;
-          for (int sidx = 0; sidx < fr.nfrag; ++sidx)
-            mx = fmaxf(mx, __ldcg(a.part_lse + ((size_t)sidx * a.total_tokens + tok) * a.hq + head));
-          float acc = 0.f, den = 0.f;
-          for (int sidx = 0; sidx < fr.nfrag; ++sidx) {
-            const size_t row = ((size_t)sidx * a.total_tokens + tok) * a.hq + head;
-            const float ls = __ldcg(a.part_lse + row);
-            if (ls == -INFINITY) continue;
-            const float wgt = exp2f(ls - mx);
-            acc += wgt * __ldcg(a.part_o + row * kD + r);
-            den += wgt;
-          }
-          val = den > 0.f ? acc / den : 0.f;
+          val = mg[h];
         }
         if (a.out_q != nullptr) {
           // the 32 features of this warp are one scale block of the row: quantise here instead of in a kernel of its own
