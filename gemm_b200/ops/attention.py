@@ -42,8 +42,13 @@ def build_work(q_lens: Sequence[int], hq: int, hkv: int, num_splits: int = 1) ->
     return torch.tensor(items, dtype=torch.int32).reshape(-1, 4)
 
 
-# decode: one equal piece of the KV stream per resident CTA (GB_DECODE_STREAMK=0: one CTA per (sequence, KV head, split))
-DECODE_STREAMK = os.environ.get("GB_DECODE_STREAMK", "1") != "0"
+# Decode work lists.  Default: one CTA per (sequence, KV head, split), the splits of an item merged inside the kernel by the CTA
+# that writes the last partial (no combine launch).  GB_DECODE_STREAMK=1 switches to the stream-K list (one equal piece of the KV
+# stream per resident CTA, pieces spanning items): it levels the SMs' loads (256 items on 296 CTA slots leave 40 SMs half idle) but
+# measured slower: 89 us against 75 us at 64 x 2048, 57 against 50 at 32 x 2048, 40 against 28 at 8 x 2048 (32 / 4 heads): a
+# fragment boundary drains the K / V ring, reloads Q and serialises the next block's softmax behind the fragment's epilogue and
+# merge, which costs more than the up to 13 % of balance it buys.
+DECODE_STREAMK = os.environ.get("GB_DECODE_STREAMK", "0") == "1"
 _item_ctr = {}
 
 
@@ -130,6 +135,10 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_
     if out is None:
         out = torch.empty(t, hq, d, dtype=torch.bfloat16, device=q.device)
     lib = _native.cuda()
+    if decode and USE_DECODE_KERNEL and hq // hkv <= 16 and (work.dim() == 3 or (num_splits > 1 and scratch is None)):
+        # stream-K work list, or a classic split list: either way the partials are merged inside the kernel
+        _decode_merged(q, k_cache, v_cache, out, None, None, 0, work, cu_q, kv_len, block_table, page_size, num_splits, window)
+        return out
     part_o = part_lse = None
     if num_splits > 1:
         if scratch is not None:
@@ -138,10 +147,6 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_
             part_o = torch.empty(num_splits, t, hq, d, dtype=torch.float32, device=q.device)
             part_lse = torch.empty(num_splits, t, hq, dtype=torch.float32, device=q.device)
     stream = _c(torch.cuda.current_stream().cuda_stream)
-    if decode and USE_DECODE_KERNEL and hq // hkv <= 16 and (work.dim() == 3 or (num_splits > 1 and scratch is None and DECODE_STREAMK)):
-        # stream-K work list, or a classic split list: either way the partials are merged inside the kernel
-        _decode_merged(q, k_cache, v_cache, out, None, None, 0, work, cu_q, kv_len, block_table, page_size, num_splits, window)
-        return out
     if decode and USE_DECODE_KERNEL and hq // hkv <= 16:
         rc = lib.gb_flash_decode(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
                                  _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
@@ -221,7 +226,7 @@ def attention_decode_mx(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     rp = (t + 127) // 128 * 128
     oq = torch.empty(rp, hq * d, dtype=torch.uint8, device=q.device)
     sf = ew.sf_alloc(rp, hq * d, q.device, sf_layout, init=False)
-    if work.dim() == 3 or (num_splits > 1 and DECODE_STREAMK):
+    if work.dim() == 3 or num_splits > 1:
         _decode_merged(q, k_cache, v_cache, None, oq, sf, 1 if sf_layout == 32 else 0, work, cu_q, kv_len, block_table, page_size, num_splits, window)
         return MxTensor(oq, sf, t, hq * d, sf_layout)
     if num_splits > 1:
