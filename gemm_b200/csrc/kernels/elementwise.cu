@@ -108,16 +108,19 @@ rmsnorm_kernel(__nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __rest
 #pragma unroll
           for (int j = 0; j < 8; ++j) d[j] = 0.f;
           // partial p = (rank, K split): ranks are partial_stride apart, the splits of one rank part_inner_stride
-          for (int p = 0; p < n_partials; ++p) {
-            const int po = p / part_inner, pi = p - po * part_inner;
-            const size_t off = (size_t)po * partial_stride + (size_t)pi * part_inner_stride + (size_t)row * hidden + vi * 8;
-            if (bc.partials_bf16) {
+          if (bc.partials_bf16) {
+            // a reduce-scatter that travelled as bf16 rows (prefill-sized tensor parallelism)
+            for (int p = 0; p < n_partials; ++p) {
               float t8[8];
-              load8(reinterpret_cast<const __nv_bfloat16*>(partials) + off, t8);
+              load8(reinterpret_cast<const __nv_bfloat16*>(partials) + (size_t)p * partial_stride + (size_t)row * hidden + vi * 8, t8);
 #pragma unroll
               for (int j = 0; j < 8; ++j) d[j] += t8[j];
-            } else {
-              const float4* src = reinterpret_cast<const float4*>(partials + off);
+            }
+          } else {
+            for (int p = 0; p < n_partials; ++p) {
+              const int po = p / part_inner, pi = p - po * part_inner;
+              const float4* src = reinterpret_cast<const float4*>(partials + (size_t)po * partial_stride + (size_t)pi * part_inner_stride +
+                                                                  (size_t)row * hidden + vi * 8);
               const float4 a = src[0], b = src[1];
               d[0] += a.x; d[1] += a.y; d[2] += a.z; d[3] += a.w; d[4] += b.x; d[5] += b.y; d[6] += b.z; d[7] += b.w;
             }

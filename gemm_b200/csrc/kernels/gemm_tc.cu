@@ -80,6 +80,7 @@ struct GemmArgs {
   size_t sfa_bytes, sfb_bytes, out_bytes, out_sf_bytes;
   // ---- weight layout: 0 = row-major [rows, k]; 1 = tiled [rows/128][k-blocks][128 rows][128 bytes], every 16 KB operand
   // tile of the main loop is one contiguous block of memory (one DRAM burst sequence instead of 128 strided lines)
+  int early_weights;  // != 0: a plain decode-sized launch requests its first weight tiles before the dependency wait
   int dual_raw;  // DUAL without the activation: the second accumulator is the row block up_row_offset further down the same matrix
   int w_tiled;
 };
@@ -191,7 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // tail.  The stage's barrier gets the byte count of this part without an arrival; the token tile (and its arrival) follow
   // in the producer loop below.
   int pre_stages = 0;
-  if (threadIdx.x == 0 && args.num_groups == 0 && args.wait_n == 0 && SFG == 1) {
+  if (threadIdx.x == 0 && args.early_weights && args.num_groups == 0 && args.wait_n == 0 && SFG == 1) {
     TileCursor<TN> cur0; Tile t0;
     if (cur0.get(args, s_start, s_count, blockIdx.x, t0)) {
       const int kb0 = t0.ks * kb_per, kb1 = min(num_kb, kb0 + kb_per);
@@ -778,6 +779,11 @@ GB_API int gb_gemm(const void* w, const void* x, void* out, int n_out, int k, in
   a.up_row_offset = up_row_offset; a.seg_start = seg_start; a.seg_count = seg_count;
   a.sfa = (const uint8_t*)sfa; a.sfb = (const uint8_t*)sfb; a.out = out; a.ldo = ldo; a.out_f32 = (flags & GEMM_OUT_F32) ? 1 : 0;
   a.w_tiled = w_tiled ? 1 : 0;
+  {
+    static int early = -1;                      // GB_GEMM_EARLY_WEIGHTS=0 switches the early weight requests off (A/B measurements)
+    if (early < 0) { const char* e = getenv("GB_GEMM_EARLY_WEIGHTS"); early = (e != nullptr && atoi(e) == 0) ? 0 : 1; }
+    a.early_weights = early;
+  }
   a.dual_raw = (flags & GEMM_DUAL_RAW) ? 1 : 0;
   if (a.dual_raw && (!dual || qo)) return fail("gemm: GEMM_DUAL_RAW needs GEMM_DUAL without GEMM_QUANT_OUT%s");
   a.out_sf = (uint8_t*)out_sf; a.bias = bias; a.row_map = row_map; a.row_scale = row_scale; a.status = (KernelStatus*)status;
