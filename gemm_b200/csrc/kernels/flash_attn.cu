@@ -49,10 +49,6 @@ struct FaArgs {
   uint8_t* out_q;
   uint8_t* out_sf;
   int out_sf32;             // scale-atom layout: one atom per 32 rows (1) or per 128 rows (0)
-  // decode kernel only: stream-K work list (see fd_fragment) and the per-item arrival counters of its in-kernel merge
-  int streamk;
-  int* item_ctr;            // [n_seq * hkv] zero between launches (the merging CTA resets its item's counter); null: partials are left
-                            // for gb_fa_combine
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -397,54 +393,6 @@ __device__ __forceinline__ bool softmax_bar_and(bool pred) {
   return r != 0;
 }
 
-// One fragment of the CTA's work: a range of KV blocks of one (sequence, KV head) item.
-//   classic work list  [n, 4] = {seq, kv_head, -, split}: the CTA has ONE fragment, split `split` of `num_splits` equal block ranges.
-//   stream-K work list [n_cta, kFdMaxFrag, 4] = {seq (< 0: no more), kv_head | slot << 8 | nfrag << 16, frac_lo, frac_hi}: the host cuts
-//     the concatenated block ranges of all items into one equal piece per CTA, so a piece may end inside an item and continue into
-//     the next: fragment = blocks [nb * frac_lo, nb * frac_hi) / 65536 of the item's nb blocks (nb comes from the device-side
-//     length, so the cut moves with the sequence), `slot` = which of the item's `nfrag` partials this is.  256 items on 296
-//     resident CTAs otherwise leave 40 SMs with half the work of the others.
-constexpr int kFdMaxFrag = 4;
-struct FdFrag { int seq, kvh, slot, nfrag, blk_lo, n_blk, tok, kv_len, qpos, first_pos, item; bool bad; };
-
-__device__ __forceinline__ bool fd_fragment(const FaArgs& a, int f, FdFrag& fr) {
-  int frac_lo = 0, frac_hi = 65536;
-  if (a.streamk) {
-    if (f >= kFdMaxFrag) return false;
-    const int* wk = a.work + ((size_t)blockIdx.x * kFdMaxFrag + f) * 4;
-    fr.seq = wk[0];
-    if (fr.seq < 0) return false;
-    fr.kvh = wk[1] & 0xff; fr.slot = (wk[1] >> 8) & 0xff; fr.nfrag = (wk[1] >> 16) & 0xff;
-    frac_lo = wk[2]; frac_hi = wk[3];
-  } else {
-    if (f > 0) return false;
-    const int* wk = a.work + (size_t)blockIdx.x * 4;
-    fr.seq = wk[0]; fr.kvh = wk[1]; fr.slot = wk[3]; fr.nfrag = a.num_splits;
-  }
-  const int G = a.hq / a.hkv;
-  fr.tok = a.cu_q[fr.seq];
-  fr.kv_len = a.kv_len[fr.seq];
-  fr.qpos = fr.kv_len - 1;
-  fr.first_pos = (a.window > 0) ? max(0, fr.qpos - a.window + 1) : 0;
-  int blk_lo = fr.first_pos / kBN, blk_hi = (fr.kv_len > 0) ? (fr.kv_len - 1) / kBN + 1 : 0;
-  const int nb = max(0, blk_hi - blk_lo);
-  if (a.streamk) {
-    const int lo = (int)(((long long)nb * frac_lo) >> 16), hi = (int)(((long long)nb * frac_hi) >> 16);
-    blk_hi = blk_lo + hi; blk_lo = blk_lo + lo;
-  } else if (a.num_splits > 1) {
-    const int per = (nb + a.num_splits - 1) / a.num_splits;
-    blk_lo = blk_lo + fr.slot * per;
-    blk_hi = min(blk_hi, blk_lo + per);
-  }
-  fr.blk_lo = blk_lo;
-  fr.n_blk = max(0, blk_hi - blk_lo);
-  fr.item = fr.seq * a.hkv + fr.kvh;
-  fr.bad = fr.kvh < 0 || fr.kvh >= a.hkv || G > kFdN || (a.cu_q[fr.seq + 1] - fr.tok) != 1 || fr.slot >= max(1, a.num_splits) ||
-           frac_lo < 0 || frac_hi > 65536 || frac_lo > frac_hi;
-  if (fr.bad) fr.n_blk = 0;
-  return true;
-}
-
 __global__ void __launch_bounds__(kFdThreads, 2)
 flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const FaArgs a) {
@@ -460,11 +408,8 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* s_full = bars + 7;                 // 2
   uint64_t* p_ready = bars + 9;                // 1 (128 arrivals)
   uint64_t* o_ready = bars + 10;               // 2: block j commits to o_ready[j & 1]
-  uint64_t* q_empty = bars + 12;               // 1: the S MMAs of a fragment have read Q (the next fragment's Q may land)
-  uint64_t* o_taken = bars + 13;               // 128 arrivals: the softmax threads have read a fragment's O out of TMEM
-  uint32_t* tmem_slot = (uint32_t*)(bars + 14);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-  int* last_flag = (int*)(tmem_slot + 2);      // stream-K: this CTA wrote the last partial of the item and merges
   float* red_max = (float*)(bars + 16);        // [2 (block parity)][4 warps][16 heads]
   float* red_sum = red_max + 2 * 4 * kFdN;     // [2][4][16]
 
@@ -474,7 +419,6 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     for (int i = 0; i < 3; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 1); }
     for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
     mbar_init(p_ready, 128); mbar_init(&o_ready[0], 1); mbar_init(&o_ready[1], 1);
-    mbar_init(q_empty, 1); mbar_init(o_taken, 128);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -489,95 +433,87 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 2 * kFdN;
   pdl_wait();
-  pdl_trigger();
 
   const int G = a.hq / a.hkv;
-  // Every role walks the CTA's fragments on its own.  Counters that pick barrier slots and phases run on ACROSS fragments:
-  // t counts K / V tiles, j KV blocks, fc fragments that had work (a fragment without blocks touches no barrier).
+  const int* wk = a.work + (size_t)blockIdx.x * 4;
+  const int seq = wk[0], kvh = wk[1], split = wk[3];
+  const int tok = a.cu_q[seq];
+  const int kv_len = a.kv_len[seq];
+  const int qpos = kv_len - 1;
+  int first_pos = 0;
+  if (a.window > 0) first_pos = max(0, qpos - a.window + 1);
+  int blk_lo = first_pos / kBN, blk_hi = (kv_len > 0) ? (kv_len - 1) / kBN + 1 : 0;
+  if (a.num_splits > 1) {
+    const int nb = blk_hi - blk_lo, per = (nb + a.num_splits - 1) / a.num_splits;
+    blk_lo = blk_lo + split * per;
+    blk_hi = min(blk_hi, blk_lo + per);
+  }
+  int n_blk = max(0, blk_hi - blk_lo);
+  const bool bad_item = kvh < 0 || kvh >= a.hkv || G > kFdN || (a.cu_q[seq + 1] - tok) != 1;
+  if (bad_item) {
+    if (threadIdx.x == 0) report_status(a.status, ST_BAD_ARG, 650, kvh, a.hkv, G);
+    n_blk = 0;
+  }
 
   if (warp == 0) {
-    if (lane == 0) {
-      FdFrag fr;
-      int t_base = 0, fc = 0;
+    if (lane == 0 && n_blk > 0) {
+      mbar_expect_tx(q_full, (uint32_t)(2 * 128 * G));
+      tma_load_3d(sQ, &tmQ, q_full, 0, kvh * G, tok);
+      tma_load_3d(sQ + 2048, &tmQ, q_full, 64, kvh * G, tok);
+      const int ppb = kBN / a.page_size;
+      const uint32_t page_bytes = (uint32_t)a.page_size * 128;
+      const int* bt = a.block_table + (size_t)seq * a.max_pages;
+      const int last_page = (kv_len + a.page_size - 1) / a.page_size - 1;
       bool ok = true;
-      for (int f = 0; ok && fd_fragment(a, f, fr); ++f) {
-        if (fr.n_blk == 0) continue;
-        const int ppb = kBN / a.page_size;
-        const uint32_t page_bytes = (uint32_t)a.page_size * 128;
-        const int* bt = a.block_table + (size_t)fr.seq * a.max_pages;
-        const int last_page = (fr.kv_len + a.page_size - 1) / a.page_size - 1;
-        for (int lt = 0; lt < 2 * fr.n_blk && ok; ++lt) {
-          const int t = t_base + lt;
-          const int slot = t % 3; const uint32_t ph = (uint32_t)(t / 3) & 1;
-          const int blk = fr.blk_lo + (lt >> 1);
-          const CUtensorMap* tm = (lt & 1) ? &tmV : &tmK;
-          if (!mbar_wait(&t_empty[slot], ph ^ 1, abort_flag, a.status, 410, t)) { ok = false; break; }
-          mbar_expect_tx(&t_full[slot], 32768u);
-          for (int p = 0; p < ppb; ++p) {
-            const int page = bt[min(blk * ppb + p, last_page)];
-            uint8_t* dst = ring + slot * 32768 + p * page_bytes;
-            tma_load_3d(dst, tm, &t_full[slot], 0, fr.kvh, page * a.page_size);
-            tma_load_3d(dst + 16384, tm, &t_full[slot], 64, fr.kvh, page * a.page_size);
-          }
-          if (lt == 0) {
-            // the queries follow the fragment's first K tile: that tile is already on its way while this thread waits for the
-            // previous fragment's S products to release the Q buffer
-            if (fc > 0 && !mbar_wait(q_empty, (uint32_t)(fc - 1) & 1, abort_flag, a.status, 409, f)) { ok = false; break; }
-            mbar_expect_tx(q_full, (uint32_t)(2 * 128 * G));
-            tma_load_3d(sQ, &tmQ, q_full, 0, fr.kvh * G, fr.tok);
-            tma_load_3d(sQ + 2048, &tmQ, q_full, 64, fr.kvh * G, fr.tok);
-          }
+      for (int t = 0; t < 2 * n_blk && ok; ++t) {
+        const int slot = t % 3; const uint32_t ph = (uint32_t)(t / 3) & 1;
+        const int blk = blk_lo + (t >> 1);
+        const CUtensorMap* tm = (t & 1) ? &tmV : &tmK;
+        if (!mbar_wait(&t_empty[slot], ph ^ 1, abort_flag, a.status, 410, t)) { ok = false; break; }
+        mbar_expect_tx(&t_full[slot], 32768u);
+        for (int p = 0; p < ppb; ++p) {
+          const int page = bt[min(blk * ppb + p, last_page)];
+          uint8_t* dst = ring + slot * 32768 + p * page_bytes;
+          tma_load_3d(dst, tm, &t_full[slot], 0, kvh, page * a.page_size);
+          tma_load_3d(dst + 16384, tm, &t_full[slot], 64, kvh, page * a.page_size);
         }
-        t_base += 2 * fr.n_blk; ++fc;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && n_blk > 0) {
       constexpr uint32_t idesc_s = make_idesc(128, kFdN, 1, 1, 0, 0);
       constexpr uint32_t idesc_o = make_idesc(128, kFdN, 1, 1, 1, 0);      // A (= V^T) is MN-major
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-      FdFrag fr;
-      int t_base = 0, j_base = 0, fc = 0;
-      bool ok = true;
-      for (int f = 0; ok && fd_fragment(a, f, fr); ++f) {
-        if (fr.n_blk == 0) continue;
-        const int n_blk = fr.n_blk;
-        ok = mbar_wait(q_full, (uint32_t)fc & 1, abort_flag, a.status, 510, f);
-        auto issue_s = [&](int lj) -> bool {
-          const int j = j_base + lj, s = j & 1;
-          const int t = t_base + 2 * lj, slot = t % 3; const uint32_t ph = (uint32_t)(t / 3) & 1;
-          if (!mbar_wait(&t_full[slot], ph, abort_flag, a.status, 511, j)) return false;
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(ring + slot * 32768);
+      bool ok = mbar_wait(q_full, 0, abort_flag, a.status, 510);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        const int t = 2 * j, slot = t % 3; const uint32_t ph = (uint32_t)(t / 3) & 1;
+        if (!mbar_wait(&t_full[slot], ph, abort_flag, a.status, 511, j)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(ring + slot * 32768);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            mma_f16_ss(tmem_base + s * kFdN, make_sdesc_sw128(k_addr + (ks >> 2) * 16384 + (ks & 3) * 32),
-                       make_sdesc_sw128(q_addr + (ks >> 2) * 2048 + (ks & 3) * 32), idesc_s, ks > 0 ? 1u : 0u);
-          tc_commit(&s_full[s]);
-          tc_commit(&t_empty[slot]);
-          if (lj == n_blk - 1) tc_commit(q_empty);          // every S product of this fragment has been issued: Q may be replaced
-          return true;
-        };
-        if (ok) ok = issue_s(0);
-        for (int lj = 0; lj < n_blk && ok; ++lj) {
-          if (lj + 1 < n_blk) { if (!issue_s(lj + 1)) { ok = false; break; } }
-          const int j = j_base + lj;
-          const int tv = t_base + 2 * lj + 1, vslot = tv % 3;
-          if (!mbar_wait(p_ready, (uint32_t)j & 1, abort_flag, a.status, 512, j)) { ok = false; break; }
-          if (!mbar_wait(&t_full[vslot], (uint32_t)(tv / 3) & 1, abort_flag, a.status, 513, j)) { ok = false; break; }
-          // the first P V product of a fragment overwrites O: the previous fragment's O must have been read out
-          if (lj == 0 && fc > 0 && !mbar_wait(o_taken, (uint32_t)(fc - 1) & 1, abort_flag, a.status, 514, f)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t v_addr = smem_u32(ring + vslot * 32768);
-          const uint32_t pj = p_addr + (j & 1) * 4096;
+        for (int ks = 0; ks < 8; ++ks)
+          mma_f16_ss(tmem_base + s * kFdN, make_sdesc_sw128(k_addr + (ks >> 2) * 16384 + (ks & 3) * 32),
+                     make_sdesc_sw128(q_addr + (ks >> 2) * 2048 + (ks & 3) * 32), idesc_s, ks > 0 ? 1u : 0u);
+        tc_commit(&s_full[s]);
+        tc_commit(&t_empty[slot]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_blk && ok; ++j) {
+        if (j + 1 < n_blk) { if (!issue_s(j + 1)) { ok = false; break; } }
+        const int tv = 2 * j + 1, vslot = tv % 3;
+        if (!mbar_wait(p_ready, j & 1, abort_flag, a.status, 512, j)) { ok = false; break; }
+        if (!mbar_wait(&t_full[vslot], (uint32_t)(tv / 3) & 1, abort_flag, a.status, 513, j)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(ring + vslot * 32768);
+        const uint32_t pj = p_addr + (j & 1) * 4096;
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            mma_f16_ss(tmem_o, make_sdesc_sw128_mn(v_addr + ks * 2048, 16384), make_sdesc_sw128(pj + (ks >> 2) * 2048 + (ks & 3) * 32),
-                       idesc_o, (lj > 0 || ks > 0) ? 1u : 0u);
-          tc_commit(&o_ready[j & 1]);
-          tc_commit(&t_empty[vslot]);
-        }
-        t_base += 2 * n_blk; j_base += n_blk; ++fc;
+        for (int ks = 0; ks < 8; ++ks)
+          mma_f16_ss(tmem_o, make_sdesc_sw128_mn(v_addr + ks * 2048, 16384), make_sdesc_sw128(pj + (ks >> 2) * 2048 + (ks & 3) * 32),
+                     idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
+        tc_commit(&o_ready[j & 1]);
+        tc_commit(&t_empty[vslot]);
       }
     }
   } else {
@@ -585,181 +521,103 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int q = warp & 3;
     const int r = q * 32 + lane;
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    constexpr float kTau = 8.0f;     // O and l are only rescaled when a block raises a maximum by more than 2^kTau
-    FdFrag fr;
-    int j_base = 0, fc = 0;
-    for (int f = 0; fd_fragment(a, f, fr); ++f) {
-      const int n_blk = fr.n_blk;
-      if (fr.bad && threadIdx.x == 64) report_status(a.status, ST_BAD_ARG, 650, fr.kvh, a.hkv, G);
-      float m[kFdN], l[kFdN];        // m: the reference maximum the exponentials are taken against (may lag the true maximum by <= kTau)
+    float m[kFdN], l[kFdN];          // m: the reference maximum the exponentials are taken against (may lag the true maximum by <= kTau)
                                      // l: THIS thread's share of the row sums (its positions only); the threads' shares are added once, at the end
 #pragma unroll
-      for (int h = 0; h < kFdN; ++h) { m[h] = -INFINITY; l[h] = 0.f; }
-      bool ok = true, fail_o = false;  // fail_o: a wait for the second MMA ran out; it is put to the vote at the next barrier
-      for (int lj = 0; lj < n_blk && ok; ++lj) {
-        const int j = j_base + lj;
-        const int s = j & 1;
-        const bool got_s = mbar_wait(&s_full[s], (uint32_t)(j >> 1) & 1, abort_flag, a.status, 610, j);
-        tc_fence_after();
-        float sv[kFdN];
-        tmem_ld_x16(tmem_base + s * kFdN + lane_off, reinterpret_cast<uint32_t*>(sv));
-        tc_wait_ld();
-        const int kp = (fr.blk_lo + lj) * kBN + r;
-        const bool live = kp <= fr.qpos && kp >= fr.first_pos;
-        float* rm = red_max + (j & 1) * 4 * kFdN;
+    for (int h = 0; h < kFdN; ++h) { m[h] = -INFINITY; l[h] = 0.f; }
+    constexpr float kTau = 8.0f;     // O and l are only rescaled when a block raises a maximum by more than 2^kTau
+    bool ok = true, fail_o = false;  // fail_o: a wait for the second MMA ran out; it is put to the vote at the next barrier
+    for (int j = 0; j < n_blk && ok; ++j) {
+      const int s = j & 1;
+      const bool got_s = mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, a.status, 610, j);
+      tc_fence_after();
+      float sv[kFdN];
+      tmem_ld_x16(tmem_base + s * kFdN + lane_off, reinterpret_cast<uint32_t*>(sv));
+      tc_wait_ld();
+      const int kp = (blk_lo + j) * kBN + r;
+      const bool live = kp <= qpos && kp >= first_pos;
+      float* rm = red_max + (j & 1) * 4 * kFdN;
 #pragma unroll
-        for (int h = 0; h < kFdN; ++h) if (!live || h >= G) sv[h] = -INFINITY;
-        {
-          const float v = warp_reduce16_max(sv, lane);            // lane L ends with head L >> 1
-          if ((lane & 1) == 0) rm[q * kFdN + (lane >> 1)] = v;
-        }
-        if (!softmax_bar_and(got_s && !fail_o)) { ok = false; break; }   // maxima of all four warps are in rm; all 128 threads leave together
-        float bm[kFdN];
-        bool need = false;
-#pragma unroll
-        for (int h = 0; h < kFdN; ++h) {
-          bm[h] = fmaxf(fmaxf(rm[h], rm[kFdN + h]), fmaxf(rm[2 * kFdN + h], rm[3 * kFdN + h]));
-          need |= (h < G) && (bm[h] > m[h] + kTau);                  // also true for the first finite maximum (m = -inf)
-        }
-        float alpha[kFdN], pv[kFdN];
-#pragma unroll
-        for (int h = 0; h < kFdN; ++h) {
-          const float m_new = need ? fmaxf(m[h], bm[h]) : m[h];
-          const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-          alpha[h] = need ? fast_exp2(m[h] - m_use) : 1.0f;
-          m[h] = m_new;
-          pv[h] = fast_exp2(sv[h] - m_use);
-          l[h] = l[h] * alpha[h] + pv[h];
-        }
-        bool got_o = true;
-        if (j >= 2) {
-          // the P buffer of this parity was read by the second MMA of block j - 2 (of this fragment or of the one before)
-          got_o = mbar_wait(&o_ready[s], (uint32_t)((j - 2) >> 1) & 1, abort_flag, a.status, 611, j);
-        }
-        if (got_o && need && lj > 0) {
-          // rare: a maximum moved by more than 2^kTau.  All earlier P V products of this fragment must have landed in O before it is rescaled.
-          got_o = mbar_wait(&o_ready[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1, abort_flag, a.status, 613, j);
-          tc_fence_after();
-          if (got_o) {
-            uint32_t o[kFdN];
-            tmem_ld_x16(tmem_o + lane_off, o);
-            tc_wait_ld();
-#pragma unroll
-            for (int h = 0; h < kFdN; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * alpha[h]);
-            asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                         :: "r"(tmem_o + lane_off), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
-                            "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
-            tc_wait_st();
-          }
-        }
-        if (got_o) {
-          // P^T into shared memory as [head][position] bf16, the K-major B operand of the second MMA (128-byte swizzle)
-          uint8_t* pb = sP + s * 4096;
-          const int half = r >> 6, chunk = (r & 63) >> 3;
-#pragma unroll
-          for (int h = 0; h < kFdN; ++h)
-            *reinterpret_cast<__nv_bfloat16*>(pb + half * 2048 + h * 128 + ((chunk ^ (h & 7)) << 4) + (r & 7) * 2) = __float2bfloat16(pv[h]);
-          fence_proxy_async_smem();                // P in shared memory -> visible to the tensor core's reads
-          tc_fence_before();
-          mbar_arrive(p_ready);
-        }
-        fail_o |= !got_o;
-      }
-      if (ok && !fail_o && n_blk > 0) {
-        const int jl = j_base + n_blk - 1;
-        ok = mbar_wait(&o_ready[jl & 1], (uint32_t)(jl >> 1) & 1, abort_flag, a.status, 612);
-      }
-      // row sums: add the 128 threads' shares (one reduce-scatter per warp, then the four warps through shared memory)
+      for (int h = 0; h < kFdN; ++h) if (!live || h >= G) sv[h] = -INFINITY;
       {
-        const float v = warp_reduce16_sum(l, lane);
-        float* rs = red_sum + (f & 1) * 4 * kFdN;
-        if ((lane & 1) == 0) rs[q * kFdN + (lane >> 1)] = v;
-        ok = softmax_bar_and(ok && !fail_o);       // every softmax thread gets here exactly once per fragment, whatever happened in the loop
-#pragma unroll
-        for (int h = 0; h < kFdN; ++h) l[h] = rs[h] + rs[kFdN + h] + rs[2 * kFdN + h] + rs[3 * kFdN + h];
+        const float v = warp_reduce16_max(sv, lane);            // lane L ends with head L >> 1
+        if ((lane & 1) == 0) rm[q * kFdN + (lane >> 1)] = v;
       }
+      if (!softmax_bar_and(got_s && !fail_o)) { ok = false; break; }   // maxima of all four warps are in rm; all 128 threads leave together
+      float bm[kFdN];
+      bool need = false;
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) {
+        bm[h] = fmaxf(fmaxf(rm[h], rm[kFdN + h]), fmaxf(rm[2 * kFdN + h], rm[3 * kFdN + h]));
+        need |= (h < G) && (bm[h] > m[h] + kTau);                  // also true for the first finite maximum (m = -inf)
+      }
+      float alpha[kFdN], pv[kFdN];
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) {
+        const float m_new = need ? fmaxf(m[h], bm[h]) : m[h];
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        alpha[h] = need ? fast_exp2(m[h] - m_use) : 1.0f;
+        m[h] = m_new;
+        pv[h] = fast_exp2(sv[h] - m_use);
+        l[h] = l[h] * alpha[h] + pv[h];
+      }
+      bool got_o = true;
+      if (j >= 2) {
+        // the P buffer of this parity was read by the second MMA of block j - 2
+        got_o = mbar_wait(&o_ready[s], (uint32_t)((j - 2) >> 1) & 1, abort_flag, a.status, 611, j);
+      }
+      if (got_o && need && j > 0) {
+        // rare: a maximum moved by more than 2^kTau.  All earlier P V products must have landed in O before it is rescaled.
+        got_o = mbar_wait(&o_ready[(j - 1) & 1], (uint32_t)((j - 1) >> 1) & 1, abort_flag, a.status, 613, j);
+        tc_fence_after();
+        if (got_o) {
+          uint32_t o[kFdN];
+          tmem_ld_x16(tmem_o + lane_off, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int h = 0; h < kFdN; ++h) o[h] = __float_as_uint(__uint_as_float(o[h]) * alpha[h]);
+          asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                       :: "r"(tmem_o + lane_off), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]),
+                          "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]), "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+          tc_wait_st();
+        }
+      }
+      if (got_o) {
+        // P^T into shared memory as [head][position] bf16, the K-major B operand of the second MMA (128-byte swizzle)
+        uint8_t* pb = sP + s * 4096;
+        const int half = r >> 6, chunk = (r & 63) >> 3;
+#pragma unroll
+        for (int h = 0; h < kFdN; ++h)
+          *reinterpret_cast<__nv_bfloat16*>(pb + half * 2048 + h * 128 + ((chunk ^ (h & 7)) << 4) + (r & 7) * 2) = __float2bfloat16(pv[h]);
+        fence_proxy_async_smem();                // P in shared memory -> visible to the tensor core's reads
+        tc_fence_before();
+        mbar_arrive(p_ready);
+      }
+      fail_o |= !got_o;
+    }
+    if (ok && !fail_o && n_blk > 0) ok = mbar_wait(&o_ready[(n_blk - 1) & 1], (uint32_t)((n_blk - 1) >> 1) & 1, abort_flag, a.status, 612);
+    // row sums: add the 128 threads' shares (one reduce-scatter per warp, then the four warps through shared memory)
+    {
+      const float v = warp_reduce16_sum(l, lane);
+      if ((lane & 1) == 0) red_sum[q * kFdN + (lane >> 1)] = v;
+      ok = softmax_bar_and(ok && !fail_o);       // every softmax thread gets here exactly once, whatever happened in the loop
+#pragma unroll
+      for (int h = 0; h < kFdN; ++h) l[h] = red_sum[h] + red_sum[kFdN + h] + red_sum[2 * kFdN + h] + red_sum[3 * kFdN + h];
+    }
+    if (ok && !bad_item) {
+      tc_fence_after();
       uint32_t o[kFdN];
+      if (n_blk > 0) { tmem_ld_x16(tmem_o + lane_off, o); tc_wait_ld(); }
+      else {
 #pragma unroll
-      for (int h = 0; h < kFdN; ++h) o[h] = 0u;
-      if (n_blk > 0) {
-        if (ok) { tc_fence_after(); tmem_ld_x16(tmem_o + lane_off, o); tc_wait_ld(); tc_fence_before(); }
-        mbar_arrive(o_taken);                      // O is in registers (or given up): the next fragment may overwrite it
-      }
-      j_base += n_blk;
-      if (n_blk > 0) ++fc;
-      if (fr.bad) continue;                        // its indices cannot be trusted (reported above)
-
-      // ---- this fragment's result: the final rows (one fragment per item), or a partial that the item's last writer merges.  A
-      // fragment whose waits ran out still takes part in the count (with an empty partial), so the item's counter ends at zero.
-      const int tok = fr.tok;
-      const bool direct = a.part_o == nullptr;
-      bool merge = false;
-      if (direct && !ok) continue;
-      if (!direct) {
-#pragma unroll
-        for (int h = 0; h < kFdN; ++h) {
-          if (h >= G) continue;
-          const float inv_l = (l[h] > 0.f) ? 1.0f / l[h] : 0.f;
-          const size_t row = ((size_t)fr.slot * a.total_tokens + tok) * a.hq + (size_t)fr.kvh * G + h;
-          if (ok) a.part_o[row * kD + r] = __uint_as_float(o[h]) * inv_l;
-          if (r == 0) a.part_lse[row] = (ok && l[h] > 0.f) ? (m[h] + log2f(l[h])) : -INFINITY;
-        }
-        if (a.item_ctr != nullptr) {
-          // the writer of an item's last partial merges them (no combine launch): partials -> fence -> count; the counter resets itself
-          __threadfence();
-          softmax_bar_and(true);
-          if (threadIdx.x == 64) {
-            const int old = atomicAdd(a.item_ctr + fr.item, 1);
-            const int last = (old == fr.nfrag - 1) ? 1 : 0;
-            if (last) a.item_ctr[fr.item] = 0;
-            *last_flag = last;
-          }
-          softmax_bar_and(true);
-          merge = *last_flag != 0;
-          if (merge) __threadfence();
-          softmax_bar_and(true);                   // nobody rewrites last_flag for the next fragment before everyone has read it
-        }
-      }
-      if (!direct && !merge) continue;
-      float mg[kFdN];
-      if (!direct) {
-        // out = sum_s 2^(lse_s - lse_max) O_s / sum_s 2^(lse_s - lse_max) over the item's partials, in slot order.  One slot at a
-        // time for all heads: its 2 G loads are independent of each other (a load after a load per head and slot cost 30 us).
-        float mx[kFdN], acc[kFdN], den[kFdN];
-#pragma unroll
-        for (int h = 0; h < kFdN; ++h) { mx[h] = -INFINITY; acc[h] = 0.f; den[h] = 0.f; }
-        for (int sidx = 0; sidx < fr.nfrag; ++sidx) {
-          const size_t row0 = ((size_t)sidx * a.total_tokens + tok) * a.hq + (size_t)fr.kvh * G;
-          float ls[kFdN], pv[kFdN];
-#pragma unroll
-          for (int h = 0; h < kFdN; ++h) {
-            ls[h] = (h < G) ? __ldcg(a.part_lse + row0 + h) : -INFINITY;
-            pv[h] = (h < G) ? __ldcg(a.part_o + (row0 + h) * kD + r) : 0.f;
-          }
-#pragma unroll
-          for (int h = 0; h < kFdN; ++h) {
-            if (ls[h] == -INFINITY) continue;
-            const float m_new = fmaxf(mx[h], ls[h]);
-            const float so = exp2f(mx[h] - m_new), wn = exp2f(ls[h] - m_new);    // exp2(-inf) = 0 for the first finite slot
-            acc[h] = acc[h] * so + wn * pv[h];
-            den[h] = den[h] * so + wn;
-            mx[h] = m_new;
-          }
-        }
-#pragma unroll
-        for (int h = 0; h < kFdN; ++h) mg[h] = den[h] > 0.f ? acc[h] / den[h] : 0.f;
+        for (int h = 0; h < kFdN; ++h) o[h] = 0u;
       }
 #pragma unroll
       for (int h = 0; h < kFdN; ++h) {
         if (h >= G) continue;
-        const int head = fr.kvh * G + h;
-        float val;
-        if (direct) {
-          const float inv_l = (l[h] > 0.f) ? 1.0f / l[h] : 0.f;
-          val = __uint_as_float(o[h]) * inv_l;
-        } else {
-          val = mg[h];
-        }
+        const float inv_l = (l[h] > 0.f) ? 1.0f / l[h] : 0.f;
+        const int head = kvh * G + h;
+        const float val = __uint_as_float(o[h]) * inv_l;
         if (a.out_q != nullptr) {
           // the 32 features of this warp are one scale block of the row: quantise here instead of in a kernel of its own
           const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(val))));
@@ -776,13 +634,15 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                                           : ((size_t)(tok >> 7) * k_atoms + (blk >> 2)) * 512 + (tok & 31) * 16 + ((tok >> 5) & 3) * 4 + (blk & 3);
             a.out_sf[off] = (uint8_t)e;
           }
-        } else if (a.out != nullptr) {
-          a.out[((size_t)tok * a.hq + head) * kD + r] = __float2bfloat16(val);
-        }
+        } else if (a.part_o == nullptr) a.out[((size_t)tok * a.hq + head) * kD + r] = __float2bfloat16(val);
+        else a.part_o[(((size_t)split * a.total_tokens + tok) * a.hq + head) * kD + r] = val;
+        if (a.part_o != nullptr && r == 0)
+          a.part_lse[((size_t)split * a.total_tokens + tok) * a.hq + head] = (l[h] > 0.f) ? (m[h] + log2f(l[h])) : -INFINITY;
       }
     }
   }
 
+  pdl_trigger();           // a long kernel: its dependents are released at its end, not while it streams the cache
   if (*abort_flag) {
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
@@ -919,17 +779,13 @@ GB_API int gb_flash_attn_mx(const void* q, const void* k_cache, const void* v_ca
 static int flash_decode_impl(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_lse,
                            const int* work, int n_work, const int* cu_q, const int* kv_len, const int* block_table, int max_pages,
                            int page_size, long num_slots, int total_tokens, int hq, int hkv, int head_dim, int num_splits, int window,
-                           void* status, cudaStream_t stream, uint8_t* out_q, uint8_t* out_sf, int out_sf32, int streamk = 0,
-                           int* item_ctr = nullptr) {
+                           void* status, cudaStream_t stream, uint8_t* out_q, uint8_t* out_sf, int out_sf32) {
   if (head_dim != 128) return fail("flash_decode: head_dim must be 128%s");
   if (hq % hkv || hq / hkv > kFdN) return fail("flash_decode: needs Hq %% Hkv == 0 and a group of at most 16 heads%s");
-  if (hkv > 255) return fail("flash_decode: more than 255 KV heads%s");
   if (page_size < 8 || page_size > 128 || (128 % page_size) || (page_size % 8)) return fail("flash_decode: page_size must be 8..128, a multiple of 8 dividing 128%s");
   if (n_work <= 0) return 0;
   if (num_splits > 1 && part_o == nullptr) return fail("flash_decode: num_splits > 1 needs partial buffers%s");
-  if (part_o == nullptr && out == nullptr && out_q == nullptr) return fail("flash_decode: no output buffer%s");
-  if (part_o != nullptr && part_lse == nullptr) return fail("flash_decode: partial output needs part_lse%s");
-  if (item_ctr != nullptr && (part_o == nullptr || (out == nullptr && out_q == nullptr))) return fail("flash_decode: the in-kernel merge needs partial buffers and an output%s");
+  if (part_o == nullptr && out == nullptr) return fail("flash_decode: no output buffer%s");
   const int G = hq / hkv;
   CUtensorMap tmQ, tmK, tmV;
   {
@@ -950,8 +806,7 @@ static int flash_decode_impl(const void* q, const void* k_cache, const void* v_c
   a.work = work; a.cu_q = cu_q; a.kv_len = kv_len; a.block_table = block_table; a.max_pages = max_pages; a.page_size = page_size;
   a.hq = hq; a.hkv = hkv; a.num_splits = num_splits; a.causal = 1; a.window = window; a.out = (__nv_bfloat16*)out;
   a.part_o = part_o; a.part_lse = part_lse; a.total_tokens = total_tokens; a.status = (KernelStatus*)status;
-  a.out_q = out_q; a.out_sf = out_sf; a.out_sf32 = out_sf32; a.streamk = streamk ? 1 : 0; a.item_ctr = item_ctr;
-  if (out_q != nullptr) a.out = nullptr;
+  a.out_q = out_q; a.out_sf = out_sf; a.out_sf32 = out_sf32;
   static bool attr_set = false;
   if (!attr_set) {
     GB_CUDA_OK(cudaFuncSetAttribute(flash_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmem));
@@ -977,24 +832,6 @@ GB_API int gb_flash_decode_mx(const void* q, const void* k_cache, const void* v_
   if (out_q == nullptr || out_sf == nullptr) return fail("flash_decode_mx: no output buffer%s");
   return flash_decode_impl(q, k_cache, v_cache, out_q, nullptr, nullptr, work, n_work, cu_q, kv_len, block_table, max_pages, page_size,
                            num_slots, total_tokens, hq, hkv, head_dim, 1, window, status, stream, (uint8_t*)out_q, (uint8_t*)out_sf, sf32);
-}
-
-// Fragments a CTA of the stream-K decode work list may hold (the list is int32 [n_cta][this][4], see fd_fragment).
-GB_API int gb_flash_decode_max_frag() { return kFdMaxFrag; }
-
-// Decode attention over a stream-K work list (`n_cta` CTAs) or a classic one (streamk = 0), with the partials of an item merged
-// inside the kernel by the CTA that writes the last of them: part_o / part_lse [num_splits, T, Hq, 128] / [num_splits, T, Hq] are
-// scratch, item_ctr int32 [n_seq * Hkv] must be zero on entry and is left zero.  The result is bf16 `out` [T, Hq, 128] or, with
-// out_q / out_sf, MXFP8 rows [T, Hq * 128] (scale atoms in the 32-row layout when sf32 != 0).
-GB_API int gb_flash_decode_merged(const void* q, const void* k_cache, const void* v_cache, void* out, void* out_q, void* out_sf, int sf32,
-                                  float* part_o, float* part_lse, int* item_ctr, const int* work, int n_cta, int streamk, const int* cu_q,
-                                  const int* kv_len, const int* block_table, int max_pages, int page_size, long num_slots, int total_tokens,
-                                  int hq, int hkv, int head_dim, int num_splits, int window, void* status, cudaStream_t stream) {
-  if ((out_q == nullptr) != (out_sf == nullptr)) return fail("flash_decode_merged: out_q and out_sf go together%s");
-  if (part_o == nullptr || part_lse == nullptr || item_ctr == nullptr) return fail("flash_decode_merged: needs partial buffers and counters%s");
-  return flash_decode_impl(q, k_cache, v_cache, out, part_o, part_lse, work, n_cta, cu_q, kv_len, block_table, max_pages, page_size, num_slots,
-                           total_tokens, hq, hkv, head_dim, num_splits, window, status, stream, (uint8_t*)out_q, (uint8_t*)out_sf, sf32, streamk,
-                           item_ctr);
 }
 
 GB_API int gb_fa_combine(const float* part_o, const float* part_lse, void* out, float* out_lse, int splits, long rows, cudaStream_t stream) {

@@ -138,7 +138,6 @@ moe_ffn_kernel(const __grid_constant__ CUtensorMap tmW13, const __grid_constant_
   if (warp == 1) { tmem_alloc(tmem_slot, kFfnTmemCols); tmem_relinquish(); }
   __syncthreads();
   pdl_wait();
-  pdl_trigger();
   // Block table from the segment arrays: block seg_start / 32 + i belongs to the segment's expert.  The segments must tile
   // [0, 32 * blocks) without holes; anything else is reported and the launch does nothing.
   for (int g = threadIdx.x; g < a.num_groups; g += blockDim.x) {
@@ -365,6 +364,9 @@ moe_ffn_kernel(const __grid_constant__ CUtensorMap tmW13, const __grid_constant_
     }
   }
 
+  // The kernel behind this one may be scheduled now: released at the start, its CTAs would sit on the SMs for the whole
+  // 100 us of this kernel (measured: the decode step is 0.4 ms slower with the early release).
+  pdl_trigger();
   // Teardown.  After an abort, copies may still be landing in shared memory: give them a bounded grace period before the
   // CTA (and its shared memory) goes away.
   if (*abort_flag) {

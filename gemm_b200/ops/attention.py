@@ -42,78 +42,6 @@ def build_work(q_lens: Sequence[int], hq: int, hkv: int, num_splits: int = 1) ->
     return torch.tensor(items, dtype=torch.int32).reshape(-1, 4)
 
 
-# Decode work lists.  Default: one CTA per (sequence, KV head, split), the splits of an item merged inside the kernel by the CTA
-# that writes the last partial (no combine launch).  GB_DECODE_STREAMK=1 switches to the stream-K list (one equal piece of the KV
-# stream per resident CTA, pieces spanning items): it levels the SMs' loads (256 items on 296 CTA slots leave 40 SMs half idle) but
-# measured slower: 89 us against 75 us at 64 x 2048, 57 against 50 at 32 x 2048, 40 against 28 at 8 x 2048 (32 / 4 heads): a
-# fragment boundary drains the K / V ring, reloads Q and serialises the next block's softmax behind the fragment's epilogue and
-# merge, which costs more than the up to 13 % of balance it buys.
-DECODE_STREAMK = os.environ.get("GB_DECODE_STREAMK", "0") == "1"
-_item_ctr = {}
-
-
-def build_work_streamk(kv_lens: Sequence[int], hkv: int, n_cta: int = 296, max_frag: int = 4, block: int = 128):
-    """Stream-K work list of the decode kernel: the KV blocks of all (sequence, KV head) items, laid end to end, are cut into
-    ``n_cta`` equal pieces, one per CTA (296 = two per SM on 148 SMs, all resident at once); a piece that ends inside an item
-    continues with the next one, so a CTA holds up to ``max_frag`` fragments and an item is covered by one or more fragments whose
-    partial results the kernel merges.  Cuts are stored as fractions of the item's block count (1 / 65536), so they follow the
-    sequences as they grow.  Returns ``(work int32 [n_cta', max_frag, 4], max fragments per item)`` or ``None`` when the
-    pieces would need more than ``max_frag`` fragments (many short sequences: the classic list is the better fit)."""
-    items = [(s, h, max(1, (int(n) + block - 1) // block)) for s, n in enumerate(kv_lens) for h in range(hkv)]
-    total = sum(nb for _, _, nb in items)
-    if not items or total == 0:
-        return None
-    p = max(1, min(n_cta, total))
-    share = total / p
-    frags = [[] for _ in range(p)]
-    cta, room, worst = 0, share, 1
-    for s, h, nb in items:
-        cuts, pos, rem = [], 0.0, float(nb)
-        while rem > 1e-6:
-            take = min(rem, room)
-            cuts.append((min(cta, p - 1), pos, pos + take))
-            pos += take
-            rem -= take
-            room -= take
-            if room <= 1e-6:
-                cta, room = cta + 1, share
-        bounds = [0] + [int(round(65536.0 * hi / nb)) for _, _, hi in cuts]
-        bounds[-1] = 65536
-        if len(cuts) > 255:
-            return None
-        worst = max(worst, len(cuts))
-        for slot, (c, _, _) in enumerate(cuts):
-            frags[c].append([s, h | (slot << 8) | (len(cuts) << 16), bounds[slot], bounds[slot + 1]])
-    if max(len(f) for f in frags) > max_frag:
-        return None
-    work = torch.full((p, max_frag, 4), -1, dtype=torch.int32)
-    for c, fl in enumerate(frags):
-        for i, e in enumerate(fl):
-            work[c, i] = torch.tensor(e, dtype=torch.int32)
-    return work, worst
-
-
-def _decode_merged(q, k_cache, v_cache, out, out_q, out_sf, sf32, work, cu_q, kv_len, block_table, page_size, num_splits, window):
-    """The decode kernel with its partials merged in the kernel (stream-K or classic work list): no combine launch."""
-    t, hq, d = q.shape
-    hkv = k_cache.shape[1]
-    lib = _native.cuda()
-    n_items = int(cu_q.numel() - 1) * hkv
-    key = (q.device.index, torch.cuda.current_stream().cuda_stream)
-    ctr = _item_ctr.get(key)
-    if ctr is None or ctr.numel() < n_items:
-        # arrival counters of the merge, one per (sequence, KV head): zero between launches (the merging CTA resets its own)
-        ctr = _item_ctr[key] = torch.zeros(max(4096, n_items), dtype=torch.int32, device=q.device)
-    part_o = torch.empty(num_splits, t, hq, d, dtype=torch.float32, device=q.device)
-    part_lse = torch.empty(num_splits, t, hq, dtype=torch.float32, device=q.device)
-    streamk = work.dim() == 3
-    rc = lib.gb_flash_decode_merged(_p(q), _p(k_cache), _p(v_cache), _p(out), _p(out_q), _p(out_sf), _i(sf32), _p(part_o), _p(part_lse), _p(ctr),
-                                    _p(work), _i(work.shape[0]), _i(1 if streamk else 0), _p(cu_q), _p(kv_len), _p(block_table),
-                                    _i(block_table.shape[1]), _i(page_size), _l(k_cache.shape[0]), _i(t), _i(hq), _i(hkv), _i(d), _i(num_splits),
-                                    _i(window), _c(_native.status_ptr()), _c(torch.cuda.current_stream().cuda_stream))
-    _native.check(rc, "gb_flash_decode_merged")
-
-
 def pick_splits(n_seqs: int, hkv: int, max_kv: int, sm_count: int = 148, ctas_per_sm: int = 2) -> int:
     """Number of KV splits for decode: enough CTAs to fill the GPU (the decode kernel runs two CTAs per SM, and one CTA streams
     its KV range at a fraction of an SM's share of the memory bandwidth), at least 2 KV blocks per split."""
@@ -135,10 +63,6 @@ def attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_
     if out is None:
         out = torch.empty(t, hq, d, dtype=torch.bfloat16, device=q.device)
     lib = _native.cuda()
-    if decode and USE_DECODE_KERNEL and hq // hkv <= 16 and (work.dim() == 3 or (num_splits > 1 and scratch is None)):
-        # stream-K work list, or a classic split list: either way the partials are merged inside the kernel
-        _decode_merged(q, k_cache, v_cache, out, None, None, 0, work, cu_q, kv_len, block_table, page_size, num_splits, window)
-        return out
     part_o = part_lse = None
     if num_splits > 1:
         if scratch is not None:
@@ -226,9 +150,6 @@ def attention_decode_mx(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     rp = (t + 127) // 128 * 128
     oq = torch.empty(rp, hq * d, dtype=torch.uint8, device=q.device)
     sf = ew.sf_alloc(rp, hq * d, q.device, sf_layout, init=False)
-    if work.dim() == 3 or num_splits > 1:
-        _decode_merged(q, k_cache, v_cache, None, oq, sf, 1 if sf_layout == 32 else 0, work, cu_q, kv_len, block_table, page_size, num_splits, window)
-        return MxTensor(oq, sf, t, hq * d, sf_layout)
     if num_splits > 1:
         # split KV ranges: fp32 partials from the decode kernel, merged (and quantised) by the combine kernel
         lib, stream = _native.cuda(), _c(torch.cuda.current_stream().cuda_stream)

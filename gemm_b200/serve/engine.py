@@ -12,8 +12,12 @@ import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import ctypes
+import os
+
 import torch
 
+from .. import _native
 from ..utils import profiler
 
 from ..models.config import ModelConfig
@@ -55,6 +59,12 @@ class Engine:
                  max_prefill_tokens: int = 16384, num_pages: Optional[int] = None, kv_dtype: str = "bf16"):
         self.w = weights
         self.cfg: ModelConfig = weights.cfg
+        if weights.embed.is_cuda and "GB_PDL" not in os.environ:
+            # Programmatic dependent launch (every kernel starts its prologue under the tail of the one before): measured per model
+            # family on the decode step.  Dense stacks gain (Qwen3-8B, 2 GPUs: 7.67 against 7.95 ms); the MoE step, whose layer is
+            # two long persistent kernels and a few short ones, loses (Qwen3-30B-A3B: 11.56 against 11.14 ms on one GPU, 9.86
+            # against 9.47 on two).  GB_PDL=0 / 1 overrides.
+            _native.cuda().gb_set_pdl(ctypes.c_int(0 if self.cfg.is_moe else 1))
         self.device = weights.embed.device
         self.page_size = page_size
         self.max_batch = max_batch
@@ -163,19 +173,13 @@ class Engine:
                               for s in range(b)], dtype=torch.int32, device=self.device)
         max_kv = max(self.seq_len) + max_new_tokens + 1
         splits = att.pick_splits(b, self.hkv_local, max_kv) if self.device.type == "cuda" else 1
-        # decode attention as one equal piece of the KV stream per resident CTA (the cuts follow the sequences as they grow)
-        sk = att.build_work_streamk([n + 1 for n in self.seq_len], self.hkv_local) \
-            if (self.device.type == "cuda" and att.DECODE_STREAMK and not self.kv.quantized and self.hq_local // self.hkv_local <= 16) else None
         st = self._static
         st["ids"] = first_tokens.to(device=self.device, dtype=torch.int32).clone()
         st["positions"], st["slots"] = pos, slots
         st["kv_len"] = pos + 1
         st["block_table"] = bt
         st["cu_q"] = torch.arange(b + 1, dtype=torch.int32, device=self.device)
-        if sk is not None:
-            st["work"], splits = sk[0].to(self.device), sk[1]
-        else:
-            st["work"] = att.build_work([1] * b, self.hq_local, self.hkv_local, splits).to(self.device)
+        st["work"] = att.build_work([1] * b, self.hq_local, self.hkv_local, splits).to(self.device)
         st["rows"] = torch.arange(b, dtype=torch.int64, device=self.device)
         st["tokens"] = torch.zeros(b, dtype=torch.int32, device=self.device)
         st["seq_slots"] = torch.arange(b, dtype=torch.int32, device=self.device)
@@ -191,7 +195,6 @@ class Engine:
             saved = {k: st[k].clone() for k in ("ids", "positions", "slots", "kv_len", "step")}
             side = torch.cuda.Stream()
             side.wait_stream(torch.cuda.current_stream())
-            from .. import _native
             n0 = _native.launch_count()
             st["seq_slots"].fill_(self.max_batch)          # the warm-up run must not advance any sequence's recurrent state
             with torch.cuda.stream(side):

@@ -172,10 +172,6 @@ def _attn(args, b: int, q_len: int, ctx: int, name: str):
     if args.splits > 0:
         splits = args.splits
     work = att.build_work(q_lens, hq, hkv, splits).to("cuda")
-    if q_len == 1 and att.DECODE_STREAMK and args.splits == 0:
-        plan = att.build_work_streamk([ctx + 1] * b, hkv)          # opt-in: one equal piece of the KV stream per resident CTA
-        if plan is not None:
-            work, splits = plan[0].to("cuda"), plan[1]
 
     def run():
         att.attention(q, k, v, cu, kv_len, bt, page, work, num_splits=splits, causal=True, decode=(q_len == 1))

@@ -151,40 +151,3 @@ def test_prefill_kernel_mxfp8_output():
     assert _rel(mxfp8.dequantize(om), mxfp8.dequantize(want)) < 2e-2
     assert _rel(mxfp8.dequantize(om), out.reshape(t, hq * 128)) < 4e-2
 
-
-@pytest.mark.parametrize("hq,hkv,page,ctx,n_cta", [
-    (32, 4, 128, [2048] * 64, 296),                          # the benchmark's decode step: 256 items on 296 CTAs, 2-3 fragments per item
-    (32, 4, 128, [0, 5, 127, 128, 1000, 2047, 300], 296),    # uneven lengths, items shorter than a CTA's share
-    (8, 2, 16, [700, 90, 300, 4000], 24),                    # few CTAs: several items per CTA
-    (16, 1, 64, [5000], 40),                                 # one item cut into 40 fragments
-])
-def test_decode_kernel_stream_k(hq, hkv, page, ctx, n_cta):
-    """Stream-K work list: every CTA takes an equal piece of the concatenated KV blocks (a piece may span two or three items), the
-    CTA that writes an item's last partial merges them in the kernel.  Twice in a row: the merge counters must be back at zero."""
-    b = len(ctx)
-    q_lens = [1] * b
-    q, kc, vc, cu, kvl, bt = _setup(q_lens, ctx, hq, hkv, page, seed=9)
-    plan = att.build_work_streamk([c + 1 for c in ctx], hkv, n_cta=n_cta)
-    assert plan is not None
-    work, splits = plan
-    assert work.dim() == 3 and work.shape[0] <= n_cta
-    work = work.cuda()
-    ref = att.attention_ref(q, kc, vc, cu, kvl, bt, page)
-    for _ in range(2):
-        out = att.attention(q, kc, vc, cu, kvl, bt, page, work, num_splits=splits, decode=True)
-        torch.cuda.synchronize()
-        _native.assert_status_ok()
-        assert _rel(out, ref) < 1.5e-2
-    # the plan was made for other lengths than the ones the kernel sees (sequences grow between plans): still exact
-    kvl2 = (kvl + 3).clamp(max=int(kvl.max()))
-    out2 = att.attention(q, kc, vc, cu, kvl2, bt, page, work, num_splits=splits, decode=True)
-    ref2 = att.attention_ref(q, kc, vc, cu, kvl2, bt, page)
-    _native.assert_status_ok()
-    assert _rel(out2, ref2) < 1.5e-2
-    # MXFP8 output through the same path
-    if hq // hkv <= 16 and hq == 32:
-        from gemm_b200.ops import mxfp8
-        om = att.attention_decode_mx(q, kc, vc, cu, kvl, bt, page, work, sf_layout=32 if b <= 32 else 128, num_splits=splits)
-        _native.assert_status_ok()
-        assert _rel(mxfp8.dequantize(om), out.reshape(b, hq * 128)) < 4e-2
-
