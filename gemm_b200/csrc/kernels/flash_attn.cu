@@ -406,9 +406,14 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* t_full = bars + 1;                 // 3
   uint64_t* t_empty = bars + 4;                // 3
   uint64_t* s_full = bars + 7;                 // 2
-  uint64_t* p_ready = bars + 9;                // 1 (128 arrivals)
-  uint64_t* o_ready = bars + 10;               // 2: block j commits to o_ready[j & 1]
-  uint32_t* tmem_slot = (uint32_t*)(bars + 12);
+  // P of block j arrives at p_ready[j & 1] (128 arrivals).  Two barriers, not one: S(j + 1) is issued before the MMA thread waits
+  // for P(j), so the softmax threads can finish block j + 1 while that thread is still parked in its wait for block j; on a single
+  // barrier the phase would then flip twice, the parity the waiter looks for would never show, and the CTA would sit out its
+  // wait budget (seen as one 1.1 s step in about one run in ten; the wait site reported was the producer's, whose budget
+  // starts first).  With two barriers a second flip of the same one needs P(j + 2), which needs O(j), which needs this wait.
+  uint64_t* p_ready = bars + 9;                // 2
+  uint64_t* o_ready = bars + 11;               // 2: block j commits to o_ready[j & 1]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 13);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   float* red_max = (float*)(bars + 16);        // [2 (block parity)][4 warps][16 heads]
   float* red_sum = red_max + 2 * 4 * kFdN;     // [2][4][16]
@@ -418,7 +423,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(q_full, 1);
     for (int i = 0; i < 3; ++i) { mbar_init(&t_full[i], 1); mbar_init(&t_empty[i], 1); }
     for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
-    mbar_init(p_ready, 128); mbar_init(&o_ready[0], 1); mbar_init(&o_ready[1], 1);
+    mbar_init(&p_ready[0], 128); mbar_init(&p_ready[1], 128); mbar_init(&o_ready[0], 1); mbar_init(&o_ready[1], 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -503,7 +508,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int j = 0; j < n_blk && ok; ++j) {
         if (j + 1 < n_blk) { if (!issue_s(j + 1)) { ok = false; break; } }
         const int tv = 2 * j + 1, vslot = tv % 3;
-        if (!mbar_wait(p_ready, j & 1, abort_flag, a.status, 512, j)) { ok = false; break; }
+        if (!mbar_wait(&p_ready[j & 1], (uint32_t)(j >> 1) & 1, abort_flag, a.status, 512, j)) { ok = false; break; }
         if (!mbar_wait(&t_full[vslot], (uint32_t)(tv / 3) & 1, abort_flag, a.status, 513, j)) { ok = false; break; }
         tc_fence_after();
         const uint32_t v_addr = smem_u32(ring + vslot * 32768);
@@ -591,7 +596,7 @@ flash_decode_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           *reinterpret_cast<__nv_bfloat16*>(pb + half * 2048 + h * 128 + ((chunk ^ (h & 7)) << 4) + (r & 7) * 2) = __float2bfloat16(pv[h]);
         fence_proxy_async_smem();                // P in shared memory -> visible to the tensor core's reads
         tc_fence_before();
-        mbar_arrive(p_ready);
+        mbar_arrive(&p_ready[s]);
       }
       fail_o |= !got_o;
     }
