@@ -60,11 +60,12 @@ class Engine:
         self.w = weights
         self.cfg: ModelConfig = weights.cfg
         if weights.embed.is_cuda and "GB_PDL" not in os.environ:
-            # Programmatic dependent launch (every kernel starts its prologue under the tail of the one before): measured per model
-            # family on the decode step.  Dense stacks gain (Qwen3-8B, 2 GPUs: 7.67 against 7.95 ms); the MoE step, whose layer is
-            # two long persistent kernels and a few short ones, loses (Qwen3-30B-A3B: 11.56 against 11.14 ms on one GPU, 9.86
-            # against 9.47 on two).  GB_PDL=0 / 1 overrides.
-            _native.cuda().gb_set_pdl(ctypes.c_int(0 if self.cfg.is_moe else 1))
+            # Programmatic dependent launch (every kernel starts its prologue under the tail of the one before): chosen by what was
+            # measured on the decode step.  Dense stacks gain (Qwen3-8B, 2 GPUs: 7.67 against 7.95 ms).  The MoE step, whose layer is
+            # two long persistent kernels and a few short ones, loses on 1, 2 and 4 GPUs (Qwen3-30B-A3B: 11.56 against 11.14 ms,
+            # 9.86 against 9.47, 7.92 against 7.85) and gains on 8, where every kernel is short (7.41 against 7.62).
+            ep = getattr(par, "ep_size", 1) if par is not None else 1
+            _native.cuda().gb_set_pdl(ctypes.c_int(0 if (self.cfg.is_moe and ep <= 4) else 1))
         self.device = weights.embed.device
         self.page_size = page_size
         self.max_batch = max_batch
