@@ -733,9 +733,44 @@ __global__ void decode_advance_kernel(int* __restrict__ positions, int* __restri
   slots[b] = page * page_size + p % page_size;
 }
 
+// The same under context parallelism (the positions of a sequence are dealt to the ranks page by page: page g of a sequence lives on
+// rank g % world as that rank's page g / world): positions stay global, kv_len is the number of positions up to and including the new one
+// that THIS rank stores, the slot is -1 where another rank stores the new position (the rope kernel then skips the cache write).
+__global__ void decode_advance_cp_kernel(int* __restrict__ positions, int* __restrict__ kv_len, int* __restrict__ slots,
+                                         const int* __restrict__ block_table, int max_pages, int page_size, int n, int world, int rank,
+                                         unsigned long long* __restrict__ step_ctr) {
+  pdl_wait();
+  pdl_trigger();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b == 0 && step_ctr != nullptr) *step_ctr += 1;
+  if (b >= n) return;
+  const int p = positions[b] + 1;
+  positions[b] = p;
+  const int round = page_size * world;
+  const int rem = (p + 1) % round - rank * page_size;
+  kv_len[b] = (p + 1) / round * page_size + min(max(rem, 0), page_size);
+  const int g = p / page_size;
+  if (g % world != rank) {
+    slots[b] = -1;
+    return;
+  }
+  const int page = block_table[(size_t)b * max_pages + min(g / world, max_pages - 1)];
+  slots[b] = page * page_size + p % page_size;
+}
+
 }  // namespace gb
 
 using namespace gb;
+
+GB_API int gb_decode_advance_cp(int* positions, int* kv_len, int* slots, const int* block_table, int max_pages, int page_size, int n,
+                                int world, int rank, void* step_ctr, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (world < 1 || rank < 0 || rank >= world) return fail("decode_advance_cp: bad rank%s");
+  launch_k(decode_advance_cp_kernel, (n + 127) / 128, 128, 0, stream, positions, kv_len, slots, block_table, max_pages, page_size, n, world,
+           rank, (unsigned long long*)step_ctr);
+  GB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
 
 GB_API int gb_decode_advance(int* positions, int* kv_len, int* slots, const int* block_table, const int* live, int max_pages,
                              int page_size, int n, void* step_ctr, cudaStream_t stream) {

@@ -157,6 +157,8 @@ class ForwardBatch:
     # INT8 KV cache: where a step's new K / V rows sit in the bf16 staging buffer, and (prefill) the block table of the staged sequences
     stage_slots: Optional[torch.Tensor] = None # int32 [T]
     stage_bt: Optional[torch.Tensor] = None    # int32 [B, pages]
+    # context-parallel prefill: the cache slots whose K / V rows this rank contributes to the per-layer all-gather (staging order)
+    cp_send_slots: Optional[torch.Tensor] = None   # int64 [p_local * page_size]
 
     @staticmethod
     def build(q_lens: Sequence[int], ctx_lens: Sequence[int], ids, block_table: torch.Tensor, page_size: int, hq: int, hkv: int,
@@ -328,6 +330,8 @@ class Transformer:
         qkv = apply_linear(lw.wqkv, h, h_mx) if cfg.attn_output_gate else apply_linear_split(lw.wqkv, h, h_mx)
         if self.kv.quantized:
             return self._attention_q8(li, lw, qkv, fb)
+        if getattr(self.par, "cp_world", 1) > 1:
+            return self._attention_cp(li, lw, qkv, fb)
         q = ew.qk_norm_rope(qkv, fb.positions, fb.slots, lw.q_norm, lw.k_norm, self.kv.k[li], self.kv.v[li], self.hq_local,
                             self.hkv_local, cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
                             positions3=fb.positions3, sections=cfg.mrope_sections)
@@ -343,6 +347,27 @@ class Transformer:
             return self.par.row_linear(lw.wo, None, a_mx)
         a = att.attention(q, self.kv.k[li], self.kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, self.kv.page_size, fb.work,
                           num_splits=fb.num_splits, causal=True, window=cfg.sliding_window, decode=fb.is_decode)
+        a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
+        if cfg.attn_output_gate:
+            g0 = (self.hq_local + 2 * self.hkv_local) * cfg.head_dim
+            dn.gate_mul(a2, qkv[:, g0: g0 + self.hq_local * cfg.head_dim])
+        return self.par.row_linear(lw.wo, a2)
+
+    def _attention_cp(self, li: int, lw, qkv, fb: ForwardBatch) -> torch.Tensor:
+        """Attention under context parallelism (``parallel.context.ContextParallel`` as the parallel context).  The cache holds
+        this rank's pages only; ``fb.slots`` is -1 for a token another rank stores.  Decode: flash partials over the local shard,
+        merged across the ranks.  Prefill: the rank's own tokens attend over the all-gathered K / V rows of the prompt."""
+        cfg, kv = self.cfg, self.kv
+        q = ew.qk_norm_rope(qkv, fb.positions, fb.slots, lw.q_norm, lw.k_norm, kv.k[li], kv.v[li], self.hq_local, self.hkv_local,
+                            cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
+                            positions3=fb.positions3, sections=cfg.mrope_sections)
+        if fb.is_decode:
+            a = self.par.attention(q, kv.k[li], kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, kv.page_size, fb.work)
+        else:
+            if fb.cp_send_slots is None:
+                raise ValueError("a context-parallel prefill needs the forward batch of ContextParallel.build_prefill")
+            kg, vg = self.par.gather_kv(kv.k[li], kv.v[li], fb.cp_send_slots)
+            a = att.attention(q, kg, vg, fb.cu_q, fb.kv_len, fb.block_table, kv.page_size, fb.work, num_splits=1, causal=True)
         a2 = a.reshape(a.shape[0], self.hq_local * cfg.head_dim)
         if cfg.attn_output_gate:
             g0 = (self.hq_local + 2 * self.hkv_local) * cfg.head_dim

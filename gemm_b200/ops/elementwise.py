@@ -353,10 +353,29 @@ def softmax_scale_log2(d: int) -> float:
 
 
 def decode_advance(positions: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, page_size: int,
-                   live: Optional[torch.Tensor] = None, step_ctr: Optional[torch.Tensor] = None) -> None:
+                   live: Optional[torch.Tensor] = None, step_ctr: Optional[torch.Tensor] = None, cp_world: int = 1, cp_rank: int = 0) -> None:
     """In place: position += 1, kv_len = position + 1, slot from the block table (per decode sequence).  ``step_ctr`` (int64 [1]):
-    the step counter of the sampler, advanced by one (``ops.sampling.sample`` reads it on the device)."""
+    the step counter of the sampler, advanced by one (``ops.sampling.sample`` reads it on the device).  ``cp_world > 1`` (context
+    parallelism, page g of a sequence on rank g % world): positions stay global, ``kv_len`` counts the positions this rank stores,
+    ``block_table`` holds this rank's pages and the slot is -1 where another rank stores the new position."""
     n = positions.numel()
+    if cp_world > 1:
+        assert live is None
+        if not positions.is_cuda:
+            if step_ctr is not None:
+                step_ctr += 1
+            positions += 1
+            rnd = page_size * cp_world
+            rem = ((positions + 1) % rnd - cp_rank * page_size).clamp(0, page_size)
+            kv_len.copy_((positions + 1) // rnd * page_size + rem)
+            g = positions // page_size
+            pages = block_table[torch.arange(n), (g // cp_world).long().clamp_max(block_table.shape[1] - 1)]
+            slots.copy_(torch.where(g % cp_world == cp_rank, pages * page_size + positions % page_size, torch.full_like(slots, -1)))
+            return
+        _native.check(_native.cuda().gb_decode_advance_cp(_p(positions), _p(kv_len), _p(slots), _p(block_table), _i(block_table.shape[1]),
+                                                          _i(page_size), _i(n), _i(cp_world), _i(cp_rank), _p(step_ctr), _s()),
+                      "gb_decode_advance_cp")
+        return
     if not positions.is_cuda:
         if step_ctr is not None:
             step_ctr += 1

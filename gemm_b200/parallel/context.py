@@ -1,4 +1,4 @@
-"""Context parallelism for decode: the KV positions of every sequence are sharded block-cyclically over the ranks.
+"""Context parallelism: the KV positions of every sequence are sharded block-cyclically over the ranks.
 
 Rank r stores the K/V of the position blocks b with ``b % world == r`` (block = 128 positions) in its own paged cache; every
 rank holds the same queries, runs the flash kernel over its local shard only and gets partials (O normalised by its own
@@ -7,24 +7,36 @@ the split-KV decode, so all ranks end with identical outputs.  This is the refer
 (a64fx/m3/m3_ep_runner.c:121-140, common/glm5.h:285-298: all-reduce-MAX of the per-head maxima followed by an
 all-reduce-SUM of the rescaled [sumexp | out]); here the two all-reduces are one all-gather of ``Hq * (D + 1)`` floats per
 token and rank plus the merge kernel.  As in the reference, tensor-parallel attention is off under context parallelism.
+
+Given to ``Engine`` as its ``par`` (block = the engine's page size) the same object runs whole models: weights are replicated,
+page g of a sequence lives on rank ``g % world`` as that rank's page ``g // world``, so the cache of a rank holds 1 / world of
+every sequence.  A decode step runs the token-wise layers replicated and the attention as above.  A prefill is sequence
+parallel: every rank runs the layers over the tokens of its own pages only (1 / world of the GEMM work; pages are dealt round
+robin, so the causal attention work is balanced too), writes their K / V into its cache, and per layer the ranks all-gather the
+K / V rows of the prompt into a staging buffer that the flash kernel reads through a block table (one attention item per owned
+page: its 128 queries against the pages ``0 .. g``).  The reference has no prefill of its own under context parallelism (it
+feeds the prompt through the decode function token by token, common/m3_impl.h:643-683).
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
 
+from ..models.transformer import ForwardBatch, SingleProcess
 from ..ops import attention as att
 from .fabric import Fabric
 
 
-class ContextParallel:
+class ContextParallel(SingleProcess):
     def __init__(self, group, device: torch.device, block: int = 128, fused: bool = True, max_tokens: int = 256, hq: int = 32,
                  head_dim: int = 128):
         self.group, self.device, self.block = group, device, block
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
+        self.cp_world, self.cp_rank = self.world, self.rank
+        self._stage = {}
         self.fused = fused and device.type == "cuda"
         self.max_tokens, self.hq, self.d = max_tokens, hq, head_dim
         self.fab: Optional[Fabric] = None
@@ -46,6 +58,11 @@ class ContextParallel:
         r = self.rank if rank is None else rank
         full, rem = divmod(kv_len, self.block * self.world)
         return full * self.block + min(max(rem - r * self.block, 0), self.block)
+
+    def local_pages(self, n_pages: int, rank: Optional[int] = None) -> int:
+        """How many of the pages ``[0, n_pages)`` of a sequence the rank stores."""
+        r = self.rank if rank is None else rank
+        return (n_pages - r + self.world - 1) // self.world if n_pages > r else 0
 
     def shard_positions(self, kv_len: int, rank: Optional[int] = None) -> Sequence[int]:
         r = self.rank if rank is None else rank
@@ -72,6 +89,83 @@ class ContextParallel:
         part_lse = allp[:, :, hq * d:].reshape(self.world, t * hq).contiguous()
         out, _ = att.combine_partials(part_o, part_lse)
         return out.reshape(t, hq, d)
+
+    # ------------------------------------------------------------------------------------------ whole-model prefill
+    def build_prefill(self, prompts: Sequence[torch.Tensor], local_pages: Sequence[Sequence[int]], hq: int, hkv: int, device,
+                      seq_slots: Optional[Sequence[int]] = None) -> Tuple[ForwardBatch, List[int]]:
+        """The forward batch of THIS rank for a prefill of whole prompts (every sequence from position 0), and the sequences
+        whose last token the rank holds (their logits are the first ``len(owned)`` rows of the forward's output).
+        ``local_pages[s]``: the rank's cache pages of sequence ``s`` in order (its page ``i`` is the sequence's page
+        ``rank + i * world``).  Attention items are the rank's pages; their block tables address the gathered staging buffer,
+        where rank q's region (``p_local`` pages) holds its pages of sequence 0, then of sequence 1, and so on."""
+        page, w, r = self.block, self.world, self.rank
+        b = len(prompts)
+        lens = [int(p.numel()) for p in prompts]
+        gp = [(n + page - 1) // page for n in lens]
+        first = [[0] * (b + 1) for _ in range(w)]
+        for q in range(w):
+            for s in range(b):
+                first[q][s + 1] = first[q][s] + self.local_pages(gp[s], q)
+        p_local = max(max(first[q][b] for q in range(w)), 1)
+        ids, pos, slots, cu, kvl, tables, rows, owned = [], [], [], [0], [], [], [], []
+        send = [0] * (p_local * page)
+        for s in range(b):
+            for g in range(r, gp[s], w):
+                lo, hi = g * page, min((g + 1) * page, lens[s])
+                cache_page = int(local_pages[s][g // w])
+                ids.append(prompts[s][lo:hi].to(torch.int32).cpu())
+                pos.extend(range(lo, hi))
+                slots.extend(cache_page * page + i for i in range(hi - lo))
+                st = (first[r][s] + g // w) * page
+                send[st: st + hi - lo] = [cache_page * page + i for i in range(hi - lo)]
+                cu.append(cu[-1] + hi - lo)
+                kvl.append(hi)
+                tables.append([(g2 % w) * p_local + first[g2 % w][s] + g2 // w for g2 in range(g + 1)])
+                if hi == lens[s]:
+                    rows.append(cu[-1] - 1)
+                    owned.append(s)
+        if not pos:
+            # a rank without a page of any prompt still joins every layer's collectives: it runs one token that stores nothing
+            ids, pos, slots, cu, kvl, tables = [torch.zeros(1, dtype=torch.int32)], [0], [-1], [0, 1], [1], [[0]]
+        if not rows:
+            rows = [0]
+        i32 = dict(dtype=torch.int32, device=device)
+        q_lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
+        bt = torch.zeros(len(tables), max(len(t) for t in tables), dtype=torch.int32)
+        for i, t in enumerate(tables):
+            bt[i, : len(t)] = torch.tensor(t, dtype=torch.int32)
+        fb = ForwardBatch(ids=torch.cat(ids).to(device), positions=torch.tensor(pos, **i32), slots=torch.tensor(slots, **i32),
+                          cu_q=torch.tensor(cu, **i32), kv_len=torch.tensor(kvl, **i32), block_table=bt.to(device),
+                          work=att.build_work(q_lens, hq, hkv, 1).to(device), logit_rows=torch.tensor(rows, dtype=torch.int64, device=device),
+                          num_splits=1, n_tokens=len(pos),
+                          seq_slots=torch.tensor(list(seq_slots) if seq_slots is not None else list(range(b)), **i32), is_decode=False)
+        fb.cp_send_slots = torch.tensor(send, dtype=torch.int64, device=device)
+        return fb, owned
+
+    def gather_kv(self, k_cache: torch.Tensor, v_cache: torch.Tensor, send_slots: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """All-gather of the prompt's K / V rows of one layer: every rank contributes the rows of ``send_slots`` of its cache
+        (the staging order of ``build_prefill``); returns ``[world * len(send_slots), Hkv, D]`` caches for the flash kernel.
+        The staging buffers are kept and reused by the next layer."""
+        n = send_slots.numel()
+        key = (n, k_cache.shape[1], k_cache.shape[2], k_cache.dtype, k_cache.device)
+        if key not in self._stage:
+            self._stage.clear()
+            self._stage[key] = tuple(torch.empty(self.world * n, k_cache.shape[1], k_cache.shape[2], dtype=k_cache.dtype, device=k_cache.device)
+                                     for _ in range(2))
+        kg, vg = self._stage[key]
+        for full, cache in ((kg, k_cache), (vg, v_cache)):
+            mine = full[self.rank * n: (self.rank + 1) * n]
+            torch.index_select(cache, 0, send_slots, out=mine)
+            dist.all_gather([full[q * n: (q + 1) * n] for q in range(self.world)], mine, group=self.group)
+        return kg, vg
+
+    def merge_logits(self, logits: torch.Tensor, owned: Sequence[int], n_seqs: int) -> torch.Tensor:
+        """Every rank's last-token logits (rows of the sequences it ``owned``) put together: ``f32 [n_seqs, V]`` on all ranks."""
+        full = torch.zeros(n_seqs, logits.shape[1], dtype=torch.float32, device=logits.device)
+        if owned:
+            full[torch.tensor(list(owned), dtype=torch.int64, device=logits.device)] = logits[: len(owned)].float()
+        dist.all_reduce(full, group=self.group)
+        return full
 
     def close(self) -> None:
         if self.fab is not None:

@@ -70,6 +70,14 @@ class Engine:
         self.page_size = page_size
         self.max_batch = max_batch
         self.max_pages_per_seq = (max_seq_len + page_size - 1) // page_size
+        # context parallelism (parallel.context.ContextParallel as ``par``): this rank's cache holds every world-th page of a sequence
+        self.cp = par if getattr(par, "cp_world", 1) > 1 else None
+        if self.cp is not None:
+            if self.cp.block != page_size:
+                raise ValueError("context parallelism deals the positions out by pages: ContextParallel(block=...) must equal page_size")
+            if kv_dtype != "bf16" or self.cfg.sliding_window or any(l.ssm is not None for l in weights.layers) or weights.tp_size > 1:
+                raise NotImplementedError("context parallelism: bf16 KV cache, full attention in every layer, replicated weights")
+            self.max_pages_per_seq = (self.max_pages_per_seq + self.cp.world - 1) // self.cp.world
         n_pages = num_pages if num_pages is not None else max_batch * self.max_pages_per_seq
         hkv_local = max(1, self.cfg.n_kv_heads // weights.tp_size)
         # one recurrent-state slot per sequence plus a scratch slot (hybrid models; used by the warm-up run before graph capture)
@@ -100,6 +108,8 @@ class Engine:
 
     def _ensure_pages(self, s: int, length: int) -> None:
         need = (length + self.page_size - 1) // self.page_size
+        if self.cp is not None:
+            need = self.cp.local_pages(need)
         have = len(self.seq_pages[s])
         if need > have:
             self.seq_pages[s].extend(self.pages.alloc(need - have))
@@ -125,6 +135,17 @@ class Engine:
             self.seq_len.append(0)
             self._ensure_pages(len(self.seq_pages) - 1, pr.numel() + reserve)
         b = len(prompts)
+        if self.cp is not None:
+            # sequence-parallel prefill of whole prompts: this rank runs the tokens of its own pages
+            fb, owned = self.cp.build_prefill(prompts, self.seq_pages[base:], self.hq_local, self.hkv_local, self.device,
+                                              seq_slots=range(base, base + b))
+            if fb.n_tokens > self.max_prefill_tokens:
+                raise ValueError(f"context-parallel prefill: {fb.n_tokens} tokens on this rank exceed max_prefill_tokens")
+            with profiler.region("prefill_chunk", "step", "engine"):
+                logits = self.model.forward(fb)
+            for i in range(b):
+                self.seq_len[base + i] = prompts[i].numel()
+            return self.cp.merge_logits(logits, owned, b)
         done = [0] * b
         last_logits: List[Optional[torch.Tensor]] = [None] * b
         budget = self.max_prefill_tokens
@@ -170,14 +191,22 @@ class Engine:
             self._ensure_pages(s, self.seq_len[s] + max_new_tokens + 1)
         bt = self._block_table(range(b)).to(self.device)
         pos = torch.tensor(self.seq_len, dtype=torch.int32, device=self.device)
-        slots = torch.tensor([self.seq_pages[s][self.seq_len[s] // self.page_size] * self.page_size + self.seq_len[s] % self.page_size
-                              for s in range(b)], dtype=torch.int32, device=self.device)
+        slots = None if self.cp is not None else torch.tensor(
+            [self.seq_pages[s][self.seq_len[s] // self.page_size] * self.page_size + self.seq_len[s] % self.page_size for s in range(b)],
+            dtype=torch.int32, device=self.device)
         max_kv = max(self.seq_len) + max_new_tokens + 1
         splits = att.pick_splits(b, self.hkv_local, max_kv) if self.device.type == "cuda" else 1
+        kv_len = pos + 1
+        if self.cp is not None:
+            cp, ps = self.cp, self.page_size
+            splits = 1
+            kv_len = torch.tensor([cp.local_len(n + 1) for n in self.seq_len], dtype=torch.int32, device=self.device)
+            slots = torch.tensor([self.seq_pages[s][n // ps // cp.world] * ps + n % ps if cp.owner(n) == cp.rank else -1
+                                  for s, n in enumerate(self.seq_len)], dtype=torch.int32, device=self.device)
         st = self._static
         st["ids"] = first_tokens.to(device=self.device, dtype=torch.int32).clone()
         st["positions"], st["slots"] = pos, slots
-        st["kv_len"] = pos + 1
+        st["kv_len"] = kv_len
         st["block_table"] = bt
         st["cu_q"] = torch.arange(b + 1, dtype=torch.int32, device=self.device)
         st["work"] = att.build_work([1] * b, self.hq_local, self.hkv_local, splits).to(self.device)
@@ -225,7 +254,8 @@ class Engine:
             tok = self._sample(logits, self._sp, 0, st["step"])
         st["tokens"].copy_(tok)
         st["ids"].copy_(tok)
-        ew.decode_advance(st["positions"], st["kv_len"], st["slots"], st["block_table"], self.page_size, step_ctr=st["step"])
+        ew.decode_advance(st["positions"], st["kv_len"], st["slots"], st["block_table"], self.page_size, step_ctr=st["step"],
+                          cp_world=self.cp.world if self.cp is not None else 1, cp_rank=self.cp.rank if self.cp is not None else 0)
 
     @torch.no_grad()
     def decode_step(self) -> torch.Tensor:

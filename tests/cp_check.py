@@ -54,3 +54,46 @@ def check_context_parallel(rank, world, dev, fused):
     assert all(torch.equal(gathered[0], g) for g in gathered), "ranks disagree after the context-parallel merge"
     dist.barrier()
     cp.close()
+
+
+def check_cp_engine(rank, world, dev, fused, name="tiny-dense", fmt="bf16", page=16, prompt_lens=(70, 33, 5, 129), new_tokens=6):
+    """Whole-model generation under context parallelism (sequence-parallel prefill, sharded KV cache, merged decode attention)
+    against the unsharded engine: prefill logits, decode logits step by step (both engines are fed the reference's tokens)."""
+    from gemm_b200.models.config import get_config
+    from gemm_b200.models.weights import synthetic_weights
+    from gemm_b200.serve.engine import Engine, SamplingParams
+    cfg = get_config(name)
+    device = torch.device(dev)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g, dtype=torch.int32) for n in prompt_lens]
+    b, max_len = len(prompts), max(prompt_lens) + new_tokens + 2
+    w = synthetic_weights(cfg, fmt, device, 5)
+    ref = Engine(w, max_batch=b, max_seq_len=max_len, page_size=page)
+    cp = ContextParallel(dist.group.WORLD, device, block=page, fused=fused, max_tokens=b, hq=cfg.n_heads, head_dim=cfg.head_dim)
+    eng = Engine(w, max_batch=b, max_seq_len=max_len, page_size=page, par=cp)
+    assert eng.kv.k[0].shape[0] < ref.kv.k[0].shape[0] or world == 1, "the context-parallel cache is not smaller than the full one"
+    rel = lambda a, c: ((a.float() - c.float()).norm() / (c.float().norm() + 1e-12)).item()
+    lr = ref.prefill(prompts, reserve=new_tokens + 1)
+    lc = eng.prefill(prompts, reserve=new_tokens + 1)
+    per_seq = [round(rel(lc[i], lr[i]), 4) for i in range(b)]
+    if rank == 0:
+        print(f"cp engine {name} {fmt} world {world}: prefill logits rel per sequence {per_seq}", flush=True)
+    tol = 2e-2 if dev == "cpu" else 4e-2              # bf16 kernels with other tile shapes per rank: the tolerance of the EP / TP checks
+    assert lc.shape == lr.shape and max(per_seq) < tol, f"context-parallel prefill logits differ: rel per sequence {per_seq}"
+    first = lr.argmax(-1).to(torch.int32)
+    sp = SamplingParams(temperature=0.0)
+    ref.begin_decode(first, sp, new_tokens, use_graph=False)
+    eng.begin_decode(first, sp, new_tokens, use_graph=(dev != "cpu"))
+    agree = 0
+    for _ in range(new_tokens):
+        tr = ref.decode_step().clone()
+        tc = eng.decode_step().clone()
+        agree += int((tr == tc).sum())
+        eng.set_next_tokens(tr)                       # keep both engines on the reference's tokens (near ties may flip an arg-max)
+    assert agree >= new_tokens * b - 2, f"context-parallel decode: {agree} of {new_tokens * b} tokens agree"
+    # the decode steps wrote their K / V rows on the owners only: a last step through the logits path must still agree
+    gathered = [torch.empty_like(tc) for _ in range(world)]
+    dist.all_gather(gathered, tc.contiguous())
+    assert all(torch.equal(gathered[0], x) for x in gathered), "ranks disagree on the decoded tokens"
+    dist.barrier()
+    cp.close()

@@ -49,8 +49,11 @@ def main():
     g = torch.Generator().manual_seed(3)
     if what == "cp":
         sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-        from cp_check import check_context_parallel
+        from cp_check import check_context_parallel, check_cp_engine
         check_context_parallel(rank, world, "cpu", False)
+        check_cp_engine(rank, world, "cpu", False)
+        check_cp_engine(rank, world, "cpu", False, name="tiny-moe", prompt_lens=(40, 7))
+        check_cp_engine(rank, world, "cpu", False, prompt_lens=(10, 7), new_tokens=12)     # ranks without a page of any prompt
     if what == "groups":
         lay = ParallelLayout(tp=2, pp=2, dp=world // 4)
         grp = init_parallel(lay)
