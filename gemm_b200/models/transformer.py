@@ -362,7 +362,8 @@ class Transformer:
                             cfg.head_dim, cfg.rope_theta, cfg.rms_eps, self.q_scale, self.rope_dim, table=self.rope_table,
                             positions3=fb.positions3, sections=cfg.mrope_sections)
         if fb.is_decode:
-            a = self.par.attention(q, kv.k[li], kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, kv.page_size, fb.work)
+            a = self.par.attention(q, kv.k[li], kv.v[li], fb.cu_q, fb.kv_len, fb.block_table, kv.page_size, fb.work,
+                                   num_splits=fb.num_splits, decode=True)
         else:
             if fb.cp_send_slots is None:
                 raise ValueError("a context-parallel prefill needs the forward batch of ContextParallel.build_prefill")

@@ -200,15 +200,27 @@ def can_decode_mx(q: torch.Tensor, hkv: int, num_splits: int, decode: bool) -> b
 
 def attention_partial(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, kv_len: torch.Tensor,
                       block_table: torch.Tensor, page_size: int, work: torch.Tensor, num_splits: int = 1, causal: bool = False,
-                      window: int = 0):
+                      window: int = 0, decode: bool = False):
     """Flash partials of the attention over THIS cache only: ``(part_o f32 [S, T, Hq, D]`` normalised by its own sum,
     ``part_lse f32 [S, T, Hq]`` base 2; -inf where a row saw no key).  The caller merges them with partials of other KV
-    shards (``combine_partials``): the building block of context parallelism."""
+    shards (``combine_partials``): the building block of context parallelism.  ``decode`` (one query per sequence, which sees
+    every cached key) selects the decode-specialised kernel, whose ``num_splits`` KV ranges are partials of their own."""
     t, hq, d = q.shape
     if not q.is_cuda:
-        return _attention_partial_ref(q, k_cache, v_cache, cu_q, kv_len, block_table, page_size, causal, window)
+        o, l = _attention_partial_ref(q, k_cache, v_cache, cu_q, kv_len, block_table, page_size, causal, window)
+        if num_splits > 1:         # the reference computes one partial; the other splits saw no key
+            o = torch.cat([o, torch.zeros(num_splits - 1, *o.shape[1:])])
+            l = torch.cat([l, torch.full((num_splits - 1, *l.shape[1:]), float("-inf"))])
+        return o, l
     part_o = torch.empty(num_splits, t, hq, d, dtype=torch.float32, device=q.device)
     part_lse = torch.empty(num_splits, t, hq, dtype=torch.float32, device=q.device)
+    if decode and USE_DECODE_KERNEL and hq // k_cache.shape[1] <= 16:
+        rc = _native.cuda().gb_flash_decode(_p(q), _p(k_cache), _p(v_cache), _c(0), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
+                                            _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
+                                            _l(k_cache.shape[0]), _i(t), _i(hq), _i(k_cache.shape[1]), _i(d), _i(num_splits), _i(window),
+                                            _c(_native.status_ptr()), _c(torch.cuda.current_stream().cuda_stream))
+        _native.check(rc, "gb_flash_decode")
+        return part_o, part_lse
     rc = _native.cuda().gb_flash_attn(_p(q), _p(k_cache), _p(v_cache), _c(0), _p(part_o), _p(part_lse), _p(work), _i(work.shape[0]),
                                       _p(cu_q), _p(kv_len), _p(block_table), _i(block_table.shape[1]), _i(page_size),
                                       _l(k_cache.shape[0]), _i(t), _i(hq), _i(k_cache.shape[1]), _i(d), _i(num_splits), _i(1 if causal else 0),

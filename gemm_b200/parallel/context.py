@@ -31,17 +31,17 @@ from .fabric import Fabric
 
 class ContextParallel(SingleProcess):
     def __init__(self, group, device: torch.device, block: int = 128, fused: bool = True, max_tokens: int = 256, hq: int = 32,
-                 head_dim: int = 128):
+                 head_dim: int = 128, max_splits: int = 1):
         self.group, self.device, self.block = group, device, block
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.cp_world, self.cp_rank = self.world, self.rank
         self._stage = {}
         self.fused = fused and device.type == "cuda"
-        self.max_tokens, self.hq, self.d = max_tokens, hq, head_dim
+        self.max_tokens, self.hq, self.d, self.max_splits = max_tokens, hq, head_dim, max_splits
         self.fab: Optional[Fabric] = None
         if self.fused:
-            per = max_tokens * hq * (head_dim + 1) * 4
+            per = max_splits * max_tokens * hq * (head_dim + 1) * 4
             self.fab = Fabric(group, device, self.world * per + (1 << 20))
             self.ag = self.fab.make_exchange(per, chunks=8)
 
@@ -70,23 +70,28 @@ class ContextParallel(SingleProcess):
 
     # ------------------------------------------------------------------------------------------ attention
     def attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cu_q: torch.Tensor, local_kv_len: torch.Tensor,
-                  block_table: torch.Tensor, page_size: int, work: torch.Tensor) -> torch.Tensor:
+                  block_table: torch.Tensor, page_size: int, work: torch.Tensor, num_splits: int = 1, decode: bool = False) -> torch.Tensor:
         """``q`` bf16 [T, Hq, D] (the same on every rank, pre-scaled as the flash kernel expects; one decode token per sequence);
-        caches, ``local_kv_len`` and ``block_table`` describe THIS rank's shard.  Returns bf16 [T, Hq, D], identical on all ranks."""
+        caches, ``local_kv_len`` and ``block_table`` describe THIS rank's shard.  ``num_splits`` (<= ``max_splits``; ``work`` built
+        for it): the rank's shard is cut into that many KV ranges, each a partial of its own in the merge.  ``decode`` selects the
+        decode-specialised kernel.  Returns bf16 [T, Hq, D], identical on all ranks."""
         t, hq, d = q.shape
-        po, pl = att.attention_partial(q, k_cache, v_cache, cu_q, local_kv_len, block_table, page_size, work, causal=False)
-        mine = torch.cat([po[0].reshape(t, hq * d), pl[0].reshape(t, hq)], dim=1).contiguous()      # [T, Hq * (D + 1)] f32
+        ns = num_splits
+        po, pl = att.attention_partial(q, k_cache, v_cache, cu_q, local_kv_len, block_table, page_size, work, num_splits=ns, causal=False,
+                                       decode=decode)
+        mine = torch.cat([po.reshape(ns * t, hq * d), pl.reshape(ns * t, hq)], dim=1).contiguous()      # [S * T, Hq * (D + 1)] f32
         if self.fused:
-            assert t <= self.max_tokens and hq == self.hq and d == self.d
-            buf = torch.zeros(self.max_tokens, hq * (d + 1), dtype=torch.float32, device=q.device)
-            buf[:t] = mine
-            allp = self.ag.all_gather(buf).view(torch.float32).view(self.world, self.max_tokens, hq * (d + 1))[:, :t]
+            assert t <= self.max_tokens and ns <= self.max_splits and hq == self.hq and d == self.d
+            rows = self.max_splits * self.max_tokens
+            buf = torch.zeros(rows, hq * (d + 1), dtype=torch.float32, device=q.device)
+            buf[: ns * t] = mine
+            allp = self.ag.all_gather(buf).view(torch.float32).view(self.world, rows, hq * (d + 1))[:, : ns * t]
         else:
             parts = [torch.empty_like(mine) for _ in range(self.world)]
             dist.all_gather(parts, mine, group=self.group)
             allp = torch.stack(parts)
-        part_o = allp[:, :, : hq * d].reshape(self.world, t * hq, d).contiguous()
-        part_lse = allp[:, :, hq * d:].reshape(self.world, t * hq).contiguous()
+        part_o = allp[:, :, : hq * d].reshape(self.world * ns, t * hq, d).contiguous()
+        part_lse = allp[:, :, hq * d:].reshape(self.world * ns, t * hq).contiguous()
         out, _ = att.combine_partials(part_o, part_lse)
         return out.reshape(t, hq, d)
 

@@ -137,15 +137,27 @@ class Engine:
         b = len(prompts)
         if self.cp is not None:
             # sequence-parallel prefill of whole prompts: this rank runs the tokens of its own pages
-            fb, owned = self.cp.build_prefill(prompts, self.seq_pages[base:], self.hq_local, self.hkv_local, self.device,
-                                              seq_slots=range(base, base + b))
-            if fb.n_tokens > self.max_prefill_tokens:
-                raise ValueError(f"context-parallel prefill: {fb.n_tokens} tokens on this rank exceed max_prefill_tokens")
-            with profiler.region("prefill_chunk", "step", "engine"):
-                logits = self.model.forward(fb)
+            # (whole sequences per forward pass, as many as keep every rank within max_prefill_tokens: the same groups on all ranks)
+            cp, ps = self.cp, self.page_size
+            share = [max(min(cp.local_pages((p.numel() + ps - 1) // ps, r) * ps, p.numel()) for r in range(cp.world)) for p in prompts]
+            if max(share) > self.max_prefill_tokens:
+                raise ValueError(f"context-parallel prefill: a prompt puts {max(share)} tokens on one rank, max_prefill_tokens is "
+                                 f"{self.max_prefill_tokens}")
+            i0, parts = 0, []
+            while i0 < b:
+                i1, room = i0, self.max_prefill_tokens
+                while i1 < b and share[i1] <= room:
+                    room -= share[i1]
+                    i1 += 1
+                fb, owned = cp.build_prefill(prompts[i0:i1], self.seq_pages[base + i0: base + i1], self.hq_local, self.hkv_local, self.device,
+                                             seq_slots=range(base + i0, base + i1))
+                with profiler.region("prefill_chunk", "step", "engine"):
+                    logits = self.model.forward(fb)
+                parts.append(cp.merge_logits(logits, owned, i1 - i0))
+                i0 = i1
             for i in range(b):
                 self.seq_len[base + i] = prompts[i].numel()
-            return self.cp.merge_logits(logits, owned, b)
+            return torch.cat(parts)
         done = [0] * b
         last_logits: List[Optional[torch.Tensor]] = [None] * b
         budget = self.max_prefill_tokens
@@ -199,7 +211,8 @@ class Engine:
         kv_len = pos + 1
         if self.cp is not None:
             cp, ps = self.cp, self.page_size
-            splits = 1
+            # KV ranges per rank: by the rank's share of the longest sequence, the same on every rank (the merge gathers them all)
+            splits = min(att.pick_splits(b, self.hkv_local, (max_kv + cp.world - 1) // cp.world), cp.max_splits) if self.device.type == "cuda" else 1
             kv_len = torch.tensor([cp.local_len(n + 1) for n in self.seq_len], dtype=torch.int32, device=self.device)
             slots = torch.tensor([self.seq_pages[s][n // ps // cp.world] * ps + n % ps if cp.owner(n) == cp.rank else -1
                                   for s, n in enumerate(self.seq_len)], dtype=torch.int32, device=self.device)

@@ -69,7 +69,7 @@ def check_cp_engine(rank, world, dev, fused, name="tiny-dense", fmt="bf16", page
     b, max_len = len(prompts), max(prompt_lens) + new_tokens + 2
     w = synthetic_weights(cfg, fmt, device, 5)
     ref = Engine(w, max_batch=b, max_seq_len=max_len, page_size=page)
-    cp = ContextParallel(dist.group.WORLD, device, block=page, fused=fused, max_tokens=b, hq=cfg.n_heads, head_dim=cfg.head_dim)
+    cp = ContextParallel(dist.group.WORLD, device, block=page, fused=fused, max_tokens=b, hq=cfg.n_heads, head_dim=cfg.head_dim, max_splits=4)
     eng = Engine(w, max_batch=b, max_seq_len=max_len, page_size=page, par=cp)
     assert eng.kv.k[0].shape[0] < ref.kv.k[0].shape[0] or world == 1, "the context-parallel cache is not smaller than the full one"
     rel = lambda a, c: ((a.float() - c.float()).norm() / (c.float().norm() + 1e-12)).item()

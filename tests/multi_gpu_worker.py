@@ -288,7 +288,7 @@ def main():
         from cp_check import check_context_parallel, check_cp_engine
         for fused in (True, False):
             check_context_parallel(rank, world, dev, fused)
-        check_cp_engine(rank, world, dev, True, page=128, prompt_lens=(300, 130, 40, 513))
+        check_cp_engine(rank, world, dev, True, page=128, prompt_lens=(300, 130, 40, 1800))       # the long one: 3 KV ranges per rank
         check_cp_engine(rank, world, dev, True, name="tiny-moe", fmt="mxfp8", page=128, prompt_lens=(257, 700))
     if what in ("all", "tp"):
         for fmt, fused in (("bf16", True), ("mxfp8", True), ("bf16", False), ("q4_k", True), ("q8_0", True)):
