@@ -11,6 +11,7 @@ Reference semantics: common/transformer.h:2861-3113 and :3857-3935.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -58,6 +59,23 @@ def conv_silu(x: torch.Tensor, w: torch.Tensor, state: torch.Tensor, cu_q: torch
     return out
 
 
+# The chunked prefill scan (GB_DELTANET_CHUNKED=0 keeps the per-token kernel): taken when the launch averages at least this many
+# tokens per sequence (a decode step, one token per sequence, always takes the per-token kernel)
+CHUNKED = os.environ.get("GB_DELTANET_CHUNKED", "1") != "0"
+CHUNKED_MIN_TOKENS = 48
+_ws_cache = {}
+
+
+def _chunk_workspace(device, nbytes: int) -> torch.Tensor:
+    """Scratch of the chunked scan, kept per device and grown on demand (every layer of a forward pass reuses it: the launches
+    are ordered on the stream)."""
+    cur = _ws_cache.get(device)
+    if cur is None or cur.numel() < nbytes:
+        cur = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _ws_cache[device] = cur
+    return cur
+
+
 def deltanet_ref(qkv, z, ab, a, dt_bias, norm_w, state, cu_q, seq_slots, n_group, dt_rank, d_state, eps):
     t = qkv.shape[0]
     ds = d_state
@@ -103,6 +121,18 @@ def deltanet(qkv: torch.Tensor, z: torch.Tensor, ab: torch.Tensor, a: torch.Tens
         return deltanet_ref(qkv, z, ab, a, dt_bias, norm_w, state, cu_q, seq_slots, n_group, dt_rank, d_state, eps)
     out = torch.empty(t, dt_rank * d_state, dtype=torch.bfloat16, device=qkv.device)
     assert ab.is_contiguous() and ab.dtype == torch.float32 and state.dtype == torch.float32
+    n_seqs = cu_q.numel() - 1
+    if CHUNKED and d_state == 128 and t >= CHUNKED_MIN_TOKENS * n_seqs:
+        # prefill: the chunked scan (64 tokens per step of the serial chain, the chunk-local part parallel over all chunks)
+        lib = _native.cuda()
+        lib.gb_deltanet_chunk_workspace.restype = ctypes.c_long
+        need = int(lib.gb_deltanet_chunk_workspace(_l(t), _i(n_seqs), _i(dt_rank)))
+        ws = _chunk_workspace(qkv.device, need)
+        rc = lib.gb_deltanet_chunked(_p(qkv), _i(qkv.stride(0)), _p(z), _i(z.stride(0)), _p(ab), _p(a), _p(dt_bias), _p(norm_w), _p(state),
+                                     _p(cu_q), _p(seq_slots), _p(out), _i(n_group), _i(dt_rank), _i(d_state), _f(eps), _i(n_seqs), _l(t),
+                                     _p(ws), _l(ws.numel()), _s())
+        _native.check(rc, "gb_deltanet_chunked")
+        return out
     rc = _native.cuda().gb_deltanet(_p(qkv), _i(qkv.stride(0)), _p(z), _i(z.stride(0)), _p(ab), _p(a), _p(dt_bias), _p(norm_w), _p(state),
                                     _p(cu_q), _p(seq_slots), _p(out), _i(n_group), _i(dt_rank), _i(d_state), _f(eps), _i(cu_q.numel() - 1), _s())
     _native.check(rc, "gb_deltanet")

@@ -52,6 +52,44 @@ def test_deltanet_recurrence(ds, ng, hv):
     assert _rel(st_gpu, st_ref) < 1e-4
 
 
+@pytest.mark.parametrize("lens", [[150, 64, 70, 200], [1000], [63, 65, 128, 129, 48]])
+def test_deltanet_chunked_scan(lens):
+    """Prefill-sized launches take the chunked scan (64 tokens per serial step, bf16 tiles, fp32 state): against the per-token
+    fp32 reference and against the per-token kernel, including partial last chunks and states that are not zero."""
+    torch.manual_seed(4)
+    ds, ng, hv = 128, 2, 4
+    n = len(lens)
+    cu = torch.tensor([0] + torch.tensor(lens).cumsum(0).tolist(), dtype=torch.int32)
+    slots = torch.randperm(n + 1)[:n].to(torch.int32)
+    t = sum(lens)
+    qkv = torch.randn(t, (2 * ng + hv) * ds).bfloat16()
+    z = torch.randn(t, hv * ds + 64).bfloat16()[:, : hv * ds]
+    ab = torch.randn(t, 2 * hv)
+    a = -(torch.rand(hv) * 2 + 0.1)
+    bias = torch.randn(hv) * 0.5
+    nw = torch.rand(ds) + 0.5
+    st = torch.randn(n + 1, hv, ds, ds) * 0.1
+    st_ref, st_gpu, st_tok = st.clone(), st.clone().cuda(), st.clone().cuda()
+    assert dn.CHUNKED and t >= dn.CHUNKED_MIN_TOKENS * n
+    ref = dn.deltanet(qkv, z, ab, a, bias, nw, st_ref, cu, slots, ng, hv, ds, 1e-6)
+    args = (qkv.cuda(), z.cuda(), ab.cuda(), a.cuda(), bias.cuda(), nw.cuda())
+    got = dn.deltanet(*args, st_gpu, cu.cuda(), slots.cuda(), ng, hv, ds, 1e-6)
+    _native.assert_status_ok()
+    dn.CHUNKED = False
+    try:
+        tok = dn.deltanet(*args, st_tok, cu.cuda(), slots.cuda(), ng, hv, ds, 1e-6)
+    finally:
+        dn.CHUNKED = True
+    assert _rel(tok, ref) < 1e-2
+    assert _rel(got, ref) < 2e-2, _rel(got, ref)
+    assert _rel(st_gpu, st_ref) < 1e-2, _rel(st_gpu, st_ref)
+    unused = [i for i in range(n + 1) if i not in slots.tolist()][0]
+    assert torch.equal(st_gpu[unused].cpu(), st[unused])
+    # per sequence, so that a wrong chunk of a short sequence cannot hide behind a long one
+    for i in range(n):
+        assert _rel(got[cu[i]:cu[i + 1]], ref[cu[i]:cu[i + 1]]) < 2e-2, (i, lens[i])
+
+
 def test_sigmoid_gate_mul():
     torch.manual_seed(3)
     x = torch.randn(19, 512).bfloat16()
