@@ -8,7 +8,7 @@
 //
 // The recurrence keeps one row of the d_state x d_state state per thread in registers and walks the tokens of its sequence
 // in order, so one launch serves decode (one token) and prefill chunks alike; the state is read once and written once per
-// launch.  A chunked tensor-core formulation of the prefill scan is future work.
+// launch.  Prefill launches take the chunked scan of deltanet_chunk.cu instead.
 //
 // Math and tensor conventions follow common/transformer.h:2861-3113 (tf_ssm_deltanet_forward) and :2829-2851 (the scalar
 // recurrence): qkv channels are ordered [Q (n_group heads) | K (n_group heads) | V (dt_rank heads)], value head h uses the

@@ -34,7 +34,7 @@ constexpr int kDnD = 128;           // d_state
 constexpr int kDnLd = kDnD + 8;     // bf16 row stride of a 128-wide tile in shared memory (the pad spreads the rows over the banks)
 constexpr int kDnLc = kDnC + 8;     // bf16 row stride of a 64-wide tile
 constexpr int kDnLf = kDnD + 4;     // fp32 row stride of the 64 x 128 staging tile
-constexpr int kDnLl = kDnC + 4;     // fp32 row stride of the 64 x 64 triangular factor
+constexpr int kDnLo = kDnC;         // L (64 x 64, fp32) lives in the columns 64 .. 127 of the staging tile while T is solved
 constexpr int kDnThreads = 256;
 
 struct DnChunkArgs {
@@ -78,7 +78,8 @@ using FragA = wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::ro
 using FragB = wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major>;     // B given as [n][k] rows
 using FragC = wmma::fragment<wmma::accumulator, 16, 16, 16, float>;
 
-constexpr int kPrepSmem = (2 * kDnC * kDnLd + 2 * kDnD * kDnLc + kDnC * kDnLc) * 2 + (kDnC * kDnLl + kDnC * kDnLf + 2 * kDnC) * 4;
+// 112.5 KB: two CTAs per SM
+constexpr int kPrepSmem = (2 * kDnC * kDnLd + 2 * kDnD * kDnLc + kDnC * kDnLc) * 2 + (kDnC * kDnLf + 2 * kDnC) * 4;
 
 __global__ void __launch_bounds__(kDnThreads)
 dn_chunk_prep_kernel(const DnChunkArgs a) {
@@ -90,8 +91,8 @@ dn_chunk_prep_kernel(const DnChunkArgs a) {
   __nv_bfloat16* sVT = sK + kDnC * kDnLd;                                  // [128][kDnLc] v transposed
   __nv_bfloat16* sGKT = sVT + kDnD * kDnLc;                                // [128][kDnLc] exp(c_j) k_j transposed
   __nv_bfloat16* sT = sGKT + kDnD * kDnLc;                                 // [64][kDnLc]
-  float* sL = reinterpret_cast<float*>(sT + kDnC * kDnLc);                 // [64][kDnLl]
-  float* sF = sL + kDnC * kDnLl;                                           // [64][kDnLf]
+  float* sF = reinterpret_cast<float*>(sT + kDnC * kDnLc);                 // [64][kDnLf]
+  float* sL = sF + kDnLo;                                                  // [64][.. kDnLf], the right half of sF
   float* sc = sF + kDnC * kDnLf;                                           // [64] running log decay
   float* sb = sc + kDnC;                                                   // [64] beta
 
@@ -174,7 +175,7 @@ dn_chunk_prep_kernel(const DnChunkArgs a) {
     for (int idx = tid; idx < kDnC * kDnC; idx += kDnThreads) {
       const int i = idx / kDnC, j = idx % kDnC;
       if (pass == 0) {
-        sL[i * kDnLl + j] = (j < i) ? sb[i] * __expf(sc[i] - sc[j]) * sF[i * kDnLf + j] : 0.f;
+        sL[i * kDnLf + j] = (j < i) ? sb[i] * __expf(sc[i] - sc[j]) * sF[i * kDnLf + j] : 0.f;
       } else {
         const float m = (j <= i) ? __expf(sc[i] - sc[j]) * sF[i * kDnLf + j] : 0.f;
         a.mqk[(ws * kDnC + i) * kDnC + j] = __float2bfloat16(m);
@@ -183,13 +184,18 @@ dn_chunk_prep_kernel(const DnChunkArgs a) {
     __syncthreads();
   }
 
-  // T = (I + L)^-1 diag(beta): thread `col` solves its column by forward substitution (it reads back only what it wrote itself)
-  if (tid < kDnC) {
-    const int col = tid;
+  // T = (I + L)^-1 diag(beta) by forward substitution, column by column: four adjacent lanes share a column (each a quarter of
+  // the inner sum; x_j = 0 above the diagonal, so the sum starts at the column's block of four)
+  {
+    const int col = tid >> 2, q = tid & 3, j0 = (col & ~3) + q;
+    const float bcol = sb[col];
     for (int i = 0; i < kDnC; ++i) {
-      float acc = (i == col) ? sb[col] : 0.f;
-      for (int j = 0; j < i; ++j) acc -= sL[i * kDnLl + j] * sF[j * kDnLf + col];
-      sF[i * kDnLf + col] = acc;
+      float part = 0.f;
+      for (int j = j0; j < i; j += 4) part += sL[i * kDnLf + j] * sF[j * kDnLf + col];
+      part += __shfl_xor_sync(0xffffffffu, part, 1);
+      part += __shfl_xor_sync(0xffffffffu, part, 2);
+      if (q == 0) sF[i * kDnLf + col] = ((i == col) ? bcol : 0.f) - part;
+      __syncwarp();
     }
   }
   __syncthreads();
@@ -235,7 +241,9 @@ dn_chunk_prep_kernel(const DnChunkArgs a) {
   if (tid == 0) a.glast[ws] = __expf(c_last);
 }
 
-constexpr int kScanSmem = (2 * kDnC * kDnLd + 2 * kDnD * kDnLc + kDnC * kDnLc + kDnD * kDnLd) * 2 + (kDnC * kDnLf + 8 * 256) * 4;
+constexpr int kDnLt = kDnC + 4;     // fp32 row stride of U stored transposed (128 x 64) in the staging tile
+constexpr int kScanStage = (kDnC * kDnLf > kDnD * kDnLt ? kDnC * kDnLf : kDnD * kDnLt);
+constexpr int kScanSmem = (2 * kDnC * kDnLd + 2 * kDnD * kDnLc + kDnC * kDnLc + kDnD * kDnLd) * 2 + (kScanStage + 8 * 256) * 4;
 
 __global__ void __launch_bounds__(kDnThreads)
 dn_chunk_scan_kernel(const DnChunkArgs a) {
@@ -249,7 +257,7 @@ dn_chunk_scan_kernel(const DnChunkArgs a) {
   __nv_bfloat16* sMqk = sUT + kDnD * kDnLc;                                // [64][kDnLc]
   __nv_bfloat16* sSb = sMqk + kDnC * kDnLc;                                // [128][kDnLd] the state as bf16, [value][key]
   float* sF = reinterpret_cast<float*>(sSb + kDnD * kDnLd);                // [64][kDnLf]
-  float* sScr = sF + kDnC * kDnLf;                                         // [8 warps][16 x 16]
+  float* sScr = sF + kScanStage;                                           // [8 warps][16 x 16]
 
   const int h = blockIdx.x, s = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int seq_t0 = a.cu_q[s], seq_t1 = a.cu_q[s + 1];
@@ -320,13 +328,14 @@ dn_chunk_scan_kernel(const DnChunkArgs a) {
           wmma::mma_sync(acc[m], fa, fb, acc[m]);
         }
       }
+      __syncthreads();        // every warp has taken its columns of T V out of the staging tile: U goes back transposed, [value][token]
 #pragma unroll
-      for (int m = 0; m < 4; ++m) wmma::store_matrix_sync(sF + (16 * m) * kDnLf + 16 * warp, acc[m], kDnLf, wmma::mem_row_major);
+      for (int m = 0; m < 4; ++m) wmma::store_matrix_sync(sF + (16 * warp) * kDnLt + 16 * m, acc[m], kDnLt, wmma::mem_col_major);
     }
     __syncthreads();
-    for (int idx = tid; idx < kDnC * kDnD; idx += kDnThreads) {
-      const int j = idx / kDnD, r = idx % kDnD;
-      sUT[r * kDnLc + j] = __float2bfloat16(sF[j * kDnLf + r]);
+    for (int idx = tid; idx < kDnD * kDnC; idx += kDnThreads) {
+      const int r = idx / kDnC, j = idx % kDnC;
+      sUT[r * kDnLc + j] = __float2bfloat16(sF[r * kDnLt + j]);
     }
     __syncthreads();
 
