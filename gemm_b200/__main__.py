@@ -136,6 +136,14 @@ def cmd_compare(args):
     from .models.config import get_config
     from .models.transformer import ForwardBatch, KvCache, Transformer
     from .models.weights import synthetic_weights
+    if getattr(args, "hf", False):
+        import json
+        from .utils import hf_compare
+        vocab = get_config(args.model.split(":", 1)[1]).vocab if args.model.startswith("synthetic:") else loader.config_from_hf(args.model).vocab
+        g = torch.Generator().manual_seed(args.seed)
+        prompt = [int(x) for x in args.ids.replace(",", " ").split()] if args.ids else torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist()
+        print(json.dumps(hf_compare.compare(args.model, prompt, args.steps, args.format, "cuda" if torch.cuda.is_available() else "cpu", args.seed)))
+        return 0
     if args.model.startswith("synthetic:"):
         w_cpu = synthetic_weights(get_config(args.model.split(":", 1)[1]), args.format, device="cpu", seed=args.seed)
     elif os.path.isdir(args.model):
@@ -279,6 +287,8 @@ def main(argv=None):
     cp.add_argument("--steps", type=int, default=8)
     cp.add_argument("--seed", type=int, default=0)
     cp.add_argument("--oracle", action="store_true", help="also compare the CPU path with the fp32 oracle")
+    cp.add_argument("--hf", action="store_true", help="compare against Hugging Face transformers (fp32) on the same checkpoint instead: an "
+                    "HF directory or synthetic:<preset> of a Qwen2 / Qwen3 / Qwen3-MoE architecture")
     cp.set_defaults(fn=cmd_compare)
     dp = sub.add_parser("dump", help="per-layer hidden states as .npy")
     dp.add_argument("--model", required=True, help="GGUF file, HF safetensors directory, or synthetic:<preset>")

@@ -454,7 +454,8 @@ def save_hf_checkpoint(cfg: ModelConfig, src, path: str, mxfp8: bool = False) ->
     save_safetensors(out, os.path.join(path, "model.safetensors"))
     mt = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3moe": "qwen3_moe"}.get(cfg.arch, "qwen3")
     with open(os.path.join(path, "config.json"), "w") as fh:
-        json.dump({"model_type": mt, "hidden_size": h, "num_attention_heads": cfg.n_heads, "num_key_value_heads": cfg.n_kv_heads, "head_dim": d,
+        json.dump({"model_type": mt, "architectures": [{"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM"}[mt]],
+                   "hidden_size": h, "num_attention_heads": cfg.n_heads, "num_key_value_heads": cfg.n_kv_heads, "head_dim": d,
                    "num_hidden_layers": cfg.n_layers, "intermediate_size": cfg.ffn, "vocab_size": cfg.vocab, "rms_norm_eps": cfg.rms_eps,
                    "rope_theta": cfg.rope_theta, "tie_word_embeddings": cfg.tie_embeddings, "max_position_embeddings": cfg.max_seq_len,
                    "num_experts": cfg.n_experts, "num_experts_per_tok": cfg.n_experts_used, "moe_intermediate_size": cfg.expert_ffn,
