@@ -50,8 +50,48 @@ def _add_model_args(p):
     p.add_argument("--page-size", type=int, default=128)
 
 
+def _is_gemma4(path: str) -> bool:
+    import os
+    if not os.path.isfile(path):
+        return False
+    from .utils import gguf as G
+    try:
+        with G.GGUFFile(path) as f:
+            return f.metadata.get("general.architecture") == "gemma4"
+    except Exception:
+        return False
+
+
+def _generate_gemma4(args) -> int:
+    """Gemma4 checkpoints run through ``models.gemma4`` (greedy, one prompt at a time)."""
+    import torch
+    from .models import gemma4
+    from .utils.tokenizer import Tokenizer
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    model = gemma4.load_gguf(args.model, dev, torch.bfloat16 if dev == "cuda" else torch.float32)
+    tok = None
+    if not args.ids:
+        try:
+            from .utils import gguf as G
+            with G.GGUFFile(args.tokenizer or args.model) as f:
+                tok = Tokenizer.from_gguf(f)
+        except Exception as e:
+            sys.exit(f"no tokenizer in {args.tokenizer or args.model} ({e}): pass --ids and prompts as token ids")
+    t0, n_new = time.time(), 0
+    for p in args.prompt or ["Hello"]:
+        ids = [int(x) for x in p.replace(",", " ").split()] if args.ids else tok.encode(p)
+        out = model.generate(ids, args.max_new_tokens)
+        n_new += len(out)
+        print(json.dumps({"prompt": p, "completion": tok.decode(out) if tok is not None else " ".join(map(str, out)), "token_ids": out}))
+    dt = time.time() - t0
+    print(json.dumps({"new_tokens": n_new, "seconds": round(dt, 3), "tokens_per_s": round(n_new / max(dt, 1e-9), 1)}), file=sys.stderr)
+    return 0
+
+
 def cmd_generate(args):
     from .serve.engine import SamplingParams
+    if _is_gemma4(args.model):
+        return _generate_gemma4(args)
     llm = _load_llm(args)
     prompts = args.prompt or ["Hello"]
     sp = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, seed=args.seed)
