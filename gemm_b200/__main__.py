@@ -132,6 +132,44 @@ def cmd_serve(args):
     serve(llm, host=args.host, port=args.port, model_name=args.name or args.model, block=True)
 
 
+def cmd_encode_image(args):
+    """Image -> vision tokens (the reference's vision_encode behind its server, server/server_llm.c:503-518): the image is cut to
+    whole merge cells (patch_size * spatial_merge pixels); resize it beforehand if it is larger than the encoder's trained grid."""
+    import numpy as np
+    import torch
+    from .models import vision
+    if args.image.endswith(".npy"):
+        rgb = torch.from_numpy(np.load(args.image))
+    else:
+        with open(args.image, "rb") as fh:
+            raw = fh.read()
+        parts, pos = [], 0
+        while len(parts) < 4:                                   # magic, width, height, maxval; comments start with '#'
+            while raw[pos:pos + 1].isspace():
+                pos += 1
+            if raw[pos:pos + 1] == b"#":
+                pos = raw.index(b"\n", pos) + 1
+                continue
+            end = pos
+            while not raw[end:end + 1].isspace():
+                end += 1
+            parts.append(raw[pos:end])
+            pos = end
+        if parts[0] != b"P6" or int(parts[3]) != 255:
+            sys.exit("only binary PPM (P6) with maxval 255 is read")
+        wd, ht = int(parts[1]), int(parts[2])
+        rgb = torch.frombuffer(bytearray(raw[pos + 1: pos + 1 + wd * ht * 3]), dtype=torch.uint8).reshape(ht, wd, 3)
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    enc = vision.load_gguf(args.mmproj, dev, torch.bfloat16 if dev == "cuda" else torch.float32)
+    cell = enc.cfg.patch_size * enc.cfg.spatial_merge
+    h, w = rgb.shape[0] // cell * cell, rgb.shape[1] // cell * cell
+    feats = enc.encode(enc.normalize_image(rgb[:h, :w].to(dev)))
+    if args.out:
+        np.save(args.out, feats.cpu().numpy())
+    print(json.dumps({"image": [h, w], "tokens": feats.shape[0], "features_per_token": feats.shape[1], "deepstack_slices": feats.shape[1] // enc.cfg.proj_dim - 1}))
+    return 0
+
+
 def cmd_inspect(args):
     from .utils import gguf as G
     with G.GGUFFile(args.file) as f:
@@ -338,6 +376,11 @@ def main(argv=None):
     dp.add_argument("--out", required=True)
     dp.add_argument("--seed", type=int, default=0)
     dp.set_defaults(fn=cmd_dump)
+    ei = sub.add_parser("encode-image", help="run the Qwen3-VL vision encoder (mmproj GGUF) on an image")
+    ei.add_argument("--mmproj", required=True, help="GGUF file of the vision encoder")
+    ei.add_argument("--image", required=True, help=".npy (uint8 [H, W, 3]) or binary PPM (P6)")
+    ei.add_argument("--out", default="", help="write the features ([tokens, proj_dim * (1 + deepstack)] f32) as .npy")
+    ei.set_defaults(fn=cmd_encode_image)
     b = sub.add_parser("build", help="compile the native libraries")
     b.set_defaults(fn=cmd_build)
     args = ap.parse_args(argv)

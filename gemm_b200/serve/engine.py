@@ -123,9 +123,13 @@ class Engine:
 
     # ------------------------------------------------------------------------------------------ prefill
     @torch.no_grad()
-    def prefill(self, prompts: Sequence[torch.Tensor], reserve: int = 0) -> torch.Tensor:
+    def prefill(self, prompts: Sequence[torch.Tensor], reserve: int = 0, embeds: Optional[Sequence[torch.Tensor]] = None,
+                deepstack: Optional[Sequence[Optional[torch.Tensor]]] = None) -> torch.Tensor:
         """Batched, chunked prefill of new sequences (token id tensors, host or device).  Returns the logits of
-        the last prompt token of every sequence, ``f32 [B, V_local]``.  ``reserve`` extra positions are paged in."""
+        the last prompt token of every sequence, ``f32 [B, V_local]``.  ``reserve`` extra positions are paged in.
+        ``embeds`` (multimodal prompts): per sequence a bf16 ``[len, hidden]`` tensor of input rows that replace the token
+        embeddings (text rows embedded by the caller, vision rows from the encoder; ``models.vision.prompt_inputs`` builds
+        them); ``deepstack``: per sequence bf16 ``[n_deepstack, len, hidden]`` (zero on text rows) or None."""
         base = len(self.seq_pages)
         if base + len(prompts) > self.max_batch:
             raise ValueError(f"{base + len(prompts)} sequences exceed max_batch = {self.max_batch}")
@@ -135,6 +139,8 @@ class Engine:
             self.seq_len.append(0)
             self._ensure_pages(len(self.seq_pages) - 1, pr.numel() + reserve)
         b = len(prompts)
+        if embeds is not None and self.cp is not None:
+            raise NotImplementedError("multimodal prompts under context parallelism")
         if self.cp is not None:
             # sequence-parallel prefill of whole prompts: this rank runs the tokens of its own pages
             # (whole sequences per forward pass, as many as keep every rank within max_prefill_tokens: the same groups on all ranks)
@@ -175,6 +181,13 @@ class Engine:
             fb = ForwardBatch.build(q_lens, ctx, torch.cat([x.to(self.device) for x in ids]), self._block_table([base + i for i in seqs]),
                                     self.page_size, self.hq_local, self.hkv_local, self.device, seq_slots=[base + i for i in seqs],
                                     stage=self.kv.quantized)
+            if embeds is not None:
+                fb.embeds = torch.cat([embeds[i][c: c + q].to(self.device, torch.bfloat16) for i, c, q in zip(seqs, ctx, q_lens)])
+                if deepstack is not None and any(d is not None for d in deepstack):
+                    n_ds = next(d.shape[0] for d in deepstack if d is not None)
+                    fb.deepstack = torch.cat([deepstack[i][:, c: c + q].to(self.device, torch.bfloat16) if deepstack[i] is not None else
+                                              torch.zeros(n_ds, q, self.cfg.hidden, dtype=torch.bfloat16, device=self.device)
+                                              for i, c, q in zip(seqs, ctx, q_lens)], dim=1)
             with profiler.region("prefill_chunk", "step", "engine"):
                 logits = self.model.forward(fb)
             for j, i in enumerate(seqs):

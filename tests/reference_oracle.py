@@ -68,3 +68,17 @@ def engine_lib():
     lib.transformer_set_f64_accum.argtypes = [ctypes.c_void_p, ctypes.c_int]
     lib.ref_n_vocab.argtypes = [ctypes.c_void_p]
     return lib
+
+
+def vision_lib():
+    """ctypes handle exposing the reference's Qwen3-VL vision encoder (gguf_open, vision_load, vision_encode)."""
+    src = ('#define GGUF_LOADER_IMPLEMENTATION\n#include "gguf_loader.h"\n#define GGML_DEQUANT_IMPLEMENTATION\n#include "ggml_dequant.h"\n'
+           '#include "transformer.h"\n#define VISION_ENCODER_IMPLEMENTATION\n#include "vision_encoder.h"\n')      # transformer.h declares qtensor
+    lib = _build("ref_vision", src)
+    lib.gguf_open.restype = ctypes.c_void_p
+    lib.gguf_open.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    lib.vision_load.restype = ctypes.c_void_p
+    lib.vision_load.argtypes = [ctypes.c_void_p]
+    lib.vision_encode.restype = ctypes.POINTER(ctypes.c_float)
+    lib.vision_encode.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    return lib
