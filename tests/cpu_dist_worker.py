@@ -54,6 +54,22 @@ def main():
         check_cp_engine(rank, world, "cpu", False)
         check_cp_engine(rank, world, "cpu", False, name="tiny-moe", prompt_lens=(40, 7))
         check_cp_engine(rank, world, "cpu", False, prompt_lens=(10, 7), new_tokens=12)     # ranks without a page of any prompt
+    if what == "m3ep":
+        # MiniMax-M3 style engine: experts dealt to the ranks (e % world), partial sums all-reduced, against the unsharded model
+        from gemm_b200.models import m3
+        cfg = m3.M3Config(n_layers=3, n_dense_layers=1, hidden=64, vocab=96, n_heads=4, n_kv_heads=2, head_dim=32, rotary_dim=16, msa_index_dim=16,
+                          msa_n_index_heads=2, msa_block_size=4, msa_topk_blocks=2, msa_init_block=1, msa_local_block=1, n_experts=8, n_active=2,
+                          moe_inter=32, dense_inter=96, max_pos=64)
+        t = m3.random_tensors(cfg, 7)
+        ids = torch.randint(0, cfg.vocab, (2, 30), generator=g)
+        full = m3.M3Model(cfg, t)
+        full.reset(2, 48)
+        want = torch.cat([full.forward(ids[:, :20], all_logits=True), full.forward(ids[:, 20:], all_logits=True)], dim=1)
+        mine = m3.M3Model(cfg, t, ep_rank=rank, ep_size=world, group=dist.group.WORLD)
+        assert mine.t["l1.ex_w1"].shape[0] == len(range(rank, cfg.n_experts, world))
+        mine.reset(2, 48)
+        got = torch.cat([mine.forward(ids[:, :20], all_logits=True), mine.forward(ids[:, 20:], all_logits=True)], dim=1)
+        assert rel(got, want) < 1e-4, rel(got, want)
     if what == "groups":
         lay = ParallelLayout(tp=2, pp=2, dp=world // 4)
         grp = init_parallel(lay)

@@ -82,3 +82,65 @@ def vision_lib():
     lib.vision_encode.restype = ctypes.POINTER(ctypes.c_float)
     lib.vision_encode.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
     return lib
+
+
+_M3_SRC = r"""
+#define _GNU_SOURCE
+__asm__(".macro yield\n.endm");      /* the spin pool's Arm hint instruction: nothing on this machine */
+#define GGML_DEQUANT_IMPLEMENTATION
+#include "ggml_dequant.h"
+/* the reference defines this 8-row kernel for SVE only; on this machine it is eight of its own scalar dot products */
+static inline void matvec_bf16_8row(float* dst, const uint16_t* w0, const uint16_t* w1, const uint16_t* w2, const uint16_t* w3, const uint16_t* w4,
+                                    const uint16_t* w5, const uint16_t* w6, const uint16_t* w7, const float* x, int n) {
+  const uint16_t* w[8] = {w0, w1, w2, w3, w4, w5, w6, w7};
+  for (int r = 0; r < 8; r++) dst[r] = vec_dot_bf16_f32(w[r], x, n);
+}
+#define M3_IMPL
+#include "m3.h"
+m3_model* ref_m3_new(const int* v) {
+  m3_config c = m3_default_config();
+  c.n_layers=v[0]; c.n_dense_layers=v[1]; c.hidden=v[2]; c.vocab=v[3]; c.n_heads=v[4]; c.n_kv_heads=v[5]; c.head_dim=v[6]; c.rotary_dim=v[7];
+  c.msa_index_dim=v[8]; c.msa_n_index_heads=v[9]; c.msa_block_size=v[10]; c.msa_topk_blocks=v[11]; c.msa_init_block=v[12]; c.msa_local_block=v[13];
+  c.n_experts=v[14]; c.n_active=v[15]; c.moe_inter=v[16]; c.dense_inter=v[17]; c.max_pos=v[18];
+  return m3_alloc_synth(c, 0, 1, 1, 1);
+}
+/* which: 0 embed 1 head 2 out_norm | per layer: 10 input_norm 11 post_norm 12 wq 13 wk 14 wv 15 wo 16 q_norm 17 k_norm 18 idx_wq 19 idx_wk
+   20 idx_q_norm 21 idx_k_norm 22 gate 23 gate_bias 24 sh_w1 25 sh_w3 26 sh_w2 27 ex_w1[e] 28 ex_w3[e] 29 ex_w2[e] 30 ff_gate 31 ff_up 32 ff_down */
+void* ref_m3_tensor(m3_model* m, int l, int which, int e) {
+  if (which == 0) return m->embed; if (which == 1) return m->head.w; if (which == 2) return m->out_norm;
+  m3_layer* L = &m->layers[l];
+  switch (which) {
+    case 10: return L->input_norm; case 11: return L->post_norm; case 12: return L->wq.w; case 13: return L->wk.w; case 14: return L->wv.w;
+    case 15: return L->wo.w; case 16: return L->q_norm; case 17: return L->k_norm; case 18: return L->idx_wq.w; case 19: return L->idx_wk.w;
+    case 20: return L->idx_q_norm; case 21: return L->idx_k_norm; case 22: return L->gate.w; case 23: return L->gate_bias;
+    case 24: return L->sh_w1.w; case 25: return L->sh_w3.w; case 26: return L->sh_w2.w; case 27: return L->ex_w1[e].w; case 28: return L->ex_w3[e].w;
+    case 29: return L->ex_w2[e].w; case 30: return L->ff_gate.w; case 31: return L->ff_up.w; case 32: return L->ff_down.w;
+  }
+  return 0;
+}
+int ref_m3_forward(m3_model* m, int token, int pos, float* logits) {
+  int H = m->cfg.hidden;
+  float* x = (float*)malloc(H * sizeof(float));
+  for (int i = 0; i < H; i++) x[i] = m3_bf2f(m->embed[(size_t)token * H + i]);
+  int r = m3_forward_token(m, x, pos);
+  memcpy(logits, m->s_logits, (size_t)m->cfg.vocab * sizeof(float));
+  free(x);
+  return r;
+}
+"""
+
+
+def m3_lib():
+    """ctypes handle on the reference's MiniMax-M3 engine (common/m3.h) with synthetic weights: its scalar paths, compiled on this
+    machine with a stand-in for the Arm SVE header it includes unconditionally (the SVE code itself sits behind feature macros)."""
+    stub = tempfile.mkdtemp(prefix="gemm_ref_stub_")
+    with open(os.path.join(stub, "arm_sve.h"), "w") as f:
+        f.write("#ifndef STUB_ARM_SVE_H\n#define STUB_ARM_SVE_H\ntypedef _Float16 __fp16;\n#endif\n")
+    lib = _build("ref_m3", _M3_SRC, extra=("-fopenmp", "-I", stub))
+    lib.ref_m3_new.restype = ctypes.c_void_p
+    lib.ref_m3_new.argtypes = [ctypes.c_void_p]
+    lib.ref_m3_tensor.restype = ctypes.c_void_p
+    lib.ref_m3_tensor.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    lib.ref_m3_forward.restype = ctypes.c_int
+    lib.ref_m3_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    return lib

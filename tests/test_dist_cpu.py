@@ -16,6 +16,6 @@ def _launch(what: str, nproc: int, port: int):
     assert r.returncode == 0 and "CPU_DIST_WORKER_OK" in r.stdout, r.stderr[-4000:]
 
 
-@pytest.mark.parametrize("what,nproc,port", [("groups", 4, 29701), ("tp", 2, 29702), ("ep", 2, 29703), ("pp", 3, 29704), ("dp", 2, 29705), ("cp", 3, 29706), ("hybrid", 2, 29707)])
+@pytest.mark.parametrize("what,nproc,port", [("groups", 4, 29701), ("tp", 2, 29702), ("ep", 2, 29703), ("pp", 3, 29704), ("dp", 2, 29705), ("cp", 3, 29706), ("hybrid", 2, 29707), ("m3ep", 3, 29708)])
 def test_cpu_ranks(what, nproc, port):
     _launch(what, nproc, port)
