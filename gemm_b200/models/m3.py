@@ -168,13 +168,17 @@ class M3Model:
         gf, uf = g.float().clamp(max=lim), u.float().clamp(-lim, lim)
         return (gf * torch.sigmoid(al * gf) * (uf + 1.0)).to(g.dtype)
 
-    def _msa_mask(self, li: int, hn: torch.Tensor, positions: torch.Tensor, p0: int) -> torch.Tensor:
+    def _msa_mask(self, li: int, hn: torch.Tensor, positions: torch.Tensor, p0: int, q_lat: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Boolean ``[B, T, p0 + T]``: which cached positions every query token of a sparse layer attends.  Also stores the step's
-        index keys."""
+        index keys.  The index queries come from the normalised hidden rows (``idx_wq``) or, where the checkpoint has ``idx_wq_b``,
+        from the low-rank query latent ``q_lat``."""
         cfg, tt, p = self.cfg, self.t, f"l{li}."
         b, t, _ = hn.shape
         ih, idim, blk = cfg.msa_n_index_heads, cfg.msa_index_dim, cfg.msa_block_size
-        iq = self._rope(self._norm((hn @ tt[p + "idx_wq"].t()).reshape(b, t, ih, idim), tt[p + "idx_q_norm"]), positions)
+        iq = (q_lat @ tt[p + "idx_wq_b"].t() if (p + "idx_wq_b") in tt else hn @ tt[p + "idx_wq"].t()).reshape(b, t, ih, idim)
+        if (p + "idx_q_norm") in tt:
+            iq = self._norm(iq, tt[p + "idx_q_norm"])
+        iq = self._rope(iq, positions)
         ik = self._rope(self._norm((hn @ tt[p + "idx_wk"].t()).reshape(b, t, 1, idim), tt[p + "idx_k_norm"]), positions)
         self._store(self.cache[li], "ik", ik, p0)
         n = p0 + t

@@ -144,3 +144,65 @@ def m3_lib():
     lib.ref_m3_forward.restype = ctypes.c_int
     lib.ref_m3_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     return lib
+
+
+_GLM5_SRC = r"""
+#define _GNU_SOURCE
+__asm__(".macro yield\n.endm");
+#define GGML_DEQUANT_IMPLEMENTATION
+#include "ggml_dequant.h"
+static inline void matvec_bf16_8row(float* dst, const uint16_t* w0, const uint16_t* w1, const uint16_t* w2, const uint16_t* w3, const uint16_t* w4,
+                                    const uint16_t* w5, const uint16_t* w6, const uint16_t* w7, const float* x, int n) {
+  const uint16_t* w[8] = {w0, w1, w2, w3, w4, w5, w6, w7};
+  for (int r = 0; r < 8; r++) dst[r] = vec_dot_bf16_f32(w[r], x, n);
+}
+#define GLM5_IMPL
+#include "glm5.h"
+glm5_model* ref_glm5_new(const int* v) {
+  glm5_config c = glm5_default_config();
+  c.n_layers=v[0]; c.n_dense_layers=v[1]; c.hidden=v[2]; c.vocab=v[3]; c.n_heads=v[4]; c.n_kv_heads=v[4]; c.qk_nope_dim=v[5]; c.qk_rope_dim=v[6];
+  c.qk_head_dim=v[5]+v[6]; c.head_dim=c.qk_head_dim; c.v_head_dim=v[7]; c.q_lora=v[8]; c.kv_lora=v[9]; c.index_dim=v[10]; c.index_n_heads=v[11];
+  c.index_topk_freq=v[12]; c.rotary_dim=v[6]; c.msa_index_dim=v[10]; c.msa_n_index_heads=v[11]; c.msa_block_size=v[13]; c.msa_topk_blocks=v[14];
+  c.msa_init_block=v[15]; c.msa_local_block=v[16]; c.n_experts=v[17]; c.n_active=v[18]; c.moe_inter=v[19]; c.dense_inter=v[20]; c.max_pos=v[21];
+  return glm5_alloc_synth(c, 0, 1, 1, 1);
+}
+/* which: 0 embed 1 head 2 out_norm | per layer: 10 input_norm 11 post_norm 12 wq_a 13 wq_b 14 wkv_a 15 wkv_b 16 wo 17 q_a_norm 18 kv_a_norm
+   19 idx_wq 20 idx_wk 21 idx_q_norm 22 idx_k_norm 23 gate 24 gate_bias 25 sh_w1 26 sh_w3 27 sh_w2 28 ex_w1[e] 29 ex_w3[e] 30 ex_w2[e]
+   31 ff_gate 32 ff_up 33 ff_down */
+void* ref_glm5_tensor(glm5_model* m, int l, int which, int e) {
+  if (which == 0) return m->embed; if (which == 1) return m->head.w; if (which == 2) return m->out_norm;
+  glm5_layer* L = &m->layers[l];
+  switch (which) {
+    case 10: return L->input_norm; case 11: return L->post_norm; case 12: return L->wq_a.w; case 13: return L->wq_b.w; case 14: return L->wkv_a.w;
+    case 15: return L->wkv_b.w; case 16: return L->wo.w; case 17: return L->q_a_norm; case 18: return L->kv_a_norm; case 19: return L->idx_wq.w;
+    case 20: return L->idx_wk.w; case 21: return L->idx_q_norm; case 22: return L->idx_k_norm; case 23: return L->gate.w; case 24: return L->gate_bias;
+    case 25: return L->sh_w1.w; case 26: return L->sh_w3.w; case 27: return L->sh_w2.w; case 28: return L->ex_w1[e].w; case 29: return L->ex_w3[e].w;
+    case 30: return L->ex_w2[e].w; case 31: return L->ff_gate.w; case 32: return L->ff_up.w; case 33: return L->ff_down.w;
+  }
+  return 0;
+}
+int ref_glm5_forward(glm5_model* m, int token, int pos, float* logits) {
+  int H = m->cfg.hidden;
+  float* x = (float*)malloc(H * sizeof(float));
+  for (int i = 0; i < H; i++) x[i] = glm5_bf2f(m->embed[(size_t)token * H + i]);
+  int r = glm5_forward_token(m, x, pos);
+  memcpy(logits, m->s_logits, (size_t)m->cfg.vocab * sizeof(float));
+  free(x);
+  return r;
+}
+"""
+
+
+def glm5_lib():
+    """ctypes handle on the reference's GLM-5 engine (common/glm5.h) with synthetic weights, built like ``m3_lib``."""
+    stub = tempfile.mkdtemp(prefix="gemm_ref_stub_")
+    with open(os.path.join(stub, "arm_sve.h"), "w") as f:
+        f.write("#ifndef STUB_ARM_SVE_H\n#define STUB_ARM_SVE_H\ntypedef _Float16 __fp16;\n#endif\n")
+    lib = _build("ref_glm5", _GLM5_SRC, extra=("-fopenmp", "-I", stub))
+    lib.ref_glm5_new.restype = ctypes.c_void_p
+    lib.ref_glm5_new.argtypes = [ctypes.c_void_p]
+    lib.ref_glm5_tensor.restype = ctypes.c_void_p
+    lib.ref_glm5_tensor.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    lib.ref_glm5_forward.restype = ctypes.c_int
+    lib.ref_glm5_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    return lib
