@@ -27,6 +27,20 @@ def _load_llm(args):
     import os
     from .serve.llm import LLM
     kw = dict(max_running=args.max_running, num_pages=args.pages, page_size=args.page_size)
+    if _is_gemma4(args.model):
+        # Gemma4 runs as a tensor-op model behind the one-request-at-a-time adapter
+        import torch
+        from .models import gemma4
+        from .serve.sequential import SequentialLLM
+        from .utils import gguf as G
+        from .utils.tokenizer import Tokenizer
+        dev = args.device if (args.device != "cuda" or torch.cuda.is_available()) else "cpu"
+        model = gemma4.load_gguf(args.model, dev, torch.bfloat16 if dev != "cpu" else torch.float32)
+        tok = None
+        with G.GGUFFile(args.tokenizer or args.model) as f:
+            if "tokenizer.ggml.tokens" in f.metadata:
+                tok = Tokenizer.from_gguf(f)
+        return SequentialLLM(model, tok, max_seq_len=min(model.cfg.max_seq_len, args.pages * args.page_size))
     if args.model.startswith("synthetic:"):
         return LLM.from_synthetic(args.model.split(":", 1)[1], fmt=args.format, device=args.device, **kw)
     if os.path.isdir(args.model):
@@ -62,36 +76,8 @@ def _is_gemma4(path: str) -> bool:
         return False
 
 
-def _generate_gemma4(args) -> int:
-    """Gemma4 checkpoints run through ``models.gemma4`` (greedy, one prompt at a time)."""
-    import torch
-    from .models import gemma4
-    from .utils.tokenizer import Tokenizer
-    dev = "cuda" if torch.cuda.is_available() else "cpu"
-    model = gemma4.load_gguf(args.model, dev, torch.bfloat16 if dev == "cuda" else torch.float32)
-    tok = None
-    if not args.ids:
-        try:
-            from .utils import gguf as G
-            with G.GGUFFile(args.tokenizer or args.model) as f:
-                tok = Tokenizer.from_gguf(f)
-        except Exception as e:
-            sys.exit(f"no tokenizer in {args.tokenizer or args.model} ({e}): pass --ids and prompts as token ids")
-    t0, n_new = time.time(), 0
-    for p in args.prompt or ["Hello"]:
-        ids = [int(x) for x in p.replace(",", " ").split()] if args.ids else tok.encode(p)
-        out = model.generate(ids, args.max_new_tokens)
-        n_new += len(out)
-        print(json.dumps({"prompt": p, "completion": tok.decode(out) if tok is not None else " ".join(map(str, out)), "token_ids": out}))
-    dt = time.time() - t0
-    print(json.dumps({"new_tokens": n_new, "seconds": round(dt, 3), "tokens_per_s": round(n_new / max(dt, 1e-9), 1)}), file=sys.stderr)
-    return 0
-
-
 def cmd_generate(args):
     from .serve.engine import SamplingParams
-    if _is_gemma4(args.model):
-        return _generate_gemma4(args)
     llm = _load_llm(args)
     prompts = args.prompt or ["Hello"]
     sp = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, seed=args.seed)
@@ -105,6 +91,8 @@ def cmd_generate(args):
             enc.append(llm.tokenizer.encode(p))
     t0 = time.time()
     stats = None
+    if args.speculative > 0 and not hasattr(llm, "generate_speculative"):
+        sys.exit("--speculative needs the continuous-batching engine: this model family is served one request at a time")
     if args.speculative > 0:
         if args.temperature != 0.0:
             sys.exit("--speculative verifies drafts against greedy choices: use it with --temperature 0")
@@ -125,6 +113,8 @@ def cmd_generate(args):
 def cmd_serve(args):
     from .serve.server import serve
     llm = _load_llm(args)
+    if args.speculative > 0 and not hasattr(llm, "set_drafter"):
+        sys.exit("--speculative needs the continuous-batching engine: this model family is served one request at a time")
     if args.speculative > 0:
         from .serve.speculative import NgramDrafter
         llm.set_drafter(NgramDrafter(gamma=args.speculative))
