@@ -205,7 +205,6 @@ def cmd_compare(args):
     from .models.transformer import ForwardBatch, KvCache, Transformer
     from .models.weights import synthetic_weights
     if getattr(args, "hf", False):
-        import json
         from .utils import hf_compare
         vocab = get_config(args.model.split(":", 1)[1]).vocab if args.model.startswith("synthetic:") else loader.config_from_hf(args.model).vocab
         g = torch.Generator().manual_seed(args.seed)
