@@ -221,3 +221,132 @@ def prompt_inputs(embed_table: torch.Tensor, ids_before, features: torch.Tensor,
         ds[:, ids_before.numel(): ids_before.numel() + n_img] = features[:, proj_dim:].reshape(n_img, n_ds, proj_dim).permute(1, 0, 2).to(tab.device, torch.bfloat16)
     ids = torch.cat([ids_before, torch.zeros(n_img, dtype=torch.long), ids_after]).to(torch.int32)
     return ids, embeds, ds
+
+
+# ---------------------------------------------------------------------------------------------------- Gemma4 vision tower
+@dataclass
+class Gemma4VisionConfig:
+    n_blocks: int = 16
+    dim: int = 768
+    n_heads: int = 12
+    ffn: int = 3072
+    patch_size: int = 16
+    image_size: int = 224
+    proj_dim: int = 2560
+    pool: int = 3                     # average-pooling kernel over the patch grid
+    ln_eps: float = 1e-6
+    n_pos: int = 64                   # rows of each of the two position tables (x and y)
+    rope_theta: float = 100.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.n_heads
+
+
+class Gemma4VisionEncoder:
+    """The ViT tower of the Gemma4 mmproj files (reference: common/gemma4_vision_encoder.h:676-934 for the pieces, :1168-1290 for the
+    pipeline): pixels scaled to [-1, 1]; patch embedding; x and y position tables added; blocks of RMSNorm -> separate q / k / v
+    -> per-head RMSNorm of q and k -> 2-D RoPE (first half of a head turns with x, second half with y, pairs ``(j, j + D/4)``
+    inside a half, theta 100) -> attention WITHOUT a score scale -> output projection -> post-norm -> residual, then RMSNorm ->
+    GELU(gate) * up -> down -> post-norm -> residual; ``pool x pool`` average pooling; times sqrt(dim); ``mm.input_projection``;
+    weightless RMSNorm.  The "gemma4uv" projector variant of the same header (no transformer blocks) is not built."""
+
+    def __init__(self, cfg: Gemma4VisionConfig, tensors: Dict[str, torch.Tensor], device="cpu", dtype=torch.float32):
+        self.cfg, self.t, self.device, self.dtype = cfg, tensors, torch.device(device), dtype
+
+    @staticmethod
+    def random_tensors(cfg: Gemma4VisionConfig, seed: int = 0) -> Dict[str, torch.Tensor]:
+        g = torch.Generator().manual_seed(seed)
+        rn = lambda *s: torch.randn(*s, generator=g) * 0.05
+        nw = lambda n: 1.0 + 0.1 * torch.randn(n, generator=g)
+        d, ps = cfg.dim, cfg.patch_size
+        t = {"v.patch_embd.weight": rn(d, 3, ps, ps), "v.position_embd.weight": rn(2, cfg.n_pos, d), "mm.input_projection.weight": rn(cfg.proj_dim, d)}
+        for b in range(cfg.n_blocks):
+            p = f"v.blk.{b}."
+            t.update({p + "attn_q.weight": rn(d, d), p + "attn_k.weight": rn(d, d), p + "attn_v.weight": rn(d, d), p + "attn_out.weight": rn(d, d),
+                      p + "attn_q_norm.weight": nw(cfg.head_dim), p + "attn_k_norm.weight": nw(cfg.head_dim), p + "attn_post_norm.weight": nw(d),
+                      p + "ffn_gate.weight": rn(cfg.ffn, d), p + "ffn_up.weight": rn(cfg.ffn, d), p + "ffn_down.weight": rn(d, cfg.ffn),
+                      p + "ffn_post_norm.weight": nw(d), p + "ln1.weight": nw(d), p + "ln2.weight": nw(d)})
+        return t
+
+    @staticmethod
+    def save_gguf(cfg: Gemma4VisionConfig, tensors: Dict[str, torch.Tensor], path: str, wtype: str = "F16") -> None:
+        w = G.GGUFWriter()
+        w.add_string("general.architecture", "clip")
+        for key, v in (("block_count", cfg.n_blocks), ("embedding_length", cfg.dim), ("attention.head_count", cfg.n_heads),
+                       ("feed_forward_length", cfg.ffn), ("patch_size", cfg.patch_size), ("image_size", cfg.image_size), ("projection_dim", cfg.proj_dim)):
+            w.add_u32("clip.vision." + key, v)
+        w.add_f32("clip.vision.attention.layer_norm_epsilon", cfg.ln_eps)
+        for name, x in tensors.items():
+            w.add_tensor(name, x.float(), "F32" if x.dim() == 1 else wtype)
+        w.write(path)
+
+    @staticmethod
+    def load_gguf(path: str, device="cpu", dtype=torch.float32) -> "Gemma4VisionEncoder":
+        with G.GGUFFile(path) as f:
+            m = f.metadata
+            if m.get("clip.vision.projector_type") == "gemma4uv":
+                raise NotImplementedError("the gemma4uv projector (no transformer blocks) is not built")
+            k = lambda name, d: m.get("clip.vision." + name, d)
+            t = {}
+            for name, gt in f.tensors.items():
+                x = gt.to_float()
+                t[name] = x.to(device=device, dtype=torch.float32 if x.dim() == 1 else dtype)
+            cfg = Gemma4VisionConfig(n_blocks=int(k("block_count", 16)), dim=int(k("embedding_length", 768)), n_heads=int(k("attention.head_count", 12)),
+                                     ffn=int(k("feed_forward_length", 3072)), patch_size=int(k("patch_size", 16)), image_size=int(k("image_size", 224)),
+                                     proj_dim=int(k("projection_dim", 2560)), ln_eps=float(k("attention.layer_norm_epsilon", 1e-6)),
+                                     n_pos=int(t["v.position_embd.weight"].shape[1]))
+        return Gemma4VisionEncoder(cfg, t, device, dtype)
+
+    def _rms(self, x: torch.Tensor, w: Optional[torch.Tensor]) -> torch.Tensor:
+        xf = x.float()
+        y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.ln_eps)
+        return (y * w.float() if w is not None else y).to(x.dtype)
+
+    def _rope2d(self, x: torch.Tensor, px: torch.Tensor, py: torch.Tensor) -> torch.Tensor:
+        """``x`` [N, H, D]."""
+        d = x.shape[-1]
+        half, quarter = d // 2, d // 4
+        freq = self.cfg.rope_theta ** (-(2.0 * torch.arange(quarter, device=self.device).float()) / half)
+        out = []
+        for pos, sl in ((px, x[..., :half]), (py, x[..., half:])):
+            ang = pos.float()[:, None, None] * freq[None, None, :]
+            a, b = sl[..., :quarter].float(), sl[..., quarter:].float()
+            out += [a * ang.cos() - b * ang.sin(), a * ang.sin() + b * ang.cos()]
+        return torch.cat(out, dim=-1).to(x.dtype)
+
+    @torch.no_grad()
+    def encode(self, rgb: torch.Tensor) -> torch.Tensor:
+        """uint8 ``[H, W, 3]`` (H, W multiples of patch_size * pool) -> f32 ``[tokens, proj_dim]``."""
+        cfg, t = self.cfg, self.t
+        ps, d, nh, hd = cfg.patch_size, cfg.dim, cfg.n_heads, cfg.head_dim
+        hgt, wid, _ = rgb.shape
+        gh, gw = hgt // ps, wid // ps
+        if max(gh, gw) > cfg.n_pos or gh % cfg.pool or gw % cfg.pool:
+            raise ValueError("image larger than the position tables, or its patch grid is not a multiple of the pooling kernel")
+        img = (rgb.to(self.device).float() / 255.0 * 2.0 - 1.0).to(self.dtype)[: gh * ps, : gw * ps]
+        patches = img.reshape(gh, ps, gw, ps, 3).permute(0, 2, 4, 1, 3).reshape(gh * gw, 3 * ps * ps)
+        x = patches @ t["v.patch_embd.weight"].reshape(d, -1).t()
+        if "v.patch_embd.bias" in t:
+            x = x + t["v.patch_embd.bias"].to(x.dtype)
+        py = torch.arange(gh, device=self.device).repeat_interleave(gw)
+        px = torch.arange(gw, device=self.device).repeat(gh)
+        pos = t["v.position_embd.weight"]
+        x = x + pos[0][px].to(x.dtype) + pos[1][py].to(x.dtype)
+        for b in range(cfg.n_blocks):
+            p = f"v.blk.{b}."
+            xn = self._rms(x, t[p + "ln1.weight"])
+            q = self._rope2d(self._rms((xn @ t[p + "attn_q.weight"].t()).reshape(-1, nh, hd), t[p + "attn_q_norm.weight"]), px, py)
+            k = self._rope2d(self._rms((xn @ t[p + "attn_k.weight"].t()).reshape(-1, nh, hd), t[p + "attn_k_norm.weight"]), px, py)
+            v = (xn @ t[p + "attn_v.weight"].t()).reshape(-1, nh, hd)
+            sc = torch.einsum("qhd,khd->hqk", q.float(), k.float())                # no 1 / sqrt(d): the head norms carry the scale
+            a = torch.einsum("hqk,khd->qhd", torch.softmax(sc, dim=-1), v.float()).reshape(-1, d).to(self.dtype)
+            x = x + self._rms(a @ t[p + "attn_out.weight"].t(), t[p + "attn_post_norm.weight"])
+            xn = self._rms(x, t[p + "ln2.weight"])
+            gate = xn @ t[p + "ffn_gate.weight"].t()
+            f = (gate.float() * 0.5 * (1.0 + torch.erf(gate.float() * 0.7071067811865476))).to(self.dtype) * (xn @ t[p + "ffn_up.weight"].t())
+            x = x + self._rms(f @ t[p + "ffn_down.weight"].t(), t[p + "ffn_post_norm.weight"])
+        k_ = cfg.pool
+        pooled = x.float().reshape(gh // k_, k_, gw // k_, k_, d).mean(dim=(1, 3)).reshape(-1, d) * (d ** 0.5)
+        proj = pooled.to(self.dtype) @ t["mm.input_projection.weight"].t()
+        return self._rms(proj, None).float()

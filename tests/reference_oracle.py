@@ -206,3 +206,17 @@ def glm5_lib():
     lib.ref_glm5_forward.restype = ctypes.c_int
     lib.ref_glm5_forward.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     return lib
+
+
+def gemma4_vision_lib():
+    """ctypes handle exposing the reference's Gemma4 vision tower (gguf_open, g4v_load, g4v_encode)."""
+    src = ('#define GGUF_LOADER_IMPLEMENTATION\n#include "gguf_loader.h"\n#define GGML_DEQUANT_IMPLEMENTATION\n#include "ggml_dequant.h"\n'
+           '#include "transformer.h"\n#define GEMMA4_VISION_IMPLEMENTATION\n#include "gemma4_vision_encoder.h"\n')
+    lib = _build("ref_g4v", src)
+    lib.gguf_open.restype = ctypes.c_void_p
+    lib.gguf_open.argtypes = [ctypes.c_char_p, ctypes.c_int]
+    lib.g4v_load.restype = ctypes.c_void_p
+    lib.g4v_load.argtypes = [ctypes.c_void_p]
+    lib.g4v_encode.restype = ctypes.POINTER(ctypes.c_float)
+    lib.g4v_encode.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    return lib

@@ -92,3 +92,27 @@ def test_engine_prefill_with_image_rows():
     eng2 = Engine(w, max_batch=2, max_seq_len=32, page_size=16)
     text_only = eng2.prefill([torch.tensor([5, 6, 7, 8, 9], dtype=torch.int32)], reserve=4)
     assert _rel(logits, text_only) > 1e-2
+
+
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not present")
+@pytest.mark.parametrize("hw", [(24, 24), (12, 36)])
+def test_gemma4_vision_tower_matches_reference(tmp_path, hw):
+    cfg = vision.Gemma4VisionConfig(n_blocks=3, dim=64, n_heads=4, ffn=96, patch_size=4, image_size=24, proj_dim=40, n_pos=12)
+    path = str(tmp_path / "g4v.gguf")
+    vision.Gemma4VisionEncoder.save_gguf(cfg, vision.Gemma4VisionEncoder.random_tensors(cfg, 5), path, "F16")
+    enc = vision.Gemma4VisionEncoder.load_gguf(path)
+    assert enc.cfg.n_pos == 12 and enc.cfg.n_blocks == 3
+    h, w = hw
+    rgb = torch.randint(0, 256, (h, w, 3), generator=torch.Generator().manual_seed(6), dtype=torch.uint8)
+    got = enc.encode(rgb)
+    n_tok = (h // 4 // 3) * (w // 4 // 3)
+    assert got.shape == (n_tok, 40)
+    ref = oracle.gemma4_vision_lib()
+    g = ref.gguf_open(path.encode(), 1)
+    vm = ref.g4v_load(g)
+    assert vm, "the reference tower refused our mmproj file"
+    buf = np.ascontiguousarray(rgb.numpy())
+    p = ref.g4v_encode(vm, buf.ctypes.data, w, h)
+    assert p
+    want = torch.from_numpy(np.ctypeslib.as_array(p, shape=(n_tok, 40)).copy())
+    assert _rel(got, want) < 2e-3, _rel(got, want)
