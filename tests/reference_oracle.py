@@ -220,3 +220,14 @@ def gemma4_vision_lib():
     lib.g4v_encode.restype = ctypes.POINTER(ctypes.c_float)
     lib.g4v_encode.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     return lib
+
+
+def audio_mel_lib():
+    """ctypes handle exposing the reference's Gemma4 audio front end (g4a_mel_init, g4a_mel_extract, g4a_wav_load)."""
+    lib = _build("ref_g4a_mel", '#define GEMMA4_AUDIO_MEL_IMPLEMENTATION\n#include "gemma4_audio_mel.h"\n')
+    lib.g4a_mel_init.restype = ctypes.c_void_p
+    lib.g4a_mel_extract.restype = ctypes.POINTER(ctypes.c_float)
+    lib.g4a_mel_extract.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+    lib.g4a_wav_load.restype = ctypes.POINTER(ctypes.c_float)
+    lib.g4a_wav_load.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int)]
+    return lib
