@@ -194,7 +194,7 @@ class DS4FModel(m3.M3Model):
         cfg, tt, p = self.cfg, self.t, f"l{li}."
         b, t, h = h2.shape
         x = h2.reshape(b * t, h)
-        score = torch.sqrt(torch.nn.functional.softplus((x @ tt[p + "gate"].t()).float()))
+        score = torch.sqrt(torch.nn.functional.softplus(x.float() @ tt[p + "gate"].t()))          # the router runs in fp32
         key = score + tt[p + "gate_bias"][None, :] if (p + "gate_bias") in tt else score
         pick = torch.topk(key, cfg.n_active, dim=-1).indices
         w = torch.gather(score, 1, pick)

@@ -103,7 +103,7 @@ class M3Model:
         for k, v in tensors.items():
             if ".ex_w" in k and ep_size > 1:
                 v = v[ep_rank::ep_size]                                # this rank's experts: e % ep_size == ep_rank, slot e // ep_size
-            keep32 = k.endswith(("gate", "gate_bias")) or v.dim() == 1
+            keep32 = k.rsplit(".", 1)[-1] in ("gate", "gate_bias") or v.dim() == 1          # the router and every vector stay fp32
             self.t[k] = v.to(self.device, torch.float32 if keep32 else dtype)
         half = cfg.rotary_dim // 2
         self.inv_freq = (cfg.rope_theta ** (-2.0 * torch.arange(half, dtype=torch.float64) / cfg.rotary_dim)).to(self.device)

@@ -1,0 +1,36 @@
+"""The tensor-op engines with bf16 weights and activations (the GPU configuration) on CPU tensors: every product sees matching
+dtypes, the result stays near the fp32 run."""
+import pytest
+import torch
+
+from gemm_b200.models import gemma4, vision
+from tests.test_engines_gpu import _cases, _rel
+
+
+@pytest.mark.parametrize("name,make,vocab", list(_cases()), ids=[c[0] for c in _cases()])
+def test_bf16_path(name, make, vocab):
+    ids = torch.randint(0, vocab, (2, 40), generator=torch.Generator().manual_seed(5))
+    ref = make("cpu", torch.float32)
+    ref.reset(2, 64)
+    want = ref.forward(ids, all_logits=True)
+    half = make("cpu", torch.bfloat16)
+    half.reset(2, 64)
+    got = torch.cat([half.forward(ids[:, :29], all_logits=True), half.forward(ids[:, 29:], all_logits=True)], dim=1)
+    assert torch.isfinite(got).all() and _rel(got[:, :8], want[:, :8]) < 0.25
+
+
+def test_bf16_gemma4_and_vision():
+    cfg = gemma4.Gemma4Config(n_layers=4, hidden=64, n_heads=2, n_kv_heads=1, ffn=128, vocab=200, head_dim_full=32, head_dim_swa=16, window=8,
+                              ple_dim=8, shared_kv_layers=2, swa_pattern=[True, False, True, False], max_seq_len=64)
+    t = gemma4.random_tensors(cfg, 1)
+    tb = {k: v.to(torch.float32 if v.dim() == 1 else torch.bfloat16) for k, v in t.items()}
+    m = gemma4.Gemma4Model(cfg, tb, "cpu", torch.bfloat16)
+    m.reset(1, 32)
+    assert torch.isfinite(m.forward(torch.randint(0, 200, (1, 12)))).all()
+    vc = vision.VisionConfig(n_blocks=2, dim=64, n_heads=4, ffn=128, patch_size=4, image_size=16, proj_dim=32, deepstack_layers=[0])
+    vt = {k: v.to(torch.float32 if v.dim() == 1 else torch.bfloat16) for k, v in vision.random_tensors(vc, 1).items()}
+    assert torch.isfinite(vision.VisionEncoder(vc, vt, "cpu", torch.bfloat16).encode(torch.randn(16, 16, 3))).all()
+    gc = vision.Gemma4VisionConfig(n_blocks=2, dim=64, n_heads=4, ffn=96, patch_size=4, image_size=24, proj_dim=40, n_pos=12)
+    gt = {k: v.to(torch.float32 if v.dim() == 1 else torch.bfloat16) for k, v in vision.Gemma4VisionEncoder.random_tensors(gc, 1).items()}
+    out = vision.Gemma4VisionEncoder(gc, gt, "cpu", torch.bfloat16).encode(torch.randint(0, 256, (24, 24, 3), dtype=torch.uint8))
+    assert torch.isfinite(out).all()
