@@ -7,7 +7,7 @@ broadcast to every stage.  Here a step carries a whole packed batch ``[T, hidden
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -44,3 +44,39 @@ class PipelineStage:
             tok = sampling.argmax(logits, idx_offset=self.model.w.vocab_start).to(torch.int32)
         dist.broadcast(tok, src=self.ranks[-1], group=self.group)
         return tok
+
+    @torch.no_grad()
+    def step_many(self, fbs: Sequence[ForwardBatch]) -> List[torch.Tensor]:
+        """One forward pass over several micro-batches (disjoint groups of sequences) with the stages overlapped: the receives of
+        all micro-batches are posted up front, every hidden state is sent on without waiting for it to arrive, so stage ``r + 1``
+        works on micro-batch ``i`` while stage ``r`` runs ``i + 1`` (with ``m`` micro-batches over ``p`` stages the idle share of a
+        stage drops from ``(p - 1) / p`` to ``(p - 1) / (m + p - 1)``).  The last stage broadcasts all tokens once.  Returns the
+        greedy next tokens per micro-batch, on every stage; equal to ``step`` called per micro-batch."""
+        hidden = self.model.cfg.hidden
+        dev = fbs[0].positions.device
+        prev = None if self.first else self.ranks[self.rank - 1]
+        nxt = None if self.last else self.ranks[self.rank + 1]
+        bufs, recvs = [], []
+        if prev is not None:
+            for i, fb in enumerate(fbs):
+                buf = torch.empty(fb.n_tokens, hidden, dtype=torch.bfloat16, device=dev)
+                bufs.append(buf)
+                recvs.append(dist.irecv(buf, src=prev, group=self.group, tag=i))
+        sends, toks = [], []
+        for i, fb in enumerate(fbs):
+            x = None
+            if prev is not None:
+                recvs[i].wait()
+                x = bufs[i]
+            x = self.model.forward_hidden(fb, x=x)
+            if nxt is not None:
+                out = self.model.final_hidden(x).contiguous()
+                sends.append((dist.isend(out, dst=nxt, group=self.group, tag=i), out))      # the tensor stays alive until the send is done
+            else:
+                toks.append(sampling.argmax(self.model.head(x, fb), idx_offset=self.model.w.vocab_start).to(torch.int32))
+        for req, _ in sends:
+            req.wait()
+        sizes = [fb.logit_rows.numel() for fb in fbs]
+        tok = torch.cat(toks) if self.last else torch.empty(sum(sizes), dtype=torch.int32, device=dev)
+        dist.broadcast(tok, src=self.ranks[-1], group=self.group)
+        return list(torch.split(tok, sizes))

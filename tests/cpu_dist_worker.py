@@ -127,6 +127,20 @@ def main():
         got = run(stage.model, cfg, toks, step_fn=stage.step)
         for a, b in zip(got, ref):
             assert torch.equal(a, b), (a, b)
+        # micro-batches (one per sequence group) through the overlapped schedule give the tokens of the whole-batch step
+        from gemm_b200.ops import attention as att
+        seqs = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in (9, 14, 6, 11)]
+        page, bt_all, p0 = 16, torch.zeros(4, 1, dtype=torch.int32), 0
+        bt_all[:, 0] = torch.arange(4)
+
+        def fb_of(idx):
+            fb = ForwardBatch.build([seqs[i].numel() for i in idx], [0] * len(idx), torch.cat([seqs[i] for i in idx]), bt_all[idx], page,
+                                    cfg.n_heads, cfg.n_kv_heads, "cpu")
+            fb.work = att.build_work([seqs[i].numel() for i in idx], stage.model.hq_local, stage.model.hkv_local)
+            return fb
+        whole = stage.step(fb_of([0, 1, 2, 3]))
+        parts = stage.step_many([fb_of([0, 1]), fb_of([2]), fb_of([3])])
+        assert [p.numel() for p in parts] == [2, 1, 1] and torch.equal(torch.cat(parts), whole), (parts, whole)
     elif what == "dp":
         dp = DataParallel(dist.group.WORLD)
         items = list(range(10))
