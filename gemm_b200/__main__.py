@@ -118,8 +118,14 @@ def cmd_serve(args):
     if args.speculative > 0:
         from .serve.speculative import NgramDrafter
         llm.set_drafter(NgramDrafter(gamma=args.speculative))
+    vis = None
+    if getattr(args, "mmproj", ""):
+        import torch
+        from .models import vision
+        dev = str(llm.device) if hasattr(llm, "device") else "cpu"
+        vis = vision.load_gguf(args.mmproj, dev, torch.bfloat16 if dev.startswith("cuda") else torch.float32)
     print(f"serving {args.model} on http://{args.host}:{args.port}", file=sys.stderr)
-    serve(llm, host=args.host, port=args.port, model_name=args.name or args.model, block=True)
+    serve(llm, host=args.host, port=args.port, model_name=args.name or args.model, block=True, vision=vis)
 
 
 def cmd_encode_image(args):
@@ -128,27 +134,11 @@ def cmd_encode_image(args):
     import numpy as np
     import torch
     from .models import vision
-    if args.image.endswith(".npy"):
-        rgb = torch.from_numpy(np.load(args.image))
-    else:
-        with open(args.image, "rb") as fh:
-            raw = fh.read()
-        parts, pos = [], 0
-        while len(parts) < 4:                                   # magic, width, height, maxval; comments start with '#'
-            while raw[pos:pos + 1].isspace():
-                pos += 1
-            if raw[pos:pos + 1] == b"#":
-                pos = raw.index(b"\n", pos) + 1
-                continue
-            end = pos
-            while not raw[end:end + 1].isspace():
-                end += 1
-            parts.append(raw[pos:end])
-            pos = end
-        if parts[0] != b"P6" or int(parts[3]) != 255:
-            sys.exit("only binary PPM (P6) with maxval 255 is read")
-        wd, ht = int(parts[1]), int(parts[2])
-        rgb = torch.frombuffer(bytearray(raw[pos + 1: pos + 1 + wd * ht * 3]), dtype=torch.uint8).reshape(ht, wd, 3)
+    with open(args.image, "rb") as fh:
+        try:
+            rgb = vision.decode_image(fh.read())
+        except ValueError as e:
+            sys.exit(str(e))
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     enc = vision.load_gguf(args.mmproj, dev, torch.bfloat16 if dev == "cuda" else torch.float32)
     cell = enc.cfg.patch_size * enc.cfg.spatial_merge
@@ -321,6 +311,7 @@ def main(argv=None):
     s.add_argument("--speculative", type=int, default=0, metavar="GAMMA",
                    help="greedy requests decode speculatively with prompt-lookup drafts of up to GAMMA tokens")
     s.add_argument("--name", default="")
+    s.add_argument("--mmproj", default="", help="GGUF file of the Qwen3-VL vision encoder: requests may then carry \"image\" (base64 PPM / .npy)")
     s.set_defaults(fn=cmd_serve)
     i = sub.add_parser("inspect", help="dump a GGUF file")
     i.add_argument("file")

@@ -201,6 +201,39 @@ class VisionEncoder:
         return embeds, ds
 
 
+def decode_image(data: bytes) -> torch.Tensor:
+    """uint8 ``[H, W, 3]`` from the bytes of a binary PPM (P6, maxval 255) or of a ``.npy`` file holding such an array (the two
+    formats this framework reads without an image library)."""
+    if data[:6] == b"\x93NUMPY":
+        import io
+        import numpy as np
+        arr = np.load(io.BytesIO(data), allow_pickle=False)
+        if arr.ndim != 3 or arr.shape[2] != 3 or arr.dtype != np.uint8:
+            raise ValueError("the .npy image must be uint8 [H, W, 3]")
+        return torch.from_numpy(arr.copy())
+    parts, pos = [], 0
+    while len(parts) < 4:                                   # magic, width, height, maxval; comments start with '#'
+        while data[pos:pos + 1].isspace():
+            pos += 1
+        if data[pos:pos + 1] == b"#":
+            pos = data.index(b"\n", pos) + 1
+            continue
+        end = pos
+        while end < len(data) and not data[end:end + 1].isspace():
+            end += 1
+        if end == pos:
+            raise ValueError("truncated PPM header")
+        parts.append(data[pos:end])
+        pos = end
+    if parts[0] != b"P6" or int(parts[3]) != 255:
+        raise ValueError("only binary PPM (P6) with maxval 255, or .npy, is read")
+    wd, ht = int(parts[1]), int(parts[2])
+    body = data[pos + 1: pos + 1 + wd * ht * 3]
+    if len(body) != wd * ht * 3:
+        raise ValueError("truncated PPM data")
+    return torch.frombuffer(bytearray(body), dtype=torch.uint8).reshape(ht, wd, 3)
+
+
 def prompt_inputs(embed_table: torch.Tensor, ids_before, features: torch.Tensor, ids_after, proj_dim: int):
     """Input rows of a prompt ``text, image, text``: ``(placeholder ids int32 [T], embeds bf16 [T, hidden], deepstack bf16
     [n_deepstack, T, hidden] or None)``.  Text rows are the token embeddings, the image rows the encoder's main embedding; the

@@ -18,6 +18,7 @@ from ..models.config import ModelConfig, get_config
 from ..models.transformer import ForwardBatch, KvCache, Transformer
 from ..models.weights import ModelWeights, synthetic_weights
 from ..ops import attention as att
+from ..ops import elementwise as ew
 from ..ops import sampling
 from ..utils.tokenizer import Tokenizer
 from .engine import SamplingParams
@@ -32,6 +33,8 @@ class _Req:
     out: List[int] = field(default_factory=list)
     done: bool = False
     error: Optional[str] = None      # set when the scheduler had to drop the request (the cache can never hold it)
+    embeds: Optional[torch.Tensor] = None       # bf16 [prompt_len, hidden]: input rows of a multimodal prompt (replace the token embeddings)
+    deepstack: Optional[torch.Tensor] = None    # bf16 [n_deepstack, prompt_len, hidden]: rows added after the first layers, zero on text
 
 
 class LLM:
@@ -80,12 +83,17 @@ class LLM:
         return cls(synthetic_weights(get_config(model), fmt, device, seed), None, **kw)
 
     # ------------------------------------------------------------------------------------------ requests
-    def add_request(self, prompt_ids: Sequence[int], sp: Optional[SamplingParams] = None) -> int:
+    def add_request(self, prompt_ids: Sequence[int], sp: Optional[SamplingParams] = None, embeds: Optional[torch.Tensor] = None,
+                    deepstack: Optional[torch.Tensor] = None) -> int:
+        """``embeds`` / ``deepstack`` (multimodal prompts, ``models.vision.prompt_inputs``): input rows of the prompt positions; the
+        ids at image positions are placeholders.  Generated tokens are embedded from the table as usual."""
         sp = sp or SamplingParams()
+        if embeds is not None and (embeds.shape[0] != len(prompt_ids) or (deepstack is not None and deepstack.shape[1] != len(prompt_ids))):
+            raise ValueError("embeds / deepstack must have one row per prompt position")
         rid = self._next_id
         self._next_id += 1
         self.sched.add(rid, len(prompt_ids), sp.max_new_tokens)      # raises ValueError for a request the cache can never hold
-        self._reqs[rid] = _Req(list(prompt_ids), len(prompt_ids), sp)
+        self._reqs[rid] = _Req(list(prompt_ids), len(prompt_ids), sp, embeds=embeds, deepstack=deepstack)
         return rid
 
     def set_drafter(self, drafter) -> None:
@@ -147,6 +155,21 @@ class LLM:
                 self.kv.reset_slots([self._slot_of[it.req_id]])
         fb = ForwardBatch.build(q_lens, ctx, ids, bt, self.page_size, self.model.hq_local, self.model.hkv_local, self.device,
                                 seq_slots=[self._slot_of[it.req_id] for it in plan])
+        if any(self._reqs[it.req_id].embeds is not None and it.ctx_len < self._reqs[it.req_id].prompt_len for it in plan):
+            # a prefill chunk of a multimodal prompt is in the batch: every row of the step enters as an embedding
+            rows_in = ew.embed(fb.ids, self.w.embed).clone()
+            ds_in, p0 = None, 0
+            for it, q in zip(plan, q_lens):
+                r = self._reqs[it.req_id]
+                lo, hi = it.ctx_len, min(it.ctx_len + q, r.prompt_len)
+                if r.embeds is not None and hi > lo:
+                    rows_in[p0: p0 + hi - lo] = r.embeds[lo:hi].to(self.device, torch.bfloat16)
+                    if r.deepstack is not None:
+                        if ds_in is None:
+                            ds_in = torch.zeros(r.deepstack.shape[0], rows_in.shape[0], rows_in.shape[1], dtype=torch.bfloat16, device=self.device)
+                        ds_in[:, p0: p0 + hi - lo] = r.deepstack[:, lo:hi].to(self.device, torch.bfloat16)
+                p0 += q
+            fb.embeds, fb.deepstack = rows_in, ds_in
         # logits: one row per plan item (its last token); an item with draft tokens gets a row for each of its positions
         row0, rows, p0 = [], [], 0
         for q, d in zip(q_lens, drafts):

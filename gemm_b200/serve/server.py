@@ -47,20 +47,22 @@ class EngineThread(threading.Thread):
         self.streams: Dict[int, "queue.Queue"] = {}
         self.tokens_total = 0
         self.stop_flag = False
+        self.vision = None               # models.vision.VisionEncoder: requests may then carry an image
 
-    def submit(self, ids: List[int], sp: SamplingParams) -> "queue.Queue":
+    def submit(self, ids: List[int], sp: SamplingParams, extra: Optional[dict] = None) -> "queue.Queue":
+        """``extra``: keyword arguments for ``add_request`` (``embeds`` / ``deepstack`` of a multimodal prompt)."""
         q: "queue.Queue" = queue.Queue()
-        self.inbox.put((ids, sp, q))
+        self.inbox.put((ids, sp, q, extra or {}))
         return q
 
     def run(self):
         while not self.stop_flag:
             try:
                 while True:
-                    ids, sp, q = self.inbox.get(block=not self.llm.has_work(), timeout=0.05)
+                    ids, sp, q, extra = self.inbox.get(block=not self.llm.has_work(), timeout=0.05)
                     try:
-                        rid = self.llm.add_request(ids, sp)
-                    except ValueError:                   # the cache can never hold this request: end its stream at once
+                        rid = self.llm.add_request(ids, sp, **extra)
+                    except (ValueError, TypeError):                   # the cache can never hold this request: end its stream at once
                         q.put(None)
                         continue
                     self.streams[rid] = q
@@ -138,7 +140,30 @@ def make_handler(engine: EngineThread, model_name: str):
                 prompt = build_chat_prompt(req.get("messages", []))
             else:
                 prompt = req.get("prompt", "")
-            if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            extra = {}
+            image_b64 = req.get("image")
+            if image_b64 is not None:
+                # one image per request: base64 of a binary PPM or a .npy (uint8 [H, W, 3]); the text is split at "<image>" (the image
+                # comes first when the marker is absent), as the reference's server feeds tokens, vision rows, tokens
+                # (server/server_llm.c:503-548)
+                if engine.vision is None or llm.tokenizer is None or not hasattr(llm, "w"):
+                    return self._json(400, {"error": "no vision encoder loaded (serve --mmproj) or no tokenizer"})
+                import base64
+                from ..models import vision as V
+                try:
+                    rgb = V.decode_image(base64.b64decode(image_b64))
+                    enc = engine.vision
+                    cell = enc.cfg.patch_size * enc.cfg.spatial_merge
+                    h, w = rgb.shape[0] // cell * cell, rgb.shape[1] // cell * cell
+                    feats = enc.encode(enc.normalize_image(rgb[:h, :w]))
+                except Exception as e:                         # a bad image is the client's error, not the server's
+                    return self._json(400, {"error": f"image: {e}"})
+                text = prompt if isinstance(prompt, str) else ""
+                before, _, after = text.partition("<image>") if "<image>" in text else ("", "", text)
+                ids_t, embeds, ds = V.prompt_inputs(llm.w.embed, llm.tokenizer.encode(before), feats, llm.tokenizer.encode(after), enc.cfg.proj_dim)
+                ids = ids_t.tolist()
+                extra = {"embeds": embeds, "deepstack": ds}
+            elif isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
                 ids = prompt                                   # pre-tokenised prompt
             else:
                 if llm.tokenizer is None:
@@ -153,7 +178,7 @@ def make_handler(engine: EngineThread, model_name: str):
             stop_strings = req.get("stop") or []
             if isinstance(stop_strings, str):
                 stop_strings = [stop_strings]
-            q = engine.submit(ids, sp)
+            q = engine.submit(ids, sp, extra)
             rid = "cmpl-" + uuid.uuid4().hex[:24]
             created = int(time.time())
             obj = "chat.completion" if chat else "text_completion"
@@ -213,9 +238,11 @@ def make_handler(engine: EngineThread, model_name: str):
     return Handler
 
 
-def serve(llm: LLM, host: str = "127.0.0.1", port: int = 8080, model_name: str = "gemm_b200", block: bool = True):
-    """Start the engine thread and the HTTP server.  Returns ``(server, engine_thread)``; with ``block`` it serves for ever."""
+def serve(llm: LLM, host: str = "127.0.0.1", port: int = 8080, model_name: str = "gemm_b200", block: bool = True, vision=None):
+    """Start the engine thread and the HTTP server.  Returns ``(server, engine_thread)``; with ``block`` it serves for ever.
+    ``vision``: a ``models.vision.VisionEncoder``; requests may then carry ``"image"`` (base64 PPM or .npy)."""
     engine = EngineThread(llm)
+    engine.vision = vision
     engine.start()
     httpd = ThreadingHTTPServer((host, port), make_handler(engine, model_name))
     if block:

@@ -116,3 +116,71 @@ def test_gemma4_vision_tower_matches_reference(tmp_path, hw):
     assert p
     want = torch.from_numpy(np.ctypeslib.as_array(p, shape=(n_tok, 40)).copy())
     assert _rel(got, want) < 2e-3, _rel(got, want)
+
+
+def test_multimodal_requests_through_llm_and_server():
+    """An image + text prompt through the continuous-batching loop (chunked prefill, a text-only request in the same batch) equals the
+    engine's one-shot prefill + decode, and the HTTP endpoint takes the image as base64."""
+    import base64
+    import io
+    import json
+    import urllib.request
+    import numpy as np
+    from gemm_b200.models.config import get_config
+    from gemm_b200.models.weights import synthetic_weights
+    from gemm_b200.serve.engine import Engine, SamplingParams
+    from gemm_b200.serve.llm import LLM
+    from gemm_b200.serve.server import serve
+    from gemm_b200.utils.tokenizer import Tokenizer, toy_vocab
+    cfg_t = get_config("tiny-dense").with_(n_deepstack_layers=2)
+    cfg_v = vision.VisionConfig(n_blocks=2, dim=64, n_heads=4, ffn=128, patch_size=4, image_size=16, proj_dim=cfg_t.hidden, deepstack_layers=[0, 1])
+    enc = vision.VisionEncoder(cfg_v, vision.random_tensors(cfg_v, 1))
+    rgb = torch.randint(0, 256, (16, 16, 3), generator=torch.Generator().manual_seed(3), dtype=torch.uint8)
+    feats = enc.encode(enc.normalize_image(rgb))
+    w = synthetic_weights(cfg_t, "bf16", "cpu", 3)
+    tokens, merges = toy_vocab("describe the picture of a quick brown fox " * 3, 60)
+    tokens = (tokens + ["<|im_end|>"] + [f"<x{i}>" for i in range(cfg_t.vocab)])[: cfg_t.vocab]
+    tok = Tokenizer(tokens, merges, [1] * len(tokens), "qwen2", {"eos": tokens.index("<|im_end|>")})
+    before, after = tok.encode("describe "), tok.encode(" the picture")
+    ids, embeds, ds = vision.prompt_inputs(w.embed, before, feats, after, cfg_t.hidden)
+    # reference: the static engine, whole prompt at once
+    eng = Engine(w, max_batch=1, max_seq_len=64, page_size=16)
+    logits = eng.prefill([ids], reserve=8, embeds=[embeds], deepstack=[ds])
+    first = logits.argmax(-1).to(torch.int32)
+    eng.begin_decode(first, SamplingParams(), 8, use_graph=False)
+    want = [int(first[0])] + [int(eng.decode_step()[0]) for _ in range(4)]
+    # continuous batching with a token budget that cuts the prompt into chunks, next to a text-only request
+    llm = LLM(w, tok, max_running=4, max_batch_tokens=6, num_pages=32, page_size=16)
+    sp = SamplingParams(max_new_tokens=5)
+    r_img = llm.add_request(ids.tolist(), sp, embeds=embeds, deepstack=ds)
+    r_txt = llm.add_request(tok.encode("a quick brown fox"), sp)
+    outs = {r_img: [], r_txt: []}
+    while llm.has_work():
+        llm.step()
+        for rid, toks in llm.produced_all.items():
+            outs[rid].extend(toks)
+    assert outs[r_img] == want and len(outs[r_txt]) == 5
+    # the HTTP endpoint: the same image as base64 .npy and as PPM
+    httpd, engine = serve(llm, port=0, block=False, vision=enc)
+    port = httpd.server_address[1]
+    try:
+        buf = io.BytesIO()
+        np.save(buf, rgb.numpy())
+        ppm = b"P6\n16 16\n255\n" + rgb.numpy().tobytes()
+        got = []
+        for raw in (buf.getvalue(), ppm):
+            body = {"prompt": "describe <image> the picture", "image": base64.b64encode(raw).decode(), "max_tokens": 5}
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+            got.append(json.loads(urllib.request.urlopen(req, timeout=60).read()))
+        assert got[0]["token_ids"] == got[1]["token_ids"] == want[: len(got[0]["token_ids"])]
+        assert got[0]["usage"]["prompt_tokens"] == len(before) + 4 + len(after)
+        bad = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", data=json.dumps({"prompt": "x", "image": "AAAA"}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        try:
+            urllib.request.urlopen(bad, timeout=60)
+            assert False, "a broken image must be refused"
+        except urllib.error.HTTPError as e:
+            assert e.code == 400
+    finally:
+        engine.stop_flag = True
+        httpd.shutdown()
