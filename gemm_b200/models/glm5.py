@@ -196,3 +196,79 @@ class GLM5Model(m3.M3Model):
         xo = self._norm(x if all_logits else x[:, -1:], tt["out_norm"]).to(self.dtype)
         logits = (xo @ tt["head"].t()).float()
         return logits if all_logits else logits[:, 0]
+
+
+# ---------------------------------------------------------------------------------------------------- checkpoints
+# tensor names of the GLM-5 checkpoints as the reference's loader reads them (common/glm5_impl.h:773-1010): per layer under
+# "model.layers.<l>.", experts under ".mlp.experts.<e>."; FP8 weights carry "<name>_scale_inv" (fp32 per 128 x 128 block)
+_HF_LAYER = {"input_norm": "input_layernorm.weight", "post_norm": "post_attention_layernorm.weight", "wq_a": "self_attn.q_a_proj.weight",
+             "q_a_norm": "self_attn.q_a_layernorm.weight", "wq_b": "self_attn.q_b_proj.weight", "wkv_a": "self_attn.kv_a_proj_with_mqa.weight",
+             "kv_a_norm": "self_attn.kv_a_layernorm.weight", "wkv_b": "self_attn.kv_b_proj.weight", "wo": "self_attn.o_proj.weight",
+             "idx_wq_b": "self_attn.indexer.wq_b.weight", "idx_wk": "self_attn.indexer.wk.weight", "idx_k_norm": "self_attn.indexer.k_norm.weight",
+             "gate": "mlp.gate.weight", "gate_bias": "mlp.gate.e_score_correction_bias", "sh_w1": "mlp.shared_experts.gate_proj.weight",
+             "sh_w3": "mlp.shared_experts.up_proj.weight", "sh_w2": "mlp.shared_experts.down_proj.weight", "ff_gate": "mlp.gate_proj.weight",
+             "ff_up": "mlp.up_proj.weight", "ff_down": "mlp.down_proj.weight"}
+_HF_EXPERT = {"ex_w1": "gate_proj.weight", "ex_w3": "up_proj.weight", "ex_w2": "down_proj.weight"}
+_HF_GLOBAL = {"embed": "model.embed_tokens.weight", "head": "lm_head.weight", "out_norm": "model.norm.weight"}
+_HF_PREFIX, _HF_EXPERTS = "model.layers.{l}.", "mlp.experts.{e}."
+
+
+def checkpoint_shapes(cfg: GLM5Config) -> Dict[str, torch.Tensor]:
+    """Names, shapes and dtypes (meta tensors) of a checkpoint of ``cfg``: the indexer reads the query latent (``idx_wq_b``) and
+    exists on the MoE layers that have one of their own."""
+    with torch.device("meta"):
+        h, nh = cfg.hidden, cfg.n_heads
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16)
+        t = {"embed": bf(cfg.vocab, h), "head": bf(cfg.vocab, h), "out_norm": bf(h)}
+        for li in range(cfg.n_layers):
+            p = f"l{li}."
+            t.update({p + "input_norm": bf(h), p + "post_norm": bf(h), p + "wq_a": bf(cfg.q_lora, h), p + "wq_b": bf(nh * cfg.qk_head_dim, cfg.q_lora),
+                      p + "wkv_a": bf(cfg.kv_cache_dim, h), p + "wkv_b": bf(nh * (cfg.qk_nope_dim + cfg.v_head_dim), cfg.kv_lora),
+                      p + "wo": bf(h, nh * cfg.v_head_dim), p + "q_a_norm": bf(cfg.q_lora), p + "kv_a_norm": bf(cfg.kv_lora)})
+            if cfg.is_moe(li):
+                e, it = cfg.n_experts, cfg.moe_inter
+                if cfg.has_full_indexer(li):
+                    t.update({p + "idx_wq_b": bf(cfg.index_n_heads * cfg.index_dim, cfg.q_lora), p + "idx_wk": bf(cfg.index_dim, h),
+                              p + "idx_k_norm": bf(cfg.index_dim)})
+                t.update({p + "gate": bf(e, h), p + "gate_bias": torch.empty(e, dtype=torch.float32), p + "sh_w1": bf(it, h), p + "sh_w3": bf(it, h),
+                          p + "sh_w2": bf(h, it), p + "ex_w1": bf(e, it, h), p + "ex_w3": bf(e, it, h), p + "ex_w2": bf(e, h, it)})
+            else:
+                t.update({p + "ff_gate": bf(cfg.dense_inter, h), p + "ff_up": bf(cfg.dense_inter, h), p + "ff_down": bf(h, cfg.dense_inter)})
+    return t
+
+
+def save_checkpoint(cfg: GLM5Config, tensors: Dict[str, torch.Tensor], path: str, fp8: bool = False) -> None:
+    """An HF-layout directory; ``fp8`` stores the projection matrices as F8_E4M3 with fp32 ``_scale_inv`` per 128 x 128 block (the
+    dense format of the GLM-5 checkpoints)."""
+    import dataclasses
+    import json
+    import os
+    from .loader import save_safetensors
+    os.makedirs(path, exist_ok=True)
+    named = m3.checkpoint_names(tensors, _HF_LAYER, _HF_EXPERT, _HF_GLOBAL, _HF_PREFIX, _HF_EXPERTS)
+    out: Dict[str, torch.Tensor] = {}
+    for name, v in named.items():
+        quant = fp8 and v.dim() == 2 and "norm" not in name and "embed" not in name and "lm_head" not in name and "gate.weight" not in name
+        if quant:
+            rows, cols = v.shape
+            pr, pc = (rows + 127) // 128 * 128, (cols + 127) // 128 * 128
+            w = torch.zeros(pr, pc)
+            w[:rows, :cols] = v.float()
+            sc = (w.reshape(pr // 128, 128, pc // 128, 128).abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
+            q = (w / sc.repeat_interleave(128, 0).repeat_interleave(128, 1))[:rows, :cols].to(torch.float8_e4m3fn)
+            out[name], out[name + "_scale_inv"] = q, sc.float()
+        else:
+            out[name] = v
+    save_safetensors(out, os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as fh:
+        json.dump({"model_type": "glm5", "gemm_b200": dataclasses.asdict(cfg)}, fh)
+
+
+def load_checkpoint(path: str, device="cpu", dtype=torch.float32, cfg: Optional[GLM5Config] = None, **kw) -> "GLM5Model":
+    import json
+    import os
+    if cfg is None:
+        with open(os.path.join(path, "config.json")) as fh:
+            cfg = GLM5Config(**json.load(fh)["gemm_b200"])
+    t = m3.read_checkpoint(path, checkpoint_shapes(cfg), _HF_LAYER, _HF_EXPERT, _HF_GLOBAL, _HF_PREFIX, _HF_EXPERTS)
+    return GLM5Model(cfg, t, device, dtype, **kw)

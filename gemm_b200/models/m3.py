@@ -289,3 +289,103 @@ class M3Model:
             out.append(int(logits[0].argmax()))
             logits = self.forward(torch.tensor([[out[-1]]]))
         return out
+
+
+# ---------------------------------------------------------------------------------------------------- checkpoints
+# tensor names of the MiniMax-M3 checkpoints, as the reference's loader reads them (common/m3_impl.h:463-560): per layer under
+# "language_model.model.layers.<l>.", experts under ".block_sparse_moe.experts.<e>."
+_HF_LAYER = {"input_norm": "input_layernorm.weight", "post_norm": "post_attention_layernorm.weight", "wq": "self_attn.q_proj.weight",
+             "wk": "self_attn.k_proj.weight", "wv": "self_attn.v_proj.weight", "wo": "self_attn.o_proj.weight", "q_norm": "self_attn.q_norm.weight",
+             "k_norm": "self_attn.k_norm.weight", "idx_wq": "self_attn.index_q_proj.weight", "idx_wk": "self_attn.index_k_proj.weight",
+             "idx_q_norm": "self_attn.index_q_norm.weight", "idx_k_norm": "self_attn.index_k_norm.weight", "gate": "block_sparse_moe.gate.weight",
+             "gate_bias": "block_sparse_moe.e_score_correction_bias", "sh_w1": "block_sparse_moe.shared_experts.gate_proj.weight",
+             "sh_w3": "block_sparse_moe.shared_experts.up_proj.weight", "sh_w2": "block_sparse_moe.shared_experts.down_proj.weight",
+             "ff_gate": "mlp.gate_proj.weight", "ff_up": "mlp.up_proj.weight", "ff_down": "mlp.down_proj.weight"}
+_HF_EXPERT = {"ex_w1": "w1.weight", "ex_w3": "w3.weight", "ex_w2": "w2.weight"}
+_HF_GLOBAL = {"embed": "language_model.model.embed_tokens.weight", "head": "language_model.lm_head.weight", "out_norm": "language_model.model.norm.weight"}
+_HF_PREFIX, _HF_EXPERTS = "language_model.model.layers.{l}.", "block_sparse_moe.experts.{e}."
+
+
+def checkpoint_names(tensors: Dict[str, torch.Tensor], layer: Dict[str, str], expert: Dict[str, str], glob: Dict[str, str], prefix: str,
+                     experts: str) -> Dict[str, torch.Tensor]:
+    """Our tensor dictionary under checkpoint names (stacked expert tensors become one entry per expert)."""
+    out: Dict[str, torch.Tensor] = {}
+    for k, v in tensors.items():
+        if k in glob:
+            out[glob[k]] = v
+            continue
+        li, key = int(k[1:k.index(".")]), k[k.index(".") + 1:]
+        if key in expert:
+            for e in range(v.shape[0]):
+                out[prefix.format(l=li) + experts.format(e=e) + expert[key]] = v[e]
+        else:
+            out[prefix.format(l=li) + layer[key]] = v
+    return out
+
+
+def read_checkpoint(path: str, shapes: Dict[str, torch.Tensor], layer, expert, glob, prefix, experts) -> Dict[str, torch.Tensor]:
+    """The tensors named by ``shapes`` (a dictionary of the wanted names, e.g. ``random_tensors(cfg)``) from an HF safetensors
+    directory: bf16 as stored; FP8 with E8M0 or 128 x 128 fp32 block scales and MXFP4 dequantised (``loader.SafetensorsSource``)."""
+    from .loader import SafetensorsSource
+    src = SafetensorsSource(path)
+    out: Dict[str, torch.Tensor] = {}
+    for k, like in shapes.items():
+        if k in glob:
+            t = src._raw(glob[k])
+        else:
+            li, key = int(k[1:k.index(".")]), k[k.index(".") + 1:]
+            if key in expert:
+                t = torch.stack([src._raw(prefix.format(l=li) + experts.format(e=e) + expert[key]) for e in range(like.shape[0])])
+            else:
+                name = prefix.format(l=li) + layer[key]
+                if name not in src.where:
+                    continue                                    # optional tensors (a checkpoint without an indexer norm, ...)
+                t = src._raw(name)
+        if tuple(t.shape) != tuple(like.shape):
+            raise ValueError(f"{k}: checkpoint has shape {tuple(t.shape)}, the configuration wants {tuple(like.shape)}")
+        out[k] = t.to(like.dtype, copy=True)            # a copy: the file's mapping goes away with ``src``
+    return out
+
+
+def save_checkpoint(cfg: M3Config, tensors: Dict[str, torch.Tensor], path: str) -> None:
+    """An HF-layout directory (``model.safetensors`` + ``config.json`` holding the fields of ``M3Config``)."""
+    import dataclasses
+    import json
+    import os
+    from .loader import save_safetensors
+    os.makedirs(path, exist_ok=True)
+    save_safetensors(checkpoint_names(tensors, _HF_LAYER, _HF_EXPERT, _HF_GLOBAL, _HF_PREFIX, _HF_EXPERTS), os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as fh:
+        json.dump({"model_type": "minimax_m3", "gemm_b200": dataclasses.asdict(cfg)}, fh)
+
+
+def load_checkpoint(path: str, device="cpu", dtype=torch.float32, cfg: Optional[M3Config] = None, **kw) -> "M3Model":
+    import json
+    import os
+    if cfg is None:
+        with open(os.path.join(path, "config.json")) as fh:
+            cfg = M3Config(**json.load(fh)["gemm_b200"])
+    wanted = {k: torch.empty(v.shape, dtype=v.dtype, device="meta") for k, v in _shapes(cfg).items()}
+    t = read_checkpoint(path, wanted, _HF_LAYER, _HF_EXPERT, _HF_GLOBAL, _HF_PREFIX, _HF_EXPERTS)
+    return M3Model(cfg, t, device, dtype, **kw)
+
+
+def _shapes(cfg: M3Config) -> Dict[str, torch.Tensor]:
+    """Names, shapes and dtypes of a checkpoint of ``cfg`` without allocating it."""
+    with torch.device("meta"):
+        h, qd, kvd, hd = cfg.hidden, cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim, cfg.head_dim
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16)
+        f32 = lambda *s: torch.empty(*s, dtype=torch.float32)
+        t = {"embed": bf(cfg.vocab, h), "head": bf(cfg.vocab, h), "out_norm": bf(h)}
+        for li in range(cfg.n_layers):
+            p = f"l{li}."
+            t.update({p + "input_norm": bf(h), p + "post_norm": bf(h), p + "wq": bf(qd, h), p + "wk": bf(kvd, h), p + "wv": bf(kvd, h),
+                      p + "wo": bf(h, qd), p + "q_norm": bf(hd), p + "k_norm": bf(hd)})
+            if cfg.is_moe(li):
+                iqd, idim, e, it = cfg.msa_n_index_heads * cfg.msa_index_dim, cfg.msa_index_dim, cfg.n_experts, cfg.moe_inter
+                t.update({p + "idx_wq": bf(iqd, h), p + "idx_wk": bf(idim, h), p + "idx_q_norm": bf(idim), p + "idx_k_norm": bf(idim),
+                          p + "gate": f32(e, h), p + "gate_bias": f32(e), p + "sh_w1": bf(it, h), p + "sh_w3": bf(it, h), p + "sh_w2": bf(h, it),
+                          p + "ex_w1": bf(e, it, h), p + "ex_w3": bf(e, it, h), p + "ex_w2": bf(e, h, it)})
+            else:
+                t.update({p + "ff_gate": bf(cfg.dense_inter, h), p + "ff_up": bf(cfg.dense_inter, h), p + "ff_down": bf(h, cfg.dense_inter)})
+    return t

@@ -95,3 +95,38 @@ def test_latent_cache_is_small_and_indexer_changes_late_tokens():
     per_pos = sum(v.shape[-1] for c in dense.cache for v in c.values())
     assert per_pos == CFG.n_layers * CFG.kv_cache_dim + (CFG.n_layers - CFG.n_dense_layers) * CFG.index_dim
     assert CFG.kv_cache_dim < 2 * CFG.n_heads * CFG.v_head_dim / 8
+
+
+def test_checkpoint_round_trip_bf16_and_fp8(tmp_path):
+    """HF-layout checkpoints under the reference loader's tensor names: bf16 reads back exactly; FP8 with 128 x 128 block scales reads
+    back as the values it encodes (the model then runs on the dequantised weights); the indexer takes the query latent."""
+    from gemm_b200.models import m3
+    cfg = glm5.GLM5Config(**{**CFG.__dict__, "hidden": 128, "q_lora": 128, "moe_inter": 128, "dense_inter": 128})
+    shapes = glm5.checkpoint_shapes(cfg)
+    g = torch.Generator().manual_seed(3)
+    t = {k: (((torch.rand(v.shape, generator=g) * 2 - 1) * 0.05) + (1.0 if k.endswith("norm") else 0.0)).to(v.dtype) for k, v in shapes.items()}
+    assert "l2.idx_wq_b" in t and "l1.idx_wq_b" not in t and "l0.idx_wk" not in t          # layer 2 is the first MoE layer with an indexer
+    toks = torch.randint(0, cfg.vocab, (1, 40), generator=g)
+    base = glm5.GLM5Model(cfg, t, msa=True)
+    want = base.forward(toks, all_logits=True)
+    d = str(tmp_path / "bf16")
+    glm5.save_checkpoint(cfg, t, d)
+    m = glm5.load_checkpoint(d, msa=True)
+    assert m.cfg == cfg and torch.equal(m.forward(toks, all_logits=True), want)
+    d8 = str(tmp_path / "fp8")
+    glm5.save_checkpoint(cfg, t, d8, fp8=True)
+    from gemm_b200.models.loader import SafetensorsSource
+    src = SafetensorsSource(d8)
+    assert "model.layers.1.self_attn.q_a_proj.weight_scale_inv" in src.where and "model.layers.1.mlp.experts.3.down_proj.weight_scale_inv" in src.where
+    del src
+    m8 = glm5.load_checkpoint(d8, msa=True)
+    got = m8.forward(toks, all_logits=True)
+    assert _rel(m8.t["l1.wq_a"], base.t["l1.wq_a"]) < 0.05 and _rel(got[:, :8], want[:, :8]) < 0.5 and torch.isfinite(got).all()       # e4m3 keeps 3 mantissa bits
+    # M3 checkpoints the same way
+    c3 = m3.M3Config(n_layers=2, n_dense_layers=1, hidden=64, vocab=96, n_heads=4, n_kv_heads=2, head_dim=32, rotary_dim=16, msa_index_dim=16,
+                     msa_n_index_heads=2, msa_block_size=4, msa_topk_blocks=2, n_experts=4, n_active=2, moe_inter=32, dense_inter=96, max_pos=64)
+    t3 = m3.random_tensors(c3, 1)
+    d3 = str(tmp_path / "m3")
+    m3.save_checkpoint(c3, t3, d3)
+    x = torch.randint(0, 96, (1, 20), generator=g)
+    assert torch.equal(m3.load_checkpoint(d3).forward(x, all_logits=True), m3.M3Model(c3, t3).forward(x, all_logits=True))
