@@ -41,6 +41,24 @@ def _load_llm(args):
             if "tokenizer.ggml.tokens" in f.metadata:
                 tok = Tokenizer.from_gguf(f)
         return SequentialLLM(model, tok, max_seq_len=min(model.cfg.max_seq_len, args.pages * args.page_size))
+    if os.path.isfile(os.path.join(args.model, "config.json")):
+        # M3 / GLM-5 style checkpoints (models.m3 / models.glm5 save_checkpoint layout) run as tensor-op models
+        with open(os.path.join(args.model, "config.json")) as fh:
+            mt = json.load(fh).get("model_type", "")
+        if mt in ("minimax_m3", "glm5"):
+            import torch
+            from .models import glm5, m3
+            from .serve.sequential import SequentialLLM
+            dev = args.device if (args.device != "cuda" or torch.cuda.is_available()) else "cpu"
+            mod = m3 if mt == "minimax_m3" else glm5
+            model = mod.load_checkpoint(args.model, dev, torch.bfloat16 if dev != "cpu" else torch.float32)
+            tok = None
+            if args.tokenizer:
+                from .utils import gguf as G
+                from .utils.tokenizer import Tokenizer
+                with G.GGUFFile(args.tokenizer) as f:
+                    tok = Tokenizer.from_gguf(f)
+            return SequentialLLM(model, tok, max_seq_len=min(model.cfg.max_pos, args.pages * args.page_size))
     if args.model.startswith("synthetic:"):
         return LLM.from_synthetic(args.model.split(":", 1)[1], fmt=args.format, device=args.device, **kw)
     if os.path.isdir(args.model):

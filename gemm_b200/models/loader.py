@@ -374,7 +374,7 @@ class SafetensorsSource:
             return t.to(torch.float32) * sc
         if t.dtype == torch.uint8 and (name + "_scale") in self.where:  # MXFP4
             return mxfp4_dequant(t, self.where[name + "_scale"].get(name + "_scale"))
-        return t.to(torch.float32)
+        return t.to(torch.float32, copy=True)           # a copy also for F32 tensors: the file's mapping ends with this object
 
     def has(self, name: str) -> bool:
         return hf_name(name) in self.where
