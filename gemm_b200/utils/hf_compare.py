@@ -84,3 +84,63 @@ def compare(model: str, prompt: Sequence[int], steps: int = 8, fmt: str = "bf16"
     rel: List[float] = [float((ours_l[i] - hf_l[i]).norm() / (hf_l[i].norm() + 1e-12)) for i in range(min(same + 1, n))]
     return {"prompt_len": len(prompt), "steps": steps, "ours_tokens": ours_t, "hf_tokens": hf_t, "logit_rel_per_step": [round(r, 5) for r in rel],
             "token_agreement": sum(int(a == b) for a, b in zip(ours_t, hf_t)) / max(1, n), "edit_distance": edit_distance(ours_t, hf_t)}
+
+
+def hf_qwen35_model(cfg, src):
+    """A Hugging Face ``Qwen3_5ForCausalLM`` (fp32, eager) holding the weights of ``src`` (a tensor source with GGUF names, e.g.
+    ``models.weights.RandomSource``) for a dense hybrid configuration (gated Delta-Net + gated attention layers).
+
+    What differs between the two layouts: HF's RMSNorm multiplies by ``1 + w`` (GGUF files carry ``1 + w``); HF's value head ``j`` of
+    a Delta-Net layer uses key head ``j // (Hv / Hk)``, the GGUF order is ``j % Hk`` (common/transformer.h:2861-3113), so value
+    heads (rows of the V block of ``attn_qkv``, of ``attn_gate``, ``ssm_alpha``, ``ssm_beta``, conv channels, ``ssm_a``, ``ssm_dt.bias``,
+    columns of ``ssm_out``) are permuted; ``ssm_a`` is ``-exp(A_log)``."""
+    from transformers.models.qwen3_5 import modeling_qwen3_5 as M
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
+    if cfg.is_moe or not cfg.attn_output_gate:
+        raise ValueError("the Hugging Face arm for hybrid models covers the dense qwen35 architecture")
+    g_, hv, ds, h = cfg.ssm_n_heads_k, cfg.ssm_n_heads_v, cfg.ssm_head_dim, cfg.hidden
+    r_ = hv // g_
+    perm = torch.tensor([(j % r_) * g_ + (j // r_) for j in range(hv)])
+    hc = Qwen3_5TextConfig(
+        hidden_size=h, num_hidden_layers=cfg.n_layers, num_attention_heads=cfg.n_heads, num_key_value_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
+        intermediate_size=cfg.ffn, vocab_size=cfg.vocab, rms_norm_eps=cfg.rms_eps, linear_conv_kernel_dim=cfg.ssm_d_conv, linear_key_head_dim=ds,
+        linear_value_head_dim=ds, linear_num_key_heads=g_, linear_num_value_heads=hv,
+        layer_types=["linear_attention" if cfg.is_ssm_layer(i) else "full_attention" for i in range(cfg.n_layers)],
+        rope_parameters={"rope_type": "default", "rope_theta": cfg.rope_theta, "partial_rotary_factor": (cfg.rope_dim or cfg.head_dim) / cfg.head_dim,
+                         "mrope_section": list(cfg.mrope_sections[:3]) if cfg.mrope_sections else [11, 11, 10]},
+        tie_word_embeddings=False, attention_bias=False, max_position_embeddings=max(cfg.max_seq_len, 4096), hidden_act="silu")
+    hc._attn_implementation = "eager"
+    model = M.Qwen3_5ForCausalLM(hc).float().eval()
+    f32 = lambda name, shape: src.get(name, shape).float()
+    qd, di, kdim = cfg.ssm_qkv_dim, cfg.ssm_d_inner, g_ * ds
+    vrows = (perm[:, None] * ds + torch.arange(ds)[None, :]).reshape(-1)
+    chan = torch.cat([torch.arange(2 * kdim), 2 * kdim + vrows])
+    new = {"model.embed_tokens.weight": f32("token_embd.weight", (cfg.vocab, h)), "lm_head.weight": f32("output.weight", (cfg.vocab, h)),
+           "model.norm.weight": f32("output_norm.weight", (h,)) - 1.0}
+    for li in range(cfg.n_layers):
+        p, q = f"blk.{li}.", f"model.layers.{li}."
+        new[q + "input_layernorm.weight"] = f32(p + "attn_norm.weight", (h,)) - 1.0
+        new[q + "post_attention_layernorm.weight"] = f32(p + "ffn_norm.weight", (h,)) - 1.0
+        for a, b_, shp in (("ffn_gate", "gate_proj", (cfg.ffn, h)), ("ffn_up", "up_proj", (cfg.ffn, h)), ("ffn_down", "down_proj", (h, cfg.ffn))):
+            new[q + f"mlp.{b_}.weight"] = f32(p + a + ".weight", shp)
+        if cfg.is_ssm_layer(li):
+            la = q + "linear_attn."
+            new[la + "in_proj_qkv.weight"] = f32(p + "attn_qkv.weight", (qd, h))[chan]
+            new[la + "in_proj_z.weight"] = f32(p + "attn_gate.weight", (di, h))[vrows]
+            new[la + "in_proj_a.weight"] = f32(p + "ssm_alpha.weight", (hv, h))[perm]
+            new[la + "in_proj_b.weight"] = f32(p + "ssm_beta.weight", (hv, h))[perm]
+            new[la + "conv1d.weight"] = f32(p + "ssm_conv1d.weight", (qd, cfg.ssm_d_conv))[chan].unsqueeze(1)
+            new[la + "A_log"] = torch.log(-f32(p + "ssm_a", (hv,)))[perm]
+            new[la + "dt_bias"] = f32(p + "ssm_dt.bias", (hv,))[perm]
+            new[la + "norm.weight"] = f32(p + "ssm_norm.weight", (ds,))
+            new[la + "out_proj.weight"] = f32(p + "ssm_out.weight", (h, di))[:, vrows]
+        else:
+            sa = q + "self_attn."
+            new[sa + "q_proj.weight"] = f32(p + "attn_q.weight", (2 * cfg.q_dim, h))          # [q_h | gate_h] per head in both layouts
+            new[sa + "k_proj.weight"] = f32(p + "attn_k.weight", (cfg.kv_dim, h))
+            new[sa + "v_proj.weight"] = f32(p + "attn_v.weight", (cfg.kv_dim, h))
+            new[sa + "o_proj.weight"] = f32(p + "attn_output.weight", (h, cfg.q_dim))
+            new[sa + "q_norm.weight"] = f32(p + "attn_q_norm.weight", (cfg.head_dim,)) - 1.0
+            new[sa + "k_norm.weight"] = f32(p + "attn_k_norm.weight", (cfg.head_dim,)) - 1.0
+    model.load_state_dict(new)
+    return model
