@@ -88,29 +88,38 @@ def compare(model: str, prompt: Sequence[int], steps: int = 8, fmt: str = "bf16"
 
 def hf_qwen35_model(cfg, src):
     """A Hugging Face ``Qwen3_5ForCausalLM`` (fp32, eager) holding the weights of ``src`` (a tensor source with GGUF names, e.g.
-    ``models.weights.RandomSource``) for a dense hybrid configuration (gated Delta-Net + gated attention layers).
+    ``models.weights.RandomSource``) for a hybrid configuration (gated Delta-Net + gated attention layers; dense FFN or MoE with a
+    gated shared expert: ``Qwen3_5MoeForCausalLM``).
 
     What differs between the two layouts: HF's RMSNorm multiplies by ``1 + w`` (GGUF files carry ``1 + w``); HF's value head ``j`` of
     a Delta-Net layer uses key head ``j // (Hv / Hk)``, the GGUF order is ``j % Hk`` (common/transformer.h:2861-3113), so value
     heads (rows of the V block of ``attn_qkv``, of ``attn_gate``, ``ssm_alpha``, ``ssm_beta``, conv channels, ``ssm_a``, ``ssm_dt.bias``,
     columns of ``ssm_out``) are permuted; ``ssm_a`` is ``-exp(A_log)``."""
-    from transformers.models.qwen3_5 import modeling_qwen3_5 as M
-    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
-    if cfg.is_moe or not cfg.attn_output_gate:
-        raise ValueError("the Hugging Face arm for hybrid models covers the dense qwen35 architecture")
+    if not cfg.attn_output_gate or cfg.full_attention_interval <= 0:
+        raise ValueError("the Hugging Face arm for hybrid models covers the qwen35 / qwen35moe architectures")
+    if cfg.is_moe:
+        # the MoE variant: softmax router with renormalised top-k, stacked experts ([gate | up] rows), shared expert behind a sigmoid gate
+        from transformers.models.qwen3_5_moe import modeling_qwen3_5_moe as M
+        from transformers.models.qwen3_5_moe.configuration_qwen3_5_moe import Qwen3_5MoeTextConfig as Qwen3_5TextConfig
+        extra = dict(moe_intermediate_size=cfg.expert_ffn, shared_expert_intermediate_size=cfg.shared_expert_ffn, num_experts=cfg.n_experts,
+                     num_experts_per_tok=cfg.n_experts_used)
+    else:
+        from transformers.models.qwen3_5 import modeling_qwen3_5 as M
+        from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5TextConfig
+        extra = dict(intermediate_size=cfg.ffn)
     g_, hv, ds, h = cfg.ssm_n_heads_k, cfg.ssm_n_heads_v, cfg.ssm_head_dim, cfg.hidden
     r_ = hv // g_
     perm = torch.tensor([(j % r_) * g_ + (j // r_) for j in range(hv)])
     hc = Qwen3_5TextConfig(
         hidden_size=h, num_hidden_layers=cfg.n_layers, num_attention_heads=cfg.n_heads, num_key_value_heads=cfg.n_kv_heads, head_dim=cfg.head_dim,
-        intermediate_size=cfg.ffn, vocab_size=cfg.vocab, rms_norm_eps=cfg.rms_eps, linear_conv_kernel_dim=cfg.ssm_d_conv, linear_key_head_dim=ds,
+        vocab_size=cfg.vocab, rms_norm_eps=cfg.rms_eps, linear_conv_kernel_dim=cfg.ssm_d_conv, linear_key_head_dim=ds, **extra,
         linear_value_head_dim=ds, linear_num_key_heads=g_, linear_num_value_heads=hv,
         layer_types=["linear_attention" if cfg.is_ssm_layer(i) else "full_attention" for i in range(cfg.n_layers)],
         rope_parameters={"rope_type": "default", "rope_theta": cfg.rope_theta, "partial_rotary_factor": (cfg.rope_dim or cfg.head_dim) / cfg.head_dim,
                          "mrope_section": list(cfg.mrope_sections[:3]) if cfg.mrope_sections else [11, 11, 10]},
         tie_word_embeddings=False, attention_bias=False, max_position_embeddings=max(cfg.max_seq_len, 4096), hidden_act="silu")
     hc._attn_implementation = "eager"
-    model = M.Qwen3_5ForCausalLM(hc).float().eval()
+    model = (M.Qwen3_5MoeForCausalLM if cfg.is_moe else M.Qwen3_5ForCausalLM)(hc).float().eval()
     f32 = lambda name, shape: src.get(name, shape).float()
     qd, di, kdim = cfg.ssm_qkv_dim, cfg.ssm_d_inner, g_ * ds
     vrows = (perm[:, None] * ds + torch.arange(ds)[None, :]).reshape(-1)
@@ -121,8 +130,18 @@ def hf_qwen35_model(cfg, src):
         p, q = f"blk.{li}.", f"model.layers.{li}."
         new[q + "input_layernorm.weight"] = f32(p + "attn_norm.weight", (h,)) - 1.0
         new[q + "post_attention_layernorm.weight"] = f32(p + "ffn_norm.weight", (h,)) - 1.0
-        for a, b_, shp in (("ffn_gate", "gate_proj", (cfg.ffn, h)), ("ffn_up", "up_proj", (cfg.ffn, h)), ("ffn_down", "down_proj", (h, cfg.ffn))):
-            new[q + f"mlp.{b_}.weight"] = f32(p + a + ".weight", shp)
+        if cfg.is_moe:
+            e, it, fs = cfg.n_experts, cfg.expert_ffn, cfg.shared_expert_ffn
+            new[q + "mlp.gate.weight"] = f32(p + "ffn_gate_inp.weight", (e, h))
+            new[q + "mlp.experts.gate_up_proj"] = torch.stack([torch.cat([src.get_expert(p + "ffn_gate_exps.weight", x, (it, h)).float(),
+                                                                             src.get_expert(p + "ffn_up_exps.weight", x, (it, h)).float()]) for x in range(e)])
+            new[q + "mlp.experts.down_proj"] = torch.stack([src.get_expert(p + "ffn_down_exps.weight", x, (h, it)).float() for x in range(e)])
+            for a, b_, shp in (("ffn_gate_shexp", "gate_proj", (fs, h)), ("ffn_up_shexp", "up_proj", (fs, h)), ("ffn_down_shexp", "down_proj", (h, fs))):
+                new[q + f"mlp.shared_expert.{b_}.weight"] = f32(p + a + ".weight", shp)
+            new[q + "mlp.shared_expert_gate.weight"] = f32(p + "ffn_gate_inp_shexp.weight", (h,)).reshape(1, h)
+        else:
+            for a, b_, shp in (("ffn_gate", "gate_proj", (cfg.ffn, h)), ("ffn_up", "up_proj", (cfg.ffn, h)), ("ffn_down", "down_proj", (h, cfg.ffn))):
+                new[q + f"mlp.{b_}.weight"] = f32(p + a + ".weight", shp)
         if cfg.is_ssm_layer(li):
             la = q + "linear_attn."
             new[la + "in_proj_qkv.weight"] = f32(p + "attn_qkv.weight", (qd, h))[chan]
