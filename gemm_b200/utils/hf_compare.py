@@ -163,3 +163,29 @@ def hf_qwen35_model(cfg, src):
             new[sa + "k_norm.weight"] = f32(p + "attn_k_norm.weight", (cfg.head_dim,)) - 1.0
     model.load_state_dict(new)
     return model
+
+
+def hf_qwen3vl_text_model(cfg, src):
+    """``(Qwen3VLTextModel in fp32, LM head matrix)`` holding the weights of ``src`` (GGUF names) for a dense Qwen3 configuration with
+    M-RoPE sections: the text side of Qwen3-VL, which takes embedding rows, (t, h, w) positions and DeepStack features."""
+    from transformers.models.qwen3_vl import modeling_qwen3_vl as M
+    from transformers.models.qwen3_vl.configuration_qwen3_vl import Qwen3VLTextConfig
+    h = cfg.hidden
+    hc = Qwen3VLTextConfig(hidden_size=h, num_hidden_layers=cfg.n_layers, num_attention_heads=cfg.n_heads, num_key_value_heads=cfg.n_kv_heads,
+                           head_dim=cfg.head_dim, intermediate_size=cfg.ffn, vocab_size=cfg.vocab, rms_norm_eps=cfg.rms_eps,
+                           rope_parameters={"rope_type": "default", "rope_theta": cfg.rope_theta, "mrope_section": list(cfg.mrope_sections[:3])},
+                           tie_word_embeddings=False, attention_bias=False, max_position_embeddings=max(cfg.max_seq_len, 4096))
+    hc._attn_implementation = "eager"
+    model = M.Qwen3VLTextModel(hc).float().eval()
+    sd = model.state_dict()
+    f32 = lambda name, shape: src.get(name, shape).float()
+    new = {"embed_tokens.weight": f32("token_embd.weight", (cfg.vocab, h)), "norm.weight": f32("output_norm.weight", (h,))}
+    names = {"attn_norm": "input_layernorm", "ffn_norm": "post_attention_layernorm", "attn_q": "self_attn.q_proj", "attn_k": "self_attn.k_proj",
+             "attn_v": "self_attn.v_proj", "attn_output": "self_attn.o_proj", "attn_q_norm": "self_attn.q_norm", "attn_k_norm": "self_attn.k_norm",
+             "ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj"}
+    for li in range(cfg.n_layers):
+        for a, b in names.items():
+            k = f"layers.{li}.{b}.weight"
+            new[k] = f32(f"blk.{li}.{a}.weight", tuple(sd[k].shape))
+    model.load_state_dict(new)
+    return model, f32("output.weight", (cfg.vocab, h))
