@@ -28,6 +28,7 @@
 #include <functional>
 #include <mutex>
 #include <thread>
+#include <sys/mman.h>
 
 extern "C" {
 void* gbh_gguf_open(const char* path);
@@ -125,8 +126,13 @@ struct CpuEngine {
   QMat embed, head;
   std::vector<float> kc, vc;       // [layer][pos][n_kv * head_dim]
   double t_prefill = 0, t_decode = 0;
+  // seconds per phase since the last reset (gbh_cpu_engine_profile): qkv, rope + cache write, attention, o_proj, norms + residual adds,
+  // gate / up + SiLU, down, head (final norm + LM head), embedding
+  double prof[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
   Pool* pool = nullptr;
-  ~CpuEngine() { delete pool; }
+  void* huge = nullptr;            // the matrices copied out of the file mapping into 2 MB pages (see place_weights)
+  size_t huge_bytes = 0;
+  ~CpuEngine() { delete pool; if (huge != nullptr) munmap(huge, huge_bytes); }
 };
 
 float dot_f32(const float* a, const float* b, int n) {
@@ -178,6 +184,41 @@ void dot4_f32(const float* r0, const float* r1, const float* r2, const float* r3
 #endif
 }
 
+// Four rows against two vectors: a 4 x 2 register tile (eight accumulators, four row loads and two token loads per step) keeps the
+// FMA units busier than the loads.  Every (row, token) sum is accumulated in the order of dot4_f32, so the results are the same bits.
+void dot4x2_f32(const float* r0, const float* r1, const float* r2, const float* r3, const float* xa, const float* xb, int n, float* oa,
+                float* ob) {
+#if defined(__AVX2__)
+  __m256 a0 = _mm256_setzero_ps(), a1 = a0, a2 = a0, a3 = a0, b0 = a0, b1 = a0, b2 = a0, b3 = a0;
+  int i = 0;
+  for (; i + 8 <= n; i += 8) {
+    const __m256 va = _mm256_loadu_ps(xa + i), vb = _mm256_loadu_ps(xb + i);
+    __m256 w = _mm256_loadu_ps(r0 + i);
+    a0 = _mm256_fmadd_ps(w, va, a0); b0 = _mm256_fmadd_ps(w, vb, b0);
+    w = _mm256_loadu_ps(r1 + i);
+    a1 = _mm256_fmadd_ps(w, va, a1); b1 = _mm256_fmadd_ps(w, vb, b1);
+    w = _mm256_loadu_ps(r2 + i);
+    a2 = _mm256_fmadd_ps(w, va, a2); b2 = _mm256_fmadd_ps(w, vb, b2);
+    w = _mm256_loadu_ps(r3 + i);
+    a3 = _mm256_fmadd_ps(w, va, a3); b3 = _mm256_fmadd_ps(w, vb, b3);
+  }
+  const __m256 acc[8] = {a0, a1, a2, a3, b0, b1, b2, b3};
+  const float* rows[4] = {r0, r1, r2, r3};
+  for (int j = 0; j < 8; ++j) {
+    __m128 lo = _mm_add_ps(_mm256_castps256_ps128(acc[j]), _mm256_extractf128_ps(acc[j], 1));
+    lo = _mm_add_ps(lo, _mm_movehl_ps(lo, lo));
+    lo = _mm_add_ss(lo, _mm_shuffle_ps(lo, lo, 1));
+    float sum = _mm_cvtss_f32(lo);
+    const float* x = j < 4 ? xa : xb;
+    for (int k2 = i; k2 < n; ++k2) sum += rows[j & 3][k2] * x[k2];
+    (j < 4 ? oa : ob)[j & 3] = sum;
+  }
+#else
+  dot4_f32(r0, r1, r2, r3, xa, n, oa);
+  dot4_f32(r0, r1, r2, r3, xb, n, ob);
+#endif
+}
+
 // One row of a Q8_0 matrix times an fp32 vector: per 32-block  d * sum(q * x).  Two blocks per iteration (independent FMA
 // chains), the fp16 scales converted by the F16C unit.
 float dot_q8_0(const uint8_t* row, const float* x, int k) {
@@ -217,27 +258,195 @@ float dot_q8_0(const uint8_t* row, const float* x, int k) {
   return total;
 }
 
-// y[t, n] = sum_k W[n, k] x[t, k] for t < T.  Rows are split over the threads; a row is decoded once (into `scratch`, one slice
-// per thread) when there are several tokens or its type has no direct kernel, and streamed straight from its blocks otherwise.
+#if defined(__x86_64__)
+// AVX-512 variants, compiled for their target by attribute and chosen at run time (the library itself is built for AVX2 machines):
+// 16 lanes per instruction halve the instruction count of the two kernels the engine spends its time in.  GB_CPU_AVX512=0 keeps AVX2.
+#define GB_AVX512 __attribute__((target("avx512f,avx512bw,avx512vl,avx512dq,f16c,fma")))
+
+GB_AVX512 float dot_q8_0_avx512(const uint8_t* row, const float* x, int k) {
+  const int nb = k / 32;
+  __m512 acc0 = _mm512_setzero_ps(), acc1 = _mm512_setzero_ps();
+  auto block = [&](const uint8_t* blk, const float* xb, __m512& acc) GB_AVX512 {
+    uint16_t dh; memcpy(&dh, blk, 2);
+    const __m512 d = _mm512_set1_ps(_cvtsh_ss(dh));
+    const __m512 lo = _mm512_cvtepi32_ps(_mm512_cvtepi8_epi32(_mm_loadu_si128((const __m128i*)(blk + 2))));
+    const __m512 hi = _mm512_cvtepi32_ps(_mm512_cvtepi8_epi32(_mm_loadu_si128((const __m128i*)(blk + 18))));
+    __m512 sum = _mm512_mul_ps(lo, _mm512_loadu_ps(xb));
+    sum = _mm512_fmadd_ps(hi, _mm512_loadu_ps(xb + 16), sum);
+    acc = _mm512_fmadd_ps(d, sum, acc);
+  };
+  int b = 0;
+  for (; b + 2 <= nb; b += 2) {
+    block(row + (size_t)b * 34, x + b * 32, acc0);
+    block(row + (size_t)(b + 1) * 34, x + (b + 1) * 32, acc1);
+  }
+  if (b < nb) block(row + (size_t)b * 34, x + b * 32, acc0);
+  return _mm512_reduce_add_ps(_mm512_add_ps(acc0, acc1));
+}
+
+// 4 rows x 4 tokens: sixteen accumulators, four row loads and four token loads per step of 16 features
+GB_AVX512 void dot4x4_f32_avx512(const float* r0, const float* r1, const float* r2, const float* r3, const float* const* xs, int n, float* out) {
+  __m512 a[16];
+  for (int j = 0; j < 16; ++j) a[j] = _mm512_setzero_ps();
+  int i = 0;
+  for (; i + 16 <= n; i += 16) {
+    const __m512 w0 = _mm512_loadu_ps(r0 + i), w1 = _mm512_loadu_ps(r1 + i), w2 = _mm512_loadu_ps(r2 + i), w3 = _mm512_loadu_ps(r3 + i);
+#pragma GCC unroll 4
+    for (int t = 0; t < 4; ++t) {
+      const __m512 xv = _mm512_loadu_ps(xs[t] + i);
+      a[t * 4 + 0] = _mm512_fmadd_ps(w0, xv, a[t * 4 + 0]);
+      a[t * 4 + 1] = _mm512_fmadd_ps(w1, xv, a[t * 4 + 1]);
+      a[t * 4 + 2] = _mm512_fmadd_ps(w2, xv, a[t * 4 + 2]);
+      a[t * 4 + 3] = _mm512_fmadd_ps(w3, xv, a[t * 4 + 3]);
+    }
+  }
+  const float* rows[4] = {r0, r1, r2, r3};
+  for (int t = 0; t < 4; ++t)
+    for (int q = 0; q < 4; ++q) {
+      float sum = _mm512_reduce_add_ps(a[t * 4 + q]);
+      for (int k2 = i; k2 < n; ++k2) sum += rows[q][k2] * xs[t][k2];
+      out[t * 4 + q] = sum;                                   // out[token][row]
+    }
+}
+
+bool use_avx512() {
+  static const bool on = [] {
+    const char* e = getenv("GB_CPU_AVX512");
+    if (e != nullptr && e[0] == '0') return false;
+    return __builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw") && __builtin_cpu_supports("avx512vl") &&
+           __builtin_cpu_supports("avx512dq");
+  }();
+  return on;
+}
+#else
+inline bool use_avx512() { return false; }
+#endif
+
+inline float dot_q8_0_best(const uint8_t* row, const float* x, int k) {
+#if defined(__x86_64__)
+  if (use_avx512()) return dot_q8_0_avx512(row, x, k);
+#endif
+  return dot_q8_0(row, x, k);
+}
+
+// Rows [n0, n1) of y[t, n] = sum_k W[n, k] x[t, k] for t < T.  With several tokens a row is decoded once (four at a time into `row`)
+// and multiplied with the tokens two at a time; a single token streams Q8_0 rows straight from their blocks.
+void matmul_rows(const QMat& w, const float* x, int ldx, int T, float* y, int ldy, const float* bias, int n0, int n1, std::vector<float>& row) {
+  int n = n0;
+  const size_t k = (size_t)w.k;
+  if (T > 1) {
+    if (row.size() < 4 * k) row.resize(4 * k);
+    float* r = row.data();
+    for (; n + 4 <= n1; n += 4) {                            // four decoded rows share every token load
+      for (int q = 0; q < 4; ++q) dequant_row(w.type, w.data + (size_t)(n + q) * w.row_bytes, r + q * k, w.k);
+      const float b4[4] = {bias ? bias[n] : 0.f, bias ? bias[n + 1] : 0.f, bias ? bias[n + 2] : 0.f, bias ? bias[n + 3] : 0.f};
+      int t = 0;
+#if defined(__x86_64__)
+      if (use_avx512())
+        for (; t + 4 <= T; t += 4) {
+          const float* xs[4] = {x + (size_t)t * ldx, x + (size_t)(t + 1) * ldx, x + (size_t)(t + 2) * ldx, x + (size_t)(t + 3) * ldx};
+          float o16[16];
+          dot4x4_f32_avx512(r, r + k, r + 2 * k, r + 3 * k, xs, w.k, o16);
+          for (int tt = 0; tt < 4; ++tt)
+            for (int q = 0; q < 4; ++q) y[(size_t)(t + tt) * ldy + n + q] = o16[tt * 4 + q] + b4[q];
+        }
+#endif
+      for (; t + 2 <= T; t += 2) {
+        float oa[4], ob[4];
+        dot4x2_f32(r, r + k, r + 2 * k, r + 3 * k, x + (size_t)t * ldx, x + (size_t)(t + 1) * ldx, w.k, oa, ob);
+        for (int q = 0; q < 4; ++q) { y[(size_t)t * ldy + n + q] = oa[q] + b4[q]; y[(size_t)(t + 1) * ldy + n + q] = ob[q] + b4[q]; }
+      }
+      if (t < T) {
+        float o4[4];
+        dot4_f32(r, r + k, r + 2 * k, r + 3 * k, x + (size_t)t * ldx, w.k, o4);
+        for (int q = 0; q < 4; ++q) y[(size_t)t * ldy + n + q] = o4[q] + b4[q];
+      }
+    }
+  }
+  for (; n < n1; ++n) {
+    const uint8_t* src = w.data + (size_t)n * w.row_bytes;
+    const float b = bias ? bias[n] : 0.f;
+    if (T == 1 && w.type == T_Q8_0) { y[n] = dot_q8_0_best(src, x, w.k) + b; continue; }
+    if (row.size() < k) row.resize(k);
+    dequant_row(w.type, src, row.data(), w.k);
+    for (int t = 0; t < T; ++t) y[(size_t)t * ldy + n] = dot_f32(row.data(), x + (size_t)t * ldx, w.k) + b;
+  }
+}
+
+// Several projections of the same input (q / k / v) as ONE job of the pool: their rows are laid end to end and split over the
+// threads, so a decode step pays one wake-up and one join instead of three.
+struct MatJob { const QMat* w; float* y; int ldy; const float* bias; };
+
+void matmul_multi(const CpuEngine& e, const MatJob* jobs, int n_jobs, const float* x, int ldx, int T) {
+  int total = 0;
+  for (int j = 0; j < n_jobs; ++j) total += jobs[j].w->rows;
+  e.pool->run(total, [&](int g0, int g1) {
+    std::vector<float> row;
+    int base = 0;
+    for (int j = 0; j < n_jobs; ++j) {
+      const int rows = jobs[j].w->rows;
+      const int lo = std::max(g0, base) - base, hi = std::min(g1, base + rows) - base;
+      if (hi > lo) matmul_rows(*jobs[j].w, x, ldx, T, jobs[j].y, jobs[j].ldy, jobs[j].bias, lo, hi, row);
+      base += rows;
+    }
+  });
+}
+
 void matmul(const CpuEngine& e, const QMat& w, const float* x, int ldx, int T, float* y, int ldy, const float* bias = nullptr) {
-  e.pool->run(w.rows, [&](int n0, int n1) {
-    std::vector<float> row((size_t)w.k * 4);
+  const MatJob j{&w, y, ldy, bias};
+  matmul_multi(e, &j, 1, x, ldx, T);
+}
+
+// g[t, n] = SiLU(gate[n] . x[t]) * (up[n] . x[t]): the two FFN input projections and the activation as one job (a thread computes
+// both sums of an output feature, so nothing is written in between).
+void ffn_gate_up_silu(const CpuEngine& e, const QMat& wg, const QMat& wu, const float* x, int ldx, int T, float* g, int ldg) {
+  e.pool->run(wg.rows, [&](int n0, int n1) {
+    const size_t k = (size_t)wg.k;
+    std::vector<float> rg, ru;
+    auto act = [](float a, float b) { return a / (1.0f + expf(-a)) * b; };
     int n = n0;
-    if (T > 1)
-      for (; n + 4 <= n1; n += 4) {                          // four decoded rows share every token load
-        for (int r = 0; r < 4; ++r) dequant_row(w.type, w.data + (size_t)(n + r) * w.row_bytes, row.data() + (size_t)r * w.k, w.k);
-        for (int t = 0; t < T; ++t) {
-          float o4[4];
-          dot4_f32(row.data(), row.data() + w.k, row.data() + 2 * (size_t)w.k, row.data() + 3 * (size_t)w.k, x + (size_t)t * ldx, w.k, o4);
-          for (int r = 0; r < 4; ++r) y[(size_t)t * ldy + n + r] = o4[r] + (bias ? bias[n + r] : 0.f);
+    if (T > 1) {
+      rg.resize(4 * k); ru.resize(4 * k);
+      for (; n + 4 <= n1; n += 4) {
+        for (int q = 0; q < 4; ++q) {
+          dequant_row(wg.type, wg.data + (size_t)(n + q) * wg.row_bytes, rg.data() + q * k, wg.k);
+          dequant_row(wu.type, wu.data + (size_t)(n + q) * wu.row_bytes, ru.data() + q * k, wu.k);
+        }
+        int t = 0;
+#if defined(__x86_64__)
+        if (use_avx512())
+          for (; t + 4 <= T; t += 4) {
+            const float* xs[4] = {x + (size_t)t * ldx, x + (size_t)(t + 1) * ldx, x + (size_t)(t + 2) * ldx, x + (size_t)(t + 3) * ldx};
+            float g16[16], u16[16];
+            dot4x4_f32_avx512(rg.data(), rg.data() + k, rg.data() + 2 * k, rg.data() + 3 * k, xs, wg.k, g16);
+            dot4x4_f32_avx512(ru.data(), ru.data() + k, ru.data() + 2 * k, ru.data() + 3 * k, xs, wu.k, u16);
+            for (int tt = 0; tt < 4; ++tt)
+              for (int q = 0; q < 4; ++q) g[(size_t)(t + tt) * ldg + n + q] = act(g16[tt * 4 + q], u16[tt * 4 + q]);
+          }
+#endif
+        for (; t + 2 <= T; t += 2) {
+          float ga[4], gb[4], ua[4], ub[4];
+          const float* xa = x + (size_t)t * ldx; const float* xb = x + (size_t)(t + 1) * ldx;
+          dot4x2_f32(rg.data(), rg.data() + k, rg.data() + 2 * k, rg.data() + 3 * k, xa, xb, wg.k, ga, gb);
+          dot4x2_f32(ru.data(), ru.data() + k, ru.data() + 2 * k, ru.data() + 3 * k, xa, xb, wu.k, ua, ub);
+          for (int q = 0; q < 4; ++q) { g[(size_t)t * ldg + n + q] = act(ga[q], ua[q]); g[(size_t)(t + 1) * ldg + n + q] = act(gb[q], ub[q]); }
+        }
+        if (t < T) {
+          float g4[4], u4[4];
+          dot4_f32(rg.data(), rg.data() + k, rg.data() + 2 * k, rg.data() + 3 * k, x + (size_t)t * ldx, wg.k, g4);
+          dot4_f32(ru.data(), ru.data() + k, ru.data() + 2 * k, ru.data() + 3 * k, x + (size_t)t * ldx, wu.k, u4);
+          for (int q = 0; q < 4; ++q) g[(size_t)t * ldg + n + q] = act(g4[q], u4[q]);
         }
       }
+    }
     for (; n < n1; ++n) {
-      const uint8_t* src = w.data + (size_t)n * w.row_bytes;
-      const float b = bias ? bias[n] : 0.f;
-      if (T == 1 && w.type == T_Q8_0) { y[n] = dot_q8_0(src, x, w.k) + b; continue; }
-      dequant_row(w.type, src, row.data(), w.k);
-      for (int t = 0; t < T; ++t) y[(size_t)t * ldy + n] = dot_f32(row.data(), x + (size_t)t * ldx, w.k) + b;
+      const uint8_t* sg = wg.data + (size_t)n * wg.row_bytes;
+      const uint8_t* su = wu.data + (size_t)n * wu.row_bytes;
+      if (T == 1 && wg.type == T_Q8_0 && wu.type == T_Q8_0) { g[n] = act(dot_q8_0_best(sg, x, wg.k), dot_q8_0_best(su, x, wu.k)); continue; }
+      if (rg.size() < k) { rg.resize(k); ru.resize(k); }
+      dequant_row(wg.type, sg, rg.data(), wg.k);
+      dequant_row(wu.type, su, ru.data(), wu.k);
+      for (int t = 0; t < T; ++t) g[(size_t)t * ldg + n] = act(dot_f32(rg.data(), x + (size_t)t * ldx, wg.k), dot_f32(ru.data(), x + (size_t)t * ldx, wu.k));
     }
   });
 }
@@ -291,22 +500,31 @@ double kv_num(void* g, const std::string& key, double dflt) {
 }
 
 // Layers + final norm over T tokens at positions pos0 .. pos0 + T - 1 (rows of x, [T, hidden], updated in place).
+struct Phase {                        // adds its lifetime to one slot of the profile
+  double* slot;
+  std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
+  explicit Phase(double* s) : slot(s) {}
+  ~Phase() { *slot += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); }
+};
+
 void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
   const int H = e.hidden, D = e.head_dim, QD = e.n_heads * D, KD = e.n_kv * D, F = e.ffn;
   std::vector<float> h((size_t)T * H), q((size_t)T * QD), k((size_t)T * KD), v((size_t)T * KD), att((size_t)T * QD), o((size_t)T * H);
-  std::vector<float> g((size_t)T * F), u((size_t)T * F);
+  std::vector<float> g((size_t)T * F);
   const float scale = 1.0f / sqrtf((float)D);
   const int group = e.n_heads / e.n_kv;
   for (int li = 0; li < e.n_layers; ++li) {
     const Layer& L = e.layers[li];
     float* kc = e.kc.data() + (size_t)li * e.max_seq * KD;
     float* vc = e.vc.data() + (size_t)li * e.max_seq * KD;
+    { Phase ph(&e.prof[4]);
     e.pool->run(T, [&](int t0, int t1) {
       for (int t = t0; t < t1; ++t) rmsnorm(x + (size_t)t * H, L.attn_norm.data(), h.data() + (size_t)t * H, H, e.eps);
-    });
-    matmul(e, L.wq, h.data(), H, T, q.data(), QD, e.has_bias ? L.bq.data() : nullptr);
-    matmul(e, L.wk, h.data(), H, T, k.data(), KD, e.has_bias ? L.bk.data() : nullptr);
-    matmul(e, L.wv, h.data(), H, T, v.data(), KD, e.has_bias ? L.bv.data() : nullptr);
+    }); }
+    const MatJob qkv[3] = {{&L.wq, q.data(), QD, e.has_bias ? L.bq.data() : nullptr}, {&L.wk, k.data(), KD, e.has_bias ? L.bk.data() : nullptr},
+                           {&L.wv, v.data(), KD, e.has_bias ? L.bv.data() : nullptr}};
+    { Phase ph(&e.prof[0]); matmul_multi(e, qkv, 3, h.data(), H, T); }
+    { Phase ph(&e.prof[1]);
     e.pool->run(T, [&](int t0, int t1) {
     for (int t = t0; t < t1; ++t) {
       const int pos = pos0 + t;
@@ -323,8 +541,9 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
       memcpy(kc + (size_t)pos * KD, k.data() + (size_t)t * KD, sizeof(float) * KD);
       memcpy(vc + (size_t)pos * KD, v.data() + (size_t)t * KD, sizeof(float) * KD);
     }
-    });
+    }); }
     // causal attention: token t sees positions 0 .. pos0 + t
+    { Phase ph(&e.prof[2]);
     e.pool->run(T * e.n_heads, [&](int i0, int i1) {
       std::vector<float> sc((size_t)pos0 + T);
       for (int idx = i0; idx < i1; ++idx) {
@@ -345,8 +564,9 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
           for (int d = 0; d < D; ++d) out[d] += w * vh[d];
         }
       }
-    });
-    matmul(e, L.wo, att.data(), QD, T, o.data(), H);
+    }); }
+    { Phase ph(&e.prof[3]); matmul(e, L.wo, att.data(), QD, T, o.data(), H); }
+    { Phase ph(&e.prof[4]);
     e.pool->run(T, [&](int t0, int t1) {
       for (int t = t0; t < t1; ++t) {
         float* xr = x + (size_t)t * H;
@@ -354,18 +574,10 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
         for (int i = 0; i < H; ++i) xr[i] += orow[i];
         rmsnorm(xr, L.ffn_norm.data(), h.data() + (size_t)t * H, H, e.eps);
       }
-    });
-    matmul(e, L.wgate, h.data(), H, T, g.data(), F);
-    matmul(e, L.wup, h.data(), H, T, u.data(), F);
-    e.pool->run(T * 8, [&](int c0, int c1) {               // (token, eighth of the FFN width) items: a single token still spreads
-      for (int c = c0; c < c1; ++c) {
-        const int t = c / 8, part = c % 8;
-        float* gr = g.data() + (size_t)t * F;
-        const float* ur = u.data() + (size_t)t * F;
-        for (int i = (int)((long)F * part / 8); i < (int)((long)F * (part + 1) / 8); ++i) gr[i] = gr[i] / (1.0f + expf(-gr[i])) * ur[i];
-      }
-    });
-    matmul(e, L.wdown, g.data(), F, T, o.data(), H);
+    }); }
+    { Phase ph(&e.prof[5]); ffn_gate_up_silu(e, L.wgate, L.wup, h.data(), H, T, g.data(), F); }
+    { Phase ph(&e.prof[6]); matmul(e, L.wdown, g.data(), F, T, o.data(), H); }
+    Phase ph_res(&e.prof[4]);
     for (int t = 0; t < T; ++t) {
       float* xr = x + (size_t)t * H;
       const float* orow = o.data() + (size_t)t * H;
@@ -383,6 +595,7 @@ void embed_rows(const CpuEngine& e, const int* tokens, int T, float* x) {
 }
 
 void logits_of(CpuEngine& e, const float* xrow, float* logits) {
+  Phase ph(&e.prof[7]);
   std::vector<float> hn((size_t)e.hidden);
   rmsnorm(xrow, e.final_norm.data(), hn.data(), e.hidden, e.eps);
   matmul(e, e.head, hn.data(), e.hidden, 1, logits, e.vocab);
@@ -400,6 +613,40 @@ int argmax(const float* v, int n) {
 using namespace gbh;
 
 // Open a GGUF checkpoint of a dense qwen2 / qwen3 model for CPU inference.  threads <= 0: all cores.  NULL on error.
+// A decode step streams every matrix once; out of the file mapping that is one TLB miss per 4 KB.  Copy the matrices into one
+// anonymous region the kernel may back with 2 MB pages (the reference does the same at load: MADV_HUGEPAGE or a 2 MB-aligned
+// buffer, common/gguf_loader.h).  Every thread copies, and so first touches, a slice of every matrix.  GB_CPU_HUGEPAGES=0 keeps the mapping.
+void place_weights(CpuEngine& e) {
+  const char* env = getenv("GB_CPU_HUGEPAGES");
+  if (env != nullptr && env[0] == '0') return;
+  std::vector<QMat*> mats;
+  mats.push_back(&e.embed);
+  const bool tied = e.head.data == e.embed.data;
+  if (!tied) mats.push_back(&e.head);
+  for (Layer& L : e.layers)
+    for (QMat* m : {&L.wq, &L.wk, &L.wv, &L.wo, &L.wgate, &L.wup, &L.wdown}) mats.push_back(m);
+  size_t total = 0;
+  std::vector<size_t> off;
+  for (QMat* m : mats) { off.push_back(total); total += ((size_t)m->rows * m->row_bytes + 4095) & ~(size_t)4095; }
+  const size_t two_mb = (size_t)2 << 20;
+  total = (total + two_mb - 1) & ~(two_mb - 1);
+  void* p = mmap(nullptr, total, PROT_READ | PROT_WRITE, MAP_PRIVATE | MAP_ANONYMOUS, -1, 0);
+  if (p == MAP_FAILED) return;                                  // not enough memory for a second copy: run from the file mapping
+#ifdef MADV_HUGEPAGE
+  madvise(p, total, MADV_HUGEPAGE);
+#endif
+  for (size_t i = 0; i < mats.size(); ++i) {
+    QMat* m = mats[i];
+    uint8_t* dst = (uint8_t*)p + off[i];
+    const uint8_t* src = m->data;
+    const long rb = m->row_bytes;
+    e.pool->run(m->rows, [&](int r0, int r1) { memcpy(dst + (size_t)r0 * rb, src + (size_t)r0 * rb, (size_t)(r1 - r0) * rb); });
+    m->data = dst;
+  }
+  if (tied) e.head = e.embed;
+  e.huge = p; e.huge_bytes = total;
+}
+
 GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
   void* g = gbh_gguf_open(path);
   if (g == nullptr) return nullptr;
@@ -451,6 +698,7 @@ GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
   for (int j = 0; j < D / 2; ++j) e->inv_freq[j] = powf(e->theta, -2.0f * (float)j / (float)D);
   const size_t kvn = (size_t)e->n_layers * e->max_seq * e->n_kv * D;
   e->kc.assign(kvn, 0.f); e->vc.assign(kvn, 0.f);
+  place_weights(*e);
   return e;
 }
 
@@ -473,6 +721,14 @@ GBH_API int gbh_cpu_engine_forward(void* h, const int* tokens, int n, int pos0, 
   forward_hidden(*e, x.data(), n, pos0);
   if (logits != nullptr) logits_of(*e, x.data() + (size_t)(n - 1) * e->hidden, logits);
   return 0;
+}
+
+// Seconds per phase since the engine was loaded or since the last call with reset != 0 (nine slots: qkv, rope + cache, attention, o_proj,
+// norms + residuals, gate / up + SiLU, down, head, unused).  The counterpart of the reference's per-op tables (common/profiler.h).
+GBH_API int gbh_cpu_engine_profile(void* h, double* out, int reset) {
+  auto* e = (CpuEngine*)h;
+  for (int i = 0; i < 9; ++i) { if (out) out[i] = e->prof[i]; if (reset) e->prof[i] = 0; }
+  return 9;
 }
 
 // Greedy generation: batched prefill of the prompt, then max_new - 1 single-token steps.  Writes max_new token ids and the

@@ -21,6 +21,7 @@ def _lib():
         lib.gbh_cpu_engine_free.argtypes = [ctypes.c_void_p]
         lib.gbh_cpu_engine_vocab.argtypes = [ctypes.c_void_p]
         lib.gbh_cpu_engine_threads.argtypes = [ctypes.c_void_p]
+        lib.gbh_cpu_engine_profile.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
         lib.gbh_cpu_engine_forward.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
         lib.gbh_cpu_engine_generate.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
                                                 ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)]
@@ -43,6 +44,15 @@ class CpuEngine:
         if _lib().gbh_cpu_engine_forward(self._h, ids.ctypes.data, len(ids), pos0, out.ctypes.data) != 0:
             raise RuntimeError(_lib().gbh_last_error().decode(errors="replace"))
         return out
+
+    PHASES = ("qkv", "rope_cache", "attention", "o_proj", "norm_residual", "gate_up_silu", "down", "head")
+
+    def profile(self, reset: bool = True) -> dict:
+        """Seconds per phase since the engine was loaded or since the last reset (the reference prints such tables from
+        common/profiler.h)."""
+        buf = (ctypes.c_double * 9)()
+        _lib().gbh_cpu_engine_profile(self._h, buf, 1 if reset else 0)
+        return {k: float(buf[i]) for i, k in enumerate(self.PHASES)}
 
     def generate(self, prompt: Sequence[int], max_new_tokens: int) -> Tuple[List[int], float, float]:
         """Greedy generation.  Returns ``(tokens, prefill seconds, decode seconds)``."""

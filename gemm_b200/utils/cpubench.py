@@ -108,6 +108,8 @@ def main(argv=None) -> int:
     ap.add_argument("--threads", type=int, default=os.cpu_count() or 1)
     ap.add_argument("--gguf", default="", help="checkpoint to use (default: write the synthetic one to a temporary file)")
     ap.add_argument("--reference-root", default=os.environ.get("GEMM_REFERENCE_ROOT", ""), help="source tree of the reference project (optional)")
+    ap.add_argument("--repeat", type=int, default=3, help="runs per arm, alternating; the fastest prefill and the fastest decode of each arm are "
+                    "reported (other jobs on the machine only ever slow a run down)")
     args = ap.parse_args(argv)
     from ..models.config import get_config
     cfg = get_config(args.model)
@@ -122,12 +124,20 @@ def main(argv=None) -> int:
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist()
     toks, tp, td = run_ours(path, prompt, args.new, args.threads)
+    ref = run_reference(args.reference_root, path, prompt, args.new, args.threads) if args.reference_root else None
+    for _ in range(max(0, args.repeat - 1)):
+        t2, p2, d2 = run_ours(path, prompt, args.new, args.threads)
+        assert t2 == toks, "the engine is not deterministic"
+        tp, td = min(tp, p2), min(td, d2)
+        if ref is not None:
+            r2 = run_reference(args.reference_root, path, prompt, args.new, args.threads)
+            ref = (ref[0], min(ref[1], r2[1]), min(ref[2], r2[2]))
     n_tok = args.prompt_len + args.new
     line = {"config": {"model": args.model, "wtype": args.wtype, "prompt_len": args.prompt_len, "new_tokens": args.new, "threads": args.threads},
             "ours": {"prefill_s": round(tp, 4), "decode_s": round(td, 4), "total_s": round(tp + td, 4), "prefill_tok_s": round(args.prompt_len / tp, 2),
                      "decode_tok_s": round((args.new - 1) / td, 2) if td > 0 else None, "tok_s_overall": round(n_tok / (tp + td), 2)}}
+    line["config"]["repeat"] = args.repeat
     if args.reference_root:
-        ref = run_reference(args.reference_root, path, prompt, args.new, args.threads)
         if ref is not None:
             rt, rp, rd = ref
             line["reference"] = {"prefill_s": round(rp, 4), "decode_s": round(rd, 4), "total_s": round(rp + rd, 4), "prefill_tok_s": round(args.prompt_len / rp, 2),
