@@ -60,3 +60,35 @@ def test_load_errors_are_reported(tmp_path):
     eng = CpuEngine(eng_path, max_seq_len=8)
     with pytest.raises(RuntimeError, match="cache"):
         eng.forward(list(range(9)), 0)
+
+
+def test_profile_covers_the_forward_pass(tmp_path):
+    cfg = get_config("tiny-dense")
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=3), path, "Q8_0")
+    eng = CpuEngine(path, max_seq_len=64, threads=2)
+    eng.profile()                                               # reset
+    eng.forward(list(range(1, 17)), 0)
+    prof = eng.profile()
+    assert set(prof) == set(CpuEngine.PHASES) and all(v >= 0.0 for v in prof.values())
+    assert prof["qkv"] > 0.0 and prof["down"] > 0.0 and prof["head"] > 0.0
+    assert sum(eng.profile().values()) == 0.0                  # the call above reset the counters
+
+
+def test_portable_paths_give_the_same_logits(tmp_path):
+    """The AVX2 tiles on pageable weights (both switches off) against whatever this CPU selects by default."""
+    import os
+    import subprocess
+    import sys
+    cfg = get_config("tiny-dense")
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=5), path, "Q8_0")
+    toks = list(range(3, 22))
+    here = CpuEngine(path, max_seq_len=64, threads=2).forward(toks, 0)
+    out = str(tmp_path / "logits.npy")
+    code = ("import numpy as np; from gemm_b200.serve.cpu_engine import CpuEngine; "
+            f"np.save({out!r}, CpuEngine({path!r}, max_seq_len=64, threads=2).forward({toks!r}, 0))")
+    env = dict(os.environ, GB_CPU_AVX512="0", GB_CPU_HUGEPAGES="0")
+    subprocess.run([sys.executable, "-c", code], check=True, env=env, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    there = np.load(out)
+    assert np.abs(here - there).max() < 1e-3 * max(1.0, np.abs(here).max())
