@@ -168,6 +168,27 @@ def cmd_encode_image(args):
     return 0
 
 
+def cmd_encode_audio(args):
+    """WAV -> log-mel -> Conformer soft tokens (the audio path of the reference's Gemma4 driver, cuda/llm/test_gemma4_st.c:83-104:
+    the clip is cut to ``--max-seconds`` first, 30 s being what the model was trained on)."""
+    import numpy as np
+    import torch
+    from .models import audio
+    pcm, rate = audio.wav_load(args.wav)
+    if rate != audio.RATE:
+        sys.exit(f"{args.wav}: {rate} Hz; the encoder takes {audio.RATE} Hz mono (resample beforehand)")
+    if args.max_seconds > 0:
+        pcm = pcm[: int(args.max_seconds * audio.RATE)]
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    enc = audio.Gemma4AudioEncoder.from_checkpoint(args.model, device=dev, dtype=torch.bfloat16 if dev == "cuda" else torch.float32)
+    mel = audio.log_mel(pcm)
+    soft = enc.encode(mel)
+    if args.out:
+        np.save(args.out, soft.float().cpu().numpy())
+    print(json.dumps({"seconds": round(pcm.numel() / audio.RATE, 3), "mel_frames": mel.shape[0], "tokens": soft.shape[0], "features_per_token": soft.shape[1]}))
+    return 0
+
+
 def cmd_inspect(args):
     from .utils import gguf as G
     with G.GGUFFile(args.file) as f:
@@ -379,6 +400,12 @@ def main(argv=None):
     ei.add_argument("--image", required=True, help=".npy (uint8 [H, W, 3]) or binary PPM (P6)")
     ei.add_argument("--out", default="", help="write the features ([tokens, proj_dim * (1 + deepstack)] f32) as .npy")
     ei.set_defaults(fn=cmd_encode_image)
+    ea = sub.add_parser("encode-audio", help="run the Gemma4 audio encoder (safetensors checkpoint) on a 16 kHz WAV file")
+    ea.add_argument("--model", required=True, help="checkpoint directory or .safetensors file holding model.audio_tower.*")
+    ea.add_argument("--wav", required=True)
+    ea.add_argument("--max-seconds", type=float, default=30.0, help="cut the clip (0: keep all of it)")
+    ea.add_argument("--out", default="", help="write the soft tokens ([tokens, 1536] f32) as .npy")
+    ea.set_defaults(fn=cmd_encode_audio)
     b = sub.add_parser("build", help="compile the native libraries")
     b.set_defaults(fn=cmd_build)
     args = ap.parse_args(argv)

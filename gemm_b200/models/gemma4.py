@@ -279,9 +279,12 @@ class Gemma4Model:
 
     # ------------------------------------------------------------------------------------------ forward
     @torch.no_grad()
-    def forward(self, ids: torch.Tensor, all_logits: bool = False) -> torch.Tensor:
+    def forward(self, ids: torch.Tensor, all_logits: bool = False, embeds: Optional[torch.Tensor] = None,
+                embeds_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``ids`` int [B, T]: the next T tokens of every sequence.  Returns f32 logits [B, V] of the last token (``all_logits``:
-        [B, T, V]) and advances the position."""
+        [B, T, V]) and advances the position.  Where ``embeds_mask`` [B, T] is set, row ``embeds[b, t]`` ([B, T, hidden], soft tokens
+        of the vision or audio encoder) enters the stack unscaled in place of the token's embedding, and the per-layer embedding
+        is the one of token 0 (common/transformer.h:4317-4332)."""
         cfg, tt = self.cfg, self.t
         ids = ids.to(self.device).long()
         b, t = ids.shape
@@ -291,6 +294,10 @@ class Gemma4Model:
         positions = torch.arange(p0, p0 + t, device=self.device)
         eps, h, L = cfg.rms_eps, cfg.hidden, cfg.n_layers
         x = tt["token_embd.weight"][ids].to(self.dtype) * math.sqrt(h)
+        if embeds is not None:
+            mask = torch.ones(b, t, dtype=torch.bool, device=self.device) if embeds_mask is None else embeds_mask.to(self.device).bool()
+            x = torch.where(mask[..., None], embeds.to(self.device, self.dtype), x)
+            ids = ids.masked_fill(mask, 0)
         ple = None
         if self.has_ple:
             tok = tt["per_layer_token_embd.weight"][ids].float() * math.sqrt(cfg.ple_dim)               # [B, T, L * ple]
@@ -337,18 +344,30 @@ class Gemma4Model:
         return logits if all_logits else logits[:, 0]
 
     @torch.no_grad()
-    def prefill(self, ids: torch.Tensor, chunk: int = 2048) -> torch.Tensor:
+    def prefill(self, ids: torch.Tensor, chunk: int = 2048, embeds: Optional[torch.Tensor] = None,
+                embeds_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run a prompt ``[B, T]`` in chunks (the score matrix of a chunk is materialised); returns the logits of the last token."""
         out = None
         for i in range(0, ids.shape[1], chunk):
-            out = self.forward(ids[:, i: i + chunk])
+            e = None if embeds is None else embeds[:, i: i + chunk]
+            m = None if embeds_mask is None else embeds_mask[:, i: i + chunk]
+            out = self.forward(ids[:, i: i + chunk], embeds=e, embeds_mask=m)
         return out
 
     @torch.no_grad()
-    def generate(self, prompt: Sequence[int], max_new_tokens: int = 16) -> List[int]:
-        """Greedy continuation of one prompt."""
-        self.reset(1, len(prompt) + max_new_tokens + 1)
-        logits = self.prefill(torch.tensor([list(prompt)]))
+    def generate(self, prompt: Sequence[int], max_new_tokens: int = 16, soft: Optional[torch.Tensor] = None, soft_at: int = 0) -> List[int]:
+        """Greedy continuation of one prompt.  ``soft`` [n, hidden]: encoder rows spliced in front of prompt token ``soft_at`` (the
+        reference's multimodal prompt: text, the image or audio rows, text; cuda/llm/test_gemma4_st.c:150-156)."""
+        ids, embeds, mask = list(prompt), None, None
+        if soft is not None and soft.shape[0] > 0:
+            n = soft.shape[0]
+            ids = ids[:soft_at] + [0] * n + ids[soft_at:]
+            embeds = torch.zeros(1, len(ids), self.cfg.hidden, dtype=torch.float32)
+            embeds[0, soft_at: soft_at + n] = soft.float().cpu()
+            mask = torch.zeros(1, len(ids), dtype=torch.bool)
+            mask[0, soft_at: soft_at + n] = True
+        self.reset(1, len(ids) + max_new_tokens + 1)
+        logits = self.prefill(torch.tensor([ids]), embeds=embeds, embeds_mask=mask)
         out = []
         for _ in range(max_new_tokens):
             out.append(int(logits[0].argmax()))

@@ -22,6 +22,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import torch
+import torch.nn.functional as F
 
 from ..utils import gguf as G
 
@@ -270,10 +271,15 @@ class Gemma4VisionConfig:
     ln_eps: float = 1e-6
     n_pos: int = 64                   # rows of each of the two position tables (x and y)
     rope_theta: float = 100.0
+    projector: str = ""               # "gemma4uv": the block-free variant, one token per (patch_size * pool)-pixel square
 
     @property
     def head_dim(self) -> int:
         return self.dim // self.n_heads
+
+    @property
+    def unified(self) -> bool:
+        return self.projector == "gemma4uv"
 
 
 class Gemma4VisionEncoder:
@@ -282,7 +288,11 @@ class Gemma4VisionEncoder:
     -> per-head RMSNorm of q and k -> 2-D RoPE (first half of a head turns with x, second half with y, pairs ``(j, j + D/4)``
     inside a half, theta 100) -> attention WITHOUT a score scale -> output projection -> post-norm -> residual, then RMSNorm ->
     GELU(gate) * up -> down -> post-norm -> residual; ``pool x pool`` average pooling; times sqrt(dim); ``mm.input_projection``;
-    weightless RMSNorm.  The "gemma4uv" projector variant of the same header (no transformer blocks) is not built."""
+    weightless RMSNorm.
+
+    The "gemma4uv" projector of the same files (common/gemma4_vision_encoder.h:936-1166) has no transformer blocks: squares of
+    ``patch_size * pool`` pixels -> LayerNorm over the square's values -> patch matrix + bias -> LayerNorm -> x and y position rows
+    added -> LayerNorm -> weightless RMSNorm -> ``mm.input_projection``; one token per square."""
 
     def __init__(self, cfg: Gemma4VisionConfig, tensors: Dict[str, torch.Tensor], device="cpu", dtype=torch.float32):
         self.cfg, self.t, self.device, self.dtype = cfg, tensors, torch.device(device), dtype
@@ -294,6 +304,12 @@ class Gemma4VisionEncoder:
         nw = lambda n: 1.0 + 0.1 * torch.randn(n, generator=g)
         d, ps = cfg.dim, cfg.patch_size
         t = {"v.patch_embd.weight": rn(d, 3, ps, ps), "v.position_embd.weight": rn(2, cfg.n_pos, d), "mm.input_projection.weight": rn(cfg.proj_dim, d)}
+        if cfg.unified:
+            pd = 3 * (ps * cfg.pool) ** 2
+            t["v.patch_embd.weight"], t["v.patch_embd.bias"] = rn(d, pd), rn(d)
+            for i, n in ((1, pd), (2, d), (3, d)):
+                t[f"v.patch_norm.{i}.weight"], t[f"v.patch_norm.{i}.bias"] = nw(n), rn(n)
+            return t
         for b in range(cfg.n_blocks):
             p = f"v.blk.{b}."
             t.update({p + "attn_q.weight": rn(d, d), p + "attn_k.weight": rn(d, d), p + "attn_v.weight": rn(d, d), p + "attn_out.weight": rn(d, d),
@@ -310,6 +326,8 @@ class Gemma4VisionEncoder:
                        ("feed_forward_length", cfg.ffn), ("patch_size", cfg.patch_size), ("image_size", cfg.image_size), ("projection_dim", cfg.proj_dim)):
             w.add_u32("clip.vision." + key, v)
         w.add_f32("clip.vision.attention.layer_norm_epsilon", cfg.ln_eps)
+        if cfg.projector:
+            w.add_string("clip.vision.projector_type", cfg.projector)
         for name, x in tensors.items():
             w.add_tensor(name, x.float(), "F32" if x.dim() == 1 else wtype)
         w.write(path)
@@ -318,8 +336,6 @@ class Gemma4VisionEncoder:
     def load_gguf(path: str, device="cpu", dtype=torch.float32) -> "Gemma4VisionEncoder":
         with G.GGUFFile(path) as f:
             m = f.metadata
-            if m.get("clip.vision.projector_type") == "gemma4uv":
-                raise NotImplementedError("the gemma4uv projector (no transformer blocks) is not built")
             k = lambda name, d: m.get("clip.vision." + name, d)
             t = {}
             for name, gt in f.tensors.items():
@@ -328,8 +344,30 @@ class Gemma4VisionEncoder:
             cfg = Gemma4VisionConfig(n_blocks=int(k("block_count", 16)), dim=int(k("embedding_length", 768)), n_heads=int(k("attention.head_count", 12)),
                                      ffn=int(k("feed_forward_length", 3072)), patch_size=int(k("patch_size", 16)), image_size=int(k("image_size", 224)),
                                      proj_dim=int(k("projection_dim", 2560)), ln_eps=float(k("attention.layer_norm_epsilon", 1e-6)),
-                                     n_pos=int(t["v.position_embd.weight"].shape[1]))
+                                     n_pos=int(t["v.position_embd.weight"].shape[1]),
+                                     projector="gemma4uv" if k("projector_type", "") == "gemma4uv" else "")
         return Gemma4VisionEncoder(cfg, t, device, dtype)
+
+    def _ln(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        return F.layer_norm(x.float(), x.shape[-1:], self.t[name + ".weight"].float(), self.t[name + ".bias"].float(), self.cfg.ln_eps).to(x.dtype)
+
+    def _encode_unified(self, rgb: torch.Tensor) -> torch.Tensor:
+        cfg, t = self.cfg, self.t
+        ps = cfg.patch_size * cfg.pool
+        gh, gw = rgb.shape[0] // ps, rgb.shape[1] // ps
+        if max(gh, gw) > cfg.n_pos or gh * gw == 0:
+            raise ValueError("image smaller than one square of the projector or larger than its position tables")
+        img = (rgb.to(self.device).float() / 255.0 * 2.0 - 1.0)[: gh * ps, : gw * ps]
+        sq = img.reshape(gh, ps, gw, ps, 3).permute(0, 2, 4, 1, 3).reshape(gh * gw, 3 * ps * ps)        # channel, row, column inside a square
+        x = self._ln(sq, "v.patch_norm.1").to(self.dtype) @ t["v.patch_embd.weight"].reshape(cfg.dim, -1).t()
+        if "v.patch_embd.bias" in t:
+            x = x + t["v.patch_embd.bias"].to(x.dtype)
+        x = self._ln(x, "v.patch_norm.2")
+        py = torch.arange(gh, device=self.device).repeat_interleave(gw)
+        px = torch.arange(gw, device=self.device).repeat(gh)
+        pos = t["v.position_embd.weight"]
+        x = self._ln(x + pos[0][px].to(x.dtype) + pos[1][py].to(x.dtype), "v.patch_norm.3")
+        return (self._rms(x, None) @ t["mm.input_projection.weight"].t()).float()
 
     def _rms(self, x: torch.Tensor, w: Optional[torch.Tensor]) -> torch.Tensor:
         xf = x.float()
@@ -352,6 +390,8 @@ class Gemma4VisionEncoder:
     def encode(self, rgb: torch.Tensor) -> torch.Tensor:
         """uint8 ``[H, W, 3]`` (H, W multiples of patch_size * pool) -> f32 ``[tokens, proj_dim]``."""
         cfg, t = self.cfg, self.t
+        if cfg.unified:
+            return self._encode_unified(rgb)
         ps, d, nh, hd = cfg.patch_size, cfg.dim, cfg.n_heads, cfg.head_dim
         hgt, wid, _ = rgb.shape
         gh, gw = hgt // ps, wid // ps

@@ -66,6 +66,8 @@ def engine_lib():
     lib.transformer_forward_logits.restype = ctypes.POINTER(ctypes.c_float)
     lib.transformer_forward_logits.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int]
     lib.transformer_set_f64_accum.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.transformer_forward_embd_logits.restype = ctypes.POINTER(ctypes.c_float)
+    lib.transformer_forward_embd_logits.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
     lib.ref_n_vocab.argtypes = [ctypes.c_void_p]
     return lib
 
@@ -230,4 +232,17 @@ def audio_mel_lib():
     lib.g4a_mel_extract.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
     lib.g4a_wav_load.restype = ctypes.POINTER(ctypes.c_float)
     lib.g4a_wav_load.argtypes = [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int)]
+    return lib
+
+
+def audio_encoder_lib():
+    """ctypes handle exposing the reference's Gemma4 audio Conformer (g4a_load_safetensors, g4a_encode, g4a_free)."""
+    lib = _build("ref_g4a_enc", '#define SAFETENSORS_IMPLEMENTATION\n#include "safetensors.h"\n#define GEMMA4_AUDIO_IMPLEMENTATION\n'
+                 '#include "gemma4_audio_encoder.h"\nvoid ref_free(void *p) { free(p); }\n')
+    lib.g4a_load_safetensors.restype = ctypes.c_void_p
+    lib.g4a_load_safetensors.argtypes = [ctypes.c_char_p]
+    lib.g4a_encode.restype = ctypes.POINTER(ctypes.c_float)
+    lib.g4a_encode.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+    lib.g4a_free.argtypes = [ctypes.c_void_p]
+    lib.ref_free.argtypes = [ctypes.c_void_p]
     return lib

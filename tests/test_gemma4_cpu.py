@@ -68,3 +68,42 @@ def test_matches_reference_cpu_engine(tmp_path, variant):
     # greedy generation through the public call
     out = model.generate(toks[:10].tolist(), 4)
     assert len(out) == 4
+
+
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not present")
+def test_soft_token_rows_match_the_reference(tmp_path):
+    """Encoder rows spliced into a prompt (text, 5 soft tokens, text) against the reference's embedding entry point."""
+    cfg = _cfg()
+    t = gemma4.random_tensors(cfg, seed=8, v_proj_on_swa=False)
+    path = str(tmp_path / "g4.gguf")
+    gemma4.save_gguf(cfg, t, path, "F16")
+    ref = oracle.engine_lib()
+    m = ref.transformer_load(ref.gguf_open(path.encode(), 1), 64)
+    assert m
+    ref.transformer_set_f64_accum(m, 1)
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(1, cfg.vocab, (12,), generator=g)
+    soft = torch.randn(5, cfg.hidden, generator=g).contiguous()
+    want, pos = [], 0
+    for tk in toks[:4].tolist():
+        p = ref.transformer_forward_logits(m, tk, pos); pos += 1
+    for r in range(5):
+        p = ref.transformer_forward_embd_logits(m, soft[r].data_ptr(), pos); pos += 1
+        want.append(torch.from_numpy(np.ctypeslib.as_array(p, shape=(cfg.vocab,)).copy()))
+    for tk in toks[4:].tolist():
+        p = ref.transformer_forward_logits(m, tk, pos); pos += 1
+        want.append(torch.from_numpy(np.ctypeslib.as_array(p, shape=(cfg.vocab,)).copy()))
+    want = torch.stack(want)
+    model = gemma4.load_gguf(path, "cpu", torch.float32)
+    model.reset(1, 64)
+    ids = torch.cat([toks[:4], torch.zeros(5, dtype=toks.dtype), toks[4:]])[None]
+    embeds = torch.zeros(1, 17, cfg.hidden)
+    embeds[0, 4:9] = soft
+    mask = torch.zeros(1, 17, dtype=torch.bool)
+    mask[0, 4:9] = True
+    got = model.forward(ids, all_logits=True, embeds=embeds, embeds_mask=mask)[0, 4:]
+    for i in (0, 4, 5, 12):
+        assert _rel(got[i], want[i]) < 2e-3, (i, _rel(got[i], want[i]))
+    # the public call gives the continuation of the same prompt
+    first = model.generate(toks.tolist(), 3, soft=soft, soft_at=4)
+    assert first[0] == int(want[-1].argmax())

@@ -118,6 +118,30 @@ def test_gemma4_vision_tower_matches_reference(tmp_path, hw):
     assert _rel(got, want) < 2e-3, _rel(got, want)
 
 
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not present")
+@pytest.mark.parametrize("hw", [(24, 24), (12, 36)])
+def test_gemma4_unified_projector_matches_reference(tmp_path, hw):
+    """The block-free "gemma4uv" projector: one token per 12-pixel square (patch 4 x merge 3)."""
+    cfg = vision.Gemma4VisionConfig(n_blocks=0, dim=64, n_heads=4, ffn=96, patch_size=4, image_size=24, proj_dim=40, n_pos=12, projector="gemma4uv")
+    path = str(tmp_path / "g4uv.gguf")
+    vision.Gemma4VisionEncoder.save_gguf(cfg, vision.Gemma4VisionEncoder.random_tensors(cfg, 7), path, "F16")
+    enc = vision.Gemma4VisionEncoder.load_gguf(path)
+    assert enc.cfg.unified and enc.cfg.n_blocks == 0
+    h, w = hw
+    rgb = torch.randint(0, 256, (h, w, 3), generator=torch.Generator().manual_seed(8), dtype=torch.uint8)
+    got = enc.encode(rgb)
+    n_tok = (h // 12) * (w // 12)
+    assert got.shape == (n_tok, 40)
+    ref = oracle.gemma4_vision_lib()
+    vm = ref.g4v_load(ref.gguf_open(path.encode(), 1))
+    assert vm, "the reference tower refused our mmproj file"
+    buf = np.ascontiguousarray(rgb.numpy())
+    p = ref.g4v_encode(vm, buf.ctypes.data, w, h)
+    assert p
+    want = torch.from_numpy(np.ctypeslib.as_array(p, shape=(n_tok, 40)).copy())
+    assert _rel(got, want) < 2e-3, _rel(got, want)
+
+
 def test_multimodal_requests_through_llm_and_server():
     """An image + text prompt through the continuous-batching loop (chunked prefill, a text-only request in the same batch) equals the
     engine's one-shot prefill + decode, and the HTTP endpoint takes the image as base64."""
