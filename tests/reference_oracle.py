@@ -246,3 +246,141 @@ def audio_encoder_lib():
     lib.g4a_free.argtypes = [ctypes.c_void_p]
     lib.ref_free.argtypes = [ctypes.c_void_p]
     return lib
+
+
+# A scalar stand-in for the Arm SVE intrinsics the DS4F header uses unconditionally, at a 512-bit vector length.  Every vector type
+# is one 64-byte union (so the reinterpret casts are the identity) and a predicate holds one flag per byte lane.  It exists so that
+# the header COMPILES here; the oracle below only calls the header's scalar validation paths.
+_SVE_STUB = r"""/* Scalar stand-in for the Arm SVE intrinsics at a 512-bit vector length: every vector type is the same 64-byte union, so the
+ * reinterpret casts are the identity; predicates hold one flag per byte lane. */
+#ifndef STUB_ARM_SVE_H
+#define STUB_ARM_SVE_H
+#include <stdint.h>
+#include <string.h>
+#include <math.h>
+typedef _Float16 __fp16;
+typedef union { float f[16]; uint32_t u[16]; int32_t s[16]; uint16_t h[32]; int8_t b[64]; uint8_t ub[64]; } svreg_t;
+typedef svreg_t svfloat32_t, svuint32_t, svint32_t, svuint16_t, svint16_t, svint8_t, svuint8_t;
+typedef struct { uint8_t m[64]; } svbool_t;
+static inline uint64_t svcntw(void) { return 16; }
+static inline uint64_t svcnth(void) { return 32; }
+static inline uint64_t svcntb(void) { return 64; }
+static inline svbool_t svptrue_b8(void)  { svbool_t p; memset(p.m, 1, 64); return p; }
+static inline svbool_t svptrue_b16(void) { svbool_t p; memset(p.m, 0, 64); for (int i = 0; i < 32; i++) p.m[2 * i] = 1; return p; }
+static inline svbool_t svptrue_b32(void) { svbool_t p; memset(p.m, 0, 64); for (int i = 0; i < 16; i++) p.m[4 * i] = 1; return p; }
+static inline svbool_t sv_whilelt_b32(long long a, long long b) { svbool_t p; memset(p.m, 0, 64); for (int i = 0; i < 16; i++) p.m[4 * i] = (a + i < b); return p; }
+#define svwhilelt_b32(a, b) sv_whilelt_b32((long long)(a), (long long)(b))
+#define SV_ON32(pg, i) ((pg).m[4 * (i)])
+static inline svreg_t svdup_f32(float x) { svreg_t r; for (int i = 0; i < 16; i++) r.f[i] = x; return r; }
+static inline svreg_t svdup_s32(int32_t x) { svreg_t r; for (int i = 0; i < 16; i++) r.s[i] = x; return r; }
+static inline svreg_t svdup_u32(uint32_t x) { svreg_t r; for (int i = 0; i < 16; i++) r.u[i] = x; return r; }
+static inline svreg_t svld1_f32(svbool_t pg, const float *p) { svreg_t r; for (int i = 0; i < 16; i++) r.f[i] = SV_ON32(pg, i) ? p[i] : 0.0f; return r; }
+#define svld1(pg, p) svld1_f32((pg), (p))
+static inline svreg_t svld1_s8(svbool_t pg, const int8_t *p) { svreg_t r; for (int i = 0; i < 64; i++) r.b[i] = pg.m[i] ? p[i] : 0; return r; }
+static inline svreg_t svld1uh_u32(svbool_t pg, const uint16_t *p) { svreg_t r; for (int i = 0; i < 16; i++) r.u[i] = SV_ON32(pg, i) ? p[i] : 0; return r; }
+static inline svreg_t svld1ub_u32(svbool_t pg, const uint8_t *p) { svreg_t r; for (int i = 0; i < 16; i++) r.u[i] = SV_ON32(pg, i) ? p[i] : 0; return r; }
+static inline svreg_t svld1sb_s32(svbool_t pg, const int8_t *p) { svreg_t r; for (int i = 0; i < 16; i++) r.s[i] = SV_ON32(pg, i) ? p[i] : 0; return r; }
+static inline svreg_t svld1_gather_u32index_u32(svbool_t pg, const uint32_t *base, svreg_t idx) { svreg_t r; for (int i = 0; i < 16; i++) r.u[i] = SV_ON32(pg, i) ? base[idx.u[i]] : 0; return r; }
+static inline void svst1_f32(svbool_t pg, float *p, svreg_t v) { for (int i = 0; i < 16; i++) if (SV_ON32(pg, i)) p[i] = v.f[i]; }
+#define svst1(pg, p, v) svst1_f32((pg), (p), (v))
+static inline void svst1_u16(svbool_t pg, uint16_t *p, svreg_t v) { for (int i = 0; i < 32; i++) if (pg.m[2 * i]) p[i] = v.h[i]; }
+static inline void svst1b_s32(svbool_t pg, int8_t *p, svreg_t v) { for (int i = 0; i < 16; i++) if (SV_ON32(pg, i)) p[i] = (int8_t)v.s[i]; }
+static inline svreg_t svmla_f32_x(svbool_t pg, svreg_t a, svreg_t x, svreg_t y) { for (int i = 0; i < 16; i++) if (SV_ON32(pg, i)) a.f[i] += x.f[i] * y.f[i]; return a; }
+#define svmla_x svmla_f32_x
+static inline svreg_t svmul_f32_x(svbool_t pg, svreg_t x, svreg_t y) { for (int i = 0; i < 16; i++) x.f[i] *= y.f[i]; (void)pg; return x; }
+#define svmul_x svmul_f32_x
+static inline svreg_t svadd_f32_x(svbool_t pg, svreg_t x, svreg_t y) { for (int i = 0; i < 16; i++) x.f[i] += y.f[i]; (void)pg; return x; }
+static inline svreg_t svmax_f32_x(svbool_t pg, svreg_t x, svreg_t y) { for (int i = 0; i < 16; i++) x.f[i] = x.f[i] > y.f[i] ? x.f[i] : y.f[i]; (void)pg; return x; }
+#define svmax_x svmax_f32_x
+static inline svreg_t svabs_f32_x(svbool_t pg, svreg_t x) { for (int i = 0; i < 16; i++) x.f[i] = fabsf(x.f[i]); (void)pg; return x; }
+#define svabs_x svabs_f32_x
+static inline svreg_t svmax_s32_x(svbool_t pg, svreg_t x, svreg_t y) { for (int i = 0; i < 16; i++) x.s[i] = x.s[i] > y.s[i] ? x.s[i] : y.s[i]; (void)pg; return x; }
+static inline svreg_t svmin_s32_x(svbool_t pg, svreg_t x, svreg_t y) { for (int i = 0; i < 16; i++) x.s[i] = x.s[i] < y.s[i] ? x.s[i] : y.s[i]; (void)pg; return x; }
+static inline float svaddv_f32(svbool_t pg, svreg_t v) { float s = 0.0f; for (int i = 0; i < 16; i++) if (SV_ON32(pg, i)) s += v.f[i]; return s; }
+static inline float svmaxv_f32(svbool_t pg, svreg_t v) { float s = -INFINITY; for (int i = 0; i < 16; i++) if (SV_ON32(pg, i) && v.f[i] > s) s = v.f[i]; return s; }
+static inline int64_t svaddv_s32(svbool_t pg, svreg_t v) { int64_t s = 0; for (int i = 0; i < 16; i++) if (SV_ON32(pg, i)) s += v.s[i]; return s; }
+static inline svreg_t svdot_s32(svreg_t acc, svreg_t a, svreg_t b) { for (int i = 0; i < 16; i++) for (int j = 0; j < 4; j++) acc.s[i] += (int32_t)a.b[4 * i + j] * (int32_t)b.b[4 * i + j]; return acc; }
+#define svdot svdot_s32
+#define svreinterpret_f32_u32(v) (v)
+#define svreinterpret_u32_f32(v) (v)
+#define svreinterpret_u16_u32(v) (v)
+#define svreinterpret_s32_u32(v) (v)
+#define svreinterpret_u32_s32(v) (v)
+static inline svreg_t svlsr_n_u32_x(svbool_t pg, svreg_t v, unsigned n) { for (int i = 0; i < 16; i++) v.u[i] >>= n; (void)pg; return v; }
+static inline svreg_t svlsl_n_u32_x(svbool_t pg, svreg_t v, unsigned n) { for (int i = 0; i < 16; i++) v.u[i] <<= n; (void)pg; return v; }
+static inline svreg_t svand_n_u32_x(svbool_t pg, svreg_t v, uint32_t n) { for (int i = 0; i < 16; i++) v.u[i] &= n; (void)pg; return v; }
+static inline svreg_t sveor_n_u32_x(svbool_t pg, svreg_t v, uint32_t n) { for (int i = 0; i < 16; i++) v.u[i] ^= n; (void)pg; return v; }
+static inline svreg_t svorr_u32_x(svbool_t pg, svreg_t v, svreg_t w) { for (int i = 0; i < 16; i++) v.u[i] |= w.u[i]; (void)pg; return v; }
+static inline svreg_t svsub_n_s32_x(svbool_t pg, svreg_t v, int32_t n) { for (int i = 0; i < 16; i++) v.s[i] -= n; (void)pg; return v; }
+static inline svreg_t svtbl_f32(svreg_t v, svreg_t idx) { svreg_t r; for (int i = 0; i < 16; i++) r.u[i] = idx.u[i] < 16 ? v.u[idx.u[i]] : 0; return r; }
+#define svtbl svtbl_f32
+static inline svreg_t svuzp1_u16(svreg_t a, svreg_t b) { svreg_t r; for (int i = 0; i < 16; i++) { r.h[i] = a.h[2 * i]; r.h[16 + i] = b.h[2 * i]; } return r; }
+static inline svreg_t svzip1_u16(svreg_t a, svreg_t b) { svreg_t r; for (int i = 0; i < 16; i++) { r.h[2 * i] = a.h[i]; r.h[2 * i + 1] = b.h[i]; } return r; }
+static inline svreg_t svzip1_f32(svreg_t a, svreg_t b) { svreg_t r; for (int i = 0; i < 8; i++) { r.f[2 * i] = a.f[i]; r.f[2 * i + 1] = b.f[i]; } return r; }
+static inline svreg_t svzip2_f32(svreg_t a, svreg_t b) { svreg_t r; for (int i = 0; i < 8; i++) { r.f[2 * i] = a.f[8 + i]; r.f[2 * i + 1] = b.f[8 + i]; } return r; }
+static inline svreg_t svcvt_f32_s32_x(svbool_t pg, svreg_t v) { for (int i = 0; i < 16; i++) v.f[i] = (float)v.s[i]; (void)pg; return v; }
+static inline svreg_t svcvt_s32_f32_x(svbool_t pg, svreg_t v) { for (int i = 0; i < 16; i++) v.s[i] = (int32_t)v.f[i]; (void)pg; return v; }
+#endif
+"""
+
+_DS4F_SRC = r"""
+#define _GNU_SOURCE
+__asm__(".macro yield\n.endm");
+#define GGML_DEQUANT_IMPLEMENTATION
+/* the e2m1 code points; the kernel header that defines this table is not part of the reference's common/ tree */
+static const float ds4f_kvalues_mxfp4_f32[16] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+#include "ds4f.h"
+void ref_rotate(float *x, int n) { ds4f_rotate_activation(x, n); }
+void ref_fp4(float *x, int n, int block) { ds4f_fp4_act_quant_inplace(x, n, block); }
+void ref_compress_prefill(const float *x, int seqlen, int dim, int d, int rd, int ratio, const float *wkv, const float *wgate, const float *ape,
+                          const uint16_t *norm_w, const float *rcos, const float *rsin, float eps, int rotate, float *out) {
+    ds4f_compress_prefill(x, seqlen, dim, d, rd, ratio, wkv, wgate, ape, norm_w, rcos, rsin, eps, rotate, out);
+}
+void ref_compress_reset(float *kv_state, float *score_state, int ratio, int d) { ds4f_compress_state_reset(kv_state, score_state, ratio, d); }
+int ref_compress_step(const float *x, int dim, int d, int rd, int ratio, int start_pos, const float *wkv, const float *wgate, const float *ape,
+                      const uint16_t *norm_w, const float *rcos, const float *rsin, float eps, int rotate, float *kv_state, float *score_state, float *out) {
+    return ds4f_compress_step(x, dim, d, rd, ratio, start_pos, wkv, wgate, 0, ape, norm_w, rcos, rsin, eps, rotate, kv_state, score_state, out, NULL);
+}
+void ref_index_score(const float *q, const float *kvc, const float *weights, int H, int hd, int T, float *score) {
+    ds4f_index_score(q, kvc, weights, H, hd, T, score, NULL);
+}
+void ref_index_topk(const float *score, int T, int thr, int k, int offset, int *sel) { ds4f_index_topk(score, T, thr, k, offset, sel); }
+int ref_index_step(const float *x, int dim, const float *qr, int qlora, int H, int hd, int rd, int ratio, int start_pos, int offset, int k,
+                   const float *wq_b, const float *wproj, const float *cwkv, const float *cwgate, const float *cape, const uint16_t *cnorm,
+                   const float *rcos, const float *rsin, float eps, float *kv_state, float *score_state, float *idx_kv, float *q_scr,
+                   float *score_scr, int *sel) {
+    return ds4f_index_step(x, dim, qr, qlora, H, hd, rd, ratio, start_pos, offset, k, wq_b, wproj, 0, cwkv, cwgate, cape, cnorm, rcos, rsin, eps,
+                           kv_state, score_state, idx_kv, NULL, NULL, NULL, q_scr, score_scr, sel, NULL, 0, 0, 0, NULL, NULL, 0, 1, NULL, NULL);
+}
+void ref_sparse_attn(const float *q, const float *kv, const float *sink, const int *topk_idxs, int m, int h, int d, int topk, float scale, float *o) {
+    ds4f_sparse_attn(q, kv, sink, topk_idxs, m, h, d, topk, scale, o);
+}
+int ref_window_idx_decode(int window, int start_pos, int *row) { return ds4f_window_idx_decode(window, start_pos, row); }
+void ref_rope_apply(float *v, const float *cosb, const float *sinb, int pos, int half, int inverse) { ds4f_rope_apply(v, cosb, sinb, pos, half, inverse); }
+"""
+
+
+def ds4f_lib():
+    """ctypes handle on the scalar Tier-B2 building blocks of the reference's DeepSeek-V4-Flash engine (common/ds4f_impl.h: the
+    compressor for a whole prompt and token by token, indexer scoring / top-k / the indexer step, the gathered attention with
+    sinks, Hadamard rotation, FP4 rounding).  The engine as a whole cannot run here: its matrix kernels live outside common/."""
+    stub = tempfile.mkdtemp(prefix="gemm_ref_stub_")
+    with open(os.path.join(stub, "arm_sve.h"), "w") as f:
+        f.write(_SVE_STUB)
+    lib = _build("ref_ds4f", _DS4F_SRC, extra=("-I", stub))
+    P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+    lib.ref_rotate.argtypes = [P, I]
+    lib.ref_fp4.argtypes = [P, I, I]
+    lib.ref_compress_prefill.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, F, I, P]
+    lib.ref_compress_reset.argtypes = [P, P, I, I]
+    lib.ref_compress_step.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, F, I, P, P, P]
+    lib.ref_compress_step.restype = I
+    lib.ref_index_score.argtypes = [P, P, P, I, I, I, P]
+    lib.ref_index_topk.argtypes = [P, I, I, I, I, P]
+    lib.ref_index_step.argtypes = [P, I, P, I, I, I, I, I, I, I, I, P, P, P, P, P, P, P, P, F, P, P, P, P, P, P]
+    lib.ref_index_step.restype = I
+    lib.ref_sparse_attn.argtypes = [P, P, P, P, I, I, I, I, F, P]
+    lib.ref_window_idx_decode.argtypes = [I, I, P]
+    lib.ref_window_idx_decode.restype = I
+    lib.ref_rope_apply.argtypes = [P, P, P, I, I, I]
+    return lib

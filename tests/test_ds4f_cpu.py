@@ -200,8 +200,8 @@ def test_expert_shards_sum_to_the_whole():
     t = ds4f.random_tensors(CFG, 8)
     full = ds4f.DS4FModel(CFG, t)
     h2 = torch.randn(1, 5, CFG.hidden, generator=torch.Generator().manual_seed(4))
-    whole = full._moe(1, h2)
-    parts = [ds4f.DS4FModel(CFG, t, ep_rank=r, ep_size=2)._moe(1, h2) for r in range(2)]
+    whole = full._moe("l1.", h2)
+    parts = [ds4f.DS4FModel(CFG, t, ep_rank=r, ep_size=2)._moe("l1.", h2) for r in range(2)]
     # each part carries the shared expert once
     x = h2.reshape(5, -1)
     sh = (full._swiglu(x @ full.t["l1.sh_w1"].t(), x @ full.t["l1.sh_w3"].t()) @ full.t["l1.sh_w2"].t()).reshape(1, 5, -1)

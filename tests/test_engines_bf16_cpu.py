@@ -34,3 +34,20 @@ def test_bf16_gemma4_and_vision():
     gt = {k: v.to(torch.float32 if v.dim() == 1 else torch.bfloat16) for k, v in vision.Gemma4VisionEncoder.random_tensors(gc, 1).items()}
     out = vision.Gemma4VisionEncoder(gc, gt, "cpu", torch.bfloat16).encode(torch.randint(0, 256, (24, 24, 3), dtype=torch.uint8))
     assert torch.isfinite(out).all()
+
+
+def test_audio_and_unified_vision_encoders_in_bf16():
+    """The encoders' bf16 mode (what a GPU runs) stays close to fp32 and mixes no dtypes in a product."""
+    from gemm_b200.models import audio, vision
+    cfg = audio.Gemma4AudioConfig(hidden=64, heads=4, layers=2, ffn=128, out_dim=48, conv_channels=(16, 8), n_mel=32)
+    t = audio.random_audio_tensors(cfg, 0)
+    mel = torch.randn(50, 32, generator=torch.Generator().manual_seed(1))
+    a = audio.Gemma4AudioEncoder(cfg, t).encode(mel)
+    b = audio.Gemma4AudioEncoder(cfg, t, dtype=torch.bfloat16).encode(mel)
+    assert b.dtype == torch.bfloat16 and ((a - b.float()).norm() / a.norm()).item() < 3e-2
+    c = vision.Gemma4VisionConfig(n_blocks=0, dim=64, n_heads=4, ffn=96, patch_size=4, image_size=24, proj_dim=40, n_pos=12, projector="gemma4uv")
+    tt = vision.Gemma4VisionEncoder.random_tensors(c, 1)
+    rgb = torch.randint(0, 256, (24, 24, 3), generator=torch.Generator().manual_seed(2), dtype=torch.uint8)
+    x = vision.Gemma4VisionEncoder(c, tt).encode(rgb)
+    y = vision.Gemma4VisionEncoder(c, {k: (v if v.dim() == 1 else v.bfloat16()) for k, v in tt.items()}, dtype=torch.bfloat16).encode(rgb)
+    assert ((x - y).norm() / x.norm()).item() < 3e-2
