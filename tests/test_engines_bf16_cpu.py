@@ -51,3 +51,19 @@ def test_audio_and_unified_vision_encoders_in_bf16():
     x = vision.Gemma4VisionEncoder(c, tt).encode(rgb)
     y = vision.Gemma4VisionEncoder(c, {k: (v if v.dim() == 1 else v.bfloat16()) for k, v in tt.items()}, dtype=torch.bfloat16).encode(rgb)
     assert ((x - y).norm() / x.norm()).item() < 3e-2
+
+
+def test_ds4f_compressed_attention_and_mtp_in_bf16():
+    from gemm_b200.models import ds4f
+    cfg = ds4f.DS4FConfig(n_layers=3, hidden=64, vocab=96, n_heads=4, q_head_dim=32, qk_rope_dim=8, q_lora=32, kv_lora=32, o_groups=2, o_lora=16,
+                          n_experts=8, n_active=2, moe_inter=32, shared_inter=32, window_size=6, max_pos=96, original_seq_len=16, hc_iters=5,
+                          compress_ratios=[0, 4, 8], tierb2=True, index_n_heads=4, index_head_dim=32, index_topk=3, n_hash_layers=1, mtp=True)
+    t = ds4f.random_tensors(cfg, 1)
+    ids = torch.randint(0, cfg.vocab, (1, 30), generator=torch.Generator().manual_seed(0))
+    a = ds4f.DS4FModel(cfg, t)
+    a.reset(1, 64)
+    b = ds4f.DS4FModel(cfg, t, dtype=torch.bfloat16)
+    b.reset(1, 64)
+    la, lb = a.forward(ids), b.forward(ids)
+    assert ((la - lb).norm() / la.norm()).item() < 5e-2
+    assert b.mtp_predict(ids[:, 1:], b.last_hc[:, :-1], 0).shape == (1, 29, cfg.vocab)
