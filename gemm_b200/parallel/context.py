@@ -29,6 +29,75 @@ from ..ops import attention as att
 from .fabric import Fabric
 
 
+def merge_two(o1: torch.Tensor, l1: torch.Tensor, o2: torch.Tensor, l2: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merge of two attention partials (outputs normalised by their own sums, base-2 log-sum-exps); symmetric in its arguments,
+    so two ranks that swap partials compute the same bits."""
+    m = torch.maximum(l1, l2)
+    safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+    w1, w2 = torch.exp2(l1 - safe), torch.exp2(l2 - safe)
+    den = w1 + w2
+    o = (w1[..., None] * o1 + w2[..., None] * o2) / den.clamp_min(1e-30)[..., None]
+    return o, safe + torch.log2(den)
+
+
+def _swap(send: torch.Tensor, dst: int, src: int, group) -> torch.Tensor:
+    recv = torch.empty_like(send)
+    ops = [dist.P2POp(dist.isend, send, dist.get_global_rank(group, dst) if group is not None else dst, group),
+           dist.P2POp(dist.irecv, recv, dist.get_global_rank(group, src) if group is not None else src, group)]
+    for w in dist.batch_isend_irecv(ops):
+        w.wait()
+    return recv
+
+
+def merge_ring(o: torch.Tensor, lse: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The partials of all ranks merged by passing them around the ring: ``world - 1`` hops, each rank forwards what it received
+    last and folds it into its running result.  Every rank ends with the merge of all partials, folded in a different order, so
+    the results agree to rounding only: a benchmark variant (the reference times the same pattern,
+    a64fx/utofu-tests/ring_attn_bench.c:19-27), not what the engine runs."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    pay = torch.cat([o.float().reshape(-1, o.shape[-1]), lse.float().reshape(-1, 1)], dim=1).contiguous()
+    acc_o, acc_l, cur = o.float(), lse.float(), pay
+    for _ in range(world - 1):
+        cur = _swap(cur, (rank + 1) % world, (rank - 1) % world, group)
+        acc_o, acc_l = merge_two(acc_o, acc_l, cur[:, :-1].reshape(o.shape), cur[:, -1].reshape(lse.shape))
+    return acc_o, acc_l
+
+
+def merge_tree(o: torch.Tensor, lse: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same by recursive doubling: ``log2(world)`` rounds, in round k rank r swaps its running result with rank ``r ^ 2^k``.
+    Both partners compute the same merge, so all ranks end with identical bits.  A world size that is not a power of two folds
+    its upper ranks into the lower ones first and hands them the result at the end (the reference measures this against the ring,
+    a64fx/utofu-tests/ring_attn_bench.c:23-27)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    pof2 = 1 << (world.bit_length() - 1)
+    acc_o, acc_l = o.float(), lse.float()
+    pack = lambda a, b: torch.cat([a.reshape(-1, a.shape[-1]), b.reshape(-1, 1)], dim=1).contiguous()
+
+    def send(t, dst):
+        dist.send(t, dist.get_global_rank(group, dst) if group is not None else dst, group=group)
+
+    def recv(like, src):
+        buf = torch.empty_like(like)
+        dist.recv(buf, dist.get_global_rank(group, src) if group is not None else src, group=group)
+        return buf
+    if rank >= pof2:                                             # an upper rank: give, then wait for the result
+        send(pack(acc_o, acc_l), rank - pof2)
+        res = recv(pack(acc_o, acc_l), rank - pof2)
+        return res[:, :-1].reshape(o.shape), res[:, -1].reshape(lse.shape)
+    if rank + pof2 < world:
+        got = recv(pack(acc_o, acc_l), rank + pof2)
+        acc_o, acc_l = merge_two(acc_o, acc_l, got[:, :-1].reshape(o.shape), got[:, -1].reshape(lse.shape))
+    k = 1
+    while k < pof2:
+        peer = rank ^ k
+        got = _swap(pack(acc_o, acc_l), peer, peer, group)
+        acc_o, acc_l = merge_two(acc_o, acc_l, got[:, :-1].reshape(o.shape), got[:, -1].reshape(lse.shape))
+        k <<= 1
+    if rank + pof2 < world:
+        send(pack(acc_o, acc_l), rank + pof2)
+    return acc_o, acc_l
+
+
 class ContextParallel(SingleProcess):
     def __init__(self, group, device: torch.device, block: int = 128, fused: bool = True, max_tokens: int = 256, hq: int = 32,
                  head_dim: int = 128, max_splits: int = 1):

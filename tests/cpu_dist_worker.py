@@ -141,6 +141,26 @@ def main():
         whole = stage.step(fb_of([0, 1, 2, 3]))
         parts = stage.step_many([fb_of([0, 1]), fb_of([2]), fb_of([3])])
         assert [p.numel() for p in parts] == [2, 1, 1] and torch.equal(torch.cat(parts), whole), (parts, whole)
+    elif what == "cpmerge":
+        # ring and tree merges of attention partials against the all-gather + combine rule
+        from gemm_b200.ops import attention as att
+        from gemm_b200.parallel import context as cpx
+        gq = torch.Generator().manual_seed(100 + rank)
+        o, lse = torch.randn(5, 8, 16, generator=gq), torch.randn(5, 8, generator=gq) * 4
+        if rank == 1:
+            lse[0] = float("-inf")                                # a rank without keys for that query
+        parts_o, parts_l = [torch.empty_like(o) for _ in range(world)], [torch.empty_like(lse) for _ in range(world)]
+        dist.all_gather(parts_o, o)
+        dist.all_gather(parts_l, lse)
+        want, want_l = att.combine_partials(torch.stack(parts_o).reshape(world, 40, 16), torch.stack(parts_l).reshape(world, 40))
+        for fn in (cpx.merge_ring, cpx.merge_tree):
+            got_o, got_l = fn(o, lse)
+            assert rel(got_o.reshape(40, 16), want) < 5e-3, (fn.__name__, rel(got_o.reshape(40, 16), want))
+            assert (got_l.reshape(40) - want_l).abs().max() < 1e-4
+        got_o, _ = cpx.merge_tree(o, lse)
+        same = [torch.empty_like(got_o) for _ in range(world)]
+        dist.all_gather(same, got_o)
+        assert all(torch.equal(same[0], x) for x in same), "tree merge: ranks disagree"
     elif what == "dp":
         dp = DataParallel(dist.group.WORLD)
         items = list(range(10))
