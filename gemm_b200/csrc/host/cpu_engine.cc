@@ -1,4 +1,4 @@
-// Native CPU engine for dense Qwen2 / Qwen3 checkpoints in GGUF: the model runs straight from the file's (memory-mapped) ggml
+// Native CPU engine for Qwen2 / Qwen3 (dense) and Qwen3-MoE checkpoints in GGUF: the model runs straight from the file's (memory-mapped) ggml
 // blocks, single process, a pool of worker threads.  It is the counterpart of the reference's CPU engine
 // (common/transformer.h: transformer_load :1598, transformer_forward_pos :3499-3548, layer loop :3550-4174, Q8_0 dot
 // tf_qmatvec_worker :648-738, sampler :5415-5467) for the configuration that has no GPU in it: Qwen3-0.6B, Q8_0, batch 1.
@@ -114,11 +114,14 @@ struct QMat {                      // a [rows, k] matrix as it sits in the file
 struct Layer {
   std::vector<float> attn_norm, ffn_norm, q_norm, k_norm, bq, bk, bv;
   QMat wq, wk, wv, wo, wgate, wup, wdown;
+  QMat wrouter;                    // MoE layers: [n_experts, hidden]
+  std::vector<QMat> eg, eu, ed;    // per expert: gate / up [expert_ffn, hidden], down [hidden, expert_ffn] (slices of the 3-D tensors)
 };
 
 struct CpuEngine {
   void* gguf = nullptr;
   int n_layers = 0, hidden = 0, n_heads = 0, n_kv = 0, head_dim = 0, ffn = 0, vocab = 0, max_seq = 0, threads = 1;
+  int n_experts = 0, n_used = 0, expert_ffn = 0;     // > 0: every layer's FFN is a routed mixture (qwen3moe)
   float eps = 1e-6f, theta = 1e6f;
   bool qk_norm = false, has_bias = false;
   std::vector<Layer> layers;
@@ -482,6 +485,26 @@ int get_mat(void* g, const std::string& name, QMat* m, int want_rows, int want_k
   return 0;
 }
 
+// The experts of a 3-D tensor [n_experts][rows][k] (ggml dims {k, rows, n_experts}) as one matrix each.
+int get_experts(void* g, const std::string& name, std::vector<QMat>* out, int n_experts, int want_rows, int want_k) {
+  const int i = gbh_gguf_find_tensor(g, name.c_str());
+  if (i < 0) return fail("cpu engine: tensor %s is missing", name.c_str());
+  int nd, type; uint64_t dims[4], nbytes; char nm[8];
+  gbh_gguf_tensor_info(g, i, nm, 8, &nd, dims, &type, &nbytes);
+  if (nd != 3 || (int)dims[0] != want_k || (int)dims[1] != want_rows || (int)dims[2] != n_experts)
+    return fail("cpu engine: %s has shape [%d, %d, %d], wanted [%d, %d, %d]", name.c_str(), (int)dims[2], (int)dims[1], (int)dims[0], n_experts, want_rows, want_k);
+  const TypeInfo* ti = type_info(type);
+  if (ti == nullptr || want_k % ti->block) return fail("cpu engine: %s: unsupported tensor type %d", name.c_str(), type);
+  const long rb = (long)(want_k / ti->block) * ti->bytes;
+  const uint8_t* base = (const uint8_t*)gbh_gguf_tensor_data(g, i);
+  out->resize((size_t)n_experts);
+  for (int e = 0; e < n_experts; ++e) {
+    QMat& m = (*out)[(size_t)e];
+    m.data = base + (size_t)e * want_rows * rb; m.type = type; m.rows = want_rows; m.k = want_k; m.row_bytes = rb;
+  }
+  return 0;
+}
+
 int get_vec(void* g, const std::string& name, std::vector<float>* v, int n, bool optional = false) {
   const int i = gbh_gguf_find_tensor(g, name.c_str());
   if (i < 0) return optional ? 1 : fail("cpu engine: tensor %s is missing", name.c_str());
@@ -507,10 +530,67 @@ struct Phase {                        // adds its lifetime to one slot of the pr
   ~Phase() { *slot += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count(); }
 };
 
+// Routed FFN of one layer over the rows h [T, hidden] -> o [T, hidden].  Router: softmax over all experts, the n_used largest
+// (ties to the lower index), their weights renormalised to sum 1 (common/transformer.h:4050-4130).  A single token runs its
+// experts one after the other, each matrix split over the threads by rows; a batch gathers the rows of each expert and runs them
+// through the same register-tiled products as the dense FFN, then scatters the weighted results.
+void moe_ffn(CpuEngine& e, const Layer& L, const float* h, int T, float* o) {
+  const int H = e.hidden, E = e.n_experts, K = e.n_used, F = e.expert_ffn;
+  std::vector<float> logits((size_t)T * E);
+  matmul(e, L.wrouter, h, H, T, logits.data(), E);
+  std::vector<int> pick((size_t)T * K);
+  std::vector<float> wt((size_t)T * K);
+  for (int t = 0; t < T; ++t) {
+    float* lg = logits.data() + (size_t)t * E;
+    float mx = lg[0];
+    for (int i = 1; i < E; ++i) mx = std::max(mx, lg[i]);
+    float sum = 0.f;
+    for (int i = 0; i < E; ++i) { lg[i] = expf(lg[i] - mx); sum += lg[i]; }
+    for (int i = 0; i < E; ++i) lg[i] /= sum;
+    float chosen = 0.f;
+    for (int k = 0; k < K; ++k) {
+      int best = -1;
+      for (int i = 0; i < E; ++i) {
+        bool taken = false;
+        for (int j = 0; j < k; ++j) taken = taken || pick[(size_t)t * K + j] == i;
+        if (!taken && (best < 0 || lg[i] > lg[best])) best = i;
+      }
+      pick[(size_t)t * K + k] = best; wt[(size_t)t * K + k] = lg[best]; chosen += lg[best];
+    }
+    for (int k = 0; k < K; ++k) wt[(size_t)t * K + k] /= chosen;
+  }
+  for (size_t i = 0; i < (size_t)T * H; ++i) o[i] = 0.f;
+  std::vector<float> xe, ge, ye;
+  std::vector<int> rows; std::vector<float> rw;
+  for (int ex = 0; ex < E; ++ex) {
+    rows.clear(); rw.clear();
+    for (int t = 0; t < T; ++t)
+      for (int k = 0; k < K; ++k)
+        if (pick[(size_t)t * K + k] == ex) { rows.push_back(t); rw.push_back(wt[(size_t)t * K + k]); }
+    const int n = (int)rows.size();
+    if (n == 0) continue;
+    const float* xin = h;
+    if (!(n == T)) {                                             // gather this expert's rows
+      xe.resize((size_t)n * H);
+      for (int r = 0; r < n; ++r) memcpy(xe.data() + (size_t)r * H, h + (size_t)rows[r] * H, sizeof(float) * H);
+      xin = xe.data();
+    }
+    ge.resize((size_t)n * F); ye.resize((size_t)n * H);
+    ffn_gate_up_silu(e, L.eg[(size_t)ex], L.eu[(size_t)ex], xin, H, n, ge.data(), F);
+    matmul(e, L.ed[(size_t)ex], ge.data(), F, n, ye.data(), H);
+    for (int r = 0; r < n; ++r) {
+      float* dst = o + (size_t)rows[r] * H;
+      const float* src = ye.data() + (size_t)r * H;
+      const float w = rw[(size_t)r];
+      for (int i = 0; i < H; ++i) dst[i] += w * src[i];
+    }
+  }
+}
+
 void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
   const int H = e.hidden, D = e.head_dim, QD = e.n_heads * D, KD = e.n_kv * D, F = e.ffn;
   std::vector<float> h((size_t)T * H), q((size_t)T * QD), k((size_t)T * KD), v((size_t)T * KD), att((size_t)T * QD), o((size_t)T * H);
-  std::vector<float> g((size_t)T * F);
+  std::vector<float> g(e.n_experts > 0 ? 0 : (size_t)T * F);
   const float scale = 1.0f / sqrtf((float)D);
   const int group = e.n_heads / e.n_kv;
   for (int li = 0; li < e.n_layers; ++li) {
@@ -575,8 +655,11 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
         rmsnorm(xr, L.ffn_norm.data(), h.data() + (size_t)t * H, H, e.eps);
       }
     }); }
-    { Phase ph(&e.prof[5]); ffn_gate_up_silu(e, L.wgate, L.wup, h.data(), H, T, g.data(), F); }
-    { Phase ph(&e.prof[6]); matmul(e, L.wdown, g.data(), F, T, o.data(), H); }
+    if (e.n_experts > 0) { Phase ph(&e.prof[5]); moe_ffn(e, L, h.data(), T, o.data()); }
+    else {
+      { Phase ph(&e.prof[5]); ffn_gate_up_silu(e, L.wgate, L.wup, h.data(), H, T, g.data(), F); }
+      { Phase ph(&e.prof[6]); matmul(e, L.wdown, g.data(), F, T, o.data(), H); }
+    }
     Phase ph_res(&e.prof[4]);
     for (int t = 0; t < T; ++t) {
       float* xr = x + (size_t)t * H;
@@ -612,7 +695,7 @@ int argmax(const float* v, int n) {
 
 using namespace gbh;
 
-// Open a GGUF checkpoint of a dense qwen2 / qwen3 model for CPU inference.  threads <= 0: all cores.  NULL on error.
+// Open a GGUF checkpoint of a qwen2 / qwen3 / qwen3moe model for CPU inference.  threads <= 0: all cores.  NULL on error.
 // A decode step streams every matrix once; out of the file mapping that is one TLB miss per 4 KB.  Copy the matrices into one
 // anonymous region the kernel may back with 2 MB pages (the reference does the same at load: MADV_HUGEPAGE or a 2 MB-aligned
 // buffer, common/gguf_loader.h).  Every thread copies, and so first touches, a slice of every matrix.  GB_CPU_HUGEPAGES=0 keeps the mapping.
@@ -623,8 +706,15 @@ void place_weights(CpuEngine& e) {
   mats.push_back(&e.embed);
   const bool tied = e.head.data == e.embed.data;
   if (!tied) mats.push_back(&e.head);
-  for (Layer& L : e.layers)
-    for (QMat* m : {&L.wq, &L.wk, &L.wv, &L.wo, &L.wgate, &L.wup, &L.wdown}) mats.push_back(m);
+  for (Layer& L : e.layers) {
+    for (QMat* m : {&L.wq, &L.wk, &L.wv, &L.wo}) mats.push_back(m);
+    if (e.n_experts > 0) {
+      mats.push_back(&L.wrouter);
+      for (std::vector<QMat>* v : {&L.eg, &L.eu, &L.ed}) for (QMat& m : *v) mats.push_back(&m);
+    } else {
+      for (QMat* m : {&L.wgate, &L.wup, &L.wdown}) mats.push_back(m);
+    }
+  }
   size_t total = 0;
   std::vector<size_t> off;
   for (QMat* m : mats) { off.push_back(total); total += ((size_t)m->rows * m->row_bytes + 4095) & ~(size_t)4095; }
@@ -655,12 +745,22 @@ GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
   std::string arch = "qwen3";
   const int ai = gbh_gguf_find_key(g, "general.architecture");
   if (ai >= 0) { uint64_t len = 0; const char* s = gbh_gguf_kv_string(g, ai, -1, &len); if (s) arch.assign(s, (size_t)len); }
-  if (arch != "qwen2" && arch != "qwen3") { fail("cpu engine: architecture %s is not a dense qwen2 / qwen3 model", arch.c_str()); delete e; gbh_gguf_close(g); return nullptr; }
+  if (arch != "qwen2" && arch != "qwen3" && arch != "qwen3moe") {
+    fail("cpu engine: architecture %s is not qwen2 / qwen3 / qwen3moe", arch.c_str()); delete e; gbh_gguf_close(g); return nullptr;
+  }
   const std::string p = arch + ".";
   e->n_layers = (int)kv_num(g, p + "block_count", 0); e->hidden = (int)kv_num(g, p + "embedding_length", 0);
   e->n_heads = (int)kv_num(g, p + "attention.head_count", 0); e->n_kv = (int)kv_num(g, p + "attention.head_count_kv", e->n_heads);
   e->head_dim = (int)kv_num(g, p + "attention.key_length", e->n_heads ? e->hidden / e->n_heads : 0);
   e->ffn = (int)kv_num(g, p + "feed_forward_length", 0);
+  if (arch == "qwen3moe") {
+    e->n_experts = (int)kv_num(g, p + "expert_count", 0); e->n_used = (int)kv_num(g, p + "expert_used_count", 0);
+    e->expert_ffn = (int)kv_num(g, p + "expert_feed_forward_length", 0);
+    if (e->n_experts <= 0 || e->n_used <= 0 || e->n_used > e->n_experts || e->expert_ffn <= 0) {
+      fail("cpu engine: incomplete expert hyper-parameters in %s", path); delete e; gbh_gguf_close(g); return nullptr;
+    }
+    if (e->ffn <= 0) e->ffn = e->expert_ffn;
+  }
   e->eps = (float)kv_num(g, p + "attention.layer_norm_rms_epsilon", 1e-6); e->theta = (float)kv_num(g, p + "rope.freq_base", 1e6);
   e->max_seq = max_seq > 0 ? max_seq : 4096;
   e->threads = threads > 0 ? threads : (int)std::max(1u, std::thread::hardware_concurrency());
@@ -683,9 +783,15 @@ GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
     const std::string b = "blk." + std::to_string(li) + ".";
     ok = get_vec(g, b + "attn_norm.weight", &L.attn_norm, H) == 0 && get_vec(g, b + "ffn_norm.weight", &L.ffn_norm, H) == 0 &&
          get_mat(g, b + "attn_q.weight", &L.wq, e->n_heads * D, H) == 0 && get_mat(g, b + "attn_k.weight", &L.wk, e->n_kv * D, H) == 0 &&
-         get_mat(g, b + "attn_v.weight", &L.wv, e->n_kv * D, H) == 0 && get_mat(g, b + "attn_output.weight", &L.wo, H, e->n_heads * D) == 0 &&
-         get_mat(g, b + "ffn_gate.weight", &L.wgate, e->ffn, H) == 0 && get_mat(g, b + "ffn_up.weight", &L.wup, e->ffn, H) == 0 &&
-         get_mat(g, b + "ffn_down.weight", &L.wdown, H, e->ffn) == 0;
+         get_mat(g, b + "attn_v.weight", &L.wv, e->n_kv * D, H) == 0 && get_mat(g, b + "attn_output.weight", &L.wo, H, e->n_heads * D) == 0;
+    if (ok && e->n_experts > 0)
+      ok = get_mat(g, b + "ffn_gate_inp.weight", &L.wrouter, e->n_experts, H) == 0 &&
+           get_experts(g, b + "ffn_gate_exps.weight", &L.eg, e->n_experts, e->expert_ffn, H) == 0 &&
+           get_experts(g, b + "ffn_up_exps.weight", &L.eu, e->n_experts, e->expert_ffn, H) == 0 &&
+           get_experts(g, b + "ffn_down_exps.weight", &L.ed, e->n_experts, H, e->expert_ffn) == 0;
+    else if (ok)
+      ok = get_mat(g, b + "ffn_gate.weight", &L.wgate, e->ffn, H) == 0 && get_mat(g, b + "ffn_up.weight", &L.wup, e->ffn, H) == 0 &&
+           get_mat(g, b + "ffn_down.weight", &L.wdown, H, e->ffn) == 0;
     if (!ok) break;
     const int qn = get_vec(g, b + "attn_q_norm.weight", &L.q_norm, D, true);
     if (qn == 0) { e->qk_norm = true; ok = get_vec(g, b + "attn_k_norm.weight", &L.k_norm, D) == 0; } else if (qn < 0) ok = false;

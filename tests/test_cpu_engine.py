@@ -17,7 +17,8 @@ def _rel(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
-@pytest.mark.parametrize("name,wtype", [("tiny-dense", "Q8_0"), ("tiny-qwen2", "Q8_0"), ("tiny-dense", "Q4_K"), ("tiny-dense", "F16")])
+@pytest.mark.parametrize("name,wtype", [("tiny-dense", "Q8_0"), ("tiny-qwen2", "Q8_0"), ("tiny-dense", "Q4_K"), ("tiny-dense", "F16"),
+                                        ("tiny-moe", "Q8_0"), ("tiny-moe", "F16")])
 def test_logits_match_the_fp32_oracle(tmp_path, name, wtype):
     cfg = get_config(name)
     path = str(tmp_path / "m.gguf")
@@ -31,7 +32,7 @@ def test_logits_match_the_fp32_oracle(tmp_path, name, wtype):
     eng2 = CpuEngine(path, max_seq_len=64, threads=1)
     for i, t in enumerate(toks):                                # token by token on one thread: same cache, same logits
         got_seq = eng2.forward([t], i)
-    assert np.abs(got_seq - got_batched).max() < 1e-3 * max(1.0, np.abs(got_batched).max())
+    assert np.abs(got_seq - got_batched).max() < (2e-2 if cfg.is_moe else 1e-3) * max(1.0, np.abs(got_batched).max())   # MoE: a near-tie may route differently
     out, _, _ = eng.generate(toks, 5)
     out1, _, _ = eng2.generate(toks, 5)
     assert out == out1 and len(out) == 5
@@ -48,11 +49,22 @@ def test_greedy_tokens_equal_the_reference_engine(tmp_path):
     assert ref is not None and ours[0] == ref[0]
 
 
-def test_load_errors_are_reported(tmp_path):
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not available")
+def test_moe_greedy_tokens_equal_the_reference_engine(tmp_path):
     cfg = get_config("tiny-moe")
     path = str(tmp_path / "moe.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=4), path, "Q8_0")
+    prompt = torch.randint(0, cfg.vocab, (20,), generator=torch.Generator().manual_seed(5)).tolist()
+    ref = cpubench.run_reference(oracle.REF_ROOT, path, prompt, 10, threads=1)
+    ours = cpubench.run_ours(path, prompt, 10, threads=4)
+    assert ref is not None and ours[0] == ref[0]
+
+
+def test_load_errors_are_reported(tmp_path):
+    cfg = get_config("tiny-qwen35")
+    path = str(tmp_path / "hybrid.gguf")
     loader.save_gguf(cfg, RandomSource(cfg, seed=1), path, "Q8_0")
-    with pytest.raises(RuntimeError, match="dense"):
+    with pytest.raises(RuntimeError, match="architecture"):
         CpuEngine(path)
     eng_path = str(tmp_path / "d.gguf")
     cfg2 = get_config("tiny-dense")
