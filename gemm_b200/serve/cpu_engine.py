@@ -73,3 +73,28 @@ class CpuEngine:
             self.close()
         except Exception:
             pass
+
+
+class CpuEngineModel:
+    """The native engine behind the interface ``serve.sequential.SequentialLLM`` drives (``reset`` / ``forward`` on ``[1, T]`` ids,
+    logits of the last token), so that ``generate`` and the HTTP server run a GGUF checkpoint on a machine without a GPU, which is
+    what the reference's server does with its CPU engine (server/server_llm.c over common/transformer.h)."""
+
+    def __init__(self, gguf_path: str, max_seq_len: int = 4096, threads: int = 0):
+        import torch
+        self._torch = torch
+        self.engine = CpuEngine(gguf_path, max_seq_len=max_seq_len, threads=threads)
+        self.max_seq_len, self.pos = max_seq_len, 0
+
+    def reset(self, batch: int = 1, max_pos: int = 0) -> None:
+        if batch != 1:
+            raise ValueError("the CPU engine runs one sequence at a time")
+        if max_pos > self.max_seq_len:
+            raise ValueError(f"the request needs {max_pos} positions, the cache holds {self.max_seq_len}")
+        self.pos = 0                                             # the cache is overwritten from position 0 on
+
+    def forward(self, ids):
+        row = [int(v) for v in ids.reshape(-1).tolist()]
+        logits = self.engine.forward(row, self.pos)
+        self.pos += len(row)
+        return self._torch.from_numpy(logits)[None]

@@ -104,3 +104,37 @@ def test_portable_paths_give_the_same_logits(tmp_path):
     subprocess.run([sys.executable, "-c", code], check=True, env=env, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     there = np.load(out)
     assert np.abs(here - there).max() < 1e-3 * max(1.0, np.abs(here).max())
+
+
+def test_generate_and_server_on_the_native_engine(tmp_path, capsys):
+    """``generate --cpu-engine`` and the HTTP server over the native engine give the engine's own greedy tokens."""
+    import json
+    import urllib.request
+    from gemm_b200.__main__ import main
+    from gemm_b200.serve.cpu_engine import CpuEngineModel
+    from gemm_b200.serve.sequential import SequentialLLM
+    from gemm_b200.serve.server import serve
+    cfg = get_config("tiny-moe")
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=6), path, "Q8_0")
+    prompt = [5, 9, 200, 31, 7]
+    want, _, _ = CpuEngine(path, max_seq_len=64, threads=2).generate(prompt, 6)
+    main(["generate", "--model", path, "--cpu-engine", "--threads", "2", "--ids", "--prompt", " ".join(map(str, prompt)), "--max-new-tokens", "6",
+          "--pages", "4", "--page-size", "16"])
+    out = [json.loads(l) for l in capsys.readouterr().out.strip().splitlines()]
+    assert out[0]["token_ids"] == want
+    llm = SequentialLLM(CpuEngineModel(path, max_seq_len=64, threads=2), None, max_seq_len=64)
+    httpd, eng = serve(llm, port=0, block=False)
+    try:
+        req = urllib.request.Request(f"http://127.0.0.1:{httpd.server_address[1]}/v1/completions", data=json.dumps({"prompt": prompt, "max_tokens": 6}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        got = json.loads(urllib.request.urlopen(req, timeout=60).read())
+        assert got["token_ids"] == want
+    finally:
+        eng.stop_flag = True
+        httpd.shutdown()
+    with pytest.raises(SystemExit):
+        hyb = str(tmp_path / "h.gguf")
+        c2 = get_config("tiny-qwen35")
+        loader.save_gguf(c2, RandomSource(c2, seed=1), hyb, "Q8_0")
+        main(["generate", "--model", hyb, "--cpu-engine", "--ids", "--prompt", "1 2 3", "--max-new-tokens", "2"])
