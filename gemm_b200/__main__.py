@@ -207,6 +207,29 @@ def cmd_encode_audio(args):
     return 0
 
 
+def cmd_mesh(args):
+    """Scalar grid (.npy, [nx, ny, nz]) -> welded triangle mesh of its level set (PLY or OBJ), optionally a preview image of it
+    (the reference: common/marching_cubes.h mc_write_ply / mc_write_obj, common/preview_render.h)."""
+    import numpy as np
+    import torch
+    from . import geometry as geo
+    dev = "cuda" if torch.cuda.is_available() else "cpu"
+    grid = torch.from_numpy(np.load(args.grid).astype(np.float32)).to(dev)
+    verts, tris = geo.isosurface(grid, args.iso, bounds=args.bounds)
+    (geo.write_mesh_obj if args.out.endswith(".obj") else geo.write_mesh_ply)(args.out, verts, tris)
+    line = {"vertices": verts.shape[0], "triangles": tris.shape[0], "area": round(geo.mesh_area(verts, tris), 6), "volume": round(geo.mesh_volume(verts, tris), 6)}
+    if args.render and tris.shape[0]:
+        lo, hi = verts.min(0).values.cpu(), verts.max(0).values.cpu()
+        mid, rad = (lo + hi) / 2, float((hi - lo).norm()) / 2
+        eye = (float(mid[0]) + 0.8 * rad, float(mid[1]) + 0.9 * rad, float(mid[2]) - 2.6 * rad)
+        img = geo.Bvh(verts, tris, device=dev).render(eye, tuple(float(x) for x in mid), args.size, args.size)
+        geo.write_ppm(args.render, img["rgb"])
+        line["preview"] = args.render
+        line["coverage"] = round(float(img["mask"].mean()), 4)
+    print(json.dumps(line))
+    return 0
+
+
 def cmd_inspect(args):
     from .utils import gguf as G
     with G.GGUFFile(args.file) as f:
@@ -424,6 +447,14 @@ def main(argv=None):
     ea.add_argument("--max-seconds", type=float, default=30.0, help="cut the clip (0: keep all of it)")
     ea.add_argument("--out", default="", help="write the soft tokens ([tokens, 1536] f32) as .npy")
     ea.set_defaults(fn=cmd_encode_audio)
+    ms = sub.add_parser("mesh", help="level set of a scalar grid (.npy) as a triangle mesh, with an optional preview image")
+    ms.add_argument("--grid", required=True, help=".npy file, float [nx, ny, nz]; values below --iso are inside")
+    ms.add_argument("--iso", type=float, default=0.0)
+    ms.add_argument("--bounds", type=float, nargs=6, default=None, metavar=("XMIN", "YMIN", "ZMIN", "XMAX", "YMAX", "ZMAX"), help="extent of the grid (default: [-1, 1]^3)")
+    ms.add_argument("--out", required=True, help="mesh file, .ply (binary) or .obj")
+    ms.add_argument("--render", default="", help="also write a preview image (binary PPM)")
+    ms.add_argument("--size", type=int, default=256)
+    ms.set_defaults(fn=cmd_mesh)
     b = sub.add_parser("build", help="compile the native libraries")
     b.set_defaults(fn=cmd_build)
     args = ap.parse_args(argv)

@@ -82,9 +82,12 @@ def _build_lib(name, sources, compiler_cmd, link_cmd, hdr_time, force, verbose, 
     return out
 
 
+SHARED_HEADER = CSRC / "kernels" / "geometry.cuh"      # inline code the host library compiles too (host/geometry_host.cc)
+
+
 def build_host(force=False, verbose=False) -> Path:
     srcs = sorted((CSRC / "host").glob("*.cc"))
-    hdr = _newest_header([CSRC / "host"])
+    hdr = max(_newest_header([CSRC / "host"]), SHARED_HEADER.stat().st_mtime)
     cxx = os.environ.get("CXX", "g++")
     return _build_lib("libgb_host.so", srcs, [cxx] + CXX_FLAGS + ["-I", str(CSRC / "host")],
                       [cxx, "-shared", "-pthread"], hdr, force, verbose)
@@ -98,7 +101,7 @@ def build_host_sanitized(force=False, verbose=False) -> Path:
     ``GEMM_B200_HOST_LIB=libgb_host_san.so`` and the ASan runtime preloaded (``sanitizer_runtime()``); tests/test_host_sanitizers.py
     runs the host-side unit tests that way."""
     srcs = sorted((CSRC / "host").glob("*.cc"))
-    hdr = _newest_header([CSRC / "host"])
+    hdr = max(_newest_header([CSRC / "host"]), SHARED_HEADER.stat().st_mtime)
     cxx = _sanitizer_compiler()
     if cxx is None:
         raise RuntimeError("no C++ compiler with an AddressSanitizer runtime found")

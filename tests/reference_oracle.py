@@ -384,3 +384,16 @@ def ds4f_lib():
     lib.ref_window_idx_decode.restype = I
     lib.ref_rope_apply.argtypes = [P, P, P, I, I, I]
     return lib
+
+
+def geometry_lib():
+    """ctypes handle on the reference's marching-cubes extractor and Gaussian-splat PLY writer (common/marching_cubes.h,
+    common/gs_ply_writer.h)."""
+    src = ('#define MARCHING_CUBES_IMPLEMENTATION\n#include "marching_cubes.h"\n#define GS_PLY_WRITER_IMPLEMENTATION\n#include "gs_ply_writer.h"\n'
+           'int ref_mc(const float *grid, int nx, int ny, int nz, float iso, const float *bounds, float **verts, int **tris, int *nv, int *nt) {\n'
+           '  mc_mesh m = mc_marching_cubes(grid, nx, ny, nz, iso, bounds); *verts = m.vertices; *tris = m.triangles; *nv = m.n_verts; *nt = m.n_tris; return 0; }\n')
+    lib = _build("ref_geometry", src)
+    lib.ref_mc.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_float)),
+                           ctypes.POINTER(ctypes.POINTER(ctypes.c_int)), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+    lib.gs_ply_write.argtypes = [ctypes.c_char_p, ctypes.c_int] + [ctypes.c_void_p] * 6
+    return lib
