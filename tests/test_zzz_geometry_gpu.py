@@ -32,7 +32,7 @@ def test_geometry_kernels_equal_the_host_path():
     tdv, trid, uvd = bd.trace(o.to(dev), d.to(dev))
     hit = (trih >= 0) & (trid.cpu() >= 0)
     assert ((trid.cpu() >= 0) != (trih >= 0)).sum() <= 2          # a ray along an edge may fall either way (fused multiply-adds differ)
-    assert hit.float().mean() > 0.2 and torch.allclose(tdv.cpu()[hit], th[hit], atol=1e-4, rtol=1e-4)
+    assert hit.float().mean() > 0.1 and torch.allclose(tdv.cpu()[hit], th[hit], atol=1e-4, rtol=1e-4)
     assert ((bd.trace(o, d, any_hit=True)[1].cpu() >= 0) != (trih >= 0)).sum() <= 2
     q = torch.randn(4000, 3, generator=g)
     dh, _, ph, _ = bh.closest(q)
