@@ -111,6 +111,18 @@ class M3Model:
         self.cache: List[Dict[str, torch.Tensor]] = []
 
     # ------------------------------------------------------------------------------------------ state
+    def clone_runtime(self):
+        """Another runtime over the SAME weights with caches and position of its own: several sequences (or streams of a server)
+        advance independently at one copy of the parameters (common/glm5_impl.h:640-660 ``glm5_clone_runtime``; the subclasses
+        inherit it).  The clone starts empty; call ``reset`` on it."""
+        import copy
+        other = copy.copy(self)                                  # shares self.t, the tables and the configuration
+        other.pos, other.batch, other.cache = 0, 0, []
+        for name in ("comp", "icomp", "mtp_cache", "trace", "last_hc"):
+            if hasattr(other, name):
+                setattr(other, name, {} if name in ("comp", "icomp") else None)
+        return other
+
     def reset(self, batch: int = 1, max_pos: Optional[int] = None) -> None:
         cfg = self.cfg
         n = max_pos or cfg.max_pos

@@ -130,3 +130,33 @@ def test_checkpoint_round_trip_bf16_and_fp8(tmp_path):
     m3.save_checkpoint(c3, t3, d3)
     x = torch.randint(0, 96, (1, 20), generator=g)
     assert torch.equal(m3.load_checkpoint(d3).forward(x, all_logits=True), m3.M3Model(c3, t3).forward(x, all_logits=True))
+
+
+def test_runtime_clones_share_weights_and_keep_their_own_state():
+    import torch
+    from gemm_b200.models import ds4f, glm5, m3
+    cfg = glm5.GLM5Config(n_layers=2, n_dense_layers=1, hidden=32, vocab=120, n_heads=2, qk_nope_dim=8, qk_rope_dim=8, v_head_dim=16, q_lora=16,
+                          kv_lora=8, index_dim=8, index_n_heads=2, n_experts=4, n_active=2, moe_inter=16, dense_inter=32, max_pos=64)
+    a = glm5.GLM5Model(cfg, glm5.random_tensors(cfg, 3))
+    b = a.clone_runtime()
+    assert all(b.t[k].data_ptr() == a.t[k].data_ptr() for k in a.t)
+    g = torch.Generator().manual_seed(0)
+    s1, s2 = torch.randint(0, cfg.vocab, (1, 12), generator=g), torch.randint(0, cfg.vocab, (1, 9), generator=g)
+    a.reset(1, 32); b.reset(1, 32)
+    # interleaved steps of two different sequences on the two runtimes equal each sequence run alone
+    la = [a.forward(s1[:, :5])]; lb = [b.forward(s2[:, :4])]; la.append(a.forward(s1[:, 5:])); lb.append(b.forward(s2[:, 4:]))
+    alone = glm5.GLM5Model(cfg, glm5.random_tensors(cfg, 3))
+    alone.reset(1, 32); wa = alone.forward(s1)
+    alone.reset(1, 32); wb = alone.forward(s2)
+    assert torch.allclose(la[-1], wa, atol=1e-5) and torch.allclose(lb[-1], wb, atol=1e-5) and a.pos == 12 and b.pos == 9
+    # the DS4F engine's clone drops the compressor state as well
+    dcfg = ds4f.DS4FConfig(n_layers=2, hidden=64, vocab=96, n_heads=4, q_head_dim=32, qk_rope_dim=8, q_lora=32, kv_lora=32, o_groups=2, o_lora=16,
+                           n_experts=8, n_active=2, moe_inter=32, shared_inter=32, window_size=6, max_pos=64, original_seq_len=16, hc_iters=5,
+                           compress_ratios=[0, 4], tierb2=True, index_n_heads=4, index_head_dim=32, index_topk=3)
+    d = ds4f.DS4FModel(dcfg, ds4f.random_tensors(dcfg, 1))
+    ids = torch.randint(0, dcfg.vocab, (1, 20), generator=g)
+    d.reset(1, 32); want = d.forward(ids)
+    e = d.clone_runtime()
+    assert e.comp == {} and e.cache == []
+    e.reset(1, 32)
+    assert torch.allclose(e.forward(ids), want, atol=1e-5) and e.comp[1] is not d.comp[1]
