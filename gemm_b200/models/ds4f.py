@@ -407,11 +407,15 @@ class DS4FModel(m3.M3Model):
             xe = x[rows]
             act = self._swiglu(xe @ tt[p + "ex_w1"][slot].t(), xe @ tt[p + "ex_w3"][slot].t())
             route.index_add_(0, rows, (act @ tt[p + "ex_w2"][slot].t()).float() * (w * hit)[rows].sum(-1, keepdim=True))
-        if self.ep_size > 1 and self.group is not None:
+        pending = None
+        if self.ep_size > 1 and self.group is not None:          # the reduce over the ranks overlaps the shared expert
             import torch.distributed as dist
-            dist.all_reduce(route, group=self.group)
-        if (p + "sh_w1") in tt:
-            route = route + (self._swiglu(x @ tt[p + "sh_w1"].t(), x @ tt[p + "sh_w3"].t()) @ tt[p + "sh_w2"].t()).float()
+            pending = dist.all_reduce(route, group=self.group, async_op=True)
+        sh = (self._swiglu(x @ tt[p + "sh_w1"].t(), x @ tt[p + "sh_w3"].t()) @ tt[p + "sh_w2"].t()).float() if (p + "sh_w1") in tt else None
+        if pending is not None:
+            pending.wait()
+        if sh is not None:
+            route = route + sh
         return route.reshape(b, t, h)
 
     # ------------------------------------------------------------------------------------------ forward

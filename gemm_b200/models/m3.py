@@ -239,10 +239,13 @@ class M3Model:
             act = self._swiglu(xe @ tt[p + "ex_w1"][slot].t(), xe @ tt[p + "ex_w3"][slot].t())
             ye = (act @ tt[p + "ex_w2"][slot].t()).float()
             route.index_add_(0, rows, ye * (w * hit)[rows].sum(-1, keepdim=True))
-        if self.ep_size > 1 and self.group is not None:
-            import torch.distributed as dist
-            dist.all_reduce(route, group=self.group)
+        pending = None
+        if self.ep_size > 1 and self.group is not None:          # the sum over the ranks runs while this rank computes the shared
+            import torch.distributed as dist                     # expert (a64fx/m3/m3_ep_runner.c:143-169 does the same with its
+            pending = dist.all_reduce(route, group=self.group, async_op=True)     # asynchronous reduce)
         sh = self._swiglu(x @ tt[p + "sh_w1"].t(), x @ tt[p + "sh_w3"].t()) @ tt[p + "sh_w2"].t()
+        if pending is not None:
+            pending.wait()
         return (route + sh.float()).reshape(b, t, h).to(h2.dtype)
 
     # ------------------------------------------------------------------------------------------ forward
