@@ -78,6 +78,29 @@ def run_ours(path: str, prompt: List[int], max_new: int, threads: int) -> Tuple[
         eng.close()
 
 
+def run_profile(path: str, prompt: List[int], max_new: int, threads: int) -> dict:
+    """Milliseconds per phase of the native engine: one batched prefill of the prompt, then ``max_new`` single-token steps (per token)."""
+    from ..serve.cpu_engine import CpuEngine
+    eng = CpuEngine(path, max_seq_len=len(prompt) + max_new + 8, threads=threads)
+    try:
+        eng.forward(prompt[: min(8, len(prompt))], 0)                        # warm-up: pages touched, threads started
+        eng.profile()
+        t0 = time.perf_counter()
+        eng.forward(prompt, 0)
+        t1 = time.perf_counter()
+        pre = eng.profile()
+        pos = len(prompt)
+        for _ in range(max_new):
+            eng.forward([1], pos)
+            pos += 1
+        t2 = time.perf_counter()
+        dec = eng.profile()
+    finally:
+        eng.close()
+    return {"threads": threads, "prefill_ms": round((t1 - t0) * 1e3, 2), "prefill_phases_ms": {k: round(v * 1e3, 2) for k, v in pre.items()},
+            "decode_ms_per_token": round((t2 - t1) / max_new * 1e3, 3), "decode_phases_ms_per_token": {k: round(v / max_new * 1e3, 3) for k, v in dec.items()}}
+
+
 def run_reference(ref_root: str, path: str, prompt: List[int], max_new: int, threads: int) -> Optional[Tuple[List[int], float, float]]:
     """The reference CPU engine on the same file (None when its tree or gcc is missing)."""
     if not os.path.isdir(os.path.join(ref_root, "common")) or shutil.which("gcc") is None:
@@ -112,6 +135,7 @@ def main(argv=None) -> int:
     ap.add_argument("--threads", type=int, default=os.cpu_count() or 1)
     ap.add_argument("--gguf", default="", help="checkpoint to use (default: write the synthetic one to a temporary file)")
     ap.add_argument("--reference-root", default=os.environ.get("GEMM_REFERENCE_ROOT", ""), help="source tree of the reference project (optional)")
+    ap.add_argument("--profile", action="store_true", help="print the native engine's time per phase (prefill, and per decoded token) instead of the comparison")
     ap.add_argument("--repeat", type=int, default=3, help="runs per arm, alternating; the fastest prefill and the fastest decode of each arm are "
                     "reported (other jobs on the machine only ever slow a run down)")
     args = ap.parse_args(argv)
@@ -127,6 +151,12 @@ def main(argv=None) -> int:
         print(f"[cpubench] wrote {path} ({os.path.getsize(path) / 2**20:.0f} MiB) in {time.time() - t0:.1f}s")
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist()
+    if args.profile:
+        print(json.dumps({"config": {"model": args.model, "layers": args.layers or cfg.n_layers, "wtype": args.wtype, "prompt_len": args.prompt_len,
+                                     "new_tokens": args.new, "file_mib": round(os.path.getsize(path) / 2**20, 1)}, **run_profile(path, prompt, args.new, args.threads)}))
+        if tmp is not None:
+            shutil.rmtree(tmp, ignore_errors=True)
+        return 0
     toks, tp, td = run_ours(path, prompt, args.new, args.threads)
     ref = run_reference(args.reference_root, path, prompt, args.new, args.threads) if args.reference_root else None
     for _ in range(max(0, args.repeat - 1)):
