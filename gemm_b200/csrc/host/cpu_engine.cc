@@ -127,7 +127,7 @@ struct CpuEngine {
   std::vector<Layer> layers;
   std::vector<float> final_norm, inv_freq;
   QMat embed, head;
-  std::vector<float> kc, vc;       // [layer][pos][n_kv * head_dim]
+  std::vector<float> kc, vc;       // [layer][kv head][pos][head_dim]: the positions of one head are contiguous, a decode step streams them
   double t_prefill = 0, t_decode = 0;
   // seconds per phase since the last reset (gbh_cpu_engine_profile): qkv, rope + cache write, attention, o_proj, norms + residual adds,
   // gate / up + SiLU, down, head (final norm + LM head), embedding
@@ -618,8 +618,10 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
         if (e.qk_norm) rmsnorm(kh, L.k_norm.data(), kh, D, e.eps);
         rope_neox(kh, D, pos, e.inv_freq.data());
       }
-      memcpy(kc + (size_t)pos * KD, k.data() + (size_t)t * KD, sizeof(float) * KD);
-      memcpy(vc + (size_t)pos * KD, v.data() + (size_t)t * KD, sizeof(float) * KD);
+      for (int hk = 0; hk < e.n_kv; ++hk) {
+        memcpy(kc + ((size_t)hk * e.max_seq + pos) * D, k.data() + (size_t)t * KD + hk * D, sizeof(float) * D);
+        memcpy(vc + ((size_t)hk * e.max_seq + pos) * D, v.data() + (size_t)t * KD + hk * D, sizeof(float) * D);
+      }
     }
     }); }
     // causal attention: token t sees positions 0 .. pos0 + t
@@ -632,7 +634,9 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
         const int n_ctx = pos0 + t + 1, hk = hq / group;
         const float* qh = q.data() + (size_t)t * QD + hq * D;
         float mx = -INFINITY;
-        for (int p = 0; p < n_ctx; ++p) { sc[p] = dot_f32(qh, kc + (size_t)p * KD + hk * D, D) * scale; mx = std::max(mx, sc[p]); }
+        const float* kh = kc + (size_t)hk * e.max_seq * D;
+        const float* vhead = vc + (size_t)hk * e.max_seq * D;
+        for (int p = 0; p < n_ctx; ++p) { sc[p] = dot_f32(qh, kh + (size_t)p * D, D) * scale; mx = std::max(mx, sc[p]); }
         float sum = 0.f;
         for (int p = 0; p < n_ctx; ++p) { sc[p] = expf(sc[p] - mx); sum += sc[p]; }
         const float inv = 1.0f / sum;
@@ -640,7 +644,7 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
         for (int d = 0; d < D; ++d) out[d] = 0.f;
         for (int p = 0; p < n_ctx; ++p) {
           const float w = sc[p] * inv;
-          const float* vh = vc + (size_t)p * KD + hk * D;
+          const float* vh = vhead + (size_t)p * D;
           for (int d = 0; d < D; ++d) out[d] += w * vh[d];
         }
       }
