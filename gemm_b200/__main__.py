@@ -178,6 +178,9 @@ def cmd_encode_image(args):
     dev = "cuda" if torch.cuda.is_available() else "cpu"
     enc = vision.load_gguf(args.mmproj, dev, torch.bfloat16 if dev == "cuda" else torch.float32)
     cell = enc.cfg.patch_size * enc.cfg.spatial_merge
+    if args.max_side > 0 and max(rgb.shape[0], rgb.shape[1]) > args.max_side:
+        f = args.max_side / max(rgb.shape[0], rgb.shape[1])
+        rgb = vision.resize_image(rgb, max(cell, int(rgb.shape[0] * f)), max(cell, int(rgb.shape[1] * f)))
     h, w = rgb.shape[0] // cell * cell, rgb.shape[1] // cell * cell
     feats = enc.encode(enc.normalize_image(rgb[:h, :w].to(dev)))
     if args.out:
@@ -438,7 +441,8 @@ def main(argv=None):
     dp.set_defaults(fn=cmd_dump)
     ei = sub.add_parser("encode-image", help="run the Qwen3-VL vision encoder (mmproj GGUF) on an image")
     ei.add_argument("--mmproj", required=True, help="GGUF file of the vision encoder")
-    ei.add_argument("--image", required=True, help=".npy (uint8 [H, W, 3]) or binary PPM (P6)")
+    ei.add_argument("--image", required=True, help="PNG, baseline JPEG, binary PPM (P6) or .npy (uint8 [H, W, 3])")
+    ei.add_argument("--max-side", type=int, default=0, help="shrink the image so that its longer side is at most this many pixels (0: keep)")
     ei.add_argument("--out", default="", help="write the features ([tokens, proj_dim * (1 + deepstack)] f32) as .npy")
     ei.set_defaults(fn=cmd_encode_image)
     ea = sub.add_parser("encode-audio", help="run the Gemma4 audio encoder (safetensors checkpoint) on a 16 kHz WAV file")

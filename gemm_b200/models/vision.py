@@ -202,9 +202,91 @@ class VisionEncoder:
         return embeds, ds
 
 
+def _decode_png(data: bytes) -> torch.Tensor:
+    """8-bit non-interlaced PNG (grey, grey + alpha, RGB, RGBA, palette) -> uint8 [H, W, 3]; alpha is dropped.  The container and
+    the inflate step are handled here, the scanline filters by the host library (csrc/host/image.cc)."""
+    import ctypes
+    import struct
+    import zlib
+    from .. import _native
+    pos, idat, plte, hdr = 8, [], None, None
+    while pos + 8 <= len(data):
+        n, kind = struct.unpack(">I4s", data[pos: pos + 8])
+        body = data[pos + 8: pos + 8 + n]
+        if kind == b"IHDR":
+            if len(body) != 13:
+                raise ValueError("PNG header of the wrong size")
+            hdr = struct.unpack(">IIBBBBB", body)
+        elif kind == b"PLTE":
+            if len(body) % 3 or not body:
+                raise ValueError("PNG palette of the wrong size")
+            plte = torch.frombuffer(bytearray(body), dtype=torch.uint8).reshape(-1, 3)
+        elif kind == b"IDAT":
+            idat.append(body)
+        elif kind == b"IEND":
+            break
+        pos += 12 + n
+    if hdr is None or not idat:
+        raise ValueError("PNG without header or data")
+    wd, ht, depth, ctype, _, _, interlace = hdr
+    channels = {0: 1, 2: 3, 3: 1, 4: 2, 6: 4}.get(ctype)
+    if depth != 8 or channels is None or interlace != 0:
+        raise ValueError("only 8-bit non-interlaced PNG files are read")
+    row = wd * channels
+    if wd <= 0 or ht <= 0 or wd * ht > (1 << 26):
+        raise ValueError(f"PNG of {wd} x {ht} pixels is not read (64 Mpixel at most)")
+    try:
+        raw = zlib.decompressobj().decompress(b"".join(idat), ht * (row + 1) + 1)      # bounded: the header says how much there is
+    except zlib.error as e:
+        raise ValueError(f"PNG data: {e}")
+    if len(raw) != ht * (row + 1):
+        raise ValueError("PNG data does not match its header")
+    out = torch.empty(ht, wd, channels, dtype=torch.uint8)
+    src = torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+    if _native.host().gbh_png_unfilter(ctypes.c_void_p(src.data_ptr()), ctypes.c_long(ht), ctypes.c_long(row), ctypes.c_int(channels),
+                                       ctypes.c_void_p(out.data_ptr())) != 0:
+        raise ValueError(_native.host().gbh_last_error().decode(errors="replace"))
+    if ctype == 3:
+        if plte is None:
+            raise ValueError("palette PNG without a palette")
+        if int(out.max()) >= plte.shape[0]:
+            raise ValueError("PNG pixel names a colour outside its palette")
+        return plte[out[..., 0].long()].contiguous()
+    if ctype in (0, 4):
+        return out[..., :1].expand(ht, wd, 3).contiguous()
+    return out[..., :3].contiguous()
+
+
+def _decode_jpeg(data: bytes) -> torch.Tensor:
+    """Baseline JPEG -> uint8 [H, W, 3] through the host library's decoder (csrc/host/image.cc)."""
+    import ctypes
+    from .. import _native
+    lib = _native.host()
+    buf = torch.frombuffer(bytearray(data), dtype=torch.uint8)
+    w, h, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    if lib.gbh_jpeg_info(ctypes.c_void_p(buf.data_ptr()), ctypes.c_long(len(data)), ctypes.byref(w), ctypes.byref(h), ctypes.byref(c)) != 0:
+        raise ValueError(lib.gbh_last_error().decode(errors="replace"))
+    out = torch.empty(h.value, w.value, 3, dtype=torch.uint8)
+    if lib.gbh_jpeg_decode(ctypes.c_void_p(buf.data_ptr()), ctypes.c_long(len(data)), ctypes.c_void_p(out.data_ptr())) != 0:
+        raise ValueError(lib.gbh_last_error().decode(errors="replace"))
+    return out
+
+
+def resize_image(rgb: torch.Tensor, height: int, width: int) -> torch.Tensor:
+    """uint8 [H, W, 3] -> uint8 [height, width, 3], bilinear with anti-aliasing when shrinking (the reference's server resizes
+    with an area filter before it encodes, cuda/llm/test_gemma4_st.c:165-168)."""
+    x = rgb.permute(2, 0, 1)[None].float()
+    y = torch.nn.functional.interpolate(x, size=(height, width), mode="bilinear", antialias=True, align_corners=False)
+    return y[0].permute(1, 2, 0).round().clamp(0, 255).to(torch.uint8).contiguous()
+
+
 def decode_image(data: bytes) -> torch.Tensor:
-    """uint8 ``[H, W, 3]`` from the bytes of a binary PPM (P6, maxval 255) or of a ``.npy`` file holding such an array (the two
-    formats this framework reads without an image library)."""
+    """uint8 ``[H, W, 3]`` from the bytes of a PNG, a baseline JPEG, a binary PPM (P6, maxval 255) or a ``.npy`` file holding such an
+    array; no image library is involved."""
+    if data[:8] == b"\x89PNG\r\n\x1a\n":
+        return _decode_png(data)
+    if data[:2] == b"\xff\xd8":
+        return _decode_jpeg(data)
     if data[:6] == b"\x93NUMPY":
         import io
         import numpy as np
@@ -227,7 +309,7 @@ def decode_image(data: bytes) -> torch.Tensor:
         parts.append(data[pos:end])
         pos = end
     if parts[0] != b"P6" or int(parts[3]) != 255:
-        raise ValueError("only binary PPM (P6) with maxval 255, or .npy, is read")
+        raise ValueError("only PNG, baseline JPEG, binary PPM (P6, maxval 255) and .npy images are read")
     wd, ht = int(parts[1]), int(parts[2])
     body = data[pos + 1: pos + 1 + wd * ht * 3]
     if len(body) != wd * ht * 3:

@@ -143,7 +143,7 @@ def make_handler(engine: EngineThread, model_name: str):
             extra = {}
             image_b64 = req.get("image")
             if image_b64 is not None:
-                # one image per request: base64 of a binary PPM or a .npy (uint8 [H, W, 3]); the text is split at "<image>" (the image
+                # one image per request: base64 of a PNG, a baseline JPEG, a binary PPM or a .npy (uint8 [H, W, 3]); the text is split at "<image>" (the image
                 # comes first when the marker is absent), as the reference's server feeds tokens, vision rows, tokens
                 # (server/server_llm.c:503-548)
                 if engine.vision is None or llm.tokenizer is None or not hasattr(llm, "w"):
@@ -154,6 +154,10 @@ def make_handler(engine: EngineThread, model_name: str):
                     rgb = V.decode_image(base64.b64decode(image_b64))
                     enc = engine.vision
                     cell = enc.cfg.patch_size * enc.cfg.spatial_merge
+                    side = int(req.get("image_max_side", enc.cfg.image_size))
+                    if max(rgb.shape[0], rgb.shape[1]) > side:   # larger than the encoder's grid: shrink, keeping the aspect ratio
+                        f = side / max(rgb.shape[0], rgb.shape[1])
+                        rgb = V.resize_image(rgb, max(cell, int(rgb.shape[0] * f)), max(cell, int(rgb.shape[1] * f)))
                     h, w = rgb.shape[0] // cell * cell, rgb.shape[1] // cell * cell
                     feats = enc.encode(enc.normalize_image(rgb[:h, :w]))
                 except Exception as e:                         # a bad image is the client's error, not the server's

@@ -1,4 +1,4 @@
-"""The host-side C++ (GGUF reader / writer, dequantisers, tokenizer, block manager, scheduler, CPU engine, geometry helpers) under
+"""The host-side C++ (GGUF reader / writer, dequantisers, tokenizer, block manager, scheduler, CPU engine, geometry helpers, image decoders) under
 AddressSanitizer + UndefinedBehaviorSanitizer: ``gemm_b200.build.build_host_sanitized`` compiles the same sources into
 ``_lib/libgb_host_san.so``, and the unit tests of that code run once more in a child interpreter with the ASan runtime
 preloaded and ``GEMM_B200_HOST_LIB`` pointing at the instrumented build.  Any report aborts the child."""
@@ -11,7 +11,7 @@ import pytest
 from gemm_b200 import build
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-FILES = ["test_runtime_cpu.py", "test_gguf_cpu.py", "test_tokenizer_cpu.py", "test_cpu_engine.py", "test_geometry_cpu.py"]
+FILES = ["test_runtime_cpu.py", "test_gguf_cpu.py", "test_tokenizer_cpu.py", "test_cpu_engine.py", "test_geometry_cpu.py", "test_image_decode_cpu.py"]
 
 CHILD = r"""
 import sys, pytest

@@ -208,3 +208,41 @@ def test_multimodal_requests_through_llm_and_server():
     finally:
         engine.stop_flag = True
         httpd.shutdown()
+
+
+def test_png_and_jpeg_decoding_and_resize():
+    """PNG (all 8-bit colour types) bit-exact and baseline JPEG (4:4:4, 4:2:2, 4:2:0, grey, restart markers, optimised tables) within
+    rounding of a reference decoder; progressive files are refused with a message; resizing keeps flat colours."""
+    import io
+    Image = pytest.importorskip("PIL.Image")
+    g = np.random.default_rng(0)
+    yy, xx = np.mgrid[0:75, 0:101]
+    img = np.stack([(127 + 100 * np.sin(xx / 9.0) * np.cos(yy / 7.0)), (xx * 2.3) % 256, (yy * 3.1 + xx) % 256], -1).astype(np.uint8)
+    img[20:40, 30:60] = g.integers(0, 256, (20, 30, 3))
+    for mode in ("RGB", "RGBA", "L", "LA", "P"):
+        im = Image.fromarray(img).convert(mode)
+        buf = io.BytesIO()
+        im.save(buf, "PNG")
+        assert torch.equal(vision.decode_image(buf.getvalue()), torch.from_numpy(np.array(im.convert("RGB")))), mode
+    cases = [("RGB", dict(quality=90, subsampling=0), 2.5, 0.1), ("RGB", dict(quality=85, subsampling=2), 6.0, 0.8), ("RGB", dict(quality=75, subsampling=1), 6.0, 0.8),
+             ("RGB", dict(quality=95, subsampling=0, optimize=True), 2.5, 0.1), ("RGB", dict(quality=80, subsampling=2, restart_marker_blocks=5), 6.0, 0.8),
+             ("L", dict(quality=90), 2.5, 0.2)]
+    for mode, kw, worst, mean in cases:
+        buf = io.BytesIO()
+        Image.fromarray(img).convert(mode).save(buf, "JPEG", **kw)
+        got = vision.decode_image(buf.getvalue()).float()
+        want = torch.from_numpy(np.array(Image.open(io.BytesIO(buf.getvalue())).convert("RGB"))).float()
+        d = (got - want).abs()
+        assert got.shape == (75, 101, 3) and d.max() <= worst and d.mean() <= mean, (kw, d.max().item(), d.mean().item())
+    buf = io.BytesIO()
+    Image.fromarray(img).save(buf, "JPEG", progressive=True)
+    with pytest.raises(ValueError, match="progressive"):
+        vision.decode_image(buf.getvalue())
+    with pytest.raises(ValueError):
+        vision.decode_image(b"\x89PNG\r\n\x1a\n" + b"\0" * 20)
+    flat = torch.full((60, 90, 3), 77, dtype=torch.uint8)
+    small = vision.resize_image(flat, 20, 32)
+    assert small.shape == (20, 32, 3) and (small == 77).all()
+    ramp = torch.arange(64, dtype=torch.uint8)[None, :, None].expand(8, 64, 3).contiguous()
+    half = vision.resize_image(ramp, 8, 32)[0, :, 0].float()
+    assert (half[1:] >= half[:-1]).all() and abs(float(half.mean()) - 31.5) < 1.0
