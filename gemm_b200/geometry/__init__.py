@@ -4,6 +4,7 @@
   the binary file (the reference: common/gs_ply_writer.h);
 * ``isosurface``: triangle mesh of a level set of a scalar grid, welded (the reference: common/marching_cubes.h; here by
   tetrahedra, see csrc/kernels/geometry.cuh), ``write_mesh_ply`` / ``write_mesh_obj``, ``mesh_volume`` / ``mesh_area``;
+* ``dual_grid_mesh``: mesh of a sparse "flexible dual grid" prediction (the reference: common/trellis2_fdg_mesh.h);
 * ``Bvh``: bounding-volume hierarchy over a triangle mesh with ``trace`` (closest or any hit of rays), ``closest`` (closest point
   and barycentric weights, the reference: common/closest_point_bvh.h) and ``render`` (preview image with depth / normal / mask,
   the reference: common/preview_render.h), ``write_ppm``.
@@ -256,3 +257,46 @@ def write_ppm(path: str, rgb: torch.Tensor, gamma: float = 2.2) -> None:
     with open(path, "wb") as fh:
         fh.write(b"P6\n%d %d\n255\n" % (img.shape[1], img.shape[0]))
         fh.write(img.numpy().tobytes())
+
+
+# ------------------------------------------------------------------------------------------------------ dual grid
+_EDGE_NEIGHBOURS = (((0, 0, 0), (0, 0, 1), (0, 1, 1), (0, 1, 0)),      # the four voxels (z, y, x offsets) around a voxel's x edge,
+                    ((0, 0, 0), (1, 0, 0), (1, 0, 1), (0, 0, 1)),      # its y edge,
+                    ((0, 0, 0), (0, 1, 0), (1, 1, 0), (1, 0, 0)))      # its z edge
+
+
+def dual_grid_mesh(coords: torch.Tensor, feats: torch.Tensor, voxel_size: float, aabb: Sequence[float]) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Mesh of a sparse "flexible dual grid" prediction (common/trellis2_fdg_mesh.h:139-222): ``coords`` int [N, 3] voxel indices
+    (z, y, x), ``feats`` [N, 7] = vertex offset inside the voxel (x, y, z in 0..1), one crossing flag per axis (> 0: the voxel's edge
+    along that axis crosses the surface), a split weight.  Every voxel contributes one vertex; every crossed edge whose four
+    surrounding voxels all exist contributes a quad over their vertices, cut along the diagonal whose two split weights have the
+    larger product.  Returns ``(vertices f32 [N, 3], triangles i32 [M, 3])`` in the reference's order (voxel by voxel, axis by axis).
+    Sorting and binary search take the place of the reference's hash table, so the same code runs on a GPU."""
+    c = coords.to(torch.int64)
+    f = feats.to(torch.float32)
+    n, dev = c.shape[0], c.device
+    lo = torch.tensor([float(v) for v in aabb[:3]], dtype=torch.float32, device=dev)
+    verts = (c[:, [2, 1, 0]].float() + f[:, :3]) * voxel_size + lo
+    if n == 0:
+        return verts, torch.zeros(0, 3, dtype=torch.int32, device=dev)
+    key = lambda z, y, x: (z << 40) | ((y & 0xFFFFF) << 20) | (x & 0xFFFFF)
+    keys, order = torch.sort(key(c[:, 0], c[:, 1], c[:, 2]))
+    tris, tags = [], []
+    for axis in range(3):
+        rows = (f[:, 3 + axis] > 0).nonzero(as_tuple=True)[0]
+        quad, ok = [], torch.ones(rows.numel(), dtype=torch.bool, device=dev)
+        for dz, dy, dx in _EDGE_NEIGHBOURS[axis]:
+            want = key(c[rows, 0] + dz, c[rows, 1] + dy, c[rows, 2] + dx)
+            at = torch.searchsorted(keys, want).clamp_max(n - 1)
+            ok &= keys[at] == want
+            quad.append(order[at])
+        q = torch.stack(quad, 1)[ok]
+        rows = rows[ok]
+        w = f[:, 6]
+        first = (w[q[:, 0]] * w[q[:, 2]] > w[q[:, 1]] * w[q[:, 3]])[:, None]
+        a = torch.where(first, q[:, [0, 1, 2]], q[:, [0, 1, 3]])
+        b = torch.where(first, q[:, [0, 2, 3]], q[:, [3, 1, 2]])
+        tris.append(torch.stack([a, b], 1).reshape(-1, 3))
+        tags.append((rows * 3 + axis).repeat_interleave(2) * 2 + torch.arange(2, device=dev).repeat(rows.numel()))
+    tris, tags = torch.cat(tris), torch.cat(tags)
+    return verts, tris[torch.argsort(tags)].to(torch.int32).contiguous()

@@ -390,10 +390,15 @@ def geometry_lib():
     """ctypes handle on the reference's marching-cubes extractor and Gaussian-splat PLY writer (common/marching_cubes.h,
     common/gs_ply_writer.h)."""
     src = ('#define MARCHING_CUBES_IMPLEMENTATION\n#include "marching_cubes.h"\n#define GS_PLY_WRITER_IMPLEMENTATION\n#include "gs_ply_writer.h"\n'
+           '#define T2_FDG_MESH_IMPLEMENTATION\n#include "trellis2_fdg_mesh.h"\n'
+           'int ref_fdg(const int *coords, const float *feats, int n, float voxel, const float *aabb, float **verts, int **tris, int *nt) {\n'
+           '  t2_fdg_mesh m = t2_fdg_to_mesh(coords, feats, n, voxel, aabb); *verts = m.vertices; *tris = m.triangles; *nt = m.n_tris; return m.n_verts; }\n'
            'int ref_mc(const float *grid, int nx, int ny, int nz, float iso, const float *bounds, float **verts, int **tris, int *nv, int *nt) {\n'
            '  mc_mesh m = mc_marching_cubes(grid, nx, ny, nz, iso, bounds); *verts = m.vertices; *tris = m.triangles; *nv = m.n_verts; *nt = m.n_tris; return 0; }\n')
     lib = _build("ref_geometry", src)
     lib.ref_mc.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_float)),
                            ctypes.POINTER(ctypes.POINTER(ctypes.c_int)), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
     lib.gs_ply_write.argtypes = [ctypes.c_char_p, ctypes.c_int] + [ctypes.c_void_p] * 6
+    lib.ref_fdg.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_float)),
+                            ctypes.POINTER(ctypes.POINTER(ctypes.c_int)), ctypes.POINTER(ctypes.c_int)]
     return lib

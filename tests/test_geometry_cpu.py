@@ -208,3 +208,27 @@ def test_mesh_command(tmp_path, capsys):
     v, _, f = geo.read_ply(str(tmp_path / "m.ply"))
     assert v.shape[0] == line["vertices"] and f.shape[0] == line["triangles"]
     assert open(tmp_path / "p.ppm", "rb").read(2) == b"P6"
+
+
+@needs_ref
+def test_dual_grid_mesh_equals_the_reference():
+    """A sparse shell of voxels around a sphere with random offsets, crossing flags and split weights: vertices and triangles equal
+    the reference's, in its order."""
+    lib = oracle.geometry_lib()
+    g = torch.Generator().manual_seed(4)
+    zz, yy, xx = torch.meshgrid(torch.arange(20), torch.arange(20), torch.arange(20), indexing="ij")
+    r = ((zz - 9.5) ** 2 + (yy - 9.5) ** 2 + (xx - 9.5) ** 2).float().sqrt()
+    shell = (r > 5.5) & (r < 8.0)
+    coords = torch.stack([zz[shell], yy[shell], xx[shell]], 1).to(torch.int32)
+    coords = coords[torch.randperm(coords.shape[0], generator=g)].contiguous()                  # no order assumed
+    n = coords.shape[0]
+    feats = torch.cat([torch.rand(n, 3, generator=g), torch.randn(n, 3, generator=g), torch.rand(n, 1, generator=g)], 1).contiguous()
+    aabb = torch.tensor([-0.5, -0.4, -0.3, 0.5, 0.6, 0.7])
+    vp, tp, nt = ctypes.POINTER(ctypes.c_float)(), ctypes.POINTER(ctypes.c_int)(), ctypes.c_int()
+    nv = lib.ref_fdg(coords.data_ptr(), feats.data_ptr(), n, 0.05, aabb.data_ptr(), ctypes.byref(vp), ctypes.byref(tp), ctypes.byref(nt))
+    rv = torch.from_numpy(np.ctypeslib.as_array(vp, shape=(nv, 3)).copy())
+    rt = torch.from_numpy(np.ctypeslib.as_array(tp, shape=(nt.value, 3)).copy())
+    v, t = geo.dual_grid_mesh(coords, feats, 0.05, aabb.tolist())
+    assert nt.value > 1000 and torch.allclose(v, rv, atol=1e-6) and torch.equal(t, rt)
+    ev, et = geo.dual_grid_mesh(coords[:0], feats[:0], 0.05, aabb.tolist())
+    assert ev.shape == (0, 3) and et.shape == (0, 3)
