@@ -121,7 +121,8 @@ GBH_API void gbh_geo_closest(const float* verts, const int* tris, const void* no
   }
 }
 
-// cam: org fwd right up [12] + tan(fov / 2); light: sun_dir sun_rgb zenith_rgb horizon_rgb [12]; images are [height][width](x 3)
+// cam: org fwd right up [12] + tan(fov / 2); light: sun_dir sun_rgb zenith_rgb horizon_rgb [12]; albedo: diffuse rgb, roughness,
+// normal reflectance [5]; images are [height][width](x 3)
 GBH_API void gbh_geo_render(const float* verts, const int* tris, const void* nodes, const int* order, int n_nodes, const float* cam, int width, int height,
                             const float* light, const float* albedo, float* rgb, float* depth, float* normal, float* mask) {
   const Mesh m = mesh_of(verts, tris, nodes, order, n_nodes);

@@ -75,7 +75,7 @@ __global__ void closest_kernel(MeshArg a, long n_points, const float* pts, float
   for (int i = 0; i < 3; ++i) { out_point[3 * r + i] = cp[i]; out_w[3 * r + i] = w[i]; }
 }
 
-struct RenderArg { Camera cam; Light light; float albedo[3]; };
+struct RenderArg { Camera cam; Light light; float albedo[5]; };   // diffuse rgb, roughness, normal reflectance
 
 __global__ void render_kernel(MeshArg a, RenderArg ra, float* rgb, float* depth, float* normal, float* mask) {
   const int x = blockIdx.x * blockDim.x + threadIdx.x, y = blockIdx.y * blockDim.y + threadIdx.y;
@@ -151,7 +151,7 @@ GB_API int gb_geo_render(const float* verts, const int* tris, const void* nodes,
   RenderArg ra;
   memcpy(ra.cam.org, cam, sizeof(float) * 12); ra.cam.tan_half_fov = cam[12]; ra.cam.width = width; ra.cam.height = height;
   memcpy(ra.light.sun_dir, light, sizeof(float) * 12);
-  for (int i = 0; i < 3; ++i) ra.albedo[i] = albedo[i];
+  for (int i = 0; i < 5; ++i) ra.albedo[i] = albedo[i];
   const dim3 block(16, 8), grid((width + 15) / 16, (height + 7) / 8);
   render_kernel<<<grid, block, 0, stream>>>(mesh_arg(verts, tris, nodes, order, n_nodes), ra, rgb, depth, normal, mask);
   GB_CUDA_OK(cudaGetLastError());

@@ -10,7 +10,7 @@
 //    emit them at the cell's offset; a vertex is identified by the grid edge it lies on, so equal keys weld;
 //  * rays and points against a triangle mesh through a bounding-volume hierarchy (the reference: common/lightrt.hh SBVH,
 //    common/closest_point_bvh.h, common/preview_render.h): closest hit, any hit (shadows), closest point, and the preview
-//    shading of a pixel (Lambert under a sun with hard shadows plus a sky gradient; depth, normal and mask as side outputs).
+//    shading of a pixel (Lambert + a GGX lobe under a sun with hard shadows, plus a sky gradient; depth, normal and mask as side outputs).
 #pragma once
 #include <math.h>
 #include <stdint.h>
@@ -262,6 +262,26 @@ struct Camera {         // pinhole: pixel (x, y) of a width x height image looks
 
 struct Light { float sun_dir[3], sun_rgb[3], zenith_rgb[3], horizon_rgb[3]; };
 
+// GGX microfacet lobe for light l, view v, normal n (unit vectors, n.l > 0): D G F / (4 n.l n.v) * n.l with the Trowbridge-Reitz
+// distribution, the separable Smith-Schlick visibility term and Schlick's Fresnel term at a normal reflectance f0.
+GB_HD float ggx_specular(const float* n, const float* v, const float* l, float roughness, float f0) {
+  float h[3] = {v[0] + l[0], v[1] + l[1], v[2] + l[2]};
+  const float hl = sqrtf(h[0] * h[0] + h[1] * h[1] + h[2] * h[2]);
+  if (hl <= 0.0f) return 0.0f;
+  for (int i = 0; i < 3; ++i) h[i] /= hl;
+  const float nl = n[0] * l[0] + n[1] * l[1] + n[2] * l[2], nv = n[0] * v[0] + n[1] * v[1] + n[2] * v[2];
+  if (nl <= 0.0f || nv <= 0.0f) return 0.0f;
+  const float nh = n[0] * h[0] + n[1] * h[1] + n[2] * h[2], vh = v[0] * h[0] + v[1] * h[1] + v[2] * h[2];
+  const float a = roughness * roughness, a2 = a * a;
+  const float dd = nh * nh * (a2 - 1.0f) + 1.0f;
+  const float D = a2 / (3.14159265f * dd * dd);
+  const float k = (roughness + 1.0f) * (roughness + 1.0f) * 0.125f;
+  const float G = (nl / (nl * (1.0f - k) + k)) * (nv / (nv * (1.0f - k) + k));
+  const float m = 1.0f - (vh < 0.0f ? 0.0f : vh), m2 = m * m;
+  const float F = f0 + (1.0f - f0) * m2 * m2 * m;
+  return D * G * F / (4.0f * nv);
+}
+
 GB_HD void sky(const Light& l, const float* d, float* rgb) {
   float h = d[1] < 0.0f ? 0.0f : d[1];
   h = sqrtf(h);
@@ -269,6 +289,7 @@ GB_HD void sky(const Light& l, const float* d, float* rgb) {
 }
 
 // One pixel: rgb [3] (linear), depth (distance along the ray, 0 on a miss), normal [3] (facing the camera), mask (1 on a hit).
+// albedo_rgb[3] is the diffuse colour; albedo_rgb[3] / [4] are the roughness (<= 0: no specular lobe) and the normal reflectance.
 GB_HD void shade_pixel(const Mesh& m, const Camera& cam, const Light& l, const float* albedo_rgb, int x, int y, float* rgb, float* depth,
                        float* normal, float* mask) {
   const float aspect = (float)cam.width / (float)cam.height;
@@ -295,7 +316,12 @@ GB_HD void shade_pixel(const Mesh& m, const Camera& cam, const Light& l, const f
   if (cosl > 0.0f && trace(m, p, l.sun_dir, 1e-5f, 1e30f, true).tri < 0) lit = cosl;
   float amb[3];
   sky(l, n, amb);
-  for (int i = 0; i < 3; ++i) rgb[i] = albedo_rgb[i] * (l.sun_rgb[i] * lit + 0.5f * amb[i]);
+  float spec = 0.0f;
+  if (lit > 0.0f && albedo_rgb[3] > 0.0f) {
+    const float view[3] = {-d[0], -d[1], -d[2]};
+    spec = ggx_specular(n, view, l.sun_dir, albedo_rgb[3], albedo_rgb[4]);
+  }
+  for (int i = 0; i < 3; ++i) rgb[i] = albedo_rgb[i] * (l.sun_rgb[i] * lit + 0.5f * amb[i]) + l.sun_rgb[i] * spec;
   *depth = h.t; *mask = 1.0f;
   for (int i = 0; i < 3; ++i) normal[i] = n[i];
 }

@@ -224,10 +224,11 @@ class Bvh:
 
     def render(self, eye: Sequence[float], target: Sequence[float], width: int = 256, height: int = 256, fov_deg: float = 40.0,
                up: Sequence[float] = (0.0, 1.0, 0.0), sun_dir: Sequence[float] = (0.3, 0.6, 0.4), albedo: Sequence[float] = (0.8, 0.8, 0.8),
+               roughness: float = 0.0, f0: float = 0.04,
                sun_rgb: Sequence[float] = (3.0, 2.9, 2.6), zenith_rgb: Sequence[float] = (0.18, 0.32, 0.62),
                horizon_rgb: Sequence[float] = (0.85, 0.78, 0.70)):
-        """Preview image from a pinhole camera: Lambert under a sun with hard shadows plus half of the sky colour in the direction of
-        the normal as ambient light; a miss shows the sky.  Returns ``dict(rgb [h, w, 3] linear, depth [h, w], normal [h, w, 3], mask [h, w])``."""
+        """Preview image from a pinhole camera: Lambert (and, with ``roughness`` > 0, a GGX lobe of normal reflectance ``f0``) under
+        a sun with hard shadows plus half of the sky colour in the direction of the normal as ambient light; a miss shows the sky.  Returns ``dict(rgb [h, w, 3] linear, depth [h, w], normal [h, w, 3], mask [h, w])``."""
         e, tg, u = (torch.tensor([float(x) for x in v], dtype=torch.float64) for v in (eye, target, up))
         fwd = (tg - e) / (tg - e).norm()
         right = torch.linalg.cross(fwd, u)
@@ -237,7 +238,7 @@ class Bvh:
         sun = sun / sun.norm()
         cam = _f3(list(e) + list(fwd) + list(right) + list(upv) + [math.tan(math.radians(fov_deg) / 2)])
         light = _f3(list(sun) + list(sun_rgb) + list(zenith_rgb) + list(horizon_rgb))
-        alb = _f3(albedo)
+        alb = _f3(list(albedo) + [roughness, f0])
         dev = self.device
         rgb = torch.empty(height, width, 3, dtype=torch.float32, device=dev)
         depth = torch.empty(height, width, dtype=torch.float32, device=dev)

@@ -232,3 +232,19 @@ def test_dual_grid_mesh_equals_the_reference():
     assert nt.value > 1000 and torch.allclose(v, rv, atol=1e-6) and torch.equal(t, rt)
     ev, et = geo.dual_grid_mesh(coords[:0], feats[:0], 0.05, aabb.tolist())
     assert ev.shape == (0, 3) and et.shape == (0, 3)
+
+
+def test_specular_lobe_adds_a_highlight_where_the_sun_reflects():
+    grid = _grid(41, lambda x, y, z: (x * x + y * y + z * z).sqrt() - 0.6)
+    v, t = geo.isosurface(grid, 0.0)
+    bvh = geo.Bvh(v, t)
+    kw = dict(eye=(0, 0, -3.0), target=(0, 0, 0), width=96, height=96, fov_deg=30, sun_dir=(0.0, 0.5, -1.0), albedo=(0.5, 0.5, 0.5))
+    matte = bvh.render(**kw)["rgb"]
+    shiny = bvh.render(roughness=0.25, **kw)["rgb"]
+    diff = (shiny - matte).sum(-1)
+    assert diff.min() > -1e-5 and diff.max() > 0.3                       # only adds light
+    y, x = divmod(int(diff.argmax()), 96)
+    # the highlight sits where the normal halves the directions to the sun and to the eye: above the centre, on the sphere
+    assert y < 48 and abs(x - 48) < 6 and bvh.render(**kw)["mask"][y, x] == 1
+    rough = bvh.render(roughness=0.8, **kw)["rgb"]
+    assert (rough - matte).sum(-1).max() < diff.max()                    # a rougher surface spreads the lobe
