@@ -27,6 +27,22 @@ def _load_llm(args):
     import os
     from .serve.llm import LLM
     kw = dict(max_running=args.max_running, num_pages=args.pages, page_size=args.page_size)
+    if getattr(args, "cpu_engine", False) and os.path.isfile(args.model):
+        # a dense or mixture Qwen GGUF on a machine without a GPU: the native CPU engine, one request at a time
+        from .serve.cpu_engine import CpuEngineModel
+        from .serve.sequential import SequentialLLM
+        from .utils import gguf as G
+        from .utils.tokenizer import Tokenizer
+        with G.GGUFFile(args.model) as f:
+            arch = f.metadata.get("general.architecture", "")
+            tok = Tokenizer.from_gguf(f) if "tokenizer.ggml.tokens" in f.metadata else None
+        if tok is None and args.tokenizer:
+            with G.GGUFFile(args.tokenizer) as f:
+                tok = Tokenizer.from_gguf(f)
+        if arch not in ("qwen2", "qwen3", "qwen3moe", "qwen35", "qwen35moe"):
+            sys.exit(f"--cpu-engine: architecture {arch!r} is not one the native CPU engine runs (qwen2, qwen3, qwen3moe, qwen35, qwen35moe)")
+        n = args.pages * args.page_size
+        return SequentialLLM(CpuEngineModel(args.model, max_seq_len=n, threads=getattr(args, "threads", 0)), tok, max_seq_len=n)
     if _is_gemma4(args.model):
         # Gemma4 runs as a tensor-op model behind the one-request-at-a-time adapter
         import torch
@@ -59,22 +75,6 @@ def _load_llm(args):
                 with G.GGUFFile(args.tokenizer) as f:
                     tok = Tokenizer.from_gguf(f)
             return SequentialLLM(model, tok, max_seq_len=min(model.cfg.max_pos, args.pages * args.page_size))
-    if getattr(args, "cpu_engine", False) and os.path.isfile(args.model):
-        # a dense or mixture Qwen GGUF on a machine without a GPU: the native CPU engine, one request at a time
-        from .serve.cpu_engine import CpuEngineModel
-        from .serve.sequential import SequentialLLM
-        from .utils import gguf as G
-        from .utils.tokenizer import Tokenizer
-        with G.GGUFFile(args.model) as f:
-            arch = f.metadata.get("general.architecture", "")
-            tok = Tokenizer.from_gguf(f) if "tokenizer.ggml.tokens" in f.metadata else None
-        if tok is None and args.tokenizer:
-            with G.GGUFFile(args.tokenizer) as f:
-                tok = Tokenizer.from_gguf(f)
-        if arch not in ("qwen2", "qwen3", "qwen3moe"):
-            sys.exit(f"--cpu-engine: architecture {arch!r} is not one the native CPU engine runs (qwen2, qwen3, qwen3moe)")
-        n = args.pages * args.page_size
-        return SequentialLLM(CpuEngineModel(args.model, max_seq_len=n, threads=getattr(args, "threads", 0)), tok, max_seq_len=n)
     if args.model.startswith("synthetic:"):
         return LLM.from_synthetic(args.model.split(":", 1)[1], fmt=args.format, device=args.device, **kw)
     if os.path.isdir(args.model):
@@ -96,7 +96,7 @@ def _add_model_args(p):
     p.add_argument("--max-running", type=int, default=64)
     p.add_argument("--pages", type=int, default=512, help="KV cache pages")
     p.add_argument("--page-size", type=int, default=128)
-    p.add_argument("--cpu-engine", action="store_true", help="run a qwen2 / qwen3 / qwen3moe GGUF on the native CPU engine (no GPU; one request at a time)")
+    p.add_argument("--cpu-engine", action="store_true", help="run a qwen2 / qwen3 / qwen3moe / qwen35 / qwen35moe GGUF on the native CPU engine (no GPU; one request at a time)")
     p.add_argument("--threads", type=int, default=0, help="worker threads of the native CPU engine (0: all cores)")
 
 

@@ -38,6 +38,8 @@ int gbh_gguf_tensor_info(void* h, int i, char* name, int name_cap, int* n_dims, 
 const void* gbh_gguf_tensor_data(void* h, int i);
 int gbh_gguf_find_key(void* h, const char* key);
 int gbh_gguf_kv_scalar(void* h, int i, double* out);
+int gbh_gguf_kv_info(void* h, int i, char* key, int key_cap, int* type, int* elem_type, uint64_t* count);
+const void* gbh_gguf_kv_array_data(void* h, int i);
 const char* gbh_gguf_kv_string(void* h, int i, long j, uint64_t* len);
 }
 
@@ -116,12 +118,26 @@ struct Layer {
   QMat wq, wk, wv, wo, wgate, wup, wdown;
   QMat wrouter;                    // MoE layers: [n_experts, hidden]
   std::vector<QMat> eg, eu, ed;    // per expert: gate / up [expert_ffn, hidden], down [hidden, expert_ffn] (slices of the 3-D tensors)
+  QMat sh_gate, sh_up, sh_down;    // shared expert (qwen35moe), added to the routed output times sigmoid(sh_inp . x)
+  std::vector<float> sh_inp;
+  // gated Delta-Net layers of the hybrid models: projections of the layer input, the causal convolution over q | k | v, the
+  // per-head decay and write strength, the output norm and projection; and the running state of the one sequence the engine holds
+  bool is_ssm = false;
+  QMat s_qkv, s_z, s_alpha, s_beta, s_out;
+  std::vector<float> conv_w, s_norm, s_a, s_dt;
+  std::vector<float> ring;         // the last d_conv - 1 rows of q | k | v in front of the convolution
+  std::vector<float> state;        // [v heads][head_dim (value)][head_dim (key)]
 };
 
 struct CpuEngine {
   void* gguf = nullptr;
   int n_layers = 0, hidden = 0, n_heads = 0, n_kv = 0, head_dim = 0, ffn = 0, vocab = 0, max_seq = 0, threads = 1;
-  int n_experts = 0, n_used = 0, expert_ffn = 0;     // > 0: every layer's FFN is a routed mixture (qwen3moe)
+  int n_experts = 0, n_used = 0, expert_ffn = 0;     // > 0: every layer's FFN is a routed mixture (qwen3moe, qwen35moe)
+  int shared_ffn = 0;                                // > 0: plus a shared expert of this width
+  // hybrid models (qwen35, qwen35moe): every full_interval-th layer is gated attention, the others are Delta-Net layers
+  int full_interval = 0, rope_dim = 0, d_conv = 4, ssm_kh = 0, ssm_vh = 0, ssm_d = 0;
+  bool attn_gate = false;
+  int ssm_pos = 0;                                   // position the recurrent state stands at
   float eps = 1e-6f, theta = 1e6f;
   bool qk_norm = false, has_bias = false;
   std::vector<Layer> layers;
@@ -585,12 +601,115 @@ void moe_ffn(CpuEngine& e, const Layer& L, const float* h, int T, float* o) {
       for (int i = 0; i < H; ++i) dst[i] += w * src[i];
     }
   }
+  if (e.shared_ffn > 0) {
+    const int FS = e.shared_ffn;
+    ge.resize((size_t)T * FS); ye.resize((size_t)T * H);
+    ffn_gate_up_silu(e, L.sh_gate, L.sh_up, h, H, T, ge.data(), FS);
+    matmul(e, L.sh_down, ge.data(), FS, T, ye.data(), H);
+    for (int t = 0; t < T; ++t) {
+      float g = 1.0f;
+      if (!L.sh_inp.empty()) g = 1.0f / (1.0f + expf(-dot_f32(L.sh_inp.data(), h + (size_t)t * H, H)));
+      for (int i = 0; i < H; ++i) o[(size_t)t * H + i] += g * ye[(size_t)t * H + i];
+    }
+  }
+}
+
+// One gated Delta-Net layer over the rows h [T, hidden] -> o [T, hidden], continuing the layer's running state
+// (common/transformer.h:2861-3113).  Projections and the convolution run over the whole batch; the recurrence walks the tokens in
+// order, one thread per value head: S *= decay; delta = (v - S k) * beta; S += delta k^T; out = S q, with L2-normalised q (scaled
+// by d^-1/2) and k of the head's key group (value head h uses key head h % key heads).
+void deltanet_layer(CpuEngine& e, Layer& L, const float* h, int T, float* o) {
+  const int H = e.hidden, KH = e.ssm_kh, VH = e.ssm_vh, D = e.ssm_d, CK = e.d_conv;
+  const int QD = 2 * KH * D + VH * D, DI = VH * D;
+  std::vector<float> qkv((size_t)T * QD), z((size_t)T * DI), al((size_t)T * VH), be((size_t)T * VH), y((size_t)T * DI);
+  const MatJob jobs[4] = {{&L.s_qkv, qkv.data(), QD, nullptr}, {&L.s_z, z.data(), DI, nullptr}, {&L.s_alpha, al.data(), VH, nullptr},
+                          {&L.s_beta, be.data(), VH, nullptr}};
+  matmul_multi(e, jobs, 4, h, H, T);
+  // causal depthwise convolution + SiLU, channel by channel over the ring of earlier rows and this batch
+  std::vector<float> conv((size_t)T * QD);
+  e.pool->run(QD, [&](int c0, int c1) {
+    for (int c = c0; c < c1; ++c) {
+      const float* w = L.conv_w.data() + (size_t)c * CK;
+      for (int t = 0; t < T; ++t) {
+        float acc = 0.f;
+        for (int f = 0; f < CK; ++f) {
+          const int src = t - (CK - 1) + f;                     // row of this batch, or of the ring when negative
+          const float v = src >= 0 ? qkv[(size_t)src * QD + c] : L.ring[(size_t)(CK - 1 + src) * QD + c];
+          acc += v * w[f];
+        }
+        conv[(size_t)t * QD + c] = acc / (1.0f + expf(-acc));
+      }
+    }
+  });
+  for (int r = 0; r < CK - 1; ++r) {                             // the ring becomes the last CK - 1 rows seen so far
+    const int src = T - (CK - 1) + r;
+    if (src >= 0) memcpy(L.ring.data() + (size_t)r * QD, qkv.data() + (size_t)src * QD, sizeof(float) * QD);
+    else memmove(L.ring.data() + (size_t)r * QD, L.ring.data() + (size_t)(r + T) * QD, sizeof(float) * QD);
+  }
+  e.pool->run(VH, [&](int h0, int h1) {
+    std::vector<float> qn((size_t)D), kn((size_t)D), sk((size_t)D);
+    for (int hv = h0; hv < h1; ++hv) {
+      const int hk = hv % KH;
+      float* S = L.state.data() + (size_t)hv * D * D;
+      for (int t = 0; t < T; ++t) {
+        const float* q = conv.data() + (size_t)t * QD + (size_t)hk * D;
+        const float* k = conv.data() + (size_t)t * QD + (size_t)(KH + hk) * D;
+        const float* v = conv.data() + (size_t)t * QD + (size_t)2 * KH * D + (size_t)hv * D;
+        const float qs = 1.0f / sqrtf(dot_f32(q, q, D) + e.eps) / sqrtf((float)D), ks = 1.0f / sqrtf(dot_f32(k, k, D) + e.eps);
+        for (int i = 0; i < D; ++i) { qn[i] = q[i] * qs; kn[i] = k[i] * ks; }
+        const float a = al[(size_t)t * VH + hv] + L.s_dt[(size_t)hv];
+        const float sp = a > 20.0f ? a : log1pf(expf(a));
+        const float decay = expf(sp * L.s_a[(size_t)hv]);
+        const float beta = 1.0f / (1.0f + expf(-be[(size_t)t * VH + hv]));
+        float* out = y.data() + (size_t)t * DI + (size_t)hv * D;
+        for (int r = 0; r < D; ++r) {
+          float* row = S + (size_t)r * D;
+          for (int c = 0; c < D; ++c) row[c] *= decay;
+          const float delta = (v[r] - dot_f32(row, kn.data(), D)) * beta;
+          for (int c = 0; c < D; ++c) row[c] += delta * kn[c];
+          out[r] = dot_f32(row, qn.data(), D);
+        }
+        // per-head RMSNorm with the shared weight, then the SiLU gate of z
+        float ss = 0.f;
+        for (int r = 0; r < D; ++r) ss += out[r] * out[r];
+        const float inv = 1.0f / sqrtf(ss / D + e.eps);
+        const float* zz = z.data() + (size_t)t * DI + (size_t)hv * D;
+        for (int r = 0; r < D; ++r) out[r] = out[r] * inv * L.s_norm[(size_t)r] * (zz[r] / (1.0f + expf(-zz[r])));
+      }
+    }
+  });
+  matmul(e, L.s_out, y.data(), DI, T, o, H);
+}
+
+// x += o (the mixer's output); then the FFN on the normalised rows, added to x.  h, o, g are scratch of the caller.
+void ffn_block(CpuEngine& e, const Layer& L, float* x, float* h, float* o, float* g, int T) {
+  const int H = e.hidden, F = e.ffn;
+  { Phase ph(&e.prof[4]);
+  e.pool->run(T, [&](int t0, int t1) {
+    for (int t = t0; t < t1; ++t) {
+      float* xr = x + (size_t)t * H;
+      const float* orow = o + (size_t)t * H;
+      for (int i = 0; i < H; ++i) xr[i] += orow[i];
+      rmsnorm(xr, L.ffn_norm.data(), h + (size_t)t * H, H, e.eps);
+    }
+  }); }
+  if (e.n_experts > 0) { Phase ph(&e.prof[5]); moe_ffn(e, L, h, T, o); }
+  else {
+    { Phase ph(&e.prof[5]); ffn_gate_up_silu(e, L.wgate, L.wup, h, H, T, g, F); }
+    { Phase ph(&e.prof[6]); matmul(e, L.wdown, g, F, T, o, H); }
+  }
+  Phase ph_res(&e.prof[4]);
+  for (int t = 0; t < T; ++t) {
+    float* xr = x + (size_t)t * H;
+    const float* orow = o + (size_t)t * H;
+    for (int i = 0; i < H; ++i) xr[i] += orow[i];
+  }
 }
 
 void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
   const int H = e.hidden, D = e.head_dim, QD = e.n_heads * D, KD = e.n_kv * D, F = e.ffn;
   std::vector<float> h((size_t)T * H), q((size_t)T * QD), k((size_t)T * KD), v((size_t)T * KD), att((size_t)T * QD), o((size_t)T * H);
-  std::vector<float> g(e.n_experts > 0 ? 0 : (size_t)T * F);
+  std::vector<float> g(e.n_experts > 0 ? 0 : (size_t)T * F), qg(e.attn_gate ? (size_t)T * 2 * QD : 0);
   const float scale = 1.0f / sqrtf((float)D);
   const int group = e.n_heads / e.n_kv;
   for (int li = 0; li < e.n_layers; ++li) {
@@ -601,9 +720,20 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
     e.pool->run(T, [&](int t0, int t1) {
       for (int t = t0; t < t1; ++t) rmsnorm(x + (size_t)t * H, L.attn_norm.data(), h.data() + (size_t)t * H, H, e.eps);
     }); }
-    const MatJob qkv[3] = {{&L.wq, q.data(), QD, e.has_bias ? L.bq.data() : nullptr}, {&L.wk, k.data(), KD, e.has_bias ? L.bk.data() : nullptr},
+    if (L.is_ssm) {
+      { Phase ph(&e.prof[2]); deltanet_layer(e, e.layers[li], h.data(), T, o.data()); }
+      ffn_block(e, L, x, h.data(), o.data(), g.data(), T);
+      continue;
+    }
+    float* qdst = e.attn_gate ? qg.data() : q.data();             // gated attention: attn_q emits [q | gate] per head
+    const int QW = e.attn_gate ? 2 * QD : QD;
+    const MatJob qkv[3] = {{&L.wq, qdst, QW, e.has_bias ? L.bq.data() : nullptr}, {&L.wk, k.data(), KD, e.has_bias ? L.bk.data() : nullptr},
                            {&L.wv, v.data(), KD, e.has_bias ? L.bv.data() : nullptr}};
     { Phase ph(&e.prof[0]); matmul_multi(e, qkv, 3, h.data(), H, T); }
+    if (e.attn_gate)
+      for (int t = 0; t < T; ++t)
+        for (int hq = 0; hq < e.n_heads; ++hq)
+          memcpy(q.data() + (size_t)t * QD + hq * D, qg.data() + (size_t)t * QW + (size_t)hq * 2 * D, sizeof(float) * D);
     { Phase ph(&e.prof[1]);
     e.pool->run(T, [&](int t0, int t1) {
     for (int t = t0; t < t1; ++t) {
@@ -611,12 +741,12 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
       for (int hq = 0; hq < e.n_heads; ++hq) {
         float* qh = q.data() + (size_t)t * QD + hq * D;
         if (e.qk_norm) rmsnorm(qh, L.q_norm.data(), qh, D, e.eps);
-        rope_neox(qh, D, pos, e.inv_freq.data());
+        rope_neox(qh, e.rope_dim, pos, e.inv_freq.data());
       }
       for (int hk = 0; hk < e.n_kv; ++hk) {
         float* kh = k.data() + (size_t)t * KD + hk * D;
         if (e.qk_norm) rmsnorm(kh, L.k_norm.data(), kh, D, e.eps);
-        rope_neox(kh, D, pos, e.inv_freq.data());
+        rope_neox(kh, e.rope_dim, pos, e.inv_freq.data());
       }
       for (int hk = 0; hk < e.n_kv; ++hk) {
         memcpy(kc + ((size_t)hk * e.max_seq + pos) * D, k.data() + (size_t)t * KD + hk * D, sizeof(float) * D);
@@ -649,27 +779,15 @@ void forward_hidden(CpuEngine& e, float* x, int T, int pos0) {
         }
       }
     }); }
+    if (e.attn_gate)
+      for (int t = 0; t < T; ++t)
+        for (int hq = 0; hq < e.n_heads; ++hq) {
+          const float* gt = qg.data() + (size_t)t * QW + (size_t)hq * 2 * D + D;
+          float* a = att.data() + (size_t)t * QD + hq * D;
+          for (int d = 0; d < D; ++d) a[d] *= 1.0f / (1.0f + expf(-gt[d]));
+        }
     { Phase ph(&e.prof[3]); matmul(e, L.wo, att.data(), QD, T, o.data(), H); }
-    { Phase ph(&e.prof[4]);
-    e.pool->run(T, [&](int t0, int t1) {
-      for (int t = t0; t < t1; ++t) {
-        float* xr = x + (size_t)t * H;
-        const float* orow = o.data() + (size_t)t * H;
-        for (int i = 0; i < H; ++i) xr[i] += orow[i];
-        rmsnorm(xr, L.ffn_norm.data(), h.data() + (size_t)t * H, H, e.eps);
-      }
-    }); }
-    if (e.n_experts > 0) { Phase ph(&e.prof[5]); moe_ffn(e, L, h.data(), T, o.data()); }
-    else {
-      { Phase ph(&e.prof[5]); ffn_gate_up_silu(e, L.wgate, L.wup, h.data(), H, T, g.data(), F); }
-      { Phase ph(&e.prof[6]); matmul(e, L.wdown, g.data(), F, T, o.data(), H); }
-    }
-    Phase ph_res(&e.prof[4]);
-    for (int t = 0; t < T; ++t) {
-      float* xr = x + (size_t)t * H;
-      const float* orow = o.data() + (size_t)t * H;
-      for (int i = 0; i < H; ++i) xr[i] += orow[i];
-    }
+    ffn_block(e, L, x, h.data(), o.data(), g.data(), T);
   }
 }
 
@@ -711,7 +829,9 @@ void place_weights(CpuEngine& e) {
   const bool tied = e.head.data == e.embed.data;
   if (!tied) mats.push_back(&e.head);
   for (Layer& L : e.layers) {
-    for (QMat* m : {&L.wq, &L.wk, &L.wv, &L.wo}) mats.push_back(m);
+    if (L.is_ssm) { for (QMat* m : {&L.s_qkv, &L.s_z, &L.s_alpha, &L.s_beta, &L.s_out}) mats.push_back(m); }
+    else { for (QMat* m : {&L.wq, &L.wk, &L.wv, &L.wo}) mats.push_back(m); }
+    if (e.shared_ffn > 0) for (QMat* m : {&L.sh_gate, &L.sh_up, &L.sh_down}) mats.push_back(m);
     if (e.n_experts > 0) {
       mats.push_back(&L.wrouter);
       for (std::vector<QMat>* v : {&L.eg, &L.eu, &L.ed}) for (QMat& m : *v) mats.push_back(&m);
@@ -749,21 +869,32 @@ GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
   std::string arch = "qwen3";
   const int ai = gbh_gguf_find_key(g, "general.architecture");
   if (ai >= 0) { uint64_t len = 0; const char* s = gbh_gguf_kv_string(g, ai, -1, &len); if (s) arch.assign(s, (size_t)len); }
-  if (arch != "qwen2" && arch != "qwen3" && arch != "qwen3moe") {
-    fail("cpu engine: architecture %s is not qwen2 / qwen3 / qwen3moe", arch.c_str()); delete e; gbh_gguf_close(g); return nullptr;
+  if (arch != "qwen2" && arch != "qwen3" && arch != "qwen3moe" && arch != "qwen35" && arch != "qwen35moe") {
+    fail("cpu engine: architecture %s is not qwen2 / qwen3 / qwen3moe / qwen35 / qwen35moe", arch.c_str()); delete e; gbh_gguf_close(g); return nullptr;
   }
+  const bool hybrid = arch == "qwen35" || arch == "qwen35moe";
   const std::string p = arch + ".";
   e->n_layers = (int)kv_num(g, p + "block_count", 0); e->hidden = (int)kv_num(g, p + "embedding_length", 0);
   e->n_heads = (int)kv_num(g, p + "attention.head_count", 0); e->n_kv = (int)kv_num(g, p + "attention.head_count_kv", e->n_heads);
   e->head_dim = (int)kv_num(g, p + "attention.key_length", e->n_heads ? e->hidden / e->n_heads : 0);
   e->ffn = (int)kv_num(g, p + "feed_forward_length", 0);
-  if (arch == "qwen3moe") {
+  if (hybrid) {
+    e->full_interval = (int)kv_num(g, p + "attention.full_attention_interval", 4); e->d_conv = (int)kv_num(g, p + "ssm.conv_kernel", 4);
+    e->ssm_d = (int)kv_num(g, p + "ssm.state_size", 0); e->ssm_kh = (int)kv_num(g, p + "ssm.group_count", 0);
+    e->ssm_vh = (int)kv_num(g, p + "ssm.time_step_rank", 0);
+    e->attn_gate = true;
+    if (e->full_interval < 1 || e->d_conv < 2 || e->ssm_d <= 0 || e->ssm_kh <= 0 || e->ssm_vh <= 0 || e->ssm_vh % e->ssm_kh) {
+      fail("cpu engine: incomplete Delta-Net hyper-parameters in %s", path); delete e; gbh_gguf_close(g); return nullptr;
+    }
+  }
+  if (arch == "qwen3moe" || arch == "qwen35moe") {
     e->n_experts = (int)kv_num(g, p + "expert_count", 0); e->n_used = (int)kv_num(g, p + "expert_used_count", 0);
     e->expert_ffn = (int)kv_num(g, p + "expert_feed_forward_length", 0);
     if (e->n_experts <= 0 || e->n_used <= 0 || e->n_used > e->n_experts || e->expert_ffn <= 0) {
       fail("cpu engine: incomplete expert hyper-parameters in %s", path); delete e; gbh_gguf_close(g); return nullptr;
     }
     if (e->ffn <= 0) e->ffn = e->expert_ffn;
+    e->shared_ffn = (int)kv_num(g, p + "expert_shared_feed_forward_length", 0);
   }
   e->eps = (float)kv_num(g, p + "attention.layer_norm_rms_epsilon", 1e-6); e->theta = (float)kv_num(g, p + "rope.freq_base", 1e6);
   e->max_seq = max_seq > 0 ? max_seq : 4096;
@@ -785,18 +916,46 @@ GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
   for (int li = 0; ok && li < e->n_layers; ++li) {
     Layer& L = e->layers[li];
     const std::string b = "blk." + std::to_string(li) + ".";
-    ok = get_vec(g, b + "attn_norm.weight", &L.attn_norm, H) == 0 && get_vec(g, b + "ffn_norm.weight", &L.ffn_norm, H) == 0 &&
-         get_mat(g, b + "attn_q.weight", &L.wq, e->n_heads * D, H) == 0 && get_mat(g, b + "attn_k.weight", &L.wk, e->n_kv * D, H) == 0 &&
-         get_mat(g, b + "attn_v.weight", &L.wv, e->n_kv * D, H) == 0 && get_mat(g, b + "attn_output.weight", &L.wo, H, e->n_heads * D) == 0;
+    L.is_ssm = hybrid && (li + 1) % e->full_interval != 0;
+    ok = get_vec(g, b + "attn_norm.weight", &L.attn_norm, H) == 0 &&
+         get_vec(g, b + (hybrid ? "post_attention_norm.weight" : "ffn_norm.weight"), &L.ffn_norm, H) == 0;
+    if (ok && L.is_ssm) {
+      const int SD = e->ssm_d, QDs = 2 * e->ssm_kh * SD + e->ssm_vh * SD, DI = e->ssm_vh * SD;
+      ok = get_mat(g, b + "attn_qkv.weight", &L.s_qkv, QDs, H) == 0 && get_mat(g, b + "attn_gate.weight", &L.s_z, DI, H) == 0 &&
+           get_mat(g, b + "ssm_alpha.weight", &L.s_alpha, e->ssm_vh, H) == 0 && get_mat(g, b + "ssm_beta.weight", &L.s_beta, e->ssm_vh, H) == 0 &&
+           get_mat(g, b + "ssm_out.weight", &L.s_out, H, DI) == 0 && get_vec(g, b + "ssm_norm.weight", &L.s_norm, SD) == 0 &&
+           get_vec(g, b + "ssm_a", &L.s_a, e->ssm_vh) == 0 && get_vec(g, b + "ssm_dt.bias", &L.s_dt, e->ssm_vh) == 0;
+      if (ok) {                                                  // conv weights: ggml dims {d_conv, channels} = one row of taps per channel
+        const int ci = gbh_gguf_find_tensor(g, (b + "ssm_conv1d.weight").c_str());
+        int nd = 0, type = 0; uint64_t dims[4] = {0, 0, 0, 0}, nbytes = 0; char nm[8];
+        if (ci < 0) { fail("cpu engine: tensor %sssm_conv1d.weight is missing", b.c_str()); ok = false; }
+        else {
+          gbh_gguf_tensor_info(g, ci, nm, 8, &nd, dims, &type, &nbytes);
+          if (nd != 2 || (int)dims[0] != e->d_conv || (int)dims[1] != QDs) { fail("cpu engine: %sssm_conv1d.weight has the wrong shape", b.c_str()); ok = false; }
+          else { L.conv_w.resize((size_t)QDs * e->d_conv); ok = dequant_row(type, gbh_gguf_tensor_data(g, ci), L.conv_w.data(), (long)QDs * e->d_conv) == 0; }
+        }
+      }
+      L.ring.assign((size_t)(e->d_conv - 1) * QDs, 0.f);
+      L.state.assign((size_t)e->ssm_vh * SD * SD, 0.f);
+    } else if (ok) {
+      ok = get_mat(g, b + "attn_q.weight", &L.wq, (e->attn_gate ? 2 : 1) * e->n_heads * D, H) == 0 && get_mat(g, b + "attn_k.weight", &L.wk, e->n_kv * D, H) == 0 &&
+           get_mat(g, b + "attn_v.weight", &L.wv, e->n_kv * D, H) == 0 && get_mat(g, b + "attn_output.weight", &L.wo, H, e->n_heads * D) == 0;
+    }
     if (ok && e->n_experts > 0)
       ok = get_mat(g, b + "ffn_gate_inp.weight", &L.wrouter, e->n_experts, H) == 0 &&
            get_experts(g, b + "ffn_gate_exps.weight", &L.eg, e->n_experts, e->expert_ffn, H) == 0 &&
            get_experts(g, b + "ffn_up_exps.weight", &L.eu, e->n_experts, e->expert_ffn, H) == 0 &&
            get_experts(g, b + "ffn_down_exps.weight", &L.ed, e->n_experts, H, e->expert_ffn) == 0;
-    else if (ok)
+    if (ok && e->n_experts > 0 && e->shared_ffn > 0) {
+      ok = get_mat(g, b + "ffn_gate_shexp.weight", &L.sh_gate, e->shared_ffn, H) == 0 && get_mat(g, b + "ffn_up_shexp.weight", &L.sh_up, e->shared_ffn, H) == 0 &&
+           get_mat(g, b + "ffn_down_shexp.weight", &L.sh_down, H, e->shared_ffn) == 0;
+      if (ok && get_vec(g, b + "ffn_gate_inp_shexp.weight", &L.sh_inp, H, true) < 0) ok = false;
+    }
+    if (ok && e->n_experts == 0)
       ok = get_mat(g, b + "ffn_gate.weight", &L.wgate, e->ffn, H) == 0 && get_mat(g, b + "ffn_up.weight", &L.wup, e->ffn, H) == 0 &&
            get_mat(g, b + "ffn_down.weight", &L.wdown, H, e->ffn) == 0;
     if (!ok) break;
+    if (L.is_ssm) continue;
     const int qn = get_vec(g, b + "attn_q_norm.weight", &L.q_norm, D, true);
     if (qn == 0) { e->qk_norm = true; ok = get_vec(g, b + "attn_k_norm.weight", &L.k_norm, D) == 0; } else if (qn < 0) ok = false;
     const int bq = get_vec(g, b + "attn_q.bias", &L.bq, e->n_heads * D, true);
@@ -804,8 +963,20 @@ GBH_API void* gbh_cpu_engine_load(const char* path, int max_seq, int threads) {
     else if (bq < 0) ok = false;
   }
   if (!ok) { gbh_gguf_close(g); delete e; return nullptr; }
-  e->inv_freq.resize((size_t)D / 2);
-  for (int j = 0; j < D / 2; ++j) e->inv_freq[j] = powf(e->theta, -2.0f * (float)j / (float)D);
+  e->rope_dim = (int)kv_num(g, p + "rope.dimension_count", D);
+  {                                                               // M-RoPE files carry the section sizes instead: with one position for
+    const int si = gbh_gguf_find_key(g, (p + "rope.dimension_sections").c_str());   // all three axes the rotated width is twice their sum
+    int type = 0, elem = 0; uint64_t count = 0;
+    if (si >= 0 && gbh_gguf_kv_info(g, si, nullptr, 0, &type, &elem, &count) == 0 && count > 0 && count <= 8) {
+      const void* arr = gbh_gguf_kv_array_data(g, si);
+      long sum = 0;
+      if (arr != nullptr && (elem == 5 || elem == 4)) for (uint64_t i = 0; i < count; ++i) { int32_t v; memcpy(&v, (const uint8_t*)arr + 4 * i, 4); sum += v; }
+      if (sum > 0) e->rope_dim = (int)(2 * sum);
+    }
+  }
+  if (e->rope_dim <= 0 || e->rope_dim > D || e->rope_dim % 2) e->rope_dim = D;
+  e->inv_freq.resize((size_t)e->rope_dim / 2);
+  for (int j = 0; j < e->rope_dim / 2; ++j) e->inv_freq[j] = powf(e->theta, -2.0f * (float)j / (float)e->rope_dim);
   const size_t kvn = (size_t)e->n_layers * e->max_seq * e->n_kv * D;
   e->kc.assign(kvn, 0.f); e->vc.assign(kvn, 0.f);
   place_weights(*e);
@@ -826,6 +997,11 @@ GBH_API int gbh_cpu_engine_threads(void* h) { return ((CpuEngine*)h)->threads; }
 GBH_API int gbh_cpu_engine_forward(void* h, const int* tokens, int n, int pos0, float* logits) {
   auto* e = (CpuEngine*)h;
   if (n <= 0 || pos0 < 0 || pos0 + n > e->max_seq) return fail("cpu engine: positions %d .. %d leave the cache of %d", pos0, pos0 + n, e->max_seq);
+  if (e->full_interval > 0) {                                    // a recurrent state cannot be rewound: start over at 0 or continue
+    if (pos0 == 0) for (Layer& L : e->layers) { std::fill(L.ring.begin(), L.ring.end(), 0.f); std::fill(L.state.begin(), L.state.end(), 0.f); }
+    else if (pos0 != e->ssm_pos) return fail("cpu engine: the recurrent state stands at position %d, not %d (restart from 0)", e->ssm_pos, pos0);
+    e->ssm_pos = pos0 + n;
+  }
   std::vector<float> x((size_t)n * e->hidden);
   embed_rows(*e, tokens, n, x.data());
   forward_hidden(*e, x.data(), n, pos0);

@@ -39,12 +39,15 @@ def config_from_gguf(f: G.GGUFFile) -> ModelConfig:
     if vocab is None:
         vocab = f.tensors["token_embd.weight"].shape[0]
     n_exp = int(key("expert_count", 0) or 0)
+    n_layers_probe = int(key("block_count"))
     cfg = ModelConfig(
         arch=arch, n_layers=int(key("block_count")), hidden=hidden, n_heads=n_heads,
         n_kv_heads=int(key("attention.head_count_kv", n_heads)), head_dim=head_dim, ffn=int(key("feed_forward_length", 0) or 0),
         vocab=int(vocab), rms_eps=float(key("attention.layer_norm_rms_epsilon", 1e-6)), rope_theta=float(key("rope.freq_base", 1e6)),
         rope_dim=(int(key("rope.dimension_count")) if key("rope.dimension_count") not in (None, head_dim) else None),
-        qk_norm="blk.0.attn_q_norm.weight" in f.tensors, qkv_bias="blk.0.attn_q.bias" in f.tensors,
+        # any layer: in the hybrid models block 0 is a Delta-Net layer and carries neither tensor
+        qk_norm=any(f"blk.{i}.attn_q_norm.weight" in f.tensors for i in range(n_layers_probe)),
+        qkv_bias=any(f"blk.{i}.attn_q.bias" in f.tensors for i in range(n_layers_probe)),
         tie_embeddings="output.weight" not in f.tensors, max_seq_len=int(key("context_length", 4096)),
         n_experts=n_exp, n_experts_used=int(key("expert_used_count", 0) or 0), expert_ffn=int(key("expert_feed_forward_length", 0) or 0),
         shared_expert_ffn=int(key("expert_shared_feed_forward_length", 0) or 0),

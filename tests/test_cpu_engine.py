@@ -61,9 +61,11 @@ def test_moe_greedy_tokens_equal_the_reference_engine(tmp_path):
 
 
 def test_load_errors_are_reported(tmp_path):
-    cfg = get_config("tiny-qwen35")
-    path = str(tmp_path / "hybrid.gguf")
-    loader.save_gguf(cfg, RandomSource(cfg, seed=1), path, "Q8_0")
+    from gemm_b200.models import gemma4
+    gcfg = gemma4.Gemma4Config(n_layers=2, hidden=64, n_heads=2, n_kv_heads=1, ffn=128, vocab=64, head_dim_full=32, head_dim_swa=32, window=8, ple_dim=8,
+                               shared_kv_layers=0, swa_pattern=[True, False], max_seq_len=32)
+    path = str(tmp_path / "g4.gguf")
+    gemma4.save_gguf(gcfg, gemma4.random_tensors(gcfg, seed=1), path, "F16")
     with pytest.raises(RuntimeError, match="architecture"):
         CpuEngine(path)
     eng_path = str(tmp_path / "d.gguf")
@@ -134,7 +136,50 @@ def test_generate_and_server_on_the_native_engine(tmp_path, capsys):
         eng.stop_flag = True
         httpd.shutdown()
     with pytest.raises(SystemExit):
-        hyb = str(tmp_path / "h.gguf")
-        c2 = get_config("tiny-qwen35")
-        loader.save_gguf(c2, RandomSource(c2, seed=1), hyb, "Q8_0")
-        main(["generate", "--model", hyb, "--cpu-engine", "--ids", "--prompt", "1 2 3", "--max-new-tokens", "2"])
+        from gemm_b200.models import gemma4
+        gcfg = gemma4.Gemma4Config(n_layers=2, hidden=64, n_heads=2, n_kv_heads=1, ffn=128, vocab=64, head_dim_full=32, head_dim_swa=32, window=8, ple_dim=8,
+                                   shared_kv_layers=0, swa_pattern=[True, False], max_seq_len=32)
+        other = str(tmp_path / "g4.gguf")
+        gemma4.save_gguf(gcfg, gemma4.random_tensors(gcfg, seed=1), other, "F16")
+        main(["generate", "--model", other, "--cpu-engine", "--ids", "--prompt", "1 2 3", "--max-new-tokens", "2"])
+
+
+@pytest.mark.parametrize("name,wtype", [("tiny-qwen35", "F16"), ("tiny-qwen35", "Q8_0"), ("tiny-qwen35moe", "F16")])
+def test_hybrid_models_on_the_native_engine(tmp_path, name, wtype):
+    """Delta-Net layers interleaved with gated attention (and, in the mixture variant, a gated shared expert): logits against the fp32
+    oracle, whole prompt against chunks against token by token (the recurrent state carries over), and the rule that a recurrent
+    state cannot be rewound."""
+    cfg = get_config(name)
+    path = str(tmp_path / "m.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=8), path, wtype)
+    w = loader.load_gguf(path, "bf16", device="cpu")
+    toks = torch.randint(0, cfg.vocab, (23,), generator=torch.Generator().manual_seed(2)).tolist()
+    want = reference.reference_logits(w, torch.tensor(toks))
+    eng = CpuEngine(path, max_seq_len=64, threads=3)
+    whole = eng.forward(toks, 0)
+    assert _rel(whole, want[-1]) < (2e-2 if wtype == "Q8_0" else 1e-4)
+    eng.forward(toks[:9], 0)
+    eng.forward(toks[9:10], 9)
+    chunks = eng.forward(toks[10:], 10)
+    one = CpuEngine(path, max_seq_len=64, threads=1)
+    for i, t in enumerate(toks):
+        single = one.forward([t], i)
+    tol = 2e-2 if cfg.is_moe else 1e-4
+    assert np.abs(chunks - whole).max() < tol * max(1.0, np.abs(whole).max()) and np.abs(single - whole).max() < tol * max(1.0, np.abs(whole).max())
+    with pytest.raises(RuntimeError, match="recurrent state"):
+        eng.forward(toks[:2], 5)
+    assert np.abs(eng.forward(toks, 0) - whole).max() < 1e-5 * max(1.0, np.abs(whole).max())      # position 0 starts a new sequence
+    out, _, _ = eng.generate(toks, 5)
+    out1, _, _ = one.generate(toks, 5)
+    assert out == out1
+
+
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not available")
+def test_hybrid_greedy_tokens_equal_the_reference_engine(tmp_path):
+    cfg = get_config("tiny-qwen35")
+    path = str(tmp_path / "h.gguf")
+    loader.save_gguf(cfg, RandomSource(cfg, seed=3), path, "Q8_0")
+    prompt = torch.randint(0, cfg.vocab, (18,), generator=torch.Generator().manual_seed(4)).tolist()
+    ref = cpubench.run_reference(oracle.REF_ROOT, path, prompt, 10, threads=1)
+    ours = cpubench.run_ours(path, prompt, 10, threads=4)
+    assert ref is not None and ours[0] == ref[0]

@@ -1,6 +1,6 @@
 """The hybrid stack (gated Delta-Net layers mixed with gated attention layers, partial rotary, output gates) against Hugging Face's
-Qwen3.5 text model in fp32 on the same random weights: the mixed stack, which the reference's CPU engine does not pin (it disagrees
-with both from the second position on), agrees with an implementation that shares nothing with either."""
+Qwen3.5 text model in fp32 on the same random weights: a third implementation that shares nothing with this framework or with the
+reference's CPU engine (which pins the same stack from a GGUF file in tests/test_loader_cpu.py)."""
 import pytest
 import torch
 

@@ -56,16 +56,18 @@ def test_hf_safetensors_roundtrip(tmp_path, mx):
 
 @pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not present")
 @pytest.mark.parametrize("name,wtype", [("tiny-dense", "Q8_0"), ("tiny-moe", "F16"), ("tiny-qwen2", "Q4_K"), ("tiny-qwen35:ssm", "F16"),
-                                        ("tiny-qwen35:attn", "F16")])
+                                        ("tiny-qwen35:attn", "F16"), ("tiny-qwen35:mixed", "F16")])
 def test_engine_matches_reference_cpu_engine(tmp_path, name, wtype):
     """The reference's own transformer.h loads the GGUF our writer produced and runs it token by token; our engine
     (loading the same file) must give the same logits up to bf16 rounding of activations."""
     if ":" in name:
-        # Qwen3.5 hybrid: the stack of Delta-Net layers and the stack of gated-attention (M-RoPE) layers are each checked against
-        # the reference engine.  (In a mixed stack the reference's logits differ from position 1 on although they do not depend on
-        # the weights of a muted Delta-Net layer; both layer types alone agree to round-off.)
+        # Qwen3.5 hybrid: a stack of Delta-Net layers, a stack of gated-attention (M-RoPE) layers, and the released interleaving of
+        # the two (block 0 is then a Delta-Net layer without QK-norm tensors: what a loader finds in block 0 says nothing about
+        # the attention layers)
         name, kind = name.split(":")
-        cfg = get_config(name).with_(full_attention_interval=5 if kind == "ssm" else 1)
+        cfg = get_config(name)
+        if kind != "mixed":
+            cfg = cfg.with_(full_attention_interval=5 if kind == "ssm" else 1)
     else:
         cfg = get_config(name)
     path = str(tmp_path / "m.gguf")
@@ -84,6 +86,8 @@ def test_engine_matches_reference_cpu_engine(tmp_path, name, wtype):
         p = ref.transformer_forward_logits(m, t, pos)
         ref_logits.append(torch.from_numpy(np.ctypeslib.as_array(p, shape=(cfg.vocab,)).copy()))
     w = loader.load_gguf(path, "bf16", device="cpu")
+    if any(not cfg.is_ssm_layer(i) for i in range(cfg.n_layers)):                 # read off the attention layers, wherever they sit
+        assert w.cfg.qk_norm == cfg.qk_norm and w.cfg.qkv_bias == cfg.qkv_bias
     # fp32 oracle on the loaded weights == the reference arithmetic
     ours32 = reference.reference_logits(w, toks)
     assert _rel(ours32[-1], ref_logits[-1]) < 5e-3 and _rel(ours32[5], ref_logits[5]) < 5e-3
