@@ -57,15 +57,28 @@ int ref_generate(const char *path, int max_seq, int n_threads, const int *prompt
 '''
 
 
-def make_checkpoint(path: str, model: str = "qwen3-0.6b", wtype: str = "Q8_0", seed: int = 0, layers: int = 0) -> None:
-    """Write the random-init checkpoint (N(0, 0.02) matrices, unit norms) of ``model`` (cut to ``layers`` layers when > 0) as a GGUF
-    file in ggml type ``wtype``."""
-    from ..models import loader
+def _config(model: str, layers: int = 0, overrides=()):
+    """The preset ``model``, cut to ``layers`` layers when > 0, with ``key=value`` overrides of integer fields (a hybrid shape at a
+    size that fits: ``--model tiny-qwen35 --set hidden=1024 --set n_layers=8 ...``)."""
     from ..models.config import get_config
-    from ..models.weights import RandomSource
     cfg = get_config(model)
     if layers > 0:
         cfg = cfg.with_(n_layers=layers)
+    kw = {}
+    for item in overrides:
+        k, _, v = item.partition("=")
+        if not hasattr(cfg, k):
+            raise ValueError(f"--set {item}: the configuration has no field {k!r}")
+        kw[k] = int(v)
+    return cfg.with_(**kw) if kw else cfg
+
+
+def make_checkpoint(path: str, model: str = "qwen3-0.6b", wtype: str = "Q8_0", seed: int = 0, layers: int = 0, overrides=()) -> None:
+    """Write the random-init checkpoint (N(0, 0.02) matrices, unit norms) of ``model`` (cut to ``layers`` layers when > 0) as a GGUF
+    file in ggml type ``wtype``."""
+    from ..models import loader
+    from ..models.weights import RandomSource
+    cfg = _config(model, layers, overrides)
     loader.save_gguf(cfg, RandomSource(cfg, seed, "cpu"), path, wtype)
 
 
@@ -132,6 +145,7 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-len", type=int, default=128)
     ap.add_argument("--new", type=int, default=32)
     ap.add_argument("--layers", type=int, default=0, help="cut the model to this many layers (0: all): a mixture model's shape at a size that fits")
+    ap.add_argument("--set", action="append", default=[], metavar="FIELD=INT", help="override an integer field of the preset (repeatable)")
     ap.add_argument("--threads", type=int, default=os.cpu_count() or 1)
     ap.add_argument("--gguf", default="", help="checkpoint to use (default: write the synthetic one to a temporary file)")
     ap.add_argument("--reference-root", default=os.environ.get("GEMM_REFERENCE_ROOT", ""), help="source tree of the reference project (optional)")
@@ -139,15 +153,14 @@ def main(argv=None) -> int:
     ap.add_argument("--repeat", type=int, default=3, help="runs per arm, alternating; the fastest prefill and the fastest decode of each arm are "
                     "reported (other jobs on the machine only ever slow a run down)")
     args = ap.parse_args(argv)
-    from ..models.config import get_config
-    cfg = get_config(args.model)
+    cfg = _config(args.model, args.layers, args.set)
     path = args.gguf
     tmp = None
     if not path:
         tmp = tempfile.mkdtemp(prefix="gemm_b200_cpubench_")
         path = os.path.join(tmp, "model.gguf")
         t0 = time.time()
-        make_checkpoint(path, args.model, args.wtype, layers=args.layers)
+        make_checkpoint(path, args.model, args.wtype, layers=args.layers, overrides=args.set)
         print(f"[cpubench] wrote {path} ({os.path.getsize(path) / 2**20:.0f} MiB) in {time.time() - t0:.1f}s")
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab, (args.prompt_len,), generator=g).tolist()
@@ -167,7 +180,7 @@ def main(argv=None) -> int:
             r2 = run_reference(args.reference_root, path, prompt, args.new, args.threads)
             ref = (ref[0], min(ref[1], r2[1]), min(ref[2], r2[2]))
     n_tok = args.prompt_len + args.new
-    line = {"config": {"model": args.model, "layers": args.layers or cfg.n_layers, "wtype": args.wtype, "prompt_len": args.prompt_len, "new_tokens": args.new, "threads": args.threads},
+    line = {"config": {"model": args.model, "layers": cfg.n_layers, "overrides": args.set, "wtype": args.wtype, "prompt_len": args.prompt_len, "new_tokens": args.new, "threads": args.threads},
             "ours": {"prefill_s": round(tp, 4), "decode_s": round(td, 4), "total_s": round(tp + td, 4), "prefill_tok_s": round(args.prompt_len / tp, 2),
                      "decode_tok_s": round((args.new - 1) / td, 2) if td > 0 else None, "tok_s_overall": round(n_tok / (tp + td), 2)}}
     line["config"]["repeat"] = args.repeat
