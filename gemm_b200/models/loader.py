@@ -151,6 +151,8 @@ def save_gguf(cfg: ModelConfig, src, path: str, wtype: str = "F16", tokens=None,
         w.add_array(f"{a}.rope.dimension_sections", [int(x) for x in cfg.mrope_sections])
     elif cfg.rope_dim:
         w.add_u32(f"{a}.rope.dimension_count", cfg.rope_dim)
+    if cfg.n_deepstack_layers:
+        w.add_u32(f"{a}.n_deepstack_layers", cfg.n_deepstack_layers)
     if cfg.is_hybrid:
         w.add_u32(f"{a}.attention.full_attention_interval", cfg.full_attention_interval)
         w.add_u32(f"{a}.ssm.conv_kernel", cfg.ssm_d_conv)

@@ -57,7 +57,9 @@ def engine_lib():
     """ctypes handle exposing the reference CPU engine (gguf_open, transformer_load, transformer_forward_logits, ...)."""
     src = ('#define GGUF_LOADER_IMPLEMENTATION\n#include "gguf_loader.h"\n#define GGML_DEQUANT_IMPLEMENTATION\n#include "ggml_dequant.h"\n'
            '#define TRANSFORMER_IMPLEMENTATION\n#include "transformer.h"\n'
-           'int ref_n_vocab(transformer_model *m) { return m->n_vocab; }\n')
+           'int ref_n_vocab(transformer_model *m) { return m->n_vocab; }\n'
+           'int ref_n_deepstack(transformer_model *m) { return m->n_deepstack; }\n'
+           'void ref_set_ds_stride(transformer_model *m, int s) { m->ds_embd_stride = s; }\n')
     lib = _build("ref_engine", src)
     lib.gguf_open.restype = ctypes.c_void_p
     lib.gguf_open.argtypes = [ctypes.c_char_p, ctypes.c_int]
@@ -69,6 +71,10 @@ def engine_lib():
     lib.transformer_forward_embd_logits.restype = ctypes.POINTER(ctypes.c_float)
     lib.transformer_forward_embd_logits.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
     lib.ref_n_vocab.argtypes = [ctypes.c_void_p]
+    lib.ref_n_deepstack.argtypes = [ctypes.c_void_p]
+    lib.ref_set_ds_stride.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    lib.transformer_forward_embd_logits_pos.restype = ctypes.POINTER(ctypes.c_float)
+    lib.transformer_forward_embd_logits_pos.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int]
     return lib
 
 

@@ -148,3 +148,53 @@ def test_gguf_blocks_are_kept_without_conversion(tmp_path, wtype):
         full = w.layers[li].w_down.dequantized()
         got = torch.cat([p.layers[li].w_down.dequantized() for p in parts], dim=1)
         assert all(p.layers[li].w_down.k % 256 == 0 for p in parts) and torch.equal(got, full)
+
+
+@pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not present")
+def test_mrope_positions_and_deepstack_match_reference_cpu_engine(tmp_path):
+    """A Qwen3-VL style text model from our GGUF file: text tokens, then image rows fed as embeddings with separate t / h / w positions
+    and DeepStack slices, then text again, through the reference's embedding entry point and through ours."""
+    cfg = get_config("tiny-dense").with_(arch="qwen3vl", mrope_sections=[24, 20, 20, 0], n_deepstack_layers=2)
+    path = str(tmp_path / "vl.gguf")
+    src = RandomSource(cfg, seed=6)
+    loader.save_gguf(cfg, src, path, "F16")
+    ref = oracle.engine_lib()
+    m = ref.transformer_load(ref.gguf_open(path.encode(), 1), 64)
+    assert m and ref.ref_n_deepstack(m) == 2
+    ref.transformer_set_f64_accum(m, 1)
+    h, t = cfg.hidden, 18
+    ref.ref_set_ds_stride(m, 3 * h)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.vocab, (t,), generator=g)
+    vis = torch.zeros(t, dtype=torch.bool)
+    vis[4:10] = True                                                # an image of 2 x 3 merged patches at t = 4
+    pos3 = torch.arange(t).repeat(3, 1)
+    pos3[0, 4:10] = 4
+    pos3[1, 4:10] = 4 + torch.arange(6) // 3
+    pos3[2, 4:10] = 4 + torch.arange(6) % 3
+    pos3[:, 10:] = torch.arange(10, t) - 10 + 4 + 3
+    rows = torch.randn(6, 3 * h, generator=g) * 0.05                 # main embedding | DeepStack slice 0 | slice 1
+    w = loader.load_gguf(path, "bf16", device="cpu")
+    want = []
+    for i in range(t):
+        if vis[i]:
+            r = rows[i - 4].contiguous()
+            p = ref.transformer_forward_embd_logits_pos(m, r.data_ptr(), i, int(pos3[0, i]), int(pos3[1, i]), int(pos3[2, i]))
+        elif i < 4:
+            p = ref.transformer_forward_logits(m, int(ids[i]), i)
+        else:                                                        # text behind the image: its position is not its cache slot
+            e = w.embed[int(ids[i])].float().contiguous()
+            p = ref.transformer_forward_embd_logits_pos(m, torch.cat([e, torch.zeros(2 * h)]).contiguous().data_ptr(), i, int(pos3[0, i]), int(pos3[1, i]), int(pos3[2, i]))
+        want.append(torch.from_numpy(np.ctypeslib.as_array(p, shape=(cfg.vocab,)).copy()))
+    want = torch.stack(want)
+    assert w.cfg.n_deepstack_layers == 2 and list(w.cfg.mrope_sections) == [24, 20, 20, 0]
+    model = Transformer(w, KvCache.allocate(w.cfg, 4, 16, "cpu"))
+    fb = ForwardBatch.build([t], [0], ids, torch.tensor([[0, 1]], dtype=torch.int32), 16, cfg.n_heads, cfg.n_kv_heads, "cpu", all_logits=True)
+    emb = w.embed[ids.long()].float().clone()
+    emb[vis] = rows[:, :h]
+    ds = torch.zeros(2, t, h)
+    ds[0, vis], ds[1, vis] = rows[:, h: 2 * h], rows[:, 2 * h:]
+    fb.embeds, fb.positions3, fb.deepstack = emb.to(torch.bfloat16), pos3.to(torch.int32), ds.to(torch.bfloat16)
+    got = model.forward(fb).float()
+    for i in (0, 3, 4, 9, 10, 17):
+        assert _rel(got[i], want[i]) < 3e-2, (i, _rel(got[i], want[i]))
