@@ -184,7 +184,8 @@ def test_mrope_positions_and_deepstack_match_reference_cpu_engine(tmp_path):
             p = ref.transformer_forward_logits(m, int(ids[i]), i)
         else:                                                        # text behind the image: its position is not its cache slot
             e = w.embed[int(ids[i])].float().contiguous()
-            p = ref.transformer_forward_embd_logits_pos(m, torch.cat([e, torch.zeros(2 * h)]).contiguous().data_ptr(), i, int(pos3[0, i]), int(pos3[1, i]), int(pos3[2, i]))
+            buf = torch.cat([e, torch.zeros(2 * h)]).contiguous()      # kept alive across the call
+            p = ref.transformer_forward_embd_logits_pos(m, buf.data_ptr(), i, int(pos3[0, i]), int(pos3[1, i]), int(pos3[2, i]))
         want.append(torch.from_numpy(np.ctypeslib.as_array(p, shape=(cfg.vocab,)).copy()))
     want = torch.stack(want)
     assert w.cfg.n_deepstack_layers == 2 and list(w.cfg.mrope_sections) == [24, 20, 20, 0]
