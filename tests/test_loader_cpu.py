@@ -56,7 +56,7 @@ def test_hf_safetensors_roundtrip(tmp_path, mx):
 
 @pytest.mark.skipif(not oracle.available(), reason="reference source tree or gcc not present")
 @pytest.mark.parametrize("name,wtype", [("tiny-dense", "Q8_0"), ("tiny-moe", "F16"), ("tiny-qwen2", "Q4_K"), ("tiny-qwen35:ssm", "F16"),
-                                        ("tiny-qwen35:attn", "F16"), ("tiny-qwen35:mixed", "F16")])
+                                        ("tiny-qwen35:attn", "F16"), ("tiny-qwen35:mixed", "F16"), ("tiny-moe:vl", "F16"), ("tiny-qwen2:vl", "F16")])
 def test_engine_matches_reference_cpu_engine(tmp_path, name, wtype):
     """The reference's own transformer.h loads the GGUF our writer produced and runs it token by token; our engine
     (loading the same file) must give the same logits up to bf16 rounding of activations."""
@@ -66,7 +66,10 @@ def test_engine_matches_reference_cpu_engine(tmp_path, name, wtype):
         # the attention layers)
         name, kind = name.split(":")
         cfg = get_config(name)
-        if kind != "mixed":
+        if kind == "vl":                                         # the vision-language variants of the text stacks: M-RoPE sections (+ DeepStack)
+            cfg = cfg.with_(arch="qwen3vlmoe", mrope_sections=[24, 20, 20, 0], n_deepstack_layers=2) if cfg.is_moe else \
+                cfg.with_(arch="qwen2vl", mrope_sections=[16, 24, 24, 0])
+        elif kind != "mixed":
             cfg = cfg.with_(full_attention_interval=5 if kind == "ssm" else 1)
     else:
         cfg = get_config(name)
