@@ -400,11 +400,15 @@ def config_from_hf(path: str) -> ModelConfig:
     mt = c.get("model_type", "qwen3")
     arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3moe"}.get(mt, "qwen3")
     hidden, heads = c["hidden_size"], c["num_attention_heads"]
+    # two generations of config.json: ``rope_theta`` / ``num_experts`` at the top level (the checkpoints on the Hub), or
+    # ``rope_parameters.rope_theta`` / ``num_local_experts`` (what current transformers writes)
+    rope_theta = c.get("rope_theta") or (c.get("rope_parameters") or {}).get("rope_theta") or 1e6
+    n_experts = c.get("num_experts") or c.get("num_local_experts") or 0
     return ModelConfig(arch=arch, n_layers=c["num_hidden_layers"], hidden=hidden, n_heads=heads, n_kv_heads=c.get("num_key_value_heads", heads),
                        head_dim=c.get("head_dim", hidden // heads), ffn=c.get("intermediate_size", 0), vocab=c["vocab_size"],
-                       rms_eps=c.get("rms_norm_eps", 1e-6), rope_theta=c.get("rope_theta", 1e6), qk_norm=(mt != "qwen2"), qkv_bias=(mt == "qwen2"),
+                       rms_eps=c.get("rms_norm_eps", 1e-6), rope_theta=float(rope_theta), qk_norm=(mt != "qwen2"), qkv_bias=(mt == "qwen2"),
                        tie_embeddings=c.get("tie_word_embeddings", False), max_seq_len=c.get("max_position_embeddings", 4096),
-                       n_experts=c.get("num_experts", 0), n_experts_used=c.get("num_experts_per_tok", 0),
+                       n_experts=int(n_experts), n_experts_used=c.get("num_experts_per_tok", 0) if n_experts else 0,
                        expert_ffn=c.get("moe_intermediate_size", 0), norm_topk=c.get("norm_topk_prob", True))
 
 
