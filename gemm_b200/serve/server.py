@@ -14,6 +14,7 @@ requests share every forward pass.  Standard library only.
 from __future__ import annotations
 
 import json
+import os
 import queue
 import threading
 import time
@@ -118,6 +119,15 @@ def make_handler(engine: EngineThread, model_name: str):
             self.wfile.write(body)
 
         def do_GET(self):
+            if self.path in ("/", "/index.html", "/chat"):       # the chat page (the reference ships web/llm_chat.html beside its server)
+                with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "chat.html"), "rb") as fh:
+                    body = fh.read()
+                self.send_response(200)
+                self.send_header("Content-Type", "text/html; charset=utf-8")
+                self.send_header("Content-Length", str(len(body)))
+                self.end_headers()
+                self.wfile.write(body)
+                return
             if self.path == "/health":
                 return self._json(200, {"status": "ok"})
             if self.path == "/v1/models":

@@ -30,6 +30,8 @@ def test_server_endpoints():
     port = httpd.server_address[1]
     try:
         assert json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=10).read())["status"] == "ok"
+        page = urllib.request.urlopen(f"http://127.0.0.1:{port}/", timeout=10)
+        assert page.headers["Content-Type"].startswith("text/html") and b"/v1/chat/completions" in page.read()      # the built-in chat page
         out = json.loads(_post(port, "/v1/completions", {"prompt": "the quick brown", "max_tokens": 5}))
         assert out["object"] == "text_completion" and len(out["token_ids"]) <= 5 and out["usage"]["prompt_tokens"] > 0
         # the same prompt as token ids gives the same tokens (greedy)
