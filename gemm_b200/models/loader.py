@@ -394,10 +394,130 @@ class SafetensorsSource:
         return self._raw(hf_name(name, e))
 
 
+class HFQwen35Source(SafetensorsSource):
+    """Qwen3.5 (dense and MoE hybrids) from the Hugging Face layout, served under the GGUF tensor names the model builder asks for.
+    What changes on the way (the inverse of what a GGUF converter does; the same rules as ``utils.hf_compare.hf_qwen35_model``):
+    RMSNorm weights are stored as ``w`` and used as ``1 + w``; value head ``j`` of a Delta-Net layer belongs to key head ``j // R``
+    there and to ``j % Hk`` here, so the value-head blocks of ``in_proj_qkv``, ``in_proj_z``, ``in_proj_a / b``, ``conv1d``, ``A_log``,
+    ``dt_bias`` and the columns of ``out_proj`` are permuted; ``ssm_a = -exp(A_log)``; the convolution weight drops its singleton axis;
+    experts come one tensor per expert or stacked (``experts.gate_up_proj`` [E, 2 I, H])."""
+
+    _LIN = {"attn_qkv": "in_proj_qkv.weight", "attn_gate": "in_proj_z.weight", "ssm_alpha": "in_proj_a.weight", "ssm_beta": "in_proj_b.weight",
+            "ssm_out": "out_proj.weight", "ssm_conv1d": "conv1d.weight", "ssm_norm": "norm.weight"}
+    _ATT = {"attn_q": "q_proj", "attn_k": "k_proj", "attn_v": "v_proj", "attn_output": "o_proj", "attn_q_norm": "q_norm", "attn_k_norm": "k_norm"}
+    _FFN = {"ffn_gate": "mlp.gate_proj", "ffn_up": "mlp.up_proj", "ffn_down": "mlp.down_proj", "ffn_gate_inp": "mlp.gate",
+            "ffn_gate_shexp": "mlp.shared_expert.gate_proj", "ffn_up_shexp": "mlp.shared_expert.up_proj", "ffn_down_shexp": "mlp.shared_expert.down_proj",
+            "ffn_gate_inp_shexp": "mlp.shared_expert_gate"}
+
+    def __init__(self, path: str, cfg: ModelConfig):
+        super().__init__(path)
+        self.cfg = cfg
+        self.prefix = "model.language_model." if any(k.startswith("model.language_model.") for k in self.where) else "model."
+        hk, hv, ds = cfg.ssm_n_heads_k, cfg.ssm_n_heads_v, cfg.ssm_head_dim
+        r = hv // hk
+        # our value head i = (i % hk) + hk * (i // hk) sits at their index (i % hk) * r + i // hk
+        self.heads = torch.tensor([(i % hk) * r + i // hk for i in range(hv)])
+        self.vrows = (self.heads[:, None] * ds + torch.arange(ds)[None, :]).reshape(-1)
+        self.chan = torch.cat([torch.arange(2 * hk * ds), 2 * hk * ds + self.vrows])
+
+    def _name(self, name: str) -> str:
+        if name == "token_embd.weight":
+            return self.prefix + "embed_tokens.weight"
+        if name == "output_norm.weight":
+            return self.prefix + "norm.weight"
+        if name == "output.weight":
+            return "lm_head.weight"
+        _, li, rest = name.split(".", 2)
+        base, _, kind = rest.rpartition(".")
+        if not base:                                             # "ssm_a": a bare parameter
+            base, kind = rest, ""
+        lp = f"{self.prefix}layers.{li}."
+        if base == "attn_norm":
+            return lp + "input_layernorm.weight"
+        if base in ("ffn_norm", "post_attention_norm"):
+            return lp + "post_attention_layernorm.weight"
+        if base in self._LIN:
+            return lp + "linear_attn." + self._LIN[base]
+        if base == "ssm_a":
+            return lp + "linear_attn.A_log"
+        if base == "ssm_dt":
+            return lp + "linear_attn.dt_bias"
+        if base in self._ATT:
+            return lp + "self_attn." + self._ATT[base] + "." + kind
+        return lp + self._FFN[base] + "." + kind
+
+    def has(self, name: str) -> bool:
+        return self._name(name) in self.where
+
+    def get(self, name: str, shape) -> torch.Tensor:
+        t = self._raw(self._name(name))
+        base = name.split(".", 2)[2].rpartition(".")[0] if name.startswith("blk.") else name.rpartition(".")[0]
+        if name.startswith("blk.") and not base:
+            base = name.split(".", 2)[2]
+        if base in ("attn_norm", "ffn_norm", "post_attention_norm", "attn_q_norm", "attn_k_norm", "output_norm"):
+            t = t + 1.0
+        elif base == "attn_qkv":
+            t = t[self.chan]
+        elif base == "ssm_conv1d":
+            t = t.reshape(t.shape[0], -1)[self.chan]
+        elif base == "attn_gate":
+            t = t[self.vrows]
+        elif base in ("ssm_alpha", "ssm_beta"):
+            t = t[self.heads]
+        elif base == "ssm_out":
+            t = t[:, self.vrows]
+        elif base == "ssm_a":
+            t = -torch.exp(t[self.heads])
+        elif base == "ssm_dt":
+            t = t[self.heads]
+        elif base == "ffn_gate_inp_shexp":
+            t = t.reshape(-1)
+        t = t.contiguous()
+        if tuple(t.shape) != tuple(shape):
+            raise ValueError(f"{name}: checkpoint has shape {tuple(t.shape)}, model wants {tuple(shape)}")
+        return t
+
+    def get_expert(self, name: str, e: int, shape) -> torch.Tensor:
+        _, li, rest = name.split(".", 2)
+        lp = f"{self.prefix}layers.{li}.mlp.experts."
+        which = {"ffn_gate_exps": "gate_proj", "ffn_up_exps": "up_proj", "ffn_down_exps": "down_proj"}[rest.rsplit(".", 1)[0]]
+        if f"{lp}{e}.{which}.weight" in self.where:
+            return self._raw(f"{lp}{e}.{which}.weight")
+        inter = self.cfg.expert_ffn                                 # stacked: [E, 2 I, H] = gate rows then up rows, and [E, H, I]
+        if which == "down_proj":
+            return self._raw(lp + "down_proj")[e].contiguous()
+        gu = self._raw(lp + "gate_up_proj")[e]
+        return (gu[:inter] if which == "gate_proj" else gu[inter:]).contiguous()
+
+
+def _qwen35_config_from_hf(c: dict) -> ModelConfig:
+    c = c.get("text_config", c)
+    moe = "moe" in c.get("model_type", "")
+    rp = c.get("rope_parameters") or {}
+    hd = c.get("head_dim", c["hidden_size"] // c["num_attention_heads"])
+    factor = rp.get("partial_rotary_factor", c.get("partial_rotary_factor", 1.0))
+    types = c.get("layer_types") or []
+    interval = (types.index("full_attention") + 1) if "full_attention" in types else int(c.get("full_attention_interval", 4))
+    sections = list(rp.get("mrope_section") or [])
+    return ModelConfig(
+        arch="qwen35moe" if moe else "qwen35", n_layers=c["num_hidden_layers"], hidden=c["hidden_size"], n_heads=c["num_attention_heads"],
+        n_kv_heads=c.get("num_key_value_heads", c["num_attention_heads"]), head_dim=hd, ffn=c.get("intermediate_size", 0) or 0, vocab=c["vocab_size"],
+        rms_eps=c.get("rms_norm_eps", 1e-6), rope_theta=float(rp.get("rope_theta") or c.get("rope_theta") or 1e7), rope_dim=int(round(hd * factor)),
+        qk_norm=True, qkv_bias=False, tie_embeddings=c.get("tie_word_embeddings", False), max_seq_len=c.get("max_position_embeddings", 4096),
+        full_attention_interval=interval, ssm_d_conv=c.get("linear_conv_kernel_dim", 4), ssm_n_heads_k=c["linear_num_key_heads"],
+        ssm_n_heads_v=c["linear_num_value_heads"], ssm_head_dim=c["linear_key_head_dim"], attn_output_gate=True,
+        mrope_sections=(sections + [0] * (4 - len(sections))) if sections else None,
+        n_experts=int(c.get("num_experts") or c.get("num_local_experts") or 0) if moe else 0, n_experts_used=c.get("num_experts_per_tok", 0) if moe else 0,
+        expert_ffn=c.get("moe_intermediate_size", 0) if moe else 0, shared_expert_ffn=c.get("shared_expert_intermediate_size", 0) if moe else 0,
+        norm_topk=True)
+
+
 def config_from_hf(path: str) -> ModelConfig:
     with open(os.path.join(path, "config.json")) as fh:
         c = json.load(fh)
     mt = c.get("model_type", "qwen3")
+    if mt.startswith("qwen3_5"):
+        return _qwen35_config_from_hf(c)
     arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3moe"}.get(mt, "qwen3")
     hidden, heads = c["hidden_size"], c["num_attention_heads"]
     # two generations of config.json: ``rope_theta`` / ``num_experts`` at the top level (the checkpoints on the Hub), or
@@ -415,7 +535,8 @@ def config_from_hf(path: str) -> ModelConfig:
 def load_safetensors(path: str, fmt: str = "bf16", device="cuda", cfg: Optional[ModelConfig] = None, **shard) -> ModelWeights:
     """Load an HF checkpoint directory (config.json + *.safetensors)."""
     cfg = cfg or config_from_hf(path)
-    return build_weights(cfg, SafetensorsSource(path), fmt, device, **shard)
+    src = HFQwen35Source(path, cfg) if cfg.is_hybrid else SafetensorsSource(path)
+    return build_weights(cfg, src, fmt, device, **shard)
 
 
 def save_hf_checkpoint(cfg: ModelConfig, src, path: str, mxfp8: bool = False) -> None:

@@ -49,3 +49,25 @@ def test_mixed_stack_matches_transformers(name):
     got = torch.cat(outs)
     tol = 8e-2 if cfg.is_moe else 4e-2              # bf16 activations flip a near-tie of the router here and there
     assert _rel(got, want) < tol and (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.85
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen35", "tiny-qwen35moe"])
+def test_checkpoints_written_by_transformers_load_and_agree(tmp_path, name):
+    """The import direction: a hybrid model saved by transformers (``save_pretrained``: its tensor names under ``model.language_model.``,
+    its configuration keys) read by ``loader.load_safetensors`` gives transformers' logits."""
+    from gemm_b200.models import loader
+    from gemm_b200.utils import hf_compare
+    cfg = get_config(name)
+    hf = hf_compare.hf_qwen35_model(cfg, RandomSource(cfg, 9))
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    got_cfg = loader.config_from_hf(str(tmp_path))
+    for field in ("arch", "n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "rope_dim", "full_attention_interval", "ssm_n_heads_k", "ssm_n_heads_v",
+                  "ssm_head_dim", "ssm_d_conv", "n_experts", "n_experts_used", "expert_ffn", "shared_expert_ffn", "attn_output_gate", "qk_norm"):
+        assert getattr(got_cfg, field) == getattr(cfg, field), field
+    assert list(got_cfg.mrope_sections) == list(cfg.mrope_sections)
+    w = loader.load_safetensors(str(tmp_path), "bf16", device="cpu")
+    ids = torch.randint(0, cfg.vocab, (17,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+    got = reference.reference_logits(w, ids)
+    assert ((got - want).norm() / want.norm()).item() < 3e-2                  # our copy of the weights is bf16
