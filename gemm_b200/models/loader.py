@@ -367,7 +367,14 @@ class SafetensorsSource:
         self.files = [SafetensorsFile(p) for p in files]
         self.where = {k: f for f in self.files for k in f.keys()}
 
+    def _resolve(self, name: str) -> str:
+        """The multimodal checkpoints keep the text model under ``model.language_model.``."""
+        if name not in self.where and name.startswith("model.") and ("model.language_model." + name[6:]) in self.where:
+            return "model.language_model." + name[6:]
+        return name
+
     def _raw(self, name: str) -> torch.Tensor:
+        name = self._resolve(name)
         t = self.where[name].get(name)
         if t.dtype == torch.float8_e4m3fn:
             s = self.where[name + "_scale_inv"].get(name + "_scale_inv")
@@ -382,7 +389,7 @@ class SafetensorsSource:
         return t.to(torch.float32, copy=True)           # a copy also for F32 tensors: the file's mapping ends with this object
 
     def has(self, name: str) -> bool:
-        return hf_name(name) in self.where
+        return self._resolve(hf_name(name)) in self.where
 
     def get(self, name: str, shape) -> torch.Tensor:
         t = self._raw(hf_name(name))
@@ -518,7 +525,18 @@ def config_from_hf(path: str) -> ModelConfig:
     mt = c.get("model_type", "qwen3")
     if mt.startswith("qwen3_5"):
         return _qwen35_config_from_hf(c)
-    arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3moe"}.get(mt, "qwen3")
+    vl_sections, n_deepstack = None, 0
+    if mt.startswith("qwen3_vl") or mt.startswith("qwen2_vl") or mt.startswith("qwen2_5_vl"):
+        # the text side of a vision-language checkpoint: its own sub-configuration, M-RoPE sections, one DeepStack slice per listed
+        # vision layer
+        n_deepstack = len((c.get("vision_config") or {}).get("deepstack_visual_indexes") or [])
+        tie = c.get("tie_word_embeddings", False)
+        c = dict(c.get("text_config", c))
+        c.setdefault("tie_word_embeddings", tie)
+        sec = list(((c.get("rope_parameters") or c.get("rope_scaling") or {}).get("mrope_section")) or [])
+        vl_sections = (sec + [0] * (4 - len(sec))) if sec else None
+        mt = {"qwen3_vl_moe": "qwen3_vl_moe", "qwen3_vl_moe_text": "qwen3_vl_moe", "qwen3_vl": "qwen3_vl", "qwen3_vl_text": "qwen3_vl"}.get(mt, "qwen2_vl")
+    arch = {"qwen2": "qwen2", "qwen3": "qwen3", "qwen3_moe": "qwen3moe", "qwen3_vl": "qwen3vl", "qwen3_vl_moe": "qwen3vlmoe", "qwen2_vl": "qwen2vl"}.get(mt, "qwen3")
     hidden, heads = c["hidden_size"], c["num_attention_heads"]
     # two generations of config.json: ``rope_theta`` / ``num_experts`` at the top level (the checkpoints on the Hub), or
     # ``rope_parameters.rope_theta`` / ``num_local_experts`` (what current transformers writes)
@@ -526,10 +544,11 @@ def config_from_hf(path: str) -> ModelConfig:
     n_experts = c.get("num_experts") or c.get("num_local_experts") or 0
     return ModelConfig(arch=arch, n_layers=c["num_hidden_layers"], hidden=hidden, n_heads=heads, n_kv_heads=c.get("num_key_value_heads", heads),
                        head_dim=c.get("head_dim", hidden // heads), ffn=c.get("intermediate_size", 0), vocab=c["vocab_size"],
-                       rms_eps=c.get("rms_norm_eps", 1e-6), rope_theta=float(rope_theta), qk_norm=(mt != "qwen2"), qkv_bias=(mt == "qwen2"),
+                       rms_eps=c.get("rms_norm_eps", 1e-6), rope_theta=float(rope_theta), qk_norm=(mt not in ("qwen2", "qwen2_vl")), qkv_bias=(mt in ("qwen2", "qwen2_vl")),
                        tie_embeddings=c.get("tie_word_embeddings", False), max_seq_len=c.get("max_position_embeddings", 4096),
                        n_experts=int(n_experts), n_experts_used=c.get("num_experts_per_tok", 0) if n_experts else 0,
-                       expert_ffn=c.get("moe_intermediate_size", 0), norm_topk=c.get("norm_topk_prob", True))
+                       expert_ffn=c.get("moe_intermediate_size", 0), norm_topk=c.get("norm_topk_prob", True), mrope_sections=vl_sections,
+                       n_deepstack_layers=n_deepstack)
 
 
 def load_safetensors(path: str, fmt: str = "bf16", device="cuda", cfg: Optional[ModelConfig] = None, **shard) -> ModelWeights:

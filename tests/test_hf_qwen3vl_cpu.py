@@ -48,3 +48,26 @@ def test_mrope_and_deepstack_match_transformers():
     got = m.forward(fb).float()
     assert _rel(got, want) < 2e-2 and _rel(got[5:13], want[5:13]) < 2e-2 and _rel(got[13:], want[13:]) < 2e-2
     assert _rel(plain[13:], want[13:]) > 5e-2            # the image positions and features do change the rows behind them
+
+
+def test_vision_language_checkpoint_written_by_transformers_loads_and_agrees(tmp_path):
+    """The text side of a Qwen3-VL checkpoint saved by transformers (weights under ``model.language_model.``, ``text_config`` nesting,
+    M-RoPE sections, DeepStack indexes in the vision configuration) through ``loader.load_safetensors``: text-only logits equal."""
+    from transformers import Qwen3VLConfig, Qwen3VLForConditionalGeneration
+    from gemm_b200.models import loader, reference
+    tc = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+              max_position_embeddings=128, rope_parameters={"rope_type": "default", "rope_theta": 50000.0, "mrope_section": [6, 5, 5]}, tie_word_embeddings=False)
+    vc = dict(depth=2, hidden_size=32, intermediate_size=64, num_heads=2, patch_size=4, spatial_merge_size=2, temporal_patch_size=2, out_hidden_size=64,
+              num_position_embeddings=16, deepstack_visual_indexes=[0, 1], in_channels=3)
+    torch.manual_seed(0)
+    hf = Qwen3VLForConditionalGeneration(Qwen3VLConfig(text_config=tc, vision_config=vc, image_token_id=290, video_token_id=291, vision_start_token_id=292,
+                                                       vision_end_token_id=293)).float().eval()
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    cfg = loader.config_from_hf(str(tmp_path))
+    assert cfg.arch == "qwen3vl" and list(cfg.mrope_sections) == [6, 5, 5, 0] and cfg.n_deepstack_layers == 2 and cfg.rope_theta == 50000.0 and cfg.qk_norm
+    w = loader.load_safetensors(str(tmp_path), "bf16", device="cpu")
+    ids = torch.randint(0, 280, (15,), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        want = hf(input_ids=ids[None]).logits[0]
+    got = reference.reference_logits(w, ids)
+    assert _rel(got, want) < 2e-2
