@@ -2,6 +2,7 @@
 
 Endpoints (the set the reference serves in server/server.c:2094-2270 for its LLM):
   POST /v1/chat/completions   messages -> ChatML prompt -> completion (``stream: true`` gives server-sent events)
+  POST /v1/similarity         {ref, hyp} -> token agreement and character edit distance of two texts
   POST /v1/completions        raw prompt completion
   GET  /v1/models             the loaded model
   GET  /v1/progress           queue / running counts and tokens produced so far (server.c:1632)
@@ -143,6 +144,25 @@ def make_handler(engine: EngineThread, model_name: str):
                 req = json.loads(self.rfile.read(n) or b"{}")
             except json.JSONDecodeError:
                 return self._json(400, {"error": "invalid JSON"})
+            if self.path == "/v1/similarity":
+                # agreement of two texts, e.g. this server's completion against another implementation's
+                # (the reference's comparison server answers the same request, ref/llm/llm_server.py:45-66)
+                from ..utils.hf_compare import edit_distance
+                ref_t, hyp_t = str(req.get("ref", "")), str(req.get("hyp", ""))
+                ced = edit_distance([ord(ch) for ch in ref_t], [ord(ch) for ch in hyp_t])
+                metrics = {"char_len_ref": len(ref_t), "char_len_hyp": len(hyp_t), "char_edit_distance": ced,
+                           "char_similarity": 1.0 - ced / max(len(ref_t), len(hyp_t), 1)}
+                method = "char-levenshtein"
+                if llm.tokenizer is not None:
+                    a, b = llm.tokenizer.encode(ref_t), llm.tokenizer.encode(hyp_t)
+                    n, k = min(len(a), len(b)), 0
+                    while k < n and a[k] == b[k]:
+                        k += 1
+                    same = sum(1 for x, y in zip(a, b) if x == y)
+                    metrics.update({"len_ref": len(a), "len_hyp": len(b), "common_prefix_tokens": k, "first_divergence_pos": k,
+                                    "token_match_rate": same / max(len(a), len(b), 1), "token_edit_distance": edit_distance(a, b)})
+                    method = "token-agreement"
+                return self._json(200, {"ok": True, "method": method, "metrics": metrics})
             chat = self.path == "/v1/chat/completions"
             if not chat and self.path != "/v1/completions":
                 return self._json(404, {"error": "not found"})

@@ -1,5 +1,7 @@
 """HTTP front end on CPU: completions, chat, streaming, concurrent requests sharing the engine."""
 import json
+
+import pytest
 import threading
 import urllib.request
 
@@ -30,6 +32,11 @@ def test_server_endpoints():
     port = httpd.server_address[1]
     try:
         assert json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=10).read())["status"] == "ok"
+        sim = json.loads(_post(port, "/v1/similarity", {"ref": "the quick brown fox", "hyp": "the quick brown dog"}))
+        assert sim["ok"] and sim["method"] == "token-agreement" and sim["metrics"]["char_edit_distance"] == 2
+        assert 0 < sim["metrics"]["common_prefix_tokens"] <= sim["metrics"]["len_ref"] and sim["metrics"]["char_similarity"] == pytest.approx(1 - 2 / 19)
+        same = json.loads(_post(port, "/v1/similarity", {"ref": "abc", "hyp": "abc"}))["metrics"]
+        assert same["token_match_rate"] == 1.0 and same["char_edit_distance"] == 0 and same["first_divergence_pos"] == same["len_ref"]
         page = urllib.request.urlopen(f"http://127.0.0.1:{port}/", timeout=10)
         assert page.headers["Content-Type"].startswith("text/html") and b"/v1/chat/completions" in page.read()      # the built-in chat page
         out = json.loads(_post(port, "/v1/completions", {"prompt": "the quick brown", "max_tokens": 5}))
