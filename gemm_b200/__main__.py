@@ -112,8 +112,45 @@ def _is_gemma4(path: str) -> bool:
         return False
 
 
+def _generate_with_audio(args):
+    """Gemma4 with an audio clip (the reference's driver: cuda/llm/test_gemma4_st.c:83-160): the clip is encoded to soft tokens,
+    which are spliced into the prompt where ``<audio>`` stands (in front of it when the marker is absent); greedy decoding."""
+    import torch
+    from .models import audio, gemma4
+    from .utils import gguf as G
+    from .utils.tokenizer import Tokenizer
+    dev = args.device if (args.device != "cuda" or torch.cuda.is_available()) else "cpu"
+    model = gemma4.load_gguf(args.model, dev, torch.bfloat16 if dev != "cpu" else torch.float32)
+    pcm, rate = audio.wav_load(args.audio)
+    if rate != audio.RATE:
+        sys.exit(f"{args.audio}: {rate} Hz; the encoder takes {audio.RATE} Hz mono (resample beforehand)")
+    enc = audio.Gemma4AudioEncoder.from_checkpoint(args.audio_model, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32)
+    soft = enc.encode_pcm(pcm[: int(30.0 * audio.RATE)])
+    if soft.shape[1] != model.cfg.hidden:
+        sys.exit(f"the audio encoder emits rows of {soft.shape[1]}, the text model is {model.cfg.hidden} wide")
+    tok = None
+    with G.GGUFFile(args.tokenizer or args.model) as f:
+        if "tokenizer.ggml.tokens" in f.metadata:
+            tok = Tokenizer.from_gguf(f)
+    for p in (args.prompt or [""]):
+        before, _, after = p.partition("<audio>") if "<audio>" in p else ("", "", p)
+        if args.ids:
+            a, b = ([int(x) for x in part.replace(",", " ").split()] for part in (before, after))
+        elif tok is None:
+            sys.exit("this checkpoint carries no tokenizer: pass --ids and prompts as token ids, or --tokenizer <gguf>")
+        else:
+            a, b = tok.encode(before), tok.encode(after)
+        out = model.generate(a + b, args.max_new_tokens, soft=soft, soft_at=len(a))
+        text = tok.decode(out) if tok is not None else " ".join(map(str, out))
+        print(json.dumps({"prompt": p, "audio_tokens": soft.shape[0], "completion": text, "token_ids": out}))
+
+
 def cmd_generate(args):
     from .serve.engine import SamplingParams
+    if getattr(args, "audio", ""):
+        if not (_is_gemma4(args.model) and args.audio_model):
+            sys.exit("--audio needs a gemma4 GGUF as --model and --audio-model <checkpoint with the audio tower>")
+        return _generate_with_audio(args)
     llm = _load_llm(args)
     prompts = args.prompt or ["Hello"]
     sp = SamplingParams(max_new_tokens=args.max_new_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, seed=args.seed)
@@ -384,6 +421,8 @@ def main(argv=None):
     g.add_argument("--top-k", type=int, default=0)
     g.add_argument("--top-p", type=float, default=1.0)
     g.add_argument("--seed", type=int, default=0)
+    g.add_argument("--audio", default="", help="16 kHz WAV clip for a gemma4 model; write <audio> in the prompt where it belongs")
+    g.add_argument("--audio-model", default="", help="safetensors checkpoint holding the gemma4 audio tower")
     g.add_argument("--speculative", type=int, default=0, metavar="GAMMA",
                    help="greedy speculative decoding with prompt-lookup drafts of up to GAMMA tokens, verified in one batched step")
     g.set_defaults(fn=cmd_generate)

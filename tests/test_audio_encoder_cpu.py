@@ -162,3 +162,30 @@ def test_encode_audio_command(tmp_path, capsys, monkeypatch):
     frames = (8000 + 160 - 321) // 160 + 1
     assert line["mel_frames"] == frames and line["tokens"] == ((frames - 1) // 2) // 2 + 1 and line["features_per_token"] == 48
     assert np.load(out).shape == (line["tokens"], 48)
+
+
+def test_generate_with_an_audio_clip(tmp_path, capsys, monkeypatch):
+    """``generate --audio``: WAV -> mel -> soft tokens -> spliced into the Gemma4 prompt at ``<audio>``; equals the same steps by hand."""
+    import json
+    import struct
+    from gemm_b200 import __main__ as cli
+    from gemm_b200.models import gemma4
+    acfg = audio.Gemma4AudioConfig(hidden=64, heads=4, layers=2, ffn=128, out_dim=64, conv_channels=(8, 2))
+    audio.save_audio_checkpoint(acfg, audio.random_audio_tensors(acfg, seed=2), str(tmp_path / "aud"))
+    gcfg = gemma4.Gemma4Config(n_layers=4, hidden=64, n_heads=2, n_kv_heads=1, ffn=128, vocab=96, head_dim_full=32, head_dim_swa=32, window=8, ple_dim=8,
+                               shared_kv_layers=0, swa_pattern=[True, True, True, False], max_seq_len=128)
+    gguf = str(tmp_path / "g4.gguf")
+    gemma4.save_gguf(gcfg, gemma4.random_tensors(gcfg, seed=3), gguf, "F16")
+    n = 6400
+    pcm = (torch.sin(torch.arange(n) * 2 * math.pi * 330 / 16000) * 9000).to(torch.int16)
+    wav = tmp_path / "a.wav"
+    with open(wav, "wb") as fh:
+        fh.write(b"RIFF" + struct.pack("<I", 36 + 2 * n) + b"WAVEfmt " + struct.pack("<IHHIIHH", 16, 1, 1, 16000, 32000, 2, 16))
+        fh.write(b"data" + struct.pack("<I", 2 * n) + pcm.numpy().tobytes())
+    monkeypatch.setattr(audio, "Gemma4AudioConfig", lambda: acfg)
+    assert cli.main(["generate", "--model", gguf, "--device", "cpu", "--ids", "--audio", str(wav), "--audio-model", str(tmp_path / "aud"),
+                     "--prompt", "5 6 7 <audio> 8 9", "--max-new-tokens", "4"]) is None
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    soft = audio.Gemma4AudioEncoder.from_checkpoint(str(tmp_path / "aud"), acfg).encode_pcm(audio.wav_load(str(wav))[0])
+    want = gemma4.load_gguf(gguf, "cpu", torch.float32).generate([5, 6, 7, 8, 9], 4, soft=soft, soft_at=3)
+    assert line["token_ids"] == want and line["audio_tokens"] == soft.shape[0] > 5
